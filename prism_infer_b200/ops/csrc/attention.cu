@@ -1,0 +1,598 @@
+// Attention kernels.
+//
+//  * paged_decode_kernel: one new query token per sequence against a paged KV cache
+//    (bf16, unit-scale fp8 or scaled fp8 with one fp32 scale per token and KV head).
+//    One CTA handles ALL query heads that share a KV head (GQA packing), so every KV byte
+//    is read once instead of Hq/Hkv times, and the context is split across CTAs
+//    (split-KV) with a small combine kernel; the loop bound comes from a device array so
+//    one CUDA graph serves every context length.  Replaces the reference's Triton
+//    one-program-per-query-head kernel (prism_infer/ops/paged_decode.py:41-180).
+//  * flash_fwd_kernel: tiled online-softmax attention for prefill and for the vision
+//    tower.  Keys/values come either from contiguous bf16 rows (no history, ViT frame
+//    segments) or straight from the paged cache, including shared read-only prefix
+//    pages and scaled-fp8 pages, so chunked prefill and prefix hits no longer go through
+//    a per-sequence Python gather loop (prism_infer/ops/paged_attention_reference.py:185-390).
+//
+// Cache layout everywhere: payload [blocks][Hkv][page][D], scales [blocks][Hkv][page].
+#include "common.cuh"
+
+PRISM_DEFINE_TU_STATUS(attn)
+
+namespace {
+
+typedef __nv_bfloat16 bf16;
+
+__device__ __forceinline__ float2 fp8x2_to_float2(unsigned short v) {
+  const __half2_raw h = __nv_cvt_fp8x2_to_halfraw2((__nv_fp8x2_storage_t)v, __NV_E4M3);
+  return __half22float2(*reinterpret_cast<const __half2*>(&h));
+}
+
+// =====================================================================================
+// Decode
+// =====================================================================================
+struct DecodeArgs {
+  const bf16* q;            // [B][Hq][D]
+  const void* k_cache;
+  const void* v_cache;
+  const float* k_scale;     // null unless scaled fp8
+  const float* v_scale;
+  const int* block_tables;  // [B][max_blocks], < 0 = hole
+  const int* context_lens;  // [B]
+  float* part_o;            // [B][Hq][nsplit][D]
+  float* part_ml;           // [B][Hq][nsplit][2]  (max, sum)
+  bf16* out;                // [B][Hq][D] (written directly when nsplit == 1)
+  int Hq, Hkv, page, max_blocks, nsplit;
+  float scale;
+};
+
+// KV8 = true: fp8 payload (16 elements per lane), false: bf16 payload (8 elements per lane)
+template <int D, int G, bool KV8>
+__global__ void __launch_bounds__(128) paged_decode_kernel(const DecodeArgs a) {
+  constexpr int EPL = KV8 ? 16 : 8;   // elements per lane
+  constexpr int LPT = D / EPL;        // lanes per token
+  constexpr int TPW = 32 / LPT;       // tokens per warp iteration
+  constexpr int NWARP = 4;
+  const int b = blockIdx.x, kvh = blockIdx.y, split = blockIdx.z;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int slot = lane / LPT;        // token slot inside the warp
+  const int part = lane % LPT;        // which EPL-wide slice of the head dim
+  pdl_launch_dependents();
+  pdl_wait();
+  const int ctx = a.context_lens[b];
+  const int per_split = ((ctx + a.nsplit - 1) / a.nsplit + TPW * NWARP - 1) / (TPW * NWARP) * (TPW * NWARP);
+  const int j_begin = split * per_split;
+  const int j_end = min(ctx, j_begin + per_split);
+
+  float q[G][EPL];
+#pragma unroll
+  for (int g = 0; g < G; ++g) {
+    const bf16* qp = a.q + ((size_t)b * a.Hq + (size_t)kvh * G + g) * D + part * EPL;
+#pragma unroll
+    for (int e = 0; e < EPL; ++e) q[g][e] = __bfloat162float(qp[e]) * a.scale;
+  }
+  float m[G], l[G], acc[G][EPL];
+#pragma unroll
+  for (int g = 0; g < G; ++g) {
+    m[g] = -INFINITY;
+    l[g] = 0.0f;
+#pragma unroll
+    for (int e = 0; e < EPL; ++e) acc[g][e] = 0.0f;
+  }
+  const int* bt = a.block_tables + (size_t)b * a.max_blocks;
+
+  for (int j0 = j_begin + warp * TPW; j0 < j_end; j0 += TPW * NWARP) {
+    const int j = j0 + slot;
+    int blk = -1;
+    if (j < j_end) blk = bt[j / a.page];
+    const bool valid = blk >= 0;
+    float kf[EPL], vf[EPL];
+    float ks = 1.0f, vs = 1.0f;
+    if (valid) {
+      const size_t row = ((size_t)blk * a.Hkv + kvh) * a.page + (j % a.page);
+      if (KV8) {
+        const uint4 kr = *reinterpret_cast<const uint4*>(reinterpret_cast<const uint8_t*>(a.k_cache) + row * D + part * 16);
+        const uint4 vr = *reinterpret_cast<const uint4*>(reinterpret_cast<const uint8_t*>(a.v_cache) + row * D + part * 16);
+        const unsigned short* kp = reinterpret_cast<const unsigned short*>(&kr);
+        const unsigned short* vp = reinterpret_cast<const unsigned short*>(&vr);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+          const float2 kk = fp8x2_to_float2(kp[e]);
+          const float2 vv = fp8x2_to_float2(vp[e]);
+          kf[2 * e] = kk.x;
+          kf[2 * e + 1] = kk.y;
+          vf[2 * e] = vv.x;
+          vf[2 * e + 1] = vv.y;
+        }
+        if (a.k_scale != nullptr) {
+          ks = a.k_scale[row];
+          vs = a.v_scale[row];
+        }
+      } else {
+        const uint4 kr = *reinterpret_cast<const uint4*>(reinterpret_cast<const bf16*>(a.k_cache) + row * D + part * 8);
+        const uint4 vr = *reinterpret_cast<const uint4*>(reinterpret_cast<const bf16*>(a.v_cache) + row * D + part * 8);
+        const __nv_bfloat162* kp = reinterpret_cast<const __nv_bfloat162*>(&kr);
+        const __nv_bfloat162* vp = reinterpret_cast<const __nv_bfloat162*>(&vr);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float2 kk = __bfloat1622float2(kp[e]);
+          const float2 vv = __bfloat1622float2(vp[e]);
+          kf[2 * e] = kk.x;
+          kf[2 * e + 1] = kk.y;
+          vf[2 * e] = vv.x;
+          vf[2 * e + 1] = vv.y;
+        }
+      }
+    } else {
+#pragma unroll
+      for (int e = 0; e < EPL; ++e) {
+        kf[e] = 0.0f;
+        vf[e] = 0.0f;
+      }
+    }
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+      float s = 0.0f;
+#pragma unroll
+      for (int e = 0; e < EPL; ++e) s += q[g][e] * kf[e];
+#pragma unroll
+      for (int o = LPT / 2; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+      if (valid) {
+        s *= ks;
+        const float mn = fmaxf(m[g], s);
+        const float corr = __expf(m[g] - mn);
+        const float p = __expf(s - mn);
+        l[g] = l[g] * corr + p;
+        const float pv = p * vs;
+#pragma unroll
+        for (int e = 0; e < EPL; ++e) acc[g][e] = acc[g][e] * corr + pv * vf[e];
+        m[g] = mn;
+      }
+    }
+  }
+  // merge the TPW token slots of the warp
+#pragma unroll
+  for (int g = 0; g < G; ++g) {
+#pragma unroll
+    for (int o = LPT; o < 32; o <<= 1) {
+      const float mo = __shfl_xor_sync(0xffffffffu, m[g], o);
+      const float lo = __shfl_xor_sync(0xffffffffu, l[g], o);
+      const float mn = fmaxf(m[g], mo);
+      const float c0 = (m[g] == -INFINITY) ? 0.0f : __expf(m[g] - mn);
+      const float c1 = (mo == -INFINITY) ? 0.0f : __expf(mo - mn);
+      l[g] = l[g] * c0 + lo * c1;
+#pragma unroll
+      for (int e = 0; e < EPL; ++e) {
+        const float ao = __shfl_xor_sync(0xffffffffu, acc[g][e], o);
+        acc[g][e] = acc[g][e] * c0 + ao * c1;
+      }
+      m[g] = mn;
+    }
+  }
+  // merge the warps through shared memory
+  __shared__ float s_m[NWARP][G], s_l[NWARP][G];
+  __shared__ float s_acc[NWARP][G][D];
+  if (slot == 0) {
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+      if (part == 0) {
+        s_m[warp][g] = m[g];
+        s_l[warp][g] = l[g];
+      }
+#pragma unroll
+      for (int e = 0; e < EPL; ++e) s_acc[warp][g][part * EPL + e] = acc[g][e];
+    }
+  }
+  __syncthreads();
+  for (int idx = threadIdx.x; idx < G * D; idx += blockDim.x) {
+    const int g = idx / D, d = idx % D;
+    float mm = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < NWARP; ++w) mm = fmaxf(mm, s_m[w][g]);
+    float ll = 0.0f, oo = 0.0f;
+#pragma unroll
+    for (int w = 0; w < NWARP; ++w) {
+      const float c = (s_m[w][g] == -INFINITY) ? 0.0f : __expf(s_m[w][g] - mm);
+      ll += s_l[w][g] * c;
+      oo += s_acc[w][g][d] * c;
+    }
+    const int hq = kvh * G + g;
+    if (a.nsplit == 1) {
+      a.out[((size_t)b * a.Hq + hq) * D + d] = __float2bfloat16_rn(ll > 0.0f ? oo / ll : 0.0f);
+    } else {
+      const size_t pidx = ((size_t)b * a.Hq + hq) * a.nsplit + split;
+      a.part_o[pidx * D + d] = oo;
+      if (d == 0) {
+        a.part_ml[pidx * 2] = mm;
+        a.part_ml[pidx * 2 + 1] = ll;
+      }
+    }
+  }
+}
+
+__global__ void __launch_bounds__(128) decode_combine_kernel(const float* part_o, const float* part_ml, bf16* out,
+                                                             int nsplit, int D) {
+  const size_t bh = blockIdx.x;  // b * Hq + hq
+  pdl_launch_dependents();
+  pdl_wait();
+  float mm = -INFINITY;
+  for (int s = 0; s < nsplit; ++s) mm = fmaxf(mm, part_ml[(bh * nsplit + s) * 2]);
+  for (int d = threadIdx.x; d < D; d += blockDim.x) {
+    float ll = 0.0f, oo = 0.0f;
+    for (int s = 0; s < nsplit; ++s) {
+      const float ms = part_ml[(bh * nsplit + s) * 2];
+      const float c = (ms == -INFINITY) ? 0.0f : __expf(ms - mm);
+      ll += part_ml[(bh * nsplit + s) * 2 + 1] * c;
+      oo += part_o[(bh * nsplit + s) * D + d] * c;
+    }
+    out[bh * D + d] = __float2bfloat16_rn(ll > 0.0f ? oo / ll : 0.0f);
+  }
+}
+
+// =====================================================================================
+// Prefill / vision: tiled online-softmax attention on mma.sync m16n8k16 (bf16).
+// The GEMM-heavy part of prefill lives in the tcgen05 kernels; this kernel is the
+// memory-format adapter (paged / fp8 / ragged segments) around a 64x64 tile loop.
+// =====================================================================================
+struct FlashArgs {
+  const bf16* q;            // token-major, q_stride elements per token, heads packed with HD_REAL
+  long long q_stride;
+  bf16* out;                // [T][Hq][HD_REAL]
+  long long o_stride;
+  const int* cu_q;          // [S+1]
+  // contiguous K/V (mode 0)
+  const bf16* k;
+  const bf16* v;
+  long long kv_stride;
+  // paged K/V (mode 1 bf16, mode 2 fp8)
+  const void* k_cache;
+  const void* v_cache;
+  const float* k_scale;
+  const float* v_scale;
+  const int* block_tables;
+  const int* kv_lens;       // [S] total keys visible to the sequence (history + this chunk)
+  int max_blocks, page;
+  int Hq, Hkv;
+  int causal;
+  float scale;
+};
+
+__device__ __forceinline__ void ldsm_x4(uint32_t (&r)[4], uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(addr));
+}
+__device__ __forceinline__ void ldsm_x4_t(uint32_t (&r)[4], uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(addr));
+}
+__device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+
+template <int HD, int HD_REAL, int MODE>
+__global__ void __launch_bounds__(128) flash_fwd_kernel(const FlashArgs a) {
+  constexpr int BM = 64, BN = 64;
+  constexpr int LDS = HD + 8;          // padded row (elements) -> conflict-free ldmatrix
+  constexpr int CHUNKS = HD_REAL / 8;  // 8-element chunks per row
+  extern __shared__ __align__(16) uint8_t fsm[];
+  bf16* Qs = reinterpret_cast<bf16*>(fsm);
+  bf16* Ks = Qs + BM * LDS;
+  bf16* Vs = Ks + BN * LDS;
+
+  const int seq = blockIdx.z, head = blockIdx.y, qt = blockIdx.x;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int g = lane >> 2, t4 = lane & 3;
+  pdl_launch_dependents();
+  pdl_wait();
+  const int q_start = a.cu_q[seq];
+  const int q_len = a.cu_q[seq + 1] - q_start;
+  const int q0 = qt * BM;
+  if (q0 >= q_len) return;
+  const int kv_len = (MODE == 0) ? q_len : a.kv_lens[seq];
+  const int kvh = head / (a.Hq / a.Hkv);
+  const int pos_off = kv_len - q_len;  // absolute key position of local query 0
+
+  // zero the padding columns once (HD_REAL < HD only for the 72-wide vision heads)
+  if constexpr (HD_REAL < HD) {
+    for (int i = tid; i < (BM + 2 * BN) * (HD - HD_REAL); i += 128) {
+      const int r = i / (HD - HD_REAL), c = HD_REAL + i % (HD - HD_REAL);
+      Qs[r * LDS + c] = __float2bfloat16(0.0f);  // Qs, Ks, Vs are contiguous with the same pitch
+    }
+  }
+  // Q tile
+  for (int i = tid; i < BM * CHUNKS; i += 128) {
+    const int r = i / CHUNKS, c = i % CHUNKS;
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (q0 + r < q_len)
+      v = *reinterpret_cast<const uint4*>(a.q + (size_t)(q_start + q0 + r) * a.q_stride + (size_t)head * HD_REAL + c * 8);
+    *reinterpret_cast<uint4*>(Qs + r * LDS + c * 8) = v;
+  }
+  __syncthreads();
+  uint32_t qf[HD / 16][4];
+  {
+    const int r = warp * 16 + (lane & 7) + 8 * ((lane >> 3) & 1);
+    const int c = 8 * (lane >> 4);
+#pragma unroll
+    for (int kk = 0; kk < HD / 16; ++kk) ldsm_x4(qf[kk], smem_u32(Qs + r * LDS + kk * 16 + c));
+  }
+  float o[HD / 8][4];
+#pragma unroll
+  for (int i = 0; i < HD / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.0f;
+  float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.0f, 0.0f};
+  const float sl2 = a.scale * 1.4426950408889634f;
+
+  int kv_end = kv_len;
+  if (a.causal) kv_end = min(kv_len, pos_off + min(q0 + BM, q_len));
+  const int n_tiles = (kv_end + BN - 1) / BN;
+  const int* bt = (MODE == 0) ? nullptr : a.block_tables + (size_t)seq * a.max_blocks;
+
+  for (int tile = 0; tile < n_tiles; ++tile) {
+    const int j0 = tile * BN;
+    __syncthreads();  // previous tile fully consumed
+    for (int i = tid; i < BN * CHUNKS; i += 128) {
+      const int r = i / CHUNKS, c = i % CHUNKS;
+      const int j = j0 + r;
+      uint4 kv4 = make_uint4(0, 0, 0, 0), vv4 = make_uint4(0, 0, 0, 0);
+      if (j < kv_len) {
+        if (MODE == 0) {
+          const size_t off = (size_t)(q_start + j) * a.kv_stride + (size_t)kvh * HD_REAL + c * 8;
+          kv4 = *reinterpret_cast<const uint4*>(a.k + off);
+          vv4 = *reinterpret_cast<const uint4*>(a.v + off);
+        } else {
+          const int blk = bt[j / a.page];
+          if (blk >= 0) {
+            const size_t row = ((size_t)blk * a.Hkv + kvh) * a.page + (j % a.page);
+            if (MODE == 1) {
+              kv4 = *reinterpret_cast<const uint4*>(reinterpret_cast<const bf16*>(a.k_cache) + row * HD_REAL + c * 8);
+              vv4 = *reinterpret_cast<const uint4*>(reinterpret_cast<const bf16*>(a.v_cache) + row * HD_REAL + c * 8);
+            } else {
+              const uint2 k8 = *reinterpret_cast<const uint2*>(reinterpret_cast<const uint8_t*>(a.k_cache) + row * HD_REAL + c * 8);
+              const uint2 v8 = *reinterpret_cast<const uint2*>(reinterpret_cast<const uint8_t*>(a.v_cache) + row * HD_REAL + c * 8);
+              const float ks = a.k_scale ? a.k_scale[row] : 1.0f;
+              const float vs = a.v_scale ? a.v_scale[row] : 1.0f;
+              const unsigned short* kp = reinterpret_cast<const unsigned short*>(&k8);
+              const unsigned short* vp = reinterpret_cast<const unsigned short*>(&v8);
+              uint32_t* ko = reinterpret_cast<uint32_t*>(&kv4);
+              uint32_t* vo = reinterpret_cast<uint32_t*>(&vv4);
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                const float2 kk = fp8x2_to_float2(kp[e]);
+                const float2 vv = fp8x2_to_float2(vp[e]);
+                ko[e] = pack_bf16(kk.x * ks, kk.y * ks);
+                vo[e] = pack_bf16(vv.x * vs, vv.y * vs);
+              }
+            }
+          }
+        }
+      }
+      *reinterpret_cast<uint4*>(Ks + r * LDS + c * 8) = kv4;
+      *reinterpret_cast<uint4*>(Vs + r * LDS + c * 8) = vv4;
+    }
+    __syncthreads();
+
+    // S = Q K^T  (16 x 64 per warp)
+    float s[BN / 8][4];
+#pragma unroll
+    for (int i = 0; i < BN / 8; ++i) s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.0f;
+#pragma unroll
+    for (int kk = 0; kk < HD / 16; ++kk) {
+#pragma unroll
+      for (int np = 0; np < BN / 16; ++np) {
+        uint32_t kb[4];
+        const int n = np * 16 + (lane & 7) + 8 * (lane >> 4);
+        const int c = kk * 16 + 8 * ((lane >> 3) & 1);
+        ldsm_x4(kb, smem_u32(Ks + n * LDS + c));
+        mma_bf16(s[2 * np], qf[kk], kb[0], kb[1]);
+        mma_bf16(s[2 * np + 1], qf[kk], kb[2], kb[3]);
+      }
+    }
+    // mask + online softmax (rows g and g+8 of this warp's 16-row slab)
+    const int row0 = q0 + warp * 16 + g;
+    const bool need_mask = (j0 + BN > kv_len) || (a.causal && (j0 + BN - 1 > pos_off + q0 + warp * 16));
+    float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+    for (int i = 0; i < BN / 8; ++i) {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        float v = s[i][e] * sl2;
+        if (need_mask) {
+          const int col = j0 + i * 8 + t4 * 2 + (e & 1);
+          const int row = row0 + ((e >> 1) ? 8 : 0);
+          if (col >= kv_len || (a.causal && col > pos_off + row)) v = -INFINITY;
+        }
+        s[i][e] = v;
+        mx[e >> 1] = fmaxf(mx[e >> 1], v);
+      }
+    }
+    float corr[2], m_use[2];
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
+      mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
+      const float mn = fmaxf(m_run[r], mx[r]);
+      m_use[r] = (mn == -INFINITY) ? 0.0f : mn;
+      corr[r] = (m_run[r] == -INFINITY) ? 0.0f : exp2f(m_run[r] - m_use[r]);
+      m_run[r] = mn;
+    }
+    float rs[2] = {0.0f, 0.0f};
+#pragma unroll
+    for (int i = 0; i < BN / 8; ++i) {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float p = exp2f(s[i][e] - m_use[e >> 1]);
+        s[i][e] = p;
+        rs[e >> 1] += p;
+      }
+    }
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      rs[r] += __shfl_xor_sync(0xffffffffu, rs[r], 1);
+      rs[r] += __shfl_xor_sync(0xffffffffu, rs[r], 2);
+      l_run[r] = l_run[r] * corr[r] + rs[r];
+    }
+#pragma unroll
+    for (int i = 0; i < HD / 8; ++i) {
+      o[i][0] *= corr[0];
+      o[i][1] *= corr[0];
+      o[i][2] *= corr[1];
+      o[i][3] *= corr[1];
+    }
+    // O += P V
+#pragma unroll
+    for (int kt = 0; kt < BN / 16; ++kt) {
+      uint32_t pa[4];
+      pa[0] = pack_bf16(s[2 * kt][0], s[2 * kt][1]);
+      pa[1] = pack_bf16(s[2 * kt][2], s[2 * kt][3]);
+      pa[2] = pack_bf16(s[2 * kt + 1][0], s[2 * kt + 1][1]);
+      pa[3] = pack_bf16(s[2 * kt + 1][2], s[2 * kt + 1][3]);
+#pragma unroll
+      for (int dp = 0; dp < HD / 16; ++dp) {
+        uint32_t vb[4];
+        const int tok = kt * 16 + (lane & 7) + 8 * ((lane >> 3) & 1);
+        const int d = dp * 16 + 8 * (lane >> 4);
+        ldsm_x4_t(vb, smem_u32(Vs + tok * LDS + d));
+        mma_bf16(o[2 * dp], pa, vb[0], vb[1]);
+        mma_bf16(o[2 * dp + 1], pa, vb[2], vb[3]);
+      }
+    }
+  }
+  // normalise and store
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    const int row = q0 + warp * 16 + g + 8 * r;
+    if (row >= q_len) continue;
+    const float inv = l_run[r] > 0.0f ? 1.0f / l_run[r] : 0.0f;
+    bf16* dst = a.out + (size_t)(q_start + row) * a.o_stride + (size_t)head * HD_REAL;
+#pragma unroll
+    for (int i = 0; i < HD / 8; ++i) {
+      const int d = i * 8 + t4 * 2;
+      if (d < HD_REAL) {
+        *reinterpret_cast<__nv_bfloat162*>(dst + d) = __floats2bfloat162_rn(o[i][2 * r] * inv, o[i][2 * r + 1] * inv);
+      }
+    }
+  }
+}
+
+template <int HD, int HD_REAL, int MODE>
+int launch_flash(const FlashArgs& a, int max_q_tiles, int S, cudaStream_t stream, bool pdl) {
+  const size_t smem = (size_t)(64 + 2 * 64) * (HD + 8) * sizeof(bf16);
+  static bool configured = false;
+  if (!configured && smem > 48 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(flash_fwd_kernel<HD, HD_REAL, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+    configured = true;
+  }
+  return (int)prism_launch(flash_fwd_kernel<HD, HD_REAL, MODE>, dim3(max_q_tiles, a.Hq, S), dim3(128), smem, stream, pdl, a);
+}
+
+template <int MODE>
+int dispatch_flash(const FlashArgs& a, int hd, int max_q_tiles, int S, cudaStream_t stream, bool pdl) {
+  switch (hd) {
+    case 128: return launch_flash<128, 128, MODE>(a, max_q_tiles, S, stream, pdl);
+    case 64: return launch_flash<64, 64, MODE>(a, max_q_tiles, S, stream, pdl);
+    case 72: return launch_flash<80, 72, MODE>(a, max_q_tiles, S, stream, pdl);
+    case 32: return launch_flash<32, 32, MODE>(a, max_q_tiles, S, stream, pdl);
+  }
+  return -2;
+}
+
+template <int D, bool KV8>
+int dispatch_decode(const DecodeArgs& a, int B, cudaStream_t stream, bool pdl) {
+  dim3 grid(B, a.Hkv, a.nsplit), block(128);
+  switch (a.Hq / a.Hkv) {
+    case 1: return (int)prism_launch(paged_decode_kernel<D, 1, KV8>, grid, block, 0, stream, pdl, a);
+    case 2: return (int)prism_launch(paged_decode_kernel<D, 2, KV8>, grid, block, 0, stream, pdl, a);
+    case 4: return (int)prism_launch(paged_decode_kernel<D, 4, KV8>, grid, block, 0, stream, pdl, a);
+    case 8: return (int)prism_launch(paged_decode_kernel<D, 8, KV8>, grid, block, 0, stream, pdl, a);
+  }
+  return -3;
+}
+
+}  // namespace
+
+// kv_mode: 0 bf16, 1 fp8 unit scale, 2 scaled fp8.  part_o / part_ml are scratch of
+// B*Hq*nsplit*D and B*Hq*nsplit*2 floats (unused when nsplit == 1).
+PRISM_API int prism_paged_decode(const void* q, const void* k_cache, const void* v_cache, const void* k_scale,
+                                 const void* v_scale, const void* block_tables, const void* context_lens, void* part_o,
+                                 void* part_ml, void* out, int B, int Hq, int Hkv, int D, int page, int max_blocks,
+                                 int nsplit, int kv_mode, float scale, void* stream, int pdl) {
+  if (B <= 0) return 0;
+  if (Hq % Hkv) return -1;
+  DecodeArgs a;
+  a.q = (const bf16*)q;
+  a.k_cache = k_cache;
+  a.v_cache = v_cache;
+  a.k_scale = kv_mode == 2 ? (const float*)k_scale : nullptr;
+  a.v_scale = kv_mode == 2 ? (const float*)v_scale : nullptr;
+  a.block_tables = (const int*)block_tables;
+  a.context_lens = (const int*)context_lens;
+  a.part_o = (float*)part_o;
+  a.part_ml = (float*)part_ml;
+  a.out = (bf16*)out;
+  a.Hq = Hq;
+  a.Hkv = Hkv;
+  a.page = page;
+  a.max_blocks = max_blocks;
+  a.nsplit = nsplit < 1 ? 1 : nsplit;
+  a.scale = scale;
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  int rc;
+  if (D == 128) rc = kv_mode ? dispatch_decode<128, true>(a, B, s, pdl != 0) : dispatch_decode<128, false>(a, B, s, pdl != 0);
+  else if (D == 64) rc = kv_mode ? dispatch_decode<64, true>(a, B, s, pdl != 0) : dispatch_decode<64, false>(a, B, s, pdl != 0);
+  else return -2;
+  if (rc) return rc;
+  if (a.nsplit > 1) {
+    rc = (int)prism_launch(decode_combine_kernel, dim3(B * Hq), dim3(128), 0, s, pdl != 0, (const float*)part_o,
+                           (const float*)part_ml, (bf16*)out, a.nsplit, D);
+  }
+  return rc;
+}
+
+// mode 0: contiguous bf16 K/V rows (k, v, kv_stride); mode 1: paged bf16; mode 2: paged fp8
+// (k_scale/v_scale may be null for unit scale).  cu_q has S+1 entries.
+PRISM_API int prism_flash_attention(const void* q, long long q_stride, void* out, long long o_stride, const void* cu_q,
+                                    const void* k, const void* v, long long kv_stride, const void* k_cache,
+                                    const void* v_cache, const void* k_scale, const void* v_scale,
+                                    const void* block_tables, const void* kv_lens, int max_blocks, int page, int S,
+                                    int max_q_len, int Hq, int Hkv, int hd, int mode, int causal, float scale,
+                                    void* stream, int pdl) {
+  if (S <= 0 || max_q_len <= 0) return 0;
+  if (Hq % Hkv) return -1;
+  FlashArgs a;
+  a.q = (const bf16*)q;
+  a.q_stride = q_stride;
+  a.out = (bf16*)out;
+  a.o_stride = o_stride;
+  a.cu_q = (const int*)cu_q;
+  a.k = (const bf16*)k;
+  a.v = (const bf16*)v;
+  a.kv_stride = kv_stride;
+  a.k_cache = k_cache;
+  a.v_cache = v_cache;
+  a.k_scale = (const float*)k_scale;
+  a.v_scale = (const float*)v_scale;
+  a.block_tables = (const int*)block_tables;
+  a.kv_lens = (const int*)kv_lens;
+  a.max_blocks = max_blocks;
+  a.page = page;
+  a.Hq = Hq;
+  a.Hkv = Hkv;
+  a.causal = causal;
+  a.scale = scale;
+  const int tiles = (max_q_len + 63) / 64;
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  switch (mode) {
+    case 0: return dispatch_flash<0>(a, hd, tiles, S, s, pdl != 0);
+    case 1: return dispatch_flash<1>(a, hd, tiles, S, s, pdl != 0);
+    case 2: return dispatch_flash<2>(a, hd, tiles, S, s, pdl != 0);
+  }
+  return -3;
+}

@@ -1,0 +1,388 @@
+// Weight-stationary-in-M GEMM family for sm_100a:  D[feature, token] = W[feature, :] . X[token, :]
+//
+// Every linear layer of the engine goes through this one kernel.  The weight matrix
+// (nn.Linear layout [out_features, in_features], i.e. K-major) is the tcgen05 A operand
+// with a fixed 128-row tile; the activations [tokens, in_features] (also K-major) are the
+// B operand with a token tile BN in {16, 32, 64, 128, 256}.  A decode step with a handful
+// of tokens therefore issues the same 128 x BN x 16 UMMA as a 2048-token prefill chunk;
+// only BN, split-K and the pipeline depth change.  Both operands are staged by TMA
+// (cp.async.bulk.tensor.2d, 128-byte swizzle, no cluster qualifier) into a ring of
+// shared-memory stages; one elected thread issues tcgen05.mma into a TMEM accumulator and
+// four epilogue warps read it back with tcgen05.ld.
+//
+// Epilogues: bias (per feature), GELU (tanh or erf), residual add, bf16 store
+// out[token][feature]; fp32 split-K partials part[split][token][feature]; and the dual
+// form (two weight tiles per stage, two accumulators) that writes
+// silu(gate) * up directly, which replaces the reference's CUTLASS DualGemm
+// (prism_infer/ops/csrc/cutlass_dual_gemm_swiglu.cu:85-215, mma.sync Sm80) and every
+// F.linear of prism_infer/layers/linear.py:62-190.
+//
+// Programmatic dependent launch: the producer thread prefetches the first ring of weight
+// tiles (which never depend on the previous kernel) before griddepcontrol.wait, then
+// loads activations.
+#include <mutex>
+#include <unordered_map>
+
+#include "common.cuh"
+
+PRISM_DEFINE_TU_STATUS(gemm)
+
+namespace {
+
+constexpr int BM = 128;
+constexpr int BK = 64;
+constexpr int UMMA_K = 16;
+constexpr int W_TILE_BYTES = BM * BK * 2;
+constexpr int GEMM_THREADS = 192;
+constexpr int SMEM_LIMIT = 232448;  // 227 KB
+
+struct GemmArgs {
+  int M;             // valid weight rows (features)
+  int T;             // valid tokens
+  int kb_total;      // ceil(K / 64)
+  int kb_per_split;  // k-blocks handled by one blockIdx.z
+  int w2_row_off;    // dual: first row of the second weight matrix inside the same tensor map
+  int stages;
+  int out_f32;       // 1: fp32 partial output, one slab per split
+  int act;           // 0 none, 1 gelu(tanh), 2 gelu(erf)
+  long long ldo;     // output row stride (elements)
+  long long ldr;     // residual row stride (elements)
+  long long split_stride;  // elements between split slabs
+  const __nv_bfloat16* bias;
+  const __nv_bfloat16* residual;
+  void* out;
+};
+
+template <int BN, bool DUAL>
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
+gemm_wx_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX, const GemmArgs a) {
+  constexpr int X_TILE_BYTES = BN * BK * 2;
+  constexpr int W_STAGE_BYTES = W_TILE_BYTES * (DUAL ? 2 : 1);
+  constexpr int STAGE_BYTES = W_STAGE_BYTES + X_TILE_BYTES;
+  constexpr int ACC_COLS = DUAL ? 2 * BN : BN;
+  constexpr int TMEM_COLS = ACC_COLS < 32 ? 32 : ACC_COLS;  // power of two by construction
+  constexpr uint32_t IDESC = umma_idesc_bf16(BM, BN);
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  const int stages = a.stages;
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + (size_t)stages * STAGE_BYTES);
+  uint64_t* empty = full + stages;
+  uint64_t* tmem_full = empty + stages;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_full + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int m0 = blockIdx.x * BM;
+  const int n0 = blockIdx.y * BN;
+  const int split = blockIdx.z;
+  const int kb_begin = split * a.kb_per_split;
+  const int kb_end = min(a.kb_total, kb_begin + a.kb_per_split);
+  const int num_kb = kb_end - kb_begin;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < stages; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 1);
+    }
+    mbar_init(tmem_full, 1);
+    fence_barrier_init();
+    tma_prefetch_desc(&tmW);
+    tma_prefetch_desc(&tmX);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  pdl_launch_dependents();
+
+  if (warp == 0) {
+    if (lane == 0) {
+      // ------------------------------ TMA producer ------------------------------
+      const int pre = min(stages, num_kb);
+      for (int i = 0; i < pre; ++i) {
+        uint8_t* st = smem + (size_t)i * STAGE_BYTES;
+        mbar_expect_tx(&full[i], STAGE_BYTES);
+        tma_load_2d(st, &tmW, &full[i], (kb_begin + i) * BK, m0);
+        if (DUAL) tma_load_2d(st + W_TILE_BYTES, &tmW, &full[i], (kb_begin + i) * BK, a.w2_row_off + m0);
+      }
+      pdl_wait();  // activations come from the previous kernel
+      for (int i = 0; i < pre; ++i) {
+        uint8_t* st = smem + (size_t)i * STAGE_BYTES;
+        tma_load_2d(st + W_STAGE_BYTES, &tmX, &full[i], (kb_begin + i) * BK, n0);
+      }
+      int issued = pre;
+      bool ok = true;
+      for (int kb = pre; kb < num_kb && ok; ++kb) {
+        const int s = kb % stages;
+        const uint32_t round = kb / stages;
+        ok = mbar_wait(&empty[s], (round - 1) & 1, 1);
+        if (!ok) break;
+        uint8_t* st = smem + (size_t)s * STAGE_BYTES;
+        mbar_expect_tx(&full[s], STAGE_BYTES);
+        tma_load_2d(st, &tmW, &full[s], (kb_begin + kb) * BK, m0);
+        if (DUAL) tma_load_2d(st + W_TILE_BYTES, &tmW, &full[s], (kb_begin + kb) * BK, a.w2_row_off + m0);
+        tma_load_2d(st + W_STAGE_BYTES, &tmX, &full[s], (kb_begin + kb) * BK, n0);
+        issued = kb + 1;
+      }
+      if (!ok) {
+        // Unwinding after a timed-out wait: let copies already in flight land before the
+        // CTA's shared memory is released.
+        for (int kb = max(0, issued - stages); kb < issued; ++kb) {
+          (void)mbar_wait(&full[kb % stages], (kb / stages) & 1, 4);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      // ------------------------------ MMA issuer ------------------------------
+      bool ok = true;
+      for (int kb = 0; kb < num_kb; ++kb) {
+        const int s = kb % stages;
+        ok = mbar_wait(&full[s], (kb / stages) & 1, 2);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t st = smem_u32(smem + (size_t)s * STAGE_BYTES);
+        const uint64_t da = umma_desc_sw128(st);
+        const uint64_t db = umma_desc_sw128(st + W_STAGE_BYTES);
+#pragma unroll
+        for (int k = 0; k < BK / UMMA_K; ++k) {
+          const uint32_t acc = (kb | k) != 0;
+          tc_mma_f16(tmem_base, da + 2 * k, db + 2 * k, IDESC, acc);
+          if (DUAL) {
+            const uint64_t da2 = umma_desc_sw128(st + W_TILE_BYTES);
+            tc_mma_f16(tmem_base + BN, da2 + 2 * k, db + 2 * k, IDESC, acc);
+          }
+        }
+        tc_commit(&empty[s]);
+      }
+      if (ok) tc_commit(tmem_full);
+    }
+  } else {
+    // ------------------------------ epilogue warps 2..5 ------------------------------
+    const int q = warp & 3;  // TMEM lane quarter this warp may read
+    pdl_wait();
+    if (mbar_wait(tmem_full, 0, 3)) {
+      tc_fence_after();
+      const int m = m0 + q * 32 + lane;
+      const bool m_ok = m < a.M;
+      const float bias_v = (a.bias != nullptr && m_ok) ? __bfloat162float(a.bias[m]) : 0.0f;
+      const uint32_t t_lane = tmem_base + ((uint32_t)(q * 32) << 16);
+      float* out_f = reinterpret_cast<float*>(a.out) + (size_t)split * a.split_stride;
+      __nv_bfloat16* out_b = reinterpret_cast<__nv_bfloat16*>(a.out);
+      for (int c0 = 0; c0 < BN; c0 += 16) {
+        if (n0 + c0 >= a.T) break;
+        uint32_t r[16];
+        uint32_t r2[16];
+        tmem_ld16(t_lane + c0, r);
+        if (DUAL) tmem_ld16(t_lane + BN + c0, r2);
+        tmem_ld_wait();
+        if (m_ok) {
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            const int n = n0 + c0 + j;
+            if (n < a.T) {
+              float v = __uint_as_float(r[j]);
+              if (DUAL) {
+                // rounding points follow the eager bf16 graph: silu(gate) -> bf16, * up -> bf16
+                const float g = bf16_round(__uint_as_float(r[j]));
+                const float u = bf16_round(__uint_as_float(r2[j]));
+                v = bf16_round(silu(g)) * u;
+                out_b[(size_t)n * a.ldo + m] = __float2bfloat16_rn(v);
+              } else if (a.out_f32) {
+                out_f[(size_t)n * a.ldo + m] = v;
+              } else {
+                v += bias_v;
+                if (a.act == 1) v = gelu_tanh(v);
+                else if (a.act == 2) v = gelu_erf(v);
+                if (a.residual != nullptr) v = bf16_round(v) + __bfloat162float(a.residual[(size_t)n * a.ldr + m]);
+                out_b[(size_t)n * a.ldo + m] = __float2bfloat16_rn(v);
+              }
+            }
+          }
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) tmem_dealloc(tmem_base, TMEM_COLS);
+}
+
+// ------------------------------------------------------------------------------------
+// Host side: tensor-map cache and launcher.
+// ------------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn get_encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess) {
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+    }
+  });
+  return fn;
+}
+
+struct MapKey {
+  const void* ptr;
+  unsigned long long rows, cols, ld;
+  unsigned box_rows;
+  bool operator==(const MapKey& o) const {
+    return ptr == o.ptr && rows == o.rows && cols == o.cols && ld == o.ld && box_rows == o.box_rows;
+  }
+};
+struct MapKeyHash {
+  size_t operator()(const MapKey& k) const {
+    size_t h = reinterpret_cast<size_t>(k.ptr);
+    h ^= k.rows * 0x9E3779B97F4A7C15ull + (h << 6) + (h >> 2);
+    h ^= k.cols * 0xC2B2AE3D27D4EB4Full + (h << 6) + (h >> 2);
+    h ^= k.ld * 0x165667B19E3779F9ull + (h << 6) + (h >> 2);
+    h ^= k.box_rows * 0x27D4EB2F165667C5ull;
+    return h;
+  }
+};
+
+std::mutex g_map_mutex;
+std::unordered_map<MapKey, CUtensorMap, MapKeyHash> g_maps;
+
+// A [rows, cols] bf16 row-major matrix with row stride ld (elements); box = box_rows x 64.
+int get_tensor_map(const void* ptr, unsigned long long rows, unsigned long long cols, unsigned long long ld,
+                   unsigned box_rows, CUtensorMap* out) {
+  MapKey key{ptr, rows, cols, ld, box_rows};
+  std::lock_guard<std::mutex> lock(g_map_mutex);
+  auto it = g_maps.find(key);
+  if (it != g_maps.end()) {
+    *out = it->second;
+    return 0;
+  }
+  EncodeTiledFn fn = get_encode_fn();
+  if (!fn) return -100;
+  if ((reinterpret_cast<uintptr_t>(ptr) & 15) || ((ld * 2) & 15)) return -101;
+  cuuint64_t dims[2] = {cols, rows};
+  cuuint64_t strides[1] = {ld * 2};
+  cuuint32_t box[2] = {BK, box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUtensorMap m;
+  CUresult r = fn(&m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return -102 - (int)r;
+  if (g_maps.size() > 65536) g_maps.clear();
+  g_maps.emplace(key, m);
+  *out = m;
+  return 0;
+}
+
+template <int BN, bool DUAL>
+int launch_gemm(const CUtensorMap& tw, const CUtensorMap& tx, GemmArgs& a, int m_tiles, int splits, int stages_override,
+                cudaStream_t stream, bool pdl) {
+  constexpr int STAGE_BYTES = W_TILE_BYTES * (DUAL ? 2 : 1) + BN * BK * 2;
+  int max_stages = (SMEM_LIMIT - 1024 - 512) / STAGE_BYTES;
+  if (max_stages > 16) max_stages = 16;
+  int stages = stages_override > 0 ? min(stages_override, max_stages) : max_stages;
+  if (stages > a.kb_per_split) stages = a.kb_per_split;
+  if (stages < 1) stages = 1;
+  a.stages = stages;
+  const size_t smem = (size_t)stages * STAGE_BYTES + 1024 + (2 * stages + 1) * 8 + 16;
+  static int configured_smem = 0;
+  if ((int)smem > configured_smem) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_wx_kernel<BN, DUAL>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_LIMIT);
+    if (e != cudaSuccess) return (int)e;
+    configured_smem = SMEM_LIMIT;
+  }
+  dim3 grid(m_tiles, (a.T + BN - 1) / BN, splits);
+  cudaError_t e = prism_launch(gemm_wx_kernel<BN, DUAL>, grid, dim3(GEMM_THREADS), smem, stream, pdl, tw, tx, a);
+  return (int)e;
+}
+
+}  // namespace
+
+// W [w_rows_total, K] (row stride ldw), X [T, K] (row stride ldx), both bf16.
+// out: bf16 [T, ldo] (features along the row) or fp32 [splits][T][ldo] when out_f32.
+// dual: second weight tile starts at row w2_row_off; output = silu(W1 x) * (W2 x), M rows.
+// Returns 0 on success, a cudaError_t (>0) or a negative validation code.
+PRISM_API int prism_gemm_wx(const void* W, const void* X, void* out, int M, int T, int K, long long ldw, long long ldx,
+                            long long ldo, int w_rows_total, const void* bias, const void* residual, long long ldr,
+                            int act, int dual, int w2_row_off, int splits, int out_f32, long long split_stride,
+                            int bn_override, int stages_override, void* stream_ptr, int pdl) {
+  if (M <= 0 || T <= 0 || K <= 0) return -1;
+  if (K % 8) return -2;  // 16-byte row pitch for TMA
+  if (dual && (splits > 1 || out_f32)) return -3;
+  if (!out_f32 && splits > 1) return -4;
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_ptr);
+  int bn = bn_override;
+  if (bn <= 0) {
+    if (T <= 16) bn = 16;
+    else if (T <= 32) bn = 32;
+    else if (T <= 64) bn = 64;
+    else if (T <= 128) bn = 128;
+    else {
+      const int pad256 = (T + 255) / 256 * 256, pad128 = (T + 127) / 128 * 128;
+      bn = (pad256 * 100 <= pad128 * 106) ? 256 : 128;
+    }
+  }
+  if (bn != 16 && bn != 32 && bn != 64 && bn != 128 && bn != 256) return -5;
+  GemmArgs a;
+  a.M = M;
+  a.T = T;
+  a.kb_total = (K + BK - 1) / BK;
+  if (splits < 1) splits = 1;
+  if (splits > a.kb_total) splits = a.kb_total;
+  a.kb_per_split = (a.kb_total + splits - 1) / splits;
+  splits = (a.kb_total + a.kb_per_split - 1) / a.kb_per_split;  // no empty split
+  a.w2_row_off = w2_row_off;
+  a.stages = 0;
+  a.out_f32 = out_f32;
+  a.act = act;
+  a.ldo = ldo;
+  a.ldr = ldr;
+  a.split_stride = split_stride;
+  a.bias = reinterpret_cast<const __nv_bfloat16*>(bias);
+  a.residual = reinterpret_cast<const __nv_bfloat16*>(residual);
+  a.out = out;
+  CUtensorMap tw, tx;
+  int rc = get_tensor_map(W, (unsigned long long)w_rows_total, (unsigned long long)K, (unsigned long long)ldw, BM, &tw);
+  if (rc) return rc;
+  rc = get_tensor_map(X, (unsigned long long)T, (unsigned long long)K, (unsigned long long)ldx, (unsigned)bn, &tx);
+  if (rc) return rc;
+  const int m_tiles = (M + BM - 1) / BM;
+  const bool p = pdl != 0;
+#define PRISM_GEMM_CASE(BN_)                                                                            \
+  case BN_:                                                                                             \
+    return dual ? launch_gemm<BN_, true>(tw, tx, a, m_tiles, splits, stages_override, stream, p)       \
+                : launch_gemm<BN_, false>(tw, tx, a, m_tiles, splits, stages_override, stream, p);
+  switch (bn) {
+    PRISM_GEMM_CASE(16)
+    PRISM_GEMM_CASE(32)
+    PRISM_GEMM_CASE(64)
+    PRISM_GEMM_CASE(128)
+    PRISM_GEMM_CASE(256)
+  }
+#undef PRISM_GEMM_CASE
+  return -6;
+}
+
+// Number of split-K slabs prism_gemm_wx will actually write for (K, splits).
+PRISM_API int prism_gemm_effective_splits(int K, int splits) {
+  const int kb_total = (K + BK - 1) / BK;
+  if (splits < 1) splits = 1;
+  if (splits > kb_total) splits = kb_total;
+  const int per = (kb_total + splits - 1) / splits;
+  return (kb_total + per - 1) / per;
+}
+
+PRISM_API void prism_gemm_clear_tensor_maps() {
+  std::lock_guard<std::mutex> lock(g_map_mutex);
+  g_maps.clear();
+}

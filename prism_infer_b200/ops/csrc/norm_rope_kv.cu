@@ -1,0 +1,513 @@
+// Pointwise / row-wise kernels around the GEMMs:
+//   * residual add + RMSNorm that also folds split-K / tensor-parallel fp32 partial slabs
+//     and the DeepStack visual add (reference prism_infer/ops/add_rmsnorm.py:32-230 and
+//     prism_infer/models/qwen3_vl.py:1148-1162),
+//   * per-head QK-RMSNorm + interleaved M-RoPE + paged KV store with optional scaled-FP8
+//     quantisation (reference prism_infer/ops/qk_rmsnorm.py:190-548 and
+//     prism_infer/ops/kv_cache_store.py:57-167),
+//   * SwiGLU (reference prism_infer/ops/swiglu.py:27-99),
+//   * token embedding gather with visual-embedding scatter,
+//   * the vision tower's LayerNorm, 2-D rotary and position-embedding interpolation
+//     (reference prism_infer/vision/vision_encoder.py:243-262,546-653).
+// bf16 rounding points follow the eager bf16 graph: after every add, after norm, after
+// the weight multiply, after silu, after each rotary product.
+#include "common.cuh"
+
+PRISM_DEFINE_TU_STATUS(norm)
+
+namespace {
+
+typedef __nv_bfloat16 bf16;
+
+__device__ __forceinline__ float b2f(bf16 v) { return __bfloat162float(v); }
+__device__ __forceinline__ bf16 f2b(float v) { return __float2bfloat16_rn(v); }
+
+__device__ __forceinline__ float block_sum(float v, float* red) {
+  v = warp_sum(v);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+  __syncthreads();
+  if (lane == 0) red[warp] = v;
+  __syncthreads();
+  float t = (lane < nw) ? red[lane] : 0.0f;
+  t = warp_sum(t);
+  return t;
+}
+
+// ---------------------------------------------------------------------------------
+// add + RMSNorm.  One CTA per token row.
+//   delta   = bf16( sum_p partial[p][t][:] )            (P >= 1)   or  x_in[t][:]  (P == 0)
+//   added   = residual ? bf16(residual[t] + delta) : delta
+//   added   = extra ? bf16(added + extra[extra_index[t]])  (only rows with index >= 0)
+//   residual[t] = added (when residual_out != null);  out[t] = bf16(bf16(added * rstd) * w)
+// ---------------------------------------------------------------------------------
+struct AddNormArgs {
+  const float* partials;
+  long long slab_stride;
+  int P;
+  const bf16* x_in;
+  const bf16* residual_in;
+  bf16* residual_out;
+  const bf16* extra;
+  const int* extra_index;
+  const bf16* weight;
+  bf16* out;
+  int H;
+  float eps;
+};
+
+__global__ void __launch_bounds__(256) add_rmsnorm_kernel(const AddNormArgs a) {
+  extern __shared__ float row[];  // H floats
+  __shared__ float red[32];
+  const int t = blockIdx.x;
+  const int H = a.H;
+  pdl_launch_dependents();
+  pdl_wait();
+  const size_t base = (size_t)t * H;
+  int ex = -1;
+  if (a.extra != nullptr) ex = a.extra_index[t];
+  float ss = 0.0f;
+  for (int i = threadIdx.x * 2; i < H; i += blockDim.x * 2) {
+    float d0, d1;
+    if (a.P > 0) {
+      float s0 = 0.0f, s1 = 0.0f;
+      for (int p = 0; p < a.P; ++p) {
+        const float2 v = *reinterpret_cast<const float2*>(a.partials + (size_t)p * a.slab_stride + base + i);
+        s0 += v.x;
+        s1 += v.y;
+      }
+      d0 = bf16_round(s0);
+      d1 = bf16_round(s1);
+    } else {
+      const __nv_bfloat162 v = *reinterpret_cast<const __nv_bfloat162*>(a.x_in + base + i);
+      d0 = b2f(v.x);
+      d1 = b2f(v.y);
+    }
+    if (a.residual_in != nullptr) {
+      const __nv_bfloat162 r = *reinterpret_cast<const __nv_bfloat162*>(a.residual_in + base + i);
+      d0 = bf16_round(b2f(r.x) + d0);
+      d1 = bf16_round(b2f(r.y) + d1);
+    }
+    if (ex >= 0) {
+      const __nv_bfloat162 e = *reinterpret_cast<const __nv_bfloat162*>(a.extra + (size_t)ex * H + i);
+      d0 = bf16_round(d0 + b2f(e.x));
+      d1 = bf16_round(d1 + b2f(e.y));
+    }
+    if (a.residual_out != nullptr) {
+      __nv_bfloat162 o;
+      o.x = f2b(d0);
+      o.y = f2b(d1);
+      *reinterpret_cast<__nv_bfloat162*>(a.residual_out + base + i) = o;
+    }
+    row[i] = d0;
+    row[i + 1] = d1;
+    ss += d0 * d0 + d1 * d1;
+  }
+  ss = block_sum(ss, red);
+  const float rstd = rsqrtf(ss / (float)H + a.eps);
+  if (a.out != nullptr) {
+    for (int i = threadIdx.x * 2; i < H; i += blockDim.x * 2) {
+      const __nv_bfloat162 w = *reinterpret_cast<const __nv_bfloat162*>(a.weight + i);
+      __nv_bfloat162 o;
+      o.x = f2b(bf16_round(row[i] * rstd) * b2f(w.x));
+      o.y = f2b(bf16_round(row[i + 1] * rstd) * b2f(w.y));
+      *reinterpret_cast<__nv_bfloat162*>(a.out + base + i) = o;
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------------
+// LayerNorm with bias (vision tower), one CTA per row, fp32 statistics.
+// ---------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) layernorm_kernel(const bf16* x, const bf16* w, const bf16* b, bf16* out, int H,
+                                                        float eps) {
+  extern __shared__ float row[];
+  __shared__ float red[32];
+  const size_t base = (size_t)blockIdx.x * H;
+  pdl_launch_dependents();
+  pdl_wait();
+  float s = 0.0f;
+  for (int i = threadIdx.x; i < H; i += blockDim.x) {
+    const float v = b2f(x[base + i]);
+    row[i] = v;
+    s += v;
+  }
+  const float mean = block_sum(s, red) / (float)H;
+  float ss = 0.0f;
+  for (int i = threadIdx.x; i < H; i += blockDim.x) {
+    const float d = row[i] - mean;
+    ss += d * d;
+  }
+  const float rstd = rsqrtf(block_sum(ss, red) / (float)H + eps);
+  for (int i = threadIdx.x; i < H; i += blockDim.x) {
+    out[base + i] = f2b((row[i] - mean) * rstd * b2f(w[i]) + b2f(b[i]));
+  }
+}
+
+// ---------------------------------------------------------------------------------
+// QK-RMSNorm + M-RoPE + KV store.  One warp per (token, head); heads are ordered
+// [q heads | k heads | v heads] exactly like the packed QKV projection row.
+// ---------------------------------------------------------------------------------
+struct QkvArgs {
+  const bf16* qkv;          // [T][row_stride] bf16, or null when partials are given
+  const float* partials;    // [P][T][row_stride] fp32 split-K slabs
+  long long slab_stride;
+  int P;
+  long long row_stride;     // elements per token in the source
+  const int* positions;     // [3][T] (T, H, W axes)
+  const bf16* q_weight;     // [D]
+  const bf16* k_weight;     // [D]
+  const float* inv_freq;    // [D/2]
+  const int* axis;          // [D/2] in {0,1,2}
+  bf16* q_out;              // [T][Hq][D] (may be null)
+  long long q_stride;       // elements per token in q_out
+  const long long* slots;   // [T] flat slot (block * page + offset), < 0 = skip
+  void* k_cache;            // [blocks][Hkv][page][D]
+  void* v_cache;
+  float* k_scale;           // [blocks][Hkv][page]
+  float* v_scale;
+  int T, Hq, Hkv, page;
+  int kv_mode;              // 0 bf16, 1 fp8 unit scale, 2 fp8 + per-token-per-head scale
+  int apply_norm, apply_rope;
+  float eps;
+};
+
+constexpr float FP8_MAX = 448.0f;
+constexpr float FP8_SCALE_FLOOR = 1.0e-6f;
+
+template <int D>
+__global__ void __launch_bounds__(256) qk_norm_rope_store_kernel(const QkvArgs a) {
+  constexpr int PER = D / 64;  // rotary pairs per lane
+  const int warps_per_block = blockDim.x >> 5;
+  const int gw = blockIdx.x * warps_per_block + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  const int heads = a.Hq + 2 * a.Hkv;
+  pdl_launch_dependents();
+  pdl_wait();
+  if (gw >= a.T * heads) return;
+  const int t = gw / heads;
+  const int h = gw % heads;
+  const bool is_q = h < a.Hq;
+  const bool is_k = !is_q && h < a.Hq + a.Hkv;
+  const size_t src = (size_t)t * a.row_stride + (size_t)h * D;
+
+  float lo[PER], hi[PER];  // element i and element i + D/2
+#pragma unroll
+  for (int j = 0; j < PER; ++j) {
+    const int i = lane + 32 * j;
+    if (a.P > 0) {
+      float s0 = 0.0f, s1 = 0.0f;
+      for (int p = 0; p < a.P; ++p) {
+        const float* row = a.partials + (size_t)p * a.slab_stride + src;
+        s0 += row[i];
+        s1 += row[i + D / 2];
+      }
+      lo[j] = bf16_round(s0);
+      hi[j] = bf16_round(s1);
+    } else {
+      lo[j] = b2f(a.qkv[src + i]);
+      hi[j] = b2f(a.qkv[src + i + D / 2]);
+    }
+  }
+  if (is_q || is_k) {
+    if (a.apply_norm) {
+      float ss = 0.0f;
+#pragma unroll
+      for (int j = 0; j < PER; ++j) ss += lo[j] * lo[j] + hi[j] * hi[j];
+      ss = warp_sum(ss);
+      const float rstd = rsqrtf(ss / (float)D + a.eps);
+      const bf16* w = is_q ? a.q_weight : a.k_weight;
+#pragma unroll
+      for (int j = 0; j < PER; ++j) {
+        const int i = lane + 32 * j;
+        lo[j] = bf16_round(bf16_round(lo[j] * rstd) * b2f(w[i]));
+        hi[j] = bf16_round(bf16_round(hi[j] * rstd) * b2f(w[i + D / 2]));
+      }
+    }
+    if (a.apply_rope) {
+#pragma unroll
+      for (int j = 0; j < PER; ++j) {
+        const int i = lane + 32 * j;
+        const int ax = a.axis[i];
+        const float pos = (float)a.positions[(size_t)ax * a.T + t];
+        float sn, cs;
+        sincosf(pos * a.inv_freq[i], &sn, &cs);
+        sn = bf16_round(sn);
+        cs = bf16_round(cs);
+        const float x0 = lo[j], x1 = hi[j];
+        lo[j] = bf16_round(bf16_round(x0 * cs) + bf16_round(-x1 * sn));
+        hi[j] = bf16_round(bf16_round(x1 * cs) + bf16_round(x0 * sn));
+      }
+    }
+  }
+  if (is_q) {
+    if (a.q_out != nullptr) {
+      bf16* dst = a.q_out + (size_t)t * a.q_stride + (size_t)h * D;
+#pragma unroll
+      for (int j = 0; j < PER; ++j) {
+        dst[lane + 32 * j] = f2b(lo[j]);
+        dst[lane + 32 * j + D / 2] = f2b(hi[j]);
+      }
+    }
+    return;
+  }
+  const long long slot = a.slots[t];
+  if (slot < 0) return;
+  const int kvh = is_k ? h - a.Hq : h - a.Hq - a.Hkv;
+  const long long blk = slot / a.page;
+  const int off = (int)(slot % a.page);
+  const size_t row = ((size_t)blk * a.Hkv + kvh) * a.page + off;  // token row inside [blocks][Hkv][page]
+  void* cache = is_k ? a.k_cache : a.v_cache;
+  if (a.kv_mode == 0) {
+    bf16* dst = reinterpret_cast<bf16*>(cache) + row * D;
+#pragma unroll
+    for (int j = 0; j < PER; ++j) {
+      dst[lane + 32 * j] = f2b(lo[j]);
+      dst[lane + 32 * j + D / 2] = f2b(hi[j]);
+    }
+  } else {
+    float scale = 1.0f;
+    if (a.kv_mode == 2) {
+      float am = 0.0f;
+#pragma unroll
+      for (int j = 0; j < PER; ++j) am = fmaxf(am, fmaxf(fabsf(lo[j]), fabsf(hi[j])));
+      am = warp_max(am);
+      scale = fmaxf(am / FP8_MAX, FP8_SCALE_FLOOR);
+      if (lane == 0) (is_k ? a.k_scale : a.v_scale)[row] = scale;
+    }
+    __nv_fp8_storage_t* dst = reinterpret_cast<__nv_fp8_storage_t*>(cache) + row * D;
+#pragma unroll
+    for (int j = 0; j < PER; ++j) {
+      const float q0 = fminf(fmaxf(lo[j] / scale, -FP8_MAX), FP8_MAX);
+      const float q1 = fminf(fmaxf(hi[j] / scale, -FP8_MAX), FP8_MAX);
+      dst[lane + 32 * j] = __nv_cvt_float_to_fp8(q0, __NV_SATFINITE, __NV_E4M3);
+      dst[lane + 32 * j + D / 2] = __nv_cvt_float_to_fp8(q1, __NV_SATFINITE, __NV_E4M3);
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------------
+// SwiGLU on a packed [T][2I] row (gate | up), bf16 source or fp32 split-K slabs.
+// ---------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) swiglu_kernel(const bf16* gu, const float* partials, long long slab_stride, int P,
+                                                     bf16* out, int T, int I) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const size_t total = (size_t)T * I;
+  for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
+    const size_t t = idx / I, i = idx % I;
+    float g, u;
+    if (P > 0) {
+      float sg = 0.0f, su = 0.0f;
+      for (int p = 0; p < P; ++p) {
+        const float* row = partials + (size_t)p * slab_stride + t * 2 * I;
+        sg += row[i];
+        su += row[I + i];
+      }
+      g = bf16_round(sg);
+      u = bf16_round(su);
+    } else {
+      g = b2f(gu[t * 2 * I + i]);
+      u = b2f(gu[t * 2 * I + I + i]);
+    }
+    out[idx] = f2b(bf16_round(silu(g)) * u);
+  }
+}
+
+// ---------------------------------------------------------------------------------
+// Token embedding gather with vocabulary shard window and visual-embedding scatter.
+// vis_index[t] >= 0 selects row vis_index[t] of `visual` instead of the table.
+// ---------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) embed_kernel(const long long* ids, const bf16* table, const bf16* visual,
+                                                    const int* vis_index, bf16* out, int H, long long vocab_start,
+                                                    long long vocab_end) {
+  const int t = blockIdx.x;
+  pdl_launch_dependents();
+  pdl_wait();
+  const long long id = ids[t];
+  const int vi = (visual != nullptr && vis_index != nullptr) ? vis_index[t] : -1;
+  const bf16* src = nullptr;
+  if (vi >= 0) src = visual + (size_t)vi * H;
+  else if (id >= vocab_start && id < vocab_end) src = table + (size_t)(id - vocab_start) * H;
+  for (int i = threadIdx.x * 8; i < H; i += blockDim.x * 8) {
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (src != nullptr) v = *reinterpret_cast<const uint4*>(src + i);
+    *reinterpret_cast<uint4*>(out + (size_t)t * H + i) = v;
+  }
+}
+
+// hidden[t] += extra[index[t]] for rows with index >= 0 (DeepStack on an explicit tensor).
+__global__ void __launch_bounds__(256) indexed_add_kernel(bf16* hidden, const bf16* extra, const int* index, int H) {
+  const int t = blockIdx.x;
+  pdl_launch_dependents();
+  pdl_wait();
+  const int e = index[t];
+  if (e < 0) return;
+  for (int i = threadIdx.x; i < H; i += blockDim.x) {
+    hidden[(size_t)t * H + i] = f2b(b2f(hidden[(size_t)t * H + i]) + b2f(extra[(size_t)e * H + i]));
+  }
+}
+
+// ---------------------------------------------------------------------------------
+// Vision: x[n] += bf16( sum_k w[k][n] * table[idx[k][n]] )   (4-corner bilinear plan)
+// ---------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) pos_embed_add_kernel(bf16* x, const bf16* table, const long long* idx,
+                                                            const float* wt, int N, int H) {
+  const int n = blockIdx.x;
+  pdl_launch_dependents();
+  pdl_wait();
+  long long id[4];
+  float w[4];
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {
+    id[k] = idx[(size_t)k * N + n];
+    w[k] = wt[(size_t)k * N + n];
+  }
+  for (int i = threadIdx.x; i < H; i += blockDim.x) {
+    float s = 0.0f;
+#pragma unroll
+    for (int k = 0; k < 4; ++k) s += w[k] * b2f(table[(size_t)id[k] * H + i]);
+    x[(size_t)n * H + i] = f2b(b2f(x[(size_t)n * H + i]) + bf16_round(s));
+  }
+}
+
+// Vision 2-D rotary on q and k inside the packed [N][3][heads][hd] projection, in place.
+// angle[n][i] for i < hd/2: first hd/4 slots use the row coordinate, next hd/4 the column.
+__global__ void __launch_bounds__(256) vit_rope_kernel(bf16* qkv, const int* coords, const float* inv_freq, int N,
+                                                       int heads, int hd) {
+  const int n = blockIdx.x;
+  pdl_launch_dependents();
+  pdl_wait();
+  const int half = hd / 2, quarter = hd / 4;
+  const float row = (float)coords[2 * n], col = (float)coords[2 * n + 1];
+  const int work = 2 * heads * half;
+  for (int w = threadIdx.x; w < work; w += blockDim.x) {
+    const int i = w % half;
+    const int h = (w / half) % heads;
+    const int which = w / (half * heads);  // 0 = q, 1 = k
+    const float ang = (i < quarter ? row : col) * inv_freq[i % quarter];
+    float sn, cs;
+    sincosf(ang, &sn, &cs);
+    bf16* p = qkv + ((size_t)n * 3 + which) * heads * hd + (size_t)h * hd;
+    const float x0 = b2f(p[i]), x1 = b2f(p[i + half]);
+    p[i] = f2b(x0 * cs - x1 * sn);
+    p[i + half] = f2b(x1 * cs + x0 * sn);
+  }
+}
+
+}  // namespace
+
+#define STREAM(p) reinterpret_cast<cudaStream_t>(p)
+
+PRISM_API int prism_add_rmsnorm(const void* partials, long long slab_stride, int P, const void* x_in,
+                                const void* residual_in, void* residual_out, const void* extra, const void* extra_index,
+                                const void* weight, void* out, int T, int H, float eps, void* stream, int pdl) {
+  if (T <= 0) return 0;
+  if (H % 2) return -1;
+  AddNormArgs a;
+  a.partials = (const float*)partials;
+  a.slab_stride = slab_stride;
+  a.P = P;
+  a.x_in = (const bf16*)x_in;
+  a.residual_in = (const bf16*)residual_in;
+  a.residual_out = (bf16*)residual_out;
+  a.extra = (const bf16*)extra;
+  a.extra_index = (const int*)extra_index;
+  a.weight = (const bf16*)weight;
+  a.out = (bf16*)out;
+  a.H = H;
+  a.eps = eps;
+  const size_t smem = (size_t)H * sizeof(float);
+  if (smem > 48 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(add_rmsnorm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+  }
+  return (int)prism_launch(add_rmsnorm_kernel, dim3(T), dim3(256), smem, STREAM(stream), pdl != 0, a);
+}
+
+PRISM_API int prism_layernorm(const void* x, const void* w, const void* b, void* out, int T, int H, float eps,
+                              void* stream, int pdl) {
+  if (T <= 0) return 0;
+  const size_t smem = (size_t)H * sizeof(float);
+  return (int)prism_launch(layernorm_kernel, dim3(T), dim3(256), smem, STREAM(stream), pdl != 0, (const bf16*)x,
+                           (const bf16*)w, (const bf16*)b, (bf16*)out, H, eps);
+}
+
+PRISM_API int prism_qk_norm_rope_store(const void* qkv, const void* partials, long long slab_stride, int P,
+                                       long long row_stride, const void* positions, const void* q_weight,
+                                       const void* k_weight, const void* inv_freq, const void* axis, void* q_out,
+                                       long long q_stride, const void* slots, void* k_cache, void* v_cache,
+                                       void* k_scale, void* v_scale, int T, int Hq, int Hkv, int D, int page,
+                                       int kv_mode, int apply_norm, int apply_rope, float eps, void* stream, int pdl) {
+  if (T <= 0) return 0;
+  QkvArgs a;
+  a.qkv = (const bf16*)qkv;
+  a.partials = (const float*)partials;
+  a.slab_stride = slab_stride;
+  a.P = P;
+  a.row_stride = row_stride;
+  a.positions = (const int*)positions;
+  a.q_weight = (const bf16*)q_weight;
+  a.k_weight = (const bf16*)k_weight;
+  a.inv_freq = (const float*)inv_freq;
+  a.axis = (const int*)axis;
+  a.q_out = (bf16*)q_out;
+  a.q_stride = q_stride;
+  a.slots = (const long long*)slots;
+  a.k_cache = k_cache;
+  a.v_cache = v_cache;
+  a.k_scale = (float*)k_scale;
+  a.v_scale = (float*)v_scale;
+  a.T = T;
+  a.Hq = Hq;
+  a.Hkv = Hkv;
+  a.page = page;
+  a.kv_mode = kv_mode;
+  a.apply_norm = apply_norm;
+  a.apply_rope = apply_rope;
+  a.eps = eps;
+  const int warps = T * (Hq + 2 * Hkv);
+  const int wpb = 8;
+  dim3 grid((warps + wpb - 1) / wpb), block(wpb * 32);
+  if (D == 128) return (int)prism_launch(qk_norm_rope_store_kernel<128>, grid, block, 0, STREAM(stream), pdl != 0, a);
+  if (D == 64) return (int)prism_launch(qk_norm_rope_store_kernel<64>, grid, block, 0, STREAM(stream), pdl != 0, a);
+  return -2;
+}
+
+PRISM_API int prism_swiglu(const void* gu, const void* partials, long long slab_stride, int P, void* out, int T, int I,
+                           void* stream, int pdl) {
+  if (T <= 0) return 0;
+  const size_t total = (size_t)T * I;
+  int blocks = (int)((total + 255) / 256);
+  if (blocks > 148 * 8) blocks = 148 * 8;
+  return (int)prism_launch(swiglu_kernel, dim3(blocks), dim3(256), 0, STREAM(stream), pdl != 0, (const bf16*)gu,
+                           (const float*)partials, slab_stride, P, (bf16*)out, T, I);
+}
+
+PRISM_API int prism_embed(const void* ids, const void* table, const void* visual, const void* vis_index, void* out,
+                          int T, int H, long long vocab_start, long long vocab_end, void* stream, int pdl) {
+  if (T <= 0) return 0;
+  if (H % 8) return -1;
+  return (int)prism_launch(embed_kernel, dim3(T), dim3(256), 0, STREAM(stream), pdl != 0, (const long long*)ids,
+                           (const bf16*)table, (const bf16*)visual, (const int*)vis_index, (bf16*)out, H, vocab_start,
+                           vocab_end);
+}
+
+PRISM_API int prism_indexed_add(void* hidden, const void* extra, const void* index, int T, int H, void* stream, int pdl) {
+  if (T <= 0) return 0;
+  return (int)prism_launch(indexed_add_kernel, dim3(T), dim3(256), 0, STREAM(stream), pdl != 0, (bf16*)hidden,
+                           (const bf16*)extra, (const int*)index, H);
+}
+
+PRISM_API int prism_pos_embed_add(void* x, const void* table, const void* idx, const void* wt, int N, int H,
+                                  void* stream, int pdl) {
+  if (N <= 0) return 0;
+  return (int)prism_launch(pos_embed_add_kernel, dim3(N), dim3(256), 0, STREAM(stream), pdl != 0, (bf16*)x,
+                           (const bf16*)table, (const long long*)idx, (const float*)wt, N, H);
+}
+
+PRISM_API int prism_vit_rope(void* qkv, const void* coords, const void* inv_freq, int N, int heads, int hd, void* stream,
+                             int pdl) {
+  if (N <= 0) return 0;
+  return (int)prism_launch(vit_rope_kernel, dim3(N), dim3(256), 0, STREAM(stream), pdl != 0, (bf16*)qkv,
+                           (const int*)coords, (const float*)inv_freq, N, heads, hd);
+}

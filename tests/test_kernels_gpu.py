@@ -1,0 +1,322 @@
+"""sm_100a kernels against the plain-PyTorch fp32 statement of the same op.
+
+Every case runs the op twice through ``prism_infer_b200.ops``: on CUDA bf16 tensors (the
+hand-written kernel) and on CPU fp32 tensors holding the same bf16-representable values
+(the reference path).  Tolerances follow the reference's kernel tests
+(tests/test_paged_decode_kernel.py:144-146, tests/test_scaled_fp8_kv_cache.py:399-472).
+"""
+
+import math
+
+import pytest
+import torch
+
+from prism_infer_b200 import ops
+from prism_infer_b200.ops import native
+
+pytestmark = pytest.mark.gpu
+
+
+def bf(x):
+    return x.to(torch.bfloat16)
+
+
+def rand_bf16(*shape, scale=1.0, seed=0):
+    g = torch.Generator().manual_seed(seed)
+    return bf(torch.randn(*shape, generator=g) * scale)
+
+
+def close(a, b, atol, rtol, what=""):
+    a, b = a.float().cpu(), b.float().cpu()
+    err = (a - b).abs()
+    lim = atol + rtol * b.abs()
+    assert bool((err <= lim).all()), f"{what}: max err {err.max().item():.4g}, worst ratio {(err / lim).max().item():.3g}"
+
+
+@pytest.fixture(autouse=True)
+def _status(cuda_device):
+    yield
+    torch.cuda.synchronize()
+    native.check_status()
+
+
+@pytest.mark.parametrize(
+    "T,M,K",
+    [(1, 256, 512), (16, 6144, 4096), (37, 512, 256), (128, 4096, 12288), (300, 1152, 4304), (1600, 4096, 4096),
+     (5, 1000, 136), (2048, 768, 4096)],
+)
+def test_gemm_plain(cuda_device, T, M, K):
+    x, w = rand_bf16(T, K, seed=1), rand_bf16(M, K, scale=K ** -0.5, seed=2)
+    y = ops.linear(x.cuda(), w.cuda())
+    ref = x.float() @ w.float().t()
+    close(y, ref, 2e-2, 2e-2, f"gemm {T}x{M}x{K}")
+
+
+@pytest.mark.parametrize("bn", [16, 32, 64, 128, 256])
+def test_gemm_all_token_tiles(cuda_device, bn):
+    T, M, K = 200, 384, 1024
+    x, w = rand_bf16(T, K, seed=3), rand_bf16(M, K, scale=K ** -0.5, seed=4)
+    y = ops.linear(x.cuda(), w.cuda(), bn=bn)
+    close(y, x.float() @ w.float().t(), 2e-2, 2e-2, f"bn={bn}")
+
+
+@pytest.mark.parametrize("stages", [1, 2, 3])
+def test_gemm_short_pipelines(cuda_device, stages):
+    T, M, K = 64, 256, 2048
+    x, w = rand_bf16(T, K, seed=5), rand_bf16(M, K, scale=K ** -0.5, seed=6)
+    y = ops.linear(x.cuda(), w.cuda(), stages=stages)
+    close(y, x.float() @ w.float().t(), 2e-2, 2e-2, f"stages={stages}")
+
+
+def test_gemm_epilogues(cuda_device):
+    T, M, K = 70, 640, 1152
+    x, w = rand_bf16(T, K, seed=7), rand_bf16(M, K, scale=K ** -0.5, seed=8)
+    b, r = rand_bf16(M, seed=9), rand_bf16(T, M, seed=10)
+    for act in (None, "gelu_tanh", "gelu"):
+        y = ops.linear(x.cuda(), w.cuda(), bias=b.cuda(), act=act, residual=r.cuda())
+        ref = ops.linear(x.float(), w.float(), bias=b.float(), act=act, residual=r.float())
+        close(y, ref, 3e-2, 2e-2, f"epilogue {act}")
+
+
+@pytest.mark.parametrize("T,M,K,splits", [(1, 4096, 4096, 4), (8, 512, 12288, 9), (16, 6144, 4096, 3), (130, 256, 512, 2)])
+def test_gemm_split_k(cuda_device, T, M, K, splits):
+    x, w = rand_bf16(T, K, seed=11), rand_bf16(M, K, scale=K ** -0.5, seed=12)
+    parts = ops.linear_partial(x.cuda(), w.cuda(), splits)
+    assert parts.shape[0] == ops.effective_splits(K, splits)
+    close(parts.sum(0), x.float() @ w.float().t(), 1e-2, 1e-2, "split-k")
+
+
+@pytest.mark.parametrize("T,I,K", [(1, 512, 256), (24, 12288, 4096), (700, 1536, 4096)])
+def test_gemm_dual_swiglu(cuda_device, T, I, K):
+    x, w = rand_bf16(T, K, seed=13), rand_bf16(2 * I, K, scale=K ** -0.5, seed=14)
+    y = ops.gate_up_swiglu(x.cuda(), w.cuda())
+    ref = ops.gate_up_swiglu(x.float(), w.float())
+    close(y, ref, 2e-2, 3e-2, "dual swiglu")
+
+
+def test_add_rmsnorm_variants(cuda_device):
+    T, H = 9, 4096
+    w = bf(1 + 0.1 * torch.randn(H))
+    x, res = rand_bf16(T, H, seed=15), rand_bf16(T, H, seed=16)
+    parts = torch.randn(3, T, H)
+    extra, idx = rand_bf16(4, H, seed=17), torch.tensor([-1, 0, 1, -1, 2, 3, -1, -1, 0], dtype=torch.int32)
+    for kw in (dict(x=x), dict(partials=parts)):
+        for use_res in (False, True):
+            for use_extra in (False, True):
+                g = {k: v.cuda() for k, v in kw.items()}
+                c = {k: v.float() for k, v in kw.items()}
+                rg = res.clone().cuda() if use_res else None
+                rc = res.float().clone() if use_res else None
+                eg = dict(extra=extra.cuda(), extra_index=idx.cuda()) if use_extra else {}
+                ec = dict(extra=extra.float(), extra_index=idx) if use_extra else {}
+                ng, sg = ops.add_rmsnorm(w.cuda(), 1e-6, residual=rg, **g, **eg)
+                nc, sc = ops.add_rmsnorm(w.float(), 1e-6, residual=rc, **c, **ec)
+                close(sg, sc, 2e-2, 1e-2, "residual")
+                close(ng, nc, 3e-2, 2e-2, "normed")
+
+
+def test_layernorm_swiglu_embed(cuda_device):
+    x = rand_bf16(33, 1152, seed=18)
+    w, b = bf(1 + 0.1 * torch.randn(1152)), bf(0.1 * torch.randn(1152))
+    close(ops.layernorm(x.cuda(), w.cuda(), b.cuda(), 1e-6), ops.layernorm(x.float(), w.float(), b.float(), 1e-6), 2e-2, 1e-2, "ln")
+    gu = rand_bf16(7, 2 * 1536, seed=19)
+    close(ops.swiglu(gu.cuda()), ops.swiglu(gu.float()), 1e-2, 1e-2, "swiglu")
+    parts = torch.randn(2, 7, 2 * 1536)
+    close(ops.swiglu(partials=parts.cuda()), ops.swiglu(partials=parts), 2e-2, 1e-2, "swiglu partials")
+    table, vis = rand_bf16(100, 256, seed=20), rand_bf16(3, 256, seed=21)
+    ids = torch.tensor([5, 99, 40, 41, 42, 7])
+    vi = torch.tensor([-1, -1, 0, 1, 2, -1], dtype=torch.int32)
+    yg = ops.embed(ids.cuda(), table[32:96].cuda(), visual=vis.cuda(), vis_index=vi.cuda(), vocab_start=32)
+    yc = ops.embed(ids, table[32:96].float(), visual=vis.float(), vis_index=vi, vocab_start=32)
+    close(yg, yc, 0, 0, "embed")
+
+
+@pytest.mark.parametrize("mode", [ops.KV_BF16, ops.KV_FP8, ops.KV_FP8_SCALED])
+@pytest.mark.parametrize("D,Hq,Hkv,section", [(128, 32, 8, (24, 20, 20)), (64, 4, 2, (8, 12, 12))])
+def test_qk_norm_rope_store(cuda_device, mode, D, Hq, Hkv, section):
+    T, page, blocks, L = 11, 16, 6, 2
+    qkv = rand_bf16(T, (Hq + 2 * Hkv) * D, seed=22)
+    qw, kw = bf(1 + 0.1 * torch.randn(D)), bf(1 + 0.1 * torch.randn(D))
+    pos = torch.randint(0, 3000, (3, T), dtype=torch.int32)
+    slots = torch.tensor([0, 1, 2, 17, -1, 40, 41, 95, 94, 3, 50], dtype=torch.int64)
+    cg = ops.KVCache(L, blocks, Hkv, page, D, mode, "cuda")
+    cc = ops.KVCache(L, blocks, Hkv, page, D, mode, "cpu", dtype=torch.float32)
+    kwargs = dict(num_heads=Hq, num_kv_heads=Hkv, head_dim=D, theta=5e6, section=section, eps=1e-6, layer=1)
+    for src in ("bf16", "partials"):
+        if src == "bf16":
+            qg = ops.qk_norm_rope_store(qkv=qkv.cuda(), partials=None, positions=pos.cuda(), q_weight=qw.cuda(),
+                                        k_weight=kw.cuda(), slots=slots.cuda(), cache=cg, **kwargs)
+        else:
+            parts = torch.stack((qkv.float() * 0.25, qkv.float() * 0.75)).cuda()
+            qg = ops.qk_norm_rope_store(qkv=None, partials=parts, positions=pos.cuda(), q_weight=qw.cuda(),
+                                        k_weight=kw.cuda(), slots=slots.cuda(), cache=cg, **kwargs)
+        qc = ops.qk_norm_rope_store(qkv=qkv.float(), partials=None, positions=pos, q_weight=qw.float(),
+                                    k_weight=kw.float(), slots=slots, cache=cc, **kwargs)
+        close(qg, qc, 4e-2, 2e-2, "q")
+        tol = 4e-2 if mode == ops.KV_BF16 else 0.3
+        for kv in (0, 1):
+            close(cg.dequant(kv, 1), cc.dequant(kv, 1), tol, 0.07, f"cache kv={kv} mode={mode}")
+        if mode == ops.KV_FP8_SCALED:
+            close(cg.scales, cc.scales, 1e-4, 2e-2, "scales")
+        assert float(cg.dequant(0, 0).abs().sum()) == 0.0  # other layer untouched
+
+
+def test_scaled_fp8_store_matches_reference_quantiser(cuda_device):
+    """Payload bit-equal and scales equal to the reference quantiser when fed bf16 k/v directly."""
+    T, Hkv, D, page = 13, 8, 128, 16
+    k, v = rand_bf16(T, Hkv, D, seed=23), rand_bf16(T, Hkv, D, scale=3.0, seed=24)
+    slots = torch.arange(T, dtype=torch.int64) + 5
+    cg = ops.KVCache(1, 4, Hkv, page, D, ops.KV_FP8_SCALED, "cuda")
+    cg.payload.view(torch.uint8).fill_(0x7F)
+    ops.store_kv(k.cuda(), v.cuda(), slots.cuda(), cg, 0)
+    for kv, x in ((0, k), (1, v)):
+        q, scale = ops.quantize_fp8_rows(x, True)
+        blk, off = slots // page, slots % page
+        got = cg.payload[kv, 0].cpu().view(torch.uint8)[blk, :, off]
+        assert torch.equal(got, q.view(torch.uint8)), "payload bits differ"
+        torch.testing.assert_close(cg.scales[kv, 0].cpu()[blk, :, off], scale, rtol=1e-6, atol=1e-7)
+    # untouched slots keep their sentinel
+    assert int(cg.payload[0, 0].cpu().view(torch.uint8)[0, 0, 0, 0]) == 0x7F
+
+
+def _fill_cache(mode, L, blocks, Hkv, page, D, seed):
+    cc = ops.KVCache(L, blocks, Hkv, page, D, mode, "cpu", dtype=torch.float32)
+    g = torch.Generator().manual_seed(seed)
+    raw = torch.randn(2, L, blocks, Hkv, page, D, generator=g)
+    if mode == ops.KV_BF16:
+        cc.payload.copy_(bf(raw).float())
+    else:
+        q, s = ops.quantize_fp8_rows(raw, mode == ops.KV_FP8_SCALED)
+        cc.payload.copy_(q)
+        if s is not None:
+            cc.scales.copy_(s)
+    cg = ops.KVCache(L, blocks, Hkv, page, D, mode, "cuda")
+    cg.payload.copy_(cc.payload.to(cg.payload.dtype) if mode == ops.KV_BF16 else cc.payload)
+    if cc.scales is not None:
+        cg.scales.copy_(cc.scales)
+    return cg, cc
+
+
+@pytest.mark.parametrize("mode", [ops.KV_BF16, ops.KV_FP8, ops.KV_FP8_SCALED])
+@pytest.mark.parametrize("D,Hq,Hkv,page", [(128, 32, 8, 256), (128, 4, 1, 256), (64, 4, 2, 16)])
+@pytest.mark.parametrize("nsplit", [1, 4, 0])
+def test_paged_decode(cuda_device, mode, D, Hq, Hkv, page, nsplit):
+    B, blocks = 5, 24
+    cg, cc = _fill_cache(mode, 1, blocks, Hkv, page, D, seed=25)
+    maxblk = 6
+    ctx = torch.tensor([1, page + 3, 3 * page, 0, 2 * page - 1], dtype=torch.int32)
+    bt = torch.full((B, maxblk), -1, dtype=torch.int32)
+    perm = torch.randperm(blocks, generator=torch.Generator().manual_seed(26))
+    c = 0
+    for b in range(B):
+        n = (int(ctx[b]) + page - 1) // page
+        bt[b, :n] = perm[c:c + n].int()
+        c += n
+    q = rand_bf16(B, Hq, D, seed=27)
+    yg = ops.paged_decode_attention(q.cuda(), cg, 0, bt.cuda(), ctx.cuda(), nsplit=nsplit)
+    yc = ops.paged_decode_attention(q.float(), cc, 0, bt, ctx)
+    err = (yg.float().cpu() - yc).abs()
+    assert err.max() < 2e-2 and err.mean() < 2e-3, (err.max(), err.mean())
+
+
+@pytest.mark.parametrize("hd,Hq,Hkv", [(128, 8, 2), (64, 4, 2), (72, 16, 16), (32, 4, 4)])
+@pytest.mark.parametrize("causal", [False, True])
+def test_varlen_attention(cuda_device, hd, Hq, Hkv, causal):
+    lens = [5, 64, 130, 1, 257]
+    T = sum(lens)
+    cu = torch.tensor([0] + list(torch.tensor(lens).cumsum(0)), dtype=torch.int32)
+    packed = rand_bf16(T, (Hq + 2 * Hkv) * hd, seed=28)
+    def views(t):
+        return (t[:, : Hq * hd].view(T, Hq, hd), t[:, Hq * hd:(Hq + Hkv) * hd].view(T, Hkv, hd),
+                t[:, (Hq + Hkv) * hd:].view(T, Hkv, hd))
+    pg = packed.cuda()
+    yg = ops.varlen_attention(*views(pg), cu.cuda(), max(lens), causal=causal)
+    yc = ops.varlen_attention(*views(packed.float()), cu, max(lens), causal=causal)
+    err = (yg.float().cpu() - yc).abs()
+    assert err.max() < 2e-2 and err.mean() < 2e-3, (err.max(), err.mean())
+
+
+@pytest.mark.parametrize("mode", [ops.KV_BF16, ops.KV_FP8_SCALED])
+@pytest.mark.parametrize("D,Hq,Hkv,page", [(128, 8, 2, 256), (64, 4, 2, 16)])
+def test_paged_prefill(cuda_device, mode, D, Hq, Hkv, page):
+    blocks = 40
+    cg, cc = _fill_cache(mode, 1, blocks, Hkv, page, D, seed=29)
+    q_lens = [70, 1, 33]
+    kv_lens = torch.tensor([70, page + 5, 2 * page + 33], dtype=torch.int32)
+    cu = torch.tensor([0, 70, 71, 104], dtype=torch.int32)
+    maxblk = 8
+    bt = torch.full((3, maxblk), -1, dtype=torch.int32)
+    perm = torch.randperm(blocks, generator=torch.Generator().manual_seed(30))
+    c = 0
+    for s in range(3):
+        n = (int(kv_lens[s]) + page - 1) // page
+        bt[s, :n] = perm[c:c + n].int()
+        c += n
+    q = rand_bf16(104, Hq, D, seed=31)
+    yg = ops.paged_prefill_attention(q.cuda(), cg, 0, cu.cuda(), kv_lens.cuda(), bt.cuda(), max(q_lens))
+    yc = ops.paged_prefill_attention(q.float(), cc, 0, cu, kv_lens, bt, max(q_lens))
+    err = (yg.float().cpu() - yc).abs()
+    assert err.max() < 3e-2 and err.mean() < 3e-3, (err.max(), err.mean())
+
+
+def test_kv_copy_and_compaction(cuda_device):
+    L, blocks, Hkv, page, D = 3, 10, 2, 16, 64
+    cg, cc = _fill_cache(ops.KV_FP8_SCALED, L, blocks, Hkv, page, D, seed=32)
+    ops.kv_page_copy(cg, cg, [0, 1], [5, 6], [16, 7])
+    ops.kv_page_copy(cc, cc, [0, 1], [5, 6], [16, 7])
+    src = torch.tensor([3, 17, 18, 40, 41, 47], dtype=torch.int64)
+    dst = torch.tensor([0, 1, 2, 3, 16, 17], dtype=torch.int64)  # overlaps the sources
+    ops.kv_compact(cg, src.cuda(), dst.cuda())
+    ops.kv_compact(cc, src, dst)
+    assert torch.equal(cg.payload.cpu().view(torch.uint8), cc.payload.view(torch.uint8))
+    assert torch.equal(cg.scales.cpu(), cc.scales)
+    # swap out to a pinned host pool and back
+    host = ops.KVCache(L, 4, Hkv, page, D, ops.KV_FP8_SCALED, "cpu", pin_memory=True)
+    ops.kv_page_copy(cg, host, [5, 2], [0, 3])
+    torch.cuda.synchronize()
+    assert torch.equal(host.payload[:, :, 0].view(torch.uint8), cc.payload[:, :, 5].view(torch.uint8))
+    cg.payload.view(torch.uint8)[:, :, 9] = 0
+    ops.kv_page_copy(host, cg, [3], [9])
+    torch.cuda.synchronize()
+    assert torch.equal(cg.payload[:, :, 9].cpu().view(torch.uint8), cc.payload[:, :, 2].view(torch.uint8))
+    assert torch.equal(cg.scales[:, :, 9].cpu(), cc.scales[:, :, 2])
+
+
+def test_sampler(cuda_device):
+    B, V = 6, 151936
+    logits = torch.randn(B, V)
+    logits[2, 777] = logits[2, 90000] = 50.0  # tie -> lowest id
+    tok = ops.sample(logits.cuda())
+    assert tok.cpu().tolist() == logits.argmax(-1).tolist() and tok[2].item() == 777
+    slabs = torch.stack((logits * 0.5, logits * 0.5)).cuda()
+    val = torch.empty(B, device="cuda")
+    tok2 = ops.sample(slabs, vocab_offset=1000, out_val=val)
+    assert (tok2.cpu() - 1000).tolist() == logits.argmax(-1).tolist()
+    close(val, logits.max(-1).values, 1e-5, 1e-5, "max value")
+    # temperature sampling follows softmax(logits / T)
+    small = torch.tensor([[2.0, 1.0, 0.0, -1.0]]).repeat(4096, 1)
+    temp = torch.full((4096,), 0.7)
+    draws = ops.sample(small.cuda(), temp.cuda(), seed=1234)
+    freq = torch.bincount(draws.cpu(), minlength=4).float() / 4096
+    want = torch.softmax(small[0] / 0.7, -1)
+    assert (freq - want).abs().max() < 0.03, (freq, want)
+    mixed = ops.sample(small.cuda(), torch.zeros(4096).cuda())
+    assert int(mixed.sum()) == 0
+
+
+def test_vision_pointwise(cuda_device):
+    from prism_infer_b200.models.position import vision_patch_coords, vision_pos_embed_plan
+    grid = [(1, 6, 8), (2, 4, 4)]
+    idx, wt = vision_pos_embed_plan(grid, 16, 2)
+    N = idx.shape[1]
+    x, table = rand_bf16(N, 128, seed=33), rand_bf16(256, 128, seed=34)
+    yg = ops.pos_embed_add(x.clone().cuda(), table.cuda(), idx.cuda(), wt.cuda())
+    yc = ops.pos_embed_add(x.float().clone(), table.float(), idx, wt)
+    close(yg, yc, 3e-2, 1e-2, "pos embed")
+    heads, hd = 4, 32
+    qkv = rand_bf16(N, 3 * heads * hd, seed=35)
+    coords = vision_patch_coords(grid, 2).int()
+    inv = 1.0 / (10000.0 ** (torch.arange(0, hd // 2, 2).float() / (hd // 2)))
+    rg = ops.vit_rope(qkv.clone().cuda(), coords.cuda(), inv.cuda(), heads, hd)
+    rc = ops.vit_rope(qkv.float().clone(), coords, inv, heads, hd)
+    close(rg, rc, 3e-2, 1e-2, "vit rope")
