@@ -1,0 +1,108 @@
+"""Applies one ``BatchPlan`` (reference ``prism_infer/engine/executor.py:27-209``).
+
+Order inside a step: page transfers (prefix-row copies, copy-on-write, swap-out,
+swap-in), model execution on every rank, then for prefill sequences that just reached
+their multimodal prefix boundary: visual-token compaction (plan, device copy, commit) and
+publication of the prefix to the cache (which may add a tail-clone copy).  Every device
+action goes through ``runner.call`` so tensor-parallel ranks stay in lock step.
+"""
+
+from __future__ import annotations
+
+import time
+
+from .block_manager import BlockManager
+from .contracts import BatchPlan, ExecutionResult, KVTransferPlan, Phase
+from .input_preparation import ModelInputPreparer
+from .visual_pruning import PruningConfig, compute_pruning_decision, retained_positions
+from ..observability import emit_kv_event, profile_region
+
+
+class LocalRunnerGroup:
+    """Single-rank dispatch: direct method calls on the in-process runner."""
+
+    def __init__(self, runner) -> None:
+        self.runner = runner
+
+    def call(self, method: str, *args):
+        return getattr(self.runner, method)(*args)
+
+    def close(self) -> None:
+        self.runner.exit()
+
+
+class ModelExecutor:
+    def __init__(self, config, runners, block_manager: BlockManager) -> None:
+        self.config = config
+        self.runners = runners
+        self.bm = block_manager
+        self.preparer = ModelInputPreparer(config.kvcache_block_size, -(-config.max_model_len // config.kvcache_block_size))
+        self.compact = config.compacts_visual_tokens
+        self.pruning = PruningConfig(config.visual_pruning_keep_ratio, config.visual_pruning_min_keep_tokens,
+                                     config.visual_pruning_video_min_keep_tokens,
+                                     "uniform" if config.visual_pruning_strategy == "attention" else config.visual_pruning_strategy)
+        self._have_visual: set[int] = set()
+
+    def execute(self, plan: BatchPlan) -> ExecutionResult:
+        t0 = time.perf_counter()
+        if not plan.kv_transfers.empty:
+            self.runners.call("apply_kv_transfers", plan.kv_transfers)
+        if plan.is_idle:
+            return ExecutionResult((), (time.perf_counter() - t0) * 1e3)
+        with profile_region("engine.model_runner", metadata={"phase": plan.phase.value, "batch": plan.batch_size}):
+            inputs = self.preparer.prepare(plan, self._have_visual)
+            for job in inputs.vision_jobs:
+                self._have_visual.add(job.seq_id)
+            for sid in inputs.release_visual:
+                self._have_visual.discard(sid)
+            sampled = self.runners.call("execute", inputs)
+        tokens: list[int | None] = [None] * plan.batch_size
+        if plan.phase is Phase.PREFILL:
+            for i, tok in zip(inputs.sample_seq, sampled):
+                tokens[i] = int(tok)
+        else:
+            tokens = [int(t) for t in sampled]
+        compactions = self._after_prefill(plan) if plan.phase is Phase.PREFILL else 0
+        return ExecutionResult(tuple(tokens), (time.perf_counter() - t0) * 1e3, compactions)
+
+    # ------------------------------------------------------------------------------
+    def _after_prefill(self, plan: BatchPlan) -> int:
+        """Compaction and prefix publication for sequences whose chunk ended on the boundary."""
+        plans = []
+        owners = []
+        for seq, sl in zip(plan.seqs, plan.slices):
+            boundary = seq.multimodal_prefix_boundary
+            if not seq.is_multimodal or boundary <= 0 or sl.end != boundary or sl.end >= len(seq):
+                continue
+            if self.compact and seq.kv_layout is None and seq.num_cached_tokens == 0:
+                decision = compute_pruning_decision(seq.token_ids, seq.image_token_id, seq.video_token_id, self.pruning,
+                                                    end=boundary)
+                if decision is not None and decision.dropped:
+                    # the scheduler has not advanced num_computed_tokens yet
+                    seq.num_computed_tokens += sl.length
+                    try:
+                        cp = self.bm.build_compaction_plan(seq, retained_positions(boundary, decision), boundary)
+                    finally:
+                        seq.num_computed_tokens -= sl.length
+                    if cp is not None:
+                        plans.append(cp)
+                        owners.append(seq)
+                        seq.pruning_record = {"kept": len(decision.kept), "dropped": len(decision.dropped),
+                                              "total": decision.total_visual_tokens}
+        if plans:
+            self.runners.call("compact_kv", plans)
+            for seq, cp in zip(owners, plans):
+                self.bm.commit_compaction(seq, cp)
+                emit_kv_event("compact", seq_id=seq.seq_id, rows=len(cp.src_slots), released=len(cp.released_blocks))
+        copies = []
+        for seq, sl in zip(plan.seqs, plan.slices):
+            boundary = seq.multimodal_prefix_boundary
+            if seq.is_multimodal and sl.end == boundary and sl.end < len(seq) and seq.multimodal_prefix_cache_key:
+                seq.num_computed_tokens += sl.length
+                try:
+                    copies.extend(self.bm.store_multimodal_prefix(seq))
+                finally:
+                    seq.num_computed_tokens -= sl.length
+        if copies:
+            self.runners.call("apply_kv_transfers", KVTransferPlan(copy_prefix=tuple(copies)))
+        return len(plans)

@@ -1,0 +1,154 @@
+"""Host-side construction of one step's model inputs (reference
+``prism_infer/engine/input_preparation.py:51-668``).
+
+``StepInputs`` is a flat bundle of CPU tensors and small integers: it is what rank 0 hands
+to its own runner and ships to the tensor-parallel workers, so workers never need
+``Sequence`` objects.  Slot mappings and context lengths use *physical* KV positions
+(after compaction), M-RoPE positions use logical ones.
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Optional
+
+import torch
+
+from .contracts import BatchPlan, Phase
+from .sequence import Sequence
+
+
+@dataclass
+class VisionJob:
+    """Patches one sequence still has to push through the vision tower."""
+
+    seq_id: int
+    pixel_values: torch.Tensor            # [N, patch_dim]
+    grid_thw: list[tuple[int, int, int]]
+    cache_key: Optional[str] = None
+
+
+@dataclass
+class StepInputs:
+    kind: str                              # "prefill" | "decode"
+    input_ids: torch.Tensor                # [T] int64
+    positions: torch.Tensor                # [3, T] int32
+    slots: torch.Tensor                    # [T] int64
+    block_tables: torch.Tensor             # [S, max_blocks] int32
+    temperatures: torch.Tensor             # [S] fp32 (0 = greedy)
+    # prefill only
+    cu_seqlens_q: Optional[torch.Tensor] = None   # [S+1] int32
+    kv_lens: Optional[torch.Tensor] = None        # [S] int32
+    max_q_len: int = 0
+    sample_rows: Optional[torch.Tensor] = None    # [n] int64 flattened row of each finishing sequence
+    sample_seq: list[int] = field(default_factory=list)   # index into the plan of those sequences
+    vis_index: Optional[torch.Tensor] = None      # [T] int32
+    vision_jobs: list[VisionJob] = field(default_factory=list)
+    vision_rows: list[tuple[int, int, int]] = field(default_factory=list)  # (seq_id, first row, rows) in vis order
+    release_visual: list[int] = field(default_factory=list)
+    # decode only
+    context_lens: Optional[torch.Tensor] = None   # [B] int32
+
+    @property
+    def num_tokens(self) -> int:
+        return int(self.input_ids.shape[0])
+
+    @property
+    def num_seqs(self) -> int:
+        return int(self.block_tables.shape[0])
+
+
+class ModelInputPreparer:
+    def __init__(self, page: int, max_blocks: int) -> None:
+        self.page = page
+        self.max_blocks = max_blocks
+
+    def _block_table(self, seqs: tuple[Sequence, ...]) -> torch.Tensor:
+        width = max(1, max(len(s.block_table) for s in seqs))
+        bt = torch.full((len(seqs), width), -1, dtype=torch.int32)
+        for i, s in enumerate(seqs):
+            if s.block_table:
+                bt[i, : len(s.block_table)] = torch.tensor(s.block_table, dtype=torch.int32)
+        return bt
+
+    def prepare(self, plan: BatchPlan, have_visual: set[int] | None = None) -> StepInputs:
+        if plan.phase is Phase.PREFILL:
+            return self.prepare_prefill(plan, have_visual or set())
+        return self.prepare_decode(plan)
+
+    def prepare_prefill(self, plan: BatchPlan, have_visual: set[int]) -> StepInputs:
+        ids: list[int] = []
+        pos_parts: list[torch.Tensor] = []
+        slots: list[int] = []
+        cu = [0]
+        kv_lens: list[int] = []
+        sample_rows: list[int] = []
+        sample_seq: list[int] = []
+        vis_index: list[int] = []
+        vision_jobs: list[VisionJob] = []
+        vision_rows: list[tuple[int, int, int]] = []
+        release: list[int] = []
+        vis_cursor = 0
+        any_visual = False
+        for i, (seq, sl) in enumerate(zip(plan.seqs, plan.slices)):
+            start, end = sl.start, sl.end
+            ids.extend(seq.token_ids[start:end])
+            pos_parts.append(seq.positions_for(start, end))
+            slots.extend(seq.slot_of(j) for j in range(start, end))
+            cu.append(cu[-1] + sl.length)
+            kv_lens.append(seq.physical_len(end))
+            if end == len(seq):
+                sample_rows.append(cu[-1] - 1)
+                sample_seq.append(i)
+            lo, hi = seq.visual_index_range(start, end) if seq.is_multimodal else (0, 0)
+            if hi > lo:
+                any_visual = True
+                if seq.seq_id not in have_visual and seq.pixel_values is not None:
+                    grids = list(seq.image_grid_thw) + list(seq.video_grid_thw)
+                    vision_jobs.append(VisionJob(seq.seq_id, seq.pixel_values, grids, seq.visual_embedding_cache_key))
+                vision_rows.append((seq.seq_id, lo, hi - lo))
+                cursor = vis_cursor
+                for tok in seq.token_ids[start:end]:
+                    if tok == seq.image_token_id or tok == seq.video_token_id:
+                        vis_index.append(cursor)
+                        cursor += 1
+                    else:
+                        vis_index.append(-1)
+                vis_cursor = cursor
+            else:
+                vis_index.extend([-1] * sl.length)
+            if seq.is_multimodal and end >= seq.multimodal_prefix_boundary:
+                release.append(seq.seq_id)
+        temps = torch.tensor([plan.seqs[i].temperature for i in sample_seq], dtype=torch.float32)
+        return StepInputs(
+            kind="prefill",
+            input_ids=torch.tensor(ids, dtype=torch.int64),
+            positions=torch.cat(pos_parts, dim=1).to(torch.int32).contiguous(),
+            slots=torch.tensor(slots, dtype=torch.int64),
+            block_tables=self._block_table(plan.seqs),
+            temperatures=temps,
+            cu_seqlens_q=torch.tensor(cu, dtype=torch.int32),
+            kv_lens=torch.tensor(kv_lens, dtype=torch.int32),
+            max_q_len=max(s.length for s in plan.slices),
+            sample_rows=torch.tensor(sample_rows, dtype=torch.int64),
+            sample_seq=sample_seq,
+            vis_index=torch.tensor(vis_index, dtype=torch.int32) if any_visual else None,
+            vision_jobs=vision_jobs,
+            vision_rows=vision_rows,
+            release_visual=release,
+        )
+
+    def prepare_decode(self, plan: BatchPlan) -> StepInputs:
+        seqs = plan.seqs
+        n = len(seqs)
+        ids = torch.tensor([s.last_token for s in seqs], dtype=torch.int64)
+        p = torch.tensor([len(s) - 1 + s.rope_delta for s in seqs], dtype=torch.int32)
+        return StepInputs(
+            kind="decode",
+            input_ids=ids,
+            positions=p.expand(3, n).contiguous(),
+            slots=torch.tensor([s.slot_of(len(s) - 1) for s in seqs], dtype=torch.int64),
+            block_tables=self._block_table(seqs),
+            temperatures=torch.tensor([s.temperature for s in seqs], dtype=torch.float32),
+            context_lens=torch.tensor([s.physical_len() for s in seqs], dtype=torch.int32),
+        )

@@ -1,0 +1,304 @@
+"""Engine orchestrator behind the public ``LLM`` class (reference
+``prism_infer/engine/llm_engine.py:146-1538``).
+
+Builds the configuration, starts the tensor-parallel ranks, owns tokenizer, processor,
+scheduler and executor, and exposes request submission (``add_*_request``), the step loop
+(``step_result`` / ``step`` / ``is_finished``), cancellation, metrics and the synchronous
+``generate*`` helpers.  Generation results are dictionaries with ``text``, ``raw_text`` and
+``token_ids``.
+"""
+
+from __future__ import annotations
+
+import atexit
+import hashlib
+import time
+from typing import Any, Sequence as Seq
+
+import torch
+
+from ..config import Config
+from ..models.position import rope_index
+from ..observability import profile_region, profile_step_metadata
+from ..sampling_params import SamplingParams
+from ..utils.tokenizer import load_tokenizer
+from .contracts import BatchPlan, Phase, RequestOutput, StepResult
+from .executor import LocalRunnerGroup, ModelExecutor
+from .input_preparation import VisionJob
+from .metrics import EngineMetrics
+from .request import RequestIdAllocator, RequestState
+from .scheduler import Scheduler
+from .sequence import Sequence
+from .vl_inputs import (ImageInputs, PatchProcessor, VideoInputs, prepare_image_inputs,
+                        prepare_interleaved_image_inputs, prepare_video_inputs)
+
+
+def content_key(*parts: Any) -> str:
+    """Content-addressed key over tensors / arrays / bytes / strings."""
+    h = hashlib.sha256()
+    for p in parts:
+        if isinstance(p, torch.Tensor):
+            h.update(str(tuple(p.shape)).encode())
+            h.update(p.detach().cpu().contiguous().view(torch.uint8).numpy().tobytes())
+        elif isinstance(p, (bytes, bytearray)):
+            h.update(bytes(p))
+        else:
+            h.update(repr(p).encode())
+    return h.hexdigest()
+
+
+class LLMEngine:
+    def __init__(self, model: str, *, runner_group=None, weights: dict[str, torch.Tensor] | None = None,
+                 device: str | None = None, **kwargs: Any) -> None:
+        self.config = Config(model, **kwargs)
+        cfg = self.config
+        self.arch = cfg.arch
+        self.tokenizer = load_tokenizer(cfg.model, self.arch)
+        self.processor = PatchProcessor(self.arch, min_pixels=cfg.image_min_pixels, max_pixels=cfg.image_max_pixels,
+                                        video_max_pixels=cfg.video_max_pixels)
+        self._ids = RequestIdAllocator()
+        self.metrics = EngineMetrics()
+        self._closed = False
+        if runner_group is not None:
+            self.runners = runner_group
+        elif cfg.tp > 1:
+            from ..parallel.launch import start_tensor_parallel_group
+
+            self.runners = start_tensor_parallel_group(cfg, weights=weights)
+        else:
+            from .model_runner import ModelRunner
+
+            self.runners = LocalRunnerGroup(ModelRunner(cfg, device=device, weights=weights))
+        # the runner resolved the KV capacity into the config
+        self.scheduler = Scheduler(cfg, metrics=self.metrics)
+        self.executor = ModelExecutor(cfg, self.runners, self.scheduler.block_manager)
+        self._sequences: dict[int, Sequence] = {}
+        atexit.register(self.exit)
+
+    # ------------------------------------------------------------------- lifecycle
+    def exit(self) -> None:
+        if self._closed:
+            return
+        self._closed = True
+        try:
+            self.runners.close()
+        except Exception:  # pragma: no cover - shutdown must not raise
+            pass
+
+    # ------------------------------------------------------------------ submission
+    def _sampling(self, sp: SamplingParams | None) -> SamplingParams:
+        return sp if sp is not None else SamplingParams()
+
+    def _submit(self, seq: Sequence, *, raise_on_reject: bool = True) -> int:
+        cfg = self.config
+        seq.arrival_ns = seq.arrival_ns or time.perf_counter_ns()
+        self.metrics.on_request_submitted(seq)
+        self._sequences[seq.seq_id] = seq
+        hit = None
+        if seq.is_multimodal and seq.multimodal_prefix_cache_key:
+            hit = self.scheduler.block_manager.probe_multimodal_prefix(seq)
+        if (cfg.enable_visual_embedding_cache and cfg.tp == 1 and seq.is_multimodal and hit is None
+                and seq.pixel_values is not None and seq.visual_embedding_cache_key):
+            grids = list(seq.image_grid_thw) + list(seq.video_grid_thw)
+            self.runners.call("hydrate_visual_embedding", VisionJob(seq.seq_id, seq.pixel_values, grids,
+                                                                    seq.visual_embedding_cache_key))
+        if not self.scheduler.add(seq):
+            self.metrics.on_request_finished(seq)
+            if raise_on_reject:
+                raise ValueError(f"request rejected: {seq.lifecycle.finish_reason}")
+        return seq.seq_id
+
+    def add_request(self, prompt: str | Seq[int], sampling_params: SamplingParams | None = None, *,
+                    raise_on_reject: bool = True) -> int:
+        ids = self.tokenizer.encode(prompt) if isinstance(prompt, str) else [int(t) for t in prompt]
+        seq = Sequence(self._ids(), ids, self._sampling(sampling_params), image_token_id=self.arch.image_token_id,
+                       video_token_id=self.arch.video_token_id)
+        return self._submit(seq, raise_on_reject=raise_on_reject)
+
+    def _multimodal_sequence(self, inputs: ImageInputs | VideoInputs, sp: SamplingParams | None,
+                             media_key: str | None = None) -> Sequence:
+        arch = self.arch
+        image_grid = getattr(inputs, "image_grid_thw", None)
+        video_grid = getattr(inputs, "video_grid_thw", None)
+        inputs.validate(arch)
+        pos, delta = rope_index(inputs.input_ids, image_grid_thw=image_grid, video_grid_thw=video_grid,
+                                image_token_id=arch.image_token_id, video_token_id=arch.video_token_id,
+                                spatial_merge_size=arch.vision.spatial_merge_size)
+        seq = Sequence(self._ids(), inputs.input_ids, self._sampling(sp), image_token_id=arch.image_token_id,
+                       video_token_id=arch.video_token_id, pixel_values=inputs.pixel_values,
+                       image_grid_thw=image_grid, video_grid_thw=video_grid, position_ids=pos[:, 0, :],
+                       rope_delta=delta, merge_size=arch.vision.spatial_merge_size)
+        if self.config.enable_prefix_caching or self.config.enable_visual_embedding_cache:
+            key = media_key or content_key(inputs.pixel_values, image_grid, video_grid)
+            seq.visual_embedding_cache_key = key
+            if self.config.enable_prefix_caching:
+                seq.multimodal_prefix_cache_key = key
+        return seq
+
+    def add_prepared_image_request(self, inputs: ImageInputs, sampling_params: SamplingParams | None = None, *,
+                                   media_key: str | None = None, raise_on_reject: bool = True) -> int:
+        return self._submit(self._multimodal_sequence(inputs, sampling_params, media_key), raise_on_reject=raise_on_reject)
+
+    def add_prepared_video_request(self, inputs: VideoInputs, sampling_params: SamplingParams | None = None, *,
+                                   media_key: str | None = None, raise_on_reject: bool = True) -> int:
+        return self._submit(self._multimodal_sequence(inputs, sampling_params, media_key), raise_on_reject=raise_on_reject)
+
+    def add_vl_request(self, prompt: str | Seq[int], image: Any, sampling_params: SamplingParams | None = None, **kw) -> int:
+        with profile_region("preprocess.image", cuda=False):
+            inputs = prepare_image_inputs(self.processor, self.tokenizer, prompt, [image])
+        return self.add_prepared_image_request(inputs, sampling_params, **kw)
+
+    def add_images_request(self, prompt: str | Seq[int], images: Seq[Any], sampling_params: SamplingParams | None = None, **kw) -> int:
+        with profile_region("preprocess.images", cuda=False):
+            inputs = prepare_image_inputs(self.processor, self.tokenizer, prompt, list(images))
+        return self.add_prepared_image_request(inputs, sampling_params, **kw)
+
+    def add_interleaved_images_request(self, prompt: str, images: Seq[Any], sampling_params: SamplingParams | None = None,
+                                       *, image_marker: str = "<image>", **kw) -> int:
+        with profile_region("preprocess.interleaved_images", cuda=False):
+            inputs = prepare_interleaved_image_inputs(self.processor, self.tokenizer, prompt, list(images), image_marker)
+        return self.add_prepared_image_request(inputs, sampling_params, **kw)
+
+    def add_video_request(self, prompt: str | Seq[int], frames: Seq[Any], sampling_params: SamplingParams | None = None, **kw) -> int:
+        with profile_region("preprocess.video", cuda=False):
+            inputs = prepare_video_inputs(self.processor, self.tokenizer, prompt, list(frames))
+        return self.add_prepared_video_request(inputs, sampling_params, **kw)
+
+    # ------------------------------------------------------------------------ step
+    def step_result(self) -> StepResult:
+        with profile_region("engine.step", cuda=False):
+            with profile_region("engine.scheduler.schedule", cuda=False):
+                plan = self.scheduler.schedule()
+            if plan.is_idle and plan.kv_transfers.empty:
+                return StepResult(Phase.IDLE)
+            profile_step_metadata({"phase": plan.phase.value, "batch_size": plan.batch_size, "tokens": plan.num_tokens,
+                                   "vision_patches": plan.num_vision_patches})
+            result = self.executor.execute(plan)
+            if plan.is_idle:
+                return StepResult(Phase.IDLE)
+            with profile_region("engine.scheduler.postprocess", cuda=False):
+                outputs = self.scheduler.postprocess(plan, result.tokens)
+            self.metrics.on_batch_completed(plan, result.duration_ms, result.compactions)
+            for o in outputs:
+                if o.finished:
+                    self._sequences.pop(o.request_id, None)
+            return StepResult(plan.phase, tuple(outputs), plan.num_tokens)
+
+    def step(self) -> tuple[list[tuple[int, list[int]]], int]:
+        """Compatibility form: ``([(request_id, completion_token_ids), ...], signed token count)``
+        where the count is positive for prefill and negative for decode."""
+        res = self.step_result()
+        done = [(o.request_id, list(o.token_ids)) for o in res.finished]
+        return done, (res.num_tokens if res.phase is Phase.PREFILL else -res.num_tokens)
+
+    def is_finished(self) -> bool:
+        return self.scheduler.is_finished()
+
+    def cancel_request(self, request_id: int) -> bool:
+        ok = self.scheduler.cancel(request_id)
+        self._sequences.pop(request_id, None)
+        return ok
+
+    def request_state(self, request_id: int) -> RequestState | None:
+        seq = self._sequences.get(request_id) or self.scheduler.find(request_id)
+        return seq.state if seq is not None else None
+
+    # --------------------------------------------------------------------- metrics
+    def metrics_snapshot(self) -> dict[str, object]:
+        return {"engine": self.metrics.snapshot(), "scheduler": self.scheduler.metrics_snapshot()}
+
+    def reset_metrics(self) -> None:
+        self.metrics.reset()
+
+    def multimodal_prefix_cache_metadata(self) -> dict[str, object]:
+        meta = self.scheduler.block_manager.prefix_cache_metadata()
+        per_page = self.config.kv_bytes_per_page()
+        meta["resident_bytes"] = int(meta["resident_pages"]) * per_page
+        meta["bytes_per_page"] = per_page
+        return meta
+
+    def visual_embedding_cache_metadata(self) -> dict[str, object]:
+        return self.runners.call("visual_embedding_cache_metadata")
+
+    def graph_metadata(self) -> dict[str, object]:
+        return self.runners.call("graph_metadata")
+
+    # -------------------------------------------------------------------- generate
+    def _format(self, token_ids: list[int]) -> dict[str, Any]:
+        raw = self.tokenizer.decode(token_ids, skip_special_tokens=False)
+        text = self.tokenizer.decode(token_ids, skip_special_tokens=True)
+        return {"text": text, "raw_text": raw, "token_ids": list(token_ids)}
+
+    def _run_until_done(self, ids: list[int]) -> dict[int, list[int]]:
+        want = set(ids)
+        out: dict[int, list[int]] = {}
+        while want - set(out):
+            res = self.step_result()
+            for o in res.finished:
+                out[o.request_id] = list(o.token_ids)
+            if res.phase is Phase.IDLE and self.is_finished():
+                break
+        for rid in want - set(out):  # rejected or cancelled
+            out[rid] = []
+        return out
+
+    def _broadcast_sp(self, n: int, sp) -> list[SamplingParams | None]:
+        if isinstance(sp, (list, tuple)):
+            if len(sp) != n:
+                raise ValueError("one SamplingParams per prompt is required")
+            return list(sp)
+        return [sp] * n
+
+    def generate(self, prompts: Seq[str] | Seq[Seq[int]], sampling_params=None, use_tqdm: bool = False) -> list[dict[str, Any]]:
+        sps = self._broadcast_sp(len(prompts), sampling_params)
+        ids = [self.add_request(p, sp) for p, sp in zip(prompts, sps)]
+        done = self._run_until_done(ids)
+        return [self._format(done[i]) for i in ids]
+
+    def generate_vl(self, prompt, image, sampling_params=None) -> dict[str, Any]:
+        rid = self.add_vl_request(prompt, image, sampling_params)
+        return self._format(self._run_until_done([rid])[rid])
+
+    def generate_images(self, prompt, images, sampling_params=None) -> dict[str, Any]:
+        rid = self.add_images_request(prompt, images, sampling_params)
+        return self._format(self._run_until_done([rid])[rid])
+
+    def generate_interleaved_images(self, prompt, images, sampling_params=None, *, image_marker: str = "<image>") -> dict[str, Any]:
+        rid = self.add_interleaved_images_request(prompt, images, sampling_params, image_marker=image_marker)
+        return self._format(self._run_until_done([rid])[rid])
+
+    def generate_video(self, prompt, frames, sampling_params=None) -> dict[str, Any]:
+        rid = self.add_video_request(prompt, frames, sampling_params)
+        return self._format(self._run_until_done([rid])[rid])
+
+    def generate_prepared_image_inputs(self, inputs: ImageInputs, sampling_params=None) -> dict[str, Any]:
+        rid = self.add_prepared_image_request(inputs, sampling_params)
+        return self._format(self._run_until_done([rid])[rid])
+
+    def generate_prepared_video_inputs(self, inputs: VideoInputs, sampling_params=None) -> dict[str, Any]:
+        rid = self.add_prepared_video_request(inputs, sampling_params)
+        return self._format(self._run_until_done([rid])[rid])
+
+    def generate_mixed(self, requests: Seq[dict[str, Any]], sampling_params=None) -> list[dict[str, Any]]:
+        """Batch of heterogeneous requests: each dict has ``type`` in ``text | image | images |
+        interleaved_images | video`` plus ``prompt`` and the matching media field."""
+        sps = self._broadcast_sp(len(requests), sampling_params)
+        ids = []
+        for req, sp in zip(requests, sps):
+            kind = req.get("type", "text")
+            sp = req.get("sampling_params", sp)
+            if kind == "text":
+                ids.append(self.add_request(req["prompt"], sp))
+            elif kind == "image":
+                ids.append(self.add_vl_request(req["prompt"], req["image"], sp))
+            elif kind == "images":
+                ids.append(self.add_images_request(req["prompt"], req["images"], sp))
+            elif kind == "interleaved_images":
+                ids.append(self.add_interleaved_images_request(req["prompt"], req["images"], sp,
+                                                               image_marker=req.get("image_marker", "<image>")))
+            elif kind == "video":
+                ids.append(self.add_video_request(req["prompt"], req.get("frames", req.get("video")), sp))
+            else:
+                raise ValueError(f"unknown request type {kind!r}")
+        done = self._run_until_done(ids)
+        return [self._format(done[i]) for i in ids]

@@ -1,0 +1,106 @@
+"""Thread-safe per-request and per-batch metrics ledger (reference
+``prism_infer/engine/metrics.py:17-231``): queue time, TTFT, mean TPOT, inter-token
+latencies, end-to-end latency, cached tokens, finish reason; batch phase / size / tokens /
+patches / duration / compactions."""
+
+from __future__ import annotations
+
+import threading
+import time
+from dataclasses import dataclass, field
+from typing import Callable
+
+from .contracts import BatchPlan
+from .sequence import Sequence
+
+
+@dataclass
+class RequestMetrics:
+    request_id: int
+    prompt_tokens: int
+    submitted_ns: int
+    scheduled_ns: int | None = None
+    first_token_ns: int | None = None
+    last_token_ns: int | None = None
+    finished_ns: int | None = None
+    cached_tokens: int = 0
+    output_tokens: int = 0
+    finish_reason: str | None = None
+    inter_token_ms: list[float] = field(default_factory=list)
+
+    def record(self) -> dict[str, object]:
+        ms = lambda a, b: None if a is None or b is None else (b - a) / 1e6  # noqa: E731
+        tpot = sum(self.inter_token_ms) / len(self.inter_token_ms) if self.inter_token_ms else None
+        return {
+            "request_id": self.request_id, "prompt_tokens": self.prompt_tokens, "cached_tokens": self.cached_tokens,
+            "output_tokens": self.output_tokens, "queue_ms": ms(self.submitted_ns, self.scheduled_ns),
+            "ttft_ms": ms(self.submitted_ns, self.first_token_ns), "tpot_ms": tpot,
+            "inter_token_ms": list(self.inter_token_ms), "latency_ms": ms(self.submitted_ns, self.finished_ns),
+            "finish_reason": self.finish_reason,
+        }
+
+
+class EngineMetrics:
+    def __init__(self, clock_ns: Callable[[], int] = time.perf_counter_ns) -> None:
+        self._clock = clock_ns
+        self._lock = threading.Lock()
+        self.requests: dict[int, RequestMetrics] = {}
+        self.batches: list[dict[str, object]] = []
+
+    def reset(self) -> None:
+        with self._lock:
+            self.requests.clear()
+            self.batches.clear()
+
+    def on_request_submitted(self, seq: Sequence) -> None:
+        with self._lock:
+            t = seq.arrival_ns if seq.arrival_ns is not None else self._clock()
+            self.requests[seq.seq_id] = RequestMetrics(seq.seq_id, seq.num_prompt_tokens, t)
+
+    def on_request_scheduled(self, seq: Sequence) -> None:
+        with self._lock:
+            m = self.requests.get(seq.seq_id)
+            if m is not None and m.scheduled_ns is None:
+                m.scheduled_ns = self._clock()
+                m.cached_tokens = seq.num_cached_tokens
+
+    def on_tokens(self, seq: Sequence, n: int = 1) -> None:
+        with self._lock:
+            m = self.requests.get(seq.seq_id)
+            if m is None:
+                return
+            now = self._clock()
+            if m.first_token_ns is None:
+                m.first_token_ns = now
+            elif m.last_token_ns is not None:
+                m.inter_token_ms.append((now - m.last_token_ns) / 1e6 / max(1, n))
+            m.last_token_ns = now
+            m.output_tokens += n
+
+    def on_request_finished(self, seq: Sequence) -> None:
+        with self._lock:
+            m = self.requests.get(seq.seq_id)
+            if m is not None:
+                m.finished_ns = self._clock()
+                m.finish_reason = seq.lifecycle.finish_reason
+
+    def on_batch_completed(self, plan: BatchPlan, duration_ms: float, compactions: int = 0) -> None:
+        with self._lock:
+            self.batches.append({
+                "phase": plan.phase.value, "batch_size": plan.batch_size, "tokens": plan.num_tokens,
+                "vision_patches": plan.num_vision_patches, "duration_ms": duration_ms, "compactions": compactions,
+            })
+
+    def snapshot(self) -> dict[str, object]:
+        with self._lock:
+            return {"requests": [m.record() for m in self.requests.values()], "batches": list(self.batches)}
+
+
+class NullMetrics:
+    def on_request_submitted(self, seq): ...
+    def on_request_scheduled(self, seq): ...
+    def on_tokens(self, seq, n=1): ...
+    def on_request_finished(self, seq): ...
+    def on_batch_completed(self, plan, duration_ms, compactions=0): ...
+    def reset(self): ...
+    def snapshot(self): return {"requests": [], "batches": []}

@@ -1,0 +1,330 @@
+"""Per-rank owner of the model weights, the KV arena and the decode CUDA graphs
+(reference ``prism_infer/engine/model_runner.py``: KV sizing ``:795-815``, allocation
+``:817-890``, page copies ``:908-1031``, graph capture ``:1131-1158,2082-2127``, replay
+with packed staging ``:1219-1313``).
+
+B200-specific choices:
+
+* One KV allocation ``[2, L, pages, Hkv/tp, page, D]`` (+ fp32 scales), sized from free HBM,
+  head-major inside a page so each (page, head) is one contiguous 32 KB run of E4M3 bytes.
+* Decode runs as one CUDA graph per batch bucket (1, 2, 4, 8, 16, 32, ...).  A single packed
+  pinned host buffer is copied to the device by a memcpy node *inside* the graph, and the
+  sampled tokens are copied back to pinned memory by another node, so a step is: fill the
+  pinned buffer, replay, wait on the stream, read the tokens.  One graph per bucket serves
+  greedy and temperature sampling (temperature is an input) and every context length (the
+  attention loop bound is read from device memory).
+* Kernels are launched with programmatic stream serialization so a GEMM prefetches its
+  weight tiles while the previous kernel drains.
+"""
+
+from __future__ import annotations
+
+import time
+from typing import Optional, Sequence as Seq
+
+import torch
+
+from .. import ops
+from ..config import Config
+from ..models.qwen3_vl import AttnMeta, Qwen3VLModel, TPComm
+from ..models.weights import open_weight_source
+from ..observability import profile_region
+from .contracts import KVTransferPlan
+from .input_preparation import StepInputs
+from .kv_layout import CompactionPlan
+
+
+def decode_buckets(max_num_seqs: int) -> list[int]:
+    out = [b for b in (1, 2, 4, 8) if b <= max_num_seqs]
+    b = 16
+    while b < max_num_seqs:
+        out.append(b)
+        b *= 2
+    if not out or out[-1] < max_num_seqs:
+        out.append(max_num_seqs)
+    return sorted(set(out))
+
+
+class _DecodeGraph:
+    """Static buffers + captured graph of one batch bucket."""
+
+    def __init__(self, runner: "ModelRunner", bucket: int) -> None:
+        self.bucket = bucket
+        dev = runner.device
+        mb = runner.max_blocks
+        # byte layout of the packed staging buffer (all offsets 16-byte aligned)
+        def al(x: int) -> int:
+            return (x + 15) // 16 * 16
+        self.off_ids = 0
+        self.off_slots = al(self.off_ids + bucket * 8)
+        self.off_pos = al(self.off_slots + bucket * 8)
+        self.off_ctx = al(self.off_pos + 3 * bucket * 4)
+        self.off_temp = al(self.off_ctx + bucket * 4)
+        self.off_bt = al(self.off_temp + bucket * 4)
+        self.nbytes = al(self.off_bt + bucket * mb * 4)
+        pin = runner.on_cuda
+        self.host = torch.zeros(self.nbytes, dtype=torch.uint8, pin_memory=pin)
+        self.dev = torch.zeros(self.nbytes, dtype=torch.uint8, device=dev)
+        self.h_ids, self.h_slots, self.h_pos, self.h_ctx, self.h_temp, self.h_bt = self._views(self.host, bucket, mb)
+        self.d_ids, self.d_slots, self.d_pos, self.d_ctx, self.d_temp, self.d_bt = self._views(self.dev, bucket, mb)
+        self.tokens = torch.zeros(bucket, dtype=torch.int64, device=dev)
+        self.tokens_host = torch.zeros(bucket, dtype=torch.int64, pin_memory=pin)
+        self.step = torch.zeros(1, dtype=torch.int64, device=dev)
+        self.graph: Optional[torch.cuda.CUDAGraph] = None
+        self.reset_rows(0)
+
+    def _views(self, buf: torch.Tensor, b: int, mb: int):
+        ids = buf[self.off_ids:self.off_ids + b * 8].view(torch.int64)
+        slots = buf[self.off_slots:self.off_slots + b * 8].view(torch.int64)
+        pos = buf[self.off_pos:self.off_pos + 3 * b * 4].view(torch.int32).view(3, b)
+        ctx = buf[self.off_ctx:self.off_ctx + b * 4].view(torch.int32)
+        temp = buf[self.off_temp:self.off_temp + b * 4].view(torch.float32)
+        bt = buf[self.off_bt:self.off_bt + b * mb * 4].view(torch.int32).view(b, mb)
+        return ids, slots, pos, ctx, temp, bt
+
+    def reset_rows(self, start: int) -> None:
+        """Padding rows: token 0, no slot, empty context, no pages."""
+        self.h_ids[start:] = 0
+        self.h_slots[start:] = -1
+        self.h_pos[:, start:] = 0
+        self.h_ctx[start:] = 0
+        self.h_temp[start:] = 0
+        self.h_bt[start:] = -1
+
+    def fill(self, inp: StepInputs) -> int:
+        n = inp.num_seqs
+        self.h_ids[:n] = inp.input_ids
+        self.h_slots[:n] = inp.slots
+        self.h_pos[:, :n] = inp.positions
+        self.h_ctx[:n] = inp.context_lens
+        self.h_temp[:n] = inp.temperatures
+        w = inp.block_tables.shape[1]
+        self.h_bt[:n, :w] = inp.block_tables
+        self.h_bt[:n, w:] = -1
+        self.reset_rows(n)
+        return n
+
+
+class ModelRunner:
+    def __init__(self, config: Config, *, rank: int = 0, comm: TPComm | None = None, device: str | None = None,
+                 weights: dict[str, torch.Tensor] | None = None) -> None:
+        self.config = config
+        self.rank = rank
+        self.comm = comm or TPComm()
+        self.on_cuda = torch.cuda.is_available() if device is None else str(device).startswith("cuda")
+        self.device = torch.device(device if device is not None else (f"cuda:{torch.cuda.current_device()}" if self.on_cuda else "cpu"))
+        self.dtype = torch.bfloat16 if self.on_cuda else torch.float32
+        arch = config.arch
+        if self.on_cuda:
+            from ..ops import native
+
+            native.lib()  # fail loudly when the kernel library is missing
+            ops.set_pdl(config.programmatic_dependent_launch)
+        with profile_region("runner.load_weights"):
+            self.model = Qwen3VLModel(arch, device=self.device, dtype=self.dtype, comm=self.comm)
+            source = weights.items() if weights is not None else open_weight_source(
+                config.model, arch, dtype=self.dtype, device=self.device, seed=config.seed)()
+            self.model.load(source)
+        self.page = config.kvcache_block_size
+        self.max_blocks = -(-config.max_model_len // self.page)
+        self.kv_mode = config.kv_mode
+        self._allocate_kv()
+        self._visual: dict[int, tuple[torch.Tensor, list[torch.Tensor]]] = {}
+        self._visual_cache: dict[str, tuple[torch.Tensor, list[torch.Tensor]]] = {}
+        self._visual_cache_bytes = 0
+        self.visual_cache_counters = {"hits": 0, "misses": 0, "evictions": 0}
+        self.graphs: dict[int, _DecodeGraph] = {}
+        self.buckets = decode_buckets(min(config.max_num_seqs, 512))
+        self.sample_seed = config.seed
+        self.steps_run = 0
+        if self.on_cuda and config.prism.execution.uses_graphs:
+            self.capture_graphs()
+
+    # ------------------------------------------------------------------ KV arena
+    def _allocate_kv(self) -> None:
+        cfg, t = self.config, self.config.arch.text
+        hkv = t.num_kv_heads // self.comm.size
+        per_page = cfg.kv_bytes_per_page()
+        blocks = cfg.num_kvcache_blocks
+        if blocks <= 0:
+            if self.on_cuda:
+                free, total = torch.cuda.mem_get_info(self.device)
+                reserve = 6 << 30  # activations of a full prefill chunk, vision tower, graph pools
+                budget = int(total * cfg.gpu_memory_utilization) - (total - free) - reserve
+                blocks = max(1, budget // per_page)
+            else:
+                blocks = max(8, 4 * self.max_blocks)
+        cpu_blocks = cfg.num_cpu_blocks
+        if cpu_blocks <= 0:
+            want = int(blocks * cfg.cpu_kv_cache_ratio)
+            cap = (4 << 30) // per_page if self.on_cuda else 64
+            cpu_blocks = min(want, cap)
+        self.kv = ops.KVCache(t.num_layers, blocks, hkv, self.page, t.head_dim, self.kv_mode, self.device, dtype=self.dtype)
+        self.cpu_kv = ops.KVCache(t.num_layers, max(1, cpu_blocks), hkv, self.page, t.head_dim, self.kv_mode, "cpu",
+                                  dtype=self.dtype, pin_memory=self.on_cuda) if cpu_blocks > 0 else None
+        cfg.with_cache_capacity(blocks, cpu_blocks)
+
+    # --------------------------------------------------------------- page traffic
+    def apply_kv_transfers(self, tr: KVTransferPlan) -> None:
+        """Order matters: prefix-row copies, copy-on-write, swap-out, swap-in."""
+        if tr.copy_prefix:
+            with profile_region("engine.kv.copy_prefix"):
+                ops.kv_page_copy(self.kv, self.kv, [s for s, _, _ in tr.copy_prefix], [d for _, d, _ in tr.copy_prefix],
+                                 [r for _, _, r in tr.copy_prefix])
+        if tr.copy_on_write:
+            with profile_region("engine.kv.copy_on_write"):
+                ops.kv_page_copy(self.kv, self.kv, [s for s, _ in tr.copy_on_write], [d for _, d in tr.copy_on_write])
+        if tr.swap_out:
+            with profile_region("engine.kv.swap_out"):
+                ops.kv_page_copy(self.kv, self.cpu_kv, [g for g, _ in tr.swap_out], [c for _, c in tr.swap_out])
+                if self.on_cuda:
+                    torch.cuda.current_stream().synchronize()
+        if tr.swap_in:
+            with profile_region("engine.kv.swap_in"):
+                ops.kv_page_copy(self.cpu_kv, self.kv, [c for c, _ in tr.swap_in], [g for _, g in tr.swap_in])
+
+    def compact_kv(self, plans: Seq[CompactionPlan]) -> None:
+        with profile_region("engine.kv.visual_compact"):
+            for plan in plans:
+                src = torch.tensor(plan.src_slots, dtype=torch.int64, device=self.device)
+                dst = torch.tensor(plan.dst_slots, dtype=torch.int64, device=self.device)
+                ops.kv_compact(self.kv, src, dst)
+
+    # ------------------------------------------------------------------- vision
+    def _encode(self, job) -> tuple[torch.Tensor, list[torch.Tensor]]:
+        key = job.cache_key if self.config.enable_visual_embedding_cache else None
+        if key is not None and key in self._visual_cache:
+            self.visual_cache_counters["hits"] += 1
+            val = self._visual_cache.pop(key)
+            self._visual_cache[key] = val  # LRU refresh
+            return val
+        with profile_region("model.vision.encoder"):
+            main, deep = self.model.encode_vision(job.pixel_values, job.grid_thw)
+        if key is not None:
+            self.visual_cache_counters["misses"] += 1
+            size = (1 + len(deep)) * main.numel() * main.element_size()
+            budget = self.config.visual_embedding_cache_bytes
+            while self._visual_cache and self._visual_cache_bytes + size > budget:
+                _, (m, d) = next(iter(self._visual_cache.items()))
+                self._visual_cache_bytes -= (1 + len(d)) * m.numel() * m.element_size()
+                self._visual_cache.pop(next(iter(self._visual_cache)))
+                self.visual_cache_counters["evictions"] += 1
+            if size <= budget:
+                self._visual_cache[key] = (main, deep)
+                self._visual_cache_bytes += size
+        return main, deep
+
+    def hydrate_visual_embedding(self, job) -> None:
+        """Run the vision tower ahead of scheduling and keep the result in the LRU cache."""
+        self._encode(job)
+
+    def visual_embedding_cache_metadata(self) -> dict[str, object]:
+        return {"enabled": self.config.enable_visual_embedding_cache, "entries": len(self._visual_cache),
+                "bytes": self._visual_cache_bytes, **self.visual_cache_counters}
+
+    # ------------------------------------------------------------------ execution
+    def execute(self, inp: StepInputs) -> list[int]:
+        """Run one step; returns the sampled token of every sampling row."""
+        self.steps_run += 1
+        if inp.kind == "prefill":
+            return self._run_prefill(inp)
+        if self.graphs and inp.num_seqs <= self.buckets[-1]:
+            return self._run_decode_graph(inp)
+        return self._run_decode_eager(inp)
+
+    def _to_dev(self, t: Optional[torch.Tensor]) -> Optional[torch.Tensor]:
+        if t is None or not self.on_cuda:
+            return t
+        return t.pin_memory().to(self.device, non_blocking=True)
+
+    def _run_prefill(self, inp: StepInputs) -> list[int]:
+        with profile_region("runner.prepare_inputs"):
+            for job in inp.vision_jobs:
+                self._visual[job.seq_id] = self._encode(job)
+            visual = deep = None
+            if inp.vision_rows:
+                mains, deeps = [], None
+                for seq_id, lo, n in inp.vision_rows:
+                    m, d = self._visual[seq_id]
+                    mains.append(m[lo:lo + n])
+                    if deeps is None:
+                        deeps = [[] for _ in d]
+                    for k, dk in enumerate(d):
+                        deeps[k].append(dk[lo:lo + n])
+                visual = mains[0] if len(mains) == 1 else torch.cat(mains)
+                deep = [dk[0] if len(dk) == 1 else torch.cat(dk) for dk in (deeps or [])]
+            meta = AttnMeta(
+                is_prefill=True, block_tables=self._to_dev(inp.block_tables), slots=self._to_dev(inp.slots),
+                cu_seqlens_q=self._to_dev(inp.cu_seqlens_q), kv_lens=self._to_dev(inp.kv_lens), max_q_len=inp.max_q_len)
+            ids, pos, vis_index = self._to_dev(inp.input_ids), self._to_dev(inp.positions), self._to_dev(inp.vis_index)
+        with profile_region("runner.run_model"):
+            hidden = self.model.forward(ids, pos, meta, self.kv, visual=visual, vis_index=vis_index, deepstack=deep)
+        for seq_id in inp.release_visual:
+            self._visual.pop(seq_id, None)
+        if inp.sample_rows is None or inp.sample_rows.numel() == 0:
+            if self.on_cuda:
+                torch.cuda.current_stream().synchronize()
+            return []
+        with profile_region("runner.sampler"):
+            rows = hidden[self._to_dev(inp.sample_rows)]
+            temps = self._to_dev(inp.temperatures) if bool((inp.temperatures > 0).any()) else None
+            step = torch.tensor([self.steps_run], dtype=torch.int64, device=self.device)
+            tok = self.model.sample(rows, temps, seed=self.sample_seed, step=step)
+        return tok.tolist()
+
+    def _run_decode_eager(self, inp: StepInputs) -> list[int]:
+        meta = AttnMeta(is_prefill=False, block_tables=self._to_dev(inp.block_tables), slots=self._to_dev(inp.slots),
+                        context_lens=self._to_dev(inp.context_lens))
+        hidden = self.model.forward(self._to_dev(inp.input_ids), self._to_dev(inp.positions), meta, self.kv)
+        temps = self._to_dev(inp.temperatures) if bool((inp.temperatures > 0).any()) else None
+        step = torch.tensor([self.steps_run], dtype=torch.int64, device=self.device)
+        return self.model.sample(hidden, temps, seed=self.sample_seed, step=step).tolist()
+
+    # ---------------------------------------------------------------- CUDA graphs
+    def _decode_body(self, g: _DecodeGraph) -> None:
+        meta = AttnMeta(is_prefill=False, block_tables=g.d_bt, slots=g.d_slots, context_lens=g.d_ctx,
+                        nsplit=ops.decode_splits(g.bucket, self.kv.num_kv_heads))
+        hidden = self.model.forward(g.d_ids, g.d_pos, meta, self.kv)
+        self.model.sample(hidden, g.d_temp, seed=self.sample_seed, step=g.step, out=g.tokens)
+
+    def capture_graphs(self) -> None:
+        """Capture one graph per bucket, largest first so smaller ones reuse its pool."""
+        pool = None
+        stream = torch.cuda.Stream(device=self.device)
+        for bucket in sorted(self.buckets, reverse=True):
+            g = _DecodeGraph(self, bucket)
+            with torch.cuda.stream(stream):
+                for _ in range(2):  # warm-up outside capture (lazy kernel attributes, tensor maps)
+                    g.dev.copy_(g.host, non_blocking=True)
+                    self._decode_body(g)
+                stream.synchronize()
+                graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(graph, pool=pool, stream=stream):
+                    g.dev.copy_(g.host, non_blocking=True)
+                    self._decode_body(g)
+                    g.tokens_host.copy_(g.tokens, non_blocking=True)
+                    g.step.add_(1)
+            g.graph = graph
+            pool = graph.pool() if pool is None else pool
+            self.graphs[bucket] = g
+        torch.cuda.synchronize(self.device)
+
+    def _run_decode_graph(self, inp: StepInputs) -> list[int]:
+        n = inp.num_seqs
+        bucket = next(b for b in self.buckets if b >= n)
+        g = self.graphs[bucket]
+        with profile_region("runner.cudagraph.copy_inputs"):
+            g.fill(inp)
+        with profile_region("runner.cudagraph.replay"):
+            g.graph.replay()
+            torch.cuda.current_stream().synchronize()
+        return g.tokens_host[:n].tolist()
+
+    def graph_metadata(self) -> dict[str, object]:
+        return {"buckets": list(self.graphs), "pdl": ops.pdl_enabled(), "kv_pages": self.kv.num_blocks,
+                "kv_bytes_per_page": self.config.kv_bytes_per_page(), "kv_mode": self.kv_mode}
+
+    def exit(self) -> None:
+        self.graphs.clear()
+        self._visual.clear()
+        self._visual_cache.clear()

@@ -1,0 +1,218 @@
+"""Multimodal request preparation on the CPU (reference ``prism_infer/engine/vl_inputs.py``).
+
+``PatchProcessor`` is the built-in image / video preprocessor with the output contract of
+the Hugging Face Qwen3-VL processor: ``pixel_values [N, C * Tp * P * P]`` in
+merge-window-major patch order ``(t, h_block, w_block, h_in, w_in)``, ``grid_thw`` rows
+``(T, H, W)`` in patches, still images duplicated to fill the temporal patch, sizes snapped
+to multiples of ``patch * merge`` inside the pixel budget, and one placeholder token per
+merged 2x2 window.  When the model directory ships processor files the Hugging Face
+processor can be used instead (``load_hf_processor``); the prompt builders and validators
+below are shared.
+"""
+
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass
+from typing import Any, Sequence
+
+import numpy as np
+import torch
+import torch.nn.functional as F
+
+IMAGE_MEAN = (0.5, 0.5, 0.5)
+IMAGE_STD = (0.5, 0.5, 0.5)
+
+
+@dataclass
+class ImageInputs:
+    input_ids: list[int]
+    pixel_values: torch.Tensor
+    image_grid_thw: list[tuple[int, int, int]]
+
+    def validate(self, arch) -> None:
+        _validate(self.input_ids, self.pixel_values, self.image_grid_thw, arch.image_token_id, arch)
+
+
+@dataclass
+class VideoInputs:
+    input_ids: list[int]
+    pixel_values: torch.Tensor
+    video_grid_thw: list[tuple[int, int, int]]
+
+    def validate(self, arch) -> None:
+        _validate(self.input_ids, self.pixel_values, self.video_grid_thw, arch.video_token_id, arch)
+
+
+def _validate(ids: Sequence[int], pixels: torch.Tensor, grid: Sequence[Sequence[int]], token_id: int, arch) -> None:
+    v = arch.vision
+    if pixels.dim() != 2 or pixels.shape[1] != v.patch_input_dim:
+        raise ValueError(f"pixel_values must be [N, {v.patch_input_dim}], got {list(pixels.shape)}")
+    patches = sum(int(t) * int(h) * int(w) for t, h, w in grid)
+    if patches != pixels.shape[0]:
+        raise ValueError(f"grid_thw describes {patches} patches but pixel_values has {pixels.shape[0]}")
+    for t, h, w in grid:
+        if h % v.spatial_merge_size or w % v.spatial_merge_size:
+            raise ValueError(f"grid {t, h, w} is not a multiple of the spatial merge size")
+    expected = patches // v.merge_unit
+    found = sum(1 for t in ids if t == token_id)
+    if found != expected:
+        raise ValueError(f"prompt has {found} placeholder tokens, the grids need {expected}")
+
+
+def to_uint8_hwc(image: Any) -> np.ndarray:
+    """PIL image, numpy array or torch tensor -> ``uint8 [H, W, 3]``."""
+    if isinstance(image, torch.Tensor):
+        arr = image.detach().cpu().numpy()
+    elif isinstance(image, np.ndarray):
+        arr = image
+    else:  # PIL
+        arr = np.asarray(image.convert("RGB"))
+    if arr.ndim == 3 and arr.shape[0] == 3 and arr.shape[-1] != 3:
+        arr = np.transpose(arr, (1, 2, 0))
+    if arr.ndim != 3 or arr.shape[-1] != 3:
+        raise ValueError(f"image must be HxWx3, got shape {arr.shape}")
+    if arr.dtype != np.uint8:
+        arr = np.clip(arr * (255.0 if arr.max() <= 1.0 else 1.0), 0, 255).astype(np.uint8)
+    return arr
+
+
+def smart_resize(h: int, w: int, factor: int, min_pixels: int, max_pixels: int) -> tuple[int, int]:
+    hb = max(factor, round(h / factor) * factor)
+    wb = max(factor, round(w / factor) * factor)
+    if hb * wb > max_pixels:
+        beta = math.sqrt(h * w / max_pixels)
+        hb = max(factor, math.floor(h / beta / factor) * factor)
+        wb = max(factor, math.floor(w / beta / factor) * factor)
+    elif hb * wb < min_pixels:
+        beta = math.sqrt(min_pixels / (h * w))
+        hb = math.ceil(h * beta / factor) * factor
+        wb = math.ceil(w * beta / factor) * factor
+    return hb, wb
+
+
+class PatchProcessor:
+    def __init__(self, arch, *, min_pixels: int | None = None, max_pixels: int | None = None,
+                 video_max_pixels: int | None = None) -> None:
+        self.arch = arch
+        v = arch.vision
+        self.factor = v.patch_size * v.spatial_merge_size
+        self.min_pixels = min_pixels or 4 * self.factor * self.factor
+        self.max_pixels = max_pixels or 16384 * self.factor * self.factor
+        self.video_max_pixels = video_max_pixels or self.max_pixels
+
+    def _frames_to_patches(self, frames: np.ndarray) -> tuple[torch.Tensor, tuple[int, int, int]]:
+        """``uint8 [F, H, W, 3]`` (F a multiple of the temporal patch) -> patches, grid."""
+        v = self.arch.vision
+        f, h, w, _ = frames.shape
+        x = torch.from_numpy(frames).permute(0, 3, 1, 2).float() / 255.0
+        mean = torch.tensor(IMAGE_MEAN).view(1, 3, 1, 1)
+        std = torch.tensor(IMAGE_STD).view(1, 3, 1, 1)
+        x = (x - mean) / std
+        tp, p, m = v.temporal_patch_size, v.patch_size, v.spatial_merge_size
+        gt, gh, gw = f // tp, h // p, w // p
+        x = x.view(gt, tp, 3, gh // m, m, p, gw // m, m, p)
+        # -> (t, h_block, w_block, h_in, w_in, C, Tp, P, P)
+        x = x.permute(0, 3, 6, 4, 7, 2, 1, 5, 8).contiguous()
+        return x.view(gt * gh * gw, 3 * tp * p * p), (gt, gh, gw)
+
+    def process_image(self, image: Any) -> tuple[torch.Tensor, tuple[int, int, int]]:
+        arr = to_uint8_hwc(image)
+        h, w = arr.shape[:2]
+        nh, nw = smart_resize(h, w, self.factor, self.min_pixels, self.max_pixels)
+        if (nh, nw) != (h, w):
+            t = torch.from_numpy(arr).permute(2, 0, 1).unsqueeze(0).float()
+            t = F.interpolate(t, size=(nh, nw), mode="bicubic", align_corners=False).clamp(0, 255)
+            arr = t.squeeze(0).permute(1, 2, 0).round().to(torch.uint8).numpy()
+        tp = self.arch.vision.temporal_patch_size
+        return self._frames_to_patches(np.repeat(arr[None], tp, axis=0))
+
+    def process_video(self, frames: Sequence[Any]) -> tuple[torch.Tensor, tuple[int, int, int]]:
+        arrs = [to_uint8_hwc(f) for f in frames]
+        tp = self.arch.vision.temporal_patch_size
+        while len(arrs) % tp:
+            arrs.append(arrs[-1])
+        h, w = arrs[0].shape[:2]
+        nh, nw = smart_resize(h, w, self.factor, self.min_pixels, self.video_max_pixels)
+        stack = np.stack(arrs)
+        if (nh, nw) != (h, w):
+            t = torch.from_numpy(stack).permute(0, 3, 1, 2).float()
+            t = F.interpolate(t, size=(nh, nw), mode="bicubic", align_corners=False).clamp(0, 255)
+            stack = t.permute(0, 2, 3, 1).round().to(torch.uint8).numpy()
+        return self._frames_to_patches(stack)
+
+    def tokens_for(self, grid: tuple[int, int, int]) -> int:
+        return grid[0] * grid[1] * grid[2] // self.arch.vision.merge_unit
+
+
+def image_block(arch, n_tokens: int) -> list[int]:
+    return [arch.vision_start_token_id] + [arch.image_token_id] * n_tokens + [arch.vision_end_token_id]
+
+
+def video_blocks(arch, grid: tuple[int, int, int], merge_unit: int) -> list[int]:
+    """One placeholder run per temporal group (timestamps would sit between them)."""
+    per = grid[1] * grid[2] // merge_unit
+    out: list[int] = []
+    for _ in range(grid[0]):
+        out += [arch.vision_start_token_id] + [arch.video_token_id] * per + [arch.vision_end_token_id]
+    return out
+
+
+def prepare_image_inputs(processor: PatchProcessor, tokenizer, prompt: str | Sequence[int], images: Sequence[Any]) -> ImageInputs:
+    """All images first, then the question (media-first layout)."""
+    arch = processor.arch
+    ids: list[int] = []
+    pixels, grids = [], []
+    for img in images:
+        pv, grid = processor.process_image(img)
+        pixels.append(pv)
+        grids.append(grid)
+        ids += image_block(arch, processor.tokens_for(grid))
+    ids += list(prompt) if not isinstance(prompt, str) else tokenizer.encode(prompt)
+    out = ImageInputs(ids, torch.cat(pixels), grids)
+    out.validate(arch)
+    return out
+
+
+def prepare_interleaved_image_inputs(processor: PatchProcessor, tokenizer, prompt: str, images: Sequence[Any],
+                                     image_marker: str = "<image>") -> ImageInputs:
+    """The prompt names where each image goes with ``image_marker``."""
+    arch = processor.arch
+    parts = prompt.split(image_marker)
+    if len(parts) - 1 != len(images):
+        raise ValueError(f"prompt has {len(parts) - 1} {image_marker!r} markers for {len(images)} images")
+    ids: list[int] = []
+    pixels, grids = [], []
+    for i, text in enumerate(parts):
+        if text.strip():
+            ids += tokenizer.encode(text)
+        if i < len(images):
+            pv, grid = processor.process_image(images[i])
+            pixels.append(pv)
+            grids.append(grid)
+            ids += image_block(arch, processor.tokens_for(grid))
+    out = ImageInputs(ids, torch.cat(pixels), grids)
+    out.validate(arch)
+    return out
+
+
+def prepare_video_inputs(processor: PatchProcessor, tokenizer, prompt: str | Sequence[int], frames: Sequence[Any]) -> VideoInputs:
+    arch = processor.arch
+    pv, grid = processor.process_video(frames)
+    ids = video_blocks(arch, grid, arch.vision.merge_unit)
+    ids += list(prompt) if not isinstance(prompt, str) else tokenizer.encode(prompt)
+    out = VideoInputs(ids, pv, [grid])
+    out.validate(arch)
+    return out
+
+
+def load_hf_processor(model: str, *, longest_edge: int | None = None):
+    """Hugging Face ``AutoProcessor`` for real checkpoints (optional)."""
+    from transformers import AutoProcessor
+
+    proc = AutoProcessor.from_pretrained(model)
+    if longest_edge is not None and hasattr(proc, "image_processor"):
+        size = dict(getattr(proc.image_processor, "size", {}) or {})
+        size["longest_edge"] = longest_edge
+        proc.image_processor.size = size
+    return proc

@@ -1,0 +1,413 @@
+"""Qwen3-VL as the engine runs it: packed, tensor-parallel weights and a forward built
+only from ``prism_infer_b200.ops``.
+
+Storage: per decoder layer one packed ``qkv`` matrix ``[(Hq + 2 Hkv) D / tp, H]`` (rank-local
+heads), ``o`` ``[H, Hq D / tp]``, one packed ``gate_up`` ``[2 I / tp, H]`` (gate rows then up
+rows, consumed by the dual-accumulator GEMM) and ``down`` ``[H, I / tp]``; embedding and LM
+head are vocabulary-sharded.  Checkpoints keep their Hugging Face names; ``load`` routes
+``q_proj / k_proj / v_proj`` and ``gate_proj / up_proj`` into the packed tensors (reference
+``prism_infer/models/qwen3_vl.py:184-250,1572-1601`` and ``prism_infer/layers/linear.py:47-190``).
+
+Forward (reference hot loop ``prism_infer/models/qwen3_vl.py:925-1022``): every layer is
+add+RMSNorm -> QKV GEMM -> QK-norm + M-RoPE + KV store -> paged attention -> o_proj ->
+add+RMSNorm -> dual GEMM with SwiGLU -> down_proj, with the residual carried separately and
+DeepStack features added after layers 0..k-1.  Row-parallel projections produce fp32
+partial slabs (split-K and, under tensor parallelism, one group per rank) that the next
+add+RMSNorm sums in a fixed order.
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Iterable, Iterator, Optional, Sequence
+
+import torch
+
+from .. import ops
+from .architecture import Qwen3VLArch
+from .position import vision_patch_coords, vision_pos_embed_plan, vision_segments
+from .weights import LM, VIS
+
+SMALL_T = 128  # at or below this many tokens the GEMMs are weight-streaming: split-K + fp32 partials
+
+
+@dataclass
+class AttnMeta:
+    """Device-side attention metadata of one step."""
+
+    is_prefill: bool
+    block_tables: torch.Tensor                     # [S, max_blocks] int32
+    slots: torch.Tensor                            # [T] int64 flat KV slots of the new tokens
+    # prefill
+    cu_seqlens_q: Optional[torch.Tensor] = None    # [S+1] int32
+    kv_lens: Optional[torch.Tensor] = None         # [S] int32 keys visible (history + chunk)
+    max_q_len: int = 0
+    last_rows: Optional[torch.Tensor] = None       # [S] int64 row of each sequence's last token
+    # decode
+    context_lens: Optional[torch.Tensor] = None    # [B] int32 (including the new token)
+    nsplit: int = 0
+    workspace: Optional[tuple[torch.Tensor, torch.Tensor]] = None
+
+
+@dataclass
+class LayerWeights:
+    input_norm: torch.Tensor
+    qkv: torch.Tensor
+    q_norm: torch.Tensor
+    k_norm: torch.Tensor
+    o: torch.Tensor
+    post_norm: torch.Tensor
+    gate_up: torch.Tensor
+    down: torch.Tensor
+
+
+@dataclass
+class VisionBlockWeights:
+    norm1_w: torch.Tensor
+    norm1_b: torch.Tensor
+    qkv_w: torch.Tensor
+    qkv_b: torch.Tensor
+    proj_w: torch.Tensor
+    proj_b: torch.Tensor
+    norm2_w: torch.Tensor
+    norm2_b: torch.Tensor
+    fc1_w: torch.Tensor
+    fc1_b: torch.Tensor
+    fc2_w: torch.Tensor
+    fc2_b: torch.Tensor
+
+
+@dataclass
+class MergerWeights:
+    norm_w: torch.Tensor
+    norm_b: torch.Tensor
+    fc1_w: torch.Tensor
+    fc1_b: torch.Tensor
+    fc2_w: torch.Tensor
+    fc2_b: torch.Tensor
+    post_norm: bool = False
+
+
+class TPComm:
+    """Collective hooks of a tensor-parallel rank; the single-rank default does nothing."""
+
+    rank = 0
+    size = 1
+
+    def reduce_partials(self, partials: torch.Tensor) -> torch.Tensor:
+        """fp32 ``[S, T, H]`` rank-local partial slabs -> slabs whose sum is the full result."""
+        return partials
+
+    def reduce_dense(self, x: torch.Tensor) -> torch.Tensor:
+        """bf16 ``[T, H]`` rank-local partial result -> summed over ranks."""
+        return x
+
+    def greedy_merge(self, local_val: torch.Tensor, local_id: torch.Tensor) -> torch.Tensor:
+        return local_id
+
+    def gather_logits(self, logits: torch.Tensor) -> torch.Tensor:
+        return logits
+
+    def all_gather_rows(self, x: torch.Tensor) -> torch.Tensor:
+        return x
+
+
+class Qwen3VLModel:
+    def __init__(self, arch: Qwen3VLArch, *, device, dtype: torch.dtype, comm: TPComm | None = None,
+                 load_vision: bool = True) -> None:
+        self.arch = arch
+        self.device = torch.device(device)
+        self.dtype = dtype
+        self.comm = comm or TPComm()
+        self.tp, self.rank = self.comm.size, self.comm.rank
+        t = arch.text
+        self.Hq, self.Hkv = t.num_heads // self.tp, t.num_kv_heads // self.tp
+        self.D, self.H, self.I = t.head_dim, t.hidden_size, t.intermediate_size // self.tp
+        self.V = t.vocab_size // self.tp
+        self.vocab_start = self.rank * self.V
+        self.load_vision = load_vision
+        self._alloc()
+
+    # ------------------------------------------------------------------- storage
+    def _e(self, *shape: int) -> torch.Tensor:
+        return torch.empty(shape, dtype=self.dtype, device=self.device)
+
+    def _alloc(self) -> None:
+        a, t, v = self.arch, self.arch.text, self.arch.vision
+        qkv_rows = (self.Hq + 2 * self.Hkv) * self.D
+        self.embed = self._e(self.V, self.H)
+        self.lm_head = self.embed if t.tie_word_embeddings else self._e(self.V, self.H)
+        self.final_norm = self._e(self.H)
+        self.layers = [
+            LayerWeights(self._e(self.H), self._e(qkv_rows, self.H), self._e(self.D), self._e(self.D),
+                         self._e(self.H, self.Hq * self.D), self._e(self.H), self._e(2 * self.I, self.H),
+                         self._e(self.H, self.I))
+            for _ in range(t.num_layers)
+        ]
+        self.vision_blocks: list[VisionBlockWeights] = []
+        self.mergers: dict[str, MergerWeights] = {}
+        if self.load_vision:
+            vh, vi = v.hidden_size, v.intermediate_size
+            self.patch_w, self.patch_b = self._e(vh, v.patch_input_dim), self._e(vh)
+            self.pos_embed = self._e(v.num_position_embeddings, vh)
+            self.vision_blocks = [
+                VisionBlockWeights(self._e(vh), self._e(vh), self._e(3 * vh, vh), self._e(3 * vh), self._e(vh, vh),
+                                   self._e(vh), self._e(vh), self._e(vh), self._e(vi, vh), self._e(vi),
+                                   self._e(vh, vi), self._e(vh))
+                for _ in range(v.depth)
+            ]
+            md = v.merged_dim
+
+            def merger(norm_dim: int, post: bool) -> MergerWeights:
+                return MergerWeights(self._e(norm_dim), self._e(norm_dim), self._e(md, md), self._e(md),
+                                     self._e(v.out_hidden_size, md), self._e(v.out_hidden_size), post)
+
+            self.mergers["main"] = merger(vh, False)
+            for k in range(len(v.deepstack_visual_indexes)):
+                self.mergers[f"deepstack.{k}"] = merger(md, True)
+            hd = v.head_dim
+            self.vit_inv_freq = (1.0 / (v.rope_theta ** (torch.arange(0, hd // 2, 2, dtype=torch.float32) / (hd // 2)))).to(self.device)
+
+    def weight_bytes(self) -> int:
+        seen, total = set(), 0
+        for t in self._all_tensors():
+            if t.data_ptr() not in seen:
+                seen.add(t.data_ptr())
+                total += t.numel() * t.element_size()
+        return total
+
+    def _all_tensors(self) -> Iterator[torch.Tensor]:
+        yield self.embed
+        yield self.lm_head
+        yield self.final_norm
+        for l in self.layers:
+            yield from (l.input_norm, l.qkv, l.q_norm, l.k_norm, l.o, l.post_norm, l.gate_up, l.down)
+        if self.load_vision:
+            yield from (self.patch_w, self.patch_b, self.pos_embed)
+            for b in self.vision_blocks:
+                yield from b.__dict__.values()
+            for m in self.mergers.values():
+                yield from (m.norm_w, m.norm_b, m.fc1_w, m.fc1_b, m.fc2_w, m.fc2_b)
+
+    # ------------------------------------------------------------------- loading
+    def _route(self, name: str) -> tuple[torch.Tensor, Optional[tuple[int, int, int]]] | None:
+        """HF name -> (destination view, (dim, start, length) slice of the checkpoint tensor)."""
+        r, D = self.rank, self.D
+        if name.startswith(f"{LM}.layers."):
+            rest = name[len(f"{LM}.layers."):]
+            idx, sub = rest.split(".", 1)
+            l = self.layers[int(idx)]
+            q_rows, kv_rows = self.Hq * D, self.Hkv * D
+            table = {
+                "input_layernorm.weight": (l.input_norm, None),
+                "post_attention_layernorm.weight": (l.post_norm, None),
+                "self_attn.q_norm.weight": (l.q_norm, None),
+                "self_attn.k_norm.weight": (l.k_norm, None),
+                "self_attn.q_proj.weight": (l.qkv[:q_rows], (0, r * q_rows, q_rows)),
+                "self_attn.k_proj.weight": (l.qkv[q_rows:q_rows + kv_rows], (0, r * kv_rows, kv_rows)),
+                "self_attn.v_proj.weight": (l.qkv[q_rows + kv_rows:], (0, r * kv_rows, kv_rows)),
+                "self_attn.o_proj.weight": (l.o, (1, r * q_rows, q_rows)),
+                "mlp.gate_proj.weight": (l.gate_up[: self.I], (0, r * self.I, self.I)),
+                "mlp.up_proj.weight": (l.gate_up[self.I:], (0, r * self.I, self.I)),
+                "mlp.down_proj.weight": (l.down, (1, r * self.I, self.I)),
+            }
+            return table.get(sub)
+        if name == f"{LM}.embed_tokens.weight":
+            return self.embed, (0, r * self.V, self.V)
+        if name == "lm_head.weight":
+            return (None if self.arch.text.tie_word_embeddings else (self.lm_head, (0, r * self.V, self.V)))
+        if name == f"{LM}.norm.weight":
+            return self.final_norm, None
+        if not self.load_vision or not name.startswith(VIS):
+            return None
+        if name == f"{VIS}.patch_embed.proj.weight":
+            return self.patch_w, None
+        if name == f"{VIS}.patch_embed.proj.bias":
+            return self.patch_b, None
+        if name == f"{VIS}.pos_embed.weight":
+            return self.pos_embed, None
+        if name.startswith(f"{VIS}.blocks."):
+            rest = name[len(f"{VIS}.blocks."):]
+            idx, sub = rest.split(".", 1)
+            b = self.vision_blocks[int(idx)]
+            table = {
+                "norm1.weight": b.norm1_w, "norm1.bias": b.norm1_b, "norm2.weight": b.norm2_w, "norm2.bias": b.norm2_b,
+                "attn.qkv.weight": b.qkv_w, "attn.qkv.bias": b.qkv_b, "attn.proj.weight": b.proj_w,
+                "attn.proj.bias": b.proj_b, "mlp.linear_fc1.weight": b.fc1_w, "mlp.linear_fc1.bias": b.fc1_b,
+                "mlp.linear_fc2.weight": b.fc2_w, "mlp.linear_fc2.bias": b.fc2_b,
+            }
+            dst = table.get(sub)
+            return None if dst is None else (dst, None)
+        for key, prefix in [("main", f"{VIS}.merger.")] + [
+            (f"deepstack.{k}", f"{VIS}.deepstack_merger_list.{k}.") for k in range(len(self.arch.vision.deepstack_visual_indexes))
+        ]:
+            if name.startswith(prefix):
+                m = self.mergers[key]
+                table = {"norm.weight": m.norm_w, "norm.bias": m.norm_b, "linear_fc1.weight": m.fc1_w,
+                         "linear_fc1.bias": m.fc1_b, "linear_fc2.weight": m.fc2_w, "linear_fc2.bias": m.fc2_b}
+                dst = table.get(name[len(prefix):])
+                return None if dst is None else (dst, None)
+        return None
+
+    def load(self, tensors: Iterable[tuple[str, torch.Tensor]], *, strict: bool = True) -> None:
+        """Copy (and shard) checkpoint tensors into the packed storage."""
+        from .weights import weight_shapes
+
+        expected = set(weight_shapes(self.arch))
+        if not self.load_vision:
+            expected = {n for n in expected if not n.startswith(VIS)}
+        seen: set[str] = set()
+        for name, tensor in tensors:
+            routed = self._route(name)
+            if routed is None:
+                if name in expected and not (name == "lm_head.weight" and self.arch.text.tie_word_embeddings):
+                    if self.load_vision or not name.startswith(VIS):
+                        raise KeyError(f"no destination for checkpoint tensor {name}")
+                continue
+            dst, sl = routed
+            src = tensor
+            if sl is not None:
+                src = src.narrow(sl[0], sl[1], sl[2])
+            src = src.reshape(dst.shape) if src.numel() == dst.numel() else src
+            if src.shape != dst.shape:
+                raise ValueError(f"{name}: checkpoint shape {tuple(tensor.shape)} does not fit {tuple(dst.shape)}")
+            dst.copy_(src.to(device=self.device, dtype=self.dtype, non_blocking=True))
+            seen.add(name)
+        if strict:
+            missing = expected - seen
+            if self.arch.text.tie_word_embeddings:
+                missing.discard("lm_head.weight")
+            if missing:
+                raise KeyError(f"checkpoint is missing {len(missing)} tensors, e.g. {sorted(missing)[:3]}")
+
+    # -------------------------------------------------------------------- vision
+    @torch.no_grad()
+    def encode_vision(self, pixel_values: torch.Tensor, grid_thw: Sequence[Sequence[int]]) -> tuple[torch.Tensor, list[torch.Tensor]]:
+        """``pixel_values [N, C*Tp*P*P]`` -> merged visual tokens ``[N/4, H]`` and one
+        DeepStack feature tensor per tap, all replicated on every rank."""
+        v = self.arch.vision
+        grid = [tuple(int(x) for x in g) for g in grid_thw]
+        dev = self.device
+        x = ops.linear(pixel_values.to(device=dev, dtype=self.dtype), self.patch_w, bias=self.patch_b)
+        idx, wt = vision_pos_embed_plan(grid, v.grid_per_side, v.spatial_merge_size)
+        ops.pos_embed_add(x, self.pos_embed, idx.to(dev), wt.to(dev))
+        coords = vision_patch_coords(grid, v.spatial_merge_size).to(torch.int32).to(dev)
+        segs = vision_segments(grid)
+        cu = torch.tensor([0] + list(torch.tensor(segs).cumsum(0).tolist()), dtype=torch.int32, device=dev)
+        max_len = max(segs)
+        N, vh, heads, hd = x.shape[0], v.hidden_size, v.num_heads, v.head_dim
+        deep: list[torch.Tensor] = []
+        for i, b in enumerate(self.vision_blocks):
+            h = ops.layernorm(x, b.norm1_w, b.norm1_b, v.layer_norm_eps)
+            qkv = ops.linear(h, b.qkv_w, bias=b.qkv_b)
+            ops.vit_rope(qkv, coords, self.vit_inv_freq, heads, hd)
+            q = qkv[:, :vh].view(N, heads, hd)
+            k = qkv[:, vh:2 * vh].view(N, heads, hd)
+            val = qkv[:, 2 * vh:].view(N, heads, hd)
+            a = ops.varlen_attention(q, k, val, cu, max_len, causal=False)
+            x = ops.linear(a.view(N, vh), b.proj_w, bias=b.proj_b, residual=x, out=x if x.is_cuda else None)
+            h = ops.layernorm(x, b.norm2_w, b.norm2_b, v.layer_norm_eps)
+            h = ops.linear(h, b.fc1_w, bias=b.fc1_b, act="gelu_tanh")
+            x = ops.linear(h, b.fc2_w, bias=b.fc2_b, residual=x, out=x if x.is_cuda else None)
+            if i in v.deepstack_visual_indexes:
+                deep.append(self._merge(x, self.mergers[f"deepstack.{v.deepstack_visual_indexes.index(i)}"]))
+        return self._merge(x, self.mergers["main"]), deep
+
+    def _merge(self, x: torch.Tensor, m: MergerWeights) -> torch.Tensor:
+        v = self.arch.vision
+        if m.post_norm:
+            h = ops.layernorm(x.view(-1, v.merged_dim), m.norm_w, m.norm_b, v.layer_norm_eps)
+        else:
+            h = ops.layernorm(x, m.norm_w, m.norm_b, v.layer_norm_eps).view(-1, v.merged_dim)
+        h = ops.linear(h, m.fc1_w, bias=m.fc1_b, act="gelu")
+        return ops.linear(h, m.fc2_w, bias=m.fc2_b)
+
+    # ---------------------------------------------------------------------- text
+    def _row_parallel(self, x: torch.Tensor, w: torch.Tensor):
+        """Row-parallel projection.  Returns ``(dense, partials)``: exactly one is set."""
+        T = x.shape[0]
+        if T <= SMALL_T:
+            splits = ops.choose_splits(w.shape[0], w.shape[1], T) if x.is_cuda else 1
+            return None, self.comm.reduce_partials(ops.linear_partial(x, w, splits))
+        return self.comm.reduce_dense(ops.linear(x, w)), None
+
+    @torch.no_grad()
+    def forward(
+        self,
+        input_ids: torch.Tensor,
+        positions: torch.Tensor,
+        meta: AttnMeta,
+        cache: ops.KVCache,
+        *,
+        visual: Optional[torch.Tensor] = None,
+        vis_index: Optional[torch.Tensor] = None,
+        deepstack: Optional[Sequence[torch.Tensor]] = None,
+    ) -> torch.Tensor:
+        """Hidden states ``[T, H]`` after the final norm.
+
+        ``input_ids [T]`` int64, ``positions [3, T]`` int32, ``vis_index [T]`` int32 maps
+        visual placeholder rows to rows of ``visual`` / ``deepstack[k]`` (-1 elsewhere).
+        """
+        t = self.arch.text
+        T = input_ids.shape[0]
+        small = T <= SMALL_T
+        x = ops.embed(input_ids, self.embed, visual=visual, vis_index=vis_index, vocab_start=self.vocab_start)
+        if self.tp > 1:
+            x = self.comm.reduce_dense(x)
+        residual: Optional[torch.Tensor] = None
+        dense, partials = x, None
+        n_deep = len(deepstack) if deepstack is not None else 0
+        for i, l in enumerate(self.layers):
+            extra = deepstack[i - 1] if 0 < i <= n_deep else None
+            h, residual = ops.add_rmsnorm(l.input_norm, t.rms_norm_eps, x=dense, partials=partials, residual=residual,
+                                          extra=extra, extra_index=vis_index if extra is not None else None)
+            if small and h.is_cuda:
+                qkv_p = ops.linear_partial(h, l.qkv, ops.choose_splits(l.qkv.shape[0], self.H, T))
+                q = ops.qk_norm_rope_store(qkv=None, partials=qkv_p, positions=positions, q_weight=l.q_norm, k_weight=l.k_norm,
+                                           num_heads=self.Hq, num_kv_heads=self.Hkv, head_dim=self.D, theta=t.rope_theta,
+                                           section=t.mrope_section, eps=t.rms_norm_eps, slots=meta.slots, cache=cache, layer=i)
+            else:
+                qkv = ops.linear(h, l.qkv)
+                q = ops.qk_norm_rope_store(qkv=qkv, partials=None, positions=positions, q_weight=l.q_norm, k_weight=l.k_norm,
+                                           num_heads=self.Hq, num_kv_heads=self.Hkv, head_dim=self.D, theta=t.rope_theta,
+                                           section=t.mrope_section, eps=t.rms_norm_eps, slots=meta.slots, cache=cache, layer=i)
+            if meta.is_prefill:
+                a = ops.paged_prefill_attention(q, cache, i, meta.cu_seqlens_q, meta.kv_lens, meta.block_tables, meta.max_q_len)
+            else:
+                a = ops.paged_decode_attention(q, cache, i, meta.block_tables, meta.context_lens, nsplit=meta.nsplit,
+                                               workspace=meta.workspace)
+            dense, partials = self._row_parallel(a.view(T, self.Hq * self.D), l.o)
+            h, residual = ops.add_rmsnorm(l.post_norm, t.rms_norm_eps, x=dense, partials=partials, residual=residual)
+            act = ops.gate_up_swiglu(h, l.gate_up)
+            dense, partials = self._row_parallel(act, l.down)
+        extra = deepstack[n_deep - 1] if n_deep == len(self.layers) else None
+        h, _ = ops.add_rmsnorm(self.final_norm, t.rms_norm_eps, x=dense, partials=partials, residual=residual,
+                               extra=extra, extra_index=vis_index if extra is not None else None)
+        return h
+
+    @torch.no_grad()
+    def logits(self, hidden: torch.Tensor) -> torch.Tensor:
+        """fp32 rank-local logits ``[B, V / tp]`` for the given hidden rows."""
+        if hidden.is_cuda:
+            return ops.linear_partial(hidden, self.lm_head, 1)[0]
+        return ops.linear(hidden, self.lm_head).float()
+
+    @torch.no_grad()
+    def sample(self, hidden: torch.Tensor, temperature: Optional[torch.Tensor], *, seed: int = 0,
+               step: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """Next token per row: LM head, then arg-max / exponential-race sampling; under tensor
+        parallelism ranks exchange their shard winners so every rank returns the same ids."""
+        logits = self.logits(hidden)
+        if self.tp == 1:
+            return ops.sample(logits, temperature, seed=seed, step=step, out=out)
+        greedy = temperature is None
+        if greedy:
+            val = torch.empty(logits.shape[0], dtype=torch.float32, device=logits.device)
+            ids = ops.sample(logits, None, vocab_offset=self.vocab_start, out_val=val)
+            tok = self.comm.greedy_merge(val, ids)
+        else:
+            tok = ops.sample(self.comm.gather_logits(logits), temperature, seed=seed, step=step)
+        if out is not None:
+            out.copy_(tok)
+            return out
+        return tok

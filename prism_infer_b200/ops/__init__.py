@@ -432,8 +432,9 @@ def embed(ids: torch.Tensor, table: torch.Tensor, *, visual: Optional[torch.Tens
     if out is None:
         out = torch.empty((T, H), dtype=torch.bfloat16, device=table.device)
     assert ids.dtype == torch.int64
+    # first kernel of a step: it may follow a memcpy node, so it takes a full dependency
     native.call("prism_embed", _p(ids), _p(table), _p(visual), _p(vis_index), _p(out), T, H, vocab_start,
-                vocab_start + table.shape[0], _s(), _pdl())
+                vocab_start + table.shape[0], _s(), 0)
     return out
 
 
