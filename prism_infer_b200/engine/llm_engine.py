@@ -223,6 +223,19 @@ class LLMEngine:
     def graph_metadata(self) -> dict[str, object]:
         return self.runners.call("graph_metadata")
 
+    def time_decode_graph(self, steps: int) -> float:
+        """Device ms per decode step from back-to-back graph launches (max over ranks)."""
+        res = self.runners.call("time_decode_graph", steps)
+        return max(res) if isinstance(res, (list, tuple)) else float(res)
+
+    @property
+    def is_driver(self) -> bool:
+        return getattr(self.runners, "is_driver", True)
+
+    def serve_forever(self) -> None:
+        """Tensor-parallel worker ranks (torchrun launch) execute rank 0's commands here."""
+        self.runners.serve_forever()
+
     # -------------------------------------------------------------------- generate
     def _format(self, token_ids: list[int]) -> dict[str, Any]:
         raw = self.tokenizer.decode(token_ids, skip_special_tokens=False)

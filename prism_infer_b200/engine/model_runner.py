@@ -293,18 +293,22 @@ class ModelRunner:
         stream = torch.cuda.Stream(device=self.device)
         for bucket in sorted(self.buckets, reverse=True):
             g = _DecodeGraph(self, bucket)
+            from ..ops import native as _native
+
             with torch.cuda.stream(stream):
                 for _ in range(2):  # warm-up outside capture (lazy kernel attributes, tensor maps)
                     g.dev.copy_(g.host, non_blocking=True)
                     self._decode_body(g)
                 stream.synchronize()
                 graph = torch.cuda.CUDAGraph()
+                before = _native.launch_count()
                 with torch.cuda.graph(graph, pool=pool, stream=stream):
                     g.dev.copy_(g.host, non_blocking=True)
                     self._decode_body(g)
                     g.tokens_host.copy_(g.tokens, non_blocking=True)
                     g.step.add_(1)
             g.graph = graph
+            g.launches = _native.launch_count() - before
             pool = graph.pool() if pool is None else pool
             self.graphs[bucket] = g
         torch.cuda.synchronize(self.device)
@@ -313,6 +317,7 @@ class ModelRunner:
         n = inp.num_seqs
         bucket = next(b for b in self.buckets if b >= n)
         g = self.graphs[bucket]
+        self._last_bucket = bucket
         with profile_region("runner.cudagraph.copy_inputs"):
             g.fill(inp)
         with profile_region("runner.cudagraph.replay"):
@@ -320,9 +325,28 @@ class ModelRunner:
             torch.cuda.current_stream().synchronize()
         return g.tokens_host[:n].tolist()
 
+    def time_decode_graph(self, steps: int) -> float:
+        """Device milliseconds per decode step: CUDA events around ``steps`` back-to-back
+        launches of the most recently used bucket graph (inputs stay as last filled)."""
+        g = self.graphs[getattr(self, "_last_bucket", self.buckets[0])]
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize(self.device)
+        start.record()
+        for _ in range(steps):
+            g.graph.replay()
+        end.record()
+        torch.cuda.synchronize(self.device)
+        return start.elapsed_time(end) / steps
+
     def graph_metadata(self) -> dict[str, object]:
         return {"buckets": list(self.graphs), "pdl": ops.pdl_enabled(), "kv_pages": self.kv.num_blocks,
-                "kv_bytes_per_page": self.config.kv_bytes_per_page(), "kv_mode": self.kv_mode}
+                "kv_bytes_per_page": self.config.kv_bytes_per_page(), "kv_mode": self.kv_mode,
+                "launches_per_decode_graph": {str(b): getattr(g, "launches", 0) for b, g in self.graphs.items()},
+                "staging_bytes": {str(b): g.nbytes for b, g in self.graphs.items()},
+                "weight_bytes": self.model.weight_bytes()}
+
+    def capacity(self) -> tuple[int, int]:
+        return self.config.num_kvcache_blocks, self.config.num_cpu_blocks
 
     def exit(self) -> None:
         self.graphs.clear()

@@ -1,0 +1,104 @@
+"""The engine on a B200: tiny model against the fp32 oracle, graph decode == eager decode."""
+
+import numpy as np
+import pytest
+import torch
+
+from prism_infer_b200 import LLM, SamplingParams
+from prism_infer_b200.engine.vl_inputs import PatchProcessor, prepare_image_inputs
+from prism_infer_b200.models.architecture import Qwen3VLArch
+from prism_infer_b200.models.reference_model import ReferenceQwen3VL
+from prism_infer_b200.models.weights import random_weights
+from prism_infer_b200.ops import native
+from prism_infer_b200.utils.tokenizer import load_tokenizer
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def tiny(cuda_device):
+    arch = Qwen3VLArch.tiny()
+    # bf16-representable weights so the oracle (fp32) and the engine (bf16) hold the same values
+    weights = {k: v.to(torch.bfloat16).float() for k, v in random_weights(arch, dtype=torch.float32, seed=0).items()}
+    return arch, weights, ReferenceQwen3VL(arch, weights)
+
+
+def _inputs(arch, n_text=24, seed=0):
+    image = np.random.default_rng(seed).integers(0, 256, (224, 224, 3), dtype=np.uint8)
+    g = torch.Generator().manual_seed(seed)
+    text = torch.randint(0, 1000, (n_text,), generator=g).tolist()
+    return prepare_image_inputs(PatchProcessor(arch), load_tokenizer("random:tiny", arch), text, [image])
+
+
+def _agree(got, want_tokens, want_logits, margin=0.05):
+    """Token-exact wherever the oracle's top-2 margin is not within bf16 noise."""
+    for i, (g, w) in enumerate(zip(got, want_tokens)):
+        if g != w:
+            top2 = want_logits[i].topk(2).values
+            assert float(top2[0] - top2[1]) < margin, f"step {i}: got {g}, oracle {w} with margin {float(top2[0] - top2[1])}"
+            return  # later steps follow a different history
+    assert len(got) == len(want_tokens)
+
+
+@pytest.mark.parametrize("backend", ["eager", "cuda_graph"])
+@pytest.mark.parametrize("mode", ["off", "scaled_fp8_kv"])
+def test_tiny_image_prompt_on_gpu(tiny, backend, mode):
+    arch, weights, oracle = tiny
+    inputs = _inputs(arch)
+    want, logits = oracle.generate_greedy(inputs.input_ids, 16, pixel_values=inputs.pixel_values,
+                                          image_grid_thw=inputs.image_grid_thw, return_logits=True)
+    llm = LLM("random:tiny", weights=weights, max_model_len=512, kvcache_block_size=256, num_kvcache_blocks=8,
+              execution_backend=backend, compression_mode=mode, max_num_seqs=4, cpu_kv_cache_ratio=0.0)
+    got = llm.generate_prepared_image_inputs(inputs, SamplingParams(temperature=0.0, max_tokens=16, ignore_eos=True))
+    torch.cuda.synchronize()
+    native.check_status()
+    _agree(got["token_ids"], want, logits, margin=0.05 if mode == "off" else 0.3)
+    llm.exit()
+
+
+def test_graph_decode_equals_eager_decode(tiny):
+    arch, weights, _ = tiny
+    prompts = [torch.randint(0, 1000, (n,), generator=torch.Generator().manual_seed(n)).tolist() for n in (9, 33, 70)]
+    sp = SamplingParams(temperature=0.0, max_tokens=12, ignore_eos=True)
+    outs = {}
+    for backend in ("eager", "cuda_graph"):
+        llm = LLM("random:tiny", weights=weights, max_model_len=512, kvcache_block_size=16, num_kvcache_blocks=64,
+                  execution_backend=backend, compression_mode="scaled_fp8_kv", max_num_seqs=8, cpu_kv_cache_ratio=0.0)
+        outs[backend] = [o["token_ids"] for o in llm.generate(prompts, sp)]
+        llm.exit()
+    assert outs["eager"] == outs["cuda_graph"]
+    native.check_status()
+
+
+def test_prefix_hit_and_compaction_on_gpu(tiny):
+    arch, weights, _ = tiny
+    llm = LLM("random:tiny", weights=weights, max_model_len=512, kvcache_block_size=16, num_kvcache_blocks=64,
+              compression_mode="visual_compact_scaled_fp8", visual_pruning_keep_ratio=0.5, visual_pruning_min_keep_tokens=8,
+              max_num_seqs=4, cpu_kv_cache_ratio=0.0)
+    sp = SamplingParams(temperature=0.0, max_tokens=6, ignore_eos=True)
+    a, b = _inputs(arch, 5, seed=7), _inputs(arch, 9, seed=7)
+    b.input_ids[-9:] = [5, 6, 7, 8, 9, 10, 11, 12, 13]
+    r1 = llm.generate_prepared_image_inputs(a, sp)
+    llm.generate_prepared_image_inputs(b, sp)
+    r3 = llm.generate_prepared_image_inputs(a, sp)
+    meta = llm.multimodal_prefix_cache_metadata()
+    assert meta["hits"] == 2 and meta["stores"] == 1
+    assert r1["token_ids"] == r3["token_ids"]
+    native.check_status()
+    llm.exit()
+
+
+def test_temperature_sampling_runs_in_graph(tiny):
+    arch, weights, _ = tiny
+    llm = LLM("random:tiny", weights=weights, max_model_len=256, kvcache_block_size=16, num_kvcache_blocks=32,
+              max_num_seqs=4, cpu_kv_cache_ratio=0.0)
+    outs = llm.generate([[1, 2, 3], [4, 5, 6, 7]], [SamplingParams(temperature=0.0, max_tokens=5, ignore_eos=True),
+                                                    SamplingParams(temperature=1.5, max_tokens=5, ignore_eos=True)])
+    assert all(len(o["token_ids"]) == 5 for o in outs)
+    llm.exit()
+
+
+def test_smoke_entry(cuda_device):
+    import __graft_entry__
+
+    __graft_entry__.smoke()
