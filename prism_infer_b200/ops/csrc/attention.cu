@@ -596,3 +596,86 @@ PRISM_API int prism_flash_attention(const void* q, long long q_stride, void* out
   }
   return -3;
 }
+
+// =====================================================================================
+// Allocation-free entry point (declared in prism_noalloc.h; it has no counterpart in the
+// reference).  Same split-KV decode attention as prism_paged_decode, but the split
+// partials live in a fixed file-scope device array instead of caller-provided scratch, so
+// a caller that must not allocate device memory can still use the split-KV path.
+// =====================================================================================
+#include "prism_noalloc.h"
+
+#include <cstdio>
+#include <mutex>
+
+namespace {
+
+// Every GPU that loads this library keeps these bytes resident until the process exits.
+static __device__ __align__(256) unsigned char g_noalloc_scratch[PRISM_NOALLOC_SCRATCH_BYTES];
+
+constexpr int kMaxDevices = 64;
+void* g_noalloc_ptr[kMaxDevices] = {nullptr};  // device address of the array, per device
+std::mutex g_noalloc_mutex;
+thread_local char g_noalloc_error[256] = "";
+
+int noalloc_fail(int code, const char* msg) {
+  snprintf(g_noalloc_error, sizeof(g_noalloc_error), "%s", msg);
+  return code;
+}
+
+}  // namespace
+
+PRISM_API const char* prism_noalloc_last_error() { return g_noalloc_error; }
+
+PRISM_API long long prism_paged_decode_noalloc_scratch_bytes(int B, int Hq, int D, int nsplit) {
+  if (nsplit <= 1) return 0;
+  const long long rows = (long long)B * Hq * nsplit;
+  const long long part_o = (rows * D * 4 + 255) / 256 * 256;
+  return part_o + rows * 2 * 4;
+}
+
+PRISM_API int prism_paged_decode_noalloc(const void* q, const void* k_cache, const void* v_cache, const void* k_scale,
+                                         const void* v_scale, const void* block_tables, const void* context_lens,
+                                         void* out, int B, int Hq, int Hkv, int D, int page, int max_blocks, int nsplit,
+                                         int kv_mode, float scale, void* stream) {
+  g_noalloc_error[0] = 0;
+  if (B <= 0) return 0;
+  if (nsplit < 1) nsplit = 1;
+  const long long need = prism_paged_decode_noalloc_scratch_bytes(B, Hq, D, nsplit);
+  if (need > (long long)PRISM_NOALLOC_SCRATCH_BYTES) {
+    char msg[256];
+    snprintf(msg, sizeof(msg),
+             "prism_paged_decode_noalloc: B=%d Hq=%d D=%d nsplit=%d needs %lld bytes of split-KV scratch, the built-in "
+             "array holds %lld; lower nsplit or the batch, or use prism_paged_decode with your own scratch",
+             B, Hq, D, nsplit, need, (long long)PRISM_NOALLOC_SCRATCH_BYTES);
+    return noalloc_fail(-10, msg);
+  }
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return noalloc_fail((int)e, "prism_paged_decode_noalloc: cudaGetDevice failed");
+  if (dev < 0 || dev >= kMaxDevices) return noalloc_fail(-11, "prism_paged_decode_noalloc: device index out of range");
+  void* base = nullptr;
+  {
+    // One-time set-up per device, with that device current: the host-side name of a
+    // __device__ array is not a device address, so it is resolved here and cached.
+    std::lock_guard<std::mutex> lock(g_noalloc_mutex);
+    if (g_noalloc_ptr[dev] == nullptr) {
+      void* p = nullptr;
+      e = cudaGetSymbolAddress(&p, g_noalloc_scratch);
+      if (e != cudaSuccess || p == nullptr)
+        return noalloc_fail(e != cudaSuccess ? (int)e : -12, "prism_paged_decode_noalloc: cudaGetSymbolAddress failed");
+      g_noalloc_ptr[dev] = p;
+    }
+    base = g_noalloc_ptr[dev];
+  }
+  const long long rows = (long long)B * Hq * nsplit;
+  void* part_o = base;
+  void* part_ml = static_cast<unsigned char*>(base) + (rows * D * 4 + 255) / 256 * 256;
+  // Every (sequence, head, split) cell of both partial arrays is rewritten by each launch
+  // (empty splits store max = -inf, sum = 0), so nothing has to be cleared between calls.
+  const int rc = prism_paged_decode(q, k_cache, v_cache, k_scale, v_scale, block_tables, context_lens,
+                                    nsplit > 1 ? part_o : nullptr, nsplit > 1 ? part_ml : nullptr, out, B, Hq, Hkv, D, page,
+                                    max_blocks, nsplit, kv_mode, scale, stream, 0);
+  if (rc != 0) return noalloc_fail(rc, "prism_paged_decode_noalloc: kernel launch failed");
+  return 0;
+}
