@@ -57,7 +57,9 @@ def choose_splits(m: int, k: int, tokens: int) -> int:
         return 1
     tiles = (m + 127) // 128
     kb = (k + 63) // 64
-    want = max(1, round(SM_COUNT / tiles))
+    # one CTA per SM is resident (the operand ring fills shared memory), so more CTAs than
+    # SMs means a second, mostly empty wave: stay at or below the SM count
+    want = max(1, SM_COUNT // tiles)
     return max(1, min(want, kb // 4 if kb >= 8 else 1, 16))
 
 
@@ -440,8 +442,20 @@ def embed(ids: torch.Tensor, table: torch.Tensor, *, visual: Optional[torch.Tens
 
 # --------------------------------------------------------------------------- attention
 def decode_splits(batch: int, num_kv_heads: int) -> int:
-    want = max(1, (2 * SM_COUNT) // max(1, batch * num_kv_heads))
-    return int(min(32, want))
+    want = max(1, SM_COUNT // max(1, batch * num_kv_heads))
+    return int(min(16, want))
+
+
+_DECODE_COUNTERS: dict = {}
+
+
+def _decode_counters(device, n: int) -> torch.Tensor:
+    """Zero-initialised, self-resetting arrival counters shared by all decode launches."""
+    t = _DECODE_COUNTERS.get(str(device))
+    if t is None or t.numel() < n:
+        t = torch.zeros(max(n, 8192), dtype=torch.int32, device=device)
+        _DECODE_COUNTERS[str(device)] = t
+    return t
 
 
 def paged_decode_attention(
@@ -491,6 +505,7 @@ def paged_decode_attention(
     native.call(
         "prism_paged_decode", _p(q), _p(cache.k(layer)), _p(cache.v(layer)), _p(cache.k_scale(layer)),
         _p(cache.v_scale(layer)), _p(block_tables), _p(context_lens), _p(part_o), _p(part_ml), _p(out),
+        _p(_decode_counters(q.device, B * cache.num_kv_heads)) if nsplit > 1 else None,
         B, Hq, cache.num_kv_heads, D, cache.page, block_tables.shape[1], nsplit, cache.mode, scale, _s(), _pdl(),
     )
     return out
@@ -667,8 +682,14 @@ def sample(
     assert slabs.dtype == torch.float32 and slabs.stride(2) == 1
     if out is None:
         out = torch.empty((B,), dtype=torch.int64, device=logits.device)
+    chunks = max(1, min(64, (V + 2047) // 2048, (4 * SM_COUNT) // B)) if V > 8192 else 1
+    cand_val = cand_id = None
+    if chunks > 1:
+        cand_val = torch.empty((chunks, B), dtype=torch.float32, device=logits.device)
+        cand_id = torch.empty((chunks, B), dtype=torch.int64, device=logits.device)
     native.call("prism_sample", _p(slabs), slabs.stride(1), slabs.stride(0), P, _p(temperature), _p(out), _p(out_val),
-                B, V, vocab_offset, int(seed) & 0xFFFFFFFFFFFFFFFF, _p(step), _s(), _pdl())
+                B, V, vocab_offset, int(seed) & 0xFFFFFFFFFFFFFFFF, _p(step), _p(cand_val), _p(cand_id), chunks,
+                _s(), _pdl())
     return out
 
 

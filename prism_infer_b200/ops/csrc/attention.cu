@@ -41,6 +41,7 @@ struct DecodeArgs {
   float* part_o;            // [B][Hq][nsplit][D]
   float* part_ml;           // [B][Hq][nsplit][2]  (max, sum)
   bf16* out;                // [B][Hq][D] (written directly when nsplit == 1)
+  int* counters;            // [B * Hkv] zero-initialised, self-resetting; null = separate combine kernel
   int Hq, Hkv, page, max_blocks, nsplit;
   float scale;
 };
@@ -206,6 +207,34 @@ __global__ void __launch_bounds__(128) paged_decode_kernel(const DecodeArgs a) {
         a.part_ml[pidx * 2 + 1] = ll;
       }
     }
+  }
+  if (a.nsplit == 1 || a.counters == nullptr) return;
+  // The last split CTA of this (sequence, KV head) to finish merges all splits, which saves
+  // the separate combine launch.  Classic fence / counter / fence hand-off.
+  __shared__ int s_last;
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const int old = atomicAdd(&a.counters[b * a.Hkv + kvh], 1);
+    s_last = (old == a.nsplit - 1);
+    if (s_last) a.counters[b * a.Hkv + kvh] = 0;
+  }
+  __syncthreads();
+  if (!s_last) return;
+  __threadfence();
+  for (int idx = threadIdx.x; idx < G * D; idx += blockDim.x) {
+    const int g = idx / D, d = idx % D;
+    const size_t bh = (size_t)b * a.Hq + kvh * G + g;
+    float mm = -INFINITY;
+    for (int s = 0; s < a.nsplit; ++s) mm = fmaxf(mm, __ldcg(&a.part_ml[(bh * a.nsplit + s) * 2]));
+    float ll = 0.0f, oo = 0.0f;
+    for (int s = 0; s < a.nsplit; ++s) {
+      const float ms = __ldcg(&a.part_ml[(bh * a.nsplit + s) * 2]);
+      const float c = (ms == -INFINITY) ? 0.0f : __expf(ms - mm);
+      ll += __ldcg(&a.part_ml[(bh * a.nsplit + s) * 2 + 1]) * c;
+      oo += __ldcg(&a.part_o[(bh * a.nsplit + s) * D + d]) * c;
+    }
+    a.out[bh * D + d] = __float2bfloat16_rn(ll > 0.0f ? oo / ll : 0.0f);
   }
 }
 
@@ -522,8 +551,8 @@ int dispatch_decode(const DecodeArgs& a, int B, cudaStream_t stream, bool pdl) {
 // B*Hq*nsplit*D and B*Hq*nsplit*2 floats (unused when nsplit == 1).
 PRISM_API int prism_paged_decode(const void* q, const void* k_cache, const void* v_cache, const void* k_scale,
                                  const void* v_scale, const void* block_tables, const void* context_lens, void* part_o,
-                                 void* part_ml, void* out, int B, int Hq, int Hkv, int D, int page, int max_blocks,
-                                 int nsplit, int kv_mode, float scale, void* stream, int pdl) {
+                                 void* part_ml, void* out, void* counters, int B, int Hq, int Hkv, int D, int page,
+                                 int max_blocks, int nsplit, int kv_mode, float scale, void* stream, int pdl) {
   if (B <= 0) return 0;
   if (Hq % Hkv) return -1;
   DecodeArgs a;
@@ -537,6 +566,7 @@ PRISM_API int prism_paged_decode(const void* q, const void* k_cache, const void*
   a.part_o = (float*)part_o;
   a.part_ml = (float*)part_ml;
   a.out = (bf16*)out;
+  a.counters = (int*)counters;
   a.Hq = Hq;
   a.Hkv = Hkv;
   a.page = page;
@@ -549,7 +579,7 @@ PRISM_API int prism_paged_decode(const void* q, const void* k_cache, const void*
   else if (D == 64) rc = kv_mode ? dispatch_decode<64, true>(a, B, s, pdl != 0) : dispatch_decode<64, false>(a, B, s, pdl != 0);
   else return -2;
   if (rc) return rc;
-  if (a.nsplit > 1) {
+  if (a.nsplit > 1 && a.counters == nullptr) {
     rc = (int)prism_launch(decode_combine_kernel, dim3(B * Hq), dim3(128), 0, s, pdl != 0, (const float*)part_o,
                            (const float*)part_ml, (bf16*)out, a.nsplit, D);
   }
@@ -674,8 +704,8 @@ PRISM_API int prism_paged_decode_noalloc(const void* q, const void* k_cache, con
   // Every (sequence, head, split) cell of both partial arrays is rewritten by each launch
   // (empty splits store max = -inf, sum = 0), so nothing has to be cleared between calls.
   const int rc = prism_paged_decode(q, k_cache, v_cache, k_scale, v_scale, block_tables, context_lens,
-                                    nsplit > 1 ? part_o : nullptr, nsplit > 1 ? part_ml : nullptr, out, B, Hq, Hkv, D, page,
-                                    max_blocks, nsplit, kv_mode, scale, stream, 0);
+                                    nsplit > 1 ? part_o : nullptr, nsplit > 1 ? part_ml : nullptr, out, nullptr, B, Hq, Hkv,
+                                    D, page, max_blocks, nsplit, kv_mode, scale, stream, 0);
   if (rc != 0) return noalloc_fail(rc, "prism_paged_decode_noalloc: kernel launch failed");
   return 0;
 }

@@ -55,7 +55,7 @@ struct AddNormArgs {
   float eps;
 };
 
-__global__ void __launch_bounds__(256) add_rmsnorm_kernel(const AddNormArgs a) {
+__global__ void __launch_bounds__(1024) add_rmsnorm_kernel(const AddNormArgs a) {
   extern __shared__ float row[];  // H floats
   __shared__ float red[32];
   const int t = blockIdx.x;
@@ -66,51 +66,71 @@ __global__ void __launch_bounds__(256) add_rmsnorm_kernel(const AddNormArgs a) {
   int ex = -1;
   if (a.extra != nullptr) ex = a.extra_index[t];
   float ss = 0.0f;
-  for (int i = threadIdx.x * 2; i < H; i += blockDim.x * 2) {
-    float d0, d1;
+  // Four elements per thread and iteration; all partial-slab loads of an iteration are
+  // independent, so a single small-batch row keeps P * 16 bytes per thread in flight.
+  for (int i = threadIdx.x * 4; i < H; i += blockDim.x * 4) {
+    float d[4];
     if (a.P > 0) {
-      float s0 = 0.0f, s1 = 0.0f;
+      float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+      const float* p0 = a.partials + base + i;
+#pragma unroll 8
       for (int p = 0; p < a.P; ++p) {
-        const float2 v = *reinterpret_cast<const float2*>(a.partials + (size_t)p * a.slab_stride + base + i);
-        s0 += v.x;
-        s1 += v.y;
+        const float4 v = __ldg(reinterpret_cast<const float4*>(p0 + (size_t)p * a.slab_stride));
+        acc.x += v.x;
+        acc.y += v.y;
+        acc.z += v.z;
+        acc.w += v.w;
       }
-      d0 = bf16_round(s0);
-      d1 = bf16_round(s1);
+      d[0] = bf16_round(acc.x);
+      d[1] = bf16_round(acc.y);
+      d[2] = bf16_round(acc.z);
+      d[3] = bf16_round(acc.w);
     } else {
-      const __nv_bfloat162 v = *reinterpret_cast<const __nv_bfloat162*>(a.x_in + base + i);
-      d0 = b2f(v.x);
-      d1 = b2f(v.y);
+      const uint2 raw = *reinterpret_cast<const uint2*>(a.x_in + base + i);
+      const __nv_bfloat162* v = reinterpret_cast<const __nv_bfloat162*>(&raw);
+      d[0] = b2f(v[0].x);
+      d[1] = b2f(v[0].y);
+      d[2] = b2f(v[1].x);
+      d[3] = b2f(v[1].y);
     }
     if (a.residual_in != nullptr) {
-      const __nv_bfloat162 r = *reinterpret_cast<const __nv_bfloat162*>(a.residual_in + base + i);
-      d0 = bf16_round(b2f(r.x) + d0);
-      d1 = bf16_round(b2f(r.y) + d1);
+      const uint2 raw = *reinterpret_cast<const uint2*>(a.residual_in + base + i);
+      const __nv_bfloat162* r = reinterpret_cast<const __nv_bfloat162*>(&raw);
+      d[0] = bf16_round(b2f(r[0].x) + d[0]);
+      d[1] = bf16_round(b2f(r[0].y) + d[1]);
+      d[2] = bf16_round(b2f(r[1].x) + d[2]);
+      d[3] = bf16_round(b2f(r[1].y) + d[3]);
     }
     if (ex >= 0) {
-      const __nv_bfloat162 e = *reinterpret_cast<const __nv_bfloat162*>(a.extra + (size_t)ex * H + i);
-      d0 = bf16_round(d0 + b2f(e.x));
-      d1 = bf16_round(d1 + b2f(e.y));
+      const uint2 raw = *reinterpret_cast<const uint2*>(a.extra + (size_t)ex * H + i);
+      const __nv_bfloat162* e = reinterpret_cast<const __nv_bfloat162*>(&raw);
+      d[0] = bf16_round(d[0] + b2f(e[0].x));
+      d[1] = bf16_round(d[1] + b2f(e[0].y));
+      d[2] = bf16_round(d[2] + b2f(e[1].x));
+      d[3] = bf16_round(d[3] + b2f(e[1].y));
     }
     if (a.residual_out != nullptr) {
-      __nv_bfloat162 o;
-      o.x = f2b(d0);
-      o.y = f2b(d1);
-      *reinterpret_cast<__nv_bfloat162*>(a.residual_out + base + i) = o;
+      uint2 o;
+      *reinterpret_cast<__nv_bfloat162*>(&o.x) = __floats2bfloat162_rn(d[0], d[1]);
+      *reinterpret_cast<__nv_bfloat162*>(&o.y) = __floats2bfloat162_rn(d[2], d[3]);
+      *reinterpret_cast<uint2*>(a.residual_out + base + i) = o;
     }
-    row[i] = d0;
-    row[i + 1] = d1;
-    ss += d0 * d0 + d1 * d1;
+    *reinterpret_cast<float4*>(row + i) = make_float4(d[0], d[1], d[2], d[3]);
+    ss += d[0] * d[0] + d[1] * d[1] + d[2] * d[2] + d[3] * d[3];
   }
   ss = block_sum(ss, red);
   const float rstd = rsqrtf(ss / (float)H + a.eps);
   if (a.out != nullptr) {
-    for (int i = threadIdx.x * 2; i < H; i += blockDim.x * 2) {
-      const __nv_bfloat162 w = *reinterpret_cast<const __nv_bfloat162*>(a.weight + i);
-      __nv_bfloat162 o;
-      o.x = f2b(bf16_round(row[i] * rstd) * b2f(w.x));
-      o.y = f2b(bf16_round(row[i + 1] * rstd) * b2f(w.y));
-      *reinterpret_cast<__nv_bfloat162*>(a.out + base + i) = o;
+    for (int i = threadIdx.x * 4; i < H; i += blockDim.x * 4) {
+      const uint2 raw = *reinterpret_cast<const uint2*>(a.weight + i);
+      const __nv_bfloat162* w = reinterpret_cast<const __nv_bfloat162*>(&raw);
+      const float4 r = *reinterpret_cast<const float4*>(row + i);
+      uint2 o;
+      *reinterpret_cast<__nv_bfloat162*>(&o.x) =
+          __floats2bfloat162_rn(bf16_round(r.x * rstd) * b2f(w[0].x), bf16_round(r.y * rstd) * b2f(w[0].y));
+      *reinterpret_cast<__nv_bfloat162*>(&o.y) =
+          __floats2bfloat162_rn(bf16_round(r.z * rstd) * b2f(w[1].x), bf16_round(r.w * rstd) * b2f(w[1].y));
+      *reinterpret_cast<uint2*>(a.out + base + i) = o;
     }
   }
 }
@@ -402,7 +422,7 @@ PRISM_API int prism_add_rmsnorm(const void* partials, long long slab_stride, int
                                 const void* residual_in, void* residual_out, const void* extra, const void* extra_index,
                                 const void* weight, void* out, int T, int H, float eps, void* stream, int pdl) {
   if (T <= 0) return 0;
-  if (H % 2) return -1;
+  if (H % 4) return -1;
   AddNormArgs a;
   a.partials = (const float*)partials;
   a.slab_stride = slab_stride;
@@ -421,7 +441,10 @@ PRISM_API int prism_add_rmsnorm(const void* partials, long long slab_stride, int
     cudaError_t e = cudaFuncSetAttribute(add_rmsnorm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
   }
-  return (int)prism_launch(add_rmsnorm_kernel, dim3(T), dim3(256), smem, STREAM(stream), pdl != 0, a);
+  // few rows: one wide CTA per row so every element has its own thread; many rows: 256 threads
+  int threads = T <= 64 ? 1024 : 256;
+  while (threads > 32 && threads * 4 > H * 2) threads >>= 1;
+  return (int)prism_launch(add_rmsnorm_kernel, dim3(T), dim3(threads), smem, STREAM(stream), pdl != 0, a);
 }
 
 PRISM_API int prism_layernorm(const void* x, const void* w, const void* b, void* out, int T, int H, float eps,

@@ -24,8 +24,11 @@ __device__ __forceinline__ uint64_t mix64(uint64_t z) {
 __global__ void __launch_bounds__(1024) sample_kernel(const float* logits, long long row_stride, long long slab_stride,
                                                       int P, const float* temperature, long long* out_id,
                                                       float* out_val, int V, long long vocab_offset,
-                                                      unsigned long long seed, const long long* step) {
+                                                      unsigned long long seed, const long long* step,
+                                                      float* cand_val, long long* cand_id) {
   const int b = blockIdx.x;
+  // blockIdx.y selects a contiguous chunk of the vocabulary; with gridDim.y > 1 the winners
+  // go to cand_val / cand_id ([chunk][B]) and merge_candidates_kernel picks the final one.
   pdl_launch_dependents();
   pdl_wait();
   const float temp = temperature ? temperature[b] : 0.0f;
@@ -33,7 +36,9 @@ __global__ void __launch_bounds__(1024) sample_kernel(const float* logits, long 
   const float* row = logits + (size_t)b * row_stride;
   float best = -INFINITY;
   int best_i = 0x7fffffff;
-  for (int i = threadIdx.x; i < V; i += blockDim.x) {
+  const int chunk = (V + gridDim.y - 1) / gridDim.y;
+  const int i_begin = blockIdx.y * chunk, i_end = min(V, i_begin + chunk);
+  for (int i = i_begin + threadIdx.x; i < i_end; i += blockDim.x) {
     float v = 0.0f;
     for (int p = 0; p < P; ++p) v += row[(size_t)p * slab_stride + i];
     if (temp > 0.0f) {
@@ -77,14 +82,20 @@ __global__ void __launch_bounds__(1024) sample_kernel(const float* logits, long 
       }
     }
     if (lane == 0) {
-      out_id[b] = (long long)best_i + vocab_offset;
-      if (out_val) out_val[b] = best;
+      if (gridDim.y > 1) {
+        cand_val[(size_t)blockIdx.y * gridDim.x + b] = best;
+        cand_id[(size_t)blockIdx.y * gridDim.x + b] = (long long)best_i + vocab_offset;
+      } else {
+        out_id[b] = (long long)best_i + vocab_offset;
+        if (out_val) out_val[b] = best;
+      }
     }
   }
 }
 
 // Winner over R candidate (value, id) pairs per row: vals [R][B], ids [R][B].
-__global__ void merge_candidates_kernel(const float* vals, const long long* ids, long long* out, int R, int B) {
+__global__ void merge_candidates_kernel(const float* vals, const long long* ids, long long* out, float* out_val, int R,
+                                        int B) {
   const int b = blockIdx.x * blockDim.x + threadIdx.x;
   pdl_launch_dependents();
   pdl_wait();
@@ -100,22 +111,33 @@ __global__ void merge_candidates_kernel(const float* vals, const long long* ids,
     }
   }
   out[b] = best_i;
+  if (out_val) out_val[b] = best;
 }
 
 }  // namespace
 
+// cand_val / cand_id: scratch of chunks * B entries each (chunks > 1 spreads a row over
+// several CTAs; required to keep a 150k-entry row from being read by a single CTA).
 PRISM_API int prism_sample(const void* logits, long long row_stride, long long slab_stride, int P,
                            const void* temperature, void* out_id, void* out_val, int B, int V, long long vocab_offset,
-                           unsigned long long seed, const void* step, void* stream, int pdl) {
+                           unsigned long long seed, const void* step, void* cand_val, void* cand_id, int chunks,
+                           void* stream, int pdl) {
   if (B <= 0) return 0;
-  return (int)prism_launch(sample_kernel, dim3(B), dim3(1024), 0, reinterpret_cast<cudaStream_t>(stream), pdl != 0,
-                           (const float*)logits, row_stride, slab_stride, P < 1 ? 1 : P, (const float*)temperature,
-                           (long long*)out_id, (float*)out_val, V, vocab_offset, seed, (const long long*)step);
+  if (chunks < 1 || cand_val == nullptr || cand_id == nullptr) chunks = 1;
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  int rc = (int)prism_launch(sample_kernel, dim3(B, chunks), dim3(chunks > 1 ? 256 : 1024), 0, s, pdl != 0,
+                             (const float*)logits, row_stride, slab_stride, P < 1 ? 1 : P, (const float*)temperature,
+                             (long long*)out_id, (float*)out_val, V, vocab_offset, seed, (const long long*)step,
+                             (float*)cand_val, (long long*)cand_id);
+  if (rc || chunks == 1) return rc;
+  return (int)prism_launch(merge_candidates_kernel, dim3((B + 127) / 128), dim3(128), 0, s, pdl != 0,
+                           (const float*)cand_val, (const long long*)cand_id, (long long*)out_id, (float*)out_val, chunks,
+                           B);
 }
 
 PRISM_API int prism_merge_candidates(const void* vals, const void* ids, void* out, int R, int B, void* stream, int pdl) {
   if (B <= 0) return 0;
   return (int)prism_launch(merge_candidates_kernel, dim3((B + 127) / 128), dim3(128), 0,
                            reinterpret_cast<cudaStream_t>(stream), pdl != 0, (const float*)vals, (const long long*)ids,
-                           (long long*)out, R, B);
+                           (long long*)out, (float*)nullptr, R, B);
 }

@@ -37,11 +37,11 @@ _SIGNATURES = {
     "prism_indexed_add": "pppiipi",
     "prism_pos_embed_add": "ppppiipi",
     "prism_vit_rope": "pppiiipi",
-    "prism_paged_decode": "ppppppppppiiiiiiiifpi",
+    "prism_paged_decode": "pppppppppppiiiiiiiifpi",
     "prism_flash_attention": "plplppplppppppiiiiiiiiifpi",
     "prism_kv_page_copy": "ppllippllpppiiiip",
     "prism_kv_compact": "pliplppppiiiip",
-    "prism_sample": "pllipppiiluppi",
+    "prism_sample": "pllipppiilupppipi",
     "prism_merge_candidates": "pppiipi",
 }
 _STATUS_UNITS = ("gemm", "norm", "attn", "kvops", "sampler", "comm")
