@@ -374,8 +374,10 @@ class Config:
             if flat_options:
                 raise TypeError("flat options cannot be combined with a PrismConfig")
             self.prism = model
+            self._flat_options = {}
         else:
             self.prism = PrismConfig.from_flat_options(model, flat_options)
+            self._flat_options = dict(flat_options)  # replayed verbatim by spawned worker ranks
         self.arch = arch if arch is not None else resolve_arch(self.prism.model.model)
         validate_tensor_parallel(self.arch, self.prism.model.tensor_parallel_size)
         self.max_model_len = min(self.prism.model.max_model_len, self.arch.text.max_position_embeddings)

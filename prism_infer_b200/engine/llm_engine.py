@@ -65,6 +65,8 @@ class LLMEngine:
             from ..parallel.launch import start_tensor_parallel_group
 
             self.runners = start_tensor_parallel_group(cfg, weights=weights)
+            if self.runners.is_driver:
+                cfg.with_cache_capacity(*self.runners.call("capacity"))
         else:
             from .model_runner import ModelRunner
 

@@ -48,8 +48,9 @@ def decode_buckets(max_num_seqs: int) -> list[int]:
 class _DecodeGraph:
     """Static buffers + captured graph of one batch bucket."""
 
-    def __init__(self, runner: "ModelRunner", bucket: int) -> None:
+    def __init__(self, runner: "ModelRunner", bucket: int, greedy_only: bool = False) -> None:
         self.bucket = bucket
+        self.greedy_only = greedy_only
         dev = runner.device
         mb = runner.max_blocks
         # byte layout of the packed staging buffer (all offsets 16-byte aligned)
@@ -134,6 +135,7 @@ class ModelRunner:
         self._visual_cache_bytes = 0
         self.visual_cache_counters = {"hits": 0, "misses": 0, "evictions": 0}
         self.graphs: dict[int, _DecodeGraph] = {}
+        self.greedy_graphs: dict[int, _DecodeGraph] = {}
         self.buckets = decode_buckets(min(config.max_num_seqs, 512))
         self.sample_seed = config.seed
         self.steps_run = 0
@@ -285,14 +287,17 @@ class ModelRunner:
         meta = AttnMeta(is_prefill=False, block_tables=g.d_bt, slots=g.d_slots, context_lens=g.d_ctx,
                         nsplit=ops.decode_splits(g.bucket, self.kv.num_kv_heads))
         hidden = self.model.forward(g.d_ids, g.d_pos, meta, self.kv)
-        self.model.sample(hidden, g.d_temp, seed=self.sample_seed, step=g.step, out=g.tokens)
+        self.model.sample(hidden, None if g.greedy_only else g.d_temp, seed=self.sample_seed, step=g.step, out=g.tokens)
 
     def capture_graphs(self) -> None:
         """Capture one graph per bucket, largest first so smaller ones reuse its pool."""
         pool = None
         stream = torch.cuda.Stream(device=self.device)
-        for bucket in sorted(self.buckets, reverse=True):
-            g = _DecodeGraph(self, bucket)
+        # one graph per bucket takes the temperature as an input; tensor-parallel ranks add a
+        # greedy-only graph whose sampler is the one-kernel (value, id) exchange
+        variants = [(b, False) for b in self.buckets] + ([(b, True) for b in self.buckets] if self.comm.size > 1 else [])
+        for bucket, greedy_only in sorted(variants, reverse=True):
+            g = _DecodeGraph(self, bucket, greedy_only)
             from ..ops import native as _native
 
             with torch.cuda.stream(stream):
@@ -310,14 +315,15 @@ class ModelRunner:
             g.graph = graph
             g.launches = _native.launch_count() - before
             pool = graph.pool() if pool is None else pool
-            self.graphs[bucket] = g
+            (self.greedy_graphs if greedy_only else self.graphs)[bucket] = g
         torch.cuda.synchronize(self.device)
 
     def _run_decode_graph(self, inp: StepInputs) -> list[int]:
         n = inp.num_seqs
         bucket = next(b for b in self.buckets if b >= n)
-        g = self.graphs[bucket]
-        self._last_bucket = bucket
+        greedy = bucket in self.greedy_graphs and not bool((inp.temperatures > 0).any())
+        g = (self.greedy_graphs if greedy else self.graphs)[bucket]
+        self._last_bucket, self._last_greedy = bucket, greedy
         with profile_region("runner.cudagraph.copy_inputs"):
             g.fill(inp)
         with profile_region("runner.cudagraph.replay"):
@@ -328,7 +334,8 @@ class ModelRunner:
     def time_decode_graph(self, steps: int) -> float:
         """Device milliseconds per decode step: CUDA events around ``steps`` back-to-back
         launches of the most recently used bucket graph (inputs stay as last filled)."""
-        g = self.graphs[getattr(self, "_last_bucket", self.buckets[0])]
+        table = self.greedy_graphs if getattr(self, "_last_greedy", False) else self.graphs
+        g = table[getattr(self, "_last_bucket", self.buckets[0])]
         start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         torch.cuda.synchronize(self.device)
         start.record()
@@ -345,10 +352,23 @@ class ModelRunner:
                 "staging_bytes": {str(b): g.nbytes for b, g in self.graphs.items()},
                 "weight_bytes": self.model.weight_bytes()}
 
+    def barrier(self) -> None:
+        if self.on_cuda:
+            torch.cuda.synchronize(self.device)
+
+    def status(self) -> dict:
+        """Device status words (bounded waits that ran out, bounds checks) of this rank."""
+        if not self.on_cuda:
+            return {}
+        from ..ops import native
+
+        return native.read_status(reset=True)
+
     def capacity(self) -> tuple[int, int]:
         return self.config.num_kvcache_blocks, self.config.num_cpu_blocks
 
     def exit(self) -> None:
         self.graphs.clear()
+        self.greedy_graphs.clear()
         self._visual.clear()
         self._visual_cache.clear()

@@ -111,6 +111,22 @@ class TPComm:
     def all_gather_rows(self, x: torch.Tensor) -> torch.Tensor:
         return x
 
+    def begin_step(self) -> None:
+        return None
+
+    def row_parallel(self, x: torch.Tensor, w: torch.Tensor):
+        """Row-parallel projection -> ``(dense, partials, ticket)``; exactly one is set."""
+        T = x.shape[0]
+        if T <= SMALL_T:
+            splits = ops.choose_splits(w.shape[0], w.shape[1], T) if x.is_cuda else 1
+            return None, ops.linear_partial(x, w, splits), None
+        return ops.linear(x, w), None, None
+
+    def add_rmsnorm(self, weight, eps, dense, partials, ticket, residual, extra=None, extra_index=None):
+        """``(normed, new_residual)`` from whatever ``row_parallel`` returned."""
+        return ops.add_rmsnorm(weight, eps, x=dense, partials=partials, residual=residual, extra=extra,
+                               extra_index=extra_index)
+
 
 class Qwen3VLModel:
     def __init__(self, arch: Qwen3VLArch, *, device, dtype: torch.dtype, comm: TPComm | None = None,
@@ -323,14 +339,6 @@ class Qwen3VLModel:
         return ops.linear(h, m.fc2_w, bias=m.fc2_b)
 
     # ---------------------------------------------------------------------- text
-    def _row_parallel(self, x: torch.Tensor, w: torch.Tensor):
-        """Row-parallel projection.  Returns ``(dense, partials)``: exactly one is set."""
-        T = x.shape[0]
-        if T <= SMALL_T:
-            splits = ops.choose_splits(w.shape[0], w.shape[1], T) if x.is_cuda else 1
-            return None, self.comm.reduce_partials(ops.linear_partial(x, w, splits))
-        return self.comm.reduce_dense(ops.linear(x, w)), None
-
     @torch.no_grad()
     def forward(
         self,
@@ -351,16 +359,21 @@ class Qwen3VLModel:
         t = self.arch.text
         T = input_ids.shape[0]
         small = T <= SMALL_T
-        x = ops.embed(input_ids, self.embed, visual=visual, vis_index=vis_index, vocab_start=self.vocab_start)
+        comm = self.comm
+        comm.begin_step()
+        emb_visual = visual
+        if self.tp > 1 and visual is not None and self.rank != 0:
+            emb_visual = torch.zeros_like(visual)  # only rank 0 contributes visual rows to the sum
+        x = ops.embed(input_ids, self.embed, visual=emb_visual, vis_index=vis_index, vocab_start=self.vocab_start)
         if self.tp > 1:
             x = self.comm.reduce_dense(x)
         residual: Optional[torch.Tensor] = None
-        dense, partials = x, None
+        dense, partials, ticket = x, None, None
         n_deep = len(deepstack) if deepstack is not None else 0
         for i, l in enumerate(self.layers):
             extra = deepstack[i - 1] if 0 < i <= n_deep else None
-            h, residual = ops.add_rmsnorm(l.input_norm, t.rms_norm_eps, x=dense, partials=partials, residual=residual,
-                                          extra=extra, extra_index=vis_index if extra is not None else None)
+            h, residual = comm.add_rmsnorm(l.input_norm, t.rms_norm_eps, dense, partials, ticket, residual,
+                                           extra, vis_index if extra is not None else None)
             if small and h.is_cuda:
                 qkv_p = ops.linear_partial(h, l.qkv, ops.choose_splits(l.qkv.shape[0], self.H, T))
                 q = ops.qk_norm_rope_store(qkv=None, partials=qkv_p, positions=positions, q_weight=l.q_norm, k_weight=l.k_norm,
@@ -376,13 +389,13 @@ class Qwen3VLModel:
             else:
                 a = ops.paged_decode_attention(q, cache, i, meta.block_tables, meta.context_lens, nsplit=meta.nsplit,
                                                workspace=meta.workspace)
-            dense, partials = self._row_parallel(a.view(T, self.Hq * self.D), l.o)
-            h, residual = ops.add_rmsnorm(l.post_norm, t.rms_norm_eps, x=dense, partials=partials, residual=residual)
+            dense, partials, ticket = comm.row_parallel(a.view(T, self.Hq * self.D), l.o)
+            h, residual = comm.add_rmsnorm(l.post_norm, t.rms_norm_eps, dense, partials, ticket, residual)
             act = ops.gate_up_swiglu(h, l.gate_up)
-            dense, partials = self._row_parallel(act, l.down)
+            dense, partials, ticket = comm.row_parallel(act, l.down)
         extra = deepstack[n_deep - 1] if n_deep == len(self.layers) else None
-        h, _ = ops.add_rmsnorm(self.final_norm, t.rms_norm_eps, x=dense, partials=partials, residual=residual,
-                               extra=extra, extra_index=vis_index if extra is not None else None)
+        h, _ = comm.add_rmsnorm(self.final_norm, t.rms_norm_eps, dense, partials, ticket, residual,
+                                extra, vis_index if extra is not None else None)
         return h
 
     @torch.no_grad()

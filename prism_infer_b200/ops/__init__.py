@@ -442,8 +442,8 @@ def embed(ids: torch.Tensor, table: torch.Tensor, *, visual: Optional[torch.Tens
 
 # --------------------------------------------------------------------------- attention
 def decode_splits(batch: int, num_kv_heads: int) -> int:
-    want = max(1, SM_COUNT // max(1, batch * num_kv_heads))
-    return int(min(16, want))
+    want = max(1, (2 * SM_COUNT) // max(1, batch * num_kv_heads))
+    return int(min(32, want))
 
 
 _DECODE_COUNTERS: dict = {}

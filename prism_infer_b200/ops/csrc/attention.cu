@@ -60,7 +60,7 @@ __global__ void __launch_bounds__(128) paged_decode_kernel(const DecodeArgs a) {
   pdl_launch_dependents();
   pdl_wait();
   const int ctx = a.context_lens[b];
-  const int per_split = ((ctx + a.nsplit - 1) / a.nsplit + TPW * NWARP - 1) / (TPW * NWARP) * (TPW * NWARP);
+  const int per_split = ((ctx + a.nsplit - 1) / a.nsplit + TPW * NWARP * 4 - 1) / (TPW * NWARP * 4) * (TPW * NWARP * 4);
   const int j_begin = split * per_split;
   const int j_end = min(ctx, j_begin + per_split);
 
@@ -81,38 +81,53 @@ __global__ void __launch_bounds__(128) paged_decode_kernel(const DecodeArgs a) {
   }
   const int* bt = a.block_tables + (size_t)b * a.max_blocks;
 
-  for (int j0 = j_begin + warp * TPW; j0 < j_end; j0 += TPW * NWARP) {
-    const int j = j0 + slot;
-    int blk = -1;
-    if (j < j_end) blk = bt[j / a.page];
-    const bool valid = blk >= 0;
-    float kf[EPL], vf[EPL];
-    float ks = 1.0f, vs = 1.0f;
-    if (valid) {
-      const size_t row = ((size_t)blk * a.Hkv + kvh) * a.page + (j % a.page);
+  // UNR independent token groups per warp iteration: all page-table, payload and scale
+  // loads of an iteration are issued before any arithmetic, so a short context costs one
+  // or two memory round trips instead of one per group.
+  constexpr int UNR = 4;
+  for (int j0 = j_begin + warp * TPW * UNR; j0 < j_end; j0 += TPW * NWARP * UNR) {
+    uint4 kr[UNR], vr[UNR];
+    float ks[UNR], vs[UNR];
+    bool valid[UNR];
+#pragma unroll
+    for (int u = 0; u < UNR; ++u) {
+      const int j = j0 + u * TPW + slot;
+      int blk = -1;
+      if (j < j_end) blk = bt[j / a.page];
+      valid[u] = blk >= 0;
+      kr[u] = make_uint4(0, 0, 0, 0);
+      vr[u] = make_uint4(0, 0, 0, 0);
+      ks[u] = 1.0f;
+      vs[u] = 1.0f;
+      if (valid[u]) {
+        const size_t row = ((size_t)blk * a.Hkv + kvh) * a.page + (j % a.page);
+        const size_t off = row * D * (KV8 ? 1 : 2) + (size_t)part * 16;
+        kr[u] = __ldg(reinterpret_cast<const uint4*>(reinterpret_cast<const uint8_t*>(a.k_cache) + off));
+        vr[u] = __ldg(reinterpret_cast<const uint4*>(reinterpret_cast<const uint8_t*>(a.v_cache) + off));
+        if (KV8 && a.k_scale != nullptr) {
+          ks[u] = __ldg(a.k_scale + row);
+          vs[u] = __ldg(a.v_scale + row);
+        }
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < UNR; ++u) {
+      float kf[EPL], vf[EPL];
       if (KV8) {
-        const uint4 kr = *reinterpret_cast<const uint4*>(reinterpret_cast<const uint8_t*>(a.k_cache) + row * D + part * 16);
-        const uint4 vr = *reinterpret_cast<const uint4*>(reinterpret_cast<const uint8_t*>(a.v_cache) + row * D + part * 16);
-        const unsigned short* kp = reinterpret_cast<const unsigned short*>(&kr);
-        const unsigned short* vp = reinterpret_cast<const unsigned short*>(&vr);
+        const unsigned short* kp = reinterpret_cast<const unsigned short*>(&kr[u]);
+        const unsigned short* vp = reinterpret_cast<const unsigned short*>(&vr[u]);
 #pragma unroll
         for (int e = 0; e < 8; ++e) {
           const float2 kk = fp8x2_to_float2(kp[e]);
           const float2 vv = fp8x2_to_float2(vp[e]);
-          kf[2 * e] = kk.x;
-          kf[2 * e + 1] = kk.y;
-          vf[2 * e] = vv.x;
-          vf[2 * e + 1] = vv.y;
-        }
-        if (a.k_scale != nullptr) {
-          ks = a.k_scale[row];
-          vs = a.v_scale[row];
+          kf[(2 * e) % EPL] = kk.x;
+          kf[(2 * e + 1) % EPL] = kk.y;
+          vf[(2 * e) % EPL] = vv.x;
+          vf[(2 * e + 1) % EPL] = vv.y;
         }
       } else {
-        const uint4 kr = *reinterpret_cast<const uint4*>(reinterpret_cast<const bf16*>(a.k_cache) + row * D + part * 8);
-        const uint4 vr = *reinterpret_cast<const uint4*>(reinterpret_cast<const bf16*>(a.v_cache) + row * D + part * 8);
-        const __nv_bfloat162* kp = reinterpret_cast<const __nv_bfloat162*>(&kr);
-        const __nv_bfloat162* vp = reinterpret_cast<const __nv_bfloat162*>(&vr);
+        const __nv_bfloat162* kp = reinterpret_cast<const __nv_bfloat162*>(&kr[u]);
+        const __nv_bfloat162* vp = reinterpret_cast<const __nv_bfloat162*>(&vr[u]);
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
           const float2 kk = __bfloat1622float2(kp[e]);
@@ -123,30 +138,24 @@ __global__ void __launch_bounds__(128) paged_decode_kernel(const DecodeArgs a) {
           vf[2 * e + 1] = vv.y;
         }
       }
-    } else {
 #pragma unroll
-      for (int e = 0; e < EPL; ++e) {
-        kf[e] = 0.0f;
-        vf[e] = 0.0f;
-      }
-    }
+      for (int g = 0; g < G; ++g) {
+        float s = 0.0f;
 #pragma unroll
-    for (int g = 0; g < G; ++g) {
-      float s = 0.0f;
+        for (int e = 0; e < EPL; ++e) s += q[g][e] * kf[e];
 #pragma unroll
-      for (int e = 0; e < EPL; ++e) s += q[g][e] * kf[e];
+        for (int o = LPT / 2; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+        if (valid[u]) {
+          s *= ks[u];
+          const float mn = fmaxf(m[g], s);
+          const float corr = __expf(m[g] - mn);
+          const float p = __expf(s - mn);
+          l[g] = l[g] * corr + p;
+          const float pv = p * vs[u];
 #pragma unroll
-      for (int o = LPT / 2; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
-      if (valid) {
-        s *= ks;
-        const float mn = fmaxf(m[g], s);
-        const float corr = __expf(m[g] - mn);
-        const float p = __expf(s - mn);
-        l[g] = l[g] * corr + p;
-        const float pv = p * vs;
-#pragma unroll
-        for (int e = 0; e < EPL; ++e) acc[g][e] = acc[g][e] * corr + pv * vf[e];
-        m[g] = mn;
+          for (int e = 0; e < EPL; ++e) acc[g][e] = acc[g][e] * corr + pv * vf[e];
+          m[g] = mn;
+        }
       }
     }
   }
@@ -228,6 +237,7 @@ __global__ void __launch_bounds__(128) paged_decode_kernel(const DecodeArgs a) {
     float mm = -INFINITY;
     for (int s = 0; s < a.nsplit; ++s) mm = fmaxf(mm, __ldcg(&a.part_ml[(bh * a.nsplit + s) * 2]));
     float ll = 0.0f, oo = 0.0f;
+#pragma unroll 4
     for (int s = 0; s < a.nsplit; ++s) {
       const float ms = __ldcg(&a.part_ml[(bh * a.nsplit + s) * 2]);
       const float c = (ms == -INFINITY) ? 0.0f : __expf(ms - mm);

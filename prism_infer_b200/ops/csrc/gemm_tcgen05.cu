@@ -51,6 +51,15 @@ struct GemmArgs {
   const __nv_bfloat16* bias;
   const __nv_bfloat16* residual;
   void* out;
+  // push mode (tensor parallel, fused GEMM -> exchange): the fp32 partial tile is written
+  // into every rank's slab group and the last CTA raises a flag on every rank.
+  int n_peers;               // 0 = off
+  int my_rank;
+  int point;                 // exchange point index inside the step
+  int* cta_counter;          // local, zero-initialised, self-resetting
+  const unsigned long long* epoch;  // local device word: sequence base of the current step
+  float* peer_out[8];        // slab buffers of this exchange slot on every rank (incl. own)
+  unsigned long long* peer_flag[8];  // flag arrays [tp] of this slot on every rank
 };
 
 template <int BN, bool DUAL>
@@ -193,6 +202,10 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
                 const float u = bf16_round(__uint_as_float(r2[j]));
                 v = bf16_round(silu(g)) * u;
                 out_b[(size_t)n * a.ldo + m] = __float2bfloat16_rn(v);
+              } else if (a.n_peers > 0) {
+                const size_t off = (size_t)(a.my_rank * (int)gridDim.z + split) * a.split_stride + (size_t)n * a.ldo + m;
+#pragma unroll 8
+                for (int p = 0; p < a.n_peers; ++p) a.peer_out[p][off] = v;
               } else if (a.out_f32) {
                 out_f[(size_t)n * a.ldo + m] = v;
               } else {
@@ -208,9 +221,22 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
       }
     }
   }
+  if (a.n_peers > 0 && warp >= 2) __threadfence_system();  // partial tiles visible to every GPU
   tc_fence_before();
   __syncthreads();
   if (warp == 1) tmem_dealloc(tmem_base, TMEM_COLS);
+  if (a.n_peers > 0 && threadIdx.x == 0) {
+    const int total = gridDim.x * gridDim.y * gridDim.z;
+    const int old = atomicAdd(a.cta_counter, 1);
+    if (old == total - 1) {
+      *a.cta_counter = 0;
+      __threadfence_system();
+      const unsigned long long seq = *a.epoch + (unsigned long long)a.point;
+      for (int p = 0; p < a.n_peers; ++p) {
+        asm volatile("st.release.sys.global.u64 [%0], %1;" ::"l"(a.peer_flag[p] + a.my_rank), "l"(seq) : "memory");
+      }
+    }
+  }
 }
 
 // ------------------------------------------------------------------------------------
@@ -312,10 +338,18 @@ int launch_gemm(const CUtensorMap& tw, const CUtensorMap& tx, GemmArgs& a, int m
 // out: bf16 [T, ldo] (features along the row) or fp32 [splits][T][ldo] when out_f32.
 // dual: second weight tile starts at row w2_row_off; output = silu(W1 x) * (W2 x), M rows.
 // Returns 0 on success, a cudaError_t (>0) or a negative validation code.
-PRISM_API int prism_gemm_wx(const void* W, const void* X, void* out, int M, int T, int K, long long ldw, long long ldx,
-                            long long ldo, int w_rows_total, const void* bias, const void* residual, long long ldr,
-                            int act, int dual, int w2_row_off, int splits, int out_f32, long long split_stride,
-                            int bn_override, int stages_override, void* stream_ptr, int pdl) {
+struct PushSpec {
+  int n_peers, my_rank, point;
+  int* cta_counter;
+  const unsigned long long* epoch;
+  float* peer_out[8];
+  unsigned long long* peer_flag[8];
+};
+
+static int gemm_wx_impl(const void* W, const void* X, void* out, int M, int T, int K, long long ldw, long long ldx,
+                        long long ldo, int w_rows_total, const void* bias, const void* residual, long long ldr, int act,
+                        int dual, int w2_row_off, int splits, int out_f32, long long split_stride, int bn_override,
+                        int stages_override, void* stream_ptr, int pdl, const PushSpec* push) {
   if (M <= 0 || T <= 0 || K <= 0) return -1;
   if (K % 8) return -2;  // 16-byte row pitch for TMA
   if (dual && (splits > 1 || out_f32)) return -3;
@@ -351,6 +385,26 @@ PRISM_API int prism_gemm_wx(const void* W, const void* X, void* out, int M, int 
   a.bias = reinterpret_cast<const __nv_bfloat16*>(bias);
   a.residual = reinterpret_cast<const __nv_bfloat16*>(residual);
   a.out = out;
+  a.n_peers = 0;
+  a.my_rank = 0;
+  a.point = 0;
+  a.cta_counter = nullptr;
+  a.epoch = nullptr;
+  for (int p = 0; p < 8; ++p) {
+    a.peer_out[p] = nullptr;
+    a.peer_flag[p] = nullptr;
+  }
+  if (push != nullptr) {
+    a.n_peers = push->n_peers;
+    a.my_rank = push->my_rank;
+    a.point = push->point;
+    a.cta_counter = push->cta_counter;
+    a.epoch = push->epoch;
+    for (int p = 0; p < push->n_peers && p < 8; ++p) {
+      a.peer_out[p] = push->peer_out[p];
+      a.peer_flag[p] = push->peer_flag[p];
+    }
+  }
   CUtensorMap tw, tx;
   int rc = get_tensor_map(W, (unsigned long long)w_rows_total, (unsigned long long)K, (unsigned long long)ldw, BM, &tw);
   if (rc) return rc;
@@ -371,6 +425,39 @@ PRISM_API int prism_gemm_wx(const void* W, const void* X, void* out, int M, int 
   }
 #undef PRISM_GEMM_CASE
   return -6;
+}
+
+PRISM_API int prism_gemm_wx(const void* W, const void* X, void* out, int M, int T, int K, long long ldw, long long ldx,
+                            long long ldo, int w_rows_total, const void* bias, const void* residual, long long ldr,
+                            int act, int dual, int w2_row_off, int splits, int out_f32, long long split_stride,
+                            int bn_override, int stages_override, void* stream_ptr, int pdl) {
+  return gemm_wx_impl(W, X, out, M, T, K, ldw, ldx, ldo, w_rows_total, bias, residual, ldr, act, dual, w2_row_off, splits,
+                      out_f32, split_stride, bn_override, stages_override, stream_ptr, pdl, nullptr);
+}
+
+// Fused row-parallel GEMM -> one-shot exchange: the fp32 partial of rank `my_rank`, split s,
+// lands in slab (my_rank * splits + s) of every rank's buffer (peer_out[p], p < n_peers, own
+// rank included; row stride ldo, slab stride split_stride elements), then flag[my_rank] on
+// every rank is set to *epoch + point.  peer_out / peer_flag are host arrays of device
+// pointers (peer-mapped through CUDA IPC).  The consumer is prism_add_rmsnorm_wait.
+PRISM_API int prism_gemm_wx_push(const void* W, const void* X, int M, int T, int K, long long ldw, long long ldx,
+                                 long long ldo, int w_rows_total, int splits, long long split_stride,
+                                 const void* const* peer_out, const void* const* peer_flag, int n_peers, int my_rank,
+                                 int point, void* cta_counter, const void* epoch, int bn_override, int stages_override,
+                                 void* stream_ptr, int pdl) {
+  if (n_peers < 1 || n_peers > 8) return -20;
+  PushSpec ps;
+  ps.n_peers = n_peers;
+  ps.my_rank = my_rank;
+  ps.point = point;
+  ps.cta_counter = reinterpret_cast<int*>(cta_counter);
+  ps.epoch = reinterpret_cast<const unsigned long long*>(epoch);
+  for (int p = 0; p < 8; ++p) {
+    ps.peer_out[p] = p < n_peers ? reinterpret_cast<float*>(const_cast<void*>(peer_out[p])) : nullptr;
+    ps.peer_flag[p] = p < n_peers ? reinterpret_cast<unsigned long long*>(const_cast<void*>(peer_flag[p])) : nullptr;
+  }
+  return gemm_wx_impl(W, X, const_cast<void*>(peer_out[my_rank]), M, T, K, ldw, ldx, ldo, w_rows_total, nullptr, nullptr,
+                      0, 0, 0, 0, splits, 1, split_stride, bn_override, stages_override, stream_ptr, pdl, &ps);
 }
 
 // Number of split-K slabs prism_gemm_wx will actually write for (K, splits).

@@ -53,7 +53,28 @@ struct AddNormArgs {
   bf16* out;
   int H;
   float eps;
+  // tensor-parallel consumer side of the fused GEMM -> exchange: wait until every source
+  // rank's flag reached *epoch + point before reading the partial slabs
+  const unsigned long long* wait_flags;  // [n_wait] local flags written by the peers
+  int n_wait;
+  const unsigned long long* epoch;
+  int point;
 };
+
+// Bounded acquire-spin on a flag another GPU writes.  Returns false after
+// PRISM_WAIT_CYCLES and records PRISM_ERR_PEER_TIMEOUT: the caller continues with whatever
+// data is there, the host sees the status word, nothing hangs.
+__device__ __forceinline__ bool wait_flag_ge(const unsigned long long* flag, unsigned long long want, int tag) {
+  const long long t0 = clock64();
+  for (;;) {
+    unsigned long long v;
+    asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(flag) : "memory");
+    if (v >= want) return true;
+    if (clock64() - t0 > PRISM_WAIT_CYCLES) break;
+  }
+  prism_report(PRISM_ERR_PEER_TIMEOUT, tag);
+  return false;
+}
 
 __global__ void __launch_bounds__(1024) add_rmsnorm_kernel(const AddNormArgs a) {
   extern __shared__ float row[];  // H floats
@@ -62,6 +83,10 @@ __global__ void __launch_bounds__(1024) add_rmsnorm_kernel(const AddNormArgs a) 
   const int H = a.H;
   pdl_launch_dependents();
   pdl_wait();
+  if (a.n_wait > 0) {
+    if ((int)threadIdx.x < a.n_wait) wait_flag_ge(a.wait_flags + threadIdx.x, *a.epoch + (unsigned long long)a.point, threadIdx.x);
+    __syncthreads();
+  }
   const size_t base = (size_t)t * H;
   int ex = -1;
   if (a.extra != nullptr) ex = a.extra_index[t];
@@ -75,7 +100,7 @@ __global__ void __launch_bounds__(1024) add_rmsnorm_kernel(const AddNormArgs a) 
       const float* p0 = a.partials + base + i;
 #pragma unroll 8
       for (int p = 0; p < a.P; ++p) {
-        const float4 v = __ldg(reinterpret_cast<const float4*>(p0 + (size_t)p * a.slab_stride));
+        const float4 v = __ldcg(reinterpret_cast<const float4*>(p0 + (size_t)p * a.slab_stride));
         acc.x += v.x;
         acc.y += v.y;
         acc.z += v.z;
@@ -418,9 +443,10 @@ __global__ void __launch_bounds__(256) vit_rope_kernel(bf16* qkv, const int* coo
 
 #define STREAM(p) reinterpret_cast<cudaStream_t>(p)
 
-PRISM_API int prism_add_rmsnorm(const void* partials, long long slab_stride, int P, const void* x_in,
-                                const void* residual_in, void* residual_out, const void* extra, const void* extra_index,
-                                const void* weight, void* out, int T, int H, float eps, void* stream, int pdl) {
+static int add_rmsnorm_impl(const void* partials, long long slab_stride, int P, const void* x_in,
+                            const void* residual_in, void* residual_out, const void* extra, const void* extra_index,
+                            const void* weight, void* out, int T, int H, float eps, void* stream, int pdl,
+                            const void* wait_flags, int n_wait, const void* epoch, int point) {
   if (T <= 0) return 0;
   if (H % 4) return -1;
   AddNormArgs a;
@@ -436,6 +462,10 @@ PRISM_API int prism_add_rmsnorm(const void* partials, long long slab_stride, int
   a.out = (bf16*)out;
   a.H = H;
   a.eps = eps;
+  a.wait_flags = (const unsigned long long*)wait_flags;
+  a.n_wait = n_wait;
+  a.epoch = (const unsigned long long*)epoch;
+  a.point = point;
   const size_t smem = (size_t)H * sizeof(float);
   if (smem > 48 * 1024) {
     cudaError_t e = cudaFuncSetAttribute(add_rmsnorm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -445,6 +475,23 @@ PRISM_API int prism_add_rmsnorm(const void* partials, long long slab_stride, int
   int threads = T <= 64 ? 1024 : 256;
   while (threads > 32 && threads * 4 > H * 2) threads >>= 1;
   return (int)prism_launch(add_rmsnorm_kernel, dim3(T), dim3(threads), smem, STREAM(stream), pdl != 0, a);
+}
+
+PRISM_API int prism_add_rmsnorm(const void* partials, long long slab_stride, int P, const void* x_in,
+                                const void* residual_in, void* residual_out, const void* extra, const void* extra_index,
+                                const void* weight, void* out, int T, int H, float eps, void* stream, int pdl) {
+  return add_rmsnorm_impl(partials, slab_stride, P, x_in, residual_in, residual_out, extra, extra_index, weight, out, T, H,
+                          eps, stream, pdl, nullptr, 0, nullptr, 0);
+}
+
+// Same, but first waits (bounded) until wait_flags[0..n_wait) >= *epoch + point: the
+// consumer of prism_gemm_wx_push.  partials must be the local slab buffer of that slot.
+PRISM_API int prism_add_rmsnorm_wait(const void* partials, long long slab_stride, int P, const void* residual_in,
+                                     void* residual_out, const void* extra, const void* extra_index, const void* weight,
+                                     void* out, int T, int H, float eps, const void* wait_flags, int n_wait,
+                                     const void* epoch, int point, void* stream, int pdl) {
+  return add_rmsnorm_impl(partials, slab_stride, P, nullptr, residual_in, residual_out, extra, extra_index, weight, out, T,
+                          H, eps, stream, pdl, wait_flags, n_wait, epoch, point);
 }
 
 PRISM_API int prism_layernorm(const void* x, const void* w, const void* b, void* out, int T, int H, float eps,

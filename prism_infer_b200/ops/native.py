@@ -43,6 +43,15 @@ _SIGNATURES = {
     "prism_kv_compact": "pliplppppiiiip",
     "prism_sample": "pllipppiilupppipi",
     "prism_merge_candidates": "pppiipi",
+    "prism_gemm_wx_push": "ppiiillliilppiiippiipi",
+    "prism_add_rmsnorm_wait": "plippppppiifpipipi",
+    "prism_ipc_alloc": "lp",
+    "prism_ipc_free": "p",
+    "prism_ipc_get_handle": "pp",
+    "prism_ipc_open_handle": "pp",
+    "prism_ipc_close_handle": "p",
+    "prism_epoch_advance": "plpi",
+    "prism_argmax_exchange": "ppppppppiiiiipi",
 }
 _STATUS_UNITS = ("gemm", "norm", "attn", "kvops", "sampler", "comm")
 

@@ -1,0 +1,149 @@
+"""Tensor-parallel collectives behind the model's ``TPComm`` hooks.
+
+* ``NcclComm``: the baseline arm, what the reference does (``dist.all_reduce`` after every
+  row-parallel GEMM, ``prism_infer/layers/linear.py:186-190``; vocabulary-parallel embedding
+  all-reduce and distributed greedy arg-max, ``prism_infer/layers/embed_head.py:49-125``).
+* ``FusedComm``: the product path for decode-sized steps (at most 128 tokens).  The
+  row-parallel GEMM writes its fp32 partial tiles straight into every rank's slab buffer
+  over NVLink from its epilogue and raises a per-rank flag (``prism_gemm_wx_push``); the
+  following add+RMSNorm kernel waits on the flags, sums the ``tp * splits`` slabs in rank
+  order (bitwise identical on every rank) and normalises (``prism_add_rmsnorm_wait``).  No
+  NCCL call, no separate all-reduce kernel, two exchange slots used alternately.  The
+  greedy token is agreed on by a one-kernel (value, id) exchange.  Prefill-sized steps fall
+  back to the NCCL path.
+"""
+
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+import torch.distributed as dist
+
+from .. import ops
+from ..models.qwen3_vl import SMALL_T, TPComm
+from ..ops import native
+from . import symm
+
+
+class NcclComm(TPComm):
+    def __init__(self, rank: int, size: int, group=None) -> None:
+        self.rank, self.size, self.group = rank, size, group
+
+    def begin_step(self) -> None:
+        return None
+
+    def reduce_partials(self, partials: torch.Tensor) -> torch.Tensor:
+        total = partials.sum(0, keepdim=True) if partials.shape[0] > 1 else partials
+        dist.all_reduce(total, group=self.group)
+        return total
+
+    def reduce_dense(self, x: torch.Tensor) -> torch.Tensor:
+        dist.all_reduce(x, group=self.group)
+        return x
+
+    def greedy_merge(self, local_val: torch.Tensor, local_id: torch.Tensor) -> torch.Tensor:
+        packed = torch.stack((local_val.double(), local_id.double()))  # ids < 2**53 are exact
+        gathered = [torch.empty_like(packed) for _ in range(self.size)]
+        dist.all_gather(gathered, packed, group=self.group)
+        allv = torch.stack([g[0] for g in gathered])  # [tp, B]
+        alli = torch.stack([g[1] for g in gathered])
+        best = allv.max(0).values
+        cand = torch.where(allv == best[None], alli, torch.full_like(alli, float("inf")))
+        return cand.min(0).values.long()
+
+    def gather_logits(self, logits: torch.Tensor) -> torch.Tensor:
+        parts = [torch.empty_like(logits) for _ in range(self.size)]
+        dist.all_gather(parts, logits.contiguous(), group=self.group)
+        return torch.cat(parts, dim=-1)
+
+    def all_gather_rows(self, x: torch.Tensor) -> torch.Tensor:
+        parts = [torch.empty_like(x) for _ in range(self.size)]
+        dist.all_gather(parts, x.contiguous(), group=self.group)
+        return torch.cat(parts, dim=0)
+
+    def row_parallel(self, x: torch.Tensor, w: torch.Tensor):
+        T = x.shape[0]
+        if T <= SMALL_T and x.is_cuda:
+            parts = ops.linear_partial(x, w, ops.choose_splits(w.shape[0], w.shape[1], T))
+            return None, self.reduce_partials(parts), None
+        y = ops.linear(x, w)
+        return self.reduce_dense(y), None, None
+
+    def add_rmsnorm(self, weight, eps, dense, partials, ticket, residual, extra=None, extra_index=None):
+        return ops.add_rmsnorm(weight, eps, x=dense, partials=partials, residual=residual, extra=extra,
+                               extra_index=extra_index)
+
+
+class FusedComm(NcclComm):
+    """One-shot fused exchange over peer memory for decode-sized steps."""
+
+    def __init__(self, rank: int, size: int, hidden: int, group=None, region: symm.SymmetricRegion | None = None) -> None:
+        super().__init__(rank, size, group)
+        self.region = region or symm.SymmetricRegion.create(rank, size, hidden, group)
+        self.hidden = hidden
+        self.point = 0
+        r = self.region
+        self._slab_ptrs = [r.ptr_array(symm.OFF_SLABS + s * r.slab_bytes) for s in (0, 1)]
+        self._flag_ptrs = [r.ptr_array(symm.OFF_FLAGS[s]) for s in (0, 1)]
+        self._argmax_val = r.ptr_array(symm.OFF_ARGMAX_VAL)
+        self._argmax_id = r.ptr_array(symm.OFF_ARGMAX_ID)
+        self._argmax_flag = r.ptr_array(symm.OFF_ARGMAX_FLAGS)
+
+    def begin_step(self) -> None:
+        """Advance the step epoch (a kernel, so it is captured into decode graphs)."""
+        self.point = 0
+        native.call("prism_epoch_advance", self.region.local(symm.OFF_EPOCH), symm.POINTS_PER_STEP,
+                    torch.cuda.current_stream().cuda_stream, 0)
+
+    def row_parallel(self, x: torch.Tensor, w: torch.Tensor):
+        T, K = x.shape
+        M = w.shape[0]
+        if T > SMALL_T or M != self.hidden or self.point >= symm.ARGMAX_POINT:
+            return super().row_parallel(x, w)
+        splits = min(symm.S_MAX, ops.choose_splits(M, K, T))
+        eff = ops.effective_splits(K, splits)
+        point, slot = self.point, self.point % 2
+        self.point += 1
+        r = self.region
+        native.call(
+            "prism_gemm_wx_push", w.data_ptr(), x.data_ptr(), M, T, K,
+            w.stride(0), x.stride(0), M, M, eff, T * M, self._slab_ptrs[slot], self._flag_ptrs[slot], self.size,
+            self.rank, point, r.local(symm.OFF_COUNTER[slot]), r.local(symm.OFF_EPOCH), 0, 0,
+            torch.cuda.current_stream().cuda_stream, 1 if ops.pdl_enabled() else 0,
+        )
+        return None, None, (slot, point, self.size * eff, T)
+
+    def add_rmsnorm(self, weight, eps, dense, partials, ticket, residual, extra=None, extra_index=None):
+        if ticket is None:
+            return super().add_rmsnorm(weight, eps, dense, partials, None, residual, extra, extra_index)
+        slot, point, P, T = ticket
+        H = self.hidden
+        r = self.region
+        out = torch.empty((T, H), dtype=torch.bfloat16, device=weight.device)
+        new_res = residual if residual is not None else torch.empty((T, H), dtype=torch.bfloat16, device=weight.device)
+        native.call(
+            "prism_add_rmsnorm_wait", r.local(symm.OFF_SLABS + slot * r.slab_bytes), T * H, P,
+            None if residual is None else residual.data_ptr(), new_res.data_ptr(),
+            None if extra is None else extra.data_ptr(), None if extra is None else extra_index.data_ptr(),
+            weight.data_ptr(), out.data_ptr(), T, H, float(eps), r.local(symm.OFF_FLAGS[slot]), self.size,
+            r.local(symm.OFF_EPOCH), point, torch.cuda.current_stream().cuda_stream, 1 if ops.pdl_enabled() else 0,
+        )
+        return out, new_res
+
+    def greedy_merge(self, local_val: torch.Tensor, local_id: torch.Tensor) -> torch.Tensor:
+        B = local_val.shape[0]
+        if B > symm.B_MAX:
+            return super().greedy_merge(local_val, local_id)
+        out = torch.empty(B, dtype=torch.int64, device=local_val.device)
+        r = self.region
+        native.call(
+            "prism_argmax_exchange", local_val.data_ptr(), local_id.data_ptr(), self._argmax_val, self._argmax_id,
+            self._argmax_flag, r.local(symm.OFF_ARGMAX_FLAGS), r.local(symm.OFF_EPOCH), out.data_ptr(), self.size,
+            self.rank, symm.ARGMAX_POINT, B, symm.B_MAX, torch.cuda.current_stream().cuda_stream,
+            1 if ops.pdl_enabled() else 0,
+        )
+        return out
+
+    def close(self) -> None:
+        self.region.close()

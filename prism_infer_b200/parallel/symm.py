@@ -1,0 +1,126 @@
+"""Symmetric device memory across the tensor-parallel ranks of one node.
+
+Every rank allocates an identically laid out region with ``cudaMalloc`` (through the kernel
+library), exports it with CUDA IPC, and maps all peers' regions, which yields plain peer
+pointers kernels can store to and load from over NVLink.  Handles travel through
+``torch.distributed.all_gather_object`` once at start-up; nothing else uses the process
+group on the fused paths.  The reference has no such layer (NCCL only).
+
+Region layout (bytes)::
+
+    0     flags of exchange slot 0   u64[8]      256   flags of slot 1   u64[8]
+    512   flags of the arg-max exchange u64[8]   768   step epoch word   u64
+    1024  CTA counter slot 0  i32                1280  CTA counter slot 1  i32
+    4096  arg-max values f32[8][BMAX]            then  arg-max ids i64[8][BMAX]
+    SLAB0 / SLAB1: two slab buffers of  tp * S_MAX * T_MAX * H  fp32 each
+"""
+
+from __future__ import annotations
+
+import ctypes
+from dataclasses import dataclass
+
+import torch
+
+from ..ops import native
+
+T_MAX = 128
+S_MAX = 4
+B_MAX = 512
+OFF_FLAGS = (0, 256)
+OFF_ARGMAX_FLAGS = 512
+OFF_EPOCH = 768
+OFF_COUNTER = (1024, 1280)
+OFF_ARGMAX_VAL = 4096
+OFF_ARGMAX_ID = OFF_ARGMAX_VAL + 8 * B_MAX * 4
+OFF_SLABS = (OFF_ARGMAX_ID + 8 * B_MAX * 8 + 4095) // 4096 * 4096
+POINTS_PER_STEP = 128
+ARGMAX_POINT = POINTS_PER_STEP - 1
+
+
+def _check(rc: int, what: str) -> None:
+    if rc != 0:
+        raise native.NativeError(f"{what} failed with cudaError {rc}")
+
+
+class _DevView:
+    """Exposes a raw device range to torch through ``__cuda_array_interface__``."""
+
+    def __init__(self, ptr: int, nbytes: int) -> None:
+        self.__cuda_array_interface__ = {"shape": (nbytes,), "typestr": "|u1", "data": (ptr, False), "version": 2}
+
+
+@dataclass
+class SymmetricRegion:
+    rank: int
+    size: int
+    hidden: int
+    local_ptr: int
+    peer_ptrs: list[int]          # device addresses of every rank's region as seen from this rank
+    nbytes: int
+    slab_bytes: int
+
+    @classmethod
+    def create(cls, rank: int, size: int, hidden: int, group=None) -> "SymmetricRegion":
+        import torch.distributed as dist
+
+        lib = native.lib()
+        slab_bytes = size * S_MAX * T_MAX * hidden * 4
+        nbytes = OFF_SLABS + 2 * slab_bytes
+        out = ctypes.c_void_p()
+        _check(lib.prism_ipc_alloc(nbytes, ctypes.byref(out)), "prism_ipc_alloc")
+        handle = (ctypes.c_char * 64)()
+        _check(lib.prism_ipc_get_handle(out, ctypes.cast(handle, ctypes.c_void_p)), "prism_ipc_get_handle")
+        handles: list[bytes] = [b""] * size
+        dist.all_gather_object(handles, bytes(handle.raw), group=group)
+        peers: list[int] = []
+        for r in range(size):
+            if r == rank:
+                peers.append(out.value)
+                continue
+            mapped = ctypes.c_void_p()
+            buf = (ctypes.c_char * 64).from_buffer_copy(handles[r])
+            _check(lib.prism_ipc_open_handle(ctypes.cast(buf, ctypes.c_void_p), ctypes.byref(mapped)), "prism_ipc_open_handle")
+            peers.append(mapped.value)
+        dist.barrier(group=group)
+        return cls(rank, size, hidden, out.value, peers, nbytes, slab_bytes)
+
+    @classmethod
+    def create_emulated(cls, size: int, hidden: int) -> list["SymmetricRegion"]:
+        """All ranks' regions on the current device (single-GPU tests of the fused kernels)."""
+        lib = native.lib()
+        slab_bytes = size * S_MAX * T_MAX * hidden * 4
+        nbytes = OFF_SLABS + 2 * slab_bytes
+        ptrs = []
+        for _ in range(size):
+            out = ctypes.c_void_p()
+            _check(lib.prism_ipc_alloc(nbytes, ctypes.byref(out)), "prism_ipc_alloc")
+            ptrs.append(out.value)
+        return [cls(r, size, hidden, ptrs[r], list(ptrs), nbytes, slab_bytes) for r in range(size)]
+
+    # ---- typed local views ---------------------------------------------------------
+    def local_bytes(self) -> torch.Tensor:
+        return torch.as_tensor(_DevView(self.local_ptr, self.nbytes), device="cuda")
+
+    def slabs(self, slot: int, groups: int, tokens: int) -> torch.Tensor:
+        """Local fp32 view ``[groups, tokens, hidden]`` at the start of slab buffer ``slot``."""
+        n = groups * tokens * self.hidden
+        raw = self.local_bytes()[OFF_SLABS + slot * self.slab_bytes: OFF_SLABS + slot * self.slab_bytes + n * 4]
+        return raw.view(torch.float32).view(groups, tokens, self.hidden)
+
+    # ---- pointer tables for the launchers ------------------------------------------------
+    def ptr_array(self, offset: int):
+        arr = (ctypes.c_void_p * 8)()
+        for r in range(self.size):
+            arr[r] = self.peer_ptrs[r] + offset
+        return arr
+
+    def local(self, offset: int) -> int:
+        return self.local_ptr + offset
+
+    def close(self) -> None:
+        lib = native.lib()
+        for r, p in enumerate(self.peer_ptrs):
+            if r != self.rank and p != self.local_ptr:
+                lib.prism_ipc_close_handle(ctypes.c_void_p(p))
+        lib.prism_ipc_free(ctypes.c_void_p(self.local_ptr))

@@ -1,0 +1,81 @@
+"""Fused row-parallel GEMM -> exchange -> add+RMSNorm kernels.
+
+On one GPU every rank's symmetric region is allocated on the same device and the ranks run
+one after another in one stream (all pushes before any wait), which exercises the exact
+kernels, pointer tables, slab indexing and flag sequence numbers without two kernels ever
+waiting on each other.  The multi-GPU form (real peer memory over NVLink) runs when at
+least two devices are visible.
+"""
+
+import pytest
+import torch
+
+from prism_infer_b200 import ops
+from prism_infer_b200.ops import native
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.parametrize("tp,T,K", [(2, 1, 2048), (4, 8, 1024), (8, 128, 512), (8, 3, 1536)])
+def test_push_gemm_then_wait_norm_emulated_ranks(cuda_device, tp, T, K):
+    from prism_infer_b200.parallel import symm
+    from prism_infer_b200.parallel.comm import FusedComm
+
+    H = 4096
+    ops.set_pdl(False)
+    regions = symm.SymmetricRegion.create_emulated(tp, H)
+    comms = [FusedComm(r, tp, H, region=regions[r]) for r in range(tp)]
+    g = torch.Generator().manual_seed(tp * 100 + T)
+    xs = [(torch.randn(T, K, generator=g)).to(torch.bfloat16).cuda() for _ in range(tp)]
+    ws = [(torch.randn(H, K, generator=g) * (K * tp) ** -0.5).to(torch.bfloat16).cuda() for _ in range(tp)]
+    weight = (1 + 0.1 * torch.randn(H, generator=g)).to(torch.bfloat16).cuda()
+    res0 = torch.randn(T, H, generator=g).to(torch.bfloat16).cuda()
+    try:
+        for step in range(3):  # several steps: sequence numbers grow, slots alternate
+            for c in comms:
+                c.begin_step()
+            for point_pair in range(2):
+                tickets = [c.row_parallel(xs[r], ws[r])[2] for r, c in enumerate(comms)]
+                assert all(t is not None for t in tickets)
+                want = sum(x.float() @ w.float().t() for x, w in zip(xs, ws))
+                outs = []
+                for r, c in enumerate(comms):
+                    res = res0.clone()
+                    normed, new_res = c.add_rmsnorm(weight, 1e-6, None, None, tickets[r], res)
+                    outs.append((normed, new_res))
+                torch.cuda.synchronize()
+                ref_n, ref_r = ops.add_rmsnorm(weight.float().cpu(), 1e-6, x=want.cpu(), residual=res0.float().cpu().clone())
+                for normed, new_res in outs:
+                    assert (new_res.float().cpu() - ref_r).abs().max() < 5e-2
+                    assert (normed.float().cpu() - ref_n).abs().max() < 8e-2
+                # every rank computed bit-identical results (fixed summation order)
+                for normed, new_res in outs[1:]:
+                    assert torch.equal(normed, outs[0][0]) and torch.equal(new_res, outs[0][1])
+        native.check_status()
+    finally:
+        for reg in regions:
+            native.lib().prism_ipc_free(__import__("ctypes").c_void_p(reg.local_ptr))
+
+
+def test_wait_that_never_completes_reports_status_and_returns(cuda_device):
+    """A flag nobody sets: the bounded wait runs out, the status word says so, the context
+    stays usable.  (The wait limit is about two seconds.)"""
+    from prism_infer_b200.parallel import symm
+    from prism_infer_b200.parallel.comm import FusedComm
+
+    H = 4096
+    ops.set_pdl(False)
+    regions = symm.SymmetricRegion.create_emulated(2, H)
+    c = FusedComm(0, 2, H, region=regions[0])
+    c.begin_step()
+    weight = torch.ones(H, dtype=torch.bfloat16, device="cuda")
+    res = torch.zeros(1, H, dtype=torch.bfloat16, device="cuda")
+    native.read_status(reset=True)
+    c.add_rmsnorm(weight, 1e-6, None, None, (0, 0, 2, 1), res)  # nobody pushed for point 0
+    torch.cuda.synchronize()
+    status = native.read_status(reset=True)
+    assert status["norm"][0] == 2, status  # PRISM_ERR_PEER_TIMEOUT
+    y = ops.rmsnorm(torch.ones(2, H, dtype=torch.bfloat16, device="cuda"), weight, 1e-6)  # context still works
+    assert torch.isfinite(y.float()).all()
+    for reg in regions:
+        native.lib().prism_ipc_free(__import__("ctypes").c_void_p(reg.local_ptr))

@@ -1,0 +1,41 @@
+"""Tensor-parallel host logic on CPU ranks (gloo): spawned workers, shared-memory control
+plane, sharded weights, vocabulary-parallel embedding / LM head, lock-step KV commands."""
+
+import numpy as np
+import pytest
+import torch
+
+from prism_infer_b200 import LLM, SamplingParams
+from prism_infer_b200.engine.vl_inputs import PatchProcessor, prepare_image_inputs
+from prism_infer_b200.models.architecture import Qwen3VLArch
+from prism_infer_b200.models.reference_model import ReferenceQwen3VL
+from prism_infer_b200.models.weights import random_weights
+from prism_infer_b200.utils.tokenizer import load_tokenizer
+
+pytestmark = pytest.mark.distributed
+
+
+@pytest.mark.timeout(300)
+def test_tp2_cpu_matches_oracle_and_prefix_cache_works():
+    arch = Qwen3VLArch.tiny()
+    weights = random_weights(arch, dtype=torch.float32, seed=0)
+    oracle = ReferenceQwen3VL(arch, weights)
+    llm = LLM("random:tiny", weights=weights, tensor_parallel_size=2, max_model_len=512, kvcache_block_size=16,
+              num_kvcache_blocks=64, enforce_eager=True, max_chunk_size=64, tensor_parallel_timeout_seconds=120)
+    try:
+        sp = SamplingParams(temperature=0.0, max_tokens=6, ignore_eos=True)
+        prompts = [[5, 6, 7, 8, 9], list(range(100, 140))]
+        outs = llm.generate(prompts, sp)
+        for p, o in zip(prompts, outs):
+            assert o["token_ids"] == oracle.generate_greedy(p, 6)
+        img = np.random.default_rng(0).integers(0, 256, (64, 64, 3), dtype=np.uint8)
+        tok = load_tokenizer("random:tiny", arch)
+        a = prepare_image_inputs(PatchProcessor(arch), tok, [11, 12, 13], [img])
+        b = prepare_image_inputs(PatchProcessor(arch), tok, [21, 22], [img])
+        ra = llm.generate_prepared_image_inputs(a, sp)
+        rb = llm.generate_prepared_image_inputs(b, sp)  # prefix hit: copy_prefix runs on both ranks
+        assert llm.multimodal_prefix_cache_metadata()["hits"] == 1
+        assert ra["token_ids"] == oracle.generate_greedy(a.input_ids, 6, pixel_values=a.pixel_values, image_grid_thw=a.image_grid_thw)
+        assert rb["token_ids"] == oracle.generate_greedy(b.input_ids, 6, pixel_values=b.pixel_values, image_grid_thw=b.image_grid_thw)
+    finally:
+        llm.exit()
