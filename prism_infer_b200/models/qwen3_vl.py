@@ -391,7 +391,13 @@ class Qwen3VLModel:
                                                workspace=meta.workspace)
             dense, partials, ticket = comm.row_parallel(a.view(T, self.Hq * self.D), l.o)
             h, residual = comm.add_rmsnorm(l.post_norm, t.rms_norm_eps, dense, partials, ticket, residual)
-            act = ops.gate_up_swiglu(h, l.gate_up)
+            if small and h.is_cuda and self.I // 128 < 96:
+                # too few 128-row tiles for the dual-accumulator kernel to keep enough SMs
+                # streaming weights: split-K over the packed matrix, SwiGLU on the partial sums
+                gu = ops.linear_partial(h, l.gate_up, ops.choose_splits(2 * self.I, self.H, T))
+                act = ops.swiglu(partials=gu)
+            else:
+                act = ops.gate_up_swiglu(h, l.gate_up)
             dense, partials, ticket = comm.row_parallel(act, l.down)
         extra = deepstack[n_deep - 1] if n_deep == len(self.layers) else None
         h, _ = comm.add_rmsnorm(self.final_norm, t.rms_norm_eps, dense, partials, ticket, residual,
