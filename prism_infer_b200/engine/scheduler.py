@@ -152,7 +152,7 @@ class Scheduler:
             try_add(seq)
         while self.waiting and budget > 0 and len(self.running) < self.max_num_seqs:
             seq = self.waiting[0]
-            if not self.block_manager.can_allocate(seq):
+            if not self.policy.may_admit(self, seq) or not self.block_manager.can_allocate(seq):
                 break
             try:
                 transfers = self.block_manager.allocate(seq)

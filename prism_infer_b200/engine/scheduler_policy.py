@@ -90,6 +90,10 @@ class FCFSPolicy:
     def on_prefill_batch(self, seqs: Seq[Sequence]) -> None:
         return None
 
+    def may_admit(self, sched: "Scheduler", seq: Sequence) -> bool:
+        """Checked for every waiting sequence before it joins a prefill batch."""
+        return True
+
     def is_heavy(self, seq: Sequence) -> bool:
         return seq.vision_patch_count(seq.num_computed_tokens) >= self.heavy_threshold
 
@@ -120,6 +124,11 @@ class VisionAwarePolicy(FCFSPolicy):
         if not super().allow_prefill(sched, head):
             return False
         if head is not None and self.is_heavy(head) and sched.num_decoding > 0:
+            return self.decode_batches_since_heavy >= self.min_decode_between_heavy
+        return True
+
+    def may_admit(self, sched: "Scheduler", seq: Sequence) -> bool:
+        if self.is_heavy(seq) and sched.num_decoding > 0:
             return self.decode_batches_since_heavy >= self.min_decode_between_heavy
         return True
 

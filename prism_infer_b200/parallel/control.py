@@ -14,6 +14,7 @@ Segment layout (little-endian 64-bit words unless noted)::
     [0]   command sequence number (written last by the driver)
     [1]   payload length in bytes
     [2]   shutdown flag
+    [3]   payload capacity in bytes        [4]   reply capacity per worker in bytes
     [8 + 8*r ...]  per-worker slot r: ack sequence, status (0 ok, 1 error), reply length
     [HEADER ...]                       command payload (pickle)
     [HEADER + payload_cap + r*reply_cap ...]   reply area of worker r (pickle)
@@ -32,7 +33,7 @@ import numpy as np
 
 HEADER_WORDS = 8 + 8 * 64
 HEADER_BYTES = HEADER_WORDS * 8
-DEFAULT_PAYLOAD_CAP = 256 << 20
+DEFAULT_PAYLOAD_CAP = 96 << 20
 DEFAULT_REPLY_CAP = 1 << 20
 
 
@@ -75,7 +76,6 @@ class ControlSegment:
     def __init__(self, name: str | None, n_workers: int, *, create: bool, payload_cap: int = DEFAULT_PAYLOAD_CAP,
                  reply_cap: int = DEFAULT_REPLY_CAP) -> None:
         self.n_workers = n_workers
-        self.payload_cap, self.reply_cap = payload_cap, reply_cap
         size = HEADER_BYTES + payload_cap + n_workers * reply_cap
         if create:
             self.shm = shared_memory.SharedMemory(name=name, create=True, size=size)
@@ -85,6 +85,10 @@ class ControlSegment:
         self.owner = create
         self.words = np.ndarray((HEADER_WORDS,), dtype=np.int64, buffer=self.shm.buf)
         self.buf = self.shm.buf
+        if create:
+            self.words[3], self.words[4] = payload_cap, reply_cap
+        # the geometry travels in the header so attaching processes never guess it
+        self.payload_cap, self.reply_cap = int(self.words[3]), int(self.words[4])
 
     @property
     def name(self) -> str:

@@ -1,0 +1,356 @@
+"""Pure host logic: config rules, request FSM, page pools, prefix caches, compaction,
+scheduler policies, preemption.  No device, no checkpoint; tiny pages (4 tokens)."""
+
+from types import SimpleNamespace
+
+import pytest
+
+from prism_infer_b200.config import Config, PrismConfig
+from prism_infer_b200.engine.block_manager import BlockManager, chain_hash
+from prism_infer_b200.engine.block_pool import CpuBlockPool, GpuBlockPool, OutOfBlocks
+from prism_infer_b200.engine.compression import kv_bytes_per_token, traits
+from prism_infer_b200.engine.contracts import BatchPlan, Phase
+from prism_infer_b200.engine.kv_layout import CompactionPlan, KVLayout
+from prism_infer_b200.engine.request import InvalidTransition, RequestLifecycle, RequestState
+from prism_infer_b200.engine.scheduler import Scheduler
+from prism_infer_b200.engine.scheduler_policy import FCFSPolicy, SLOAwarePolicy, VisionAwarePolicy
+from prism_infer_b200.engine.sequence import Sequence
+from prism_infer_b200.engine.visual_pruning import (PruningConfig, compute_pruning_decision, retained_positions,
+                                                    target_keep_count, uniform_keep)
+from prism_infer_b200.sampling_params import SamplingParams
+
+IMG, VID, VS, VE, EOS = 901, 902, 903, 904, 905
+
+
+def cfg(**kw):
+    base = dict(max_num_seqs=8, max_num_batched_tokens=64, max_vision_patches_per_batch=4096, max_model_len=256, eos=EOS,
+                num_kvcache_blocks=32, kvcache_block_size=4, num_cpu_blocks=0, enable_prefix_caching=True,
+                compacts_visual_tokens=False, scheduler_policy="fcfs", max_queue_size=None, enable_chunked_prefill=True,
+                max_chunk_size=16, max_consecutive_prefill_batches=1, heavy_prefill_vision_patch_threshold=64,
+                min_decode_batches_between_heavy_prefills=3, max_light_prefill_bypasses_per_heavy=1)
+    base.update(kw)
+    return SimpleNamespace(**base)
+
+
+def text_seq(i, n, max_tokens=4, base=10, **kw):
+    return Sequence(i, list(range(base, base + n)), SamplingParams(temperature=0.0, max_tokens=max_tokens, **kw),
+                    image_token_id=IMG, video_token_id=VID)
+
+
+def mm_seq(i, n_visual, question, key="media-A", max_tokens=4):
+    ids = [VS] + [IMG] * n_visual + [VE] + list(question)
+    s = Sequence(i, ids, SamplingParams(temperature=0.0, max_tokens=max_tokens, ignore_eos=True), image_token_id=IMG,
+                 video_token_id=VID, image_grid_thw=[(1, 2, 2 * n_visual)], merge_size=2)
+    s.multimodal_prefix_cache_key = key
+    return s
+
+
+# ------------------------------------------------------------------------------ config
+def test_flat_config_adapter_rules():
+    with pytest.raises(TypeError, match="unknown Prism config option"):
+        PrismConfig.from_flat_options("random:tiny", {"no_such_knob": 1})
+    c = PrismConfig.from_flat_options("random:tiny", {"kvcache_block_size": 64, "num_kvcache_blocks": 10,
+                                                      "compression_mode": "scaled_fp8_kv"})
+    assert c.cache.page_size == 64 and c.cache.num_gpu_blocks == 10 and c.execution.backend == "cuda_graph"
+    assert c.quantization.kv_dtype == "fp8_e4m3" and c.quantization.kv_scaled
+    assert PrismConfig.from_flat_options("random:tiny", {"enforce_eager": True}).execution.backend == "eager"
+    with pytest.raises(ValueError, match="conflicts"):
+        PrismConfig.from_flat_options("random:tiny", {"enforce_eager": True, "execution_backend": "cuda_graph"})
+    with pytest.raises(ValueError, match="mutually exclusive"):
+        PrismConfig.from_flat_options("random:tiny", {"decode_compile_region": "attention"})
+    with pytest.raises(ValueError, match="logits_precision"):
+        PrismConfig.from_flat_options("random:tiny", {"tensor_parallel_size": 2, "logits_precision": "fp32"})
+    with pytest.raises(ValueError, match="eager-only"):
+        PrismConfig.from_flat_options("random:tiny", {"compression_mode": "visual_prune"})
+    with pytest.raises(ValueError):
+        PrismConfig.from_flat_options("random:tiny", {"kvcache_block_size": 48})
+    with pytest.raises(ValueError):
+        PrismConfig.from_flat_options("/no/such/dir", {})
+    with pytest.raises(ValueError, match="does not divide"):
+        Config("random:tiny", tensor_parallel_size=3)
+
+
+def test_kv_page_accounting_matches_reference_numbers():
+    c8 = Config("random:qwen3-vl-8b", compression_mode="scaled_fp8_kv")
+    assert c8.kv_bytes_per_page() == 19_464_192  # 18 874 368 payload + 589 824 scales
+    assert c8.kv_bytes_per_page() * 220 == 4_282_122_240
+    assert kv_bytes_per_token(36, 8, 128, 2) / kv_bytes_per_token(36, 8, 128, 0) == 0.515625
+    assert Config("random:qwen3-vl-8b", compression_mode="scaled_fp8_kv", tensor_parallel_size=8).kv_bytes_per_page() * 8 == 19_464_192
+    assert traits("visual_compact_scaled_fp8").compacts and traits("visual_prune").logical_prune
+
+
+# ------------------------------------------------------------------------- request FSM
+def test_request_lifecycle_transitions():
+    lc = RequestLifecycle(1)
+    lc.transition(RequestState.PREFILLING)
+    lc.transition(RequestState.DECODING)
+    lc.transition(RequestState.SWAPPED, "preempt")
+    lc.transition(RequestState.DECODING)
+    lc.transition(RequestState.FINISHED, "eos")
+    assert lc.finish_reason == "eos" and len(lc.history) == 5
+    with pytest.raises(InvalidTransition):
+        lc.transition(RequestState.DECODING)
+    with pytest.raises(InvalidTransition):
+        RequestLifecycle(2).transition(RequestState.DECODING)
+    r = RequestLifecycle(3)
+    r.transition(RequestState.REJECTED, "too long")
+    assert r.state.terminal
+
+
+# ------------------------------------------------------------------------------- pools
+def test_gpu_pool_refcounts_and_hash_revival():
+    pool = GpuBlockPool(3)
+    a = pool.allocate()
+    pool.publish(a, 123, (1, 2, 3, 4))
+    pool.release(a)
+    assert pool.num_free == 3 and pool.lookup(123, (1, 2, 3, 4)) == a  # freed but still findable
+    pool.retain(a)  # revive
+    assert pool.num_free == 2 and pool.blocks[a].ref_count == 1
+    assert pool.lookup(123, (9, 9, 9, 9)) is None  # token check guards collisions
+    b, c = pool.allocate(), pool.allocate()
+    with pytest.raises(OutOfBlocks):
+        pool.allocate()
+    pool.release(b)
+    with pytest.raises(RuntimeError):
+        pool.release(b)
+    assert {a, b, c} == {0, 1, 2}
+    cpu = CpuBlockPool(2)
+    with pytest.raises(OutOfBlocks):
+        cpu.allocate_many(3)
+    assert cpu.num_free == 2  # all-or-nothing
+
+
+# ----------------------------------------------------------------------- block manager
+def test_text_prefix_sharing_append_and_cow():
+    bm = BlockManager(16, 4)
+    s1, s2 = text_seq(1, 10), text_seq(2, 10)
+    bm.allocate(s1)
+    assert s1.num_cached_tokens == 0 and len(s1.block_table) == 3
+    bm.allocate(s2)
+    assert s2.num_cached_tokens == 8 and s2.block_table[:2] == s1.block_table[:2] and s2.block_table[2] != s1.block_table[2]
+    exact = text_seq(3, 8)
+    bm.allocate(exact)  # all pages would hit, but the last token must be computed
+    assert exact.num_cached_tokens == 4
+    s1.num_computed_tokens = 10
+    s1.append_token(5)
+    s1.append_token(6)  # 12 tokens: KV row 11 still fits in page 2
+    assert not bm.needs_new_page(s1)
+    s1.append_token(7)  # 13 tokens: row 12 opens page 3
+    assert bm.needs_new_page(s1) and bm.append(s1) == () and len(s1.block_table) == 4
+    shared = s1.block_table[0]
+    pair = bm.copy_on_write(s1, 0)
+    assert pair[0] == shared and s1.block_table[0] == pair[1] and bm.gpu.blocks[shared].ref_count == 2
+    for s in (s1, s2, exact):
+        bm.deallocate(s)
+    assert bm.gpu.num_free == 16
+
+
+def test_swap_out_and_in_restore_hashes():
+    bm = BlockManager(4, 4, num_cpu_blocks=4)
+    s = text_seq(1, 8)
+    bm.allocate(s)
+    s.num_computed_tokens = 8
+    hashes = [bm.gpu.blocks[b].hash for b in s.block_table]
+    out_pairs = bm.swap_out(s)
+    assert len(out_pairs) == 2 and not s.block_table and len(s.cpu_block_table) == 2 and bm.gpu.num_free == 4
+    filler = text_seq(2, 16)
+    bm.allocate(filler)
+    assert not bm.can_swap_in(s)
+    bm.deallocate(filler)
+    in_pairs = bm.swap_in(s)
+    assert len(in_pairs) == 2 and bm.cpu.num_free == 4
+    assert [bm.gpu.blocks[b].hash for b in s.block_table][0] in hashes + [None]
+
+
+def test_multimodal_prefix_store_hit_tail_clone_and_eviction():
+    bm = BlockManager(12, 4)
+    a = mm_seq(1, 5, [50, 51, 52])  # prefix = VS + 5 IMG = 6 tokens -> 1 full page + 2 tail rows
+    assert a.multimodal_prefix_boundary == 6 and bm.probe_multimodal_prefix(a) is None
+    bm.allocate(a)
+    assert a.num_cached_tokens == 0  # multimodal prompts never share by token hash
+    a.num_computed_tokens = 6
+    copies = bm.store_multimodal_prefix(a)
+    assert len(copies) == 1 and copies[0][0] == a.block_table[1] and copies[0][2] == 2  # tail clone of 2 rows
+    entry = next(iter(bm.entries.values()))
+    assert entry.prefix_len == 6 and entry.tail_rows == 2 and entry.pages[0] == a.block_table[0]
+    b = mm_seq(2, 5, [60, 61])
+    assert bm.probe_multimodal_prefix(b) is entry
+    plan = bm.allocate(b)
+    assert b.num_cached_tokens == 6 and b.num_computed_tokens == 6 and b.block_table[0] == a.block_table[0]
+    assert plan.copy_prefix == ((entry.pages[1], b.block_table[1], 2),)
+    other = mm_seq(3, 5, [60, 61], key="media-B")
+    assert bm.probe_multimodal_prefix(other) is None
+    bm.deallocate(a)
+    bm.deallocate(b)
+    assert bm.gpu.num_free == 12 - 2  # the cache still holds its two pages
+    big = text_seq(4, 44)  # needs 11 pages -> forces eviction of the entry
+    bm.allocate(big)
+    assert not bm.entries and bm.counters.evictions == 1
+    stale = mm_seq(5, 5, [1])
+    bm.deallocate(big)
+    bm.allocate(stale, expected_hit=True)
+    assert bm.counters.stale_probes == 1 and stale.num_cached_tokens == 0
+
+
+def test_compaction_plan_commit_and_layout():
+    bm = BlockManager(16, 4)
+    s = mm_seq(1, 12, [70, 71, 72])  # prefix 13 tokens, prompt 17 tokens -> 5 pages
+    bm.allocate(s)
+    s.num_computed_tokens = 13
+    dec = compute_pruning_decision(s.token_ids, IMG, VID, PruningConfig(0.5, 2), end=13)
+    keep = retained_positions(13, dec)
+    assert len(dec.kept) == 6 and keep[0] == 0 and len(keep) == 7
+    plan = bm.build_compaction_plan(s, keep, 13)
+    assert isinstance(plan, CompactionPlan) and plan.layout.dropped == 6
+    assert len(plan.kept_blocks) == 3 and len(plan.released_blocks) == 2  # 17 - 6 = 11 rows -> 3 pages
+    assert plan.dst_slots[:4] == tuple(s.block_table[0] * 4 + i for i in range(4))
+    free_before = bm.gpu.num_free
+    table_before = list(s.block_table)
+    bm.commit_compaction(s, plan)
+    assert bm.gpu.num_free == free_before + 2 and s.block_table == table_before[:3]
+    assert s.physical_len() == 11 and s.slot_of(13) == s.block_table[1] * 4 + 3  # logical 13 -> physical 7
+    with pytest.raises(RuntimeError, match="stale"):
+        bm.commit_compaction(s, plan)
+    with pytest.raises(ValueError):
+        KVLayout(5, (0, 2, 2))
+    with pytest.raises(ValueError):
+        KVLayout(5, (0, 7))
+    copies = bm.store_multimodal_prefix(s)
+    entry = next(iter(bm.entries.values()))
+    assert entry.layout is s.kv_layout and entry.physical_len == 7 and copies[0][2] == 3
+    hit = mm_seq(2, 12, [80])
+    bm.allocate(hit)
+    assert hit.kv_layout is s.kv_layout and hit.physical_len() == len(hit) - 6
+
+
+# ------------------------------------------------------------------------- pruning math
+def test_pruning_keep_counts_and_uniform_selection():
+    assert target_keep_count(1568, 768, 0.6) == 941 and target_keep_count(1000, 768, 0.6) == 768
+    assert target_keep_count(500, 768, 0.6) == 500 and target_keep_count(0, 32, 0.6) == 0
+    idx = list(range(100, 120))
+    kept = uniform_keep(idx, 5)
+    assert kept[0] == 100 and kept[-1] == 119 and len(kept) == 5 and list(kept) == sorted(kept)
+    assert uniform_keep(idx, 1) == (110,) and uniform_keep(idx, 50) == tuple(idx)
+    video_only = [VS] + [VID] * 40 + [VE]
+    assert compute_pruning_decision(video_only, IMG, VID, PruningConfig(0.5, 4)).dropped == ()  # video floor unset
+    assert len(compute_pruning_decision(video_only, IMG, VID, PruningConfig(0.5, 4, 10)).kept) == 20
+    scores = {i: float(i % 7) for i in range(1, 41)}
+    d = compute_pruning_decision(video_only, IMG, VID, PruningConfig(0.25, 4, 4, "score"), scores=scores)
+    assert len(d.kept) == 10 and all(scores[i] >= 5 for i in d.kept)
+
+
+# --------------------------------------------------------------------------- scheduler
+def run_step(sched, tokens=None):
+    plan = sched.schedule()
+    if plan.is_idle:
+        return plan, []
+    toks = tokens if tokens is not None else [7] * plan.batch_size
+    return plan, sched.postprocess(plan, toks)
+
+
+def test_scheduler_admission_chunking_and_finish():
+    sched = Scheduler(cfg())
+    too_long = text_seq(1, 300)
+    assert not sched.add(too_long) and too_long.state is RequestState.REJECTED and sched.counters["rejected"] == 1
+    wide = mm_seq(2, 40, [1])  # one visual span wider than the chunk limit
+    assert not sched.add(wide)
+    s = text_seq(3, 40, max_tokens=2)
+    assert sched.add(s)
+    plan, outs = run_step(sched)
+    assert plan.phase is Phase.PREFILL and plan.slices[0].length == 16 and outs[0].new_token is None
+    run_step(sched)
+    plan, outs = run_step(sched)
+    assert plan.slices[0].start == 32 and plan.slices[0].length == 8 and outs[0].new_token == 7
+    assert s.state is RequestState.DECODING
+    plan, outs = run_step(sched)
+    assert plan.phase is Phase.DECODE and outs[0].finished and outs[0].finish_reason == "length"
+    assert sched.is_finished() and sched.block_manager.gpu.num_free == 32
+    e = text_seq(4, 5, max_tokens=9)
+    sched.add(e)
+    run_step(sched)
+    _, outs = run_step(sched, [EOS])
+    assert outs[0].finish_reason == "eos"
+
+
+def test_chunks_never_split_visual_spans_and_stop_at_prefix():
+    pol = FCFSPolicy(cfg(max_chunk_size=16))
+    s = mm_seq(1, 10, list(range(20)))  # VS, 10 IMG, VE, 20 text; boundary = 11
+    assert pol.prefill_token_count(s, 64, stop_at_prefix=True) == 11
+    assert pol.prefill_token_count(s, 64, stop_at_prefix=False) == 16
+    assert pol.prefill_token_count(s, 5, stop_at_prefix=False) == 1  # only VS fits before the span
+    s.num_computed_tokens = 1
+    assert pol.prefill_token_count(s, 5, stop_at_prefix=False) == 0  # the span does not fit the budget
+    assert pol.prefill_token_count(s, 12, stop_at_prefix=True) == 10
+    two = Sequence(2, [VS] + [IMG] * 6 + [VE] + [5, 6] + [VS] + [IMG] * 6 + [VE] + [9], SamplingParams(),
+                   image_token_id=IMG, video_token_id=VID)
+    assert pol.prefill_token_count(two, 64, stop_at_prefix=False) == 11  # would cut the second span at 16
+
+
+def test_lifo_preemption_recompute_and_swap():
+    sched = Scheduler(cfg(num_kvcache_blocks=4, max_chunk_size=64))
+    a, b = text_seq(1, 7, max_tokens=20, ignore_eos=True), text_seq(2, 7, max_tokens=20, base=500, ignore_eos=True)
+    sched.add(a)
+    sched.add(b)
+    run_step(sched)  # both prefill: 2 pages each, pool full
+    assert sched.block_manager.gpu.num_free == 0
+    plan, _ = run_step(sched)  # a and b at 8 tokens: row 7 fits
+    assert plan.phase is Phase.DECODE and plan.batch_size == 2
+    plan, _ = run_step(sched)  # 9 tokens each: both need a page -> b (last in) is preempted by recompute
+    assert sched.counters["preempt_recompute"] == 1 and b.state is RequestState.WAITING and not b.block_table
+    assert plan.seqs == (a,) and sched.waiting[0] is b and b.num_computed_tokens == 0
+    sw = Scheduler(cfg(num_kvcache_blocks=4, num_cpu_blocks=8, max_chunk_size=64))
+    a, b = text_seq(1, 7, max_tokens=20, ignore_eos=True), text_seq(2, 7, max_tokens=20, base=500, ignore_eos=True)
+    sw.add(a)
+    sw.add(b)
+    run_step(sw)
+    run_step(sw)
+    plan, _ = run_step(sw)
+    assert sw.counters["preempt_swap"] == 1 and b.state is RequestState.SWAPPED and len(plan.kv_transfers.swap_out) == 2
+    assert sw.cancel(a.seq_id) and a.state is RequestState.CANCELLED
+    plan, _ = run_step(sw)
+    assert b.state is RequestState.DECODING and len(plan.kv_transfers.swap_in) == 2 and sw.counters["swap_in"] == 1
+
+
+def test_cancel_in_every_queue_frees_pages():
+    sched = Scheduler(cfg())
+    w, r = text_seq(1, 6), text_seq(2, 6, max_tokens=50, ignore_eos=True)
+    sched.add(r)
+    run_step(sched)
+    sched.add(w)
+    assert sched.cancel(w.seq_id) and sched.cancel(r.seq_id) and not sched.cancel(99)
+    assert sched.block_manager.gpu.num_free == 32 and sched.is_finished() and sched.counters["cancelled"] == 2
+
+
+def test_vision_aware_and_slo_policies():
+    c = cfg(scheduler_policy="vision_aware", max_chunk_size=64, max_num_batched_tokens=64)
+    pol = VisionAwarePolicy(c)
+    sched = Scheduler(c, policy=pol)
+    dec = text_seq(1, 4, max_tokens=100, ignore_eos=True)
+    sched.add(dec)
+    run_step(sched)
+    heavy = mm_seq(2, 20, [1, 2])  # 80 patches >= threshold 64
+    light = text_seq(3, 4)
+    pol.decode_batches_since_heavy = 0
+    sched.add(heavy)
+    sched.add(light)
+    plan, _ = run_step(sched)
+    assert plan.phase is Phase.DECODE  # prefill / decode alternation comes first
+    plan, _ = run_step(sched)
+    assert plan.phase is Phase.PREFILL and plan.seqs == (light,)  # light overtakes the blocked heavy head
+    phases = []
+    for _ in range(6):
+        plan, _ = run_step(sched)
+        phases.append(plan.phase)
+    assert Phase.DECODE in phases[:3] and any(p is Phase.PREFILL for p in phases)  # heavy admitted after enough decodes
+    slo = SLOAwarePolicy(cfg(scheduler_policy="slo_aware"))
+    x, y, z = text_seq(1, 4), text_seq(2, 4), mm_seq(3, 20, [1])
+    x.deadline_ns, y.deadline_ns, z.deadline_ns = 900_000_000, 300_000_000, 800_000_000
+    q = [x, y, z]
+    slo.order_waiting(q, 0)
+    assert q == [z, y, x] and slo.cost_tier(z) == 2 and slo.cost_tier(x) == 0  # heavy vision reserves 700 ms
+
+
+def test_batch_plan_contract():
+    with pytest.raises(ValueError):
+        BatchPlan(Phase.PREFILL, (text_seq(1, 3),), ())
+    assert BatchPlan(Phase.IDLE).is_idle and chain_hash([1, 2], None) != chain_hash([1, 2], 5)

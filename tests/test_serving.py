@@ -1,0 +1,251 @@
+"""Serving runtime and HTTP app against a fake engine that implements only the
+``ServingEngine`` protocol (the reference's strategy, tests/test_serving_runtime.py:28-114)."""
+
+import asyncio
+import base64
+import io
+import json
+import threading
+import time
+
+import httpx
+import pytest
+
+from prism_infer_b200.engine.contracts import Phase, RequestOutput, StepResult
+from prism_infer_b200.engine.request import RequestState
+from prism_infer_b200.sampling_params import SamplingParams
+from prism_infer_b200.serving import (DuplicateRequest, EventKind, GenerationRequest, IngressFull, Modality,
+                                      ServingRuntime)
+from prism_infer_b200.serving.app import create_app
+from prism_infer_b200.serving.cli import load_engine_options
+
+
+class FakeTokenizer:
+    def decode(self, ids, skip_special_tokens=True):
+        return " ".join(f"t{i}" for i in ids)
+
+
+class FakeEngine:
+    """Emits tokens 100, 101, ... per request, one per step, up to max_tokens."""
+
+    def __init__(self, fail_after=None, step_delay=0.0):
+        self.tokenizer = FakeTokenizer()
+        self.live = {}
+        self.next_id = 0
+        self.fail_after = fail_after
+        self.steps = 0
+        self.step_delay = step_delay
+        self.cancelled = []
+        self.exited = False
+        self.media_seen = []
+
+    def _add(self, prompt, sp, media=None, raise_on_reject=True):
+        if prompt == "reject me":
+            eid = self.next_id
+            self.next_id += 1
+            self.live[eid] = None
+            return eid
+        eid = self.next_id
+        self.next_id += 1
+        self.live[eid] = [sp.max_tokens, 0]
+        self.media_seen.append(media)
+        return eid
+
+    def add_request(self, prompt, sampling_params=None, *, raise_on_reject=True):
+        return self._add(prompt, sampling_params, None, raise_on_reject)
+
+    def add_vl_request(self, prompt, image, sampling_params=None, **kw):
+        return self._add(prompt, sampling_params, ("image", image))
+
+    def add_images_request(self, prompt, images, sampling_params=None, **kw):
+        return self._add(prompt, sampling_params, ("images", len(images)))
+
+    def add_video_request(self, prompt, frames, sampling_params=None, **kw):
+        return self._add(prompt, sampling_params, ("video", len(frames)))
+
+    def request_state(self, eid):
+        if self.live.get(eid, 0) is None:
+            del self.live[eid]
+            return RequestState.REJECTED
+        return RequestState.WAITING
+
+    def is_finished(self):
+        return not self.live
+
+    def cancel_request(self, eid):
+        self.cancelled.append(eid)
+        return self.live.pop(eid, None) is not None
+
+    def step_result(self):
+        self.steps += 1
+        if self.fail_after is not None and self.steps > self.fail_after:
+            raise RuntimeError("boom")
+        if self.step_delay:
+            time.sleep(self.step_delay)
+        outs = []
+        for eid, st in list(self.live.items()):
+            st[1] += 1
+            done = st[1] >= st[0]
+            outs.append(RequestOutput(eid, 100 + st[1], done, "length" if done else None))
+            if done:
+                del self.live[eid]
+        return StepResult(Phase.DECODE, tuple(outs), len(outs))
+
+    def exit(self):
+        self.exited = True
+
+
+def _req(rid, prompt="hello", max_tokens=3, modality=Modality.TEXT, media=None):
+    return GenerationRequest(rid, prompt, modality, media, SamplingParams(temperature=0.0, max_tokens=max_tokens))
+
+
+def _drain(handle, timeout=5.0):
+    events = []
+    while True:
+        ev = handle.next_event_blocking(timeout)
+        events.append(ev)
+        if ev.kind in (EventKind.DONE, EventKind.ERROR):
+            return events
+
+
+def test_runtime_streams_tokens_then_done_and_shuts_down():
+    eng = FakeEngine()
+    rt = ServingRuntime(lambda: eng, ingress_capacity=4)
+    rt.start()
+    assert rt.is_healthy
+    events = _drain(rt.submit(_req("a", max_tokens=3)))
+    kinds = [e.kind for e in events]
+    assert kinds == [EventKind.ACCEPTED, EventKind.TOKEN, EventKind.TOKEN, EventKind.TOKEN, EventKind.DONE]
+    assert [e.token_id for e in events[1:4]] == [101, 102, 103]
+    assert events[1].token_text == "t101"
+    done = events[-1]
+    assert done.token_ids == (101, 102, 103) and done.text == "t101 t102 t103" and done.finish_reason == "length"
+    assert done.to_dict()["token_ids"] == [101, 102, 103]
+    rejected = _drain(rt.submit(_req("r", prompt="reject me")))
+    assert rejected[-1].kind is EventKind.DONE and rejected[-1].finish_reason == "rejected"
+    rt.stop()
+    assert eng.exited and not rt.is_healthy
+
+
+def test_runtime_backpressure_duplicates_and_cancellation():
+    eng = FakeEngine(step_delay=0.02)
+    rt = ServingRuntime(lambda: eng, ingress_capacity=64)
+    rt.start()
+    h = rt.submit(_req("long", max_tokens=10_000))
+    with pytest.raises(DuplicateRequest):
+        rt.submit(_req("long"))
+    first = h.next_event_blocking(5.0)
+    assert first.kind is EventKind.ACCEPTED
+    rt.cancel("long")
+    events = _drain(h)
+    assert events[-1].kind is EventKind.DONE and events[-1].finish_reason == "cancelled"
+    assert eng.cancelled == [first.engine_request_id]
+    rt.stop()
+    # a stalled owner thread makes the bounded ingress overflow
+    gate = threading.Event()
+
+    class Stalled(FakeEngine):
+        def is_finished(self):
+            gate.wait(5.0)
+            return super().is_finished()
+
+    rt2 = ServingRuntime(lambda: Stalled(), ingress_capacity=2)
+    rt2.start()
+    time.sleep(0.05)
+    rt2.submit(_req("x1"))
+    rt2.submit(_req("x2"))
+    with pytest.raises(IngressFull):
+        for i in range(3, 8):
+            rt2.submit(_req(f"x{i}"))
+    gate.set()
+    rt2.stop()
+
+
+def test_engine_failure_reaches_every_request_and_health():
+    eng = FakeEngine(fail_after=2)
+    rt = ServingRuntime(lambda: eng)
+    rt.start()
+    h1, h2 = rt.submit(_req("a", max_tokens=50)), rt.submit(_req("b", max_tokens=50))
+    for h in (h1, h2):
+        events = _drain(h)
+        assert events[-1].kind is EventKind.ERROR and "boom" in events[-1].error
+    time.sleep(0.05)
+    assert not rt.is_healthy and isinstance(rt.failure, RuntimeError)
+    rt.stop()
+
+
+def test_shutdown_finishes_open_requests():
+    eng = FakeEngine(step_delay=0.01)
+    rt = ServingRuntime(lambda: eng)
+    rt.start()
+    h = rt.submit(_req("s", max_tokens=100_000))
+    assert h.next_event_blocking(5.0).kind is EventKind.ACCEPTED
+    rt.stop()
+    events = _drain(h)
+    assert events[-1].finish_reason == "shutdown"
+
+
+def _png_data_url():
+    from PIL import Image
+
+    buf = io.BytesIO()
+    Image.new("RGB", (32, 32), (10, 20, 30)).save(buf, format="PNG")
+    return "data:image/png;base64," + base64.b64encode(buf.getvalue()).decode()
+
+
+def test_http_app_json_sse_and_status_codes():
+    eng = FakeEngine()
+    rt = ServingRuntime(lambda: eng, ingress_capacity=8)
+    rt.start()
+    app = create_app(rt, manage_runtime=False)
+
+    async def scenario():
+        transport = httpx.ASGITransport(app=app)
+        async with httpx.AsyncClient(transport=transport, base_url="http://t") as client:
+            assert (await client.get("/health")).json() == {"status": "ok"}
+            r = await client.post("/v1/generate", json={"prompt": "hi", "sampling": {"max_tokens": 2}})
+            assert r.status_code == 200
+            body = r.json()
+            assert body["event"] == "done" and body["token_ids"] == [101, 102] and body["finish_reason"] == "length"
+            # unknown field -> 422 from the strict schema; inconsistent media -> 422
+            assert (await client.post("/v1/generate", json={"prompt": "hi", "bogus": 1})).status_code == 422
+            assert (await client.post("/v1/generate", json={"prompt": "hi", "modality": "image"})).status_code == 422
+            # image and video bodies reach the right engine entry points
+            url = _png_data_url()
+            r = await client.post("/v1/generate", json={"prompt": "what", "modality": "image", "media": url,
+                                                         "sampling": {"max_tokens": 1}})
+            assert r.status_code == 200
+            r = await client.post("/v1/generate", json={"prompt": "what", "modality": "video", "media": [url, url],
+                                                         "sampling": {"max_tokens": 1}})
+            assert r.status_code == 200
+            r = await client.post("/v1/generate", json={"prompt": "x", "modality": "image", "media": "data:image/png;base64,@@"})
+            assert r.status_code == 400
+            # SSE stream
+            async with client.stream("POST", "/v1/generate", json={"prompt": "hi", "stream": True, "request_id": "sse-1",
+                                                                  "sampling": {"max_tokens": 2}}) as resp:
+                text = (await resp.aread()).decode()
+            frames = [f for f in text.split("\n\n") if f]
+            assert [f.split("\n")[0] for f in frames] == ["event: accepted", "event: token", "event: token", "event: done"]
+            assert json.loads(frames[-1].split("data: ", 1)[1])["token_ids"] == [101, 102]
+
+    asyncio.run(scenario())
+    assert eng.media_seen[-3][0] == "image" and eng.media_seen[-2] == ("video", 2)
+    rt.stop()
+
+    async def down():
+        transport = httpx.ASGITransport(app=app)
+        async with httpx.AsyncClient(transport=transport, base_url="http://t") as client:
+            assert (await client.get("/health")).status_code == 503
+            assert (await client.post("/v1/generate", json={"prompt": "hi"})).status_code == 503
+
+    asyncio.run(down())
+
+
+def test_cli_engine_config(tmp_path):
+    p = tmp_path / "cfg.json"
+    p.write_text(json.dumps({"tensor_parallel_size": 2, "max_model_len": 512}))
+    assert load_engine_options(str(p)) == {"tensor_parallel_size": 2, "max_model_len": 512}
+    p.write_text(json.dumps({"model": "x"}))
+    with pytest.raises(ValueError):
+        load_engine_options(str(p))
+    assert load_engine_options(None) == {}
