@@ -300,9 +300,58 @@ class Qwen3VLModel:
     @torch.no_grad()
     def encode_vision(self, pixel_values: torch.Tensor, grid_thw: Sequence[Sequence[int]]) -> tuple[torch.Tensor, list[torch.Tensor]]:
         """``pixel_values [N, C*Tp*P*P]`` -> merged visual tokens ``[N/4, H]`` and one
-        DeepStack feature tensor per tap, all replicated on every rank."""
-        v = self.arch.vision
+        DeepStack feature tensor per tap, identical on every rank.
+
+        Tensor-parallel ranks with the fused communicator split the work by attention
+        segment (one image or one temporal group each): every rank runs the blocks on its
+        own segments only and the merger's last GEMM writes its rows into every rank's
+        gathered output from its epilogue (fused merger GEMM -> all-gather).  The reference
+        replicates the whole tower on every rank (``docs/ARCHITECTURE.md:83``).
+        """
         grid = [tuple(int(x) for x in g) for g in grid_thw]
+        unit = self.arch.vision.merge_unit
+        total_tokens = sum(t * h * w for t, h, w in grid) // unit
+        comm = self.comm
+        if self.tp > 1 and pixel_values.device.type != "meta" and hasattr(comm, "vision_begin") and self.device.type == "cuda" \
+                and comm.vision_begin(total_tokens):
+            return self._encode_vision_sharded(pixel_values, grid, total_tokens)
+        main, deep = self._vision_tower(pixel_values, grid, None, 0)
+        return main, deep
+
+    def _vision_shards(self, grid: list[tuple[int, int, int]]) -> list[tuple[int, int, list[tuple[int, int, int]]]]:
+        """Contiguous, patch-balanced assignment of (item, temporal group) segments to ranks:
+        per rank ``(first patch row, patch rows, sub-grid)``."""
+        segs = [(h * w, (1, h, w)) for t, h, w in grid for _ in range(t)]
+        total = sum(n for n, _ in segs)
+        out = []
+        i, start = 0, 0
+        for r in range(self.tp):
+            want_end = total * (r + 1) / self.tp
+            rows, sub = 0, []
+            while i < len(segs) and (start + rows + segs[i][0] / 2 <= want_end or (r == self.tp - 1)):
+                rows += segs[i][0]
+                g = segs[i][1]
+                if sub and sub[-1][1:] == g[1:]:
+                    sub[-1] = (sub[-1][0] + 1, g[1], g[2])  # consecutive frames of one clip
+                else:
+                    sub.append(g)
+                i += 1
+            out.append((start, rows, sub))
+            start += rows
+        return out
+
+    def _encode_vision_sharded(self, pixel_values: torch.Tensor, grid, total_tokens: int):
+        comm = self.comm
+        unit = self.arch.vision.merge_unit
+        start, rows, sub = self._vision_shards(grid)[self.rank]
+        n_out = 1 + len(self.arch.vision.deepstack_visual_indexes)
+        if rows > 0:
+            self._vision_tower(pixel_values[start:start + rows], sub, comm, start // unit)
+        outs = comm.vision_finish(n_out, total_tokens)
+        return outs[0], outs[1:]
+
+    def _vision_tower(self, pixel_values: torch.Tensor, grid, comm, token_base: int):
+        v = self.arch.vision
         dev = self.device
         x = ops.linear(pixel_values.to(device=dev, dtype=self.dtype), self.patch_w, bias=self.patch_b)
         idx, wt = vision_pos_embed_plan(grid, v.grid_per_side, v.spatial_merge_size)
@@ -326,16 +375,20 @@ class Qwen3VLModel:
             h = ops.linear(h, b.fc1_w, bias=b.fc1_b, act="gelu_tanh")
             x = ops.linear(h, b.fc2_w, bias=b.fc2_b, residual=x, out=x if x.is_cuda else None)
             if i in v.deepstack_visual_indexes:
-                deep.append(self._merge(x, self.mergers[f"deepstack.{v.deepstack_visual_indexes.index(i)}"]))
-        return self._merge(x, self.mergers["main"]), deep
+                k_idx = v.deepstack_visual_indexes.index(i)
+                deep.append(self._merge(x, self.mergers[f"deepstack.{k_idx}"], comm, 1 + k_idx, token_base))
+        return self._merge(x, self.mergers["main"], comm, 0, token_base), deep
 
-    def _merge(self, x: torch.Tensor, m: MergerWeights) -> torch.Tensor:
+    def _merge(self, x: torch.Tensor, m: MergerWeights, comm=None, output: int = 0, token_base: int = 0):
         v = self.arch.vision
         if m.post_norm:
             h = ops.layernorm(x.view(-1, v.merged_dim), m.norm_w, m.norm_b, v.layer_norm_eps)
         else:
             h = ops.layernorm(x, m.norm_w, m.norm_b, v.layer_norm_eps).view(-1, v.merged_dim)
         h = ops.linear(h, m.fc1_w, bias=m.fc1_b, act="gelu")
+        if comm is not None:
+            comm.allgather_linear(h, m.fc2_w, m.fc2_b, output, token_base)
+            return None
         return ops.linear(h, m.fc2_w, bias=m.fc2_b)
 
     # ---------------------------------------------------------------------- text

@@ -87,7 +87,58 @@ __global__ void __launch_bounds__(256) argmax_exchange_kernel(const ArgmaxArgs a
   }
 }
 
+// Raise flag[my_rank] = seq on every peer (a rank that had nothing to contribute).
+struct SignalArgs {
+  unsigned long long* peer_flag[8];
+  int n_peers, my_rank;
+  unsigned long long seq;
+};
+__global__ void signal_kernel(const SignalArgs a) {
+  pdl_launch_dependents();
+  pdl_wait();
+  if ((int)threadIdx.x < a.n_peers) {
+    __threadfence_system();
+    asm volatile("st.release.sys.global.u64 [%0], %1;" ::"l"(a.peer_flag[threadIdx.x] + a.my_rank), "l"(a.seq) : "memory");
+  }
+}
+
+// Bounded wait until flags[0..n) >= seq (data other GPUs pushed is then visible to the
+// kernels that follow in the stream).
+__global__ void wait_flags_kernel(const unsigned long long* flags, int n, unsigned long long seq) {
+  pdl_launch_dependents();
+  pdl_wait();
+  if ((int)threadIdx.x < n) {
+    const long long t0 = clock64();
+    bool ok = false;
+    for (;;) {
+      unsigned long long v;
+      asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(flags + threadIdx.x) : "memory");
+      if (v >= seq) {
+        ok = true;
+        break;
+      }
+      if (clock64() - t0 > PRISM_WAIT_CYCLES) break;
+    }
+    if (!ok) prism_report(PRISM_ERR_PEER_TIMEOUT, 200 + threadIdx.x);
+  }
+}
+
 }  // namespace
+
+PRISM_API int prism_signal_peers(const void* const* peer_flag, int n_peers, int my_rank, long long seq, void* stream) {
+  if (n_peers < 1 || n_peers > 8) return -20;
+  SignalArgs a;
+  for (int p = 0; p < 8; ++p) a.peer_flag[p] = p < n_peers ? (unsigned long long*)peer_flag[p] : nullptr;
+  a.n_peers = n_peers;
+  a.my_rank = my_rank;
+  a.seq = (unsigned long long)seq;
+  return (int)prism_launch(signal_kernel, dim3(1), dim3(32), 0, reinterpret_cast<cudaStream_t>(stream), false, a);
+}
+
+PRISM_API int prism_wait_flags(const void* flags, int n, long long seq, void* stream) {
+  return (int)prism_launch(wait_flags_kernel, dim3(1), dim3(32), 0, reinterpret_cast<cudaStream_t>(stream), false,
+                           (const unsigned long long*)flags, n, (unsigned long long)seq);
+}
 
 PRISM_API int prism_ipc_alloc(long long bytes, void** out) {
   void* p = nullptr;

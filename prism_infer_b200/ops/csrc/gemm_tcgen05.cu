@@ -55,10 +55,12 @@ struct GemmArgs {
   // into every rank's slab group and the last CTA raises a flag on every rank.
   int n_peers;               // 0 = off
   int my_rank;
-  int point;                 // exchange point index inside the step
+  int push_rows;             // 1: all-gather form, bf16 rows [row_base + token] on every rank
+  long long row_base;
+  long long point;           // exchange point inside the step (or an absolute sequence number)
   int* cta_counter;          // local, zero-initialised, self-resetting
-  const unsigned long long* epoch;  // local device word: sequence base of the current step
-  float* peer_out[8];        // slab buffers of this exchange slot on every rank (incl. own)
+  const unsigned long long* epoch;  // local device word: sequence base of the current step (null: 0)
+  float* peer_out[8];        // slab buffers (or bf16 row buffers) of this slot on every rank (incl. own)
   unsigned long long* peer_flag[8];  // flag arrays [tp] of this slot on every rank
 };
 
@@ -202,6 +204,15 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
                 const float u = bf16_round(__uint_as_float(r2[j]));
                 v = bf16_round(silu(g)) * u;
                 out_b[(size_t)n * a.ldo + m] = __float2bfloat16_rn(v);
+              } else if (a.n_peers > 0 && a.push_rows) {
+                // fused GEMM -> all-gather: this rank's rows land in every rank's copy
+                v += bias_v;
+                if (a.act == 1) v = gelu_tanh(v);
+                else if (a.act == 2) v = gelu_erf(v);
+                const __nv_bfloat16 bv = __float2bfloat16_rn(v);
+                const size_t off = (size_t)(a.row_base + n) * a.ldo + m;
+#pragma unroll 8
+                for (int p = 0; p < a.n_peers; ++p) reinterpret_cast<__nv_bfloat16*>(a.peer_out[p])[off] = bv;
               } else if (a.n_peers > 0) {
                 const size_t off = (size_t)(a.my_rank * (int)gridDim.z + split) * a.split_stride + (size_t)n * a.ldo + m;
 #pragma unroll 8
@@ -231,7 +242,7 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
     if (old == total - 1) {
       *a.cta_counter = 0;
       __threadfence_system();
-      const unsigned long long seq = *a.epoch + (unsigned long long)a.point;
+      const unsigned long long seq = (a.epoch ? *a.epoch : 0ull) + (unsigned long long)a.point;
       for (int p = 0; p < a.n_peers; ++p) {
         asm volatile("st.release.sys.global.u64 [%0], %1;" ::"l"(a.peer_flag[p] + a.my_rank), "l"(seq) : "memory");
       }
@@ -339,7 +350,8 @@ int launch_gemm(const CUtensorMap& tw, const CUtensorMap& tx, GemmArgs& a, int m
 // dual: second weight tile starts at row w2_row_off; output = silu(W1 x) * (W2 x), M rows.
 // Returns 0 on success, a cudaError_t (>0) or a negative validation code.
 struct PushSpec {
-  int n_peers, my_rank, point;
+  int n_peers, my_rank, push_rows;
+  long long point, row_base;
   int* cta_counter;
   const unsigned long long* epoch;
   float* peer_out[8];
@@ -388,6 +400,8 @@ static int gemm_wx_impl(const void* W, const void* X, void* out, int M, int T, i
   a.n_peers = 0;
   a.my_rank = 0;
   a.point = 0;
+  a.push_rows = 0;
+  a.row_base = 0;
   a.cta_counter = nullptr;
   a.epoch = nullptr;
   for (int p = 0; p < 8; ++p) {
@@ -398,6 +412,8 @@ static int gemm_wx_impl(const void* W, const void* X, void* out, int M, int T, i
     a.n_peers = push->n_peers;
     a.my_rank = push->my_rank;
     a.point = push->point;
+    a.push_rows = push->push_rows;
+    a.row_base = push->row_base;
     a.cta_counter = push->cta_counter;
     a.epoch = push->epoch;
     for (int p = 0; p < push->n_peers && p < 8; ++p) {
@@ -443,13 +459,15 @@ PRISM_API int prism_gemm_wx(const void* W, const void* X, void* out, int M, int 
 PRISM_API int prism_gemm_wx_push(const void* W, const void* X, int M, int T, int K, long long ldw, long long ldx,
                                  long long ldo, int w_rows_total, int splits, long long split_stride,
                                  const void* const* peer_out, const void* const* peer_flag, int n_peers, int my_rank,
-                                 int point, void* cta_counter, const void* epoch, int bn_override, int stages_override,
+                                 long long point, void* cta_counter, const void* epoch, int bn_override, int stages_override,
                                  void* stream_ptr, int pdl) {
   if (n_peers < 1 || n_peers > 8) return -20;
   PushSpec ps;
   ps.n_peers = n_peers;
   ps.my_rank = my_rank;
   ps.point = point;
+  ps.push_rows = 0;
+  ps.row_base = 0;
   ps.cta_counter = reinterpret_cast<int*>(cta_counter);
   ps.epoch = reinterpret_cast<const unsigned long long*>(epoch);
   for (int p = 0; p < 8; ++p) {
@@ -458,6 +476,31 @@ PRISM_API int prism_gemm_wx_push(const void* W, const void* X, int M, int T, int
   }
   return gemm_wx_impl(W, X, const_cast<void*>(peer_out[my_rank]), M, T, K, ldw, ldx, ldo, w_rows_total, nullptr, nullptr,
                       0, 0, 0, 0, splits, 1, split_stride, bn_override, stages_override, stream_ptr, pdl, &ps);
+}
+
+// Fused GEMM -> all-gather: out rows [row_base, row_base + T) = act(X W^T + bias) as bf16 are
+// written into every rank's buffer (peer_out[p], row stride ldo), then flag[my_rank] on every
+// rank is set to (*epoch or 0) + seq.  Used for the sharded vision tower's merger output.
+PRISM_API int prism_gemm_wx_allgather(const void* W, const void* X, int M, int T, int K, long long ldw, long long ldx,
+                                      long long ldo, long long row_base, const void* bias, int act,
+                                      const void* const* peer_out, const void* const* peer_flag, int n_peers,
+                                      int my_rank, long long seq, void* cta_counter, const void* epoch,
+                                      void* stream_ptr, int pdl) {
+  if (n_peers < 1 || n_peers > 8) return -20;
+  PushSpec ps;
+  ps.n_peers = n_peers;
+  ps.my_rank = my_rank;
+  ps.point = seq;
+  ps.push_rows = 1;
+  ps.row_base = row_base;
+  ps.cta_counter = reinterpret_cast<int*>(cta_counter);
+  ps.epoch = reinterpret_cast<const unsigned long long*>(epoch);
+  for (int p = 0; p < 8; ++p) {
+    ps.peer_out[p] = p < n_peers ? reinterpret_cast<float*>(const_cast<void*>(peer_out[p])) : nullptr;
+    ps.peer_flag[p] = p < n_peers ? reinterpret_cast<unsigned long long*>(const_cast<void*>(peer_flag[p])) : nullptr;
+  }
+  return gemm_wx_impl(W, X, const_cast<void*>(peer_out[my_rank]), M, T, K, ldw, ldx, ldo, M, bias, nullptr, 0, act, 0, 0,
+                      1, 0, 0, 0, 0, stream_ptr, pdl, &ps);
 }
 
 // Number of split-K slabs prism_gemm_wx will actually write for (K, splits).

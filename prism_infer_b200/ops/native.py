@@ -43,8 +43,11 @@ _SIGNATURES = {
     "prism_kv_compact": "pliplppppiiiip",
     "prism_sample": "pllipppiilupppipi",
     "prism_merge_candidates": "pppiipi",
-    "prism_gemm_wx_push": "ppiiillliilppiiippiipi",
+    "prism_gemm_wx_push": "ppiiillliilppiilppiipi",
     "prism_add_rmsnorm_wait": "plippppppiifpipipi",
+    "prism_gemm_wx_allgather": "ppiiillllpippiilpppi",
+    "prism_signal_peers": "piilp",
+    "prism_wait_flags": "pilp",
     "prism_ipc_alloc": "lp",
     "prism_ipc_free": "p",
     "prism_ipc_get_handle": "pp",

@@ -145,5 +145,42 @@ class FusedComm(NcclComm):
         )
         return out
 
+    # ---- sharded vision tower: merger GEMM -> all-gather ------------------------------------
+    def vision_begin(self, total_tokens: int) -> bool:
+        """Start a sharded vision-tower call; False when the gathered outputs would not fit."""
+        if total_tokens > symm.VIS_T_MAX:
+            return False
+        self.vision_seq = getattr(self, "vision_seq", 0) + 1
+        self._vis_set = self.vision_seq % 2
+        self._vis_pushed: set[int] = set()
+        return True
+
+    def allgather_linear(self, x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor, output: int, row_base: int) -> None:
+        """``x @ w.T + bias`` written as bf16 rows ``[row_base, row_base + T)`` of gathered
+        output ``output`` on every rank, straight from the GEMM epilogue."""
+        r = self.region
+        T, K = x.shape
+        flags = r.ptr_array(symm.OFF_VIS_FLAGS + (self._vis_set * symm.VIS_OUTPUTS + output) * 64)
+        bufs = r.ptr_array(r.vis_offset(self._vis_set, output))
+        native.call(
+            "prism_gemm_wx_allgather", w.data_ptr(), x.data_ptr(), w.shape[0], T, K, w.stride(0), x.stride(0),
+            self.hidden, row_base, bias.data_ptr(), 0, bufs, flags, self.size, self.rank, self.vision_seq,
+            r.local(symm.OFF_VIS_COUNTER), None, torch.cuda.current_stream().cuda_stream, 0,
+        )
+        self._vis_pushed.add(output)
+
+    def vision_finish(self, n_outputs: int, total_tokens: int) -> list[torch.Tensor]:
+        """Signal for outputs this rank had no rows for, wait for every rank, return copies."""
+        r = self.region
+        stream = torch.cuda.current_stream().cuda_stream
+        outs = []
+        for k in range(n_outputs):
+            off = symm.OFF_VIS_FLAGS + (self._vis_set * symm.VIS_OUTPUTS + k) * 64
+            if k not in self._vis_pushed:
+                native.call("prism_signal_peers", r.ptr_array(off), self.size, self.rank, self.vision_seq, stream)
+            native.call("prism_wait_flags", r.local(off), self.size, self.vision_seq, stream)
+            outs.append(r.vis_rows(self._vis_set, k, total_tokens).clone())
+        return outs
+
     def close(self) -> None:
         self.region.close()

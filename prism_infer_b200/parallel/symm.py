@@ -11,8 +11,10 @@ Region layout (bytes)::
     0     flags of exchange slot 0   u64[8]      256   flags of slot 1   u64[8]
     512   flags of the arg-max exchange u64[8]   768   step epoch word   u64
     1024  CTA counter slot 0  i32                1280  CTA counter slot 1  i32
+    1344  CTA counter of the vision all-gather  1536  vision flags: 2 sets x 4 outputs x u64[8]
     4096  arg-max values f32[8][BMAX]            then  arg-max ids i64[8][BMAX]
     SLAB0 / SLAB1: two slab buffers of  tp * S_MAX * T_MAX * H  fp32 each
+    VIS: 2 sets x 4 outputs x VIS_T_MAX x H bf16 (gathered merger outputs of the vision tower)
 """
 
 from __future__ import annotations
@@ -31,6 +33,10 @@ OFF_FLAGS = (0, 256)
 OFF_ARGMAX_FLAGS = 512
 OFF_EPOCH = 768
 OFF_COUNTER = (1024, 1280)
+OFF_VIS_COUNTER = 1344
+OFF_VIS_FLAGS = 1536          # 8 arrays (2 buffer sets x 4 outputs) of u64[8]
+VIS_OUTPUTS = 4               # main merger + up to three DeepStack mergers
+VIS_T_MAX = 4096              # merged visual tokens per vision-tower call on the fused path
 OFF_ARGMAX_VAL = 4096
 OFF_ARGMAX_ID = OFF_ARGMAX_VAL + 8 * B_MAX * 4
 OFF_SLABS = (OFF_ARGMAX_ID + 8 * B_MAX * 8 + 4095) // 4096 * 4096
@@ -66,7 +72,7 @@ class SymmetricRegion:
 
         lib = native.lib()
         slab_bytes = size * S_MAX * T_MAX * hidden * 4
-        nbytes = OFF_SLABS + 2 * slab_bytes
+        nbytes = OFF_SLABS + 2 * slab_bytes + 2 * VIS_OUTPUTS * VIS_T_MAX * hidden * 2
         out = ctypes.c_void_p()
         _check(lib.prism_ipc_alloc(nbytes, ctypes.byref(out)), "prism_ipc_alloc")
         handle = (ctypes.c_char * 64)()
@@ -90,7 +96,7 @@ class SymmetricRegion:
         """All ranks' regions on the current device (single-GPU tests of the fused kernels)."""
         lib = native.lib()
         slab_bytes = size * S_MAX * T_MAX * hidden * 4
-        nbytes = OFF_SLABS + 2 * slab_bytes
+        nbytes = OFF_SLABS + 2 * slab_bytes + 2 * VIS_OUTPUTS * VIS_T_MAX * hidden * 2
         ptrs = []
         for _ in range(size):
             out = ctypes.c_void_p()
@@ -107,6 +113,15 @@ class SymmetricRegion:
         n = groups * tokens * self.hidden
         raw = self.local_bytes()[OFF_SLABS + slot * self.slab_bytes: OFF_SLABS + slot * self.slab_bytes + n * 4]
         return raw.view(torch.float32).view(groups, tokens, self.hidden)
+
+    def vis_offset(self, buffer_set: int, output: int) -> int:
+        return OFF_SLABS + 2 * self.slab_bytes + (buffer_set * VIS_OUTPUTS + output) * VIS_T_MAX * self.hidden * 2
+
+    def vis_rows(self, buffer_set: int, output: int, rows: int) -> torch.Tensor:
+        """Local bf16 view ``[rows, hidden]`` of one gathered vision output."""
+        off = self.vis_offset(buffer_set, output)
+        raw = self.local_bytes()[off: off + rows * self.hidden * 2]
+        return raw.view(torch.bfloat16).view(rows, self.hidden)
 
     # ---- pointer tables for the launchers ------------------------------------------------
     def ptr_array(self, offset: int):

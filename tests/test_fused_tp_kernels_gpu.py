@@ -79,3 +79,57 @@ def test_wait_that_never_completes_reports_status_and_returns(cuda_device):
     assert torch.isfinite(y.float()).all()
     for reg in regions:
         native.lib().prism_ipc_free(__import__("ctypes").c_void_p(reg.local_ptr))
+
+
+def test_sharded_vision_tower_matches_single_rank(cuda_device):
+    """Segment-sharded vision tower with the fused merger GEMM -> all-gather, ranks emulated
+    on one device: every rank's pushes are issued before any rank waits."""
+    import ctypes
+
+    import numpy as np
+
+    from prism_infer_b200.engine.vl_inputs import PatchProcessor
+    from prism_infer_b200.models.architecture import Qwen3VLArch
+    from prism_infer_b200.models.qwen3_vl import Qwen3VLModel
+    from prism_infer_b200.models.weights import random_weights
+    from prism_infer_b200.parallel import symm
+    from prism_infer_b200.parallel.comm import FusedComm
+
+    ops.set_pdl(False)
+    arch = Qwen3VLArch.tiny()
+    weights = random_weights(arch, dtype=torch.float32, seed=0)
+    model = Qwen3VLModel(arch, device="cuda", dtype=torch.bfloat16)
+    model.load(weights.items())
+    proc = PatchProcessor(arch)
+    rng = np.random.default_rng(0)
+    parts = [proc.process_image(rng.integers(0, 256, (s, s, 3), dtype=np.uint8)) for s in (64, 96, 64)]
+    vid = proc.process_video([rng.integers(0, 256, (64, 64, 3), dtype=np.uint8) for _ in range(6)])
+    pixel_values = torch.cat([p for p, _ in parts] + [vid[0]]).cuda()
+    grid = [g for _, g in parts] + [vid[1]]
+    want_main, want_deep = model._vision_tower(pixel_values, grid, None, 0)
+    total_tokens = want_main.shape[0]
+    tp = 4
+    H = arch.text.hidden_size
+    regions = symm.SymmetricRegion.create_emulated(tp, H)
+    comms = [FusedComm(r, tp, H, region=regions[r]) for r in range(tp)]
+    model.tp = tp
+    try:
+        for call in range(3):  # alternate buffer sets across calls
+            shards = model._vision_shards(grid)
+            assert sum(rows for _, rows, _ in shards) == pixel_values.shape[0]
+            for r, c in enumerate(comms):
+                assert c.vision_begin(total_tokens)
+                start, rows, sub = shards[r]
+                if rows:
+                    model._vision_tower(pixel_values[start:start + rows], sub, c, start // arch.vision.merge_unit)
+            for c in comms:
+                outs = c.vision_finish(1 + len(want_deep), total_tokens)
+                assert torch.equal(outs[0], want_main)
+                for got, want in zip(outs[1:], want_deep):
+                    assert torch.equal(got, want)
+        torch.cuda.synchronize()
+        native.check_status()
+    finally:
+        model.tp = 1
+        for reg in regions:
+            native.lib().prism_ipc_free(ctypes.c_void_p(reg.local_ptr))
