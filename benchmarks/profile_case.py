@@ -1,0 +1,82 @@
+"""Run one small, fixed kernel case a few times, for Nsight Compute captures.
+
+The inputs are larger than the 126 MB L2 where bandwidth matters but only a few hundred MB
+in total, and only a handful of launches run, so a ``--set full`` capture of one kernel ends
+by itself in about a minute.
+
+    python benchmarks/profile_case.py gemm_decode      # qkv-shaped weight-streaming GEMM, 1 token, split-K
+    python benchmarks/profile_case.py gemm_prefill     # 2048 x 4096 x 6144 bf16 GEMM
+    python benchmarks/profile_case.py gemm_dual        # dual-accumulator gate/up GEMM + SwiGLU, 2048 tokens
+    python benchmarks/profile_case.py decode_attention # scaled-FP8 paged decode, batch 32, ctx 2048
+    python benchmarks/profile_case.py prefill_attention
+    python benchmarks/profile_case.py add_rmsnorm
+"""
+
+from __future__ import annotations
+
+import os
+import sys
+
+import torch
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+from prism_infer_b200 import ops  # noqa: E402
+
+
+def main() -> None:
+    case = sys.argv[1] if len(sys.argv) > 1 else "gemm_decode"
+    reps = int(sys.argv[2]) if len(sys.argv) > 2 else 4
+    dev = torch.device("cuda:0")
+    g = torch.Generator(device=dev).manual_seed(0)
+
+    def rnd(*shape, scale=1.0):
+        return (torch.randn(*shape, generator=g, device=dev) * scale).to(torch.bfloat16)
+
+    if case == "gemm_decode":
+        ws = [rnd(6144, 4096, scale=0.02) for _ in range(4)]  # 4 x 50 MB: every launch misses L2
+        x = rnd(1, 4096)
+        for i in range(reps):
+            ops.linear_partial(x, ws[i % 4], 3)
+    elif case == "gemm_prefill":
+        w, x = rnd(6144, 4096, scale=0.02), rnd(2048, 4096)
+        for _ in range(reps):
+            ops.linear(x, w)
+    elif case == "gemm_dual":
+        w, x = rnd(24576, 4096, scale=0.02), rnd(2048, 4096)
+        for _ in range(reps):
+            ops.gate_up_swiglu(x, w)
+    elif case == "decode_attention":
+        B, ctx, page = 32, 2048, 256
+        cache = ops.KVCache(1, B * ctx // page, 8, page, 128, ops.KV_FP8_SCALED, dev)
+        cache.payload.view(torch.uint8).random_(0, 120)
+        cache.scales.uniform_(0.005, 0.02)
+        bt = torch.arange(B * ctx // page, dtype=torch.int32, device=dev).view(B, -1)
+        cl = torch.full((B,), ctx, dtype=torch.int32, device=dev)
+        q = rnd(B, 32, 128)
+        for _ in range(reps):
+            ops.paged_decode_attention(q, cache, 0, bt, cl)
+    elif case == "prefill_attention":
+        T, page = 2048, 256
+        cache = ops.KVCache(1, T // page, 8, page, 128, ops.KV_FP8_SCALED, dev)
+        cache.payload.view(torch.uint8).random_(0, 120)
+        cache.scales.uniform_(0.005, 0.02)
+        bt = torch.arange(T // page, dtype=torch.int32, device=dev).view(1, -1)
+        q = rnd(T, 32, 128)
+        cu = torch.tensor([0, T], dtype=torch.int32, device=dev)
+        kv = torch.tensor([T], dtype=torch.int32, device=dev)
+        for _ in range(reps):
+            ops.paged_prefill_attention(q, cache, 0, cu, kv, bt, T)
+    elif case == "add_rmsnorm":
+        parts = torch.randn(4, 8, 4096, device=dev)
+        res, w = rnd(8, 4096), rnd(4096)
+        for _ in range(reps):
+            ops.add_rmsnorm(w, 1e-6, partials=parts, residual=res)
+    else:
+        raise SystemExit(f"unknown case {case}")
+    torch.cuda.synchronize()
+    print("done", case)
+
+
+if __name__ == "__main__":
+    main()
