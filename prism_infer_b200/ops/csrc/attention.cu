@@ -231,20 +231,32 @@ __global__ void __launch_bounds__(128) paged_decode_kernel(const DecodeArgs a) {
   __syncthreads();
   if (!s_last) return;
   __threadfence();
+  // Merge: coefficients of every (head, split) go to shared memory first, then each thread
+  // accumulates its outputs with independent loads (no serial chain over the splits).
+  __shared__ float s_coef[G][32];
+  __shared__ float s_inv[G];
+  const int ns = a.nsplit;  // <= 32
+  if (warp < G || G > NWARP) {
+    for (int g = warp; g < G; g += NWARP) {
+      const size_t bh = (size_t)b * a.Hq + kvh * G + g;
+      const float ms = lane < ns ? __ldcg(&a.part_ml[(bh * ns + lane) * 2]) : -INFINITY;
+      const float ls = lane < ns ? __ldcg(&a.part_ml[(bh * ns + lane) * 2 + 1]) : 0.0f;
+      const float mm = warp_max(ms);
+      const float c = (ms == -INFINITY) ? 0.0f : __expf(ms - mm);
+      const float ll = warp_sum(ls * c);
+      s_coef[g][lane] = c;
+      if (lane == 0) s_inv[g] = ll > 0.0f ? 1.0f / ll : 0.0f;
+    }
+  }
+  __syncthreads();
   for (int idx = threadIdx.x; idx < G * D; idx += blockDim.x) {
     const int g = idx / D, d = idx % D;
     const size_t bh = (size_t)b * a.Hq + kvh * G + g;
-    float mm = -INFINITY;
-    for (int s = 0; s < a.nsplit; ++s) mm = fmaxf(mm, __ldcg(&a.part_ml[(bh * a.nsplit + s) * 2]));
-    float ll = 0.0f, oo = 0.0f;
-#pragma unroll 4
-    for (int s = 0; s < a.nsplit; ++s) {
-      const float ms = __ldcg(&a.part_ml[(bh * a.nsplit + s) * 2]);
-      const float c = (ms == -INFINITY) ? 0.0f : __expf(ms - mm);
-      ll += __ldcg(&a.part_ml[(bh * a.nsplit + s) * 2 + 1]) * c;
-      oo += __ldcg(&a.part_o[(bh * a.nsplit + s) * D + d]) * c;
-    }
-    a.out[bh * D + d] = __float2bfloat16_rn(ll > 0.0f ? oo / ll : 0.0f);
+    const float* po = a.part_o + bh * ns * D + d;
+    float oo = 0.0f;
+#pragma unroll 8
+    for (int s = 0; s < ns; ++s) oo += __ldcg(po + (size_t)s * D) * s_coef[g][s];
+    a.out[bh * D + d] = __float2bfloat16_rn(oo * s_inv[g]);
   }
 }
 
@@ -581,7 +593,7 @@ PRISM_API int prism_paged_decode(const void* q, const void* k_cache, const void*
   a.Hkv = Hkv;
   a.page = page;
   a.max_blocks = max_blocks;
-  a.nsplit = nsplit < 1 ? 1 : nsplit;
+  a.nsplit = nsplit < 1 ? 1 : (nsplit > 32 ? 32 : nsplit);
   a.scale = scale;
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   int rc;
