@@ -127,6 +127,12 @@ class TPComm:
         return ops.add_rmsnorm(weight, eps, x=dense, partials=partials, residual=residual, extra=extra,
                                extra_index=extra_index)
 
+    def norm_source(self, dense, partials, ticket) -> dict:
+        """Keyword arguments that tell ``ops.linear_normx`` where the pending delta lives."""
+        if partials is not None:
+            return dict(partials_ptr=partials.data_ptr(), slab_stride=partials.stride(0), P=partials.shape[0])
+        return dict(x=dense)
+
 
 class Qwen3VLModel:
     def __init__(self, arch: Qwen3VLArch, *, device, dtype: torch.dtype, comm: TPComm | None = None,
@@ -423,8 +429,36 @@ class Qwen3VLModel:
         residual: Optional[torch.Tensor] = None
         dense, partials, ticket = x, None, None
         n_deep = len(deepstack) if deepstack is not None else 0
+        # at most four tokens on CUDA: residual add + RMSNorm run inside the next projection
+        fuse_norm = x.is_cuda and T <= ops.NORMX_MAX_TOKENS and n_deep == 0 and self.H % 64 == 0
+        if fuse_norm:
+            res_bufs = [torch.empty((T, self.H), dtype=torch.bfloat16, device=x.device) for _ in range(2)]
+            flip = 0
         for i, l in enumerate(self.layers):
             extra = deepstack[i - 1] if 0 < i <= n_deep else None
+            if fuse_norm:
+                qkv_p = ops.linear_normx(l.qkv, l.input_norm, t.rms_norm_eps, T, residual=residual, residual_out=res_bufs[flip],
+                                         splits=ops.choose_splits(l.qkv.shape[0], self.H, T),
+                                         **comm.norm_source(dense, partials, ticket))
+                residual, flip = res_bufs[flip], flip ^ 1
+                q = ops.qk_norm_rope_store(qkv=None, partials=qkv_p, positions=positions, q_weight=l.q_norm, k_weight=l.k_norm,
+                                           num_heads=self.Hq, num_kv_heads=self.Hkv, head_dim=self.D, theta=t.rope_theta,
+                                           section=t.mrope_section, eps=t.rms_norm_eps, slots=meta.slots, cache=cache, layer=i)
+                a = ops.paged_prefill_attention(q, cache, i, meta.cu_seqlens_q, meta.kv_lens, meta.block_tables, meta.max_q_len) \
+                    if meta.is_prefill else ops.paged_decode_attention(q, cache, i, meta.block_tables, meta.context_lens,
+                                                                       nsplit=meta.nsplit, workspace=meta.workspace)
+                dense, partials, ticket = comm.row_parallel(a.view(T, self.Hq * self.D), l.o)
+                src = comm.norm_source(dense, partials, ticket)
+                if self.I // 128 < 96:
+                    gu = ops.linear_normx(l.gate_up, l.post_norm, t.rms_norm_eps, T, residual=residual, residual_out=res_bufs[flip],
+                                          splits=ops.choose_splits(2 * self.I, self.H, T), **src)
+                    act = ops.swiglu(partials=gu)
+                else:
+                    act = ops.linear_normx(l.gate_up, l.post_norm, t.rms_norm_eps, T, residual=residual,
+                                           residual_out=res_bufs[flip], dual=True, **src)
+                residual, flip = res_bufs[flip], flip ^ 1
+                dense, partials, ticket = comm.row_parallel(act, l.down)
+                continue
             h, residual = comm.add_rmsnorm(l.input_norm, t.rms_norm_eps, dense, partials, ticket, residual,
                                            extra, vis_index if extra is not None else None)
             if small and h.is_cuda:

@@ -153,6 +153,54 @@ def gate_up_swiglu(x: torch.Tensor, w_gate_up: torch.Tensor, out: Optional[torch
     return out
 
 
+NORMX_MAX_TOKENS = 4
+
+
+def linear_normx(
+    w: torch.Tensor,
+    norm_weight: torch.Tensor,
+    eps: float,
+    tokens: int,
+    *,
+    residual_out: torch.Tensor,
+    partials_ptr: int | None = None,
+    slab_stride: int = 0,
+    P: int = 0,
+    x: Optional[torch.Tensor] = None,
+    residual: Optional[torch.Tensor] = None,
+    dual: bool = False,
+    splits: int = 1,
+    wait: Optional[tuple[int, int, int, int]] = None,
+) -> torch.Tensor:
+    """Projection with the preceding residual add + RMSNorm fused into its prologue (CUDA
+    only, at most ``NORMX_MAX_TOKENS`` tokens).
+
+    The activation operand is produced inside the GEMM from ``residual + sum of the P fp32
+    slabs at partials_ptr`` (or ``+ x`` when ``P == 0``); ``residual_out`` receives that
+    pre-norm sum.  ``wait = (flags_ptr, n, point, epoch_ptr)`` makes the kernel wait for a
+    tensor-parallel exchange first.  Returns fp32 split-K slabs ``[S, T, M]``, or with
+    ``dual`` the bf16 ``silu(gate) * up`` of a packed ``[2I, K]`` weight.
+    """
+    K = w.shape[1]
+    T = tokens
+    assert T <= NORMX_MAX_TOKENS and w.is_cuda
+    flags, n_wait, point, epoch = wait if wait is not None else (None, 0, 0, None)
+    if dual:
+        M = w.shape[0] // 2
+        out = torch.empty((T, M), dtype=torch.bfloat16, device=w.device)
+        native.call("prism_gemm_wx_normx", _p(w), _p(out), M, T, K, w.stride(0), out.stride(0), 2 * M, 1, M, 1, 0, 0,
+                    partials_ptr, slab_stride, P, _p(x), _p(residual), _p(residual_out), _p(norm_weight), float(eps),
+                    flags, n_wait, point, epoch, 0, _s(), _pdl())
+        return out
+    M = w.shape[0]
+    eff = effective_splits(K, splits)
+    out = torch.empty((eff, T, M), dtype=torch.float32, device=w.device)
+    native.call("prism_gemm_wx_normx", _p(w), _p(out), M, T, K, w.stride(0), out.stride(1), M, 0, 0, eff, 1, out.stride(0),
+                partials_ptr, slab_stride, P, _p(x), _p(residual), _p(residual_out), _p(norm_weight), float(eps),
+                flags, n_wait, point, epoch, 0, _s(), _pdl())
+    return out
+
+
 # ------------------------------------------------------------------------- norm family
 def add_rmsnorm(
     weight: torch.Tensor,

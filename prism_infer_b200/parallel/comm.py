@@ -131,6 +131,14 @@ class FusedComm(NcclComm):
         )
         return out, new_res
 
+    def norm_source(self, dense, partials, ticket) -> dict:
+        if ticket is None:
+            return super().norm_source(dense, partials, None)
+        slot, point, P, T = ticket
+        r = self.region
+        return dict(partials_ptr=r.local(symm.OFF_SLABS + slot * r.slab_bytes), slab_stride=T * self.hidden, P=P,
+                    wait=(r.local(symm.OFF_FLAGS[slot]), self.size, point, r.local(symm.OFF_EPOCH)))
+
     def greedy_merge(self, local_val: torch.Tensor, local_id: torch.Tensor) -> torch.Tensor:
         B = local_val.shape[0]
         if B > symm.B_MAX:

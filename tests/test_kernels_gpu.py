@@ -320,3 +320,38 @@ def test_vision_pointwise(cuda_device):
     rg = ops.vit_rope(qkv.clone().cuda(), coords.cuda(), inv.cuda(), heads, hd)
     rc = ops.vit_rope(qkv.float().clone(), coords, inv, heads, hd)
     close(rg, rc, 3e-2, 1e-2, "vit rope")
+
+
+@pytest.mark.parametrize("T", [1, 3, 4])
+@pytest.mark.parametrize("source", ["partials", "dense", "first_layer"])
+def test_gemm_with_fused_residual_rmsnorm_prologue(cuda_device, T, source):
+    """NORMX projections equal add+RMSNorm followed by the plain projection, bit for bit."""
+    H, M, I = 4096, 6144, 1536
+    g = torch.Generator().manual_seed(40 + T)
+    w = (torch.randn(M, H, generator=g) * H ** -0.5).to(torch.bfloat16).cuda()
+    wgu = (torch.randn(2 * I, H, generator=g) * H ** -0.5).to(torch.bfloat16).cuda()
+    nw = (1 + 0.1 * torch.randn(H, generator=g)).to(torch.bfloat16).cuda()
+    res = torch.randn(T, H, generator=g).to(torch.bfloat16).cuda()
+    parts = torch.randn(3, T, H, generator=g).cuda()
+    dense = torch.randn(T, H, generator=g).to(torch.bfloat16).cuda()
+    if source == "partials":
+        kw_ref = dict(partials=parts, residual=res.clone())
+        kw = dict(partials_ptr=parts.data_ptr(), slab_stride=parts.stride(0), P=3, residual=res)
+    elif source == "dense":
+        kw_ref = dict(x=dense, residual=res.clone())
+        kw = dict(x=dense, residual=res)
+    else:
+        kw_ref = dict(x=dense)
+        kw = dict(x=dense)
+    normed, new_res = ops.add_rmsnorm(nw, 1e-6, **kw_ref)
+    want = ops.linear_partial(normed, w, 3)
+    res_out = torch.empty(T, H, dtype=torch.bfloat16, device="cuda")
+    got = ops.linear_normx(w, nw, 1e-6, T, residual_out=res_out, splits=3, **kw)
+    torch.cuda.synchronize()
+    assert torch.equal(res_out, new_res)
+    assert torch.equal(got, want)
+    want_act = ops.gate_up_swiglu(normed, wgu)
+    res_out2 = torch.empty_like(res_out)
+    got_act = ops.linear_normx(wgu, nw, 1e-6, T, residual_out=res_out2, dual=True, **kw)
+    torch.cuda.synchronize()
+    assert torch.equal(got_act, want_act) and torch.equal(res_out2, new_res)
