@@ -509,6 +509,7 @@ def _decode_counters(device, n: int) -> torch.Tensor:
 def paged_decode_attention(
     q: torch.Tensor, cache: KVCache, layer: int, block_tables: torch.Tensor, context_lens: torch.Tensor,
     *, nsplit: int = 0, out: Optional[torch.Tensor] = None, workspace: Optional[tuple[torch.Tensor, torch.Tensor]] = None,
+    use_mma: Optional[bool] = None,
 ) -> torch.Tensor:
     """``q [B, Hq, D]`` against the paged cache; ``block_tables [B, maxblk]`` int32 (-1 = hole)."""
     B, Hq, D = q.shape
@@ -554,7 +555,8 @@ def paged_decode_attention(
         "prism_paged_decode", _p(q), _p(cache.k(layer)), _p(cache.v(layer)), _p(cache.k_scale(layer)),
         _p(cache.v_scale(layer)), _p(block_tables), _p(context_lens), _p(part_o), _p(part_ml), _p(out),
         _p(_decode_counters(q.device, B * cache.num_kv_heads)) if nsplit > 1 else None,
-        B, Hq, cache.num_kv_heads, D, cache.page, block_tables.shape[1], nsplit, cache.mode, scale, _s(), _pdl(),
+        B, Hq, cache.num_kv_heads, D, cache.page, block_tables.shape[1], nsplit, cache.mode, scale,
+        1 if (use_mma if use_mma is not None else B >= 4) else 0, _s(), _pdl(),
     )
     return out
 

@@ -532,6 +532,236 @@ __global__ void __launch_bounds__(128) flash_fwd_kernel(const FlashArgs a) {
   }
 }
 
+// =====================================================================================
+// Decode on the tensor cores (mma.sync m16n8k16): the G query heads of a KV head are rows of
+// one 16-row A tile, a 64-token K/V tile is dequantised to bf16 in shared memory once and
+// each warp scores and accumulates 16 of its tokens.  Used for larger batches, where the
+// SIMT kernel above is instruction-bound (one FMA per head and byte); same split-KV
+// partial format and in-kernel merge.
+// =====================================================================================
+template <int D, int G, bool KV8>
+__global__ void __launch_bounds__(128) paged_decode_mma_kernel(const DecodeArgs a) {
+  constexpr int BN = 64, NWARP = 4;
+  constexpr int LDS = D + 8;
+  constexpr int CHUNKS = D / 8;
+  extern __shared__ __align__(16) uint8_t dsm[];
+  bf16* Qs = reinterpret_cast<bf16*>(dsm);
+  bf16* Ks = Qs + 16 * LDS;
+  bf16* Vs = Ks + BN * LDS;
+  const int b = blockIdx.x, kvh = blockIdx.y, split = blockIdx.z;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int g = lane >> 2, t4 = lane & 3;
+  pdl_launch_dependents();
+  pdl_wait();
+  const int ctx = a.context_lens[b];
+  const int per_split = ((ctx + a.nsplit - 1) / a.nsplit + BN - 1) / BN * BN;
+  const int j_begin = split * per_split;
+  const int j_end = min(ctx, j_begin + per_split);
+  const int* bt = a.block_tables + (size_t)b * a.max_blocks;
+
+  for (int i = tid; i < 16 * CHUNKS; i += 128) {
+    const int r = i / CHUNKS, c = i % CHUNKS;
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (r < G) v = *reinterpret_cast<const uint4*>(a.q + ((size_t)b * a.Hq + (size_t)kvh * G + r) * D + c * 8);
+    *reinterpret_cast<uint4*>(Qs + r * LDS + c * 8) = v;
+  }
+  __syncthreads();
+  uint32_t qf[D / 16][4];
+  {
+    const int r = (lane & 7) + 8 * ((lane >> 3) & 1);
+    const int c = 8 * (lane >> 4);
+#pragma unroll
+    for (int kk = 0; kk < D / 16; ++kk) ldsm_x4(qf[kk], smem_u32(Qs + r * LDS + kk * 16 + c));
+  }
+  float o[D / 8][4];
+#pragma unroll
+  for (int i = 0; i < D / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.0f;
+  float m_run = -INFINITY, l_run = 0.0f;  // row g (rows >= G are padding)
+  const float sl2 = a.scale * 1.4426950408889634f;
+
+  for (int j0 = j_begin; j0 < j_end; j0 += BN) {
+    __syncthreads();
+    for (int i = tid; i < BN * CHUNKS; i += 128) {
+      const int r = i / CHUNKS, c = i % CHUNKS;
+      const int j = j0 + r;
+      uint4 k4 = make_uint4(0, 0, 0, 0), v4 = make_uint4(0, 0, 0, 0);
+      if (j < j_end) {
+        const int blk = bt[j / a.page];
+        if (blk >= 0) {
+          const size_t row = ((size_t)blk * a.Hkv + kvh) * a.page + (j % a.page);
+          if (KV8) {
+            const uint2 k8 = __ldg(reinterpret_cast<const uint2*>(reinterpret_cast<const uint8_t*>(a.k_cache) + row * D + c * 8));
+            const uint2 v8 = __ldg(reinterpret_cast<const uint2*>(reinterpret_cast<const uint8_t*>(a.v_cache) + row * D + c * 8));
+            const float ks = a.k_scale ? __ldg(a.k_scale + row) : 1.0f;
+            const float vs = a.v_scale ? __ldg(a.v_scale + row) : 1.0f;
+            const unsigned short* kp = reinterpret_cast<const unsigned short*>(&k8);
+            const unsigned short* vp = reinterpret_cast<const unsigned short*>(&v8);
+            uint32_t* ko = reinterpret_cast<uint32_t*>(&k4);
+            uint32_t* vo = reinterpret_cast<uint32_t*>(&v4);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              const float2 kk = fp8x2_to_float2(kp[e]);
+              const float2 vv = fp8x2_to_float2(vp[e]);
+              ko[e] = pack_bf16(kk.x * ks, kk.y * ks);
+              vo[e] = pack_bf16(vv.x * vs, vv.y * vs);
+            }
+          } else {
+            k4 = __ldg(reinterpret_cast<const uint4*>(reinterpret_cast<const bf16*>(a.k_cache) + row * D + c * 8));
+            v4 = __ldg(reinterpret_cast<const uint4*>(reinterpret_cast<const bf16*>(a.v_cache) + row * D + c * 8));
+          }
+        }
+      }
+      *reinterpret_cast<uint4*>(Ks + r * LDS + c * 8) = k4;
+      *reinterpret_cast<uint4*>(Vs + r * LDS + c * 8) = v4;
+    }
+    __syncthreads();
+    const int tok0 = warp * 16;  // this warp's 16 tokens of the tile
+    if (j0 + tok0 >= j_end) continue;
+    float s[2][4];
+#pragma unroll
+    for (int i = 0; i < 2; ++i) s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.0f;
+#pragma unroll
+    for (int kk = 0; kk < D / 16; ++kk) {
+      uint32_t kb[4];
+      const int n = tok0 + (lane & 7) + 8 * (lane >> 4);
+      const int c = kk * 16 + 8 * ((lane >> 3) & 1);
+      ldsm_x4(kb, smem_u32(Ks + n * LDS + c));
+      mma_bf16(s[0], qf[kk], kb[0], kb[1]);
+      mma_bf16(s[1], qf[kk], kb[2], kb[3]);
+    }
+    // only row g (c0, c1 of each n-tile) is a real query head; rows g + 8 are padding
+    float mx = -INFINITY;
+    float p[2][2];
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        const int j = j0 + tok0 + i * 8 + t4 * 2 + e;
+        bool ok = j < j_end;
+        if (ok) ok = bt[j / a.page] >= 0;
+        const float v = ok ? s[i][e] * sl2 : -INFINITY;
+        p[i][e] = v;
+        mx = fmaxf(mx, v);
+      }
+    }
+    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+    const float mn = fmaxf(m_run, mx);
+    const float m_use = (mn == -INFINITY) ? 0.0f : mn;
+    const float corr = (m_run == -INFINITY) ? 0.0f : exp2f(m_run - m_use);
+    m_run = mn;
+    float rs = 0.0f;
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        p[i][e] = exp2f(p[i][e] - m_use);
+        rs += p[i][e];
+      }
+    }
+    rs += __shfl_xor_sync(0xffffffffu, rs, 1);
+    rs += __shfl_xor_sync(0xffffffffu, rs, 2);
+    l_run = l_run * corr + rs;
+#pragma unroll
+    for (int i = 0; i < D / 8; ++i) {
+      o[i][0] *= corr;
+      o[i][1] *= corr;
+    }
+    uint32_t pa[4];
+    pa[0] = pack_bf16(p[0][0], p[0][1]);
+    pa[1] = 0;  // rows g + 8
+    pa[2] = pack_bf16(p[1][0], p[1][1]);
+    pa[3] = 0;
+#pragma unroll
+    for (int dp = 0; dp < D / 16; ++dp) {
+      uint32_t vb[4];
+      const int tok = tok0 + (lane & 7) + 8 * ((lane >> 3) & 1);
+      const int d = dp * 16 + 8 * (lane >> 4);
+      ldsm_x4_t(vb, smem_u32(Vs + tok * LDS + d));
+      mma_bf16(o[2 * dp], pa, vb[0], vb[1]);
+      mma_bf16(o[2 * dp + 1], pa, vb[2], vb[3]);
+    }
+  }
+  // merge the four warps (rows g < G only), reusing the tile buffers
+  __syncthreads();
+  float* s_m = reinterpret_cast<float*>(Ks);          // [NWARP][G]
+  float* s_l = s_m + NWARP * G;                        // [NWARP][G]
+  float* s_acc = s_l + NWARP * G;                      // [NWARP][G][D]
+  if (g < G) {
+    if (t4 == 0) {
+      s_m[warp * G + g] = m_run;
+      s_l[warp * G + g] = l_run;
+    }
+#pragma unroll
+    for (int i = 0; i < D / 8; ++i) {
+      s_acc[(warp * G + g) * D + i * 8 + t4 * 2] = o[i][0];
+      s_acc[(warp * G + g) * D + i * 8 + t4 * 2 + 1] = o[i][1];
+    }
+  }
+  __syncthreads();
+  for (int idx = tid; idx < G * D; idx += 128) {
+    const int gg = idx / D, d = idx % D;
+    float mm = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < NWARP; ++w) mm = fmaxf(mm, s_m[w * G + gg]);
+    float ll = 0.0f, oo = 0.0f;
+#pragma unroll
+    for (int w = 0; w < NWARP; ++w) {
+      const float ms = s_m[w * G + gg];
+      const float c = (ms == -INFINITY) ? 0.0f : exp2f(ms - mm);
+      ll += s_l[w * G + gg] * c;
+      oo += s_acc[(w * G + gg) * D + d] * c;
+    }
+    const int hq = kvh * G + gg;
+    if (a.nsplit == 1) {
+      a.out[((size_t)b * a.Hq + hq) * D + d] = __float2bfloat16_rn(ll > 0.0f ? oo / ll : 0.0f);
+    } else {
+      // partial format shared with the SIMT kernel: natural-log domain maximum
+      const size_t pidx = ((size_t)b * a.Hq + hq) * a.nsplit + split;
+      a.part_o[pidx * D + d] = oo;
+      if (d == 0) {
+        a.part_ml[pidx * 2] = (mm == -INFINITY) ? -INFINITY : mm * 0.6931471805599453f;
+        a.part_ml[pidx * 2 + 1] = ll;
+      }
+    }
+  }
+  if (a.nsplit == 1 || a.counters == nullptr) return;
+  __shared__ int s_last2;
+  __threadfence();
+  __syncthreads();
+  if (tid == 0) {
+    const int old = atomicAdd(&a.counters[b * a.Hkv + kvh], 1);
+    s_last2 = (old == a.nsplit - 1);
+    if (s_last2) a.counters[b * a.Hkv + kvh] = 0;
+  }
+  __syncthreads();
+  if (!s_last2) return;
+  __threadfence();
+  __shared__ float s_coef2[G][32];
+  __shared__ float s_inv2[G];
+  const int ns = a.nsplit;
+  for (int gg = warp; gg < G; gg += NWARP) {
+    const size_t bh = (size_t)b * a.Hq + kvh * G + gg;
+    const float ms = lane < ns ? __ldcg(&a.part_ml[(bh * ns + lane) * 2]) : -INFINITY;
+    const float ls = lane < ns ? __ldcg(&a.part_ml[(bh * ns + lane) * 2 + 1]) : 0.0f;
+    const float mm = warp_max(ms);
+    const float c = (ms == -INFINITY) ? 0.0f : __expf(ms - mm);
+    const float ll = warp_sum(ls * c);
+    s_coef2[gg][lane] = c;
+    if (lane == 0) s_inv2[gg] = ll > 0.0f ? 1.0f / ll : 0.0f;
+  }
+  __syncthreads();
+  for (int idx = tid; idx < G * D; idx += 128) {
+    const int gg = idx / D, d = idx % D;
+    const size_t bh = (size_t)b * a.Hq + kvh * G + gg;
+    const float* po = a.part_o + bh * ns * D + d;
+    float oo = 0.0f;
+#pragma unroll 8
+    for (int sidx = 0; sidx < ns; ++sidx) oo += __ldcg(po + (size_t)sidx * D) * s_coef2[gg][sidx];
+    a.out[bh * D + d] = __float2bfloat16_rn(oo * s_inv2[gg]);
+  }
+}
+
 template <int HD, int HD_REAL, int MODE>
 int launch_flash(const FlashArgs& a, int max_q_tiles, int S, cudaStream_t stream, bool pdl) {
   const size_t smem = (size_t)(64 + 2 * 64) * (HD + 8) * sizeof(bf16);
@@ -555,9 +785,31 @@ int dispatch_flash(const FlashArgs& a, int hd, int max_q_tiles, int S, cudaStrea
   return -2;
 }
 
+template <int D, int G, bool KV8>
+int launch_decode_mma(const DecodeArgs& a, int B, cudaStream_t stream, bool pdl) {
+  const size_t smem = (size_t)(16 + 2 * 64) * (D + 8) * sizeof(bf16);
+  static bool configured = false;
+  if (!configured && smem > 48 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(paged_decode_mma_kernel<D, G, KV8>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+    configured = true;
+  }
+  return (int)prism_launch(paged_decode_mma_kernel<D, G, KV8>, dim3(B, a.Hkv, a.nsplit), dim3(128), smem, stream, pdl, a);
+}
+
+// use_mma: tensor-core kernel (larger batches); otherwise the SIMT kernel (lowest latency at batch 1)
 template <int D, bool KV8>
-int dispatch_decode(const DecodeArgs& a, int B, cudaStream_t stream, bool pdl) {
+int dispatch_decode(const DecodeArgs& a, int B, cudaStream_t stream, bool pdl, bool use_mma) {
   dim3 grid(B, a.Hkv, a.nsplit), block(128);
+  if (use_mma) {
+    switch (a.Hq / a.Hkv) {
+      case 1: return launch_decode_mma<D, 1, KV8>(a, B, stream, pdl);
+      case 2: return launch_decode_mma<D, 2, KV8>(a, B, stream, pdl);
+      case 4: return launch_decode_mma<D, 4, KV8>(a, B, stream, pdl);
+      case 8: return launch_decode_mma<D, 8, KV8>(a, B, stream, pdl);
+    }
+    return -3;
+  }
   switch (a.Hq / a.Hkv) {
     case 1: return (int)prism_launch(paged_decode_kernel<D, 1, KV8>, grid, block, 0, stream, pdl, a);
     case 2: return (int)prism_launch(paged_decode_kernel<D, 2, KV8>, grid, block, 0, stream, pdl, a);
@@ -574,7 +826,8 @@ int dispatch_decode(const DecodeArgs& a, int B, cudaStream_t stream, bool pdl) {
 PRISM_API int prism_paged_decode(const void* q, const void* k_cache, const void* v_cache, const void* k_scale,
                                  const void* v_scale, const void* block_tables, const void* context_lens, void* part_o,
                                  void* part_ml, void* out, void* counters, int B, int Hq, int Hkv, int D, int page,
-                                 int max_blocks, int nsplit, int kv_mode, float scale, void* stream, int pdl) {
+                                 int max_blocks, int nsplit, int kv_mode, float scale, int use_mma, void* stream,
+                                 int pdl) {
   if (B <= 0) return 0;
   if (Hq % Hkv) return -1;
   DecodeArgs a;
@@ -597,8 +850,9 @@ PRISM_API int prism_paged_decode(const void* q, const void* k_cache, const void*
   a.scale = scale;
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   int rc;
-  if (D == 128) rc = kv_mode ? dispatch_decode<128, true>(a, B, s, pdl != 0) : dispatch_decode<128, false>(a, B, s, pdl != 0);
-  else if (D == 64) rc = kv_mode ? dispatch_decode<64, true>(a, B, s, pdl != 0) : dispatch_decode<64, false>(a, B, s, pdl != 0);
+  const bool mma = use_mma != 0;
+  if (D == 128) rc = kv_mode ? dispatch_decode<128, true>(a, B, s, pdl != 0, mma) : dispatch_decode<128, false>(a, B, s, pdl != 0, mma);
+  else if (D == 64) rc = kv_mode ? dispatch_decode<64, true>(a, B, s, pdl != 0, mma) : dispatch_decode<64, false>(a, B, s, pdl != 0, mma);
   else return -2;
   if (rc) return rc;
   if (a.nsplit > 1 && a.counters == nullptr) {
@@ -727,7 +981,7 @@ PRISM_API int prism_paged_decode_noalloc(const void* q, const void* k_cache, con
   // (empty splits store max = -inf, sum = 0), so nothing has to be cleared between calls.
   const int rc = prism_paged_decode(q, k_cache, v_cache, k_scale, v_scale, block_tables, context_lens,
                                     nsplit > 1 ? part_o : nullptr, nsplit > 1 ? part_ml : nullptr, out, nullptr, B, Hq, Hkv,
-                                    D, page, max_blocks, nsplit, kv_mode, scale, stream, 0);
+                                    D, page, max_blocks, nsplit, kv_mode, scale, 0, stream, 0);
   if (rc != 0) return noalloc_fail(rc, "prism_paged_decode_noalloc: kernel launch failed");
   return 0;
 }

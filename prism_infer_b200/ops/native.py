@@ -37,7 +37,7 @@ _SIGNATURES = {
     "prism_indexed_add": "pppiipi",
     "prism_pos_embed_add": "ppppiipi",
     "prism_vit_rope": "pppiiipi",
-    "prism_paged_decode": "pppppppppppiiiiiiiifpi",
+    "prism_paged_decode": "pppppppppppiiiiiiiifipi",
     "prism_flash_attention": "plplppplppppppiiiiiiiiifpi",
     "prism_kv_page_copy": "ppllippllpppiiiip",
     "prism_kv_compact": "pliplppppiiiip",

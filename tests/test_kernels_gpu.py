@@ -200,7 +200,8 @@ def _fill_cache(mode, L, blocks, Hkv, page, D, seed):
 @pytest.mark.parametrize("mode", [ops.KV_BF16, ops.KV_FP8, ops.KV_FP8_SCALED])
 @pytest.mark.parametrize("D,Hq,Hkv,page", [(128, 32, 8, 256), (128, 4, 1, 256), (64, 4, 2, 16)])
 @pytest.mark.parametrize("nsplit", [1, 4, 0])
-def test_paged_decode(cuda_device, mode, D, Hq, Hkv, page, nsplit):
+@pytest.mark.parametrize("use_mma", [False, True])
+def test_paged_decode(cuda_device, mode, D, Hq, Hkv, page, nsplit, use_mma):
     B, blocks = 5, 24
     cg, cc = _fill_cache(mode, 1, blocks, Hkv, page, D, seed=25)
     maxblk = 6
@@ -213,7 +214,7 @@ def test_paged_decode(cuda_device, mode, D, Hq, Hkv, page, nsplit):
         bt[b, :n] = perm[c:c + n].int()
         c += n
     q = rand_bf16(B, Hq, D, seed=27)
-    yg = ops.paged_decode_attention(q.cuda(), cg, 0, bt.cuda(), ctx.cuda(), nsplit=nsplit)
+    yg = ops.paged_decode_attention(q.cuda(), cg, 0, bt.cuda(), ctx.cuda(), nsplit=nsplit, use_mma=use_mma)
     yc = ops.paged_decode_attention(q.float(), cc, 0, bt, ctx)
     err = (yg.float().cpu() - yc).abs()
     assert err.max() < 2e-2 and err.mean() < 2e-3, (err.max(), err.mean())
