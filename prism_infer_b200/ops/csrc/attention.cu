@@ -579,42 +579,70 @@ __global__ void __launch_bounds__(128) paged_decode_mma_kernel(const DecodeArgs 
   float m_run = -INFINITY, l_run = 0.0f;  // row g (rows >= G are padding)
   const float sl2 = a.scale * 1.4426950408889634f;
 
-  for (int j0 = j_begin; j0 < j_end; j0 += BN) {
-    __syncthreads();
-    for (int i = tid; i < BN * CHUNKS; i += 128) {
-      const int r = i / CHUNKS, c = i % CHUNKS;
+  // Software pipeline: the global loads of tile i+1 are in flight (in registers) while
+  // tile i is scored; 16-byte loads, CPR chunks per token row.
+  constexpr int CPR = KV8 ? D / 16 : D / 8;      // 16-byte chunks per row
+  constexpr int NL = BN * CPR / 128;             // chunks per thread (K and V each)
+  __shared__ unsigned char s_valid[BN];
+  uint4 kreg[NL], vreg[NL];
+  float ksc[NL], vsc[NL];
+  auto prefetch = [&](int j0) {
+#pragma unroll
+    for (int u = 0; u < NL; ++u) {
+      const int idx = tid + u * 128;
+      const int r = idx / CPR, c = idx % CPR;
       const int j = j0 + r;
-      uint4 k4 = make_uint4(0, 0, 0, 0), v4 = make_uint4(0, 0, 0, 0);
+      kreg[u] = make_uint4(0, 0, 0, 0);
+      vreg[u] = make_uint4(0, 0, 0, 0);
+      ksc[u] = -1.0f;  // marks an absent row
+      vsc[u] = 1.0f;
       if (j < j_end) {
         const int blk = bt[j / a.page];
         if (blk >= 0) {
           const size_t row = ((size_t)blk * a.Hkv + kvh) * a.page + (j % a.page);
-          if (KV8) {
-            const uint2 k8 = __ldg(reinterpret_cast<const uint2*>(reinterpret_cast<const uint8_t*>(a.k_cache) + row * D + c * 8));
-            const uint2 v8 = __ldg(reinterpret_cast<const uint2*>(reinterpret_cast<const uint8_t*>(a.v_cache) + row * D + c * 8));
-            const float ks = a.k_scale ? __ldg(a.k_scale + row) : 1.0f;
-            const float vs = a.v_scale ? __ldg(a.v_scale + row) : 1.0f;
-            const unsigned short* kp = reinterpret_cast<const unsigned short*>(&k8);
-            const unsigned short* vp = reinterpret_cast<const unsigned short*>(&v8);
-            uint32_t* ko = reinterpret_cast<uint32_t*>(&k4);
-            uint32_t* vo = reinterpret_cast<uint32_t*>(&v4);
-#pragma unroll
-            for (int e = 0; e < 4; ++e) {
-              const float2 kk = fp8x2_to_float2(kp[e]);
-              const float2 vv = fp8x2_to_float2(vp[e]);
-              ko[e] = pack_bf16(kk.x * ks, kk.y * ks);
-              vo[e] = pack_bf16(vv.x * vs, vv.y * vs);
-            }
-          } else {
-            k4 = __ldg(reinterpret_cast<const uint4*>(reinterpret_cast<const bf16*>(a.k_cache) + row * D + c * 8));
-            v4 = __ldg(reinterpret_cast<const uint4*>(reinterpret_cast<const bf16*>(a.v_cache) + row * D + c * 8));
-          }
+          const size_t off = row * D * (KV8 ? 1 : 2) + (size_t)c * 16;
+          kreg[u] = __ldg(reinterpret_cast<const uint4*>(reinterpret_cast<const uint8_t*>(a.k_cache) + off));
+          vreg[u] = __ldg(reinterpret_cast<const uint4*>(reinterpret_cast<const uint8_t*>(a.v_cache) + off));
+          ksc[u] = (KV8 && a.k_scale) ? __ldg(a.k_scale + row) : 1.0f;
+          vsc[u] = (KV8 && a.v_scale) ? __ldg(a.v_scale + row) : 1.0f;
         }
       }
-      *reinterpret_cast<uint4*>(Ks + r * LDS + c * 8) = k4;
-      *reinterpret_cast<uint4*>(Vs + r * LDS + c * 8) = v4;
+    }
+  };
+  if (j_begin < j_end) prefetch(j_begin);
+  for (int j0 = j_begin; j0 < j_end; j0 += BN) {
+    __syncthreads();
+#pragma unroll
+    for (int u = 0; u < NL; ++u) {
+      const int idx = tid + u * 128;
+      const int r = idx / CPR, c = idx % CPR;
+      const bool present = ksc[u] >= 0.0f;
+      if (c == 0) s_valid[r] = present ? 1 : 0;
+      if (KV8) {
+        const unsigned short* kp = reinterpret_cast<const unsigned short*>(&kreg[u]);
+        const unsigned short* vp = reinterpret_cast<const unsigned short*>(&vreg[u]);
+        uint4 ko[2], vo[2];
+        uint32_t* kw = reinterpret_cast<uint32_t*>(ko);
+        uint32_t* vw = reinterpret_cast<uint32_t*>(vo);
+        const float ks = present ? ksc[u] : 0.0f, vs = vsc[u];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+          const float2 kk = fp8x2_to_float2(kp[e]);
+          const float2 vv = fp8x2_to_float2(vp[e]);
+          kw[e] = pack_bf16(kk.x * ks, kk.y * ks);
+          vw[e] = pack_bf16(vv.x * vs, vv.y * vs);
+        }
+        *reinterpret_cast<uint4*>(Ks + r * LDS + c * 16) = ko[0];
+        *reinterpret_cast<uint4*>(Ks + r * LDS + c * 16 + 8) = ko[1];
+        *reinterpret_cast<uint4*>(Vs + r * LDS + c * 16) = vo[0];
+        *reinterpret_cast<uint4*>(Vs + r * LDS + c * 16 + 8) = vo[1];
+      } else {
+        *reinterpret_cast<uint4*>(Ks + r * LDS + c * 8) = kreg[u];
+        *reinterpret_cast<uint4*>(Vs + r * LDS + c * 8) = vreg[u];
+      }
     }
     __syncthreads();
+    if (j0 + BN < j_end) prefetch(j0 + BN);
     const int tok0 = warp * 16;  // this warp's 16 tokens of the tile
     if (j0 + tok0 >= j_end) continue;
     float s[2][4];
@@ -636,9 +664,7 @@ __global__ void __launch_bounds__(128) paged_decode_mma_kernel(const DecodeArgs 
     for (int i = 0; i < 2; ++i) {
 #pragma unroll
       for (int e = 0; e < 2; ++e) {
-        const int j = j0 + tok0 + i * 8 + t4 * 2 + e;
-        bool ok = j < j_end;
-        if (ok) ok = bt[j / a.page] >= 0;
+        const bool ok = s_valid[tok0 + i * 8 + t4 * 2 + e] != 0;
         const float v = ok ? s[i][e] * sl2 : -INFINITY;
         p[i][e] = v;
         mx = fmaxf(mx, v);

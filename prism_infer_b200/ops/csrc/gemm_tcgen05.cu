@@ -43,6 +43,7 @@ struct GemmArgs {
   int kb_per_split;  // k-blocks handled by one blockIdx.z
   int w2_row_off;    // dual: first row of the second weight matrix inside the same tensor map
   int stages;
+  int tokens_fastest;  // grid rasterisation, see the kernel
   int out_f32;       // 1: fp32 partial output, one slab per split
   int act;           // 0 none, 1 gelu(tanh), 2 gelu(erf)
   long long ldo;     // output row stride (elements)
@@ -110,10 +111,11 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  // token tiles vary fastest: the CTAs that share a weight tile run together, so each weight
-  // tile leaves DRAM once and the (much smaller) activation matrix stays in L2
-  const int m0 = blockIdx.y * BM;
-  const int n0 = blockIdx.x * BN;
+  // Rasterisation.  When the weight matrix does not fit the 126 MB L2, token tiles vary
+  // fastest so the CTAs that share a weight tile run together and it leaves DRAM once;
+  // otherwise feature tiles vary fastest (measured faster while everything is L2-resident).
+  const int m0 = (a.tokens_fastest ? blockIdx.y : blockIdx.x) * BM;
+  const int n0 = (a.tokens_fastest ? blockIdx.x : blockIdx.y) * BN;
   const int split = blockIdx.z;
   const int kb_begin = split * a.kb_per_split;
   const int kb_end = min(a.kb_total, kb_begin + a.kb_per_split);
@@ -228,56 +230,99 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
         named_bar_sync(1, 128);
       }
       const bool writer = (blockIdx.x | blockIdx.y | blockIdx.z) == 0 && a.nx_residual_out != nullptr;
-      // pass 1: added = bf16(residual + bf16(sum of slabs)), kept in shared memory; rms per row
+      // pass 1, per token: every thread owns up to NX_IT 4-element groups of the row.  All
+      // global loads of a token (slabs, residual, norm weight) are issued up front, so the
+      // whole row costs about one memory round trip; the normalised row ends in shared memory.
+      constexpr int NX_IT = 8;  // covers K <= 128 threads * 4 * 8 = 4096
+      uint2 wreg[NX_IT];
+#pragma unroll
+      for (int u = 0; u < NX_IT; ++u) {
+        const int i = (et + u * 128) * 4;
+        wreg[u] = make_uint2(0, 0);
+        if (i < K) wreg[u] = __ldg(reinterpret_cast<const uint2*>(a.nx_weight + i));
+      }
       for (int t = 0; t < a.T; ++t) {
         const size_t base = (size_t)t * K;
-        float ss = 0.0f;
-        for (int i = et * 4; i < K; i += 128 * 4) {
-          float d0, d1, d2, d3;
-          if (a.nx_P > 0) {
-            float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-            const float* p0 = a.nx_partials + base + i;
-#pragma unroll 8
-            for (int p = 0; p < a.nx_P; ++p) {
-              const float4 v = __ldcg(reinterpret_cast<const float4*>(p0 + (size_t)p * a.nx_slab_stride));
-              acc.x += v.x;
-              acc.y += v.y;
-              acc.z += v.z;
-              acc.w += v.w;
+        float4 acc[NX_IT];
+        uint2 rres[NX_IT];
+#pragma unroll
+        for (int u = 0; u < NX_IT; ++u) {
+          const int i = (et + u * 128) * 4;
+          acc[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+          rres[u] = make_uint2(0, 0);
+          if (i < K) {
+            if (a.nx_residual_in != nullptr) rres[u] = __ldcg(reinterpret_cast<const uint2*>(a.nx_residual_in + base + i));
+            if (a.nx_P == 0) {
+              const uint2 raw = __ldcg(reinterpret_cast<const uint2*>(a.nx_x + base + i));
+              const __nv_bfloat162* v = reinterpret_cast<const __nv_bfloat162*>(&raw);
+              acc[u] = make_float4(__bfloat162float(v[0].x), __bfloat162float(v[0].y), __bfloat162float(v[1].x),
+                                   __bfloat162float(v[1].y));
             }
-            d0 = bf16_round(acc.x);
-            d1 = bf16_round(acc.y);
-            d2 = bf16_round(acc.z);
-            d3 = bf16_round(acc.w);
-          } else {
-            const uint2 raw = *reinterpret_cast<const uint2*>(a.nx_x + base + i);
-            const __nv_bfloat162* v = reinterpret_cast<const __nv_bfloat162*>(&raw);
-            d0 = __bfloat162float(v[0].x);
-            d1 = __bfloat162float(v[0].y);
-            d2 = __bfloat162float(v[1].x);
-            d3 = __bfloat162float(v[1].y);
           }
-          if (a.nx_residual_in != nullptr) {
-            const uint2 raw = *reinterpret_cast<const uint2*>(a.nx_residual_in + base + i);
-            const __nv_bfloat162* r = reinterpret_cast<const __nv_bfloat162*>(&raw);
-            d0 = bf16_round(__bfloat162float(r[0].x) + d0);
-            d1 = bf16_round(__bfloat162float(r[0].y) + d1);
-            d2 = bf16_round(__bfloat162float(r[1].x) + d2);
-            d3 = bf16_round(__bfloat162float(r[1].y) + d3);
+        }
+        for (int p = 0; p < a.nx_P; ++p) {
+          const float* p0 = a.nx_partials + (size_t)p * a.nx_slab_stride + base;
+#pragma unroll
+          for (int u = 0; u < NX_IT; ++u) {
+            const int i = (et + u * 128) * 4;
+            if (i < K) {
+              const float4 v = __ldcg(reinterpret_cast<const float4*>(p0 + i));
+              acc[u].x += v.x;
+              acc[u].y += v.y;
+              acc[u].z += v.z;
+              acc[u].w += v.w;
+            }
           }
-          uint2 o;
-          *reinterpret_cast<__nv_bfloat162*>(&o.x) = __floats2bfloat162_rn(d0, d1);
-          *reinterpret_cast<__nv_bfloat162*>(&o.y) = __floats2bfloat162_rn(d2, d3);
-          *reinterpret_cast<uint2*>(nx_added + base + i) = o;
-          if (writer) *reinterpret_cast<uint2*>(a.nx_residual_out + base + i) = o;
-          ss += d0 * d0 + d1 * d1 + d2 * d2 + d3 * d3;
+        }
+        float ss = 0.0f;
+#pragma unroll
+        for (int u = 0; u < NX_IT; ++u) {
+          const int i = (et + u * 128) * 4;
+          if (i < K) {
+            float d0 = acc[u].x, d1 = acc[u].y, d2 = acc[u].z, d3 = acc[u].w;
+            if (a.nx_P > 0) {
+              d0 = bf16_round(d0);
+              d1 = bf16_round(d1);
+              d2 = bf16_round(d2);
+              d3 = bf16_round(d3);
+            }
+            if (a.nx_residual_in != nullptr) {
+              const __nv_bfloat162* r = reinterpret_cast<const __nv_bfloat162*>(&rres[u]);
+              d0 = bf16_round(__bfloat162float(r[0].x) + d0);
+              d1 = bf16_round(__bfloat162float(r[0].y) + d1);
+              d2 = bf16_round(__bfloat162float(r[1].x) + d2);
+              d3 = bf16_round(__bfloat162float(r[1].y) + d3);
+            }
+            acc[u] = make_float4(d0, d1, d2, d3);
+            if (writer) {
+              uint2 o;
+              *reinterpret_cast<__nv_bfloat162*>(&o.x) = __floats2bfloat162_rn(d0, d1);
+              *reinterpret_cast<__nv_bfloat162*>(&o.y) = __floats2bfloat162_rn(d2, d3);
+              *reinterpret_cast<uint2*>(a.nx_residual_out + base + i) = o;
+            }
+            ss += d0 * d0 + d1 * d1 + d2 * d2 + d3 * d3;
+          }
         }
         ss = warp_sum(ss);
         if (lane == 0) nx_red[q] = ss;
         named_bar_sync(1, 128);
-        if (et == 0) nx_rstd[t] = rsqrtf((nx_red[0] + nx_red[1] + nx_red[2] + nx_red[3]) / (float)K + a.nx_eps);
-        named_bar_sync(1, 128);
+        const float rstd = rsqrtf((nx_red[0] + nx_red[1] + nx_red[2] + nx_red[3]) / (float)K + a.nx_eps);
+        named_bar_sync(1, 128);  // nx_red is reused by the next token
+#pragma unroll
+        for (int u = 0; u < NX_IT; ++u) {
+          const int i = (et + u * 128) * 4;
+          if (i < K) {
+            const __nv_bfloat162* w2 = reinterpret_cast<const __nv_bfloat162*>(&wreg[u]);
+            uint2 o;
+            *reinterpret_cast<__nv_bfloat162*>(&o.x) = __floats2bfloat162_rn(
+                bf16_round(acc[u].x * rstd) * __bfloat162float(w2[0].x), bf16_round(acc[u].y * rstd) * __bfloat162float(w2[0].y));
+            *reinterpret_cast<__nv_bfloat162*>(&o.y) = __floats2bfloat162_rn(
+                bf16_round(acc[u].z * rstd) * __bfloat162float(w2[1].x), bf16_round(acc[u].w * rstd) * __bfloat162float(w2[1].y));
+            *reinterpret_cast<uint2*>(nx_added + base + i) = o;  // now holds the normalised row
+          }
+        }
       }
+      named_bar_sync(1, 128);
       // pass 2: each warp writes the activation tiles of its k-blocks (128-byte swizzle, rows
       // beyond T are zero) straight into the operand ring and arrives on the stage barrier
       const int ew = warp - 2;
@@ -293,21 +338,7 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
         for (int j = 0; j < BN / 4; ++j) {
           const int row = (lane >> 3) + 4 * j;
           uint4 val = make_uint4(0, 0, 0, 0);
-          if (row < a.T && col < K) {
-            const uint4 raw = *reinterpret_cast<const uint4*>(nx_added + (size_t)row * K + col);
-            const uint4 wraw = *reinterpret_cast<const uint4*>(a.nx_weight + col);
-            const __nv_bfloat162* x2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
-            const __nv_bfloat162* w2 = reinterpret_cast<const __nv_bfloat162*>(&wraw);
-            const float r = nx_rstd[row];
-            uint32_t* o = reinterpret_cast<uint32_t*>(&val);
-#pragma unroll
-            for (int e = 0; e < 4; ++e) {
-              const float lo = bf16_round(__bfloat162float(x2[e].x) * r) * __bfloat162float(w2[e].x);
-              const float hi = bf16_round(__bfloat162float(x2[e].y) * r) * __bfloat162float(w2[e].y);
-              __nv_bfloat162 pk = __floats2bfloat162_rn(lo, hi);
-              o[e] = *reinterpret_cast<uint32_t*>(&pk);
-            }
-          }
+          if (row < a.T && col < K) val = *reinterpret_cast<const uint4*>(nx_added + (size_t)row * K + col);
           *reinterpret_cast<uint4*>(xt + (row >> 3) * 1024 + (row & 7) * 128 + ((chunk ^ (row & 7)) << 4)) = val;
         }
         fence_proxy_async();
@@ -477,7 +508,8 @@ int launch_gemm(const CUtensorMap& tw, const CUtensorMap& tx, GemmArgs& a, int m
     if (e != cudaSuccess) return (int)e;
     configured_smem = SMEM_LIMIT;
   }
-  dim3 grid((a.T + BN - 1) / BN, m_tiles, splits);
+  const int n_tiles = (a.T + BN - 1) / BN;
+  dim3 grid = a.tokens_fastest ? dim3(n_tiles, m_tiles, splits) : dim3(m_tiles, n_tiles, splits);
   cudaError_t e = prism_launch(gemm_wx_kernel<BN, DUAL, NORMX>, grid, dim3(GEMM_THREADS), smem, stream, pdl, tw, tx, a);
   return (int)e;
 }
@@ -544,6 +576,7 @@ static int gemm_wx_impl(const void* W, const void* X, void* out, int M, int T, i
   splits = (a.kb_total + a.kb_per_split - 1) / a.kb_per_split;  // no empty split
   a.w2_row_off = w2_row_off;
   a.stages = 0;
+  a.tokens_fastest = ((long long)w_rows_total * K * 2 > (100ll << 20) || (M + BM - 1) / BM > 65535) ? 1 : 0;
   a.out_f32 = out_f32;
   a.act = act;
   a.ldo = ldo;
@@ -589,7 +622,7 @@ static int gemm_wx_impl(const void* W, const void* X, void* out, int M, int T, i
   a.nx_n_wait = 0;
   a.nx_wait_point = 0;
   if (norm != nullptr) {
-    if (T > NORMX_T || (K % 64) != 0) return -30;
+    if (T > NORMX_T || (K % 64) != 0 || K > 4096) return -30;
     a.nx_partials = norm->partials;
     a.nx_slab_stride = norm->slab_stride;
     a.nx_P = norm->P;
