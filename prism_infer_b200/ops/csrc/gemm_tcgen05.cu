@@ -354,48 +354,94 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
       const uint32_t t_lane = tmem_base + ((uint32_t)(q * 32) << 16);
       float* out_f = reinterpret_cast<float*>(a.out) + (size_t)split * a.split_stride;
       __nv_bfloat16* out_b = reinterpret_cast<__nv_bfloat16*>(a.out);
-      for (int c0 = 0; c0 < BN; c0 += 16) {
-        if (n0 + c0 >= a.T) break;
+      // One compact store loop per output form; the form is chosen once, outside the column
+      // loops, so the instruction stream of a tile touches only the code it needs.
+      enum { EPI_BF16_PLAIN, EPI_BF16_FULL, EPI_F32, EPI_PUSH_F32, EPI_PUSH_ROWS, EPI_DUAL };
+      int mode;
+      if (DUAL) mode = EPI_DUAL;
+      else if (a.n_peers > 0) mode = a.push_rows ? EPI_PUSH_ROWS : EPI_PUSH_F32;
+      else if (a.out_f32) mode = EPI_F32;
+      else mode = (a.bias == nullptr && a.act == 0 && a.residual == nullptr) ? EPI_BF16_PLAIN : EPI_BF16_FULL;
+      const int n_valid = min(BN, a.T - n0);
+      for (int c0 = 0; c0 < n_valid; c0 += 16) {
         uint32_t r[16];
         uint32_t r2[16];
         tmem_ld16(t_lane + c0, r);
         if (DUAL) tmem_ld16(t_lane + BN + c0, r2);
         tmem_ld_wait();
-        if (m_ok) {
+        if (!m_ok) continue;
+        const int cols = min(16, n_valid - c0);
+        const size_t row0 = (size_t)(n0 + c0);
+        switch (mode) {
+          case EPI_BF16_PLAIN: {
+            __nv_bfloat16* dst = out_b + row0 * a.ldo + m;
 #pragma unroll
-          for (int j = 0; j < 16; ++j) {
-            const int n = n0 + c0 + j;
-            if (n < a.T) {
-              float v = __uint_as_float(r[j]);
-              if (DUAL) {
-                // rounding points follow the eager bf16 graph: silu(gate) -> bf16, * up -> bf16
-                const float g = bf16_round(__uint_as_float(r[j]));
-                const float u = bf16_round(__uint_as_float(r2[j]));
-                v = bf16_round(silu(g)) * u;
-                out_b[(size_t)n * a.ldo + m] = __float2bfloat16_rn(v);
-              } else if (a.n_peers > 0 && a.push_rows) {
-                // fused GEMM -> all-gather: this rank's rows land in every rank's copy
-                v += bias_v;
+            for (int j = 0; j < 16; ++j)
+              if (j < cols) dst[(size_t)j * a.ldo] = __float2bfloat16_rn(__uint_as_float(r[j]));
+            break;
+          }
+          case EPI_BF16_FULL: {
+            __nv_bfloat16* dst = out_b + row0 * a.ldo + m;
+            const __nv_bfloat16* rsd = a.residual ? a.residual + row0 * a.ldr + m : nullptr;
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              if (j < cols) {
+                float v = __uint_as_float(r[j]) + bias_v;
                 if (a.act == 1) v = gelu_tanh(v);
                 else if (a.act == 2) v = gelu_erf(v);
-                const __nv_bfloat16 bv = __float2bfloat16_rn(v);
-                const size_t off = (size_t)(a.row_base + n) * a.ldo + m;
-#pragma unroll 8
-                for (int p = 0; p < a.n_peers; ++p) reinterpret_cast<__nv_bfloat16*>(a.peer_out[p])[off] = bv;
-              } else if (a.n_peers > 0) {
-                const size_t off = (size_t)(a.my_rank * (int)gridDim.z + split) * a.split_stride + (size_t)n * a.ldo + m;
-#pragma unroll 8
-                for (int p = 0; p < a.n_peers; ++p) a.peer_out[p][off] = v;
-              } else if (a.out_f32) {
-                out_f[(size_t)n * a.ldo + m] = v;
-              } else {
-                v += bias_v;
-                if (a.act == 1) v = gelu_tanh(v);
-                else if (a.act == 2) v = gelu_erf(v);
-                if (a.residual != nullptr) v = bf16_round(v) + __bfloat162float(a.residual[(size_t)n * a.ldr + m]);
-                out_b[(size_t)n * a.ldo + m] = __float2bfloat16_rn(v);
+                if (rsd != nullptr) v = bf16_round(v) + __bfloat162float(rsd[(size_t)j * a.ldr]);
+                dst[(size_t)j * a.ldo] = __float2bfloat16_rn(v);
               }
             }
+            break;
+          }
+          case EPI_F32: {
+            float* dst = out_f + row0 * a.ldo + m;
+#pragma unroll
+            for (int j = 0; j < 16; ++j)
+              if (j < cols) dst[(size_t)j * a.ldo] = __uint_as_float(r[j]);
+            break;
+          }
+          case EPI_PUSH_F32: {
+            const size_t off = (size_t)(a.my_rank * (int)gridDim.z + split) * a.split_stride + row0 * a.ldo + m;
+            for (int p = 0; p < a.n_peers; ++p) {
+              float* dst = a.peer_out[p] + off;
+#pragma unroll
+              for (int j = 0; j < 16; ++j)
+                if (j < cols) dst[(size_t)j * a.ldo] = __uint_as_float(r[j]);
+            }
+            break;
+          }
+          case EPI_PUSH_ROWS: {
+            // fused GEMM -> all-gather: this rank's rows land in every rank's copy
+            uint32_t packed[16];
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              float v = __uint_as_float(r[j]) + bias_v;
+              if (a.act == 1) v = gelu_tanh(v);
+              else if (a.act == 2) v = gelu_erf(v);
+              packed[j] = (uint32_t)__bfloat16_as_ushort(__float2bfloat16_rn(v));
+            }
+            const size_t off = (size_t)(a.row_base + row0) * a.ldo + m;
+            for (int p = 0; p < a.n_peers; ++p) {
+              unsigned short* dst = reinterpret_cast<unsigned short*>(a.peer_out[p]) + off;
+#pragma unroll
+              for (int j = 0; j < 16; ++j)
+                if (j < cols) dst[(size_t)j * a.ldo] = (unsigned short)packed[j];
+            }
+            break;
+          }
+          default: {  // EPI_DUAL: silu(gate) -> bf16, * up -> bf16 (rounding points of the eager graph)
+            __nv_bfloat16* dst = out_b + row0 * a.ldo + m;
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              if (j < cols) {
+                const float g = bf16_round(__uint_as_float(r[j]));
+                const float u = bf16_round(__uint_as_float(r2[j]));
+                dst[(size_t)j * a.ldo] = __float2bfloat16_rn(bf16_round(silu(g)) * u);
+              }
+            }
+            break;
           }
         }
       }
