@@ -84,14 +84,14 @@ class ClockSampler:
 
 
 def run_reference(args) -> None:
-    ref_dir = os.path.join(ROOT, "baseline", "_ref")
-    why = None
-    if not os.path.isdir(os.path.join(ref_dir, "prism_infer")):
-        why = "reference is not installed under baseline/_ref"
-    else:
-        why = ("reference LLM() needs a checkpoint directory with Hugging Face tokenizer and processor files and "
-               "transformers>=5.13; neither is available offline (image has transformers 5.5, no Qwen3-VL files)")
-    print(json.dumps({"impl": "reference", "unavailable": why}))
+    """The unmodified reference from baseline/_ref through its own public API."""
+    sys.path.insert(0, os.path.join(ROOT, "baseline"))
+    try:
+        import reference_arm
+    except Exception as exc:  # pragma: no cover
+        print(json.dumps({"impl": "reference", "unavailable": f"cannot import baseline/reference_arm.py: {exc}"}))
+        return
+    reference_arm.main(args)
 
 
 def main() -> None:
