@@ -54,14 +54,16 @@ def main() -> None:
     ap.add_argument("--groups", type=int, default=42)
     ap.add_argument("--questions", type=int, default=85)
     ap.add_argument("--pages", type=int, default=220)
+    ap.add_argument("--min-images", type=int, default=1)
+    ap.add_argument("--max-images", type=int, default=8)
     ap.add_argument("--image-size", type=int, default=448)
     ap.add_argument("--max-tokens", type=int, default=16)
     ap.add_argument("--seed", type=int, default=wsp.DEFAULT_SEED)
     ap.add_argument("--out", default="")
     args = ap.parse_args()
 
-    groups = wsp.synthetic_groups(args.groups, args.questions, seed=args.seed,
-                                  tokens_per_image=(args.image_size // 32) ** 2 + 2)
+    groups = wsp.synthetic_groups(args.groups, args.questions, seed=args.seed, min_images=args.min_images,
+                                  max_images=args.max_images, tokens_per_image=(args.image_size // 32) ** 2 + 2)
     plan = wsp.build_plan(groups, num_requests=args.requests, alpha=args.alpha, rate=args.rate, seed=args.seed,
                           page_budget=args.pages)
     llm = LLM(args.model, tensor_parallel_size=args.tp, max_model_len=8192, max_num_batched_tokens=8192, max_num_seqs=8,
@@ -94,7 +96,7 @@ def main() -> None:
         "engine": "prism_infer_b200", "model": args.model, "data": "synthetic",
         "hardware": {"gpus": args.tp},
         "config": {"variant": args.variant, "groups": args.groups, "questions": args.questions, "requests": args.requests,
-                   "rate_per_s": args.rate, "alpha": args.alpha, "pages": args.pages, "page_tokens": 256,
+                   "rate_per_s": args.rate, "alpha": args.alpha, "pages": args.pages, "page_tokens": 256, "images_per_group": [args.min_images, args.max_images],
                    "kv_budget_bytes": args.pages * llm.config.kv_bytes_per_page(), "working_set_pages": plan.working_set_pages,
                    "max_tokens": args.max_tokens, "seed": args.seed, "tp": args.tp},
         "results": {

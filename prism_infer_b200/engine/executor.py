@@ -43,6 +43,19 @@ class ModelExecutor:
                                      "uniform" if config.visual_pruning_strategy == "attention" else config.visual_pruning_strategy)
         self._have_visual: set[int] = set()
 
+    def hydrate_vision(self, plan: BatchPlan) -> int:
+        """Cooperative prefill quantum: push the plan's pending vision-tower work through the
+        runner now (page transfers included) and leave the language prefill to a later step,
+        so running decodes are not stalled behind vision + prefill in one piece (reference
+        ``engine/llm_engine.py:913-1017``).  Returns the number of sequences hydrated."""
+        if not plan.kv_transfers.empty:
+            self.runners.call("apply_kv_transfers", plan.kv_transfers)
+        inputs = self.preparer.prepare(plan, self._have_visual)
+        for job in inputs.vision_jobs:
+            self.runners.call("encode_for_sequence", job)
+            self._have_visual.add(job.seq_id)
+        return len(inputs.vision_jobs)
+
     def execute(self, plan: BatchPlan) -> ExecutionResult:
         t0 = time.perf_counter()
         if not plan.kv_transfers.empty:

@@ -216,6 +216,10 @@ class ModelRunner:
                 self._visual_cache_bytes += size
         return main, deep
 
+    def encode_for_sequence(self, job) -> None:
+        """Vision tower for one sequence, kept until its prefill consumes it."""
+        self._visual[job.seq_id] = self._encode(job)
+
     def hydrate_visual_embedding(self, job) -> None:
         """Run the vision tower ahead of scheduling and keep the result in the LRU cache."""
         self._encode(job)
