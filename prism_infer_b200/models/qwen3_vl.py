@@ -122,6 +122,10 @@ class TPComm:
             return None, ops.linear_partial(x, w, splits), None
         return ops.linear(x, w), None, None
 
+    def row_parallel_swiglu(self, gate_up_partials: torch.Tensor, w: torch.Tensor):
+        """``row_parallel(swiglu(gate_up_partials), w)`` with the SwiGLU inside the GEMM."""
+        return None, ops.linear_actx(gate_up_partials, w, ops.choose_splits(w.shape[0], w.shape[1], gate_up_partials.shape[1])), None
+
     def add_rmsnorm(self, weight, eps, dense, partials, ticket, residual, extra=None, extra_index=None):
         """``(normed, new_residual)`` from whatever ``row_parallel`` returned."""
         return ops.add_rmsnorm(weight, eps, x=dense, partials=partials, residual=residual, extra=extra,
@@ -430,7 +434,7 @@ class Qwen3VLModel:
         dense, partials, ticket = x, None, None
         n_deep = len(deepstack) if deepstack is not None else 0
         # at most four tokens on CUDA: residual add + RMSNorm run inside the next projection
-        fuse_norm = x.is_cuda and T <= ops.NORMX_MAX_TOKENS and n_deep == 0 and self.H % 64 == 0
+        fuse_norm = x.is_cuda and ops.NORMX_ENABLED and T <= ops.NORMX_MAX_TOKENS and n_deep == 0 and self.H % 64 == 0
         if fuse_norm:
             res_bufs = [torch.empty((T, self.H), dtype=torch.bfloat16, device=x.device) for _ in range(2)]
             flip = 0
@@ -452,10 +456,14 @@ class Qwen3VLModel:
                 if self.I // 128 < 96:
                     gu = ops.linear_normx(l.gate_up, l.post_norm, t.rms_norm_eps, T, residual=residual, residual_out=res_bufs[flip],
                                           splits=ops.choose_splits(2 * self.I, self.H, T), **src)
-                    act = ops.swiglu(partials=gu)
-                else:
-                    act = ops.linear_normx(l.gate_up, l.post_norm, t.rms_norm_eps, T, residual=residual,
-                                           residual_out=res_bufs[flip], dual=True, **src)
+                    residual, flip = res_bufs[flip], flip ^ 1
+                    if ops.ACTX_ENABLED:
+                        dense, partials, ticket = comm.row_parallel_swiglu(gu, l.down)
+                    else:
+                        dense, partials, ticket = comm.row_parallel(ops.swiglu(partials=gu), l.down)
+                    continue
+                act = ops.linear_normx(l.gate_up, l.post_norm, t.rms_norm_eps, T, residual=residual,
+                                       residual_out=res_bufs[flip], dual=True, **src)
                 residual, flip = res_bufs[flip], flip ^ 1
                 dense, partials, ticket = comm.row_parallel(act, l.down)
                 continue

@@ -154,6 +154,12 @@ def gate_up_swiglu(x: torch.Tensor, w_gate_up: torch.Tensor, out: Optional[torch
 
 
 NORMX_MAX_TOKENS = 4
+# tuning switches (read once at import): fused add+RMSNorm prologue, smallest batch that uses
+# the tensor-core decode-attention kernel
+import os as _os
+
+NORMX_ENABLED = _os.environ.get("PRISM_NORMX", "1") != "0"
+DECODE_MMA_MIN_BATCH = int(_os.environ.get("PRISM_DECODE_MMA_MIN_BATCH", "4"))
 
 
 def linear_normx(
@@ -198,6 +204,29 @@ def linear_normx(
     native.call("prism_gemm_wx_normx", _p(w), _p(out), M, T, K, w.stride(0), out.stride(1), M, 0, 0, eff, 1, out.stride(0),
                 partials_ptr, slab_stride, P, _p(x), _p(residual), _p(residual_out), _p(norm_weight), float(eps),
                 flags, n_wait, point, epoch, 0, _s(), _pdl())
+    return out
+
+
+ACTX_ENABLED = _os.environ.get("PRISM_ACTX", "1") != "0"
+
+
+def linear_actx(gate_up_partials: torch.Tensor, w: torch.Tensor, splits: int) -> torch.Tensor:
+    """Down projection with SwiGLU fused into its prologue (at most ``NORMX_MAX_TOKENS`` tokens).
+
+    ``gate_up_partials [P, T, 2I]`` are the fp32 split-K slabs of the packed gate/up
+    projection; the activation ``silu(sum gate) * sum up`` (bf16 roundings as in ``swiglu``) is
+    formed inside the GEMM.  Returns fp32 split-K slabs ``[S, T, M]`` of ``act @ w.T``.
+    """
+    P, T, I2 = gate_up_partials.shape
+    M, K = w.shape
+    assert I2 == 2 * K
+    if not w.is_cuda:
+        return linear_partial(swiglu(partials=gate_up_partials).to(w.dtype), w, splits)
+    assert T <= NORMX_MAX_TOKENS and gate_up_partials.stride(1) == I2
+    eff = effective_splits(K, splits)
+    out = torch.empty((eff, T, M), dtype=torch.float32, device=w.device)
+    native.call("prism_gemm_wx_actx", _p(w), _p(out), M, T, K, w.stride(0), M, eff, out.stride(0),
+                _p(gate_up_partials), gate_up_partials.stride(0), P, None, None, 0, 0, 0, None, None, _s(), _pdl())
     return out
 
 
@@ -556,7 +585,7 @@ def paged_decode_attention(
         _p(cache.v_scale(layer)), _p(block_tables), _p(context_lens), _p(part_o), _p(part_ml), _p(out),
         _p(_decode_counters(q.device, B * cache.num_kv_heads)) if nsplit > 1 else None,
         B, Hq, cache.num_kv_heads, D, cache.page, block_tables.shape[1], nsplit, cache.mode, scale,
-        1 if (use_mma if use_mma is not None else B >= 4) else 0, _s(), _pdl(),
+        1 if (use_mma if use_mma is not None else B >= DECODE_MMA_MIN_BATCH) else 0, _s(), _pdl(),
     )
     return out
 

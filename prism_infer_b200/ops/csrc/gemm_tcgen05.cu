@@ -78,6 +78,7 @@ struct GemmArgs {
   const unsigned long long* nx_wait_flags;  // tensor parallel: flags to wait for before reading the slabs
   int nx_n_wait;
   long long nx_wait_point;
+  int nx_mode;                       // 0: residual + RMSNorm;  1: SwiGLU of packed (gate | up) slabs [P][T][2K]
 };
 
 constexpr int NORMX_T = 4;
@@ -106,7 +107,7 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
   // NORMX scratch: pre-norm rows (bf16), reciprocal rms per row, reduction slots
   __nv_bfloat16* nx_added = reinterpret_cast<__nv_bfloat16*>(
       (reinterpret_cast<uintptr_t>(tmem_slot + 4) + 15) & ~uintptr_t(15));
-  float* nx_rstd = reinterpret_cast<float*>(nx_added + (NORMX ? NORMX_T * a.nx_K : 0));
+  float* nx_rstd = reinterpret_cast<float*>(nx_added + ((NORMX && a.nx_mode == 0) ? NORMX_T * a.nx_K : 0));
   float* nx_red = nx_rstd + NORMX_T;
 
   const int warp = threadIdx.x >> 5;
@@ -234,6 +235,7 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
       // global loads of a token (slabs, residual, norm weight) are issued up front, so the
       // whole row costs about one memory round trip; the normalised row ends in shared memory.
       constexpr int NX_IT = 8;  // covers K <= 128 threads * 4 * 8 = 4096
+      if (a.nx_mode == 0) {
       uint2 wreg[NX_IT];
 #pragma unroll
       for (int u = 0; u < NX_IT; ++u) {
@@ -323,6 +325,7 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
         }
       }
       named_bar_sync(1, 128);
+      }
       // pass 2: each warp writes the activation tiles of its k-blocks (128-byte swizzle, rows
       // beyond T are zero) straight into the operand ring and arrives on the stage barrier
       const int ew = warp - 2;
@@ -338,7 +341,36 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
         for (int j = 0; j < BN / 4; ++j) {
           const int row = (lane >> 3) + 4 * j;
           uint4 val = make_uint4(0, 0, 0, 0);
-          if (row < a.T && col < K) val = *reinterpret_cast<const uint4*>(nx_added + (size_t)row * K + col);
+          if (row < a.T && col < K) {
+            if (a.nx_mode == 0) {
+              val = *reinterpret_cast<const uint4*>(nx_added + (size_t)row * K + col);
+            } else {
+              // activation = bf16(bf16(silu(bf16(sum gate))) * bf16(sum up)) for 8 columns
+              float gsum[8], usum[8];
+#pragma unroll
+              for (int e = 0; e < 8; ++e) gsum[e] = usum[e] = 0.0f;
+              const float* p0 = a.nx_partials + (size_t)row * 2 * K + col;
+              for (int p = 0; p < a.nx_P; ++p) {
+                const float* pp = p0 + (size_t)p * a.nx_slab_stride;
+                const float4 g0 = __ldcg(reinterpret_cast<const float4*>(pp));
+                const float4 g1 = __ldcg(reinterpret_cast<const float4*>(pp + 4));
+                const float4 u0 = __ldcg(reinterpret_cast<const float4*>(pp + K));
+                const float4 u1 = __ldcg(reinterpret_cast<const float4*>(pp + K + 4));
+                gsum[0] += g0.x; gsum[1] += g0.y; gsum[2] += g0.z; gsum[3] += g0.w;
+                gsum[4] += g1.x; gsum[5] += g1.y; gsum[6] += g1.z; gsum[7] += g1.w;
+                usum[0] += u0.x; usum[1] += u0.y; usum[2] += u0.z; usum[3] += u0.w;
+                usum[4] += u1.x; usum[5] += u1.y; usum[6] += u1.z; usum[7] += u1.w;
+              }
+              uint32_t* o = reinterpret_cast<uint32_t*>(&val);
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                const float lo = bf16_round(silu(bf16_round(gsum[2 * e]))) * bf16_round(usum[2 * e]);
+                const float hi = bf16_round(silu(bf16_round(gsum[2 * e + 1]))) * bf16_round(usum[2 * e + 1]);
+                __nv_bfloat162 pk = __floats2bfloat162_rn(lo, hi);
+                o[e] = *reinterpret_cast<uint32_t*>(&pk);
+              }
+            }
+          }
           *reinterpret_cast<uint4*>(xt + (row >> 3) * 1024 + (row & 7) * 128 + ((chunk ^ (row & 7)) << 4)) = val;
         }
         fence_proxy_async();
@@ -540,7 +572,7 @@ template <int BN, bool DUAL, bool NORMX = false>
 int launch_gemm(const CUtensorMap& tw, const CUtensorMap& tx, GemmArgs& a, int m_tiles, int splits, int stages_override,
                 cudaStream_t stream, bool pdl) {
   constexpr int STAGE_BYTES = W_TILE_BYTES * (DUAL ? 2 : 1) + BN * BK * 2;
-  const int nx_bytes = NORMX ? NORMX_T * a.nx_K * 2 + 64 : 0;
+  const int nx_bytes = NORMX ? (a.nx_mode == 0 ? NORMX_T * a.nx_K * 2 : 0) + 64 : 0;
   int max_stages = (SMEM_LIMIT - 1024 - 512 - nx_bytes) / STAGE_BYTES;
   if (max_stages > 16) max_stages = 16;
   int stages = stages_override > 0 ? min(stages_override, max_stages) : max_stages;
@@ -579,6 +611,7 @@ struct NormSpec {
   int n_wait;
   long long wait_point;
   const unsigned long long* epoch;
+  int mode;
 };
 
 struct PushSpec {
@@ -667,8 +700,10 @@ static int gemm_wx_impl(const void* W, const void* X, void* out, int M, int T, i
   a.nx_wait_flags = nullptr;
   a.nx_n_wait = 0;
   a.nx_wait_point = 0;
+  a.nx_mode = 0;
   if (norm != nullptr) {
-    if (T > NORMX_T || (K % 64) != 0 || K > 4096) return -30;
+    a.nx_mode = norm->mode;
+    if (T > NORMX_T || (K % 64) != 0 || (norm->mode == 0 && K > 4096)) return -30;
     a.nx_partials = norm->partials;
     a.nx_slab_stride = norm->slab_stride;
     a.nx_P = norm->P;
@@ -798,9 +833,55 @@ PRISM_API int prism_gemm_wx_normx(const void* W, void* out, int M, int T, int K,
   ns.n_wait = n_wait;
   ns.wait_point = wait_point;
   ns.epoch = reinterpret_cast<const unsigned long long*>(epoch);
+  ns.mode = 0;
   if (residual_out != nullptr && residual_out == residual_in) return -31;
   return gemm_wx_impl(W, W, out, M, T, K, ldw, ldw, ldo, w_rows_total, nullptr, nullptr, 0, 0, dual, w2_row_off, splits,
                       out_f32, split_stride, 16, stages_override, stream_ptr, pdl, nullptr, &ns);
+}
+
+// Down projection with the SwiGLU of the packed gate/up split-K slabs fused into its
+// prologue (at most 4 tokens):  x = silu(sum_p slabs[p][:, :K]) * sum_p slabs[p][:, K:].
+// Output: fp32 split-K slabs at `out`, or, when n_peers > 0, the tensor-parallel push form
+// of prism_gemm_wx_push (out is ignored).
+PRISM_API int prism_gemm_wx_actx(const void* W, void* out, int M, int T, int K, long long ldw, long long ldo,
+                                 int splits, long long split_stride, const void* gate_up_partials,
+                                 long long slab_stride, int P, const void* const* peer_out,
+                                 const void* const* peer_flag, int n_peers, int my_rank, long long point,
+                                 void* cta_counter, const void* epoch, void* stream_ptr, int pdl) {
+  NormSpec ns;
+  ns.partials = reinterpret_cast<const float*>(gate_up_partials);
+  ns.slab_stride = slab_stride;
+  ns.P = P;
+  ns.x = nullptr;
+  ns.residual_in = nullptr;
+  ns.residual_out = nullptr;
+  ns.weight = nullptr;
+  ns.eps = 0.0f;
+  ns.wait_flags = nullptr;
+  ns.n_wait = 0;
+  ns.wait_point = 0;
+  ns.epoch = nullptr;
+  ns.mode = 1;
+  PushSpec ps;
+  const PushSpec* pp = nullptr;
+  if (n_peers > 0) {
+    if (n_peers > 8) return -20;
+    ps.n_peers = n_peers;
+    ps.my_rank = my_rank;
+    ps.point = point;
+    ps.push_rows = 0;
+    ps.row_base = 0;
+    ps.cta_counter = reinterpret_cast<int*>(cta_counter);
+    ps.epoch = reinterpret_cast<const unsigned long long*>(epoch);
+    for (int p = 0; p < 8; ++p) {
+      ps.peer_out[p] = p < n_peers ? reinterpret_cast<float*>(const_cast<void*>(peer_out[p])) : nullptr;
+      ps.peer_flag[p] = p < n_peers ? reinterpret_cast<unsigned long long*>(const_cast<void*>(peer_flag[p])) : nullptr;
+    }
+    pp = &ps;
+    out = const_cast<void*>(peer_out[my_rank]);
+  }
+  return gemm_wx_impl(W, W, out, M, T, K, ldw, ldw, ldo, M, nullptr, nullptr, 0, 0, 0, 0, splits, 1, split_stride, 16, 0,
+                      stream_ptr, pdl, pp, &ns);
 }
 
 // Number of split-K slabs prism_gemm_wx will actually write for (K, splits).

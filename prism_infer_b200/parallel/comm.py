@@ -70,6 +70,11 @@ class NcclComm(TPComm):
         y = ops.linear(x, w)
         return self.reduce_dense(y), None, None
 
+    def row_parallel_swiglu(self, gate_up_partials: torch.Tensor, w: torch.Tensor):
+        T = gate_up_partials.shape[1]
+        parts = ops.linear_actx(gate_up_partials, w, ops.choose_splits(w.shape[0], w.shape[1], T))
+        return None, self.reduce_partials(parts), None
+
     def add_rmsnorm(self, weight, eps, dense, partials, ticket, residual, extra=None, extra_index=None):
         return ops.add_rmsnorm(weight, eps, x=dense, partials=partials, residual=residual, extra=extra,
                                extra_index=extra_index)
@@ -110,6 +115,24 @@ class FusedComm(NcclComm):
             "prism_gemm_wx_push", w.data_ptr(), x.data_ptr(), M, T, K,
             w.stride(0), x.stride(0), M, M, eff, T * M, self._slab_ptrs[slot], self._flag_ptrs[slot], self.size,
             self.rank, point, r.local(symm.OFF_COUNTER[slot]), r.local(symm.OFF_EPOCH), 0, 0,
+            torch.cuda.current_stream().cuda_stream, 1 if ops.pdl_enabled() else 0,
+        )
+        return None, None, (slot, point, self.size * eff, T)
+
+    def row_parallel_swiglu(self, gate_up_partials: torch.Tensor, w: torch.Tensor):
+        """SwiGLU prologue + down projection + push of the fp32 slabs to every peer, one kernel."""
+        P, T, I2 = gate_up_partials.shape
+        M, K = w.shape
+        if T > ops.NORMX_MAX_TOKENS or M != self.hidden or self.point >= symm.ARGMAX_POINT:
+            return super().row_parallel_swiglu(gate_up_partials, w)
+        eff = ops.effective_splits(K, min(symm.S_MAX, ops.choose_splits(M, K, T)))
+        point, slot = self.point, self.point % 2
+        self.point += 1
+        r = self.region
+        native.call(
+            "prism_gemm_wx_actx", w.data_ptr(), None, M, T, K, w.stride(0), M, eff, T * M,
+            gate_up_partials.data_ptr(), gate_up_partials.stride(0), P, self._slab_ptrs[slot], self._flag_ptrs[slot],
+            self.size, self.rank, point, r.local(symm.OFF_COUNTER[slot]), r.local(symm.OFF_EPOCH),
             torch.cuda.current_stream().cuda_stream, 1 if ops.pdl_enabled() else 0,
         )
         return None, None, (slot, point, self.size * eff, T)

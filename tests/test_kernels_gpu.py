@@ -356,3 +356,22 @@ def test_gemm_with_fused_residual_rmsnorm_prologue(cuda_device, T, source):
     got_act = ops.linear_normx(wgu, nw, 1e-6, T, residual_out=res_out2, dual=True, **kw)
     torch.cuda.synchronize()
     assert torch.equal(got_act, want_act) and torch.equal(res_out2, new_res)
+
+
+@pytest.mark.parametrize("T", [1, 4])
+@pytest.mark.parametrize("I,P", [(1536, 1), (6144, 2)])
+def test_down_projection_with_fused_swiglu_prologue(cuda_device, T, I, P):
+    """SwiGLU formed inside the down projection equals swiglu() then the split-K GEMM, bit for bit,
+    and both agree with the fp32 statement of the op."""
+    H = 4096
+    g = torch.Generator().manual_seed(70 + T + I)
+    w = (torch.randn(H, I, generator=g) * I ** -0.5).to(torch.bfloat16).cuda()
+    gu = torch.randn(P, T, 2 * I, generator=g).cuda()
+    act = ops.swiglu(partials=gu)
+    want = ops.linear_partial(act, w, 4)
+    got = ops.linear_actx(gu, w, 4)
+    torch.cuda.synchronize()
+    assert got.shape == want.shape and torch.equal(got, want)
+    full = gu.sum(0).cpu()
+    ref = (torch.nn.functional.silu(full[:, :I]) * full[:, I:]) @ w.float().cpu().T
+    close(got.sum(0), ref, 3e-2, 3e-2, "actx vs fp32")
