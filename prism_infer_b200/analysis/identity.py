@@ -13,3 +13,6 @@ def canonical_json(value: Any) -> str:
 
 def record_identity(value: Any) -> str:
     return hashlib.sha256(canonical_json(value).encode("utf-8")).hexdigest()
+
+
+canonical_json_sha256 = record_identity

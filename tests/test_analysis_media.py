@@ -1,0 +1,155 @@
+"""Video sampling, HTTP range reader, free-text scores, quality protocol validator (CPU)."""
+
+import http.server
+import io
+import threading
+import zipfile
+
+import numpy as np
+import pytest
+
+from prism_infer_b200.analysis import http_range_reader as hrr
+from prism_infer_b200.analysis import quality_protocol as qp
+from prism_infer_b200.analysis import reference_quality as rq
+from prism_infer_b200.analysis import video_sampling as vs
+
+
+def test_segment_centre_indices_match_the_published_rule():
+    # 100 frames, 8 samples: segment 12.375 -> centres 6, 18, 31, 43, 56, 68, 80, 93
+    got = vs.uniform_segment_center_indices(first_index=0, max_index=99, frames=8, fps=25.0)
+    seg = 99 / 8
+    assert got == [int(seg / 2 + round(seg * i)) for i in range(8)] == [6, 18, 31, 43, 56, 68, 80, 93]
+    bounded = vs.uniform_segment_center_indices(first_index=1, max_index=300, frames=4, fps=3.0, temporal_bound={"start": 10.0, "end": 20.0})
+    assert bounded[0] >= 30 and bounded[-1] <= 60 and bounded == sorted(bounded)
+    with pytest.raises(ValueError):
+        vs.uniform_segment_center_indices(first_index=0, max_index=9, frames=2, fps=1.0, temporal_bound={"start": 50, "end": 60})
+    with pytest.raises(ValueError):
+        vs.uniform_segment_center_indices(first_index=0, max_index=9, frames=True, fps=1.0)
+
+
+def test_frame_sequence_and_manifest_sampling(tmp_path):
+    from PIL import Image
+
+    rng = np.random.default_rng(0)
+    frames = [rng.integers(0, 256, (8, 8, 3), dtype=np.uint8) for _ in range(20)]
+    picked, rec = vs.sample_frame_sequence(frames, frames=4, fps=10.0)
+    assert rec["sampled_indices"] == vs.uniform_segment_center_indices(first_index=0, max_index=19, frames=4, fps=10.0)
+    assert all(np.array_equal(p, frames[i]) for p, i in zip(picked, rec["sampled_indices"]))
+    records = []
+    for i, f in enumerate(frames, 1):
+        Image.fromarray(f).save(tmp_path / f"f{i}.png")
+        records.append({"archive_member_path": f"clip/{i:05d}.jpg", "materialized_path": f"f{i}.png"})
+    picked2, rec2 = vs.sample_frame_manifest(records, materialized_root=tmp_path, frames=4, fps=3.0)
+    assert rec2["source_frame_count"] == 20 and all(1 <= i <= 20 for i in rec2["sampled_indices"])
+    assert np.array_equal(picked2[0], frames[rec2["sampled_indices"][0] - 1])
+    with pytest.raises(ValueError, match="gaps"):
+        vs.sample_frame_manifest(records[:5] + records[6:], materialized_root=tmp_path, frames=2, fps=3.0)
+    bad = [dict(records[0], materialized_path="../outside.png")]
+    with pytest.raises(ValueError, match="escapes"):
+        vs.sample_frame_manifest(bad, materialized_root=tmp_path, frames=1, fps=3.0)
+
+
+class _RangeHandler(http.server.BaseHTTPRequestHandler):
+    payload = b""
+    hits = 0
+    fail_first = 0
+
+    def do_GET(self):  # noqa: N802
+        cls = type(self)
+        cls.hits += 1
+        if cls.fail_first > 0:
+            cls.fail_first -= 1
+            self.send_response(503)
+            self.end_headers()
+            return
+        rng = self.headers.get("Range")
+        if rng is None or self.path == "/norange":
+            self.send_response(200)
+            self.send_header("Content-Length", str(len(cls.payload)))
+            self.end_headers()
+            self.wfile.write(cls.payload)
+            return
+        a, b = rng.split("=")[1].split("-")
+        a, b = int(a), int(b)
+        body = cls.payload[a:b + 1]
+        self.send_response(206)
+        self.send_header("Content-Range", f"bytes {a}-{b}/{len(cls.payload)}")
+        self.send_header("Content-Length", str(len(body)))
+        self.end_headers()
+        self.wfile.write(body)
+
+    def log_message(self, *args):
+        pass
+
+
+@pytest.fixture()
+def range_server():
+    buf = io.BytesIO()
+    with zipfile.ZipFile(buf, "w", zipfile.ZIP_STORED) as z:
+        for i in range(6):
+            z.writestr(f"m{i}.bin", bytes([i]) * 5000)
+    _RangeHandler.payload, _RangeHandler.hits, _RangeHandler.fail_first = buf.getvalue(), 0, 0
+    srv = http.server.ThreadingHTTPServer(("127.0.0.1", 0), _RangeHandler)
+    t = threading.Thread(target=srv.serve_forever, daemon=True)
+    t.start()
+    yield f"http://127.0.0.1:{srv.server_address[1]}"
+    srv.shutdown()
+    srv.server_close()
+
+
+def test_http_range_reader_reads_one_zip_member_without_the_whole_archive(range_server):
+    size = len(_RangeHandler.payload)
+    r = hrr.HTTPRangeReader(range_server + "/a.zip", expected_size=size, chunk_bytes=2048, cache_chunks=3, backoff_seconds=0.01)
+    with zipfile.ZipFile(r) as z:
+        assert z.read("m4.bin") == bytes([4]) * 5000
+    assert 0 < r.range_response_bytes < size and r.cache_hits > 0
+    r.seek(-10, io.SEEK_END)
+    assert r.read() == _RangeHandler.payload[-10:] and r.read(5) == b""
+    assert r.seek(3) == 3 and r.read(4) == _RangeHandler.payload[3:7]
+
+
+def test_http_range_reader_rejects_bad_servers_and_retries(range_server):
+    size = len(_RangeHandler.payload)
+    with pytest.raises(OSError, match="recorded size"):
+        hrr.HTTPRangeReader(range_server + "/a.zip", expected_size=size + 1, backoff_seconds=0.01)
+    with pytest.raises(OSError, match="ignored the Range"):
+        hrr.HTTPRangeReader(range_server + "/norange", expected_size=size, backoff_seconds=0.01)
+    _RangeHandler.fail_first = 2
+    r = hrr.HTTPRangeReader(range_server + "/a.zip", expected_size=size, backoff_seconds=0.01)
+    assert r.read(4) == _RangeHandler.payload[:4]
+    for bad in (None, "bytes 5-2/10", "bytes 0-10/10", "items 0-1/2"):
+        with pytest.raises(ValueError):
+            hrr.parse_content_range(bad)
+    assert hrr.parse_content_range("bytes 0-0/10") == (0, 0, 10)
+
+
+def test_reference_text_scores():
+    assert rq.token_f1("The cat sat.", "the CAT sat") == 1.0
+    assert rq.token_f1("", "") == 1.0 and rq.token_f1("a", "") == 0.0
+    assert abs(rq.token_f1("a b c d", "a b x y") - 0.5) < 1e-9
+    assert rq.lcs_length("a b c d e".split(), "a x c y e".split()) == 3
+    assert abs(rq.rouge_l_f1("a b c d e", "a x c y e") - 0.6) < 1e-9
+    out = rq.score_reference_batch({"1": "red car", "2": "blue"}, {"1": ["a red car", "red car"], "2": ["green"]})
+    assert out["samples"]["1"]["exact_match"] == 1.0 and out["mean"]["exact_match"] == 0.5
+    with pytest.raises(ValueError):
+        rq.score_reference_batch({"1": "x"}, {"2": ["x"]})
+
+
+def test_quality_protocol_validator():
+    rev = "0123456789abcdef0123456789abcdef01234567"
+    good = {"schema_version": 2, "name": "p", "model": {"revision": rev, "processor_revision": rev},
+            "selection": {"algorithm": "sha256-rank", "seed": 7, "materialization_requires_media_sha256": True},
+            "datasets": [{"id": "docvqa", "category": "doc", "source": "hf", "repository": "x/y", "split": "val",
+                          "sample_id_field": "id", "metric": "anls", "revision": rev, "development_samples": 10,
+                          "final_samples": 100, "materialization_status": "materialized"}]}
+    qp.validate_quality_protocol(good)
+    for mutate, msg in ((lambda p: p["model"].update(revision="ABC"), "hexadecimal"),
+                        (lambda p: p["datasets"].append(dict(p["datasets"][0])), "duplicate"),
+                        (lambda p: p["datasets"][0].update(development_samples=1000), "exceeds"),
+                        (lambda p: p["selection"].update(seed=True), "positive integer"),
+                        (lambda p: p["datasets"][0].update(materialization_status="??"), "unsupported")):
+        import copy
+        bad = copy.deepcopy(good)
+        mutate(bad)
+        with pytest.raises(ValueError, match=msg):
+            qp.validate_quality_protocol(bad)
