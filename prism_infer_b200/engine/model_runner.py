@@ -121,6 +121,7 @@ class ModelRunner:
 
             native.lib()  # fail loudly when the kernel library is missing
             ops.set_pdl(config.programmatic_dependent_launch)
+            ops.apply_tuning()
         with profile_region("runner.load_weights"):
             self.model = Qwen3VLModel(arch, device=self.device, dtype=self.dtype, comm=self.comm)
             source = weights.items() if weights is not None else open_weight_source(

@@ -490,6 +490,9 @@ class Qwen3VLModel:
                 # too few 128-row tiles for the dual-accumulator kernel to keep enough SMs
                 # streaming weights: split-K over the packed matrix, SwiGLU on the partial sums
                 gu = ops.linear_partial(h, l.gate_up, ops.choose_splits(2 * self.I, self.H, T))
+                if ops.ACTX_ENABLED and T <= ops.NORMX_MAX_TOKENS:
+                    dense, partials, ticket = comm.row_parallel_swiglu(gu, l.down)
+                    continue
                 act = ops.swiglu(partials=gu)
             else:
                 act = ops.gate_up_swiglu(h, l.gate_up)

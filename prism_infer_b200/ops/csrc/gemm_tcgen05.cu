@@ -107,7 +107,7 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
   // NORMX scratch: pre-norm rows (bf16), reciprocal rms per row, reduction slots
   __nv_bfloat16* nx_added = reinterpret_cast<__nv_bfloat16*>(
       (reinterpret_cast<uintptr_t>(tmem_slot + 4) + 15) & ~uintptr_t(15));
-  float* nx_rstd = reinterpret_cast<float*>(nx_added + ((NORMX && a.nx_mode == 0) ? NORMX_T * a.nx_K : 0));
+  float* nx_rstd = reinterpret_cast<float*>(nx_added + ((NORMX && a.nx_mode == 0) ? a.T * a.nx_K : 0));
   float* nx_red = nx_rstd + NORMX_T;
 
   const int warp = threadIdx.x >> 5;
@@ -568,13 +568,22 @@ int get_tensor_map(const void* ptr, unsigned long long rows, unsigned long long 
   return 0;
 }
 
+int g_small_tile_smem_cap = 0;
+
 template <int BN, bool DUAL, bool NORMX = false>
 int launch_gemm(const CUtensorMap& tw, const CUtensorMap& tx, GemmArgs& a, int m_tiles, int splits, int stages_override,
                 cudaStream_t stream, bool pdl) {
   constexpr int STAGE_BYTES = W_TILE_BYTES * (DUAL ? 2 : 1) + BN * BK * 2;
-  const int nx_bytes = NORMX ? (a.nx_mode == 0 ? NORMX_T * a.nx_K * 2 : 0) + 64 : 0;
+  const int nx_bytes = NORMX ? (a.nx_mode == 0 ? a.T * a.nx_K * 2 : 0) + 64 : 0;
   int max_stages = (SMEM_LIMIT - 1024 - 512 - nx_bytes) / STAGE_BYTES;
   if (max_stages > 16) max_stages = 16;
+  if (BN <= 32 && g_small_tile_smem_cap > 0) {
+    // decode-sized launches: leave room for the next kernel's CTA on the same SM, so that its
+    // weight prefetch (issued before griddepcontrol.wait) overlaps this kernel's tail
+    int capped = (g_small_tile_smem_cap - 1024 - 512 - nx_bytes) / STAGE_BYTES;
+    if (capped < 2) capped = 2;
+    if (capped < max_stages) max_stages = capped;
+  }
   int stages = stages_override > 0 ? min(stages_override, max_stages) : max_stages;
   if (stages > a.kb_per_split) stages = a.kb_per_split;
   if (stages < 1) stages = 1;
@@ -882,6 +891,12 @@ PRISM_API int prism_gemm_wx_actx(const void* W, void* out, int M, int T, int K, 
   }
   return gemm_wx_impl(W, W, out, M, T, K, ldw, ldw, ldo, M, nullptr, nullptr, 0, 0, 0, 0, splits, 1, split_stride, 16, 0,
                       stream_ptr, pdl, pp, &ns);
+}
+
+// Shared-memory budget (bytes, 0 = whole SM) of GEMM launches with at most 32 tokens per tile.
+PRISM_API int prism_gemm_set_small_tile_smem_cap(int bytes) {
+  g_small_tile_smem_cap = bytes;
+  return 0;
 }
 
 // Number of split-K slabs prism_gemm_wx will actually write for (K, splits).

@@ -46,6 +46,7 @@ _SIGNATURES = {
     "prism_gemm_wx_push": "ppiiillliilppiilppiipi",
     "prism_add_rmsnorm_wait": "plippppppiifpipipi",
     "prism_gemm_wx_normx": "ppiiilliiiiilplippppfpilpipi",
+    "prism_gemm_set_small_tile_smem_cap": "i",
     "prism_gemm_wx_actx": "ppiiillilplippiilpppi",
     "prism_gemm_wx_allgather": "ppiiillllpippiilpppi",
     "prism_signal_peers": "piilp",
