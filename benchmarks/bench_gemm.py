@@ -50,9 +50,11 @@ def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--json", default="")
+    ap.add_argument("--only", default="", help="substring filter on case names")
     args = ap.parse_args()
     pk = peaks()
     dev = torch.device("cuda:0")
+    ops.apply_tuning()
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
     rows = []
     cases = [
@@ -63,9 +65,13 @@ def main() -> None:
         ("qkv b128", 128, 6144, 4096, "plain"), ("down b128", 128, 4096, 12288, "plain"),
         ("qkv t2048", 2048, 6144, 4096, "plain"), ("down t2048", 2048, 4096, 12288, "plain"),
         ("gate_up dual t2048", 2048, 12288, 4096, "dual"), ("o t8192", 8192, 4096, 4096, "plain"),
-        ("vit fc1 t6272", 6272, 4304, 1152, "plain"),
+        ("vit fc1 t6272", 6272, 4304, 1152, "plain"), ("vit qkv t6272", 6272, 3456, 1152, "plain"),
+        ("vit proj t6272", 6272, 1152, 1152, "plain"), ("vit fc2 t6272", 6272, 1152, 4304, "plain"),
+        ("qkv t1616", 1616, 6144, 4096, "plain"), ("gate_up dual t1616", 1616, 12288, 4096, "dual"),
     ]
     for name, T, M, K, kind in cases:
+        if args.only and args.only not in name:
+            continue
         x = torch.randn(T, K, device=dev).to(torch.bfloat16)
         rowsW = 2 * M if kind == "dual" else M
         w = (torch.randn(rowsW, K, device=dev) * K ** -0.5).to(torch.bfloat16)
@@ -81,18 +87,21 @@ def main() -> None:
             ref = lambda: x @ w.t()  # noqa: E731
         else:
             out = torch.empty((T, M), dtype=torch.bfloat16, device=dev)
-            variants = {"bn256": lambda: ops.linear(x, w, out=out, bn=256), "bn128": lambda: ops.linear(x, w, out=out, bn=128)}
+            variants = {"bn256": lambda: ops.linear(x, w, out=out, bn=256), "bn128": lambda: ops.linear(x, w, out=out, bn=128),
+                        "persistent": lambda: ops.linear(x, w, out=out)}
             ref = lambda: x @ w.t()  # noqa: E731
         t_ref = timeit(ref, args.iters, flush)
+        all_ms = {}
         for vname, fn in variants.items():
             ms = timeit(fn, args.iters, flush)
+            all_ms[vname] = round(ms, 5)
             if best is None or ms < best[1]:
                 best = (vname, ms)
         ms = best[1]
         bytes_ = rowsW * K * 2 + T * K * 2 + T * M * 2
         flops = 2.0 * T * rowsW * K
         row = {
-            "case": name, "T": T, "M": rowsW, "K": K, "variant": best[0], "ms": round(ms, 5), "cublas_ms": round(t_ref, 5),
+            "case": name, "T": T, "M": rowsW, "K": K, "variant": best[0], "ms": round(ms, 5), "all_ms": all_ms, "cublas_ms": round(t_ref, 5),
             "gbs": round(bytes_ / ms / 1e6, 1), "tflops": round(flops / ms / 1e9, 1),
             "frac_hbm_of_measured": round(bytes_ / ms / 1e6 / pk["hbm_gbs"], 3),
             "frac_bf16_of_measured": round(flops / ms / 1e9 / pk["bf16_tflops"], 3),

@@ -43,6 +43,12 @@ def main() -> None:
         w, x = rnd(6144, 4096, scale=0.02), rnd(2048, 4096)
         for _ in range(reps):
             ops.linear(x, w)
+    elif case in ("gemm_vit_fc1", "gemm_vit_fc1_tiled"):
+        # vision-tower MLP up-projection: 6272 patches, 1152 -> 4304, bias + GELU(tanh); the
+        # "_tiled" form forces the one-tile-per-CTA kernel (bn=256)
+        w, x, b = rnd(4304, 1152, scale=0.03), rnd(6272, 1152), rnd(4304)
+        for _ in range(reps):
+            ops.linear(x, w, bias=b, act="gelu_tanh", bn=256 if case.endswith("tiled") else 0)
     elif case == "gemm_dual":
         w, x = rnd(24576, 4096, scale=0.02), rnd(2048, 4096)
         for _ in range(reps):

@@ -44,6 +44,7 @@ struct DecodeArgs {
   int* counters;            // [B * Hkv] zero-initialised, self-resetting; null = separate combine kernel
   int Hq, Hkv, page, max_blocks, nsplit;
   float scale;
+  PrefetchSpec pf;
 };
 
 // KV8 = true: fp8 payload (16 elements per lane), false: bf16 payload (8 elements per lane)
@@ -59,6 +60,7 @@ __global__ void __launch_bounds__(128) paged_decode_kernel(const DecodeArgs a) {
   const int part = lane % LPT;        // which EPL-wide slice of the head dim
   pdl_launch_dependents();
   pdl_wait();
+  l2_prefetch_rows(a.pf, (blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x, gridDim.x * gridDim.y * gridDim.z);
   const int ctx = a.context_lens[b];
   const int per_split = ((ctx + a.nsplit - 1) / a.nsplit + TPW * NWARP * 4 - 1) / (TPW * NWARP * 4) * (TPW * NWARP * 4);
   const int j_begin = split * per_split;
@@ -553,6 +555,7 @@ __global__ void __launch_bounds__(128) paged_decode_mma_kernel(const DecodeArgs 
   const int g = lane >> 2, t4 = lane & 3;
   pdl_launch_dependents();
   pdl_wait();
+  l2_prefetch_rows(a.pf, (blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x, gridDim.x * gridDim.y * gridDim.z);
   const int ctx = a.context_lens[b];
   const int per_split = ((ctx + a.nsplit - 1) / a.nsplit + BN - 1) / BN * BN;
   const int j_begin = split * per_split;
@@ -874,6 +877,7 @@ PRISM_API int prism_paged_decode(const void* q, const void* k_cache, const void*
   a.max_blocks = max_blocks;
   a.nsplit = nsplit < 1 ? 1 : (nsplit > 32 ? 32 : nsplit);
   a.scale = scale;
+  a.pf = prism_take_prefetch();
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   int rc;
   const bool mma = use_mma != 0;

@@ -497,6 +497,212 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
   }
 }
 
+
+// ------------------------------------------------------------------------------------
+// Persistent form for prefill-sized problems (no split-K, bf16 output): one CTA per SM walks
+// a strided list of output tiles.  The TMA producer runs ahead across tile boundaries, the
+// MMA thread alternates between two TMEM accumulators when both fit (BN * (DUAL ? 2 : 1)
+// <= 256 columns), and the epilogue warps drain one accumulator while the next tile's MMAs
+// run, so tile set-up, pipeline fill and the store loop are off the tensor pipe's critical
+// path.
+// ------------------------------------------------------------------------------------
+struct PersistArgs {
+  int M, T, kb_total, w2_row_off, stages;
+  int m_tiles, n_tiles;
+  int tokens_fastest;
+  int act;
+  long long ldo, ldr;
+  const __nv_bfloat16* bias;
+  const __nv_bfloat16* residual;
+  __nv_bfloat16* out;
+};
+
+template <int BN, bool DUAL>
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
+gemm_wx_persistent_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX,
+                          const PersistArgs a) {
+  constexpr int X_TILE_BYTES = BN * BK * 2;
+  constexpr int W_STAGE_BYTES = W_TILE_BYTES * (DUAL ? 2 : 1);
+  constexpr int STAGE_BYTES = W_STAGE_BYTES + X_TILE_BYTES;
+  constexpr int ACC_COLS = DUAL ? 2 * BN : BN;
+  constexpr int NBUF = ACC_COLS * 2 <= 512 ? 2 : 1;
+  constexpr int TMEM_COLS = ACC_COLS * NBUF < 32 ? 32 : ACC_COLS * NBUF;
+  constexpr uint32_t IDESC = umma_idesc_bf16(BM, BN);
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  const int stages = a.stages;
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + (size_t)stages * STAGE_BYTES);
+  uint64_t* empty = full + stages;
+  uint64_t* acc_full = empty + stages;   // [NBUF] MMA -> epilogue
+  uint64_t* acc_empty = acc_full + 2;    // [NBUF] epilogue -> MMA
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int num_tiles = a.m_tiles * a.n_tiles;
+  const int num_kb = a.kb_total;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < stages; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&acc_full[b], 1);
+      mbar_init(&acc_empty[b], 4);  // one arrival per epilogue warp
+    }
+    fence_barrier_init();
+    tma_prefetch_desc(&tmW);
+    tma_prefetch_desc(&tmX);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  pdl_launch_dependents();
+
+  // tile id -> (m0, n0); consecutive ids share a weight tile (tokens fastest) or an
+  // activation tile (features fastest)
+#define PRISM_TILE_COORDS(tile_, m0_, n0_)                                             \
+  const int m0_ = (a.tokens_fastest ? (tile_) / a.n_tiles : (tile_) % a.m_tiles) * BM; \
+  const int n0_ = (a.tokens_fastest ? (tile_) % a.n_tiles : (tile_) / a.m_tiles) * BN;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      // ------------------------------ TMA producer ------------------------------
+      pdl_wait();  // activations come from the previous kernel
+      long long it = 0;  // running k-block count across tiles
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        PRISM_TILE_COORDS(tile, m0, n0)
+        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+          const int s = (int)(it % stages);
+          const uint32_t round = (uint32_t)(it / stages);
+          if (round > 0) {
+            ok = mbar_wait(&empty[s], (round - 1) & 1, 1);
+            if (!ok) break;
+          }
+          uint8_t* st = smem + (size_t)s * STAGE_BYTES;
+          mbar_expect_tx(&full[s], STAGE_BYTES);
+          tma_load_2d(st, &tmW, &full[s], kb * BK, m0);
+          if (DUAL) tma_load_2d(st + W_TILE_BYTES, &tmW, &full[s], kb * BK, a.w2_row_off + m0);
+          tma_load_2d(st + W_STAGE_BYTES, &tmX, &full[s], kb * BK, n0);
+        }
+      }
+      if (!ok) {
+        // unwinding after a timed-out wait: let copies already in flight land before the
+        // CTA's shared memory is released
+        for (long long j = it - stages < 0 ? 0 : it - stages; j < it; ++j)
+          (void)mbar_wait(&full[j % stages], (uint32_t)(j / stages) & 1, 4);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      // ------------------------------ MMA issuer ------------------------------
+      long long it = 0;
+      int local = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local) {
+        const int buf = local % NBUF;
+        const uint32_t use = (uint32_t)(local / NBUF);
+        if (use > 0) {
+          ok = mbar_wait(&acc_empty[buf], (use - 1) & 1, 5);
+          if (!ok) break;
+          tc_fence_after();
+        }
+        const uint32_t acc_addr = tmem_base + buf * ACC_COLS;
+        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+          const int s = (int)(it % stages);
+          ok = mbar_wait(&full[s], (uint32_t)(it / stages) & 1, 2);
+          if (!ok) break;
+          tc_fence_after();
+          const uint32_t st = smem_u32(smem + (size_t)s * STAGE_BYTES);
+          const uint64_t da = umma_desc_sw128(st);
+          const uint64_t db = umma_desc_sw128(st + W_STAGE_BYTES);
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k) {
+            const uint32_t acc = (kb | k) != 0;
+            tc_mma_f16(acc_addr, da + 2 * k, db + 2 * k, IDESC, acc);
+            if (DUAL) {
+              const uint64_t da2 = umma_desc_sw128(st + W_TILE_BYTES);
+              tc_mma_f16(acc_addr + BN, da2 + 2 * k, db + 2 * k, IDESC, acc);
+            }
+          }
+          tc_commit(&empty[s]);
+        }
+        if (ok) tc_commit(&acc_full[buf]);
+      }
+    }
+  } else {
+    // ------------------------------ epilogue warps 2..5 ------------------------------
+    const int q = warp & 3;  // TMEM lane quarter this warp may read
+    pdl_wait();
+    const bool plain = !DUAL && a.bias == nullptr && a.act == 0 && a.residual == nullptr;
+    int local = 0;
+    for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++local) {
+      const int buf = local % NBUF;
+      if (!mbar_wait(&acc_full[buf], (uint32_t)(local / NBUF) & 1, 3)) break;
+      tc_fence_after();
+      PRISM_TILE_COORDS(tile, m0, n0)
+      const int m = m0 + q * 32 + lane;
+      const bool m_ok = m < a.M;
+      const float bias_v = (a.bias != nullptr && m_ok) ? __bfloat162float(a.bias[m]) : 0.0f;
+      const uint32_t t_lane = tmem_base + buf * ACC_COLS + ((uint32_t)(q * 32) << 16);
+      const int n_valid = min(BN, a.T - n0);
+      for (int c0 = 0; c0 < n_valid; c0 += 16) {
+        uint32_t r[16];
+        uint32_t r2[16];
+        tmem_ld16(t_lane + c0, r);
+        if (DUAL) tmem_ld16(t_lane + BN + c0, r2);
+        tmem_ld_wait();
+        if (!m_ok) continue;
+        const int cols = min(16, n_valid - c0);
+        const size_t row0 = (size_t)(n0 + c0);
+        __nv_bfloat16* dst = a.out + row0 * a.ldo + m;
+        if (DUAL) {
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            if (j < cols) {
+              const float g = bf16_round(__uint_as_float(r[j]));
+              const float u = bf16_round(__uint_as_float(r2[j]));
+              dst[(size_t)j * a.ldo] = __float2bfloat16_rn(bf16_round(silu(g)) * u);
+            }
+          }
+        } else if (plain) {
+#pragma unroll
+          for (int j = 0; j < 16; ++j)
+            if (j < cols) dst[(size_t)j * a.ldo] = __float2bfloat16_rn(__uint_as_float(r[j]));
+        } else {
+          const __nv_bfloat16* rsd = a.residual ? a.residual + row0 * a.ldr + m : nullptr;
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            if (j < cols) {
+              float v = __uint_as_float(r[j]) + bias_v;
+              if (a.act == 1) v = gelu_tanh(v);
+              else if (a.act == 2) v = gelu_erf(v);
+              if (rsd != nullptr) v = bf16_round(v) + __bfloat162float(rsd[(size_t)j * a.ldr]);
+              dst[(size_t)j * a.ldo] = __float2bfloat16_rn(v);
+            }
+          }
+        }
+      }
+      // this warp's reads of the accumulator are complete: hand the buffer back
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&acc_empty[buf]);
+    }
+  }
+#undef PRISM_TILE_COORDS
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) tmem_dealloc(tmem_base, TMEM_COLS);
+}
+
 // ------------------------------------------------------------------------------------
 // Host side: tensor-map cache and launcher.
 // ------------------------------------------------------------------------------------
@@ -599,6 +805,34 @@ int launch_gemm(const CUtensorMap& tw, const CUtensorMap& tx, GemmArgs& a, int m
   dim3 grid = a.tokens_fastest ? dim3(n_tiles, m_tiles, splits) : dim3(m_tiles, n_tiles, splits);
   cudaError_t e = prism_launch(gemm_wx_kernel<BN, DUAL, NORMX>, grid, dim3(GEMM_THREADS), smem, stream, pdl, tw, tx, a);
   return (int)e;
+}
+
+
+int g_persistent_min_tokens = 512;  // 0 disables the persistent form
+int g_sm_count = 0;
+
+template <int BN, bool DUAL>
+int launch_persistent(const CUtensorMap& tw, const CUtensorMap& tx, PersistArgs& a, cudaStream_t stream, bool pdl) {
+  constexpr int STAGE_BYTES = W_TILE_BYTES * (DUAL ? 2 : 1) + BN * BK * 2;
+  int stages = (SMEM_LIMIT - 1024 - 512) / STAGE_BYTES;
+  if (stages > 12) stages = 12;
+  if (stages < 2) return -7;
+  a.stages = stages;
+  const size_t smem = (size_t)stages * STAGE_BYTES + 1024 + (2 * stages + 4) * 8 + 64;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_wx_persistent_kernel<BN, DUAL>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_LIMIT);
+    if (e != cudaSuccess) return (int)e;
+    configured = true;
+  }
+  if (g_sm_count == 0) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&g_sm_count, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess)
+      g_sm_count = 148;
+  }
+  const int tiles = a.m_tiles * a.n_tiles;
+  const int grid = tiles < g_sm_count ? tiles : g_sm_count;
+  return (int)prism_launch(gemm_wx_persistent_kernel<BN, DUAL>, dim3(grid), dim3(GEMM_THREADS), smem, stream, pdl, tw, tx, a);
 }
 
 }  // namespace
@@ -741,6 +975,29 @@ static int gemm_wx_impl(const void* W, const void* X, void* out, int M, int T, i
   if (norm != nullptr) {
     return dual ? launch_gemm<16, true, true>(tw, tx, a, m_tiles, splits, stages_override, stream, p)
                 : launch_gemm<16, false, true>(tw, tx, a, m_tiles, splits, stages_override, stream, p);
+  }
+  if (g_persistent_min_tokens > 0 && T >= g_persistent_min_tokens && splits == 1 && !out_f32 && push == nullptr &&
+      bn_override <= 0 && stages_override <= 0) {
+    PersistArgs pa;
+    pa.M = M;
+    pa.T = T;
+    pa.kb_total = a.kb_total;
+    pa.w2_row_off = w2_row_off;
+    pa.m_tiles = m_tiles;
+    pa.tokens_fastest = a.tokens_fastest;
+    pa.act = act;
+    pa.ldo = ldo;
+    pa.ldr = ldr;
+    pa.bias = a.bias;
+    pa.residual = a.residual;
+    pa.out = reinterpret_cast<__nv_bfloat16*>(out);
+    // dual: two accumulators per tile, so 128 tokens per tile keep two tiles in TMEM
+    const int pbn = dual ? 128 : 256;
+    pa.n_tiles = (T + pbn - 1) / pbn;
+    CUtensorMap txp;
+    rc = get_tensor_map(X, (unsigned long long)T, (unsigned long long)K, (unsigned long long)ldx, (unsigned)pbn, &txp);
+    if (rc) return rc;
+    return dual ? launch_persistent<128, true>(tw, txp, pa, stream, p) : launch_persistent<256, false>(tw, txp, pa, stream, p);
   }
 #define PRISM_GEMM_CASE(BN_)                                                                            \
   case BN_:                                                                                             \
@@ -891,6 +1148,12 @@ PRISM_API int prism_gemm_wx_actx(const void* W, void* out, int M, int T, int K, 
   }
   return gemm_wx_impl(W, W, out, M, T, K, ldw, ldw, ldo, M, nullptr, nullptr, 0, 0, 0, 0, splits, 1, split_stride, 16, 0,
                       stream_ptr, pdl, pp, &ns);
+}
+
+// Smallest token count that uses the persistent kernel (0 = never).
+PRISM_API int prism_gemm_set_persistent_min_tokens(int tokens) {
+  g_persistent_min_tokens = tokens;
+  return 0;
 }
 
 // Shared-memory budget (bytes, 0 = whole SM) of GEMM launches with at most 32 tokens per tile.

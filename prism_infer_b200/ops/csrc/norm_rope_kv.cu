@@ -59,6 +59,8 @@ struct AddNormArgs {
   int n_wait;
   const unsigned long long* epoch;
   int point;
+  int T;
+  PrefetchSpec pf;
 };
 
 // Bounded acquire-spin on a flag another GPU writes.  Returns false after
@@ -82,6 +84,10 @@ __global__ void __launch_bounds__(1024) add_rmsnorm_kernel(const AddNormArgs a) 
   const int t = blockIdx.x;
   const int H = a.H;
   pdl_launch_dependents();
+  if (t >= a.T) {  // helper CTA: weights are static, no need to wait for the previous kernel
+    l2_prefetch_rows(a.pf, t - a.T, gridDim.x - a.T);
+    return;
+  }
   pdl_wait();
   if (a.n_wait > 0) {
     if ((int)threadIdx.x < a.n_wait) wait_flag_ge(a.wait_flags + threadIdx.x, *a.epoch + (unsigned long long)a.point, threadIdx.x);
@@ -214,6 +220,8 @@ struct QkvArgs {
   int kv_mode;              // 0 bf16, 1 fp8 unit scale, 2 fp8 + per-token-per-head scale
   int apply_norm, apply_rope;
   float eps;
+  int real_ctas;
+  PrefetchSpec pf;
 };
 
 constexpr float FP8_MAX = 448.0f;
@@ -227,6 +235,10 @@ __global__ void __launch_bounds__(256) qk_norm_rope_store_kernel(const QkvArgs a
   const int lane = threadIdx.x & 31;
   const int heads = a.Hq + 2 * a.Hkv;
   pdl_launch_dependents();
+  if ((int)blockIdx.x >= a.real_ctas) {  // helper CTA
+    l2_prefetch_rows(a.pf, blockIdx.x - a.real_ctas, gridDim.x - a.real_ctas);
+    return;
+  }
   pdl_wait();
   if (gw >= a.T * heads) return;
   const int t = gw / heads;
@@ -466,6 +478,10 @@ static int add_rmsnorm_impl(const void* partials, long long slab_stride, int P, 
   a.n_wait = n_wait;
   a.epoch = (const unsigned long long*)epoch;
   a.point = point;
+  a.T = T;
+  a.pf = prism_take_prefetch();
+  const int helpers = a.pf.rows > 0 ? a.pf.helpers : 0;
+  if (helpers == 0) a.pf.rows = 0;
   const size_t smem = (size_t)H * sizeof(float);
   if (smem > 48 * 1024) {
     cudaError_t e = cudaFuncSetAttribute(add_rmsnorm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -474,7 +490,7 @@ static int add_rmsnorm_impl(const void* partials, long long slab_stride, int P, 
   // few rows: one wide CTA per row so every element has its own thread; many rows: 256 threads
   int threads = T <= 64 ? 1024 : 256;
   while (threads > 32 && threads * 4 > H * 2) threads >>= 1;
-  return (int)prism_launch(add_rmsnorm_kernel, dim3(T), dim3(threads), smem, STREAM(stream), pdl != 0, a);
+  return (int)prism_launch(add_rmsnorm_kernel, dim3(T + helpers), dim3(threads), smem, STREAM(stream), pdl != 0, a);
 }
 
 PRISM_API int prism_add_rmsnorm(const void* partials, long long slab_stride, int P, const void* x_in,
@@ -535,9 +551,13 @@ PRISM_API int prism_qk_norm_rope_store(const void* qkv, const void* partials, lo
   a.apply_norm = apply_norm;
   a.apply_rope = apply_rope;
   a.eps = eps;
+  a.pf = prism_take_prefetch();
   const int warps = T * (Hq + 2 * Hkv);
   const int wpb = 8;
-  dim3 grid((warps + wpb - 1) / wpb), block(wpb * 32);
+  a.real_ctas = (warps + wpb - 1) / wpb;
+  const int helpers = a.pf.rows > 0 ? a.pf.helpers : 0;
+  if (helpers == 0) a.pf.rows = 0;
+  dim3 grid(a.real_ctas + helpers), block(wpb * 32);
   if (D == 128) return (int)prism_launch(qk_norm_rope_store_kernel<128>, grid, block, 0, STREAM(stream), pdl != 0, a);
   if (D == 64) return (int)prism_launch(qk_norm_rope_store_kernel<64>, grid, block, 0, STREAM(stream), pdl != 0, a);
   return -2;

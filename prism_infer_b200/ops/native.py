@@ -47,6 +47,8 @@ _SIGNATURES = {
     "prism_add_rmsnorm_wait": "plippppppiifpipipi",
     "prism_gemm_wx_normx": "ppiiilliiiiilplippppfpilpipi",
     "prism_gemm_set_small_tile_smem_cap": "i",
+    "prism_gemm_set_persistent_min_tokens": "i",
+    "prism_set_next_prefetch": "pliii",
     "prism_gemm_wx_actx": "ppiiillilplippiilpppi",
     "prism_gemm_wx_allgather": "ppiiillllpippiilpppi",
     "prism_signal_peers": "piilp",

@@ -375,3 +375,27 @@ def test_down_projection_with_fused_swiglu_prologue(cuda_device, T, I, P):
     full = gu.sum(0).cpu()
     ref = (torch.nn.functional.silu(full[:, :I]) * full[:, I:]) @ w.float().cpu().T
     close(got.sum(0), ref, 3e-2, 3e-2, "actx vs fp32")
+
+
+@pytest.mark.parametrize("T,M,K", [(3000, 2000, 320), (6272, 1152, 1152), (777, 4304, 1152)])
+def test_gemm_persistent_matches_tiled_kernel(cuda_device, T, M, K):
+    """The persistent form (several tiles per CTA, two TMEM accumulators) gives the same bits as
+    the one-tile-per-CTA kernel for every epilogue, and both match the fp32 reference."""
+    x, w = rand_bf16(T, K, seed=21).cuda(), rand_bf16(M, K, scale=K ** -0.5, seed=22).cuda()
+    b, r = rand_bf16(M, seed=23).cuda(), rand_bf16(T, M, seed=24).cuda()
+    for kw in (dict(), dict(bias=b, act="gelu_tanh"), dict(bias=b, residual=r)):
+        got = ops.linear(x, w, **kw)            # T >= 512: persistent kernel
+        want = ops.linear(x, w, bn=256, **kw)   # explicit tile size: one tile per CTA
+        torch.cuda.synchronize()
+        assert torch.equal(got, want), f"persistent vs tiled differ for {list(kw)}"
+    close(got, ops.linear(x.float().cpu(), w.float().cpu(), bias=b.float().cpu(), residual=r.float().cpu()), 3e-2, 2e-2, "persistent")
+
+
+def test_gemm_persistent_dual_swiglu(cuda_device):
+    T, I, K = 2500, 1280, 512  # 10 x 20 tiles of 128 tokens: more tiles than SMs
+    x, w = rand_bf16(T, K, seed=25).cuda(), rand_bf16(2 * I, K, scale=K ** -0.5, seed=26).cuda()
+    got = ops.gate_up_swiglu(x, w)
+    want = ops.gate_up_swiglu(x, w, bn=128)
+    torch.cuda.synchronize()
+    assert torch.equal(got, want)
+    close(got, ops.gate_up_swiglu(x.float().cpu(), w.float().cpu()), 2e-2, 3e-2, "persistent dual")
