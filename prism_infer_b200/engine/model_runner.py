@@ -262,7 +262,8 @@ class ModelRunner:
                 deep = [dk[0] if len(dk) == 1 else torch.cat(dk) for dk in (deeps or [])]
             meta = AttnMeta(
                 is_prefill=True, block_tables=self._to_dev(inp.block_tables), slots=self._to_dev(inp.slots),
-                cu_seqlens_q=self._to_dev(inp.cu_seqlens_q), kv_lens=self._to_dev(inp.kv_lens), max_q_len=inp.max_q_len)
+                cu_seqlens_q=self._to_dev(inp.cu_seqlens_q), kv_lens=self._to_dev(inp.kv_lens), max_q_len=inp.max_q_len,
+                no_history=bool(torch.equal(inp.kv_lens, inp.cu_seqlens_q[1:] - inp.cu_seqlens_q[:-1])))
             ids, pos, vis_index = self._to_dev(inp.input_ids), self._to_dev(inp.positions), self._to_dev(inp.vis_index)
         with profile_region("runner.run_model"):
             hidden = self.model.forward(ids, pos, meta, self.kv, visual=visual, vis_index=vis_index, deepstack=deep)

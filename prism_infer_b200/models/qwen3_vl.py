@@ -43,6 +43,7 @@ class AttnMeta:
     kv_lens: Optional[torch.Tensor] = None         # [S] int32 keys visible (history + chunk)
     max_q_len: int = 0
     last_rows: Optional[torch.Tensor] = None       # [S] int64 row of each sequence's last token
+    no_history: bool = False                       # every sequence attends only to this chunk's own keys
     # decode
     context_lens: Optional[torch.Tensor] = None    # [B] int32 (including the new token)
     nsplit: int = 0
@@ -473,6 +474,7 @@ class Qwen3VLModel:
                 ops.prefetch_next(l.qkv, ops.L2_PREFETCH[0])
             h, residual = comm.add_rmsnorm(l.input_norm, t.rms_norm_eps, dense, partials, ticket, residual,
                                            extra, vis_index if extra is not None else None)
+            direct = False
             if small and h.is_cuda:
                 qkv_p = ops.linear_partial(h, l.qkv, ops.choose_splits(l.qkv.shape[0], self.H, T))
                 if pf:
@@ -482,10 +484,19 @@ class Qwen3VLModel:
                                            section=t.mrope_section, eps=t.rms_norm_eps, slots=meta.slots, cache=cache, layer=i)
             else:
                 qkv = ops.linear(h, l.qkv)
+                # no history: attend over the fresh bf16 K/V rows of the projection itself (as the
+                # reference does, prism_infer/layers/attention.py:180-193) instead of re-reading
+                # and dequantising the pages just written
+                direct = meta.is_prefill and meta.no_history and qkv.is_cuda
                 q = ops.qk_norm_rope_store(qkv=qkv, partials=None, positions=positions, q_weight=l.q_norm, k_weight=l.k_norm,
                                            num_heads=self.Hq, num_kv_heads=self.Hkv, head_dim=self.D, theta=t.rope_theta,
-                                           section=t.mrope_section, eps=t.rms_norm_eps, slots=meta.slots, cache=cache, layer=i)
-            if meta.is_prefill:
+                                           section=t.mrope_section, eps=t.rms_norm_eps, slots=meta.slots, cache=cache, layer=i,
+                                           k_writeback=direct)
+            if direct:
+                heads = qkv.view(T, self.Hq + 2 * self.Hkv, self.D)
+                a = ops.varlen_attention(q, heads[:, self.Hq:self.Hq + self.Hkv], heads[:, self.Hq + self.Hkv:],
+                                         meta.cu_seqlens_q, meta.max_q_len, causal=True)
+            elif meta.is_prefill:
                 a = ops.paged_prefill_attention(q, cache, i, meta.cu_seqlens_q, meta.kv_lens, meta.block_tables, meta.max_q_len)
             else:
                 if pf:

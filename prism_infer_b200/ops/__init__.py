@@ -429,8 +429,11 @@ def qk_norm_rope_store(
     q_out: Optional[torch.Tensor] = None,
     apply_norm: bool = True,
     apply_rope: bool = True,
+    k_writeback: bool = False,
 ) -> torch.Tensor:
     """Per-head RMSNorm of q/k, interleaved M-RoPE, then K/V written to the paged cache.
+    With ``k_writeback`` (CUDA, bf16 ``qkv`` source) the normalised, rotated K also replaces
+    its slice of ``qkv`` so a prefill without history can attend over ``qkv`` directly.
 
     ``qkv [T, (Hq + 2 Hkv) * D]`` (or fp32 split-K ``partials [P, T, ...]``), ``positions
     [3, T]`` int32, ``slots [T]`` int64 flat slot (``block * page + offset``, negative =
@@ -470,7 +473,7 @@ def qk_norm_rope_store(
         0 if partials is None else partials.shape[0], src.stride(0), _p(positions), _p(q_weight), _p(k_weight),
         _p(inv_freq), _p(axis), _p(q_out), q_out.stride(0), _p(slots), _p(cache.k(layer)), _p(cache.v(layer)),
         _p(cache.k_scale(layer)), _p(cache.v_scale(layer)), T, Hq, Hkv, D, cache.page, cache.mode,
-        1 if apply_norm else 0, 1 if apply_rope else 0, float(eps), _s(), _pdl(),
+        1 if apply_norm else 0, 1 if apply_rope else 0, float(eps), 1 if (k_writeback and qkv is not None) else 0, _s(), _pdl(),
     )
     return q_out
 
@@ -487,7 +490,7 @@ def store_kv(k: torch.Tensor, v: torch.Tensor, slots: torch.Tensor, cache: KVCac
             "prism_qk_norm_rope_store", _p(packed), None, 0, 0, packed.stride(0), _p(pos), _p(one), _p(one),
             _p(inv_freq), _p(axis), None, 0, _p(slots), _p(cache.k(layer)), _p(cache.v(layer)),
             _p(cache.k_scale(layer)), _p(cache.v_scale(layer)), T, 0, Hkv, D, cache.page, cache.mode, 0, 0,
-            1e-6, _s(), _pdl(),
+            1e-6, 0, _s(), _pdl(),
         )
         return
     keep = slots >= 0

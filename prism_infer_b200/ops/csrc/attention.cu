@@ -330,15 +330,33 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   return *reinterpret_cast<uint32_t*>(&v);
 }
 
-template <int HD, int HD_REAL, int MODE>
-__global__ void __launch_bounds__(128) flash_fwd_kernel(const FlashArgs a) {
-  constexpr int BM = 64, BN = 64;
+__device__ __forceinline__ float ex2_fast(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ void cp_async16(void* smem_dst, const void* gmem_src, bool valid) {
+  // src-size 0 zero-fills the 16 bytes without touching global memory
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_u32(smem_dst)), "l"(gmem_src), "r"(valid ? 16 : 0)
+               : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
+
+// BM query rows per CTA (16 per warp), 64-key tiles, K/V double-buffered in shared memory:
+// while the warps score tile i, tile i+1 is on its way (cp.async for bf16 sources; for FP8
+// pages the bytes are fetched into registers before the math and dequantised into the
+// other buffer after it).  One __syncthreads per tile.
+template <int HD, int HD_REAL, int MODE, int BM>
+__global__ void __launch_bounds__(BM * 2, MODE == 2 ? (BM == 128 ? 1 : 2) : (BM == 128 ? 2 : 3)) flash_fwd_kernel(const FlashArgs a) {
+  constexpr int BN = 64;
+  constexpr int NT = BM * 2;           // threads
   constexpr int LDS = HD + 8;          // padded row (elements) -> conflict-free ldmatrix
   constexpr int CHUNKS = HD_REAL / 8;  // 8-element chunks per row
+  constexpr int NI = (BN * CHUNKS + NT - 1) / NT;  // chunks per thread and tile
   extern __shared__ __align__(16) uint8_t fsm[];
   bf16* Qs = reinterpret_cast<bf16*>(fsm);
-  bf16* Ks = Qs + BM * LDS;
-  bf16* Vs = Ks + BN * LDS;
+  bf16* KV = Qs + BM * LDS;  // [buffer][k|v][BN][LDS]
 
   const int seq = blockIdx.z, head = blockIdx.y, qt = blockIdx.x;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -352,170 +370,234 @@ __global__ void __launch_bounds__(128) flash_fwd_kernel(const FlashArgs a) {
   const int kv_len = (MODE == 0) ? q_len : a.kv_lens[seq];
   const int kvh = head / (a.Hq / a.Hkv);
   const int pos_off = kv_len - q_len;  // absolute key position of local query 0
+  const int* bt = (MODE == 0) ? nullptr : a.block_tables + (size_t)seq * a.max_blocks;
 
   // zero the padding columns once (HD_REAL < HD only for the 72-wide vision heads)
   if constexpr (HD_REAL < HD) {
-    for (int i = tid; i < (BM + 2 * BN) * (HD - HD_REAL); i += 128) {
+    for (int i = tid; i < (BM + 4 * BN) * (HD - HD_REAL); i += NT) {
       const int r = i / (HD - HD_REAL), c = HD_REAL + i % (HD - HD_REAL);
-      Qs[r * LDS + c] = __float2bfloat16(0.0f);  // Qs, Ks, Vs are contiguous with the same pitch
+      Qs[r * LDS + c] = __float2bfloat16(0.0f);  // Q and the K/V buffers are contiguous with the same pitch
     }
   }
-  // Q tile
-  for (int i = tid; i < BM * CHUNKS; i += 128) {
+  for (int i = tid; i < BM * CHUNKS; i += NT) {
     const int r = i / CHUNKS, c = i % CHUNKS;
     uint4 v = make_uint4(0, 0, 0, 0);
     if (q0 + r < q_len)
       v = *reinterpret_cast<const uint4*>(a.q + (size_t)(q_start + q0 + r) * a.q_stride + (size_t)head * HD_REAL + c * 8);
     *reinterpret_cast<uint4*>(Qs + r * LDS + c * 8) = v;
   }
-  __syncthreads();
-  uint32_t qf[HD / 16][4];
-  {
-    const int r = warp * 16 + (lane & 7) + 8 * ((lane >> 3) & 1);
-    const int c = 8 * (lane >> 4);
+
+  int kv_end = kv_len;
+  if (a.causal) kv_end = min(kv_len, pos_off + min(q0 + BM, q_len));
+  const int n_tiles = (kv_end + BN - 1) / BN;
+
+  // ---- tile movers ------------------------------------------------------------------
+  uint2 st_k[NI], st_v[NI];
+  float st_ks[NI], st_vs[NI];
+  auto issue_async = [&](int tile, int buf) {  // MODE 0 / 1: global bf16 -> shared, asynchronous
+    bf16* Kd = KV + (size_t)(buf * 2) * BN * LDS;
+    bf16* Vd = Kd + BN * LDS;
+    const int j0 = tile * BN;
 #pragma unroll
-    for (int kk = 0; kk < HD / 16; ++kk) ldsm_x4(qf[kk], smem_u32(Qs + r * LDS + kk * 16 + c));
+    for (int it = 0; it < NI; ++it) {
+      const int i = tid + it * NT;
+      if (i < BN * CHUNKS) {
+        const int r = i / CHUNKS, c = i % CHUNKS;
+        const int j = j0 + r;
+        const bf16* ksrc = a.q;  // any valid address for the zero-fill form
+        const bf16* vsrc = a.q;
+        bool ok = j < kv_len;
+        if (ok) {
+          if (MODE == 0) {
+            const size_t off = (size_t)(q_start + j) * a.kv_stride + (size_t)kvh * HD_REAL + c * 8;
+            ksrc = a.k + off;
+            vsrc = a.v + off;
+          } else {
+            const int blk = bt[j / a.page];
+            ok = blk >= 0;
+            if (ok) {
+              const size_t row = ((size_t)blk * a.Hkv + kvh) * a.page + (j % a.page);
+              ksrc = reinterpret_cast<const bf16*>(a.k_cache) + row * HD_REAL + c * 8;
+              vsrc = reinterpret_cast<const bf16*>(a.v_cache) + row * HD_REAL + c * 8;
+            }
+          }
+        }
+        cp_async16(Kd + r * LDS + c * 8, ksrc, ok);
+        cp_async16(Vd + r * LDS + c * 8, vsrc, ok);
+      }
+    }
+    cp_async_commit();
+  };
+  auto fetch_fp8 = [&](int tile) {  // MODE 2: FP8 bytes and scales -> registers
+    const int j0 = tile * BN;
+#pragma unroll
+    for (int it = 0; it < NI; ++it) {
+      const int i = tid + it * NT;
+      st_k[it] = make_uint2(0, 0);
+      st_v[it] = make_uint2(0, 0);
+      st_ks[it] = st_vs[it] = 0.0f;
+      if (i < BN * CHUNKS) {
+        const int r = i / CHUNKS, c = i % CHUNKS;
+        const int j = j0 + r;
+        if (j < kv_len) {
+          const int blk = bt[j / a.page];
+          if (blk >= 0) {
+            const size_t row = ((size_t)blk * a.Hkv + kvh) * a.page + (j % a.page);
+            st_k[it] = *reinterpret_cast<const uint2*>(reinterpret_cast<const uint8_t*>(a.k_cache) + row * HD_REAL + c * 8);
+            st_v[it] = *reinterpret_cast<const uint2*>(reinterpret_cast<const uint8_t*>(a.v_cache) + row * HD_REAL + c * 8);
+            st_ks[it] = a.k_scale ? a.k_scale[row] : 1.0f;
+            st_vs[it] = a.v_scale ? a.v_scale[row] : 1.0f;
+          }
+        }
+      }
+    }
+  };
+  auto stash_fp8 = [&](int buf) {  // registers -> bf16 in shared memory
+    bf16* Kd = KV + (size_t)(buf * 2) * BN * LDS;
+    bf16* Vd = Kd + BN * LDS;
+#pragma unroll
+    for (int it = 0; it < NI; ++it) {
+      const int i = tid + it * NT;
+      if (i < BN * CHUNKS) {
+        const int r = i / CHUNKS, c = i % CHUNKS;
+        const unsigned short* kp = reinterpret_cast<const unsigned short*>(&st_k[it]);
+        const unsigned short* vp = reinterpret_cast<const unsigned short*>(&st_v[it]);
+        uint4 kv4, vv4;
+        uint32_t* ko = reinterpret_cast<uint32_t*>(&kv4);
+        uint32_t* vo = reinterpret_cast<uint32_t*>(&vv4);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float2 kk = fp8x2_to_float2(kp[e]);
+          const float2 vv = fp8x2_to_float2(vp[e]);
+          ko[e] = pack_bf16(kk.x * st_ks[it], kk.y * st_ks[it]);
+          vo[e] = pack_bf16(vv.x * st_vs[it], vv.y * st_vs[it]);
+        }
+        *reinterpret_cast<uint4*>(Kd + r * LDS + c * 8) = kv4;
+        *reinterpret_cast<uint4*>(Vd + r * LDS + c * 8) = vv4;
+      }
+    }
+  };
+
+  if (MODE == 2) {
+    fetch_fp8(0);
+    stash_fp8(0);
+  } else {
+    issue_async(0, 0);
   }
+
   float o[HD / 8][4];
 #pragma unroll
   for (int i = 0; i < HD / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.0f;
   float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.0f, 0.0f};
   const float sl2 = a.scale * 1.4426950408889634f;
-
-  int kv_end = kv_len;
-  if (a.causal) kv_end = min(kv_len, pos_off + min(q0 + BM, q_len));
-  const int n_tiles = (kv_end + BN - 1) / BN;
-  const int* bt = (MODE == 0) ? nullptr : a.block_tables + (size_t)seq * a.max_blocks;
+  const int q_r = warp * 16 + (lane & 7) + 8 * ((lane >> 3) & 1);
+  const int q_c = 8 * (lane >> 4);
+  const int warp_last_row = q0 + warp * 16 + 15;  // last query row of this warp (local index)
 
   for (int tile = 0; tile < n_tiles; ++tile) {
+    const int buf = tile & 1;
     const int j0 = tile * BN;
-    __syncthreads();  // previous tile fully consumed
-    for (int i = tid; i < BN * CHUNKS; i += 128) {
-      const int r = i / CHUNKS, c = i % CHUNKS;
-      const int j = j0 + r;
-      uint4 kv4 = make_uint4(0, 0, 0, 0), vv4 = make_uint4(0, 0, 0, 0);
-      if (j < kv_len) {
-        if (MODE == 0) {
-          const size_t off = (size_t)(q_start + j) * a.kv_stride + (size_t)kvh * HD_REAL + c * 8;
-          kv4 = *reinterpret_cast<const uint4*>(a.k + off);
-          vv4 = *reinterpret_cast<const uint4*>(a.v + off);
-        } else {
-          const int blk = bt[j / a.page];
-          if (blk >= 0) {
-            const size_t row = ((size_t)blk * a.Hkv + kvh) * a.page + (j % a.page);
-            if (MODE == 1) {
-              kv4 = *reinterpret_cast<const uint4*>(reinterpret_cast<const bf16*>(a.k_cache) + row * HD_REAL + c * 8);
-              vv4 = *reinterpret_cast<const uint4*>(reinterpret_cast<const bf16*>(a.v_cache) + row * HD_REAL + c * 8);
-            } else {
-              const uint2 k8 = *reinterpret_cast<const uint2*>(reinterpret_cast<const uint8_t*>(a.k_cache) + row * HD_REAL + c * 8);
-              const uint2 v8 = *reinterpret_cast<const uint2*>(reinterpret_cast<const uint8_t*>(a.v_cache) + row * HD_REAL + c * 8);
-              const float ks = a.k_scale ? a.k_scale[row] : 1.0f;
-              const float vs = a.v_scale ? a.v_scale[row] : 1.0f;
-              const unsigned short* kp = reinterpret_cast<const unsigned short*>(&k8);
-              const unsigned short* vp = reinterpret_cast<const unsigned short*>(&v8);
-              uint32_t* ko = reinterpret_cast<uint32_t*>(&kv4);
-              uint32_t* vo = reinterpret_cast<uint32_t*>(&vv4);
+    if (MODE != 2) cp_async_wait_all();
+    __syncthreads();  // this tile is in shared memory; everyone is done with the other buffer
+    const bool more = tile + 1 < n_tiles;
+    if (more) {
+      if (MODE == 2) fetch_fp8(tile + 1);
+      else issue_async(tile + 1, buf ^ 1);
+    }
+    // a warp whose rows all lie before this tile's first key has nothing to add (causal)
+    const bool active = !(a.causal && j0 > pos_off + warp_last_row) && (q0 + warp * 16 < q_len);
+    if (active) {
+      const bf16* Ks = KV + (size_t)(buf * 2) * BN * LDS;
+      const bf16* Vs = Ks + BN * LDS;
+      // S = Q K^T  (16 x 64 per warp)
+      float s[BN / 8][4];
 #pragma unroll
-              for (int e = 0; e < 4; ++e) {
-                const float2 kk = fp8x2_to_float2(kp[e]);
-                const float2 vv = fp8x2_to_float2(vp[e]);
-                ko[e] = pack_bf16(kk.x * ks, kk.y * ks);
-                vo[e] = pack_bf16(vv.x * vs, vv.y * vs);
-              }
-            }
+      for (int i = 0; i < BN / 8; ++i) s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.0f;
+#pragma unroll
+      for (int kk = 0; kk < HD / 16; ++kk) {
+        uint32_t qf[4];
+        ldsm_x4(qf, smem_u32(Qs + q_r * LDS + kk * 16 + q_c));
+#pragma unroll
+        for (int np = 0; np < BN / 16; ++np) {
+          uint32_t kb[4];
+          const int n = np * 16 + (lane & 7) + 8 * (lane >> 4);
+          const int c = kk * 16 + 8 * ((lane >> 3) & 1);
+          ldsm_x4(kb, smem_u32(Ks + n * LDS + c));
+          mma_bf16(s[2 * np], qf, kb[0], kb[1]);
+          mma_bf16(s[2 * np + 1], qf, kb[2], kb[3]);
+        }
+      }
+      // mask + online softmax (rows g and g+8 of this warp's 16-row slab)
+      const int row0 = q0 + warp * 16 + g;
+      const bool need_mask = (j0 + BN > kv_len) || (a.causal && (j0 + BN - 1 > pos_off + q0 + warp * 16));
+      float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+      for (int i = 0; i < BN / 8; ++i) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          float v = s[i][e] * sl2;
+          if (need_mask) {
+            const int col = j0 + i * 8 + t4 * 2 + (e & 1);
+            const int row = row0 + ((e >> 1) ? 8 : 0);
+            if (col >= kv_len || (a.causal && col > pos_off + row)) v = -INFINITY;
           }
+          s[i][e] = v;
+          mx[e >> 1] = fmaxf(mx[e >> 1], v);
         }
       }
-      *reinterpret_cast<uint4*>(Ks + r * LDS + c * 8) = kv4;
-      *reinterpret_cast<uint4*>(Vs + r * LDS + c * 8) = vv4;
-    }
-    __syncthreads();
-
-    // S = Q K^T  (16 x 64 per warp)
-    float s[BN / 8][4];
+      float corr[2], m_use[2];
 #pragma unroll
-    for (int i = 0; i < BN / 8; ++i) s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.0f;
-#pragma unroll
-    for (int kk = 0; kk < HD / 16; ++kk) {
-#pragma unroll
-      for (int np = 0; np < BN / 16; ++np) {
-        uint32_t kb[4];
-        const int n = np * 16 + (lane & 7) + 8 * (lane >> 4);
-        const int c = kk * 16 + 8 * ((lane >> 3) & 1);
-        ldsm_x4(kb, smem_u32(Ks + n * LDS + c));
-        mma_bf16(s[2 * np], qf[kk], kb[0], kb[1]);
-        mma_bf16(s[2 * np + 1], qf[kk], kb[2], kb[3]);
+      for (int r = 0; r < 2; ++r) {
+        mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
+        mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
+        const float mn = fmaxf(m_run[r], mx[r]);
+        m_use[r] = (mn == -INFINITY) ? 0.0f : mn;
+        corr[r] = (m_run[r] == -INFINITY) ? 0.0f : ex2_fast(m_run[r] - m_use[r]);
+        m_run[r] = mn;
       }
-    }
-    // mask + online softmax (rows g and g+8 of this warp's 16-row slab)
-    const int row0 = q0 + warp * 16 + g;
-    const bool need_mask = (j0 + BN > kv_len) || (a.causal && (j0 + BN - 1 > pos_off + q0 + warp * 16));
-    float mx[2] = {-INFINITY, -INFINITY};
+      float rs[2] = {0.0f, 0.0f};
 #pragma unroll
-    for (int i = 0; i < BN / 8; ++i) {
+      for (int i = 0; i < BN / 8; ++i) {
 #pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        float v = s[i][e] * sl2;
-        if (need_mask) {
-          const int col = j0 + i * 8 + t4 * 2 + (e & 1);
-          const int row = row0 + ((e >> 1) ? 8 : 0);
-          if (col >= kv_len || (a.causal && col > pos_off + row)) v = -INFINITY;
+        for (int e = 0; e < 4; ++e) {
+          const float p = ex2_fast(s[i][e] - m_use[e >> 1]);
+          s[i][e] = p;
+          rs[e >> 1] += p;
         }
-        s[i][e] = v;
-        mx[e >> 1] = fmaxf(mx[e >> 1], v);
+      }
+#pragma unroll
+      for (int r = 0; r < 2; ++r) {
+        rs[r] += __shfl_xor_sync(0xffffffffu, rs[r], 1);
+        rs[r] += __shfl_xor_sync(0xffffffffu, rs[r], 2);
+        l_run[r] = l_run[r] * corr[r] + rs[r];
+      }
+#pragma unroll
+      for (int i = 0; i < HD / 8; ++i) {
+        o[i][0] *= corr[0];
+        o[i][1] *= corr[0];
+        o[i][2] *= corr[1];
+        o[i][3] *= corr[1];
+      }
+      // O += P V
+#pragma unroll
+      for (int kt = 0; kt < BN / 16; ++kt) {
+        uint32_t pa[4];
+        pa[0] = pack_bf16(s[2 * kt][0], s[2 * kt][1]);
+        pa[1] = pack_bf16(s[2 * kt][2], s[2 * kt][3]);
+        pa[2] = pack_bf16(s[2 * kt + 1][0], s[2 * kt + 1][1]);
+        pa[3] = pack_bf16(s[2 * kt + 1][2], s[2 * kt + 1][3]);
+#pragma unroll
+        for (int dp = 0; dp < HD / 16; ++dp) {
+          uint32_t vb[4];
+          const int tok = kt * 16 + (lane & 7) + 8 * ((lane >> 3) & 1);
+          const int d = dp * 16 + 8 * (lane >> 4);
+          ldsm_x4_t(vb, smem_u32(Vs + tok * LDS + d));
+          mma_bf16(o[2 * dp], pa, vb[0], vb[1]);
+          mma_bf16(o[2 * dp + 1], pa, vb[2], vb[3]);
+        }
       }
     }
-    float corr[2], m_use[2];
-#pragma unroll
-    for (int r = 0; r < 2; ++r) {
-      mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
-      mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
-      const float mn = fmaxf(m_run[r], mx[r]);
-      m_use[r] = (mn == -INFINITY) ? 0.0f : mn;
-      corr[r] = (m_run[r] == -INFINITY) ? 0.0f : exp2f(m_run[r] - m_use[r]);
-      m_run[r] = mn;
-    }
-    float rs[2] = {0.0f, 0.0f};
-#pragma unroll
-    for (int i = 0; i < BN / 8; ++i) {
-#pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        const float p = exp2f(s[i][e] - m_use[e >> 1]);
-        s[i][e] = p;
-        rs[e >> 1] += p;
-      }
-    }
-#pragma unroll
-    for (int r = 0; r < 2; ++r) {
-      rs[r] += __shfl_xor_sync(0xffffffffu, rs[r], 1);
-      rs[r] += __shfl_xor_sync(0xffffffffu, rs[r], 2);
-      l_run[r] = l_run[r] * corr[r] + rs[r];
-    }
-#pragma unroll
-    for (int i = 0; i < HD / 8; ++i) {
-      o[i][0] *= corr[0];
-      o[i][1] *= corr[0];
-      o[i][2] *= corr[1];
-      o[i][3] *= corr[1];
-    }
-    // O += P V
-#pragma unroll
-    for (int kt = 0; kt < BN / 16; ++kt) {
-      uint32_t pa[4];
-      pa[0] = pack_bf16(s[2 * kt][0], s[2 * kt][1]);
-      pa[1] = pack_bf16(s[2 * kt][2], s[2 * kt][3]);
-      pa[2] = pack_bf16(s[2 * kt + 1][0], s[2 * kt + 1][1]);
-      pa[3] = pack_bf16(s[2 * kt + 1][2], s[2 * kt + 1][3]);
-#pragma unroll
-      for (int dp = 0; dp < HD / 16; ++dp) {
-        uint32_t vb[4];
-        const int tok = kt * 16 + (lane & 7) + 8 * ((lane >> 3) & 1);
-        const int d = dp * 16 + 8 * (lane >> 4);
-        ldsm_x4_t(vb, smem_u32(Vs + tok * LDS + d));
-        mma_bf16(o[2 * dp], pa, vb[0], vb[1]);
-        mma_bf16(o[2 * dp + 1], pa, vb[2], vb[3]);
-      }
-    }
+    if (MODE == 2 && more) stash_fp8(buf ^ 1);
   }
   // normalise and store
 #pragma unroll
@@ -791,25 +873,35 @@ __global__ void __launch_bounds__(128) paged_decode_mma_kernel(const DecodeArgs 
   }
 }
 
-template <int HD, int HD_REAL, int MODE>
-int launch_flash(const FlashArgs& a, int max_q_tiles, int S, cudaStream_t stream, bool pdl) {
-  const size_t smem = (size_t)(64 + 2 * 64) * (HD + 8) * sizeof(bf16);
+template <int HD, int HD_REAL, int MODE, int BM>
+int launch_flash(const FlashArgs& a, int max_q_len, int S, cudaStream_t stream, bool pdl) {
+  const size_t smem = (size_t)(BM + 4 * 64) * (HD + 8) * sizeof(bf16);
   static bool configured = false;
   if (!configured && smem > 48 * 1024) {
-    cudaError_t e = cudaFuncSetAttribute(flash_fwd_kernel<HD, HD_REAL, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaError_t e = cudaFuncSetAttribute(flash_fwd_kernel<HD, HD_REAL, MODE, BM>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
-  return (int)prism_launch(flash_fwd_kernel<HD, HD_REAL, MODE>, dim3(max_q_tiles, a.Hq, S), dim3(128), smem, stream, pdl, a);
+  const int tiles = (max_q_len + BM - 1) / BM;
+  return (int)prism_launch(flash_fwd_kernel<HD, HD_REAL, MODE, BM>, dim3(tiles, a.Hq, S), dim3(BM * 2), smem, stream, pdl, a);
 }
 
 template <int MODE>
-int dispatch_flash(const FlashArgs& a, int hd, int max_q_tiles, int S, cudaStream_t stream, bool pdl) {
+int dispatch_flash(const FlashArgs& a, int hd, int max_q_len, int S, cudaStream_t stream, bool pdl) {
+  // 128 query rows per CTA halve the K/V traffic per query; short sequences keep 64 so that
+  // more CTAs exist
+  const bool wide = max_q_len > 256;
   switch (hd) {
-    case 128: return launch_flash<128, 128, MODE>(a, max_q_tiles, S, stream, pdl);
-    case 64: return launch_flash<64, 64, MODE>(a, max_q_tiles, S, stream, pdl);
-    case 72: return launch_flash<80, 72, MODE>(a, max_q_tiles, S, stream, pdl);
-    case 32: return launch_flash<32, 32, MODE>(a, max_q_tiles, S, stream, pdl);
+    case 128:
+      return wide ? launch_flash<128, 128, MODE, 128>(a, max_q_len, S, stream, pdl)
+                  : launch_flash<128, 128, MODE, 64>(a, max_q_len, S, stream, pdl);
+    case 64:
+      return wide ? launch_flash<64, 64, MODE, 128>(a, max_q_len, S, stream, pdl)
+                  : launch_flash<64, 64, MODE, 64>(a, max_q_len, S, stream, pdl);
+    case 72:
+      return wide ? launch_flash<80, 72, MODE, 128>(a, max_q_len, S, stream, pdl)
+                  : launch_flash<80, 72, MODE, 64>(a, max_q_len, S, stream, pdl);
+    case 32: return launch_flash<32, 32, MODE, 64>(a, max_q_len, S, stream, pdl);
   }
   return -2;
 }
@@ -923,12 +1015,11 @@ PRISM_API int prism_flash_attention(const void* q, long long q_stride, void* out
   a.Hkv = Hkv;
   a.causal = causal;
   a.scale = scale;
-  const int tiles = (max_q_len + 63) / 64;
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   switch (mode) {
-    case 0: return dispatch_flash<0>(a, hd, tiles, S, s, pdl != 0);
-    case 1: return dispatch_flash<1>(a, hd, tiles, S, s, pdl != 0);
-    case 2: return dispatch_flash<2>(a, hd, tiles, S, s, pdl != 0);
+    case 0: return dispatch_flash<0>(a, hd, max_q_len, S, s, pdl != 0);
+    case 1: return dispatch_flash<1>(a, hd, max_q_len, S, s, pdl != 0);
+    case 2: return dispatch_flash<2>(a, hd, max_q_len, S, s, pdl != 0);
   }
   return -3;
 }

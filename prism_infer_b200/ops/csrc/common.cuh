@@ -61,9 +61,17 @@ __device__ __forceinline__ float warp_max(float v) {
   for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
   return v;
 }
+// tanh.approx.f32 is one MUFU instruction with about 2^-11 relative error, far below the
+// bf16 rounding of the result; the library tanhf costs tens of instructions per element,
+// which made the GELU epilogue of the vision MLP longer than its main loop.
+__device__ __forceinline__ float tanh_fast(float x) {
+  float y;
+  asm("tanh.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
 __device__ __forceinline__ float gelu_tanh(float x) {
   const float k0 = 0.7978845608028654f, k1 = 0.044715f;
-  return 0.5f * x * (1.0f + tanhf(k0 * (x + k1 * x * x * x)));
+  return 0.5f * x * (1.0f + tanh_fast(k0 * (x + k1 * x * x * x)));
 }
 __device__ __forceinline__ float gelu_erf(float x) {
   return 0.5f * x * (1.0f + erff(x * 0.7071067811865476f));

@@ -220,6 +220,7 @@ struct QkvArgs {
   int kv_mode;              // 0 bf16, 1 fp8 unit scale, 2 fp8 + per-token-per-head scale
   int apply_norm, apply_rope;
   float eps;
+  int k_writeback;          // 1: the normalised, rotated K also replaces its source in qkv (bf16 source only)
   int real_ctas;
   PrefetchSpec pf;
 };
@@ -306,6 +307,15 @@ __global__ void __launch_bounds__(256) qk_norm_rope_store_kernel(const QkvArgs a
       }
     }
     return;
+  }
+  if (is_k && a.k_writeback && a.qkv != nullptr) {
+    // prefill without history attends over these bf16 rows directly instead of the paged copy
+    bf16* dst = const_cast<bf16*>(a.qkv) + src;
+#pragma unroll
+    for (int j = 0; j < PER; ++j) {
+      dst[lane + 32 * j] = f2b(lo[j]);
+      dst[lane + 32 * j + D / 2] = f2b(hi[j]);
+    }
   }
   const long long slot = a.slots[t];
   if (slot < 0) return;
@@ -523,7 +533,8 @@ PRISM_API int prism_qk_norm_rope_store(const void* qkv, const void* partials, lo
                                        const void* k_weight, const void* inv_freq, const void* axis, void* q_out,
                                        long long q_stride, const void* slots, void* k_cache, void* v_cache,
                                        void* k_scale, void* v_scale, int T, int Hq, int Hkv, int D, int page,
-                                       int kv_mode, int apply_norm, int apply_rope, float eps, void* stream, int pdl) {
+                                       int kv_mode, int apply_norm, int apply_rope, float eps, int k_writeback,
+                                       void* stream, int pdl) {
   if (T <= 0) return 0;
   QkvArgs a;
   a.qkv = (const bf16*)qkv;
@@ -551,6 +562,7 @@ PRISM_API int prism_qk_norm_rope_store(const void* qkv, const void* partials, lo
   a.apply_norm = apply_norm;
   a.apply_rope = apply_rope;
   a.eps = eps;
+  a.k_writeback = k_writeback;
   a.pf = prism_take_prefetch();
   const int warps = T * (Hq + 2 * Hkv);
   const int wpb = 8;

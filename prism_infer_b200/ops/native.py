@@ -31,7 +31,7 @@ _SIGNATURES = {
     "prism_gemm_clear_tensor_maps": "",
     "prism_add_rmsnorm": "plipppppppiifpi",
     "prism_layernorm": "ppppiifpi",
-    "prism_qk_norm_rope_store": "pplilpppppplpppppiiiiiiiifpi",
+    "prism_qk_norm_rope_store": "pplilpppppplpppppiiiiiiiifipi",
     "prism_swiglu": "pplipiipi",
     "prism_embed": "pppppiillpi",
     "prism_indexed_add": "pppiipi",
