@@ -354,6 +354,11 @@ _RANDOM_ARCHS = {
     "tiny": Qwen3VLArch.tiny,
     "qwen3-vl-8b": Qwen3VLArch.qwen3_vl_8b,
     "qwen3_vl_8b": Qwen3VLArch.qwen3_vl_8b,
+    # profiling aids: the language-model compute of ONE rank of an n-way tensor-parallel group
+    # (heads, KV heads, MLP width and vocabulary divided by n), run without any exchange
+    "qwen3-vl-8b-tp2-shard": lambda: Qwen3VLArch.qwen3_vl_8b().rank_shard(2),
+    "qwen3-vl-8b-tp4-shard": lambda: Qwen3VLArch.qwen3_vl_8b().rank_shard(4),
+    "qwen3-vl-8b-tp8-shard": lambda: Qwen3VLArch.qwen3_vl_8b().rank_shard(8),
 }
 
 

@@ -141,6 +141,17 @@ class Qwen3VLArch:
     def qwen3_vl_8b(cls) -> "Qwen3VLArch":
         return cls()
 
+    def rank_shard(self, n: int) -> "Qwen3VLArch":
+        """Architecture whose language model equals one rank's share of an ``n``-way
+        tensor-parallel split (for single-GPU profiling of the per-rank kernel chain)."""
+        import dataclasses
+
+        validate_tensor_parallel(self, n)
+        t = self.text
+        text = dataclasses.replace(t, num_heads=t.num_heads // n, num_kv_heads=t.num_kv_heads // n,
+                                   intermediate_size=t.intermediate_size // n, vocab_size=t.vocab_size // n)
+        return dataclasses.replace(self, text=text)
+
     @classmethod
     def tiny(cls) -> "Qwen3VLArch":
         """The small CPU test model: 2+2 layers, hidden 256/128, head_dim 64."""
