@@ -8,7 +8,7 @@ Launch with one process per GPU:
 Cases (Qwen3-VL-8B shapes, tensor-parallel over N ranks):
 
 * ``o_proj`` / ``down_proj`` row-parallel GEMM -> one-shot exchange -> residual add + RMSNorm
-  (``prism_gemm_wx_push`` + ``prism_add_rmsnorm_wait``) for T in {1, 8, 32, 128} tokens,
+  (``prism_gemm_wx_push`` + ``prism_add_rmsnorm_packed``) for T in {1, 8, 32, 128} tokens,
   versus split-K GEMM + ``dist.all_reduce`` + add+RMSNorm.
 * vision merger GEMM -> all-gather (``prism_gemm_wx_allgather``) for 196 and 1568 tokens,
   versus GEMM + ``dist.all_gather``.

@@ -435,7 +435,8 @@ class Qwen3VLModel:
         dense, partials, ticket = x, None, None
         n_deep = len(deepstack) if deepstack is not None else 0
         # at most four tokens on CUDA: residual add + RMSNorm run inside the next projection
-        fuse_norm = x.is_cuda and ops.NORMX_ENABLED and T <= ops.NORMX_MAX_TOKENS and n_deep == 0 and self.H % 64 == 0
+        fuse_norm = (x.is_cuda and ops.NORMX_ENABLED and self.tp == 1 and T <= ops.NORMX_MAX_TOKENS and n_deep == 0
+                     and self.H % 64 == 0)
         if fuse_norm:
             res_bufs = [torch.empty((T, self.H), dtype=torch.bfloat16, device=x.device) for _ in range(2)]
             flip = 0

@@ -395,6 +395,9 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
       else if (a.out_f32) mode = EPI_F32;
       else mode = (a.bias == nullptr && a.act == 0 && a.residual == nullptr) ? EPI_BF16_PLAIN : EPI_BF16_FULL;
       const int n_valid = min(BN, a.T - n0);
+      unsigned long long push_seq = 0;
+      if (mode == EPI_PUSH_F32)
+        push_seq = (((a.epoch ? *a.epoch : 0ull) + (unsigned long long)a.point) & 0xffffffffull) << 32;
       for (int c0 = 0; c0 < n_valid; c0 += 16) {
         uint32_t r[16];
         uint32_t r2[16];
@@ -435,12 +438,20 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
             break;
           }
           case EPI_PUSH_F32: {
+            // one 8-byte store per element: fp32 value in the low half, the exchange's sequence
+            // number in the high half.  An aligned 8-byte store is single-copy atomic, so a
+            // consumer that sees the expected sequence number also sees the value; no fence,
+            // counter or flag is needed on this path.
             const size_t off = (size_t)(a.my_rank * (int)gridDim.z + split) * a.split_stride + row0 * a.ldo + m;
             for (int p = 0; p < a.n_peers; ++p) {
-              float* dst = a.peer_out[p] + off;
+              unsigned long long* dst = reinterpret_cast<unsigned long long*>(a.peer_out[p]) + off;
 #pragma unroll
-              for (int j = 0; j < 16; ++j)
-                if (j < cols) dst[(size_t)j * a.ldo] = __uint_as_float(r[j]);
+              for (int j = 0; j < 16; ++j) {
+                if (j < cols) {
+                  const unsigned long long word = push_seq | (unsigned long long)r[j];
+                  asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(dst + (size_t)j * a.ldo), "l"(word) : "memory");
+                }
+              }
             }
             break;
           }
@@ -479,19 +490,22 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
       }
     }
   }
-  if (a.n_peers > 0 && warp >= 2) __threadfence_system();  // partial tiles visible to every GPU
+  const bool flagged = a.n_peers > 0 && a.push_rows;  // the all-gather form signals with flags
+  if (flagged && warp >= 2) __threadfence_system();  // this CTA's rows visible to every GPU
   tc_fence_before();
   __syncthreads();
   if (warp == 1) tmem_dealloc(tmem_base, TMEM_COLS);
-  if (a.n_peers > 0 && threadIdx.x == 0) {
+  if (flagged && threadIdx.x == 0) {
     const int total = gridDim.x * gridDim.y * gridDim.z;
     const int old = atomicAdd(a.cta_counter, 1);
     if (old == total - 1) {
       *a.cta_counter = 0;
       __threadfence_system();
+      // one fence above, then plain posted stores: a release store per peer would serialise
+      // one NVLink round trip per peer
       const unsigned long long seq = (a.epoch ? *a.epoch : 0ull) + (unsigned long long)a.point;
       for (int p = 0; p < a.n_peers; ++p) {
-        asm volatile("st.release.sys.global.u64 [%0], %1;" ::"l"(a.peer_flag[p] + a.my_rank), "l"(seq) : "memory");
+        asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(a.peer_flag[p] + a.my_rank), "l"(seq) : "memory");
       }
     }
   }
@@ -1024,9 +1038,11 @@ PRISM_API int prism_gemm_wx(const void* W, const void* X, void* out, int M, int 
 
 // Fused row-parallel GEMM -> one-shot exchange: the fp32 partial of rank `my_rank`, split s,
 // lands in slab (my_rank * splits + s) of every rank's buffer (peer_out[p], p < n_peers, own
-// rank included; row stride ldo, slab stride split_stride elements), then flag[my_rank] on
-// every rank is set to *epoch + point.  peer_out / peer_flag are host arrays of device
-// pointers (peer-mapped through CUDA IPC).  The consumer is prism_add_rmsnorm_wait.
+// rank included; row stride ldo, slab stride split_stride, both in 8-byte elements).  Every
+// element is one 8-byte word {fp32 value, low 32 bits of *epoch + point}; the consumer
+// (prism_add_rmsnorm_packed) polls the words themselves, so there is no fence, counter or
+// flag on this path (peer_flag and cta_counter are unused).  peer_out is a host array of
+// device pointers (peer-mapped through CUDA IPC).
 PRISM_API int prism_gemm_wx_push(const void* W, const void* X, int M, int T, int K, long long ldw, long long ldx,
                                  long long ldo, int w_rows_total, int splits, long long split_stride,
                                  const void* const* peer_out, const void* const* peer_flag, int n_peers, int my_rank,

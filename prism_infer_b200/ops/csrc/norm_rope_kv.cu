@@ -60,6 +60,7 @@ struct AddNormArgs {
   const unsigned long long* epoch;
   int point;
   int T;
+  int packed;  // 1: partials are 8-byte {fp32 value, sequence} words polled until sequence == *epoch + point
   PrefetchSpec pf;
 };
 
@@ -101,7 +102,40 @@ __global__ void __launch_bounds__(1024) add_rmsnorm_kernel(const AddNormArgs a) 
   // independent, so a single small-batch row keeps P * 16 bytes per thread in flight.
   for (int i = threadIdx.x * 4; i < H; i += blockDim.x * 4) {
     float d[4];
-    if (a.P > 0) {
+    if (a.P > 0 && a.packed) {
+      // Packed exchange slabs: sum optimistically with every load in flight, and repeat the
+      // pass while any word still carries an older sequence number (bounded).
+      const unsigned long long* q0 = reinterpret_cast<const unsigned long long*>(a.partials) + base + i;
+      const unsigned int want = (unsigned int)((*a.epoch + (unsigned long long)a.point) & 0xffffffffull);
+      const long long t0 = clock64();
+      float4 acc;
+      for (;;) {
+        acc = make_float4(0.f, 0.f, 0.f, 0.f);
+        unsigned int stale = 0;
+#pragma unroll 8
+        for (int p = 0; p < a.P; ++p) {
+          unsigned long long w0, w1, w2, w3;
+          const unsigned long long* src = q0 + (size_t)p * a.slab_stride;
+          asm volatile("ld.relaxed.sys.global.v2.u64 {%0, %1}, [%2];" : "=l"(w0), "=l"(w1) : "l"(src) : "memory");
+          asm volatile("ld.relaxed.sys.global.v2.u64 {%0, %1}, [%2];" : "=l"(w2), "=l"(w3) : "l"(src + 2) : "memory");
+          stale |= ((unsigned int)(w0 >> 32) ^ want) | ((unsigned int)(w1 >> 32) ^ want) |
+                   ((unsigned int)(w2 >> 32) ^ want) | ((unsigned int)(w3 >> 32) ^ want);
+          acc.x += __uint_as_float((unsigned int)w0);
+          acc.y += __uint_as_float((unsigned int)w1);
+          acc.z += __uint_as_float((unsigned int)w2);
+          acc.w += __uint_as_float((unsigned int)w3);
+        }
+        if (stale == 0) break;
+        if (clock64() - t0 > PRISM_WAIT_CYCLES) {
+          prism_report(PRISM_ERR_PEER_TIMEOUT, (int)threadIdx.x);
+          break;
+        }
+      }
+      d[0] = bf16_round(acc.x);
+      d[1] = bf16_round(acc.y);
+      d[2] = bf16_round(acc.z);
+      d[3] = bf16_round(acc.w);
+    } else if (a.P > 0) {
       float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
       const float* p0 = a.partials + base + i;
 #pragma unroll 8
@@ -468,10 +502,12 @@ __global__ void __launch_bounds__(256) vit_rope_kernel(bf16* qkv, const int* coo
 static int add_rmsnorm_impl(const void* partials, long long slab_stride, int P, const void* x_in,
                             const void* residual_in, void* residual_out, const void* extra, const void* extra_index,
                             const void* weight, void* out, int T, int H, float eps, void* stream, int pdl,
-                            const void* wait_flags, int n_wait, const void* epoch, int point) {
+                            const void* wait_flags, int n_wait, const void* epoch, int point, int packed = 0) {
   if (T <= 0) return 0;
   if (H % 4) return -1;
+  if (packed && (epoch == nullptr || P <= 0)) return -3;
   AddNormArgs a;
+  a.packed = packed;
   a.partials = (const float*)partials;
   a.slab_stride = slab_stride;
   a.P = P;
@@ -518,6 +554,17 @@ PRISM_API int prism_add_rmsnorm_wait(const void* partials, long long slab_stride
                                      const void* epoch, int point, void* stream, int pdl) {
   return add_rmsnorm_impl(partials, slab_stride, P, nullptr, residual_in, residual_out, extra, extra_index, weight, out, T,
                           H, eps, stream, pdl, wait_flags, n_wait, epoch, point);
+}
+
+// Consumer of prism_gemm_wx_push: partials are 8-byte {fp32 value, sequence} words (strides in
+// 8-byte elements) that are polled (bounded) until every sequence equals the low 32 bits of
+// *epoch + point, then summed in slab order.
+PRISM_API int prism_add_rmsnorm_packed(const void* partials, long long slab_stride, int P, const void* residual_in,
+                                       void* residual_out, const void* extra, const void* extra_index,
+                                       const void* weight, void* out, int T, int H, float eps, const void* epoch,
+                                       int point, void* stream, int pdl) {
+  return add_rmsnorm_impl(partials, slab_stride, P, nullptr, residual_in, residual_out, extra, extra_index, weight, out, T,
+                          H, eps, stream, pdl, nullptr, 0, epoch, point, 1);
 }
 
 PRISM_API int prism_layernorm(const void* x, const void* w, const void* b, void* out, int T, int H, float eps,

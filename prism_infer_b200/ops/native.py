@@ -45,6 +45,7 @@ _SIGNATURES = {
     "prism_merge_candidates": "pppiipi",
     "prism_gemm_wx_push": "ppiiillliilppiilppiipi",
     "prism_add_rmsnorm_wait": "plippppppiifpipipi",
+    "prism_add_rmsnorm_packed": "plippppppiifpipi",
     "prism_gemm_wx_normx": "ppiiilliiiiilplippppfpilpipi",
     "prism_gemm_set_small_tile_smem_cap": "i",
     "prism_gemm_set_persistent_min_tokens": "i",

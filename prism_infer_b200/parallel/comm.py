@@ -5,10 +5,13 @@
   all-reduce and distributed greedy arg-max, ``prism_infer/layers/embed_head.py:49-125``).
 * ``FusedComm``: the product path for decode-sized steps (at most 128 tokens).  The
   row-parallel GEMM writes its fp32 partial tiles straight into every rank's slab buffer
-  over NVLink from its epilogue and raises a per-rank flag (``prism_gemm_wx_push``); the
-  following add+RMSNorm kernel waits on the flags, sums the ``tp * splits`` slabs in rank
-  order (bitwise identical on every rank) and normalises (``prism_add_rmsnorm_wait``).  No
-  NCCL call, no separate all-reduce kernel, two exchange slots used alternately.  The
+  over NVLink from its epilogue, each element as one 8-byte word {value, sequence number}
+  (``prism_gemm_wx_push``); the following add+RMSNorm kernel polls the words until they
+  carry this exchange's sequence number, sums the ``tp * splits`` slabs in rank order
+  (bitwise identical on every rank) and normalises (``prism_add_rmsnorm_packed``).  No NCCL
+  call, no separate all-reduce kernel, no fence or flag round trip; two exchange slots are
+  used alternately (a rank can only reach the next use of a slot after every peer has
+  consumed the previous one, because the exchange in between needs all peers' data).  The
   greedy token is agreed on by a one-kernel (value, id) exchange.  Prefill-sized steps fall
   back to the NCCL path.
 """
@@ -146,21 +149,18 @@ class FusedComm(NcclComm):
         out = torch.empty((T, H), dtype=torch.bfloat16, device=weight.device)
         new_res = residual if residual is not None else torch.empty((T, H), dtype=torch.bfloat16, device=weight.device)
         native.call(
-            "prism_add_rmsnorm_wait", r.local(symm.OFF_SLABS + slot * r.slab_bytes), T * H, P,
+            "prism_add_rmsnorm_packed", r.local(symm.OFF_SLABS + slot * r.slab_bytes), T * H, P,
             None if residual is None else residual.data_ptr(), new_res.data_ptr(),
             None if extra is None else extra.data_ptr(), None if extra is None else extra_index.data_ptr(),
-            weight.data_ptr(), out.data_ptr(), T, H, float(eps), r.local(symm.OFF_FLAGS[slot]), self.size,
-            r.local(symm.OFF_EPOCH), point, torch.cuda.current_stream().cuda_stream, 1 if ops.pdl_enabled() else 0,
+            weight.data_ptr(), out.data_ptr(), T, H, float(eps), r.local(symm.OFF_EPOCH), point,
+            torch.cuda.current_stream().cuda_stream, 1 if ops.pdl_enabled() else 0,
         )
         return out, new_res
 
     def norm_source(self, dense, partials, ticket) -> dict:
         if ticket is None:
             return super().norm_source(dense, partials, None)
-        slot, point, P, T = ticket
-        r = self.region
-        return dict(partials_ptr=r.local(symm.OFF_SLABS + slot * r.slab_bytes), slab_stride=T * self.hidden, P=P,
-                    wait=(r.local(symm.OFF_FLAGS[slot]), self.size, point, r.local(symm.OFF_EPOCH)))
+        raise RuntimeError("the fused-norm GEMM prologue does not consume packed exchange slabs")
 
     def greedy_merge(self, local_val: torch.Tensor, local_id: torch.Tensor) -> torch.Tensor:
         B = local_val.shape[0]

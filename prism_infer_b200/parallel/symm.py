@@ -13,7 +13,7 @@ Region layout (bytes)::
     1024  CTA counter slot 0  i32                1280  CTA counter slot 1  i32
     1344  CTA counter of the vision all-gather  1536  vision flags: 2 sets x 4 outputs x u64[8]
     4096  arg-max values f32[8][BMAX]            then  arg-max ids i64[8][BMAX]
-    SLAB0 / SLAB1: two slab buffers of  tp * S_MAX * T_MAX * H  fp32 each
+    SLAB0 / SLAB1: two slab buffers of  tp * S_MAX * T_MAX * H  8-byte {fp32 value, sequence} words each
     VIS: 2 sets x 4 outputs x VIS_T_MAX x H bf16 (gathered merger outputs of the vision tower)
 """
 
@@ -71,7 +71,7 @@ class SymmetricRegion:
         import torch.distributed as dist
 
         lib = native.lib()
-        slab_bytes = size * S_MAX * T_MAX * hidden * 4
+        slab_bytes = size * S_MAX * T_MAX * hidden * 8
         nbytes = OFF_SLABS + 2 * slab_bytes + 2 * VIS_OUTPUTS * VIS_T_MAX * hidden * 2
         out = ctypes.c_void_p()
         _check(lib.prism_ipc_alloc(nbytes, ctypes.byref(out)), "prism_ipc_alloc")
@@ -95,7 +95,7 @@ class SymmetricRegion:
     def create_emulated(cls, size: int, hidden: int) -> list["SymmetricRegion"]:
         """All ranks' regions on the current device (single-GPU tests of the fused kernels)."""
         lib = native.lib()
-        slab_bytes = size * S_MAX * T_MAX * hidden * 4
+        slab_bytes = size * S_MAX * T_MAX * hidden * 8
         nbytes = OFF_SLABS + 2 * slab_bytes + 2 * VIS_OUTPUTS * VIS_T_MAX * hidden * 2
         ptrs = []
         for _ in range(size):
@@ -109,10 +109,11 @@ class SymmetricRegion:
         return torch.as_tensor(_DevView(self.local_ptr, self.nbytes), device="cuda")
 
     def slabs(self, slot: int, groups: int, tokens: int) -> torch.Tensor:
-        """Local fp32 view ``[groups, tokens, hidden]`` at the start of slab buffer ``slot``."""
+        """Local view ``[groups, tokens, hidden, 2]`` (fp32 value, int32 sequence as raw bits) at the
+        start of slab buffer ``slot``; ``[..., 0]`` are the values."""
         n = groups * tokens * self.hidden
-        raw = self.local_bytes()[OFF_SLABS + slot * self.slab_bytes: OFF_SLABS + slot * self.slab_bytes + n * 4]
-        return raw.view(torch.float32).view(groups, tokens, self.hidden)
+        raw = self.local_bytes()[OFF_SLABS + slot * self.slab_bytes: OFF_SLABS + slot * self.slab_bytes + n * 8]
+        return raw.view(torch.float32).view(groups, tokens, self.hidden, 2)
 
     def vis_offset(self, buffer_set: int, output: int) -> int:
         return OFF_SLABS + 2 * self.slab_bytes + (buffer_set * VIS_OUTPUTS + output) * VIS_T_MAX * self.hidden * 2

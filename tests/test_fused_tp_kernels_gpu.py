@@ -2,7 +2,7 @@
 
 On one GPU every rank's symmetric region is allocated on the same device and the ranks run
 one after another in one stream (all pushes before any wait), which exercises the exact
-kernels, pointer tables, slab indexing and flag sequence numbers without two kernels ever
+kernels, pointer tables, slab indexing and sequence numbers without two kernels ever
 waiting on each other.  The multi-GPU form (real peer memory over NVLink) runs when at
 least two devices are visible.
 """
@@ -58,7 +58,7 @@ def test_push_gemm_then_wait_norm_emulated_ranks(cuda_device, tp, T, K):
 
 
 def test_wait_that_never_completes_reports_status_and_returns(cuda_device):
-    """A flag nobody sets: the bounded wait runs out, the status word says so, the context
+    """Slabs nobody wrote: the bounded poll runs out, the status word says so, the context
     stays usable.  (The wait limit is about two seconds.)"""
     from prism_infer_b200.parallel import symm
     from prism_infer_b200.parallel.comm import FusedComm
