@@ -14,7 +14,7 @@ Cases (Qwen3-VL-8B shapes, tensor-parallel over N ranks):
   versus GEMM + ``dist.all_gather``.
 
 Each number is device time (CUDA events around ``iters`` back-to-back iterations, max over
-ranks).  Roofline per iteration = max(local weight + activation bytes / measured HBM
+ranks); the GEMM -> exchange cases are captured into a CUDA graph first, like a decode step.  Roofline per iteration = max(local weight + activation bytes / measured HBM
 bandwidth, bytes that must cross NVLink per rank / 770 GB/s, FLOPs / measured bf16 peak).
 """
 
@@ -37,16 +37,35 @@ from prism_infer_b200.parallel.comm import FusedComm, NcclComm  # noqa: E402
 NVLINK_GBS = 770.0
 
 
-def timed(fn, iters: int) -> float:
+def timed(fn, iters: int, graph: bool = False) -> float:
+    """Device time per call.  With ``graph`` the call is captured once into a CUDA graph and
+    replayed, as the decode step does, so host launch cost does not hide the kernels."""
     for _ in range(5):
         fn()
+    torch.cuda.synchronize()
+    if graph:
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.stream(side):
+            fn()
+            side.synchronize()
+            dist.barrier()
+            with torch.cuda.graph(g, stream=side):
+                fn()
+        torch.cuda.current_stream().wait_stream(side)
+        run = g.replay
+        for _ in range(3):
+            run()
+    else:
+        run = fn
     torch.cuda.synchronize()
     dist.barrier()
     torch.cuda.synchronize()
     s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     s.record()
     for _ in range(iters):
-        fn()
+        run()
     e.record()
     torch.cuda.synchronize()
     ms = torch.tensor([s.elapsed_time(e) / iters], device="cuda")
@@ -87,8 +106,8 @@ def main() -> None:
                     d, p, t = nccl.row_parallel(x, w)
                     nccl.add_rmsnorm(weight, 1e-6, d, p, t, res)
 
-            t_f = timed(run_fused, args.iters) / 2
-            t_n = timed(run_nccl, args.iters) / 2
+            t_f = timed(run_fused, args.iters, graph=True) / 2
+            t_n = timed(run_nccl, args.iters, graph=True) / 2
             local_bytes = H * K * 2 + T * K * 2
             link_bytes = T * H * 4 * (world - 1)  # fp32 partial rows pushed to every peer
             flops = 2.0 * T * H * K

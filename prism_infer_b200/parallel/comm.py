@@ -107,7 +107,9 @@ class FusedComm(NcclComm):
     def row_parallel(self, x: torch.Tensor, w: torch.Tensor):
         T, K = x.shape
         M = w.shape[0]
-        if T > SMALL_T or M != self.hidden or self.point >= symm.ARGMAX_POINT:
+        # every rank sends tp * splits * T rows of 8-byte words, so the one-shot exchange only wins
+        # while T * tp is small (measured: TP8 ties with NCCL at 32 tokens, TP2 wins up to 128)
+        if T > SMALL_T or T * self.size > 192 or M != self.hidden or self.point >= symm.ARGMAX_POINT:
             return super().row_parallel(x, w)
         splits = min(symm.S_MAX, ops.choose_splits(M, K, T))
         eff = ops.effective_splits(K, splits)
