@@ -18,8 +18,41 @@ from .contracts import BatchPlan, Phase
 from .sequence import Sequence
 
 
+def _pack_tensor(t: Optional[torch.Tensor]):
+    """Tensor -> picklable (numpy array, torch dtype name).  The default tensor pickle goes through
+    torch's storage serialisation (about 50 us per tensor each way); a numpy array is a memcpy,
+    which matters because these objects cross the tensor-parallel control plane every step."""
+    if t is None:
+        return None
+    t = t.detach().contiguous()
+    if t.dtype == torch.bfloat16:
+        return t.view(torch.int16).numpy(), "bfloat16"
+    return t.numpy(), None
+
+
+def _unpack_tensor(packed) -> Optional[torch.Tensor]:
+    if packed is None:
+        return None
+    arr, special = packed
+    t = torch.from_numpy(arr)
+    return t.view(torch.bfloat16) if special == "bfloat16" else t
+
+
+class _TensorStatePickle:
+    """Mixin: dataclass fields holding CPU tensors travel as numpy arrays."""
+
+    def __getstate__(self):
+        return {k: (("__tensor__", _pack_tensor(v)) if isinstance(v, torch.Tensor) else v) for k, v in self.__dict__.items()}
+
+    def __setstate__(self, state):
+        for k, v in state.items():
+            if isinstance(v, tuple) and len(v) == 2 and isinstance(v[0], str) and v[0] == "__tensor__":
+                v = _unpack_tensor(v[1])
+            self.__dict__[k] = v
+
+
 @dataclass
-class VisionJob:
+class VisionJob(_TensorStatePickle):
     """Patches one sequence still has to push through the vision tower."""
 
     seq_id: int
@@ -29,7 +62,7 @@ class VisionJob:
 
 
 @dataclass
-class StepInputs:
+class StepInputs(_TensorStatePickle):
     kind: str                              # "prefill" | "decode"
     input_ids: torch.Tensor                # [T] int64
     positions: torch.Tensor                # [3, T] int32

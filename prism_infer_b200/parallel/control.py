@@ -16,8 +16,13 @@ Segment layout (little-endian 64-bit words unless noted)::
     [2]   shutdown flag
     [3]   payload capacity in bytes        [4]   reply capacity per worker in bytes
     [8 + 8*r ...]  per-worker slot r: ack sequence, status (0 ok, 1 error), reply length
-    [HEADER ...]                       command payload (pickle)
+    [HEADER ...]                       command payload (see below)
     [HEADER + payload_cap + r*reply_cap ...]   reply area of worker r (pickle)
+
+Command payload: ``u64 n_buffers, u64 pickle_length, u64 size[n_buffers]``, the pickle
+(protocol 5), then every out-of-band buffer at a 64-byte boundary.  Arrays of 64 KiB and more
+(pixel patches of a prefill) travel out of band: the driver copies them into the segment once
+and the workers unpickle zero-copy views of the segment, valid until they acknowledge.
 """
 
 from __future__ import annotations
@@ -113,6 +118,51 @@ class ControlSegment:
             pass
 
 
+OUT_OF_BAND_MIN_BYTES = 64 << 10
+
+
+def write_payload(seg: ControlSegment, obj: Any) -> int:
+    """Serialise ``obj`` into the command area; returns the number of bytes used."""
+    buffers: list[pickle.PickleBuffer] = []
+
+    def keep_in_band(buf: pickle.PickleBuffer) -> bool:
+        if buf.raw().nbytes < OUT_OF_BAND_MIN_BYTES:
+            return True
+        buffers.append(buf)
+        return False
+
+    blob = pickle.dumps(obj, protocol=5, buffer_callback=keep_in_band)
+    head = 16 + 8 * len(buffers)
+    offsets, cursor = [], (head + len(blob) + 63) // 64 * 64
+    for b in buffers:
+        offsets.append(cursor)
+        cursor = (cursor + b.raw().nbytes + 63) // 64 * 64
+    if cursor > seg.payload_cap:
+        raise TPControlError(f"command payload of {cursor} bytes exceeds the channel capacity")
+    area = seg.payload(cursor)
+    words = np.ndarray((2 + len(buffers),), dtype=np.int64, buffer=area)
+    words[0], words[1] = len(buffers), len(blob)
+    for i, b in enumerate(buffers):
+        words[2 + i] = b.raw().nbytes
+    area[head:head + len(blob)] = blob
+    for off, b in zip(offsets, buffers):
+        raw = b.raw()
+        area[off:off + raw.nbytes] = raw
+    return cursor
+
+
+def read_payload(seg: ControlSegment, total: int) -> Any:
+    area = seg.payload(total)
+    n_buf, blob_len = (int(v) for v in np.ndarray((2,), dtype=np.int64, buffer=area))
+    sizes = [int(v) for v in np.ndarray((n_buf,), dtype=np.int64, buffer=area, offset=16)]
+    head = 16 + 8 * n_buf
+    views, cursor = [], (head + blob_len + 63) // 64 * 64
+    for size in sizes:
+        views.append(area[cursor:cursor + size])
+        cursor = (cursor + size + 63) // 64 * 64
+    return pickle.loads(bytes(area[head:head + blob_len]), buffers=views)
+
+
 class ControlDriver:
     """Driver side: broadcast a command, run the local copy, collect acknowledgements."""
 
@@ -124,11 +174,8 @@ class ControlDriver:
 
     def post(self, method: TPMethod | str, args: tuple) -> int:
         m = TPMethod(method) if not isinstance(method, TPMethod) else method
-        blob = pickle.dumps((m.value, args), protocol=pickle.HIGHEST_PROTOCOL)
-        if len(blob) > self.seg.payload_cap:
-            raise TPControlError(f"command payload of {len(blob)} bytes exceeds the channel capacity")
-        self.seg.payload(len(blob))[:] = blob
-        self.seg.words[1] = len(blob)
+        total = write_payload(self.seg, (m.value, args))
+        self.seg.words[1] = total
         self.request_id += 1
         self.seg.words[0] = self.request_id  # publish last
         return self.request_id
@@ -185,7 +232,7 @@ class ControlWorker:
             seq = int(self.seg.words[0])
             if seq > self.last:
                 n = int(self.seg.words[1])
-                method, args = pickle.loads(bytes(self.seg.payload(n)))
+                method, args = read_payload(self.seg, n)
                 return seq, method, args
             if int(self.seg.words[2]):
                 return None

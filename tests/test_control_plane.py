@@ -124,3 +124,31 @@ def test_oversized_payload_is_refused():
             driver.post("execute", (b"x" * 4096,))
     finally:
         seg.close()
+
+
+def test_large_arrays_travel_out_of_band_and_small_ones_in_band():
+    import numpy as np
+    import torch
+
+    from prism_infer_b200.engine.input_preparation import StepInputs, VisionJob
+    from prism_infer_b200.parallel import control
+
+    seg = control.ControlSegment(None, 1, create=True, payload_cap=8 << 20, reply_cap=1 << 16)
+    try:
+        big = torch.randn(300, 1536).to(torch.bfloat16)           # 900 KiB -> out of band
+        inp = StepInputs(kind="prefill", input_ids=torch.arange(7), positions=torch.zeros(3, 7, dtype=torch.int32),
+                         slots=torch.arange(7), block_tables=torch.zeros(1, 4, dtype=torch.int32), temperatures=torch.zeros(1),
+                         vision_jobs=[VisionJob(5, big, [(1, 10, 30)], "k")])
+        n = control.write_payload(seg, ("execute", (inp,)))
+        assert n > big.numel() * 2
+        header = np.ndarray((3,), dtype=np.int64, buffer=seg.payload(n))
+        assert header[0] == 1 and header[2] == big.numel() * 2   # exactly one out-of-band buffer: the patches
+        method, (got,) = control.read_payload(seg, n)
+        assert method == "execute" and torch.equal(got.input_ids, inp.input_ids) and got.kv_lens is None
+        job = got.vision_jobs[0]
+        assert job.pixel_values.dtype == torch.bfloat16 and torch.equal(job.pixel_values, big) and job.grid_thw == [(1, 10, 30)]
+        del got, job, header
+        with pytest.raises(control.TPControlError):
+            control.write_payload(seg, torch.zeros(16 << 20, dtype=torch.uint8).numpy())
+    finally:
+        seg.close()
