@@ -361,16 +361,33 @@ class Qwen3VLModel:
         outs = comm.vision_finish(n_out, total_tokens)
         return outs[0], outs[1:]
 
+    def _vision_geometry(self, grid):
+        """Device tensors that depend only on the (t, h, w) grids of a call: position-embedding
+        interpolation plan, rotary patch coordinates, attention segment offsets.  Serving
+        repeats a handful of image shapes, so the last few results are kept."""
+        key = tuple(tuple(int(v) for v in g) for g in grid)
+        cache = self.__dict__.setdefault("_geometry_cache", {})
+        hit = cache.get(key)
+        if hit is not None:
+            cache[key] = cache.pop(key)  # most recently used last
+            return hit
+        v, dev = self.arch.vision, self.device
+        idx, wt = vision_pos_embed_plan(grid, v.grid_per_side, v.spatial_merge_size)
+        coords = vision_patch_coords(grid, v.spatial_merge_size).to(torch.int32)
+        segs = vision_segments(grid)
+        cu = torch.tensor([0] + list(torch.tensor(segs).cumsum(0).tolist()), dtype=torch.int32)
+        out = (idx.to(dev), wt.to(dev), coords.to(dev), cu.to(dev), max(segs))
+        cache[key] = out
+        while len(cache) > 32:
+            cache.pop(next(iter(cache)))
+        return out
+
     def _vision_tower(self, pixel_values: torch.Tensor, grid, comm, token_base: int):
         v = self.arch.vision
         dev = self.device
-        x = ops.linear(pixel_values.to(device=dev, dtype=self.dtype), self.patch_w, bias=self.patch_b)
-        idx, wt = vision_pos_embed_plan(grid, v.grid_per_side, v.spatial_merge_size)
-        ops.pos_embed_add(x, self.pos_embed, idx.to(dev), wt.to(dev))
-        coords = vision_patch_coords(grid, v.spatial_merge_size).to(torch.int32).to(dev)
-        segs = vision_segments(grid)
-        cu = torch.tensor([0] + list(torch.tensor(segs).cumsum(0).tolist()), dtype=torch.int32, device=dev)
-        max_len = max(segs)
+        x = ops.linear(pixel_values.to(device=dev, dtype=self.dtype, non_blocking=True), self.patch_w, bias=self.patch_b)
+        idx, wt, coords, cu, max_len = self._vision_geometry(grid)
+        ops.pos_embed_add(x, self.pos_embed, idx, wt)
         N, vh, heads, hd = x.shape[0], v.hidden_size, v.num_heads, v.head_dim
         deep: list[torch.Tensor] = []
         for i, b in enumerate(self.vision_blocks):

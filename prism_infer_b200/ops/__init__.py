@@ -115,6 +115,13 @@ def linear_partial(
         out.zero_()
         out[0].copy_(y)
         return out
+    if gemv_applies(T, K) and bn == 0 and stages == 0:
+        # at most four tokens: whole-row weight streaming, finished sums (a single "slab")
+        if out is None:
+            out = torch.empty((1, T, M), dtype=torch.float32, device=x.device)
+        native.call("prism_gemv", _p(w), _p(x), _p(out), M, T, K, w.stride(0), x.stride(0), out.stride(1), 0, 0,
+                    None, 0, 0, 0, 0, None, _s(), _pdl())
+        return out[:1]
     eff = effective_splits(K, splits)
     if out is None:
         out = torch.empty((eff, T, M), dtype=torch.float32, device=x.device)
@@ -124,6 +131,15 @@ def linear_partial(
         None, None, 0, 0, 0, 0, eff, 1, out.stride(0), bn, stages, _s(), _pdl(),
     )
     return out[:eff]
+
+
+# decode steps of at most this many tokens use the whole-row weight-streaming kernel (gemv.cu)
+# instead of the tcgen05 GEMM; 0 disables it
+GEMV_MAX_TOKENS = int(__import__("os").environ.get("PRISM_GEMV_MAX_TOKENS", "4"))
+
+
+def gemv_applies(tokens: int, k: int) -> bool:
+    return 0 < tokens <= min(GEMV_MAX_TOKENS, 4) and k % 8 == 0 and tokens * k * 2 <= 200 * 1024
 
 
 def effective_splits(k: int, splits: int) -> int:
@@ -146,6 +162,10 @@ def gate_up_swiglu(x: torch.Tensor, w_gate_up: torch.Tensor, out: Optional[torch
         return y
     if out is None:
         out = torch.empty((T, I), dtype=torch.bfloat16, device=x.device)
+    if gemv_applies(T, K) and bn == 0:
+        native.call("prism_gemv", _p(w_gate_up), _p(x), _p(out), I, T, K, w_gate_up.stride(0), x.stride(0), out.stride(0),
+                    1, I, None, 0, 0, 0, 0, None, _s(), _pdl())
+        return out
     native.call(
         "prism_gemm_wx", _p(w_gate_up), _p(x), _p(out), I, T, K, w_gate_up.stride(0), x.stride(0), out.stride(0),
         2 * I, None, None, 0, 0, 1, I, 1, 0, 0, bn, 0, _s(), _pdl(),

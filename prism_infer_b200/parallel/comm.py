@@ -111,11 +111,17 @@ class FusedComm(NcclComm):
         # while T * tp is small (measured: TP8 ties with NCCL at 32 tokens, TP2 wins up to 128)
         if T > SMALL_T or T * self.size > 192 or M != self.hidden or self.point >= symm.ARGMAX_POINT:
             return super().row_parallel(x, w)
+        point, slot = self.point, self.point % 2
+        r = self.region
+        if ops.gemv_applies(T, K) and x.stride(1) == 1:
+            self.point += 1
+            native.call("prism_gemv", w.data_ptr(), x.data_ptr(), None, M, T, K, w.stride(0), x.stride(0), M, 2, 0,
+                        self._slab_ptrs[slot], self.size, self.rank, point, T * M, r.local(symm.OFF_EPOCH),
+                        torch.cuda.current_stream().cuda_stream, 1 if ops.pdl_enabled() else 0)
+            return None, None, (slot, point, self.size, T)
         splits = min(symm.S_MAX, ops.choose_splits(M, K, T))
         eff = ops.effective_splits(K, splits)
-        point, slot = self.point, self.point % 2
         self.point += 1
-        r = self.region
         native.call(
             "prism_gemm_wx_push", w.data_ptr(), x.data_ptr(), M, T, K,
             w.stride(0), x.stride(0), M, M, eff, T * M, self._slab_ptrs[slot], self._flag_ptrs[slot], self.size,

@@ -81,7 +81,7 @@ def test_gemm_epilogues(cuda_device):
 @pytest.mark.parametrize("T,M,K,splits", [(1, 4096, 4096, 4), (8, 512, 12288, 9), (16, 6144, 4096, 3), (130, 256, 512, 2)])
 def test_gemm_split_k(cuda_device, T, M, K, splits):
     x, w = rand_bf16(T, K, seed=11), rand_bf16(M, K, scale=K ** -0.5, seed=12)
-    parts = ops.linear_partial(x.cuda(), w.cuda(), splits)
+    parts = ops.linear_partial(x.cuda(), w.cuda(), splits, bn=16 if T <= 16 else 0)  # explicit tile: the tcgen05 kernel
     assert parts.shape[0] == ops.effective_splits(K, splits)
     close(parts.sum(0), x.float() @ w.float().t(), 1e-2, 1e-2, "split-k")
 
@@ -399,3 +399,19 @@ def test_gemm_persistent_dual_swiglu(cuda_device):
     torch.cuda.synchronize()
     assert torch.equal(got, want)
     close(got, ops.gate_up_swiglu(x.float().cpu(), w.float().cpu()), 2e-2, 3e-2, "persistent dual")
+
+
+@pytest.mark.parametrize("T,M,K", [(1, 4096, 4096), (2, 6144, 4096), (4, 4096, 12288), (3, 1000, 136), (1, 151936, 4096), (4, 768, 1536)])
+def test_gemv_matches_fp32_reference(cuda_device, T, M, K):
+    """Whole-row weight streaming for at most four tokens (finished sums, one slab)."""
+    x, w = rand_bf16(T, K, seed=31), rand_bf16(M, K, scale=K ** -0.5, seed=32)
+    parts = ops.linear_partial(x.cuda(), w.cuda(), 4)
+    assert parts.shape == (1, T, M)
+    close(parts[0], x.float() @ w.float().t(), 1e-2, 1e-2, "gemv")
+
+
+@pytest.mark.parametrize("T,I,K", [(1, 12288, 4096), (4, 1536, 4096), (2, 520, 264)])
+def test_gemv_dual_swiglu(cuda_device, T, I, K):
+    x, w = rand_bf16(T, K, seed=33), rand_bf16(2 * I, K, scale=K ** -0.5, seed=34)
+    y = ops.gate_up_swiglu(x.cuda(), w.cuda())
+    close(y, ops.gate_up_swiglu(x.float(), w.float()), 2e-2, 3e-2, "gemv dual swiglu")
