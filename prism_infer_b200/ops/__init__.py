@@ -133,9 +133,12 @@ def linear_partial(
     return out[:eff]
 
 
-# decode steps of at most this many tokens use the whole-row weight-streaming kernel (gemv.cu)
-# instead of the tcgen05 GEMM; 0 disables it
-GEMV_MAX_TOKENS = int(__import__("os").environ.get("PRISM_GEMV_MAX_TOKENS", "4"))
+# decode steps of at most this many tokens (<= 4) use the whole-row weight-streaming kernel
+# (gemv.cu) instead of the tcgen05 GEMM; 0 disables it.  Off by default: on the headline step it
+# measured 5.18 ms against 3.85 ms (the 12-stage TMA ring prefetches ~29 MB of weights before the
+# dependency wait, the register buffers of the SIMT kernel cannot), 3.25 vs 2.98 ms on the TP2
+# shard and 1.76 vs 1.83 ms on the TP8 shard.
+GEMV_MAX_TOKENS = int(__import__("os").environ.get("PRISM_GEMV_MAX_TOKENS", "0"))
 
 
 def gemv_applies(tokens: int, k: int) -> bool:

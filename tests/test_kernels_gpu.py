@@ -402,8 +402,9 @@ def test_gemm_persistent_dual_swiglu(cuda_device):
 
 
 @pytest.mark.parametrize("T,M,K", [(1, 4096, 4096), (2, 6144, 4096), (4, 4096, 12288), (3, 1000, 136), (1, 151936, 4096), (4, 768, 1536)])
-def test_gemv_matches_fp32_reference(cuda_device, T, M, K):
+def test_gemv_matches_fp32_reference(cuda_device, T, M, K, monkeypatch):
     """Whole-row weight streaming for at most four tokens (finished sums, one slab)."""
+    monkeypatch.setattr(ops, "GEMV_MAX_TOKENS", 4)
     x, w = rand_bf16(T, K, seed=31), rand_bf16(M, K, scale=K ** -0.5, seed=32)
     parts = ops.linear_partial(x.cuda(), w.cuda(), 4)
     assert parts.shape == (1, T, M)
@@ -411,7 +412,8 @@ def test_gemv_matches_fp32_reference(cuda_device, T, M, K):
 
 
 @pytest.mark.parametrize("T,I,K", [(1, 12288, 4096), (4, 1536, 4096), (2, 520, 264)])
-def test_gemv_dual_swiglu(cuda_device, T, I, K):
+def test_gemv_dual_swiglu(cuda_device, T, I, K, monkeypatch):
+    monkeypatch.setattr(ops, "GEMV_MAX_TOKENS", 4)
     x, w = rand_bf16(T, K, seed=33), rand_bf16(2 * I, K, scale=K ** -0.5, seed=34)
     y = ops.gate_up_swiglu(x.cuda(), w.cuda())
     close(y, ops.gate_up_swiglu(x.float(), w.float()), 2e-2, 3e-2, "gemv dual swiglu")
