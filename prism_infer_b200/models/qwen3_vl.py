@@ -115,12 +115,13 @@ class TPComm:
     def begin_step(self) -> None:
         return None
 
-    def row_parallel(self, x: torch.Tensor, w: torch.Tensor):
-        """Row-parallel projection -> ``(dense, partials, ticket)``; exactly one is set."""
+    def row_parallel(self, x: torch.Tensor, w: torch.Tensor, stages: int = 0):
+        """Row-parallel projection -> ``(dense, partials, ticket)``; exactly one is set.
+        ``stages`` caps the operand ring of a decode-sized launch (0 = as deep as fits)."""
         T = x.shape[0]
         if T <= SMALL_T:
             splits = ops.choose_splits(w.shape[0], w.shape[1], T) if x.is_cuda else 1
-            return None, ops.linear_partial(x, w, splits), None
+            return None, ops.linear_partial(x, w, splits, stages=stages), None
         return ops.linear(x, w), None, None
 
     def row_parallel_swiglu(self, gate_up_partials: torch.Tensor, w: torch.Tensor):
@@ -472,7 +473,7 @@ class Qwen3VLModel:
                 a = ops.paged_prefill_attention(q, cache, i, meta.cu_seqlens_q, meta.kv_lens, meta.block_tables, meta.max_q_len) \
                     if meta.is_prefill else ops.paged_decode_attention(q, cache, i, meta.block_tables, meta.context_lens,
                                                                        nsplit=meta.nsplit, workspace=meta.workspace)
-                dense, partials, ticket = comm.row_parallel(a.view(T, self.Hq * self.D), l.o)
+                dense, partials, ticket = comm.row_parallel(a.view(T, self.Hq * self.D), l.o, stages=ops.O_PROJ_STAGES if small else 0)
                 src = comm.norm_source(dense, partials, ticket)
                 if self.I // 128 < 96:
                     gu = ops.linear_normx(l.gate_up, l.post_norm, t.rms_norm_eps, T, residual=residual, residual_out=res_bufs[flip],
@@ -521,7 +522,7 @@ class Qwen3VLModel:
                     ops.prefetch_next(l.gate_up, ops.L2_PREFETCH[2])
                 a = ops.paged_decode_attention(q, cache, i, meta.block_tables, meta.context_lens, nsplit=meta.nsplit,
                                                workspace=meta.workspace)
-            dense, partials, ticket = comm.row_parallel(a.view(T, self.Hq * self.D), l.o)
+            dense, partials, ticket = comm.row_parallel(a.view(T, self.Hq * self.D), l.o, stages=ops.O_PROJ_STAGES if small else 0)
             if pf:
                 ops.prefetch_next(l.down, ops.L2_PREFETCH[3])
             h, residual = comm.add_rmsnorm(l.post_norm, t.rms_norm_eps, dense, partials, ticket, residual)

@@ -115,7 +115,7 @@ def linear_partial(
         out.zero_()
         out[0].copy_(y)
         return out
-    if gemv_applies(T, K) and bn == 0 and stages == 0:
+    if gemv_applies(T, K) and bn == 0:
         # at most four tokens: whole-row weight streaming, finished sums (a single "slab")
         if out is None:
             out = torch.empty((1, T, M), dtype=torch.float32, device=x.device)
@@ -234,6 +234,11 @@ def linear_normx(
 
 # measured at TP2 on the headline step: 3.84 ms with the SwiGLU prologue, 3.68 ms with the separate kernel
 ACTX_ENABLED = _os.environ.get("PRISM_ACTX", "0") != "0"
+# operand-ring depth of the decode-sized o_proj GEMM (0 = as deep as fits).  A shallower ring
+# leaves shared memory for the attention CTAs that precede it, so its weight prefetch can start
+# while attention still runs.
+O_PROJ_STAGES = int(_os.environ.get("PRISM_O_PROJ_STAGES", "0"))
+ATTN_TC_ENABLED = _os.environ.get("PRISM_ATTN_TC", "1") != "0"
 PERSISTENT_MIN_TOKENS = int(_os.environ.get("PRISM_PERSISTENT_MIN_TOKENS", "512"))
 SMALL_TILE_SMEM_CAP = int(_os.environ.get("PRISM_SMALL_TILE_SMEM", "0"))
 
@@ -678,6 +683,14 @@ def varlen_attention(
         out = torch.empty((T, Hq, D), dtype=torch.bfloat16, device=q.device)
     assert q.stride(2) == 1 and q.stride(1) == D and k.stride(1) == D and v.stride(1) == D
     assert k.stride(0) == v.stride(0) and cu_seqlens.dtype == torch.int32
+    if (ATTN_TC_ENABLED and D == 128 and q.stride(0) % 8 == 0 and k.stride(0) % 8 == 0
+            and (q.data_ptr() | k.data_ptr() | v.data_ptr() | out.data_ptr()) % 16 == 0):
+        # head dimension 128: the tcgen05 / TMEM kernel
+        native.call(
+            "prism_flash_attention_tc", _p(q), q.stride(0), _p(k), _p(v), k.stride(0), _p(out), out.stride(0),
+            _p(cu_seqlens), T, cu_seqlens.shape[0] - 1, int(max_len), Hq, Hkv, 1 if causal else 0, scale, _s(), _pdl(),
+        )
+        return out
     native.call(
         "prism_flash_attention", _p(q), q.stride(0), _p(out), out.stride(0), _p(cu_seqlens), _p(k), _p(v),
         k.stride(0), None, None, None, None, None, None, 0, 1, cu_seqlens.shape[0] - 1, int(max_len), Hq, Hkv, D,

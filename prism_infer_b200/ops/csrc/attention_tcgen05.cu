@@ -1,0 +1,334 @@
+// Prefill attention on the fifth-generation tensor cores (head dimension 128, bf16 Q/K/V rows).
+//
+// One CTA handles 128 query rows of one (sequence, query head) and walks the keys in tiles of
+// 64.  Warp 0 streams K/V tiles with TMA (128-byte swizzle) into a four-stage ring, one thread
+// of warp 1 issues the MMAs, warps 2-5 are the softmax: thread i owns query row i, so row
+// maxima and sums need no shuffles.
+//
+//   S  = Q K^T      tcgen05.mma, A = Q (shared, K-major), B = K tile (shared, K-major),
+//                   fp32 accumulator in TMEM, two S buffers so tile j+1 is scored while the
+//                   softmax of tile j runs
+//   P  = exp2(S - m) as bf16 pairs, written over the S buffer with tcgen05.st
+//   O_j = P V       tcgen05.mma with the A operand read from TMEM and B = V tile as loaded
+//                   (keys are its K index, so it is an MN-major operand), fresh accumulator
+//   O  += O_j       in the softmax threads' registers with the usual running-max rescale
+//
+// TMEM columns: S/P buffers 2 x 64, O_j buffers 2 x 128 (384 of 512).  Every wait is bounded
+// (common.cuh: mbar_wait); on a timeout the status word is set, roles unwind and the CTA
+// frees its TMEM.  Replaces the reference's flash-attn / SDPA calls for prefill without
+// history (prism_infer/layers/attention.py:180-250).
+#include "common.cuh"
+
+PRISM_DEFINE_TU_STATUS(attn_tc)
+
+namespace {
+
+constexpr int FA_BM = 128;
+constexpr int FA_BN = 64;
+constexpr int FA_HD = 128;
+constexpr int FA_STAGES = 4;
+constexpr int FA_THREADS = 192;
+constexpr int Q_BYTES = FA_BM * FA_HD * 2;      // two 64-column atoms of 128 rows
+constexpr int K_BYTES = FA_BN * FA_HD * 2;      // two 64-column atoms of 64 rows
+constexpr int V_BYTES = FA_BN * FA_HD * 2;      // two 64-column boxes of 64 keys
+constexpr int STAGE_BYTES = K_BYTES + V_BYTES;  // 32 KB
+constexpr int TMEM_S = 0;                       // S/P buffer b at column b * 64
+constexpr int TMEM_O = 128;                     // O_j buffer b at column 128 + b * 128
+
+struct FaArgs {
+  const int* cu_q;        // [S + 1] row offsets of the sequences
+  __nv_bfloat16* out;     // [T][Hq * 128]
+  long long o_stride;
+  int Hq, Hkv;
+  int q_col0, k_col0, v_col0;  // first column of head 0 inside the respective tensor map
+  int causal;
+  float scale;
+};
+
+__device__ __forceinline__ float ex2f(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+__global__ void __launch_bounds__(FA_THREADS, 1)
+flash_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                const __grid_constant__ CUtensorMap tmV, const FaArgs a) {
+  extern __shared__ uint8_t fa_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(fa_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* q_s = smem;
+  uint8_t* ring = smem + Q_BYTES;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(ring + FA_STAGES * STAGE_BYTES);
+  uint64_t* q_full = bars;
+  uint64_t* kv_full = bars + 1;                  // [FA_STAGES]
+  uint64_t* kv_empty = kv_full + FA_STAGES;      // [FA_STAGES]
+  uint64_t* s_full = kv_empty + FA_STAGES;       // [2] MMA -> softmax: S tile ready
+  uint64_t* p_full = s_full + 2;                 // [2] softmax -> MMA: P written (128 arrivals)
+  uint64_t* o_full = p_full + 2;                 // [2] MMA -> softmax: O_j ready
+  uint64_t* o_free = o_full + 2;                 // [2] softmax -> MMA: O_j consumed (128 arrivals)
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(o_free + 2);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int seq = blockIdx.z, head = blockIdx.y, qt = blockIdx.x;
+  const int kvh = head / (a.Hq / a.Hkv);
+
+  if (threadIdx.x == 0) {
+    mbar_init(q_full, 1);
+    for (int s = 0; s < FA_STAGES; ++s) {
+      mbar_init(&kv_full[s], 1);
+      mbar_init(&kv_empty[s], 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&s_full[b], 1);
+      mbar_init(&p_full[b], 128);
+      mbar_init(&o_full[b], 1);
+      mbar_init(&o_free[b], 128);
+    }
+    fence_barrier_init();
+    tma_prefetch_desc(&tmQ);
+    tma_prefetch_desc(&tmK);
+    tma_prefetch_desc(&tmV);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  pdl_launch_dependents();
+  pdl_wait();
+
+  const int q_start = a.cu_q[seq];
+  const int q_len = a.cu_q[seq + 1] - q_start;
+  const int q0 = qt * FA_BM;
+  const bool live = q0 < q_len;  // uniform over the CTA
+  int n_tiles = 0;
+  if (live) {
+    int kv_end = q_len;
+    if (a.causal) kv_end = min(q_len, q0 + FA_BM);
+    n_tiles = (kv_end + FA_BN - 1) / FA_BN;
+  }
+
+  if (warp == 0) {
+    if (lane == 0 && live) {
+      // ------------------------------ TMA producer ------------------------------
+      mbar_expect_tx(q_full, Q_BYTES);
+      tma_load_2d(q_s, &tmQ, q_full, a.q_col0 + head * FA_HD, q_start + q0);
+      tma_load_2d(q_s + Q_BYTES / 2, &tmQ, q_full, a.q_col0 + head * FA_HD + 64, q_start + q0);
+      bool ok = true;
+      int issued = 0;
+      for (int j = 0; j < n_tiles && ok; ++j) {
+        const int s = j % FA_STAGES;
+        if (j >= FA_STAGES) {
+          ok = mbar_wait(&kv_empty[s], ((j / FA_STAGES) - 1) & 1, 11);
+          if (!ok) break;
+        }
+        uint8_t* st = ring + (size_t)s * STAGE_BYTES;
+        const int row = q_start + j * FA_BN;
+        mbar_expect_tx(&kv_full[s], STAGE_BYTES);
+        tma_load_2d(st, &tmK, &kv_full[s], a.k_col0 + kvh * FA_HD, row);
+        tma_load_2d(st + K_BYTES / 2, &tmK, &kv_full[s], a.k_col0 + kvh * FA_HD + 64, row);
+        tma_load_2d(st + K_BYTES, &tmV, &kv_full[s], a.v_col0 + kvh * FA_HD, row);
+        tma_load_2d(st + K_BYTES + V_BYTES / 2, &tmV, &kv_full[s], a.v_col0 + kvh * FA_HD + 64, row);
+        issued = j + 1;
+      }
+      if (!ok) {
+        for (int j = max(0, issued - FA_STAGES); j < issued; ++j)
+          (void)mbar_wait(&kv_full[j % FA_STAGES], (j / FA_STAGES) & 1, 12);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0 && live) {
+      // ------------------------------ MMA issuer ------------------------------
+      constexpr uint32_t IDESC_S = umma_idesc_bf16(FA_BM, FA_BN);
+      constexpr uint32_t IDESC_O = umma_idesc_bf16(FA_BM, FA_HD) | UMMA_B_MN_MAJOR;
+      const uint32_t q_addr = smem_u32(q_s);
+      bool ok = mbar_wait(q_full, 0, 13);
+      auto score = [&](int j) {  // S[j % 2] = Q K_j^T
+        const uint32_t st = smem_u32(ring + (size_t)(j % FA_STAGES) * STAGE_BYTES);
+        const uint32_t d = tmem_base + TMEM_S + (j & 1) * FA_BN;
+#pragma unroll
+        for (int k = 0; k < FA_HD / 16; ++k) {
+          const uint64_t da = umma_desc_sw128(q_addr + (k >> 2) * (Q_BYTES / 2)) + 2 * (k & 3);
+          const uint64_t db = umma_desc_sw128(st + (k >> 2) * (K_BYTES / 2)) + 2 * (k & 3);
+          tc_mma_f16(d, da, db, IDESC_S, k != 0);
+        }
+        tc_commit(&s_full[j & 1]);
+      };
+      if (ok) ok = mbar_wait(&kv_full[0], 0, 14);
+      if (ok) {
+        tc_fence_after();
+        score(0);
+      }
+      for (int j = 0; j < n_tiles && ok; ++j) {
+        const int b = j & 1;
+        if (j + 1 < n_tiles) {
+          ok = mbar_wait(&kv_full[(j + 1) % FA_STAGES], ((j + 1) / FA_STAGES) & 1, 15);
+          if (!ok) break;
+          tc_fence_after();
+          score(j + 1);  // overwrites S/P[(j+1) & 1]: PV(j-1) was issued before, so it reads first
+        }
+        ok = mbar_wait(&p_full[b], (j >> 1) & 1, 16);
+        if (!ok) break;
+        if (j >= 2) {
+          ok = mbar_wait(&o_free[b], ((j >> 1) - 1) & 1, 17);
+          if (!ok) break;
+        }
+        tc_fence_after();
+        const uint32_t vt = smem_u32(ring + (size_t)(j % FA_STAGES) * STAGE_BYTES + K_BYTES);
+        const uint32_t d = tmem_base + TMEM_O + b * FA_HD;
+        const uint32_t p_t = tmem_base + TMEM_S + b * FA_BN;
+#pragma unroll
+        for (int k = 0; k < FA_BN / 16; ++k) {
+          // 16 keys per step: 8 packed columns of P, two 8-key groups (2048 bytes) of V
+          const uint64_t db = umma_desc_sw128_mn(vt + k * 2048, V_BYTES / 2);
+          tc_mma_f16_ts(d, p_t + k * 8, db, IDESC_O, k != 0);
+        }
+        tc_commit(&o_full[b]);
+        tc_commit(&kv_empty[j % FA_STAGES]);
+      }
+    }
+  } else if (live) {
+    // ------------------------------ softmax warps 2..5 ------------------------------
+    const int q = warp & 3;                 // TMEM lane quarter of this warp
+    const int row = q0 + q * 32 + lane;     // query row (local index) owned by this thread
+    const uint32_t lane_addr = tmem_base + ((uint32_t)(q * 32) << 16);
+    const float sl2 = a.scale * 1.4426950408889634f;
+    float o_acc[FA_HD];
+#pragma unroll
+    for (int i = 0; i < FA_HD; ++i) o_acc[i] = 0.0f;
+    float m_run = -INFINITY, l_run = 0.0f;
+    float corr_prev = 1.0f;  // rescale that belongs to the O_j still in flight
+    bool ok = true;
+    auto fold = [&](int j, float corr) {  // o_acc = o_acc * corr + O_j
+      const int b = j & 1;
+      if (!mbar_wait(&o_full[b], (j >> 1) & 1, 18)) return false;
+      tc_fence_after();
+#pragma unroll
+      for (int c = 0; c < FA_HD / 16; ++c) {
+        uint32_t r[16];
+        tmem_ld16(lane_addr + TMEM_O + b * FA_HD + c * 16, r);
+        tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 16; ++i) o_acc[c * 16 + i] = fmaf(o_acc[c * 16 + i], corr, __uint_as_float(r[i]));
+      }
+      tc_fence_before();
+      mbar_arrive(&o_free[b]);
+      return true;
+    };
+    for (int j = 0; j < n_tiles && ok; ++j) {
+      const int b = j & 1;
+      ok = mbar_wait(&s_full[b], (j >> 1) & 1, 19);
+      if (!ok) break;
+      tc_fence_after();
+      float s[FA_BN];
+#pragma unroll
+      for (int c = 0; c < FA_BN / 16; ++c) {
+        uint32_t r[16];
+        tmem_ld16(lane_addr + TMEM_S + b * FA_BN + c * 16, r);
+        tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 16; ++i) s[c * 16 + i] = __uint_as_float(r[i]) * sl2;
+      }
+      const int j0 = j * FA_BN;
+      if (j0 + FA_BN > q_len || (a.causal && j0 + FA_BN - 1 > row)) {
+#pragma unroll
+        for (int i = 0; i < FA_BN; ++i)
+          if (j0 + i >= q_len || (a.causal && j0 + i > row)) s[i] = -INFINITY;
+      }
+      float mx = m_run;
+#pragma unroll
+      for (int i = 0; i < FA_BN; ++i) mx = fmaxf(mx, s[i]);
+      const float m_use = (mx == -INFINITY) ? 0.0f : mx;
+      const float corr = (m_run == -INFINITY) ? 0.0f : ex2f(m_run - m_use);
+      m_run = mx;
+      float sum = 0.0f;
+      uint32_t packed[FA_BN / 2];
+#pragma unroll
+      for (int i = 0; i < FA_BN; i += 2) {
+        const float p0 = ex2f(s[i] - m_use), p1 = ex2f(s[i + 1] - m_use);
+        sum += p0 + p1;
+        __nv_bfloat162 v = __floats2bfloat162_rn(p0, p1);
+        packed[i >> 1] = *reinterpret_cast<uint32_t*>(&v);
+      }
+      l_run = l_run * corr + sum;
+#pragma unroll
+      for (int c = 0; c < FA_BN / 32; ++c) {
+        uint32_t r[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) r[i] = packed[c * 16 + i];
+        tmem_st16(lane_addr + TMEM_S + b * FA_BN + c * 16, r);
+      }
+      tmem_st_wait();
+      tc_fence_before();
+      mbar_arrive(&p_full[b]);
+      // while the tensor core multiplies P_j V_j, fold the previous tile's product
+      if (j >= 1) ok = fold(j - 1, corr_prev);
+      corr_prev = corr;
+    }
+    if (ok && n_tiles > 0) ok = fold(n_tiles - 1, corr_prev);
+    if (ok && row < q_len) {
+      const float inv = l_run > 0.0f ? 1.0f / l_run : 0.0f;
+      __nv_bfloat16* dst = a.out + (size_t)(q_start + row) * a.o_stride + (size_t)head * FA_HD;
+#pragma unroll
+      for (int c = 0; c < FA_HD / 8; ++c) {
+        uint4 v;
+        uint32_t* w = reinterpret_cast<uint32_t*>(&v);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          __nv_bfloat162 h = __floats2bfloat162_rn(o_acc[c * 8 + 2 * e] * inv, o_acc[c * 8 + 2 * e + 1] * inv);
+          w[e] = *reinterpret_cast<uint32_t*>(&h);
+        }
+        *reinterpret_cast<uint4*>(dst + c * 8) = v;
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) tmem_dealloc(tmem_base, 512);
+}
+
+}  // namespace
+
+// Causal or bidirectional self-attention over contiguous segments, head dimension 128.
+// q [T][q_stride], k / v [T][kv_stride] bf16 with the heads side by side (views into a packed
+// QKV projection are fine); out [T][o_stride].  Rows and strides must be 16-byte aligned.
+PRISM_API int prism_flash_attention_tc(const void* q, long long q_stride, const void* k, const void* v,
+                                       long long kv_stride, void* out, long long o_stride, const void* cu_q, int T,
+                                       int S, int max_q_len, int Hq, int Hkv, int causal, float scale, void* stream,
+                                       int pdl) {
+  if (S <= 0 || max_q_len <= 0 || T <= 0) return 0;
+  if (Hq % Hkv) return -1;
+  if ((q_stride % 8) || (kv_stride % 8) || (o_stride % 8)) return -2;
+  if ((reinterpret_cast<unsigned long long>(q) | reinterpret_cast<unsigned long long>(k) |
+       reinterpret_cast<unsigned long long>(v) | reinterpret_cast<unsigned long long>(out)) & 15ull)
+    return -3;
+  CUtensorMap tq, tk, tv;
+  int rc = prism_get_tensor_map(q, (unsigned long long)T, (unsigned long long)Hq * FA_HD, (unsigned long long)q_stride, FA_BM, &tq);
+  if (rc) return rc;
+  rc = prism_get_tensor_map(k, (unsigned long long)T, (unsigned long long)Hkv * FA_HD, (unsigned long long)kv_stride, FA_BN, &tk);
+  if (rc) return rc;
+  rc = prism_get_tensor_map(v, (unsigned long long)T, (unsigned long long)Hkv * FA_HD, (unsigned long long)kv_stride, FA_BN, &tv);
+  if (rc) return rc;
+  FaArgs a;
+  a.cu_q = reinterpret_cast<const int*>(cu_q);
+  a.out = reinterpret_cast<__nv_bfloat16*>(out);
+  a.o_stride = o_stride;
+  a.Hq = Hq;
+  a.Hkv = Hkv;
+  a.q_col0 = a.k_col0 = a.v_col0 = 0;
+  a.causal = causal;
+  a.scale = scale;
+  const size_t smem = 1024 + Q_BYTES + (size_t)FA_STAGES * STAGE_BYTES + 32 * 8 + 64;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(flash_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+    configured = true;
+  }
+  const int tiles = (max_q_len + FA_BM - 1) / FA_BM;
+  return (int)prism_launch(flash_tc_kernel, dim3(tiles, Hq, S), dim3(FA_THREADS), smem, reinterpret_cast<cudaStream_t>(stream),
+                           pdl != 0, tq, tk, tv, a);
+}

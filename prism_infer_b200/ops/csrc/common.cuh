@@ -234,6 +234,27 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
       : "memory");
 }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+// Store counterpart: thread t writes lane (taddr.lane + t), columns taddr.col .. +15.
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
+      ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
+        "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+      : "memory");
+}
+__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+// D[tmem] (+)= A[tmem] * B[smem desc]: the A operand (M lanes x K 16-bit elements, two per
+// 32-bit column) is read from tensor memory.
+__device__ __forceinline__ void tc_mma_f16_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc,
+                                              uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
 
 // Shared-memory matrix descriptor for a K-major bf16 tile whose rows are 128 bytes
 // (64 elements) and stored with the 128-byte swizzle TMA produces: 8-row groups are
@@ -247,12 +268,29 @@ __device__ __forceinline__ uint64_t umma_desc_sw128(uint32_t smem_addr) {
   d |= (uint64_t)2 << 61;            // SWIZZLE_128B
   return d;
 }
+// MN-major bf16 tile with the 128-byte swizzle: rows are 64 elements along M/N (128 bytes), one
+// row per K index; 8-row groups along K are 1024 bytes apart (stride byte offset) and the next
+// 64 elements along M/N start lbo_bytes further on (leading byte offset).
+__device__ __forceinline__ uint64_t umma_desc_sw128_mn(uint32_t smem_addr, uint32_t lbo_bytes) {
+  uint64_t d = 0;
+  d |= (uint64_t)((smem_addr & 0x3FFFFu) >> 4);
+  d |= (uint64_t)((lbo_bytes >> 4) & 0x3FFFu) << 16;
+  d |= (uint64_t)(1024 >> 4) << 32;
+  d |= (uint64_t)1 << 46;
+  d |= (uint64_t)2 << 61;
+  return d;
+}
+constexpr uint32_t UMMA_B_MN_MAJOR = 1u << 16;  // instruction-descriptor bit: B operand is MN-major
 // Instruction descriptor: bf16 x bf16 -> fp32, both operands K-major, M x N tile.
 __host__ __device__ constexpr uint32_t umma_idesc_bf16(int m, int n) {
   return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
 }
 
 // ---- host-side declarations shared between translation units -------------------------
+// Cached CUtensorMap of a [rows, cols] bf16 row-major matrix with row stride ld (elements) and a
+// box of box_rows x 64 elements, 128-byte swizzle (defined in gemm_tcgen05.cu).
+int prism_get_tensor_map(const void* ptr, unsigned long long rows, unsigned long long cols, unsigned long long ld,
+                         unsigned box_rows, CUtensorMap* out);
 struct PrismLaunch {
   cudaStream_t stream;
   int pdl;  // 1: launch with programmatic stream serialization

@@ -851,6 +851,11 @@ int launch_persistent(const CUtensorMap& tw, const CUtensorMap& tx, PersistArgs&
 
 }  // namespace
 
+int prism_get_tensor_map(const void* ptr, unsigned long long rows, unsigned long long cols, unsigned long long ld,
+                         unsigned box_rows, CUtensorMap* out) {
+  return get_tensor_map(ptr, rows, cols, ld, box_rows, out);
+}
+
 // W [w_rows_total, K] (row stride ldw), X [T, K] (row stride ldx), both bf16.
 // out: bf16 [T, ldo] (features along the row) or fp32 [splits][T][ldo] when out_f32.
 // dual: second weight tile starts at row w2_row_off; output = silu(W1 x) * (W2 x), M rows.

@@ -65,10 +65,10 @@ class NcclComm(TPComm):
         dist.all_gather(parts, x.contiguous(), group=self.group)
         return torch.cat(parts, dim=0)
 
-    def row_parallel(self, x: torch.Tensor, w: torch.Tensor):
+    def row_parallel(self, x: torch.Tensor, w: torch.Tensor, stages: int = 0):
         T = x.shape[0]
         if T <= SMALL_T and x.is_cuda:
-            parts = ops.linear_partial(x, w, ops.choose_splits(w.shape[0], w.shape[1], T))
+            parts = ops.linear_partial(x, w, ops.choose_splits(w.shape[0], w.shape[1], T), stages=stages)
             return None, self.reduce_partials(parts), None
         y = ops.linear(x, w)
         return self.reduce_dense(y), None, None
@@ -104,13 +104,13 @@ class FusedComm(NcclComm):
         native.call("prism_epoch_advance", self.region.local(symm.OFF_EPOCH), symm.POINTS_PER_STEP,
                     torch.cuda.current_stream().cuda_stream, 0)
 
-    def row_parallel(self, x: torch.Tensor, w: torch.Tensor):
+    def row_parallel(self, x: torch.Tensor, w: torch.Tensor, stages: int = 0):
         T, K = x.shape
         M = w.shape[0]
         # every rank sends tp * splits * T rows of 8-byte words, so the one-shot exchange only wins
         # while T * tp is small (measured: TP8 ties with NCCL at 32 tokens, TP2 wins up to 128)
         if T > SMALL_T or T * self.size > 192 or M != self.hidden or self.point >= symm.ARGMAX_POINT:
-            return super().row_parallel(x, w)
+            return super().row_parallel(x, w, stages)
         point, slot = self.point, self.point % 2
         r = self.region
         if ops.gemv_applies(T, K) and x.stride(1) == 1:
@@ -125,7 +125,7 @@ class FusedComm(NcclComm):
         native.call(
             "prism_gemm_wx_push", w.data_ptr(), x.data_ptr(), M, T, K,
             w.stride(0), x.stride(0), M, M, eff, T * M, self._slab_ptrs[slot], self._flag_ptrs[slot], self.size,
-            self.rank, point, r.local(symm.OFF_COUNTER[slot]), r.local(symm.OFF_EPOCH), 0, 0,
+            self.rank, point, r.local(symm.OFF_COUNTER[slot]), r.local(symm.OFF_EPOCH), 0, stages,
             torch.cuda.current_stream().cuda_stream, 1 if ops.pdl_enabled() else 0,
         )
         return None, None, (slot, point, self.size * eff, T)

@@ -417,3 +417,26 @@ def test_gemv_dual_swiglu(cuda_device, T, I, K, monkeypatch):
     x, w = rand_bf16(T, K, seed=33), rand_bf16(2 * I, K, scale=K ** -0.5, seed=34)
     y = ops.gate_up_swiglu(x.cuda(), w.cuda())
     close(y, ops.gate_up_swiglu(x.float(), w.float()), 2e-2, 3e-2, "gemv dual swiglu")
+
+
+@pytest.mark.parametrize("causal", [True, False])
+@pytest.mark.parametrize("lens,Hq,Hkv", [((300, 129, 64), 8, 2), ((1616,), 32, 8), ((1, 127, 128, 700), 4, 4)])
+def test_tcgen05_flash_attention_matches_fp32_reference(cuda_device, causal, lens, Hq, Hkv, monkeypatch):
+    """Head dimension 128, K/V read as strided views of a packed projection, ragged segments."""
+    D = 128
+    T = sum(lens)
+    g = torch.Generator().manual_seed(len(lens) * 7 + Hq)
+    qkv = (torch.randn(T, (Hq + 2 * Hkv) * D, generator=g) * 0.7).to(torch.bfloat16)
+    heads = qkv.view(T, Hq + 2 * Hkv, D)
+    cu = torch.tensor([0] + list(torch.tensor(lens).cumsum(0).tolist()), dtype=torch.int32)
+    ref = ops.varlen_attention(heads[:, :Hq].float(), heads[:, Hq:Hq + Hkv].float(), heads[:, Hq + Hkv:].float(), cu, max(lens),
+                               causal=causal)
+    dev = heads.cuda()
+    q = dev[:, :Hq].contiguous()
+    monkeypatch.setattr(ops, "ATTN_TC_ENABLED", True)
+    got = ops.varlen_attention(q, dev[:, Hq:Hq + Hkv], dev[:, Hq + Hkv:], cu.cuda(), max(lens), causal=causal)
+    torch.cuda.synchronize()
+    close(got, ref, 2e-2, 2e-2, f"tcgen05 attention causal={causal} lens={lens}")
+    monkeypatch.setattr(ops, "ATTN_TC_ENABLED", False)
+    legacy = ops.varlen_attention(q, dev[:, Hq:Hq + Hkv], dev[:, Hq + Hkv:], cu.cuda(), max(lens), causal=causal)
+    close(got, legacy.float().cpu(), 2e-2, 2e-2, "tcgen05 vs mma.sync attention")
