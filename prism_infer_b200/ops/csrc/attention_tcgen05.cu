@@ -1,19 +1,18 @@
 // Prefill attention on the fifth-generation tensor cores (head dimension 128, bf16 Q/K/V rows).
 //
 // One CTA handles 128 query rows of one (sequence, query head) and walks the keys in tiles of
-// 64.  Warp 0 streams K/V tiles with TMA (128-byte swizzle) into a four-stage ring, one thread
-// of warp 1 issues the MMAs, warps 2-5 are the softmax: thread i owns query row i, so row
-// maxima and sums need no shuffles.
+// 64.  Warp 0 streams K/V tiles with TMA (128-byte swizzle) into a two-stage ring, one thread
+// of warp 1 issues the MMAs, warps 2-9 are the softmax: two threads per query row, each with
+// half of a tile's keys and half of the output columns.
 //
 //   S  = Q K^T      tcgen05.mma, A = Q (shared, K-major), B = K tile (shared, K-major),
 //                   fp32 accumulator in TMEM, two S buffers so tile j+1 is scored while the
 //                   softmax of tile j runs
 //   P  = exp2(S - m) as bf16 pairs, written over the S buffer with tcgen05.st
-//   O_j = P V       tcgen05.mma with the A operand read from TMEM and B = V tile as loaded
-//                   (keys are its K index, so it is an MN-major operand), fresh accumulator
-//   O  += O_j       in the softmax threads' registers with the usual running-max rescale
+//   O += P V        tcgen05.mma with the A operand read from TMEM and B = V tile as loaded
+//                   (keys are its K index, so it is an MN-major operand), accumulating in TMEM
 //
-// TMEM columns: S/P buffers 2 x 64, O_j buffers 2 x 128 (384 of 512).  Every wait is bounded
+// TMEM columns: S/P buffers 2 x 64, O accumulator 128 (256 allocated).  Every wait is bounded
 // (common.cuh: mbar_wait); on a timeout the status word is set, roles unwind and the CTA
 // frees its TMEM.  Replaces the reference's flash-attn / SDPA calls for prefill without
 // history (prism_infer/layers/attention.py:180-250).
@@ -26,14 +25,14 @@ namespace {
 constexpr int FA_BM = 128;
 constexpr int FA_BN = 64;
 constexpr int FA_HD = 128;
-constexpr int FA_STAGES = 4;
-constexpr int FA_THREADS = 192;
+constexpr int FA_STAGES = 2;  // 32 KB each; with Q that is 96 KB, so two CTAs share an SM
+constexpr int FA_THREADS = 320;  // TMA warp, MMA warp, eight softmax warps
 constexpr int Q_BYTES = FA_BM * FA_HD * 2;      // two 64-column atoms of 128 rows
 constexpr int K_BYTES = FA_BN * FA_HD * 2;      // two 64-column atoms of 64 rows
 constexpr int V_BYTES = FA_BN * FA_HD * 2;      // two 64-column boxes of 64 keys
 constexpr int STAGE_BYTES = K_BYTES + V_BYTES;  // 32 KB
 constexpr int TMEM_S = 0;                       // S/P buffer b at column b * 64
-constexpr int TMEM_O = 128;                     // O_j buffer b at column 128 + b * 128
+constexpr int TMEM_O = 128;                     // O accumulator, 128 columns
 
 struct FaArgs {
   const int* cu_q;        // [S + 1] row offsets of the sequences
@@ -45,13 +44,29 @@ struct FaArgs {
   float scale;
 };
 
+__device__ __forceinline__ void named_bar(int id, int threads) {
+  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
+}
+// Named barrier that also returns the OR of a predicate over the participating threads.
+__device__ __forceinline__ bool named_bar_or(int id, int threads, bool pred) {
+  uint32_t out;
+  asm volatile(
+      "{\n\t.reg .pred p, q;\n\t"
+      "setp.ne.b32 p, %3, 0;\n\t"
+      "barrier.cta.red.or.pred q, %1, %2, p;\n\t"
+      "selp.u32 %0, 1, 0, q;\n\t}"
+      : "=r"(out)
+      : "r"(id), "r"(threads), "r"((uint32_t)pred)
+      : "memory");
+  return out != 0;
+}
 __device__ __forceinline__ float ex2f(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
 
-__global__ void __launch_bounds__(FA_THREADS, 1)
+__global__ void __launch_bounds__(FA_THREADS, 2)
 flash_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                 const __grid_constant__ CUtensorMap tmV, const FaArgs a) {
   extern __shared__ uint8_t fa_raw[];
@@ -63,13 +78,14 @@ flash_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   uint64_t* kv_full = bars + 1;                  // [FA_STAGES]
   uint64_t* kv_empty = kv_full + FA_STAGES;      // [FA_STAGES]
   uint64_t* s_full = kv_empty + FA_STAGES;       // [2] MMA -> softmax: S tile ready
-  uint64_t* p_full = s_full + 2;                 // [2] softmax -> MMA: P written (128 arrivals)
-  uint64_t* o_full = p_full + 2;                 // [2] MMA -> softmax: O_j ready
-  uint64_t* o_free = o_full + 2;                 // [2] softmax -> MMA: O_j consumed (128 arrivals)
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(o_free + 2);
+  uint64_t* p_full = s_full + 2;                 // [2] softmax -> MMA: P written (256 arrivals)
+  uint64_t* pv_done = p_full + 2;                // [2] MMA -> softmax: P V of tile j accumulated (slot j % 2)
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(pv_done + 2);
+  float* mx_s = reinterpret_cast<float*>(tmem_slot + 4);  // [2 buffers][2 halves][128 rows] maxima, then [2 halves][128 rows] sums
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int seq = blockIdx.z, head = blockIdx.y, qt = blockIdx.x;
+  // late query tiles see the most keys under a causal mask: schedule them first
+  const int seq = blockIdx.z, head = blockIdx.y, qt = gridDim.x - 1 - blockIdx.x;
   const int kvh = head / (a.Hq / a.Hkv);
 
   if (threadIdx.x == 0) {
@@ -80,9 +96,8 @@ flash_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(&s_full[b], 1);
-      mbar_init(&p_full[b], 128);
-      mbar_init(&o_full[b], 1);
-      mbar_init(&o_free[b], 128);
+      mbar_init(&p_full[b], 256);
+      mbar_init(&pv_done[b], 1);
     }
     fence_barrier_init();
     tma_prefetch_desc(&tmQ);
@@ -90,7 +105,7 @@ flash_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     tma_prefetch_desc(&tmV);
   }
   if (warp == 1) {
-    tmem_alloc(tmem_slot, 512);
+    tmem_alloc(tmem_slot, 256);
     tmem_relinquish();
   }
   tc_fence_before();
@@ -172,122 +187,148 @@ flash_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         }
         ok = mbar_wait(&p_full[b], (j >> 1) & 1, 16);
         if (!ok) break;
-        if (j >= 2) {
-          ok = mbar_wait(&o_free[b], ((j >> 1) - 1) & 1, 17);
-          if (!ok) break;
-        }
         tc_fence_after();
         const uint32_t vt = smem_u32(ring + (size_t)(j % FA_STAGES) * STAGE_BYTES + K_BYTES);
-        const uint32_t d = tmem_base + TMEM_O + b * FA_HD;
+        const uint32_t d = tmem_base + TMEM_O;
         const uint32_t p_t = tmem_base + TMEM_S + b * FA_BN;
 #pragma unroll
         for (int k = 0; k < FA_BN / 16; ++k) {
           // 16 keys per step: 8 packed columns of P, two 8-key groups (2048 bytes) of V
           const uint64_t db = umma_desc_sw128_mn(vt + k * 2048, V_BYTES / 2);
-          tc_mma_f16_ts(d, p_t + k * 8, db, IDESC_O, k != 0);
+          tc_mma_f16_ts(d, p_t + k * 8, db, IDESC_O, (j | k) != 0);
         }
-        tc_commit(&o_full[b]);
+        tc_commit(&pv_done[b]);
         tc_commit(&kv_empty[j % FA_STAGES]);
       }
     }
   } else if (live) {
-    // ------------------------------ softmax warps 2..5 ------------------------------
+    // ------------------------------ softmax warps 2..9 ------------------------------
+    // Two threads per query row: warps 2-5 take keys 0-31 of a tile and output columns 0-63,
+    // warps 6-9 keys 32-63 and columns 64-127.  The pair agrees on the tile's row maximum
+    // through shared memory (one named barrier per tile); each keeps the sum of its own keys.
+    //
+    // P is scaled by a per-row reference maximum that is only raised when a tile exceeds it
+    // by more than 2^8 (P then stays below 256).  Raising it means multiplying the row of
+    // the O accumulator in TMEM, which needs the previous P V product to have finished, so
+    // the whole CTA takes that path together (the barrier carries an OR over all rows).  It
+    // is rare after the first tiles.
     const int q = warp & 3;                 // TMEM lane quarter of this warp
-    const int row = q0 + q * 32 + lane;     // query row (local index) owned by this thread
+    const int half = (warp - 2) >> 2;
+    const int r_local = q * 32 + lane;      // row inside the tile
+    const int row = q0 + r_local;           // query row (local index of the sequence)
     const uint32_t lane_addr = tmem_base + ((uint32_t)(q * 32) << 16);
     const float sl2 = a.scale * 1.4426950408889634f;
-    float o_acc[FA_HD];
-#pragma unroll
-    for (int i = 0; i < FA_HD; ++i) o_acc[i] = 0.0f;
-    float m_run = -INFINITY, l_run = 0.0f;
-    float corr_prev = 1.0f;  // rescale that belongs to the O_j still in flight
+    constexpr int HC = FA_BN / 2;           // keys per thread and tile
+    constexpr int HO = FA_HD / 2;           // output columns per thread
+    constexpr float RAISE = 8.0f;
+    float m_ref = -INFINITY, l_run = 0.0f;
     bool ok = true;
-    auto fold = [&](int j, float corr) {  // o_acc = o_acc * corr + O_j
+    for (int j = 0; j < n_tiles; ++j) {
       const int b = j & 1;
-      if (!mbar_wait(&o_full[b], (j >> 1) & 1, 18)) return false;
-      tc_fence_after();
+      float s[HC];
+      float mx = -INFINITY;
+      const int j0 = j * FA_BN + half * HC;
+      if (ok) ok = mbar_wait(&s_full[b], (j >> 1) & 1, 19);
+      ok = __all_sync(0xffffffffu, ok);  // the TMEM accesses below are warp-wide
+      if (ok) {
+        tc_fence_after();
+        uint32_t r[HC];
+        {
+          uint32_t(&r0)[16] = *reinterpret_cast<uint32_t(*)[16]>(&r[0]);
+          uint32_t(&r1)[16] = *reinterpret_cast<uint32_t(*)[16]>(&r[16]);
+          tmem_ld16(lane_addr + TMEM_S + b * FA_BN + half * HC, r0);
+          tmem_ld16(lane_addr + TMEM_S + b * FA_BN + half * HC + 16, r1);
+          tmem_ld_wait();
+        }
 #pragma unroll
-      for (int c = 0; c < FA_HD / 16; ++c) {
-        uint32_t r[16];
-        tmem_ld16(lane_addr + TMEM_O + b * FA_HD + c * 16, r);
-        tmem_ld_wait();
+        for (int i = 0; i < HC; ++i) s[i] = __uint_as_float(r[i]) * sl2;
+        if (j0 + HC > q_len || (a.causal && j0 + HC - 1 > row)) {
 #pragma unroll
-        for (int i = 0; i < 16; ++i) o_acc[c * 16 + i] = fmaf(o_acc[c * 16 + i], corr, __uint_as_float(r[i]));
+          for (int i = 0; i < HC; ++i)
+            if (j0 + i >= q_len || (a.causal && j0 + i > row)) s[i] = -INFINITY;
+        }
+#pragma unroll
+        for (int i = 0; i < HC; ++i) mx = fmaxf(mx, s[i]);
       }
-      tc_fence_before();
-      mbar_arrive(&o_free[b]);
-      return true;
-    };
-    for (int j = 0; j < n_tiles && ok; ++j) {
-      const int b = j & 1;
-      ok = mbar_wait(&s_full[b], (j >> 1) & 1, 19);
-      if (!ok) break;
-      tc_fence_after();
-      float s[FA_BN];
+      // pair maximum, and an OR over the CTA of "some row must raise its reference"
+      mx_s[(b * 2 + half) * FA_BM + r_local] = mx;
+      const bool raise_local = ok && j > 0 && mx > m_ref + RAISE;
+      const bool raise_any = named_bar_or(1, 256, raise_local);
+      if (!ok) continue;
+      mx = fmaxf(mx, mx_s[(b * 2 + (half ^ 1)) * FA_BM + r_local]);
+      if (j == 0) {
+        m_ref = mx;  // nothing accumulated yet
+      } else if (raise_any) {
+        ok = __all_sync(0xffffffffu, mbar_wait(&pv_done[b ^ 1], ((j - 1) >> 1) & 1, 20));  // P V of tile j-1 accumulated
+        if (!ok) continue;
+        tc_fence_after();
+        // tcgen05.ld / st are warp-wide (.sync.aligned): every lane takes this path, rows that
+        // keep their reference multiply by one
+        float f = 1.0f;
+        if (mx > m_ref + RAISE) {
+          f = (m_ref == -INFINITY) ? 0.0f : ex2f(m_ref - mx);
+          m_ref = mx;
+          l_run *= f;
+        }
 #pragma unroll
-      for (int c = 0; c < FA_BN / 16; ++c) {
-        uint32_t r[16];
-        tmem_ld16(lane_addr + TMEM_S + b * FA_BN + c * 16, r);
-        tmem_ld_wait();
+        for (int c = 0; c < HO / 16; ++c) {
+          uint32_t r[16];
+          tmem_ld16(lane_addr + TMEM_O + half * HO + c * 16, r);
+          tmem_ld_wait();
 #pragma unroll
-        for (int i = 0; i < 16; ++i) s[c * 16 + i] = __uint_as_float(r[i]) * sl2;
+          for (int i = 0; i < 16; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * f);
+          tmem_st16(lane_addr + TMEM_O + half * HO + c * 16, r);
+        }
       }
-      const int j0 = j * FA_BN;
-      if (j0 + FA_BN > q_len || (a.causal && j0 + FA_BN - 1 > row)) {
-#pragma unroll
-        for (int i = 0; i < FA_BN; ++i)
-          if (j0 + i >= q_len || (a.causal && j0 + i > row)) s[i] = -INFINITY;
-      }
-      float mx = m_run;
-#pragma unroll
-      for (int i = 0; i < FA_BN; ++i) mx = fmaxf(mx, s[i]);
-      const float m_use = (mx == -INFINITY) ? 0.0f : mx;
-      const float corr = (m_run == -INFINITY) ? 0.0f : ex2f(m_run - m_use);
-      m_run = mx;
+      const float m_use = (m_ref == -INFINITY) ? 0.0f : m_ref;
       float sum = 0.0f;
-      uint32_t packed[FA_BN / 2];
+      uint32_t packed[HC / 2];
 #pragma unroll
-      for (int i = 0; i < FA_BN; i += 2) {
+      for (int i = 0; i < HC; i += 2) {
         const float p0 = ex2f(s[i] - m_use), p1 = ex2f(s[i + 1] - m_use);
         sum += p0 + p1;
         __nv_bfloat162 v = __floats2bfloat162_rn(p0, p1);
         packed[i >> 1] = *reinterpret_cast<uint32_t*>(&v);
       }
-      l_run = l_run * corr + sum;
-#pragma unroll
-      for (int c = 0; c < FA_BN / 32; ++c) {
-        uint32_t r[16];
-#pragma unroll
-        for (int i = 0; i < 16; ++i) r[i] = packed[c * 16 + i];
-        tmem_st16(lane_addr + TMEM_S + b * FA_BN + c * 16, r);
-      }
+      l_run += sum;
+      tmem_st16(lane_addr + TMEM_S + b * FA_BN + half * (HC / 2), packed);
       tmem_st_wait();
       tc_fence_before();
       mbar_arrive(&p_full[b]);
-      // while the tensor core multiplies P_j V_j, fold the previous tile's product
-      if (j >= 1) ok = fold(j - 1, corr_prev);
-      corr_prev = corr;
     }
-    if (ok && n_tiles > 0) ok = fold(n_tiles - 1, corr_prev);
-    if (ok && row < q_len) {
+    // the pair's row sum, then the finished accumulator
+    mx_s[(4 + half) * FA_BM + r_local] = l_run;  // own region: the maxima slots may still be read
+    named_bar(1, 256);
+    l_run += mx_s[(4 + (half ^ 1)) * FA_BM + r_local];
+    if (ok && n_tiles > 0) ok = mbar_wait(&pv_done[(n_tiles - 1) & 1], ((n_tiles - 1) >> 1) & 1, 21);
+    ok = __all_sync(0xffffffffu, ok);
+    if (ok) {  // whole warps read TMEM; only rows inside the sequence are stored
+      tc_fence_after();
+      const bool store = row < q_len;
       const float inv = l_run > 0.0f ? 1.0f / l_run : 0.0f;
-      __nv_bfloat16* dst = a.out + (size_t)(q_start + row) * a.o_stride + (size_t)head * FA_HD;
+      __nv_bfloat16* dst = a.out + (size_t)(q_start + row) * a.o_stride + (size_t)head * FA_HD + half * HO;
 #pragma unroll
-      for (int c = 0; c < FA_HD / 8; ++c) {
-        uint4 v;
-        uint32_t* w = reinterpret_cast<uint32_t*>(&v);
+      for (int c = 0; c < HO / 16; ++c) {
+        uint32_t r[16];
+        tmem_ld16(lane_addr + TMEM_O + half * HO + c * 16, r);
+        tmem_ld_wait();
+        uint4 v[2];
+        uint32_t* w = reinterpret_cast<uint32_t*>(v);
 #pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          __nv_bfloat162 h = __floats2bfloat162_rn(o_acc[c * 8 + 2 * e] * inv, o_acc[c * 8 + 2 * e + 1] * inv);
+        for (int e = 0; e < 8; ++e) {
+          __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(r[2 * e]) * inv, __uint_as_float(r[2 * e + 1]) * inv);
           w[e] = *reinterpret_cast<uint32_t*>(&h);
         }
-        *reinterpret_cast<uint4*>(dst + c * 8) = v;
+        if (store) {
+          *reinterpret_cast<uint4*>(dst + c * 16) = v[0];
+          *reinterpret_cast<uint4*>(dst + c * 16 + 8) = v[1];
+        }
       }
     }
   }
   tc_fence_before();
   __syncthreads();
-  if (warp == 1) tmem_dealloc(tmem_base, 512);
+  if (warp == 1) tmem_dealloc(tmem_base, 256);
 }
 
 }  // namespace
@@ -321,7 +362,7 @@ PRISM_API int prism_flash_attention_tc(const void* q, long long q_stride, const 
   a.q_col0 = a.k_col0 = a.v_col0 = 0;
   a.causal = causal;
   a.scale = scale;
-  const size_t smem = 1024 + Q_BYTES + (size_t)FA_STAGES * STAGE_BYTES + 32 * 8 + 64;
+  const size_t smem = 1024 + Q_BYTES + (size_t)FA_STAGES * STAGE_BYTES + 32 * 8 + 64 + 6 * FA_BM * sizeof(float);
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(flash_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
