@@ -418,13 +418,18 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
           case EPI_BF16_FULL: {
             __nv_bfloat16* dst = out_b + row0 * a.ldo + m;
             const __nv_bfloat16* rsd = a.residual ? a.residual + row0 * a.ldr + m : nullptr;
+            // all residual loads first: out may alias residual (in-place add), and loads that
+            // sit between the stores would each wait for the store before them
+            float res[16];
+#pragma unroll
+            for (int j = 0; j < 16; ++j) res[j] = (rsd != nullptr && j < cols) ? __bfloat162float(rsd[(size_t)j * a.ldr]) : 0.0f;
 #pragma unroll
             for (int j = 0; j < 16; ++j) {
               if (j < cols) {
                 float v = __uint_as_float(r[j]) + bias_v;
                 if (a.act == 1) v = gelu_tanh(v);
                 else if (a.act == 2) v = gelu_erf(v);
-                if (rsd != nullptr) v = bf16_round(v) + __bfloat162float(rsd[(size_t)j * a.ldr]);
+                if (rsd != nullptr) v = bf16_round(v) + res[j];
                 dst[(size_t)j * a.ldo] = __float2bfloat16_rn(v);
               }
             }
@@ -693,13 +698,18 @@ gemm_wx_persistent_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_
             if (j < cols) dst[(size_t)j * a.ldo] = __float2bfloat16_rn(__uint_as_float(r[j]));
         } else {
           const __nv_bfloat16* rsd = a.residual ? a.residual + row0 * a.ldr + m : nullptr;
+          // all residual loads first: out may alias residual (in-place add), and loads that sit
+          // between the stores would each wait for the store before them
+          float res[16];
+#pragma unroll
+          for (int j = 0; j < 16; ++j) res[j] = (rsd != nullptr && j < cols) ? __bfloat162float(rsd[(size_t)j * a.ldr]) : 0.0f;
 #pragma unroll
           for (int j = 0; j < 16; ++j) {
             if (j < cols) {
               float v = __uint_as_float(r[j]) + bias_v;
               if (a.act == 1) v = gelu_tanh(v);
               else if (a.act == 2) v = gelu_erf(v);
-              if (rsd != nullptr) v = bf16_round(v) + __bfloat162float(rsd[(size_t)j * a.ldr]);
+              if (rsd != nullptr) v = bf16_round(v) + res[j];
               dst[(size_t)j * a.ldo] = __float2bfloat16_rn(v);
             }
           }

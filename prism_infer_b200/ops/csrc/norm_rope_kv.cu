@@ -228,6 +228,66 @@ __global__ void __launch_bounds__(256) layernorm_kernel(const bf16* x, const bf1
   }
 }
 
+// Rows of at most 2048 elements (the vision tower: 1152 and 4608): one warp per row, the row
+// lives in registers as 16-byte vectors, statistics with shuffles only.
+constexpr int LN_VEC = 8;  // vectors of 8 bf16 per lane
+__global__ void __launch_bounds__(256) layernorm_rows_kernel(const bf16* x, const bf16* w, const bf16* b, bf16* out, int T,
+                                                             int H, float eps) {
+  const int lane = threadIdx.x & 31;
+  const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  pdl_launch_dependents();
+  pdl_wait();
+  if (row >= T) return;
+  const int nvec = H >> 3;
+  const uint4* src = reinterpret_cast<const uint4*>(x + (size_t)row * H);
+  uint4 v[LN_VEC];
+  float s = 0.0f;
+#pragma unroll
+  for (int k = 0; k < LN_VEC; ++k) {
+    const int i = lane + 32 * k;
+    v[k] = i < nvec ? src[i] : make_uint4(0, 0, 0, 0);
+    const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&v[k]);
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const float2 f = __bfloat1622float2(p[e]);
+      s += f.x + f.y;
+    }
+  }
+  const float mean = warp_sum(s) / (float)H;
+  float ss = 0.0f;
+#pragma unroll
+  for (int k = 0; k < LN_VEC; ++k) {
+    if (lane + 32 * k < nvec) {
+      const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&v[k]);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float2 f = __bfloat1622float2(p[e]);
+        ss += (f.x - mean) * (f.x - mean) + (f.y - mean) * (f.y - mean);
+      }
+    }
+  }
+  const float rstd = rsqrtf(warp_sum(ss) / (float)H + eps);
+  uint4* dst = reinterpret_cast<uint4*>(out + (size_t)row * H);
+#pragma unroll
+  for (int k = 0; k < LN_VEC; ++k) {
+    const int i = lane + 32 * k;
+    if (i < nvec) {
+      const uint4 wv = reinterpret_cast<const uint4*>(w)[i], bv = reinterpret_cast<const uint4*>(b)[i];
+      const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&v[k]);
+      const __nv_bfloat162* wp = reinterpret_cast<const __nv_bfloat162*>(&wv);
+      const __nv_bfloat162* bp = reinterpret_cast<const __nv_bfloat162*>(&bv);
+      uint4 o;
+      __nv_bfloat162* op = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float2 f = __bfloat1622float2(p[e]), wf = __bfloat1622float2(wp[e]), bf = __bfloat1622float2(bp[e]);
+        op[e] = __floats2bfloat162_rn((f.x - mean) * rstd * wf.x + bf.x, (f.y - mean) * rstd * wf.y + bf.y);
+      }
+      dst[i] = o;
+    }
+  }
+}
+
 // ---------------------------------------------------------------------------------
 // QK-RMSNorm + M-RoPE + KV store.  One warp per (token, head); heads are ordered
 // [q heads | k heads | v heads] exactly like the packed QKV projection row.
@@ -475,23 +535,31 @@ __global__ void __launch_bounds__(256) pos_embed_add_kernel(bf16* x, const bf16*
 // angle[n][i] for i < hd/2: first hd/4 slots use the row coordinate, next hd/4 the column.
 __global__ void __launch_bounds__(256) vit_rope_kernel(bf16* qkv, const int* coords, const float* inv_freq, int N,
                                                        int heads, int hd) {
+  // The angle depends on (patch, i) only: 36 sin/cos pairs per patch are computed once into
+  // shared memory, then every (q|k, head) row is rotated with 4-byte accesses.
+  __shared__ float sn_s[128], cs_s[128];
   const int n = blockIdx.x;
   pdl_launch_dependents();
   pdl_wait();
   const int half = hd / 2, quarter = hd / 4;
-  const float row = (float)coords[2 * n], col = (float)coords[2 * n + 1];
-  const int work = 2 * heads * half;
+  if ((int)threadIdx.x < half) {
+    const int i = threadIdx.x;
+    const float pos = (float)coords[2 * n + (i < quarter ? 0 : 1)];
+    sincosf(pos * inv_freq[i % quarter], &sn_s[i], &cs_s[i]);
+  }
+  __syncthreads();
+  const int pairs = half / 2;  // two adjacent i per thread and step
+  const int work = 2 * heads * pairs;
   for (int w = threadIdx.x; w < work; w += blockDim.x) {
-    const int i = w % half;
-    const int h = (w / half) % heads;
-    const int which = w / (half * heads);  // 0 = q, 1 = k
-    const float ang = (i < quarter ? row : col) * inv_freq[i % quarter];
-    float sn, cs;
-    sincosf(ang, &sn, &cs);
+    const int i = (w % pairs) * 2;
+    const int h = (w / pairs) % heads;
+    const int which = w / (pairs * heads);  // 0 = q, 1 = k
     bf16* p = qkv + ((size_t)n * 3 + which) * heads * hd + (size_t)h * hd;
-    const float x0 = b2f(p[i]), x1 = b2f(p[i + half]);
-    p[i] = f2b(x0 * cs - x1 * sn);
-    p[i + half] = f2b(x1 * cs + x0 * sn);
+    const float2 x0 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(p + i));
+    const float2 x1 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(p + i + half));
+    const float c0 = cs_s[i], c1 = cs_s[i + 1], s0 = sn_s[i], s1 = sn_s[i + 1];
+    *reinterpret_cast<__nv_bfloat162*>(p + i) = __floats2bfloat162_rn(x0.x * c0 - x1.x * s0, x0.y * c1 - x1.y * s1);
+    *reinterpret_cast<__nv_bfloat162*>(p + i + half) = __floats2bfloat162_rn(x1.x * c0 + x0.x * s0, x1.y * c1 + x0.y * s1);
   }
 }
 
@@ -570,6 +638,12 @@ PRISM_API int prism_add_rmsnorm_packed(const void* partials, long long slab_stri
 PRISM_API int prism_layernorm(const void* x, const void* w, const void* b, void* out, int T, int H, float eps,
                               void* stream, int pdl) {
   if (T <= 0) return 0;
+  const unsigned long long addr = reinterpret_cast<unsigned long long>(x) | reinterpret_cast<unsigned long long>(w) |
+                                  reinterpret_cast<unsigned long long>(b) | reinterpret_cast<unsigned long long>(out);
+  if (H % 8 == 0 && H <= 32 * 8 * LN_VEC && (addr & 15ull) == 0) {
+    return (int)prism_launch(layernorm_rows_kernel, dim3((T + 7) / 8), dim3(256), 0, STREAM(stream), pdl != 0, (const bf16*)x,
+                             (const bf16*)w, (const bf16*)b, (bf16*)out, T, H, eps);
+  }
   const size_t smem = (size_t)H * sizeof(float);
   return (int)prism_launch(layernorm_kernel, dim3(T), dim3(256), smem, STREAM(stream), pdl != 0, (const bf16*)x,
                            (const bf16*)w, (const bf16*)b, (bf16*)out, H, eps);
@@ -657,6 +731,7 @@ PRISM_API int prism_pos_embed_add(void* x, const void* table, const void* idx, c
 PRISM_API int prism_vit_rope(void* qkv, const void* coords, const void* inv_freq, int N, int heads, int hd, void* stream,
                              int pdl) {
   if (N <= 0) return 0;
+  if (hd % 4 || hd > 256) return -1;
   return (int)prism_launch(vit_rope_kernel, dim3(N), dim3(256), 0, STREAM(stream), pdl != 0, (bf16*)qkv,
                            (const int*)coords, (const float*)inv_freq, N, heads, hd);
 }
