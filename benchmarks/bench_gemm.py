@@ -112,6 +112,27 @@ def main() -> None:
         }
         rows.append(row)
         print(json.dumps(row), flush=True)
+    # epilogue forms of the vision tower on the persistent kernel
+    for name, T, M, K, form in (("vit proj", 6272, 1152, 1152, "bias+residual in place"), ("vit fc2", 6272, 1152, 4304, "bias+residual in place"),
+                                ("vit fc1", 6272, 4304, 1152, "bias+gelu_tanh"), ("vit proj", 6272, 1152, 1152, "bias+residual separate")):
+        if args.only and args.only not in f"{name} epilogue":
+            continue
+        x = torch.randn(T, K, device=dev).to(torch.bfloat16)
+        w = (torch.randn(M, K, device=dev) * K ** -0.5).to(torch.bfloat16)
+        b = torch.randn(M, device=dev).to(torch.bfloat16)
+        res = torch.randn(T, M, device=dev).to(torch.bfloat16)
+        out = torch.empty_like(res)
+        if form == "bias+residual in place":
+            fn = lambda: ops.linear(x, w, bias=b, residual=res, out=res)  # noqa: E731
+        elif form == "bias+residual separate":
+            fn = lambda: ops.linear(x, w, bias=b, residual=res, out=out)  # noqa: E731
+        else:
+            fn = lambda: ops.linear(x, w, bias=b, act="gelu_tanh", out=out)  # noqa: E731
+        plain = timeit(lambda: ops.linear(x, w, out=out), args.iters, flush)
+        ms = timeit(fn, args.iters, flush)
+        row = {"case": f"{name} epilogue {form}", "T": T, "M": M, "K": K, "ms": round(ms, 5), "plain_ms": round(plain, 5)}
+        rows.append(row)
+        print(json.dumps(row), flush=True)
     if args.json:
         with open(args.json, "w") as fh:
             json.dump({"peaks": pk, "rows": rows}, fh, indent=1)

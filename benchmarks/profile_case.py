@@ -49,6 +49,11 @@ def main() -> None:
         w, x, b = rnd(4304, 1152, scale=0.03), rnd(6272, 1152), rnd(4304)
         for _ in range(reps):
             ops.linear(x, w, bias=b, act="gelu_tanh", bn=256 if case.endswith("tiled") else 0)
+    elif case == "gemm_vit_proj":
+        # vision-tower attention output projection with bias and in-place residual add
+        w, x, b, res = rnd(1152, 1152, scale=0.03), rnd(6272, 1152), rnd(1152), rnd(6272, 1152)
+        for _ in range(reps):
+            ops.linear(x, w, bias=b, residual=res, out=res)
     elif case == "gemm_dual":
         w, x = rnd(24576, 4096, scale=0.02), rnd(2048, 4096)
         for _ in range(reps):

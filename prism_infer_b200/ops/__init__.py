@@ -239,6 +239,7 @@ ACTX_ENABLED = _os.environ.get("PRISM_ACTX", "0") != "0"
 # while attention still runs.
 O_PROJ_STAGES = int(_os.environ.get("PRISM_O_PROJ_STAGES", "0"))
 ATTN_TC_ENABLED = _os.environ.get("PRISM_ATTN_TC", "1") != "0"
+PERSISTENT_ROWMAJOR = _os.environ.get("PRISM_PERSISTENT_ROWMAJOR", "1") != "0"
 PERSISTENT_MIN_TOKENS = int(_os.environ.get("PRISM_PERSISTENT_MIN_TOKENS", "512"))
 SMALL_TILE_SMEM_CAP = int(_os.environ.get("PRISM_SMALL_TILE_SMEM", "0"))
 
@@ -269,6 +270,7 @@ def apply_tuning() -> None:
     """Push the process-wide launch tuning into the native library (CUDA only)."""
     native.call("prism_gemm_set_small_tile_smem_cap", SMALL_TILE_SMEM_CAP)
     native.call("prism_gemm_set_persistent_min_tokens", PERSISTENT_MIN_TOKENS)
+    native.call("prism_gemm_set_persistent_rowmajor", 1 if PERSISTENT_ROWMAJOR else 0)
 
 
 def linear_actx(gate_up_partials: torch.Tensor, w: torch.Tensor, splits: int) -> torch.Tensor:

@@ -536,7 +536,12 @@ struct PersistArgs {
   __nv_bfloat16* out;
 };
 
-template <int BN, bool DUAL>
+// ROWMAJOR: the A operand (128-row tiles, TMEM lanes) holds the tokens and B the weights, so an
+// epilogue thread owns one token row and 16 consecutive features per TMEM load: bias, residual
+// and output move as 16-byte vectors instead of sixteen strided 2-byte accesses (the strided
+// residual loads made the vision projections 6x slower than their main loop).  In that form
+// a.M counts tokens and a.T features.
+template <int BN, bool DUAL, bool ROWMAJOR = false>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_wx_persistent_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX,
                           const PersistArgs a) {
@@ -670,9 +675,67 @@ gemm_wx_persistent_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_
       PRISM_TILE_COORDS(tile, m0, n0)
       const int m = m0 + q * 32 + lane;
       const bool m_ok = m < a.M;
-      const float bias_v = (a.bias != nullptr && m_ok) ? __bfloat162float(a.bias[m]) : 0.0f;
       const uint32_t t_lane = tmem_base + buf * ACC_COLS + ((uint32_t)(q * 32) << 16);
       const int n_valid = min(BN, a.T - n0);
+      if (ROWMAJOR) {
+        // lane = token m, columns = features n0 + c0 .. + 15 (a.T is a multiple of 16 here)
+        for (int c0 = 0; c0 < n_valid; c0 += 16) {
+          uint32_t r[16];
+          tmem_ld16(t_lane + c0, r);
+          tmem_ld_wait();
+          if (!m_ok) continue;
+          const int f0 = n0 + c0;
+          float v[16];
+#pragma unroll
+          for (int j = 0; j < 16; ++j) v[j] = __uint_as_float(r[j]);
+          if (a.bias != nullptr) {
+            const uint4 b0 = *reinterpret_cast<const uint4*>(a.bias + f0), b1 = *reinterpret_cast<const uint4*>(a.bias + f0 + 8);
+            const __nv_bfloat162* p0 = reinterpret_cast<const __nv_bfloat162*>(&b0);
+            const __nv_bfloat162* p1 = reinterpret_cast<const __nv_bfloat162*>(&b1);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              const float2 x0 = __bfloat1622float2(p0[e]), x1 = __bfloat1622float2(p1[e]);
+              v[2 * e] += x0.x;
+              v[2 * e + 1] += x0.y;
+              v[8 + 2 * e] += x1.x;
+              v[8 + 2 * e + 1] += x1.y;
+            }
+          }
+          if (a.act == 1) {
+#pragma unroll
+            for (int j = 0; j < 16; ++j) v[j] = gelu_tanh(v[j]);
+          } else if (a.act == 2) {
+#pragma unroll
+            for (int j = 0; j < 16; ++j) v[j] = gelu_erf(v[j]);
+          }
+          if (a.residual != nullptr) {
+            const __nv_bfloat16* rs = a.residual + (size_t)m * a.ldr + f0;
+            const uint4 r0 = *reinterpret_cast<const uint4*>(rs), r1 = *reinterpret_cast<const uint4*>(rs + 8);
+            const __nv_bfloat162* p0 = reinterpret_cast<const __nv_bfloat162*>(&r0);
+            const __nv_bfloat162* p1 = reinterpret_cast<const __nv_bfloat162*>(&r1);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              const float2 x0 = __bfloat1622float2(p0[e]), x1 = __bfloat1622float2(p1[e]);
+              v[2 * e] = bf16_round(v[2 * e]) + x0.x;
+              v[2 * e + 1] = bf16_round(v[2 * e + 1]) + x0.y;
+              v[8 + 2 * e] = bf16_round(v[8 + 2 * e]) + x1.x;
+              v[8 + 2 * e + 1] = bf16_round(v[8 + 2 * e + 1]) + x1.y;
+            }
+          }
+          uint4 o[2];
+          __nv_bfloat162* op = reinterpret_cast<__nv_bfloat162*>(o);
+#pragma unroll
+          for (int e = 0; e < 8; ++e) op[e] = __floats2bfloat162_rn(v[2 * e], v[2 * e + 1]);
+          __nv_bfloat16* dst = a.out + (size_t)m * a.ldo + f0;
+          *reinterpret_cast<uint4*>(dst) = o[0];
+          *reinterpret_cast<uint4*>(dst + 8) = o[1];
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&acc_empty[buf]);
+        continue;
+      }
+      const float bias_v = (a.bias != nullptr && m_ok) ? __bfloat162float(a.bias[m]) : 0.0f;
       for (int c0 = 0; c0 < n_valid; c0 += 16) {
         uint32_t r[16];
         uint32_t r2[16];
@@ -833,9 +896,10 @@ int launch_gemm(const CUtensorMap& tw, const CUtensorMap& tx, GemmArgs& a, int m
 
 
 int g_persistent_min_tokens = 512;  // 0 disables the persistent form
+int g_persistent_rowmajor = 1;      // 1: tokens on the TMEM lanes for the non-dual persistent GEMM
 int g_sm_count = 0;
 
-template <int BN, bool DUAL>
+template <int BN, bool DUAL, bool ROWMAJOR = false>
 int launch_persistent(const CUtensorMap& tw, const CUtensorMap& tx, PersistArgs& a, cudaStream_t stream, bool pdl) {
   constexpr int STAGE_BYTES = W_TILE_BYTES * (DUAL ? 2 : 1) + BN * BK * 2;
   int stages = (SMEM_LIMIT - 1024 - 512) / STAGE_BYTES;
@@ -845,7 +909,7 @@ int launch_persistent(const CUtensorMap& tw, const CUtensorMap& tx, PersistArgs&
   const size_t smem = (size_t)stages * STAGE_BYTES + 1024 + (2 * stages + 4) * 8 + 64;
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_wx_persistent_kernel<BN, DUAL>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_LIMIT);
+    cudaError_t e = cudaFuncSetAttribute(gemm_wx_persistent_kernel<BN, DUAL, ROWMAJOR>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_LIMIT);
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
@@ -856,7 +920,7 @@ int launch_persistent(const CUtensorMap& tw, const CUtensorMap& tx, PersistArgs&
   }
   const int tiles = a.m_tiles * a.n_tiles;
   const int grid = tiles < g_sm_count ? tiles : g_sm_count;
-  return (int)prism_launch(gemm_wx_persistent_kernel<BN, DUAL>, dim3(grid), dim3(GEMM_THREADS), smem, stream, pdl, tw, tx, a);
+  return (int)prism_launch(gemm_wx_persistent_kernel<BN, DUAL, ROWMAJOR>, dim3(grid), dim3(GEMM_THREADS), smem, stream, pdl, tw, tx, a);
 }
 
 }  // namespace
@@ -1020,6 +1084,23 @@ static int gemm_wx_impl(const void* W, const void* X, void* out, int M, int T, i
     pa.bias = a.bias;
     pa.residual = a.residual;
     pa.out = reinterpret_cast<__nv_bfloat16*>(out);
+    const unsigned long long vec_addr = reinterpret_cast<unsigned long long>(out) | reinterpret_cast<unsigned long long>(bias) |
+                                        reinterpret_cast<unsigned long long>(residual);
+    if (!dual && g_persistent_rowmajor && M % 16 == 0 && ldo % 8 == 0 && (residual == nullptr || ldr % 8 == 0) &&
+        (vec_addr & 15ull) == 0) {
+      // tokens on the TMEM lanes: vectorised bias / residual / output rows
+      CUtensorMap ta, tb;
+      rc = get_tensor_map(X, (unsigned long long)T, (unsigned long long)K, (unsigned long long)ldx, BM, &ta);
+      if (rc) return rc;
+      rc = get_tensor_map(W, (unsigned long long)w_rows_total, (unsigned long long)K, (unsigned long long)ldw, 256, &tb);
+      if (rc) return rc;
+      pa.M = T;
+      pa.T = M;
+      pa.m_tiles = (T + BM - 1) / BM;
+      pa.n_tiles = (M + 255) / 256;
+      pa.tokens_fastest = a.tokens_fastest ? 0 : 1;  // the A-row tile index is the token tile here
+      return launch_persistent<256, false, true>(ta, tb, pa, stream, p);
+    }
     // dual: two accumulators per tile, so 128 tokens per tile keep two tiles in TMEM
     const int pbn = dual ? 128 : 256;
     pa.n_tiles = (T + pbn - 1) / pbn;
@@ -1179,6 +1260,11 @@ PRISM_API int prism_gemm_wx_actx(const void* W, void* out, int M, int T, int K, 
   }
   return gemm_wx_impl(W, W, out, M, T, K, ldw, ldw, ldo, M, nullptr, nullptr, 0, 0, 0, 0, splits, 1, split_stride, 16, 0,
                       stream_ptr, pdl, pp, &ns);
+}
+
+PRISM_API int prism_gemm_set_persistent_rowmajor(int on) {
+  g_persistent_rowmajor = on;
+  return 0;
 }
 
 // Smallest token count that uses the persistent kernel (0 = never).

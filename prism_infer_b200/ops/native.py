@@ -51,6 +51,7 @@ _SIGNATURES = {
     "prism_gemv": "pppiiillliipiillppi",
     "prism_gemm_set_small_tile_smem_cap": "i",
     "prism_gemm_set_persistent_min_tokens": "i",
+    "prism_gemm_set_persistent_rowmajor": "i",
     "prism_set_next_prefetch": "pliii",
     "prism_gemm_wx_actx": "ppiiillilplippiilpppi",
     "prism_gemm_wx_allgather": "ppiiillllpippiilpppi",
