@@ -526,6 +526,7 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
 // path.
 // ------------------------------------------------------------------------------------
 struct PersistArgs {
+  int dual_rm;  // row-major form only: the B tile is 128 gate rows followed by 128 up rows, epilogue = SwiGLU
   int M, T, kb_total, w2_row_off, stages;
   int m_tiles, n_tiles;
   int tokens_fastest;
@@ -615,7 +616,13 @@ gemm_wx_persistent_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_
           mbar_expect_tx(&full[s], STAGE_BYTES);
           tma_load_2d(st, &tmW, &full[s], kb * BK, m0);
           if (DUAL) tma_load_2d(st + W_TILE_BYTES, &tmW, &full[s], kb * BK, a.w2_row_off + m0);
-          tma_load_2d(st + W_STAGE_BYTES, &tmX, &full[s], kb * BK, n0);
+          if (ROWMAJOR && a.dual_rm) {
+            // one 256-row B tile made of 128 gate rows and the matching 128 up rows
+            tma_load_2d(st + W_STAGE_BYTES, &tmX, &full[s], kb * BK, n0 / 2);
+            tma_load_2d(st + W_STAGE_BYTES + X_TILE_BYTES / 2, &tmX, &full[s], kb * BK, a.w2_row_off + n0 / 2);
+          } else {
+            tma_load_2d(st + W_STAGE_BYTES, &tmX, &full[s], kb * BK, n0);
+          }
         }
       }
       if (!ok) {
@@ -677,6 +684,33 @@ gemm_wx_persistent_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_
       const bool m_ok = m < a.M;
       const uint32_t t_lane = tmem_base + buf * ACC_COLS + ((uint32_t)(q * 32) << 16);
       const int n_valid = min(BN, a.T - n0);
+      if (ROWMAJOR && a.dual_rm) {
+        // lane = token m; accumulator columns 0..127 = gate features n0/2 + c, 128..255 = up
+        const int f_base = n0 / 2;
+        const int f_valid = min(BN / 2, a.T / 2 - f_base);
+        for (int c0 = 0; c0 < f_valid; c0 += 16) {
+          uint32_t rg[16], ru[16];
+          tmem_ld16(t_lane + c0, rg);
+          tmem_ld16(t_lane + BN / 2 + c0, ru);
+          tmem_ld_wait();
+          if (!m_ok) continue;
+          uint4 o[2];
+          __nv_bfloat162* op = reinterpret_cast<__nv_bfloat162*>(o);
+#pragma unroll
+          for (int e = 0; e < 8; ++e) {
+            const float g0 = bf16_round(__uint_as_float(rg[2 * e])), g1 = bf16_round(__uint_as_float(rg[2 * e + 1]));
+            const float u0 = bf16_round(__uint_as_float(ru[2 * e])), u1 = bf16_round(__uint_as_float(ru[2 * e + 1]));
+            op[e] = __floats2bfloat162_rn(bf16_round(silu(g0)) * u0, bf16_round(silu(g1)) * u1);
+          }
+          __nv_bfloat16* dst = a.out + (size_t)m * a.ldo + f_base + c0;
+          *reinterpret_cast<uint4*>(dst) = o[0];
+          *reinterpret_cast<uint4*>(dst + 8) = o[1];
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&acc_empty[buf]);
+        continue;
+      }
       if (ROWMAJOR) {
         // lane = token m, columns = features n0 + c0 .. + 15 (a.T is a multiple of 16 here)
         for (int c0 = 0; c0 < n_valid; c0 += 16) {
@@ -1086,6 +1120,23 @@ static int gemm_wx_impl(const void* W, const void* X, void* out, int M, int T, i
     pa.out = reinterpret_cast<__nv_bfloat16*>(out);
     const unsigned long long vec_addr = reinterpret_cast<unsigned long long>(out) | reinterpret_cast<unsigned long long>(bias) |
                                         reinterpret_cast<unsigned long long>(residual);
+    pa.dual_rm = 0;
+    if (dual && g_persistent_rowmajor && M % 16 == 0 && ldo % 8 == 0 && (vec_addr & 15ull) == 0 && bias == nullptr &&
+        residual == nullptr && act == 0) {
+      // SwiGLU with tokens on the TMEM lanes: one N = 256 MMA per step over [128 gate rows | 128 up rows]
+      CUtensorMap ta, tb;
+      rc = get_tensor_map(X, (unsigned long long)T, (unsigned long long)K, (unsigned long long)ldx, BM, &ta);
+      if (rc) return rc;
+      rc = get_tensor_map(W, (unsigned long long)w_rows_total, (unsigned long long)K, (unsigned long long)ldw, 128, &tb);
+      if (rc) return rc;
+      pa.dual_rm = 1;
+      pa.M = T;
+      pa.T = 2 * M;                       // accumulator columns per full sweep: gate + up
+      pa.m_tiles = (T + BM - 1) / BM;
+      pa.n_tiles = (M + 127) / 128;       // 128 features (256 accumulator columns) per tile
+      pa.tokens_fastest = a.tokens_fastest ? 0 : 1;
+      return launch_persistent<256, false, true>(ta, tb, pa, stream, p);
+    }
     if (!dual && g_persistent_rowmajor && M % 16 == 0 && ldo % 8 == 0 && (residual == nullptr || ldr % 8 == 0) &&
         (vec_addr & 15ull) == 0) {
       // tokens on the TMEM lanes: vectorised bias / residual / output rows
