@@ -685,12 +685,12 @@ def varlen_attention(
         out = torch.empty((T, Hq, D), dtype=torch.bfloat16, device=q.device)
     assert q.stride(2) == 1 and q.stride(1) == D and k.stride(1) == D and v.stride(1) == D
     assert k.stride(0) == v.stride(0) and cu_seqlens.dtype == torch.int32
-    if (ATTN_TC_ENABLED and D == 128 and q.stride(0) % 8 == 0 and k.stride(0) % 8 == 0
+    if (ATTN_TC_ENABLED and D in (128, 72) and q.stride(0) % 8 == 0 and k.stride(0) % 8 == 0
             and (q.data_ptr() | k.data_ptr() | v.data_ptr() | out.data_ptr()) % 16 == 0):
-        # head dimension 128: the tcgen05 / TMEM kernel
+        # the tcgen05 / TMEM kernel (head dimension 128, or 72 padded to 80)
         native.call(
             "prism_flash_attention_tc", _p(q), q.stride(0), _p(k), _p(v), k.stride(0), _p(out), out.stride(0),
-            _p(cu_seqlens), T, cu_seqlens.shape[0] - 1, int(max_len), Hq, Hkv, 1 if causal else 0, scale, _s(), _pdl(),
+            _p(cu_seqlens), T, cu_seqlens.shape[0] - 1, int(max_len), Hq, Hkv, D, 1 if causal else 0, scale, _s(), _pdl(),
         )
         return out
     native.call(

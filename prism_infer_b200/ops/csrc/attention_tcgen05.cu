@@ -1,4 +1,5 @@
-// Prefill attention on the fifth-generation tensor cores (head dimension 128, bf16 Q/K/V rows).
+// Prefill and vision attention on the fifth-generation tensor cores (bf16 Q/K/V rows, head
+// dimension 128, or 72 padded to 80 with zero columns that the TMA unit fills in).
 //
 // One CTA handles 128 query rows of one (sequence, query head) and walks the keys in tiles of
 // 64.  Warp 0 streams K/V tiles with TMA (128-byte swizzle) into a two-stage ring, one thread
@@ -36,10 +37,10 @@ constexpr int TMEM_O = 128;                     // O accumulator, 128 columns
 
 struct FaArgs {
   const int* cu_q;        // [S + 1] row offsets of the sequences
-  __nv_bfloat16* out;     // [T][Hq * 128]
+  __nv_bfloat16* out;     // [T][Hq * hd]
   long long o_stride;
   int Hq, Hkv;
-  int q_col0, k_col0, v_col0;  // first column of head 0 inside the respective tensor map
+  int hd;                 // real head dimension (<= HD_PAD)
   int causal;
   float scale;
 };
@@ -66,6 +67,10 @@ __device__ __forceinline__ float ex2f(float x) {
   return y;
 }
 
+// HD_PAD: head dimension rounded up to a multiple of 16 (the K extent of Q K^T and the N extent
+// of P V).  Shared-memory tiles always have two 64-column atoms; with HD_PAD = 80 the second
+// atom holds 8 real columns and zeros.
+template <int HD_PAD>
 __global__ void __launch_bounds__(FA_THREADS, 2)
 flash_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                 const __grid_constant__ CUtensorMap tmV, const FaArgs a) {
@@ -130,8 +135,8 @@ flash_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     if (lane == 0 && live) {
       // ------------------------------ TMA producer ------------------------------
       mbar_expect_tx(q_full, Q_BYTES);
-      tma_load_2d(q_s, &tmQ, q_full, a.q_col0 + head * FA_HD, q_start + q0);
-      tma_load_2d(q_s + Q_BYTES / 2, &tmQ, q_full, a.q_col0 + head * FA_HD + 64, q_start + q0);
+      tma_load_3d(q_s, &tmQ, q_full, 0, head, q_start + q0);
+      tma_load_3d(q_s + Q_BYTES / 2, &tmQ, q_full, 64, head, q_start + q0);
       bool ok = true;
       int issued = 0;
       for (int j = 0; j < n_tiles && ok; ++j) {
@@ -143,10 +148,10 @@ flash_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         uint8_t* st = ring + (size_t)s * STAGE_BYTES;
         const int row = q_start + j * FA_BN;
         mbar_expect_tx(&kv_full[s], STAGE_BYTES);
-        tma_load_2d(st, &tmK, &kv_full[s], a.k_col0 + kvh * FA_HD, row);
-        tma_load_2d(st + K_BYTES / 2, &tmK, &kv_full[s], a.k_col0 + kvh * FA_HD + 64, row);
-        tma_load_2d(st + K_BYTES, &tmV, &kv_full[s], a.v_col0 + kvh * FA_HD, row);
-        tma_load_2d(st + K_BYTES + V_BYTES / 2, &tmV, &kv_full[s], a.v_col0 + kvh * FA_HD + 64, row);
+        tma_load_3d(st, &tmK, &kv_full[s], 0, kvh, row);
+        tma_load_3d(st + K_BYTES / 2, &tmK, &kv_full[s], 64, kvh, row);
+        tma_load_3d(st + K_BYTES, &tmV, &kv_full[s], 0, kvh, row);
+        tma_load_3d(st + K_BYTES + V_BYTES / 2, &tmV, &kv_full[s], 64, kvh, row);
         issued = j + 1;
       }
       if (!ok) {
@@ -158,14 +163,14 @@ flash_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     if (lane == 0 && live) {
       // ------------------------------ MMA issuer ------------------------------
       constexpr uint32_t IDESC_S = umma_idesc_bf16(FA_BM, FA_BN);
-      constexpr uint32_t IDESC_O = umma_idesc_bf16(FA_BM, FA_HD) | UMMA_B_MN_MAJOR;
+      constexpr uint32_t IDESC_O = umma_idesc_bf16(FA_BM, HD_PAD) | UMMA_B_MN_MAJOR;
       const uint32_t q_addr = smem_u32(q_s);
       bool ok = mbar_wait(q_full, 0, 13);
       auto score = [&](int j) {  // S[j % 2] = Q K_j^T
         const uint32_t st = smem_u32(ring + (size_t)(j % FA_STAGES) * STAGE_BYTES);
         const uint32_t d = tmem_base + TMEM_S + (j & 1) * FA_BN;
 #pragma unroll
-        for (int k = 0; k < FA_HD / 16; ++k) {
+        for (int k = 0; k < HD_PAD / 16; ++k) {
           const uint64_t da = umma_desc_sw128(q_addr + (k >> 2) * (Q_BYTES / 2)) + 2 * (k & 3);
           const uint64_t db = umma_desc_sw128(st + (k >> 2) * (K_BYTES / 2)) + 2 * (k & 3);
           tc_mma_f16(d, da, db, IDESC_S, k != 0);
@@ -219,7 +224,9 @@ flash_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     const uint32_t lane_addr = tmem_base + ((uint32_t)(q * 32) << 16);
     const float sl2 = a.scale * 1.4426950408889634f;
     constexpr int HC = FA_BN / 2;           // keys per thread and tile
-    constexpr int HO = FA_HD / 2;           // output columns per thread
+    constexpr int HO = 64;                  // first output column of the second thread of a pair
+    constexpr int CHUNKS = HD_PAD / 16;     // 16-column chunks of the accumulator
+    const int c_begin = half * 4, c_end = half ? CHUNKS : (CHUNKS < 4 ? CHUNKS : 4);  // this thread's chunks
     constexpr float RAISE = 8.0f;
     float m_ref = -INFINITY, l_run = 0.0f;
     bool ok = true;
@@ -271,13 +278,13 @@ flash_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
           l_run *= f;
         }
 #pragma unroll
-        for (int c = 0; c < HO / 16; ++c) {
+        for (int c = c_begin; c < c_end; ++c) {
           uint32_t r[16];
-          tmem_ld16(lane_addr + TMEM_O + half * HO + c * 16, r);
+          tmem_ld16(lane_addr + TMEM_O + c * 16, r);
           tmem_ld_wait();
 #pragma unroll
           for (int i = 0; i < 16; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * f);
-          tmem_st16(lane_addr + TMEM_O + half * HO + c * 16, r);
+          tmem_st16(lane_addr + TMEM_O + c * 16, r);
         }
       }
       const float m_use = (m_ref == -INFINITY) ? 0.0f : m_ref;
@@ -306,11 +313,10 @@ flash_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       tc_fence_after();
       const bool store = row < q_len;
       const float inv = l_run > 0.0f ? 1.0f / l_run : 0.0f;
-      __nv_bfloat16* dst = a.out + (size_t)(q_start + row) * a.o_stride + (size_t)head * FA_HD + half * HO;
-#pragma unroll
-      for (int c = 0; c < HO / 16; ++c) {
+      __nv_bfloat16* dst = a.out + (size_t)(q_start + row) * a.o_stride + (size_t)head * a.hd;
+      for (int c = c_begin; c < c_end; ++c) {
         uint32_t r[16];
-        tmem_ld16(lane_addr + TMEM_O + half * HO + c * 16, r);
+        tmem_ld16(lane_addr + TMEM_O + c * 16, r);
         tmem_ld_wait();
         uint4 v[2];
         uint32_t* w = reinterpret_cast<uint32_t*>(v);
@@ -319,9 +325,9 @@ flash_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
           __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(r[2 * e]) * inv, __uint_as_float(r[2 * e + 1]) * inv);
           w[e] = *reinterpret_cast<uint32_t*>(&h);
         }
-        if (store) {
-          *reinterpret_cast<uint4*>(dst + c * 16) = v[0];
-          *reinterpret_cast<uint4*>(dst + c * 16 + 8) = v[1];
+        if (store) {  // the head dimension is a multiple of 8: whole 16-byte pieces or nothing
+          if (c * 16 + 8 <= a.hd) *reinterpret_cast<uint4*>(dst + c * 16) = v[0];
+          if (c * 16 + 16 <= a.hd) *reinterpret_cast<uint4*>(dst + c * 16 + 8) = v[1];
         }
       }
     }
@@ -333,25 +339,26 @@ flash_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
 
 }  // namespace
 
-// Causal or bidirectional self-attention over contiguous segments, head dimension 128.
+// Causal or bidirectional self-attention over contiguous segments, head dimension 128 or 72.
 // q [T][q_stride], k / v [T][kv_stride] bf16 with the heads side by side (views into a packed
 // QKV projection are fine); out [T][o_stride].  Rows and strides must be 16-byte aligned.
 PRISM_API int prism_flash_attention_tc(const void* q, long long q_stride, const void* k, const void* v,
                                        long long kv_stride, void* out, long long o_stride, const void* cu_q, int T,
-                                       int S, int max_q_len, int Hq, int Hkv, int causal, float scale, void* stream,
-                                       int pdl) {
+                                       int S, int max_q_len, int Hq, int Hkv, int hd, int causal, float scale,
+                                       void* stream, int pdl) {
   if (S <= 0 || max_q_len <= 0 || T <= 0) return 0;
   if (Hq % Hkv) return -1;
   if ((q_stride % 8) || (kv_stride % 8) || (o_stride % 8)) return -2;
   if ((reinterpret_cast<unsigned long long>(q) | reinterpret_cast<unsigned long long>(k) |
        reinterpret_cast<unsigned long long>(v) | reinterpret_cast<unsigned long long>(out)) & 15ull)
     return -3;
+  if (hd != 128 && hd != 72) return -4;
   CUtensorMap tq, tk, tv;
-  int rc = prism_get_tensor_map(q, (unsigned long long)T, (unsigned long long)Hq * FA_HD, (unsigned long long)q_stride, FA_BM, &tq);
+  int rc = prism_make_head_tensor_map(q, (unsigned long long)T, (unsigned)Hq, (unsigned)hd, (unsigned long long)q_stride, FA_BM, &tq);
   if (rc) return rc;
-  rc = prism_get_tensor_map(k, (unsigned long long)T, (unsigned long long)Hkv * FA_HD, (unsigned long long)kv_stride, FA_BN, &tk);
+  rc = prism_make_head_tensor_map(k, (unsigned long long)T, (unsigned)Hkv, (unsigned)hd, (unsigned long long)kv_stride, FA_BN, &tk);
   if (rc) return rc;
-  rc = prism_get_tensor_map(v, (unsigned long long)T, (unsigned long long)Hkv * FA_HD, (unsigned long long)kv_stride, FA_BN, &tv);
+  rc = prism_make_head_tensor_map(v, (unsigned long long)T, (unsigned)Hkv, (unsigned)hd, (unsigned long long)kv_stride, FA_BN, &tv);
   if (rc) return rc;
   FaArgs a;
   a.cu_q = reinterpret_cast<const int*>(cu_q);
@@ -359,17 +366,20 @@ PRISM_API int prism_flash_attention_tc(const void* q, long long q_stride, const 
   a.o_stride = o_stride;
   a.Hq = Hq;
   a.Hkv = Hkv;
-  a.q_col0 = a.k_col0 = a.v_col0 = 0;
+  a.hd = hd;
   a.causal = causal;
   a.scale = scale;
   const size_t smem = 1024 + Q_BYTES + (size_t)FA_STAGES * STAGE_BYTES + 32 * 8 + 64 + 6 * FA_BM * sizeof(float);
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(flash_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaError_t e = cudaFuncSetAttribute(flash_tc_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(flash_tc_kernel<80>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
   const int tiles = (max_q_len + FA_BM - 1) / FA_BM;
-  return (int)prism_launch(flash_tc_kernel, dim3(tiles, Hq, S), dim3(FA_THREADS), smem, reinterpret_cast<cudaStream_t>(stream),
-                           pdl != 0, tq, tk, tv, a);
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  if (hd == 128)
+    return (int)prism_launch(flash_tc_kernel<128>, dim3(tiles, Hq, S), dim3(FA_THREADS), smem, st, pdl != 0, tq, tk, tv, a);
+  return (int)prism_launch(flash_tc_kernel<80>, dim3(tiles, Hq, S), dim3(FA_THREADS), smem, st, pdl != 0, tq, tk, tv, a);
 }

@@ -174,6 +174,12 @@ __device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* m
       ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(m)), "r"(smem_u32(bar)), "r"(x), "r"(y)
       : "memory");
 }
+__device__ __forceinline__ void tma_load_3d(void* smem_dst, const CUtensorMap* m, uint64_t* bar, int x, int y, int z) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+      ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(m)), "r"(smem_u32(bar)), "r"(x), "r"(y), "r"(z)
+      : "memory");
+}
 __device__ __forceinline__ void tma_load_2d_hint(void* smem_dst, const CUtensorMap* m, uint64_t* bar, int x, int y,
                                                  uint64_t policy) {
   asm volatile(
@@ -291,6 +297,10 @@ __host__ __device__ constexpr uint32_t umma_idesc_bf16(int m, int n) {
 // box of box_rows x 64 elements, 128-byte swizzle (defined in gemm_tcgen05.cu).
 int prism_get_tensor_map(const void* ptr, unsigned long long rows, unsigned long long cols, unsigned long long ld,
                          unsigned box_rows, CUtensorMap* out);
+// [tokens][heads][head_dim] view, box = box_rows tokens x 1 head x 64 columns (columns past
+// head_dim read as zeros); see gemm_tcgen05.cu.
+int prism_make_head_tensor_map(const void* ptr, unsigned long long tokens, unsigned heads, unsigned head_dim,
+                               unsigned long long ld, unsigned box_rows, CUtensorMap* out);
 struct PrismLaunch {
   cudaStream_t stream;
   int pdl;  // 1: launch with programmatic stream serialization

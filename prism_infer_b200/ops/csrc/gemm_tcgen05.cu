@@ -964,6 +964,25 @@ int prism_get_tensor_map(const void* ptr, unsigned long long rows, unsigned long
   return get_tensor_map(ptr, rows, cols, ld, box_rows, out);
 }
 
+// [tokens][heads][head_dim] bf16 view (head stride = head_dim, token stride ld elements) with a
+// box of box_rows tokens x 1 head x 64 columns, 128-byte swizzle.  Columns past head_dim are
+// out of bounds of the innermost dimension and read as zeros, whatever the neighbouring head
+// holds.  Not cached: the encode costs about a microsecond.
+int prism_make_head_tensor_map(const void* ptr, unsigned long long tokens, unsigned heads, unsigned head_dim,
+                               unsigned long long ld, unsigned box_rows, CUtensorMap* out) {
+  EncodeTiledFn fn = get_encode_fn();
+  if (!fn) return -100;
+  if ((reinterpret_cast<uintptr_t>(ptr) & 15) || ((ld * 2) & 15) || ((head_dim * 2) & 15)) return -101;
+  cuuint64_t dims[3] = {head_dim, heads, tokens};
+  cuuint64_t strides[2] = {(cuuint64_t)head_dim * 2, ld * 2};
+  cuuint32_t box[3] = {BK, 1, box_rows};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(ptr), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : -102 - (int)r;
+}
+
 // W [w_rows_total, K] (row stride ldw), X [T, K] (row stride ldx), both bf16.
 // out: bf16 [T, ldo] (features along the row) or fp32 [splits][T][ldo] when out_f32.
 // dual: second weight tile starts at row w2_row_off; output = silu(W1 x) * (W2 x), M rows.

@@ -47,7 +47,7 @@ _SIGNATURES = {
     "prism_add_rmsnorm_wait": "plippppppiifpipipi",
     "prism_add_rmsnorm_packed": "plippppppiifpipi",
     "prism_gemm_wx_normx": "ppiiilliiiiilplippppfpilpipi",
-    "prism_flash_attention_tc": "plpplplpiiiiiifpi",
+    "prism_flash_attention_tc": "plpplplpiiiiiiifpi",
     "prism_gemv": "pppiiillliipiillppi",
     "prism_gemm_set_small_tile_smem_cap": "i",
     "prism_gemm_set_persistent_min_tokens": "i",

@@ -440,3 +440,21 @@ def test_tcgen05_flash_attention_matches_fp32_reference(cuda_device, causal, len
     monkeypatch.setattr(ops, "ATTN_TC_ENABLED", False)
     legacy = ops.varlen_attention(q, dev[:, Hq:Hq + Hkv], dev[:, Hq + Hkv:], cu.cuda(), max(lens), causal=causal)
     close(got, legacy.float().cpu(), 2e-2, 2e-2, "tcgen05 vs mma.sync attention")
+
+
+@pytest.mark.parametrize("lens", [(784, 784, 100), (196,), (130, 1, 257)])
+def test_tcgen05_flash_attention_head_dim_72(cuda_device, lens, monkeypatch):
+    """Vision-tower shape: 16 heads x 72 read as views of the packed QKV rows; the kernel pads the
+    head to 80 columns with zeros supplied by the TMA unit."""
+    H, D = 16, 72
+    N = sum(lens)
+    g = torch.Generator().manual_seed(N)
+    qkv = (torch.randn(N, 3 * H * D, generator=g) * 0.8).to(torch.bfloat16)
+    hv = qkv.view(N, 3, H, D)
+    cu = torch.tensor([0] + list(torch.tensor(lens).cumsum(0).tolist()), dtype=torch.int32)
+    ref = ops.varlen_attention(hv[:, 0].float(), hv[:, 1].float(), hv[:, 2].float(), cu, max(lens), causal=False)
+    dev = hv.cuda()
+    monkeypatch.setattr(ops, "ATTN_TC_ENABLED", True)
+    got = ops.varlen_attention(dev[:, 0], dev[:, 1], dev[:, 2], cu.cuda(), max(lens), causal=False)
+    torch.cuda.synchronize()
+    close(got, ref, 2e-2, 2e-2, f"tcgen05 attention hd 72 lens={lens}")
