@@ -79,6 +79,15 @@ def main() -> None:
         kv = torch.tensor([T], dtype=torch.int32, device=dev)
         for _ in range(reps):
             ops.paged_prefill_attention(q, cache, 0, cu, kv, bt, T)
+    elif case == "attention_tc":
+        # causal prefill attention over fresh bf16 K/V rows (views of a packed projection), tcgen05 kernel
+        T, Hq, Hkv, D = 2048, 32, 8, 128
+        qkv = rnd(T, (Hq + 2 * Hkv) * D)
+        heads = qkv.view(T, Hq + 2 * Hkv, D)
+        q = heads[:, :Hq].contiguous()
+        cu = torch.tensor([0, T], dtype=torch.int32, device=dev)
+        for _ in range(reps):
+            ops.varlen_attention(q, heads[:, Hq:Hq + Hkv], heads[:, Hq + Hkv:], cu, T, causal=True)
     elif case == "gemm_normx":
         ws = [rnd(6144, 4096, scale=0.02) for _ in range(4)]
         parts = torch.randn(4, 1, 4096, device=dev)

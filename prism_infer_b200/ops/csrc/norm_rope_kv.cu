@@ -447,6 +447,107 @@ __global__ void __launch_bounds__(256) qk_norm_rope_store_kernel(const QkvArgs a
 }
 
 // ---------------------------------------------------------------------------------
+// Prefill form of the kernel above (bf16 source rows, head dimension 128): one CTA per token.
+// The 64 rotary angles of the token are evaluated once into shared memory instead of once
+// per head, and every lane moves adjacent element pairs (4-byte accesses).  Same rounding
+// points as the per-head kernel.
+// ---------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) qk_norm_rope_store_token_kernel(const QkvArgs a) {
+  constexpr int D = 128, HALF = 64;
+  __shared__ float cs_s[HALF], sn_s[HALF];
+  const int t = blockIdx.x;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int heads = a.Hq + 2 * a.Hkv;
+  pdl_launch_dependents();
+  pdl_wait();
+  if ((int)threadIdx.x < HALF && a.apply_rope) {
+    const int i = threadIdx.x;
+    const float pos = (float)a.positions[(size_t)a.axis[i] * a.T + t];
+    float sn, cs;
+    sincosf(pos * a.inv_freq[i], &sn, &cs);
+    sn_s[i] = bf16_round(sn);
+    cs_s[i] = bf16_round(cs);
+  }
+  __syncthreads();
+  const long long slot = a.slots[t];
+  const int i0 = 2 * lane;  // this lane's elements: i0, i0 + 1 and i0 + 64, i0 + 65
+  for (int h = warp; h < heads; h += 8) {
+    const bool is_q = h < a.Hq;
+    const bool is_k = !is_q && h < a.Hq + a.Hkv;
+    bf16* src = const_cast<bf16*>(a.qkv) + (size_t)t * a.row_stride + (size_t)h * D;
+    const float2 lo2 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(src + i0));
+    const float2 hi2 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(src + i0 + HALF));
+    float lo[2] = {lo2.x, lo2.y}, hi[2] = {hi2.x, hi2.y};
+    if (is_q || is_k) {
+      if (a.apply_norm) {
+        float ss = lo[0] * lo[0] + lo[1] * lo[1] + hi[0] * hi[0] + hi[1] * hi[1];
+        ss = warp_sum(ss);
+        const float rstd = rsqrtf(ss / (float)D + a.eps);
+        const bf16* w = is_q ? a.q_weight : a.k_weight;
+        const float2 wl = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(w + i0));
+        const float2 wh = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(w + i0 + HALF));
+        lo[0] = bf16_round(bf16_round(lo[0] * rstd) * wl.x);
+        lo[1] = bf16_round(bf16_round(lo[1] * rstd) * wl.y);
+        hi[0] = bf16_round(bf16_round(hi[0] * rstd) * wh.x);
+        hi[1] = bf16_round(bf16_round(hi[1] * rstd) * wh.y);
+      }
+      if (a.apply_rope) {
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+          const float cs = cs_s[i0 + e], sn = sn_s[i0 + e];
+          const float x0 = lo[e], x1 = hi[e];
+          lo[e] = bf16_round(bf16_round(x0 * cs) + bf16_round(-x1 * sn));
+          hi[e] = bf16_round(bf16_round(x1 * cs) + bf16_round(x0 * sn));
+        }
+      }
+    }
+    const __nv_bfloat162 lo_b = __floats2bfloat162_rn(lo[0], lo[1]), hi_b = __floats2bfloat162_rn(hi[0], hi[1]);
+    if (is_q) {
+      if (a.q_out != nullptr) {
+        bf16* dst = a.q_out + (size_t)t * a.q_stride + (size_t)h * D;
+        *reinterpret_cast<__nv_bfloat162*>(dst + i0) = lo_b;
+        *reinterpret_cast<__nv_bfloat162*>(dst + i0 + HALF) = hi_b;
+      }
+      continue;
+    }
+    if (is_k && a.k_writeback) {
+      *reinterpret_cast<__nv_bfloat162*>(src + i0) = lo_b;
+      *reinterpret_cast<__nv_bfloat162*>(src + i0 + HALF) = hi_b;
+    }
+    if (slot < 0) continue;
+    const int kvh = is_k ? h - a.Hq : h - a.Hq - a.Hkv;
+    const long long blk = slot / a.page;
+    const int off = (int)(slot % a.page);
+    const size_t row = ((size_t)blk * a.Hkv + kvh) * a.page + off;
+    void* cache = is_k ? a.k_cache : a.v_cache;
+    if (a.kv_mode == 0) {
+      bf16* dst = reinterpret_cast<bf16*>(cache) + row * D;
+      *reinterpret_cast<__nv_bfloat162*>(dst + i0) = lo_b;
+      *reinterpret_cast<__nv_bfloat162*>(dst + i0 + HALF) = hi_b;
+    } else {
+      float scale = 1.0f;
+      if (a.kv_mode == 2) {
+        float am = fmaxf(fmaxf(fabsf(lo[0]), fabsf(lo[1])), fmaxf(fabsf(hi[0]), fabsf(hi[1])));
+        am = warp_max(am);
+        scale = fmaxf(am / FP8_MAX, FP8_SCALE_FLOOR);
+        if (lane == 0) (is_k ? a.k_scale : a.v_scale)[row] = scale;
+      }
+      __nv_fp8_storage_t* dst = reinterpret_cast<__nv_fp8_storage_t*>(cache) + row * D;
+      unsigned short lo8 = 0, hi8 = 0;
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        const float q0 = fminf(fmaxf(lo[e] / scale, -FP8_MAX), FP8_MAX);
+        const float q1 = fminf(fmaxf(hi[e] / scale, -FP8_MAX), FP8_MAX);
+        lo8 |= (unsigned short)__nv_cvt_float_to_fp8(q0, __NV_SATFINITE, __NV_E4M3) << (8 * e);
+        hi8 |= (unsigned short)__nv_cvt_float_to_fp8(q1, __NV_SATFINITE, __NV_E4M3) << (8 * e);
+      }
+      *reinterpret_cast<unsigned short*>(dst + i0) = lo8;
+      *reinterpret_cast<unsigned short*>(dst + i0 + HALF) = hi8;
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------------
 // SwiGLU on a packed [T][2I] row (gate | up), bf16 source or fp32 split-K slabs.
 // ---------------------------------------------------------------------------------
 __global__ void __launch_bounds__(256) swiglu_kernel(const bf16* gu, const float* partials, long long slab_stride, int P,
@@ -691,6 +792,11 @@ PRISM_API int prism_qk_norm_rope_store(const void* qkv, const void* partials, lo
   const int helpers = a.pf.rows > 0 ? a.pf.helpers : 0;
   if (helpers == 0) a.pf.rows = 0;
   dim3 grid(a.real_ctas + helpers), block(wpb * 32);
+  if (D == 128 && qkv != nullptr && T >= 64 && (row_stride % 2) == 0 && (q_stride % 2) == 0 &&
+      ((reinterpret_cast<unsigned long long>(qkv) | reinterpret_cast<unsigned long long>(q_out)) & 3ull) == 0) {
+    a.pf.rows = 0;
+    return (int)prism_launch(qk_norm_rope_store_token_kernel, dim3(T), dim3(256), 0, STREAM(stream), pdl != 0, a);
+  }
   if (D == 128) return (int)prism_launch(qk_norm_rope_store_kernel<128>, grid, block, 0, STREAM(stream), pdl != 0, a);
   if (D == 64) return (int)prism_launch(qk_norm_rope_store_kernel<64>, grid, block, 0, STREAM(stream), pdl != 0, a);
   return -2;
