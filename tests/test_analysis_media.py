@@ -153,3 +153,65 @@ def test_quality_protocol_validator():
         mutate(bad)
         with pytest.raises(ValueError, match=msg):
             qp.validate_quality_protocol(bad)
+
+
+def test_selection_materialisation_and_verification(tmp_path):
+    import io
+
+    from PIL import Image
+
+    from prism_infer_b200.analysis import quality_materialization as qm
+    from prism_infer_b200.utils import verify_quality_data as vq
+
+    ids = [f"s{i}" for i in range(40)] + [7]
+    sel = qm.select_sample_ids(ids, dataset_id="docvqa", revision="abc", seed=11, development_samples=5, final_samples=12)
+    assert sel.final_ids[:5] == sel.development_ids and len(set(sel.final_ids)) == 12
+    again = qm.select_sample_ids(list(reversed(ids)), dataset_id="docvqa", revision="abc", seed=11, development_samples=5, final_samples=12)
+    assert again == sel                                    # independent of input order
+    assert qm.select_sample_ids(ids, dataset_id="docvqa", revision="abc", seed=12, development_samples=5, final_samples=12) != sel
+    with pytest.raises(ValueError):
+        qm.select_sample_ids(["a", "a"], dataset_id="d", revision="r", seed=1, development_samples=1, final_samples=1)
+    rng = np.random.default_rng(0)
+    records = []
+    for sid in sel.final_ids:
+        buf = io.BytesIO()
+        Image.fromarray(rng.integers(0, 256, (12, 16, 3), dtype=np.uint8)).save(buf, format="PNG")
+        media = qm.materialize_image(buf.getvalue(), root=tmp_path, dataset_id="docvqa")
+        assert media["width"] == 16 and media["height"] == 12 and (tmp_path / media["materialized_path"]).exists()
+        records.append({"sample_id": sid, "question": "q", "media": [media]})
+    manifest = qm.materialization_manifest(dataset_id="docvqa", revision="abc", seed=11, selection=sel, records=records)
+    out = vq.verify(manifest, records, ids, str(tmp_path))
+    assert out == {"records": 12, "unique_media_files": 12, "bytes": out["bytes"]} and out["bytes"] > 0
+    victim = tmp_path / records[3]["media"][0]["materialized_path"]
+    victim.write_bytes(victim.read_bytes() + b"x")
+    with pytest.raises(OSError, match="hash mismatch"):
+        vq.verify(manifest, records, ids, str(tmp_path))
+    with pytest.raises(ValueError, match="escapes"):
+        qm.safe_materialized_path(tmp_path, "../x")
+    with pytest.raises(ValueError, match="do not match"):
+        qm.validate_selected_records(records[1:], sel.final_ids)
+
+
+def test_media_groups_and_media_first_prompt():
+    from prism_infer_b200.analysis import working_set_quality as wq
+
+    def rec(sid, digests, **kw):
+        return {"sample_id": sid, "media": [{"sha256": d * 64} for d in digests], **kw}
+
+    records = [rec("a", "12"), rec("b", "21"), rec("c", "12"), rec("d", "3"), rec("e", "12"), rec("f", "21")]
+    groups = wq.select_multi_question_groups(records)
+    by_group = {}
+    for g in groups:
+        by_group.setdefault(g.media_group_id, []).append((g.record["sample_id"], g.question_index, g.group_size))
+    assert sorted(by_group.values()) == [[("a", 0, 3), ("c", 1, 3), ("e", 2, 3)], [("b", 0, 2), ("f", 1, 2)]]
+    assert len(wq.select_multi_question_groups(records, max_groups=1)) in (2, 3)
+    assert wq.media_group_id(rec("x", "12")) != wq.media_group_id(rec("x", "12", temporal_bound={"start": 0, "end": 2}))
+    with pytest.raises(ValueError):
+        wq.ordered_media_sha256({"media": [{"sha256": "zz"}]})
+    prompt = wq.build_media_first_prompt("Is <image> brighter than <image>?", 2, options=["A. yes", "B. no"], hint="Answer with a letter.")
+    assert prompt.startswith("Image 1: <image>\nImage 2: <image>\nThe images above are numbered Image 1 through Image 2 in order.\n")
+    assert "Is Image 1 brighter than Image 2?" in prompt and prompt.endswith("Answer with a letter.")
+    dense = [{"sample_id": i, "correct": i % 2 == 0} for i in range(6)]
+    compact = [{"sample_id": i, "correct": i % 3 == 0, "deleted_visual_tokens": 10 if i >= 2 else 0} for i in range(6)]
+    assert wq.paired_deleted_subset(dense, compact) == {"cohort": 4, "dense_correct": 2, "compact_correct": 1}
+    assert wq.summarize_stage_samples(compact)["samples_with_deletions"] == 4
