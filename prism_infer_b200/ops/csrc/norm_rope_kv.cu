@@ -201,6 +201,83 @@ __global__ void __launch_bounds__(1024) add_rmsnorm_kernel(const AddNormArgs a) 
 }
 
 // ---------------------------------------------------------------------------------
+// Prefill form of add+RMSNorm (bf16 delta rows, hidden size at most 8192): one warp per row,
+// the pre-norm row lives in registers as 16-byte vectors, no shared memory or block barrier.
+// Same rounding points as add_rmsnorm_kernel.
+// ---------------------------------------------------------------------------------
+constexpr int RN_VEC = 32;  // vectors of 8 bf16 per lane (8192 / 32 / 8)
+template <int NV>
+__global__ void __launch_bounds__(256) add_rmsnorm_rows_kernel(const AddNormArgs a) {
+  const int lane = threadIdx.x & 31;
+  const int t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  pdl_launch_dependents();
+  pdl_wait();
+  if (t >= a.T) return;
+  const int H = a.H, nvec = H >> 3;
+  const size_t base = (size_t)t * H;
+  const int ex = a.extra != nullptr ? a.extra_index[t] : -1;
+  uint4 v[NV];
+  float ss = 0.0f;
+#pragma unroll
+  for (int k = 0; k < NV; ++k) {
+    const int i = lane + 32 * k;
+    if (i < nvec) {
+      uint4 x = reinterpret_cast<const uint4*>(a.x_in + base)[i];
+      __nv_bfloat162* xp = reinterpret_cast<__nv_bfloat162*>(&x);
+      float2 d[4];
+#pragma unroll
+      for (int e = 0; e < 4; ++e) d[e] = __bfloat1622float2(xp[e]);
+      if (a.residual_in != nullptr) {
+        const uint4 r = reinterpret_cast<const uint4*>(a.residual_in + base)[i];
+        const __nv_bfloat162* rp = reinterpret_cast<const __nv_bfloat162*>(&r);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float2 f = __bfloat1622float2(rp[e]);
+          d[e].x = bf16_round(f.x + d[e].x);
+          d[e].y = bf16_round(f.y + d[e].y);
+        }
+      }
+      if (ex >= 0) {
+        const uint4 r = reinterpret_cast<const uint4*>(a.extra + (size_t)ex * H)[i];
+        const __nv_bfloat162* rp = reinterpret_cast<const __nv_bfloat162*>(&r);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float2 f = __bfloat1622float2(rp[e]);
+          d[e].x = bf16_round(d[e].x + f.x);
+          d[e].y = bf16_round(d[e].y + f.y);
+        }
+      }
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        ss += d[e].x * d[e].x + d[e].y * d[e].y;
+        xp[e] = __floats2bfloat162_rn(d[e].x, d[e].y);  // exact: the sums are already bf16 values
+      }
+      v[k] = x;
+      if (a.residual_out != nullptr) reinterpret_cast<uint4*>(a.residual_out + base)[i] = x;
+    }
+  }
+  const float rstd = rsqrtf(warp_sum(ss) / (float)H + a.eps);
+  if (a.out == nullptr) return;
+#pragma unroll
+  for (int k = 0; k < NV; ++k) {
+    const int i = lane + 32 * k;
+    if (i < nvec) {
+      const uint4 w = reinterpret_cast<const uint4*>(a.weight)[i];
+      const __nv_bfloat162* wp = reinterpret_cast<const __nv_bfloat162*>(&w);
+      const __nv_bfloat162* xp = reinterpret_cast<const __nv_bfloat162*>(&v[k]);
+      uint4 o;
+      __nv_bfloat162* op = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float2 f = __bfloat1622float2(xp[e]), wf = __bfloat1622float2(wp[e]);
+        op[e] = __floats2bfloat162_rn(bf16_round(f.x * rstd) * wf.x, bf16_round(f.y * rstd) * wf.y);
+      }
+      reinterpret_cast<uint4*>(a.out + base)[i] = o;
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------------
 // LayerNorm with bias (vision tower), one CTA per row, fp32 statistics.
 // ---------------------------------------------------------------------------------
 __global__ void __launch_bounds__(256) layernorm_kernel(const bf16* x, const bf16* w, const bf16* b, bf16* out, int H,
@@ -701,6 +778,18 @@ static int add_rmsnorm_impl(const void* partials, long long slab_stride, int P, 
   if (smem > 48 * 1024) {
     cudaError_t e = cudaFuncSetAttribute(add_rmsnorm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
+  }
+  {
+    const unsigned long long addr = reinterpret_cast<unsigned long long>(x_in) | reinterpret_cast<unsigned long long>(residual_in) |
+                                    reinterpret_cast<unsigned long long>(residual_out) | reinterpret_cast<unsigned long long>(extra) |
+                                    reinterpret_cast<unsigned long long>(weight) | reinterpret_cast<unsigned long long>(out);
+    if (T >= 64 && P == 0 && x_in != nullptr && n_wait == 0 && H % 8 == 0 && H <= 8192 && (addr & 15ull) == 0) {
+      a.pf.rows = 0;
+      dim3 grid((T + 7) / 8), block(256);
+      if (H <= 2048) return (int)prism_launch(add_rmsnorm_rows_kernel<8>, grid, block, 0, STREAM(stream), pdl != 0, a);
+      if (H <= 4096) return (int)prism_launch(add_rmsnorm_rows_kernel<16>, grid, block, 0, STREAM(stream), pdl != 0, a);
+      return (int)prism_launch(add_rmsnorm_rows_kernel<RN_VEC>, grid, block, 0, STREAM(stream), pdl != 0, a);
+    }
   }
   // few rows: one wide CTA per row so every element has its own thread; many rows: 256 threads
   int threads = T <= 64 ? 1024 : 256;
