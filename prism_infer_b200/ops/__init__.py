@@ -102,6 +102,21 @@ def linear(
     return out
 
 
+def linear_pair(x: torch.Tensor, w: torch.Tensor, *, bias: Optional[torch.Tensor] = None, act: Optional[str] = None,
+                residual: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None, dual: bool = False,
+                accumulators: int = 2, debug: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``linear`` / ``gate_up_swiglu`` on the two-SM (``cta_group::2``) kernel; CUDA only."""
+    T, K = x.shape
+    M = w.shape[0] // 2 if dual else w.shape[0]
+    if out is None:
+        out = torch.empty((T, M), dtype=torch.bfloat16, device=x.device)
+    code = {None: 0, "gelu_tanh": 1, "gelu": 2}[act]
+    native.call("prism_gemm_pair", _p(w), _p(x), _p(out), M, T, K, w.stride(0), x.stride(0), out.stride(0), w.shape[0],
+                _p(bias), _p(residual), residual.stride(0) if residual is not None else 0, code, 1 if dual else 0,
+                M if dual else 0, accumulators, _p(debug), _s(), _pdl())
+    return out
+
+
 def linear_partial(
     x: torch.Tensor, w: torch.Tensor, splits: int, out: Optional[torch.Tensor] = None, *, bn: int = 0, stages: int = 0
 ) -> torch.Tensor:

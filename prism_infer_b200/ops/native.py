@@ -48,6 +48,7 @@ _SIGNATURES = {
     "prism_add_rmsnorm_packed": "plippppppiifpipi",
     "prism_gemm_wx_normx": "ppiiilliiiiilplippppfpilpipi",
     "prism_flash_attention_tc": "plpplplpiiiiiiifpi",
+    "prism_gemm_pair": "pppiiilllippliiiippi",
     "prism_gemv": "pppiiillliipiillppi",
     "prism_gemm_set_small_tile_smem_cap": "i",
     "prism_gemm_set_persistent_min_tokens": "i",
@@ -65,7 +66,7 @@ _SIGNATURES = {
     "prism_epoch_advance": "plpi",
     "prism_argmax_exchange": "ppppppppiiiiipi",
 }
-_STATUS_UNITS = ("gemm", "gemv", "norm", "attn", "attn_tc", "kvops", "sampler", "comm")
+_STATUS_UNITS = ("gemm", "gemm_pair", "gemv", "norm", "attn", "attn_tc", "kvops", "sampler", "comm")
 
 
 class NativeError(RuntimeError):
