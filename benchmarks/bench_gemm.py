@@ -78,6 +78,8 @@ def main() -> None:
         best = None
         if kind == "dual":
             variants = {"dual": lambda: ops.gate_up_swiglu(x, w, bn=16 if T <= 16 else 0)}
+            if T >= 512:
+                variants["pair"] = lambda: ops.linear_pair(x, w, dual=True)
             if T <= 4:
                 variants["gemv"] = lambda: ops.gate_up_swiglu(x, w)  # with PRISM_GEMV_MAX_TOKENS=4
             ref = lambda: torch.nn.functional.silu((x @ w.t())[:, :M]) * (x @ w.t())[:, M:]  # noqa: E731
@@ -92,7 +94,7 @@ def main() -> None:
         else:
             out = torch.empty((T, M), dtype=torch.bfloat16, device=dev)
             variants = {"bn256": lambda: ops.linear(x, w, out=out, bn=256), "bn128": lambda: ops.linear(x, w, out=out, bn=128),
-                        "persistent": lambda: ops.linear(x, w, out=out)}
+                        "persistent": lambda: ops.linear(x, w, out=out), "pair": lambda: ops.linear_pair(x, w, out=out)}
             ref = lambda: x @ w.t()  # noqa: E731
         t_ref = timeit(ref, args.iters, flush)
         all_ms = {}

@@ -458,3 +458,26 @@ def test_tcgen05_flash_attention_head_dim_72(cuda_device, lens, monkeypatch):
     got = ops.varlen_attention(dev[:, 0], dev[:, 1], dev[:, 2], cu.cuda(), max(lens), causal=False)
     torch.cuda.synchronize()
     close(got, ref, 2e-2, 2e-2, f"tcgen05 attention hd 72 lens={lens}")
+
+
+@pytest.mark.parametrize("T,M,K", [(512, 512, 256), (1616, 4304, 1152), (700, 1152, 320)])
+def test_two_sm_pair_gemm_matches_persistent_kernel(cuda_device, T, M, K):
+    """cta_group::2 kernel (pairs of CTAs, M = 256 MMAs): same bits as the one-SM persistent kernel for
+    every epilogue form, with one and with two TMEM accumulators."""
+    x, w = rand_bf16(T, K, seed=41).cuda(), rand_bf16(M, K, scale=K ** -0.5, seed=42).cuda()
+    b, r = rand_bf16(M, seed=43).cuda(), rand_bf16(T, M, seed=44).cuda()
+    for kw in (dict(), dict(bias=b, act="gelu_tanh"), dict(bias=b, residual=r)):
+        want = ops.linear(x, w, **kw)
+        for acc in (1, 2):
+            got = ops.linear_pair(x, w, accumulators=acc, **kw)
+            torch.cuda.synchronize()
+            assert torch.equal(got, want), f"pair kernel differs for {list(kw)} with {acc} accumulator(s)"
+    close(want, ops.linear(x.float().cpu(), w.float().cpu(), bias=b.float().cpu(), residual=r.float().cpu()), 3e-2, 2e-2, "pair")
+
+
+def test_two_sm_pair_dual_swiglu(cuda_device):
+    T, I, K = 1300, 1280, 512
+    x, w = rand_bf16(T, K, seed=45).cuda(), rand_bf16(2 * I, K, scale=K ** -0.5, seed=46).cuda()
+    got = ops.linear_pair(x, w, dual=True)
+    torch.cuda.synchronize()
+    assert torch.equal(got, ops.gate_up_swiglu(x, w))
