@@ -92,8 +92,15 @@ def main(args) -> None:
         arch = Qwen3VLArch.qwen3_vl_8b()
         ckpt = os.path.join(tempfile.gettempdir(), "prism_ref_qwen3vl8b_random")
         write_checkpoint(ckpt, arch)
-        for k in ("RANK", "WORLD_SIZE", "LOCAL_RANK", "MASTER_ADDR", "MASTER_PORT", "TORCHELASTIC_RUN_ID"):
-            os.environ.pop(k, None)
+        # The reference starts its own worker ranks with its own tcp:// rendezvous.  Under torchrun the
+        # elastic agent's variables must go, above all TORCHELASTIC_USE_AGENT_STORE: with it set,
+        # init_process_group treats even rank 0 as a client of the agent's store and waits for a server
+        # that does not exist on the reference's port.
+        for k in list(os.environ):
+            if k.startswith("TORCHELASTIC_") or k in ("RANK", "WORLD_SIZE", "LOCAL_RANK", "LOCAL_WORLD_SIZE", "GROUP_RANK",
+                                                       "GROUP_WORLD_SIZE", "ROLE_RANK", "ROLE_WORLD_SIZE", "ROLE_NAME",
+                                                       "MASTER_ADDR", "MASTER_PORT", "TORCH_NCCL_ASYNC_ERROR_HANDLING"):
+                os.environ.pop(k, None)
         sys.path.insert(0, REF)
         from prism_infer import LLM, SamplingParams  # the unmodified reference
         from prism_infer.engine.vl_inputs import ImageInputs
