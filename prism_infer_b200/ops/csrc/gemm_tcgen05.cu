@@ -535,6 +535,16 @@ struct PersistArgs {
   const __nv_bfloat16* bias;
   const __nv_bfloat16* residual;
   __nv_bfloat16* out;
+  // scatter form (row-major only; fused row-parallel GEMM -> reduce-scatter): token row m belongs
+  // to rank m / rows_per_owner and is written into that rank's buffer, slab my_rank, as bf16; when
+  // every CTA is done flag[my_rank] on every rank is set to seq.
+  int scatter;
+  int rows_per_owner;
+  int n_peers, my_rank;
+  unsigned long long seq;
+  int* cta_counter;
+  __nv_bfloat16* peer_out[8];
+  unsigned long long* peer_flag[8];
 };
 
 // ROWMAJOR: the A operand (128-row tiles, TMEM lanes) holds the tokens and B the weights, so an
@@ -760,7 +770,13 @@ gemm_wx_persistent_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_
           __nv_bfloat162* op = reinterpret_cast<__nv_bfloat162*>(o);
 #pragma unroll
           for (int e = 0; e < 8; ++e) op[e] = __floats2bfloat162_rn(v[2 * e], v[2 * e + 1]);
-          __nv_bfloat16* dst = a.out + (size_t)m * a.ldo + f0;
+          __nv_bfloat16* dst;
+          if (a.scatter) {
+            const int owner = m / a.rows_per_owner;
+            dst = a.peer_out[owner] + ((size_t)a.my_rank * a.rows_per_owner + (m - owner * a.rows_per_owner)) * a.ldo + f0;
+          } else {
+            dst = a.out + (size_t)m * a.ldo + f0;
+          }
           *reinterpret_cast<uint4*>(dst) = o[0];
           *reinterpret_cast<uint4*>(dst + 8) = o[1];
         }
@@ -819,9 +835,19 @@ gemm_wx_persistent_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_
     }
   }
 #undef PRISM_TILE_COORDS
+  if (ROWMAJOR && a.scatter && warp >= 2) __threadfence_system();  // this CTA's rows visible to their owners
   tc_fence_before();
   __syncthreads();
   if (warp == 1) tmem_dealloc(tmem_base, TMEM_COLS);
+  if (ROWMAJOR && a.scatter && threadIdx.x == 0) {
+    const int old = atomicAdd(a.cta_counter, 1);
+    if (old == (int)gridDim.x - 1) {
+      *a.cta_counter = 0;
+      __threadfence_system();
+      for (int p = 0; p < a.n_peers; ++p)
+        asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(a.peer_flag[p] + a.my_rank), "l"(a.seq) : "memory");
+    }
+  }
 }
 
 // ------------------------------------------------------------------------------------
@@ -1137,6 +1163,16 @@ static int gemm_wx_impl(const void* W, const void* X, void* out, int M, int T, i
     pa.bias = a.bias;
     pa.residual = a.residual;
     pa.out = reinterpret_cast<__nv_bfloat16*>(out);
+    pa.scatter = 0;
+    pa.rows_per_owner = 1;
+    pa.n_peers = 0;
+    pa.my_rank = 0;
+    pa.seq = 0;
+    pa.cta_counter = nullptr;
+    for (int i = 0; i < 8; ++i) {
+      pa.peer_out[i] = nullptr;
+      pa.peer_flag[i] = nullptr;
+    }
     const unsigned long long vec_addr = reinterpret_cast<unsigned long long>(out) | reinterpret_cast<unsigned long long>(bias) |
                                         reinterpret_cast<unsigned long long>(residual);
     pa.dual_rm = 0;
@@ -1336,6 +1372,51 @@ PRISM_API int prism_gemm_wx_actx(const void* W, void* out, int M, int T, int K, 
   }
   return gemm_wx_impl(W, W, out, M, T, K, ldw, ldw, ldo, M, nullptr, nullptr, 0, 0, 0, 0, splits, 1, split_stride, 16, 0,
                       stream_ptr, pdl, pp, &ns);
+}
+
+// Fused row-parallel GEMM -> reduce-scatter for prefill-sized steps: out rows are bf16
+// X[t] . W^T (this rank's partial sum over its K shard); row t is written into the buffer of
+// rank t / rows_per_owner at slab my_rank, local row t % rows_per_owner (row stride M), and
+// flag[my_rank] on every rank becomes seq once all CTAs have stored.  peer_out / peer_flag:
+// host arrays of device pointers (own rank included).  M a multiple of 16.  The consumer is
+// prism_reduce_norm_allgather.
+PRISM_API int prism_gemm_wx_scatter(const void* W, const void* X, int M, int T, int K, long long ldw, long long ldx,
+                                    int rows_per_owner, const void* const* peer_out, const void* const* peer_flag,
+                                    int n_peers, int my_rank, long long seq, void* cta_counter, void* stream_ptr, int pdl) {
+  if (T <= 0) return 0;
+  if (n_peers < 1 || n_peers > 8 || rows_per_owner < 1 || (long long)rows_per_owner * n_peers < T) return -20;
+  if (M % 16) return -21;
+  CUtensorMap ta, tb;
+  int rc = get_tensor_map(X, (unsigned long long)T, (unsigned long long)K, (unsigned long long)ldx, BM, &ta);
+  if (rc) return rc;
+  rc = get_tensor_map(W, (unsigned long long)M, (unsigned long long)K, (unsigned long long)ldw, 256, &tb);
+  if (rc) return rc;
+  PersistArgs pa;
+  pa.dual_rm = 0;
+  pa.M = T;
+  pa.T = M;
+  pa.kb_total = (K + BK - 1) / BK;
+  pa.w2_row_off = 0;
+  pa.m_tiles = (T + BM - 1) / BM;
+  pa.n_tiles = (M + 255) / 256;
+  pa.tokens_fastest = 0;
+  pa.act = 0;
+  pa.ldo = M;
+  pa.ldr = 0;
+  pa.bias = nullptr;
+  pa.residual = nullptr;
+  pa.out = nullptr;
+  pa.scatter = 1;
+  pa.rows_per_owner = rows_per_owner;
+  pa.n_peers = n_peers;
+  pa.my_rank = my_rank;
+  pa.seq = (unsigned long long)seq;
+  pa.cta_counter = reinterpret_cast<int*>(cta_counter);
+  for (int i = 0; i < 8; ++i) {
+    pa.peer_out[i] = i < n_peers ? reinterpret_cast<__nv_bfloat16*>(const_cast<void*>(peer_out[i])) : nullptr;
+    pa.peer_flag[i] = i < n_peers ? reinterpret_cast<unsigned long long*>(const_cast<void*>(peer_flag[i])) : nullptr;
+  }
+  return launch_persistent<256, false, true>(ta, tb, pa, reinterpret_cast<cudaStream_t>(stream_ptr), pdl != 0);
 }
 
 PRISM_API int prism_gemm_set_persistent_rowmajor(int on) {

@@ -278,6 +278,128 @@ __global__ void __launch_bounds__(256) add_rmsnorm_rows_kernel(const AddNormArgs
 }
 
 // ---------------------------------------------------------------------------------
+// Consumer of prism_gemm_wx_scatter (tensor-parallel prefill): this rank owns `rows` token
+// rows.  For each of them (one warp per row): wait for every rank's partial (bounded), sum the
+// tp bf16 partial rows in rank order, add the residual shard (and a DeepStack row), write the
+// new residual shard, RMSNorm, and store the normalised row into EVERY rank's activation
+// buffer at its global row index (the all-gather).  The last CTA then raises flag[my_rank]
+// on every rank.  Residuals stay sharded by token row between layers.
+// ---------------------------------------------------------------------------------
+struct RnaArgs {
+  const bf16* rs;                       // local [tp][rows_per_owner][H]
+  const unsigned long long* rs_flags;   // local [tp]
+  unsigned long long rs_seq;
+  int tp, my_rank, rows_per_owner, rows, row0, H;
+  const bf16* residual_in;              // first owned row, row stride ld_res (may be null)
+  long long ld_res;
+  bf16* residual_out;                   // [rows][H]
+  const bf16* extra;                    // DeepStack rows (may be null)
+  const int* extra_index;               // [T] global row -> row of extra, or < 0
+  const bf16* weight;
+  float eps;
+  bf16* peer_x[8];                      // [T][H] on every rank
+  unsigned long long* peer_flag[8];     // [tp] on every rank
+  unsigned long long ag_seq;
+  int* cta_counter;
+};
+
+template <int NV>
+__global__ void __launch_bounds__(256) reduce_norm_allgather_kernel(const RnaArgs a) {
+  const int lane = threadIdx.x & 31;
+  const int i = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  pdl_launch_dependents();
+  pdl_wait();
+  const int H = a.H, nvec = H >> 3;
+  if (i < a.rows) {
+    if (lane < a.tp) wait_flag_ge(a.rs_flags + lane, a.rs_seq, lane);
+    __syncwarp();
+    const int g_row = a.row0 + i;
+    const int ex = a.extra != nullptr ? a.extra_index[g_row] : -1;
+    uint4 v[NV];
+    float ss = 0.0f;
+#pragma unroll
+    for (int k = 0; k < NV; ++k) {
+      const int c = lane + 32 * k;
+      if (c < nvec) {
+        float acc[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) acc[e] = 0.0f;
+        for (int r = 0; r < a.tp; ++r) {
+          const uint4 p = __ldcg(reinterpret_cast<const uint4*>(a.rs + ((size_t)r * a.rows_per_owner + i) * H) + c);
+          const __nv_bfloat162* pp = reinterpret_cast<const __nv_bfloat162*>(&p);
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const float2 f = __bfloat1622float2(pp[e]);
+            acc[2 * e] += f.x;
+            acc[2 * e + 1] += f.y;
+          }
+        }
+#pragma unroll
+        for (int e = 0; e < 8; ++e) acc[e] = bf16_round(acc[e]);
+        if (a.residual_in != nullptr) {
+          const uint4 rv = reinterpret_cast<const uint4*>(a.residual_in + (size_t)i * a.ld_res)[c];
+          const __nv_bfloat162* rp = reinterpret_cast<const __nv_bfloat162*>(&rv);
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const float2 f = __bfloat1622float2(rp[e]);
+            acc[2 * e] = bf16_round(f.x + acc[2 * e]);
+            acc[2 * e + 1] = bf16_round(f.y + acc[2 * e + 1]);
+          }
+        }
+        if (ex >= 0) {
+          const uint4 rv = reinterpret_cast<const uint4*>(a.extra + (size_t)ex * H)[c];
+          const __nv_bfloat162* rp = reinterpret_cast<const __nv_bfloat162*>(&rv);
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const float2 f = __bfloat1622float2(rp[e]);
+            acc[2 * e] = bf16_round(acc[2 * e] + f.x);
+            acc[2 * e + 1] = bf16_round(acc[2 * e + 1] + f.y);
+          }
+        }
+        uint4 x;
+        __nv_bfloat162* xp = reinterpret_cast<__nv_bfloat162*>(&x);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          ss += acc[2 * e] * acc[2 * e] + acc[2 * e + 1] * acc[2 * e + 1];
+          xp[e] = __floats2bfloat162_rn(acc[2 * e], acc[2 * e + 1]);
+        }
+        v[k] = x;
+        reinterpret_cast<uint4*>(a.residual_out + (size_t)i * H)[c] = x;
+      }
+    }
+    const float rstd = rsqrtf(warp_sum(ss) / (float)H + a.eps);
+#pragma unroll
+    for (int k = 0; k < NV; ++k) {
+      const int c = lane + 32 * k;
+      if (c < nvec) {
+        const uint4 w = reinterpret_cast<const uint4*>(a.weight)[c];
+        const __nv_bfloat162* wp = reinterpret_cast<const __nv_bfloat162*>(&w);
+        const __nv_bfloat162* xp = reinterpret_cast<const __nv_bfloat162*>(&v[k]);
+        uint4 o;
+        __nv_bfloat162* op = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float2 f = __bfloat1622float2(xp[e]), wf = __bfloat1622float2(wp[e]);
+          op[e] = __floats2bfloat162_rn(bf16_round(f.x * rstd) * wf.x, bf16_round(f.y * rstd) * wf.y);
+        }
+        for (int p = 0; p < a.tp; ++p) reinterpret_cast<uint4*>(a.peer_x[p] + (size_t)g_row * H)[c] = o;
+      }
+    }
+    __threadfence_system();  // this row is visible on every rank before the flag can be
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const int old = atomicAdd(a.cta_counter, 1);
+    if (old == (int)gridDim.x - 1) {
+      *a.cta_counter = 0;
+      __threadfence_system();
+      for (int p = 0; p < a.tp; ++p)
+        asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(a.peer_flag[p] + a.my_rank), "l"(a.ag_seq) : "memory");
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------------
 // LayerNorm with bias (vision tower), one CTA per row, fp32 statistics.
 // ---------------------------------------------------------------------------------
 __global__ void __launch_bounds__(256) layernorm_kernel(const bf16* x, const bf16* w, const bf16* b, bf16* out, int H,
@@ -823,6 +945,43 @@ PRISM_API int prism_add_rmsnorm_packed(const void* partials, long long slab_stri
                                        int point, void* stream, int pdl) {
   return add_rmsnorm_impl(partials, slab_stride, P, nullptr, residual_in, residual_out, extra, extra_index, weight, out, T,
                           H, eps, stream, pdl, nullptr, 0, epoch, point, 1);
+}
+
+PRISM_API int prism_reduce_norm_allgather(const void* rs, const void* rs_flags, long long rs_seq, int tp, int my_rank,
+                                          int rows_per_owner, int rows, int row0, int H, const void* residual_in,
+                                          long long ld_res, void* residual_out, const void* extra, const void* extra_index,
+                                          const void* weight, float eps, const void* const* peer_x,
+                                          const void* const* peer_flag, long long ag_seq, void* cta_counter, void* stream,
+                                          int pdl) {
+  if (tp < 1 || tp > 8 || rows < 0 || rows > rows_per_owner) return -20;
+  if (H % 8 || H > 8192) return -21;
+  RnaArgs a;
+  a.rs = (const bf16*)rs;
+  a.rs_flags = (const unsigned long long*)rs_flags;
+  a.rs_seq = (unsigned long long)rs_seq;
+  a.tp = tp;
+  a.my_rank = my_rank;
+  a.rows_per_owner = rows_per_owner;
+  a.rows = rows;
+  a.row0 = row0;
+  a.H = H;
+  a.residual_in = (const bf16*)residual_in;
+  a.ld_res = ld_res;
+  a.residual_out = (bf16*)residual_out;
+  a.extra = (const bf16*)extra;
+  a.extra_index = (const int*)extra_index;
+  a.weight = (const bf16*)weight;
+  a.eps = eps;
+  for (int p = 0; p < 8; ++p) {
+    a.peer_x[p] = p < tp ? (bf16*)const_cast<void*>(peer_x[p]) : nullptr;
+    a.peer_flag[p] = p < tp ? (unsigned long long*)const_cast<void*>(peer_flag[p]) : nullptr;
+  }
+  a.ag_seq = (unsigned long long)ag_seq;
+  a.cta_counter = (int*)cta_counter;
+  dim3 grid(rows > 0 ? (rows + 7) / 8 : 1), block(256);
+  if (H <= 2048) return (int)prism_launch(reduce_norm_allgather_kernel<8>, grid, block, 0, STREAM(stream), pdl != 0, a);
+  if (H <= 4096) return (int)prism_launch(reduce_norm_allgather_kernel<16>, grid, block, 0, STREAM(stream), pdl != 0, a);
+  return (int)prism_launch(reduce_norm_allgather_kernel<32>, grid, block, 0, STREAM(stream), pdl != 0, a);
 }
 
 PRISM_API int prism_layernorm(const void* x, const void* w, const void* b, void* out, int T, int H, float eps,

@@ -45,6 +45,8 @@ _SIGNATURES = {
     "prism_merge_candidates": "pppiipi",
     "prism_gemm_wx_push": "ppiiillliilppiilppiipi",
     "prism_add_rmsnorm_wait": "plippppppiifpipipi",
+    "prism_gemm_wx_scatter": "ppiiillippiilppi",
+    "prism_reduce_norm_allgather": "ppliiiiiiplppppfpplppi",
     "prism_add_rmsnorm_packed": "plippppppiifpipi",
     "prism_gemm_wx_normx": "ppiiilliiiiilplippppfpilpipi",
     "prism_flash_attention_tc": "plpplplpiiiiiiifpi",

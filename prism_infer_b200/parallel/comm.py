@@ -184,6 +184,53 @@ class FusedComm(NcclComm):
         )
         return out
 
+    # ---- prefill: row-parallel GEMM -> reduce-scatter, then reduce + norm -> all-gather -----------
+    def prefill_fused(self, tokens: int) -> bool:
+        return SMALL_T < tokens <= symm.PRE_T_MAX and self.hidden % 16 == 0
+
+    def scatter_linear(self, x: torch.Tensor, w: torch.Tensor):
+        """Row-parallel projection whose epilogue writes each token row, as bf16, into the rank that
+        owns it (``ceil(T / tp)`` consecutive rows per rank).  Returns the ticket for
+        ``reduce_norm_allgather``."""
+        T, K = x.shape
+        rpo = -(-T // self.size)
+        self.pre_seq = getattr(self, "pre_seq", 0) + 1
+        slot, seq, r = self.pre_seq % 2, self.pre_seq, self.region
+        native.call("prism_gemm_wx_scatter", w.data_ptr(), x.data_ptr(), w.shape[0], T, K, w.stride(0), x.stride(0), rpo,
+                    r.ptr_array(r.pre_offsets(slot)[0]), r.ptr_array(symm.OFF_PRE_RS_FLAGS[slot]), self.size, self.rank, seq,
+                    r.local(symm.OFF_PRE_COUNTER[0]), torch.cuda.current_stream().cuda_stream, 1 if ops.pdl_enabled() else 0)
+        return slot, seq, T, rpo
+
+    def reduce_norm_allgather(self, ticket, weight: torch.Tensor, eps: float, residual: torch.Tensor | None, *,
+                              residual_is_shard: bool, extra: torch.Tensor | None = None,
+                              extra_index: torch.Tensor | None = None, wait: bool = True):
+        """Sum the tp partial rows this rank owns, add the residual (a full ``[T, H]`` tensor or this
+        rank's shard), RMSNorm, and store the normalised rows into every rank's activation buffer.
+        Returns ``(h [T, H] view of the gathered rows, residual shard [rows_per_owner, H])``."""
+        slot, seq, T, rpo = ticket
+        r, H = self.region, self.hidden
+        row0 = self.rank * rpo
+        rows = max(0, min(T, row0 + rpo) - row0)
+        shard = residual if (residual is not None and residual_is_shard) else torch.empty((rpo, H), dtype=torch.bfloat16, device=weight.device)
+        res_ptr = None
+        if residual is not None and rows > 0:
+            res_ptr = residual.data_ptr() if residual_is_shard else residual[row0:].data_ptr()
+        stream = torch.cuda.current_stream().cuda_stream
+        native.call("prism_reduce_norm_allgather", r.local(r.pre_offsets(slot)[0]), r.local(symm.OFF_PRE_RS_FLAGS[slot]), seq,
+                    self.size, self.rank, rpo, rows, row0, H, res_ptr, H, shard.data_ptr(),
+                    None if extra is None else extra.data_ptr(), None if extra is None else extra_index.data_ptr(),
+                    weight.data_ptr(), float(eps), r.ptr_array(r.pre_offsets(slot)[1]), r.ptr_array(symm.OFF_PRE_AG_FLAGS[slot]),
+                    seq, r.local(symm.OFF_PRE_COUNTER[1]), stream, 1 if ops.pdl_enabled() else 0)
+        if wait:
+            self.wait_allgather(ticket)
+        return r.pre_rows(slot, T), shard
+
+    def wait_allgather(self, ticket) -> None:
+        """Bounded wait until every rank's rows of this exchange are in the local activation buffer."""
+        slot, seq, _, _ = ticket
+        native.call("prism_wait_flags", self.region.local(symm.OFF_PRE_AG_FLAGS[slot]), self.size, seq,
+                    torch.cuda.current_stream().cuda_stream)
+
     # ---- sharded vision tower: merger GEMM -> all-gather ------------------------------------
     def vision_begin(self, total_tokens: int) -> bool:
         """Start a sharded vision-tower call; False when the gathered outputs would not fit."""

@@ -13,8 +13,11 @@ Region layout (bytes)::
     1024  CTA counter slot 0  i32                1280  CTA counter slot 1  i32
     1344  CTA counter of the vision all-gather  1536  vision flags: 2 sets x 4 outputs x u64[8]
     4096  arg-max values f32[8][BMAX]            then  arg-max ids i64[8][BMAX]
+    2048  prefill reduce-scatter flags: 2 slots x u64[8]   2176  prefill all-gather flags: 2 slots x u64[8]
+    2304  CTA counters of the prefill scatter GEMM and of the reduce + norm + all-gather kernel
     SLAB0 / SLAB1: two slab buffers of  tp * S_MAX * T_MAX * H  8-byte {fp32 value, sequence} words each
     VIS: 2 sets x 4 outputs x VIS_T_MAX x H bf16 (gathered merger outputs of the vision tower)
+    PRE: 2 slots x (reduce-scatter slabs tp x ceil(PRE_T_MAX / tp) x H bf16, all-gathered rows PRE_T_MAX x H bf16)
 """
 
 from __future__ import annotations
@@ -37,11 +40,26 @@ OFF_VIS_COUNTER = 1344
 OFF_VIS_FLAGS = 1536          # 8 arrays (2 buffer sets x 4 outputs) of u64[8]
 VIS_OUTPUTS = 4               # main merger + up to three DeepStack mergers
 VIS_T_MAX = 4096              # merged visual tokens per vision-tower call on the fused path
+OFF_PRE_RS_FLAGS = (2048, 2112)
+OFF_PRE_AG_FLAGS = (2176, 2240)
+OFF_PRE_COUNTER = (2304, 2368)  # scatter GEMM, reduce + norm + all-gather kernel
+PRE_T_MAX = 8192              # prefill tokens per step on the fused tensor-parallel path
 OFF_ARGMAX_VAL = 4096
 OFF_ARGMAX_ID = OFF_ARGMAX_VAL + 8 * B_MAX * 4
 OFF_SLABS = (OFF_ARGMAX_ID + 8 * B_MAX * 8 + 4095) // 4096 * 4096
 POINTS_PER_STEP = 128
 ARGMAX_POINT = POINTS_PER_STEP - 1
+
+
+def _pre_bytes(size: int, hidden: int) -> tuple[int, int]:
+    """(reduce-scatter slab bytes, all-gather bytes) of one prefill slot."""
+    rows = -(-PRE_T_MAX // size)
+    return size * rows * hidden * 2, PRE_T_MAX * hidden * 2
+
+
+def _region_bytes(size: int, hidden: int, slab_bytes: int) -> int:
+    rs, ag = _pre_bytes(size, hidden)
+    return OFF_SLABS + 2 * slab_bytes + 2 * VIS_OUTPUTS * VIS_T_MAX * hidden * 2 + 2 * (rs + ag)
 
 
 def _check(rc: int, what: str) -> None:
@@ -72,7 +90,7 @@ class SymmetricRegion:
 
         lib = native.lib()
         slab_bytes = size * S_MAX * T_MAX * hidden * 8
-        nbytes = OFF_SLABS + 2 * slab_bytes + 2 * VIS_OUTPUTS * VIS_T_MAX * hidden * 2
+        nbytes = _region_bytes(size, hidden, slab_bytes)
         out = ctypes.c_void_p()
         _check(lib.prism_ipc_alloc(nbytes, ctypes.byref(out)), "prism_ipc_alloc")
         handle = (ctypes.c_char * 64)()
@@ -96,7 +114,7 @@ class SymmetricRegion:
         """All ranks' regions on the current device (single-GPU tests of the fused kernels)."""
         lib = native.lib()
         slab_bytes = size * S_MAX * T_MAX * hidden * 8
-        nbytes = OFF_SLABS + 2 * slab_bytes + 2 * VIS_OUTPUTS * VIS_T_MAX * hidden * 2
+        nbytes = _region_bytes(size, hidden, slab_bytes)
         ptrs = []
         for _ in range(size):
             out = ctypes.c_void_p()
@@ -121,6 +139,18 @@ class SymmetricRegion:
     def vis_rows(self, buffer_set: int, output: int, rows: int) -> torch.Tensor:
         """Local bf16 view ``[rows, hidden]`` of one gathered vision output."""
         off = self.vis_offset(buffer_set, output)
+        raw = self.local_bytes()[off: off + rows * self.hidden * 2]
+        return raw.view(torch.bfloat16).view(rows, self.hidden)
+
+    def pre_offsets(self, slot: int) -> tuple[int, int]:
+        """Byte offsets of (reduce-scatter slabs, all-gathered rows) of prefill slot ``slot``."""
+        rs, ag = _pre_bytes(self.size, self.hidden)
+        base = OFF_SLABS + 2 * self.slab_bytes + 2 * VIS_OUTPUTS * VIS_T_MAX * self.hidden * 2 + slot * (rs + ag)
+        return base, base + rs
+
+    def pre_rows(self, slot: int, rows: int) -> torch.Tensor:
+        """Local bf16 view ``[rows, hidden]`` of the all-gathered activations of a prefill slot."""
+        off = self.pre_offsets(slot)[1]
         raw = self.local_bytes()[off: off + rows * self.hidden * 2]
         return raw.view(torch.bfloat16).view(rows, self.hidden)
 

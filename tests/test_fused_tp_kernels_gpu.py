@@ -138,3 +138,65 @@ def test_sharded_vision_tower_matches_single_rank(cuda_device):
         model.tp = 1
         for reg in regions:
             native.lib().prism_ipc_free(ctypes.c_void_p(reg.local_ptr))
+
+
+@pytest.mark.parametrize("tp,T,K", [(2, 700, 512), (4, 1616, 1024), (8, 1000, 512), (8, 520, 256)])
+def test_prefill_scatter_gemm_then_reduce_norm_allgather_emulated_ranks(cuda_device, tp, T, K):
+    """Row-parallel GEMM -> reduce-scatter -> residual + RMSNorm -> all-gather for prefill-sized
+    steps, ranks emulated one after another on one device (every rank's GEMM, then every rank's
+    reduce, then the waits).  Two exchanges in a row: full residual first, sharded afterwards."""
+    import ctypes
+
+    from prism_infer_b200.parallel import symm
+    from prism_infer_b200.parallel.comm import FusedComm
+
+    H = 4096
+    ops.set_pdl(False)
+    regions = symm.SymmetricRegion.create_emulated(tp, H)
+    comms = [FusedComm(r, tp, H, region=regions[r]) for r in range(tp)]
+    g = torch.Generator().manual_seed(tp * 1000 + T)
+    weight = (1 + 0.1 * torch.randn(H, generator=g)).to(torch.bfloat16).cuda()
+    extra = torch.randn(37, H, generator=g).to(torch.bfloat16).cuda()
+    extra_index = torch.full((T,), -1, dtype=torch.int32)
+    extra_index[5:42] = torch.arange(37, dtype=torch.int32)
+    extra_index = extra_index.cuda()
+    res_full = torch.randn(T, H, generator=g).to(torch.bfloat16).cuda()
+    try:
+        residual_ref = res_full.float().cpu()
+        shards = [None] * tp
+        for exchange in range(3):
+            xs = [(torch.randn(T, K, generator=g)).to(torch.bfloat16).cuda() for _ in range(tp)]
+            ws = [(torch.randn(H, K, generator=g) * (K * tp) ** -0.5).to(torch.bfloat16).cuda() for _ in range(tp)]
+            tickets = [c.scatter_linear(xs[r], ws[r]) for r, c in enumerate(comms)]
+            use_extra = exchange == 1
+            outs = []
+            for r, c in enumerate(comms):
+                res = res_full if exchange == 0 else shards[r]
+                h, shard = c.reduce_norm_allgather(tickets[r], weight, 1e-6, res, residual_is_shard=exchange > 0,
+                                                   extra=extra if use_extra else None, extra_index=extra_index if use_extra else None,
+                                                   wait=False)
+                shards[r] = shard
+                outs.append(h)
+            for r, c in enumerate(comms):
+                c.wait_allgather(tickets[r])
+            torch.cuda.synchronize()
+            native.check_status()
+            # reference: bf16 partial per rank, summed in fp32, rounded, + residual (+ extra), RMSNorm
+            partial = sum((x.float() @ w.float().t()).to(torch.bfloat16).float().cpu() for x, w in zip(xs, ws))
+            delta = partial.to(torch.bfloat16).float()
+            new_res = (residual_ref + delta).to(torch.bfloat16).float()
+            if use_extra:
+                idx = extra_index.cpu()
+                sel = idx >= 0
+                new_res[sel] = (new_res[sel] + extra.float().cpu()[idx[sel].long()]).to(torch.bfloat16).float()
+            normed = (new_res * torch.rsqrt(new_res.pow(2).mean(-1, keepdim=True) + 1e-6)).to(torch.bfloat16).float() * weight.float().cpu()
+            rpo = -(-T // tp)
+            for r in range(tp):
+                assert torch.equal(outs[r], outs[0]), "every rank holds the same gathered rows"
+                rows = max(0, min(T, (r + 1) * rpo) - r * rpo)
+                close(shards[r][:rows], new_res[r * rpo: r * rpo + rows], 6e-2, 2e-2, f"residual shard of rank {r}")
+            close(outs[0], normed, 8e-2, 3e-2, f"gathered normalised rows, exchange {exchange}")
+            residual_ref = torch.cat([shards[r][:max(0, min(T, (r + 1) * rpo) - r * rpo)].float().cpu() for r in range(tp)])
+    finally:
+        for reg in regions:
+            native.lib().prism_ipc_free(ctypes.c_void_p(reg.local_ptr))
