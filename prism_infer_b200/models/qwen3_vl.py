@@ -460,6 +460,9 @@ class Qwen3VLModel:
             flip = 0
         # decode-sized steps: kernels that leave HBM idle request the next weights into L2
         pf = x.is_cuda and not meta.is_prefill and T <= 16
+        if (self.tp > 1 and x.is_cuda and meta.is_prefill and hasattr(comm, "prefill_fused") and comm.prefill_fused(T)
+                and ops.TP_PREFILL_FUSED):
+            return self._forward_prefill_fused(x, positions, meta, cache, deepstack, vis_index)
         for i, l in enumerate(self.layers):
             extra = deepstack[i - 1] if 0 < i <= n_deep else None
             if fuse_norm:
@@ -540,6 +543,46 @@ class Qwen3VLModel:
         extra = deepstack[n_deep - 1] if n_deep == len(self.layers) else None
         h, _ = comm.add_rmsnorm(self.final_norm, t.rms_norm_eps, dense, partials, ticket, residual,
                                 extra, vis_index if extra is not None else None)
+        return h
+
+    def _forward_prefill_fused(self, x, positions, meta, cache, deepstack, vis_index):
+        """Tensor-parallel prefill with the exchanges fused into the kernels around them: each
+        row-parallel projection (o_proj, down_proj) scatters its bf16 partial rows to the ranks
+        that own them from the GEMM epilogue, and one kernel per exchange sums the owned rows, adds
+        the residual shard (kept sharded by token row between layers), normalises and stores the
+        rows into every rank's activation buffer, which the next column-parallel GEMM reads.  The
+        reference runs an NCCL all-reduce after every row-parallel GEMM
+        (``prism_infer/layers/linear.py:186-190``)."""
+        t, comm = self.arch.text, self.comm
+        T = x.shape[0]
+        n_deep = len(deepstack) if deepstack is not None else 0
+        layers = self.layers
+        h, residual = comm.add_rmsnorm(layers[0].input_norm, t.rms_norm_eps, x, None, None, None)
+        shard = False  # residual is the full [T, H] tensor until the first exchange
+        for i, l in enumerate(layers):
+            qkv = ops.linear(h, l.qkv)
+            direct = meta.no_history
+            q = ops.qk_norm_rope_store(qkv=qkv, partials=None, positions=positions, q_weight=l.q_norm, k_weight=l.k_norm,
+                                       num_heads=self.Hq, num_kv_heads=self.Hkv, head_dim=self.D, theta=t.rope_theta,
+                                       section=t.mrope_section, eps=t.rms_norm_eps, slots=meta.slots, cache=cache, layer=i,
+                                       k_writeback=direct)
+            if direct:
+                heads = qkv.view(T, self.Hq + 2 * self.Hkv, self.D)
+                a = ops.varlen_attention(q, heads[:, self.Hq:self.Hq + self.Hkv], heads[:, self.Hq + self.Hkv:],
+                                         meta.cu_seqlens_q, meta.max_q_len, causal=True)
+            else:
+                a = ops.paged_prefill_attention(q, cache, i, meta.cu_seqlens_q, meta.kv_lens, meta.block_tables, meta.max_q_len)
+            ticket = comm.scatter_linear(a.view(T, self.Hq * self.D), l.o)
+            h, residual = comm.reduce_norm_allgather(ticket, l.post_norm, t.rms_norm_eps, residual, residual_is_shard=shard)
+            shard = True
+            act = ops.gate_up_swiglu(h, l.gate_up)
+            ticket = comm.scatter_linear(act, l.down)
+            last = i + 1 == len(layers)
+            norm_w = self.final_norm if last else layers[i + 1].input_norm
+            # the DeepStack features of layer i + 1 are added where its input is formed
+            extra = deepstack[i] if i < n_deep else None
+            h, residual = comm.reduce_norm_allgather(ticket, norm_w, t.rms_norm_eps, residual, residual_is_shard=True, extra=extra,
+                                                     extra_index=vis_index if extra is not None else None)
         return h
 
     @torch.no_grad()

@@ -253,6 +253,8 @@ ACTX_ENABLED = _os.environ.get("PRISM_ACTX", "0") != "0"
 # leaves shared memory for the attention CTAs that precede it, so its weight prefetch can start
 # while attention still runs.
 O_PROJ_STAGES = int(_os.environ.get("PRISM_O_PROJ_STAGES", "0"))
+# tensor-parallel prefill: GEMM -> reduce-scatter / reduce + norm -> all-gather kernels (0: NCCL all-reduce arm)
+TP_PREFILL_FUSED = _os.environ.get("PRISM_TP_PREFILL_FUSED", "1") != "0"
 ATTN_TC_ENABLED = _os.environ.get("PRISM_ATTN_TC", "1") != "0"
 PERSISTENT_ROWMAJOR = _os.environ.get("PRISM_PERSISTENT_ROWMAJOR", "1") != "0"
 PERSISTENT_MIN_TOKENS = int(_os.environ.get("PRISM_PERSISTENT_MIN_TOKENS", "512"))

@@ -40,3 +40,32 @@ def test_tp2_matches_tp1_on_gpu(cuda_device):
     # TP changes the summation order of row-parallel GEMMs, so allow a late divergence only
     for b, f in zip(base, fused):
         assert b[:3] == f[:3]
+
+
+@pytest.mark.timeout(600)
+def test_tp2_fused_prefill_matches_nccl_prefill(cuda_device):
+    """Prompts longer than the decode-sized threshold: the prefill runs through the fused GEMM ->
+    reduce-scatter / reduce + norm -> all-gather kernels and must produce the tokens of the NCCL
+    all-reduce arm (first tokens exactly; later ones may differ by summation order)."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    arch = Qwen3VLArch.tiny()
+    weights = {k: v.to(torch.bfloat16).float() for k, v in random_weights(arch, dtype=torch.float32, seed=0).items()}
+    g = torch.Generator().manual_seed(3)
+    prompts = [torch.randint(5, 900, (n,), generator=g).tolist() for n in (300, 150, 421)]
+    sp = SamplingParams(temperature=0.0, max_tokens=6, ignore_eos=True)
+
+    def run(fused_prefill: bool):
+        os.environ["PRISM_TP_PREFILL_FUSED"] = "1" if fused_prefill else "0"
+        import prism_infer_b200.ops as ops_mod
+
+        ops_mod.TP_PREFILL_FUSED = fused_prefill  # the driver rank imported ops already; workers read the variable
+        return _run(2, "fused", weights, prompts, sp)
+
+    try:
+        plain = run(False)
+        fused = run(True)
+    finally:
+        os.environ.pop("PRISM_TP_PREFILL_FUSED", None)
+    for p, f in zip(plain, fused):
+        assert p[:2] == f[:2], (p, f)
