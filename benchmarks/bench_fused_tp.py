@@ -10,6 +10,9 @@ Cases (Qwen3-VL-8B shapes, tensor-parallel over N ranks):
 * ``o_proj`` / ``down_proj`` row-parallel GEMM -> one-shot exchange -> residual add + RMSNorm
   (``prism_gemm_wx_push`` + ``prism_add_rmsnorm_packed``) for T in {1, 8, 32, 128} tokens,
   versus split-K GEMM + ``dist.all_reduce`` + add+RMSNorm.
+* the prefill-sized form of the same exchange for 1616 and 4096 tokens: GEMM -> reduce-scatter
+  (``prism_gemm_wx_scatter``) + reduce / residual / RMSNorm -> all-gather
+  (``prism_reduce_norm_allgather``), versus GEMM + ``dist.all_reduce`` + add+RMSNorm.
 * vision merger GEMM -> all-gather (``prism_gemm_wx_allgather``) for 196 and 1568 tokens,
   versus GEMM + ``dist.all_gather``.
 
@@ -115,6 +118,35 @@ def main() -> None:
             rows.append({"kernel": f"{name} GEMM->exchange->add+RMSNorm", "tp": world, "tokens": T, "fused_us": round(t_f * 1e3, 2),
                          "nccl_us": round(t_n * 1e3, 2), "roofline_us": round(roof_ms * 1e3, 3),
                          "frac_of_roofline": round(roof_ms / t_f, 4), "speedup_vs_nccl": round(t_n / t_f, 2)})
+    # prefill-sized exchange: row-parallel GEMM -> reduce-scatter -> residual + RMSNorm -> all-gather
+    for name, K in (("o_proj", H // world), ("down_proj", I // world)):
+        w = (torch.randn(H, K, generator=g, device="cuda") * 0.02).to(torch.bfloat16)
+        for T in (1616, 4096):
+            x = torch.randn(T, K, generator=g, device="cuda").to(torch.bfloat16)
+            res_full = torch.zeros(T, H, dtype=torch.bfloat16, device="cuda")
+            state = {"shard": None}
+
+            def run_fused_prefill():
+                ticket = fused.scatter_linear(x, w)
+                res = res_full if state["shard"] is None else state["shard"]
+                _, state["shard"] = fused.reduce_norm_allgather(ticket, weight, 1e-6, res, residual_is_shard=state["shard"] is not None)
+
+            def run_nccl_prefill():
+                d, p, t = nccl.row_parallel(x, w)
+                nccl.add_rmsnorm(weight, 1e-6, d, p, t, res_full)
+
+            t_f = timed(run_fused_prefill, max(20, args.iters // 4))
+            t_n = timed(run_nccl_prefill, max(20, args.iters // 4))
+            rows = -(-T // world)
+            link_bytes = (world - 1) * rows * H * 2 * 2  # partial rows out to their owners, normalised rows out to every peer
+            flops = 2.0 * T * H * K
+            local_bytes = H * K * 2 + T * K * 2 + T * H * 2
+            roof_ms = max(local_bytes / peaks["hbm_gbs"] / 1e6, link_bytes / NVLINK_GBS / 1e6, flops / peaks["bf16_tflops"] / 1e9)
+            rows_out = {"kernel": f"{name} GEMM->reduce-scatter->add+RMSNorm->all-gather", "tp": world, "tokens": T,
+                        "fused_us": round(t_f * 1e3, 2), "nccl_us": round(t_n * 1e3, 2), "roofline_us": round(roof_ms * 1e3, 3),
+                        "frac_of_roofline": round(roof_ms / t_f, 4), "speedup_vs_nccl": round(t_n / t_f, 2)}
+            if rank == 0:
+                print(json.dumps(rows_out), flush=True)
     # vision merger fc2 GEMM -> all-gather
     md = 4608
     w2 = (torch.randn(H, md, generator=g, device="cuda") * 0.02).to(torch.bfloat16)
