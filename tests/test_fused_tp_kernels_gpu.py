@@ -16,6 +16,13 @@ from prism_infer_b200.ops import native
 pytestmark = pytest.mark.gpu
 
 
+def close(a, b, atol, rtol, what):
+    a, b = a.float().cpu(), b.float().cpu()
+    err = (a - b).abs()
+    lim = atol + rtol * b.abs()
+    assert bool((err <= lim).all()), f"{what}: max err {err.max().item():.4g}, worst ratio {(err / lim).max().item():.3g}"
+
+
 @pytest.mark.parametrize("tp,T,K", [(2, 1, 2048), (4, 8, 1024), (2, 96, 512), (8, 24, 512), (8, 3, 1536)])
 @pytest.mark.parametrize("gemv", [False, True])
 def test_push_gemm_then_wait_norm_emulated_ranks(cuda_device, tp, T, K, gemv, monkeypatch):
