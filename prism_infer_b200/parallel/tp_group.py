@@ -32,13 +32,23 @@ def _free_port() -> int:
         return s.getsockname()[1]
 
 
-def _init_process_group(rank: int, world: int, init_method: str, use_cuda: bool, timeout_s: int) -> None:
+def _init_process_group(rank: int, world: int, init_method: str, use_cuda: bool, timeout_s: int, store=None) -> None:
+    """``init_method`` is ``tcp://host:port`` (external launch) or ``store://host:port`` for groups
+    spawned here: the driver then already owns a ``TCPStore`` it bound to port 0 (passed as
+    ``store``), so there is no window in which another process can take a probed "free" port."""
     import datetime
 
     if dist.is_initialized():
         return
-    kwargs: dict[str, Any] = dict(backend="nccl" if use_cuda else "gloo", init_method=init_method, rank=rank,
-                                  world_size=world, timeout=datetime.timedelta(seconds=timeout_s))
+    timeout = datetime.timedelta(seconds=timeout_s)
+    kwargs: dict[str, Any] = dict(backend="nccl" if use_cuda else "gloo", rank=rank, world_size=world, timeout=timeout)
+    if init_method.startswith("store://"):
+        if store is None:
+            host, port = init_method[len("store://"):].rsplit(":", 1)
+            store = dist.TCPStore(host, int(port), world, False, timeout=timeout)
+        kwargs["store"] = store
+    else:
+        kwargs["init_method"] = init_method
     if use_cuda:
         kwargs["device_id"] = torch.device("cuda", torch.cuda.current_device())
     dist.init_process_group(**kwargs)
@@ -117,7 +127,10 @@ class TensorParallelGroup:
                 if torch.cuda.device_count() < world:
                     raise ValueError(f"tensor_parallel_size {world} needs {world} GPUs, found {torch.cuda.device_count()}")
                 torch.cuda.set_device(0)
-            init_method = f"tcp://127.0.0.1:{_free_port()}"
+            import datetime
+
+            master = dist.TCPStore("127.0.0.1", 0, world, True, timeout=datetime.timedelta(seconds=timeout), wait_for_workers=False)
+            init_method = f"store://127.0.0.1:{master.port}"
             self.seg = ControlSegment(None, world - 1, create=True)
             ctx = mp.get_context("spawn")
             flat = dict(getattr(config, "_flat_options", {}))
@@ -127,7 +140,7 @@ class TensorParallelGroup:
                 p.start()
                 self.procs.append(p)
             try:
-                _init_process_group(0, world, init_method, self.use_cuda, timeout)
+                _init_process_group(0, world, init_method, self.use_cuda, timeout, store=master)
             except Exception:
                 self._terminate_workers()
                 raise
