@@ -101,8 +101,8 @@ def main() -> None:
             def run_fused():
                 fused.begin_step()
                 for _ in range(2):  # two exchange points per step, alternating slots
-                    _, _, ticket = fused.row_parallel(x, w)
-                    fused.add_rmsnorm(weight, 1e-6, None, None, ticket, res)
+                    d, p, ticket = fused.row_parallel(x, w)  # falls back to the NCCL arm when tokens * tp is large
+                    fused.add_rmsnorm(weight, 1e-6, d, p, ticket, res)
 
             def run_nccl():
                 for _ in range(2):
