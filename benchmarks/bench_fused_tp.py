@@ -137,8 +137,8 @@ def main() -> None:
 
             t_f = timed(run_fused_prefill, max(20, args.iters // 4))
             t_n = timed(run_nccl_prefill, max(20, args.iters // 4))
-            rows = -(-T // world)
-            link_bytes = (world - 1) * rows * H * 2 * 2  # partial rows out to their owners, normalised rows out to every peer
+            own_rows = -(-T // world)
+            link_bytes = (world - 1) * own_rows * H * 2 * 2  # partial rows out to their owners, normalised rows out to every peer
             flops = 2.0 * T * H * K
             local_bytes = H * K * 2 + T * K * 2 + T * H * 2
             roof_ms = max(local_bytes / peaks["hbm_gbs"] / 1e6, link_bytes / NVLINK_GBS / 1e6, flops / peaks["bf16_tflops"] / 1e9)
