@@ -279,7 +279,7 @@ __global__ void __launch_bounds__(256) add_rmsnorm_rows_kernel(const AddNormArgs
 
 // ---------------------------------------------------------------------------------
 // Consumer of prism_gemm_wx_scatter (tensor-parallel prefill): this rank owns `rows` token
-// rows.  For each of them (one warp per row): wait for every rank's partial (bounded), sum the
+// rows.  For each of them (one CTA per row): wait for every rank's partial (bounded), sum the
 // tp bf16 partial rows in rank order, add the residual shard (and a DeepStack row), write the
 // new residual shard, RMSNorm, and store the normalised row into EVERY rank's activation
 // buffer at its global row index (the all-gather).  The last CTA then raises flag[my_rank]
@@ -303,27 +303,31 @@ struct RnaArgs {
   int* cta_counter;
 };
 
+// One CTA of 128 threads per owned row (a rank owns only T / tp rows, so a warp per row would
+// leave most SMs idle); NV 16-byte vectors per thread.
 template <int NV>
-__global__ void __launch_bounds__(256) reduce_norm_allgather_kernel(const RnaArgs a) {
-  const int lane = threadIdx.x & 31;
-  const int i = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+__global__ void __launch_bounds__(128) reduce_norm_allgather_kernel(const RnaArgs a) {
+  __shared__ float red[4];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int i = blockIdx.x;
   pdl_launch_dependents();
   pdl_wait();
   const int H = a.H, nvec = H >> 3;
   if (i < a.rows) {
-    if (lane < a.tp) wait_flag_ge(a.rs_flags + lane, a.rs_seq, lane);
-    __syncwarp();
+    if ((int)threadIdx.x < a.tp) wait_flag_ge(a.rs_flags + threadIdx.x, a.rs_seq, threadIdx.x);
+    __syncthreads();
     const int g_row = a.row0 + i;
     const int ex = a.extra != nullptr ? a.extra_index[g_row] : -1;
     uint4 v[NV];
     float ss = 0.0f;
 #pragma unroll
     for (int k = 0; k < NV; ++k) {
-      const int c = lane + 32 * k;
+      const int c = threadIdx.x + 128 * k;
       if (c < nvec) {
         float acc[8];
 #pragma unroll
         for (int e = 0; e < 8; ++e) acc[e] = 0.0f;
+#pragma unroll 8
         for (int r = 0; r < a.tp; ++r) {
           const uint4 p = __ldcg(reinterpret_cast<const uint4*>(a.rs + ((size_t)r * a.rows_per_owner + i) * H) + c);
           const __nv_bfloat162* pp = reinterpret_cast<const __nv_bfloat162*>(&p);
@@ -367,10 +371,13 @@ __global__ void __launch_bounds__(256) reduce_norm_allgather_kernel(const RnaArg
         reinterpret_cast<uint4*>(a.residual_out + (size_t)i * H)[c] = x;
       }
     }
-    const float rstd = rsqrtf(warp_sum(ss) / (float)H + a.eps);
+    ss = warp_sum(ss);
+    if (lane == 0) red[warp] = ss;
+    __syncthreads();
+    const float rstd = rsqrtf((red[0] + red[1] + red[2] + red[3]) / (float)H + a.eps);
 #pragma unroll
     for (int k = 0; k < NV; ++k) {
-      const int c = lane + 32 * k;
+      const int c = threadIdx.x + 128 * k;
       if (c < nvec) {
         const uint4 w = reinterpret_cast<const uint4*>(a.weight)[c];
         const __nv_bfloat162* wp = reinterpret_cast<const __nv_bfloat162*>(&w);
@@ -978,10 +985,10 @@ PRISM_API int prism_reduce_norm_allgather(const void* rs, const void* rs_flags, 
   }
   a.ag_seq = (unsigned long long)ag_seq;
   a.cta_counter = (int*)cta_counter;
-  dim3 grid(rows > 0 ? (rows + 7) / 8 : 1), block(256);
-  if (H <= 2048) return (int)prism_launch(reduce_norm_allgather_kernel<8>, grid, block, 0, STREAM(stream), pdl != 0, a);
-  if (H <= 4096) return (int)prism_launch(reduce_norm_allgather_kernel<16>, grid, block, 0, STREAM(stream), pdl != 0, a);
-  return (int)prism_launch(reduce_norm_allgather_kernel<32>, grid, block, 0, STREAM(stream), pdl != 0, a);
+  dim3 grid(rows > 0 ? rows : 1), block(128);
+  if (H <= 2048) return (int)prism_launch(reduce_norm_allgather_kernel<2>, grid, block, 0, STREAM(stream), pdl != 0, a);
+  if (H <= 4096) return (int)prism_launch(reduce_norm_allgather_kernel<4>, grid, block, 0, STREAM(stream), pdl != 0, a);
+  return (int)prism_launch(reduce_norm_allgather_kernel<8>, grid, block, 0, STREAM(stream), pdl != 0, a);
 }
 
 PRISM_API int prism_layernorm(const void* x, const void* w, const void* b, void* out, int T, int H, float eps,
