@@ -75,7 +75,7 @@ def main(args) -> None:
     if rank != 0:
         return  # the reference starts its own worker ranks from one process
     if not os.path.isdir(os.path.join(REF, "prism_infer")):
-        unavailable("reference is not installed under baseline/_ref (pip install --no-deps --target baseline/_ref /root/reference)")
+        unavailable("reference is not installed under baseline/_ref (pip install --no-deps --target baseline/_ref <reference checkout>)")
         return
     try:
         import numpy as np
