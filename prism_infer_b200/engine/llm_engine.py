@@ -26,6 +26,7 @@ from .contracts import BatchPlan, Phase, RequestOutput, StepResult
 from .executor import LocalRunnerGroup, ModelExecutor
 from .input_preparation import VisionJob
 from .metrics import EngineMetrics
+from .progress import GenerationProgress
 from .request import RequestIdAllocator, RequestState
 from .scheduler import Scheduler
 from .sequence import Sequence
@@ -268,15 +269,20 @@ class LLMEngine:
         text = self.tokenizer.decode(token_ids, skip_special_tokens=True)
         return {"text": text, "raw_text": raw, "token_ids": list(token_ids)}
 
-    def _run_until_done(self, ids: list[int]) -> dict[int, list[int]]:
+    def _run_until_done(self, ids: list[int], use_tqdm: bool | None = None) -> dict[int, list[int]]:
         want = set(ids)
         out: dict[int, list[int]] = {}
-        while want - set(out):
-            res = self.step_result()
-            for o in res.finished:
-                out[o.request_id] = list(o.token_ids)
-            if res.phase is Phase.IDLE and self.is_finished():
-                break
+        with GenerationProgress(len(want), enabled=use_tqdm) as progress:
+            while want - set(out):
+                t0 = time.perf_counter()
+                res = self.step_result()
+                progress.observe_step(res.phase, res.num_tokens, time.perf_counter() - t0)
+                for o in res.finished:
+                    out[o.request_id] = list(o.token_ids)
+                    if o.request_id in want:
+                        progress.complete_request()
+                if res.phase is Phase.IDLE and self.is_finished():
+                    break
         for rid in want - set(out):  # rejected or cancelled
             out[rid] = []
         return out
@@ -288,37 +294,38 @@ class LLMEngine:
             return list(sp)
         return [sp] * n
 
-    def generate(self, prompts: Seq[str] | Seq[Seq[int]], sampling_params=None, use_tqdm: bool = False) -> list[dict[str, Any]]:
+    def generate(self, prompts: Seq[str] | Seq[Seq[int]], sampling_params=None, use_tqdm: bool | None = None) -> list[dict[str, Any]]:
         sps = self._broadcast_sp(len(prompts), sampling_params)
         ids = [self.add_request(p, sp) for p, sp in zip(prompts, sps)]
-        done = self._run_until_done(ids)
+        done = self._run_until_done(ids, use_tqdm)
         return [self._format(done[i]) for i in ids]
 
-    def generate_vl(self, prompt, image, sampling_params=None) -> dict[str, Any]:
+    def generate_vl(self, prompt, image, sampling_params=None, use_tqdm: bool | None = None) -> dict[str, Any]:
         rid = self.add_vl_request(prompt, image, sampling_params)
-        return self._format(self._run_until_done([rid])[rid])
+        return self._format(self._run_until_done([rid], use_tqdm)[rid])
 
-    def generate_images(self, prompt, images, sampling_params=None) -> dict[str, Any]:
+    def generate_images(self, prompt, images, sampling_params=None, use_tqdm: bool | None = None) -> dict[str, Any]:
         rid = self.add_images_request(prompt, images, sampling_params)
-        return self._format(self._run_until_done([rid])[rid])
+        return self._format(self._run_until_done([rid], use_tqdm)[rid])
 
-    def generate_interleaved_images(self, prompt, images, sampling_params=None, *, image_marker: str = "<image>") -> dict[str, Any]:
+    def generate_interleaved_images(self, prompt, images, sampling_params=None, use_tqdm: bool | None = None, *,
+                                    image_marker: str = "<image>") -> dict[str, Any]:
         rid = self.add_interleaved_images_request(prompt, images, sampling_params, image_marker=image_marker)
-        return self._format(self._run_until_done([rid])[rid])
+        return self._format(self._run_until_done([rid], use_tqdm)[rid])
 
-    def generate_video(self, prompt, frames, sampling_params=None) -> dict[str, Any]:
+    def generate_video(self, prompt, frames, sampling_params=None, use_tqdm: bool | None = None) -> dict[str, Any]:
         rid = self.add_video_request(prompt, frames, sampling_params)
-        return self._format(self._run_until_done([rid])[rid])
+        return self._format(self._run_until_done([rid], use_tqdm)[rid])
 
-    def generate_prepared_image_inputs(self, inputs: ImageInputs, sampling_params=None) -> dict[str, Any]:
+    def generate_prepared_image_inputs(self, inputs: ImageInputs, sampling_params=None, use_tqdm: bool | None = None) -> dict[str, Any]:
         rid = self.add_prepared_image_request(inputs, sampling_params)
-        return self._format(self._run_until_done([rid])[rid])
+        return self._format(self._run_until_done([rid], use_tqdm)[rid])
 
-    def generate_prepared_video_inputs(self, inputs: VideoInputs, sampling_params=None) -> dict[str, Any]:
+    def generate_prepared_video_inputs(self, inputs: VideoInputs, sampling_params=None, use_tqdm: bool | None = None) -> dict[str, Any]:
         rid = self.add_prepared_video_request(inputs, sampling_params)
-        return self._format(self._run_until_done([rid])[rid])
+        return self._format(self._run_until_done([rid], use_tqdm)[rid])
 
-    def generate_mixed(self, requests: Seq[dict[str, Any]], sampling_params=None) -> list[dict[str, Any]]:
+    def generate_mixed(self, requests: Seq[dict[str, Any]], sampling_params=None, use_tqdm: bool | None = None) -> list[dict[str, Any]]:
         """Batch of heterogeneous requests: each dict has ``type`` in ``text | image | images |
         interleaved_images | video`` plus ``prompt`` and the matching media field."""
         sps = self._broadcast_sp(len(requests), sampling_params)
@@ -339,5 +346,5 @@ class LLMEngine:
                 ids.append(self.add_video_request(req["prompt"], req.get("frames", req.get("video")), sp))
             else:
                 raise ValueError(f"unknown request type {kind!r}")
-        done = self._run_until_done(ids)
+        done = self._run_until_done(ids, use_tqdm)
         return [self._format(done[i]) for i in ids]

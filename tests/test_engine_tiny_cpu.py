@@ -109,3 +109,58 @@ def test_visual_compaction_frees_pages_and_hits(tiny):
     assert r1["token_ids"] == r3["token_ids"]  # cold and hit paths see the same compacted prefix
     assert len(r2["token_ids"]) == 4
     llm.exit()
+
+
+def test_generate_progress_bar_counts_requests_and_phases(tiny, monkeypatch):
+    """``use_tqdm=True`` drives a bar: one update per finished request, prefill and decode
+    throughput in the postfix, closed at the end; results are the same with and without it."""
+    import io
+
+    from prism_infer_b200.engine import progress as progress_mod
+    from prism_infer_b200.engine.contracts import Phase
+
+    class FakeBar:
+        instances = []
+
+        def __init__(self, total, **kw):
+            self.total, self.n, self.postfixes, self.closed = total, 0, [], False
+            FakeBar.instances.append(self)
+
+        def update(self, n):
+            self.n += n
+
+        def set_postfix(self, d, refresh=True):
+            self.postfixes.append(dict(d))
+
+        def close(self):
+            self.closed = True
+
+    real = progress_mod.GenerationProgress
+    monkeypatch.setattr("prism_infer_b200.engine.llm_engine.GenerationProgress",
+                        lambda total, enabled=True: real(total, enabled=enabled, bar_factory=FakeBar))
+    arch, weights, _ = tiny
+    llm = _llm(weights)
+    sp = SamplingParams(temperature=0.0, max_tokens=6, ignore_eos=True)
+    prompts = [[1, 2, 3, 4, 5], [7, 8, 9], [11, 12, 13, 14]]
+    quiet = llm.generate(prompts, sp, use_tqdm=False)
+    assert not FakeBar.instances
+    shown = llm.generate(prompts, sp, use_tqdm=True)
+    assert [r["token_ids"] for r in shown] == [r["token_ids"] for r in quiet]
+    (bar,) = FakeBar.instances
+    assert bar.total == 3 and bar.n == 3 and bar.closed
+    assert bar.postfixes and set(bar.postfixes[-1]) == {"Prefill", "Decode"}
+    assert bar.postfixes[-1]["Decode"].endswith("tok/s") and bar.postfixes[-1]["Decode"] != "0tok/s"
+    llm.exit()
+
+    # the reporter on its own: moving averages per phase, plain lines without a bar, tri-state default
+    buf = io.StringIO()
+    p = real(2, enabled=True, file=buf, bar_factory=lambda **kw: None)
+    p.observe_step(Phase.PREFILL, 1000, 0.5)
+    p.observe_step(Phase.DECODE, 8, 0.004)
+    p.observe_step(Phase.DECODE, 8, 0.008)
+    p.observe_step(Phase.IDLE, 0, 0.001)
+    assert p.prefill_tok_s == 2000.0 and abs(p.decode_tok_s - (0.7 * 2000 + 0.3 * 1000)) < 1e-6
+    p.complete_request()
+    p.close()
+    assert buf.getvalue().startswith("[1/2] prefill 2000tok/s decode 1700tok/s")
+    assert real(1, enabled=None, file=io.StringIO()).enabled is False  # not a terminal: silent
