@@ -28,10 +28,15 @@ class ProfileSession:
         self.regions: list[dict[str, Any]] = []
         self.steps: list[dict[str, Any]] = []
         self._pending: list[tuple[dict[str, Any], Any, Any]] = []
+        self._open: list[int] = []  # indices (in start order) of the regions currently open
+        self._t0 = time.perf_counter_ns()
 
     @contextmanager
     def region(self, name: str, *, cuda: bool = True, metadata: dict[str, Any] | None = None) -> Iterator[None]:
-        rec: dict[str, Any] = {"name": name, "metadata": dict(metadata or {})}
+        # regions are listed in start order; "parent" is the index of the enclosing region
+        rec: dict[str, Any] = {"name": name, "metadata": dict(metadata or {}), "parent": self._open[-1] if self._open else None}
+        self.regions.append(rec)
+        self._open.append(len(self.regions) - 1)
         start_ev = end_ev = None
         if self.nvtx:
             torch.cuda.nvtx.range_push(f"prism::{name}")
@@ -39,16 +44,17 @@ class ProfileSession:
             start_ev, end_ev = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             start_ev.record()
         t0 = time.perf_counter_ns()
+        rec["start_ns"] = t0 - self._t0
         try:
             yield
         finally:
             rec["cpu_ms"] = (time.perf_counter_ns() - t0) / 1e6
+            self._open.pop()
             if end_ev is not None:
                 end_ev.record()
                 self._pending.append((rec, start_ev, end_ev))
             if self.nvtx:
                 torch.cuda.nvtx.range_pop()
-            self.regions.append(rec)
 
     def step(self, meta: dict[str, Any]) -> None:
         self.steps.append(dict(meta))
@@ -61,6 +67,7 @@ class ProfileSession:
             self._pending.clear()
         totals: dict[str, dict[str, float]] = {}
         for r in self.regions:
+            r.setdefault("cpu_ms", 0.0)  # a region still open when the record is taken
             t = totals.setdefault(r["name"], {"count": 0, "cpu_ms": 0.0, "cuda_ms": 0.0})
             t["count"] += 1
             t["cpu_ms"] += r["cpu_ms"]

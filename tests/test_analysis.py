@@ -105,7 +105,10 @@ def test_profile_session_records_regions_and_is_noop_outside():
             pass
     rec = pp.validate_profile_record(session.finalize())
     assert rec["totals"]["a.b"]["count"] == 2 and rec["totals"]["inner"]["count"] == 1
-    assert rec["regions"][0]["name"] == "inner" and rec["metadata"] == {"run": "t"}
+    # regions are listed in start order, each with the index of its enclosing region
+    assert [r["name"] for r in rec["regions"]] == ["a.b", "inner", "a.b"] and rec["metadata"] == {"run": "t"}
+    assert [r["parent"] for r in rec["regions"]] == [None, 0, None]
+    assert rec["regions"][0]["start_ns"] <= rec["regions"][1]["start_ns"] <= rec["regions"][2]["start_ns"]
     with profile_region("after"):
         pass
     assert len(session.regions) == 3
