@@ -59,13 +59,26 @@ def main() -> None:
     ap.add_argument("--image-size", type=int, default=448)
     ap.add_argument("--max-tokens", type=int, default=16)
     ap.add_argument("--seed", type=int, default=wsp.DEFAULT_SEED)
+    ap.add_argument("--plan", default="", help="plan document from build_working_set_plan.py (measured prefix pages); "
+                                               "overrides the group, request, rate, seed and page arguments")
     ap.add_argument("--out", default="")
     args = ap.parse_args()
 
-    groups = wsp.synthetic_groups(args.groups, args.questions, seed=args.seed, min_images=args.min_images,
-                                  max_images=args.max_images, tokens_per_image=(args.image_size // 32) ** 2 + 2)
-    plan = wsp.build_plan(groups, num_requests=args.requests, alpha=args.alpha, rate=args.rate, seed=args.seed,
-                          page_budget=args.pages)
+    plan_sha256 = None
+    if args.plan:
+        from build_working_set_plan import load_plan_document
+
+        plan, doc = load_plan_document(args.plan)
+        plan_sha256 = doc["plan_sha256"]
+        args.image_size, args.seed = doc["contract"]["image_size"], plan.seed
+        args.pages, args.rate, args.alpha = plan.page_budget, plan.rate, plan.alpha
+        args.groups, args.questions = doc["groups"], doc["questions"]
+        args.requests = len(plan.measured)
+    else:
+        groups = wsp.synthetic_groups(args.groups, args.questions, seed=args.seed, min_images=args.min_images,
+                                      max_images=args.max_images, tokens_per_image=(args.image_size // 32) ** 2 + 2)
+        plan = wsp.build_plan(groups, num_requests=args.requests, alpha=args.alpha, rate=args.rate, seed=args.seed,
+                              page_budget=args.pages)
     llm = LLM(args.model, tensor_parallel_size=args.tp, max_model_len=8192, max_num_batched_tokens=8192, max_num_seqs=8,
               max_chunk_size=8192, kvcache_block_size=256, num_kvcache_blocks=args.pages, cpu_kv_cache_ratio=0.0,
               **VARIANTS[args.variant])
@@ -98,7 +111,7 @@ def main() -> None:
         "config": {"variant": args.variant, "groups": args.groups, "questions": args.questions, "requests": args.requests,
                    "rate_per_s": args.rate, "alpha": args.alpha, "pages": args.pages, "page_tokens": 256, "images_per_group": [args.min_images, args.max_images],
                    "kv_budget_bytes": args.pages * llm.config.kv_bytes_per_page(), "working_set_pages": plan.working_set_pages,
-                   "max_tokens": args.max_tokens, "seed": args.seed, "tp": args.tp},
+                   "max_tokens": args.max_tokens, "seed": args.seed, "tp": args.tp, "plan_sha256": plan_sha256},
         "results": {
             "ttft_p50_ms": summary["ttft_ms"]["p50"], "ttft_p99_ms": summary["ttft_ms"]["p99"],
             "e2e_p50_ms": summary["e2e_ms"]["p50"], "e2e_p99_ms": summary["e2e_ms"]["p99"],
