@@ -109,3 +109,92 @@ def test_working_set_plan_builder_measures_resumes_and_round_trips(tmp_path):
     path.write_text(json.dumps(doc))
     with pytest.raises(ValueError, match="edited"):
         b.load_plan_document(path)
+
+
+def test_working_set_quality_runner_stages_resume_and_pairing(tmp_path):
+    """Two media groups with two / three questions on the tiny model: both stages run, the
+    repeat questions hit the stored prefix, an interrupted stage file resumes at a group
+    boundary, a foreign file is refused."""
+    import io
+
+    import numpy as np
+    import pytest
+    import torch
+    from PIL import Image
+
+    from prism_infer_b200 import LLM
+    from prism_infer_b200.analysis import working_set_quality as wsq
+    from prism_infer_b200.analysis.quality_materialization import materialize_image
+    from prism_infer_b200.models.architecture import Qwen3VLArch
+    from prism_infer_b200.models.weights import random_weights
+
+    q = _load("bench_working_set_quality")
+    root = tmp_path / "media"
+    rng = np.random.default_rng(0)
+
+    def png(size):
+        buf = io.BytesIO()
+        Image.fromarray(rng.integers(0, 256, (size, size, 3), dtype=np.uint8)).save(buf, format="PNG")
+        return materialize_image(buf.getvalue(), root=root, dataset_id="synthetic")
+
+    a, b, c = png(64), png(64), png(96)
+    records = [
+        {"sample_id": "s1", "question": "which is brighter", "options": ["left", "right"], "answer": "A", "media": [a, b]},
+        {"sample_id": "s2", "question": "compare <image> with <image>", "options": ["same", "other", "none"], "answer": "C", "media": [a, b]},
+        {"sample_id": "s3", "question": "read the sign", "answers": ["stop", "STOP sign"], "media": [c]},
+        {"sample_id": "s4", "question": "what colour", "answers": ["red"], "media": [c]},
+        {"sample_id": "s5", "question": "how many", "answers": ["one"], "media": [c]},
+        {"sample_id": "lonely", "question": "alone", "answers": ["x"], "media": [b]},
+    ]
+    rec_path = tmp_path / "records.jsonl"
+    rec_path.write_text("".join(json.dumps(r) + "\n" for r in records))
+    loaded = q.load_records(rec_path)
+    plan = wsq.select_multi_question_groups(loaded)
+    assert len(plan) == 5 and {it.record["sample_id"] for it in plan} == {"s1", "s2", "s3", "s4", "s5"}
+    assert q.prompt_for(loaded[1]).count("<image>") == 2 and "compare Image 1 with Image 2" in q.prompt_for(loaded[1])
+    assert q.score(loaded[0], "The answer is (A).")["correct"] and not q.score(loaded[0], "B")["correct"]
+    assert q.score(loaded[2], "Stop")["score"] == 1.0 and q.score(loaded[2], "yield")["score"] == 0.0
+    with pytest.raises(ValueError):
+        rec_bad = tmp_path / "bad.jsonl"
+        rec_bad.write_text(json.dumps({"sample_id": 1, "question": "q", "media": [a]}) + "\n")
+        q.load_records(rec_bad)
+
+    arch = Qwen3VLArch.tiny()
+    weights = random_weights(arch, dtype=torch.float32, seed=0)
+    built = []
+
+    def make_engine(extra):
+        extra = dict(extra)
+        if "visual_pruning_min_keep_tokens" in extra:
+            extra.update(visual_pruning_min_keep_tokens=2, visual_pruning_keep_ratio=0.5)
+        built.append(extra["compression_mode"])
+        return LLM("random:tiny", weights=weights, device="cpu", max_model_len=512, kvcache_block_size=16, num_kvcache_blocks=128,
+                   enforce_eager=True, max_num_batched_tokens=512, max_chunk_size=512, enable_prefix_caching=True, **extra)
+
+    out = tmp_path / "run"
+    out.mkdir()
+    quiet = lambda _m: None  # noqa: E731
+    dense = q.run_stage("dense_prefix", plan, make_engine, root, out, max_tokens=3, resume=False, log=quiet)
+    assert [r["sample_id"] for r in dense] == [it.record["sample_id"] for it in plan]
+    assert [r["prefix_hit"] for r in dense] == [it.question_index > 0 for it in plan]
+    assert all(r["deleted_visual_tokens"] == 0 for r in dense) and all(r["cached_tokens"] > 0 for r in dense if r["prefix_hit"])
+    with pytest.raises(FileExistsError):
+        q.run_stage("dense_prefix", plan, make_engine, root, out, max_tokens=3, resume=False, log=quiet)
+    # an interrupted compact stage: the first group and one line of the second survive on disk
+    compact_full = q.run_stage("compact_prefix", plan, make_engine, root, out, max_tokens=3, resume=False, log=quiet)
+    assert any(r["deleted_visual_tokens"] > 0 for r in compact_full)
+    first_group = plan[0].group_size
+    path = out / "compact_prefix.samples.jsonl"
+    path.write_text("".join(json.dumps(r) + "\n" for r in compact_full[:first_group + 1]))
+    n_built = len(built)
+    resumed = q.run_stage("compact_prefix", plan, make_engine, root, out, max_tokens=3, resume=True, log=quiet)
+    assert resumed == compact_full and len(built) == n_built + 1
+    assert q.run_stage("compact_prefix", plan, make_engine, root, out, max_tokens=3, resume=True, log=quiet) == compact_full
+    assert len(built) == n_built + 1  # complete: no engine
+    path.write_text(json.dumps(dict(compact_full[0], sample_id="zzz")) + "\n")
+    with pytest.raises(ValueError, match="does not match the plan"):
+        q.run_stage("compact_prefix", plan, make_engine, root, out, max_tokens=3, resume=True, log=quiet)
+    summary = q.summarize({"dense_prefix": dense, "compact_prefix": compact_full}, plan)
+    assert summary["samples"] == 5 and summary["groups"] == 2
+    assert summary["stages"]["dense_prefix"]["repeat_prefix_hits"] == 3 == summary["stages"]["dense_prefix"]["repeat_questions"]
+    assert summary["paired_deleted_subset"]["cohort"] == summary["stages"]["compact_prefix"]["samples_with_deletions"] > 0
