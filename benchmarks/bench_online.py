@@ -24,9 +24,11 @@ import time
 import numpy as np
 
 sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
 
 from prism_infer_b200 import LLM, SamplingParams  # noqa: E402
 from prism_infer_b200.analysis import benchmark_schema, online_serving, working_set_plan as wsp  # noqa: E402
+import harness  # noqa: E402
 from prism_infer_b200.engine.online import OnlineRequest, OnlineServingSession  # noqa: E402
 
 VARIANTS = {
@@ -108,6 +110,7 @@ def main() -> None:
         "schema_version": benchmark_schema.BENCHMARK_SCHEMA_VERSION, "benchmark": "online_working_set",
         "engine": "prism_infer_b200", "model": args.model, "data": "synthetic",
         "hardware": {"gpus": args.tp},
+        "provenance": harness.provenance(),
         "config": {"variant": args.variant, "groups": args.groups, "questions": args.questions, "requests": args.requests,
                    "rate_per_s": args.rate, "alpha": args.alpha, "pages": args.pages, "page_tokens": 256, "images_per_group": [args.min_images, args.max_images],
                    "kv_budget_bytes": args.pages * llm.config.kv_bytes_per_page(), "working_set_pages": plan.working_set_pages,

@@ -20,6 +20,9 @@ import numpy as np
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 sys.path.insert(0, ROOT)
+sys.path.insert(0, os.path.join(ROOT, "benchmarks"))
+
+import harness  # noqa: E402
 
 from prism_infer_b200 import LLM, SamplingParams  # noqa: E402
 from prism_infer_b200.analysis import benchmark_schema  # noqa: E402
@@ -99,6 +102,7 @@ def main() -> None:
     ap.add_argument("--out", default="")
     args = ap.parse_args()
     records = []
+    provenance = harness.provenance()
     for mode in args.modes:
         if mode not in MODES:
             raise SystemExit(f"unknown mode {mode!r}; known: {sorted(MODES)}")
@@ -116,7 +120,7 @@ def main() -> None:
             rec = {"schema_version": benchmark_schema.BENCHMARK_SCHEMA_VERSION, "benchmark": "system_mode_matrix", "engine": "prism_infer_b200",
                    "model": args.model, "data": "synthetic", "hardware": {"gpus": args.tensor_parallel_size},
                    "config": {"mode": mode, "workload": name, **{k: v for k, v in opts.items()}, "tp": args.tensor_parallel_size},
-                   "results": res}
+                   "results": res, "provenance": provenance}
             benchmark_schema.validate_benchmark_record(rec)
             records.append(rec)
             print(json.dumps({"mode": mode, "workload": name, **{k: (round(v, 3) if isinstance(v, float) else v) for k, v in res.items()}}), flush=True)
