@@ -215,3 +215,69 @@ def test_media_groups_and_media_first_prompt():
     compact = [{"sample_id": i, "correct": i % 3 == 0, "deleted_visual_tokens": 10 if i >= 2 else 0} for i in range(6)]
     assert wq.paired_deleted_subset(dense, compact) == {"cohort": 4, "dense_correct": 2, "compact_correct": 1}
     assert wq.summarize_stage_samples(compact)["samples_with_deletions"] == 4
+
+
+def test_materialize_quality_subset_from_local_parquet_shards(tmp_path):
+    """Two complete shards of a MuirBench-like dataset and one DocVQA-like shard, written with
+    pyarrow: selection is deterministic, only the selected rows are materialised, the manifest
+    verifies, an incomplete shard set is refused."""
+    import io
+    import json
+
+    import numpy as np
+    import pyarrow as pa
+    import pyarrow.parquet as pq
+    import pytest
+    from PIL import Image
+
+    from prism_infer_b200.analysis import quality_materialization as qmat
+    from prism_infer_b200.utils import materialize_quality_data as mq
+
+    rng = np.random.default_rng(0)
+
+    def png():
+        buf = io.BytesIO()
+        Image.fromarray(rng.integers(0, 256, (24, 24, 3), dtype=np.uint8)).save(buf, format="PNG")
+        return {"bytes": buf.getvalue(), "path": None}
+
+    shared = png()
+    raw = tmp_path / "raw"
+    raw.mkdir()
+    rows = [{"idx": i, "task": "t", "image_relation": "r", "image_type": "photo", "question": f"q{i} <image> <image>", "options": ["a", "b", "c"],
+             "answer": "ABC"[i % 3], "image_list": [shared, png()], "counterpart_idx": -1} for i in range(10)]
+    pq.write_table(pa.Table.from_pylist(rows[:6]), raw / "test-00000-of-00002.parquet")
+    pq.write_table(pa.Table.from_pylist(rows[6:]), raw / "test-00001-of-00002.parquet")
+    out = tmp_path / "quality"
+    m = mq.materialize(layout="muirbench", dataset_id="muir", revision="rev1", raw_dir=raw, split="test", out_root=out, seed=7,
+                       development=2, final=4, batch_size=3)
+    assert m["selection"]["population_samples"] == 10 and m["selection"]["final"]["samples"] == 4 and len(m["source_files"]) == 2
+    records = [json.loads(line) for line in (out / "muir.records.jsonl").read_text().splitlines()]
+    assert [r["sample_id"] for r in records] == m["selection"]["final"]["sample_ids"]
+    assert m["verification"]["unique_media_files"] == 5                      # 4 private images + the shared one, stored once
+    assert len({r["media"][0]["sha256"] for r in records}) == 1
+    qmat.verify_materialized_records(records, out)
+    again = mq.materialize(layout="muirbench", dataset_id="muir", revision="rev1", raw_dir=raw, split="test", out_root=out, seed=7,
+                           development=2, final=4)
+    assert again["records_sha256"] == m["records_sha256"]                    # idempotent
+    other = mq.materialize(layout="muirbench", dataset_id="muir", revision="rev2", raw_dir=raw, split="test", out_root=tmp_path / "q2", seed=7,
+                           development=2, final=4)
+    assert other["selection"]["final"]["sample_ids"] != m["selection"]["final"]["sample_ids"]   # the revision is part of the preimage
+    (raw / "test-00001-of-00002.parquet").unlink()
+    with pytest.raises(ValueError, match="incomplete"):
+        mq.discover_complete_shards(raw, "test")
+    with pytest.raises(FileNotFoundError):
+        mq.discover_complete_shards(raw, "validation")
+
+    doc = tmp_path / "doc"
+    doc.mkdir()
+    drows = [{"questionId": 100 + i, "question": f"what {i}", "answers": ["x", "y"], "image": png(), "question_types": ["form"], "docId": i}
+             for i in range(5)]
+    pq.write_table(pa.Table.from_pylist(drows), doc / "validation-00000-of-00001.parquet")
+    dm = mq.materialize(layout="docvqa", dataset_id="docvqa", revision="r", raw_dir=doc, split="validation", out_root=out, seed=1,
+                        development=1, final=3)
+    drec = [json.loads(line) for line in (out / "docvqa.records.jsonl").read_text().splitlines()]
+    assert len(drec) == 3 and drec[0]["answers"] == ["x", "y"] and dm["layout"] == "docvqa"
+    with pytest.raises(ValueError, match="outside its options"):
+        mq.convert_row("muirbench", dict(rows[0], answer="D"), root=out, dataset_id="muir")
+    with pytest.raises(ValueError, match="no embedded image"):
+        mq.convert_row("docvqa", dict(drows[0], image={"path": "x.png"}), root=out, dataset_id="docvqa")
