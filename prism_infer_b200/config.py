@@ -248,6 +248,7 @@ _FLAT = {
         "vision_attention_backend": "vision_attention_backend",
         "enable_vision_tensor_cudagraph": "enable_vision_tensor_cudagraph",
         "enable_visual_embedding_cache": "enable_visual_embedding_cache",
+        "visual_embedding_cache_bytes": "visual_embedding_cache_bytes",
     },
     "cache": {
         "gpu_memory_utilization": "gpu_memory_utilization", "kvcache_block_size": "page_size",

@@ -43,6 +43,16 @@ class ModelExecutor:
                                      "uniform" if config.visual_pruning_strategy == "attention" else config.visual_pruning_strategy)
         self._have_visual: set[int] = set()
 
+    def mark_visual_ready(self, seq_id: int) -> None:
+        """The runner already holds this sequence's vision result (hydrated at submission)."""
+        self._have_visual.add(seq_id)
+
+    def drop_visual(self, seq_id: int) -> None:
+        """A sequence left before its prefill consumed the vision result: free it on the ranks."""
+        if seq_id in self._have_visual:
+            self._have_visual.discard(seq_id)
+            self.runners.call("release_visual", seq_id)
+
     def hydrate_vision(self, plan: BatchPlan) -> int:
         """Cooperative prefill quantum: push the plan's pending vision-tower work through the
         runner now (page transfers included) and leave the language prefill to a later step,

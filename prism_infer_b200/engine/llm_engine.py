@@ -136,7 +136,9 @@ class LLMEngine:
             grids = list(seq.image_grid_thw) + list(seq.video_grid_thw)
             self.runners.call("hydrate_visual_embedding", VisionJob(seq.seq_id, seq.pixel_values, grids,
                                                                     seq.visual_embedding_cache_key))
+            self.executor.mark_visual_ready(seq.seq_id)
         if not self.scheduler.add(seq):
+            self.executor.drop_visual(seq.seq_id)
             self.metrics.on_request_finished(seq)
             if raise_on_reject:
                 raise ValueError(f"request rejected: {seq.lifecycle.finish_reason}")
@@ -248,6 +250,7 @@ class LLMEngine:
 
     def cancel_request(self, request_id: int) -> bool:
         ok = self.scheduler.cancel(request_id)
+        self.executor.drop_visual(request_id)
         self._sequences.pop(request_id, None)
         return ok
 

@@ -222,8 +222,16 @@ class ModelRunner:
         self._visual[job.seq_id] = self._encode(job)
 
     def hydrate_visual_embedding(self, job) -> None:
-        """Run the vision tower ahead of scheduling and keep the result in the LRU cache."""
-        self._encode(job)
+        """Run the vision tower ahead of scheduling.  The result stays attached to the sequence
+        until its prefill has consumed it (reference ``engine/model_runner.py:522-596``) - the
+        LRU cache alone would lose it when a burst of submissions exceeds the cache budget, and
+        the prefill would encode the media a second time - and in the cache for later requests
+        with the same media."""
+        self._visual[job.seq_id] = self._encode(job)
+
+    def release_visual(self, seq_id: int) -> None:
+        """Drop the vision result of a sequence that will not be prefilled (cancelled, rejected)."""
+        self._visual.pop(seq_id, None)
 
     def visual_embedding_cache_metadata(self) -> dict[str, object]:
         return {"enabled": self.config.enable_visual_embedding_cache, "entries": len(self._visual_cache),

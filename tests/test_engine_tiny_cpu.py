@@ -164,3 +164,25 @@ def test_generate_progress_bar_counts_requests_and_phases(tiny, monkeypatch):
     p.close()
     assert buf.getvalue().startswith("[1/2] prefill 2000tok/s decode 1700tok/s")
     assert real(1, enabled=None, file=io.StringIO()).enabled is False  # not a terminal: silent
+
+
+def test_hydrated_vision_result_stays_with_the_sequence(tiny):
+    """A burst of submissions larger than the visual-embedding cache: every image is still
+    encoded exactly once (the hydrated result is attached to its sequence, not only to the LRU
+    cache), nothing is left behind afterwards, and a cancelled request frees its result."""
+    arch, weights, oracle = tiny
+    llm = _llm(weights, enable_visual_embedding_cache=True, visual_embedding_cache_bytes=1, enable_prefix_caching=False, max_num_seqs=8)
+    runner = llm.runners.runner
+    sp = SamplingParams(temperature=0.0, max_tokens=2, ignore_eos=True)
+    reqs = [{"type": "image", "prompt": [3, 4, 5], "image": _image(40 + i, 64)} for i in range(4)]
+    outs = llm.generate_mixed(reqs, sp)
+    meta = llm.visual_embedding_cache_metadata()
+    assert meta["misses"] == 4 and meta["hits"] == 0 and meta["entries"] == 0
+    assert not runner._visual and not llm.executor._have_visual
+    tok = load_tokenizer("random:tiny", arch)
+    inp = prepare_image_inputs(PatchProcessor(arch), tok, [3, 4, 5], [_image(40, 64)])
+    assert outs[0]["token_ids"] == oracle.generate_greedy(inp.input_ids, 2, pixel_values=inp.pixel_values, image_grid_thw=inp.image_grid_thw)
+    rid = llm.add_vl_request([3, 4, 5], _image(50, 64), sp)
+    assert rid in runner._visual
+    assert llm.cancel_request(rid) and rid not in runner._visual and not llm.executor._have_visual
+    llm.exit()
