@@ -259,7 +259,7 @@ class BlockManager:
         need = 1 if self.needs_new_page(seq) else 0
         if not need and seq.block_table and self.gpu.blocks[seq.block_table[-1]].ref_count > 1:
             need = 1  # copy-on-write of a shared tail
-        return self.num_free_with_eviction() >= need
+        return need == 0 or self.num_free_with_eviction() >= need
 
     def append(self, seq: Sequence) -> tuple[tuple[int, int], ...]:
         """Make room for the KV row of ``seq``'s last token; returns copy-on-write pairs."""

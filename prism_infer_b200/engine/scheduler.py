@@ -183,21 +183,24 @@ class Scheduler:
             self.running.append(seq)
             self.counters["swap_in"] += 1
         batch: list[Sequence] = []
+        preempted = False  # membership in ``running`` only changes through a preemption in this pass
         for seq in list(self.running):
-            if seq.state is not RequestState.DECODING or seq not in self.running:
+            if seq.state is not RequestState.DECODING or (preempted and seq not in self.running):
                 continue
             while not bm.can_append(seq):
                 victim = self.policy.pick_victim([s for s in self.running if s.state is RequestState.DECODING])
                 swap_out.extend(self.preempt(victim))
+                preempted = True
                 if victim is seq:
                     break
-            if seq.state is not RequestState.DECODING or seq not in self.running:
+            if preempted and (seq.state is not RequestState.DECODING or seq not in self.running):
                 continue
             cow.extend(bm.append(seq))
             batch.append(seq)
             if len(batch) >= self.max_num_seqs:
                 break
-        batch = [s for s in batch if s in self.running and s.state is RequestState.DECODING]
+        if preempted:
+            batch = [s for s in batch if s in self.running and s.state is RequestState.DECODING]
         if not batch:
             if swap_out:
                 return BatchPlan(Phase.IDLE, kv_transfers=KVTransferPlan(swap_out=tuple(swap_out)))
