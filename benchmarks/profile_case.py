@@ -11,6 +11,8 @@ by itself in about a minute.
     python benchmarks/profile_case.py prefill_attention
     python benchmarks/profile_case.py add_rmsnorm
     python benchmarks/profile_case.py gemm_normx       # projection with the fused add+RMSNorm prologue
+    python benchmarks/profile_case.py decode_step 128  # ONE engine decode step at that batch inside cudaProfilerStart/Stop
+                                                       # (launch list with --profile-from-start off; full-size model)
 """
 
 from __future__ import annotations
@@ -25,9 +27,43 @@ sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 from prism_infer_b200 import ops  # noqa: E402
 
 
+def decode_step(batch: int) -> None:
+    """``batch`` one-image requests on the 8B model, stepped until all of them decode; one further
+    step runs between ``cudaProfilerStart`` and ``cudaProfilerStop``."""
+    import numpy as np
+
+    from prism_infer_b200 import LLM, SamplingParams
+    from prism_infer_b200.engine.vl_inputs import PatchProcessor, prepare_image_inputs
+
+    llm = LLM("random:qwen3-vl-8b", max_model_len=4096, kvcache_block_size=256, num_kvcache_blocks=max(64, batch * 4),
+              compression_mode="scaled_fp8_kv", max_num_seqs=batch, max_num_batched_tokens=16384, max_chunk_size=2048,
+              cpu_kv_cache_ratio=0.0, enable_prefix_caching=False)
+    rng = np.random.default_rng(0)
+    proc = PatchProcessor(llm.arch)
+    sp = SamplingParams(temperature=0.0, max_tokens=64, ignore_eos=True)
+    for _ in range(batch):
+        inp = prepare_image_inputs(proc, llm.tokenizer, rng.integers(0, 150000, 32).tolist(),
+                                   [rng.integers(0, 256, (448, 448, 3), dtype=np.uint8)])
+        llm.add_prepared_image_request(inp, sp)
+    while llm.scheduler.num_decoding < batch:
+        llm.step_result()
+    for _ in range(4):
+        llm.step_result()
+    torch.cuda.synchronize()
+    torch.cuda.profiler.start()
+    llm.step_result()
+    torch.cuda.synchronize()
+    torch.cuda.profiler.stop()
+    print("done decode_step", batch)
+    llm.exit()
+
+
 def main() -> None:
     case = sys.argv[1] if len(sys.argv) > 1 else "gemm_decode"
     reps = int(sys.argv[2]) if len(sys.argv) > 2 else 4
+    if case == "decode_step":
+        decode_step(reps if len(sys.argv) > 2 else 128)
+        return
     dev = torch.device("cuda:0")
     g = torch.Generator(device=dev).manual_seed(0)
 
