@@ -120,7 +120,8 @@ class ModelExecutor:
         copies = []
         for seq, sl in zip(plan.seqs, plan.slices):
             boundary = seq.multimodal_prefix_boundary
-            if seq.is_multimodal and sl.end == boundary and sl.end < len(seq) and seq.multimodal_prefix_cache_key:
+            crossed = sl.end == boundary if self.compact else sl.start < boundary <= sl.end
+            if seq.is_multimodal and boundary > 0 and crossed and seq.multimodal_prefix_cache_key:
                 seq.num_computed_tokens += sl.length
                 try:
                     copies.extend(self.bm.store_multimodal_prefix(seq))

@@ -42,7 +42,10 @@ class Scheduler:
         self.policy = policy or make_policy(config)
         self.metrics = metrics
         self.clock_ns = clock_ns
-        self.stop_at_prefix = bool(config.enable_prefix_caching or config.compacts_visual_tokens)
+        # a chunk must end on the multimodal prefix boundary only where the prefix is compacted in
+        # place before the rest of the prompt is written behind it; a dense prefix is published
+        # from whichever chunk crosses the boundary, without an extra prefill step
+        self.stop_at_prefix = bool(config.compacts_visual_tokens)
         self.waiting: deque[Sequence] = deque()
         self.running: list[Sequence] = []
         self.swapped: deque[Sequence] = deque()

@@ -186,3 +186,36 @@ def test_hydrated_vision_result_stays_with_the_sequence(tiny):
     assert rid in runner._visual
     assert llm.cancel_request(rid) and rid not in runner._visual and not llm.executor._have_visual
     llm.exit()
+
+
+def test_dense_prefix_is_published_without_an_extra_prefill_step(tiny):
+    """A dense multimodal prefix is stored from the chunk that crosses its boundary (one prefill
+    step for the whole prompt); only in-place compaction needs the chunk to end on the boundary."""
+    arch, weights, oracle = tiny
+    tok = load_tokenizer("random:tiny", arch)
+    sp = SamplingParams(temperature=0.0, max_tokens=3, ignore_eos=True)
+    a = prepare_image_inputs(PatchProcessor(arch), tok, [11, 12, 13], [_image(5)])
+    b = prepare_image_inputs(PatchProcessor(arch), tok, [21, 22, 23, 24], [_image(5)])
+
+    def prefill_steps(llm):
+        return sum(1 for x in llm.metrics_snapshot()["engine"]["batches"] if x["phase"] == "prefill")
+
+    dense = _llm(weights, compression_mode="scaled_fp8_kv")
+    first = dense.generate_prepared_image_inputs(a, sp)
+    assert prefill_steps(dense) == 1 and dense.multimodal_prefix_cache_metadata()["stores"] == 1
+    second = dense.generate_prepared_image_inputs(b, sp)
+    meta = dense.multimodal_prefix_cache_metadata()
+    assert meta["hits"] == 1 and prefill_steps(dense) == 2
+    assert len(first["token_ids"]) == len(second["token_ids"]) == 3
+    dense.exit()
+    compact = _llm(weights, compression_mode="visual_compact_scaled_fp8", visual_pruning_keep_ratio=0.5, visual_pruning_min_keep_tokens=4)
+    compact.generate_prepared_image_inputs(a, sp)
+    assert prefill_steps(compact) == 2 and compact.multimodal_prefix_cache_metadata()["stores"] == 1
+    compact.exit()
+    off = _llm(weights)  # bf16 dense prefix against the oracle, cold and hit, single prefill step each
+    r1 = off.generate_prepared_image_inputs(a, sp)
+    r2 = off.generate_prepared_image_inputs(b, sp)
+    assert prefill_steps(off) == 2 and off.multimodal_prefix_cache_metadata()["hits"] == 1
+    assert r1["token_ids"] == oracle.generate_greedy(a.input_ids, 3, pixel_values=a.pixel_values, image_grid_thw=a.image_grid_thw)
+    assert r2["token_ids"] == oracle.generate_greedy(b.input_ids, 3, pixel_values=b.pixel_values, image_grid_thw=b.image_grid_thw)
+    off.exit()
