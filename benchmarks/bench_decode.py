@@ -3,7 +3,9 @@ grid of (workload, batch size) at a given tensor-parallel size.  Workloads: ``im
 448x448 images + 32 tokens), ``image1`` (1 image + 32 tokens), ``video16`` (16-frame 448x448
 clip + 32 tokens, chunked prefill 2048), ``text`` (256 random tokens).  Mirrors the
 reference's ``benchmarks/bench_external_prism.py`` / ``bench_system.py`` metrics: TTFT = first
-token time after preprocessing, TPOT = (last - first token time) / (n - 1).
+token time after preprocessing, TPOT = (last - first token time) / (n - 1).  At larger batches that TPOT contains the prefill batches of the
+other requests; ``steady_step_ms_median`` is the wall time of a decode step in which every sequence of the batch
+decodes.
 
     python benchmarks/bench_decode.py --workload image1 --batches 1,8,32,128 [--tp 8] [--out rec.json]
 """
@@ -73,9 +75,14 @@ def main() -> None:
             first: dict[int, float] = {}
             last: dict[int, float] = {}
             count: dict[int, int] = {}
+            steady: list[float] = []  # wall time of decode steps in which all b sequences decode
             while not llm.is_finished():
+                full = llm.scheduler.num_decoding == b
+                t_step = time.perf_counter()
                 res = llm.step_result()
                 now = time.perf_counter()
+                if full and res.phase.value == "decode" and len(res.outputs) == b:
+                    steady.append((now - t_step) * 1e3)
                 for o in res.outputs:
                     if o.new_token is not None:
                         first.setdefault(o.request_id, now)
@@ -87,6 +94,10 @@ def main() -> None:
         row = {"batch": b, "ttft_ms_mean": float(np.mean(ttft)), "ttft_ms_max": float(np.max(ttft)),
                "tpot_ms_mean": float(np.mean(tpot)), "output_tok_per_s": b * args.output_tokens / (t_end - t_ready),
                "preprocess_ms": (t_ready - t_submit) * 1e3}
+        if len(steady) > 8:  # per-step figures without the other requests' prefill batches in between
+            core = sorted(steady[4:])
+            row["steady_step_ms_median"] = float(core[len(core) // 2])
+            row["steady_tok_per_s"] = b * 1e3 / row["steady_step_ms_median"]
         rows.append(row)
         print(json.dumps(row), flush=True)
     record = {"schema_version": benchmark_schema.BENCHMARK_SCHEMA_VERSION, "benchmark": "decode_matrix",
