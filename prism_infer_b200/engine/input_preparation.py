@@ -83,6 +83,47 @@ class StepInputs(_TensorStatePickle):
     # decode only
     context_lens: Optional[torch.Tensor] = None   # [B] int32
 
+    # ---- fixed binary form of a decode step for the tensor-parallel command channel ----------
+    # int64 words [batch, table width, 0, 0 | ids[B] | slots[B]] followed by int32 words
+    # [positions[3B] | context_lens[B] | temperature bits[B] | block_tables[B * W]].  A decode step
+    # is sent every few milliseconds; pickling its six small tensors costs about 80 us per step
+    # (write + read), this form a tenth of that, and the workers start their step that much sooner.
+    def pack_decode(self, area: memoryview) -> int:
+        """Write the step into ``area``; returns the bytes used, or 0 when this step does not fit
+        the fixed form (not a decode step, unexpected dtypes, area too small)."""
+        if self.kind != "decode" or self.context_lens is None or self.block_tables.dim() != 2:
+            return 0
+        B, W = (int(v) for v in self.block_tables.shape)
+        want = ((self.input_ids, torch.int64, B), (self.slots, torch.int64, B), (self.positions, torch.int32, 3 * B),
+                (self.context_lens, torch.int32, B), (self.temperatures, torch.float32, B), (self.block_tables, torch.int32, B * W))
+        if any(t.dtype != d or t.numel() != n or t.device.type != "cpu" for t, d, n in want):
+            return 0
+        n64 = 4 + 2 * B
+        total = n64 * 8 + 4 * (5 * B + B * W)
+        if total > len(area):
+            return 0
+        a64 = np.ndarray((n64,), dtype=np.int64, buffer=area)
+        a64[0], a64[1], a64[2], a64[3] = B, W, 0, 0
+        a64[4:4 + B] = self.input_ids.numpy()
+        a64[4 + B:] = self.slots.numpy()
+        a32 = np.ndarray((5 * B + B * W,), dtype=np.int32, buffer=area, offset=n64 * 8)
+        a32[:3 * B] = self.positions.contiguous().numpy().reshape(-1)
+        a32[3 * B:4 * B] = self.context_lens.numpy()
+        a32[4 * B:5 * B] = self.temperatures.numpy().view(np.int32)
+        a32[5 * B:] = self.block_tables.contiguous().numpy().reshape(-1)
+        return total
+
+    @classmethod
+    def unpack_decode(cls, area: memoryview) -> "StepInputs":
+        head = np.ndarray((4,), dtype=np.int64, buffer=area)
+        B, W = int(head[0]), int(head[1])
+        n64 = 4 + 2 * B
+        a64 = np.array(np.ndarray((n64,), dtype=np.int64, buffer=area))  # copies: the area is reused
+        a32 = np.array(np.ndarray((5 * B + B * W,), dtype=np.int32, buffer=area, offset=n64 * 8))
+        return cls(kind="decode", input_ids=torch.from_numpy(a64[4:4 + B]), positions=torch.from_numpy(a32[:3 * B].reshape(3, B)),
+                   slots=torch.from_numpy(a64[4 + B:]), block_tables=torch.from_numpy(a32[5 * B:].reshape(B, W)),
+                   temperatures=torch.from_numpy(a32[4 * B:5 * B].view(np.float32)), context_lens=torch.from_numpy(a32[3 * B:4 * B]))
+
     @property
     def num_tokens(self) -> int:
         return int(self.input_ids.shape[0])

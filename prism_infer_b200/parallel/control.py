@@ -120,6 +120,8 @@ class ControlSegment:
 
 
 OUT_OF_BAND_MIN_BYTES = 64 << 10
+PAYLOAD_KIND_WORD = 5   # header word: how the command area is encoded
+PAYLOAD_PICKLE, PAYLOAD_DECODE = 0, 1
 
 
 def write_payload(seg: ControlSegment, obj: Any) -> int:
@@ -175,7 +177,12 @@ class ControlDriver:
 
     def post(self, method: TPMethod | str, args: tuple) -> int:
         m = TPMethod(method) if not isinstance(method, TPMethod) else method
-        total = write_payload(self.seg, (m.value, args))
+        total = 0
+        if m is TPMethod.EXECUTE and len(args) == 1 and hasattr(args[0], "pack_decode"):
+            total = args[0].pack_decode(self.seg.payload(self.seg.payload_cap))  # fixed binary form of a decode step
+        self.seg.words[PAYLOAD_KIND_WORD] = PAYLOAD_DECODE if total else PAYLOAD_PICKLE
+        if not total:
+            total = write_payload(self.seg, (m.value, args))
         self.seg.words[1] = total
         self.request_id += 1
         self.seg.words[0] = self.request_id  # publish last
@@ -233,6 +240,10 @@ class ControlWorker:
             seq = int(self.seg.words[0])
             if seq > self.last:
                 n = int(self.seg.words[1])
+                if int(self.seg.words[PAYLOAD_KIND_WORD]) == PAYLOAD_DECODE:
+                    from ..engine.input_preparation import StepInputs
+
+                    return seq, TPMethod.EXECUTE.value, (StepInputs.unpack_decode(self.seg.payload(n)),)
                 method, args = read_payload(self.seg, n)
                 return seq, method, args
             if int(self.seg.words[2]):

@@ -152,3 +152,50 @@ def test_large_arrays_travel_out_of_band_and_small_ones_in_band():
             control.write_payload(seg, torch.zeros(16 << 20, dtype=torch.uint8).numpy())
     finally:
         seg.close()
+
+
+def test_decode_step_travels_in_the_fixed_binary_form():
+    """A decode ``StepInputs`` is sent without pickle; every field arrives bit-identical, the
+    worker's copy does not alias the command area, and anything else still goes through pickle."""
+    import numpy as np
+    import torch
+
+    from prism_infer_b200.engine.input_preparation import StepInputs
+    from prism_infer_b200.parallel import control
+    from prism_infer_b200.parallel.control import ControlDriver, ControlSegment, ControlWorker, TPMethod
+
+    seg = ControlSegment(None, 1, create=True, payload_cap=1 << 16)
+    try:
+        driver, worker = ControlDriver(seg), ControlWorker(seg, 0, 1)
+        g = torch.Generator().manual_seed(0)
+        B, W = 5, 7
+        inp = StepInputs(kind="decode", input_ids=torch.randint(0, 150000, (B,), generator=g), positions=torch.randint(0, 4000, (3, B), generator=g, dtype=torch.int32),
+                         slots=torch.randint(0, 1 << 40, (B,), generator=g), block_tables=torch.randint(-1, 900, (B, W), generator=g, dtype=torch.int32),
+                         temperatures=torch.tensor([0.0, 0.7, 1.0, 0.0, 1.3]), context_lens=torch.randint(1, 4000, (B,), generator=g, dtype=torch.int32))
+        driver.post(TPMethod.EXECUTE, (inp,))
+        assert int(seg.words[control.PAYLOAD_KIND_WORD]) == control.PAYLOAD_DECODE
+        seq, method, (got,) = worker.wait_command()
+        assert method == "execute" and got.kind == "decode" and got.num_seqs == B
+        for name in ("input_ids", "positions", "slots", "block_tables", "temperatures", "context_lens"):
+            a, b = getattr(inp, name), getattr(got, name)
+            assert a.dtype == b.dtype and a.shape == b.shape and torch.equal(a, b), name
+        worker.acknowledge(seq, [1, 2, 3])
+        assert driver.collect("execute", seq) == [[1, 2, 3]]
+        seg.payload(64)[:] = bytes(64)                      # the next command overwrites the area
+        assert torch.equal(got.input_ids, inp.input_ids)
+        # a prefill step and a non-StepInputs argument use the pickle form
+        pre = StepInputs(kind="prefill", input_ids=torch.arange(4), positions=torch.zeros(3, 4, dtype=torch.int32), slots=torch.arange(4),
+                         block_tables=torch.zeros(1, 2, dtype=torch.int32), temperatures=torch.zeros(1), cu_seqlens_q=torch.tensor([0, 4], dtype=torch.int32),
+                         kv_lens=torch.tensor([4], dtype=torch.int32), max_q_len=4)
+        driver.post(TPMethod.EXECUTE, (pre,))
+        assert int(seg.words[control.PAYLOAD_KIND_WORD]) == control.PAYLOAD_PICKLE
+        seq, method, (got,) = worker.wait_command()
+        assert got.kind == "prefill" and torch.equal(got.cu_seqlens_q, pre.cu_seqlens_q)
+        worker.acknowledge(seq)
+        driver.collect("execute", seq)
+        # unexpected dtype: falls back rather than reinterpreting bytes
+        odd = StepInputs(kind="decode", input_ids=inp.input_ids.to(torch.int32), positions=inp.positions, slots=inp.slots, block_tables=inp.block_tables,
+                         temperatures=inp.temperatures, context_lens=inp.context_lens)
+        assert odd.pack_decode(seg.payload(1 << 16)) == 0 and inp.pack_decode(seg.payload(32)) == 0
+    finally:
+        seg.close()
