@@ -284,6 +284,8 @@ class ControlWorker:
                     return
                 TPMethod(method)  # whitelist check
                 value = getattr(runner, method)(*args)
+                if method == TPMethod.EXECUTE.value:
+                    value = None  # every rank samples the same tokens; the driver keeps its own copy
             except BaseException as exc:  # noqa: BLE001 - forwarded to the driver
                 self.acknowledge(seq, error=exc)
                 return
