@@ -394,13 +394,19 @@ class Config:
         self.num_cpu_blocks = 0
 
     # flat read access used across the engine ------------------------------------
+    _flat_domain: dict[str, str] = {}  # field name -> domain, resolved once (the step loop reads flat names)
+
     def __getattr__(self, name: str) -> Any:
         prism = self.__dict__.get("prism")
         if prism is not None:
-            for dom in ("model", "cache", "scheduler", "multimodal", "execution", "quantization", "serving"):
-                d = getattr(prism, dom)
-                if name in {f.name for f in fields(d)}:
-                    return getattr(d, name)
+            dom = Config._flat_domain.get(name)
+            if dom is None:
+                for cand in ("model", "cache", "scheduler", "multimodal", "execution", "quantization", "serving"):
+                    if name in {f.name for f in fields(getattr(prism, cand))}:
+                        dom = Config._flat_domain[name] = cand
+                        break
+            if dom is not None:
+                return getattr(getattr(prism, dom), name)
         raise AttributeError(name)
 
     @property
