@@ -87,6 +87,10 @@ class LLMEngine:
                                         video_max_pixels=cfg.video_max_pixels)
         self._ids = RequestIdAllocator()
         self.metrics = EngineMetrics()
+        # CUDA engines keep a request's patches as pinned bf16 (the model's dtype): the copy to the
+        # device is then one asynchronous DMA of half the bytes instead of a staged pageable fp32
+        # copy plus a cast, and tensor-parallel workers receive half the bytes as well
+        self._stage_pixels = torch.cuda.is_available() and (device is None or str(device).startswith("cuda"))
         self._closed = False
         if runner_group is not None:
             self.runners = runner_group
@@ -151,21 +155,32 @@ class LLMEngine:
                        video_token_id=self.arch.video_token_id)
         return self._submit(seq, raise_on_reject=raise_on_reject)
 
+    def stage_pixels(self, pixels: torch.Tensor | None) -> torch.Tensor | None:
+        """Patches in the form the runner copies from (pinned bf16 on CUDA engines, unchanged
+        elsewhere).  Callers that preprocess ahead of submission (the online session's background
+        thread) can call this themselves; an already staged tensor passes through."""
+        if not self._stage_pixels or pixels is None or (pixels.dtype == torch.bfloat16 and pixels.is_pinned()):
+            return pixels
+        staged = torch.empty(pixels.shape, dtype=torch.bfloat16, pin_memory=True)
+        staged.copy_(pixels)
+        return staged
+
     def _multimodal_sequence(self, inputs: ImageInputs | VideoInputs, sp: SamplingParams | None,
                              media_key: str | None = None) -> Sequence:
         arch = self.arch
         image_grid = getattr(inputs, "image_grid_thw", None)
         video_grid = getattr(inputs, "video_grid_thw", None)
         inputs.validate(arch)
+        pixels = self.stage_pixels(inputs.pixel_values)
         pos, delta = rope_index(inputs.input_ids, image_grid_thw=image_grid, video_grid_thw=video_grid,
                                 image_token_id=arch.image_token_id, video_token_id=arch.video_token_id,
                                 spatial_merge_size=arch.vision.spatial_merge_size)
         seq = Sequence(self._ids(), inputs.input_ids, self._sampling(sp), image_token_id=arch.image_token_id,
-                       video_token_id=arch.video_token_id, pixel_values=inputs.pixel_values,
+                       video_token_id=arch.video_token_id, pixel_values=pixels,
                        image_grid_thw=image_grid, video_grid_thw=video_grid, position_ids=pos[:, 0, :],
                        rope_delta=delta, merge_size=arch.vision.spatial_merge_size)
         if self.config.enable_prefix_caching or self.config.enable_visual_embedding_cache:
-            key = media_key or content_key(inputs.pixel_values, image_grid, video_grid)
+            key = media_key or content_key(pixels, image_grid, video_grid)
             seq.visual_embedding_cache_key = key
             if self.config.enable_prefix_caching:
                 seq.multimodal_prefix_cache_key = key

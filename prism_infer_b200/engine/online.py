@@ -184,6 +184,12 @@ class OnlineServingSession:
         self._patch_cache.put(key, out)
         return key, out
 
+    def _stage(self, pixels: torch.Tensor) -> torch.Tensor:
+        """Patches of a cached layout in the form the runner copies from (pinned bf16 on CUDA
+        engines): converted once here, off the submission path, and reused by every later hit."""
+        stage = getattr(self.engine, "stage_pixels", None)
+        return stage(pixels) if stage is not None else pixels
+
     def prepare_media(self, payload: dict[str, Any]) -> tuple[ImageInputs | VideoInputs, str]:
         """Processor output for a media payload plus its content key, through the caches."""
         arch, tok = self.engine.arch, self.engine.tokenizer
@@ -195,7 +201,7 @@ class OnlineServingSession:
             layout = self._layout_cache.get_refresh(key)
             if layout is None:
                 self.counters["layout_misses"] += 1
-                layout = (video_blocks(arch, grid, arch.vision.merge_unit), pv, [grid])
+                layout = (video_blocks(arch, grid, arch.vision.merge_unit), self._stage(pv), [grid])
                 self._layout_cache.put(key, layout)
             else:
                 self.counters["layout_hits"] += 1
@@ -221,7 +227,7 @@ class OnlineServingSession:
                     if segments[i].strip():
                         ids += tok.encode(segments[i])
                     ids += image_block(arch, self.engine.processor.tokens_for(grid))
-                layout = (ids, torch.cat([pv for _, (pv, _) in parts]), [g for _, (_, g) in parts])
+                layout = (ids, self._stage(torch.cat([pv for _, (pv, _) in parts])), [g for _, (_, g) in parts])
                 self._layout_cache.put(lkey, layout)
             else:
                 self.counters["layout_hits"] += 1
@@ -235,7 +241,7 @@ class OnlineServingSession:
             ids = []
             for _, (pv, grid) in parts:
                 ids += image_block(arch, self.engine.processor.tokens_for(grid))
-            layout = (ids, torch.cat([pv for _, (pv, _) in parts]), [g for _, (_, g) in parts])
+            layout = (ids, self._stage(torch.cat([pv for _, (pv, _) in parts])), [g for _, (_, g) in parts])
             self._layout_cache.put(key, layout)
         else:
             self.counters["layout_hits"] += 1
