@@ -215,17 +215,75 @@ class ModelRunner:
             main, deep = self.model.encode_vision(job.pixel_values, job.grid_thw)
         if key is not None:
             self.visual_cache_counters["misses"] += 1
-            size = (1 + len(deep)) * main.numel() * main.element_size()
-            budget = self.config.visual_embedding_cache_bytes
-            while self._visual_cache and self._visual_cache_bytes + size > budget:
-                _, (m, d) = next(iter(self._visual_cache.items()))
-                self._visual_cache_bytes -= (1 + len(d)) * m.numel() * m.element_size()
-                self._visual_cache.pop(next(iter(self._visual_cache)))
-                self.visual_cache_counters["evictions"] += 1
-            if size <= budget:
-                self._visual_cache[key] = (main, deep)
-                self._visual_cache_bytes += size
+            self._cache_visual(key, (main, deep))
         return main, deep
+
+    def _cache_visual(self, key: str, value: tuple[torch.Tensor, list[torch.Tensor]]) -> None:
+        """LRU insertion under the byte budget; an entry larger than the budget is not kept."""
+        if key in self._visual_cache:
+            return
+        main, deep = value
+        size = (1 + len(deep)) * main.numel() * main.element_size()
+        budget = self.config.visual_embedding_cache_bytes
+        while self._visual_cache and self._visual_cache_bytes + size > budget:
+            _, (m, d) = next(iter(self._visual_cache.items()))
+            self._visual_cache_bytes -= (1 + len(d)) * m.numel() * m.element_size()
+            self._visual_cache.pop(next(iter(self._visual_cache)))
+            self.visual_cache_counters["evictions"] += 1
+        if size <= budget:
+            self._visual_cache[key] = value
+            self._visual_cache_bytes += size
+
+    def _encode_jobs(self, jobs) -> None:
+        """Vision tower for the sequences of one prefill step.  Jobs that miss the embedding cache
+        are pushed through the tower together, up to ``vision_encoder_microbatch_patches`` patches
+        per pass (reference ``models/qwen3_vl.py:1233-1281`` microbatches on frame boundaries): a
+        pass over one 448 x 448 image is launch-bound, so a prefill batch of many single-image
+        requests would otherwise pay the tower's ~300 launches once per request.  A single job is
+        never split.  Attention is per image segment and every other op is per patch, so each
+        job's rows are what a pass of its own would produce."""
+        use_cache = self.config.enable_visual_embedding_cache
+        pending = []
+        for job in jobs:
+            if use_cache and job.cache_key is not None and job.cache_key in self._visual_cache:
+                self._visual[job.seq_id] = self._encode(job)  # cache hit: no tower work
+            else:
+                pending.append(job)
+        budget = self.config.vision_encoder_microbatch_patches
+        group: list = []
+        patches = 0
+        for job in pending:
+            n = int(job.pixel_values.shape[0])
+            if group and patches + n > budget:
+                self._encode_group(group)
+                group, patches = [], 0
+            group.append(job)
+            patches += n
+        if group:
+            self._encode_group(group)
+
+    def _encode_group(self, group) -> None:
+        if len(group) == 1:
+            self._visual[group[0].seq_id] = self._encode(group[0])
+            return
+        unit = self.config.arch.vision.merge_unit
+        if self.on_cuda and self.comm.size == 1:  # each job's pinned patches travel as their own asynchronous copy
+            # (tensor-parallel ranks copy only the rows of their own shard, from the host tensor)
+            pixels = torch.cat([j.pixel_values.to(device=self.device, dtype=self.dtype, non_blocking=True) for j in group])
+        else:
+            pixels = torch.cat([j.pixel_values for j in group])
+        grids = [g for j in group for g in j.grid_thw]
+        with profile_region("model.vision.encoder", metadata={"jobs": len(group)}):
+            main, deep = self.model.encode_vision(pixels, grids)
+        row = 0
+        for job in group:
+            n = sum(int(t) * int(h) * int(w) for t, h, w in job.grid_thw) // unit
+            result = (main[row:row + n].clone(), [d[row:row + n].clone() for d in deep])  # own storage: the batch can be freed
+            row += n
+            self._visual[job.seq_id] = result
+            if self.config.enable_visual_embedding_cache and job.cache_key is not None:
+                self.visual_cache_counters["misses"] += 1
+                self._cache_visual(job.cache_key, result)
 
     def encode_for_sequence(self, job) -> None:
         """Vision tower for one sequence, kept until its prefill consumes it."""
@@ -264,8 +322,7 @@ class ModelRunner:
 
     def _run_prefill(self, inp: StepInputs) -> list[int]:
         with profile_region("runner.prepare_inputs"):
-            for job in inp.vision_jobs:
-                self._visual[job.seq_id] = self._encode(job)
+            self._encode_jobs(inp.vision_jobs)
             visual = deep = None
             if inp.vision_rows:
                 mains, deeps = [], None

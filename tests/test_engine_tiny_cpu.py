@@ -219,3 +219,39 @@ def test_dense_prefix_is_published_without_an_extra_prefill_step(tiny):
     assert r1["token_ids"] == oracle.generate_greedy(a.input_ids, 3, pixel_values=a.pixel_values, image_grid_thw=a.image_grid_thw)
     assert r2["token_ids"] == oracle.generate_greedy(b.input_ids, 3, pixel_values=b.pixel_values, image_grid_thw=b.image_grid_thw)
     off.exit()
+
+
+def test_vision_jobs_of_one_prefill_step_share_tower_passes(tiny):
+    """Five single-image requests prefilled in one step: the tower runs once per microbatch of
+    patches, not once per request, and every request still matches the oracle; with the
+    embedding cache on, the batched results are stored per request and reused."""
+    arch, weights, oracle = tiny
+    tok = load_tokenizer("random:tiny", arch)
+    sp = SamplingParams(temperature=0.0, max_tokens=3, ignore_eos=True)
+    proc = PatchProcessor(arch)
+    inputs = [prepare_image_inputs(proc, tok, [30 + i, 31 + i, 32], [_image(60 + i, 64 if i % 2 else 96)]) for i in range(5)]
+    want = [oracle.generate_greedy(x.input_ids, 3, pixel_values=x.pixel_values, image_grid_thw=x.image_grid_thw) for x in inputs]
+
+    def run(**kw):
+        llm = _llm(weights, max_num_seqs=8, enable_prefix_caching=False, **kw)
+        model = llm.runners.runner.model
+        calls = []
+        real = model.encode_vision
+        model.encode_vision = lambda pixels, grids: (calls.append((int(pixels.shape[0]), len(grids))), real(pixels, grids))[1]
+        ids = [llm.add_prepared_image_request(x, sp) for x in inputs]
+        got = llm._run_until_done(ids)
+        return llm, calls, [got[i] for i in ids]
+
+    llm, calls, got = run()
+    assert got == want and len(calls) == 1 and calls[0] == (sum(int(x.pixel_values.shape[0]) for x in inputs), 5)
+    llm.exit()
+    llm, calls, got = run(vision_encoder_microbatch_patches=60, max_vision_patches_per_batch=8192)   # 36- and 16-patch images alternate: two per pass
+    assert got == want and len(calls) == 3 and all(p <= 52 for p, _ in calls)
+    llm.exit()
+    llm, calls, got = run(enable_visual_embedding_cache=True)
+    assert got == want
+    meta = llm.visual_embedding_cache_metadata()
+    assert meta["misses"] == 5 and meta["entries"] == 5 and len(calls) == 5   # hydrated one by one at submission
+    again = llm.generate_prepared_image_inputs(inputs[2], sp)
+    assert again["token_ids"] == want[2] and llm.visual_embedding_cache_metadata()["hits"] >= 1 and len(calls) == 5
+    llm.exit()
