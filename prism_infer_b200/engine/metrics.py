@@ -5,6 +5,7 @@ patches / duration / compactions."""
 
 from __future__ import annotations
 
+import collections
 import threading
 import time
 from dataclasses import dataclass, field
@@ -41,11 +42,16 @@ class RequestMetrics:
 
 
 class EngineMetrics:
-    def __init__(self, clock_ns: Callable[[], int] = time.perf_counter_ns) -> None:
+    """``max_records`` bounds the ledger of a long-running server: the oldest batch records and
+    the oldest request records are dropped beyond it (a decode step adds a batch record every few
+    milliseconds).  Benchmarks reset the ledger between phases and never reach the bound."""
+
+    def __init__(self, clock_ns: Callable[[], int] = time.perf_counter_ns, max_records: int = 200_000) -> None:
         self._clock = clock_ns
         self._lock = threading.Lock()
+        self.max_records = max_records
         self.requests: dict[int, RequestMetrics] = {}
-        self.batches: list[dict[str, object]] = []
+        self.batches: collections.deque[dict[str, object]] = collections.deque(maxlen=max_records)
 
     def reset(self) -> None:
         with self._lock:
@@ -56,6 +62,8 @@ class EngineMetrics:
         with self._lock:
             t = seq.arrival_ns if seq.arrival_ns is not None else self._clock()
             self.requests[seq.seq_id] = RequestMetrics(seq.seq_id, seq.num_prompt_tokens, t)
+            while len(self.requests) > self.max_records:
+                self.requests.pop(next(iter(self.requests)))  # insertion order: the oldest request
 
     def on_request_scheduled(self, seq: Sequence) -> None:
         with self._lock:

@@ -354,3 +354,38 @@ def test_batch_plan_contract():
     with pytest.raises(ValueError):
         BatchPlan(Phase.PREFILL, (text_seq(1, 3),), ())
     assert BatchPlan(Phase.IDLE).is_idle and chain_hash([1, 2], None) != chain_hash([1, 2], 5)
+
+
+def test_engine_metrics_ledger_is_bounded_and_times_tokens():
+    """Per-request TTFT / TPOT from an injected clock, and the ledger bound of a long-running
+    server: the oldest request and batch records are dropped, the newest kept."""
+    from prism_infer_b200.engine.contracts import BatchPlan, Phase
+    from prism_infer_b200.engine.metrics import EngineMetrics
+    from prism_infer_b200.engine.sequence import Sequence
+    from prism_infer_b200.sampling_params import SamplingParams
+
+    now = [0]
+    m = EngineMetrics(clock_ns=lambda: now[0], max_records=3)
+    seqs = [Sequence(i, [1, 2, 3], SamplingParams(max_tokens=4)) for i in range(5)]
+    for i, s in enumerate(seqs):
+        now[0] = i * 1_000_000
+        m.on_request_submitted(s)
+    assert list(m.requests) == [2, 3, 4]
+    s = seqs[4]
+    now[0] = 10_000_000
+    m.on_request_scheduled(s)
+    now[0] = 14_000_000
+    m.on_tokens(s)                                   # first token 10 ms after arrival (arrival at 4 ms)
+    for k in range(3):
+        now[0] += 2_000_000
+        m.on_tokens(s)
+    m.on_request_finished(s)
+    rec = [r for r in m.snapshot()["requests"] if r["request_id"] == 4][0]
+    assert rec["ttft_ms"] == 10.0 and rec["tpot_ms"] == 2.0 and rec["output_tokens"] == 4 and rec["queue_ms"] == 6.0
+    m.on_tokens(seqs[0])                             # a dropped request: ignored
+    for k in range(7):
+        m.on_batch_completed(BatchPlan(Phase.DECODE, (s,), (), num_tokens=1), float(k))
+    batches = m.snapshot()["batches"]
+    assert [b["duration_ms"] for b in batches] == [4.0, 5.0, 6.0]
+    m.reset()
+    assert m.snapshot() == {"requests": [], "batches": []}
