@@ -255,3 +255,52 @@ def test_vision_jobs_of_one_prefill_step_share_tower_passes(tiny):
     again = llm.generate_prepared_image_inputs(inputs[2], sp)
     assert again["token_ids"] == want[2] and llm.visual_embedding_cache_metadata()["hits"] >= 1 and len(calls) == 5
     llm.exit()
+
+
+@pytest.mark.parametrize("cpu_ratio,counter", [(1.0, "preempt_swap"), (0.0, "preempt_recompute")])
+def test_preempted_requests_still_match_the_oracle(tiny, cpu_ratio, counter):
+    """Nine pages for three requests that each grow to four: one of them is preempted during
+    decode - swapped to CPU pages and back, or dropped and recomputed - and every request still
+    produces the oracle's tokens."""
+    arch, weights, oracle = tiny
+    llm = _llm(weights, num_kvcache_blocks=9, cpu_kv_cache_ratio=cpu_ratio, enable_prefix_caching=False, compression_mode="off")
+    g = torch.Generator().manual_seed(1)
+    prompts = [torch.randint(0, 1000, (20,), generator=g).tolist() for _ in range(3)]
+    outs = llm.generate(prompts, SamplingParams(temperature=0.0, max_tokens=40, ignore_eos=True))
+    assert [o["token_ids"] for o in outs] == [oracle.generate_greedy(p, 40) for p in prompts]
+    sched = llm.metrics_snapshot()["scheduler"]
+    assert sched[counter] >= 1 and sched["finished"] == 3 and sched["free_gpu_pages"] == 9
+    if cpu_ratio:
+        assert sched["swap_in"] == sched["preempt_swap"] and sched["free_cpu_pages"] == 9
+    llm.exit()
+
+
+def test_mixed_batch_of_text_image_and_video_matches_the_oracle(tiny):
+    """One ``generate_mixed`` call with a text, an image, a two-image and a video request: every
+    row equals the oracle run alone (fp32 on CPU is batch-invariant), results keep request order,
+    and a per-request ``sampling_params`` overrides the shared one."""
+    arch, weights, oracle = tiny
+    tok = load_tokenizer("random:tiny", arch)
+    proc = PatchProcessor(arch)
+    frames = [_image(70 + i, 64) for i in range(4)]
+    img_a, img_b = _image(80, 64), _image(81, 96)
+    reqs = [
+        {"type": "text", "prompt": [5, 6, 7, 8, 9]},
+        {"type": "image", "prompt": [11, 12], "image": img_a},
+        {"type": "images", "prompt": [13, 14, 15], "images": [img_a, img_b]},
+        {"type": "video", "prompt": [16], "frames": frames, "sampling_params": SamplingParams(temperature=0.0, max_tokens=2, ignore_eos=True)},
+    ]
+    llm = _llm(weights, max_num_seqs=8)
+    outs = llm.generate_mixed(reqs, SamplingParams(temperature=0.0, max_tokens=5, ignore_eos=True))
+    assert [len(o["token_ids"]) for o in outs] == [5, 5, 5, 2]
+    assert outs[0]["token_ids"] == oracle.generate_greedy([5, 6, 7, 8, 9], 5)
+    one = prepare_image_inputs(proc, tok, [11, 12], [img_a])
+    assert outs[1]["token_ids"] == oracle.generate_greedy(one.input_ids, 5, pixel_values=one.pixel_values, image_grid_thw=one.image_grid_thw)
+    two = prepare_image_inputs(proc, tok, [13, 14, 15], [img_a, img_b])
+    assert outs[2]["token_ids"] == oracle.generate_greedy(two.input_ids, 5, pixel_values=two.pixel_values, image_grid_thw=two.image_grid_thw)
+    vid = prepare_video_inputs(proc, tok, [16], frames)
+    assert outs[3]["token_ids"] == oracle.generate_greedy(vid.input_ids, 2, pixel_values=vid.pixel_values, video_grid_thw=vid.video_grid_thw)
+    assert all(set(o) == {"text", "raw_text", "token_ids"} and isinstance(o["text"], str) for o in outs)
+    with pytest.raises(ValueError, match="unknown request type"):
+        llm.generate_mixed([{"type": "audio", "prompt": [1]}], None)
+    llm.exit()
