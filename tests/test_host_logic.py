@@ -389,3 +389,109 @@ def test_engine_metrics_ledger_is_bounded_and_times_tokens():
     assert [b["duration_ms"] for b in batches] == [4.0, 5.0, 6.0]
     m.reset()
     assert m.snapshot() == {"requests": [], "batches": []}
+
+
+def _check_page_invariants(sched):
+    """Every GPU page's reference count equals the number of owners that name it (block tables of
+    live sequences + multimodal prefix entries); free + used = total; no page is both free and
+    referenced; CPU pages are owned exactly by the swapped sequences."""
+    bm = sched.block_manager
+    owners: dict[int, int] = {}
+    live = list(sched.running) + list(sched.waiting) + list(sched.swapped)
+    for s in live:
+        for p in s.block_table:
+            owners[p] = owners.get(p, 0) + 1
+    for e in bm.entries.values():
+        for p in e.pages:
+            owners[p] = owners.get(p, 0) + 1
+    free = set(bm.gpu.free)
+    assert len(free) == len(bm.gpu.free), "a page is on the free list twice"
+    for blk in bm.gpu.blocks:
+        want = owners.get(blk.block_id, 0)
+        if blk.block_id in free:
+            assert want == 0, f"page {blk.block_id} is free but referenced {want}x"
+        else:
+            assert blk.ref_count == want, f"page {blk.block_id}: ref_count {blk.ref_count}, owners {want}"
+    assert bm.gpu.num_free + len(owners) == bm.gpu.num_blocks
+    cpu_owned = sum(len(getattr(s, "cpu_block_table", []) or []) for s in sched.swapped)
+    assert bm.cpu.num_blocks - bm.cpu.num_free == cpu_owned
+    for s in sched.running:
+        assert s.state in (RequestState.PREFILLING, RequestState.DECODING)
+    for s in sched.swapped:
+        assert s.state is RequestState.SWAPPED and not s.block_table
+
+
+@pytest.mark.parametrize("seed", range(6))
+@pytest.mark.parametrize("cpu_blocks", [0, 12])
+def test_random_traffic_keeps_page_accounting_exact(seed, cpu_blocks):
+    """Random arrivals (text with shared prefixes, multimodal with repeated media), random
+    cancellations and random tokens (EOS included) on a pool small enough to force preemption,
+    swapping, prefix eviction and copy-on-write: the page accounting holds after every step
+    and every page is free at the end."""
+    import random
+
+    rng = random.Random(seed)
+    sched = Scheduler(cfg(num_kvcache_blocks=14, num_cpu_blocks=cpu_blocks, max_num_seqs=5, max_num_batched_tokens=48,
+                          compacts_visual_tokens=False))
+    next_id = 0
+    submitted = 0
+    for step in range(400):
+        if submitted < 60 and rng.random() < 0.45:
+            next_id += 1
+            submitted += 1
+            if rng.random() < 0.5:
+                seq = text_seq(next_id, rng.randint(3, 22), max_tokens=rng.randint(1, 12), base=rng.choice([10, 10, 50]))
+            else:
+                seq = mm_seq(next_id, rng.choice([4, 8]), [rng.randint(1, 800) for _ in range(rng.randint(1, 5))],
+                             key=rng.choice(["media-A", "media-B", "media-C"]), max_tokens=rng.randint(1, 10))
+            sched.add(seq)
+        if rng.random() < 0.08:
+            live = list(sched.running) + list(sched.waiting) + list(sched.swapped)
+            if live:
+                sched.cancel(rng.choice(live).seq_id)
+        plan = sched.schedule()
+        if not plan.is_idle:
+            toks = [EOS if rng.random() < 0.05 else rng.randint(1, 800) for _ in range(plan.batch_size)]
+            if plan.phase is Phase.PREFILL:  # what the executor does after a prefill: publish crossed prefixes
+                outs = None
+                for seq, sl in zip(plan.seqs, plan.slices):
+                    b = seq.multimodal_prefix_boundary if seq.is_multimodal else 0
+                    if b > 0 and sl.start < b <= sl.end and seq.multimodal_prefix_cache_key:
+                        seq.num_computed_tokens += sl.length
+                        try:
+                            sched.block_manager.store_multimodal_prefix(seq)
+                        finally:
+                            seq.num_computed_tokens -= sl.length
+            sched.postprocess(plan, toks)
+        _check_page_invariants(sched)
+        if submitted >= 60 and sched.is_finished():
+            break
+    for _ in range(300):  # drain
+        if sched.is_finished():
+            break
+        plan = sched.schedule()
+        if not plan.is_idle:
+            sched.postprocess(plan, [EOS] * plan.batch_size)
+        _check_page_invariants(sched)
+    assert sched.is_finished()
+    bm = sched.block_manager
+    held = sum(len(e.pages) for e in bm.entries.values())
+    assert bm.gpu.num_free + held == bm.gpu.num_blocks and bm.cpu.num_free == bm.cpu.num_blocks
+    TRAFFIC_COUNTERS.append((dict(sched.counters), dict(bm.counters.snapshot())))
+
+
+TRAFFIC_COUNTERS: list = []
+
+
+def test_random_traffic_reached_the_interesting_paths():
+    """The runs above, taken together, preempted by swap and by recompute, swapped back in,
+    hit and evicted multimodal prefixes, and finished and cancelled requests."""
+    if len(TRAFFIC_COUNTERS) < 12:
+        pytest.skip("runs only after the whole random-traffic matrix")
+    total: dict[str, int] = {}
+    for sched_c, prefix_c in TRAFFIC_COUNTERS:
+        for k, v in {**sched_c, **prefix_c}.items():
+            if isinstance(v, int):
+                total[k] = total.get(k, 0) + v
+    for key in ("preempt_swap", "preempt_recompute", "swap_in", "finished", "cancelled", "hits", "stores", "evictions"):
+        assert total.get(key, 0) > 0, (key, total)
