@@ -304,3 +304,46 @@ def test_mixed_batch_of_text_image_and_video_matches_the_oracle(tiny):
     with pytest.raises(ValueError, match="unknown request type"):
         llm.generate_mixed([{"type": "audio", "prompt": [1]}], None)
     llm.exit()
+
+
+def test_output_decoding_and_eos_with_a_scripted_runner():
+    """The engine on a runner that returns scripted tokens: generation stops at EOS unless
+    ``ignore_eos``; ``text`` drops special tokens, ``raw_text`` keeps them; string prompts go
+    through the tokenizer; ``step`` reports signed token counts (prefill +, decode -)."""
+    arch = Qwen3VLArch.tiny()
+    eos = arch.eos_token_id
+
+    class ScriptedRunners:
+        is_driver = True
+
+        def __init__(self, script):
+            self.script, self.calls = list(script), []
+
+        def call(self, method, *args):
+            self.calls.append(method)
+            if method == "execute":
+                inp = args[0]
+                n = inp.num_seqs if inp.kind == "decode" else len(inp.sample_seq)
+                return [self.script.pop(0) for _ in range(n)]
+            if method == "capacity":
+                return (64, 0)
+            return None
+
+        def close(self):
+            self.calls.append("close")
+
+    opts = dict(max_model_len=512, kvcache_block_size=16, num_kvcache_blocks=64, enforce_eager=True, max_num_batched_tokens=512, max_chunk_size=512)
+    runners = ScriptedRunners([17, 23, eos, 99, 99])
+    llm = LLM("random:tiny", runner_group=runners, device="cpu", **opts)
+    out = llm.generate(["12 13 hello"], SamplingParams(temperature=0.0, max_tokens=8))[0]
+    assert out["token_ids"] == [17, 23, eos] and out["text"] == "17 23" and out["raw_text"] == f"17 23 {eos}"
+    assert runners.script == [99, 99]                               # nothing ran past the EOS
+    rid = llm.add_request([5, 6, 7], SamplingParams(temperature=0.0, max_tokens=2, ignore_eos=True))
+    runners.script[:] = [eos, eos]
+    done, signed = llm.step()
+    assert done == [] and signed == 3                               # prefill of three tokens
+    done, signed = llm.step()
+    assert signed == -1 and done == [(rid, [eos, eos])]             # EOS ignored: ran to max_tokens
+    assert llm.is_finished() and llm.request_state(rid) is None
+    llm.exit()
+    assert runners.calls[-1] == "close"
