@@ -17,6 +17,7 @@ from __future__ import annotations
 
 from typing import Sequence
 
+import numpy as np
 import torch
 
 
@@ -34,8 +35,8 @@ def rope_index(
     ``rope_delta = max(position) + 1 - S``; a decode step at sequence length ``n``
     uses position ``n - 1 + rope_delta`` on all three axes.
     """
-    ids = [int(t) for t in (input_ids.tolist() if isinstance(input_ids, torch.Tensor) else input_ids)]
-    n = len(ids)
+    ids = np.asarray(input_ids.tolist() if isinstance(input_ids, torch.Tensor) else input_ids, dtype=np.int64).reshape(-1)
+    n = int(ids.shape[0])
 
     def _rows(grid) -> list[tuple[int, int, int]]:
         if grid is None:
@@ -47,20 +48,28 @@ def rope_index(
     # A video of T temporal groups is T consecutive single-frame spans.
     video_rows = [(1, h, w) for (t, h, w) in _rows(video_grid_thw) for _ in range(t)]
 
-    pos = torch.empty((3, n), dtype=torch.int64)
+    pos = np.empty((3, n), dtype=np.int64)
     if not image_rows and not video_rows:
-        ar = torch.arange(n, dtype=torch.int64)
-        pos[:] = ar
-        return pos.view(3, 1, n), 0
+        pos[:] = np.arange(n, dtype=np.int64)
+        return torch.from_numpy(pos).view(3, 1, n), 0
 
+    # maximal runs of equal "kind" (0 text, 1 image placeholder, 2 video placeholder); a placeholder
+    # run may hold several grids back to back, so it is consumed grid by grid below
+    kind = np.where(ids == image_token_id, 1, np.where(ids == video_token_id, 2, 0))
+    starts = np.flatnonzero(np.diff(kind, prepend=-1)).tolist() if n else []
+    ends = starts[1:] + [n]
     cursor = 0  # next position value
-    i = 0
     img_i = vid_i = 0
     m = spatial_merge_size
-    while i < n:
-        tok = ids[i]
-        if tok == image_token_id or tok == video_token_id:
-            if tok == image_token_id:
+    for lo, hi in zip(starts, ends):
+        k = int(kind[lo])
+        if k == 0:
+            pos[:, lo:hi] = np.arange(cursor, cursor + hi - lo, dtype=np.int64)
+            cursor += hi - lo
+            continue
+        i = lo
+        while i < hi:
+            if k == 1:
                 if img_i >= len(image_rows):
                     raise ValueError("more image placeholder runs than image_grid_thw rows")
                 t, h, w = image_rows[img_i]
@@ -72,30 +81,16 @@ def rope_index(
                 vid_i += 1
             gh, gw = h // m, w // m
             span = t * gh * gw
-            if i + span > n or any(ids[i + k] != tok for k in range(span)):
-                raise ValueError(
-                    f"placeholder run at {i} is shorter than its grid ({t}x{gh}x{gw} = {span})"
-                )
-            t_idx = torch.arange(t, dtype=torch.int64).view(t, 1, 1).expand(t, gh, gw).reshape(-1)
-            h_idx = torch.arange(gh, dtype=torch.int64).view(1, gh, 1).expand(t, gh, gw).reshape(-1)
-            w_idx = torch.arange(gw, dtype=torch.int64).view(1, 1, gw).expand(t, gh, gw).reshape(-1)
-            pos[0, i : i + span] = t_idx + cursor
-            pos[1, i : i + span] = h_idx + cursor
-            pos[2, i : i + span] = w_idx + cursor
+            if i + span > hi:
+                raise ValueError(f"placeholder run at {i} is shorter than its grid ({t}x{gh}x{gw} = {span})")
+            grid = np.indices((t, gh, gw), dtype=np.int64).reshape(3, span)
+            pos[:, i:i + span] = grid + cursor
             cursor += max(t, gh, gw)
             i += span
-        else:
-            j = i
-            while j < n and ids[j] != image_token_id and ids[j] != video_token_id:
-                j += 1
-            ar = torch.arange(j - i, dtype=torch.int64) + cursor
-            pos[:, i:j] = ar
-            cursor += j - i
-            i = j
     if img_i != len(image_rows) or vid_i != len(video_rows):
         raise ValueError("fewer placeholder runs than grid rows")
-    delta = int(pos.max().item()) + 1 - n
-    return pos.view(3, 1, n), delta
+    delta = int(pos.max()) + 1 - n
+    return torch.from_numpy(pos).view(3, 1, n), delta
 
 
 def mrope_axis_table(section: Sequence[int], half_dim: int) -> torch.Tensor:
