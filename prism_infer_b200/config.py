@@ -187,6 +187,7 @@ class ExecutionConfig:
     cooperative_prefill_vision_block_quantum: int = 4
     programmatic_dependent_launch: bool = True
     decode_multi_step: int = 1
+    device_status_check_interval: int = 256   # engine steps between reads of the kernels' status words (0 = never)
 
     def __post_init__(self) -> None:
         if self.backend not in BACKENDS:
@@ -201,6 +202,7 @@ class ExecutionConfig:
         _int(self.cooperative_prefill_layer_quantum, "cooperative_prefill_layer_quantum", 1)
         _int(self.cooperative_prefill_vision_block_quantum, "cooperative_prefill_vision_block_quantum", 1)
         _int(self.decode_multi_step, "decode_multi_step", 1)
+        _int(self.device_status_check_interval, "device_status_check_interval", 0)
 
     @property
     def uses_graphs(self) -> bool:
@@ -283,6 +285,7 @@ _FLAT = {
         "cooperative_prefill_vision_block_quantum": "cooperative_prefill_vision_block_quantum",
         "enable_programmatic_dependent_launch": "programmatic_dependent_launch",
         "decode_multi_step": "decode_multi_step",
+        "device_status_check_interval": "device_status_check_interval",
     },
 }
 _CONTROL = {"enforce_eager", "execution_backend"}

@@ -111,6 +111,7 @@ class LLMEngine:
         self._cooperative_pending = False
         self._replan = None
         self.cooperative_counters = {"vision_quanta": 0}
+        self._steps_since_status = 0
         atexit.register(self.exit)
 
     # ------------------------------------------------------------------- lifecycle
@@ -243,6 +244,9 @@ class LLMEngine:
             profile_step_metadata({"phase": plan.phase.value, "batch_size": plan.batch_size, "tokens": plan.num_tokens,
                                    "vision_patches": plan.num_vision_patches})
             result = self.executor.execute(plan)
+            self._steps_since_status += 1
+            if 0 < self.config.device_status_check_interval <= self._steps_since_status:
+                self.check_device_status()
             if plan.is_idle:
                 return StepResult(Phase.IDLE)
             with profile_region("engine.scheduler.postprocess", cuda=False):
@@ -262,6 +266,19 @@ class LLMEngine:
 
     def is_finished(self) -> bool:
         return self.scheduler.is_finished()
+
+    def check_device_status(self) -> None:
+        """Read every rank's kernel status words (bounded waits that ran out, failed bounds checks;
+        kernels never trap, they record and carry on) and raise when one is set.  The step loop
+        calls this every ``device_status_check_interval`` steps, so a missing peer or a corrupt page
+        table surfaces as an engine failure - an ``ERROR`` event and an unhealthy ``/health`` under
+        ``prism-serve`` - instead of silently wrong tokens."""
+        self._steps_since_status = 0
+        answer = self.runners.call("status")
+        per_rank = answer if isinstance(answer, list) else [answer]
+        bad = {(rank, unit): words for rank, st in enumerate(per_rank) if st for unit, words in st.items() if words[0] != 0}
+        if bad:
+            raise RuntimeError(f"device status reports failures (rank, unit) -> (code, detail, block, count): {bad}")
 
     def cancel_request(self, request_id: int) -> bool:
         ok = self.scheduler.cancel(request_id)

@@ -180,8 +180,8 @@ class TensorParallelGroup:
             raise
         if local_error is not None:
             raise local_error
-        if method == TPMethod.TIME_DECODE_GRAPH.value:
-            return [value, *others]
+        if method in (TPMethod.TIME_DECODE_GRAPH.value, TPMethod.STATUS.value):
+            return [value, *others]  # per-rank answers
         return value
 
     def barrier(self) -> None:

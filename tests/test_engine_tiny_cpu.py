@@ -347,3 +347,44 @@ def test_output_decoding_and_eos_with_a_scripted_runner():
     assert llm.is_finished() and llm.request_state(rid) is None
     llm.exit()
     assert runners.calls[-1] == "close"
+
+
+def test_device_status_words_are_checked_on_a_cadence():
+    """Every ``device_status_check_interval`` steps the engine reads the ranks' status words; a
+    set word (here: rank 1 reports a peer wait that ran out) becomes an engine failure."""
+    class Runners:
+        is_driver = True
+
+        def __init__(self):
+            self.status_calls = 0
+            self.fail_from = 10 ** 9
+
+        def call(self, method, *args):
+            if method == "execute":
+                inp = args[0]
+                return [7] * (inp.num_seqs if inp.kind == "decode" else len(inp.sample_seq))
+            if method == "status":
+                self.status_calls += 1
+                healthy = {"gemm": (0, 0, 0, 0), "norm": (0, 0, 0, 0)}
+                return [healthy, dict(healthy, norm=(2, 5, 17, 3)) if self.status_calls >= self.fail_from else healthy]
+            return None
+
+        def close(self):
+            pass
+
+    opts = dict(max_model_len=512, kvcache_block_size=16, num_kvcache_blocks=64, enforce_eager=True, max_num_batched_tokens=512, max_chunk_size=512)
+    runners = Runners()
+    llm = LLM("random:tiny", runner_group=runners, device="cpu", device_status_check_interval=4, **opts)
+    llm.generate([[1, 2, 3]], SamplingParams(temperature=0.0, max_tokens=9, ignore_eos=True))
+    assert runners.status_calls == 2                       # 1 prefill + 8 decode steps
+    runners.fail_from = 3
+    with pytest.raises(RuntimeError, match="'norm'.: .2, 5, 17, 3"):
+        llm.generate([[1, 2, 3]], SamplingParams(temperature=0.0, max_tokens=9, ignore_eos=True))
+    llm.exit()
+    quiet = Runners()
+    llm = LLM("random:tiny", runner_group=quiet, device="cpu", device_status_check_interval=0, **opts)
+    llm.generate([[1, 2, 3]], SamplingParams(temperature=0.0, max_tokens=9, ignore_eos=True))
+    assert quiet.status_calls == 0
+    llm.exit()
+    with pytest.raises(ValueError):
+        LLM("random:tiny", runner_group=Runners(), device="cpu", device_status_check_interval=-1, **opts)
