@@ -333,16 +333,18 @@ class BlockManager:
         pages.  Returns ``None`` when nothing would be dropped."""
         if seq.kv_layout is not None:
             raise RuntimeError("sequence is already compacted")
-        if seq.num_computed_tokens != prefix_len:
-            raise RuntimeError("compaction must run exactly when the prefix has been computed")
+        if seq.num_computed_tokens < prefix_len:
+            raise RuntimeError("compaction must run after the prefix has been computed")
         if any(self.gpu.blocks[p].ref_count > 1 for p in seq.block_table):
             raise RuntimeError("cannot compact shared pages")
         layout = KVLayout(prefix_len, tuple(retained_positions))
         if layout.dropped == 0:
             return None
         page, table = self.page, seq.block_table
-        src = tuple(table[p // page] * page + p % page for p in layout.retained_positions)
-        dst = tuple(table[i // page] * page + i % page for i in range(layout.physical_prefix_len))
+        # rows computed behind the prefix (a prompt prefilled in one piece) move down with it
+        moved = tuple(layout.retained_positions) + tuple(range(prefix_len, seq.num_computed_tokens))
+        src = tuple(table[p // page] * page + p % page for p in moved)
+        dst = tuple(table[i // page] * page + i % page for i in range(len(moved)))
         need = -(-(len(seq) - layout.dropped) // page)
         return CompactionPlan(seq.seq_id, layout, src, dst, tuple(table[:need]), tuple(table[need:]), seq.block_table_version)
 

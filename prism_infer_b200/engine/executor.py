@@ -42,6 +42,16 @@ class ModelExecutor:
                                      config.visual_pruning_video_min_keep_tokens,
                                      "uniform" if config.visual_pruning_strategy == "attention" else config.visual_pruning_strategy)
         self._have_visual: set[int] = set()
+        # attention strategy: prompts prefilled in one piece are scored by the last query's attention
+        # over their visual tokens (last N decoder layers) and compacted by those scores; prompts
+        # that need several chunks fall back to the uniform selection at the prefix boundary
+        self.attention_strategy = bool(self.compact and config.visual_pruning_strategy == "attention")
+        n_layers = config.arch.text.num_layers
+        last_n = max(1, min(n_layers, int(config.visual_pruning_attention_last_n_layers)))
+        self.score_layers = list(range(n_layers - last_n, n_layers))
+        self.pruning_scored = PruningConfig(config.visual_pruning_keep_ratio, config.visual_pruning_min_keep_tokens,
+                                            config.visual_pruning_video_min_keep_tokens, "attention")
+        self.attention_counters = {"scored": 0, "uniform_fallback": 0}
 
     def mark_visual_ready(self, seq_id: int) -> None:
         """The runner already holds this sequence's vision result (hydrated at submission)."""
@@ -78,6 +88,8 @@ class ModelExecutor:
                 self._have_visual.add(job.seq_id)
             for sid in inputs.release_visual:
                 self._have_visual.discard(sid)
+            if self.attention_strategy and plan.phase is Phase.PREFILL:
+                self._request_scores(plan, inputs)
             sampled = self.runners.call("execute", inputs)
         tokens: list[int | None] = [None] * plan.batch_size
         if plan.phase is Phase.PREFILL:
@@ -89,15 +101,50 @@ class ModelExecutor:
         return ExecutionResult(tuple(tokens), (time.perf_counter() - t0) * 1e3, compactions)
 
     # ------------------------------------------------------------------------------
+    def _whole_prompt(self, seq, sl) -> bool:
+        return (seq.is_multimodal and sl.start == 0 and sl.end == len(seq) and seq.kv_layout is None and seq.num_cached_tokens == 0
+                and 0 < seq.multimodal_prefix_boundary < len(seq))
+
+    def _request_scores(self, plan: BatchPlan, inputs) -> None:
+        """Ask the runner to score the sequences whose whole prompt is in this step."""
+        row = 0
+        for seq, sl in zip(plan.seqs, plan.slices):
+            if self._whole_prompt(seq, sl):
+                visual = tuple(i for span in seq.visual_spans for i in range(span.start, span.end))
+                if visual:
+                    inputs.score_rows.append((seq.seq_id, row, sl.length, visual))
+            row += sl.length
+        if inputs.score_rows:
+            inputs.score_layers = list(self.score_layers)
+
     def _after_prefill(self, plan: BatchPlan) -> int:
         """Compaction and prefix publication for sequences whose chunk ended on the boundary."""
         plans = []
         owners = []
+        scores = self.runners.call("take_visual_scores") if self.attention_strategy else None
         for seq, sl in zip(plan.seqs, plan.slices):
             boundary = seq.multimodal_prefix_boundary
+            if scores and seq.seq_id in scores and scores[seq.seq_id] and self._whole_prompt(seq, sl):
+                decision = compute_pruning_decision(seq.token_ids, seq.image_token_id, seq.video_token_id, self.pruning_scored,
+                                                    end=boundary, scores=scores[seq.seq_id])
+                self.attention_counters["scored"] += 1
+                if decision is not None and decision.dropped:
+                    seq.num_computed_tokens += sl.length
+                    try:
+                        cp = self.bm.build_compaction_plan(seq, retained_positions(boundary, decision), boundary)
+                    finally:
+                        seq.num_computed_tokens -= sl.length
+                    if cp is not None:
+                        plans.append(cp)
+                        owners.append(seq)
+                        seq.pruning_record = {"kept": len(decision.kept), "dropped": len(decision.dropped),
+                                              "total": decision.total_visual_tokens, "strategy": "attention"}
+                continue
             if not seq.is_multimodal or boundary <= 0 or sl.end != boundary or sl.end >= len(seq):
                 continue
             if self.compact and seq.kv_layout is None and seq.num_cached_tokens == 0:
+                if self.attention_strategy:
+                    self.attention_counters["uniform_fallback"] += 1
                 decision = compute_pruning_decision(seq.token_ids, seq.image_token_id, seq.video_token_id, self.pruning,
                                                     end=boundary)
                 if decision is not None and decision.dropped:

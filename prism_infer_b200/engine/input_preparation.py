@@ -80,6 +80,9 @@ class StepInputs(_TensorStatePickle):
     vision_jobs: list[VisionJob] = field(default_factory=list)
     vision_rows: list[tuple[int, int, int]] = field(default_factory=list)  # (seq_id, first row, rows) in vis order
     release_visual: list[int] = field(default_factory=list)
+    # attention pruning strategy: (seq_id, first row, rows, visual token indices) of the sequences to score
+    score_rows: list[tuple[int, int, int, tuple[int, ...]]] = field(default_factory=list)
+    score_layers: list[int] = field(default_factory=list)
     # decode only
     context_lens: Optional[torch.Tensor] = None   # [B] int32
 

@@ -78,8 +78,8 @@ class CompactionPlan:
     def __post_init__(self) -> None:
         if len(self.src_slots) != len(self.dst_slots):
             raise ValueError("source and destination slot lists differ in length")
-        if len(self.src_slots) != self.layout.physical_prefix_len:
-            raise ValueError("plan must move exactly the retained rows")
+        if len(self.src_slots) < self.layout.physical_prefix_len:
+            raise ValueError("plan must move every retained row (plus any rows computed behind the prefix)")
         if len(set(self.dst_slots)) != len(self.dst_slots):
             raise ValueError("destination slots must be unique")
         if set(self.kept_blocks) & set(self.released_blocks):

@@ -145,6 +145,7 @@ class ModelRunner:
         self._visual_cache: dict[str, tuple[torch.Tensor, list[torch.Tensor]]] = {}
         self._visual_cache_bytes = 0
         self.visual_cache_counters = {"hits": 0, "misses": 0, "evictions": 0}
+        self._visual_scores: dict[int, dict[int, float]] = {}
         self.graphs: dict[int, _DecodeGraph] = {}
         self.greedy_graphs: dict[int, _DecodeGraph] = {}
         self.buckets = decode_buckets(min(config.max_num_seqs, 512))
@@ -297,6 +298,12 @@ class ModelRunner:
         with the same media."""
         self._visual[job.seq_id] = self._encode(job)
 
+    def take_visual_scores(self) -> dict[int, dict[int, float]]:
+        """Attention-strategy scores of the sequences scored since the last call (identical on
+        every rank after the reduction)."""
+        out, self._visual_scores = self._visual_scores, {}
+        return out
+
     def release_visual(self, seq_id: int) -> None:
         """Drop the vision result of a sequence that will not be prefilled (cancelled, rejected)."""
         self._visual.pop(seq_id, None)
@@ -340,8 +347,14 @@ class ModelRunner:
                 cu_seqlens_q=self._to_dev(inp.cu_seqlens_q), kv_lens=self._to_dev(inp.kv_lens), max_q_len=inp.max_q_len,
                 no_history=bool(torch.equal(inp.kv_lens, inp.cu_seqlens_q[1:] - inp.cu_seqlens_q[:-1])))
             ids, pos, vis_index = self._to_dev(inp.input_ids), self._to_dev(inp.positions), self._to_dev(inp.vis_index)
+            if inp.score_rows:
+                from .visual_pruning import RuntimeVisualTokenScorer
+
+                meta.scorer = RuntimeVisualTokenScorer(inp.score_rows, inp.score_layers)
         with profile_region("runner.run_model"):
             hidden = self.model.forward(ids, pos, meta, self.kv, visual=visual, vis_index=vis_index, deepstack=deep)
+        if meta.scorer is not None:
+            self._visual_scores.update(meta.scorer.finalize(world_size=self.comm.size, reduce_sum=self.comm.reduce_dense))
         for seq_id in inp.release_visual:
             self._visual.pop(seq_id, None)
         if inp.sample_rows is None or inp.sample_rows.numel() == 0:

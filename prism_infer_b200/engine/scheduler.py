@@ -46,6 +46,9 @@ class Scheduler:
         # place before the rest of the prompt is written behind it; a dense prefix is published
         # from whichever chunk crosses the boundary, without an extra prefill step
         self.stop_at_prefix = bool(config.compacts_visual_tokens)
+        # attention strategy: a prompt that fits one chunk is prefilled whole (its last query scores the
+        # visual tokens); longer prompts still end a chunk on the boundary and compact uniformly
+        self.whole_prompt_first = bool(config.compacts_visual_tokens and getattr(config, "visual_pruning_strategy", "uniform") == "attention")
         self.waiting: deque[Sequence] = deque()
         self.running: list[Sequence] = []
         self.swapped: deque[Sequence] = deque()
@@ -135,7 +138,11 @@ class Scheduler:
 
         def try_add(seq: Sequence) -> bool:
             nonlocal budget, patches_left, patches
-            n = self.policy.prefill_token_count(seq, budget, stop_at_prefix=self.stop_at_prefix)
+            stop = self.stop_at_prefix
+            if stop and self.whole_prompt_first and seq.num_computed_tokens == 0 and seq.num_cached_tokens == 0:
+                limit = min(budget, self.policy.max_chunk) if self.policy.chunked else budget
+                stop = len(seq) > limit
+            n = self.policy.prefill_token_count(seq, budget, stop_at_prefix=stop)
             if n <= 0:
                 return False
             start = seq.num_computed_tokens

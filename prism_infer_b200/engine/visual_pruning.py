@@ -145,3 +145,66 @@ def retained_positions(prefix_len: int, decision: PruningDecision | None) -> tup
         return tuple(range(prefix_len))
     dropped = set(decision.dropped)
     return tuple(p for p in range(prefix_len) if p not in dropped)
+
+
+class RuntimeVisualTokenScorer:
+    """Query-aware scores for the ``attention`` strategy (reference
+    ``prism_infer/engine/visual_pruning.py:73-195``): in each chosen decoder layer, the attention
+    that the LAST query of every sequence pays to each of its visual tokens - softmax over all of
+    the sequence's keys, mean over query heads - summed over the layers and averaged at the end.
+
+    ``observe`` takes the step's flattened ``q [T, Hq_local, D]`` and ``k [T, Hkv_local, D]`` (after
+    QK-norm and rotary) and keeps device tensors only; ``finalize`` averages over layers, sums the
+    ranks' head means through ``reduce_sum`` (every rank holds ``Hq / world`` heads) and moves the
+    result to the host once.  ``rows`` gives each sequence's ``(seq_id, first row, row count,
+    visual token indices relative to the sequence)``; a sequence must be present with its whole
+    prompt, because the last query has to see every key."""
+
+    def __init__(self, rows: Sequence[tuple[int, int, int, Sequence[int]]], layer_ids: Sequence[int]) -> None:
+        self.layer_ids = tuple(sorted({int(i) for i in layer_ids}))
+        if not self.layer_ids or self.layer_ids[0] < 0:
+            raise ValueError(f"layer_ids must be non-empty and non-negative: {list(layer_ids)}")
+        self.rows = tuple((int(s), int(lo), int(n), tuple(int(v) for v in vis)) for s, lo, n, vis in rows)
+        self.total_tokens = max((lo + n for _, lo, n, _ in self.rows), default=0)
+        self._sums: dict[int, object] = {}
+        self._seen: set[int] = set()
+
+    def observe(self, layer_id: int, q, k, scale: float) -> None:
+        import torch
+
+        if layer_id not in self.layer_ids:
+            return
+        if layer_id in self._seen:
+            raise RuntimeError(f"layer {layer_id} observed twice")
+        if q.dim() != 3 or k.dim() != 3 or q.shape[2] != k.shape[2] or q.shape[1] % k.shape[1]:
+            raise ValueError(f"expected q [T, Hq, D] and k [T, Hkv, D] with Hq a multiple of Hkv, got {list(q.shape)} and {list(k.shape)}")
+        if q.shape[0] < self.total_tokens or k.shape[0] < self.total_tokens:
+            raise ValueError(f"scorer covers {self.total_tokens} rows, got q {q.shape[0]} and k {k.shape[0]}")
+        groups = q.shape[1] // k.shape[1]
+        for seq_id, lo, n, vis in self.rows:
+            if not vis:
+                continue
+            q_last = q[lo + n - 1].float()                                   # [Hq, D]
+            keys = k[lo:lo + n].float()                                      # [n, Hkv, D]
+            logits = torch.einsum("hgd,thd->hgt", q_last.view(k.shape[1], groups, -1), keys) * float(scale)
+            probs = torch.softmax(logits, dim=-1).mean(dim=(0, 1))           # [n]
+            picked = probs.index_select(0, torch.tensor(vis, dtype=torch.long, device=probs.device))
+            self._sums[seq_id] = picked if seq_id not in self._sums else self._sums[seq_id] + picked
+        self._seen.add(layer_id)
+
+    def finalize(self, *, world_size: int = 1, reduce_sum=None) -> dict[int, dict[int, float]]:
+        missing = sorted(set(self.layer_ids) - self._seen)
+        if missing:
+            raise RuntimeError(f"scorer did not observe layers {missing}")
+        out: dict[int, dict[int, float]] = {}
+        for seq_id, _, _, vis in self.rows:
+            if not vis:
+                out[seq_id] = {}
+                continue
+            scores = self._sums[seq_id] / len(self._seen)
+            if world_size > 1:
+                if reduce_sum is None:
+                    raise ValueError("a tensor-parallel scorer needs reduce_sum")
+                scores = reduce_sum(scores.contiguous()) / world_size
+            out[seq_id] = dict(zip(vis, (float(v) for v in scores.cpu().tolist())))
+        return out

@@ -18,6 +18,8 @@ add+RMSNorm sums in a fixed order.
 
 from __future__ import annotations
 
+import math
+
 from dataclasses import dataclass, field
 from typing import Iterable, Iterator, Optional, Sequence
 
@@ -48,6 +50,8 @@ class AttnMeta:
     context_lens: Optional[torch.Tensor] = None    # [B] int32 (including the new token)
     nsplit: int = 0
     workspace: Optional[tuple[torch.Tensor, torch.Tensor]] = None
+    # prefill with the attention pruning strategy: collects last-query attention over visual tokens
+    scorer: Optional[object] = None
 
 
 @dataclass
@@ -440,7 +444,8 @@ class Qwen3VLModel:
         """
         t = self.arch.text
         T = input_ids.shape[0]
-        small = T <= SMALL_T
+        scoring = meta.scorer is not None and meta.is_prefill
+        small = T <= SMALL_T and not scoring  # the scorer reads K rows of the dense projection
         comm = self.comm
         comm.begin_step()
         emb_visual = visual
@@ -454,14 +459,14 @@ class Qwen3VLModel:
         n_deep = len(deepstack) if deepstack is not None else 0
         # at most four tokens on CUDA: residual add + RMSNorm run inside the next projection
         fuse_norm = (x.is_cuda and ops.NORMX_ENABLED and self.tp == 1 and T <= ops.NORMX_MAX_TOKENS and n_deep == 0
-                     and self.H % 64 == 0)
+                     and self.H % 64 == 0 and not scoring)
         if fuse_norm:
             res_bufs = [torch.empty((T, self.H), dtype=torch.bfloat16, device=x.device) for _ in range(2)]
             flip = 0
         # decode-sized steps: kernels that leave HBM idle request the next weights into L2
         pf = x.is_cuda and not meta.is_prefill and T <= 16
         if (self.tp > 1 and x.is_cuda and meta.is_prefill and hasattr(comm, "prefill_fused") and comm.prefill_fused(T)
-                and ops.TP_PREFILL_FUSED):
+                and ops.TP_PREFILL_FUSED and not scoring):
             return self._forward_prefill_fused(x, positions, meta, cache, deepstack, vis_index)
         for i, l in enumerate(self.layers):
             extra = deepstack[i - 1] if 0 < i <= n_deep else None
@@ -513,7 +518,10 @@ class Qwen3VLModel:
                 q = ops.qk_norm_rope_store(qkv=qkv, partials=None, positions=positions, q_weight=l.q_norm, k_weight=l.k_norm,
                                            num_heads=self.Hq, num_kv_heads=self.Hkv, head_dim=self.D, theta=t.rope_theta,
                                            section=t.mrope_section, eps=t.rms_norm_eps, slots=meta.slots, cache=cache, layer=i,
-                                           k_writeback=direct)
+                                           k_writeback=direct or scoring)
+                if scoring:  # K rows after QK-norm and rotary now sit in the projection buffer
+                    meta.scorer.observe(i, q, qkv.view(T, self.Hq + 2 * self.Hkv, self.D)[:, self.Hq:self.Hq + self.Hkv],
+                                        1.0 / math.sqrt(self.D))
             if direct:
                 heads = qkv.view(T, self.Hq + 2 * self.Hkv, self.D)
                 a = ops.varlen_attention(q, heads[:, self.Hq:self.Hq + self.Hkv], heads[:, self.Hq + self.Hkv:],

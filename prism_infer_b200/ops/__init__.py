@@ -508,6 +508,8 @@ def qk_norm_rope_store(
                 return (zf * cos[:, None, :] + rotate_half(zf) * sin[:, None, :]).to(z.dtype)
             q, k = _r(q), _r(k)
         store_kv(k, v, slots, cache, layer)
+        if k_writeback and qkv is not None:
+            qkv[:, Hq * D:(Hq + Hkv) * D] = k.reshape(T, Hkv * D)
         if q_out is not None:
             q_out.copy_(q)
             return q_out

@@ -51,6 +51,7 @@ class TPMethod(enum.Enum):
     HYDRATE_VISUAL_EMBEDDING = "hydrate_visual_embedding"
     ENCODE_FOR_SEQUENCE = "encode_for_sequence"
     RELEASE_VISUAL = "release_visual"
+    TAKE_VISUAL_SCORES = "take_visual_scores"
     VISUAL_EMBEDDING_CACHE_METADATA = "visual_embedding_cache_metadata"
     GRAPH_METADATA = "graph_metadata"
     TIME_DECODE_GRAPH = "time_decode_graph"

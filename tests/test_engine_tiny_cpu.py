@@ -388,3 +388,65 @@ def test_device_status_words_are_checked_on_a_cadence():
     llm.exit()
     with pytest.raises(ValueError):
         LLM("random:tiny", runner_group=Runners(), device="cpu", device_status_check_interval=-1, **opts)
+
+
+def test_attention_strategy_compacts_by_last_query_scores(tiny, monkeypatch):
+    """``visual_pruning_strategy="attention"``: a prompt prefilled in one piece is scored by its
+    last query (last decoder layer here), the lowest-scored visual tokens lose their KV rows, the
+    rows of the question move down with the prefix, and decoding then equals the oracle with the
+    dropped keys masked for generated tokens only (prompt tokens saw everything at prefill)."""
+    from prism_infer_b200.models import reference_model
+
+    arch, weights, oracle = tiny
+    tok = load_tokenizer("random:tiny", arch)
+    inp = prepare_image_inputs(PatchProcessor(arch), tok, [41, 42, 43, 44, 45], [_image(90, 96), _image(91, 64)])
+    L = len(inp.input_ids)
+    llm = _llm(weights, compression_mode="visual_compact", visual_pruning_strategy="attention", visual_pruning_keep_ratio=0.5,
+               visual_pruning_min_keep_tokens=3, visual_pruning_attention_last_n_layers=1, enable_prefix_caching=True)
+    layouts, scores_seen = [], []
+    commit = llm.executor.bm.commit_compaction
+    monkeypatch.setattr(llm.executor.bm, "commit_compaction", lambda seq, plan: (layouts.append(plan.layout), commit(seq, plan))[1])
+    take = llm.runners.runner.take_visual_scores
+    llm.runners.runner.take_visual_scores = lambda: (lambda s: (scores_seen.append(s), s)[1])(take())
+    sp = SamplingParams(temperature=0.0, max_tokens=6, ignore_eos=True)
+    got = llm.generate_prepared_image_inputs(inp, sp)["token_ids"]
+    assert llm.executor.attention_counters == {"scored": 1, "uniform_fallback": 0}
+    (layout,) = layouts
+    visual = [i for i, t in enumerate(inp.input_ids) if t == arch.image_token_id]
+    kept_visual = [p for p in layout.retained_positions if p in set(visual)]
+    assert len(visual) == 13 and len(kept_visual) == 7                       # ceil(13 * 0.5)
+    scores = [s for s in scores_seen if s][0]
+    (per_token,) = scores.values()
+    assert set(per_token) == set(visual) and abs(sum(per_token.values()) - 1.0) < 1.0   # attention mass on visual tokens
+    top = sorted(sorted(visual, key=lambda i: (-per_token[i], i))[:7])
+    assert kept_visual == top                                                # the highest-scored tokens survive
+    boundary = layout.logical_prefix_len
+    assert [p for p in layout.retained_positions if p not in set(visual)] == [p for p in range(boundary) if p not in set(visual)]
+    assert llm.multimodal_prefix_cache_metadata()["stores"] == 0             # a question-specific prefix is not shared
+    llm.exit()
+
+    dropped = torch.tensor(sorted(set(visual) - set(kept_visual)))
+    real_sdpa = reference_model.F.scaled_dot_product_attention
+
+    def masked_sdpa(q, k, v, attn_mask=None, is_causal=False, **kw):
+        if not is_causal:                       # the vision tower's bidirectional attention
+            return real_sdpa(q, k, v, attn_mask=attn_mask, **kw)
+        S = q.shape[-2]
+        allowed = torch.ones(S, S, dtype=torch.bool).tril()
+        if S > L:
+            allowed[L:, dropped] = False        # generated tokens do not see the dropped rows
+        return real_sdpa(q, k, v, attn_mask=allowed)
+
+    monkeypatch.setattr(reference_model.F, "scaled_dot_product_attention", masked_sdpa)
+    want = oracle.generate_greedy(inp.input_ids, 6, pixel_values=inp.pixel_values, image_grid_thw=inp.image_grid_thw)
+    monkeypatch.setattr(reference_model.F, "scaled_dot_product_attention", real_sdpa)
+    assert got == want
+    dense = oracle.generate_greedy(inp.input_ids, 6, pixel_values=inp.pixel_values, image_grid_thw=inp.image_grid_thw)
+    assert got[0] == dense[0]                                                 # the first token comes from the uncompacted prefill
+
+    # a prompt that needs several chunks cannot be scored: uniform selection at the prefix boundary
+    llm = _llm(weights, compression_mode="visual_compact", visual_pruning_strategy="attention", visual_pruning_keep_ratio=0.5,
+               visual_pruning_min_keep_tokens=3, max_chunk_size=16, max_num_batched_tokens=512)
+    llm.generate_prepared_image_inputs(inp, sp)
+    assert llm.executor.attention_counters == {"scored": 0, "uniform_fallback": 1}
+    llm.exit()

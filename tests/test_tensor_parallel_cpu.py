@@ -39,3 +39,29 @@ def test_tp2_cpu_matches_oracle_and_prefix_cache_works():
         assert rb["token_ids"] == oracle.generate_greedy(b.input_ids, 6, pixel_values=b.pixel_values, image_grid_thw=b.image_grid_thw)
     finally:
         llm.exit()
+
+
+@pytest.mark.timeout(300)
+def test_tp2_cpu_attention_strategy_scores_are_reduced_over_ranks():
+    """Each rank scores with its own heads; after the reduction both compact the same rows, so
+    the two-rank engine produces the single-rank engine's tokens."""
+    arch = Qwen3VLArch.tiny()
+    weights = random_weights(arch, dtype=torch.float32, seed=0)
+    tok = load_tokenizer("random:tiny", arch)
+    rng = np.random.default_rng(3)
+    inp = prepare_image_inputs(PatchProcessor(arch), tok, [41, 42, 43, 44], [rng.integers(0, 256, (96, 96, 3), dtype=np.uint8)])
+    sp = SamplingParams(temperature=0.0, max_tokens=6, ignore_eos=True)
+    opts = dict(max_model_len=512, kvcache_block_size=16, num_kvcache_blocks=64, enforce_eager=True, max_chunk_size=256,
+                compression_mode="visual_compact", visual_pruning_strategy="attention", visual_pruning_keep_ratio=0.5,
+                visual_pruning_min_keep_tokens=2)
+    one = LLM("random:tiny", weights=weights, device="cpu", **opts)
+    want = one.generate_prepared_image_inputs(inp, sp)["token_ids"]
+    assert one.executor.attention_counters["scored"] == 1
+    one.exit()
+    two = LLM("random:tiny", weights=weights, tensor_parallel_size=2, tensor_parallel_timeout_seconds=120, **opts)
+    try:
+        got = two.generate_prepared_image_inputs(inp, sp)["token_ids"]
+        assert two.executor.attention_counters["scored"] == 1
+    finally:
+        two.exit()
+    assert got == want
