@@ -102,3 +102,53 @@ def test_smoke_entry(cuda_device):
     import __graft_entry__
 
     __graft_entry__.smoke()
+
+
+def test_attention_strategy_compaction_on_gpu(tiny, monkeypatch):
+    """The attention pruning strategy on the device: K rows written back by the fused QK-norm /
+    rotary kernel feed the scorer, the highest-scored visual tokens keep their rows, the question's
+    rows move down in the same compaction, and decoding agrees with the oracle that masks the
+    dropped keys for generated tokens."""
+    from prism_infer_b200.models import reference_model
+
+    arch, weights, oracle = tiny
+    inp = _inputs(arch, 7, seed=11)
+    L = len(inp.input_ids)
+    llm = LLM("random:tiny", weights=weights, max_model_len=512, kvcache_block_size=16, num_kvcache_blocks=64,
+              compression_mode="visual_compact", visual_pruning_strategy="attention", visual_pruning_keep_ratio=0.5,
+              visual_pruning_min_keep_tokens=4, visual_pruning_attention_last_n_layers=2, max_num_seqs=4, cpu_kv_cache_ratio=0.0)
+    layouts, seen = [], []
+    commit = llm.executor.bm.commit_compaction
+    monkeypatch.setattr(llm.executor.bm, "commit_compaction", lambda seq, plan: (layouts.append(plan.layout), commit(seq, plan))[1])
+    take = llm.runners.runner.take_visual_scores
+    llm.runners.runner.take_visual_scores = lambda: (lambda s: (seen.append(s), s)[1])(take())
+    got = llm.generate_prepared_image_inputs(inp, SamplingParams(temperature=0.0, max_tokens=8, ignore_eos=True))["token_ids"]
+    torch.cuda.synchronize()
+    native.check_status()
+    assert llm.executor.attention_counters == {"scored": 1, "uniform_fallback": 0}
+    llm.exit()
+    (layout,) = layouts
+    visual = [i for i, t in enumerate(inp.input_ids) if t == arch.image_token_id]
+    kept = [p for p in layout.retained_positions if p in set(visual)]
+    (scores,) = [s for s in seen if s][0].values()
+    keep = -(-len(visual) // 2)
+    assert len(kept) == keep and kept == sorted(sorted(visual, key=lambda i: (-scores[i], i))[:keep])
+    assert all(0.0 <= v <= 1.0 for v in scores.values())
+
+    dropped = torch.tensor(sorted(set(visual) - set(kept)))
+    real_sdpa = reference_model.F.scaled_dot_product_attention
+
+    def masked_sdpa(q, k, v, attn_mask=None, is_causal=False, **kw):
+        if not is_causal:
+            return real_sdpa(q, k, v, attn_mask=attn_mask, **kw)
+        S = q.shape[-2]
+        allowed = torch.ones(S, S, dtype=torch.bool, device=q.device).tril()
+        if S > L:
+            allowed[L:, dropped.to(q.device)] = False
+        return real_sdpa(q, k, v, attn_mask=allowed)
+
+    monkeypatch.setattr(reference_model.F, "scaled_dot_product_attention", masked_sdpa)
+    want, logits = oracle.generate_greedy(inp.input_ids, 8, pixel_values=inp.pixel_values, image_grid_thw=inp.image_grid_thw,
+                                          return_logits=True)
+    monkeypatch.setattr(reference_model.F, "scaled_dot_product_attention", real_sdpa)
+    _agree(got, want, logits, margin=0.05)
