@@ -30,6 +30,7 @@ def main() -> None:
     ap.add_argument("--tp", type=int, default=1)
     ap.add_argument("--model", default="random:qwen3-vl-8b")
     ap.add_argument("--out", default="")
+    ap.add_argument("--vision-graph", action="store_true", help="replay the vision tower from a CUDA graph per grid shape")
     ap.add_argument("--cuda-profiler-range", action="store_true",
                     help="bracket the last timed request with cudaProfilerStart/Stop (for ncu --profile-from-start off)")
     args = ap.parse_args()
@@ -39,7 +40,7 @@ def main() -> None:
 
     llm = LLM(args.model, tensor_parallel_size=args.tp, max_model_len=4096, kvcache_block_size=256, num_kvcache_blocks=64,
               compression_mode="scaled_fp8_kv", max_num_seqs=4, max_num_batched_tokens=16384, max_chunk_size=8192,
-              cpu_kv_cache_ratio=0.0, enable_prefix_caching=False)
+              cpu_kv_cache_ratio=0.0, enable_prefix_caching=False, enable_vision_tensor_cudagraph=args.vision_graph)
     if not llm.is_driver:
         llm.serve_forever()
         return

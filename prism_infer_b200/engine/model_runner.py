@@ -146,6 +146,8 @@ class ModelRunner:
         self._visual_cache_bytes = 0
         self.visual_cache_counters = {"hits": 0, "misses": 0, "evictions": 0}
         self._visual_scores: dict[int, dict[int, float]] = {}
+        self._vision_graphs: dict[tuple, tuple] = {}
+        self.vision_graph_counters = {"captures": 0, "replays": 0}
         self.graphs: dict[int, _DecodeGraph] = {}
         self.greedy_graphs: dict[int, _DecodeGraph] = {}
         self.buckets = decode_buckets(min(config.max_num_seqs, 512))
@@ -213,11 +215,50 @@ class ModelRunner:
             self._visual_cache[key] = val  # LRU refresh
             return val
         with profile_region("model.vision.encoder"):
-            main, deep = self.model.encode_vision(job.pixel_values, job.grid_thw)
+            main, deep = self._tower(job.pixel_values, job.grid_thw)
         if key is not None:
             self.visual_cache_counters["misses"] += 1
             self._cache_visual(key, (main, deep))
         return main, deep
+
+    VISION_GRAPH_MAX_PATCHES = 4096   # larger inputs are compute-bound: a graph would only hold memory
+    VISION_GRAPH_ENTRIES = 8
+
+    def _tower(self, pixel_values: torch.Tensor, grid_thw) -> tuple[torch.Tensor, list[torch.Tensor]]:
+        """The vision tower, replayed from a CUDA graph per grid shape when
+        ``enable_vision_tensor_cudagraph`` is set (reference ``MultimodalConfig``, ``config.py:279-322``):
+        a single 448 x 448 image is about 300 launches for half a millisecond of device work, and
+        serving repeats a handful of image shapes.  One rank, CUDA, at most
+        ``VISION_GRAPH_MAX_PATCHES`` patches; the least recently used of ``VISION_GRAPH_ENTRIES``
+        graphs is dropped.  Results are copied out of the graph's buffers."""
+        n = int(pixel_values.shape[0])
+        if not (self.on_cuda and self.comm.size == 1 and self.config.enable_vision_tensor_cudagraph and n <= self.VISION_GRAPH_MAX_PATCHES):
+            return self.model.encode_vision(pixel_values, grid_thw)
+        key = tuple(tuple(int(v) for v in g) for g in grid_thw)
+        entry = self._vision_graphs.pop(key, None)
+        if entry is None:
+            self.vision_graph_counters["captures"] += 1
+            static_in = torch.empty((n, pixel_values.shape[1]), dtype=self.dtype, device=self.device)
+            stream = torch.cuda.Stream(device=self.device)
+            stream.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(stream):
+                static_in.copy_(pixel_values, non_blocking=True)
+                self.model.encode_vision(static_in, grid_thw)      # warm-up outside capture: geometry tensors, kernel attributes
+                stream.synchronize()
+                graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(graph, stream=stream):
+                    main, deep = self.model.encode_vision(static_in, grid_thw)
+            torch.cuda.current_stream().wait_stream(stream)
+            entry = (graph, static_in, main, deep)
+            while len(self._vision_graphs) >= self.VISION_GRAPH_ENTRIES:
+                self._vision_graphs.pop(next(iter(self._vision_graphs)))
+        else:
+            self.vision_graph_counters["replays"] += 1
+        self._vision_graphs[key] = entry  # most recently used last
+        graph, static_in, main, deep = entry
+        static_in.copy_(pixel_values, non_blocking=True)
+        graph.replay()
+        return main.clone(), [d.clone() for d in deep]
 
     def _cache_visual(self, key: str, value: tuple[torch.Tensor, list[torch.Tensor]]) -> None:
         """LRU insertion under the byte budget; an entry larger than the budget is not kept."""
@@ -275,7 +316,7 @@ class ModelRunner:
             pixels = torch.cat([j.pixel_values for j in group])
         grids = [g for j in group for g in j.grid_thw]
         with profile_region("model.vision.encoder", metadata={"jobs": len(group)}):
-            main, deep = self.model.encode_vision(pixels, grids)
+            main, deep = self._tower(pixels, grids)
         row = 0
         for job in group:
             n = sum(int(t) * int(h) * int(w) for t, h, w in job.grid_thw) // unit
@@ -441,6 +482,7 @@ class ModelRunner:
 
     def graph_metadata(self) -> dict[str, object]:
         return {"buckets": list(self.graphs), "pdl": ops.pdl_enabled(), "kv_pages": self.kv.num_blocks,
+                "vision_graphs": {"entries": len(self._vision_graphs), **self.vision_graph_counters},
                 "kv_bytes_per_page": self.config.kv_bytes_per_page(), "kv_mode": self.kv_mode,
                 "launches_per_decode_graph": {str(b): getattr(g, "launches", 0) for b, g in self.graphs.items()},
                 "staging_bytes": {str(b): g.nbytes for b, g in self.graphs.items()},
@@ -464,5 +506,6 @@ class ModelRunner:
     def exit(self) -> None:
         self.graphs.clear()
         self.greedy_graphs.clear()
+        self._vision_graphs.clear()
         self._visual.clear()
         self._visual_cache.clear()

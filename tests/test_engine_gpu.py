@@ -152,3 +152,22 @@ def test_attention_strategy_compaction_on_gpu(tiny, monkeypatch):
                                           return_logits=True)
     monkeypatch.setattr(reference_model.F, "scaled_dot_product_attention", real_sdpa)
     _agree(got, want, logits, margin=0.05)
+
+
+def test_vision_tower_graph_replay_equals_eager(tiny):
+    """``enable_vision_tensor_cudagraph``: the tower is captured per grid shape and replayed for
+    later media of that shape; tokens are those of the eager tower, bit for bit (same kernels)."""
+    arch, weights, _ = tiny
+    sp = SamplingParams(temperature=0.0, max_tokens=6, ignore_eos=True)
+    reqs = [_inputs(arch, 5, seed=21), _inputs(arch, 6, seed=22), _inputs(arch, 4, seed=23)]
+    outs = {}
+    for graphs in (False, True):
+        llm = LLM("random:tiny", weights=weights, max_model_len=512, kvcache_block_size=16, num_kvcache_blocks=64,
+                  max_num_seqs=4, cpu_kv_cache_ratio=0.0, enable_prefix_caching=False, enable_vision_tensor_cudagraph=graphs)
+        outs[graphs] = [llm.generate_prepared_image_inputs(r, sp)["token_ids"] for r in reqs]
+        meta = llm.graph_metadata()["vision_graphs"]
+        assert meta == ({"entries": 1, "captures": 1, "replays": 2} if graphs else {"entries": 0, "captures": 0, "replays": 0})
+        torch.cuda.synchronize()
+        native.check_status()
+        llm.exit()
+    assert outs[True] == outs[False]
