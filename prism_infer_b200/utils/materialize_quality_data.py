@@ -120,6 +120,7 @@ def materialize(*, layout: str, dataset_id: str, revision: str, raw_dir: str | P
     manifest["layout"] = layout
     manifest["records_file"] = {"path": records_path.name, "sha256": records_sha}
     manifest["source_files"] = [{"name": p.name, "bytes": p.stat().st_size, "sha256": qmat.sha256_file(p)} for p in shards]
+    qmat.write_json_atomic(out / f"{dataset_id}.population.json", [qmat.canonical_sample_id(i) for i in ids])  # input of verify_quality_data
     manifest["verification"] = qmat.verify_materialized_records(records, out_root)
     qmat.write_json_atomic(out / f"{dataset_id}.manifest.json", manifest)
     return manifest

@@ -256,6 +256,13 @@ def test_materialize_quality_subset_from_local_parquet_shards(tmp_path):
     assert m["verification"]["unique_media_files"] == 5                      # 4 private images + the shared one, stored once
     assert len({r["media"][0]["sha256"] for r in records}) == 1
     qmat.verify_materialized_records(records, out)
+    # the stand-alone verifier reproduces the selection from the population list written beside the manifest
+    from prism_infer_b200.utils import verify_quality_data as vq
+
+    report = vq.verify(json.loads((out / "muir.manifest.json").read_text()), records, json.loads((out / "muir.population.json").read_text()), str(out))
+    assert report
+    with pytest.raises(ValueError):
+        vq.verify(json.loads((out / "muir.manifest.json").read_text()), records, ["0", "1", "2", "3", "4"], str(out))
     again = mq.materialize(layout="muirbench", dataset_id="muir", revision="rev1", raw_dir=raw, split="test", out_root=out, seed=7,
                            development=2, final=4)
     assert again["records_sha256"] == m["records_sha256"]                    # idempotent
