@@ -30,7 +30,9 @@ from .architecture import Qwen3VLArch
 from .position import vision_patch_coords, vision_pos_embed_plan, vision_segments
 from .weights import LM, VIS
 
-SMALL_T = 128  # at or below this many tokens the GEMMs are weight-streaming: split-K + fp32 partials
+# at or below this many tokens the GEMMs are weight-streaming: split-K + fp32 partials.  PRISM_SMALL_T moves the
+# boundary for experiments (prompts of 129-511 tokens run one tile per CTA without split-K and leave most SMs idle)
+SMALL_T = int(__import__("os").environ.get("PRISM_SMALL_T", "128"))
 
 
 @dataclass
