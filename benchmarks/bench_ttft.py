@@ -81,7 +81,8 @@ def main() -> None:
     table = {k: {"count_per_request": v["count"] / n, "cpu_ms": round(v["cpu_ms"] / n, 3), "cuda_ms": round(v["cuda_ms"] / n, 3)}
              for k, v in sorted(rec["totals"].items())}
     out = {"workload": f"images{args.images}", "tp": args.tp, "prompt_tokens": len(inp.input_ids), "ttft_ms": [round(t, 2) for t in ttft],
-           "ttft_median_ms": round(sorted(ttft)[n // 2], 2), "preprocess_ms_median": round(sorted(prep)[n // 2], 2), "regions": table}
+           "ttft_median_ms": round(sorted(ttft)[n // 2], 2), "ttft_p50_ms": round(float(np.percentile(ttft, 50)), 2),
+           "ttft_p99_ms": round(float(np.percentile(ttft, 99)), 2), "preprocess_ms_median": round(sorted(prep)[n // 2], 2), "regions": table}
     print(json.dumps(out), flush=True)
     if args.out:
         with open(args.out, "w") as fh:
