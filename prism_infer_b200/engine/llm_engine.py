@@ -22,7 +22,7 @@ from ..models.position import rope_index
 from ..observability import profile_region, profile_step_metadata
 from ..sampling_params import SamplingParams
 from ..utils.tokenizer import load_tokenizer
-from .contracts import BatchPlan, Phase, RequestOutput, StepResult
+from .contracts import Phase, StepResult
 from .executor import LocalRunnerGroup, ModelExecutor
 from .input_preparation import VisionJob
 from .metrics import EngineMetrics

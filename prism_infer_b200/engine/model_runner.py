@@ -19,7 +19,6 @@ B200-specific choices:
 
 from __future__ import annotations
 
-import time
 from typing import Optional, Sequence as Seq
 
 import torch
