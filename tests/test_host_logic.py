@@ -495,3 +495,18 @@ def test_random_traffic_reached_the_interesting_paths():
                 total[k] = total.get(k, 0) + v
     for key in ("preempt_swap", "preempt_recompute", "swap_in", "finished", "cancelled", "hits", "stores", "evictions"):
         assert total.get(key, 0) > 0, (key, total)
+
+
+def test_options_document_lists_every_flat_option():
+    """``docs/OPTIONS.md`` is the generated table of ``LLM`` keywords: regenerate it when the
+    configuration changes."""
+    import os
+
+    from prism_infer_b200.config import FLAT_OPTION_NAMES
+    from prism_infer_b200.utils import describe_options
+
+    rows = describe_options.option_rows()
+    assert {r[0] for r in rows} == set(FLAT_OPTION_NAMES)
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    with open(os.path.join(root, "docs", "OPTIONS.md")) as fh:
+        assert fh.read() == describe_options.markdown(), "run: python -m prism_infer_b200.utils.describe_options > docs/OPTIONS.md"
