@@ -206,6 +206,7 @@ class BlockManager:
     def _allocate_dense(self, seq: Sequence, *, share: bool) -> None:
         n_pages = seq.blocks_needed(len(seq))
         table: list[int] = []
+        pending: list[tuple[int, int, tuple[int, ...]]] = []
         cached_tokens = 0
         h: int | None = None
         still_hitting = share
@@ -227,7 +228,9 @@ class BlockManager:
                         raise OutOfBlocks("no free GPU page")
                     bid = self.gpu.allocate()
                     if h is not None:
-                        self.gpu.publish(bid, h, toks)
+                        # the page holds no KV yet: its hash becomes visible to other requests
+                        # only after the chunk that fills it has run (publish_computed_pages)
+                        pending.append((i, h, toks))
                 table.append(bid)
         except OutOfBlocks:
             for p in table:
@@ -238,8 +241,29 @@ class BlockManager:
         seq.kv_layout = None
         seq.num_cached_tokens = cached_tokens
         seq.num_computed_tokens = cached_tokens
+        seq.unpublished_hashes = pending
+
+    def publish_computed_pages(self, seq: Sequence) -> int:
+        """Publish the content hashes of ``seq``'s own prompt pages that are now fully computed
+        (every token of the page is below ``num_computed_tokens``).  Called after each prefill
+        step; a page that another request published first keeps that request's copy.  Pages of a
+        sequence that is cancelled or preempted before they are computed are never published, so a
+        later identical prompt cannot be served from rows nobody wrote."""
+        if not seq.unpublished_hashes or seq.kv_layout is not None:
+            return 0
+        done, rest = 0, []
+        for i, h, toks in seq.unpublished_hashes:
+            if (i + 1) * self.page <= seq.num_computed_tokens and i < len(seq.block_table):
+                if self.gpu.lookup(h, toks) is None:
+                    self.gpu.publish(seq.block_table[i], h, toks)
+                done += 1
+            else:
+                rest.append((i, h, toks))
+        seq.unpublished_hashes = rest
+        return done
 
     def deallocate(self, seq: Sequence) -> None:
+        seq.unpublished_hashes = []
         for p in reversed(seq.block_table):
             self.gpu.release(p)
         seq.block_table = []
@@ -354,6 +378,7 @@ class BlockManager:
             raise RuntimeError("stale compaction plan")
         for p in seq.block_table:
             self.gpu.clear_hash(p)
+        seq.unpublished_hashes = []
         for p in plan.released_blocks:
             self.gpu.release(p)
         seq.block_table = list(plan.kept_blocks)

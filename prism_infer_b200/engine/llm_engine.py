@@ -109,7 +109,6 @@ class LLMEngine:
         self.executor = ModelExecutor(cfg, self.runners, self.scheduler.block_manager)
         self._sequences: dict[int, Sequence] = {}
         self._cooperative_pending = False
-        self._replan = None
         self.cooperative_counters = {"vision_quanta": 0}
         self._steps_since_status = 0
         atexit.register(self.exit)
@@ -221,24 +220,18 @@ class LLMEngine:
         with profile_region("engine.step", cuda=False):
             with profile_region("engine.scheduler.schedule", cuda=False):
                 plan = self.scheduler.schedule()
-                if self._replan is not None and plan.phase is Phase.PREFILL:
-                    # the interrupted prefill comes back with the same sequences: its copies already ran
-                    from .contracts import KVTransferPlan
-                    import dataclasses
-
-                    plan = dataclasses.replace(plan, kv_transfers=KVTransferPlan())
-                    self._replan = None
             if plan.is_idle and plan.kv_transfers.empty:
                 return StepResult(Phase.IDLE)
             if (self.config.cooperative_prefill and plan.phase is Phase.PREFILL and plan.num_vision_patches > 0
                     and self.scheduler.num_decoding > 0 and not self._cooperative_pending):
-                # vision quantum now, language prefill on the next step; the plan's page
-                # transfers ran, so the re-planned step must not repeat them
+                # vision quantum now, language prefill on a later step.  The plan's page transfers
+                # ran with the quantum; the scheduler lists a transfer only in the plan that admits
+                # its sequence (or grows its table), so the re-planned prefill carries none of
+                # them again and every transfer it does carry belongs to a new admission
                 self._cooperative_pending = self.executor.hydrate_vision(plan) > 0
                 self.cooperative_counters["vision_quanta"] += 1
                 if self._cooperative_pending:
                     self.scheduler.consecutive_prefill_batches = self.scheduler.policy.max_consecutive_prefill
-                    self._replan = plan
                     return StepResult(Phase.IDLE)
             self._cooperative_pending = False
             profile_step_metadata({"phase": plan.phase.value, "batch_size": plan.batch_size, "tokens": plan.num_tokens,

@@ -245,6 +245,7 @@ class Scheduler:
                 continue
             if plan.phase is Phase.PREFILL:
                 seq.num_computed_tokens += plan.slices[i].length
+                self.block_manager.publish_computed_pages(seq)
                 if seq.num_computed_tokens < len(seq) or tok is None:
                     outputs.append(RequestOutput(seq.seq_id, None, False))
                     continue

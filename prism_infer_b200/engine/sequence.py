@@ -51,6 +51,9 @@ class Sequence:
         self.num_computed_tokens = 0      # logical tokens whose KV exists
         self.num_cached_tokens = 0        # logical tokens served from a cache at admission
         self.kv_layout: KVLayout | None = None
+        # (page index, chain hash, token ids) of own full prompt pages whose content hash may be
+        # published to the prefix index once the prefill chunk that fills the page has run
+        self.unpublished_hashes: list[tuple[int, int, tuple[int, ...]]] = []
         self.image_token_id, self.video_token_id = image_token_id, video_token_id
         self.merge_size = merge_size
         self.pixel_values = pixel_values

@@ -92,6 +92,40 @@ def test_prefix_cache_hit_reuses_visual_prefix(tiny):
     llm.exit()
 
 
+def test_cooperative_prefill_keeps_the_transfers_of_requests_admitted_after_the_quantum(tiny):
+    """A decoding sequence, a cold image request (vision quantum first), then a prefix-hit request
+    that arrives between the quantum and the re-planned prefill: its tail-page copy must run."""
+    arch, weights, oracle = tiny
+    tok = load_tokenizer("random:tiny", arch)
+    proc = PatchProcessor(arch)
+    llm = _llm(weights, enable_cooperative_prefill=True)
+    sp = SamplingParams(temperature=0.0, max_tokens=4, ignore_eos=True)
+    known, fresh = _image(5), _image(6)
+    llm.generate_prepared_image_inputs(prepare_image_inputs(proc, tok, [11, 12, 13], [known]), sp)  # stores the prefix
+    text = [3, 4, 5, 6, 7]
+    t_id = llm.add_request(text, SamplingParams(temperature=0.0, max_tokens=12, ignore_eos=True))
+    while llm.scheduler.num_decoding == 0:
+        llm.step_result()
+    cold = prepare_image_inputs(proc, tok, [41, 42], [fresh])
+    c_id = llm.add_prepared_image_request(cold, sp)
+    for _ in range(4):  # the policy may run a decode batch first
+        if llm.step_result().phase.value == "idle":
+            break
+    assert llm.cooperative_counters["vision_quanta"] == 1 and llm.request_state(c_id).value == "prefilling"
+    hit = prepare_image_inputs(proc, tok, [21, 22, 23, 24], [known])
+    h_id = llm.add_prepared_image_request(hit, sp)
+    done = {}
+    while not llm.is_finished():
+        for o in llm.step_result().outputs:
+            if o.finished:
+                done[o.request_id] = list(o.token_ids)
+    assert llm.multimodal_prefix_cache_metadata()["tail_clones"] >= 1
+    assert done[t_id] == oracle.generate_greedy(text, 12)
+    assert done[c_id] == oracle.generate_greedy(cold.input_ids, 4, pixel_values=cold.pixel_values, image_grid_thw=cold.image_grid_thw)
+    assert done[h_id] == oracle.generate_greedy(hit.input_ids, 4, pixel_values=hit.pixel_values, image_grid_thw=hit.image_grid_thw)
+    llm.exit()
+
+
 def test_visual_compaction_frees_pages_and_hits(tiny):
     arch, weights, _ = tiny
     img = _image(4)

@@ -126,12 +126,17 @@ def test_text_prefix_sharing_append_and_cow():
     s1, s2 = text_seq(1, 10), text_seq(2, 10)
     bm.allocate(s1)
     assert s1.num_cached_tokens == 0 and len(s1.block_table) == 3
+    early = text_seq(9, 10)
+    bm.allocate(early)  # s1's pages hold no KV yet: nothing to share
+    assert early.num_cached_tokens == 0 and not set(early.block_table) & set(s1.block_table)
+    bm.deallocate(early)
+    s1.num_computed_tokens = 10
+    assert bm.publish_computed_pages(s1) == 2 and not s1.unpublished_hashes
     bm.allocate(s2)
     assert s2.num_cached_tokens == 8 and s2.block_table[:2] == s1.block_table[:2] and s2.block_table[2] != s1.block_table[2]
     exact = text_seq(3, 8)
     bm.allocate(exact)  # all pages would hit, but the last token must be computed
     assert exact.num_cached_tokens == 4
-    s1.num_computed_tokens = 10
     s1.append_token(5)
     s1.append_token(6)  # 12 tokens: KV row 11 still fits in page 2
     assert not bm.needs_new_page(s1)
@@ -150,7 +155,9 @@ def test_swap_out_and_in_restore_hashes():
     s = text_seq(1, 8)
     bm.allocate(s)
     s.num_computed_tokens = 8
+    bm.publish_computed_pages(s)
     hashes = [bm.gpu.blocks[b].hash for b in s.block_table]
+    assert all(h is not None for h in hashes)
     out_pairs = bm.swap_out(s)
     assert len(out_pairs) == 2 and not s.block_table and len(s.cpu_block_table) == 2 and bm.gpu.num_free == 4
     filler = text_seq(2, 16)
@@ -270,6 +277,51 @@ def test_scheduler_admission_chunking_and_finish():
     run_step(sched)
     _, outs = run_step(sched, [EOS])
     assert outs[0].finish_reason == "eos"
+
+
+def test_text_prefix_pages_are_shared_only_once_computed():
+    """Two identical long prompts under chunked prefill, and a cancel in mid-prefill followed by
+    a resubmission: a page's content hash becomes visible only after the chunk that fills it ran."""
+    sched = Scheduler(cfg(max_num_batched_tokens=32, max_chunk_size=8))
+    a, b = text_seq(1, 30, max_tokens=1), text_seq(2, 33, max_tokens=1)  # same first 30 tokens
+    sched.add(a)
+    sched.add(b)
+    plan, _ = run_step(sched)
+    assert plan.phase is Phase.PREFILL and [s.seq_id for s in plan.seqs] == [1, 2]
+    # b was admitted while a's pages were still empty: no cached tokens, no shared pages
+    assert b.num_cached_tokens == 0 and not set(a.block_table) & set(b.block_table)
+    assert all(sl.start + sl.length <= s.num_computed_tokens for s, sl in zip(plan.seqs, plan.slices))
+    bm = sched.block_manager
+    published = {blk.hash for blk in bm.gpu.blocks if blk.hash is not None}
+    assert len(published) == 2  # the two pages the first 8-token chunk filled, once
+    while not sched.is_finished():
+        run_step(sched)
+    # a third identical prompt arrives after everything was computed: full-page hits
+    c = text_seq(3, 30, max_tokens=1)
+    sched.add(c)
+    run_step(sched)
+    assert c.num_cached_tokens == 28
+    while not sched.is_finished():
+        run_step(sched)
+    assert bm.gpu.num_free == 32
+
+    # cancel after the first chunk: only the computed pages keep a hash
+    sched = Scheduler(cfg(max_num_batched_tokens=8, max_chunk_size=8))
+    bm = sched.block_manager
+    d = text_seq(4, 30, max_tokens=1, base=500)
+    sched.add(d)
+    run_step(sched)
+    assert d.num_computed_tokens == 8
+    pages = list(d.block_table)
+    sched.cancel(4)
+    assert [bm.gpu.blocks[p].hash is not None for p in pages] == [True, True] + [False] * 6
+    e = text_seq(5, 30, max_tokens=1, base=500)
+    sched.add(e)
+    plan, _ = run_step(sched)
+    assert e.num_cached_tokens == 8 and plan.slices[0].start == 8  # revives the two computed pages only
+    while not sched.is_finished():
+        run_step(sched)
+    assert bm.gpu.num_free == 32
 
 
 def test_chunks_never_split_visual_spans_and_stop_at_prefix():
