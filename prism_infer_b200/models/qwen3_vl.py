@@ -465,8 +465,6 @@ class Qwen3VLModel:
         if fuse_norm:
             res_bufs = [torch.empty((T, self.H), dtype=torch.bfloat16, device=x.device) for _ in range(2)]
             flip = 0
-        # decode-sized steps: kernels that leave HBM idle request the next weights into L2
-        pf = x.is_cuda and not meta.is_prefill and T <= 16
         if (self.tp > 1 and x.is_cuda and meta.is_prefill and hasattr(comm, "prefill_fused") and comm.prefill_fused(T)
                 and ops.TP_PREFILL_FUSED and not scoring):
             return self._forward_prefill_fused(x, positions, meta, cache, deepstack, vis_index)
@@ -499,15 +497,11 @@ class Qwen3VLModel:
                 residual, flip = res_bufs[flip], flip ^ 1
                 dense, partials, ticket = comm.row_parallel(act, l.down)
                 continue
-            if pf:
-                ops.prefetch_next(l.qkv, ops.L2_PREFETCH[0])
             h, residual = comm.add_rmsnorm(l.input_norm, t.rms_norm_eps, dense, partials, ticket, residual,
                                            extra, vis_index if extra is not None else None)
             direct = False
             if small and h.is_cuda:
                 qkv_p = ops.linear_partial(h, l.qkv, ops.choose_splits(l.qkv.shape[0], self.H, T))
-                if pf:
-                    ops.prefetch_next(l.o, ops.L2_PREFETCH[1])
                 q = ops.qk_norm_rope_store(qkv=None, partials=qkv_p, positions=positions, q_weight=l.q_norm, k_weight=l.k_norm,
                                            num_heads=self.Hq, num_kv_heads=self.Hkv, head_dim=self.D, theta=t.rope_theta,
                                            section=t.mrope_section, eps=t.rms_norm_eps, slots=meta.slots, cache=cache, layer=i)
@@ -531,13 +525,9 @@ class Qwen3VLModel:
             elif meta.is_prefill:
                 a = ops.paged_prefill_attention(q, cache, i, meta.cu_seqlens_q, meta.kv_lens, meta.block_tables, meta.max_q_len)
             else:
-                if pf:
-                    ops.prefetch_next(l.gate_up, ops.L2_PREFETCH[2])
                 a = ops.paged_decode_attention(q, cache, i, meta.block_tables, meta.context_lens, nsplit=meta.nsplit,
                                                workspace=meta.workspace)
             dense, partials, ticket = comm.row_parallel(a.view(T, self.Hq * self.D), l.o, stages=ops.O_PROJ_STAGES if small else 0)
-            if pf:
-                ops.prefetch_next(l.down, ops.L2_PREFETCH[3])
             h, residual = comm.add_rmsnorm(l.post_norm, t.rms_norm_eps, dense, partials, ticket, residual)
             if small and h.is_cuda and self.I // 128 < 96:
                 # too few 128-row tiles for the dual-accumulator kernel to keep enough SMs

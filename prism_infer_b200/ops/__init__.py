@@ -261,28 +261,6 @@ PERSISTENT_MIN_TOKENS = int(_os.environ.get("PRISM_PERSISTENT_MIN_TOKENS", "512"
 SMALL_TILE_SMEM_CAP = int(_os.environ.get("PRISM_SMALL_TILE_SMEM", "0"))
 
 
-# fractions of (qkv, o, gate_up, down) weight columns requested into L2 by the HBM-idle kernels
-# that precede them in a decode step (add+RMSNorm, QK-norm/rotary/store, attention, add+RMSNorm).
-# Off by default: measured on the headline step it cost 0.07-0.4 ms (3.88 ms without).
-L2_PREFETCH = tuple(float(v) for v in _os.environ.get("PRISM_L2_PREFETCH", "0,0,0,0").split(","))
-
-
-L2_PREFETCH_HELPERS = int(_os.environ.get("PRISM_L2_PREFETCH_HELPERS", "120"))
-
-
-def prefetch_next(w: torch.Tensor, fraction: float = 1.0) -> None:
-    """Ask the next prefetch-capable kernel (add_rmsnorm, qk_norm_rope_store,
-    paged_decode_attention) to request the first ``fraction`` of every row of ``w`` into L2."""
-    if fraction <= 0.0 or not w.is_cuda:
-        return
-    row_bytes = w.shape[1] * w.element_size()
-    stride = w.stride(0) * w.element_size()
-    if row_bytes % 128 or stride % 128 or w.data_ptr() % 128:
-        return
-    nbytes = min(row_bytes, max(128, int(row_bytes * fraction) // 128 * 128))
-    native.call("prism_set_next_prefetch", _p(w), stride, w.shape[0], nbytes, L2_PREFETCH_HELPERS)
-
-
 def apply_tuning() -> None:
     """Push the process-wide launch tuning into the native library (CUDA only)."""
     native.call("prism_gemm_set_small_tile_smem_cap", SMALL_TILE_SMEM_CAP)
@@ -669,7 +647,7 @@ def paged_decode_attention(
         "prism_paged_decode", _p(q), _p(cache.k(layer)), _p(cache.v(layer)), _p(cache.k_scale(layer)),
         _p(cache.v_scale(layer)), _p(block_tables), _p(context_lens), _p(part_o), _p(part_ml), _p(out),
         _p(_decode_counters(q.device, B * cache.num_kv_heads)) if nsplit > 1 else None,
-        B, Hq, cache.num_kv_heads, D, cache.page, block_tables.shape[1], nsplit, cache.mode, scale,
+        B, Hq, cache.num_kv_heads, D, cache.page, block_tables.shape[1], cache.num_blocks, nsplit, cache.mode, scale,
         1 if (use_mma if use_mma is not None else B >= DECODE_MMA_MIN_BATCH) else 0, _s(), _pdl(),
     )
     return out
@@ -714,7 +692,7 @@ def varlen_attention(
         return out
     native.call(
         "prism_flash_attention", _p(q), q.stride(0), _p(out), out.stride(0), _p(cu_seqlens), _p(k), _p(v),
-        k.stride(0), None, None, None, None, None, None, 0, 1, cu_seqlens.shape[0] - 1, int(max_len), Hq, Hkv, D,
+        k.stride(0), None, None, None, None, None, None, 0, 0, 1, cu_seqlens.shape[0] - 1, int(max_len), Hq, Hkv, D,
         0, 1 if causal else 0, scale, _s(), _pdl(),
     )
     return out
@@ -760,7 +738,8 @@ def paged_prefill_attention(
     native.call(
         "prism_flash_attention", _p(q), q.stride(0), _p(out), out.stride(0), _p(cu_seqlens_q), None, None, 0,
         _p(cache.k(layer)), _p(cache.v(layer)), _p(cache.k_scale(layer)), _p(cache.v_scale(layer)),
-        _p(block_tables), _p(kv_lens), block_tables.shape[1], cache.page, cu_seqlens_q.shape[0] - 1, int(max_q_len),
+        _p(block_tables), _p(kv_lens), block_tables.shape[1], cache.num_blocks, cache.page, cu_seqlens_q.shape[0] - 1,
+        int(max_q_len),
         Hq, cache.num_kv_heads, D, 1 if cache.mode == KV_BF16 else 2, 1, scale, _s(), _pdl(),
     )
     return out

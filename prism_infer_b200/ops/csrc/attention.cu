@@ -43,9 +43,30 @@ struct DecodeArgs {
   bf16* out;                // [B][Hq][D] (written directly when nsplit == 1)
   int* counters;            // [B * Hkv] zero-initialised, self-resetting; null = separate combine kernel
   int Hq, Hkv, page, max_blocks, nsplit;
+  int num_blocks;           // pages in the cache; <= 0: unknown, only holes (< 0) are skipped
   float scale;
-  PrefetchSpec pf;
 };
+
+// Page-table guards shared by the decode and prefill kernels.  A context longer than the
+// table can describe is cut to the table's reach, and a page id at or beyond the cache is
+// treated as a hole; both are recorded in the status word (PRISM_ERR_BOUNDS) and the access
+// is skipped, so a stale table or an over-long length costs wrong tokens that the engine
+// reports, never an out-of-range read.
+__device__ __forceinline__ int clamp_context(int ctx, int max_blocks, int page) {
+  const long long reach = (long long)max_blocks * page;
+  if ((long long)ctx > reach) {
+    if (threadIdx.x == 0) prism_report(PRISM_ERR_BOUNDS, 1);
+    return (int)reach;
+  }
+  return ctx < 0 ? 0 : ctx;
+}
+__device__ __forceinline__ int checked_page(int blk, int num_blocks) {
+  if (num_blocks > 0 && blk >= num_blocks) {
+    prism_report(PRISM_ERR_BOUNDS, 2);
+    return -1;
+  }
+  return blk;
+}
 
 // KV8 = true: fp8 payload (16 elements per lane), false: bf16 payload (8 elements per lane)
 template <int D, int G, bool KV8>
@@ -60,8 +81,7 @@ __global__ void __launch_bounds__(128) paged_decode_kernel(const DecodeArgs a) {
   const int part = lane % LPT;        // which EPL-wide slice of the head dim
   pdl_launch_dependents();
   pdl_wait();
-  l2_prefetch_rows(a.pf, (blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x, gridDim.x * gridDim.y * gridDim.z);
-  const int ctx = a.context_lens[b];
+  const int ctx = clamp_context(a.context_lens[b], a.max_blocks, a.page);
   const int per_split = ((ctx + a.nsplit - 1) / a.nsplit + TPW * NWARP * 4 - 1) / (TPW * NWARP * 4) * (TPW * NWARP * 4);
   const int j_begin = split * per_split;
   const int j_end = min(ctx, j_begin + per_split);
@@ -95,7 +115,7 @@ __global__ void __launch_bounds__(128) paged_decode_kernel(const DecodeArgs a) {
     for (int u = 0; u < UNR; ++u) {
       const int j = j0 + u * TPW + slot;
       int blk = -1;
-      if (j < j_end) blk = bt[j / a.page];
+      if (j < j_end) blk = checked_page(bt[j / a.page], a.num_blocks);
       valid[u] = blk >= 0;
       kr[u] = make_uint4(0, 0, 0, 0);
       vr[u] = make_uint4(0, 0, 0, 0);
@@ -304,6 +324,7 @@ struct FlashArgs {
   const int* block_tables;
   const int* kv_lens;       // [S] total keys visible to the sequence (history + this chunk)
   int max_blocks, page;
+  int num_blocks;           // pages in the cache; <= 0: unknown
   int Hq, Hkv;
   int causal;
   float scale;
@@ -367,7 +388,7 @@ __global__ void __launch_bounds__(BM * 2, MODE == 2 ? (BM == 128 ? 1 : 2) : (BM 
   const int q_len = a.cu_q[seq + 1] - q_start;
   const int q0 = qt * BM;
   if (q0 >= q_len) return;
-  const int kv_len = (MODE == 0) ? q_len : a.kv_lens[seq];
+  const int kv_len = (MODE == 0) ? q_len : clamp_context(a.kv_lens[seq], a.max_blocks, a.page);
   const int kvh = head / (a.Hq / a.Hkv);
   const int pos_off = kv_len - q_len;  // absolute key position of local query 0
   const int* bt = (MODE == 0) ? nullptr : a.block_tables + (size_t)seq * a.max_blocks;
@@ -413,7 +434,7 @@ __global__ void __launch_bounds__(BM * 2, MODE == 2 ? (BM == 128 ? 1 : 2) : (BM 
             ksrc = a.k + off;
             vsrc = a.v + off;
           } else {
-            const int blk = bt[j / a.page];
+            const int blk = checked_page(bt[j / a.page], a.num_blocks);
             ok = blk >= 0;
             if (ok) {
               const size_t row = ((size_t)blk * a.Hkv + kvh) * a.page + (j % a.page);
@@ -440,7 +461,7 @@ __global__ void __launch_bounds__(BM * 2, MODE == 2 ? (BM == 128 ? 1 : 2) : (BM 
         const int r = i / CHUNKS, c = i % CHUNKS;
         const int j = j0 + r;
         if (j < kv_len) {
-          const int blk = bt[j / a.page];
+          const int blk = checked_page(bt[j / a.page], a.num_blocks);
           if (blk >= 0) {
             const size_t row = ((size_t)blk * a.Hkv + kvh) * a.page + (j % a.page);
             st_k[it] = *reinterpret_cast<const uint2*>(reinterpret_cast<const uint8_t*>(a.k_cache) + row * HD_REAL + c * 8);
@@ -637,8 +658,7 @@ __global__ void __launch_bounds__(128) paged_decode_mma_kernel(const DecodeArgs 
   const int g = lane >> 2, t4 = lane & 3;
   pdl_launch_dependents();
   pdl_wait();
-  l2_prefetch_rows(a.pf, (blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x, gridDim.x * gridDim.y * gridDim.z);
-  const int ctx = a.context_lens[b];
+  const int ctx = clamp_context(a.context_lens[b], a.max_blocks, a.page);
   const int per_split = ((ctx + a.nsplit - 1) / a.nsplit + BN - 1) / BN * BN;
   const int j_begin = split * per_split;
   const int j_end = min(ctx, j_begin + per_split);
@@ -682,7 +702,7 @@ __global__ void __launch_bounds__(128) paged_decode_mma_kernel(const DecodeArgs 
       ksc[u] = -1.0f;  // marks an absent row
       vsc[u] = 1.0f;
       if (j < j_end) {
-        const int blk = bt[j / a.page];
+        const int blk = checked_page(bt[j / a.page], a.num_blocks);
         if (blk >= 0) {
           const size_t row = ((size_t)blk * a.Hkv + kvh) * a.page + (j % a.page);
           const size_t off = row * D * (KV8 ? 1 : 2) + (size_t)c * 16;
@@ -947,10 +967,10 @@ int dispatch_decode(const DecodeArgs& a, int B, cudaStream_t stream, bool pdl, b
 PRISM_API int prism_paged_decode(const void* q, const void* k_cache, const void* v_cache, const void* k_scale,
                                  const void* v_scale, const void* block_tables, const void* context_lens, void* part_o,
                                  void* part_ml, void* out, void* counters, int B, int Hq, int Hkv, int D, int page,
-                                 int max_blocks, int nsplit, int kv_mode, float scale, int use_mma, void* stream,
-                                 int pdl) {
+                                 int max_blocks, int num_blocks, int nsplit, int kv_mode, float scale, int use_mma,
+                                 void* stream, int pdl) {
   if (B <= 0) return 0;
-  if (Hq % Hkv) return -1;
+  if (Hq <= 0 || Hkv <= 0 || Hq % Hkv || page <= 0 || max_blocks <= 0) return -1;
   DecodeArgs a;
   a.q = (const bf16*)q;
   a.k_cache = k_cache;
@@ -967,9 +987,9 @@ PRISM_API int prism_paged_decode(const void* q, const void* k_cache, const void*
   a.Hkv = Hkv;
   a.page = page;
   a.max_blocks = max_blocks;
+  a.num_blocks = num_blocks;
   a.nsplit = nsplit < 1 ? 1 : (nsplit > 32 ? 32 : nsplit);
   a.scale = scale;
-  a.pf = prism_take_prefetch();
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   int rc;
   const bool mma = use_mma != 0;
@@ -989,11 +1009,12 @@ PRISM_API int prism_paged_decode(const void* q, const void* k_cache, const void*
 PRISM_API int prism_flash_attention(const void* q, long long q_stride, void* out, long long o_stride, const void* cu_q,
                                     const void* k, const void* v, long long kv_stride, const void* k_cache,
                                     const void* v_cache, const void* k_scale, const void* v_scale,
-                                    const void* block_tables, const void* kv_lens, int max_blocks, int page, int S,
-                                    int max_q_len, int Hq, int Hkv, int hd, int mode, int causal, float scale,
-                                    void* stream, int pdl) {
+                                    const void* block_tables, const void* kv_lens, int max_blocks, int num_blocks,
+                                    int page, int S, int max_q_len, int Hq, int Hkv, int hd, int mode, int causal,
+                                    float scale, void* stream, int pdl) {
   if (S <= 0 || max_q_len <= 0) return 0;
-  if (Hq % Hkv) return -1;
+  if (Hq <= 0 || Hkv <= 0 || Hq % Hkv) return -1;
+  if (mode != 0 && (page <= 0 || max_blocks <= 0)) return -1;
   FlashArgs a;
   a.q = (const bf16*)q;
   a.q_stride = q_stride;
@@ -1010,6 +1031,7 @@ PRISM_API int prism_flash_attention(const void* q, long long q_stride, void* out
   a.block_tables = (const int*)block_tables;
   a.kv_lens = (const int*)kv_lens;
   a.max_blocks = max_blocks;
+  a.num_blocks = num_blocks;
   a.page = page;
   a.Hq = Hq;
   a.Hkv = Hkv;
@@ -1055,7 +1077,8 @@ int noalloc_fail(int code, const char* msg) {
 PRISM_API const char* prism_noalloc_last_error() { return g_noalloc_error; }
 
 PRISM_API long long prism_paged_decode_noalloc_scratch_bytes(int B, int Hq, int D, int nsplit) {
-  if (nsplit <= 1) return 0;
+  if (nsplit > 32) nsplit = 32;  // the kernels never split a context more than 32 ways
+  if (nsplit <= 1 || B <= 0 || Hq <= 0 || D <= 0) return 0;
   const long long rows = (long long)B * Hq * nsplit;
   const long long part_o = (rows * D * 4 + 255) / 256 * 256;
   return part_o + rows * 2 * 4;
@@ -1063,11 +1086,18 @@ PRISM_API long long prism_paged_decode_noalloc_scratch_bytes(int B, int Hq, int 
 
 PRISM_API int prism_paged_decode_noalloc(const void* q, const void* k_cache, const void* v_cache, const void* k_scale,
                                          const void* v_scale, const void* block_tables, const void* context_lens,
-                                         void* out, int B, int Hq, int Hkv, int D, int page, int max_blocks, int nsplit,
-                                         int kv_mode, float scale, void* stream) {
+                                         void* out, int B, int Hq, int Hkv, int D, int page, int max_blocks,
+                                         int num_blocks, int nsplit, int kv_mode, float scale, void* stream) {
   g_noalloc_error[0] = 0;
   if (B <= 0) return 0;
+  if (Hq <= 0 || Hkv <= 0 || Hq % Hkv != 0)
+    return noalloc_fail(-13, "prism_paged_decode_noalloc: Hq and Hkv must be positive and Hq a multiple of Hkv");
+  if (D != 64 && D != 128) return noalloc_fail(-14, "prism_paged_decode_noalloc: head dimension must be 64 or 128");
+  if (page <= 0 || max_blocks <= 0)
+    return noalloc_fail(-15, "prism_paged_decode_noalloc: page and max_blocks must be positive");
+  if (kv_mode < 0 || kv_mode > 2) return noalloc_fail(-16, "prism_paged_decode_noalloc: kv_mode must be 0, 1 or 2");
   if (nsplit < 1) nsplit = 1;
+  if (nsplit > 32) nsplit = 32;  // as prism_paged_decode does, before the scratch is sized
   const long long need = prism_paged_decode_noalloc_scratch_bytes(B, Hq, D, nsplit);
   if (need > (long long)PRISM_NOALLOC_SCRATCH_BYTES) {
     char msg[256];
@@ -1102,7 +1132,7 @@ PRISM_API int prism_paged_decode_noalloc(const void* q, const void* k_cache, con
   // (empty splits store max = -inf, sum = 0), so nothing has to be cleared between calls.
   const int rc = prism_paged_decode(q, k_cache, v_cache, k_scale, v_scale, block_tables, context_lens,
                                     nsplit > 1 ? part_o : nullptr, nsplit > 1 ? part_ml : nullptr, out, nullptr, B, Hq, Hkv,
-                                    D, page, max_blocks, nsplit, kv_mode, scale, 0, stream, 0);
+                                    D, page, max_blocks, num_blocks, nsplit, kv_mode, scale, 0, stream, 0);
   if (rc != 0) return noalloc_fail(rc, "prism_paged_decode_noalloc: kernel launch failed");
   return 0;
 }

@@ -84,34 +84,6 @@ __device__ __forceinline__ void pdl_launch_dependents() {
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 }
 
-// ---- L2 prefetch of a weight matrix the next GEMM will stream ---------------------------
-// A kernel that leaves HBM idle (norms, rotary + KV store, decode attention) can carry one of
-// these: `rows` runs of `bytes` bytes, `stride` bytes apart, are requested into L2 right after
-// the kernel's dependency wait, so the following weight-streaming GEMM finds them on chip.
-struct PrefetchSpec {
-  const char* base;
-  long long stride;
-  int rows;
-  int bytes;    // multiple of 128; base and stride 128-byte aligned
-  int helpers;  // extra CTAs a narrow kernel adds to its grid just to issue the requests
-};
-// One SM sustains only on the order of 100 GB/s of prefetch requests, so the requests are
-// spread over every CTA of the grid (narrow kernels add helper CTAs).  Per-line
-// prefetch.global.L2 retires at issue, so the kernel does not stay open for the fills.
-__device__ __forceinline__ void l2_prefetch_rows(const PrefetchSpec& p, int cta, int n_ctas) {
-  if (p.rows <= 0) return;
-  const int lines = p.bytes >> 7;
-  const long long total = (long long)p.rows * lines;
-  const long long n = (long long)n_ctas * blockDim.x;
-  for (long long i = (long long)cta * blockDim.x + threadIdx.x; i < total; i += n) {
-    const long long r = i / lines, l = i - r * lines;
-    asm volatile("prefetch.global.L2 [%0];" ::"l"(p.base + r * p.stride + (l << 7)) : "memory");
-  }
-}
-// Returns the spec registered by prism_set_next_prefetch and clears it (host side, one
-// consumer per registration).
-PrefetchSpec prism_take_prefetch();
-
 // ---- shared memory address / mbarrier -----------------------------------------------
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));

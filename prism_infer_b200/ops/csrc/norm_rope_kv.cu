@@ -61,7 +61,6 @@ struct AddNormArgs {
   int point;
   int T;
   int packed;  // 1: partials are 8-byte {fp32 value, sequence} words polled until sequence == *epoch + point
-  PrefetchSpec pf;
 };
 
 // Bounded acquire-spin on a flag another GPU writes.  Returns false after
@@ -85,10 +84,6 @@ __global__ void __launch_bounds__(1024) add_rmsnorm_kernel(const AddNormArgs a) 
   const int t = blockIdx.x;
   const int H = a.H;
   pdl_launch_dependents();
-  if (t >= a.T) {  // helper CTA: weights are static, no need to wait for the previous kernel
-    l2_prefetch_rows(a.pf, t - a.T, gridDim.x - a.T);
-    return;
-  }
   pdl_wait();
   if (a.n_wait > 0) {
     if ((int)threadIdx.x < a.n_wait) wait_flag_ge(a.wait_flags + threadIdx.x, *a.epoch + (unsigned long long)a.point, threadIdx.x);
@@ -521,8 +516,6 @@ struct QkvArgs {
   int apply_norm, apply_rope;
   float eps;
   int k_writeback;          // 1: the normalised, rotated K also replaces its source in qkv (bf16 source only)
-  int real_ctas;
-  PrefetchSpec pf;
 };
 
 constexpr float FP8_MAX = 448.0f;
@@ -536,10 +529,6 @@ __global__ void __launch_bounds__(256) qk_norm_rope_store_kernel(const QkvArgs a
   const int lane = threadIdx.x & 31;
   const int heads = a.Hq + 2 * a.Hkv;
   pdl_launch_dependents();
-  if ((int)blockIdx.x >= a.real_ctas) {  // helper CTA
-    l2_prefetch_rows(a.pf, blockIdx.x - a.real_ctas, gridDim.x - a.real_ctas);
-    return;
-  }
   pdl_wait();
   if (gw >= a.T * heads) return;
   const int t = gw / heads;
@@ -900,9 +889,6 @@ static int add_rmsnorm_impl(const void* partials, long long slab_stride, int P, 
   a.epoch = (const unsigned long long*)epoch;
   a.point = point;
   a.T = T;
-  a.pf = prism_take_prefetch();
-  const int helpers = a.pf.rows > 0 ? a.pf.helpers : 0;
-  if (helpers == 0) a.pf.rows = 0;
   const size_t smem = (size_t)H * sizeof(float);
   if (smem > 48 * 1024) {
     cudaError_t e = cudaFuncSetAttribute(add_rmsnorm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -913,7 +899,6 @@ static int add_rmsnorm_impl(const void* partials, long long slab_stride, int P, 
                                     reinterpret_cast<unsigned long long>(residual_out) | reinterpret_cast<unsigned long long>(extra) |
                                     reinterpret_cast<unsigned long long>(weight) | reinterpret_cast<unsigned long long>(out);
     if (T >= 64 && P == 0 && x_in != nullptr && n_wait == 0 && H % 8 == 0 && H <= 8192 && (addr & 15ull) == 0) {
-      a.pf.rows = 0;
       dim3 grid((T + 7) / 8), block(256);
       if (H <= 2048) return (int)prism_launch(add_rmsnorm_rows_kernel<8>, grid, block, 0, STREAM(stream), pdl != 0, a);
       if (H <= 4096) return (int)prism_launch(add_rmsnorm_rows_kernel<16>, grid, block, 0, STREAM(stream), pdl != 0, a);
@@ -923,7 +908,7 @@ static int add_rmsnorm_impl(const void* partials, long long slab_stride, int P, 
   // few rows: one wide CTA per row so every element has its own thread; many rows: 256 threads
   int threads = T <= 64 ? 1024 : 256;
   while (threads > 32 && threads * 4 > H * 2) threads >>= 1;
-  return (int)prism_launch(add_rmsnorm_kernel, dim3(T + helpers), dim3(threads), smem, STREAM(stream), pdl != 0, a);
+  return (int)prism_launch(add_rmsnorm_kernel, dim3(T), dim3(threads), smem, STREAM(stream), pdl != 0, a);
 }
 
 PRISM_API int prism_add_rmsnorm(const void* partials, long long slab_stride, int P, const void* x_in,
@@ -1040,16 +1025,11 @@ PRISM_API int prism_qk_norm_rope_store(const void* qkv, const void* partials, lo
   a.apply_rope = apply_rope;
   a.eps = eps;
   a.k_writeback = k_writeback;
-  a.pf = prism_take_prefetch();
   const int warps = T * (Hq + 2 * Hkv);
   const int wpb = 8;
-  a.real_ctas = (warps + wpb - 1) / wpb;
-  const int helpers = a.pf.rows > 0 ? a.pf.helpers : 0;
-  if (helpers == 0) a.pf.rows = 0;
-  dim3 grid(a.real_ctas + helpers), block(wpb * 32);
+  dim3 grid((warps + wpb - 1) / wpb), block(wpb * 32);
   if (D == 128 && qkv != nullptr && T >= 64 && (row_stride % 2) == 0 && (q_stride % 2) == 0 &&
       ((reinterpret_cast<unsigned long long>(qkv) | reinterpret_cast<unsigned long long>(q_out)) & 3ull) == 0) {
-    a.pf.rows = 0;
     return (int)prism_launch(qk_norm_rope_store_token_kernel, dim3(T), dim3(256), 0, STREAM(stream), pdl != 0, a);
   }
   if (D == 128) return (int)prism_launch(qk_norm_rope_store_kernel<128>, grid, block, 0, STREAM(stream), pdl != 0, a);

@@ -31,7 +31,12 @@
 //    left there.  The kernels overwrite every cell they later read, so no clearing is
 //    needed, but two calls whose kernels overlap on the GPU (different streams without an
 //    ordering between them) race on the array: serialise them.
-//  * Returns 0 on success, a positive cudaError_t, or a negative validation code.
+//  * num_blocks is the number of pages in the cache (0 if unknown).  A page id at or beyond
+//    it, or a context longer than max_blocks * page, is skipped and recorded in the
+//    library's status word (prism_status_attn) instead of being read.
+//  * nsplit is clamped to 1..32 before the scratch requirement is computed.
+//  * Returns 0 on success, a positive cudaError_t, or a negative validation code
+//    (-10 too large, -13..-16 invalid Hq/Hkv, head dimension, page geometry or kv_mode).
 #pragma once
 
 #ifdef __cplusplus
@@ -42,8 +47,8 @@ extern "C" {
 
 int prism_paged_decode_noalloc(const void* q, const void* k_cache, const void* v_cache, const void* k_scale,
                                const void* v_scale, const void* block_tables, const void* context_lens, void* out,
-                               int B, int Hq, int Hkv, int D, int page, int max_blocks, int nsplit, int kv_mode,
-                               float scale, void* stream);
+                               int B, int Hq, int Hkv, int D, int page, int max_blocks, int num_blocks, int nsplit,
+                               int kv_mode, float scale, void* stream);
 
 long long prism_paged_decode_noalloc_scratch_bytes(int B, int Hq, int D, int nsplit);
 

@@ -37,8 +37,8 @@ _SIGNATURES = {
     "prism_indexed_add": "pppiipi",
     "prism_pos_embed_add": "ppppiipi",
     "prism_vit_rope": "pppiiipi",
-    "prism_paged_decode": "pppppppppppiiiiiiiifipi",
-    "prism_flash_attention": "plplppplppppppiiiiiiiiifpi",
+    "prism_paged_decode": "pppppppppppiiiiiiiiifipi",
+    "prism_flash_attention": "plplppplppppppiiiiiiiiiifpi",
     "prism_kv_page_copy": "ppllippllpppiiiip",
     "prism_kv_compact": "pliplppppiiiip",
     "prism_sample": "pllipppiilupppipi",
@@ -55,7 +55,6 @@ _SIGNATURES = {
     "prism_gemm_set_small_tile_smem_cap": "i",
     "prism_gemm_set_persistent_min_tokens": "i",
     "prism_gemm_set_persistent_rowmajor": "i",
-    "prism_set_next_prefetch": "pliii",
     "prism_gemm_wx_actx": "ppiiillilplippiilpppi",
     "prism_gemm_wx_allgather": "ppiiillllpippiilpppi",
     "prism_signal_peers": "piilp",

@@ -220,6 +220,37 @@ def test_paged_decode(cuda_device, mode, D, Hq, Hkv, page, nsplit, use_mma):
     assert err.max() < 2e-2 and err.mean() < 2e-3, (err.max(), err.mean())
 
 
+@pytest.mark.parametrize("use_mma", [False, True])
+def test_paged_attention_skips_out_of_range_pages_and_reports(cuda_device, use_mma):
+    """A context longer than the page table can describe and a page id beyond the cache are not
+    read: the kernels cut the context, treat the page as a hole and set the status word."""
+    D, Hq, Hkv, page, blocks, maxblk = 64, 4, 2, 16, 4, 3
+    cg, cc = _fill_cache(ops.KV_FP8_SCALED, 1, blocks, Hkv, page, D, seed=41)
+    q = rand_bf16(2, Hq, D, seed=42)
+    bt = torch.tensor([[0, 1, 2], [3, 7, 1]], dtype=torch.int32)       # 7 >= blocks
+    ctx = torch.tensor([100, 40], dtype=torch.int32)                   # 100 > maxblk * page
+    yg = ops.paged_decode_attention(q.cuda(), cg, 0, bt.cuda(), ctx.cuda(), nsplit=2, use_mma=use_mma)
+    torch.cuda.synchronize()
+    st = native.read_status()["attn"]
+    assert st[0] == 3 and st[3] >= 2, st
+    bt_ok = torch.tensor([[0, 1, 2], [3, -1, 1]], dtype=torch.int32)
+    yc = ops.paged_decode_attention(q.float(), cc, 0, bt_ok, torch.tensor([48, 40], dtype=torch.int32))
+    err = (yg.float().cpu() - yc).abs()
+    assert err.max() < 2e-2, err.max()
+    # paged prefill: same guards
+    cu = torch.tensor([0, 3, 5], dtype=torch.int32)
+    qp = rand_bf16(5, Hq, D, seed=43)
+    kv = torch.tensor([35, 24], dtype=torch.int32)
+    bt2 = torch.tensor([[0, 9, 2], [3, 1, -1]], dtype=torch.int32)     # 9 >= blocks
+    yg = ops.paged_prefill_attention(qp.cuda(), cg, 0, cu.cuda(), kv.cuda(), bt2.cuda(), 3)
+    torch.cuda.synchronize()
+    st = native.read_status()["attn"]
+    assert st[0] == 3, st
+    bt2_ok = torch.tensor([[0, -1, 2], [3, 1, -1]], dtype=torch.int32)
+    yc = ops.paged_prefill_attention(qp.float(), cc, 0, cu, kv, bt2_ok, 3)
+    assert (yg.float().cpu() - yc).abs().max() < 3e-2
+
+
 @pytest.mark.parametrize("hd,Hq,Hkv", [(128, 8, 2), (64, 4, 2), (72, 16, 16), (32, 4, 4)])
 @pytest.mark.parametrize("causal", [False, True])
 def test_varlen_attention(cuda_device, hd, Hq, Hkv, causal):
