@@ -116,7 +116,7 @@ def main() -> None:
     from prism_infer_b200.engine.contracts import Phase
     from prism_infer_b200.engine.vl_inputs import PatchProcessor, prepare_image_inputs
     from prism_infer_b200.ops import native
-    from prism_infer_b200.parallel.launch import bench_barrier, max_over_ranks, rank_info
+    from prism_infer_b200.parallel.tp_group import rank_info
 
     rank, world = rank_info()
     if world > 1 and world != args.gpus:
@@ -159,7 +159,7 @@ def main() -> None:
     meta = llm.graph_metadata()
     sampler = ClockSampler(torch.cuda.current_device())
     sampler.start()
-    bench_barrier(llm)
+    llm.barrier()  # every rank's device idle before the timed region
     native.reset_launch_count()
     t0 = time.perf_counter()
     for _ in range(K):
@@ -167,8 +167,7 @@ def main() -> None:
     torch.cuda.synchronize()
     e2e_ms = (time.perf_counter() - t0) * 1e3 / K
     # ---- device time: K back-to-back launches of the same decode graph ------------------
-    device_ms = llm.time_decode_graph(K)
-    device_ms = max_over_ranks(llm, device_ms)
+    device_ms = llm.time_decode_graph(K)  # maximum over ranks
     clocks = sampler.stop()
     launches = int(meta.get("launches_per_decode_graph", {}).get(str(max(1, args.batch)), 0)) * K
     stage_bytes = int(meta.get("staging_bytes", {}).get(str(max(1, args.batch)), 0))

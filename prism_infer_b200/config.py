@@ -358,6 +358,7 @@ _RANDOM_ARCHS = {
     "tiny": Qwen3VLArch.tiny,
     "qwen3-vl-8b": Qwen3VLArch.qwen3_vl_8b,
     "qwen3_vl_8b": Qwen3VLArch.qwen3_vl_8b,
+    "qwen3-vl-8b-2layer": Qwen3VLArch.qwen3_vl_8b_2layer,
     # profiling aids: the language-model compute of ONE rank of an n-way tensor-parallel group
     # (heads, KV heads, MLP width and vocabulary divided by n), run without any exchange
     "qwen3-vl-8b-tp2-shard": lambda: Qwen3VLArch.qwen3_vl_8b().rank_shard(2),

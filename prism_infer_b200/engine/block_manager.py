@@ -27,6 +27,7 @@ from .block_pool import CpuBlockPool, GpuBlockPool, OutOfBlocks
 from .contracts import KVTransferPlan
 from .kv_layout import CompactionPlan, KVLayout
 from .sequence import Sequence
+from ..observability import emit_kv_event
 
 
 def chain_hash(token_ids: Seq[int], prefix: int | None) -> int:
@@ -93,16 +94,36 @@ class BlockManager:
         self.entries: dict[str, PrefixEntry] = {}
         self.counters = PrefixCacheCounters()
         self._clock = 0
+        self._entry_pages: set[int] = set()   # pages held by some prefix entry
+        self._evictable = 0                   # of those, pages no sequence borrows
         Sequence.block_size = page
 
     # ------------------------------------------------------------------ capacity
+    # A page held by a prefix entry can be reclaimed when the entry is its only holder.  The count
+    # of such pages is kept up to date where reference counts of entry pages change (store, hit,
+    # release of a borrower, eviction), because ``can_append`` asks for it once per sequence
+    # and decode step.
+    def _retain(self, page: int) -> None:
+        if page in self._entry_pages and self.gpu.blocks[page].ref_count == 1:
+            self._evictable -= 1
+        self.gpu.retain(page)
+
+    def _release(self, page: int) -> None:
+        self.gpu.release(page)
+        if page in self._entry_pages and self.gpu.blocks[page].ref_count == 1:
+            self._evictable += 1
+
     def _evictable_pages(self) -> int:
-        return sum(1 for e in self.entries.values() for p in e.pages if self.gpu.blocks[p].ref_count == 1)
+        return self._evictable
+
+    def _freed_by_eviction(self, entry: PrefixEntry) -> int:
+        return sum(1 for p in entry.pages if self.gpu.blocks[p].ref_count == 1)
 
     def _ensure_free(self, n: int, protect: str | None = None) -> bool:
-        """Evict prefix entries until ``n`` pages are free."""
+        """Evict prefix entries, lowest score first, until ``n`` pages are free.  An entry whose
+        pages are all still borrowed by running sequences would free nothing: it stays."""
         while self.gpu.num_free < n:
-            victims = [e for e in self.entries.values() if e.cache_id != protect]
+            victims = [e for e in self.entries.values() if e.cache_id != protect and self._freed_by_eviction(e) > 0]
             if not victims:
                 return False
             victim = min(victims, key=lambda e: (e.score(), e.last_use))
@@ -110,10 +131,16 @@ class BlockManager:
         return True
 
     def _evict(self, entry: PrefixEntry) -> None:
+        freed = 0
         for p in entry.pages:
+            if self.gpu.blocks[p].ref_count == 1:
+                self._evictable -= 1
+                freed += 1
+            self._entry_pages.discard(p)
             self.gpu.release(p)
         del self.entries[entry.cache_id]
         self.counters.evictions += 1
+        emit_kv_event("evict", cache_id=entry.cache_id, pages=len(entry.pages), freed=freed, hits=entry.hits)
 
     def num_free_with_eviction(self) -> int:
         return self.gpu.num_free + self._evictable_pages()
@@ -179,12 +206,12 @@ class BlockManager:
         table: list[int] = []
         try:
             for p in entry.pages[:n_full]:
-                self.gpu.retain(p)
+                self._retain(p)
                 table.append(p)
             fresh = self.gpu.allocate_many(fresh_needed)
         except OutOfBlocks:
             for p in table:
-                self.gpu.release(p)
+                self._release(p)
             return None
         table.extend(fresh)
         copies: tuple[tuple[int, int, int], ...] = ()
@@ -201,6 +228,8 @@ class BlockManager:
         self.counters.hits += 1
         self.counters.tokens_reused += entry.prefix_len
         self.counters.pages_shared += n_full
+        emit_kv_event("prefix_hit", seq_id=seq.seq_id, cache_id=entry.cache_id, tokens=entry.prefix_len, shared_pages=n_full,
+                      fresh_pages=len(fresh), tail_rows=entry.tail_rows)
         return KVTransferPlan(copy_prefix=copies)
 
     def _allocate_dense(self, seq: Sequence, *, share: bool) -> None:
@@ -220,7 +249,7 @@ class BlockManager:
                 if bid is not None and (i + 1) * self.page >= len(seq):
                     bid = None
                 if bid is not None:
-                    self.gpu.retain(bid)
+                    self._retain(bid)
                     cached_tokens += self.page
                 else:
                     still_hitting = False
@@ -234,8 +263,9 @@ class BlockManager:
                 table.append(bid)
         except OutOfBlocks:
             for p in table:
-                self.gpu.release(p)
+                self._release(p)
             raise
+        emit_kv_event("allocate", seq_id=seq.seq_id, pages=len(table), cached_tokens=cached_tokens)
         seq.block_table = table
         seq.block_table_version += 1
         seq.kv_layout = None
@@ -265,7 +295,9 @@ class BlockManager:
     def deallocate(self, seq: Sequence) -> None:
         seq.unpublished_hashes = []
         for p in reversed(seq.block_table):
-            self.gpu.release(p)
+            self._release(p)
+        if seq.block_table:
+            emit_kv_event("free", seq_id=seq.seq_id, pages=len(seq.block_table))
         seq.block_table = []
         seq.block_table_version += 1
         for p in seq.cpu_block_table:
@@ -308,7 +340,8 @@ class BlockManager:
         if not self._ensure_free(1):
             raise OutOfBlocks("no free GPU page for copy-on-write")
         new = self.gpu.allocate()
-        self.gpu.release(old)
+        self._release(old)
+        emit_kv_event("copy_on_write", seq_id=seq.seq_id, src=old, dst=new)
         seq.block_table[index] = new
         seq.block_table_version += 1
         return old, new
@@ -325,7 +358,8 @@ class BlockManager:
             if blk.hash is not None:
                 self.cpu.saved_hash[c] = (blk.hash, blk.token_ids)
             pairs.append((g, c))
-            self.gpu.release(g)
+            self._release(g)
+        emit_kv_event("swap_out", seq_id=seq.seq_id, pages=len(pairs))
         seq.cpu_block_table = cpu_pages
         seq.block_table = []
         seq.block_table_version += 1
@@ -346,6 +380,7 @@ class BlockManager:
                 self.gpu.publish(g, saved[0], saved[1])
             pairs.append((c, g))
             self.cpu.release(c)
+        emit_kv_event("swap_in", seq_id=seq.seq_id, pages=len(pairs))
         seq.block_table = gpu_pages
         seq.cpu_block_table = []
         seq.block_table_version += 1
@@ -380,7 +415,7 @@ class BlockManager:
             self.gpu.clear_hash(p)
         seq.unpublished_hashes = []
         for p in plan.released_blocks:
-            self.gpu.release(p)
+            self._release(p)
         seq.block_table = list(plan.kept_blocks)
         seq.block_table_version += 1
         seq.kv_layout = plan.layout
@@ -411,9 +446,14 @@ class BlockManager:
             self.gpu.retain(p)
         if tail_rows:
             pages.append(clone)
+        for p in pages:
+            self._entry_pages.add(p)
+            if self.gpu.blocks[p].ref_count == 1:  # the tail clone; borrowed pages count once their sequence lets go
+                self._evictable += 1
         self._clock += 1
         self.entries[cache_id] = PrefixEntry(cache_id, check, boundary, pages, tail_rows, layout, 0, self._clock)
         self.counters.stores += 1
+        emit_kv_event("prefix_store", seq_id=seq.seq_id, cache_id=cache_id, tokens=boundary, pages=len(pages), tail_rows=tail_rows)
         return copies
 
     # --------------------------------------------------------------------- metadata

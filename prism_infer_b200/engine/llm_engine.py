@@ -82,6 +82,8 @@ class LLMEngine:
         self.config = Config(model, **kwargs)
         cfg = self.config
         self.arch = cfg.arch
+        if runner_group is None:
+            self._validate_environment(device)
         self.tokenizer = load_tokenizer(cfg.model, self.arch)
         self.processor = PatchProcessor(self.arch, min_pixels=cfg.image_min_pixels, max_pixels=cfg.image_max_pixels,
                                         video_max_pixels=cfg.video_max_pixels)
@@ -95,9 +97,9 @@ class LLMEngine:
         if runner_group is not None:
             self.runners = runner_group
         elif cfg.tp > 1:
-            from ..parallel.launch import start_tensor_parallel_group
+            from ..parallel.tp_group import TensorParallelGroup
 
-            self.runners = start_tensor_parallel_group(cfg, weights=weights)
+            self.runners = TensorParallelGroup(cfg, weights=weights)
             if self.runners.is_driver:
                 cfg.with_cache_capacity(*self.runners.call("capacity"))
         else:
@@ -112,6 +114,22 @@ class LLMEngine:
         self.cooperative_counters = {"vision_quanta": 0}
         self._steps_since_status = 0
         atexit.register(self.exit)
+
+    def _validate_environment(self, device: str | None) -> None:
+        """Fail before tokenizer, worker processes or weights exist (reference
+        ``prism_infer/engine/llm_engine.py:151-167``).  A CPU engine (``device="cpu"``, the oracle
+        and test path) needs neither a GPU nor the kernel library."""
+        from ..parallel.tp_group import rank_info
+        from ..runtime_capabilities import validate_runtime_capabilities, validate_tensor_parallel_environment
+
+        cfg = self.config
+        on_cuda = torch.cuda.is_available() if device is None else str(device).startswith("cuda")
+        if on_cuda:
+            validate_runtime_capabilities(True, execution_backend=cfg.prism.execution.backend,
+                                          compression_mode=cfg.compression_mode)
+        if cfg.tp > 1:
+            devices = torch.cuda.device_count() if on_cuda else cfg.tp  # CPU ranks (gloo) need no devices
+            validate_tensor_parallel_environment(self.arch, cfg.tp, devices, world_size=rank_info()[1])
 
     # ------------------------------------------------------------------- lifecycle
     def exit(self) -> None:

@@ -153,6 +153,18 @@ class Qwen3VLArch:
         return dataclasses.replace(self, text=text)
 
     @classmethod
+    def qwen3_vl_8b_2layer(cls) -> "Qwen3VLArch":
+        """Qwen3-VL-8B widths (hidden 4096, 32 / 8 heads of 128, MLP 12288, vocabulary 151936, vision
+        hidden 1152) with two decoder and two vision layers: every kernel runs at its production
+        shape, and an end-to-end comparison against the oracle stays cheap."""
+        import dataclasses
+
+        full = cls()
+        return dataclasses.replace(
+            full, text=dataclasses.replace(full.text, num_layers=2),
+            vision=dataclasses.replace(full.vision, depth=2, deepstack_visual_indexes=(0, 1)))
+
+    @classmethod
     def tiny(cls) -> "Qwen3VLArch":
         """The small CPU test model: 2+2 layers, hidden 256/128, head_dim 64."""
         return cls(

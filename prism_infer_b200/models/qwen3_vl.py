@@ -456,6 +456,12 @@ class Qwen3VLModel:
         x = ops.embed(input_ids, self.embed, visual=emb_visual, vis_index=vis_index, vocab_start=self.vocab_start)
         if self.tp > 1:
             x = self.comm.reduce_dense(x)
+        plan = self._decode_plan(cache, T) if (x.is_cuda and not meta.is_prefill and deepstack is None) else None
+        if plan is not None:
+            # decode steps of at most 16 tokens: every layer in one persistent launch
+            pre = plan.run(x, positions, meta.slots, meta.block_tables, meta.context_lens)
+            h, _ = ops.add_rmsnorm(self.final_norm, t.rms_norm_eps, x=pre, residual=None)
+            return h
         residual: Optional[torch.Tensor] = None
         dense, partials, ticket = x, None, None
         n_deep = len(deepstack) if deepstack is not None else 0
@@ -544,6 +550,26 @@ class Qwen3VLModel:
         h, _ = comm.add_rmsnorm(self.final_norm, t.rms_norm_eps, dense, partials, ticket, residual,
                                 extra, vis_index if extra is not None else None)
         return h
+
+    def _decode_plan(self, cache: ops.KVCache, tokens: int):
+        """The persistent decode kernel's plan for this cache, or ``None`` where it does not apply
+        (tensor-parallel ranks, more than 16 tokens, unsupported head shapes, switched off)."""
+        from ..ops import decode_layers as dl
+
+        if not dl.ENABLED or self.tp != 1 or tokens > dl.MAX_TOKENS:
+            return None
+        plans = self.__dict__.setdefault("_decode_plans", {})
+        key = cache.payload.data_ptr()
+        if key not in plans:
+            t = self.arch.text
+            plan = None
+            if dl.supported(hidden=self.H, heads=self.Hq, kv_heads=self.Hkv, head_dim=self.D, intermediate=self.I):
+                inv_freq, axis = ops._rope_tables(self.D, t.rope_theta, t.mrope_section, self.device)
+                plan = dl.DecodeLayersPlan(self.layers, cache, hidden=self.H, heads=self.Hq, kv_heads=self.Hkv,
+                                           head_dim=self.D, intermediate=self.I, eps=t.rms_norm_eps, inv_freq=inv_freq,
+                                           axis=axis)
+            plans[key] = plan
+        return plans[key]
 
     def _forward_prefill_fused(self, x, positions, meta, cache, deepstack, vis_index):
         """Tensor-parallel prefill with the exchanges fused into the kernels around them: each

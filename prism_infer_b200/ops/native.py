@@ -66,8 +66,12 @@ _SIGNATURES = {
     "prism_ipc_close_handle": "p",
     "prism_epoch_advance": "plpi",
     "prism_argmax_exchange": "ppppppppiiiiipi",
+    "prism_decode_layers": "pip",
+    "prism_decode_layer_desc": "ppipppiiipppppppp",
+    "prism_decode_layers_plan": "iiiip",
+    "prism_decode_layer_desc_bytes": "",
 }
-_STATUS_UNITS = ("gemm", "gemm_pair", "gemv", "norm", "attn", "attn_tc", "kvops", "sampler", "comm")
+_STATUS_UNITS = ("gemm", "gemm_pair", "gemv", "norm", "attn", "attn_tc", "kvops", "sampler", "comm", "decode_layers")
 
 
 class NativeError(RuntimeError):

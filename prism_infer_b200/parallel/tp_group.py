@@ -23,7 +23,11 @@ import torch.distributed as dist
 import torch.multiprocessing as mp
 
 from .control import ControlDriver, ControlSegment, ControlWorker, TPMethod
-from .launch import rank_info
+
+
+def rank_info() -> tuple[int, int]:
+    """``(rank, world size)`` of a process started by ``torch.distributed.run``; ``(0, 1)`` otherwise."""
+    return int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1"))
 
 
 def _free_port() -> int:

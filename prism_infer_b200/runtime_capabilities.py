@@ -64,8 +64,33 @@ def probe_runtime_capabilities(require_cuda: bool = True) -> CapabilityReport:
     return rep
 
 
-def validate_runtime_capabilities(require_cuda: bool = True) -> CapabilityReport:
-    rep = probe_runtime_capabilities(require_cuda)
-    if not rep.ok:
-        raise RuntimeError("runtime capability check failed: " + "; ".join(rep.problems))
+def validate_runtime_capabilities(require_cuda: bool = True, *, execution_backend: str = "eager",
+                                  compression_mode: str = "off", report: CapabilityReport | None = None) -> CapabilityReport:
+    """Raise before any tokenizer, process or model side effect when the selected run cannot work
+    here.  ``execution_backend`` and ``compression_mode`` add the requirements only that path has
+    (graph capture, the E4M3 dtype); ``report`` injects a probe result (tests)."""
+    rep = report or probe_runtime_capabilities(require_cuda)
+    problems = list(rep.problems)
+    if require_cuda and execution_backend in ("cuda_graph", "compile_graph") and rep.cuda_available and not rep.cuda_graphs:
+        problems.append(f"execution backend {execution_backend!r} needs CUDA graphs")
+    if "fp8" in compression_mode and not rep.fp8_dtype:
+        problems.append(f"compression mode {compression_mode!r} needs torch.float8_e4m3fn")
+    if problems:
+        raise RuntimeError("runtime capability check failed: " + "; ".join(dict.fromkeys(problems)))
     return rep
+
+
+def validate_tensor_parallel_environment(arch, tp: int, device_count: int, *, world_size: int = 1) -> None:
+    """Hardware and sharding checks of a tensor-parallel run, before any process is spawned or
+    communicator created (reference ``prism_infer/engine/llm_engine.py:117-143``): enough visible
+    devices, an externally launched world of exactly ``tp`` ranks, every sharded dimension divisible."""
+    from .models.architecture import validate_tensor_parallel
+
+    validate_tensor_parallel(arch, tp)
+    if tp <= 1:
+        return
+    if world_size > 1 and world_size != tp:
+        raise RuntimeError(f"tensor_parallel_size={tp} but the launcher started WORLD_SIZE={world_size} ranks")
+    if tp > device_count:
+        raise RuntimeError(f"tensor_parallel_size={tp} requires at least {tp} visible CUDA devices, "
+                           f"but only {device_count} are available")

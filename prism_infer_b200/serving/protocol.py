@@ -33,20 +33,25 @@ class GenerationRequest:
     sampling_params: SamplingParams
 
     def __post_init__(self) -> None:
-        if not isinstance(self.request_id, str) or not self.request_id.strip():
-            raise ValueError("request_id must be a non-empty string")
-        if not isinstance(self.prompt, str) or not self.prompt.strip():
-            raise ValueError("prompt must be a non-empty string")
-        if not isinstance(self.modality, Modality):
-            raise TypeError("modality must be a Modality")
-        if not isinstance(self.sampling_params, SamplingParams):
-            raise TypeError("sampling_params must be SamplingParams")
-        if self.modality is Modality.TEXT and self.media is not None:
-            raise ValueError("text requests must not include media")
-        if self.modality is not Modality.TEXT and self.media is None:
-            raise ValueError(f"{self.modality.value} requests require media")
-        if isinstance(self.media, tuple) and not self.media:
-            raise ValueError("media tuples must not be empty")
+        for broken, error in _REQUEST_RULES:
+            if broken(self):
+                raise error[0](error[1].format(modality=getattr(self.modality, "value", self.modality)))
+
+
+def _blank(value: object) -> bool:
+    return not isinstance(value, str) or not value.strip()
+
+
+# (violation predicate, (exception type, message)) in the order the fields are checked
+_REQUEST_RULES = (
+    (lambda r: _blank(r.request_id), (ValueError, "request_id must be a non-empty string")),
+    (lambda r: _blank(r.prompt), (ValueError, "prompt must be a non-empty string")),
+    (lambda r: not isinstance(r.modality, Modality), (TypeError, "modality must be a Modality")),
+    (lambda r: not isinstance(r.sampling_params, SamplingParams), (TypeError, "sampling_params must be SamplingParams")),
+    (lambda r: r.modality is Modality.TEXT and r.media is not None, (ValueError, "text requests must not include media")),
+    (lambda r: r.modality is not Modality.TEXT and r.media is None, (ValueError, "{modality} requests require media")),
+    (lambda r: isinstance(r.media, tuple) and len(r.media) == 0, (ValueError, "media tuples must not be empty")),
+)
 
 
 @dataclass(frozen=True)

@@ -70,6 +70,27 @@ def test_flat_config_adapter_rules():
         Config("random:tiny", tensor_parallel_size=3)
 
 
+def test_start_up_validation_names_every_unmet_requirement():
+    from prism_infer_b200.models.architecture import Qwen3VLArch
+    from prism_infer_b200.runtime_capabilities import (CapabilityReport, validate_runtime_capabilities,
+                                                       validate_tensor_parallel_environment)
+
+    ok = CapabilityReport("2.11.0", True, "NVIDIA B200", (10, 0), True, True, True)
+    assert validate_runtime_capabilities(True, execution_backend="cuda_graph", compression_mode="scaled_fp8_kv", report=ok) is ok
+    bare = CapabilityReport("2.11.0", True, "NVIDIA B200", (10, 0), True, False, False)
+    with pytest.raises(RuntimeError, match="CUDA graphs.*float8_e4m3fn"):
+        validate_runtime_capabilities(True, execution_backend="cuda_graph", compression_mode="scaled_fp8_kv", report=bare)
+    validate_runtime_capabilities(True, execution_backend="eager", compression_mode="off", report=bare)
+    arch = Qwen3VLArch.qwen3_vl_8b()
+    validate_tensor_parallel_environment(arch, 8, 8, world_size=8)
+    with pytest.raises(RuntimeError, match="only 4 are available"):
+        validate_tensor_parallel_environment(arch, 8, 4)
+    with pytest.raises(RuntimeError, match="WORLD_SIZE=2"):
+        validate_tensor_parallel_environment(arch, 4, 8, world_size=2)
+    with pytest.raises(ValueError):
+        validate_tensor_parallel_environment(arch, 3, 8)
+
+
 def test_kv_page_accounting_matches_reference_numbers():
     c8 = Config("random:qwen3-vl-8b", compression_mode="scaled_fp8_kv")
     assert c8.kv_bytes_per_page() == 19_464_192  # 18 874 368 payload + 589 824 scales
@@ -197,6 +218,32 @@ def test_multimodal_prefix_store_hit_tail_clone_and_eviction():
     bm.deallocate(big)
     bm.allocate(stale, expected_hit=True)
     assert bm.counters.stale_probes == 1 and stale.num_cached_tokens == 0
+
+
+def test_eviction_skips_entries_whose_pages_are_all_borrowed():
+    """An entry whose pages are all still held by running sequences frees nothing when evicted: it
+    stays in the cache, and the pool reports no reclaimable page for it."""
+    bm = BlockManager(4, 4)
+    a = mm_seq(1, 8, [5])  # vision_start + 8 placeholders: two full pages + a one-row tail; 11 tokens in all
+    assert a.multimodal_prefix_boundary % 4 == 1 and len(a) <= 12
+    bm.allocate(a)
+    a.num_computed_tokens = len(a)
+    bm.store_multimodal_prefix(a)  # takes the fourth page for the tail clone
+    assert bm.gpu.num_free == 0 and bm._evictable_pages() == 1
+    events = []
+    from prism_infer_b200.observability import install_kv_trace_provider
+    install_kv_trace_provider(lambda kind, fields: events.append(kind))
+    try:
+        assert bm._ensure_free(1) and not bm.entries and bm.counters.evictions == 1  # the tail clone was reclaimable
+        bm.store_multimodal_prefix(a)
+        entry = next(iter(bm.entries.values()))
+        bm.gpu.retain(entry.pages[-1])  # pretend a sequence borrows the tail clone as well
+        bm._evictable -= 1
+        assert bm._evictable_pages() == 0
+        assert not bm._ensure_free(1) and len(bm.entries) == 1 and bm.counters.evictions == 1  # nothing to gain: kept
+    finally:
+        install_kv_trace_provider(None)
+    assert events.count("evict") == 1 and "prefix_store" in events
 
 
 def test_compaction_plan_commit_and_layout():
@@ -471,6 +518,9 @@ def _check_page_invariants(sched):
         assert s.state in (RequestState.PREFILLING, RequestState.DECODING)
     for s in sched.swapped:
         assert s.state is RequestState.SWAPPED and not s.block_table
+    # the running count of reclaimable prefix pages equals a full recount
+    assert bm._evictable_pages() == sum(1 for e in bm.entries.values() for p in e.pages if bm.gpu.blocks[p].ref_count == 1)
+    assert bm._entry_pages == {p for e in bm.entries.values() for p in e.pages}
 
 
 @pytest.mark.parametrize("seed", range(6))
