@@ -153,8 +153,18 @@ class MultimodalConfig:
     enable_vision_tensor_cudagraph: bool = False
     enable_visual_embedding_cache: bool = False
     visual_embedding_cache_bytes: int = 256 << 20
+    # string prompts of multimodal requests are wrapped in the checkpoint's chat turns: "auto" = when the
+    # tokenizer ships a chat template (instruction-tuned checkpoints), "always", or "never"
+    chat_template: str = "auto"
+    # "always": preprocess media with the checkpoint's own Hugging Face processor (needs its processor
+    # files and transformers) instead of the built-in one, which has the same output contract
+    hf_processor: str = "never"
 
     def __post_init__(self) -> None:
+        if self.chat_template not in ("auto", "always", "never"):
+            raise ValueError(f"chat_template must be 'auto', 'always' or 'never', got {self.chat_template!r}")
+        if self.hf_processor not in ("always", "never"):
+            raise ValueError(f"hf_processor must be 'always' or 'never', got {self.hf_processor!r}")
         for n in ("image_min_pixels", "image_max_pixels", "video_max_pixels"):
             v = getattr(self, n)
             if v is not None:
@@ -251,6 +261,7 @@ _FLAT = {
         "enable_vision_tensor_cudagraph": "enable_vision_tensor_cudagraph",
         "enable_visual_embedding_cache": "enable_visual_embedding_cache",
         "visual_embedding_cache_bytes": "visual_embedding_cache_bytes",
+        "chat_template": "chat_template", "hf_processor": "hf_processor",
     },
     "cache": {
         "gpu_memory_utilization": "gpu_memory_utilization", "kvcache_block_size": "page_size",

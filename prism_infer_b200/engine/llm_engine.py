@@ -87,6 +87,15 @@ class LLMEngine:
         self.tokenizer = load_tokenizer(cfg.model, self.arch)
         self.processor = PatchProcessor(self.arch, min_pixels=cfg.image_min_pixels, max_pixels=cfg.image_max_pixels,
                                         video_max_pixels=cfg.video_max_pixels)
+        from .chat_prompt import ChatPrompt, HFProcessorAdapter
+
+        mode = cfg.chat_template
+        chat = ChatPrompt(self.tokenizer)
+        self.chat = chat if (mode == "always" or (mode == "auto" and chat.has_template)) else None
+        self.hf_processor = None
+        if cfg.hf_processor == "always":
+            self.hf_processor = HFProcessorAdapter(cfg.model, image_max_pixels=cfg.image_max_pixels,
+                                                   video_max_pixels=cfg.video_max_pixels)
         self._ids = RequestIdAllocator()
         self.metrics = EngineMetrics()
         # CUDA engines keep a request's patches as pinned bf16 (the model's dtype): the copy to the
@@ -212,25 +221,48 @@ class LLMEngine:
                                    media_key: str | None = None, raise_on_reject: bool = True) -> int:
         return self._submit(self._multimodal_sequence(inputs, sampling_params, media_key), raise_on_reject=raise_on_reject)
 
+    def prepare_images(self, prompt: str | Seq[int], images: Seq[Any], *, image_marker: str | None = None) -> ImageInputs:
+        """Prompt + images -> ``ImageInputs`` the way this engine was configured: chat turns around a
+        string prompt when the checkpoint has a chat template, the checkpoint's Hugging Face processor
+        when ``hf_processor="always"``, the built-in patch processor otherwise.  ``image_marker``
+        selects the interleaved layout (images where the marker appears in the prompt)."""
+        images = list(images)
+        if self.hf_processor is not None and isinstance(prompt, str):
+            chat = self.hf_processor.chat
+            text = (chat.interleaved_image_prompt(prompt, len(images), image_marker=image_marker) if image_marker
+                    else chat.image_prompt(prompt, len(images)))
+            return self.hf_processor.image_inputs(text, images)
+        if image_marker:
+            return prepare_interleaved_image_inputs(self.processor, self.tokenizer, prompt, images, image_marker, chat=self.chat)
+        return prepare_image_inputs(self.processor, self.tokenizer, prompt, images, chat=self.chat)
+
+    def prepare_video(self, prompt: str | Seq[int], frames: Seq[Any], *, timing=None) -> VideoInputs:
+        """Prompt + sampled frames (+ ``chat_prompt.VideoTiming``) -> ``VideoInputs``; see ``prepare_images``."""
+        frames = list(frames)
+        if self.hf_processor is not None and isinstance(prompt, str):
+            return self.hf_processor.video_inputs(self.hf_processor.chat.video_prompt(prompt), frames, timing)
+        return prepare_video_inputs(self.processor, self.tokenizer, prompt, frames, chat=self.chat, timing=timing)
+
     def add_vl_request(self, prompt: str | Seq[int], image: Any, sampling_params: SamplingParams | None = None, **kw) -> int:
         with profile_region("preprocess.image", cuda=False):
-            inputs = prepare_image_inputs(self.processor, self.tokenizer, prompt, [image])
+            inputs = self.prepare_images(prompt, [image])
         return self.add_prepared_image_request(inputs, sampling_params, **kw)
 
     def add_images_request(self, prompt: str | Seq[int], images: Seq[Any], sampling_params: SamplingParams | None = None, **kw) -> int:
         with profile_region("preprocess.images", cuda=False):
-            inputs = prepare_image_inputs(self.processor, self.tokenizer, prompt, list(images))
+            inputs = self.prepare_images(prompt, images)
         return self.add_prepared_image_request(inputs, sampling_params, **kw)
 
     def add_interleaved_images_request(self, prompt: str, images: Seq[Any], sampling_params: SamplingParams | None = None,
                                        *, image_marker: str = "<image>", **kw) -> int:
         with profile_region("preprocess.interleaved_images", cuda=False):
-            inputs = prepare_interleaved_image_inputs(self.processor, self.tokenizer, prompt, list(images), image_marker)
+            inputs = self.prepare_images(prompt, images, image_marker=image_marker)
         return self.add_prepared_image_request(inputs, sampling_params, **kw)
 
-    def add_video_request(self, prompt: str | Seq[int], frames: Seq[Any], sampling_params: SamplingParams | None = None, **kw) -> int:
+    def add_video_request(self, prompt: str | Seq[int], frames: Seq[Any], sampling_params: SamplingParams | None = None, *,
+                          timing=None, **kw) -> int:
         with profile_region("preprocess.video", cuda=False):
-            inputs = prepare_video_inputs(self.processor, self.tokenizer, prompt, list(frames))
+            inputs = self.prepare_video(prompt, frames, timing=timing)
         return self.add_prepared_video_request(inputs, sampling_params, **kw)
 
     # ------------------------------------------------------------------------ step
@@ -323,6 +355,18 @@ class LLMEngine:
 
     def cooperative_prefill_policy_metadata(self) -> dict[str, object]:
         return {"enabled": self.config.cooperative_prefill, **self.cooperative_counters}
+
+    def barrier(self) -> None:
+        """Wait until every rank's device has finished the work issued so far."""
+        self.runners.call("barrier")
+
+    def keep_logits(self, on: bool = True) -> None:
+        """Debugging aid (eager execution only): keep the full fp32 logits of the last sampled rows."""
+        self.runners.call("keep_logits", bool(on))
+
+    def last_logits(self):
+        """``[rows, vocab]`` fp32 CPU tensor of the rows sampled in the last step, or ``None``."""
+        return self.runners.call("last_logits")
 
     def time_decode_graph(self, steps: int) -> float:
         """Device ms per decode step from back-to-back graph launches (max over ranks)."""

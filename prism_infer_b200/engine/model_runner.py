@@ -491,6 +491,19 @@ class ModelRunner:
         if self.on_cuda:
             torch.cuda.synchronize(self.device)
 
+    def keep_logits(self, on: bool) -> None:
+        """Debugging aid for eager execution: keep the full-vocabulary fp32 logits of the rows sampled
+        last (tensor-parallel ranks gather them), readable with ``last_logits``."""
+        self.model.keep_logits = bool(on)
+        self.model.last_logits = None
+
+    def last_logits(self):
+        """``[rows, vocab]`` fp32 on the CPU (rank 0 only; other ranks answer ``None``)."""
+        t = getattr(self.model, "last_logits", None)
+        if t is None or self.rank != 0:
+            return None
+        return t.cpu()
+
     def status(self) -> dict:
         """Device status words (bounded waits that ran out, bounds checks) of this rank."""
         if not self.on_cuda:

@@ -5,9 +5,8 @@ the Hugging Face Qwen3-VL processor: ``pixel_values [N, C * Tp * P * P]`` in
 merge-window-major patch order ``(t, h_block, w_block, h_in, w_in)``, ``grid_thw`` rows
 ``(T, H, W)`` in patches, still images duplicated to fill the temporal patch, sizes snapped
 to multiples of ``patch * merge`` inside the pixel budget, and one placeholder token per
-merged 2x2 window.  When the model directory ships processor files the Hugging Face
-processor can be used instead (``load_hf_processor``); the prompt builders and validators
-below are shared.
+merged 2x2 window.  Chat-template prompts and the optional Hugging Face processor live in
+``chat_prompt.py``; the validators below are shared.
 """
 
 from __future__ import annotations
@@ -158,8 +157,12 @@ def video_blocks(arch, grid: tuple[int, int, int], merge_unit: int) -> list[int]
     return out
 
 
-def prepare_image_inputs(processor: PatchProcessor, tokenizer, prompt: str | Sequence[int], images: Sequence[Any]) -> ImageInputs:
-    """All images first, then the question (media-first layout)."""
+def prepare_image_inputs(processor: PatchProcessor, tokenizer, prompt: str | Sequence[int], images: Sequence[Any], *,
+                         chat=None) -> ImageInputs:
+    """All images first, then the question (media-first layout).  With ``chat`` (a
+    ``chat_prompt.ChatPrompt``) a string prompt is wrapped in the checkpoint's chat turns, as the
+    reference does through the Hugging Face processor (``engine/vl_inputs.py:216-243``); token-id
+    prompts and ``chat=None`` keep the bare layout."""
     arch = processor.arch
     ids: list[int] = []
     pixels, grids = [], []
@@ -168,19 +171,35 @@ def prepare_image_inputs(processor: PatchProcessor, tokenizer, prompt: str | Seq
         pixels.append(pv)
         grids.append(grid)
         ids += image_block(arch, processor.tokens_for(grid))
-    ids += list(prompt) if not isinstance(prompt, str) else tokenizer.encode(prompt)
+    if chat is not None and isinstance(prompt, str):
+        from .chat_prompt import encode_with_media
+
+        ids = encode_with_media(tokenizer, chat.image_prompt(prompt, len(grids)), arch,
+                                image_tokens=[processor.tokens_for(g) for g in grids])
+    else:
+        ids += list(prompt) if not isinstance(prompt, str) else tokenizer.encode(prompt)
     out = ImageInputs(ids, torch.cat(pixels), grids)
     out.validate(arch)
     return out
 
 
 def prepare_interleaved_image_inputs(processor: PatchProcessor, tokenizer, prompt: str, images: Sequence[Any],
-                                     image_marker: str = "<image>") -> ImageInputs:
+                                     image_marker: str = "<image>", *, chat=None) -> ImageInputs:
     """The prompt names where each image goes with ``image_marker``."""
     arch = processor.arch
     parts = prompt.split(image_marker)
     if len(parts) - 1 != len(images):
         raise ValueError(f"prompt has {len(parts) - 1} {image_marker!r} markers for {len(images)} images")
+    if chat is not None:
+        from .chat_prompt import encode_with_media
+
+        done = [processor.process_image(img) for img in images]
+        grids = [g for _, g in done]
+        ids = encode_with_media(tokenizer, chat.interleaved_image_prompt(prompt, len(images), image_marker=image_marker), arch,
+                                image_tokens=[processor.tokens_for(g) for g in grids])
+        out = ImageInputs(ids, torch.cat([pv for pv, _ in done]), grids)
+        out.validate(arch)
+        return out
     ids: list[int] = []
     pixels, grids = [], []
     for i, text in enumerate(parts):
@@ -196,23 +215,26 @@ def prepare_interleaved_image_inputs(processor: PatchProcessor, tokenizer, promp
     return out
 
 
-def prepare_video_inputs(processor: PatchProcessor, tokenizer, prompt: str | Sequence[int], frames: Sequence[Any]) -> VideoInputs:
+def prepare_video_inputs(processor: PatchProcessor, tokenizer, prompt: str | Sequence[int], frames: Sequence[Any], *,
+                         chat=None, timing=None) -> VideoInputs:
+    """One clip, then the question.  With ``chat`` a string prompt gets the checkpoint's chat turns
+    and each temporal group is preceded by its time stamp (``timing``: a ``chat_prompt.VideoTiming``
+    with the source frame indices and frame rate; consecutive frames at 24 fps when absent, which
+    is what the Hugging Face processor assumes for pre-sampled frames)."""
     arch = processor.arch
     pv, grid = processor.process_video(frames)
-    ids = video_blocks(arch, grid, arch.vision.merge_unit)
-    ids += list(prompt) if not isinstance(prompt, str) else tokenizer.encode(prompt)
+    if chat is not None and isinstance(prompt, str):
+        from .chat_prompt import VideoTiming, encode_with_media
+
+        timing = timing or VideoTiming(tuple(range(len(frames))))
+        times = timing.group_times(arch.vision.temporal_patch_size)
+        if len(times) != grid[0]:
+            raise ValueError(f"timing describes {len(times)} temporal groups, the clip has {grid[0]}")
+        ids = encode_with_media(tokenizer, chat.video_prompt(prompt), arch,
+                                video_groups=[(grid[1] * grid[2] // arch.vision.merge_unit, times)])
+    else:
+        ids = video_blocks(arch, grid, arch.vision.merge_unit)
+        ids += list(prompt) if not isinstance(prompt, str) else tokenizer.encode(prompt)
     out = VideoInputs(ids, pv, [grid])
     out.validate(arch)
     return out
-
-
-def load_hf_processor(model: str, *, longest_edge: int | None = None):
-    """Hugging Face ``AutoProcessor`` for real checkpoints (optional)."""
-    from transformers import AutoProcessor
-
-    proc = AutoProcessor.from_pretrained(model)
-    if longest_edge is not None and hasattr(proc, "image_processor"):
-        size = dict(getattr(proc.image_processor, "size", {}) or {})
-        size["longest_edge"] = longest_edge
-        proc.image_processor.size = size
-    return proc

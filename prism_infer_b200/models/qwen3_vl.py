@@ -454,11 +454,12 @@ class Qwen3VLModel:
         if self.tp > 1 and visual is not None and self.rank != 0:
             emb_visual = torch.zeros_like(visual)  # only rank 0 contributes visual rows to the sum
         x = ops.embed(input_ids, self.embed, visual=emb_visual, vis_index=vis_index, vocab_start=self.vocab_start)
-        if self.tp > 1:
+        plan = self._decode_plan(cache, T) if (x.is_cuda and not meta.is_prefill and deepstack is None and visual is None) else None
+        if self.tp > 1 and plan is None:
             x = self.comm.reduce_dense(x)
-        plan = self._decode_plan(cache, T) if (x.is_cuda and not meta.is_prefill and deepstack is None) else None
         if plan is not None:
-            # decode steps of at most 16 tokens: every layer in one persistent launch
+            # decode steps of at most 16 tokens: every layer in one persistent launch (tensor-parallel
+            # ranks: the kernel also sums the vocabulary-sharded embedding rows over the ranks)
             pre = plan.run(x, positions, meta.slots, meta.block_tables, meta.context_lens)
             h, _ = ops.add_rmsnorm(self.final_norm, t.rms_norm_eps, x=pre, residual=None)
             return h
@@ -553,10 +554,14 @@ class Qwen3VLModel:
 
     def _decode_plan(self, cache: ops.KVCache, tokens: int):
         """The persistent decode kernel's plan for this cache, or ``None`` where it does not apply
-        (tensor-parallel ranks, more than 16 tokens, unsupported head shapes, switched off)."""
+        (more than 16 tokens, unsupported head shapes, tensor-parallel ranks without the fused
+        communicator, switched off)."""
         from ..ops import decode_layers as dl
 
-        if not dl.ENABLED or self.tp != 1 or tokens > dl.MAX_TOKENS:
+        if not dl.ENABLED or tokens > dl.MAX_TOKENS:
+            return None
+        exchange = getattr(self.comm, "decode_exchange", None)  # the fused communicator's peer-mapped buffers
+        if self.tp > 1 and exchange is None:
             return None
         plans = self.__dict__.setdefault("_decode_plans", {})
         key = cache.payload.data_ptr()
@@ -565,9 +570,11 @@ class Qwen3VLModel:
             plan = None
             if dl.supported(hidden=self.H, heads=self.Hq, kv_heads=self.Hkv, head_dim=self.D, intermediate=self.I):
                 inv_freq, axis = ops._rope_tables(self.D, t.rope_theta, t.mrope_section, self.device)
-                plan = dl.DecodeLayersPlan(self.layers, cache, hidden=self.H, heads=self.Hq, kv_heads=self.Hkv,
-                                           head_dim=self.D, intermediate=self.I, eps=t.rms_norm_eps, inv_freq=inv_freq,
-                                           axis=axis)
+                extra = exchange(self.H, dl.MAX_TOKENS) if self.tp > 1 else {}
+                if self.tp == 1 or extra:
+                    plan = dl.DecodeLayersPlan(self.layers, cache, hidden=self.H, heads=self.Hq, kv_heads=self.Hkv,
+                                               head_dim=self.D, intermediate=self.I, eps=t.rms_norm_eps, inv_freq=inv_freq,
+                                               axis=axis, **extra)
             plans[key] = plan
         return plans[key]
 
@@ -624,6 +631,9 @@ class Qwen3VLModel:
         """Next token per row: LM head, then arg-max / exponential-race sampling; under tensor
         parallelism ranks exchange their shard winners so every rank returns the same ids."""
         logits = self.logits(hidden)
+        if self.__dict__.get("keep_logits"):
+            # debugging aid (eager execution): full-vocabulary fp32 logits of the last sampled rows
+            self.last_logits = (logits if self.tp == 1 else self.comm.gather_logits(logits)).float().clone()
         if self.tp == 1:
             return ops.sample(logits, temperature, seed=seed, step=step, out=out)
         greedy = temperature is None

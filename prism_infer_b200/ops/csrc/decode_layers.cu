@@ -46,6 +46,7 @@
 // is freed); nothing traps and nothing hangs.
 #include <cstring>
 #include <mutex>
+#include <type_traits>
 
 #include "common.cuh"
 
@@ -65,7 +66,7 @@ constexpr int NTHREADS = 64 + NWT;
 constexpr int NACC = 4;                      // TMEM accumulators (16 fp32 columns each)
 constexpr int TMEM_COLS = 64;
 constexpr int MAX_T = 16;
-constexpr int SCRATCH_BYTES = 24 * 1024;
+constexpr int SCRATCH_BYTES = 20 * 1024;
 constexpr int SMEM_LIMIT = 232448;
 constexpr uint32_t IDESC = umma_idesc_bf16(BM, BN);
 constexpr float FP8_MAX = 448.0f;
@@ -102,6 +103,7 @@ struct DLParams {
   int page, max_blocks, num_blocks, kv_mode;
   int nsplit;
   int stages;
+  int pf_depth;  // units the L2 prefetch cursor may run ahead of the ring (0: off)
   float eps, attn_scale;
   GemmGeo geo[4];
   const bf16* x0;            // [T][H] embedding rows
@@ -115,13 +117,24 @@ struct DLParams {
   bf16* xw;                  // [T][H]
   bf16* attn;                // [T][Hq*D]
   bf16* act;                 // [T][I]
-  float* ssq;                // [2][MAX_T][32]
+  float* ssq;                // [2][MAX_T][SSQ_STRIDE]
   float* part_o;             // [T][Hq][nsplit][D]
   float* part_ml;            // [T][Hq][nsplit][2]
   int* attn_counters;        // [T*Hkv], zero, self-resetting
   unsigned long long* gbar;  // grid barrier ticket counter (monotonic)
   int* abort_flag;           // zero; set when a wait ran out
+  int* tile_counters;        // [3][TILE_COUNTERS] zero, self-resetting: partials delivered per tile of o_proj / gate+up / down
+  long long* timeline;       // optional [grid][n_layers][TL_STAMPS] SM clock stamps of the phase boundaries (null: off)
+  // tensor parallel: every reduce phase is also the all-reduce of a row-parallel projection (or of
+  // the vocabulary-sharded embedding).  xch[slot][r] is rank r's exchange buffer of that slot,
+  // [tp][T][H] 8-byte words {fp32 value, sequence}; epoch is the step's sequence base.
+  int tp, my_rank;
+  const unsigned long long* epoch;
+  unsigned long long* xch[2][8];
 };
+constexpr int TL_PHASES = 13;   // phase boundaries of a layer
+constexpr int TL_STAMPS = 20;   // + 7 stamps inside the CTA's first attention item
+constexpr int TILE_COUNTERS = 512;  // arrival counters per projection (weight tiles of 128 rows)
 
 __device__ __forceinline__ void named_bar_sync(int id, int threads) {
   asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
@@ -148,6 +161,36 @@ __device__ __forceinline__ void sk_tile_slabs(const GemmGeo& g, int m, int G, in
   const int u0 = m * g.kb;
   first = sk_owner(u0, g.U, G);
   n = sk_owner(u0 + g.kb - 1, g.U, G) - first + 1;
+}
+
+// Sum of up to n slabs, 8 consecutive floats each: every load is issued before the first add, so the
+// sum costs one memory round trip whatever n is (a plain loop waits for each slab in turn).
+constexpr int SLAB_UNROLL = 8;
+__device__ __forceinline__ void sum_slabs8(const float* base, long long stride, int n, float (&out)[8]) {
+  float4 v0[SLAB_UNROLL], v1[SLAB_UNROLL];
+#pragma unroll
+  for (int s = 0; s < SLAB_UNROLL; ++s) {
+    v0[s] = make_float4(0.f, 0.f, 0.f, 0.f);
+    v1[s] = v0[s];
+    if (s < n) {
+      v0[s] = __ldcg(reinterpret_cast<const float4*>(base + (size_t)s * stride));
+      v1[s] = __ldcg(reinterpret_cast<const float4*>(base + (size_t)s * stride + 4));
+    }
+  }
+  float4 a0 = v0[0], a1 = v1[0];
+#pragma unroll
+  for (int s = 1; s < SLAB_UNROLL; ++s) {
+    a0.x += v0[s].x; a0.y += v0[s].y; a0.z += v0[s].z; a0.w += v0[s].w;
+    a1.x += v1[s].x; a1.y += v1[s].y; a1.z += v1[s].z; a1.w += v1[s].w;
+  }
+  for (int s = SLAB_UNROLL; s < n; ++s) {
+    const float4 w0 = __ldcg(reinterpret_cast<const float4*>(base + (size_t)s * stride));
+    const float4 w1 = __ldcg(reinterpret_cast<const float4*>(base + (size_t)s * stride + 4));
+    a0.x += w0.x; a0.y += w0.y; a0.z += w0.z; a0.w += w0.w;
+    a1.x += w1.x; a1.y += w1.y; a1.z += w1.z; a1.w += w1.w;
+  }
+  out[0] = a0.x; out[1] = a0.y; out[2] = a0.z; out[3] = a0.w;
+  out[4] = a1.x; out[5] = a1.y; out[6] = a1.z; out[7] = a1.w;
 }
 
 // ---- abort-aware bounded waits --------------------------------------------------------------------
@@ -177,10 +220,12 @@ __device__ __forceinline__ bool mbar_wait_short(uint64_t* bar, uint32_t parity) 
   return true;
 }
 
-// Grid-wide barrier over the worker threads of every CTA.  Tickets of a monotonic 64-bit counter:
-// the k-th barrier since the buffer was created owns tickets [k G, (k+1) G), so no reset and no
-// launch-dependent base are needed.  Pattern: CTA barrier, fence + ticket by one thread, spin,
-// fence, CTA barrier (the cooperative-groups grid sync).  Returns false when aborted.
+// Grid-wide barrier over the worker threads of every CTA.  A monotonic 64-bit counter: the k-th
+// barrier since the buffer was created owns counts (k G, (k+1) G], so no reset and no
+// launch-dependent base are needed.  The first barrier of a launch takes a ticket
+// (atom.add.release) to learn k; later ones add with a fire-and-forget red.release and advance the
+// target by G.  One thread arrives for the CTA after a CTA barrier (the release is cumulative
+// over what the barrier ordered before it) and polls with ld.acquire.  Returns false when aborted.
 __device__ __forceinline__ void st_release_cta(volatile int* addr, int v) {
   asm volatile("st.release.cta.shared.u32 [%0], %1;" ::"r"(smem_u32(const_cast<int*>(addr))), "r"(v) : "memory");
 }
@@ -190,30 +235,35 @@ __device__ __forceinline__ int ld_acquire_cta(volatile int* addr) {
   return v;
 }
 __device__ __forceinline__ bool grid_barrier(const DLParams& p, int wtid, volatile int* s_abort, volatile int* s_xphase,
-                                             int xphase_value) {
+                                             int xphase_value, unsigned long long& target) {
   named_bar_sync(1, NWT);
   if (wtid == 0) {
-    __threadfence();
     const unsigned long long G = gridDim.x;
-    bool ok = !aborted(p);  // after an abort nobody waits for anybody any more
-    const unsigned long long ticket = ok ? atomicAdd(p.gbar, 1ull) : 0ull;
-    const unsigned long long target = (ticket / G + 1ull) * G;
+    bool ok = *s_abort == 0;  // after an abort nobody waits for anybody any more (peers' aborts are seen while polling)
+    if (ok) {
+      if (target == 0ull) {
+        unsigned long long ticket;
+        asm volatile("atom.add.release.gpu.global.u64 %0, [%1], 1;" : "=l"(ticket) : "l"(p.gbar) : "memory");
+        target = (ticket / G + 1ull) * G;
+      } else {
+        target += G;
+        asm volatile("red.release.gpu.global.add.u64 [%0], 1;" ::"l"(p.gbar) : "memory");
+      }
+    }
     const long long t0 = clock64();
+    int polls = 0;
     while (ok) {
       unsigned long long v;
       asm volatile("ld.acquire.gpu.global.u64 %0, [%1];" : "=l"(v) : "l"(p.gbar) : "memory");
       if (v >= target) break;
-      if (aborted(p)) {
-        ok = false;
-        break;
-      }
-      if (clock64() - t0 > PRISM_WAIT_CYCLES) {
-        raise_abort(p, PRISM_ERR_PEER_TIMEOUT, 900);
-        ok = false;
-        break;
+      if ((++polls & 15) == 0) {
+        if (aborted(p)) ok = false;
+        else if (clock64() - t0 > PRISM_WAIT_CYCLES) {
+          raise_abort(p, PRISM_ERR_PEER_TIMEOUT, 900);
+          ok = false;
+        }
       }
     }
-    __threadfence();
     if (!ok) *s_abort = 1;
     else if (xphase_value > 0) st_release_cta(s_xphase, xphase_value);  // the producer may now load this phase's activations
   }
@@ -221,159 +271,225 @@ __device__ __forceinline__ bool grid_barrier(const DLParams& p, int wtid, volati
   return *s_abort == 0;
 }
 
-// ---- reduce phase: slabs (+ residual) -> residual, xw = bf16(residual * weight), ssq ---------------
-// One warp per (token, 256-column segment); a lane owns 8 columns.
-__device__ __forceinline__ void reduce_phase(const DLParams& p, const GemmGeo* src, const bf16* x0, const bf16* weight,
-                                             bool have_residual, float* ssq_out, bool final_only, int wtid) {
-  const int G = gridDim.x, cta = blockIdx.x;
-  const int warp = wtid >> 5, lane = wtid & 31;
-  const int H = p.H, nseg = (H + 255) / 256;
-  const int items = p.T * nseg;
-  for (int it = cta + G * warp; it < items; it += G * NW) {
-    const int t = it / nseg, seg = it % nseg;
-    const int col = seg * 256 + lane * 8;
-    float ss = 0.0f;
-    if (col < H) {
-      float d[8];
-      if (src != nullptr) {
-        int first, n;
-        sk_tile_slabs(*src, col / BM, G, first, n);
-        float4 a0 = make_float4(0.f, 0.f, 0.f, 0.f), a1 = a0;
-        const float* base = src->part + (size_t)t * src->M + col;
-        for (int s = 0; s < n; ++s) {
-          const float4 v0 = __ldcg(reinterpret_cast<const float4*>(base + (size_t)s * src->slab_stride));
-          const float4 v1 = __ldcg(reinterpret_cast<const float4*>(base + (size_t)s * src->slab_stride + 4));
-          a0.x += v0.x; a0.y += v0.y; a0.z += v0.z; a0.w += v0.w;
-          a1.x += v1.x; a1.y += v1.y; a1.z += v1.z; a1.w += v1.w;
-        }
-        d[0] = bf16_round(a0.x); d[1] = bf16_round(a0.y); d[2] = bf16_round(a0.z); d[3] = bf16_round(a0.w);
-        d[4] = bf16_round(a1.x); d[5] = bf16_round(a1.y); d[6] = bf16_round(a1.z); d[7] = bf16_round(a1.w);
-      } else {
-        const uint4 raw = __ldcg(reinterpret_cast<const uint4*>(x0 + (size_t)t * H + col));
-        const __nv_bfloat162* v = reinterpret_cast<const __nv_bfloat162*>(&raw);
+// ---- reduce: slabs (+ residual) -> residual, xw = bf16(residual * weight), ssq ---------------------
+constexpr int SSQ_STRIDE = 64;  // per-token partial sums of squares, one per 128-column tile (H <= 8192)
+
+__device__ __forceinline__ float4 sum_slabs4(const float* base, long long stride, int n) {
+  float4 v[SLAB_UNROLL];
 #pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          d[2 * e] = b2f(v[e].x);
-          d[2 * e + 1] = b2f(v[e].y);
-        }
-      }
-      bf16* res = p.residual + (size_t)t * H + col;
-      if (have_residual) {
-        const uint4 raw = __ldcg(reinterpret_cast<const uint4*>(res));
-        const __nv_bfloat162* r = reinterpret_cast<const __nv_bfloat162*>(&raw);
+  for (int s = 0; s < SLAB_UNROLL; ++s) {
+    v[s] = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (s < n) v[s] = __ldcg(reinterpret_cast<const float4*>(base + (size_t)s * stride));
+  }
+  float4 a = v[0];
 #pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          d[2 * e] = bf16_round(b2f(r[e].x) + d[2 * e]);
-          d[2 * e + 1] = bf16_round(b2f(r[e].y) + d[2 * e + 1]);
-        }
-      }
-      uint4 o;
-      __nv_bfloat162* op = reinterpret_cast<__nv_bfloat162*>(&o);
+  for (int s = 1; s < SLAB_UNROLL; ++s) {
+    a.x += v[s].x; a.y += v[s].y; a.z += v[s].z; a.w += v[s].w;
+  }
+  for (int s = SLAB_UNROLL; s < n; ++s) {
+    const float4 w = __ldcg(reinterpret_cast<const float4*>(base + (size_t)s * stride));
+    a.x += w.x; a.y += w.y; a.z += w.z; a.w += w.w;
+  }
+  return a;
+}
+
+// Tensor-parallel all-reduce of 4 consecutive columns of one token, inside the reduce.  The lane
+// stores its local sums into EVERY rank's exchange buffer as {value, sequence} words (an aligned
+// 8-byte store is single-copy atomic: a reader that sees the sequence number sees the value), then
+// polls its own buffer until all ranks' words of this exchange carry the sequence number and adds
+// them in rank order, so every rank computes bit-identical rows.  No flag, fence or extra barrier;
+// consecutive exchanges alternate between two buffers: a rank can only reach the next use of a
+// buffer after all peers consumed the previous one, because the exchange in between needed every
+// peer's data.
+__device__ __forceinline__ void tp_exchange4(const DLParams& p, float (&d)[4], int t, int col, int point,
+                                             unsigned long long epoch) {
+  const unsigned long long seq = (epoch + (unsigned long long)point) & 0xffffffffull;
+  const int slot = (int)(((epoch >> 7) + (unsigned long long)point) & 1ull);
+  const size_t mine = ((size_t)p.my_rank * p.T + t) * p.H + col;
+  for (int r = 0; r < p.tp; ++r) {
+    unsigned long long* dst = p.xch[slot][r] + mine;
 #pragma unroll
-      for (int e = 0; e < 4; ++e) op[e] = __floats2bfloat162_rn(d[2 * e], d[2 * e + 1]);
-      *reinterpret_cast<uint4*>(res) = o;
-      if (!final_only) {
-        const uint4 wraw = __ldg(reinterpret_cast<const uint4*>(weight + col));
-        const __nv_bfloat162* w = reinterpret_cast<const __nv_bfloat162*>(&wraw);
-        uint4 xo;
-        __nv_bfloat162* xp = reinterpret_cast<__nv_bfloat162*>(&xo);
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          xp[e] = __floats2bfloat162_rn(d[2 * e] * b2f(w[e].x), d[2 * e + 1] * b2f(w[e].y));
-          ss += d[2 * e] * d[2 * e] + d[2 * e + 1] * d[2 * e + 1];
-        }
-        *reinterpret_cast<uint4*>(p.xw + (size_t)t * H + col) = xo;
-      }
-    }
-    if (!final_only) {
-      ss = warp_sum(ss);
-      if (lane == 0) ssq_out[t * 32 + seg] = ss;
+    for (int e = 0; e < 2; ++e) {
+      const unsigned long long w0 = (seq << 32) | (unsigned long long)__float_as_uint(d[2 * e]);
+      const unsigned long long w1 = (seq << 32) | (unsigned long long)__float_as_uint(d[2 * e + 1]);
+      asm volatile("st.relaxed.sys.global.v2.u64 [%0], {%1, %2};" ::"l"(dst + 2 * e), "l"(w0), "l"(w1) : "memory");
     }
   }
+  const unsigned long long* own = p.xch[slot][p.my_rank] + (size_t)t * p.H + col;
+  const unsigned int want = (unsigned int)seq;
+  const long long t0 = clock64();
+  for (;;) {
+    unsigned int stale = 0;
+    d[0] = d[1] = d[2] = d[3] = 0.0f;
+    for (int r = 0; r < p.tp; ++r) {
+      const unsigned long long* q0 = own + (size_t)r * p.T * p.H;
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        unsigned long long w0, w1;
+        asm volatile("ld.relaxed.sys.global.v2.u64 {%0, %1}, [%2];" : "=l"(w0), "=l"(w1) : "l"(q0 + 2 * e) : "memory");
+        stale |= ((unsigned int)(w0 >> 32) ^ want) | ((unsigned int)(w1 >> 32) ^ want);
+        d[2 * e] += __uint_as_float((unsigned int)w0);
+        d[2 * e + 1] += __uint_as_float((unsigned int)w1);
+      }
+    }
+    if (stale == 0) break;
+    if (aborted(p)) break;
+    if (clock64() - t0 > PRISM_WAIT_CYCLES) {
+      raise_abort(p, PRISM_ERR_PEER_TIMEOUT, 700 + point);
+      break;
+    }
+  }
+}
+
+// One (token, 128-column tile) on one warp; a lane owns 4 columns.  src: slabs of the projection
+// that produced the delta (null: the embedding rows x0); weight null: only the residual is updated
+// (the last layer's down projection leaves the pre-norm hidden state there).
+__device__ __forceinline__ void reduce_tile(const DLParams& p, const GemmGeo* src, const bf16* x0, const bf16* weight,
+                                            bool have_residual, float* ssq_out, int t, int m, int lane, int point,
+                                            unsigned long long epoch) {
+  const int H = p.H;
+  const int col = m * BM + lane * 4;
+  // residual and norm weight are requested together with the slabs: one memory round trip
+  bf16* res = p.residual + (size_t)t * H + col;
+  uint2 res_raw = make_uint2(0, 0), w_raw = make_uint2(0, 0), x_raw = make_uint2(0, 0);
+  if (have_residual) res_raw = __ldcg(reinterpret_cast<const uint2*>(res));
+  if (weight != nullptr) w_raw = __ldg(reinterpret_cast<const uint2*>(weight + col));
+  float d[4];
+  if (src != nullptr) {
+    int first, n;
+    sk_tile_slabs(*src, m, gridDim.x, first, n);
+    const float4 a = sum_slabs4(src->part + (size_t)t * src->M + col, src->slab_stride, n);
+    d[0] = a.x; d[1] = a.y; d[2] = a.z; d[3] = a.w;
+  } else {
+    x_raw = __ldcg(reinterpret_cast<const uint2*>(x0 + (size_t)t * H + col));
+    const __nv_bfloat162* v = reinterpret_cast<const __nv_bfloat162*>(&x_raw);
+    d[0] = b2f(v[0].x); d[1] = b2f(v[0].y); d[2] = b2f(v[1].x); d[3] = b2f(v[1].y);
+  }
+  if (p.tp > 1) tp_exchange4(p, d, t, col, point, epoch);
+#pragma unroll
+  for (int e = 0; e < 4; ++e) d[e] = bf16_round(d[e]);
+  if (have_residual) {
+    const __nv_bfloat162* r = reinterpret_cast<const __nv_bfloat162*>(&res_raw);
+    d[0] = bf16_round(b2f(r[0].x) + d[0]);
+    d[1] = bf16_round(b2f(r[0].y) + d[1]);
+    d[2] = bf16_round(b2f(r[1].x) + d[2]);
+    d[3] = bf16_round(b2f(r[1].y) + d[3]);
+  }
+  uint2 o;
+  *reinterpret_cast<__nv_bfloat162*>(&o.x) = __floats2bfloat162_rn(d[0], d[1]);
+  *reinterpret_cast<__nv_bfloat162*>(&o.y) = __floats2bfloat162_rn(d[2], d[3]);
+  *reinterpret_cast<uint2*>(res) = o;
+  if (weight != nullptr) {
+    const __nv_bfloat162* w = reinterpret_cast<const __nv_bfloat162*>(&w_raw);
+    uint2 xo;
+    *reinterpret_cast<__nv_bfloat162*>(&xo.x) = __floats2bfloat162_rn(d[0] * b2f(w[0].x), d[1] * b2f(w[0].y));
+    *reinterpret_cast<__nv_bfloat162*>(&xo.y) = __floats2bfloat162_rn(d[2] * b2f(w[1].x), d[3] * b2f(w[1].y));
+    *reinterpret_cast<uint2*>(p.xw + (size_t)t * H + col) = xo;
+    const float ss = warp_sum(d[0] * d[0] + d[1] * d[1] + d[2] * d[2] + d[3] * d[3]);
+    if (lane == 0) __stcg(ssq_out + t * SSQ_STRIDE + m, ss);
+  }
+}
+
+// The embedding rows of a step (layer 0 has no projection before it): (token, tile) items over all
+// worker warps of all CTAs.
+__device__ __forceinline__ void reduce_phase_x0(const DLParams& p, const bf16* weight, float* ssq_out, int wtid,
+                                                unsigned long long epoch) {
+  const int G = gridDim.x, cta = blockIdx.x;
+  const int warp = wtid >> 5, lane = wtid & 31;
+  const int tiles = p.H / BM;
+  const int items = p.T * tiles;
+  for (int it = cta + G * warp; it < items; it += G * NW)
+    reduce_tile(p, nullptr, p.x0, weight, false, ssq_out, it / tiles, it % tiles, lane, 0, epoch);
   fence_proxy_async_global();  // xw is read by TMA (async proxy) after the barrier
 }
 
-// 1/rms of every token from the per-segment sums of squares -> shared memory
+// 1/rms of every token from the per-tile sums of squares -> shared memory
 __device__ __forceinline__ void load_rstd(const DLParams& p, const float* ssq, float* s_rstd, int wtid) {
   const int warp = wtid >> 5, lane = wtid & 31;
-  const int nseg = (p.H + 255) / 256;
+  const int tiles = p.H / BM;
   for (int t = warp; t < p.T; t += NW) {
-    float v = lane < nseg ? __ldcg(ssq + t * 32 + lane) : 0.0f;
+    float v = lane < tiles ? __ldcg(ssq + t * SSQ_STRIDE + lane) : 0.0f;
+    if (lane + 32 < tiles) v += __ldcg(ssq + t * SSQ_STRIDE + lane + 32);
     v = warp_sum(v);
     if (lane == 0) s_rstd[t] = rsqrtf(v / (float)p.H + p.eps);
   }
   named_bar_sync(1, NWT);
 }
 
-// ---- SwiGLU phase: act = bf16(bf16(silu(bf16(rstd * sum gate))) * bf16(rstd * sum up)) -------------
-__device__ __forceinline__ void swiglu_phase(const DLParams& p, const float* s_rstd, int wtid) {
-  const int G = gridDim.x, cta = blockIdx.x;
-  const int warp = wtid >> 5, lane = wtid & 31;
+// SwiGLU of one (token, 128-column tile of the activation) on one warp:
+// act = bf16(bf16(silu(bf16(rstd * sum gate))) * bf16(rstd * sum up))
+__device__ __forceinline__ void swiglu_tile(const DLParams& p, float rstd, int t, int m, int lane) {
   const GemmGeo& g = p.geo[2];
-  const int I = p.I, nseg = (I + 255) / 256;
-  const int items = p.T * nseg;
-  for (int it = cta + G * warp; it < items; it += G * NW) {
-    const int t = it / nseg, seg = it % nseg;
-    const int col = seg * 256 + lane * 8;
-    if (col >= I) continue;
-    const float rstd = s_rstd[t];
-    float sum[2][8];
+  const int I = p.I, G = gridDim.x;
+  const int col = m * BM + lane * 4;
+  int f0, n0, f1, n1;
+  sk_tile_slabs(g, m, G, f0, n0);
+  sk_tile_slabs(g, m + I / BM, G, f1, n1);
+  const float4 ga = sum_slabs4(g.part + (size_t)t * g.M + col, g.slab_stride, n0);
+  const float4 ua = sum_slabs4(g.part + (size_t)t * g.M + I + col, g.slab_stride, n1);
+  const float gs[4] = {ga.x, ga.y, ga.z, ga.w}, us[4] = {ua.x, ua.y, ua.z, ua.w};
+  float a[4];
 #pragma unroll
-    for (int half = 0; half < 2; ++half) {
-      const int c = half * I + col;
-      int first, n;
-      sk_tile_slabs(g, c / BM, G, first, n);
-      float4 a0 = make_float4(0.f, 0.f, 0.f, 0.f), a1 = a0;
-      const float* base = g.part + (size_t)t * g.M + c;
-      for (int s = 0; s < n; ++s) {
-        const float4 v0 = __ldcg(reinterpret_cast<const float4*>(base + (size_t)s * g.slab_stride));
-        const float4 v1 = __ldcg(reinterpret_cast<const float4*>(base + (size_t)s * g.slab_stride + 4));
-        a0.x += v0.x; a0.y += v0.y; a0.z += v0.z; a0.w += v0.w;
-        a1.x += v1.x; a1.y += v1.y; a1.z += v1.z; a1.w += v1.w;
-      }
-      sum[half][0] = a0.x; sum[half][1] = a0.y; sum[half][2] = a0.z; sum[half][3] = a0.w;
-      sum[half][4] = a1.x; sum[half][5] = a1.y; sum[half][6] = a1.z; sum[half][7] = a1.w;
-    }
-    uint4 o;
-    __nv_bfloat162* op = reinterpret_cast<__nv_bfloat162*>(&o);
-#pragma unroll
-    for (int e = 0; e < 4; ++e) {
-      const float g0 = bf16_round(sum[0][2 * e] * rstd), g1 = bf16_round(sum[0][2 * e + 1] * rstd);
-      const float u0 = bf16_round(sum[1][2 * e] * rstd), u1 = bf16_round(sum[1][2 * e + 1] * rstd);
-      op[e] = __floats2bfloat162_rn(bf16_round(silu(g0)) * u0, bf16_round(silu(g1)) * u1);
-    }
-    *reinterpret_cast<uint4*>(p.act + (size_t)t * I + col) = o;
-  }
-  fence_proxy_async_global();
+  for (int e = 0; e < 4; ++e) a[e] = bf16_round(silu(bf16_round(gs[e] * rstd))) * bf16_round(us[e] * rstd);
+  uint2 o;
+  *reinterpret_cast<__nv_bfloat162*>(&o.x) = __floats2bfloat162_rn(a[0], a[1]);
+  *reinterpret_cast<__nv_bfloat162*>(&o.y) = __floats2bfloat162_rn(a[2], a[3]);
+  *reinterpret_cast<uint2*>(p.act + (size_t)t * I + col) = o;
 }
 
 // ---- attention phase ---------------------------------------------------------------------------
+// Per-step inputs that every layer reads again: copied to shared memory once per launch.
+constexpr int BT_CACHE = 1024;  // block-table entries kept in shared memory (T * max_blocks beyond that: global loads)
+struct StepConst {
+  long long slots[MAX_T];
+  int ctx[MAX_T];
+  int pos[3][MAX_T];
+  int axis[64];
+  float inv_freq[64];
+  int bt_ok;
+  int bt[BT_CACHE];
+};
 struct AttnScratch {
-  float rstd[MAX_T];
-  float q[512];          // [GQ][D] bf16 values as floats
+  float rstd[MAX_T];       // 1/rms of the layer input (QKV consumer)
+  float rstd_post[MAX_T];  // 1/rms after attention (gate/up consumer)
+  int tail_tile;           // tile whose pointwise tail this CTA runs (-1: none)
+  float q[512];            // [GQ][D] bf16 values as floats
   float kn[128], vn[128];  // the new token's K / V as attention sees them (dequantised payload)
   float kv_scale[2];
-  float m[NW][8], l[NW][8];
-  float acc[NW * 512];   // [NW][GQ][D]
+  float m[NW / 2][8], l[NW / 2][8];
+  float acc[(NW / 2) * 512];  // [NW/2][GQ][D]: warps merge in two rounds
   float coef[8][32];
   float inv[8];
   int last;
 };
-static_assert(sizeof(AttnScratch) <= SCRATCH_BYTES, "worker scratch");
+struct WorkerSmem {
+  AttnScratch attn;
+  StepConst step;
+  long long* tl_attn;  // where the current layer's attention sub-stamps go (null: off)
+};
+static_assert(sizeof(WorkerSmem) <= SCRATCH_BYTES, "worker scratch");
 
 // One (sequence, KV head, split) item on all worker warps.
 template <int D, int GQ, bool KV8>
-__device__ __noinline__ void attn_item(const DLParams& p, const LayerDesc& L, AttnScratch& sc, int b, int kvh, int split,
+__device__ __noinline__ void attn_item(const DLParams& p, const LayerDesc& L, WorkerSmem& ws, int b, int kvh, int split,
                                        int wtid) {
-  constexpr int EPL = KV8 ? 16 : 8;
-  constexpr int LPT = D / EPL;
-  constexpr int TPW = 32 / LPT;
-  constexpr int UNR = 2;
+  constexpr int EPL = 8;            // head-dimension elements per lane (8 bytes of FP8 or 16 bytes of bf16)
+  constexpr int LPT = D / EPL;      // lanes per token
+  constexpr int TPW = 32 / LPT;     // tokens per warp and load group
+  constexpr int UNR = 4;
   constexpr int PER = D / 64;
+  AttnScratch& sc = ws.attn;
+  const StepConst& cst = ws.step;
   const int G = gridDim.x;
   const int warp = wtid >> 5, lane = wtid & 31;
   const int slot_in_warp = lane / LPT, part = lane % LPT;
-  int ctx = p.context_lens[b];
+  long long* tla = ws.tl_attn;
+  int tla_i = 0;
+  auto sub_stamp = [&]() {
+    if (tla != nullptr && wtid == 0 && tla_i < TL_STAMPS - TL_PHASES) tla[tla_i++] = clock64();
+  };
+  sub_stamp();
+  int ctx = cst.ctx[b];
   {
     const long long reach = (long long)p.max_blocks * p.page;
     if ((long long)ctx > reach) {
@@ -387,8 +503,50 @@ __device__ __noinline__ void attn_item(const DLParams& p, const LayerDesc& L, At
   const int j_begin = split * per_split;
   const int j_end = min(ctx, j_begin + per_split);
   const bool owner = ctx > 0 && ctx - 1 >= j_begin && ctx - 1 < j_begin + per_split;  // this split sees the new token
+  const int j_stop = owner ? min(j_end, ctx - 1) : j_end;  // the new token comes from shared memory
   const float rstd = sc.rstd[b];
   const GemmGeo& gq = p.geo[0];
+  const int* bt_g = p.block_tables + (size_t)b * p.max_blocks;
+  const int* bt_s = cst.bt + b * p.max_blocks;
+  const bool bt_cached = cst.bt_ok != 0;
+
+  // One batch of cached tokens per warp: page-table entries, payload and scales of UNR token groups.
+  // The loaded registers are not touched before the fold (any move of a loaded value would make the
+  // warp wait for that load before it issues the next one).
+  typedef typename std::conditional<KV8, uint2, uint4>::type KvVec;  // 8 elements: 8 bytes of FP8 / 16 of bf16
+  KvVec kr[UNR], vr[UNR];
+  float ks[UNR], vs[UNR];
+  bool valid[UNR];
+  auto load_batch = [&](int j0) {
+#pragma unroll
+    for (int u = 0; u < UNR; ++u) {
+      const int j = j0 + u * TPW + slot_in_warp;
+      int blk = -1;
+      if (j < j_stop) {
+        blk = bt_cached ? bt_s[j / p.page] : bt_g[j / p.page];
+        if (p.num_blocks > 0 && blk >= p.num_blocks) {
+          prism_report(PRISM_ERR_BOUNDS, 2);
+          blk = -1;
+        }
+      }
+      valid[u] = blk >= 0;
+      ks[u] = 1.0f;
+      vs[u] = 1.0f;
+      if (valid[u]) {
+        const size_t row = ((size_t)blk * p.Hkv + kvh) * p.page + (j % p.page);
+        const size_t off = (row * D + (size_t)part * 8) * (KV8 ? 1 : 2);
+        kr[u] = __ldcg(reinterpret_cast<const KvVec*>(reinterpret_cast<const uint8_t*>(L.k_cache) + off));
+        vr[u] = __ldcg(reinterpret_cast<const KvVec*>(reinterpret_cast<const uint8_t*>(L.v_cache) + off));
+        if (KV8 && p.kv_mode == 2) {
+          ks[u] = __ldcg(L.k_scale + row);
+          vs[u] = __ldcg(L.v_scale + row);
+        }
+      }
+    }
+  };
+  // the first batch is requested before the q / k / v rows are built: it does not depend on them
+  const int j_first = j_begin + warp * TPW * UNR;
+  if (j_first < j_stop) load_batch(j_first);
 
   // ---- rows of the packed QKV projection this item needs: GQ query heads (+ K and V of the new token)
   const int nrows = GQ + (owner ? 2 : 0);
@@ -399,17 +557,41 @@ __device__ __noinline__ void attn_item(const DLParams& p, const LayerDesc& L, At
     int first, n;
     sk_tile_slabs(gq, col0 / BM, G, first, n);
     const float* base = gq.part + (size_t)b * gq.M + col0;
-    float lo[PER], hi[PER];
+    const bf16* nw = is_q ? L.q_norm : L.k_norm;
+    bf16 wlo_raw[PER], whi_raw[PER];
 #pragma unroll
-    for (int j = 0; j < PER; ++j) {
-      const int i = lane + 32 * j;
-      float s0 = 0.0f, s1 = 0.0f;
-      for (int s = 0; s < n; ++s) {
-        s0 += __ldcg(base + (size_t)s * gq.slab_stride + i);
-        s1 += __ldcg(base + (size_t)s * gq.slab_stride + i + D / 2);
+    for (int j = 0; j < PER; ++j) {  // norm weights travel together with the slabs (converted only when used)
+      wlo_raw[j] = nw[lane + 32 * j];
+      whi_raw[j] = nw[lane + 32 * j + D / 2];
+    }
+    float lo[PER], hi[PER];
+    {
+      float v0[SLAB_UNROLL][PER], v1[SLAB_UNROLL][PER];
+#pragma unroll
+      for (int s = 0; s < SLAB_UNROLL; ++s)
+#pragma unroll
+        for (int j = 0; j < PER; ++j) {
+          v0[s][j] = v1[s][j] = 0.0f;
+          if (s < n) {
+            v0[s][j] = __ldcg(base + (size_t)s * gq.slab_stride + lane + 32 * j);
+            v1[s][j] = __ldcg(base + (size_t)s * gq.slab_stride + lane + 32 * j + D / 2);
+          }
+        }
+#pragma unroll
+      for (int j = 0; j < PER; ++j) {
+        float s0 = v0[0][j], s1 = v1[0][j];
+#pragma unroll
+        for (int s = 1; s < SLAB_UNROLL; ++s) {
+          s0 += v0[s][j];
+          s1 += v1[s][j];
+        }
+        for (int s = SLAB_UNROLL; s < n; ++s) {
+          s0 += __ldcg(base + (size_t)s * gq.slab_stride + lane + 32 * j);
+          s1 += __ldcg(base + (size_t)s * gq.slab_stride + lane + 32 * j + D / 2);
+        }
+        lo[j] = bf16_round(s0 * rstd);
+        hi[j] = bf16_round(s1 * rstd);
       }
-      lo[j] = bf16_round(s0 * rstd);
-      hi[j] = bf16_round(s1 * rstd);
     }
     if (is_q || is_k) {
       float ss = 0.0f;
@@ -417,19 +599,17 @@ __device__ __noinline__ void attn_item(const DLParams& p, const LayerDesc& L, At
       for (int j = 0; j < PER; ++j) ss += lo[j] * lo[j] + hi[j] * hi[j];
       ss = warp_sum(ss);
       const float hr = rsqrtf(ss / (float)D + p.eps);
-      const bf16* w = is_q ? L.q_norm : L.k_norm;
 #pragma unroll
       for (int j = 0; j < PER; ++j) {
-        const int i = lane + 32 * j;
-        lo[j] = bf16_round(bf16_round(lo[j] * hr) * b2f(w[i]));
-        hi[j] = bf16_round(bf16_round(hi[j] * hr) * b2f(w[i + D / 2]));
+        lo[j] = bf16_round(bf16_round(lo[j] * hr) * b2f(wlo_raw[j]));
+        hi[j] = bf16_round(bf16_round(hi[j] * hr) * b2f(whi_raw[j]));
       }
 #pragma unroll
       for (int j = 0; j < PER; ++j) {
         const int i = lane + 32 * j;
-        const float pos = (float)p.positions[(size_t)p.axis[i] * p.T + b];
+        const float pos = (float)cst.pos[cst.axis[i]][b];
         float sn, cs;
-        sincosf(pos * p.inv_freq[i], &sn, &cs);
+        sincosf(pos * cst.inv_freq[i], &sn, &cs);
         sn = bf16_round(sn);
         cs = bf16_round(cs);
         const float x0 = lo[j], x1 = hi[j];
@@ -447,7 +627,7 @@ __device__ __noinline__ void attn_item(const DLParams& p, const LayerDesc& L, At
     }
     // K or V of the new token: quantise as the cache stores it, keep what attention will see
     float* keep = is_k ? sc.kn : sc.vn;
-    const long long slot = p.slots[b];
+    const long long slot = cst.slots[b];
     long long blk = slot >= 0 ? slot / p.page : -1;
     if (blk >= 0 && p.num_blocks > 0 && blk >= p.num_blocks) {
       if (lane == 0) prism_report(PRISM_ERR_BOUNDS, 3);
@@ -494,7 +674,9 @@ __device__ __noinline__ void attn_item(const DLParams& p, const LayerDesc& L, At
       }
     }
   }
+  sub_stamp();
   named_bar_sync(1, NWT);
+  sub_stamp();
 
   // ---- split-KV attention over the cached tokens [j_begin, j_stop) ------------------------------------
   float q[GQ][EPL];
@@ -510,24 +692,22 @@ __device__ __noinline__ void attn_item(const DLParams& p, const LayerDesc& L, At
 #pragma unroll
     for (int e = 0; e < EPL; ++e) acc[g][e] = 0.0f;
   }
-  const int* bt = p.block_tables + (size_t)b * p.max_blocks;
-  const int j_stop = owner ? min(j_end, ctx - 1) : j_end;  // the new token comes from shared memory
 
-  auto fold = [&](const float (&kf)[EPL], const float (&vf)[EPL], float ks, float vs, bool valid) {
+  auto fold = [&](const float (&kf)[EPL], const float (&vf)[EPL], float kscale, float vscale, bool ok) {
 #pragma unroll
     for (int g = 0; g < GQ; ++g) {
-      float s = 0.0f;
+      float sdot = 0.0f;
 #pragma unroll
-      for (int e = 0; e < EPL; ++e) s += q[g][e] * kf[e];
+      for (int e = 0; e < EPL; ++e) sdot += q[g][e] * kf[e];
 #pragma unroll
-      for (int o = LPT / 2; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
-      if (valid) {
-        s *= ks;
-        const float mn = fmaxf(m[g], s);
+      for (int o = LPT / 2; o > 0; o >>= 1) sdot += __shfl_xor_sync(0xffffffffu, sdot, o);
+      if (ok) {
+        sdot *= kscale;
+        const float mn = fmaxf(m[g], sdot);
         const float corr = __expf(m[g] - mn);
-        const float pr = __expf(s - mn);
+        const float pr = __expf(sdot - mn);
         l[g] = l[g] * corr + pr;
-        const float pv = pr * vs;
+        const float pv = pr * vscale;
 #pragma unroll
         for (int e = 0; e < EPL; ++e) acc[g][e] = acc[g][e] * corr + pv * vf[e];
         m[g] = mn;
@@ -535,37 +715,8 @@ __device__ __noinline__ void attn_item(const DLParams& p, const LayerDesc& L, At
     }
   };
 
-  for (int j0 = j_begin + warp * TPW * UNR; j0 < j_stop; j0 += TPW * NW * UNR) {
-    uint4 kr[UNR], vr[UNR];
-    float ks[UNR], vs[UNR];
-    bool valid[UNR];
-#pragma unroll
-    for (int u = 0; u < UNR; ++u) {
-      const int j = j0 + u * TPW + slot_in_warp;
-      int blk = -1;
-      if (j < j_stop) {
-        blk = bt[j / p.page];
-        if (p.num_blocks > 0 && blk >= p.num_blocks) {
-          prism_report(PRISM_ERR_BOUNDS, 2);
-          blk = -1;
-        }
-      }
-      valid[u] = blk >= 0;
-      kr[u] = make_uint4(0, 0, 0, 0);
-      vr[u] = make_uint4(0, 0, 0, 0);
-      ks[u] = 1.0f;
-      vs[u] = 1.0f;
-      if (valid[u]) {
-        const size_t row = ((size_t)blk * p.Hkv + kvh) * p.page + (j % p.page);
-        const size_t off = row * D * (KV8 ? 1 : 2) + (size_t)part * 16;
-        kr[u] = __ldcg(reinterpret_cast<const uint4*>(reinterpret_cast<const uint8_t*>(L.k_cache) + off));
-        vr[u] = __ldcg(reinterpret_cast<const uint4*>(reinterpret_cast<const uint8_t*>(L.v_cache) + off));
-        if (KV8 && p.kv_mode == 2) {
-          ks[u] = __ldcg(L.k_scale + row);
-          vs[u] = __ldcg(L.v_scale + row);
-        }
-      }
-    }
+  for (int j0 = j_first; j0 < j_stop; j0 += TPW * NW * UNR) {
+    if (j0 != j_first) load_batch(j0);
 #pragma unroll
     for (int u = 0; u < UNR; ++u) {
       float kf[EPL], vf[EPL];
@@ -573,13 +724,13 @@ __device__ __noinline__ void attn_item(const DLParams& p, const LayerDesc& L, At
         const unsigned short* kp = reinterpret_cast<const unsigned short*>(&kr[u]);
         const unsigned short* vp = reinterpret_cast<const unsigned short*>(&vr[u]);
 #pragma unroll
-        for (int e = 0; e < 8; ++e) {
+        for (int e = 0; e < 4; ++e) {
           const float2 kk = fp8x2_to_float2(kp[e]);
           const float2 vv = fp8x2_to_float2(vp[e]);
-          kf[(2 * e) % EPL] = kk.x;
-          kf[(2 * e + 1) % EPL] = kk.y;
-          vf[(2 * e) % EPL] = vv.x;
-          vf[(2 * e + 1) % EPL] = vv.y;
+          kf[2 * e] = kk.x;
+          kf[2 * e + 1] = kk.y;
+          vf[2 * e] = vv.x;
+          vf[2 * e + 1] = vv.y;
         }
       } else {
         const __nv_bfloat162* kp = reinterpret_cast<const __nv_bfloat162*>(&kr[u]);
@@ -606,7 +757,8 @@ __device__ __noinline__ void attn_item(const DLParams& p, const LayerDesc& L, At
     }
     fold(kf, vf, sc.kv_scale[0], sc.kv_scale[1], slot_in_warp == 0);
   }
-  // merge the token slots of a warp
+  sub_stamp();
+  // merge the token slots of a warp (afterwards every lane of a slice holds the warp's result)
 #pragma unroll
   for (int g = 0; g < GQ; ++g) {
 #pragma unroll
@@ -625,27 +777,49 @@ __device__ __noinline__ void attn_item(const DLParams& p, const LayerDesc& L, At
       m[g] = mn;
     }
   }
-  if (slot_in_warp == 0) {
+  // merge the warps in two rounds through NW / 2 shared-memory slots
+  constexpr int HW = NW / 2;
+  auto put = [&](int slotw) {
+    if (slot_in_warp == 0) {
+#pragma unroll
+      for (int g = 0; g < GQ; ++g) {
+        if (part == 0) {
+          sc.m[slotw][g] = m[g];
+          sc.l[slotw][g] = l[g];
+        }
+#pragma unroll
+        for (int e = 0; e < EPL; ++e) sc.acc[(slotw * GQ + g) * D + part * EPL + e] = acc[g][e];
+      }
+    }
+  };
+  if (warp >= HW) put(warp - HW);
+  named_bar_sync(1, NWT);
+  if (warp < HW) {
 #pragma unroll
     for (int g = 0; g < GQ; ++g) {
-      if (part == 0) {
-        sc.m[warp][g] = m[g];
-        sc.l[warp][g] = l[g];
-      }
+      const float mo = sc.m[warp][g], lo2 = sc.l[warp][g];
+      const float mn = fmaxf(m[g], mo);
+      const float c0 = (m[g] == -INFINITY) ? 0.0f : __expf(m[g] - mn);
+      const float c1 = (mo == -INFINITY) ? 0.0f : __expf(mo - mn);
+      l[g] = l[g] * c0 + lo2 * c1;
 #pragma unroll
-      for (int e = 0; e < EPL; ++e) sc.acc[(warp * GQ + g) * D + part * EPL + e] = acc[g][e];
+      for (int e = 0; e < EPL; ++e) acc[g][e] = acc[g][e] * c0 + sc.acc[(warp * GQ + g) * D + part * EPL + e] * c1;
+      m[g] = mn;
     }
+    __syncwarp();
+    put(warp);
   }
   named_bar_sync(1, NWT);
+  sub_stamp();
   const int ns = p.nsplit;
   for (int idx = wtid; idx < GQ * D; idx += NWT) {
     const int g = idx / D, d = idx % D;
     float mm = -INFINITY;
 #pragma unroll
-    for (int w = 0; w < NW; ++w) mm = fmaxf(mm, sc.m[w][g]);
+    for (int w = 0; w < HW; ++w) mm = fmaxf(mm, sc.m[w][g]);
     float ll = 0.0f, oo = 0.0f;
 #pragma unroll
-    for (int w = 0; w < NW; ++w) {
+    for (int w = 0; w < HW; ++w) {
       const float c = (sc.m[w][g] == -INFINITY) ? 0.0f : __expf(sc.m[w][g] - mm);
       ll += sc.l[w][g] * c;
       oo += sc.acc[(w * GQ + g) * D + d] * c;
@@ -655,10 +829,10 @@ __device__ __noinline__ void attn_item(const DLParams& p, const LayerDesc& L, At
       p.attn[((size_t)b * p.Hq + hq) * D + d] = __float2bfloat16_rn(ll > 0.0f ? oo / ll : 0.0f);
     } else {
       const size_t pidx = ((size_t)b * p.Hq + hq) * ns + split;
-      p.part_o[pidx * D + d] = oo;
+      __stcg(p.part_o + pidx * D + d, oo);
       if (d == 0) {
-        p.part_ml[pidx * 2] = mm;
-        p.part_ml[pidx * 2 + 1] = ll;
+        __stcg(p.part_ml + pidx * 2, mm);
+        __stcg(p.part_ml + pidx * 2 + 1, ll);
       }
     }
   }
@@ -672,6 +846,7 @@ __device__ __noinline__ void attn_item(const DLParams& p, const LayerDesc& L, At
       if (sc.last) p.attn_counters[b * p.Hkv + kvh] = 0;
     }
     named_bar_sync(1, NWT);
+    sub_stamp();
     if (sc.last) {
       __threadfence();
       for (int g = warp; g < GQ; g += NW) {
@@ -689,17 +864,24 @@ __device__ __noinline__ void attn_item(const DLParams& p, const LayerDesc& L, At
         const int g = idx / D, d = idx % D;
         const size_t bh = (size_t)b * p.Hq + kvh * GQ + g;
         const float* po = p.part_o + bh * ns * D + d;
+        // all partial loads in flight at once (a serial loop would pay one round trip per split)
+        float pv[32];
+#pragma unroll
+        for (int sidx = 0; sidx < 32; ++sidx) pv[sidx] = sidx < ns ? __ldcg(po + (size_t)sidx * D) : 0.0f;
         float oo = 0.0f;
-        for (int s = 0; s < ns; ++s) oo += __ldcg(po + (size_t)s * D) * sc.coef[g][s];
+#pragma unroll
+        for (int sidx = 0; sidx < 32; ++sidx) oo += pv[sidx] * sc.coef[g][sidx];
         p.attn[bh * D + d] = __float2bfloat16_rn(oo * sc.inv[g]);
       }
     }
   }
   named_bar_sync(1, NWT);  // scratch is reused by the next item
+  sub_stamp();
+  if (wtid == 0) ws.tl_attn = nullptr;  // only the CTA's first item of a layer is recorded
 }
 
 template <int D>
-__device__ __forceinline__ void attn_phase(const DLParams& p, const LayerDesc& L, AttnScratch& sc, int wtid) {
+__device__ __forceinline__ void attn_phase(const DLParams& p, const LayerDesc& L, WorkerSmem& ws, int wtid) {
   const int G = gridDim.x;
   const int GQ = p.Hq / p.Hkv;
   const int items = p.T * p.Hkv * p.nsplit;
@@ -710,8 +892,8 @@ __device__ __forceinline__ void attn_phase(const DLParams& p, const LayerDesc& L
     const int b = it / (p.nsplit * p.Hkv);
 #define PRISM_ATTN_CASE(GQ_)                                                   \
   case GQ_:                                                                    \
-    if (kv8) attn_item<D, GQ_, true>(p, L, sc, b, kvh, split, wtid);           \
-    else attn_item<D, GQ_, false>(p, L, sc, b, kvh, split, wtid);              \
+    if (kv8) attn_item<D, GQ_, true>(p, L, ws, b, kvh, split, wtid);           \
+    else attn_item<D, GQ_, false>(p, L, ws, b, kvh, split, wtid);              \
     break;
     switch (GQ) {
       PRISM_ATTN_CASE(1)
@@ -722,6 +904,50 @@ __device__ __forceinline__ void attn_phase(const DLParams& p, const LayerDesc& L
 #undef PRISM_ATTN_CASE
   }
   fence_proxy_async_global();
+}
+
+// ---- producer cursors ------------------------------------------------------------------------------
+struct UnitCursor {
+  int l, g;      // layer, GEMM (0 qkv, 1 o_proj, 2 gate/up, 3 down)
+  int u, u1;     // unit and end of this CTA's run of the current GEMM
+  int m, kb;     // weight tile and k-block of the unit
+  int kbn;       // k-blocks per tile of the current GEMM
+  bool done;
+};
+__device__ __forceinline__ void cursor_load(UnitCursor& c, const DLParams& p, int cta, int G) {
+  const GemmGeo& geo = p.geo[c.g];
+  c.u = sk_start(cta, geo.U, G);
+  c.u1 = sk_start(cta + 1, geo.U, G);
+  c.kbn = geo.kb;
+  c.m = c.u / geo.kb;
+  c.kb = c.u % geo.kb;
+}
+__device__ __forceinline__ void cursor_begin(UnitCursor& c, const DLParams& p, int cta, int G) {
+  c.l = 0;
+  c.g = 0;
+  c.done = false;
+  cursor_load(c, p, cta, G);
+}
+__device__ __forceinline__ void cursor_next(UnitCursor& c, const DLParams& p, int cta, int G) {
+  ++c.u;
+  if (++c.kb == c.kbn) {
+    c.kb = 0;
+    ++c.m;
+  }
+  if (c.u < c.u1) return;
+  if (++c.g == 4) {
+    c.g = 0;
+    if (++c.l == p.n_layers) {
+      c.done = true;
+      return;
+    }
+  }
+  cursor_load(c, p, cta, G);
+}
+// Request the box into L2 without a destination: a later TMA load of the same box hits.
+__device__ __forceinline__ void tma_prefetch_2d(const CUtensorMap* m, int x, int y) {
+  asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global.tile [%0, {%1, %2}];" ::"l"(reinterpret_cast<uint64_t>(m)), "r"(x), "r"(y)
+               : "memory");
 }
 
 // ---- the kernel ----------------------------------------------------------------------------------
@@ -772,101 +998,117 @@ decode_layers_kernel(const __grid_constant__ CUtensorMap tmXw, const __grid_cons
   if (warp == 0) {
     if (lane == 0) {
       // =============================== TMA producer ===============================
-      long long it0 = 0;  // stages issued before the current GEMM
-      bool ok = true;
-      for (int l = 0; l < p.n_layers && ok; ++l) {
-        const LayerDesc* L = p.layers + l;
-        for (int g = 0; g < 4 && ok; ++g) {
-          const GemmGeo& geo = p.geo[g];
-          const CUtensorMap* tmW = &L->tm_w[g];
-          const CUtensorMap* tmX = (g == 1) ? &tmAttn : (g == 3 ? &tmAct : &tmXw);
-          const int need_phase = l * 4 + g + 1;
-          const int u0 = sk_start(cta, geo.U, G), u1 = sk_start(cta + 1, geo.U, G);
-          int wu = u0, xu = u0;  // next unit whose weight tile / activation tile is to be issued
-          bool xready = false;
-          const long long t0 = clock64();
-          int idle = 0;
-          while (xu < u1) {
-            if (!xready && ld_acquire_cta(s_xphase) >= need_phase) {
-              xready = true;
+      // Three cursors walk this CTA's units of every GEMM of every layer in order:
+      //   P  requests weight tiles into L2 (a hint), up to pf_depth units ahead of W,
+      //   W  issues the weight tile of a unit into the next free ring stage,
+      //   X  issues the unit's activation tile once the phase that produces it has passed.
+      // W runs ahead of X by at most the ring depth and across phase and layer boundaries, so the
+      // HBM stream does not stop while the workers sit in a barrier or a pointwise phase.
+      UnitCursor P, W, X;
+      cursor_begin(P, p, cta, G);
+      W = P;
+      X = P;
+      long long n_p = 0, n_w = 0, n_x = 0;  // units passed by each cursor
+      int w_s = 0, x_s = 0;                  // ring stage of the next W / X issue
+      uint32_t w_pass = 0;                   // times the W cursor wrapped the ring
+      int xphase_seen = 0;
+      const int pf_depth = p.pf_depth;
+      long long t0 = clock64();
+      int idle = 0;
+      while (!X.done) {
+        if (n_x < n_w) {
+          const int need = X.l * 4 + X.g + 1;
+          if (xphase_seen < need) {
+            const int v = ld_acquire_cta(s_xphase);
+            if (v > xphase_seen) {
+              xphase_seen = v;
               fence_proxy_async_global();  // activations were written through the generic proxy
             }
-            if (xready && xu < wu) {
-              const long long it = it0 + (xu - u0);
-              const int s = (int)(it % stages);
-              const int kb = (int)(xu % geo.kb);
-              tma_load_2d(smem + (size_t)s * STAGE_BYTES + W_TILE_BYTES, tmX, &full[s], kb * BK, 0);
-              ++xu;
-              idle = 0;
-              continue;
-            }
-            if (wu < u1) {
-              const long long it = it0 + (wu - u0);
-              const int s = (int)(it % stages);
-              const long long round = it / stages;
-              if (round == 0 || mbar_try_wait(&empty[s], (uint32_t)(round - 1) & 1)) {
-                const int m = (int)(wu / geo.kb), kb = (int)(wu % geo.kb);
-                mbar_expect_tx(&full[s], STAGE_BYTES);
-                tma_load_2d(smem + (size_t)s * STAGE_BYTES, tmW, &full[s], kb * BK, m * BM);
-                ++wu;
-                idle = 0;
-                continue;
-              }
-            }
-            if (++idle >= 64) {
-              idle = 0;
-              if (aborted(p)) {
-                ok = false;
-                break;
-              }
-              if (clock64() - t0 > PRISM_WAIT_CYCLES) {
-                raise_abort(p, PRISM_ERR_MBAR_TIMEOUT, 100 + g);
-                ok = false;
-                break;
-              }
-            }
           }
-          if (!ok) {
-            // unwinding: weight tiles in flight must land before the CTA's shared memory is released;
-            // stages whose activation tile was never issued cannot complete and are only given a short wait
-            for (int u = (wu - u0 > stages ? wu - stages : u0); u < wu; ++u) {
-              const long long it = it0 + (u - u0);
-              (void)mbar_wait_short(&full[it % stages], (uint32_t)(it / stages) & 1);
-            }
+          if (xphase_seen >= need) {
+            const CUtensorMap* tmX = (X.g == 1) ? &tmAttn : (X.g == 3 ? &tmAct : &tmXw);
+            tma_load_2d(smem + (size_t)x_s * STAGE_BYTES + W_TILE_BYTES, tmX, &full[x_s], X.kb * BK, 0);
+            if (++x_s == stages) x_s = 0;
+            cursor_next(X, p, cta, G);
+            ++n_x;
+            idle = 0;
+            continue;
           }
-          it0 += u1 - u0;
+        }
+        if (!W.done && (w_pass == 0 || mbar_try_wait(&empty[w_s], (w_pass - 1) & 1))) {
+          mbar_expect_tx(&full[w_s], STAGE_BYTES);
+          tma_load_2d(smem + (size_t)w_s * STAGE_BYTES, &p.layers[W.l].tm_w[W.g], &full[w_s], W.kb * BK, W.m * BM);
+          if (++w_s == stages) {
+            w_s = 0;
+            ++w_pass;
+          }
+          cursor_next(W, p, cta, G);
+          ++n_w;
+          idle = 0;
+          continue;
+        }
+        if (!P.done && n_p < n_w + pf_depth) {
+          if (n_p >= n_w + stages / 2) tma_prefetch_2d(&p.layers[P.l].tm_w[P.g], P.kb * BK, P.m * BM);
+          cursor_next(P, p, cta, G);
+          ++n_p;
+          idle = 0;
+          continue;
+        }
+        if (idle == 0) t0 = clock64();
+        if (++idle >= 64) {
+          idle = 1;
+          if (aborted(p)) break;
+          if (clock64() - t0 > PRISM_WAIT_CYCLES) {
+            raise_abort(p, PRISM_ERR_MBAR_TIMEOUT, 100 + X.g);
+            break;
+          }
+        }
+      }
+      if (!X.done) {
+        // unwinding: weight tiles in flight must land before the CTA's shared memory is released;
+        // a stage whose activation tile was never issued cannot complete and only gets a short wait
+        int s2 = w_s;
+        uint32_t pass = w_pass;
+        const int back = n_w < stages ? (int)n_w : stages;
+        for (int i = 0; i < back; ++i) {
+          if (s2 == 0) {
+            s2 = stages;
+            --pass;
+          }
+          --s2;
+          (void)mbar_wait_short(&full[s2], pass & 1);
         }
       }
     }
   } else if (warp == 1) {
     if (lane == 0) {
       // =============================== MMA issuer ===============================
-      long long it = 0;
-      int segc = 0;
+      int s_i = 0;            // ring stage
+      uint32_t s_par = 0;     // its phase parity
+      int a_i = 0;            // accumulator
+      uint32_t a_use = 0;     // times the accumulator ring wrapped
       bool ok = true;
       for (int l = 0; l < p.n_layers && ok; ++l) {
         for (int g = 0; g < 4 && ok; ++g) {
           const GemmGeo& geo = p.geo[g];
           const int u0 = sk_start(cta, geo.U, G), u1 = sk_start(cta + 1, geo.U, G);
           int u = u0;
+          int kb_in_tile = u0 % geo.kb;
           while (u < u1 && ok) {
-            const int tile_end = (u / geo.kb + 1) * geo.kb;
-            const int seg_end = tile_end < u1 ? tile_end : u1;
-            const int a = segc % NACC;
-            const uint32_t use = (uint32_t)(segc / NACC);
-            if (use > 0) {
-              ok = mbar_wait_a(&acc_empty[a], (use - 1) & 1, p, 200);
+            const int left = geo.kb - kb_in_tile;
+            const int seg_end = (u + left < u1) ? u + left : u1;
+            if (a_use > 0) {
+              ok = mbar_wait_a(&acc_empty[a_i], (a_use - 1) & 1, p, 200);
               if (!ok) break;
               tc_fence_after();
             }
-            const uint32_t acc_addr = tmem_base + a * BN;
+            const uint32_t acc_addr = tmem_base + a_i * BN;
             bool first = true;
-            for (; u < seg_end; ++u, ++it) {
-              const int s = (int)(it % stages);
-              ok = mbar_wait_a(&full[s], (uint32_t)(it / stages) & 1, p, 201);
+            for (; u < seg_end; ++u) {
+              ok = mbar_wait_a(&full[s_i], s_par, p, 201);
               if (!ok) break;
               tc_fence_after();
-              const uint32_t st = smem_u32(smem + (size_t)s * STAGE_BYTES);
+              const uint32_t st = smem_u32(smem + (size_t)s_i * STAGE_BYTES);
               const uint64_t da = umma_desc_sw128(st);
               const uint64_t db = umma_desc_sw128(st + W_TILE_BYTES);
 #pragma unroll
@@ -874,10 +1116,18 @@ decode_layers_kernel(const __grid_constant__ CUtensorMap tmXw, const __grid_cons
                 tc_mma_f16(acc_addr, da + 2 * k, db + 2 * k, IDESC, (first && k == 0) ? 0u : 1u);
               }
               first = false;
-              tc_commit(&empty[s]);
+              tc_commit(&empty[s_i]);
+              if (++s_i == stages) {
+                s_i = 0;
+                s_par ^= 1;
+              }
             }
-            if (ok) tc_commit(&acc_full[a]);
-            ++segc;
+            if (ok) tc_commit(&acc_full[a_i]);
+            if (++a_i == NACC) {
+              a_i = 0;
+              ++a_use;
+            }
+            kb_in_tile = 0;
           }
         }
       }
@@ -886,14 +1136,24 @@ decode_layers_kernel(const __grid_constant__ CUtensorMap tmXw, const __grid_cons
     // =============================== workers ===============================
     const int wtid = threadIdx.x - 64;
     const int ww = wtid >> 5;  // worker warp 0..7; warps 0..3 also run the epilogues
-    AttnScratch& sc = *reinterpret_cast<AttnScratch*>(scratch);
+    WorkerSmem& ws = *reinterpret_cast<WorkerSmem*>(scratch);
+    AttnScratch& sc = ws.attn;
     int segc = 0;
     bool ok = true;
 
-    // Epilogue of GEMM g of the current layer: TMEM -> fp32 slab [slab][t][m]
-    auto epilogue = [&](int g) {
+    const unsigned long long epoch = (p.tp > 1 && p.epoch != nullptr) ? *p.epoch : 0ull;
+
+    // Epilogue of GEMM g of layer l: TMEM -> fp32 slab [slab][t][m].  For o_proj, gate/up and down
+    // the CTA that delivers the LAST partial of a weight tile (arrival counter per tile, the classic
+    // fence / counter / fence hand-off) runs the pointwise step on that tile's 128 columns right
+    // away: the reduce into the residual (+ the activation of the next GEMM and the sums of
+    // squares), or SwiGLU once the gate tile and its up tile are both complete.  No grid barrier
+    // stands between a projection and its consumer, and the tails of 32 to 96 tiles run on as many
+    // CTAs in parallel instead of on the few that a separate phase would keep busy.
+    auto epilogue = [&](int g, int l) {
       const GemmGeo& geo = p.geo[g];
       const int u0 = sk_start(cta, geo.U, G), u1 = sk_start(cta + 1, geo.U, G);
+      const int pair = p.I / BM;  // gate tile m and up tile m + pair feed the same activation tile
       int u = u0;
       while (u < u1) {
         const int m = u / geo.kb;
@@ -922,42 +1182,116 @@ decode_layers_kernel(const __grid_constant__ CUtensorMap tmXw, const __grid_cons
                 if (t < p.T) __stcg(dst + (size_t)t * geo.M, __uint_as_float(r[t]));
             }
           }
+          if (g != 0) {
+            // all four epilogue warps take part, also after a failed wait (the barrier count is fixed)
+            __threadfence();
+            named_bar_sync(2, 128);
+            if (wtid == 0) {
+              int need, first;
+              const int tile = (g == 2 && m >= pair) ? m - pair : m;
+              sk_tile_slabs(geo, tile, G, first, need);
+              if (g == 2) {
+                int n_up;
+                sk_tile_slabs(geo, tile + pair, G, first, n_up);
+                need += n_up;
+              }
+              int* cnt = p.tile_counters + (g - 1) * TILE_COUNTERS + tile;
+              const int old = atomicAdd(cnt, 1);
+              const bool last = ok && old == need - 1;
+              if (old == need - 1) *cnt = 0;  // self-resetting: the next layer's arrivals come after a grid barrier
+              sc.tail_tile = last ? tile : -1;
+            }
+            named_bar_sync(2, 128);
+            const int tile = sc.tail_tile;
+            if (tile >= 0) {
+              __threadfence();
+              if (g == 2) {
+                for (int t = ww; t < p.T; t += 4) swiglu_tile(p, sc.rstd_post[t], t, tile, lane);
+              } else if (g == 1) {
+                for (int t = ww; t < p.T; t += 4)
+                  reduce_tile(p, &geo, nullptr, p.layers[l].norm_post, true, p.ssq + MAX_T * SSQ_STRIDE, t, tile, lane, 2 * l + 1, epoch);
+              } else {
+                const bf16* w_next = l + 1 < p.n_layers ? p.layers[l + 1].norm_in : nullptr;
+                for (int t = ww; t < p.T; t += 4) reduce_tile(p, &geo, nullptr, w_next, true, p.ssq, t, tile, lane, 2 * l + 2, epoch);
+              }
+              fence_proxy_async_global();  // xw / act are read by TMA (async proxy) after the barrier
+            }
+          }
         }
         ++segc;
         u = seg_end;
       }
     };
 
+    {  // per-step inputs every layer reads again
+      StepConst& cst = ws.step;
+      const int half = D / 2;
+      for (int i = wtid; i < MAX_T; i += NWT) {
+        cst.ctx[i] = i < p.T ? p.context_lens[i] : 0;
+        cst.slots[i] = i < p.T ? p.slots[i] : -1;
+        for (int a3 = 0; a3 < 3; ++a3) cst.pos[a3][i] = i < p.T ? p.positions[(size_t)a3 * p.T + i] : 0;
+      }
+      for (int i = wtid; i < 64; i += NWT) {
+        cst.axis[i] = i < half ? min(2, max(0, p.axis[i])) : 0;
+        cst.inv_freq[i] = i < half ? p.inv_freq[i] : 0.0f;
+      }
+      const int n_bt = p.T * p.max_blocks;
+      if (wtid == 0) cst.bt_ok = n_bt <= BT_CACHE ? 1 : 0;
+      if (n_bt <= BT_CACHE)
+        for (int i = wtid; i < n_bt; i += NWT) cst.bt[i] = p.block_tables[i];
+      named_bar_sync(1, NWT);
+    }
+    unsigned long long bar_target = 0ull;
+    int stamp_i = 0;
+    long long* tl = nullptr;
+    auto stamp = [&]() {
+      if (tl != nullptr && wtid == 0 && stamp_i < TL_PHASES) tl[stamp_i++] = clock64();
+    };
+    if (wtid == 0) ws.tl_attn = nullptr;
     for (int l = 0; l < p.n_layers && ok; ++l) {
       const LayerDesc& L = p.layers[l];
-      // 1. reduce the previous projection into the residual; activation of the QKV GEMM
-      reduce_phase(p, l == 0 ? nullptr : &p.geo[3], p.x0, L.norm_in, l > 0, p.ssq, false, wtid);
-      if (!(ok = grid_barrier(p, wtid, s_abort, s_xphase, l * 4 + 1))) break;
-      // 2. QKV GEMM
-      epilogue(0);
-      if (!(ok = grid_barrier(p, wtid, s_abort, s_xphase, 0))) break;
-      // 3. q/k/v rows, KV store, attention
+      if (p.timeline != nullptr) tl = p.timeline + ((size_t)cta * p.n_layers + l) * TL_STAMPS;
+      stamp_i = 0;
+      stamp();
+      if (l == 0) {
+        // the embedding rows become the residual and the activation of the first QKV GEMM
+        reduce_phase_x0(p, L.norm_in, p.ssq, wtid, epoch);
+        stamp();
+        if (!(ok = grid_barrier(p, wtid, s_abort, s_xphase, 1, bar_target))) break;
+        stamp();
+      } else {
+        stamp();
+        stamp();
+      }
+      // 1. QKV GEMM
+      epilogue(0, l);
+      stamp();
+      if (!(ok = grid_barrier(p, wtid, s_abort, s_xphase, 0, bar_target))) break;
+      stamp();
+      // 2. q/k/v rows, KV store, attention
+      if (wtid == 0) ws.tl_attn = tl != nullptr ? tl + TL_PHASES : nullptr;
       load_rstd(p, p.ssq, sc.rstd, wtid);
-      attn_phase<D>(p, L, sc, wtid);
-      if (!(ok = grid_barrier(p, wtid, s_abort, s_xphase, l * 4 + 2))) break;
-      // 4. o_proj
-      epilogue(1);
-      if (!(ok = grid_barrier(p, wtid, s_abort, s_xphase, 0))) break;
-      // 5. reduce o_proj into the residual; activation of the gate/up GEMM
-      reduce_phase(p, &p.geo[1], nullptr, L.norm_post, true, p.ssq + MAX_T * 32, false, wtid);
-      if (!(ok = grid_barrier(p, wtid, s_abort, s_xphase, l * 4 + 3))) break;
-      // 6. gate/up GEMM
-      epilogue(2);
-      if (!(ok = grid_barrier(p, wtid, s_abort, s_xphase, 0))) break;
-      // 7. SwiGLU
-      load_rstd(p, p.ssq + MAX_T * 32, sc.rstd, wtid);
-      swiglu_phase(p, sc.rstd, wtid);
-      if (!(ok = grid_barrier(p, wtid, s_abort, s_xphase, l * 4 + 4))) break;
-      // 8. down projection
-      epilogue(3);
-      if (!(ok = grid_barrier(p, wtid, s_abort, s_xphase, 0))) break;
+      attn_phase<D>(p, L, ws, wtid);
+      stamp();
+      if (!(ok = grid_barrier(p, wtid, s_abort, s_xphase, l * 4 + 2, bar_target))) break;
+      stamp();
+      // 3. o_proj; tile tails: reduce into the residual, activation of the gate/up GEMM
+      epilogue(1, l);
+      stamp();
+      if (!(ok = grid_barrier(p, wtid, s_abort, s_xphase, l * 4 + 3, bar_target))) break;
+      stamp();
+      // 4. gate/up GEMM; tile tails: SwiGLU (needs the post-attention 1/rms)
+      load_rstd(p, p.ssq + MAX_T * SSQ_STRIDE, sc.rstd_post, wtid);
+      epilogue(2, l);
+      stamp();
+      if (!(ok = grid_barrier(p, wtid, s_abort, s_xphase, l * 4 + 4, bar_target))) break;
+      stamp();
+      // 5. down projection; tile tails: reduce into the residual, activation of the next layer's QKV GEMM
+      epilogue(3, l);
+      stamp();
+      if (!(ok = grid_barrier(p, wtid, s_abort, s_xphase, (l + 1) * 4 + 1, bar_target))) break;
+      stamp();
     }
-    if (ok) reduce_phase(p, &p.geo[3], nullptr, nullptr, true, nullptr, true, wtid);
   }
   tc_fence_before();
   __syncthreads();
@@ -1039,7 +1373,8 @@ enum DLArg {
   A_LAYERS, A_N_LAYERS, A_T, A_H, A_HQ, A_HKV, A_D, A_I, A_M_QKV, A_PAGE, A_MAX_BLOCKS, A_NUM_BLOCKS, A_KV_MODE,
   A_NSPLIT, A_EPS_BITS, A_SCALE_BITS, A_X0, A_POSITIONS, A_SLOTS, A_BLOCK_TABLES, A_CONTEXT_LENS, A_INV_FREQ, A_AXIS,
   A_RESIDUAL, A_XW, A_ATTN, A_ACT, A_SSQ, A_PART_O, A_PART_ML, A_ATTN_COUNTERS, A_GBAR, A_ABORT, A_PART_QKV, A_PART_OPROJ,
-  A_PART_GU, A_PART_DOWN, A_GRID, A_COUNT
+  A_PART_GU, A_PART_DOWN, A_GRID, A_TIMELINE, A_PF_DEPTH, A_TP, A_RANK, A_EPOCH, A_TILE_COUNTERS, A_XCH0, A_XCH1 = A_XCH0 + 8,
+  A_COUNT = A_XCH1 + 8
 };
 
 PRISM_API int prism_decode_layers(const long long* args, int n_args, void* stream_ptr) {
@@ -1075,7 +1410,7 @@ PRISM_API int prism_decode_layers(const long long* args, int n_args, void* strea
   const int GQ = p.Hq / p.Hkv;
   if ((GQ != 1 && GQ != 2 && GQ != 4 && GQ != 8) || GQ * D > 512) return -5;
   if (m_qkv != (p.Hq + 2 * p.Hkv) * D) return -6;
-  if (p.H % 64 || p.I % 64 || p.H > 8192) return -7;
+  if (p.H % 128 || p.I % 128 || p.H > 8192 || p.H / BM > TILE_COUNTERS || p.I / BM > TILE_COUNTERS) return -7;
   if (p.nsplit < 1 || p.nsplit > 32 || p.page <= 0 || p.max_blocks <= 0) return -8;
   int plan[6];
   if (prism_decode_layers_plan(p.H, m_qkv, p.Hq * D, p.I, plan) != 0) return -9;
@@ -1110,6 +1445,21 @@ PRISM_API int prism_decode_layers(const long long* args, int n_args, void* strea
   p.attn_counters = (int*)ptr(A_ATTN_COUNTERS);
   p.gbar = (unsigned long long*)ptr(A_GBAR);
   p.abort_flag = (int*)ptr(A_ABORT);
+  p.tile_counters = (int*)ptr(A_TILE_COUNTERS);
+  p.timeline = (long long*)ptr(A_TIMELINE);
+  p.pf_depth = (int)args[A_PF_DEPTH];
+  if (p.pf_depth < 0 || p.pf_depth > 256) return -11;
+  p.tp = (int)args[A_TP];
+  p.my_rank = (int)args[A_RANK];
+  p.epoch = (const unsigned long long*)ptr(A_EPOCH);
+  if (p.tp < 1 || p.tp > 8 || p.my_rank < 0 || p.my_rank >= p.tp) return -12;
+  for (int r = 0; r < 8; ++r) {
+    p.xch[0][r] = (unsigned long long*)ptr(A_XCH0 + r);
+    p.xch[1][r] = (unsigned long long*)ptr(A_XCH1 + r);
+    if (p.tp > 1 && r < p.tp && (p.xch[0][r] == nullptr || p.xch[1][r] == nullptr)) return -13;
+  }
+  if (p.tp > 1 && p.epoch == nullptr) return -13;
+  if (p.tp > 1 && 2 * p.n_layers + 1 > 127) return -14;  // exchange points of a step share the epoch's 128 sequence numbers
 
   CUtensorMap tm_xw, tm_attn, tm_act;
   int rc;

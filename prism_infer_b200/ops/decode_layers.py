@@ -27,8 +27,13 @@ _ARG_NAMES = (
     "layers", "n_layers", "T", "H", "Hq", "Hkv", "D", "I", "m_qkv", "page", "max_blocks", "num_blocks", "kv_mode",
     "nsplit", "eps_bits", "scale_bits", "x0", "positions", "slots", "block_tables", "context_lens", "inv_freq", "axis",
     "residual", "xw", "attn", "act", "ssq", "part_o", "part_ml", "attn_counters", "gbar", "abort", "part_qkv",
-    "part_oproj", "part_gu", "part_down", "grid",
-)
+    "part_oproj", "part_gu", "part_down", "grid", "timeline", "pf_depth", "tp", "rank", "epoch", "tile_counters",
+) + tuple(f"xch{s}_{r}" for s in (0, 1) for r in range(8))
+TIMELINE_STAMPS = 20  # 13 phase boundaries of a layer + 7 stamps inside the CTA's first attention item
+TIMELINE_PHASES = 13
+# weight tiles (16 KB each) the producer requests into L2 ahead of its shared-memory ring, so that HBM keeps
+# streaming while the ring waits for a barrier or a pointwise phase; 0 switches the requests off
+PREFETCH_UNITS = int(os.environ.get("PRISM_DECODE_PREFETCH_UNITS", "24"))
 
 
 def _f32_bits(x: float) -> int:
@@ -37,20 +42,28 @@ def _f32_bits(x: float) -> int:
 
 def supported(*, hidden: int, heads: int, kv_heads: int, head_dim: int, intermediate: int) -> bool:
     """Shapes the kernel handles: head dimension 64 or 128, 1 / 2 / 4 / 8 query heads per KV head
-    with at most 512 query values per KV head, 64-element multiples everywhere."""
+    with at most 512 query values per KV head, hidden and MLP widths multiples of 128."""
     if head_dim not in (64, 128) or kv_heads <= 0 or heads % kv_heads:
         return False
     gq = heads // kv_heads
     if gq not in (1, 2, 4, 8) or gq * head_dim > 512:
         return False
-    return hidden % 64 == 0 and intermediate % 64 == 0 and (heads * head_dim) % 64 == 0 and hidden <= 8192
+    return hidden % 128 == 0 and intermediate % 128 == 0 and (heads * head_dim) % 64 == 0 and hidden <= 8192
 
 
 class DecodeLayersPlan:
     def __init__(self, layers, cache, *, hidden: int, heads: int, kv_heads: int, head_dim: int, intermediate: int,
-                 eps: float, inv_freq: torch.Tensor, axis: torch.Tensor) -> None:
+                 eps: float, inv_freq: torch.Tensor, axis: torch.Tensor, tp: int = 1, rank: int = 0, epoch_ptr: int = 0,
+                 exchange_ptrs: tuple[list[int], list[int]] | None = None) -> None:
         """``layers``: the model's ``LayerWeights`` (packed qkv / o / gate_up / down and norm weights);
-        ``cache``: the ``ops.KVCache`` the layers write and read."""
+        ``cache``: the ``ops.KVCache`` the layers write and read.  Sizes are per rank.  Tensor-parallel
+        ranks pass the device address of the step-epoch word and, for each of the two exchange
+        buffers, every rank's address of it (``tp * 16 * hidden`` 8-byte words each, in peer-mapped
+        memory); the kernel then all-reduces the row-parallel projections and the embedding itself."""
+        self.tp, self.rank, self.epoch_ptr = int(tp), int(rank), int(epoch_ptr)
+        self.exchange_ptrs = exchange_ptrs
+        if self.tp > 1 and (exchange_ptrs is None or not epoch_ptr or len(exchange_ptrs[0]) < tp or len(exchange_ptrs[1]) < tp):
+            raise ValueError("tensor-parallel decode needs the epoch word and both exchange buffers of every rank")
         lib = native.lib()
         self.device = cache.payload.device
         self.cache = cache
@@ -77,8 +90,10 @@ class DecodeLayersPlan:
         self.gbar = torch.zeros(1, dtype=torch.int64, device=self.device)
         self.abort = torch.zeros(1, dtype=torch.int32, device=self.device)
         self.counters = torch.zeros(MAX_TOKENS * max(1, kv_heads), dtype=torch.int32, device=self.device)
-        self.ssq = torch.zeros(2 * MAX_TOKENS * 32, dtype=torch.float32, device=self.device)
+        self.ssq = torch.zeros(2 * MAX_TOKENS * 64, dtype=torch.float32, device=self.device)
+        self.tile_counters = torch.zeros(3 * 512, dtype=torch.int32, device=self.device)
         self._work: dict[tuple[int, int], dict[str, torch.Tensor]] = {}
+        self.timeline: torch.Tensor | None = None  # set by record_timeline(): SM clock stamps per CTA, layer, phase boundary
 
     def splits(self, tokens: int) -> int:
         """Context splits per (sequence, KV head): about one attention work item per CTA."""
@@ -125,13 +140,25 @@ class DecodeLayersPlan:
             attn_counters=self.counters.data_ptr(), gbar=self.gbar.data_ptr(), abort=self.abort.data_ptr(),
             part_qkv=w["part_qkv"].data_ptr(), part_oproj=w["part_oproj"].data_ptr(), part_gu=w["part_gu"].data_ptr(),
             part_down=w["part_down"].data_ptr(), grid=self.grid,
+            timeline=0 if self.timeline is None else self.timeline.data_ptr(), pf_depth=PREFETCH_UNITS,
+            tp=self.tp, rank=self.rank, epoch=self.epoch_ptr, tile_counters=self.tile_counters.data_ptr(),
         )
+        for slot in (0, 1):
+            for r in range(8):
+                vals[f"xch{slot}_{r}"] = self.exchange_ptrs[slot][r] if (self.tp > 1 and r < self.tp) else 0
         args = (ctypes.c_longlong * len(_ARG_NAMES))(*[int(vals[n]) for n in _ARG_NAMES])
         native.call("prism_decode_layers", ctypes.cast(args, ctypes.c_void_p), len(_ARG_NAMES),
                     torch.cuda.current_stream().cuda_stream)
         return w["residual"]
 
+    def record_timeline(self, on: bool = True) -> None:
+        """Profiling aid: have worker thread 0 of every CTA store its SM clock at each phase boundary
+        (``[grid, layers, 20]`` int64 in ``self.timeline``: 13 phase boundaries, then 7 stamps inside the CTA's
+        first attention item of the layer; differences within one CTA are cycles)."""
+        self.timeline = torch.zeros((self.grid, self.n_layers, TIMELINE_STAMPS), dtype=torch.int64, device=self.device) if on else None
+
     def reset(self) -> None:
         """Clear the abort word after a reported failure (a set word makes every later launch return at once)."""
         self.abort.zero_()
         self.counters.zero_()
+        self.tile_counters.zero_()

@@ -57,6 +57,8 @@ class TPMethod(enum.Enum):
     TIME_DECODE_GRAPH = "time_decode_graph"
     CAPACITY = "capacity"
     BARRIER = "barrier"
+    KEEP_LOGITS = "keep_logits"
+    LAST_LOGITS = "last_logits"
     STATUS = "status"
     EXIT = "exit"
 

@@ -1,0 +1,135 @@
+"""Chat-template prompts: the built-in ChatML layout, a tokenizer's own template, marker expansion
+(image placeholder runs, per-group video time stamps) and, where the reference package is
+installed next to the repository, string equality with its prompt builders on a synthetic
+checkpoint directory."""
+
+import os
+import sys
+
+import numpy as np
+import pytest
+import torch
+
+from prism_infer_b200.engine.chat_prompt import ChatPrompt, VideoTiming, encode_with_media
+from prism_infer_b200.engine.vl_inputs import (PatchProcessor, prepare_image_inputs, prepare_interleaved_image_inputs,
+                                               prepare_video_inputs)
+from prism_infer_b200.models.architecture import Qwen3VLArch
+from prism_infer_b200.utils.tokenizer import IdTokenizer
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _img(seed, size=64):
+    return np.random.default_rng(seed).integers(0, 256, (size, size, 3), dtype=np.uint8)
+
+
+def test_builtin_chatml_layouts():
+    chat = ChatPrompt(None)
+    assert not chat.has_template
+    assert chat.image_prompt("what is this?", 2) == (
+        "<|im_start|>user\n<|vision_start|><|image_pad|><|vision_end|><|vision_start|><|image_pad|><|vision_end|>"
+        "what is this?<|im_end|>\n<|im_start|>assistant\n")
+    assert chat.interleaved_image_prompt("A <image> or B <image>?", 2) == (
+        "<|im_start|>user\nA <|vision_start|><|image_pad|><|vision_end|> or B <|vision_start|><|image_pad|><|vision_end|>?"
+        "<|im_end|>\n<|im_start|>assistant\n")
+    assert chat.video_prompt("describe", add_generation_prompt=False) == (
+        "<|im_start|>user\n<|vision_start|><|video_pad|><|vision_end|>describe<|im_end|>\n")
+    with pytest.raises(ValueError, match="marker count"):
+        chat.interleaved_image_prompt("only <image> one", 2)
+
+
+def test_video_group_times_follow_the_frame_indices():
+    assert VideoTiming((0, 12, 24, 36), fps=24.0).group_times(2) == [0.25, 1.25]
+    assert VideoTiming((0, 10, 20), fps=10.0).group_times(2) == [0.5, 2.0]  # the last frame repeats
+
+
+def test_marker_expansion_with_the_offline_tokenizer():
+    arch = Qwen3VLArch.tiny()
+    tok = IdTokenizer(arch.text.vocab_size, (arch.image_token_id, arch.video_token_id, arch.vision_start_token_id,
+                                             arch.vision_end_token_id, arch.eos_token_id))
+    proc, chat = PatchProcessor(arch), ChatPrompt(None)
+    plain = prepare_image_inputs(proc, tok, "7 8 9", [_img(0), _img(1)])
+    wrapped = prepare_image_inputs(proc, tok, "7 8 9", [_img(0), _img(1)], chat=chat)
+    n_img = sum(t == arch.image_token_id for t in plain.input_ids)
+    assert n_img == sum(t == arch.image_token_id for t in wrapped.input_ids) == 2 * 4
+    assert torch.equal(plain.pixel_values, wrapped.pixel_values) and plain.image_grid_thw == wrapped.image_grid_thw
+    last = len(wrapped.input_ids) - 1 - wrapped.input_ids[::-1].index(arch.vision_end_token_id)
+    assert wrapped.input_ids[last + 1:last + 3] == [7, 8]  # the question follows the media (the offline tokenizer splits on blanks)
+    assert len(wrapped.input_ids) > len(plain.input_ids)  # the turns' own tokens
+    # token-id prompts are never wrapped
+    assert prepare_image_inputs(proc, tok, [7, 8, 9], [_img(0)], chat=chat).input_ids[-3:] == [7, 8, 9]
+    inter = prepare_interleaved_image_inputs(proc, tok, "1 <image> 2 <image> 3 4", [_img(2), _img(3)], chat=chat)
+    ids = inter.input_ids
+    first, second = ids.index(arch.vision_start_token_id), len(ids) - 1 - ids[::-1].index(arch.vision_start_token_id)
+    assert 1 in ids[:first] and 2 in ids[first:second] and 3 in ids[second:]
+    # video: one time stamp and one placeholder block per temporal group
+    frames = [_img(s) for s in range(4)]
+    vid = prepare_video_inputs(proc, tok, "5 6", frames, chat=chat, timing=VideoTiming((0, 12, 24, 36), 24.0))
+    assert vid.video_grid_thw[0][0] == 2 and sum(t == arch.vision_start_token_id for t in vid.input_ids) == 2
+    stamp = tok.encode("<0.2 seconds>")  # 0.25 formats as 0.2 (round half to even), as in the reference processor
+    at = vid.input_ids.index(arch.vision_start_token_id)
+    assert vid.input_ids[at - len(stamp):at] == stamp
+    with pytest.raises(ValueError, match="temporal groups"):
+        prepare_video_inputs(proc, tok, "5 6", frames, chat=chat, timing=VideoTiming((0, 1), 24.0))
+    with pytest.raises(ValueError, match="fewer media markers"):
+        encode_with_media(tok, "no marker here", arch, image_tokens=[4])
+
+
+@pytest.fixture(scope="module")
+def synthetic_checkpoint(tmp_path_factory):
+    """Config, word-level tokenizer with a chat template and processor configs, no weights."""
+    pytest.importorskip("tokenizers")
+    sys.path.insert(0, os.path.join(ROOT, "baseline"))
+    import reference_arm
+
+    path = str(tmp_path_factory.mktemp("ckpt"))
+    arch = Qwen3VLArch.qwen3_vl_8b()
+    reference_arm.write_checkpoint(path, arch, with_weights=False)
+    return path, arch
+
+
+def test_tokenizer_template_is_used_and_expanded(synthetic_checkpoint):
+    from transformers import AutoTokenizer
+
+    path, arch = synthetic_checkpoint
+    tok = AutoTokenizer.from_pretrained(path)
+    chat = ChatPrompt(tok)
+    assert chat.has_template
+    text = chat.image_prompt("t5 t6", 2)
+    assert text == tok.apply_chat_template([{"role": "user", "content": [{"type": "image"}, {"type": "image"},
+                                                                         {"type": "text", "text": "t5 t6"}]}],
+                                           tokenize=False, add_generation_prompt=True)
+    ids = encode_with_media(tok, text, arch, image_tokens=[3, 2])
+    assert ids.count(arch.image_token_id) == 5 and ids.count(arch.vision_start_token_id) == 2
+    # the same ids as tokenising the text with its pads repeated, which is what the Hugging Face processor does
+    expanded = text.replace("<|image_pad|>", " ".join(["<|image_pad|>"] * 3), 1)
+    head, tail = expanded.rsplit("<|image_pad|>", 1)
+    expanded = head + " ".join(["<|image_pad|>"] * 2) + tail
+    assert ids == tok.encode(expanded, add_special_tokens=False)
+
+
+def test_prompts_equal_the_reference_builders(synthetic_checkpoint):
+    """Same strings as the reference's ``build_*_prompt`` (Hugging Face processor with the same template)."""
+    ref_root = os.path.join(ROOT, "baseline", "_ref")
+    if not os.path.isdir(os.path.join(ref_root, "prism_infer")):
+        pytest.skip("the reference package is not installed under baseline/_ref")
+    from transformers import AutoTokenizer
+
+    path, _ = synthetic_checkpoint
+    tok = AutoTokenizer.from_pretrained(path)
+    with open(os.path.join(path, "chat_template.jinja"), "w") as fh:  # the processor reads its template from a file
+        fh.write(tok.chat_template)
+    sys.path.insert(0, ref_root)
+    try:
+        from prism_infer.engine.vl_inputs import (build_image_prompt, build_interleaved_image_prompt, build_video_prompt,
+                                                  load_vl_processor)
+
+        proc = load_vl_processor(path)
+    except Exception as exc:  # the reference needs more of the Hugging Face stack than this image has
+        pytest.skip(f"reference processor unavailable: {exc}")
+    finally:
+        sys.path.remove(ref_root)
+    chat, img = ChatPrompt(tok), _img(0)
+    assert chat.image_prompt("t5 t6", 2) == build_image_prompt(proc, "t5 t6", [img, img])
+    assert chat.interleaved_image_prompt("t1 <image> t2 <image>", 2) == build_interleaved_image_prompt(proc, "t1 <image> t2 <image>", [img, img])
+    assert chat.video_prompt("t9") == build_video_prompt(proc, "t9", [img, img])

@@ -56,6 +56,35 @@ def test_tiny_image_prompt_on_gpu(tiny, backend, mode):
     llm.exit()
 
 
+@pytest.fixture(scope="module")
+def wide(cuda_device):
+    """Production widths (hidden 4096, 32 / 8 heads of 128, M-RoPE 24/20/20, MLP 12288, vocabulary
+    151936, vision hidden 1152 with 72-wide heads), two decoder and two vision layers."""
+    arch = Qwen3VLArch.qwen3_vl_8b_2layer()
+    # drawn on the device (1.8 G values take minutes on the host), bf16-representable, kept on the host
+    weights = {k: v.to(torch.bfloat16).float().cpu() for k, v in random_weights(arch, dtype=torch.float32, device="cuda", seed=0).items()}
+    return arch, weights, ReferenceQwen3VL(arch, weights)
+
+
+@pytest.mark.parametrize("backend", ["eager", "cuda_graph"])
+def test_production_width_image_prompt_on_gpu(wide, backend):
+    """The whole chain at the shapes the 8B model runs (split-K slabs, 256-token scaled-FP8 pages,
+    GQA-4 decode, the persistent decode kernel, the 151936-row LM head) against the fp32 oracle."""
+    arch, weights, oracle = wide
+    image = np.random.default_rng(5).integers(0, 256, (224, 224, 3), dtype=np.uint8)
+    text = torch.randint(0, 150000, (24,), generator=torch.Generator().manual_seed(5)).tolist()
+    inputs = prepare_image_inputs(PatchProcessor(arch), load_tokenizer("random:qwen3-vl-8b-2layer", arch), text, [image])
+    want, logits = oracle.generate_greedy(inputs.input_ids, 16, pixel_values=inputs.pixel_values,
+                                          image_grid_thw=inputs.image_grid_thw, return_logits=True)
+    llm = LLM("random:qwen3-vl-8b-2layer", weights=weights, max_model_len=1024, kvcache_block_size=256, num_kvcache_blocks=6,
+              execution_backend=backend, compression_mode="scaled_fp8_kv", max_num_seqs=2, cpu_kv_cache_ratio=0.0)
+    got = llm.generate_prepared_image_inputs(inputs, SamplingParams(temperature=0.0, max_tokens=16, ignore_eos=True))
+    torch.cuda.synchronize()
+    native.check_status()
+    _agree(got["token_ids"], want, logits, margin=0.3)
+    llm.exit()
+
+
 def test_graph_decode_equals_eager_decode(tiny):
     arch, weights, _ = tiny
     prompts = [torch.randint(0, 1000, (n,), generator=torch.Generator().manual_seed(n)).tolist() for n in (9, 33, 70)]
