@@ -163,10 +163,7 @@ class ModelRunner:
         blocks = cfg.num_kvcache_blocks
         if blocks <= 0:
             if self.on_cuda:
-                free, total = torch.cuda.mem_get_info(self.device)
-                reserve = 6 << 30  # activations of a full prefill chunk, vision tower, graph pools
-                budget = int(total * cfg.gpu_memory_utilization) - (total - free) - reserve
-                blocks = max(1, budget // per_page)
+                blocks = self._measured_kv_blocks(per_page)
             else:
                 blocks = max(8, 4 * self.max_blocks)
         cpu_blocks = cfg.num_cpu_blocks
@@ -178,6 +175,45 @@ class ModelRunner:
         self.cpu_kv = ops.KVCache(t.num_layers, max(1, cpu_blocks), hkv, self.page, t.head_dim, self.kv_mode, "cpu",
                                   dtype=self.dtype, pin_memory=self.on_cuda) if cpu_blocks > 0 else None
         cfg.with_cache_capacity(blocks, cpu_blocks)
+
+    GRAPH_POOL_RESERVE = 1 << 30  # decode-graph pools, vision-tower activations and allocator slack
+
+    def _measured_kv_blocks(self, per_page: int) -> int:
+        """Pages that fit after the weights and the activations of the largest prefill step.
+
+        The activation peak is measured, not assumed (reference ``prism_infer/engine/model_runner.py:733-756,
+        795-815``): a prefill of ``max_num_batched_tokens`` placeholder tokens runs once against a scratch
+        cache, and the KV arena gets ``total * gpu_memory_utilization`` minus what is allocated now, minus
+        the measured peak above that, minus a fixed reserve for graph pools.  Every tensor-parallel rank
+        runs the same warm-up (its collectives pair up)."""
+        cfg, t = self.config, self.config.arch.text
+        dev = self.device
+        tokens = max(1, min(int(cfg.max_num_batched_tokens), int(cfg.max_model_len)))
+        hkv = t.num_kv_heads // self.comm.size
+        torch.cuda.synchronize(dev)
+        base = torch.cuda.memory_allocated(dev)
+        torch.cuda.reset_peak_memory_stats(dev)
+        scratch_pages = -(-tokens // self.page) + 1
+        scratch = ops.KVCache(t.num_layers, scratch_pages, hkv, self.page, t.head_dim, self.kv_mode, dev, dtype=self.dtype)
+        ids = torch.zeros(tokens, dtype=torch.int64, device=dev)
+        pos = torch.arange(tokens, dtype=torch.int32, device=dev).repeat(3, 1).contiguous()
+        slots = torch.arange(tokens, dtype=torch.int64, device=dev)
+        bt = torch.arange(scratch_pages, dtype=torch.int32, device=dev).view(1, -1)
+        meta = AttnMeta(is_prefill=True, block_tables=bt, slots=slots,
+                        cu_seqlens_q=torch.tensor([0, tokens], dtype=torch.int32, device=dev),
+                        kv_lens=torch.tensor([tokens], dtype=torch.int32, device=dev), max_q_len=tokens, no_history=True)
+        hidden = self.model.forward(ids, pos, meta, scratch)
+        self.model.sample(hidden[-1:], None)
+        torch.cuda.synchronize(dev)
+        peak = torch.cuda.max_memory_allocated(dev) - base - scratch.payload.numel() * scratch.payload.element_size()
+        del scratch, hidden, ids, pos, slots, bt, meta
+        torch.cuda.empty_cache()
+        free, total = torch.cuda.mem_get_info(dev)
+        used = total - free  # weights, this process's context, other processes on the device
+        budget = int(total * cfg.gpu_memory_utilization) - used - max(0, peak) - self.GRAPH_POOL_RESERVE
+        self.kv_sizing = {"warmup_tokens": tokens, "activation_peak_bytes": int(max(0, peak)), "used_bytes": int(used),
+                          "budget_bytes": int(budget)}
+        return max(1, budget // per_page)
 
     # --------------------------------------------------------------- page traffic
     def apply_kv_transfers(self, tr: KVTransferPlan) -> None:
@@ -485,7 +521,7 @@ class ModelRunner:
                 "kv_bytes_per_page": self.config.kv_bytes_per_page(), "kv_mode": self.kv_mode,
                 "launches_per_decode_graph": {str(b): getattr(g, "launches", 0) for b, g in self.graphs.items()},
                 "staging_bytes": {str(b): g.nbytes for b, g in self.graphs.items()},
-                "weight_bytes": self.model.weight_bytes()}
+                "weight_bytes": self.model.weight_bytes(), "kv_sizing": getattr(self, "kv_sizing", None)}
 
     def barrier(self) -> None:
         if self.on_cuda:

@@ -66,7 +66,7 @@ constexpr int NTHREADS = 64 + NWT;
 constexpr int NACC = 4;                      // TMEM accumulators (16 fp32 columns each)
 constexpr int TMEM_COLS = 64;
 constexpr int MAX_T = 16;
-constexpr int SCRATCH_BYTES = 20 * 1024;
+constexpr int SCRATCH_BYTES = 26 * 1024;
 constexpr int SMEM_LIMIT = 232448;
 constexpr uint32_t IDESC = umma_idesc_bf16(BM, BN);
 constexpr float FP8_MAX = 448.0f;
@@ -101,6 +101,7 @@ struct DLParams {
   int T;
   int H, Hq, Hkv, I;
   int page, max_blocks, num_blocks, kv_mode;
+  int page_shift;            // log2(page): pages are powers of two
   int nsplit;
   int stages;
   int pf_depth;  // units the L2 prefetch cursor may run ahead of the ring (0: off)
@@ -234,12 +235,29 @@ __device__ __forceinline__ int ld_acquire_cta(volatile int* addr) {
   asm volatile("ld.acquire.cta.shared.u32 %0, [%1];" : "=r"(v) : "r"(smem_u32(const_cast<int*>(addr))) : "memory");
   return v;
 }
-__device__ __forceinline__ bool grid_barrier(const DLParams& p, int wtid, volatile int* s_abort, volatile int* s_xphase,
-                                             int xphase_value, unsigned long long& target) {
+struct WorkerSmem;
+// What a worker thread carries through the phases (the phase functions are not inlined, so that
+// each exists once in the instruction stream: a decode step runs every phase once per layer, and
+// code that does not stay in the instruction cache is fetched again for every layer).
+struct WorkerCtx {
+  uint64_t* acc_full;
+  uint64_t* acc_empty;
+  uint32_t tmem_base;
+  volatile int* s_abort;
+  volatile int* s_xphase;
+  WorkerSmem* ws;
+  int wtid, ww, lane, warp;   // worker thread / worker warp / lane / warp index inside the CTA
+  int segc;                   // accumulator segments consumed so far
+  bool ok;
+  unsigned long long epoch, bar_target;
+};
+
+__device__ __noinline__ bool grid_barrier(const DLParams& p, WorkerCtx& c, int xphase_value) {
   named_bar_sync(1, NWT);
-  if (wtid == 0) {
+  if (c.wtid == 0) {
     const unsigned long long G = gridDim.x;
-    bool ok = *s_abort == 0;  // after an abort nobody waits for anybody any more (peers' aborts are seen while polling)
+    unsigned long long target = c.bar_target;
+    bool ok = *c.s_abort == 0;  // after an abort nobody waits for anybody any more (peers' aborts are seen while polling)
     if (ok) {
       if (target == 0ull) {
         unsigned long long ticket;
@@ -250,6 +268,7 @@ __device__ __forceinline__ bool grid_barrier(const DLParams& p, int wtid, volati
         asm volatile("red.release.gpu.global.add.u64 [%0], 1;" ::"l"(p.gbar) : "memory");
       }
     }
+    c.bar_target = target;
     const long long t0 = clock64();
     int polls = 0;
     while (ok) {
@@ -264,11 +283,11 @@ __device__ __forceinline__ bool grid_barrier(const DLParams& p, int wtid, volati
         }
       }
     }
-    if (!ok) *s_abort = 1;
-    else if (xphase_value > 0) st_release_cta(s_xphase, xphase_value);  // the producer may now load this phase's activations
+    if (!ok) *c.s_abort = 1;
+    else if (xphase_value > 0) st_release_cta(c.s_xphase, xphase_value);  // the producer may now load this phase's activations
   }
   named_bar_sync(1, NWT);
-  return *s_abort == 0;
+  return *c.s_abort == 0;
 }
 
 // ---- reduce: slabs (+ residual) -> residual, xw = bf16(residual * weight), ssq ---------------------
@@ -306,6 +325,7 @@ __device__ __forceinline__ void tp_exchange4(const DLParams& p, float (&d)[4], i
   const unsigned long long seq = (epoch + (unsigned long long)point) & 0xffffffffull;
   const int slot = (int)(((epoch >> 7) + (unsigned long long)point) & 1ull);
   const size_t mine = ((size_t)p.my_rank * p.T + t) * p.H + col;
+#pragma unroll 1
   for (int r = 0; r < p.tp; ++r) {
     unsigned long long* dst = p.xch[slot][r] + mine;
 #pragma unroll
@@ -317,19 +337,29 @@ __device__ __forceinline__ void tp_exchange4(const DLParams& p, float (&d)[4], i
   }
   const unsigned long long* own = p.xch[slot][p.my_rank] + (size_t)t * p.H + col;
   const unsigned int want = (unsigned int)seq;
+  const size_t rank_stride = (size_t)p.T * p.H;
   const long long t0 = clock64();
   for (;;) {
+    // every rank's words are requested before any is looked at: one round trip per attempt
+    unsigned long long w[8][4];
+#pragma unroll
+    for (int r = 0; r < 8; ++r) {
+      if (r < p.tp) {
+        const unsigned long long* q0 = own + (size_t)r * rank_stride;
+        asm volatile("ld.relaxed.sys.global.v2.u64 {%0, %1}, [%2];" : "=l"(w[r][0]), "=l"(w[r][1]) : "l"(q0) : "memory");
+        asm volatile("ld.relaxed.sys.global.v2.u64 {%0, %1}, [%2];" : "=l"(w[r][2]), "=l"(w[r][3]) : "l"(q0 + 2) : "memory");
+      }
+    }
     unsigned int stale = 0;
     d[0] = d[1] = d[2] = d[3] = 0.0f;
-    for (int r = 0; r < p.tp; ++r) {
-      const unsigned long long* q0 = own + (size_t)r * p.T * p.H;
 #pragma unroll
-      for (int e = 0; e < 2; ++e) {
-        unsigned long long w0, w1;
-        asm volatile("ld.relaxed.sys.global.v2.u64 {%0, %1}, [%2];" : "=l"(w0), "=l"(w1) : "l"(q0 + 2 * e) : "memory");
-        stale |= ((unsigned int)(w0 >> 32) ^ want) | ((unsigned int)(w1 >> 32) ^ want);
-        d[2 * e] += __uint_as_float((unsigned int)w0);
-        d[2 * e + 1] += __uint_as_float((unsigned int)w1);
+    for (int r = 0; r < 8; ++r) {
+      if (r < p.tp) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          stale |= (unsigned int)(w[r][e] >> 32) ^ want;
+          d[e] += __uint_as_float((unsigned int)w[r][e]);
+        }
       }
     }
     if (stale == 0) break;
@@ -398,15 +428,17 @@ __device__ __forceinline__ void reduce_phase_x0(const DLParams& p, const bf16* w
   const int warp = wtid >> 5, lane = wtid & 31;
   const int tiles = p.H / BM;
   const int items = p.T * tiles;
+#pragma unroll 1
   for (int it = cta + G * warp; it < items; it += G * NW)
     reduce_tile(p, nullptr, p.x0, weight, false, ssq_out, it / tiles, it % tiles, lane, 0, epoch);
   fence_proxy_async_global();  // xw is read by TMA (async proxy) after the barrier
 }
 
 // 1/rms of every token from the per-tile sums of squares -> shared memory
-__device__ __forceinline__ void load_rstd(const DLParams& p, const float* ssq, float* s_rstd, int wtid) {
+__device__ __noinline__ void load_rstd(const DLParams& p, const float* ssq, float* s_rstd, int wtid) {
   const int warp = wtid >> 5, lane = wtid & 31;
   const int tiles = p.H / BM;
+#pragma unroll 1
   for (int t = warp; t < p.T; t += NW) {
     float v = lane < tiles ? __ldcg(ssq + t * SSQ_STRIDE + lane) : 0.0f;
     if (lane + 32 < tiles) v += __ldcg(ssq + t * SSQ_STRIDE + lane + 32);
@@ -425,9 +457,35 @@ __device__ __forceinline__ void swiglu_tile(const DLParams& p, float rstd, int t
   int f0, n0, f1, n1;
   sk_tile_slabs(g, m, G, f0, n0);
   sk_tile_slabs(g, m + I / BM, G, f1, n1);
-  const float4 ga = sum_slabs4(g.part + (size_t)t * g.M + col, g.slab_stride, n0);
-  const float4 ua = sum_slabs4(g.part + (size_t)t * g.M + I + col, g.slab_stride, n1);
-  const float gs[4] = {ga.x, ga.y, ga.z, ga.w}, us[4] = {ua.x, ua.y, ua.z, ua.w};
+  // gate and up slabs are requested together (one memory round trip), then summed slab by slab
+  constexpr int SU = 4;
+  const float* gb = g.part + (size_t)t * g.M + col;
+  const float* ub = gb + I;
+  float4 gv[SU], uv[SU];
+#pragma unroll
+  for (int s2 = 0; s2 < SU; ++s2) {
+    gv[s2] = make_float4(0.f, 0.f, 0.f, 0.f);
+    uv[s2] = gv[s2];
+    if (s2 < n0) gv[s2] = __ldcg(reinterpret_cast<const float4*>(gb + (size_t)s2 * g.slab_stride));
+    if (s2 < n1) uv[s2] = __ldcg(reinterpret_cast<const float4*>(ub + (size_t)s2 * g.slab_stride));
+  }
+  float gs[4] = {gv[0].x, gv[0].y, gv[0].z, gv[0].w}, us[4] = {uv[0].x, uv[0].y, uv[0].z, uv[0].w};
+#pragma unroll
+  for (int s2 = 1; s2 < SU; ++s2) {
+    gs[0] += gv[s2].x; gs[1] += gv[s2].y; gs[2] += gv[s2].z; gs[3] += gv[s2].w;
+    us[0] += uv[s2].x; us[1] += uv[s2].y; us[2] += uv[s2].z; us[3] += uv[s2].w;
+  }
+#pragma unroll 1
+  for (int s2 = SU; s2 < max(n0, n1); ++s2) {
+    if (s2 < n0) {
+      const float4 v = __ldcg(reinterpret_cast<const float4*>(gb + (size_t)s2 * g.slab_stride));
+      gs[0] += v.x; gs[1] += v.y; gs[2] += v.z; gs[3] += v.w;
+    }
+    if (s2 < n1) {
+      const float4 v = __ldcg(reinterpret_cast<const float4*>(ub + (size_t)s2 * g.slab_stride));
+      us[0] += v.x; us[1] += v.y; us[2] += v.z; us[3] += v.w;
+    }
+  }
   float a[4];
 #pragma unroll
   for (int e = 0; e < 4; ++e) a[e] = bf16_round(silu(bf16_round(gs[e] * rstd))) * bf16_round(us[e] * rstd);
@@ -443,9 +501,8 @@ constexpr int BT_CACHE = 1024;  // block-table entries kept in shared memory (T 
 struct StepConst {
   long long slots[MAX_T];
   int ctx[MAX_T];
-  int pos[3][MAX_T];
-  int axis[64];
-  float inv_freq[64];
+  float rope_cos[MAX_T][64];  // bf16-rounded cosine / sine of every token's rotary angles: the same for all layers
+  float rope_sin[MAX_T][64];
   int bt_ok;
   int bt[BT_CACHE];
 };
@@ -469,20 +526,80 @@ struct WorkerSmem {
 };
 static_assert(sizeof(WorkerSmem) <= SCRATCH_BYTES, "worker scratch");
 
+// NB bytes (4, 8, 16 or 32) of a token row held exactly as the vector loads deliver them.  The
+// loaded registers must not be copied before they are used: a move of a loaded value makes the
+// warp wait for that load, and the loads of a batch would then complete one after another
+// instead of together.  word(i) is resolved at compile time inside unrolled loops.
+template <int NB>
+struct KvReg;
+template <>
+struct KvReg<4> {
+  uint32_t a;
+  __device__ __forceinline__ void load(const uint8_t* src) { a = __ldcg(reinterpret_cast<const uint32_t*>(src)); }
+  __device__ __forceinline__ uint32_t word(int) const { return a; }
+};
+template <>
+struct KvReg<8> {
+  uint2 a;
+  __device__ __forceinline__ void load(const uint8_t* src) { a = __ldcg(reinterpret_cast<const uint2*>(src)); }
+  __device__ __forceinline__ uint32_t word(int i) const { return i == 0 ? a.x : a.y; }
+};
+template <>
+struct KvReg<16> {
+  uint4 a;
+  __device__ __forceinline__ void load(const uint8_t* src) { a = __ldcg(reinterpret_cast<const uint4*>(src)); }
+  __device__ __forceinline__ uint32_t word(int i) const { return i == 0 ? a.x : (i == 1 ? a.y : (i == 2 ? a.z : a.w)); }
+};
+template <>
+struct KvReg<32> {
+  uint4 a, b;
+  __device__ __forceinline__ void load(const uint8_t* src) {
+    a = __ldcg(reinterpret_cast<const uint4*>(src));
+    b = __ldcg(reinterpret_cast<const uint4*>(src) + 1);
+  }
+  __device__ __forceinline__ uint32_t word(int i) const {
+    return i == 0 ? a.x : (i == 1 ? a.y : (i == 2 ? a.z : (i == 3 ? a.w : (i == 4 ? b.x : (i == 5 ? b.y : (i == 6 ? b.z : b.w))))));
+  }
+};
+template <>
+struct KvReg<64> {
+  uint4 a, b, c, d;
+  __device__ __forceinline__ void load(const uint8_t* src) {
+    a = __ldcg(reinterpret_cast<const uint4*>(src));
+    b = __ldcg(reinterpret_cast<const uint4*>(src) + 1);
+    c = __ldcg(reinterpret_cast<const uint4*>(src) + 2);
+    d = __ldcg(reinterpret_cast<const uint4*>(src) + 3);
+  }
+  __device__ __forceinline__ uint32_t word(int i) const {
+    const uint4& v = i < 4 ? a : (i < 8 ? b : (i < 12 ? c : d));
+    const int k = i & 3;
+    return k == 0 ? v.x : (k == 1 ? v.y : (k == 2 ? v.z : v.w));
+  }
+};
+
 // One (sequence, KV head, split) item on all worker warps.
+//
+// Lane layout: the GQ query heads of the KV head sit side by side in a warp (32 / GQ lanes per
+// head, D / (32 / GQ) head-dimension elements per lane), and a warp handles one cached token at a
+// time: the token's K and V slices are loaded once per slice (lanes of different heads read the
+// same address) and every head scores it in parallel.  The per-token body is a few dozen
+// instructions, so the loop stays in the instruction cache; tokens go through in batches of UNR
+// with all loads of a batch in flight together.
 template <int D, int GQ, bool KV8>
 __device__ __noinline__ void attn_item(const DLParams& p, const LayerDesc& L, WorkerSmem& ws, int b, int kvh, int split,
                                        int wtid) {
-  constexpr int EPL = 8;            // head-dimension elements per lane (8 bytes of FP8 or 16 bytes of bf16)
-  constexpr int LPT = D / EPL;      // lanes per token
-  constexpr int TPW = 32 / LPT;     // tokens per warp and load group
-  constexpr int UNR = 4;
+  constexpr int LPH = 32 / GQ;               // lanes per head
+  constexpr int EPL = D / LPH;               // head-dimension elements per lane
+  constexpr int KB = EPL * (KV8 ? 1 : 2);    // bytes of a token row per lane
+  constexpr int NWORD = KB / 4;
+  constexpr int UNR = 4;                     // tokens per warp with loads in flight together
   constexpr int PER = D / 64;
+  static_assert(EPL >= 4 && KB >= 4, "lane slice too small");
   AttnScratch& sc = ws.attn;
   const StepConst& cst = ws.step;
   const int G = gridDim.x;
   const int warp = wtid >> 5, lane = wtid & 31;
-  const int slot_in_warp = lane / LPT, part = lane % LPT;
+  const int g = lane / LPH, part = lane % LPH;
   long long* tla = ws.tl_attn;
   int tla_i = 0;
   auto sub_stamp = [&]() {
@@ -498,7 +615,7 @@ __device__ __noinline__ void attn_item(const DLParams& p, const LayerDesc& L, Wo
     }
     if (ctx < 0) ctx = 0;
   }
-  constexpr int QUANT = TPW * NW * UNR;
+  constexpr int QUANT = NW * UNR;
   const int per_split = ((ctx + p.nsplit - 1) / p.nsplit + QUANT - 1) / QUANT * QUANT;
   const int j_begin = split * per_split;
   const int j_end = min(ctx, j_begin + per_split);
@@ -506,26 +623,22 @@ __device__ __noinline__ void attn_item(const DLParams& p, const LayerDesc& L, Wo
   const int j_stop = owner ? min(j_end, ctx - 1) : j_end;  // the new token comes from shared memory
   const float rstd = sc.rstd[b];
   const GemmGeo& gq = p.geo[0];
-  const int* bt_g = p.block_tables + (size_t)b * p.max_blocks;
-  const int* bt_s = cst.bt + b * p.max_blocks;
-  const bool bt_cached = cst.bt_ok != 0;
+  const int* bt = (cst.bt_ok != 0) ? cst.bt + b * p.max_blocks : p.block_tables + (size_t)b * p.max_blocks;
 
-  // One batch of cached tokens per warp: page-table entries, payload and scales of UNR token groups.
-  // The loaded registers are not touched before the fold (any move of a loaded value would make the
-  // warp wait for that load before it issues the next one).
-  typedef typename std::conditional<KV8, uint2, uint4>::type KvVec;  // 8 elements: 8 bytes of FP8 / 16 of bf16
-  KvVec kr[UNR], vr[UNR];
+  // One batch: tokens j0 + u * NW (u < UNR) of this warp.  The loaded registers are not touched
+  // before they are used (a move of a loaded value would make the warp wait for that load).
+  KvReg<KB> kw[UNR], vw[UNR];
   float ks[UNR], vs[UNR];
   bool valid[UNR];
   auto load_batch = [&](int j0) {
 #pragma unroll
     for (int u = 0; u < UNR; ++u) {
-      const int j = j0 + u * TPW + slot_in_warp;
+      const int j = j0 + u * NW;
       int blk = -1;
       if (j < j_stop) {
-        blk = bt_cached ? bt_s[j / p.page] : bt_g[j / p.page];
+        blk = bt[j >> p.page_shift];
         if (p.num_blocks > 0 && blk >= p.num_blocks) {
-          prism_report(PRISM_ERR_BOUNDS, 2);
+          if (lane == 0) prism_report(PRISM_ERR_BOUNDS, 2);
           blk = -1;
         }
       }
@@ -533,10 +646,10 @@ __device__ __noinline__ void attn_item(const DLParams& p, const LayerDesc& L, Wo
       ks[u] = 1.0f;
       vs[u] = 1.0f;
       if (valid[u]) {
-        const size_t row = ((size_t)blk * p.Hkv + kvh) * p.page + (j % p.page);
-        const size_t off = (row * D + (size_t)part * 8) * (KV8 ? 1 : 2);
-        kr[u] = __ldcg(reinterpret_cast<const KvVec*>(reinterpret_cast<const uint8_t*>(L.k_cache) + off));
-        vr[u] = __ldcg(reinterpret_cast<const KvVec*>(reinterpret_cast<const uint8_t*>(L.v_cache) + off));
+        const size_t row = ((size_t)blk * p.Hkv + kvh) * p.page + (j & (p.page - 1));
+        const size_t off = row * D * (KV8 ? 1 : 2) + (size_t)part * KB;
+        kw[u].load(reinterpret_cast<const uint8_t*>(L.k_cache) + off);
+        vw[u].load(reinterpret_cast<const uint8_t*>(L.v_cache) + off);
         if (KV8 && p.kv_mode == 2) {
           ks[u] = __ldcg(L.k_scale + row);
           vs[u] = __ldcg(L.v_scale + row);
@@ -544,12 +657,43 @@ __device__ __noinline__ void attn_item(const DLParams& p, const LayerDesc& L, Wo
       }
     }
   };
-  // the first batch is requested before the q / k / v rows are built: it does not depend on them
-  const int j_first = j_begin + warp * TPW * UNR;
-  if (j_first < j_stop) load_batch(j_first);
+  // ---- split-KV attention over the cached tokens [j_begin, j_stop) ------------------------------------
+  float q[EPL];
+  float m = -INFINITY, l = 0.0f, acc[EPL];
+#pragma unroll
+  for (int e = 0; e < EPL; ++e) acc[e] = 0.0f;
 
+  // one token for every head of the warp: kf / vf are this lane's slice of the token's K / V row
+  auto fold = [&](const float (&kf)[EPL], const float (&vf)[EPL], float kscale, float vscale) {
+    float sdot = 0.0f;
+#pragma unroll
+    for (int e = 0; e < EPL; ++e) sdot += q[e] * kf[e];
+#pragma unroll
+    for (int o = LPH / 2; o > 0; o >>= 1) sdot += __shfl_xor_sync(0xffffffffu, sdot, o);
+    sdot *= kscale;
+    const float mn = fmaxf(m, sdot);
+    const float corr = __expf(m - mn);
+    const float pr = __expf(sdot - mn);
+    l = l * corr + pr;
+    const float pv = pr * vscale;
+#pragma unroll
+    for (int e = 0; e < EPL; ++e) acc[e] = acc[e] * corr + pv * vf[e];
+    m = mn;
+  };
+
+  // The loads of a batch are in flight while the previous batch is folded; the q / k / v rows are
+  // built inside the first pass, after the first batch (which does not depend on them) was requested.
+  const int j_first = j_begin + warp;
+  bool first_pass = true;
+#pragma unroll 1
+  for (int j0 = j_first;; j0 += NW * UNR) {
+    const bool have = j0 < j_stop;
+    if (have) load_batch(j0);
+    if (first_pass) {
+      first_pass = false;
   // ---- rows of the packed QKV projection this item needs: GQ query heads (+ K and V of the new token)
   const int nrows = GQ + (owner ? 2 : 0);
+#pragma unroll 1
   for (int r = warp; r < nrows; r += NW) {
     const bool is_q = r < GQ, is_k = r == GQ;
     const int h = is_q ? kvh * GQ + r : (is_k ? p.Hq + kvh : p.Hq + p.Hkv + kvh);
@@ -566,9 +710,10 @@ __device__ __noinline__ void attn_item(const DLParams& p, const LayerDesc& L, Wo
     }
     float lo[PER], hi[PER];
     {
-      float v0[SLAB_UNROLL][PER], v1[SLAB_UNROLL][PER];
+      constexpr int SU = 4;  // slabs whose loads are in flight together
+      float v0[SU][PER], v1[SU][PER];
 #pragma unroll
-      for (int s = 0; s < SLAB_UNROLL; ++s)
+      for (int s = 0; s < SU; ++s)
 #pragma unroll
         for (int j = 0; j < PER; ++j) {
           v0[s][j] = v1[s][j] = 0.0f;
@@ -581,11 +726,12 @@ __device__ __noinline__ void attn_item(const DLParams& p, const LayerDesc& L, Wo
       for (int j = 0; j < PER; ++j) {
         float s0 = v0[0][j], s1 = v1[0][j];
 #pragma unroll
-        for (int s = 1; s < SLAB_UNROLL; ++s) {
+        for (int s = 1; s < SU; ++s) {
           s0 += v0[s][j];
           s1 += v1[s][j];
         }
-        for (int s = SLAB_UNROLL; s < n; ++s) {
+#pragma unroll 1
+        for (int s = SU; s < n; ++s) {
           s0 += __ldcg(base + (size_t)s * gq.slab_stride + lane + 32 * j);
           s1 += __ldcg(base + (size_t)s * gq.slab_stride + lane + 32 * j + D / 2);
         }
@@ -607,11 +753,7 @@ __device__ __noinline__ void attn_item(const DLParams& p, const LayerDesc& L, Wo
 #pragma unroll
       for (int j = 0; j < PER; ++j) {
         const int i = lane + 32 * j;
-        const float pos = (float)cst.pos[cst.axis[i]][b];
-        float sn, cs;
-        sincosf(pos * cst.inv_freq[i], &sn, &cs);
-        sn = bf16_round(sn);
-        cs = bf16_round(cs);
+        const float cs = cst.rope_cos[b][i], sn = cst.rope_sin[b][i];
         const float x0 = lo[j], x1 = hi[j];
         lo[j] = bf16_round(bf16_round(x0 * cs) + bf16_round(-x1 * sn));
         hi[j] = bf16_round(bf16_round(x1 * cs) + bf16_round(x0 * sn));
@@ -674,157 +816,90 @@ __device__ __noinline__ void attn_item(const DLParams& p, const LayerDesc& L, Wo
       }
     }
   }
-  sub_stamp();
-  named_bar_sync(1, NWT);
-  sub_stamp();
-
-  // ---- split-KV attention over the cached tokens [j_begin, j_stop) ------------------------------------
-  float q[GQ][EPL];
+      sub_stamp();
+      named_bar_sync(1, NWT);
+      sub_stamp();
 #pragma unroll
-  for (int g = 0; g < GQ; ++g)
-#pragma unroll
-    for (int e = 0; e < EPL; ++e) q[g][e] = sc.q[g * D + part * EPL + e] * p.attn_scale;
-  float m[GQ], l[GQ], acc[GQ][EPL];
-#pragma unroll
-  for (int g = 0; g < GQ; ++g) {
-    m[g] = -INFINITY;
-    l[g] = 0.0f;
-#pragma unroll
-    for (int e = 0; e < EPL; ++e) acc[g][e] = 0.0f;
-  }
-
-  auto fold = [&](const float (&kf)[EPL], const float (&vf)[EPL], float kscale, float vscale, bool ok) {
-#pragma unroll
-    for (int g = 0; g < GQ; ++g) {
-      float sdot = 0.0f;
-#pragma unroll
-      for (int e = 0; e < EPL; ++e) sdot += q[g][e] * kf[e];
-#pragma unroll
-      for (int o = LPT / 2; o > 0; o >>= 1) sdot += __shfl_xor_sync(0xffffffffu, sdot, o);
-      if (ok) {
-        sdot *= kscale;
-        const float mn = fmaxf(m[g], sdot);
-        const float corr = __expf(m[g] - mn);
-        const float pr = __expf(sdot - mn);
-        l[g] = l[g] * corr + pr;
-        const float pv = pr * vscale;
-#pragma unroll
-        for (int e = 0; e < EPL; ++e) acc[g][e] = acc[g][e] * corr + pv * vf[e];
-        m[g] = mn;
-      }
+      for (int e = 0; e < EPL; ++e) q[e] = sc.q[g * D + part * EPL + e] * p.attn_scale;
     }
-  };
-
-  for (int j0 = j_first; j0 < j_stop; j0 += TPW * NW * UNR) {
-    if (j0 != j_first) load_batch(j0);
+    if (!have) break;
 #pragma unroll
     for (int u = 0; u < UNR; ++u) {
+      if (!valid[u]) continue;  // the same for every lane of the warp
       float kf[EPL], vf[EPL];
       if (KV8) {
-        const unsigned short* kp = reinterpret_cast<const unsigned short*>(&kr[u]);
-        const unsigned short* vp = reinterpret_cast<const unsigned short*>(&vr[u]);
 #pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          const float2 kk = fp8x2_to_float2(kp[e]);
-          const float2 vv = fp8x2_to_float2(vp[e]);
-          kf[2 * e] = kk.x;
-          kf[2 * e + 1] = kk.y;
-          vf[2 * e] = vv.x;
-          vf[2 * e + 1] = vv.y;
+        for (int w = 0; w < NWORD; ++w) {
+          const uint32_t kword = kw[u].word(w), vword = vw[u].word(w);
+          const float2 k0 = fp8x2_to_float2((unsigned short)(kword & 0xffffu)), k1 = fp8x2_to_float2((unsigned short)(kword >> 16));
+          const float2 v0 = fp8x2_to_float2((unsigned short)(vword & 0xffffu)), v1 = fp8x2_to_float2((unsigned short)(vword >> 16));
+          kf[4 * w] = k0.x; kf[4 * w + 1] = k0.y; kf[4 * w + 2] = k1.x; kf[4 * w + 3] = k1.y;
+          vf[4 * w] = v0.x; vf[4 * w + 1] = v0.y; vf[4 * w + 2] = v1.x; vf[4 * w + 3] = v1.y;
         }
       } else {
-        const __nv_bfloat162* kp = reinterpret_cast<const __nv_bfloat162*>(&kr[u]);
-        const __nv_bfloat162* vp = reinterpret_cast<const __nv_bfloat162*>(&vr[u]);
 #pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          const float2 kk = __bfloat1622float2(kp[e]);
-          const float2 vv = __bfloat1622float2(vp[e]);
-          kf[2 * e] = kk.x;
-          kf[2 * e + 1] = kk.y;
-          vf[2 * e] = vv.x;
-          vf[2 * e + 1] = vv.y;
+        for (int w = 0; w < NWORD; ++w) {
+          const uint32_t kword = kw[u].word(w), vword = vw[u].word(w);
+          const float2 kk = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&kword));
+          const float2 vv = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&vword));
+          kf[2 * w] = kk.x; kf[2 * w + 1] = kk.y;
+          vf[2 * w] = vv.x; vf[2 * w + 1] = vv.y;
         }
       }
-      fold(kf, vf, ks[u], vs[u], valid[u]);
+      fold(kf, vf, ks[u], vs[u]);
     }
   }
-  if (owner && warp == 0) {  // the new token, from shared memory (token slot 0 of warp 0)
+  if (owner && warp == 0) {  // the new token, from shared memory
     float kf[EPL], vf[EPL];
 #pragma unroll
     for (int e = 0; e < EPL; ++e) {
       kf[e] = sc.kn[part * EPL + e];
       vf[e] = sc.vn[part * EPL + e];
     }
-    fold(kf, vf, sc.kv_scale[0], sc.kv_scale[1], slot_in_warp == 0);
+    fold(kf, vf, sc.kv_scale[0], sc.kv_scale[1]);
   }
   sub_stamp();
-  // merge the token slots of a warp (afterwards every lane of a slice holds the warp's result)
-#pragma unroll
-  for (int g = 0; g < GQ; ++g) {
-#pragma unroll
-    for (int o = LPT; o < 32; o <<= 1) {
-      const float mo = __shfl_xor_sync(0xffffffffu, m[g], o);
-      const float lo2 = __shfl_xor_sync(0xffffffffu, l[g], o);
-      const float mn = fmaxf(m[g], mo);
-      const float c0 = (m[g] == -INFINITY) ? 0.0f : __expf(m[g] - mn);
-      const float c1 = (mo == -INFINITY) ? 0.0f : __expf(mo - mn);
-      l[g] = l[g] * c0 + lo2 * c1;
-#pragma unroll
-      for (int e = 0; e < EPL; ++e) {
-        const float ao = __shfl_xor_sync(0xffffffffu, acc[g][e], o);
-        acc[g][e] = acc[g][e] * c0 + ao * c1;
-      }
-      m[g] = mn;
-    }
-  }
   // merge the warps in two rounds through NW / 2 shared-memory slots
   constexpr int HW = NW / 2;
   auto put = [&](int slotw) {
-    if (slot_in_warp == 0) {
-#pragma unroll
-      for (int g = 0; g < GQ; ++g) {
-        if (part == 0) {
-          sc.m[slotw][g] = m[g];
-          sc.l[slotw][g] = l[g];
-        }
-#pragma unroll
-        for (int e = 0; e < EPL; ++e) sc.acc[(slotw * GQ + g) * D + part * EPL + e] = acc[g][e];
-      }
+    if (part == 0) {
+      sc.m[slotw][g] = m;
+      sc.l[slotw][g] = l;
     }
+#pragma unroll
+    for (int e = 0; e < EPL; ++e) sc.acc[(slotw * GQ + g) * D + part * EPL + e] = acc[e];
   };
   if (warp >= HW) put(warp - HW);
   named_bar_sync(1, NWT);
   if (warp < HW) {
+    const float mo = sc.m[warp][g], lo2 = sc.l[warp][g];
+    const float mn = fmaxf(m, mo);
+    const float c0 = (m == -INFINITY) ? 0.0f : __expf(m - mn);
+    const float c1 = (mo == -INFINITY) ? 0.0f : __expf(mo - mn);
+    l = l * c0 + lo2 * c1;
 #pragma unroll
-    for (int g = 0; g < GQ; ++g) {
-      const float mo = sc.m[warp][g], lo2 = sc.l[warp][g];
-      const float mn = fmaxf(m[g], mo);
-      const float c0 = (m[g] == -INFINITY) ? 0.0f : __expf(m[g] - mn);
-      const float c1 = (mo == -INFINITY) ? 0.0f : __expf(mo - mn);
-      l[g] = l[g] * c0 + lo2 * c1;
-#pragma unroll
-      for (int e = 0; e < EPL; ++e) acc[g][e] = acc[g][e] * c0 + sc.acc[(warp * GQ + g) * D + part * EPL + e] * c1;
-      m[g] = mn;
-    }
+    for (int e = 0; e < EPL; ++e) acc[e] = acc[e] * c0 + sc.acc[(warp * GQ + g) * D + part * EPL + e] * c1;
+    m = mn;
     __syncwarp();
     put(warp);
   }
   named_bar_sync(1, NWT);
   sub_stamp();
   const int ns = p.nsplit;
+#pragma unroll 1
   for (int idx = wtid; idx < GQ * D; idx += NWT) {
-    const int g = idx / D, d = idx % D;
+    const int gg = idx / D, d = idx % D;
     float mm = -INFINITY;
 #pragma unroll
-    for (int w = 0; w < HW; ++w) mm = fmaxf(mm, sc.m[w][g]);
+    for (int w = 0; w < HW; ++w) mm = fmaxf(mm, sc.m[w][gg]);
     float ll = 0.0f, oo = 0.0f;
 #pragma unroll
     for (int w = 0; w < HW; ++w) {
-      const float c = (sc.m[w][g] == -INFINITY) ? 0.0f : __expf(sc.m[w][g] - mm);
-      ll += sc.l[w][g] * c;
-      oo += sc.acc[(w * GQ + g) * D + d] * c;
+      const float c = (sc.m[w][gg] == -INFINITY) ? 0.0f : __expf(sc.m[w][gg] - mm);
+      ll += sc.l[w][gg] * c;
+      oo += sc.acc[(w * GQ + gg) * D + d] * c;
     }
-    const int hq = kvh * GQ + g;
+    const int hq = kvh * GQ + gg;
     if (ns == 1) {
       p.attn[((size_t)b * p.Hq + hq) * D + d] = __float2bfloat16_rn(ll > 0.0f ? oo / ll : 0.0f);
     } else {
@@ -849,29 +924,34 @@ __device__ __noinline__ void attn_item(const DLParams& p, const LayerDesc& L, Wo
     sub_stamp();
     if (sc.last) {
       __threadfence();
-      for (int g = warp; g < GQ; g += NW) {
-        const size_t bh = (size_t)b * p.Hq + kvh * GQ + g;
+#pragma unroll 1
+      for (int gg = warp; gg < GQ; gg += NW) {
+        const size_t bh = (size_t)b * p.Hq + kvh * GQ + gg;
         const float ms = lane < ns ? __ldcg(&p.part_ml[(bh * ns + lane) * 2]) : -INFINITY;
         const float ls = lane < ns ? __ldcg(&p.part_ml[(bh * ns + lane) * 2 + 1]) : 0.0f;
         const float mm = warp_max(ms);
         const float c = (ms == -INFINITY) ? 0.0f : __expf(ms - mm);
         const float ll = warp_sum(ls * c);
-        sc.coef[g][lane] = c;
-        if (lane == 0) sc.inv[g] = ll > 0.0f ? 1.0f / ll : 0.0f;
+        sc.coef[gg][lane] = c;
+        if (lane == 0) sc.inv[gg] = ll > 0.0f ? 1.0f / ll : 0.0f;
       }
       named_bar_sync(1, NWT);
+#pragma unroll 1
       for (int idx = wtid; idx < GQ * D; idx += NWT) {
-        const int g = idx / D, d = idx % D;
-        const size_t bh = (size_t)b * p.Hq + kvh * GQ + g;
+        const int gg = idx / D, d = idx % D;
+        const size_t bh = (size_t)b * p.Hq + kvh * GQ + gg;
         const float* po = p.part_o + bh * ns * D + d;
-        // all partial loads in flight at once (a serial loop would pay one round trip per split)
-        float pv[32];
-#pragma unroll
-        for (int sidx = 0; sidx < 32; ++sidx) pv[sidx] = sidx < ns ? __ldcg(po + (size_t)sidx * D) : 0.0f;
+        // eight partial loads in flight at a time (a plain loop would pay one round trip per split)
         float oo = 0.0f;
+#pragma unroll 1
+        for (int s0 = 0; s0 < ns; s0 += 8) {
+          float pv[8];
 #pragma unroll
-        for (int sidx = 0; sidx < 32; ++sidx) oo += pv[sidx] * sc.coef[g][sidx];
-        p.attn[bh * D + d] = __float2bfloat16_rn(oo * sc.inv[g]);
+          for (int k = 0; k < 8; ++k) pv[k] = s0 + k < ns ? __ldcg(po + (size_t)(s0 + k) * D) : 0.0f;
+#pragma unroll
+          for (int k = 0; k < 8; ++k) oo += pv[k] * sc.coef[gg][(s0 + k) & 31];
+        }
+        p.attn[bh * D + d] = __float2bfloat16_rn(oo * sc.inv[gg]);
       }
     }
   }
@@ -886,14 +966,17 @@ __device__ __forceinline__ void attn_phase(const DLParams& p, const LayerDesc& L
   const int GQ = p.Hq / p.Hkv;
   const int items = p.T * p.Hkv * p.nsplit;
   const bool kv8 = p.kv_mode != 0;
+#pragma unroll 1
   for (int it = blockIdx.x; it < items; it += G) {
     const int split = it % p.nsplit;
     const int kvh = (it / p.nsplit) % p.Hkv;
     const int b = it / (p.nsplit * p.Hkv);
 #define PRISM_ATTN_CASE(GQ_)                                                   \
   case GQ_:                                                                    \
-    if (kv8) attn_item<D, GQ_, true>(p, L, ws, b, kvh, split, wtid);           \
-    else attn_item<D, GQ_, false>(p, L, ws, b, kvh, split, wtid);              \
+    if constexpr (D * GQ_ >= 128) { /* at least four elements per lane */      \
+      if (kv8) attn_item<D, GQ_, true>(p, L, ws, b, kvh, split, wtid);         \
+      else attn_item<D, GQ_, false>(p, L, ws, b, kvh, split, wtid);            \
+    }                                                                          \
     break;
     switch (GQ) {
       PRISM_ATTN_CASE(1)
@@ -904,6 +987,91 @@ __device__ __forceinline__ void attn_phase(const DLParams& p, const LayerDesc& L
 #undef PRISM_ATTN_CASE
   }
   fence_proxy_async_global();
+}
+
+// ---- GEMM epilogue -------------------------------------------------------------------------------
+// Epilogue of GEMM g of layer l: TMEM -> fp32 slab [slab][t][m].  For o_proj, gate/up and down the
+// CTA that delivers the LAST partial of a weight tile (arrival counter per tile, the classic fence
+// / counter / fence hand-off) runs the pointwise step on that tile's 128 columns right away: the
+// reduce into the residual (+ the activation of the next GEMM and the sums of squares), or SwiGLU
+// once the gate tile and its up tile are both complete.  No grid barrier stands between a
+// projection and its consumer, and the tails of 32 to 96 tiles run on as many CTAs in parallel
+// instead of on the few that a separate phase would keep busy.
+__device__ __noinline__ void epilogue_gemm(const DLParams& p, WorkerCtx& c, int g, int l) {
+  const GemmGeo& geo = p.geo[g];
+  const int G = gridDim.x, cta = blockIdx.x;
+  AttnScratch& sc = c.ws->attn;
+  const int u0 = sk_start(cta, geo.U, G), u1 = sk_start(cta + 1, geo.U, G);
+  const int pair = p.I / BM;  // gate tile m and up tile m + pair feed the same activation tile
+  int u = u0;
+  while (u < u1) {
+    const int m = u / geo.kb;
+    const int tile_end = (m + 1) * geo.kb;
+    const int seg_end = tile_end < u1 ? tile_end : u1;
+    if (c.ww < 4) {
+      const int a = c.segc % NACC;
+      if (c.ok) c.ok = mbar_wait_a(&c.acc_full[a], (uint32_t)(c.segc / NACC) & 1, p, 300);
+      // warp-wide TMEM access stays convergent: the wait result is the same for the whole warp
+      // only after the vote
+      c.ok = __all_sync(0xffffffffu, c.ok);
+      if (c.ok) {
+        tc_fence_after();
+        const int q = (c.warp & 3);
+        uint32_t r[16];
+        tmem_ld16(c.tmem_base + a * BN + ((uint32_t)(q * 32) << 16), r);
+        tmem_ld_wait();
+        tc_fence_before();
+        if (c.lane == 0) mbar_arrive(&c.acc_empty[a]);
+        const int row = m * BM + q * 32 + c.lane;
+        if (row < geo.M) {
+          const int slab = cta - sk_owner(m * geo.kb, geo.U, G);
+          float* dst = geo.part + (size_t)slab * geo.slab_stride + row;
+#pragma unroll
+          for (int t = 0; t < BN; ++t)
+            if (t < p.T) __stcg(dst + (size_t)t * geo.M, __uint_as_float(r[t]));
+        }
+      }
+      if (g != 0) {
+        // all four epilogue warps take part, also after a failed wait (the barrier count is fixed)
+        __threadfence();
+        named_bar_sync(2, 128);
+        if (c.wtid == 0) {
+          int need, first;
+          const int tile = (g == 2 && m >= pair) ? m - pair : m;
+          sk_tile_slabs(geo, tile, G, first, need);
+          if (g == 2) {
+            int n_up;
+            sk_tile_slabs(geo, tile + pair, G, first, n_up);
+            need += n_up;
+          }
+          int* cnt = p.tile_counters + (g - 1) * TILE_COUNTERS + tile;
+          const int old = atomicAdd(cnt, 1);
+          const bool last = c.ok && old == need - 1;
+          if (old == need - 1) *cnt = 0;  // self-resetting: the next layer's arrivals come after a grid barrier
+          sc.tail_tile = last ? tile : -1;
+        }
+        named_bar_sync(2, 128);
+        const int tile = sc.tail_tile;
+        if (tile >= 0) {
+          __threadfence();
+          if (g == 2) {
+#pragma unroll 1
+            for (int t = c.ww; t < p.T; t += 4) swiglu_tile(p, sc.rstd_post[t], t, tile, c.lane);
+          } else {
+            // o_proj feeds the post-attention norm of this layer, down the input norm of the next one
+            // (none after the last layer: only the residual, the pre-norm hidden state, is written)
+            const bf16* w = g == 1 ? p.layers[l].norm_post : (l + 1 < p.n_layers ? p.layers[l + 1].norm_in : nullptr);
+            float* ssq = g == 1 ? p.ssq + MAX_T * SSQ_STRIDE : p.ssq;
+#pragma unroll 1
+            for (int t = c.ww; t < p.T; t += 4) reduce_tile(p, &geo, nullptr, w, true, ssq, t, tile, c.lane, 2 * l + (g == 1 ? 1 : 2), c.epoch);
+          }
+          fence_proxy_async_global();  // xw / act are read by TMA (async proxy) after the barrier
+        }
+      }
+    }
+    ++c.segc;
+    u = seg_end;
+  }
 }
 
 // ---- producer cursors ------------------------------------------------------------------------------
@@ -954,7 +1122,7 @@ __device__ __forceinline__ void tma_prefetch_2d(const CUtensorMap* m, int x, int
 template <int D>
 __global__ void __launch_bounds__(NTHREADS, 1)
 decode_layers_kernel(const __grid_constant__ CUtensorMap tmXw, const __grid_constant__ CUtensorMap tmAttn,
-                     const __grid_constant__ CUtensorMap tmAct, const DLParams p) {
+                     const __grid_constant__ CUtensorMap tmAct, const __grid_constant__ DLParams p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   const int stages = p.stages;
@@ -1134,94 +1302,24 @@ decode_layers_kernel(const __grid_constant__ CUtensorMap tmXw, const __grid_cons
     }
   } else {
     // =============================== workers ===============================
-    const int wtid = threadIdx.x - 64;
-    const int ww = wtid >> 5;  // worker warp 0..7; warps 0..3 also run the epilogues
     WorkerSmem& ws = *reinterpret_cast<WorkerSmem*>(scratch);
     AttnScratch& sc = ws.attn;
-    int segc = 0;
-    bool ok = true;
-
-    const unsigned long long epoch = (p.tp > 1 && p.epoch != nullptr) ? *p.epoch : 0ull;
-
-    // Epilogue of GEMM g of layer l: TMEM -> fp32 slab [slab][t][m].  For o_proj, gate/up and down
-    // the CTA that delivers the LAST partial of a weight tile (arrival counter per tile, the classic
-    // fence / counter / fence hand-off) runs the pointwise step on that tile's 128 columns right
-    // away: the reduce into the residual (+ the activation of the next GEMM and the sums of
-    // squares), or SwiGLU once the gate tile and its up tile are both complete.  No grid barrier
-    // stands between a projection and its consumer, and the tails of 32 to 96 tiles run on as many
-    // CTAs in parallel instead of on the few that a separate phase would keep busy.
-    auto epilogue = [&](int g, int l) {
-      const GemmGeo& geo = p.geo[g];
-      const int u0 = sk_start(cta, geo.U, G), u1 = sk_start(cta + 1, geo.U, G);
-      const int pair = p.I / BM;  // gate tile m and up tile m + pair feed the same activation tile
-      int u = u0;
-      while (u < u1) {
-        const int m = u / geo.kb;
-        const int tile_end = (m + 1) * geo.kb;
-        const int seg_end = tile_end < u1 ? tile_end : u1;
-        if (ww < 4) {
-          const int a = segc % NACC;
-          if (ok) ok = mbar_wait_a(&acc_full[a], (uint32_t)(segc / NACC) & 1, p, 300);
-          // warp-wide TMEM access stays convergent: the wait result is the same for the whole
-          // warp only after the vote
-          ok = __all_sync(0xffffffffu, ok);
-          if (ok) {
-            tc_fence_after();
-            const int q = (warp & 3);
-            uint32_t r[16];
-            tmem_ld16(tmem_base + a * BN + ((uint32_t)(q * 32) << 16), r);
-            tmem_ld_wait();
-            tc_fence_before();
-            if (lane == 0) mbar_arrive(&acc_empty[a]);
-            const int row = m * BM + q * 32 + lane;
-            if (row < geo.M) {
-              const int slab = cta - sk_owner(m * geo.kb, geo.U, G);
-              float* dst = geo.part + (size_t)slab * geo.slab_stride + row;
-#pragma unroll
-              for (int t = 0; t < BN; ++t)
-                if (t < p.T) __stcg(dst + (size_t)t * geo.M, __uint_as_float(r[t]));
-            }
-          }
-          if (g != 0) {
-            // all four epilogue warps take part, also after a failed wait (the barrier count is fixed)
-            __threadfence();
-            named_bar_sync(2, 128);
-            if (wtid == 0) {
-              int need, first;
-              const int tile = (g == 2 && m >= pair) ? m - pair : m;
-              sk_tile_slabs(geo, tile, G, first, need);
-              if (g == 2) {
-                int n_up;
-                sk_tile_slabs(geo, tile + pair, G, first, n_up);
-                need += n_up;
-              }
-              int* cnt = p.tile_counters + (g - 1) * TILE_COUNTERS + tile;
-              const int old = atomicAdd(cnt, 1);
-              const bool last = ok && old == need - 1;
-              if (old == need - 1) *cnt = 0;  // self-resetting: the next layer's arrivals come after a grid barrier
-              sc.tail_tile = last ? tile : -1;
-            }
-            named_bar_sync(2, 128);
-            const int tile = sc.tail_tile;
-            if (tile >= 0) {
-              __threadfence();
-              if (g == 2) {
-                for (int t = ww; t < p.T; t += 4) swiglu_tile(p, sc.rstd_post[t], t, tile, lane);
-              } else if (g == 1) {
-                for (int t = ww; t < p.T; t += 4)
-                  reduce_tile(p, &geo, nullptr, p.layers[l].norm_post, true, p.ssq + MAX_T * SSQ_STRIDE, t, tile, lane, 2 * l + 1, epoch);
-              } else {
-                const bf16* w_next = l + 1 < p.n_layers ? p.layers[l + 1].norm_in : nullptr;
-                for (int t = ww; t < p.T; t += 4) reduce_tile(p, &geo, nullptr, w_next, true, p.ssq, t, tile, lane, 2 * l + 2, epoch);
-              }
-              fence_proxy_async_global();  // xw / act are read by TMA (async proxy) after the barrier
-            }
-          }
-        }
-        ++segc;
-        u = seg_end;
-      }
-    };
+    WorkerCtx c;
+    c.acc_full = acc_full;
+    c.acc_empty = acc_empty;
+    c.tmem_base = tmem_base;
+    c.s_abort = s_abort;
+    c.s_xphase = s_xphase;
+    c.ws = &ws;
+    c.wtid = threadIdx.x - 64;
+    c.ww = c.wtid >> 5;  // worker warp 0..7; warps 0..3 also run the epilogues
+    c.lane = lane;
+    c.warp = warp;
+    c.segc = 0;
+    c.ok = true;
+    c.epoch = (p.tp > 1 && p.epoch != nullptr) ? *p.epoch : 0ull;
+    c.bar_target = 0ull;
+    const int wtid = c.wtid;
 
     {  // per-step inputs every layer reads again
       StepConst& cst = ws.step;
@@ -1229,25 +1327,32 @@ decode_layers_kernel(const __grid_constant__ CUtensorMap tmXw, const __grid_cons
       for (int i = wtid; i < MAX_T; i += NWT) {
         cst.ctx[i] = i < p.T ? p.context_lens[i] : 0;
         cst.slots[i] = i < p.T ? p.slots[i] : -1;
-        for (int a3 = 0; a3 < 3; ++a3) cst.pos[a3][i] = i < p.T ? p.positions[(size_t)a3 * p.T + i] : 0;
       }
-      for (int i = wtid; i < 64; i += NWT) {
-        cst.axis[i] = i < half ? min(2, max(0, p.axis[i])) : 0;
-        cst.inv_freq[i] = i < half ? p.inv_freq[i] : 0.0f;
+      // rotary angles depend on the token and the frequency slot, not on the layer: evaluated once
+      // per launch (position of the slot's axis times its inverse frequency; bf16 like the eager graph)
+      for (int i = wtid; i < p.T * half; i += NWT) {
+        const int t = i / half, f = i % half;
+        const int ax = min(2, max(0, p.axis[f]));
+        float sn, cs;
+        sincosf((float)p.positions[(size_t)ax * p.T + t] * p.inv_freq[f], &sn, &cs);
+        cst.rope_cos[t][f] = bf16_round(cs);
+        cst.rope_sin[t][f] = bf16_round(sn);
       }
       const int n_bt = p.T * p.max_blocks;
-      if (wtid == 0) cst.bt_ok = n_bt <= BT_CACHE ? 1 : 0;
+      if (wtid == 0) {
+        cst.bt_ok = n_bt <= BT_CACHE ? 1 : 0;
+        ws.tl_attn = nullptr;
+      }
       if (n_bt <= BT_CACHE)
         for (int i = wtid; i < n_bt; i += NWT) cst.bt[i] = p.block_tables[i];
       named_bar_sync(1, NWT);
     }
-    unsigned long long bar_target = 0ull;
     int stamp_i = 0;
     long long* tl = nullptr;
     auto stamp = [&]() {
       if (tl != nullptr && wtid == 0 && stamp_i < TL_PHASES) tl[stamp_i++] = clock64();
     };
-    if (wtid == 0) ws.tl_attn = nullptr;
+    bool ok = true;
     for (int l = 0; l < p.n_layers && ok; ++l) {
       const LayerDesc& L = p.layers[l];
       if (p.timeline != nullptr) tl = p.timeline + ((size_t)cta * p.n_layers + l) * TL_STAMPS;
@@ -1255,42 +1360,34 @@ decode_layers_kernel(const __grid_constant__ CUtensorMap tmXw, const __grid_cons
       stamp();
       if (l == 0) {
         // the embedding rows become the residual and the activation of the first QKV GEMM
-        reduce_phase_x0(p, L.norm_in, p.ssq, wtid, epoch);
+        reduce_phase_x0(p, L.norm_in, p.ssq, wtid, c.epoch);
         stamp();
-        if (!(ok = grid_barrier(p, wtid, s_abort, s_xphase, 1, bar_target))) break;
+        if (!(ok = grid_barrier(p, c, 1))) break;
         stamp();
       } else {
         stamp();
         stamp();
       }
-      // 1. QKV GEMM
-      epilogue(0, l);
-      stamp();
-      if (!(ok = grid_barrier(p, wtid, s_abort, s_xphase, 0, bar_target))) break;
-      stamp();
-      // 2. q/k/v rows, KV store, attention
-      if (wtid == 0) ws.tl_attn = tl != nullptr ? tl + TL_PHASES : nullptr;
-      load_rstd(p, p.ssq, sc.rstd, wtid);
-      attn_phase<D>(p, L, ws, wtid);
-      stamp();
-      if (!(ok = grid_barrier(p, wtid, s_abort, s_xphase, l * 4 + 2, bar_target))) break;
-      stamp();
-      // 3. o_proj; tile tails: reduce into the residual, activation of the gate/up GEMM
-      epilogue(1, l);
-      stamp();
-      if (!(ok = grid_barrier(p, wtid, s_abort, s_xphase, l * 4 + 3, bar_target))) break;
-      stamp();
-      // 4. gate/up GEMM; tile tails: SwiGLU (needs the post-attention 1/rms)
-      load_rstd(p, p.ssq + MAX_T * SSQ_STRIDE, sc.rstd_post, wtid);
-      epilogue(2, l);
-      stamp();
-      if (!(ok = grid_barrier(p, wtid, s_abort, s_xphase, l * 4 + 4, bar_target))) break;
-      stamp();
-      // 5. down projection; tile tails: reduce into the residual, activation of the next layer's QKV GEMM
-      epilogue(3, l);
-      stamp();
-      if (!(ok = grid_barrier(p, wtid, s_abort, s_xphase, (l + 1) * 4 + 1, bar_target))) break;
-      stamp();
+      // phases: 0 QKV GEMM | 1 q/k/v rows, KV store, attention | 2 o_proj (+ reduce tails) |
+      // 3 gate/up (+ SwiGLU tails) | 4 down (+ reduce tails); a grid barrier after each
+#pragma unroll 1
+      for (int ph = 0; ph < 5 && ok; ++ph) {
+        if (ph == 1) {
+          if (wtid == 0) ws.tl_attn = tl != nullptr ? tl + TL_PHASES : nullptr;
+          load_rstd(p, p.ssq, sc.rstd, wtid);
+          attn_phase<D>(p, L, ws, wtid);
+        } else {
+          const int g = ph == 0 ? 0 : ph - 1;
+          if (g == 2) load_rstd(p, p.ssq + MAX_T * SSQ_STRIDE, sc.rstd_post, wtid);  // the SwiGLU tails need the post-attention 1/rms
+          epilogue_gemm(p, c, g, l);
+        }
+        stamp();
+        // activations the producer may load after this barrier: o_proj's after attention, gate/up's
+        // after the o_proj tails, down's after the SwiGLU tails, the next layer's QKV after the down tails
+        const int xv = ph == 0 ? 0 : (ph < 4 ? l * 4 + ph + 1 : (l + 1) * 4 + 1);
+        ok = grid_barrier(p, c, xv);
+        stamp();
+      }
     }
   }
   tc_fence_before();
@@ -1408,10 +1505,12 @@ PRISM_API int prism_decode_layers(const long long* args, int n_args, void* strea
   if (D != 64 && D != 128) return -3;
   if (p.Hq <= 0 || p.Hkv <= 0 || p.Hq % p.Hkv) return -4;
   const int GQ = p.Hq / p.Hkv;
-  if ((GQ != 1 && GQ != 2 && GQ != 4 && GQ != 8) || GQ * D > 512) return -5;
+  if ((GQ != 1 && GQ != 2 && GQ != 4 && GQ != 8) || GQ * D > 512 || GQ * D < 128) return -5;
   if (m_qkv != (p.Hq + 2 * p.Hkv) * D) return -6;
   if (p.H % 128 || p.I % 128 || p.H > 8192 || p.H / BM > TILE_COUNTERS || p.I / BM > TILE_COUNTERS) return -7;
-  if (p.nsplit < 1 || p.nsplit > 32 || p.page <= 0 || p.max_blocks <= 0) return -8;
+  if (p.nsplit < 1 || p.nsplit > 32 || p.page <= 0 || (p.page & (p.page - 1)) || p.max_blocks <= 0) return -8;
+  p.page_shift = 0;
+  while ((1 << p.page_shift) < p.page) ++p.page_shift;
   int plan[6];
   if (prism_decode_layers_plan(p.H, m_qkv, p.Hq * D, p.I, plan) != 0) return -9;
   const int G = (int)args[A_GRID];

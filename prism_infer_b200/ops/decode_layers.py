@@ -42,11 +42,11 @@ def _f32_bits(x: float) -> int:
 
 def supported(*, hidden: int, heads: int, kv_heads: int, head_dim: int, intermediate: int) -> bool:
     """Shapes the kernel handles: head dimension 64 or 128, 1 / 2 / 4 / 8 query heads per KV head
-    with at most 512 query values per KV head, hidden and MLP widths multiples of 128."""
+    with 128 to 512 query values per KV head, hidden and MLP widths multiples of 128."""
     if head_dim not in (64, 128) or kv_heads <= 0 or heads % kv_heads:
         return False
     gq = heads // kv_heads
-    if gq not in (1, 2, 4, 8) or gq * head_dim > 512:
+    if gq not in (1, 2, 4, 8) or not 128 <= gq * head_dim <= 512:
         return False
     return hidden % 128 == 0 and intermediate % 128 == 0 and (heads * head_dim) % 64 == 0 and hidden <= 8192
 

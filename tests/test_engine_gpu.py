@@ -117,6 +117,22 @@ def test_prefix_hit_and_compaction_on_gpu(tiny):
     llm.exit()
 
 
+def test_kv_arena_is_sized_from_a_measured_prefill(tiny):
+    """Without an explicit page count the runner measures the activation peak of a full prefill step
+    and gives the rest of the memory budget to the KV arena."""
+    arch, weights, _ = tiny
+    llm = LLM("random:tiny", weights=weights, max_model_len=512, kvcache_block_size=64, max_num_batched_tokens=512,
+              gpu_memory_utilization=0.05, max_num_seqs=2, cpu_kv_cache_ratio=0.0)
+    meta = llm.graph_metadata()
+    sizing = meta["kv_sizing"]
+    assert sizing is not None and sizing["warmup_tokens"] == 512 and sizing["activation_peak_bytes"] > 0
+    assert meta["kv_pages"] >= 1 and meta["kv_pages"] == max(1, sizing["budget_bytes"] // meta["kv_bytes_per_page"])
+    out = llm.generate([[1, 2, 3, 4]], SamplingParams(temperature=0.0, max_tokens=4, ignore_eos=True))
+    assert len(out[0]["token_ids"]) == 4
+    native.check_status()
+    llm.exit()
+
+
 def test_temperature_sampling_runs_in_graph(tiny):
     arch, weights, _ = tiny
     llm = LLM("random:tiny", weights=weights, max_model_len=256, kvcache_block_size=16, num_kvcache_blocks=32,
