@@ -1,10 +1,11 @@
-"""Phase timeline of the persistent decode kernel (``ops/csrc/decode_layers.cu``).
+"""Step timeline of the persistent decode kernel (``ops/csrc/decode_layers.cu``).
 
-Worker thread 0 of every CTA stores its SM clock at each phase boundary of each layer; this
+Worker thread 0 of every CTA stores the GPU-wide nanosecond timer at each step boundary of each layer; this
 script runs a few decode steps of a random-init model with the recording on and prints, per
-phase, the mean and the maximum over CTAs (averaged over layers) in microseconds, next to the
-device time of a step with the recording off.  The barrier rows are waits: a long barrier after a
-short phase means some other CTA's phase was long.
+step of a layer, the mean and the maximum over CTAs (averaged over layers) in microseconds, next
+to the device time of a whole decode step with the recording off.  Most rows are waits for other
+CTAs' values (the kernel has no barriers: a CTA proceeds as soon as the words it polls carry the
+hand-off's sequence number), so a long row names the hand-off the layer is bound by.
 
     python benchmarks/profile_decode_layers.py [--model random:qwen3-vl-8b] [--context 1616] [--batch 1]
 """
@@ -20,10 +21,23 @@ sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 
 import torch
 
-PHASES = ("embedding rows -> residual, xw (first layer only)", "barrier (first layer only)", "qkv epilogue (waits for the GEMM)",
-          "barrier", "q/k/v rows + attention", "barrier", "o_proj epilogue + reduce tails", "barrier",
-          "gate/up epilogue + swiglu tails", "barrier", "down epilogue + reduce tails", "barrier")
-N_PHASE_STAMPS = 13
+PHASES = (
+    "poll residual*w + 1/rms into shared memory (QKV input)",
+    "QKV epilogue (waits for the CTA's MMAs)",
+    "attention: q/k/v rows from the QKV words, KV store",
+    "attention: fold staged cached tokens",
+    "attention: merge warps, publish the split",
+    "attention: split 0 merges the splits",
+    "poll attention output into shared memory (o_proj input)",
+    "o_proj epilogue",
+    "residual tile owner: sum o_proj words, publish residual*w",
+    "poll residual*w + 1/rms (gate/up input)",
+    "gate/up epilogue",
+    "activation tile owner: SwiGLU",
+    "poll activations (down input)",
+    "down epilogue",
+    "residual tile owner: sum down words, publish residual*w",
+)
 
 
 def main() -> None:
@@ -73,39 +87,35 @@ def main() -> None:
     plain_ms = timed(args.steps)
     plan.record_timeline(True)
     timed(2)
-    tl = plan.timeline.cpu().double()  # [grid, layers, 20]
+    tl = plan.timeline.cpu().double()  # [grid, layers, 16]
     plan.record_timeline(False)
     ops.native.check_status()
-    try:
-        mhz = float(torch.cuda.clock_rate())  # current SM clock
-    except Exception:  # no NVML binding: the part's maximum
-        mhz = 1965.0
-    sub = tl[:, :, N_PHASE_STAMPS:]
-    tl = tl[:, :, :N_PHASE_STAMPS]
-    d = (tl[:, :, 1:] - tl[:, :, :-1]) / mhz  # microseconds per phase
-    layers = slice(1, None) if d.shape[1] > 1 else slice(0, None)
-    mean = d[:, layers].mean(dim=(0, 1))
-    worst = d[:, layers].max(dim=0).values.mean(dim=0)
-    layer_us = float((tl[:, layers, -1] - tl[:, layers, 0]).mean() / mhz)
+    # stamps are nanoseconds of the GPU-wide timer: one time axis for all CTAs
+    layers = slice(1, None) if tl.shape[1] > 1 else slice(0, None)
+    tl = tl[:, layers] / 1000.0
+    d = tl[:, :, 1:] - tl[:, :, :-1]  # microseconds per step of a layer
+    mean = d.mean(dim=(0, 1))
+    worst = d.max(dim=0).values.mean(dim=0)
+    layer_us = float((tl[:, :, -1] - tl[:, :, 0]).mean())
     rows = [{"phase": name, "mean_us": round(float(m), 2), "max_over_ctas_us": round(float(w), 2)} for name, m, w in zip(PHASES, mean, worst)]
-    print(f"model {args.model}  batch {B}  context {n}  grid {plan.grid}  slabs {plan.slabs}  stages {plan.stages}  sm clock {mhz} MHz")
+    print(f"model {args.model}  batch {B}  context {n}  grid {plan.grid}  slabs {plan.slabs}  ring stages {plan.stages}  "
+          f"activation slots {plan.xslots}")
     print(f"step (layers + embedding + final norm), recording off: {plain_ms:.3f} ms; one layer on the timeline: {layer_us:.1f} us")
+    print("time spent in each step of a layer (per CTA):")
     for r in rows:
-        print(f"  {r['phase']:<40s} mean {r['mean_us']:8.2f} us   max over CTAs {r['max_over_ctas_us']:8.2f} us")
-    # inside the attention item (CTAs that had one): entry, rows built, CTA barrier, tokens folded, warps merged,
-    # partials published + arrival counted, end
-    names = ("build q/k/v rows (slab sums, norm, rotary, KV store)", "CTA barrier", "fold cached tokens", "merge warps",
-             "publish partials, fence, arrival counter", "last split: merge all splits (others: nothing)")
-    has = (sub[:, layers, 0] > 0) & (sub[:, layers, 6] > 0)
-    if bool(has.any()):
-        dd = (sub[:, layers, 1:] - sub[:, layers, :-1]) / mhz
-        print("  inside one attention item:")
-        for k, name in enumerate(names):
-            vals = dd[..., k][has]
-            print(f"    {name:<60s} mean {float(vals.mean()):7.2f} us   max {float(vals.max()):7.2f} us")
+        print(f"  {r['phase']:<58s} mean {r['mean_us']:8.2f} us   max over CTAs {r['max_over_ctas_us']:8.2f} us")
+    # when each step ENDS on the layer's own time axis (0 = the first CTA entering the layer): first, mean and last CTA
+    rel = tl - tl[:, :, 0].min(dim=0).values[None, :, None]
+    print("end of each step since the first CTA entered the layer (first / mean / last CTA):")
+    ends = []
+    for k, name in enumerate(("enter the layer",) + PHASES):
+        col = rel[:, :, k]
+        lo, mid, hi = float(col.min(dim=0).values.mean()), float(col.mean()), float(col.max(dim=0).values.mean())
+        ends.append({"step": name, "first_us": round(lo, 2), "mean_us": round(mid, 2), "last_us": round(hi, 2)})
+        print(f"  {name:<58s} {lo:8.2f} {mid:8.2f} {hi:8.2f}")
     if args.json:
         with open(args.json, "w") as fh:
-            json.dump({"model": args.model, "batch": B, "context": n, "step_ms": plain_ms, "layer_us": layer_us, "phases": rows}, fh, indent=1)
+            json.dump({"model": args.model, "batch": B, "context": n, "step_ms": plain_ms, "layer_us": layer_us, "phases": rows, "ends": ends}, fh, indent=1)
 
 
 if __name__ == "__main__":

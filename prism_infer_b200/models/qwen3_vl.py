@@ -554,7 +554,7 @@ class Qwen3VLModel:
 
     def _decode_plan(self, cache: ops.KVCache, tokens: int):
         """The persistent decode kernel's plan for this cache, or ``None`` where it does not apply
-        (more than 16 tokens, unsupported head shapes, tensor-parallel ranks without the fused
+        (more than 4 tokens, unsupported head shapes, tensor-parallel ranks without the fused
         communicator, switched off)."""
         from ..ops import decode_layers as dl
 
@@ -576,7 +576,8 @@ class Qwen3VLModel:
                                                head_dim=self.D, intermediate=self.I, eps=t.rms_norm_eps, inv_freq=inv_freq,
                                                axis=axis, **extra)
             plans[key] = plan
-        return plans[key]
+        plan = plans[key]
+        return plan if plan is not None and tokens <= plan.max_tokens else None
 
     def _forward_prefill_fused(self, x, positions, meta, cache, deepstack, vis_index):
         """Tensor-parallel prefill with the exchanges fused into the kernels around them: each

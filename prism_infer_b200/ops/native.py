@@ -70,6 +70,9 @@ _SIGNATURES = {
     "prism_decode_layer_desc": "ppipppiiipppppppp",
     "prism_decode_layers_plan": "iiiip",
     "prism_decode_layer_desc_bytes": "",
+    "prism_decode_layers_max_tokens": "",
+    "prism_decode_layers_timeline_stamps": "",
+    "prism_decode_layers_seq_step": "i",
 }
 _STATUS_UNITS = ("gemm", "gemm_pair", "gemv", "norm", "attn", "attn_tc", "kvops", "sampler", "comm", "decode_layers")
 

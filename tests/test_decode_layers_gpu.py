@@ -66,16 +66,20 @@ def _decode_inputs(model, bt, lens, page, seed, pad_to):
 @pytest.mark.parametrize("arch_name,mode,lens,pad_to", [
     ("tiny", ops.KV_FP8_SCALED, (37,), 1),
     ("tiny", ops.KV_BF16, (5, 300, 64), 4),
+    ("tiny", ops.KV_FP8_SCALED, (383, 129), 2),       # several staged chunks per split
     ("8b2", ops.KV_FP8_SCALED, (700,), 1),
-    ("8b2", ops.KV_FP8_SCALED, (255, 1, 513, 90, 256), 8),
+    ("8b2", ops.KV_FP8_SCALED, (1500,), 1),
+    ("8b2", ops.KV_FP8_SCALED, (255, 1, 513), 4),     # one padded row
+    ("8b2", ops.KV_FP8_SCALED, (1400, 90, 256, 1279), 4),
     ("8b2", ops.KV_BF16, (130, 40), 2),
-    ("8b2", ops.KV_FP8, (300,) * 11, 16),
+    ("8b2", ops.KV_BF16, (1000,), 1),
+    ("8b2", ops.KV_FP8, (300, 1100, 7), 4),
 ])
 def test_persistent_decode_matches_the_per_layer_chain(cuda_device, monkeypatch, arch_name, mode, lens, pad_to):
     arch = Qwen3VLArch.tiny() if arch_name == "tiny" else Qwen3VLArch.qwen3_vl_8b_2layer()
     t = arch.text
     page = 256 if arch_name != "tiny" else 64
-    max_blocks = 6
+    max_blocks = 8
     model = _model(arch)
     blocks = sum(-(-(n + 2) // page) for n in lens) + 1
     cache_a = ops.KVCache(t.num_layers, blocks, t.num_kv_heads, page, t.head_dim, mode, "cuda")
@@ -169,3 +173,36 @@ def test_persistent_decode_second_step_reads_the_first_steps_rows(cuda_device, m
     for a, b in zip(first, second):
         assert torch.equal(a, b)
     assert not torch.equal(first[0], first[1])
+
+
+def test_sequence_numbers_wrap_without_a_stale_word_being_taken(cuda_device, monkeypatch):
+    """The hand-off words carry 32-bit sequence numbers.  Steps taken while the base passes the end
+    of the number space give the same result as before: the base starts over, the wrap
+    generation grows and the plan's word buffers are zeroed first."""
+    arch = Qwen3VLArch.tiny()
+    t = arch.text
+    page, max_blocks, lens = 64, 4, (100, 7)
+    model = _model(arch)
+    cache = ops.KVCache(t.num_layers, 5, t.num_kv_heads, page, t.head_dim, ops.KV_FP8_SCALED, "cuda")
+    bt = _prefill(model, cache, lens, page, max_blocks, seed=5)
+    snapshot = (cache.payload.clone(), cache.scales.clone())
+    monkeypatch.setattr(dl, "ENABLED", True)
+    ids, pos, slots, ctx, table = _decode_inputs(model, bt, lens, page, seed=6, pad_to=2)
+    meta = AttnMeta(is_prefill=False, block_tables=table, slots=slots, context_lens=ctx)
+
+    def step():
+        cache.payload.copy_(snapshot[0])
+        cache.scales.copy_(snapshot[1])
+        h = model.forward(ids, pos, meta, cache).clone()
+        torch.cuda.synchronize()
+        native.check_status()
+        return h
+
+    want = step()
+    state = dl.device_state(torch.device("cuda", torch.cuda.current_device()))
+    seq_step = int(native.lib().prism_decode_layers_seq_step(t.num_layers))
+    generation = int(state[1])
+    state[0] = 0xFFFFFFFF - 4 * seq_step - 3
+    for _ in range(8):
+        assert torch.equal(step(), want)
+    assert int(state[1]) == generation + 1 and int(state[0]) < 16 * seq_step
