@@ -458,8 +458,7 @@ class Qwen3VLModel:
         if self.tp > 1 and plan is None:
             x = self.comm.reduce_dense(x)
         if plan is not None:
-            # decode steps of at most 16 tokens: every layer in one persistent launch (tensor-parallel
-            # ranks: the kernel also sums the vocabulary-sharded embedding rows over the ranks)
+            # opt-in: decode steps of at most 4 tokens on one GPU, every layer in one persistent launch
             pre = plan.run(x, positions, meta.slots, meta.block_tables, meta.context_lens)
             h, _ = ops.add_rmsnorm(self.final_norm, t.rms_norm_eps, x=pre, residual=None)
             return h
@@ -554,14 +553,11 @@ class Qwen3VLModel:
 
     def _decode_plan(self, cache: ops.KVCache, tokens: int):
         """The persistent decode kernel's plan for this cache, or ``None`` where it does not apply
-        (more than 4 tokens, unsupported head shapes, tensor-parallel ranks without the fused
-        communicator, switched off)."""
+        (switched off, which is the default; more than 4 tokens; unsupported head shapes; tensor
+        parallelism)."""
         from ..ops import decode_layers as dl
 
-        if not dl.ENABLED or tokens > dl.MAX_TOKENS:
-            return None
-        exchange = getattr(self.comm, "decode_exchange", None)  # the fused communicator's peer-mapped buffers
-        if self.tp > 1 and exchange is None:
+        if not dl.ENABLED or tokens > dl.MAX_TOKENS or self.tp > 1:
             return None
         plans = self.__dict__.setdefault("_decode_plans", {})
         key = cache.payload.data_ptr()
@@ -570,11 +566,8 @@ class Qwen3VLModel:
             plan = None
             if dl.supported(hidden=self.H, heads=self.Hq, kv_heads=self.Hkv, head_dim=self.D, intermediate=self.I):
                 inv_freq, axis = ops._rope_tables(self.D, t.rope_theta, t.mrope_section, self.device)
-                extra = exchange(self.H, dl.MAX_TOKENS) if self.tp > 1 else {}
-                if self.tp == 1 or extra:
-                    plan = dl.DecodeLayersPlan(self.layers, cache, hidden=self.H, heads=self.Hq, kv_heads=self.Hkv,
-                                               head_dim=self.D, intermediate=self.I, eps=t.rms_norm_eps, inv_freq=inv_freq,
-                                               axis=axis, **extra)
+                plan = dl.DecodeLayersPlan(self.layers, cache, hidden=self.H, heads=self.Hq, kv_heads=self.Hkv, head_dim=self.D,
+                                           intermediate=self.I, eps=t.rms_norm_eps, inv_freq=inv_freq, axis=axis)
             plans[key] = plan
         plan = plans[key]
         return plan if plan is not None and tokens <= plan.max_tokens else None

@@ -31,8 +31,9 @@
 //     that builds its q / k / v rows, stores the new token's K / V and attends over cached tokens
 //     that bulk copies stage in shared memory, the first chunks one layer ahead; split 0 merges
 //     the splits.
-//   * tensor parallel: the owner of a residual tile also all-reduces it, with the same kind of
-//     words in peer-mapped buffers over NVLink.
+//
+// One GPU only: tensor-parallel ranks run the per-layer chain, whose exchanges are fused into its
+// kernels.
 //
 // Every wait is bounded.  A wait that runs out sets a global abort word that all other waits
 // poll, records the status word and lets the kernel unwind (copies in flight are awaited, TMEM
@@ -110,7 +111,7 @@ struct DLParams {
   int pf_depth;              // units the L2 prefetch cursor may run ahead of the ring (0: off)
   float eps, attn_scale;
   GemmGeo geo[4];
-  const u64* state;          // device words {sequence base of this launch, wrap generation, launch count}: advanced before every launch
+  const u64* state;          // device words {sequence base of this launch, wrap generation}: advanced before every launch
   const bf16* x0;            // [T][H] embedding rows
   const int* positions;      // [3][T]
   const long long* slots;    // [T]
@@ -128,9 +129,6 @@ struct DLParams {
   u64* act;                  // [T][I]
   int* abort_flag;           // zero; set when a wait ran out
   long long* timeline;       // optional [grid][n_layers][TL_STAMPS] nanosecond stamps of the GPU-wide timer (null: off)
-  // tensor parallel: xch[slot][r] is rank r's exchange buffer of that slot, [tp][TMAX][H] words
-  int tp, my_rank;
-  u64* xch[2][8];
 };
 constexpr int TL_STAMPS = 16;
 
@@ -337,7 +335,6 @@ struct WorkerCtx {
   int kv_req, kv_done;         // staged chunks requested / consumed so far (slot = count & 1)
   bool ok;
   uint32_t base;               // sequence base of this launch
-  uint32_t launch;             // launches so far on this device (selects the tensor-parallel exchange buffer)
 };
 __device__ __forceinline__ uint32_t seq_of(const WorkerCtx& c, int layer, int handoff) {
   return c.base + (uint32_t)(layer * SEQ_PER_LAYER + handoff);
@@ -351,56 +348,12 @@ __device__ __forceinline__ void stamp(WorkerCtx& c) {
   }
 }
 
-// ---- tensor-parallel all-reduce of 4 columns of one token (inside an owner's reduce) ---------------------
-// The lane stores its local sums into EVERY rank's exchange buffer, then polls its own buffer
-// until all ranks' words carry this exchange's sequence number and adds them in rank order, so
-// every rank computes bit-identical rows.  Consecutive exchanges alternate between two buffers: a
-// lane can only reach the next use of a buffer after the peers' lanes of the same columns consumed
-// the previous one, because the exchange in between needed their words, sent after that read.
-__device__ __forceinline__ bool tp_exchange4(const DLParams& p, float (&d)[4], int t, int col, uint32_t seq, int slot) {
-  const size_t mine = ((size_t)p.my_rank * TMAX + t) * p.H + col;
-#pragma unroll 1
-  for (int r = 0; r < p.tp; ++r) {
-    u64* dst = p.xch[slot][r] + mine;
-    asm volatile("st.relaxed.sys.global.v2.u64 [%0], {%1, %2};" ::"l"(dst), "l"(pack(seq, d[0])), "l"(pack(seq, d[1])) : "memory");
-    asm volatile("st.relaxed.sys.global.v2.u64 [%0], {%1, %2};" ::"l"(dst + 2), "l"(pack(seq, d[2])), "l"(pack(seq, d[3])) : "memory");
-  }
-  const u64* own = p.xch[slot][p.my_rank] + (size_t)t * p.H + col;
-  const size_t rank_stride = (size_t)TMAX * p.H;
-  PollGuard guard;
-  for (;;) {
-    u64 w[8][4];
-#pragma unroll
-    for (int r = 0; r < 8; ++r) {
-      if (r < p.tp) {
-        const u64* q0 = own + (size_t)r * rank_stride;
-        asm volatile("ld.relaxed.sys.global.v2.u64 {%0, %1}, [%2];" : "=l"(w[r][0]), "=l"(w[r][1]) : "l"(q0) : "memory");
-        asm volatile("ld.relaxed.sys.global.v2.u64 {%0, %1}, [%2];" : "=l"(w[r][2]), "=l"(w[r][3]) : "l"(q0 + 2) : "memory");
-      }
-    }
-    uint32_t stale = 0;
-    d[0] = d[1] = d[2] = d[3] = 0.0f;
-#pragma unroll
-    for (int r = 0; r < 8; ++r) {
-      if (r < p.tp) {
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          stale |= seq_of_word(w[r][e]) ^ seq;
-          d[e] += val_of_word(w[r][e]);
-        }
-      }
-    }
-    if (stale == 0) return true;
-    if (!guard.keep_waiting(p, 700)) return false;
-  }
-}
-
 // ---- owner of a residual tile: delta -> residual, publish residual * weight and the sum of squares -----------
 // One warp per token; a lane owns 4 of the tile's 128 columns.  src: the projection whose slabs
 // hold the delta (null: the embedding rows x0).  weight null: last layer, the residual is the
-// output.  exchange: ordinal of this all-reduce inside the launch (tensor parallel).
+// output.
 __device__ __noinline__ void reduce_tile(const DLParams& p, WorkerCtx& c, const GemmGeo* src, uint32_t src_seq, const bf16* weight,
-                                         u64* xw_out, u64* ssq_out, uint32_t out_seq, int m, int exchange) {
+                                         u64* xw_out, u64* ssq_out, uint32_t out_seq, int m) {
   WorkerSmem& ws = *c.ws;
   const int H = p.H;
   const int col = m * BM + c.lane * 4;
@@ -416,9 +369,6 @@ __device__ __noinline__ void reduce_tile(const DLParams& p, WorkerCtx& c, const 
       const uint2 x_raw = __ldg(reinterpret_cast<const uint2*>(p.x0 + (size_t)t * H + col));
       const __nv_bfloat162* v = reinterpret_cast<const __nv_bfloat162*>(&x_raw);
       d[0] = b2f(v[0].x); d[1] = b2f(v[0].y); d[2] = b2f(v[1].x); d[3] = b2f(v[1].y);
-    }
-    if (p.tp > 1) {
-      if (!tp_exchange4(p, d, t, col, out_seq, (int)((c.launch + (uint32_t)exchange) & 1u))) c.ok = false;
     }
 #pragma unroll
     for (int e = 0; e < 4; ++e) d[e] = bf16_round(d[e]);
@@ -1411,7 +1361,6 @@ __global__ void __launch_bounds__(NTHREADS, 1) decode_layers_kernel(const __grid
     c.kv_done = 0;
     c.ok = true;
     c.base = (uint32_t)p.state[0];
-    c.launch = (uint32_t)p.state[2];
     const int wtid = c.wtid;
     const int r_tiles = p.H / BM, a_tiles = p.I / BM;
 
@@ -1450,13 +1399,14 @@ __global__ void __launch_bounds__(NTHREADS, 1) decode_layers_kernel(const __grid
     const bool has_item = cta < n_items;
     const AttnItem item = attn_item_of(p, ws, has_item ? cta : 0);
     if (has_item) {
-      if (wtid == 0 && (long long)ws.ctx[item.b] > (long long)p.max_blocks * p.page) prism_report(PRISM_ERR_BOUNDS, 1);
+      // detail: the context length that exceeds the block table's reach
+      if (wtid == 0 && (long long)ws.ctx[item.b] > (long long)p.max_blocks * p.page) prism_report(PRISM_ERR_BOUNDS, ws.ctx[item.b]);
       request_first_chunks<D>(p, c, 0, item);  // later layers' first chunks are requested from inside the previous layer's item
     }
 
     // the embedding rows start the residual and are the first QKV GEMM's input
     if (my_rtile >= 0)
-      reduce_tile(p, c, nullptr, 0u, p.layers[0].norm_in, p.xw_in, p.ssq_in, seq_of(c, 0, HO_XW_IN), my_rtile, 0);
+      reduce_tile(p, c, nullptr, 0u, p.layers[0].norm_in, p.xw_in, p.ssq_in, seq_of(c, 0, HO_XW_IN), my_rtile);
 
 #pragma unroll 1
     for (int l = 0; l < p.n_layers; ++l) {
@@ -1484,7 +1434,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) decode_layers_kernel(const __grid
       stamp(c);
       if (my_rtile >= 0)
         reduce_tile(p, c, &p.geo[1], seq_of(c, l, HO_OPROJ), p.layers[l].norm_post, p.xw_post, p.ssq_post, seq_of(c, l, HO_XW_POST),
-                    my_rtile, 1 + 2 * l);
+                    my_rtile);
       stamp(c);
       // gate / up: activation = residual * post-attention-norm weight; 1/rms for the SwiGLU owners
       fill_xbuf(p, c, 2, p.xw_post, p.H, seq_of(c, l, HO_XW_POST), p.ssq_post, ws.rstd_post);
@@ -1501,7 +1451,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) decode_layers_kernel(const __grid
       if (my_rtile >= 0) {
         const bool last = l + 1 == p.n_layers;
         reduce_tile(p, c, &p.geo[3], seq_of(c, l, HO_DOWN), last ? nullptr : p.layers[l + 1].norm_in, p.xw_in, p.ssq_in,
-                    seq_of(c, l + 1, HO_XW_IN), my_rtile, 2 + 2 * l);
+                    seq_of(c, l + 1, HO_XW_IN), my_rtile);
       }
       stamp(c);
     }
@@ -1519,23 +1469,17 @@ __global__ void __launch_bounds__(NTHREADS, 1) decode_layers_kernel(const __grid
 }
 
 // ---- sequence base ---------------------------------------------------------------------------------
-// Runs before every launch of the kernel above.  state = {base, generation, launches} is shared
-// by every plan of a device (their tensor-parallel exchange buffers are shared too): base += step,
-// launches += 1.  Sequence numbers are 32 bits wide; before they would wrap, the base starts over
-// and the generation grows.  A plan whose own generation word differs from the device's zeroes
-// its word buffers (one arena) first, so no word of an earlier pass over the number space
-// survives.  On a wrap a tensor-parallel rank also zeroes, in every rank's exchange buffers, the
-// rows that only it writes: its later stores are ordered after that, and a reader sees the old
-// word, zero or the new word, never a number of the new pass with an old value.
+// Runs before every launch of the kernel above.  state = {base, generation} may be shared by
+// several plans: base += step.  Sequence numbers are 32 bits wide; before they would wrap, the
+// base starts over and the generation grows.  A plan whose own generation word differs from the
+// state's zeroes its word buffers (one arena) first, so no word of an earlier pass over the number
+// space survives.
 struct AdvanceArgs {
   u64* state;
   u64* plan_generation;
   u64 step;
   uint4* arena;
   size_t arena_vec;
-  int tp, my_rank;
-  size_t rank_vec;       // 16-byte units of one rank's rows in an exchange buffer
-  u64* xch[2][8];
 };
 __global__ void advance_seq_kernel(const __grid_constant__ AdvanceArgs a) {
   __shared__ int wrap, stale;
@@ -1546,17 +1490,10 @@ __global__ void advance_seq_kernel(const __grid_constant__ AdvanceArgs a) {
   __syncthreads();
   if (stale)
     for (size_t i = threadIdx.x; i < a.arena_vec; i += blockDim.x) a.arena[i] = make_uint4(0, 0, 0, 0);
-  if (wrap && a.tp > 1)
-    for (int s = 0; s < 2; ++s)
-      for (int r = 0; r < a.tp; ++r) {
-        uint4* rows = reinterpret_cast<uint4*>(a.xch[s][r]) + (size_t)a.my_rank * a.rank_vec;
-        for (size_t i = threadIdx.x; i < a.rank_vec; i += blockDim.x) rows[i] = make_uint4(0, 0, 0, 0);
-      }
   __syncthreads();
   if (threadIdx.x == 0) {
     a.state[0] = wrap ? a.step : a.state[0] + a.step;
     a.state[1] += (u64)wrap;
-    a.state[2] += 1;
     *a.plan_generation = a.state[1];
   }
 }
@@ -1659,8 +1596,7 @@ enum DLArg {
   A_LAYERS, A_N_LAYERS, A_T, A_H, A_HQ, A_HKV, A_D, A_I, A_M_QKV, A_PAGE, A_MAX_BLOCKS, A_NUM_BLOCKS, A_KV_MODE,
   A_NSPLIT, A_EPS_BITS, A_SCALE_BITS, A_STATE, A_PLAN_GENERATION, A_ARENA, A_ARENA_BYTES, A_X0, A_POSITIONS, A_SLOTS, A_BLOCK_TABLES,
   A_CONTEXT_LENS, A_INV_FREQ, A_AXIS, A_OUT, A_XW_IN, A_XW_POST, A_SSQ_IN, A_SSQ_POST, A_ATTN_PART, A_ATTN, A_ACT, A_ABORT,
-  A_PART_QKV, A_PART_OPROJ, A_PART_GU, A_PART_DOWN, A_GRID, A_TIMELINE, A_PF_DEPTH, A_TP, A_RANK, A_XCH0,
-  A_XCH1 = A_XCH0 + 8, A_COUNT = A_XCH1 + 8
+  A_PART_QKV, A_PART_OPROJ, A_PART_GU, A_PART_DOWN, A_GRID, A_TIMELINE, A_PF_DEPTH, A_COUNT
 };
 
 PRISM_API int prism_decode_layers(const long long* args, int n_args, void* stream_ptr) {
@@ -1739,14 +1675,6 @@ PRISM_API int prism_decode_layers(const long long* args, int n_args, void* strea
   p.timeline = (long long*)ptr(A_TIMELINE);
   p.pf_depth = (int)args[A_PF_DEPTH];
   if (p.pf_depth < 0 || p.pf_depth > 256) return -11;
-  p.tp = (int)args[A_TP];
-  p.my_rank = (int)args[A_RANK];
-  if (p.tp < 1 || p.tp > 8 || p.my_rank < 0 || p.my_rank >= p.tp) return -12;
-  for (int r = 0; r < 8; ++r) {
-    p.xch[0][r] = (u64*)ptr(A_XCH0 + r);
-    p.xch[1][r] = (u64*)ptr(A_XCH1 + r);
-    if (p.tp > 1 && r < p.tp && (p.xch[0][r] == nullptr || p.xch[1][r] == nullptr)) return -13;
-  }
   if (p.state == nullptr || ptr(A_PLAN_GENERATION) == nullptr || (args[A_ARENA_BYTES] & 15) || (args[A_ARENA] & 15)) return -14;
 
   const size_t smem = (size_t)p.stages * STAGE_BYTES + WS_BYTES + xbuf_bytes(p.T, p.xslots) + TAIL_BYTES + 1024;
@@ -1770,10 +1698,6 @@ PRISM_API int prism_decode_layers(const long long* args, int n_args, void* strea
   adv.step = (u64)prism_decode_layers_seq_step(p.n_layers);
   adv.arena = (uint4*)ptr(A_ARENA);
   adv.arena_vec = (size_t)args[A_ARENA_BYTES] / 16;
-  adv.tp = p.tp;
-  adv.my_rank = p.my_rank;
-  adv.rank_vec = (size_t)TMAX * p.H * 8 / 16;
-  memcpy(adv.xch, p.xch, sizeof(adv.xch));
   advance_seq_kernel<<<1, 1024, 0, stream>>>(adv);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return (int)e;

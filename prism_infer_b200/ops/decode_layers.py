@@ -33,25 +33,13 @@ _ARG_NAMES = (
     "layers", "n_layers", "T", "H", "Hq", "Hkv", "D", "I", "m_qkv", "page", "max_blocks", "num_blocks", "kv_mode",
     "nsplit", "eps_bits", "scale_bits", "state", "plan_generation", "arena", "arena_bytes", "x0", "positions", "slots",
     "block_tables", "context_lens", "inv_freq", "axis", "out", "xw_in", "xw_post", "ssq_in", "ssq_post", "attn_part", "attn",
-    "act", "abort", "part_qkv", "part_oproj", "part_gu", "part_down", "grid", "timeline", "pf_depth", "tp", "rank",
-) + tuple(f"xch{s}_{r}" for s in (0, 1) for r in range(8))
+    "act", "abort", "part_qkv", "part_oproj", "part_gu", "part_down", "grid", "timeline", "pf_depth",
+)
 TIMELINE_STAMPS = 16  # worker thread 0's time stamps at the step boundaries of a layer (see benchmarks/profile_decode_layers.py)
 # weight tiles (16 KB each) the producer requests into L2 ahead of its shared-memory ring, so that HBM keeps
 # streaming while the ring waits for the activations of the next GEMM; 0 switches the requests off
 PREFETCH_UNITS = int(os.environ.get("PRISM_DECODE_PREFETCH_UNITS", "24"))
 MAX_SPLITS = 32
-
-# {sequence base, wrap generation, launch count} per device: shared by every plan of the device, because the
-# tensor-parallel exchange buffers are
-_STATE: dict[torch.device, torch.Tensor] = {}
-
-
-def device_state(device: torch.device) -> torch.Tensor:
-    device = torch.device(device)
-    if device not in _STATE:
-        _STATE[device] = torch.zeros(4, dtype=torch.int64, device=device)
-    return _STATE[device]
-
 
 def _f32_bits(x: float) -> int:
     return struct.unpack("<I", struct.pack("<f", float(x)))[0]
@@ -70,17 +58,10 @@ def supported(*, hidden: int, heads: int, kv_heads: int, head_dim: int, intermed
 
 class DecodeLayersPlan:
     def __init__(self, layers, cache, *, hidden: int, heads: int, kv_heads: int, head_dim: int, intermediate: int,
-                 eps: float, inv_freq: torch.Tensor, axis: torch.Tensor, tp: int = 1, rank: int = 0,
-                 exchange_ptrs: tuple[list[int], list[int]] | None = None) -> None:
+                 eps: float, inv_freq: torch.Tensor, axis: torch.Tensor) -> None:
         """``layers``: the model's ``LayerWeights`` (packed qkv / o / gate_up / down and norm weights);
-        ``cache``: the ``ops.KVCache`` the layers write and read.  Sizes are per rank.  Tensor-parallel
-        ranks pass, for each of the two exchange buffers, every rank's address of it
-        (``tp * 4 * hidden`` 8-byte words each, zero-filled, in peer-mapped memory used by nothing else);
-        the kernel then all-reduces the row-parallel projections and the embedding itself."""
-        self.tp, self.rank = int(tp), int(rank)
-        self.exchange_ptrs = exchange_ptrs
-        if self.tp > 1 and (exchange_ptrs is None or len(exchange_ptrs[0]) < tp or len(exchange_ptrs[1]) < tp):
-            raise ValueError("tensor-parallel decode needs both exchange buffers of every rank")
+        ``cache``: the ``ops.KVCache`` the layers write and read.  One GPU only (tensor-parallel ranks
+        run the per-layer chain)."""
         lib = native.lib()
         self.device = cache.payload.device
         self.cache = cache
@@ -106,7 +87,7 @@ class DecodeLayersPlan:
                 cache.v(i).data_ptr(), native.ptr(cache.k_scale(i)), native.ptr(cache.v_scale(i)))
         self._keep = [t for l in layers for t in (l.qkv, l.o, l.gate_up, l.down, l.input_norm, l.post_norm, l.q_norm, l.k_norm)]
         self.descs = host.to(self.device)
-        self.state = device_state(self.device)
+        self.state = torch.zeros(2, dtype=torch.int64, device=self.device)  # {sequence base, wrap generation}
         self.generation = torch.zeros(1, dtype=torch.int64, device=self.device)
         self.abort = torch.zeros(1, dtype=torch.int32, device=self.device)
         self.out = torch.zeros((MAX_TOKENS, hidden), dtype=torch.bfloat16, device=self.device)
@@ -147,13 +128,10 @@ class DecodeLayersPlan:
             arena_bytes=self.arena.numel() * 8, x0=x0.data_ptr(), positions=positions.data_ptr(), slots=slots.data_ptr(),
             block_tables=block_tables.data_ptr(), context_lens=context_lens.data_ptr(), inv_freq=self.inv_freq.data_ptr(),
             axis=self.axis.data_ptr(), out=self.out.data_ptr(), abort=self.abort.data_ptr(), grid=self.grid,
-            timeline=0 if self.timeline is None else self.timeline.data_ptr(), pf_depth=PREFETCH_UNITS, tp=self.tp, rank=self.rank,
+            timeline=0 if self.timeline is None else self.timeline.data_ptr(), pf_depth=PREFETCH_UNITS,
         )
         for name, off in self._offsets.items():
             vals[name] = base + 8 * off
-        for slot in (0, 1):
-            for r in range(8):
-                vals[f"xch{slot}_{r}"] = self.exchange_ptrs[slot][r] if (self.tp > 1 and r < self.tp) else 0
         args = (ctypes.c_longlong * len(_ARG_NAMES))(*[int(vals[n]) for n in _ARG_NAMES])
         native.call("prism_decode_layers", ctypes.cast(args, ctypes.c_void_p), len(_ARG_NAMES),
                     torch.cuda.current_stream().cuda_stream)

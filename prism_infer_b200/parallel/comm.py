@@ -98,16 +98,6 @@ class FusedComm(NcclComm):
         self._argmax_id = r.ptr_array(symm.OFF_ARGMAX_ID)
         self._argmax_flag = r.ptr_array(symm.OFF_ARGMAX_FLAGS)
 
-    def decode_exchange(self, hidden: int, max_tokens: int) -> dict:
-        """Peer-mapped buffers for the persistent decode kernel's in-kernel all-reduce: every rank's
-        address of the two exchange buffers the symmetric region reserves for it
-        (``tp * max_tokens * hidden`` 8-byte words each).  Empty when the shapes do not match."""
-        r = self.region
-        if hidden != self.hidden or max_tokens > symm.DECODE_T_MAX:
-            return {}
-        ptrs = tuple([r.peer_ptrs[k] + r.decode_exchange_offset(s) for k in range(self.size)] for s in (0, 1))
-        return dict(tp=self.size, rank=self.rank, exchange_ptrs=ptrs)
-
     def begin_step(self) -> None:
         """Advance the step epoch (a kernel, so it is captured into decode graphs)."""
         self.point = 0

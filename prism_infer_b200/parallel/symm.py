@@ -57,23 +57,9 @@ def _pre_bytes(size: int, hidden: int) -> tuple[int, int]:
     return size * rows * hidden * 2, PRE_T_MAX * hidden * 2
 
 
-DECODE_T_MAX = 4  # tokens of a step the persistent decode kernel all-reduces itself
-
-
-def _decode_exchange_bytes(size: int, hidden: int) -> int:
-    """One exchange buffer of the persistent decode kernel: every rank's 8-byte words of a step's tokens."""
-    return size * DECODE_T_MAX * hidden * 8
-
-
-def _decode_exchange_offset(size: int, hidden: int, slab_bytes: int) -> int:
-    rs, ag = _pre_bytes(size, hidden)
-    return (OFF_SLABS + 2 * slab_bytes + 2 * VIS_OUTPUTS * VIS_T_MAX * hidden * 2 + 2 * (rs + ag) + 255) // 256 * 256
-
-
 def _region_bytes(size: int, hidden: int, slab_bytes: int) -> int:
-    # the decode kernel's two exchange buffers are its own: its sequence numbers come from another
-    # counter than the step epoch, so it shares no words with the other exchanges
-    return _decode_exchange_offset(size, hidden, slab_bytes) + 2 * _decode_exchange_bytes(size, hidden)
+    rs, ag = _pre_bytes(size, hidden)
+    return OFF_SLABS + 2 * slab_bytes + 2 * VIS_OUTPUTS * VIS_T_MAX * hidden * 2 + 2 * (rs + ag)
 
 
 def _check(rc: int, what: str) -> None:
@@ -161,10 +147,6 @@ class SymmetricRegion:
         rs, ag = _pre_bytes(self.size, self.hidden)
         base = OFF_SLABS + 2 * self.slab_bytes + 2 * VIS_OUTPUTS * VIS_T_MAX * self.hidden * 2 + slot * (rs + ag)
         return base, base + rs
-
-    def decode_exchange_offset(self, slot: int) -> int:
-        """Byte offset of exchange buffer ``slot`` of the persistent decode kernel."""
-        return _decode_exchange_offset(self.size, self.hidden, self.slab_bytes) + slot * _decode_exchange_bytes(self.size, self.hidden)
 
     def pre_rows(self, slot: int, rows: int) -> torch.Tensor:
         """Local bf16 view ``[rows, hidden]`` of the all-gathered activations of a prefill slot."""

@@ -199,7 +199,7 @@ def test_sequence_numbers_wrap_without_a_stale_word_being_taken(cuda_device, mon
         return h
 
     want = step()
-    state = dl.device_state(torch.device("cuda", torch.cuda.current_device()))
+    state = model._decode_plan(cache, 2).state
     seq_step = int(native.lib().prism_decode_layers_seq_step(t.num_layers))
     generation = int(state[1])
     state[0] = 0xFFFFFFFF - 4 * seq_step - 3
