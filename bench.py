@@ -11,7 +11,8 @@ sampler, token copy-back), max over ranks.  A step streams ~15 GB of weights, fa
 the 126 MB L2, so no flush is needed between steps.
 ``e2e``: the same K steps through the public API (``LLM.step_result``): host scheduling,
 filling the pinned staging buffer, the host-to-device copy inside the graph, the
-device-to-host token read, per step.
+device-to-host token read, per step.  ``first_tokens`` / ``first_tokens_sha1``: the first eight
+generated token ids of the request, so that runs at different N can be compared by eye.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
 """
@@ -19,6 +20,7 @@ device-to-host token read, per step.
 from __future__ import annotations
 
 import argparse
+import hashlib
 import json
 import os
 import subprocess
@@ -162,10 +164,13 @@ def main() -> None:
     llm.barrier()  # every rank's device idle before the timed region
     native.reset_launch_count()
     t0 = time.perf_counter()
+    last = None
     for _ in range(K):
-        llm.step_result()
+        last = llm.step_result()
     torch.cuda.synchronize()
     e2e_ms = (time.perf_counter() - t0) * 1e3 / K
+    # the first generated tokens of the last request: the same at every N when tensor parallelism is exact enough
+    first_tokens = [int(t) for t in (last.outputs[-1].token_ids[:8] if last is not None and last.outputs else [])]
     # ---- device time: K back-to-back launches of the same decode graph ------------------
     device_ms = llm.time_decode_graph(K)  # maximum over ranks
     clocks = sampler.stop()
@@ -188,6 +193,8 @@ def main() -> None:
                 "d2h_bytes_per_step": 8 * max(1, args.batch), "output_tok_per_s": round(args.batch * 1e3 / e2e_ms, 2)},
         "gpu_launches": launches,
         "clocks": clocks,
+        "first_tokens": first_tokens,
+        "first_tokens_sha1": hashlib.sha1(",".join(map(str, first_tokens)).encode()).hexdigest()[:12],
     }
     print(json.dumps(out), flush=True)
     llm.exit()

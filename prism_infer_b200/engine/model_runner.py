@@ -463,14 +463,17 @@ class ModelRunner:
         """Capture one graph per bucket, largest first so smaller ones reuse its pool."""
         pool = None
         stream = torch.cuda.Stream(device=self.device)
+        # the capture stream does not order itself after the stream that initialised the weights, the KV arena
+        # and the exchange buffers: without this wait the warm-up launches below could overtake that work
+        stream.wait_stream(torch.cuda.current_stream(self.device))
         # one graph per bucket takes the temperature as an input; tensor-parallel ranks add a
         # greedy-only graph whose sampler is the one-kernel (value, id) exchange
         variants = [(b, False) for b in self.buckets] + ([(b, True) for b in self.buckets] if self.comm.size > 1 else [])
         for bucket, greedy_only in sorted(variants, reverse=True):
-            g = _DecodeGraph(self, bucket, greedy_only)
             from ..ops import native as _native
 
             with torch.cuda.stream(stream):
+                g = _DecodeGraph(self, bucket, greedy_only)  # its zero-filled buffers belong to the capture stream
                 for _ in range(2):  # warm-up outside capture (lazy kernel attributes, tensor maps)
                     g.dev.copy_(g.host, non_blocking=True)
                     self._decode_body(g)
@@ -486,6 +489,7 @@ class ModelRunner:
             g.launches = _native.launch_count() - before
             pool = graph.pool() if pool is None else pool
             (self.greedy_graphs if greedy_only else self.graphs)[bucket] = g
+        torch.cuda.current_stream(self.device).wait_stream(stream)
         torch.cuda.synchronize(self.device)
 
     def _run_decode_graph(self, inp: StepInputs) -> list[int]:

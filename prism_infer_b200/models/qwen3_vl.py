@@ -169,8 +169,11 @@ class Qwen3VLModel:
     def _alloc(self) -> None:
         a, t, v = self.arch, self.arch.text, self.arch.vision
         qkv_rows = (self.Hq + 2 * self.Hkv) * self.D
-        self.embed = self._e(self.V, self.H)
-        self.lm_head = self.embed if t.tie_word_embeddings else self._e(self.V, self.H)
+        # the embedding table is replicated on every rank (1.2 GB at 8B widths): a lookup needs no exchange, where
+        # the reference all-reduces vocabulary-sharded rows (prism_infer/layers/embed_head.py:49-74); the LM head
+        # stays sharded by vocabulary rows
+        self.embed = self._e(t.vocab_size, self.H)
+        self.lm_head = self.embed[self.vocab_start:self.vocab_start + self.V] if t.tie_word_embeddings else self._e(self.V, self.H)
         self.final_norm = self._e(self.H)
         self.layers = [
             LayerWeights(self._e(self.H), self._e(qkv_rows, self.H), self._e(self.D), self._e(self.D),
@@ -247,7 +250,7 @@ class Qwen3VLModel:
             }
             return table.get(sub)
         if name == f"{LM}.embed_tokens.weight":
-            return self.embed, (0, r * self.V, self.V)
+            return self.embed, None
         if name == "lm_head.weight":
             return (None if self.arch.text.tie_word_embeddings else (self.lm_head, (0, r * self.V, self.V)))
         if name == f"{LM}.norm.weight":
@@ -450,13 +453,8 @@ class Qwen3VLModel:
         small = T <= SMALL_T and not scoring  # the scorer reads K rows of the dense projection
         comm = self.comm
         comm.begin_step()
-        emb_visual = visual
-        if self.tp > 1 and visual is not None and self.rank != 0:
-            emb_visual = torch.zeros_like(visual)  # only rank 0 contributes visual rows to the sum
-        x = ops.embed(input_ids, self.embed, visual=emb_visual, vis_index=vis_index, vocab_start=self.vocab_start)
+        x = ops.embed(input_ids, self.embed, visual=visual, vis_index=vis_index)
         plan = self._decode_plan(cache, T) if (x.is_cuda and not meta.is_prefill and deepstack is None and visual is None) else None
-        if self.tp > 1 and plan is None:
-            x = self.comm.reduce_dense(x)
         if plan is not None:
             # opt-in: decode steps of at most 4 tokens on one GPU, every layer in one persistent launch
             pre = plan.run(x, positions, meta.slots, meta.block_tables, meta.context_lens)
@@ -630,12 +628,14 @@ class Qwen3VLModel:
             self.last_logits = (logits if self.tp == 1 else self.comm.gather_logits(logits)).float().clone()
         if self.tp == 1:
             return ops.sample(logits, temperature, seed=seed, step=step, out=out)
-        greedy = temperature is None
-        if greedy:
+        if temperature is None or logits.is_cuda:
+            # arg-max and the exponential race are both "largest perturbed logit wins", and the perturbation is keyed
+            # by the global token id: every rank finds the winner of its vocabulary shard and the ranks exchange
+            # (value, id) pairs; the full logits never travel
             val = torch.empty(logits.shape[0], dtype=torch.float32, device=logits.device)
-            ids = ops.sample(logits, None, vocab_offset=self.vocab_start, out_val=val)
+            ids = ops.sample(logits, temperature, seed=seed, step=step, vocab_offset=self.vocab_start, out_val=val)
             tok = self.comm.greedy_merge(val, ids)
-        else:
+        else:  # the CPU sampler draws its noise per logits row, not per token id
             tok = ops.sample(self.comm.gather_logits(logits), temperature, seed=seed, step=step)
         if out is not None:
             out.copy_(tok)

@@ -104,9 +104,11 @@ __global__ void signal_kernel(const SignalArgs a) {
 
 // Bounded wait until flags[0..n) >= seq (data other GPUs pushed is then visible to the
 // kernels that follow in the stream).
-__global__ void wait_flags_kernel(const unsigned long long* flags, int n, unsigned long long seq) {
+__global__ void wait_flags_kernel(const unsigned long long* flags, int n, unsigned long long seq,
+                                  const unsigned long long* epoch) {
   pdl_launch_dependents();
   pdl_wait();
+  if (epoch != nullptr) seq += *epoch;  // the step epoch is advanced by a kernel, so graph replays wait for fresh numbers
   if ((int)threadIdx.x < n) {
     const long long t0 = clock64();
     bool ok = false;
@@ -135,9 +137,10 @@ PRISM_API int prism_signal_peers(const void* const* peer_flag, int n_peers, int 
   return (int)prism_launch(signal_kernel, dim3(1), dim3(32), 0, reinterpret_cast<cudaStream_t>(stream), false, a);
 }
 
-PRISM_API int prism_wait_flags(const void* flags, int n, long long seq, void* stream) {
+PRISM_API int prism_wait_flags(const void* flags, int n, long long seq, const void* epoch, void* stream) {
+  if (n < 1 || n > 32) return -20;
   return (int)prism_launch(wait_flags_kernel, dim3(1), dim3(32), 0, reinterpret_cast<cudaStream_t>(stream), false,
-                           (const unsigned long long*)flags, n, (unsigned long long)seq);
+                           (const unsigned long long*)flags, n, (unsigned long long)seq, (const unsigned long long*)epoch);
 }
 
 PRISM_API int prism_ipc_alloc(long long bytes, void** out) {

@@ -542,6 +542,7 @@ struct PersistArgs {
   int rows_per_owner;
   int n_peers, my_rank;
   unsigned long long seq;
+  const unsigned long long* epoch;  // when set, the flag value is *epoch + seq (graph replays advance the epoch)
   int* cta_counter;
   __nv_bfloat16* peer_out[8];
   unsigned long long* peer_flag[8];
@@ -845,7 +846,7 @@ gemm_wx_persistent_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_
       *a.cta_counter = 0;
       __threadfence_system();
       for (int p = 0; p < a.n_peers; ++p)
-        asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(a.peer_flag[p] + a.my_rank), "l"(a.seq) : "memory");
+        asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(a.peer_flag[p] + a.my_rank), "l"((a.epoch ? *a.epoch : 0ull) + a.seq) : "memory");
     }
   }
 }
@@ -1168,6 +1169,7 @@ static int gemm_wx_impl(const void* W, const void* X, void* out, int M, int T, i
     pa.n_peers = 0;
     pa.my_rank = 0;
     pa.seq = 0;
+    pa.epoch = nullptr;
     pa.cta_counter = nullptr;
     for (int i = 0; i < 8; ++i) {
       pa.peer_out[i] = nullptr;
@@ -1382,7 +1384,8 @@ PRISM_API int prism_gemm_wx_actx(const void* W, void* out, int M, int T, int K, 
 // prism_reduce_norm_allgather.
 PRISM_API int prism_gemm_wx_scatter(const void* W, const void* X, int M, int T, int K, long long ldw, long long ldx,
                                     int rows_per_owner, const void* const* peer_out, const void* const* peer_flag,
-                                    int n_peers, int my_rank, long long seq, void* cta_counter, void* stream_ptr, int pdl) {
+                                    int n_peers, int my_rank, long long seq, const void* epoch, void* cta_counter,
+                                    void* stream_ptr, int pdl) {
   if (T <= 0) return 0;
   if (n_peers < 1 || n_peers > 8 || rows_per_owner < 1 || (long long)rows_per_owner * n_peers < T) return -20;
   if (M % 16) return -21;
@@ -1411,6 +1414,7 @@ PRISM_API int prism_gemm_wx_scatter(const void* W, const void* X, int M, int T, 
   pa.n_peers = n_peers;
   pa.my_rank = my_rank;
   pa.seq = (unsigned long long)seq;
+  pa.epoch = reinterpret_cast<const unsigned long long*>(epoch);
   pa.cta_counter = reinterpret_cast<int*>(cta_counter);
   for (int i = 0; i < 8; ++i) {
     pa.peer_out[i] = i < n_peers ? reinterpret_cast<__nv_bfloat16*>(const_cast<void*>(peer_out[i])) : nullptr;

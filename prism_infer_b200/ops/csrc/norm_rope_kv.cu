@@ -295,8 +295,61 @@ struct RnaArgs {
   bf16* peer_x[8];                      // [T][H] on every rank
   unsigned long long* peer_flag[8];     // [tp] on every rank
   unsigned long long ag_seq;
+  const unsigned long long* epoch;      // when set, both sequence numbers are offsets from *epoch
   int* cta_counter;
 };
+
+// Split-K partial rows of a row-parallel projection -> the ranks that own the rows.  One CTA per
+// token row: sum the P local fp32 slabs, round to bf16 and store the row into slab [my_rank] of
+// its owner (rows_per_owner consecutive rows per rank); the last CTA raises flag[my_rank] on
+// every rank.  Together with reduce_norm_allgather_kernel this is an all-reduce in which every
+// rank sends T rows of bf16 once (the one-shot exchange of 8-byte words sends tp x splits x T).
+struct ScatterRowsArgs {
+  const float* partials;   // [P][T][H]
+  long long slab_stride;
+  int P, T, H, rows_per_owner, tp, my_rank;
+  bf16* peer_rs[8];                   // [tp][rows_per_owner][H] on every rank
+  unsigned long long* peer_flag[8];   // [tp] on every rank
+  const unsigned long long* epoch;
+  unsigned long long seq;
+  int* cta_counter;
+};
+__global__ void __launch_bounds__(128) scatter_rows_kernel(const ScatterRowsArgs a) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int t = blockIdx.x;
+  const int owner = t / a.rows_per_owner, local = t - owner * a.rows_per_owner;
+  bf16* dst = a.peer_rs[owner] + ((size_t)a.my_rank * a.rows_per_owner + local) * a.H;
+  const float* src = a.partials + (size_t)t * a.H;
+  for (int c = threadIdx.x * 8; c < a.H; c += 128 * 8) {
+    float acc[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) acc[e] = 0.0f;
+    for (int p = 0; p < a.P; ++p) {
+      const float4 lo = __ldcg(reinterpret_cast<const float4*>(src + (size_t)p * a.slab_stride + c));
+      const float4 hi = __ldcg(reinterpret_cast<const float4*>(src + (size_t)p * a.slab_stride + c + 4));
+      acc[0] += lo.x; acc[1] += lo.y; acc[2] += lo.z; acc[3] += lo.w;
+      acc[4] += hi.x; acc[5] += hi.y; acc[6] += hi.z; acc[7] += hi.w;
+    }
+    uint4 o;
+    __nv_bfloat162* op = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+    for (int e = 0; e < 4; ++e) op[e] = __floats2bfloat162_rn(acc[2 * e], acc[2 * e + 1]);
+    *reinterpret_cast<uint4*>(dst + c) = o;
+  }
+  __threadfence_system();  // the row is visible on its owner before the flag can be
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const int old = atomicAdd(a.cta_counter, 1);
+    if (old == (int)gridDim.x - 1) {
+      *a.cta_counter = 0;
+      __threadfence_system();
+      const unsigned long long seq = (a.epoch ? *a.epoch : 0ull) + a.seq;
+      for (int p = 0; p < a.tp; ++p)
+        asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(a.peer_flag[p] + a.my_rank), "l"(seq) : "memory");
+    }
+  }
+}
 
 // One CTA of 128 threads per owned row (a rank owns only T / tp rows, so a warp per row would
 // leave most SMs idle); NV 16-byte vectors per thread.
@@ -308,8 +361,9 @@ __global__ void __launch_bounds__(128) reduce_norm_allgather_kernel(const RnaArg
   pdl_launch_dependents();
   pdl_wait();
   const int H = a.H, nvec = H >> 3;
+  const unsigned long long base = a.epoch ? *a.epoch : 0ull;
   if (i < a.rows) {
-    if ((int)threadIdx.x < a.tp) wait_flag_ge(a.rs_flags + threadIdx.x, a.rs_seq, threadIdx.x);
+    if ((int)threadIdx.x < a.tp) wait_flag_ge(a.rs_flags + threadIdx.x, base + a.rs_seq, threadIdx.x);
     __syncthreads();
     const int g_row = a.row0 + i;
     const int ex = a.extra != nullptr ? a.extra_index[g_row] : -1;
@@ -396,7 +450,7 @@ __global__ void __launch_bounds__(128) reduce_norm_allgather_kernel(const RnaArg
       *a.cta_counter = 0;
       __threadfence_system();
       for (int p = 0; p < a.tp; ++p)
-        asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(a.peer_flag[p] + a.my_rank), "l"(a.ag_seq) : "memory");
+        asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(a.peer_flag[p] + a.my_rank), "l"(base + a.ag_seq) : "memory");
     }
   }
 }
@@ -943,8 +997,8 @@ PRISM_API int prism_reduce_norm_allgather(const void* rs, const void* rs_flags, 
                                           int rows_per_owner, int rows, int row0, int H, const void* residual_in,
                                           long long ld_res, void* residual_out, const void* extra, const void* extra_index,
                                           const void* weight, float eps, const void* const* peer_x,
-                                          const void* const* peer_flag, long long ag_seq, void* cta_counter, void* stream,
-                                          int pdl) {
+                                          const void* const* peer_flag, long long ag_seq, const void* epoch,
+                                          void* cta_counter, void* stream, int pdl) {
   if (tp < 1 || tp > 8 || rows < 0 || rows > rows_per_owner) return -20;
   if (H % 8 || H > 8192) return -21;
   RnaArgs a;
@@ -969,11 +1023,37 @@ PRISM_API int prism_reduce_norm_allgather(const void* rs, const void* rs_flags, 
     a.peer_flag[p] = p < tp ? (unsigned long long*)const_cast<void*>(peer_flag[p]) : nullptr;
   }
   a.ag_seq = (unsigned long long)ag_seq;
+  a.epoch = (const unsigned long long*)epoch;
   a.cta_counter = (int*)cta_counter;
   dim3 grid(rows > 0 ? rows : 1), block(128);
   if (H <= 2048) return (int)prism_launch(reduce_norm_allgather_kernel<2>, grid, block, 0, STREAM(stream), pdl != 0, a);
   if (H <= 4096) return (int)prism_launch(reduce_norm_allgather_kernel<4>, grid, block, 0, STREAM(stream), pdl != 0, a);
   return (int)prism_launch(reduce_norm_allgather_kernel<8>, grid, block, 0, STREAM(stream), pdl != 0, a);
+}
+
+PRISM_API int prism_scatter_rows(const void* partials, long long slab_stride, int P, int T, int H, int rows_per_owner,
+                                 const void* const* peer_rs, const void* const* peer_flag, int tp, int my_rank, long long seq,
+                                 const void* epoch, void* cta_counter, void* stream, int pdl) {
+  if (T <= 0) return 0;
+  if (tp < 1 || tp > 8 || P < 1 || rows_per_owner < 1 || (long long)rows_per_owner * tp < T) return -20;
+  if (H % 8 || cta_counter == nullptr) return -21;
+  ScatterRowsArgs a;
+  a.partials = (const float*)partials;
+  a.slab_stride = slab_stride;
+  a.P = P;
+  a.T = T;
+  a.H = H;
+  a.rows_per_owner = rows_per_owner;
+  a.tp = tp;
+  a.my_rank = my_rank;
+  for (int p = 0; p < 8; ++p) {
+    a.peer_rs[p] = p < tp ? (bf16*)const_cast<void*>(peer_rs[p]) : nullptr;
+    a.peer_flag[p] = p < tp ? (unsigned long long*)const_cast<void*>(peer_flag[p]) : nullptr;
+  }
+  a.epoch = (const unsigned long long*)epoch;
+  a.seq = (unsigned long long)seq;
+  a.cta_counter = (int*)cta_counter;
+  return (int)prism_launch(scatter_rows_kernel, dim3(T), dim3(128), 0, STREAM(stream), pdl != 0, a);
 }
 
 PRISM_API int prism_layernorm(const void* x, const void* w, const void* b, void* out, int T, int H, float eps,

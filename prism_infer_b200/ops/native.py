@@ -45,8 +45,8 @@ _SIGNATURES = {
     "prism_merge_candidates": "pppiipi",
     "prism_gemm_wx_push": "ppiiillliilppiilppiipi",
     "prism_add_rmsnorm_wait": "plippppppiifpipipi",
-    "prism_gemm_wx_scatter": "ppiiillippiilppi",
-    "prism_reduce_norm_allgather": "ppliiiiiiplppppfpplppi",
+    "prism_gemm_wx_scatter": "ppiiillippiilpppi",
+    "prism_reduce_norm_allgather": "ppliiiiiiplppppfpplpppi",
     "prism_add_rmsnorm_packed": "plippppppiifpipi",
     "prism_gemm_wx_normx": "ppiiilliiiiilplippppfpilpipi",
     "prism_flash_attention_tc": "plpplplpiiiiiiifpi",
@@ -58,7 +58,8 @@ _SIGNATURES = {
     "prism_gemm_wx_actx": "ppiiillilplippiilpppi",
     "prism_gemm_wx_allgather": "ppiiillllpippiilpppi",
     "prism_signal_peers": "piilp",
-    "prism_wait_flags": "pilp",
+    "prism_scatter_rows": "pliiiippiilpppi",
+    "prism_wait_flags": "pilpp",
     "prism_ipc_alloc": "lp",
     "prism_ipc_free": "p",
     "prism_ipc_get_handle": "pp",

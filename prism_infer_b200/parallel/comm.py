@@ -109,8 +109,13 @@ class FusedComm(NcclComm):
         M = w.shape[0]
         # every rank sends tp * splits * T rows of 8-byte words, so the one-shot exchange only wins
         # while T * tp is small (measured: TP8 ties with NCCL at 32 tokens, TP2 wins up to 128)
-        if T > SMALL_T or T * self.size > 192 or M != self.hidden or self.point >= symm.ARGMAX_POINT:
+        if T > SMALL_T or M != self.hidden or self.point >= symm.ARGMAX_POINT or not x.is_cuda:
             return super().row_parallel(x, w, stages)
+        if T * self.size > 192:
+            # too many rows for the one-shot exchange: split-K partials stay local, one kernel sums them and sends
+            # each row as bf16 to the rank that owns it; add_rmsnorm finishes the all-reduce (reduce + norm + all-gather)
+            parts = ops.linear_partial(x, w, ops.choose_splits(M, K, T), stages=stages)
+            return None, None, self.scatter_partials(parts)
         point, slot = self.point, self.point % 2
         r = self.region
         if ops.gemv_applies(T, K) and x.stride(1) == 1:
@@ -151,6 +156,12 @@ class FusedComm(NcclComm):
     def add_rmsnorm(self, weight, eps, dense, partials, ticket, residual, extra=None, extra_index=None):
         if ticket is None:
             return super().add_rmsnorm(weight, eps, dense, partials, None, residual, extra, extra_index)
+        if ticket[0] == "scatter":
+            # the residual stays sharded by token row between exchanges: a full [T, H] tensor only comes from the
+            # first (local) norm of the step
+            return self.reduce_norm_allgather(ticket, weight, eps, residual,
+                                              residual_is_shard=residual is not None and residual.shape[0] != ticket[3],
+                                              extra=extra, extra_index=extra_index)
         slot, point, P, T = ticket
         H = self.hidden
         r = self.region
@@ -188,18 +199,41 @@ class FusedComm(NcclComm):
     def prefill_fused(self, tokens: int) -> bool:
         return SMALL_T < tokens <= symm.PRE_T_MAX and self.hidden % 16 == 0
 
+    def _exchange_point(self) -> tuple[int, int]:
+        """(slot, point) of the next scatter / all-gather exchange.  Flags carry ``epoch + point``: the epoch
+        is advanced by a kernel at the start of every step, so a replayed graph waits for fresh numbers."""
+        self.point += 1
+        point = self.point  # from 1: a flag that was never written (0) is below every number waited for
+        if point >= symm.ARGMAX_POINT:
+            raise RuntimeError("more exchanges in one step than the step epoch has points")
+        return point % 2, point
+
     def scatter_linear(self, x: torch.Tensor, w: torch.Tensor):
         """Row-parallel projection whose epilogue writes each token row, as bf16, into the rank that
         owns it (``ceil(T / tp)`` consecutive rows per rank).  Returns the ticket for
         ``reduce_norm_allgather``."""
         T, K = x.shape
         rpo = -(-T // self.size)
-        self.pre_seq = getattr(self, "pre_seq", 0) + 1
-        slot, seq, r = self.pre_seq % 2, self.pre_seq, self.region
+        slot, point = self._exchange_point()
+        r = self.region
         native.call("prism_gemm_wx_scatter", w.data_ptr(), x.data_ptr(), w.shape[0], T, K, w.stride(0), x.stride(0), rpo,
-                    r.ptr_array(r.pre_offsets(slot)[0]), r.ptr_array(symm.OFF_PRE_RS_FLAGS[slot]), self.size, self.rank, seq,
-                    r.local(symm.OFF_PRE_COUNTER[0]), torch.cuda.current_stream().cuda_stream, 1 if ops.pdl_enabled() else 0)
-        return slot, seq, T, rpo
+                    r.ptr_array(r.pre_offsets(slot)[0]), r.ptr_array(symm.OFF_PRE_RS_FLAGS[slot]), self.size, self.rank, point,
+                    r.local(symm.OFF_EPOCH), r.local(symm.OFF_PRE_COUNTER[0]), torch.cuda.current_stream().cuda_stream,
+                    1 if ops.pdl_enabled() else 0)
+        return "scatter", slot, point, T, rpo
+
+    def scatter_partials(self, partials: torch.Tensor):
+        """Split-K partial rows ``[P, T, H]`` fp32 of a row-parallel projection: sum the slabs and send each
+        row, as bf16, to the rank that owns it.  Returns the ticket for ``reduce_norm_allgather``."""
+        P, T, H = partials.shape
+        rpo = -(-T // self.size)
+        slot, point = self._exchange_point()
+        r = self.region
+        native.call("prism_scatter_rows", partials.data_ptr(), partials.stride(0), P, T, H, rpo,
+                    r.ptr_array(r.pre_offsets(slot)[0]), r.ptr_array(symm.OFF_PRE_RS_FLAGS[slot]), self.size, self.rank, point,
+                    r.local(symm.OFF_EPOCH), r.local(symm.OFF_PRE_COUNTER[0]), torch.cuda.current_stream().cuda_stream,
+                    1 if ops.pdl_enabled() else 0)
+        return "scatter", slot, point, T, rpo
 
     def reduce_norm_allgather(self, ticket, weight: torch.Tensor, eps: float, residual: torch.Tensor | None, *,
                               residual_is_shard: bool, extra: torch.Tensor | None = None,
@@ -207,7 +241,7 @@ class FusedComm(NcclComm):
         """Sum the tp partial rows this rank owns, add the residual (a full ``[T, H]`` tensor or this
         rank's shard), RMSNorm, and store the normalised rows into every rank's activation buffer.
         Returns ``(h [T, H] view of the gathered rows, residual shard [rows_per_owner, H])``."""
-        slot, seq, T, rpo = ticket
+        _, slot, point, T, rpo = ticket
         r, H = self.region, self.hidden
         row0 = self.rank * rpo
         rows = max(0, min(T, row0 + rpo) - row0)
@@ -216,20 +250,20 @@ class FusedComm(NcclComm):
         if residual is not None and rows > 0:
             res_ptr = residual.data_ptr() if residual_is_shard else residual[row0:].data_ptr()
         stream = torch.cuda.current_stream().cuda_stream
-        native.call("prism_reduce_norm_allgather", r.local(r.pre_offsets(slot)[0]), r.local(symm.OFF_PRE_RS_FLAGS[slot]), seq,
+        native.call("prism_reduce_norm_allgather", r.local(r.pre_offsets(slot)[0]), r.local(symm.OFF_PRE_RS_FLAGS[slot]), point,
                     self.size, self.rank, rpo, rows, row0, H, res_ptr, H, shard.data_ptr(),
                     None if extra is None else extra.data_ptr(), None if extra is None else extra_index.data_ptr(),
                     weight.data_ptr(), float(eps), r.ptr_array(r.pre_offsets(slot)[1]), r.ptr_array(symm.OFF_PRE_AG_FLAGS[slot]),
-                    seq, r.local(symm.OFF_PRE_COUNTER[1]), stream, 1 if ops.pdl_enabled() else 0)
+                    point, r.local(symm.OFF_EPOCH), r.local(symm.OFF_PRE_COUNTER[1]), stream, 1 if ops.pdl_enabled() else 0)
         if wait:
             self.wait_allgather(ticket)
         return r.pre_rows(slot, T), shard
 
     def wait_allgather(self, ticket) -> None:
         """Bounded wait until every rank's rows of this exchange are in the local activation buffer."""
-        slot, seq, _, _ = ticket
-        native.call("prism_wait_flags", self.region.local(symm.OFF_PRE_AG_FLAGS[slot]), self.size, seq,
-                    torch.cuda.current_stream().cuda_stream)
+        _, slot, point, _, _ = ticket
+        native.call("prism_wait_flags", self.region.local(symm.OFF_PRE_AG_FLAGS[slot]), self.size, point,
+                    self.region.local(symm.OFF_EPOCH), torch.cuda.current_stream().cuda_stream)
 
     # ---- sharded vision tower: merger GEMM -> all-gather ------------------------------------
     def vision_begin(self, total_tokens: int) -> bool:
@@ -264,7 +298,7 @@ class FusedComm(NcclComm):
             off = symm.OFF_VIS_FLAGS + (self._vis_set * symm.VIS_OUTPUTS + k) * 64
             if k not in self._vis_pushed:
                 native.call("prism_signal_peers", r.ptr_array(off), self.size, self.rank, self.vision_seq, stream)
-            native.call("prism_wait_flags", r.local(off), self.size, self.vision_seq, stream)
+            native.call("prism_wait_flags", r.local(off), self.size, self.vision_seq, None, stream)
             outs.append(r.vis_rows(self._vis_set, k, total_tokens).clone())
         return outs
 

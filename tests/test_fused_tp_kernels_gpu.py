@@ -207,3 +207,51 @@ def test_prefill_scatter_gemm_then_reduce_norm_allgather_emulated_ranks(cuda_dev
     finally:
         for reg in regions:
             native.lib().prism_ipc_free(ctypes.c_void_p(reg.local_ptr))
+
+
+@pytest.mark.parametrize("tp,T,P", [(8, 32, 4), (8, 100, 3), (2, 128, 2), (4, 49, 1)])
+def test_partial_rows_scatter_then_reduce_norm_allgather_emulated_ranks(cuda_device, tp, T, P):
+    """The mid-size exchange (rows x ranks above 192, at most 128 rows): every rank's split-K partial
+    rows are summed and sent as bf16 to the row's owner, which reduces over ranks, adds the residual,
+    normalises and all-gathers.  Ranks emulated one after another on one device."""
+    import ctypes
+
+    from prism_infer_b200.parallel import symm
+    from prism_infer_b200.parallel.comm import FusedComm
+
+    H = 4096
+    ops.set_pdl(False)
+    regions = symm.SymmetricRegion.create_emulated(tp, H)
+    comms = [FusedComm(r, tp, H, region=regions[r]) for r in range(tp)]
+    g = torch.Generator().manual_seed(tp * 100 + T)
+    weight = (1 + 0.1 * torch.randn(H, generator=g)).to(torch.bfloat16).cuda()
+    res_full = torch.randn(T, H, generator=g).to(torch.bfloat16).cuda()
+    try:
+        residual_ref = res_full.float().cpu()
+        shards = [None] * tp
+        for exchange in range(3):
+            parts = [(torch.randn(P, T, H, generator=g) * 0.3).cuda() for _ in range(tp)]
+            tickets = [c.scatter_partials(parts[r]) for r, c in enumerate(comms)]
+            outs = []
+            for r, c in enumerate(comms):
+                res = res_full if exchange == 0 else shards[r]
+                h, shard = c.reduce_norm_allgather(tickets[r], weight, 1e-6, res, residual_is_shard=exchange > 0, wait=False)
+                shards[r] = shard
+                outs.append(h)
+            for r, c in enumerate(comms):
+                c.wait_allgather(tickets[r])
+            torch.cuda.synchronize()
+            native.check_status()
+            delta = sum(p.sum(0).to(torch.bfloat16).float().cpu() for p in parts).to(torch.bfloat16).float()
+            new_res = (residual_ref + delta).to(torch.bfloat16).float()
+            normed = (new_res * torch.rsqrt(new_res.pow(2).mean(-1, keepdim=True) + 1e-6)).to(torch.bfloat16).float() * weight.float().cpu()
+            rpo = -(-T // tp)
+            for r in range(tp):
+                assert torch.equal(outs[r], outs[0]), "every rank holds the same gathered rows"
+                rows = max(0, min(T, (r + 1) * rpo) - r * rpo)
+                close(shards[r][:rows], new_res[r * rpo: r * rpo + rows], 6e-2, 2e-2, f"residual shard of rank {r}")
+            close(outs[0], normed, 8e-2, 3e-2, f"gathered normalised rows, exchange {exchange}")
+            residual_ref = torch.cat([shards[r][:max(0, min(T, (r + 1) * rpo) - r * rpo)].float().cpu() for r in range(tp)])
+    finally:
+        for reg in regions:
+            native.lib().prism_ipc_free(ctypes.c_void_p(reg.local_ptr))
