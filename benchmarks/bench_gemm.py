@@ -78,23 +78,17 @@ def main() -> None:
         best = None
         if kind == "dual":
             variants = {"dual": lambda: ops.gate_up_swiglu(x, w, bn=16 if T <= 16 else 0)}
-            if T >= 512:
-                variants["pair"] = lambda: ops.linear_pair(x, w, dual=True)
-            if T <= 4:
-                variants["gemv"] = lambda: ops.gate_up_swiglu(x, w)  # with PRISM_GEMV_MAX_TOKENS=4
             ref = lambda: torch.nn.functional.silu((x @ w.t())[:, :M]) * (x @ w.t())[:, M:]  # noqa: E731
         elif T <= 128:
             variants = {}
             for s in sorted({1, ops.choose_splits(M, K, T), 2, 4, 8}):
                 out = torch.empty((ops.effective_splits(K, s), T, M), dtype=torch.float32, device=dev)
                 variants[f"split{s}"] = (lambda s=s, out=out: ops.linear_partial(x, w, s, out, bn=16 if T <= 16 else 0))
-            if T <= 4:
-                variants["gemv"] = lambda: ops.linear_partial(x, w, 1)  # with PRISM_GEMV_MAX_TOKENS=4
             ref = lambda: x @ w.t()  # noqa: E731
         else:
             out = torch.empty((T, M), dtype=torch.bfloat16, device=dev)
             variants = {"bn256": lambda: ops.linear(x, w, out=out, bn=256), "bn128": lambda: ops.linear(x, w, out=out, bn=128),
-                        "persistent": lambda: ops.linear(x, w, out=out), "pair": lambda: ops.linear_pair(x, w, out=out)}
+                        "persistent": lambda: ops.linear(x, w, out=out)}
             ref = lambda: x @ w.t()  # noqa: E731
         t_ref = timeit(ref, args.iters, flush)
         all_ms = {}

@@ -10,7 +10,6 @@ by itself in about a minute.
     python benchmarks/profile_case.py decode_attention # scaled-FP8 paged decode, batch 32, ctx 2048
     python benchmarks/profile_case.py prefill_attention
     python benchmarks/profile_case.py add_rmsnorm
-    python benchmarks/profile_case.py gemm_normx       # projection with the fused add+RMSNorm prologue
     python benchmarks/profile_case.py decode_step 128  # ONE engine decode step at that batch inside cudaProfilerStart/Stop
                                                        # (launch list with --profile-from-start off; full-size model)
 """
@@ -124,14 +123,6 @@ def main() -> None:
         cu = torch.tensor([0, T], dtype=torch.int32, device=dev)
         for _ in range(reps):
             ops.varlen_attention(q, heads[:, Hq:Hq + Hkv], heads[:, Hq + Hkv:], cu, T, causal=True)
-    elif case == "gemm_normx":
-        ws = [rnd(6144, 4096, scale=0.02) for _ in range(4)]
-        parts = torch.randn(4, 1, 4096, device=dev)
-        res, nw = rnd(1, 4096), rnd(4096)
-        out_res = torch.empty_like(res)
-        for i in range(reps):
-            ops.linear_normx(ws[i % 4], nw, 1e-6, 1, residual_out=out_res, partials_ptr=parts.data_ptr(),
-                             slab_stride=parts.stride(0), P=4, residual=res, splits=3)
     elif case == "add_rmsnorm":
         parts = torch.randn(4, 8, 4096, device=dev)
         res, w = rnd(8, 4096), rnd(4096)

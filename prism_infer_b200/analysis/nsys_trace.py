@@ -25,8 +25,7 @@ REQUIRED_TABLES = ("StringIds", "NVTX_EVENTS", "CUPTI_ACTIVITY_KIND_RUNTIME", "C
 
 # first match wins; fragments are matched against the lower-cased kernel name
 KERNEL_CATEGORIES: tuple[tuple[str, tuple[str, ...]], ...] = (
-    ("gemm_tcgen05", ("gemm_wx", "gemm_pair")),
-    ("gemv", ("gemv",)),
+    ("gemm_tcgen05", ("gemm_wx",)),
     ("attention_prefill", ("flash_tc", "flash_fwd")),
     ("attention_decode", ("paged_decode", "decode_merge", "decode_attn")),
     ("norm_rope_kv", ("rmsnorm", "layernorm", "qk_norm", "vit_rope", "reduce_norm_allgather")),

@@ -8,8 +8,8 @@ COMPUTE_CAPABILITY_COMPONENT_COUNT = 2
 PERCENTAGE_POINTS_SCALE = 100.0
 # names of the fused decode regions recorded in benchmark metadata: here they are kernels, not
 # compiler subgraphs
-DECODE_FUSED_PROJECTION = "normx_qkv_projection_qk_norm_mrope_kv_store"
-DECODE_FUSED_MLP = "normx_dual_gate_up_swiglu"
+DECODE_FUSED_PROJECTION = "split_k_qkv_projection_qk_norm_mrope_kv_store"
+DECODE_FUSED_MLP = "dual_gate_up_swiglu"
 DECODE_KV_BOUNDARY = "scaled_fp8_store_and_paged_decode"
 
 

@@ -30,9 +30,8 @@ from .architecture import Qwen3VLArch
 from .position import vision_patch_coords, vision_pos_embed_plan, vision_segments
 from .weights import LM, VIS
 
-# at or below this many tokens the GEMMs are weight-streaming: split-K + fp32 partials.  PRISM_SMALL_T moves the
-# boundary for experiments (prompts of 129-511 tokens run one tile per CTA without split-K and leave most SMs idle)
-SMALL_T = int(__import__("os").environ.get("PRISM_SMALL_T", "128"))
+# at or below this many tokens the GEMMs are weight-streaming: split-K + fp32 partials
+SMALL_T = 128
 
 
 @dataclass
@@ -125,25 +124,18 @@ class TPComm:
         """Row-parallel projection -> ``(dense, partials, ticket)``; exactly one is set.
         ``stages`` caps the operand ring of a decode-sized launch (0 = as deep as fits)."""
         T = x.shape[0]
-        if T <= SMALL_T:
+        # short prefills (up to 511 tokens) split K too: o_proj and down_proj have 32 weight tiles at 8B widths,
+        # one CTA each would leave 116 SMs idle
+        if T <= SMALL_T or (x.is_cuda and T <= ops.SPLIT_K_MAX_TOKENS):
             splits = ops.choose_splits(w.shape[0], w.shape[1], T) if x.is_cuda else 1
-            return None, ops.linear_partial(x, w, splits, stages=stages), None
+            if splits > 1 or T <= SMALL_T:
+                return None, ops.linear_partial(x, w, splits, stages=stages), None
         return ops.linear(x, w), None, None
-
-    def row_parallel_swiglu(self, gate_up_partials: torch.Tensor, w: torch.Tensor):
-        """``row_parallel(swiglu(gate_up_partials), w)`` with the SwiGLU inside the GEMM."""
-        return None, ops.linear_actx(gate_up_partials, w, ops.choose_splits(w.shape[0], w.shape[1], gate_up_partials.shape[1])), None
 
     def add_rmsnorm(self, weight, eps, dense, partials, ticket, residual, extra=None, extra_index=None):
         """``(normed, new_residual)`` from whatever ``row_parallel`` returned."""
         return ops.add_rmsnorm(weight, eps, x=dense, partials=partials, residual=residual, extra=extra,
                                extra_index=extra_index)
-
-    def norm_source(self, dense, partials, ticket) -> dict:
-        """Keyword arguments that tell ``ops.linear_normx`` where the pending delta lives."""
-        if partials is not None:
-            return dict(partials_ptr=partials.data_ptr(), slab_stride=partials.stride(0), P=partials.shape[0])
-        return dict(x=dense)
 
 
 class Qwen3VLModel:
@@ -463,44 +455,11 @@ class Qwen3VLModel:
         residual: Optional[torch.Tensor] = None
         dense, partials, ticket = x, None, None
         n_deep = len(deepstack) if deepstack is not None else 0
-        # at most four tokens on CUDA: residual add + RMSNorm run inside the next projection
-        fuse_norm = (x.is_cuda and ops.NORMX_ENABLED and self.tp == 1 and T <= ops.NORMX_MAX_TOKENS and n_deep == 0
-                     and self.H % 64 == 0 and not scoring)
-        if fuse_norm:
-            res_bufs = [torch.empty((T, self.H), dtype=torch.bfloat16, device=x.device) for _ in range(2)]
-            flip = 0
         if (self.tp > 1 and x.is_cuda and meta.is_prefill and hasattr(comm, "prefill_fused") and comm.prefill_fused(T)
                 and ops.TP_PREFILL_FUSED and not scoring):
             return self._forward_prefill_fused(x, positions, meta, cache, deepstack, vis_index)
         for i, l in enumerate(self.layers):
             extra = deepstack[i - 1] if 0 < i <= n_deep else None
-            if fuse_norm:
-                qkv_p = ops.linear_normx(l.qkv, l.input_norm, t.rms_norm_eps, T, residual=residual, residual_out=res_bufs[flip],
-                                         splits=ops.choose_splits(l.qkv.shape[0], self.H, T),
-                                         **comm.norm_source(dense, partials, ticket))
-                residual, flip = res_bufs[flip], flip ^ 1
-                q = ops.qk_norm_rope_store(qkv=None, partials=qkv_p, positions=positions, q_weight=l.q_norm, k_weight=l.k_norm,
-                                           num_heads=self.Hq, num_kv_heads=self.Hkv, head_dim=self.D, theta=t.rope_theta,
-                                           section=t.mrope_section, eps=t.rms_norm_eps, slots=meta.slots, cache=cache, layer=i)
-                a = ops.paged_prefill_attention(q, cache, i, meta.cu_seqlens_q, meta.kv_lens, meta.block_tables, meta.max_q_len) \
-                    if meta.is_prefill else ops.paged_decode_attention(q, cache, i, meta.block_tables, meta.context_lens,
-                                                                       nsplit=meta.nsplit, workspace=meta.workspace)
-                dense, partials, ticket = comm.row_parallel(a.view(T, self.Hq * self.D), l.o, stages=ops.O_PROJ_STAGES if small else 0)
-                src = comm.norm_source(dense, partials, ticket)
-                if self.I // 128 < 96:
-                    gu = ops.linear_normx(l.gate_up, l.post_norm, t.rms_norm_eps, T, residual=residual, residual_out=res_bufs[flip],
-                                          splits=ops.choose_splits(2 * self.I, self.H, T), **src)
-                    residual, flip = res_bufs[flip], flip ^ 1
-                    if ops.ACTX_ENABLED:
-                        dense, partials, ticket = comm.row_parallel_swiglu(gu, l.down)
-                    else:
-                        dense, partials, ticket = comm.row_parallel(ops.swiglu(partials=gu), l.down)
-                    continue
-                act = ops.linear_normx(l.gate_up, l.post_norm, t.rms_norm_eps, T, residual=residual,
-                                       residual_out=res_bufs[flip], dual=True, **src)
-                residual, flip = res_bufs[flip], flip ^ 1
-                dense, partials, ticket = comm.row_parallel(act, l.down)
-                continue
             h, residual = comm.add_rmsnorm(l.input_norm, t.rms_norm_eps, dense, partials, ticket, residual,
                                            extra, vis_index if extra is not None else None)
             direct = False
@@ -537,9 +496,6 @@ class Qwen3VLModel:
                 # too few 128-row tiles for the dual-accumulator kernel to keep enough SMs
                 # streaming weights: split-K over the packed matrix, SwiGLU on the partial sums
                 gu = ops.linear_partial(h, l.gate_up, ops.choose_splits(2 * self.I, self.H, T))
-                if ops.ACTX_ENABLED and T <= ops.NORMX_MAX_TOKENS:
-                    dense, partials, ticket = comm.row_parallel_swiglu(gu, l.down)
-                    continue
                 act = ops.swiglu(partials=gu)
             else:
                 act = ops.gate_up_swiglu(h, l.gate_up)

@@ -51,11 +51,18 @@ def _pdl() -> int:
 
 
 # ------------------------------------------------------------------------------- GEMM
+SPLIT_K_MAX_TOKENS = 511  # from 512 tokens the persistent GEMM (several tiles per CTA) takes over
+
+
 def choose_splits(m: int, k: int, tokens: int) -> int:
-    """Split-K factor that fills the 148 SMs for a weight-streaming (small-token) GEMM."""
-    if tokens > 128:
+    """Split-K factor that fills the 148 SMs: for a weight-streaming GEMM (at most 128 tokens, one token
+    tile) and for the short prefills above it (up to 511 tokens, one or two token tiles), where a
+    row-parallel projection with 32 weight tiles would otherwise keep a fifth of the SMs busy."""
+    if tokens > SPLIT_K_MAX_TOKENS:
         return 1
     tiles = (m + 127) // 128
+    if tokens > 128:
+        tiles *= (tokens + 255) // 256  # upper bound of the kernel's own tile choice (128 or 256 tokens)
     kb = (k + 63) // 64
     # one CTA per SM is resident (the operand ring fills shared memory), so more CTAs than
     # SMs means a second, mostly empty wave: stay at or below the SM count
@@ -102,21 +109,6 @@ def linear(
     return out
 
 
-def linear_pair(x: torch.Tensor, w: torch.Tensor, *, bias: Optional[torch.Tensor] = None, act: Optional[str] = None,
-                residual: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None, dual: bool = False,
-                accumulators: int = 2, debug: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """``linear`` / ``gate_up_swiglu`` on the two-SM (``cta_group::2``) kernel; CUDA only."""
-    T, K = x.shape
-    M = w.shape[0] // 2 if dual else w.shape[0]
-    if out is None:
-        out = torch.empty((T, M), dtype=torch.bfloat16, device=x.device)
-    code = {None: 0, "gelu_tanh": 1, "gelu": 2}[act]
-    native.call("prism_gemm_pair", _p(w), _p(x), _p(out), M, T, K, w.stride(0), x.stride(0), out.stride(0), w.shape[0],
-                _p(bias), _p(residual), residual.stride(0) if residual is not None else 0, code, 1 if dual else 0,
-                M if dual else 0, accumulators, _p(debug), _s(), _pdl())
-    return out
-
-
 def linear_partial(
     x: torch.Tensor, w: torch.Tensor, splits: int, out: Optional[torch.Tensor] = None, *, bn: int = 0, stages: int = 0
 ) -> torch.Tensor:
@@ -130,13 +122,6 @@ def linear_partial(
         out.zero_()
         out[0].copy_(y)
         return out
-    if gemv_applies(T, K) and bn == 0:
-        # at most four tokens: whole-row weight streaming, finished sums (a single "slab")
-        if out is None:
-            out = torch.empty((1, T, M), dtype=torch.float32, device=x.device)
-        native.call("prism_gemv", _p(w), _p(x), _p(out), M, T, K, w.stride(0), x.stride(0), out.stride(1), 0, 0,
-                    None, 0, 0, 0, 0, None, _s(), _pdl())
-        return out[:1]
     eff = effective_splits(K, splits)
     if out is None:
         out = torch.empty((eff, T, M), dtype=torch.float32, device=x.device)
@@ -146,18 +131,6 @@ def linear_partial(
         None, None, 0, 0, 0, 0, eff, 1, out.stride(0), bn, stages, _s(), _pdl(),
     )
     return out[:eff]
-
-
-# decode steps of at most this many tokens (<= 4) use the whole-row weight-streaming kernel
-# (gemv.cu) instead of the tcgen05 GEMM; 0 disables it.  Off by default: on the headline step it
-# measured 5.18 ms against 3.85 ms (the 12-stage TMA ring prefetches ~29 MB of weights before the
-# dependency wait, the register buffers of the SIMT kernel cannot), 3.25 vs 2.98 ms on the TP2
-# shard and 1.76 vs 1.83 ms on the TP8 shard.
-GEMV_MAX_TOKENS = int(__import__("os").environ.get("PRISM_GEMV_MAX_TOKENS", "0"))
-
-
-def gemv_applies(tokens: int, k: int) -> bool:
-    return 0 < tokens <= min(GEMV_MAX_TOKENS, 4) and k % 8 == 0 and tokens * k * 2 <= 200 * 1024
 
 
 def effective_splits(k: int, splits: int) -> int:
@@ -180,10 +153,6 @@ def gate_up_swiglu(x: torch.Tensor, w_gate_up: torch.Tensor, out: Optional[torch
         return y
     if out is None:
         out = torch.empty((T, I), dtype=torch.bfloat16, device=x.device)
-    if gemv_applies(T, K) and bn == 0:
-        native.call("prism_gemv", _p(w_gate_up), _p(x), _p(out), I, T, K, w_gate_up.stride(0), x.stride(0), out.stride(0),
-                    1, I, None, 0, 0, 0, 0, None, _s(), _pdl())
-        return out
     native.call(
         "prism_gemm_wx", _p(w_gate_up), _p(x), _p(out), I, T, K, w_gate_up.stride(0), x.stride(0), out.stride(0),
         2 * I, None, None, 0, 0, 1, I, 1, 0, 0, bn, 0, _s(), _pdl(),
@@ -191,74 +160,25 @@ def gate_up_swiglu(x: torch.Tensor, w_gate_up: torch.Tensor, out: Optional[torch
     return out
 
 
-NORMX_MAX_TOKENS = 4
-# tuning switches (read once at import): fused add+RMSNorm prologue, smallest batch that uses
-# the tensor-core decode-attention kernel
 import os as _os
 
-# measured on the headline decode step (batch 1, context ~1650): fused-norm prologue 4.45 ms vs
-# separate add+RMSNorm kernels 4.04 ms; tensor-core decode attention at batch 1 a further -0.17 ms
-NORMX_ENABLED = _os.environ.get("PRISM_NORMX", "0") != "0"
-DECODE_MMA_MIN_BATCH = int(_os.environ.get("PRISM_DECODE_MMA_MIN_BATCH", "1"))
-
-
-def linear_normx(
-    w: torch.Tensor,
-    norm_weight: torch.Tensor,
-    eps: float,
-    tokens: int,
-    *,
-    residual_out: torch.Tensor,
-    partials_ptr: int | None = None,
-    slab_stride: int = 0,
-    P: int = 0,
-    x: Optional[torch.Tensor] = None,
-    residual: Optional[torch.Tensor] = None,
-    dual: bool = False,
-    splits: int = 1,
-    wait: Optional[tuple[int, int, int, int]] = None,
-) -> torch.Tensor:
-    """Projection with the preceding residual add + RMSNorm fused into its prologue (CUDA
-    only, at most ``NORMX_MAX_TOKENS`` tokens).
-
-    The activation operand is produced inside the GEMM from ``residual + sum of the P fp32
-    slabs at partials_ptr`` (or ``+ x`` when ``P == 0``); ``residual_out`` receives that
-    pre-norm sum.  ``wait = (flags_ptr, n, point, epoch_ptr)`` makes the kernel wait for a
-    tensor-parallel exchange first.  Returns fp32 split-K slabs ``[S, T, M]``, or with
-    ``dual`` the bf16 ``silu(gate) * up`` of a packed ``[2I, K]`` weight.
-    """
-    K = w.shape[1]
-    T = tokens
-    assert T <= NORMX_MAX_TOKENS and w.is_cuda
-    flags, n_wait, point, epoch = wait if wait is not None else (None, 0, 0, None)
-    if dual:
-        M = w.shape[0] // 2
-        out = torch.empty((T, M), dtype=torch.bfloat16, device=w.device)
-        native.call("prism_gemm_wx_normx", _p(w), _p(out), M, T, K, w.stride(0), out.stride(0), 2 * M, 1, M, 1, 0, 0,
-                    partials_ptr, slab_stride, P, _p(x), _p(residual), _p(residual_out), _p(norm_weight), float(eps),
-                    flags, n_wait, point, epoch, 0, _s(), _pdl())
-        return out
-    M = w.shape[0]
-    eff = effective_splits(K, splits)
-    out = torch.empty((eff, T, M), dtype=torch.float32, device=w.device)
-    native.call("prism_gemm_wx_normx", _p(w), _p(out), M, T, K, w.stride(0), out.stride(1), M, 0, 0, eff, 1, out.stride(0),
-                partials_ptr, slab_stride, P, _p(x), _p(residual), _p(residual_out), _p(norm_weight), float(eps),
-                flags, n_wait, point, epoch, 0, _s(), _pdl())
-    return out
-
-
-# measured at TP2 on the headline step: 3.84 ms with the SwiGLU prologue, 3.68 ms with the separate kernel
-ACTX_ENABLED = _os.environ.get("PRISM_ACTX", "0") != "0"
-# operand-ring depth of the decode-sized o_proj GEMM (0 = as deep as fits).  A shallower ring
-# leaves shared memory for the attention CTAs that precede it, so its weight prefetch can start
-# while attention still runs.
-O_PROJ_STAGES = int(_os.environ.get("PRISM_O_PROJ_STAGES", "0"))
-# tensor-parallel prefill: GEMM -> reduce-scatter / reduce + norm -> all-gather kernels (0: NCCL all-reduce arm)
+# Launch tuning, fixed where a measurement settled it (the numbers are in the profiles next to the repo's
+# benchmarks); tests set the attributes directly.
+# smallest decode batch that uses the tensor-core (mma) decode-attention kernel: on the headline decode step
+# (batch 1, context ~1650) it measured 0.17 ms faster than the SIMT kernel
+DECODE_MMA_MIN_BATCH = 1
+# operand-ring depth of the decode-sized o_proj GEMM (0 = as deep as fits)
+O_PROJ_STAGES = 0
+# tcgen05 attention for contiguous bf16 K / V (prefill without history, the vision tower)
+ATTN_TC_ENABLED = True
+# prefill GEMMs of at least this many tokens run the persistent form, tokens on the TMEM lanes
+PERSISTENT_ROWMAJOR = True
+PERSISTENT_MIN_TOKENS = 512
+# shared-memory cap of decode-sized GEMM launches (0 = none)
+SMALL_TILE_SMEM_CAP = 0
+# tensor-parallel prefill: GEMM -> reduce-scatter / reduce + norm -> all-gather kernels; PRISM_TP_PREFILL_FUSED=0
+# selects the NCCL all-reduce arm the benchmarks compare against
 TP_PREFILL_FUSED = _os.environ.get("PRISM_TP_PREFILL_FUSED", "1") != "0"
-ATTN_TC_ENABLED = _os.environ.get("PRISM_ATTN_TC", "1") != "0"
-PERSISTENT_ROWMAJOR = _os.environ.get("PRISM_PERSISTENT_ROWMAJOR", "1") != "0"
-PERSISTENT_MIN_TOKENS = int(_os.environ.get("PRISM_PERSISTENT_MIN_TOKENS", "512"))
-SMALL_TILE_SMEM_CAP = int(_os.environ.get("PRISM_SMALL_TILE_SMEM", "0"))
 
 
 def apply_tuning() -> None:
@@ -266,26 +186,6 @@ def apply_tuning() -> None:
     native.call("prism_gemm_set_small_tile_smem_cap", SMALL_TILE_SMEM_CAP)
     native.call("prism_gemm_set_persistent_min_tokens", PERSISTENT_MIN_TOKENS)
     native.call("prism_gemm_set_persistent_rowmajor", 1 if PERSISTENT_ROWMAJOR else 0)
-
-
-def linear_actx(gate_up_partials: torch.Tensor, w: torch.Tensor, splits: int) -> torch.Tensor:
-    """Down projection with SwiGLU fused into its prologue (at most ``NORMX_MAX_TOKENS`` tokens).
-
-    ``gate_up_partials [P, T, 2I]`` are the fp32 split-K slabs of the packed gate/up
-    projection; the activation ``silu(sum gate) * sum up`` (bf16 roundings as in ``swiglu``) is
-    formed inside the GEMM.  Returns fp32 split-K slabs ``[S, T, M]`` of ``act @ w.T``.
-    """
-    P, T, I2 = gate_up_partials.shape
-    M, K = w.shape
-    assert I2 == 2 * K
-    if not w.is_cuda:
-        return linear_partial(swiglu(partials=gate_up_partials).to(w.dtype), w, splits)
-    assert T <= NORMX_MAX_TOKENS and gate_up_partials.stride(1) == I2
-    eff = effective_splits(K, splits)
-    out = torch.empty((eff, T, M), dtype=torch.float32, device=w.device)
-    native.call("prism_gemm_wx_actx", _p(w), _p(out), M, T, K, w.stride(0), M, eff, out.stride(0),
-                _p(gate_up_partials), gate_up_partials.stride(0), P, None, None, 0, 0, 0, None, None, _s(), _pdl())
-    return out
 
 
 # ------------------------------------------------------------------------- norm family

@@ -63,31 +63,9 @@ struct GemmArgs {
   const unsigned long long* epoch;  // local device word: sequence base of the current step (null: 0)
   float* peer_out[8];        // slab buffers (or bf16 row buffers) of this slot on every rank (incl. own)
   unsigned long long* peer_flag[8];  // flag arrays [tp] of this slot on every rank
-  // NORMX mode (at most NORMX_T tokens): the B operand is not loaded but produced in the
-  // kernel as  rmsnorm(residual + sum of partial slabs) * weight, which fuses the consumer
-  // side of an exchange, the residual add and the RMSNorm into the next projection.
-  const float* nx_partials;          // [P][T][K] fp32 (null with P == 0: nx_x is used)
-  long long nx_slab_stride;
-  int nx_P;
-  const __nv_bfloat16* nx_x;         // [T][K] bf16 delta when P == 0
-  const __nv_bfloat16* nx_residual_in;   // may be null
-  __nv_bfloat16* nx_residual_out;    // written by CTA (0,0,0) only; must not alias residual_in
-  const __nv_bfloat16* nx_weight;    // [K]
-  float nx_eps;
-  int nx_K;
-  const unsigned long long* nx_wait_flags;  // tensor parallel: flags to wait for before reading the slabs
-  int nx_n_wait;
-  long long nx_wait_point;
-  int nx_mode;                       // 0: residual + RMSNorm;  1: SwiGLU of packed (gate | up) slabs [P][T][2K]
 };
 
-constexpr int NORMX_T = 4;
-
-__device__ __forceinline__ void named_bar_sync(int id, int threads) {
-  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
-}
-
-template <int BN, bool DUAL, bool NORMX = false>
+template <int BN, bool DUAL>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_wx_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX, const GemmArgs a) {
   constexpr int X_TILE_BYTES = BN * BK * 2;
@@ -104,11 +82,6 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
   uint64_t* empty = full + stages;
   uint64_t* tmem_full = empty + stages;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_full + 1);
-  // NORMX scratch: pre-norm rows (bf16), reciprocal rms per row, reduction slots
-  __nv_bfloat16* nx_added = reinterpret_cast<__nv_bfloat16*>(
-      (reinterpret_cast<uintptr_t>(tmem_slot + 4) + 15) & ~uintptr_t(15));
-  float* nx_rstd = reinterpret_cast<float*>(nx_added + ((NORMX && a.nx_mode == 0) ? a.T * a.nx_K : 0));
-  float* nx_red = nx_rstd + NORMX_T;
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -124,7 +97,7 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < stages; ++s) {
-      mbar_init(&full[s], NORMX ? 2 : 1);  // TMA transaction (+ the in-kernel activation tile)
+      mbar_init(&full[s], 1);  // the TMA transaction
       mbar_init(&empty[s], 1);
     }
     mbar_init(tmem_full, 1);
@@ -148,16 +121,14 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
       const int pre = min(stages, num_kb);
       for (int i = 0; i < pre; ++i) {
         uint8_t* st = smem + (size_t)i * STAGE_BYTES;
-        mbar_expect_tx(&full[i], NORMX ? W_STAGE_BYTES : STAGE_BYTES);
+        mbar_expect_tx(&full[i], STAGE_BYTES);
         tma_load_2d(st, &tmW, &full[i], (kb_begin + i) * BK, m0);
         if (DUAL) tma_load_2d(st + W_TILE_BYTES, &tmW, &full[i], (kb_begin + i) * BK, a.w2_row_off + m0);
       }
-      if (!NORMX) {
-        pdl_wait();  // activations come from the previous kernel
-        for (int i = 0; i < pre; ++i) {
-          uint8_t* st = smem + (size_t)i * STAGE_BYTES;
-          tma_load_2d(st + W_STAGE_BYTES, &tmX, &full[i], (kb_begin + i) * BK, n0);
-        }
+      pdl_wait();  // activations come from the previous kernel
+      for (int i = 0; i < pre; ++i) {
+        uint8_t* st = smem + (size_t)i * STAGE_BYTES;
+        tma_load_2d(st + W_STAGE_BYTES, &tmX, &full[i], (kb_begin + i) * BK, n0);
       }
       int issued = pre;
       bool ok = true;
@@ -167,10 +138,10 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
         ok = mbar_wait(&empty[s], (round - 1) & 1, 1);
         if (!ok) break;
         uint8_t* st = smem + (size_t)s * STAGE_BYTES;
-        mbar_expect_tx(&full[s], NORMX ? W_STAGE_BYTES : STAGE_BYTES);
+        mbar_expect_tx(&full[s], STAGE_BYTES);
         tma_load_2d(st, &tmW, &full[s], (kb_begin + kb) * BK, m0);
         if (DUAL) tma_load_2d(st + W_TILE_BYTES, &tmW, &full[s], (kb_begin + kb) * BK, a.w2_row_off + m0);
-        if (!NORMX) tma_load_2d(st + W_STAGE_BYTES, &tmX, &full[s], (kb_begin + kb) * BK, n0);
+        tma_load_2d(st + W_STAGE_BYTES, &tmX, &full[s], (kb_begin + kb) * BK, n0);
         issued = kb + 1;
       }
       if (!ok) {
@@ -210,175 +181,7 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
     // ------------------------------ epilogue warps 2..5 ------------------------------
     const int q = warp & 3;  // TMEM lane quarter this warp may read
     pdl_wait();
-    bool nx_ok = true;
-    if (NORMX) {
-      const int et = threadIdx.x - 64;  // 0..127 among the four epilogue warps
-      const int K = a.nx_K;
-      if (a.nx_n_wait > 0) {
-        if (et < a.nx_n_wait) {
-          const unsigned long long want = (a.epoch ? *a.epoch : 0ull) + (unsigned long long)a.nx_wait_point;
-          const long long t0 = clock64();
-          for (;;) {
-            unsigned long long v;
-            asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(a.nx_wait_flags + et) : "memory");
-            if (v >= want) break;
-            if (clock64() - t0 > PRISM_WAIT_CYCLES) {
-              prism_report(PRISM_ERR_PEER_TIMEOUT, 300 + et);
-              break;
-            }
-          }
-        }
-        named_bar_sync(1, 128);
-      }
-      const bool writer = (blockIdx.x | blockIdx.y | blockIdx.z) == 0 && a.nx_residual_out != nullptr;
-      // pass 1, per token: every thread owns up to NX_IT 4-element groups of the row.  All
-      // global loads of a token (slabs, residual, norm weight) are issued up front, so the
-      // whole row costs about one memory round trip; the normalised row ends in shared memory.
-      constexpr int NX_IT = 8;  // covers K <= 128 threads * 4 * 8 = 4096
-      if (a.nx_mode == 0) {
-      uint2 wreg[NX_IT];
-#pragma unroll
-      for (int u = 0; u < NX_IT; ++u) {
-        const int i = (et + u * 128) * 4;
-        wreg[u] = make_uint2(0, 0);
-        if (i < K) wreg[u] = __ldg(reinterpret_cast<const uint2*>(a.nx_weight + i));
-      }
-      for (int t = 0; t < a.T; ++t) {
-        const size_t base = (size_t)t * K;
-        float4 acc[NX_IT];
-        uint2 rres[NX_IT];
-#pragma unroll
-        for (int u = 0; u < NX_IT; ++u) {
-          const int i = (et + u * 128) * 4;
-          acc[u] = make_float4(0.f, 0.f, 0.f, 0.f);
-          rres[u] = make_uint2(0, 0);
-          if (i < K) {
-            if (a.nx_residual_in != nullptr) rres[u] = __ldcg(reinterpret_cast<const uint2*>(a.nx_residual_in + base + i));
-            if (a.nx_P == 0) {
-              const uint2 raw = __ldcg(reinterpret_cast<const uint2*>(a.nx_x + base + i));
-              const __nv_bfloat162* v = reinterpret_cast<const __nv_bfloat162*>(&raw);
-              acc[u] = make_float4(__bfloat162float(v[0].x), __bfloat162float(v[0].y), __bfloat162float(v[1].x),
-                                   __bfloat162float(v[1].y));
-            }
-          }
-        }
-        for (int p = 0; p < a.nx_P; ++p) {
-          const float* p0 = a.nx_partials + (size_t)p * a.nx_slab_stride + base;
-#pragma unroll
-          for (int u = 0; u < NX_IT; ++u) {
-            const int i = (et + u * 128) * 4;
-            if (i < K) {
-              const float4 v = __ldcg(reinterpret_cast<const float4*>(p0 + i));
-              acc[u].x += v.x;
-              acc[u].y += v.y;
-              acc[u].z += v.z;
-              acc[u].w += v.w;
-            }
-          }
-        }
-        float ss = 0.0f;
-#pragma unroll
-        for (int u = 0; u < NX_IT; ++u) {
-          const int i = (et + u * 128) * 4;
-          if (i < K) {
-            float d0 = acc[u].x, d1 = acc[u].y, d2 = acc[u].z, d3 = acc[u].w;
-            if (a.nx_P > 0) {
-              d0 = bf16_round(d0);
-              d1 = bf16_round(d1);
-              d2 = bf16_round(d2);
-              d3 = bf16_round(d3);
-            }
-            if (a.nx_residual_in != nullptr) {
-              const __nv_bfloat162* r = reinterpret_cast<const __nv_bfloat162*>(&rres[u]);
-              d0 = bf16_round(__bfloat162float(r[0].x) + d0);
-              d1 = bf16_round(__bfloat162float(r[0].y) + d1);
-              d2 = bf16_round(__bfloat162float(r[1].x) + d2);
-              d3 = bf16_round(__bfloat162float(r[1].y) + d3);
-            }
-            acc[u] = make_float4(d0, d1, d2, d3);
-            if (writer) {
-              uint2 o;
-              *reinterpret_cast<__nv_bfloat162*>(&o.x) = __floats2bfloat162_rn(d0, d1);
-              *reinterpret_cast<__nv_bfloat162*>(&o.y) = __floats2bfloat162_rn(d2, d3);
-              *reinterpret_cast<uint2*>(a.nx_residual_out + base + i) = o;
-            }
-            ss += d0 * d0 + d1 * d1 + d2 * d2 + d3 * d3;
-          }
-        }
-        ss = warp_sum(ss);
-        if (lane == 0) nx_red[q] = ss;
-        named_bar_sync(1, 128);
-        const float rstd = rsqrtf((nx_red[0] + nx_red[1] + nx_red[2] + nx_red[3]) / (float)K + a.nx_eps);
-        named_bar_sync(1, 128);  // nx_red is reused by the next token
-#pragma unroll
-        for (int u = 0; u < NX_IT; ++u) {
-          const int i = (et + u * 128) * 4;
-          if (i < K) {
-            const __nv_bfloat162* w2 = reinterpret_cast<const __nv_bfloat162*>(&wreg[u]);
-            uint2 o;
-            *reinterpret_cast<__nv_bfloat162*>(&o.x) = __floats2bfloat162_rn(
-                bf16_round(acc[u].x * rstd) * __bfloat162float(w2[0].x), bf16_round(acc[u].y * rstd) * __bfloat162float(w2[0].y));
-            *reinterpret_cast<__nv_bfloat162*>(&o.y) = __floats2bfloat162_rn(
-                bf16_round(acc[u].z * rstd) * __bfloat162float(w2[1].x), bf16_round(acc[u].w * rstd) * __bfloat162float(w2[1].y));
-            *reinterpret_cast<uint2*>(nx_added + base + i) = o;  // now holds the normalised row
-          }
-        }
-      }
-      named_bar_sync(1, 128);
-      }
-      // pass 2: each warp writes the activation tiles of its k-blocks (128-byte swizzle, rows
-      // beyond T are zero) straight into the operand ring and arrives on the stage barrier
-      const int ew = warp - 2;
-      const int chunk = lane & 7;
-      for (int kb = ew; kb < num_kb && nx_ok; kb += 4) {
-        const int s = kb % stages;
-        const uint32_t round = kb / stages;
-        if (round > 0) nx_ok = mbar_wait(&empty[s], (round - 1) & 1, 5);
-        if (!nx_ok) break;
-        uint8_t* xt = smem + (size_t)s * STAGE_BYTES + W_STAGE_BYTES;
-        const int col = (kb_begin + kb) * BK + chunk * 8;
-#pragma unroll
-        for (int j = 0; j < BN / 4; ++j) {
-          const int row = (lane >> 3) + 4 * j;
-          uint4 val = make_uint4(0, 0, 0, 0);
-          if (row < a.T && col < K) {
-            if (a.nx_mode == 0) {
-              val = *reinterpret_cast<const uint4*>(nx_added + (size_t)row * K + col);
-            } else {
-              // activation = bf16(bf16(silu(bf16(sum gate))) * bf16(sum up)) for 8 columns
-              float gsum[8], usum[8];
-#pragma unroll
-              for (int e = 0; e < 8; ++e) gsum[e] = usum[e] = 0.0f;
-              const float* p0 = a.nx_partials + (size_t)row * 2 * K + col;
-              for (int p = 0; p < a.nx_P; ++p) {
-                const float* pp = p0 + (size_t)p * a.nx_slab_stride;
-                const float4 g0 = __ldcg(reinterpret_cast<const float4*>(pp));
-                const float4 g1 = __ldcg(reinterpret_cast<const float4*>(pp + 4));
-                const float4 u0 = __ldcg(reinterpret_cast<const float4*>(pp + K));
-                const float4 u1 = __ldcg(reinterpret_cast<const float4*>(pp + K + 4));
-                gsum[0] += g0.x; gsum[1] += g0.y; gsum[2] += g0.z; gsum[3] += g0.w;
-                gsum[4] += g1.x; gsum[5] += g1.y; gsum[6] += g1.z; gsum[7] += g1.w;
-                usum[0] += u0.x; usum[1] += u0.y; usum[2] += u0.z; usum[3] += u0.w;
-                usum[4] += u1.x; usum[5] += u1.y; usum[6] += u1.z; usum[7] += u1.w;
-              }
-              uint32_t* o = reinterpret_cast<uint32_t*>(&val);
-#pragma unroll
-              for (int e = 0; e < 4; ++e) {
-                const float lo = bf16_round(silu(bf16_round(gsum[2 * e]))) * bf16_round(usum[2 * e]);
-                const float hi = bf16_round(silu(bf16_round(gsum[2 * e + 1]))) * bf16_round(usum[2 * e + 1]);
-                __nv_bfloat162 pk = __floats2bfloat162_rn(lo, hi);
-                o[e] = *reinterpret_cast<uint32_t*>(&pk);
-              }
-            }
-          }
-          *reinterpret_cast<uint4*>(xt + (row >> 3) * 1024 + (row & 7) * 128 + ((chunk ^ (row & 7)) << 4)) = val;
-        }
-        fence_proxy_async();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&full[s]);
-      }
-    }
-    if (nx_ok && mbar_wait(tmem_full, 0, 3)) {
+    if (mbar_wait(tmem_full, 0, 3)) {
       tc_fence_after();
       const int m = m0 + q * 32 + lane;
       const bool m_ok = m < a.M;
@@ -924,17 +727,16 @@ int get_tensor_map(const void* ptr, unsigned long long rows, unsigned long long 
 
 int g_small_tile_smem_cap = 0;
 
-template <int BN, bool DUAL, bool NORMX = false>
+template <int BN, bool DUAL>
 int launch_gemm(const CUtensorMap& tw, const CUtensorMap& tx, GemmArgs& a, int m_tiles, int splits, int stages_override,
                 cudaStream_t stream, bool pdl) {
   constexpr int STAGE_BYTES = W_TILE_BYTES * (DUAL ? 2 : 1) + BN * BK * 2;
-  const int nx_bytes = NORMX ? (a.nx_mode == 0 ? a.T * a.nx_K * 2 : 0) + 64 : 0;
-  int max_stages = (SMEM_LIMIT - 1024 - 512 - nx_bytes) / STAGE_BYTES;
+  int max_stages = (SMEM_LIMIT - 1024 - 512) / STAGE_BYTES;
   if (max_stages > 16) max_stages = 16;
   if (BN <= 32 && g_small_tile_smem_cap > 0) {
     // decode-sized launches: leave room for the next kernel's CTA on the same SM, so that its
     // weight prefetch (issued before griddepcontrol.wait) overlaps this kernel's tail
-    int capped = (g_small_tile_smem_cap - 1024 - 512 - nx_bytes) / STAGE_BYTES;
+    int capped = (g_small_tile_smem_cap - 1024 - 512) / STAGE_BYTES;
     if (capped < 2) capped = 2;
     if (capped < max_stages) max_stages = capped;
   }
@@ -942,16 +744,16 @@ int launch_gemm(const CUtensorMap& tw, const CUtensorMap& tx, GemmArgs& a, int m
   if (stages > a.kb_per_split) stages = a.kb_per_split;
   if (stages < 1) stages = 1;
   a.stages = stages;
-  const size_t smem = (size_t)stages * STAGE_BYTES + 1024 + (2 * stages + 1) * 8 + 48 + nx_bytes;
+  const size_t smem = (size_t)stages * STAGE_BYTES + 1024 + (2 * stages + 1) * 8 + 48;
   static int configured_smem = 0;
   if ((int)smem > configured_smem) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_wx_kernel<BN, DUAL, NORMX>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_LIMIT);
+    cudaError_t e = cudaFuncSetAttribute(gemm_wx_kernel<BN, DUAL>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_LIMIT);
     if (e != cudaSuccess) return (int)e;
     configured_smem = SMEM_LIMIT;
   }
   const int n_tiles = (a.T + BN - 1) / BN;
   dim3 grid = a.tokens_fastest ? dim3(n_tiles, m_tiles, splits) : dim3(m_tiles, n_tiles, splits);
-  cudaError_t e = prism_launch(gemm_wx_kernel<BN, DUAL, NORMX>, grid, dim3(GEMM_THREADS), smem, stream, pdl, tw, tx, a);
+  cudaError_t e = prism_launch(gemm_wx_kernel<BN, DUAL>, grid, dim3(GEMM_THREADS), smem, stream, pdl, tw, tx, a);
   return (int)e;
 }
 
@@ -1014,22 +816,6 @@ int prism_make_head_tensor_map(const void* ptr, unsigned long long tokens, unsig
 // out: bf16 [T, ldo] (features along the row) or fp32 [splits][T][ldo] when out_f32.
 // dual: second weight tile starts at row w2_row_off; output = silu(W1 x) * (W2 x), M rows.
 // Returns 0 on success, a cudaError_t (>0) or a negative validation code.
-struct NormSpec {
-  const float* partials;
-  long long slab_stride;
-  int P;
-  const __nv_bfloat16* x;
-  const __nv_bfloat16* residual_in;
-  __nv_bfloat16* residual_out;
-  const __nv_bfloat16* weight;
-  float eps;
-  const unsigned long long* wait_flags;
-  int n_wait;
-  long long wait_point;
-  const unsigned long long* epoch;
-  int mode;
-};
-
 struct PushSpec {
   int n_peers, my_rank, push_rows;
   long long point, row_base;
@@ -1042,8 +828,7 @@ struct PushSpec {
 static int gemm_wx_impl(const void* W, const void* X, void* out, int M, int T, int K, long long ldw, long long ldx,
                         long long ldo, int w_rows_total, const void* bias, const void* residual, long long ldr, int act,
                         int dual, int w2_row_off, int splits, int out_f32, long long split_stride, int bn_override,
-                        int stages_override, void* stream_ptr, int pdl, const PushSpec* push,
-                        const NormSpec* norm = nullptr) {
+                        int stages_override, void* stream_ptr, int pdl, const PushSpec* push) {
   if (M <= 0 || T <= 0 || K <= 0) return -1;
   if (K % 8) return -2;  // 16-byte row pitch for TMA
   if (dual && (splits > 1 || out_f32)) return -3;
@@ -1104,51 +889,13 @@ static int gemm_wx_impl(const void* W, const void* X, void* out, int M, int T, i
       a.peer_flag[p] = push->peer_flag[p];
     }
   }
-  a.nx_partials = nullptr;
-  a.nx_slab_stride = 0;
-  a.nx_P = 0;
-  a.nx_x = nullptr;
-  a.nx_residual_in = nullptr;
-  a.nx_residual_out = nullptr;
-  a.nx_weight = nullptr;
-  a.nx_eps = 0.0f;
-  a.nx_K = K;
-  a.nx_wait_flags = nullptr;
-  a.nx_n_wait = 0;
-  a.nx_wait_point = 0;
-  a.nx_mode = 0;
-  if (norm != nullptr) {
-    a.nx_mode = norm->mode;
-    if (T > NORMX_T || (K % 64) != 0 || (norm->mode == 0 && K > 4096)) return -30;
-    a.nx_partials = norm->partials;
-    a.nx_slab_stride = norm->slab_stride;
-    a.nx_P = norm->P;
-    a.nx_x = norm->x;
-    a.nx_residual_in = norm->residual_in;
-    a.nx_residual_out = norm->residual_out;
-    a.nx_weight = norm->weight;
-    a.nx_eps = norm->eps;
-    a.nx_wait_flags = norm->wait_flags;
-    a.nx_n_wait = norm->n_wait;
-    a.nx_wait_point = norm->wait_point;
-    if (norm->epoch != nullptr) a.epoch = norm->epoch;
-    bn = 16;
-  }
   CUtensorMap tw, tx;
   int rc = get_tensor_map(W, (unsigned long long)w_rows_total, (unsigned long long)K, (unsigned long long)ldw, BM, &tw);
   if (rc) return rc;
-  if (norm != nullptr) {
-    tx = tw;  // unused by the kernel in this mode
-  } else {
-    rc = get_tensor_map(X, (unsigned long long)T, (unsigned long long)K, (unsigned long long)ldx, (unsigned)bn, &tx);
-    if (rc) return rc;
-  }
+  rc = get_tensor_map(X, (unsigned long long)T, (unsigned long long)K, (unsigned long long)ldx, (unsigned)bn, &tx);
+  if (rc) return rc;
   const int m_tiles = (M + BM - 1) / BM;
   const bool p = pdl != 0;
-  if (norm != nullptr) {
-    return dual ? launch_gemm<16, true, true>(tw, tx, a, m_tiles, splits, stages_override, stream, p)
-                : launch_gemm<16, false, true>(tw, tx, a, m_tiles, splits, stages_override, stream, p);
-  }
   if (g_persistent_min_tokens > 0 && T >= g_persistent_min_tokens && splits == 1 && !out_f32 && push == nullptr &&
       bn_override <= 0 && stages_override <= 0) {
     PersistArgs pa;
@@ -1298,82 +1045,6 @@ PRISM_API int prism_gemm_wx_allgather(const void* W, const void* X, int M, int T
   }
   return gemm_wx_impl(W, X, const_cast<void*>(peer_out[my_rank]), M, T, K, ldw, ldx, ldo, M, bias, nullptr, 0, act, 0, 0,
                       1, 0, 0, 0, 0, stream_ptr, pdl, &ps);
-}
-
-// Projection with the preceding residual add + RMSNorm (and, under tensor parallelism, the
-// wait for the exchange that produced the slabs) fused into its prologue; at most 4 tokens.
-//   x = rmsnorm(residual_in + sum_p partials[p]  (or + x_in when P == 0)) * norm_weight
-//   residual_out = the pre-norm sum (written once; must not alias residual_in)
-// Output: fp32 split-K slabs (out_f32 = 1) or, with dual, bf16 silu(W1 x) * (W2 x).
-PRISM_API int prism_gemm_wx_normx(const void* W, void* out, int M, int T, int K, long long ldw, long long ldo,
-                                  int w_rows_total, int dual, int w2_row_off, int splits, int out_f32,
-                                  long long split_stride, const void* partials, long long slab_stride, int P,
-                                  const void* x_in, const void* residual_in, void* residual_out,
-                                  const void* norm_weight, float eps, const void* wait_flags, int n_wait,
-                                  long long wait_point, const void* epoch, int stages_override, void* stream_ptr,
-                                  int pdl) {
-  NormSpec ns;
-  ns.partials = reinterpret_cast<const float*>(partials);
-  ns.slab_stride = slab_stride;
-  ns.P = P;
-  ns.x = reinterpret_cast<const __nv_bfloat16*>(x_in);
-  ns.residual_in = reinterpret_cast<const __nv_bfloat16*>(residual_in);
-  ns.residual_out = reinterpret_cast<__nv_bfloat16*>(residual_out);
-  ns.weight = reinterpret_cast<const __nv_bfloat16*>(norm_weight);
-  ns.eps = eps;
-  ns.wait_flags = reinterpret_cast<const unsigned long long*>(wait_flags);
-  ns.n_wait = n_wait;
-  ns.wait_point = wait_point;
-  ns.epoch = reinterpret_cast<const unsigned long long*>(epoch);
-  ns.mode = 0;
-  if (residual_out != nullptr && residual_out == residual_in) return -31;
-  return gemm_wx_impl(W, W, out, M, T, K, ldw, ldw, ldo, w_rows_total, nullptr, nullptr, 0, 0, dual, w2_row_off, splits,
-                      out_f32, split_stride, 16, stages_override, stream_ptr, pdl, nullptr, &ns);
-}
-
-// Down projection with the SwiGLU of the packed gate/up split-K slabs fused into its
-// prologue (at most 4 tokens):  x = silu(sum_p slabs[p][:, :K]) * sum_p slabs[p][:, K:].
-// Output: fp32 split-K slabs at `out`, or, when n_peers > 0, the tensor-parallel push form
-// of prism_gemm_wx_push (out is ignored).
-PRISM_API int prism_gemm_wx_actx(const void* W, void* out, int M, int T, int K, long long ldw, long long ldo,
-                                 int splits, long long split_stride, const void* gate_up_partials,
-                                 long long slab_stride, int P, const void* const* peer_out,
-                                 const void* const* peer_flag, int n_peers, int my_rank, long long point,
-                                 void* cta_counter, const void* epoch, void* stream_ptr, int pdl) {
-  NormSpec ns;
-  ns.partials = reinterpret_cast<const float*>(gate_up_partials);
-  ns.slab_stride = slab_stride;
-  ns.P = P;
-  ns.x = nullptr;
-  ns.residual_in = nullptr;
-  ns.residual_out = nullptr;
-  ns.weight = nullptr;
-  ns.eps = 0.0f;
-  ns.wait_flags = nullptr;
-  ns.n_wait = 0;
-  ns.wait_point = 0;
-  ns.epoch = nullptr;
-  ns.mode = 1;
-  PushSpec ps;
-  const PushSpec* pp = nullptr;
-  if (n_peers > 0) {
-    if (n_peers > 8) return -20;
-    ps.n_peers = n_peers;
-    ps.my_rank = my_rank;
-    ps.point = point;
-    ps.push_rows = 0;
-    ps.row_base = 0;
-    ps.cta_counter = reinterpret_cast<int*>(cta_counter);
-    ps.epoch = reinterpret_cast<const unsigned long long*>(epoch);
-    for (int p = 0; p < 8; ++p) {
-      ps.peer_out[p] = p < n_peers ? reinterpret_cast<float*>(const_cast<void*>(peer_out[p])) : nullptr;
-      ps.peer_flag[p] = p < n_peers ? reinterpret_cast<unsigned long long*>(const_cast<void*>(peer_flag[p])) : nullptr;
-    }
-    pp = &ps;
-    out = const_cast<void*>(peer_out[my_rank]);
-  }
-  return gemm_wx_impl(W, W, out, M, T, K, ldw, ldw, ldo, M, nullptr, nullptr, 0, 0, 0, 0, splits, 1, split_stride, 16, 0,
-                      stream_ptr, pdl, pp, &ns);
 }
 
 // Fused row-parallel GEMM -> reduce-scatter for prefill-sized steps: out rows are bf16

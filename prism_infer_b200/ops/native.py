@@ -48,14 +48,10 @@ _SIGNATURES = {
     "prism_gemm_wx_scatter": "ppiiillippiilpppi",
     "prism_reduce_norm_allgather": "ppliiiiiiplppppfpplpppi",
     "prism_add_rmsnorm_packed": "plippppppiifpipi",
-    "prism_gemm_wx_normx": "ppiiilliiiiilplippppfpilpipi",
     "prism_flash_attention_tc": "plpplplpiiiiiiifpi",
-    "prism_gemm_pair": "pppiiilllippliiiippi",
-    "prism_gemv": "pppiiillliipiillppi",
     "prism_gemm_set_small_tile_smem_cap": "i",
     "prism_gemm_set_persistent_min_tokens": "i",
     "prism_gemm_set_persistent_rowmajor": "i",
-    "prism_gemm_wx_actx": "ppiiillilplippiilpppi",
     "prism_gemm_wx_allgather": "ppiiillllpippiilpppi",
     "prism_signal_peers": "piilp",
     "prism_scatter_rows": "pliiiippiilpppi",
@@ -75,7 +71,7 @@ _SIGNATURES = {
     "prism_decode_layers_timeline_stamps": "",
     "prism_decode_layers_seq_step": "i",
 }
-_STATUS_UNITS = ("gemm", "gemm_pair", "gemv", "norm", "attn", "attn_tc", "kvops", "sampler", "comm", "decode_layers")
+_STATUS_UNITS = ("gemm", "norm", "attn", "attn_tc", "kvops", "sampler", "comm", "decode_layers")
 
 
 class NativeError(RuntimeError):

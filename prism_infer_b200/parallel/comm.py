@@ -73,11 +73,6 @@ class NcclComm(TPComm):
         y = ops.linear(x, w)
         return self.reduce_dense(y), None, None
 
-    def row_parallel_swiglu(self, gate_up_partials: torch.Tensor, w: torch.Tensor):
-        T = gate_up_partials.shape[1]
-        parts = ops.linear_actx(gate_up_partials, w, ops.choose_splits(w.shape[0], w.shape[1], T))
-        return None, self.reduce_partials(parts), None
-
     def add_rmsnorm(self, weight, eps, dense, partials, ticket, residual, extra=None, extra_index=None):
         return ops.add_rmsnorm(weight, eps, x=dense, partials=partials, residual=residual, extra=extra,
                                extra_index=extra_index)
@@ -118,12 +113,6 @@ class FusedComm(NcclComm):
             return None, None, self.scatter_partials(parts)
         point, slot = self.point, self.point % 2
         r = self.region
-        if ops.gemv_applies(T, K) and x.stride(1) == 1:
-            self.point += 1
-            native.call("prism_gemv", w.data_ptr(), x.data_ptr(), None, M, T, K, w.stride(0), x.stride(0), M, 2, 0,
-                        self._slab_ptrs[slot], self.size, self.rank, point, T * M, r.local(symm.OFF_EPOCH),
-                        torch.cuda.current_stream().cuda_stream, 1 if ops.pdl_enabled() else 0)
-            return None, None, (slot, point, self.size, T)
         splits = min(symm.S_MAX, ops.choose_splits(M, K, T))
         eff = ops.effective_splits(K, splits)
         self.point += 1
@@ -131,24 +120,6 @@ class FusedComm(NcclComm):
             "prism_gemm_wx_push", w.data_ptr(), x.data_ptr(), M, T, K,
             w.stride(0), x.stride(0), M, M, eff, T * M, self._slab_ptrs[slot], self._flag_ptrs[slot], self.size,
             self.rank, point, r.local(symm.OFF_COUNTER[slot]), r.local(symm.OFF_EPOCH), 0, stages,
-            torch.cuda.current_stream().cuda_stream, 1 if ops.pdl_enabled() else 0,
-        )
-        return None, None, (slot, point, self.size * eff, T)
-
-    def row_parallel_swiglu(self, gate_up_partials: torch.Tensor, w: torch.Tensor):
-        """SwiGLU prologue + down projection + push of the fp32 slabs to every peer, one kernel."""
-        P, T, I2 = gate_up_partials.shape
-        M, K = w.shape
-        if T > ops.NORMX_MAX_TOKENS or M != self.hidden or self.point >= symm.ARGMAX_POINT:
-            return super().row_parallel_swiglu(gate_up_partials, w)
-        eff = ops.effective_splits(K, min(symm.S_MAX, ops.choose_splits(M, K, T)))
-        point, slot = self.point, self.point % 2
-        self.point += 1
-        r = self.region
-        native.call(
-            "prism_gemm_wx_actx", w.data_ptr(), None, M, T, K, w.stride(0), M, eff, T * M,
-            gate_up_partials.data_ptr(), gate_up_partials.stride(0), P, self._slab_ptrs[slot], self._flag_ptrs[slot],
-            self.size, self.rank, point, r.local(symm.OFF_COUNTER[slot]), r.local(symm.OFF_EPOCH),
             torch.cuda.current_stream().cuda_stream, 1 if ops.pdl_enabled() else 0,
         )
         return None, None, (slot, point, self.size * eff, T)
@@ -175,11 +146,6 @@ class FusedComm(NcclComm):
             torch.cuda.current_stream().cuda_stream, 1 if ops.pdl_enabled() else 0,
         )
         return out, new_res
-
-    def norm_source(self, dense, partials, ticket) -> dict:
-        if ticket is None:
-            return super().norm_source(dense, partials, None)
-        raise RuntimeError("the fused-norm GEMM prologue does not consume packed exchange slabs")
 
     def greedy_merge(self, local_val: torch.Tensor, local_id: torch.Tensor) -> torch.Tensor:
         B = local_val.shape[0]

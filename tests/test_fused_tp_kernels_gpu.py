@@ -24,14 +24,9 @@ def close(a, b, atol, rtol, what):
 
 
 @pytest.mark.parametrize("tp,T,K", [(2, 1, 2048), (4, 8, 1024), (2, 96, 512), (8, 24, 512), (8, 3, 1536)])
-@pytest.mark.parametrize("gemv", [False, True])
-def test_push_gemm_then_wait_norm_emulated_ranks(cuda_device, tp, T, K, gemv, monkeypatch):
+def test_push_gemm_then_wait_norm_emulated_ranks(cuda_device, tp, T, K):
     from prism_infer_b200.parallel import symm
     from prism_infer_b200.parallel.comm import FusedComm
-
-    if gemv and T > 4:
-        pytest.skip("the weight-streaming kernel serves at most four tokens")
-    monkeypatch.setattr(ops, "GEMV_MAX_TOKENS", 4 if gemv else 0)
 
     H = 4096
     ops.set_pdl(False)
