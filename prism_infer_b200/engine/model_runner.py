@@ -136,6 +136,8 @@ class ModelRunner:
             source = weights.items() if weights is not None else open_weight_source(
                 config.model, arch, dtype=self.dtype, device=self.device, seed=config.seed)()
             self.model.load(source)
+            if config.logits_precision == "selective_fp32" and self.on_cuda:
+                self.model.enable_fp8_candidate_head()
         self.page = config.kvcache_block_size
         self.max_blocks = -(-config.max_model_len // self.page)
         self.kv_mode = config.kv_mode
@@ -468,7 +470,9 @@ class ModelRunner:
         stream.wait_stream(torch.cuda.current_stream(self.device))
         # one graph per bucket takes the temperature as an input; tensor-parallel ranks add a
         # greedy-only graph whose sampler is the one-kernel (value, id) exchange
-        variants = [(b, False) for b in self.buckets] + ([(b, True) for b in self.buckets] if self.comm.size > 1 else [])
+        # ... and so does a rank with the FP8 candidate head, which serves greedy rows only
+        greedy_variants = self.comm.size > 1 or getattr(self.model, "lm_head_fp8", None) is not None
+        variants = [(b, False) for b in self.buckets] + ([(b, True) for b in self.buckets] if greedy_variants else [])
         for bucket, greedy_only in sorted(variants, reverse=True):
             from ..ops import native as _native
 

@@ -567,6 +567,13 @@ class Qwen3VLModel:
         return h
 
     @torch.no_grad()
+    def enable_fp8_candidate_head(self) -> None:
+        """``logits_precision="selective_fp32"``: keep a row-scaled E4M3 copy of the LM head for greedy decode steps
+        of one row (reference ``prism_infer/models/qwen3_vl.py:1659-1753``); one rank, CUDA."""
+        if self.tp == 1 and self.lm_head.is_cuda and self.lm_head.dtype == torch.bfloat16 and self.H % 16 == 0:
+            self.lm_head_fp8 = ops.quantize_lm_head_fp8(self.lm_head)
+
+    @torch.no_grad()
     def logits(self, hidden: torch.Tensor) -> torch.Tensor:
         """fp32 rank-local logits ``[B, V / tp]`` for the given hidden rows."""
         if hidden.is_cuda:
@@ -578,6 +585,11 @@ class Qwen3VLModel:
                step: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None) -> torch.Tensor:
         """Next token per row: LM head, then arg-max / exponential-race sampling; under tensor
         parallelism ranks exchange their shard winners so every rank returns the same ids."""
+        fp8_head = self.__dict__.get("lm_head_fp8")
+        if (fp8_head is not None and temperature is None and self.tp == 1 and hidden.is_cuda
+                and hidden.shape[0] <= ops.LM_HEAD_FP8_BATCH and not self.__dict__.get("keep_logits")):
+            # greedy rows: candidates from the E4M3 copy of the head (half the bytes), exact rerank with the bf16 rows
+            return ops.lm_head_fp8_greedy(hidden, fp8_head[0], fp8_head[1], self.lm_head, out=out)
         logits = self.logits(hidden)
         if self.__dict__.get("keep_logits"):
             # debugging aid (eager execution): full-vocabulary fp32 logits of the last sampled rows

@@ -744,6 +744,53 @@ def sample(
     return out
 
 
+# ------------------------------------------------------------------ FP8 candidate LM head
+LM_HEAD_FP8_MAX_BATCH = 4  # the kernel's limit; measured, the candidate head beats the bf16 head at one row only
+LM_HEAD_FP8_BATCH = 1      # rows up to which Qwen3VLModel.sample uses it
+
+
+def quantize_lm_head_fp8(weight: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
+    """Row-scaled E4M3 copy of the LM head ``[V, H]`` for candidate generation: ``(codes uint8 [V, H], scale
+    fp32 [V])`` with ``weight ~ codes * scale[:, None]`` (reference
+    ``prism_infer/models/qwen3_vl.py:1723-1743``).  Done once at load time."""
+    w = weight.float()
+    scale = (w.abs().amax(dim=1) / 448.0).clamp_min(1e-12)
+    codes = (w / scale[:, None]).clamp(-448.0, 448.0).to(torch.float8_e4m3fn)
+    return codes.view(torch.uint8).contiguous(), scale.contiguous()
+
+
+def lm_head_fp8_greedy(hidden: torch.Tensor, codes: torch.Tensor, scale: torch.Tensor, weight: torch.Tensor, *,
+                       vocab_offset: int = 0, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Greedy token per row of ``hidden [B, H]`` (B at most 4): candidates from the E4M3 head, exact fp32 rerank
+    with the bf16 rows of ``weight``, lowest id on ties.  The CPU statement is the exact arg-max."""
+    B, H = hidden.shape
+    V = weight.shape[0]
+    if not hidden.is_cuda:
+        tok = F.linear(hidden.float(), weight.float()).argmax(-1) + vocab_offset
+        if out is not None:
+            out.copy_(tok)
+            return out
+        return tok
+    assert B <= LM_HEAD_FP8_MAX_BATCH and hidden.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16
+    assert codes.dtype == torch.uint8 and codes.shape == (V, H) and codes.is_contiguous() and scale.dtype == torch.float32
+    import ctypes as _ct
+
+    plan = (_ct.c_int * 3)()
+    native.call("prism_lm_head_fp8_plan", _ct.cast(plan, _ct.c_void_p))
+    n_cand, n_list = int(plan[0]), int(plan[1])
+    dev = hidden.device
+    cand_val = torch.empty((B, n_cand), dtype=torch.float32, device=dev)
+    cand_id = torch.empty((B, n_cand), dtype=torch.int32, device=dev)
+    list_val = torch.empty((n_list, B), dtype=torch.float32, device=dev)
+    list_id = torch.empty((n_list, B), dtype=torch.int64, device=dev)
+    if out is None:
+        out = torch.empty((B,), dtype=torch.int64, device=dev)
+    native.call("prism_lm_head_fp8_candidates", _p(codes), _p(scale), _p(weight), weight.stride(0), _p(hidden), hidden.stride(0),
+                B, V, H, vocab_offset, _p(cand_val), _p(cand_id), _p(list_val), _p(list_id), _s(), _pdl())
+    native.call("prism_merge_candidates", _p(list_val), _p(list_id), _p(out), n_list, B, _s(), _pdl())
+    return out
+
+
 # ------------------------------------------------------------------------------- vision
 def pos_embed_add(x: torch.Tensor, table: torch.Tensor, idx: torch.Tensor, wt: torch.Tensor) -> torch.Tensor:
     """In place ``x[n] += sum_k wt[k, n] * table[idx[k, n]]`` (bilinear 4-corner plan)."""

@@ -43,6 +43,8 @@ _SIGNATURES = {
     "prism_kv_compact": "pliplppppiiiip",
     "prism_sample": "pllipppiilupppipi",
     "prism_merge_candidates": "pppiipi",
+    "prism_lm_head_fp8_plan": "p",
+    "prism_lm_head_fp8_candidates": "ppplpliiilpppppi",
     "prism_gemm_wx_push": "ppiiillliilppiilppiipi",
     "prism_add_rmsnorm_wait": "plippppppiifpipipi",
     "prism_gemm_wx_scatter": "ppiiillippiilpppi",
@@ -71,7 +73,7 @@ _SIGNATURES = {
     "prism_decode_layers_timeline_stamps": "",
     "prism_decode_layers_seq_step": "i",
 }
-_STATUS_UNITS = ("gemm", "norm", "attn", "attn_tc", "kvops", "sampler", "comm", "decode_layers")
+_STATUS_UNITS = ("gemm", "norm", "attn", "attn_tc", "kvops", "sampler", "comm", "decode_layers", "lm_head_fp8")
 
 
 class NativeError(RuntimeError):

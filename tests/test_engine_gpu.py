@@ -66,10 +66,12 @@ def wide(cuda_device):
     return arch, weights, ReferenceQwen3VL(arch, weights)
 
 
+@pytest.mark.parametrize("logits_precision", ["model", "selective_fp32"])
 @pytest.mark.parametrize("backend", ["eager", "cuda_graph"])
-def test_production_width_image_prompt_on_gpu(wide, backend):
+def test_production_width_image_prompt_on_gpu(wide, backend, logits_precision):
     """The whole chain at the shapes the 8B model runs (split-K slabs, 256-token scaled-FP8 pages,
-    GQA-4 decode, the persistent decode kernel, the 151936-row LM head) against the fp32 oracle."""
+    GQA-4 decode, the 151936-row LM head; with ``selective_fp32`` the E4M3 candidate head and its exact
+    rerank) against the fp32 oracle."""
     arch, weights, oracle = wide
     image = np.random.default_rng(5).integers(0, 256, (224, 224, 3), dtype=np.uint8)
     text = torch.randint(0, 150000, (24,), generator=torch.Generator().manual_seed(5)).tolist()
@@ -77,7 +79,9 @@ def test_production_width_image_prompt_on_gpu(wide, backend):
     want, logits = oracle.generate_greedy(inputs.input_ids, 16, pixel_values=inputs.pixel_values,
                                           image_grid_thw=inputs.image_grid_thw, return_logits=True)
     llm = LLM("random:qwen3-vl-8b-2layer", weights=weights, max_model_len=1024, kvcache_block_size=256, num_kvcache_blocks=6,
-              execution_backend=backend, compression_mode="scaled_fp8_kv", max_num_seqs=2, cpu_kv_cache_ratio=0.0)
+              execution_backend=backend, compression_mode="scaled_fp8_kv", max_num_seqs=2, cpu_kv_cache_ratio=0.0,
+              logits_precision=logits_precision)
+    assert (getattr(llm.runners.runner.model, "lm_head_fp8", None) is not None) == (logits_precision == "selective_fp32")
     got = llm.generate_prepared_image_inputs(inputs, SamplingParams(temperature=0.0, max_tokens=16, ignore_eos=True))
     torch.cuda.synchronize()
     native.check_status()

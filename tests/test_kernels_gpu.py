@@ -438,3 +438,29 @@ def test_tcgen05_flash_attention_head_dim_72(cuda_device, lens, monkeypatch):
     got = ops.varlen_attention(dev[:, 0], dev[:, 1], dev[:, 2], cu.cuda(), max(lens), causal=False)
     torch.cuda.synchronize()
     close(got, ref, 2e-2, 2e-2, f"tcgen05 attention hd 72 lens={lens}")
+
+
+@pytest.mark.parametrize("B,V,H", [(1, 151936, 4096), (4, 151936, 4096), (3, 5000, 256), (2, 1024, 8192)])
+def test_fp8_candidate_lm_head_finds_the_exact_argmax(cuda_device, B, V, H):
+    """Greedy token through the E4M3 candidate head + exact bf16 rerank equals the arg-max of the fp32 logits of the
+    bf16 head; near ties (the two best logits closer than the rerank's summation-order noise) may pick either."""
+    g = torch.Generator().manual_seed(B * 7 + H)
+    w = (torch.randn(V, H, generator=g) * H ** -0.5).to(torch.bfloat16).cuda()
+    x = (torch.randn(B, H, generator=g) * 3.0).to(torch.bfloat16).cuda()
+    # plant clear and narrow winners: rows aligned with the activations
+    for b in range(B):
+        w[(1000 + 37 * b) % V] = (x[b].float() / x[b].float().norm() * (2.0 + b)).to(torch.bfloat16)
+    codes, scale = ops.quantize_lm_head_fp8(w)
+    deq = codes.view(torch.float8_e4m3fn).float() * scale[:, None]
+    assert float((deq - w.float()).abs().max() / w.float().abs().max()) < 0.07
+    got = ops.lm_head_fp8_greedy(x, codes, scale, w, vocab_offset=11)
+    torch.cuda.synchronize()
+    native.check_status()
+    logits = x.float() @ w.float().t()
+    want = logits.argmax(-1)
+    top2 = logits.topk(2, dim=-1).values
+    for b in range(B):
+        if float(top2[b, 0] - top2[b, 1]) > 1e-3:
+            assert int(got[b]) == int(want[b]) + 11, (b, int(got[b]), int(want[b]))
+        else:
+            assert float(logits[b, int(got[b]) - 11]) >= float(top2[b, 1]) - 1e-3
