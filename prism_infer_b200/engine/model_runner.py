@@ -346,14 +346,30 @@ class ModelRunner:
             self._visual[group[0].seq_id] = self._encode(group[0])
             return
         unit = self.config.arch.vision.merge_unit
-        if self.on_cuda and self.comm.size == 1:  # each job's pinned patches travel as their own asynchronous copy
-            # (tensor-parallel ranks copy only the rows of their own shard, from the host tensor)
-            pixels = torch.cat([j.pixel_values.to(device=self.device, dtype=self.dtype, non_blocking=True) for j in group])
-        else:
-            pixels = torch.cat([j.pixel_values for j in group])
         grids = [g for j in group for g in j.grid_thw]
-        with profile_region("model.vision.encoder", metadata={"jobs": len(group)}):
-            main, deep = self._tower(pixels, grids)
+        shard = self.model.vision_shard_rows(grids) if (self.on_cuda and self.comm.size > 1) else None
+        if shard is not None:
+            # tensor-parallel ranks run the blocks on their own segments: upload those rows only, job by job, instead of
+            # concatenating every job's patches on the host (nine processes doing that at once starve one another)
+            lo, n = shard
+            pieces, row = [], 0
+            for j in group:
+                rows_j = int(j.pixel_values.shape[0])
+                a, b = max(lo, row), min(lo + n, row + rows_j)
+                if a < b:
+                    pieces.append(j.pixel_values[a - row:b - row].to(device=self.device, dtype=self.dtype, non_blocking=True))
+                row += rows_j
+            pixels = (pieces[0] if len(pieces) == 1 else torch.cat(pieces)) if pieces else \
+                torch.empty((0, group[0].pixel_values.shape[1]), dtype=self.dtype, device=self.device)
+            with profile_region("model.vision.encoder", metadata={"jobs": len(group)}):
+                main, deep = self.model.encode_vision(pixels, grids, local_rows=shard)
+        else:
+            if self.on_cuda:  # each job's pinned patches travel as their own asynchronous copy
+                pixels = torch.cat([j.pixel_values.to(device=self.device, dtype=self.dtype, non_blocking=True) for j in group])
+            else:
+                pixels = torch.cat([j.pixel_values for j in group])
+            with profile_region("model.vision.encoder", metadata={"jobs": len(group)}):
+                main, deep = self._tower(pixels, grids)
         row = 0
         for job in group:
             n = sum(int(t) * int(h) * int(w) for t, h, w in job.grid_thw) // unit

@@ -311,7 +311,19 @@ class Qwen3VLModel:
 
     # -------------------------------------------------------------------- vision
     @torch.no_grad()
-    def encode_vision(self, pixel_values: torch.Tensor, grid_thw: Sequence[Sequence[int]]) -> tuple[torch.Tensor, list[torch.Tensor]]:
+    def vision_shard_rows(self, grid_thw: Sequence[Sequence[int]]) -> Optional[tuple[int, int]]:
+        """``(first patch row, patch rows)`` this rank runs the vision blocks on when the tower is split over the
+        ranks, or ``None`` when every rank runs all of it.  A caller that holds the patches on the host can then
+        upload its own rows only and pass them to ``encode_vision(..., local_rows=...)``."""
+        grid = [tuple(int(x) for x in g) for g in grid_thw]
+        total_tokens = sum(t * h * w for t, h, w in grid) // self.arch.vision.merge_unit
+        if not (self.tp > 1 and hasattr(self.comm, "vision_begin") and self.device.type == "cuda" and total_tokens <= self.comm.vision_capacity()):
+            return None
+        start, rows, _ = self._vision_shards(grid)[self.rank]
+        return start, rows
+
+    def encode_vision(self, pixel_values: torch.Tensor, grid_thw: Sequence[Sequence[int]], *,
+                      local_rows: Optional[tuple[int, int]] = None) -> tuple[torch.Tensor, list[torch.Tensor]]:
         """``pixel_values [N, C*Tp*P*P]`` -> merged visual tokens ``[N/4, H]`` and one
         DeepStack feature tensor per tap, identical on every rank.
 
@@ -327,7 +339,9 @@ class Qwen3VLModel:
         comm = self.comm
         if self.tp > 1 and pixel_values.device.type != "meta" and hasattr(comm, "vision_begin") and self.device.type == "cuda" \
                 and comm.vision_begin(total_tokens):
-            return self._encode_vision_sharded(pixel_values, grid, total_tokens)
+            return self._encode_vision_sharded(pixel_values, grid, total_tokens, local_rows)
+        if local_rows is not None:
+            raise ValueError("local_rows is only meaningful when the tower is split over the ranks (see vision_shard_rows)")
         main, deep = self._vision_tower(pixel_values, grid, None, 0)
         return main, deep
 
@@ -353,13 +367,19 @@ class Qwen3VLModel:
             start += rows
         return out
 
-    def _encode_vision_sharded(self, pixel_values: torch.Tensor, grid, total_tokens: int):
+    def _encode_vision_sharded(self, pixel_values: torch.Tensor, grid, total_tokens: int, local_rows=None):
         comm = self.comm
         unit = self.arch.vision.merge_unit
         start, rows, sub = self._vision_shards(grid)[self.rank]
         n_out = 1 + len(self.arch.vision.deepstack_visual_indexes)
+        if local_rows is not None:  # the caller uploaded this rank's rows only
+            if tuple(local_rows) != (start, rows) or int(pixel_values.shape[0]) != rows:
+                raise ValueError(f"local_rows {local_rows} with {int(pixel_values.shape[0])} rows does not match this rank's shard {(start, rows)}")
+            mine = pixel_values
+        else:
+            mine = pixel_values[start:start + rows]
         if rows > 0:
-            self._vision_tower(pixel_values[start:start + rows], sub, comm, start // unit)
+            self._vision_tower(mine, sub, comm, start // unit)
         outs = comm.vision_finish(n_out, total_tokens)
         return outs[0], outs[1:]
 

@@ -232,6 +232,10 @@ class FusedComm(NcclComm):
                     self.region.local(symm.OFF_EPOCH), torch.cuda.current_stream().cuda_stream)
 
     # ---- sharded vision tower: merger GEMM -> all-gather ------------------------------------
+    def vision_capacity(self) -> int:
+        """Merged visual tokens one sharded vision-tower call can gather."""
+        return symm.VIS_T_MAX
+
     def vision_begin(self, total_tokens: int) -> bool:
         """Start a sharded vision-tower call; False when the gathered outputs would not fit."""
         if total_tokens > symm.VIS_T_MAX:

@@ -75,6 +75,13 @@ def _build_runner(config, rank: int, world: int, use_cuda: bool, weights):
     return ModelRunner(config, rank=rank, comm=comm, device=device, weights=weights)
 
 
+def _share_host_threads(world: int) -> None:
+    """Every rank is a process with its own intra-op thread pool; sized for the whole machine each, the pools
+    of eight ranks fight over the cores whenever the ranks do the same host work at the same time."""
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(max(1, min(torch.get_num_threads(), cores // max(1, world))))
+
+
 def _worker_entry(rank: int, world: int, init_method: str, seg_name: str, model: str, flat_options: dict, weights,
                   use_cuda: bool) -> None:
     """Process target of a spawned worker rank."""
@@ -82,6 +89,7 @@ def _worker_entry(rank: int, world: int, init_method: str, seg_name: str, model:
 
     if use_cuda:
         torch.cuda.set_device(rank)
+        _share_host_threads(world)
     config = Config(model, **flat_options)
     _init_process_group(rank, world, init_method, use_cuda, config.tensor_parallel_timeout_seconds)
     seg = ControlSegment(seg_name, world - 1, create=False)
@@ -131,6 +139,7 @@ class TensorParallelGroup:
                 if torch.cuda.device_count() < world:
                     raise ValueError(f"tensor_parallel_size {world} needs {world} GPUs, found {torch.cuda.device_count()}")
                 torch.cuda.set_device(0)
+                _share_host_threads(world)
             import datetime
 
             master = dist.TCPStore("127.0.0.1", 0, world, True, timeout=datetime.timedelta(seconds=timeout), wait_for_workers=False)
