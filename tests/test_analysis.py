@@ -122,3 +122,86 @@ def test_runtime_capabilities_fail_closed():
     if not torch.cuda.is_available():
         with pytest.raises(RuntimeError, match="no CUDA device"):
             validate_runtime_capabilities(require_cuda=True)
+
+
+def _record(benchmark, config, results, gpus=1):
+    return {"schema_version": bs.BENCHMARK_SCHEMA_VERSION, "benchmark": benchmark, "engine": "prism_infer_b200", "model": "random:tiny",
+            "hardware": {"gpus": gpus}, "data": "synthetic", "config": config, "results": results}
+
+
+def test_each_benchmark_has_its_own_record_contract():
+    """A record must carry the fields of its benchmark and satisfy the relations between them."""
+    import copy
+
+    row = {"batch": 8, "ttft_ms_mean": 30.0, "ttft_ms_max": 45.0, "tpot_ms_mean": 3.1, "output_tok_per_s": 1800.0, "preprocess_ms": 17.0,
+           "steady_step_ms_median": 3.2, "steady_tok_per_s": 2500.0}
+    good = _record("decode_matrix", {"workload": "image1", "output_tokens": 64, "tp": 8, "kv": "scaled_fp8"}, {"rows": [row]}, gpus=8)
+    bs.validate_benchmark_record(good)
+    for mutate, needle in (
+        (lambda r: r["results"]["rows"][0].pop("tpot_ms_mean"), "tpot_ms_mean is missing"),
+        (lambda r: r["results"]["rows"][0].update(ttft_ms_max=10.0), "below the mean"),
+        (lambda r: r["results"]["rows"][0].update(steady_tok_per_s=9000.0), "does not follow"),
+        (lambda r: r["results"]["rows"].append(dict(row)), "appears twice"),
+        (lambda r: r["hardware"].update(gpus=2), "disagree"),
+        (lambda r: r["results"]["rows"][0].update(batch=0), "not a valid posint"),
+    ):
+        bad = copy.deepcopy(good)
+        mutate(bad)
+        with pytest.raises(bs.SchemaError, match=needle):
+            bs.validate_benchmark_record(bad)
+
+    online = _record("online_working_set",
+                     {"variant": "compact", "groups": 42, "questions": 85, "requests": 600, "rate_per_s": 4.0, "pages": 220, "page_tokens": 256,
+                      "kv_budget_bytes": 220 * 1000, "working_set_pages": 312, "max_tokens": 16, "tp": 1},
+                     {"ttft_p50_ms": 14.2, "ttft_p99_ms": 29.3, "e2e_p50_ms": 76.6, "e2e_p99_ms": 101.7, "recomputed_prompt_tokens": 29984,
+                      "prompt_tokens": 400000, "output_tokens_per_s": 63.0, "completed": 600, "duration_s": 151.0, "resident_media": 42,
+                      "prefix_evictions": 0, "prefix_hits": 558, "resident_pages": 168})
+    bs.validate_benchmark_record(online)
+    for key, value, needle in (("ttft_p99_ms", 1.0, "below"), ("recomputed_prompt_tokens", 10 ** 9, "recomputed"), ("completed", 601, "completed"),
+                               ("resident_pages", 221, "budget"), ("resident_media", 43, "groups")):
+        bad = copy.deepcopy(online)
+        bad["results"][key] = value
+        with pytest.raises(bs.SchemaError, match=needle):
+            bs.validate_benchmark_record(bad)
+
+    cell = {"repeat_rate": 0.5, "requests": 8, "wall_s": 0.4, "requests_per_s": 20.0, "output_tokens": 64,
+            "visual_embedding_cache": {"hits": 4, "misses": 4}, "prefix_cache": {"hits": 4, "misses": 4, "stores": 4, "evictions": 0}}
+    media = _record("media_cache_reuse", {"case": "eight_image_448", "batch": 8, "mode": "scaled_fp8_kv", "max_tokens": 8}, {"cells": [cell]})
+    bs.validate_benchmark_record(media)
+    bad = copy.deepcopy(media)
+    bad["results"]["cells"][0]["output_tokens"] = 65
+    with pytest.raises(bs.SchemaError, match="more output tokens"):
+        bs.validate_benchmark_record(bad)
+    bad = copy.deepcopy(media)
+    bad["results"]["cells"][0]["repeat_rate"] = 1.5
+    with pytest.raises(bs.SchemaError, match="frac"):
+        bs.validate_benchmark_record(bad)
+
+    system = _record("system_mode_matrix", {"mode": "graph", "workload": "single_image_448", "tp": 1},
+                     {"ttft_ms": 16.0, "tpot_ms": 3.9, "e2e_ms": 500.0, "output_tokens_per_s": 250.0, "batch": 1})
+    bs.validate_benchmark_record(system)
+    system["results"]["e2e_ms"] = 1.0
+    with pytest.raises(bs.SchemaError, match="below"):
+        bs.validate_benchmark_record(system)
+
+
+def test_mvbench_prompt_and_answer_extraction():
+    from prism_infer_b200.analysis import quality_metrics as qm
+
+    assert qm.mvbench_prompt("What does the person do?", ["runs", "jumps", "sits"]) == \
+        "Question:What does the person do?\nOption:\n(A) runs\n(B) jumps\n(C) sits\nOnly give the best option.\n"
+    with pytest.raises(ValueError):
+        qm.mvbench_prompt("", ["a", "b"])
+    with pytest.raises(ValueError):
+        qm.mvbench_prompt("q", ["only one"])
+    cases = {"B. the man walks": ("B", "leading_label_period"), "The answer is (C).": ("C", "embedded_label"), "a": ("A", "embedded_label"),
+             "I think it's D, because 1,000 people": ("D", "embedded_label"), "none of them": (None, "unparseable"), "": (None, "unparseable"),
+             "  d. because\nit moves": ("D", "embedded_label"), "[E]": ("E", "embedded_label")}
+    for text, want in cases.items():
+        assert qm.mvbench_choice(text) == want, text
+    rec = {"candidates": ["runs", "jumps", "sits"], "answer_index": 1}
+    hit, miss, silent = qm.mvbench_score(rec, "(B) jumps"), qm.mvbench_score(rec, "C"), qm.mvbench_score(rec, "  ")
+    assert hit["score"] == 1 and hit["target"] == "B" and miss["score"] == 0 and not silent["answered"] and silent["prediction"] is None
+    agg = qm.mvbench_accuracy([hit, miss, silent])
+    assert agg == {"samples": 3, "accuracy": 1 / 3, "answered": 2 / 3, "unparseable": 1}
+    assert qm.mvbench_accuracy([]) == {"samples": 0}
