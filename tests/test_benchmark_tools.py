@@ -18,9 +18,12 @@ def _record(ttft):
     from prism_infer_b200.analysis import benchmark_schema
 
     return {"schema_version": benchmark_schema.BENCHMARK_SCHEMA_VERSION, "benchmark": "online_working_set", "engine": "prism_infer_b200",
-            "model": "random:tiny", "data": "synthetic", "hardware": {"gpus": 1}, "config": {"variant": "compact_prefix"},
+            "model": "random:tiny", "data": "synthetic", "hardware": {"gpus": 1},
+            "config": {"variant": "compact_prefix", "groups": 42, "questions": 85, "requests": 600, "rate_per_s": 4.0, "pages": 220,
+                       "page_tokens": 256, "kv_budget_bytes": 220 * 1000, "working_set_pages": 148, "max_tokens": 16, "tp": 1},
             "results": {"ttft_p50_ms": ttft, "ttft_p99_ms": ttft * 2, "e2e_p50_ms": 80.0, "e2e_p99_ms": 120.0,
-                        "recomputed_prompt_tokens": 100, "output_tokens_per_s": 64.0, "resident_media": 42, "prefix_evictions": 0}}
+                        "recomputed_prompt_tokens": 100, "prompt_tokens": 5000, "output_tokens_per_s": 64.0, "completed": 600,
+                        "duration_s": 150.0, "resident_media": 42, "prefix_evictions": 0, "prefix_hits": 500, "resident_pages": 148}}
 
 
 def test_matrix_resume_skips_complete_cells_and_archives_interrupted_ones(tmp_path):
