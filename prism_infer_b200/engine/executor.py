@@ -76,6 +76,47 @@ class ModelExecutor:
             self._have_visual.add(job.seq_id)
         return len(inputs.vision_jobs)
 
+    # ---- cooperative prefill: one prefill plan run a few decoder layers at a time (reference
+    # ``engine/executor.py:35-95``: begin / advance / finish) ----------------------------------------
+    def begin_prefill(self, plan: BatchPlan):
+        """Page transfers, input preparation, vision tower and embedding of a prefill plan; the layers follow
+        through ``advance_prefill``.  Returns the handle ``finish_prefill`` takes."""
+        assert plan.phase is Phase.PREFILL
+        t0 = time.perf_counter()
+        if not plan.kv_transfers.empty:
+            self.runners.call("apply_kv_transfers", plan.kv_transfers)
+        with profile_region("engine.model_runner", metadata={"phase": "prefill_begin", "batch": plan.batch_size}):
+            inputs = self.preparer.prepare(plan, self._have_visual)
+            for job in inputs.vision_jobs:
+                self._have_visual.add(job.seq_id)
+            for sid in inputs.release_visual:
+                self._have_visual.discard(sid)
+            if self.attention_strategy:
+                self._request_scores(plan, inputs)
+            runner_handle = self.runners.call("begin_prefill", inputs)
+        return {"plan": plan, "inputs": inputs, "runner": runner_handle, "ms": (time.perf_counter() - t0) * 1e3, "quanta": 0}
+
+    def advance_prefill(self, handle, max_layers: int) -> bool:
+        """Up to ``max_layers`` more decoder layers; True when every layer has run."""
+        t0 = time.perf_counter()
+        with profile_region("engine.model_runner", metadata={"phase": "prefill_quantum", "layers": max_layers}):
+            done = bool(self.runners.call("advance_prefill", handle["runner"], int(max_layers)))
+        handle["ms"] += (time.perf_counter() - t0) * 1e3
+        handle["quanta"] += 1
+        return done
+
+    def finish_prefill(self, handle) -> ExecutionResult:
+        """Whatever layers are left, the final norm and the first tokens of the plan's sequences."""
+        t0 = time.perf_counter()
+        plan, inputs = handle["plan"], handle["inputs"]
+        with profile_region("engine.model_runner", metadata={"phase": "prefill_finish", "batch": plan.batch_size}):
+            sampled = self.runners.call("finish_prefill", handle["runner"])
+        tokens: list[int | None] = [None] * plan.batch_size
+        for i, tok in zip(inputs.sample_seq, sampled):
+            tokens[i] = int(tok)
+        compactions = self._after_prefill(plan)
+        return ExecutionResult(tuple(tokens), handle["ms"] + (time.perf_counter() - t0) * 1e3, compactions)
+
     def execute(self, plan: BatchPlan) -> ExecutionResult:
         t0 = time.perf_counter()
         if not plan.kv_transfers.empty:

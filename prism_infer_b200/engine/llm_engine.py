@@ -120,7 +120,9 @@ class LLMEngine:
         self.executor = ModelExecutor(cfg, self.runners, self.scheduler.block_manager)
         self._sequences: dict[int, Sequence] = {}
         self._cooperative_pending = False
-        self.cooperative_counters = {"vision_quanta": 0}
+        self._pending_prefill = None          # executor handle of a prefill whose layers run in quanta
+        self._deferred: list[StepResult] = []  # results produced outside step_result (a pending prefill drained by a cancel)
+        self.cooperative_counters = {"vision_quanta": 0, "layer_quantum_prefills": 0, "layer_quanta": 0, "decode_steps_between_quanta": 0}
         self._steps_since_status = 0
         atexit.register(self.exit)
 
@@ -268,12 +270,16 @@ class LLMEngine:
     # ------------------------------------------------------------------------ step
     def step_result(self) -> StepResult:
         with profile_region("engine.step", cuda=False):
+            if self._deferred:
+                return self._deferred.pop(0)
+            if self._pending_prefill is not None:
+                return self._continue_pending_prefill()
             with profile_region("engine.scheduler.schedule", cuda=False):
                 plan = self.scheduler.schedule()
             if plan.is_idle and plan.kv_transfers.empty:
                 return StepResult(Phase.IDLE)
-            if (self.config.cooperative_prefill and plan.phase is Phase.PREFILL and plan.num_vision_patches > 0
-                    and self.scheduler.num_decoding > 0 and not self._cooperative_pending):
+            cooperative = self.config.cooperative_prefill and plan.phase is Phase.PREFILL and self.scheduler.num_decoding > 0
+            if cooperative and plan.num_vision_patches > 0 and not self._cooperative_pending:
                 # vision quantum now, language prefill on a later step.  The plan's page transfers
                 # ran with the quantum; the scheduler lists a transfer only in the plan that admits
                 # its sequence (or grows its table), so the re-planned prefill carries none of
@@ -284,21 +290,61 @@ class LLMEngine:
                     self.scheduler.consecutive_prefill_batches = self.scheduler.policy.max_consecutive_prefill
                     return StepResult(Phase.IDLE)
             self._cooperative_pending = False
-            profile_step_metadata({"phase": plan.phase.value, "batch_size": plan.batch_size, "tokens": plan.num_tokens,
-                                   "vision_patches": plan.num_vision_patches})
-            result = self.executor.execute(plan)
-            self._steps_since_status += 1
-            if 0 < self.config.device_status_check_interval <= self._steps_since_status:
-                self.check_device_status()
-            if plan.is_idle:
-                return StepResult(Phase.IDLE)
-            with profile_region("engine.scheduler.postprocess", cuda=False):
-                outputs = self.scheduler.postprocess(plan, result.tokens)
-            self.metrics.on_batch_completed(plan, result.duration_ms, result.compactions)
-            for o in outputs:
-                if o.finished:
-                    self._sequences.pop(o.request_id, None)
-            return StepResult(plan.phase, tuple(outputs), plan.num_tokens)
+            if cooperative and not self.executor.attention_strategy:
+                # layer quanta: the prefill's embedding now, its decoder layers a few at a time with a decode step
+                # of the running sequences after every quantum (reference engine/llm_engine.py:1040-1103)
+                profile_step_metadata({"phase": "prefill_begin", "batch_size": plan.batch_size, "tokens": plan.num_tokens,
+                                       "vision_patches": plan.num_vision_patches})
+                self._pending_prefill = self.executor.begin_prefill(plan)
+                self.cooperative_counters["layer_quantum_prefills"] += 1
+                return self._decode_between_quanta()
+            return self._run_plan(plan)
+
+    def _run_plan(self, plan) -> StepResult:
+        profile_step_metadata({"phase": plan.phase.value, "batch_size": plan.batch_size, "tokens": plan.num_tokens,
+                               "vision_patches": plan.num_vision_patches})
+        result = self.executor.execute(plan)
+        return self._commit(plan, result)
+
+    def _commit(self, plan, result) -> StepResult:
+        self._steps_since_status += 1
+        if 0 < self.config.device_status_check_interval <= self._steps_since_status:
+            self.check_device_status()
+        if plan.is_idle:
+            return StepResult(Phase.IDLE)
+        with profile_region("engine.scheduler.postprocess", cuda=False):
+            outputs = self.scheduler.postprocess(plan, result.tokens)
+        self.metrics.on_batch_completed(plan, result.duration_ms, result.compactions)
+        for o in outputs:
+            if o.finished:
+                self._sequences.pop(o.request_id, None)
+        return StepResult(plan.phase, tuple(outputs), plan.num_tokens)
+
+    # ---- cooperative prefill by layer quanta ------------------------------------------------------
+    def _decode_between_quanta(self) -> StepResult:
+        """One decode step of the running sequences while a prefill is pending; the scheduler's decode plan only
+        touches decoding sequences (victims of a preemption included), never the ones whose prefill is under way."""
+        with profile_region("engine.scheduler.schedule", cuda=False):
+            plan = self.scheduler.schedule_decode()
+        if plan is None:
+            return StepResult(Phase.IDLE)
+        self.scheduler.counters["decode_batches"] += 1
+        self.cooperative_counters["decode_steps_between_quanta"] += 1
+        return self._run_plan(plan)
+
+    def _finish_pending_prefill(self) -> StepResult:
+        handle, self._pending_prefill = self._pending_prefill, None
+        result = self.executor.finish_prefill(handle)
+        self.cooperative_counters["layer_quanta"] += handle["quanta"]
+        return self._commit(handle["plan"], result)
+
+    def _continue_pending_prefill(self) -> StepResult:
+        if self.scheduler.num_decoding == 0:  # nothing left to protect: run the rest in one piece
+            return self._finish_pending_prefill()
+        done = self.executor.advance_prefill(self._pending_prefill, self.config.cooperative_prefill_layer_quantum)
+        if done:
+            return self._finish_pending_prefill()
+        return self._decode_between_quanta()
 
     def step(self) -> tuple[list[tuple[int, list[int]]], int]:
         """Compatibility form: ``([(request_id, completion_token_ids), ...], signed token count)``
@@ -308,7 +354,7 @@ class LLMEngine:
         return done, (res.num_tokens if res.phase is Phase.PREFILL else -res.num_tokens)
 
     def is_finished(self) -> bool:
-        return self.scheduler.is_finished()
+        return self.scheduler.is_finished() and not self._deferred
 
     def check_device_status(self) -> None:
         """Read every rank's kernel status words (bounded waits that ran out, failed bounds checks;
@@ -324,6 +370,11 @@ class LLMEngine:
             raise RuntimeError(f"device status reports failures (rank, unit) -> (code, detail, block, count): {bad}")
 
     def cancel_request(self, request_id: int) -> bool:
+        pending = self._pending_prefill
+        if pending is not None and any(seq.seq_id == request_id for seq in pending["plan"].seqs):
+            # its pages must stay allocated until the layers that still write them have run: finish the prefill
+            # first (the other sequences' first tokens are delivered by the next step_result), then cancel
+            self._deferred.append(self._finish_pending_prefill())
         ok = self.scheduler.cancel(request_id)
         self.executor.drop_visual(request_id)
         self._sequences.pop(request_id, None)

@@ -421,7 +421,8 @@ class ModelRunner:
             return t
         return t.pin_memory().to(self.device, non_blocking=True)
 
-    def _run_prefill(self, inp: StepInputs) -> list[int]:
+    def _prefill_inputs(self, inp: StepInputs):
+        """Vision tower for the step's jobs and the device-side inputs of its language prefill."""
         with profile_region("runner.prepare_inputs"):
             self._encode_jobs(inp.vision_jobs)
             visual = deep = None
@@ -445,8 +446,10 @@ class ModelRunner:
                 from .visual_pruning import RuntimeVisualTokenScorer
 
                 meta.scorer = RuntimeVisualTokenScorer(inp.score_rows, inp.score_layers)
-        with profile_region("runner.run_model"):
-            hidden = self.model.forward(ids, pos, meta, self.kv, visual=visual, vis_index=vis_index, deepstack=deep)
+        return ids, pos, meta, visual, vis_index, deep
+
+    def _prefill_outputs(self, inp: StepInputs, meta: AttnMeta, hidden: torch.Tensor) -> list[int]:
+        """After the layers: visual-token scores, release of consumed visual embeddings, first tokens."""
         if meta.scorer is not None:
             self._visual_scores.update(meta.scorer.finalize(world_size=self.comm.size, reduce_sum=self.comm.reduce_dense))
         for seq_id in inp.release_visual:
@@ -461,6 +464,41 @@ class ModelRunner:
             step = torch.tensor([self.steps_run], dtype=torch.int64, device=self.device)
             tok = self.model.sample(rows, temps, seed=self.sample_seed, step=step)
         return tok.tolist()
+
+    def _run_prefill(self, inp: StepInputs) -> list[int]:
+        ids, pos, meta, visual, vis_index, deep = self._prefill_inputs(inp)
+        with profile_region("runner.run_model"):
+            hidden = self.model.forward(ids, pos, meta, self.kv, visual=visual, vis_index=vis_index, deepstack=deep)
+        return self._prefill_outputs(inp, meta, hidden)
+
+    # ---- cooperative prefill: the same step, a few decoder layers at a time (reference
+    # ``engine/model_runner.py:1346-1650``; one rank) -----------------------------------------------
+    def begin_prefill(self, inp: StepInputs) -> int:
+        """Vision tower, embedding and device inputs of a prefill step whose layers ``advance_prefill`` runs in
+        quanta, so that decode steps of running sequences can go in between.  Returns a handle."""
+        if self.comm.size != 1:
+            raise ValueError("cooperative prefill runs on one rank")
+        self.steps_run += 1
+        ids, pos, meta, visual, vis_index, deep = self._prefill_inputs(inp)
+        state = self.model.begin_layers(ids, pos, meta, self.kv, visual=visual, vis_index=vis_index, deepstack=deep)
+        handle = self.__dict__.setdefault("_prefill_handles", 0) + 1
+        self._prefill_handles = handle
+        self.__dict__.setdefault("_pending_prefills", {})[handle] = (inp, state)
+        return handle
+
+    def advance_prefill(self, handle: int, max_layers: int) -> bool:
+        """Up to ``max_layers`` more decoder layers of a begun prefill; True when all have run."""
+        _, state = self._pending_prefills[handle]
+        with profile_region("runner.run_model", metadata={"layers": max_layers}):
+            return self.model.advance_layers(state, max_layers)
+
+    def finish_prefill(self, handle: int) -> list[int]:
+        """Remaining layers, final norm, sampling; returns the first token of every sampling row."""
+        inp, state = self._pending_prefills.pop(handle)
+        with profile_region("runner.run_model"):
+            self.model.advance_layers(state, len(self.model.layers))
+            hidden = self.model.finish_layers(state)
+        return self._prefill_outputs(inp, state.meta, hidden)
 
     def _run_decode_eager(self, inp: StepInputs) -> list[int]:
         meta = AttnMeta(is_prefill=False, block_tables=self._to_dev(inp.block_tables), slots=self._to_dev(inp.slots),

@@ -94,6 +94,26 @@ class MergerWeights:
     post_norm: bool = False
 
 
+@dataclass
+class LayerwiseState:
+    """What the layer loop carries from one layer to the next: the pending output of the last row-parallel projection
+    (dense rows, split-K slabs or an exchange ticket), the residual, and the step's inputs."""
+
+    positions: torch.Tensor
+    meta: "AttnMeta"
+    cache: "ops.KVCache"
+    vis_index: Optional[torch.Tensor]
+    deepstack: Optional[Sequence[torch.Tensor]]
+    tokens: int
+    small: bool
+    scoring: bool
+    dense: Optional[torch.Tensor] = None
+    partials: Optional[torch.Tensor] = None
+    ticket: object = None
+    residual: Optional[torch.Tensor] = None
+    next_layer: int = 0
+
+
 class TPComm:
     """Collective hooks of a tensor-parallel rank; the single-rank default does nothing."""
 
@@ -472,13 +492,39 @@ class Qwen3VLModel:
             pre = plan.run(x, positions, meta.slots, meta.block_tables, meta.context_lens)
             h, _ = ops.add_rmsnorm(self.final_norm, t.rms_norm_eps, x=pre, residual=None)
             return h
-        residual: Optional[torch.Tensor] = None
-        dense, partials, ticket = x, None, None
-        n_deep = len(deepstack) if deepstack is not None else 0
         if (self.tp > 1 and x.is_cuda and meta.is_prefill and hasattr(comm, "prefill_fused") and comm.prefill_fused(T)
                 and ops.TP_PREFILL_FUSED and not scoring):
             return self._forward_prefill_fused(x, positions, meta, cache, deepstack, vis_index)
-        for i, l in enumerate(self.layers):
+        state = LayerwiseState(positions, meta, cache, vis_index, deepstack, T, small, scoring, dense=x)
+        self.advance_layers(state, len(self.layers))
+        return self.finish_layers(state)
+
+    # ---- resumable form of the layer loop (cooperative prefill runs it a few layers at a time) ----------
+    @torch.no_grad()
+    def begin_layers(self, input_ids: torch.Tensor, positions: torch.Tensor, meta: AttnMeta, cache: ops.KVCache, *,
+                     visual: Optional[torch.Tensor] = None, vis_index: Optional[torch.Tensor] = None,
+                     deepstack: Optional[Sequence[torch.Tensor]] = None) -> "LayerwiseState":
+        """Embedding of a step whose layers will be run by ``advance_layers`` in pieces (one rank; the reference's
+        resumable layer-quantum forward is ``prism_infer/models/qwen3_vl.py:1024-1146``)."""
+        if self.tp != 1:
+            raise ValueError("the layer-by-layer form runs on one rank")
+        T = input_ids.shape[0]
+        scoring = meta.scorer is not None and meta.is_prefill
+        self.comm.begin_step()
+        x = ops.embed(input_ids, self.embed, visual=visual, vis_index=vis_index)
+        return LayerwiseState(positions, meta, cache, vis_index, deepstack, T, T <= SMALL_T and not scoring, scoring, dense=x)
+
+    @torch.no_grad()
+    def advance_layers(self, st: "LayerwiseState", max_layers: int) -> bool:
+        """Run up to ``max_layers`` more decoder layers; True once all layers have run."""
+        t, comm = self.arch.text, self.comm
+        positions, meta, cache, vis_index, deepstack, T = st.positions, st.meta, st.cache, st.vis_index, st.deepstack, st.tokens
+        small, scoring = st.small, st.scoring
+        n_deep = len(deepstack) if deepstack is not None else 0
+        dense, partials, ticket, residual = st.dense, st.partials, st.ticket, st.residual
+        stop = min(len(self.layers), st.next_layer + max(0, int(max_layers)))
+        for i in range(st.next_layer, stop):
+            l = self.layers[i]
             extra = deepstack[i - 1] if 0 < i <= n_deep else None
             h, residual = comm.add_rmsnorm(l.input_norm, t.rms_norm_eps, dense, partials, ticket, residual,
                                            extra, vis_index if extra is not None else None)
@@ -520,9 +566,19 @@ class Qwen3VLModel:
             else:
                 act = ops.gate_up_swiglu(h, l.gate_up)
             dense, partials, ticket = comm.row_parallel(act, l.down)
-        extra = deepstack[n_deep - 1] if n_deep == len(self.layers) else None
-        h, _ = comm.add_rmsnorm(self.final_norm, t.rms_norm_eps, dense, partials, ticket, residual,
-                                extra, vis_index if extra is not None else None)
+        st.dense, st.partials, st.ticket, st.residual, st.next_layer = dense, partials, ticket, residual, stop
+        return stop == len(self.layers)
+
+    @torch.no_grad()
+    def finish_layers(self, st: "LayerwiseState") -> torch.Tensor:
+        """Final norm (with the last DeepStack tap when every layer has one); hidden states ``[T, H]``."""
+        if st.next_layer != len(self.layers):
+            raise RuntimeError(f"finish_layers after {st.next_layer} of {len(self.layers)} layers")
+        t = self.arch.text
+        n_deep = len(st.deepstack) if st.deepstack is not None else 0
+        extra = st.deepstack[n_deep - 1] if n_deep == len(self.layers) else None
+        h, _ = self.comm.add_rmsnorm(self.final_norm, t.rms_norm_eps, st.dense, st.partials, st.ticket, st.residual,
+                                     extra, st.vis_index if extra is not None else None)
         return h
 
     def _decode_plan(self, cache: ops.KVCache, tokens: int):

@@ -103,6 +103,36 @@ def test_graph_decode_equals_eager_decode(tiny):
     native.check_status()
 
 
+def test_cooperative_layer_quanta_interleave_with_graph_decode(tiny):
+    """A prompt arriving while another sequence decodes: its prefill runs one layer per quantum between graph decode
+    steps; the tokens equal those of the engine without cooperative prefill."""
+    arch, weights, _ = tiny
+    first = torch.randint(0, 1000, (12,), generator=torch.Generator().manual_seed(1)).tolist()
+    late = torch.randint(0, 1000, (150,), generator=torch.Generator().manual_seed(2)).tolist()
+    outs = {}
+    for cooperative in (False, True):
+        llm = LLM("random:tiny", weights=weights, max_model_len=512, kvcache_block_size=16, num_kvcache_blocks=64,
+                  execution_backend="cuda_graph", compression_mode="scaled_fp8_kv", max_num_seqs=8, cpu_kv_cache_ratio=0.0,
+                  enable_cooperative_prefill=cooperative, cooperative_prefill_layer_quantum=1)
+        a = llm.add_request(first, SamplingParams(temperature=0.0, max_tokens=16, ignore_eos=True))
+        while llm.scheduler.num_decoding == 0:
+            llm.step_result()
+        b = llm.add_request(late, SamplingParams(temperature=0.0, max_tokens=6, ignore_eos=True))
+        done = {}
+        while not llm.is_finished():
+            for o in llm.step_result().outputs:
+                if o.finished:
+                    done[o.request_id] = list(o.token_ids)
+        torch.cuda.synchronize()
+        native.check_status()
+        outs[cooperative] = (done[a], done[b])
+        if cooperative:
+            c = llm.cooperative_counters
+            assert c["layer_quantum_prefills"] == 1 and c["layer_quanta"] == arch.text.num_layers and c["decode_steps_between_quanta"] >= 2
+        llm.exit()
+    assert outs[True] == outs[False]
+
+
 def test_prefix_hit_and_compaction_on_gpu(tiny):
     arch, weights, _ = tiny
     llm = LLM("random:tiny", weights=weights, max_model_len=512, kvcache_block_size=16, num_kvcache_blocks=64,

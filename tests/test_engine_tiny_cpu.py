@@ -126,6 +126,67 @@ def test_cooperative_prefill_keeps_the_transfers_of_requests_admitted_after_the_
     llm.exit()
 
 
+def test_cooperative_prefill_runs_the_layers_in_quanta_between_decode_steps(tiny):
+    """With a sequence decoding, a new prompt's prefill runs one decoder layer per quantum and every quantum is
+    followed by a decode step of the running sequence; tokens equal the oracle's (and thus the atomic prefill's)."""
+    arch, weights, oracle = tiny
+    llm = _llm(weights, enable_cooperative_prefill=True, cooperative_prefill_layer_quantum=1)
+    first = [3, 4, 5, 6, 7]
+    a_id = llm.add_request(first, SamplingParams(temperature=0.0, max_tokens=14, ignore_eos=True))
+    while llm.scheduler.num_decoding == 0:
+        llm.step_result()
+    late = list(range(40, 71))
+    b_id = llm.add_request(late, SamplingParams(temperature=0.0, max_tokens=5, ignore_eos=True))
+    phases, done = [], {}
+    while not llm.is_finished():
+        res = llm.step_result()
+        phases.append((res.phase.value, llm.request_state(b_id).value if llm.request_state(b_id) else "gone"))
+        for o in res.outputs:
+            if o.finished:
+                done[o.request_id] = list(o.token_ids)
+    c = llm.cooperative_counters
+    # two layers, one per quantum: begin, decode, layer 0, decode, layer 1 + final norm + first token
+    assert c["layer_quantum_prefills"] == 1 and c["layer_quanta"] == arch.text.num_layers == 2
+    assert c["decode_steps_between_quanta"] == 2
+    # while B was prefilling, decode steps of A went through
+    assert ("decode", "prefilling") in phases
+    assert [p for p, _ in phases].count("prefill") == 1
+    assert done[a_id] == oracle.generate_greedy(first, 14)
+    assert done[b_id] == oracle.generate_greedy(late, 5)
+    llm.exit()
+
+
+def test_cancelling_a_request_whose_prefill_is_pending_drains_the_prefill_first(tiny):
+    """The pages of a sequence in a pending prefill stay allocated until the remaining layers have written them: a
+    cancel finishes the prefill, the other sequence of the same plan still gets its first token, nothing leaks."""
+    arch, weights, oracle = tiny
+    llm = _llm(weights, enable_cooperative_prefill=True, cooperative_prefill_layer_quantum=1)
+    free0 = llm.scheduler.block_manager.gpu.num_free
+    a_id = llm.add_request([3, 4, 5, 6, 7], SamplingParams(temperature=0.0, max_tokens=10, ignore_eos=True))
+    while llm.scheduler.num_decoding == 0:
+        llm.step_result()
+    keep, drop = list(range(40, 60)), list(range(80, 105))
+    k_id = llm.add_request(keep, SamplingParams(temperature=0.0, max_tokens=4, ignore_eos=True))
+    d_id = llm.add_request(drop, SamplingParams(temperature=0.0, max_tokens=4, ignore_eos=True))
+    done = {}
+    for _ in range(6):
+        for o in llm.step_result().outputs:
+            if o.finished:
+                done[o.request_id] = list(o.token_ids)
+        if llm._pending_prefill is not None:
+            break
+    assert llm._pending_prefill is not None and {s.seq_id for s in llm._pending_prefill["plan"].seqs} == {k_id, d_id}
+    assert llm.cancel_request(d_id) and llm._pending_prefill is None
+    while not llm.is_finished():
+        for o in llm.step_result().outputs:
+            if o.finished:
+                done[o.request_id] = list(o.token_ids)
+    assert done[k_id] == oracle.generate_greedy(keep, 4) and d_id not in done
+    assert done[a_id] == oracle.generate_greedy([3, 4, 5, 6, 7], 10)
+    assert llm.scheduler.block_manager.gpu.num_free == free0
+    llm.exit()
+
+
 def test_visual_compaction_frees_pages_and_hits(tiny):
     arch, weights, _ = tiny
     img = _image(4)
