@@ -48,14 +48,28 @@ REFERENCE_MODES: list[tuple[str, dict]] = [
 ]
 
 
-def reference_modes() -> list[tuple[str, dict]]:
+# Under tensor parallelism the reference requires ``logits_precision="model"`` (``config.py``: "tensor parallel
+# execution requires logits_precision='model'") and its own tensor-parallel modes compile the attention region only
+# (``benchmarks/bench_system.py:217-243``, ``tp2_tuned_graph`` / ``tp2_compile_graph``); KV stays scaled FP8, the
+# configuration of this benchmark.
+_TUNED_TP = dict(logits_precision="model", paged_decode_block_n=256)
+REFERENCE_MODES_TP: list[tuple[str, dict]] = [
+    ("scaled_fp8_kv_tp_compile_graph", dict(execution_backend="compile_graph", decode_compile_region="attention", **_TUNED_TP, **_FUSED)),
+    ("scaled_fp8_kv_tp_tuned_graph", dict(execution_backend="cuda_graph", **_TUNED_TP, **_FUSED)),
+    ("scaled_fp8_kv_tp_bn256_graph", dict(execution_backend="cuda_graph", **_TUNED_TP)),
+    ("scaled_fp8_kv_graph (package defaults)", {}),
+]
+
+
+def reference_modes(world: int = 1) -> list[tuple[str, dict]]:
+    modes = REFERENCE_MODES if world <= 1 else REFERENCE_MODES_TP
     pinned = os.environ.get("PRISM_REFERENCE_MODE")
     if pinned:
-        chosen = [m for m in REFERENCE_MODES if m[0].split(" ")[0] == pinned]
+        chosen = [m for m in modes if m[0].split(" ")[0] == pinned]
         if not chosen:
-            raise ValueError(f"PRISM_REFERENCE_MODE={pinned!r} is none of {[m[0].split(' ')[0] for m in REFERENCE_MODES]}")
+            raise ValueError(f"PRISM_REFERENCE_MODE={pinned!r} is none of {[m[0].split(' ')[0] for m in modes]}")
         return chosen
-    return list(REFERENCE_MODES)
+    return list(modes)
 
 
 def unavailable(why: str) -> None:
@@ -173,7 +187,7 @@ def main(args) -> None:
             return s.elapsed_time(e), (time.perf_counter() - t0) * 1e3
 
         llm, mode_name, skipped = None, "", []
-        for mode_name, extra in reference_modes():
+        for mode_name, extra in reference_modes(args.gpus):
             try:
                 llm = LLM(ckpt, **base, **extra)
                 timed(W + 1)  # warm-up: kernel JIT / compilation, graph replay paths
