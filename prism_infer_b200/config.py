@@ -197,6 +197,7 @@ class ExecutionConfig:
     cooperative_prefill_vision_block_quantum: int = 4
     programmatic_dependent_launch: bool = True
     decode_multi_step: int = 1
+    decode_run_ahead: bool = True             # launch the next greedy decode graph before the host has read this one's tokens
     device_status_check_interval: int = 256   # engine steps between reads of the kernels' status words (0 = never)
 
     def __post_init__(self) -> None:
@@ -207,7 +208,7 @@ class ExecutionConfig:
         if self.paged_decode_block_n not in (16, 32, 64, 128, 256):
             raise ValueError("paged_decode_block_n must be a power of two in [16, 256]")
         for n in ("fused_qk_rmsnorm", "fused_qk_mrope", "fused_add_rmsnorm", "packed_kv_projection",
-                  "cooperative_prefill", "programmatic_dependent_launch"):
+                  "cooperative_prefill", "programmatic_dependent_launch", "decode_run_ahead"):
             _bool(getattr(self, n), n)
         _int(self.cooperative_prefill_layer_quantum, "cooperative_prefill_layer_quantum", 1)
         _int(self.cooperative_prefill_vision_block_quantum, "cooperative_prefill_vision_block_quantum", 1)
@@ -296,6 +297,7 @@ _FLAT = {
         "cooperative_prefill_vision_block_quantum": "cooperative_prefill_vision_block_quantum",
         "enable_programmatic_dependent_launch": "programmatic_dependent_launch",
         "decode_multi_step": "decode_multi_step",
+        "enable_decode_run_ahead": "decode_run_ahead",
         "device_status_check_interval": "device_status_check_interval",
     },
 }

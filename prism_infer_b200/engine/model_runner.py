@@ -63,17 +63,30 @@ class _DecodeGraph:
         self.off_bt = al(self.off_temp + bucket * 4)
         self.nbytes = al(self.off_bt + bucket * mb * 4)
         pin = runner.on_cuda
-        self.host = torch.zeros(self.nbytes, dtype=torch.uint8, pin_memory=pin)
+        # Two pinned staging buffers and two token read-back buffers, used alternately: the host may stage step n + 1
+        # while the copies of step n are still pending (one step runs ahead at most).  The copies run outside the
+        # captured graph, which therefore reads and writes fixed device buffers only.
+        self.hosts = [torch.zeros(self.nbytes, dtype=torch.uint8, pin_memory=pin) for _ in range(2)]
         self.dev = torch.zeros(self.nbytes, dtype=torch.uint8, device=dev)
-        self.h_ids, self.h_slots, self.h_pos, self.h_ctx, self.h_temp, self.h_bt = self._views(self.host, bucket, mb)
         self.d_ids, self.d_slots, self.d_pos, self.d_ctx, self.d_temp, self.d_bt = self._views(self.dev, bucket, mb)
         self.tokens = torch.zeros(bucket, dtype=torch.int64, device=dev)
-        self.tokens_host = torch.zeros(bucket, dtype=torch.int64, pin_memory=pin)
+        self.tokens_hosts = [torch.zeros(bucket, dtype=torch.int64, pin_memory=pin) for _ in range(2)]
+        self.done = [torch.cuda.Event() for _ in range(2)] if pin else [None, None]
+        self.flip = 0
         self.step = torch.zeros(1, dtype=torch.int64, device=dev)
         self.graph: Optional[torch.cuda.CUDAGraph] = None
-        self._np = tuple(t.numpy() for t in (self.h_ids, self.h_slots, self.h_pos, self.h_ctx, self.h_temp, self.h_bt))
-        self._rows = 0  # rows of the staging buffer that hold real sequences
-        self.reset_rows(0)
+        self._nps = [tuple(t.numpy() for t in self._views(h, bucket, mb)) for h in self.hosts]
+        self._rows = [0, 0]  # rows of each staging buffer that hold real sequences
+        for k in (0, 1):
+            self.reset_rows(k, 0)
+
+    @property
+    def host(self) -> torch.Tensor:
+        return self.hosts[self.flip]
+
+    @property
+    def tokens_host(self) -> torch.Tensor:
+        return self.tokens_hosts[self.flip]
 
     def _views(self, buf: torch.Tensor, b: int, mb: int):
         ids = buf[self.off_ids:self.off_ids + b * 8].view(torch.int64)
@@ -84,9 +97,9 @@ class _DecodeGraph:
         bt = buf[self.off_bt:self.off_bt + b * mb * 4].view(torch.int32).view(b, mb)
         return ids, slots, pos, ctx, temp, bt
 
-    def reset_rows(self, start: int) -> None:
-        """Padding rows: token 0, no slot, empty context, no pages."""
-        n = self._np
+    def reset_rows(self, k: int, start: int) -> None:
+        """Padding rows of staging buffer ``k``: token 0, no slot, empty context, no pages."""
+        n = self._nps[k]
         n[0][start:] = 0
         n[1][start:] = -1
         n[2][:, start:] = 0
@@ -94,25 +107,43 @@ class _DecodeGraph:
         n[4][start:] = 0
         n[5][start:] = -1
 
-    def fill(self, inp: StepInputs) -> int:
-        """Stage one step's inputs in the pinned buffer the graph's copy node reads.  Writes go
-        through numpy views of the pinned memory (a tenth of the cost of tensor slice assignment,
-        and this runs on the critical path of every decode step); padding rows are rewritten only
-        when the batch shrank."""
+    def fill(self, inp: StepInputs, *, ahead: int = 0) -> int:
+        """Stage one step's inputs in the next pinned buffer.  Writes go through numpy views of the
+        pinned memory (a tenth of the cost of tensor slice assignment, and this runs on the critical
+        path of every decode step); padding rows are rewritten only when the batch shrank.
+        ``ahead = 1`` stages the step AFTER ``inp`` instead (same sequences one token later; the ids are
+        taken from the device)."""
+        self.flip ^= 1
+        k = self.flip
         n = inp.num_seqs
-        ids, slots, pos, ctx, temp, bt = self._np
+        ids, slots, pos, ctx, temp, bt = self._nps[k]
         ids[:n] = inp.input_ids.numpy()
-        slots[:n] = inp.slots.numpy()
-        pos[:, :n] = inp.positions.numpy()
-        ctx[:n] = inp.context_lens.numpy()
+        slots[:n] = inp.slots.numpy() + ahead
+        pos[:, :n] = inp.positions.numpy() + ahead
+        ctx[:n] = inp.context_lens.numpy() + ahead
         temp[:n] = inp.temperatures.numpy()
         w = inp.block_tables.shape[1]
         bt[:n, :w] = inp.block_tables.numpy()
         bt[:n, w:] = -1
-        if n < self._rows:
-            self.reset_rows(n)
-        self._rows = n
-        return n
+        if n < self._rows[k]:
+            self.reset_rows(k, n)
+        self._rows[k] = n
+        return k
+
+    def launch(self, k: int, n: int, *, ids_from_device: bool = False) -> None:
+        """Copy staging buffer ``k`` to the device, replay the graph, read the tokens back into read-back buffer
+        ``k``, record its event.  ``ids_from_device``: the input ids are the tokens the previous launch sampled
+        (still in flight; stream order makes them ready)."""
+        self.dev.copy_(self.hosts[k], non_blocking=True)
+        if ids_from_device:
+            self.d_ids[:n].copy_(self.tokens[:n], non_blocking=True)
+        self.graph.replay()
+        self.tokens_hosts[k].copy_(self.tokens, non_blocking=True)
+        self.done[k].record()
+
+    def wait(self, k: int, n: int) -> list[int]:
+        self.done[k].synchronize()
+        return self.tokens_hosts[k][:n].tolist()
 
 
 class ModelRunner:
@@ -151,6 +182,7 @@ class ModelRunner:
         self.vision_graph_counters = {"captures": 0, "replays": 0}
         self.graphs: dict[int, _DecodeGraph] = {}
         self.greedy_graphs: dict[int, _DecodeGraph] = {}
+        self.run_ahead_counters = {"taken": 0, "discarded": 0}
         self.buckets = decode_buckets(min(config.max_num_seqs, 512))
         self.sample_seed = config.seed
         self.steps_run = 0
@@ -410,10 +442,13 @@ class ModelRunner:
     def execute(self, inp: StepInputs) -> list[int]:
         """Run one step; returns the sampled token of every sampling row."""
         self.steps_run += 1
+        if self.graphs and inp.kind != "prefill" and inp.num_seqs <= self.buckets[-1]:
+            return self._run_decode_graph(inp)
+        if getattr(self, "_ahead", None) is not None:  # a launch that ran ahead is not taken over across other kinds of steps
+            self._ahead = None
+            self.run_ahead_counters["discarded"] += 1
         if inp.kind == "prefill":
             return self._run_prefill(inp)
-        if self.graphs and inp.num_seqs <= self.buckets[-1]:
-            return self._run_decode_graph(inp)
         return self._run_decode_eager(inp)
 
     def _to_dev(self, t: Optional[torch.Tensor]) -> Optional[torch.Tensor]:
@@ -479,6 +514,7 @@ class ModelRunner:
         if self.comm.size != 1:
             raise ValueError("cooperative prefill runs on one rank")
         self.steps_run += 1
+        self._ahead = None
         ids, pos, meta, visual, vis_index, deep = self._prefill_inputs(inp)
         state = self.model.begin_layers(ids, pos, meta, self.kv, visual=visual, vis_index=vis_index, deepstack=deep)
         handle = self.__dict__.setdefault("_prefill_handles", 0) + 1
@@ -539,9 +575,7 @@ class ModelRunner:
                 graph = torch.cuda.CUDAGraph()
                 before = _native.launch_count()
                 with torch.cuda.graph(graph, pool=pool, stream=stream):
-                    g.dev.copy_(g.host, non_blocking=True)
-                    self._decode_body(g)
-                    g.tokens_host.copy_(g.tokens, non_blocking=True)
+                    self._decode_body(g)  # the staging copy and the token read-back run outside the graph (see launch)
                     g.step.add_(1)
             g.graph = graph
             g.launches = _native.launch_count() - before
@@ -551,17 +585,58 @@ class ModelRunner:
         torch.cuda.synchronize(self.device)
 
     def _run_decode_graph(self, inp: StepInputs) -> list[int]:
+        """One decode step from the bucket's graph.  With ``decode_run_ahead`` the step after this one is launched
+        before the host waits for this one's tokens, whenever it can be predicted: greedy rows only, the same
+        sequences one position later, nobody's next slot in a new page.  Its input ids are the tokens this step
+        samples, copied on the device.  The next call takes the launch over if its inputs are the predicted ones
+        (the ids must be the tokens this step returned); otherwise the launch is left to finish unobserved: it wrote
+        one K / V row per sequence at a position past that sequence's end, which nothing reads before it is written
+        again, and every later kernel is ordered after it on the stream."""
         n = inp.num_seqs
         bucket = next(b for b in self.buckets if b >= n)
         greedy = bucket in self.greedy_graphs and not bool((inp.temperatures > 0).any())
         g = (self.greedy_graphs if greedy else self.graphs)[bucket]
         self._last_bucket, self._last_greedy = bucket, greedy
-        with profile_region("runner.cudagraph.copy_inputs"):
-            g.fill(inp)
-        with profile_region("runner.cudagraph.replay"):
-            g.graph.replay()
-            torch.cuda.current_stream().synchronize()
-        return g.tokens_host[:n].tolist()
+        ahead, self._ahead = getattr(self, "_ahead", None), None
+        if ahead is not None and ahead["graph"] is g and self._is_predicted(ahead, inp):
+            k = ahead["k"]
+            self.run_ahead_counters["taken"] += 1
+        else:
+            if ahead is not None:
+                self.run_ahead_counters["discarded"] += 1
+            with profile_region("runner.cudagraph.copy_inputs"):
+                k = g.fill(inp)
+            with profile_region("runner.cudagraph.replay"):
+                g.launch(k, n)
+        all_greedy = not bool((inp.temperatures > 0).any())
+        if self.config.decode_run_ahead and all_greedy and self._next_is_predictable(inp):
+            with profile_region("runner.cudagraph.run_ahead"):
+                k_next = g.fill(inp, ahead=1)
+                g.launch(k_next, n, ids_from_device=True)
+            self._ahead = {"graph": g, "k": k_next, "n": n, "slots": inp.slots + 1, "positions": inp.positions + 1,
+                           "context_lens": inp.context_lens + 1, "block_tables": inp.block_tables}
+        with profile_region("runner.cudagraph.wait"):
+            tokens = g.wait(k, n)
+        if self._ahead is not None:
+            self._ahead["ids"] = tokens
+        return tokens
+
+    def _next_is_predictable(self, inp: StepInputs) -> bool:
+        # the next token of a row goes to slot + 1 unless that is the first slot of a page the scheduler has yet to pick
+        return bool(((inp.slots + 1) % self.page != 0).all()) and bool((inp.slots >= 0).all())
+
+    @staticmethod
+    def _is_predicted(ahead: dict, inp: StepInputs) -> bool:
+        if inp.num_seqs != ahead["n"] or bool((inp.temperatures > 0).any()):
+            return False
+        if inp.input_ids.tolist() != ahead["ids"]:
+            return False
+        if not (torch.equal(inp.slots, ahead["slots"]) and torch.equal(inp.positions, ahead["positions"])
+                and torch.equal(inp.context_lens, ahead["context_lens"])):
+            return False
+        a, b = inp.block_tables, ahead["block_tables"]
+        w = min(a.shape[1], b.shape[1])
+        return bool(torch.equal(a[:, :w], b[:, :w]) and (a[:, w:] < 0).all() and (b[:, w:] < 0).all())
 
     def time_decode_graph(self, steps: int) -> float:
         """Device milliseconds per decode step: CUDA events around ``steps`` back-to-back
@@ -572,7 +647,9 @@ class ModelRunner:
         torch.cuda.synchronize(self.device)
         start.record()
         for _ in range(steps):
+            g.dev.copy_(g.host, non_blocking=True)  # the step's staging copy and token read-back, as in launch()
             g.graph.replay()
+            g.tokens_host.copy_(g.tokens, non_blocking=True)
         end.record()
         torch.cuda.synchronize(self.device)
         return start.elapsed_time(end) / steps
@@ -583,7 +660,8 @@ class ModelRunner:
                 "kv_bytes_per_page": self.config.kv_bytes_per_page(), "kv_mode": self.kv_mode,
                 "launches_per_decode_graph": {str(b): getattr(g, "launches", 0) for b, g in self.graphs.items()},
                 "staging_bytes": {str(b): g.nbytes for b, g in self.graphs.items()},
-                "weight_bytes": self.model.weight_bytes(), "kv_sizing": getattr(self, "kv_sizing", None)}
+                "weight_bytes": self.model.weight_bytes(), "kv_sizing": getattr(self, "kv_sizing", None),
+                "decode_run_ahead": dict(self.run_ahead_counters)}
 
     def barrier(self) -> None:
         if self.on_cuda:

@@ -133,6 +133,31 @@ def test_cooperative_layer_quanta_interleave_with_graph_decode(tiny):
     assert outs[True] == outs[False]
 
 
+def test_decode_run_ahead_gives_the_same_tokens(tiny):
+    """Greedy decode with the next graph launched before this step's tokens are read: same tokens as without, most
+    steps taken over from the launch that ran ahead (page boundaries, the first step and the batch changes are not),
+    sampled rows never run ahead."""
+    arch, weights, _ = tiny
+    prompts = [torch.randint(0, 1000, (n,), generator=torch.Generator().manual_seed(n)).tolist() for n in (9, 33)]
+    outs, meta = {}, {}
+    for ahead in (False, True):
+        llm = LLM("random:tiny", weights=weights, max_model_len=512, kvcache_block_size=16, num_kvcache_blocks=64,
+                  execution_backend="cuda_graph", compression_mode="scaled_fp8_kv", max_num_seqs=8, cpu_kv_cache_ratio=0.0,
+                  enable_decode_run_ahead=ahead)
+        # 41 tokens: the last decode step's rows sit at offsets 0 and 8 of their 16-token pages, so a launch runs ahead
+        # of it and is left unobserved when the sequences finish
+        outs[ahead] = [o["token_ids"] for o in llm.generate(prompts, SamplingParams(temperature=0.0, max_tokens=41, ignore_eos=True))]
+        sampled = llm.generate([prompts[0]], SamplingParams(temperature=0.8, max_tokens=8, ignore_eos=True))
+        assert len(sampled[0]["token_ids"]) == 8
+        meta[ahead] = llm.graph_metadata()["decode_run_ahead"]
+        torch.cuda.synchronize()
+        native.check_status()
+        llm.exit()
+    assert outs[True] == outs[False]
+    assert meta[False] == {"taken": 0, "discarded": 0}
+    assert meta[True]["taken"] >= 25 and meta[True]["discarded"] >= 1
+
+
 def test_prefix_hit_and_compaction_on_gpu(tiny):
     arch, weights, _ = tiny
     llm = LLM("random:tiny", weights=weights, max_model_len=512, kvcache_block_size=16, num_kvcache_blocks=64,
