@@ -10,8 +10,9 @@ back-to-back launches of the engine's own decode graph (staging copy, 36 layers,
 sampler, token copy-back), max over ranks.  A step streams ~15 GB of weights, far more than
 the 126 MB L2, so no flush is needed between steps.
 ``e2e``: the same K steps through the public API (``LLM.step_result``): host scheduling,
-filling the pinned staging buffer, the host-to-device copy inside the graph, the
-device-to-host token read, per step.  ``first_tokens`` / ``first_tokens_sha1``: the first eight
+filling the pinned staging buffer, the host-to-device copy of the step's inputs, the
+device-to-host token read, per step (on one GPU the engine launches the next greedy step before
+it waits for the current one, so host work overlaps device work).  ``first_tokens`` / ``first_tokens_sha1``: the first eight
 generated token ids of the request, so that runs at different N can be compared by eye.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
