@@ -122,7 +122,9 @@ class LLMEngine:
         self._cooperative_pending = False
         self._pending_prefill = None          # executor handle of a prefill whose layers run in quanta
         self._deferred: list[StepResult] = []  # results produced outside step_result (a pending prefill drained by a cancel)
-        self.cooperative_counters = {"vision_quanta": 0, "layer_quantum_prefills": 0, "layer_quanta": 0, "decode_steps_between_quanta": 0}
+        self._decode_after_interrupt = False
+        self.cooperative_counters = {"vision_quanta": 0, "layer_quantum_prefills": 0, "layer_quanta": 0, "decode_steps_between_quanta": 0,
+                                     "slo_prefill_interruptions": 0, "slo_pending_deadline_finishes": 0, "slo_deadline_atomic_prefills": 0}
         self._steps_since_status = 0
         atexit.register(self.exit)
 
@@ -290,6 +292,10 @@ class LLMEngine:
                     self.scheduler.consecutive_prefill_batches = self.scheduler.policy.max_consecutive_prefill
                     return StepResult(Phase.IDLE)
             self._cooperative_pending = False
+            if cooperative and not self.executor.attention_strategy and self._slo_due(plan.seqs):
+                # a request of the plan has used up its time-to-first-token slack: no yielding to decode steps
+                self.cooperative_counters["slo_deadline_atomic_prefills"] += 1
+                cooperative = False
             if cooperative and not self.executor.attention_strategy:
                 # layer quanta: the prefill's embedding now, its decoder layers a few at a time with a decode step
                 # of the running sequences after every quantum (reference engine/llm_engine.py:1040-1103)
@@ -338,7 +344,51 @@ class LLMEngine:
         self.cooperative_counters["layer_quanta"] += handle["quanta"]
         return self._commit(handle["plan"], result)
 
+    # ---- service-level side (SLO-aware policy; reference engine/llm_engine.py:870-912, 1040-1077) --------------
+    def _release_ns(self, seq) -> int | None:
+        """When a request's prefill has to run without further delay: its time-to-first-token deadline minus the
+        reserve of its cost tier.  None without a deadline or without the SLO-aware policy."""
+        policy = self.scheduler.policy
+        if seq.deadline_ns is None or not hasattr(policy, "reserve_ns"):
+            return None
+        return seq.deadline_ns - policy.reserve_ns(seq)
+
+    def _slo_due(self, seqs) -> bool:
+        now = self.scheduler.clock_ns()
+        return any(r is not None and now >= r for r in map(self._release_ns, seqs))
+
+    def _slo_interrupt_tier(self) -> int | None:
+        """The cost tier an interrupting prefill may admit up to, when a waiting request that is cheaper than
+        everything in the pending prefill has reached its release time."""
+        policy = self.scheduler.policy
+        if not hasattr(policy, "cost_tier"):
+            return None
+        pending_tier = min(policy.cost_tier(s) for s in self._pending_prefill["plan"].seqs)
+        if pending_tier <= 0:
+            return None
+        now = self.scheduler.clock_ns()
+        for seq in self.scheduler.waiting:
+            release = self._release_ns(seq)
+            if policy.cost_tier(seq) < pending_tier and release is not None and now >= release:
+                return pending_tier - 1
+        return None
+
     def _continue_pending_prefill(self) -> StepResult:
+        if self._decode_after_interrupt:  # the running sequences get their step before the next decision
+            self._decode_after_interrupt = False
+            if self.scheduler.num_decoding > 0:
+                return self._decode_between_quanta()
+        tier = self._slo_interrupt_tier()
+        if tier is not None:
+            with profile_region("engine.scheduler.schedule", cuda=False):
+                plan = self.scheduler.schedule_prefill(max_cost_tier=tier)
+            if plan is not None:
+                self.cooperative_counters["slo_prefill_interruptions"] += 1
+                self._decode_after_interrupt = True
+                return self._run_plan(plan)
+        if self._slo_due(self._pending_prefill["plan"].seqs):
+            self.cooperative_counters["slo_pending_deadline_finishes"] += 1
+            return self._finish_pending_prefill()
         if self.scheduler.num_decoding == 0:  # nothing left to protect: run the rest in one piece
             return self._finish_pending_prefill()
         done = self.executor.advance_prefill(self._pending_prefill, self.config.cooperative_prefill_layer_quantum)

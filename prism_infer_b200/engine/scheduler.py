@@ -122,13 +122,29 @@ class Scheduler:
         self.policy.order_waiting(items, self.clock_ns())
         self.waiting = deque(items)
 
-    def schedule_prefill(self) -> BatchPlan | None:
-        return self._prefill_plan([s for s in self.running if s.state is RequestState.PREFILLING])
+    def schedule_prefill(self, *, max_cost_tier: int | None = None) -> BatchPlan | None:
+        """A prefill plan now.  With ``max_cost_tier`` (SLO-aware policy) only waiting requests of that cost tier or
+        a cheaper one are admitted and nothing that is already prefilling is continued: the plan that interrupts a
+        pending, more expensive prefill."""
+        if max_cost_tier is None:
+            return self._prefill_plan([s for s in self.running if s.state is RequestState.PREFILLING])
+        tier = getattr(self.policy, "cost_tier", None)
+        if tier is None:
+            return None
+        self._order_waiting()
+        items = list(self.waiting)  # eligible requests first, both groups in policy order
+        self.waiting = deque([s for s in items if tier(s) <= max_cost_tier] + [s for s in items if tier(s) > max_cost_tier])
+        plan = self._prefill_plan([], max_cost_tier=max_cost_tier)
+        self._order_waiting()
+        if plan is not None:
+            self.counters["prefill_batches"] += 1
+            self.policy.on_prefill_batch(plan.seqs)
+        return plan
 
     def schedule_decode(self) -> BatchPlan | None:
         return self._decode_plan()
 
-    def _prefill_plan(self, prefilling: list[Sequence]) -> BatchPlan | None:
+    def _prefill_plan(self, prefilling: list[Sequence], *, max_cost_tier: int | None = None) -> BatchPlan | None:
         budget = self.max_num_batched_tokens
         patches_left = self.max_vision_patches
         seqs: list[Sequence] = []
@@ -162,6 +178,8 @@ class Scheduler:
             try_add(seq)
         while self.waiting and budget > 0 and len(self.running) < self.max_num_seqs:
             seq = self.waiting[0]
+            if max_cost_tier is not None and self.policy.cost_tier(seq) > max_cost_tier:
+                break
             if not self.policy.may_admit(self, seq) or not self.block_manager.can_allocate(seq):
                 break
             try:

@@ -187,6 +187,112 @@ def test_cancelling_a_request_whose_prefill_is_pending_drains_the_prefill_first(
     llm.exit()
 
 
+def _slo_engine(weights, now):
+    llm = _llm(weights, enable_cooperative_prefill=True, cooperative_prefill_layer_quantum=1, scheduler_policy="slo_aware",
+               num_kvcache_blocks=96)
+    llm.scheduler.clock_ns = lambda: now[0]
+    return llm
+
+
+def _drain(llm, done):
+    while not llm.is_finished():
+        for o in llm.step_result().outputs:
+            if o.finished:
+                done[o.request_id] = list(o.token_ids)
+
+
+def test_a_due_cheaper_request_interrupts_a_pending_prefill(tiny):
+    """SLO-aware policy: while a long prompt (cost tier 1) is prefilling by layer quanta, a short prompt (tier 0)
+    whose release time has come gets its whole prefill at once; the running sequence decodes next, then the long
+    prompt's quanta go on.  Every request's tokens equal the oracle's."""
+    arch, weights, oracle = tiny
+    now = [1_000_000_000]
+    llm = _slo_engine(weights, now)
+    first = [3, 4, 5, 6, 7]
+    a_id = llm.add_request(first, SamplingParams(temperature=0.0, max_tokens=12, ignore_eos=True))
+    while llm.scheduler.num_decoding == 0:
+        llm.step_result()
+    g = torch.Generator().manual_seed(7)
+    long = torch.randint(0, 1000, (300,), generator=g).tolist()
+    b_id = llm.add_request(long, SamplingParams(temperature=0.0, max_tokens=3, ignore_eos=True))
+    done = {}
+    for _ in range(4):
+        for o in llm.step_result().outputs:
+            if o.finished:
+                done[o.request_id] = list(o.token_ids)
+        if llm._pending_prefill is not None:
+            break
+    assert llm._pending_prefill is not None and llm.scheduler.policy.cost_tier(llm._sequences[b_id]) == 1
+    short = [9, 8, 7, 6]
+    c_id = llm.add_request(short, SamplingParams(temperature=0.0, max_tokens=4, ignore_eos=True))
+    seq_c = llm._sequences[c_id]
+    seq_c.deadline_ns = now[0] + 200_000_000  # release in 80 ms (tier 0 reserves 120 ms): not due yet
+    quanta_before = llm.cooperative_counters["decode_steps_between_quanta"]
+    res = llm.step_result()
+    assert llm.cooperative_counters["slo_prefill_interruptions"] == 0 and res.phase.value == "decode"
+    now[0] += 100_000_000  # past the release time
+    res = llm.step_result()
+    assert res.phase.value == "prefill" and llm.cooperative_counters["slo_prefill_interruptions"] == 1
+    assert llm.request_state(c_id).value == "decoding" and llm.request_state(b_id).value == "prefilling"
+    assert llm._pending_prefill is not None
+    res = llm.step_result()  # the sequences that were running decode before anything else
+    assert res.phase.value == "decode" and llm.cooperative_counters["decode_steps_between_quanta"] == quanta_before + 2
+    _drain(llm, done)
+    assert done[a_id] == oracle.generate_greedy(first, 12)
+    assert done[b_id] == oracle.generate_greedy(long, 3)
+    assert done[c_id] == oracle.generate_greedy(short, 4)
+    assert llm.cooperative_counters["slo_prefill_interruptions"] == 1
+    llm.exit()
+
+
+def test_a_pending_prefill_whose_own_release_time_passes_finishes_in_one_piece(tiny):
+    arch, weights, oracle = tiny
+    now = [5_000_000_000]
+    llm = _slo_engine(weights, now)
+    first = [3, 4, 5, 6, 7]
+    a_id = llm.add_request(first, SamplingParams(temperature=0.0, max_tokens=10, ignore_eos=True))
+    while llm.scheduler.num_decoding == 0:
+        llm.step_result()
+    late = list(range(40, 71))
+    b_id = llm.add_request(late, SamplingParams(temperature=0.0, max_tokens=4, ignore_eos=True))
+    llm._sequences[b_id].deadline_ns = now[0] + 1_000_000_000
+    done = {}
+    for _ in range(4):
+        for o in llm.step_result().outputs:
+            if o.finished:
+                done[o.request_id] = list(o.token_ids)
+        if llm._pending_prefill is not None:
+            break
+    assert llm._pending_prefill is not None and llm.cooperative_counters["slo_deadline_atomic_prefills"] == 0
+    now[0] += 900_000_000  # 100 ms before the deadline: inside the 120 ms reserve
+    res = llm.step_result()
+    c = llm.cooperative_counters
+    assert res.phase.value == "prefill" and llm._pending_prefill is None and c["slo_pending_deadline_finishes"] == 1
+    assert c["layer_quanta"] == 0  # no layer had run as a quantum: all of them ran in the finishing step
+    _drain(llm, done)
+    assert done[a_id] == oracle.generate_greedy(first, 10) and done[b_id] == oracle.generate_greedy(late, 4)
+    llm.exit()
+
+
+def test_a_prefill_that_is_already_due_does_not_yield_to_decode_steps(tiny):
+    arch, weights, oracle = tiny
+    now = [5_000_000_000]
+    llm = _slo_engine(weights, now)
+    first = [3, 4, 5, 6, 7]
+    a_id = llm.add_request(first, SamplingParams(temperature=0.0, max_tokens=8, ignore_eos=True))
+    while llm.scheduler.num_decoding == 0:
+        llm.step_result()
+    late = list(range(40, 71))
+    b_id = llm.add_request(late, SamplingParams(temperature=0.0, max_tokens=4, ignore_eos=True))
+    llm._sequences[b_id].deadline_ns = now[0] + 50_000_000
+    done = {}
+    _drain(llm, done)
+    c = llm.cooperative_counters
+    assert c["slo_deadline_atomic_prefills"] == 1 and c["layer_quantum_prefills"] == 0
+    assert done[a_id] == oracle.generate_greedy(first, 8) and done[b_id] == oracle.generate_greedy(late, 4)
+    llm.exit()
+
+
 def test_visual_compaction_frees_pages_and_hits(tiny):
     arch, weights, _ = tiny
     img = _image(4)
