@@ -68,7 +68,30 @@ def main() -> None:
         bt = torch.arange(nblk, dtype=torch.int32, device=dev).view(1, -1)
         kvl = torch.tensor([T], dtype=torch.int32, device=dev)
         ms = timeit(lambda: ops.paged_prefill_attention(q, cache, 0, cu, kvl, bt, T), args.iters, flush)
-        print(json.dumps({"case": f"text causal scaled-FP8 pages T={T}", "ms": round(ms, 4), "tflops": round(flops / ms / 1e9, 1)}), flush=True)
+        print(json.dumps({"case": f"text causal scaled-FP8 pages T={T}, page-reading mma.sync kernel", "ms": round(ms, 4),
+                          "tflops": round(flops / ms / 1e9, 1)}), flush=True)
+        kw = dict(cu_seqlens_kv=cu, total_kv=T, max_kv_len=T)
+        ms = timeit(lambda: ops.paged_prefill_attention(q, cache, 0, cu, kvl, bt, T, **kw), args.iters, flush)
+        print(json.dumps({"case": f"text causal scaled-FP8 pages T={T}, gather + tcgen05 kernel", "ms": round(ms, 4),
+                          "tflops": round(flops / ms / 1e9, 1)}), flush=True)
+    # a 2048-token chunk over a 14336-token history (chunked prefill of a long video), scaled-FP8 pages
+    Hq, Hkv, D, page, Tq, hist = 32, 8, 128, 256, 2048, 14336
+    Tk = hist + Tq
+    q = rnd(Tq, Hq, D)
+    nblk = Tk // page
+    cache = ops.KVCache(1, nblk, Hkv, page, D, ops.KV_FP8_SCALED, dev)
+    for lo in range(0, Tk, 4096):
+        n = min(4096, Tk - lo)
+        ops.store_kv(rnd(n, Hkv, D), rnd(n, Hkv, D), torch.arange(lo, lo + n, dtype=torch.int64, device=dev), cache, 0)
+    bt = torch.arange(nblk, dtype=torch.int32, device=dev).view(1, -1)
+    cu = torch.tensor([0, Tq], dtype=torch.int32, device=dev)
+    cu_kv = torch.tensor([0, Tk], dtype=torch.int32, device=dev)
+    kvl = torch.tensor([Tk], dtype=torch.int32, device=dev)
+    flops = 4.0 * D * Hq * (Tq * hist + Tq * Tq / 2)
+    for name, kw in (("page-reading mma.sync kernel", {}), ("gather + tcgen05 kernel", dict(cu_seqlens_kv=cu_kv, total_kv=Tk, max_kv_len=Tk))):
+        ms = timeit(lambda: ops.paged_prefill_attention(q, cache, 0, cu, kvl, bt, Tq, **kw), args.iters, flush)
+        print(json.dumps({"case": f"chunk {Tq} over history {hist}, scaled-FP8 pages, {name}", "ms": round(ms, 4),
+                          "tflops": round(flops / ms / 1e9, 1)}), flush=True)
     n_img, seg, H, hd = 8, 784, 16, 72
     N = n_img * seg
     qkv = rnd(N, 3 * H * hd)

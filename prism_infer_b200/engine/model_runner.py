@@ -476,6 +476,10 @@ class ModelRunner:
                 is_prefill=True, block_tables=self._to_dev(inp.block_tables), slots=self._to_dev(inp.slots),
                 cu_seqlens_q=self._to_dev(inp.cu_seqlens_q), kv_lens=self._to_dev(inp.kv_lens), max_q_len=inp.max_q_len,
                 no_history=bool(torch.equal(inp.kv_lens, inp.cu_seqlens_q[1:] - inp.cu_seqlens_q[:-1])))
+            if not meta.no_history:  # key ranges for the gather + tensor-core attention over the paged cache
+                cu_kv = torch.zeros(inp.kv_lens.shape[0] + 1, dtype=torch.int32)
+                cu_kv[1:] = torch.cumsum(inp.kv_lens, 0)
+                meta.cu_seqlens_kv, meta.total_kv, meta.max_kv_len = self._to_dev(cu_kv), int(cu_kv[-1]), int(inp.kv_lens.max())
             ids, pos, vis_index = self._to_dev(inp.input_ids), self._to_dev(inp.positions), self._to_dev(inp.vis_index)
             if inp.score_rows:
                 from .visual_pruning import RuntimeVisualTokenScorer

@@ -44,6 +44,9 @@ class AttnMeta:
     # prefill
     cu_seqlens_q: Optional[torch.Tensor] = None    # [S+1] int32
     kv_lens: Optional[torch.Tensor] = None         # [S] int32 keys visible (history + chunk)
+    cu_seqlens_kv: Optional[torch.Tensor] = None   # [S+1] int32 running sum of kv_lens (None: the page-reading kernel)
+    total_kv: int = 0                              # sum and maximum of kv_lens, known on the host
+    max_kv_len: int = 0
     max_q_len: int = 0
     last_rows: Optional[torch.Tensor] = None       # [S] int64 row of each sequence's last token
     no_history: bool = False                       # every sequence attends only to this chunk's own keys
@@ -552,7 +555,8 @@ class Qwen3VLModel:
                 a = ops.varlen_attention(q, heads[:, self.Hq:self.Hq + self.Hkv], heads[:, self.Hq + self.Hkv:],
                                          meta.cu_seqlens_q, meta.max_q_len, causal=True)
             elif meta.is_prefill:
-                a = ops.paged_prefill_attention(q, cache, i, meta.cu_seqlens_q, meta.kv_lens, meta.block_tables, meta.max_q_len)
+                a = ops.paged_prefill_attention(q, cache, i, meta.cu_seqlens_q, meta.kv_lens, meta.block_tables, meta.max_q_len,
+                                                cu_seqlens_kv=meta.cu_seqlens_kv, total_kv=meta.total_kv, max_kv_len=meta.max_kv_len)
             else:
                 a = ops.paged_decode_attention(q, cache, i, meta.block_tables, meta.context_lens, nsplit=meta.nsplit,
                                                workspace=meta.workspace)
@@ -628,7 +632,8 @@ class Qwen3VLModel:
                 a = ops.varlen_attention(q, heads[:, self.Hq:self.Hq + self.Hkv], heads[:, self.Hq + self.Hkv:],
                                          meta.cu_seqlens_q, meta.max_q_len, causal=True)
             else:
-                a = ops.paged_prefill_attention(q, cache, i, meta.cu_seqlens_q, meta.kv_lens, meta.block_tables, meta.max_q_len)
+                a = ops.paged_prefill_attention(q, cache, i, meta.cu_seqlens_q, meta.kv_lens, meta.block_tables, meta.max_q_len,
+                                                cu_seqlens_kv=meta.cu_seqlens_kv, total_kv=meta.total_kv, max_kv_len=meta.max_kv_len)
             ticket = comm.scatter_linear(a.view(T, self.Hq * self.D), l.o)
             h, residual = comm.reduce_norm_allgather(ticket, l.post_norm, t.rms_norm_eps, residual, residual_is_shard=shard)
             shard = True

@@ -171,6 +171,9 @@ DECODE_MMA_MIN_BATCH = 1
 O_PROJ_STAGES = 0
 # tcgen05 attention for contiguous bf16 K / V (prefill without history, the vision tower)
 ATTN_TC_ENABLED = True
+# prefill over the paged cache (chunked prefill, prefix hits) at head dimension 128: gather the visible keys from
+# their pages once per layer, then the same tcgen05 kernel (False: the mma.sync kernel that reads the pages itself)
+PAGED_PREFILL_TC_ENABLED = True
 # prefill GEMMs of at least this many tokens run the persistent form, tokens on the TMEM lanes
 PERSISTENT_ROWMAJOR = True
 PERSISTENT_MIN_TOKENS = 512
@@ -598,15 +601,35 @@ def varlen_attention(
     return out
 
 
+_GATHERED_KV: dict = {}  # device -> (rows, width, K rows, V rows): the gathered keys of the layer under way
+
+
+def _gathered_kv_rows(device: torch.device, rows: int, width: int) -> tuple[torch.Tensor, torch.Tensor]:
+    """Scratch for the keys and values that ``paged_prefill_attention`` gathers from their pages; one pair per
+    device, reused by every layer (launches of one stream run in order), grown in steps of 4096 rows."""
+    have = _GATHERED_KV.get(device)
+    if have is None or have[0] < rows or have[1] != width:
+        cap = -(-rows // 4096) * 4096
+        have = (cap, width, torch.empty((cap, width), dtype=torch.bfloat16, device=device),
+                torch.empty((cap, width), dtype=torch.bfloat16, device=device))
+        _GATHERED_KV[device] = have
+    return have[2], have[3]
+
+
 def paged_prefill_attention(
     q: torch.Tensor, cache: KVCache, layer: int, cu_seqlens_q: torch.Tensor, kv_lens: torch.Tensor,
     block_tables: torch.Tensor, max_q_len: int, *, out: Optional[torch.Tensor] = None,
+    cu_seqlens_kv: Optional[torch.Tensor] = None, total_kv: int = 0, max_kv_len: int = 0,
 ) -> torch.Tensor:
     """Causal attention of the new tokens ``q [T, Hq, D]`` over the paged cache.
 
     Sequence ``s`` owns rows ``cu_seqlens_q[s]:cu_seqlens_q[s+1]``; it sees ``kv_lens[s]``
     cached keys (history, shared prefix pages and this chunk, already stored), the last
     ``q_len`` of which are the chunk itself.
+
+    With ``cu_seqlens_kv`` (``[S+1]`` int32, the running sum of ``kv_lens``), ``total_kv`` and ``max_kv_len``
+    (host integers) and head dimension 128, the keys are gathered from their pages once and the tcgen05 kernel
+    runs over them; without them the mma.sync kernel reads the pages itself.
     """
     T, Hq, D = q.shape
     scale = 1.0 / math.sqrt(D)
@@ -635,6 +658,18 @@ def paged_prefill_attention(
         out = torch.empty((T, Hq, D), dtype=torch.bfloat16, device=q.device)
     assert q.stride(2) == 1 and q.stride(1) == D
     assert cu_seqlens_q.dtype == torch.int32 and kv_lens.dtype == torch.int32 and block_tables.dtype == torch.int32
+    if (ATTN_TC_ENABLED and PAGED_PREFILL_TC_ENABLED and D == 128 and cu_seqlens_kv is not None and total_kv > 0
+            and q.stride(0) % 8 == 0 and (q.data_ptr() | out.data_ptr()) % 16 == 0):
+        assert cu_seqlens_kv.dtype == torch.int32 and cu_seqlens_kv.shape == cu_seqlens_q.shape and max_kv_len <= total_kv
+        k_rows, v_rows = _gathered_kv_rows(q.device, total_kv, cache.num_kv_heads * D)
+        native.call(
+            "prism_paged_prefill_tc", _p(q), q.stride(0), _p(out), out.stride(0), _p(cu_seqlens_q), _p(cu_seqlens_kv),
+            _p(cache.k(layer)), _p(cache.v(layer)), _p(cache.k_scale(layer)), _p(cache.v_scale(layer)), _p(block_tables),
+            block_tables.shape[1], cache.num_blocks, cache.page, _p(k_rows), _p(v_rows), T, int(total_kv),
+            cu_seqlens_q.shape[0] - 1, int(max_q_len), int(max_kv_len), Hq, cache.num_kv_heads, D, cache.mode, scale,
+            _s(), _pdl(),
+        )
+        return out
     native.call(
         "prism_flash_attention", _p(q), q.stride(0), _p(out), out.stride(0), _p(cu_seqlens_q), None, None, 0,
         _p(cache.k(layer)), _p(cache.v(layer)), _p(cache.k_scale(layer)), _p(cache.v_scale(layer)),

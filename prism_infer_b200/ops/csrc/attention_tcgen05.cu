@@ -17,6 +17,14 @@
 // (common.cuh: mbar_wait); on a timeout the status word is set, roles unwind and the CTA
 // frees its TMEM.  Replaces the reference's flash-attn / SDPA calls for prefill without
 // history (prism_infer/layers/attention.py:180-250).
+//
+// Prefill over the paged cache (chunked prefill, prefix hits; reference
+// prism_infer/ops/paged_attention_reference.py:185-390): the keys a step can see are first
+// gathered from their pages into contiguous bf16 rows (gather_pages_kernel: E4M3 payload times
+// the row scale, or a plain copy of bf16 pages), once per layer and KV head, and the same
+// tensor-core kernel then runs with its own key ranges (cu_kv): query row r of a sequence sees
+// keys 0 .. kv_len - q_len + r.  A key is dequantised once instead of once per query tile and
+// query head of its group, and the gathered rows (a few MB) stay in L2 for the TMA loads.
 #include "common.cuh"
 
 PRISM_DEFINE_TU_STATUS(attn_tc)
@@ -37,6 +45,7 @@ constexpr int TMEM_O = 128;                     // O accumulator, 128 columns
 
 struct FaArgs {
   const int* cu_q;        // [S + 1] row offsets of the sequences
+  const int* cu_kv;       // [S + 1] row offsets of the sequences' keys in K / V; null: the query rows' own
   __nv_bfloat16* out;     // [T][Hq * hd]
   long long o_stride;
   int Hq, Hkv;
@@ -122,12 +131,15 @@ flash_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
 
   const int q_start = a.cu_q[seq];
   const int q_len = a.cu_q[seq + 1] - q_start;
+  const int kv_start = a.cu_kv ? a.cu_kv[seq] : q_start;
+  const int kv_len = a.cu_kv ? max(a.cu_kv[seq + 1] - kv_start, q_len) : q_len;
+  const int pos_off = kv_len - q_len;  // key position of the sequence's first query row
   const int q0 = qt * FA_BM;
   const bool live = q0 < q_len;  // uniform over the CTA
   int n_tiles = 0;
   if (live) {
-    int kv_end = q_len;
-    if (a.causal) kv_end = min(q_len, q0 + FA_BM);
+    int kv_end = kv_len;
+    if (a.causal) kv_end = min(kv_len, pos_off + q0 + FA_BM);
     n_tiles = (kv_end + FA_BN - 1) / FA_BN;
   }
 
@@ -146,7 +158,7 @@ flash_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
           if (!ok) break;
         }
         uint8_t* st = ring + (size_t)s * STAGE_BYTES;
-        const int row = q_start + j * FA_BN;
+        const int row = kv_start + j * FA_BN;
         mbar_expect_tx(&kv_full[s], STAGE_BYTES);
         tma_load_3d(st, &tmK, &kv_full[s], 0, kvh, row);
         tma_load_3d(st + K_BYTES / 2, &tmK, &kv_full[s], 64, kvh, row);
@@ -221,6 +233,7 @@ flash_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     const int half = (warp - 2) >> 2;
     const int r_local = q * 32 + lane;      // row inside the tile
     const int row = q0 + r_local;           // query row (local index of the sequence)
+    const int last_key = pos_off + row;     // last key position this row sees under the causal mask
     const uint32_t lane_addr = tmem_base + ((uint32_t)(q * 32) << 16);
     const float sl2 = a.scale * 1.4426950408889634f;
     constexpr int HC = FA_BN / 2;           // keys per thread and tile
@@ -249,10 +262,10 @@ flash_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         }
 #pragma unroll
         for (int i = 0; i < HC; ++i) s[i] = __uint_as_float(r[i]) * sl2;
-        if (j0 + HC > q_len || (a.causal && j0 + HC - 1 > row)) {
+        if (j0 + HC > kv_len || (a.causal && j0 + HC - 1 > last_key)) {
 #pragma unroll
           for (int i = 0; i < HC; ++i)
-            if (j0 + i >= q_len || (a.causal && j0 + i > row)) s[i] = -INFINITY;
+            if (j0 + i >= kv_len || (a.causal && j0 + i > last_key)) s[i] = -INFINITY;
         }
 #pragma unroll
         for (int i = 0; i < HC; ++i) mx = fmaxf(mx, s[i]);
@@ -337,16 +350,90 @@ flash_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   if (warp == 1) tmem_dealloc(tmem_base, 256);
 }
 
+// ---------------------------------------------------------------------------------------------
+// Pages -> contiguous bf16 key / value rows.  Cache layout: payload [blocks][Hkv][page][D]
+// (E4M3 bytes or bf16), scales [blocks][Hkv][page] (null: unit scale).  One warp per key row,
+// looping over the KV heads; lane l converts elements 4l .. 4l+3 of K and of V.  A hole in the
+// page table or a page id beyond the cache gives zero rows (the latter is also recorded in the
+// status word), a key range that the table cannot describe is cut short and recorded.
+// ---------------------------------------------------------------------------------------------
+struct GatherArgs {
+  const void* k_cache;
+  const void* v_cache;
+  const float* k_scale;
+  const float* v_scale;
+  const int* block_tables;  // [S][max_blocks]
+  const int* cu_kv;         // [S + 1]
+  __nv_bfloat16* k_out;     // [Tkv][Hkv * 128]
+  __nv_bfloat16* v_out;
+  int max_blocks, num_blocks, page, Hkv, Tkv;
+};
+
+constexpr int GATHER_ROWS = 8;  // key rows (warps) per CTA
+
+__device__ __forceinline__ uint2 e4m3x4_to_bf16x4(uint32_t bytes, float scale) {
+  const __half2_raw lo = __nv_cvt_fp8x2_to_halfraw2((__nv_fp8x2_storage_t)(bytes & 0xffffu), __NV_E4M3);
+  const __half2_raw hi = __nv_cvt_fp8x2_to_halfraw2((__nv_fp8x2_storage_t)(bytes >> 16), __NV_E4M3);
+  const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&lo));
+  const float2 b = __half22float2(*reinterpret_cast<const __half2*>(&hi));
+  __nv_bfloat162 p = __floats2bfloat162_rn(a.x * scale, a.y * scale);
+  __nv_bfloat162 q = __floats2bfloat162_rn(b.x * scale, b.y * scale);
+  return make_uint2(*reinterpret_cast<uint32_t*>(&p), *reinterpret_cast<uint32_t*>(&q));
+}
+
+template <bool KV8>
+__global__ void __launch_bounds__(GATHER_ROWS * 32) gather_pages_kernel(const GatherArgs a) {
+  const int seq = blockIdx.y, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  pdl_launch_dependents();
+  pdl_wait();
+  const int kv_start = a.cu_kv[seq];
+  int kv_len = a.cu_kv[seq + 1] - kv_start;
+  const long long reach = (long long)a.max_blocks * a.page;
+  if ((long long)kv_len > reach) {
+    if (threadIdx.x == 0 && blockIdx.x == 0) prism_report(PRISM_ERR_BOUNDS, 1);
+    kv_len = (int)reach;
+  }
+  const int j = blockIdx.x * GATHER_ROWS + warp;
+  if (j >= kv_len) return;
+  const long long dst_row = (long long)kv_start + j;
+  if (dst_row < 0 || dst_row >= a.Tkv) {  // offsets that do not fit the output: record, write nothing
+    if (lane == 0) prism_report(PRISM_ERR_BOUNDS, 3);
+    return;
+  }
+  int blk = a.block_tables[(size_t)seq * a.max_blocks + j / a.page];
+  if (a.num_blocks > 0 && blk >= a.num_blocks) {
+    if (lane == 0) prism_report(PRISM_ERR_BOUNDS, 2);
+    blk = -1;
+  }
+  for (int h = 0; h < a.Hkv; ++h) {
+    uint2 kb = make_uint2(0u, 0u), vb = make_uint2(0u, 0u);
+    if (blk >= 0) {
+      const size_t row = ((size_t)blk * a.Hkv + h) * a.page + (j % a.page);
+      if constexpr (KV8) {
+        const uint32_t k4 = reinterpret_cast<const uint32_t*>(reinterpret_cast<const uint8_t*>(a.k_cache) + row * FA_HD)[lane];
+        const uint32_t v4 = reinterpret_cast<const uint32_t*>(reinterpret_cast<const uint8_t*>(a.v_cache) + row * FA_HD)[lane];
+        kb = e4m3x4_to_bf16x4(k4, a.k_scale ? a.k_scale[row] : 1.0f);
+        vb = e4m3x4_to_bf16x4(v4, a.v_scale ? a.v_scale[row] : 1.0f);
+      } else {
+        kb = reinterpret_cast<const uint2*>(reinterpret_cast<const __nv_bfloat16*>(a.k_cache) + row * FA_HD)[lane];
+        vb = reinterpret_cast<const uint2*>(reinterpret_cast<const __nv_bfloat16*>(a.v_cache) + row * FA_HD)[lane];
+      }
+    }
+    const size_t o = ((size_t)dst_row * a.Hkv + h) * FA_HD;
+    reinterpret_cast<uint2*>(a.k_out + o)[lane] = kb;
+    reinterpret_cast<uint2*>(a.v_out + o)[lane] = vb;
+  }
+}
+
 }  // namespace
 
 // Causal or bidirectional self-attention over contiguous segments, head dimension 128 or 72.
 // q [T][q_stride], k / v [T][kv_stride] bf16 with the heads side by side (views into a packed
 // QKV projection are fine); out [T][o_stride].  Rows and strides must be 16-byte aligned.
-PRISM_API int prism_flash_attention_tc(const void* q, long long q_stride, const void* k, const void* v,
-                                       long long kv_stride, void* out, long long o_stride, const void* cu_q, int T,
-                                       int S, int max_q_len, int Hq, int Hkv, int hd, int causal, float scale,
-                                       void* stream, int pdl) {
-  if (S <= 0 || max_q_len <= 0 || T <= 0) return 0;
+static int flash_tc_impl(const void* q, long long q_stride, const void* k, const void* v, long long kv_stride, void* out,
+                         long long o_stride, const void* cu_q, const void* cu_kv, int T, int Tkv, int S, int max_q_len,
+                         int Hq, int Hkv, int hd, int causal, float scale, void* stream, int pdl) {
+  if (S <= 0 || max_q_len <= 0 || T <= 0 || Tkv <= 0) return 0;
   if (Hq % Hkv) return -1;
   if ((q_stride % 8) || (kv_stride % 8) || (o_stride % 8)) return -2;
   if ((reinterpret_cast<unsigned long long>(q) | reinterpret_cast<unsigned long long>(k) |
@@ -356,12 +443,13 @@ PRISM_API int prism_flash_attention_tc(const void* q, long long q_stride, const 
   CUtensorMap tq, tk, tv;
   int rc = prism_make_head_tensor_map(q, (unsigned long long)T, (unsigned)Hq, (unsigned)hd, (unsigned long long)q_stride, FA_BM, &tq);
   if (rc) return rc;
-  rc = prism_make_head_tensor_map(k, (unsigned long long)T, (unsigned)Hkv, (unsigned)hd, (unsigned long long)kv_stride, FA_BN, &tk);
+  rc = prism_make_head_tensor_map(k, (unsigned long long)Tkv, (unsigned)Hkv, (unsigned)hd, (unsigned long long)kv_stride, FA_BN, &tk);
   if (rc) return rc;
-  rc = prism_make_head_tensor_map(v, (unsigned long long)T, (unsigned)Hkv, (unsigned)hd, (unsigned long long)kv_stride, FA_BN, &tv);
+  rc = prism_make_head_tensor_map(v, (unsigned long long)Tkv, (unsigned)Hkv, (unsigned)hd, (unsigned long long)kv_stride, FA_BN, &tv);
   if (rc) return rc;
   FaArgs a;
   a.cu_q = reinterpret_cast<const int*>(cu_q);
+  a.cu_kv = reinterpret_cast<const int*>(cu_kv);
   a.out = reinterpret_cast<__nv_bfloat16*>(out);
   a.o_stride = o_stride;
   a.Hq = Hq;
@@ -382,4 +470,51 @@ PRISM_API int prism_flash_attention_tc(const void* q, long long q_stride, const 
   if (hd == 128)
     return (int)prism_launch(flash_tc_kernel<128>, dim3(tiles, Hq, S), dim3(FA_THREADS), smem, st, pdl != 0, tq, tk, tv, a);
   return (int)prism_launch(flash_tc_kernel<80>, dim3(tiles, Hq, S), dim3(FA_THREADS), smem, st, pdl != 0, tq, tk, tv, a);
+}
+
+PRISM_API int prism_flash_attention_tc(const void* q, long long q_stride, const void* k, const void* v,
+                                       long long kv_stride, void* out, long long o_stride, const void* cu_q, int T,
+                                       int S, int max_q_len, int Hq, int Hkv, int hd, int causal, float scale,
+                                       void* stream, int pdl) {
+  return flash_tc_impl(q, q_stride, k, v, kv_stride, out, o_stride, cu_q, nullptr, T, T, S, max_q_len, Hq, Hkv, hd, causal,
+                       scale, stream, pdl);
+}
+
+// Causal attention of new tokens over the paged cache, head dimension 128: the keys each sequence
+// sees (cu_kv[s+1] - cu_kv[s] of them: history, shared prefix pages and this chunk, already
+// stored; at least as many as the sequence has query rows) are gathered into k_rows / v_rows
+// [Tkv][Hkv * 128] bf16 and the tensor-core kernel runs over those.  kv_mode: 0 bf16 pages,
+// 1 E4M3 pages with unit scale, 2 E4M3 pages with one scale per key row and head.
+PRISM_API int prism_paged_prefill_tc(const void* q, long long q_stride, void* out, long long o_stride, const void* cu_q,
+                                     const void* cu_kv, const void* k_cache, const void* v_cache, const void* k_scale,
+                                     const void* v_scale, const void* block_tables, int max_blocks, int num_blocks,
+                                     int page, void* k_rows, void* v_rows, int T, int Tkv, int S, int max_q_len,
+                                     int max_kv_len, int Hq, int Hkv, int hd, int kv_mode, float scale, void* stream,
+                                     int pdl) {
+  if (S <= 0 || max_q_len <= 0 || T <= 0) return 0;
+  if (hd != FA_HD) return -4;
+  if (Hq <= 0 || Hkv <= 0 || Hq % Hkv) return -1;
+  if (page <= 0 || max_blocks <= 0 || Tkv <= 0 || max_kv_len <= 0 || max_kv_len > Tkv) return -5;
+  if (!cu_kv || !k_rows || !v_rows || !k_cache || !v_cache || !block_tables) return -6;
+  GatherArgs g;
+  g.k_cache = k_cache;
+  g.v_cache = v_cache;
+  g.k_scale = kv_mode == 2 ? reinterpret_cast<const float*>(k_scale) : nullptr;
+  g.v_scale = kv_mode == 2 ? reinterpret_cast<const float*>(v_scale) : nullptr;
+  g.block_tables = reinterpret_cast<const int*>(block_tables);
+  g.cu_kv = reinterpret_cast<const int*>(cu_kv);
+  g.k_out = reinterpret_cast<__nv_bfloat16*>(k_rows);
+  g.v_out = reinterpret_cast<__nv_bfloat16*>(v_rows);
+  g.max_blocks = max_blocks;
+  g.num_blocks = num_blocks;
+  g.page = page;
+  g.Hkv = Hkv;
+  g.Tkv = Tkv;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  const dim3 grid((max_kv_len + GATHER_ROWS - 1) / GATHER_ROWS, S);
+  cudaError_t e = kv_mode == 0 ? prism_launch(gather_pages_kernel<false>, grid, dim3(GATHER_ROWS * 32), 0, st, pdl != 0, g)
+                               : prism_launch(gather_pages_kernel<true>, grid, dim3(GATHER_ROWS * 32), 0, st, pdl != 0, g);
+  if (e != cudaSuccess) return (int)e;
+  return flash_tc_impl(q, q_stride, k_rows, v_rows, (long long)Hkv * FA_HD, out, o_stride, cu_q, cu_kv, T, Tkv, S, max_q_len,
+                       Hq, Hkv, hd, 1, scale, stream, pdl);
 }

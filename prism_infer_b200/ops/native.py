@@ -51,6 +51,7 @@ _SIGNATURES = {
     "prism_reduce_norm_allgather": "ppliiiiiiplppppfpplpppi",
     "prism_add_rmsnorm_packed": "plippppppiifpipi",
     "prism_flash_attention_tc": "plpplplpiiiiiiifpi",
+    "prism_paged_prefill_tc": "plplpppppppiiippiiiiiiiiifpi",
     "prism_gemm_set_small_tile_smem_cap": "i",
     "prism_gemm_set_persistent_min_tokens": "i",
     "prism_gemm_set_persistent_rowmajor": "i",

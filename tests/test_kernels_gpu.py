@@ -312,6 +312,69 @@ def test_paged_prefill(cuda_device, mode, D, Hq, Hkv, page):
     assert err.max() < 3e-2 and err.mean() < 3e-3, (err.max(), err.mean())
 
 
+def _cu(lens):
+    out = torch.zeros(len(lens) + 1, dtype=torch.int32)
+    out[1:] = torch.tensor(lens, dtype=torch.int32).cumsum(0)
+    return out
+
+
+@pytest.mark.parametrize("mode", [ops.KV_BF16, ops.KV_FP8, ops.KV_FP8_SCALED])
+def test_paged_prefill_gathered_keys_on_the_tensor_cores(cuda_device, mode):
+    """Head dimension 128 with key ranges given: the keys are gathered from their pages and the tcgen05 kernel
+    runs over them.  Against the fp32 oracle, and against the page-reading kernel on the same inputs: a chunk with
+    a long history (several key tiles, query rows past one 128-row tile), a single new token, a sequence without
+    history and one whose history ends inside a page."""
+    D, Hq, Hkv, page, blocks = 128, 8, 2, 256, 24
+    cg, cc = _fill_cache(mode, 1, blocks, Hkv, page, D, seed=61)
+    q_lens = [200, 1, 70, 130]
+    kv = [3 * page + 200, page + 5, 70, 2 * page - 3]
+    kv_lens = torch.tensor(kv, dtype=torch.int32)
+    cu, cu_kv = _cu(q_lens), _cu(kv)
+    maxblk = 6
+    bt = torch.full((4, maxblk), -1, dtype=torch.int32)
+    perm = torch.randperm(blocks, generator=torch.Generator().manual_seed(62))
+    c = 0
+    for s in range(4):
+        n = (kv[s] + page - 1) // page
+        bt[s, :n] = perm[c:c + n].int()
+        c += n
+    T = sum(q_lens)
+    q = rand_bf16(T, Hq, D, seed=63)
+    qg = q.cuda()
+    args = (cg, 0, cu.cuda(), kv_lens.cuda(), bt.cuda(), max(q_lens))
+    yt = ops.paged_prefill_attention(qg, *args, cu_seqlens_kv=cu_kv.cuda(), total_kv=sum(kv), max_kv_len=max(kv))
+    ym = ops.paged_prefill_attention(qg, *args)
+    torch.cuda.synchronize()
+    assert native.read_status()["attn_tc"][0] == 0
+    yc = ops.paged_prefill_attention(q.float(), cc, 0, cu, kv_lens, bt, max(q_lens))
+    err = (yt.float().cpu() - yc).abs()
+    assert err.max() < 3e-2 and err.mean() < 3e-3, (err.max(), err.mean())
+    both = (yt.float() - ym.float()).abs()
+    assert both.max() < 2e-2 and both.mean() < 1e-3, (both.max(), both.mean())
+
+
+def test_paged_prefill_gather_skips_out_of_range_pages_and_reports(cuda_device):
+    """A page id beyond the cache gives zero key rows (as a hole does) and sets the status word; nothing is read
+    out of range."""
+    D, Hq, Hkv, page, blocks = 128, 4, 1, 16, 6
+    cg, _ = _fill_cache(ops.KV_FP8_SCALED, 1, blocks, Hkv, page, D, seed=64)
+    q_lens, kv = [3, 2], [35, 24]
+    cu, cu_kv = _cu(q_lens), _cu(kv)
+    q = rand_bf16(5, Hq, D, seed=65).cuda()
+    kvl = torch.tensor(kv, dtype=torch.int32).cuda()
+    kw = dict(cu_seqlens_kv=cu_kv.cuda(), total_kv=sum(kv), max_kv_len=max(kv))
+    bad = torch.tensor([[0, 9, 2], [3, 1, -1]], dtype=torch.int32)       # 9 >= blocks
+    yb = ops.paged_prefill_attention(q, cg, 0, cu.cuda(), kvl, bad.cuda(), 3, **kw)
+    torch.cuda.synchronize()
+    st = native.read_status()["attn_tc"]
+    assert st[0] == 3, st
+    hole = torch.tensor([[0, -1, 2], [3, 1, -1]], dtype=torch.int32)
+    yh = ops.paged_prefill_attention(q, cg, 0, cu.cuda(), kvl, hole.cuda(), 3, **kw)
+    torch.cuda.synchronize()
+    assert native.read_status()["attn_tc"][0] == 0
+    assert torch.isfinite(yb.float()).all() and torch.equal(yb, yh)
+
+
 def test_kv_copy_and_compaction(cuda_device):
     L, blocks, Hkv, page, D = 3, 10, 2, 16, 64
     cg, cc = _fill_cache(ops.KV_FP8_SCALED, L, blocks, Hkv, page, D, seed=32)
