@@ -89,6 +89,44 @@ def test_production_width_image_prompt_on_gpu(wide, backend, logits_precision):
     llm.exit()
 
 
+def test_production_width_chunked_prefill_and_prefix_hit_on_gpu(wide):
+    """Later chunks of a chunked prefill and a request admitted on a prefix-cache hit attend over the paged cache: at
+    head dimension 128 the keys are gathered from their scaled-FP8 pages and the tcgen05 kernel runs over them.
+    Tokens against the fp32 oracle for both requests."""
+    arch, weights, oracle = wide
+    g = torch.Generator().manual_seed(9)
+    prompt = torch.randint(0, 150000, (300,), generator=g).tolist()
+    longer = prompt + torch.randint(0, 150000, (12,), generator=g).tolist()
+    sp = SamplingParams(temperature=0.0, max_tokens=5, ignore_eos=True)
+    llm = LLM("random:qwen3-vl-8b-2layer", weights=weights, max_model_len=1024, kvcache_block_size=256, num_kvcache_blocks=8,
+              execution_backend="cuda_graph", compression_mode="scaled_fp8_kv", max_num_seqs=2, cpu_kv_cache_ratio=0.0,
+              max_num_batched_tokens=128, max_chunk_size=128)
+    from prism_infer_b200 import ops
+
+    calls = {"tc": 0}
+    plain = ops.native.call
+
+    def counting(name, *a):
+        if name == "prism_paged_prefill_tc":
+            calls["tc"] += 1
+        return plain(name, *a)
+
+    ops.native.call = counting
+    try:
+        for p in (prompt, longer):
+            want, logits = oracle.generate_greedy(p, 5, return_logits=True)
+            got = llm.generate([p], sp)[0]["token_ids"]
+            torch.cuda.synchronize()
+            native.check_status()
+            _agree(got, want, logits, margin=0.3)
+    finally:
+        ops.native.call = plain
+    # first request: chunks two and three of three, two layers each; second request: one prefill over the cached page
+    assert calls["tc"] == 2 * 2 + 2, calls
+    assert llm.metrics_snapshot()["engine"]["requests"][1]["cached_tokens"] == 256
+    llm.exit()
+
+
 def test_graph_decode_equals_eager_decode(tiny):
     arch, weights, _ = tiny
     prompts = [torch.randint(0, 1000, (n,), generator=torch.Generator().manual_seed(n)).tolist() for n in (9, 33, 70)]
