@@ -4,7 +4,10 @@
 Input is a JSONL of materialised quality records (``analysis/quality_materialization.py``): each
 has ``sample_id``, ``question``, ``media`` (content-addressed files under ``--media-root``) and
 either ``options`` + ``answer`` (a letter; multiple choice) or ``answers`` (free text, scored
-with ANLS >= 0.5).  Records are grouped by identical ordered media; only groups with at least
+with ANLS >= 0.5), or - MVBench video records as ``utils/materialize_mvbench_media`` completes them -
+``candidates`` + ``answer_index`` with one ``video`` / ``frames`` media entry and an optional time window:
+``--video-frames`` frames are sampled at segment centres (inside the window when there is one), the prompt is
+the benchmark's ``Question / Option / (A) ...`` form and the answer letter is parsed the benchmark's way.  Records are grouped by identical ordered media; only groups with at least
 two questions are kept, and every prompt puts the media first so that all questions of a group
 share one visual prefix.  Inside a group the first question runs cold and stores the prefix,
 the others reuse it - which is exactly the situation in which the compacted prefix could cost
@@ -52,13 +55,30 @@ def load_records(path: str | Path) -> list[dict[str, Any]]:
         raise ValueError("duplicate sample_id in the records")
     for r in rows:
         has_choice = isinstance(r.get("options"), list) and isinstance(r.get("answer"), str)
-        has_text = isinstance(r.get("answers"), list) and r["answers"]
-        if not isinstance(r.get("question"), str) or has_choice == bool(has_text):
-            raise ValueError(f"record {r.get('sample_id')!r} needs a question and either options+answer or answers")
+        has_text = isinstance(r.get("answers"), list) and bool(r["answers"])
+        if not isinstance(r.get("question"), str) or int(has_choice) + int(has_text) + int(is_video_record(r)) != 1:
+            raise ValueError(f"record {r.get('sample_id')!r} needs a question and one of options+answer, answers, "
+                             "or candidates+answer_index with a video / frames source")
     return rows
 
 
+def is_video_record(record: Mapping[str, Any]) -> bool:
+    """An MVBench question: candidates with the index of the right one, and a single video or frame-directory source."""
+    media = record.get("media")
+    idx = record.get("answer_index")
+    return (isinstance(record.get("candidates"), list) and isinstance(idx, int) and not isinstance(idx, bool)
+            and 0 <= idx < len(record["candidates"]) and isinstance(media, list) and len(media) == 1
+            and isinstance(media[0], Mapping) and media[0].get("media_type") in ("video", "frames"))
+
+
+def evaluable(records: Sequence[Mapping[str, Any]]) -> list[Mapping[str, Any]]:
+    """Video records whose media were excluded (absent from the archive, separately licensed) leave the run."""
+    return [r for r in records if not is_video_record(r) or r["media"][0].get("materialization_status") == "complete"]
+
+
 def prompt_for(record: Mapping[str, Any]) -> str:
+    if is_video_record(record):
+        return qm.mvbench_prompt(record["question"], record["candidates"])
     n = len(record["media"])
     if "options" in record:
         opts = [f"({chr(65 + i)}) {o}" for i, o in enumerate(record["options"])]
@@ -67,6 +87,9 @@ def prompt_for(record: Mapping[str, Any]) -> str:
 
 
 def score(record: Mapping[str, Any], text: str) -> dict[str, Any]:
+    if is_video_record(record):
+        t = qm.mvbench_score(dict(record), text)
+        return {"parsed": t["prediction"], "correct": bool(t["score"]), "score": float(t["score"]), "parse_method": t["parse_method"]}
     if "options" in record:
         picked = qm.parse_choice(text, len(record["options"]))
         return {"parsed": picked, "correct": picked == record["answer"], "score": float(picked == record["answer"])}
@@ -82,6 +105,27 @@ def _load_images(record: Mapping[str, Any], root: str | Path) -> list[Any]:
         with Image.open(safe_materialized_path(root, m["materialized_path"])) as im:
             out.append(im.convert("RGB").copy())
     return out
+
+
+def _load_frames(record: Mapping[str, Any], root: str | Path, frames: int, frame_dir_fps: float) -> tuple[list[Any], dict[str, Any]]:
+    """The sampled RGB frames of a video record and how they were obtained."""
+    from prism_infer_b200.analysis import video_sampling as vs
+
+    m = record["media"][0]
+    if m["media_type"] == "frames":
+        return vs.sample_frame_manifest(m["frames"], materialized_root=root, frames=frames, fps=frame_dir_fps,
+                                        temporal_bound=record.get("temporal_bound"))
+    return vs.sample_video_file(safe_materialized_path(root, m["materialized_path"]), frames=frames, temporal_bound=record.get("temporal_bound"))
+
+
+def verify_media(records: Sequence[Mapping[str, Any]], root: str | Path) -> dict[str, int]:
+    """Re-hash every file the run will read: image files, video files and every frame of a frame directory."""
+    flat = []
+    for r in records:
+        for m in r["media"]:
+            parts = m["frames"] if m.get("media_type") == "frames" else [m]
+            flat.append({"sample_id": r["sample_id"], "media": [{"sha256": p["sha256"], "materialized_path": p["materialized_path"]} for p in parts]})
+    return verify_materialized_records(flat, root)
 
 
 def _resume_lines(path: Path, plan: Sequence[wsq.GroupedQualitySample], resume: bool) -> list[dict[str, Any]]:
@@ -103,7 +147,8 @@ def _resume_lines(path: Path, plan: Sequence[wsq.GroupedQualitySample], resume: 
 
 
 def run_stage(stage: str, plan: Sequence[wsq.GroupedQualitySample], make_engine: Callable[[dict[str, Any]], Any], media_root: str | Path,
-              out_dir: Path, *, max_tokens: int, resume: bool, log: Callable[[str], None] = print) -> list[dict[str, Any]]:
+              out_dir: Path, *, max_tokens: int, resume: bool, log: Callable[[str], None] = print, video_frames: int = 16,
+              frame_dir_fps: float = 3.0) -> list[dict[str, Any]]:
     from prism_infer_b200 import SamplingParams
 
     path = out_dir / f"{stage}.samples.jsonl"
@@ -116,12 +161,20 @@ def run_stage(stage: str, plan: Sequence[wsq.GroupedQualitySample], make_engine:
         i = len(rows)
         while i < len(plan):
             group = [it for it in plan[i:i + plan[i].group_size] if it.media_group_id == plan[i].media_group_id]
-            images = _load_images(group[0].record, media_root)
+            video = is_video_record(group[0].record)
+            sampling = None
+            if video:
+                images, sampling = _load_frames(group[0].record, media_root, video_frames, frame_dir_fps)
+            else:
+                images = _load_images(group[0].record, media_root)
             deleted = 0
             for it in group:
                 before = llm.multimodal_prefix_cache_metadata()
                 n_req = len(llm.metrics_snapshot()["engine"]["requests"])
-                out = llm.generate_interleaved_images(prompt_for(it.record), images, sp, image_marker=MARKER, use_tqdm=False)
+                if video:
+                    out = llm.generate_video(prompt_for(it.record), images, sp, use_tqdm=False)
+                else:
+                    out = llm.generate_interleaved_images(prompt_for(it.record), images, sp, image_marker=MARKER, use_tqdm=False)
                 after = llm.multimodal_prefix_cache_metadata()
                 metric = llm.metrics_snapshot()["engine"]["requests"][n_req]
                 if it.question_index == 0:  # the cold request stored the prefix: what did compaction drop?
@@ -130,6 +183,9 @@ def run_stage(stage: str, plan: Sequence[wsq.GroupedQualitySample], make_engine:
                              "stage": stage, "prediction": out["text"], **score(it.record, out["text"]),
                              "prefix_hit": after["hits"] - before["hits"] == 1, "cached_tokens": metric["cached_tokens"],
                              "prompt_tokens": metric["prompt_tokens"], "deleted_visual_tokens": deleted})
+                if sampling is not None:
+                    rows[-1]["sampled_indices"] = sampling["sampled_indices"]
+                    rows[-1]["sampled_rgb_identity_sha256"] = sampling["sampled_rgb_identity_sha256"]
             i += len(group)
             write_jsonl_atomic(path, rows)
             log(f"{stage}: {i}/{len(plan)} samples")
@@ -165,14 +221,17 @@ def main() -> None:
     ap.add_argument("--tp", type=int, default=1)
     ap.add_argument("--device", default=None)
     ap.add_argument("--resume", action="store_true")
+    ap.add_argument("--video-frames", type=int, default=16, help="frames sampled from a video record")
+    ap.add_argument("--frame-dir-fps", type=float, default=3.0, help="frame rate at which frame directories were exported")
     args = ap.parse_args()
     stages = [s for s in args.stages.split(",") if s]
     for s in stages:
         if s not in STAGES:
             ap.error(f"unknown stage {s!r}; known: {sorted(STAGES)}")
-    records = load_records(args.records)
-    verify_materialized_records(records, args.media_root)
-    plan = wsq.select_multi_question_groups(records, max_groups=args.max_groups)
+    records = evaluable(load_records(args.records))
+    verify_media(records, args.media_root)
+    sampling_identity = {"video_frames": args.video_frames, "frame_dir_fps": args.frame_dir_fps} if any(map(is_video_record, records)) else None
+    plan = wsq.select_multi_question_groups(records, max_groups=args.max_groups, sampling_identity=sampling_identity)
     if not plan:
         raise SystemExit("no media group has two or more questions")
     out_dir = Path(args.out)
@@ -185,7 +244,8 @@ def main() -> None:
                    max_num_seqs=2, max_chunk_size=8192, kvcache_block_size=256, num_kvcache_blocks=args.pages, cpu_kv_cache_ratio=0.0,
                    enable_prefix_caching=True, **extra)
 
-    rows = {s: run_stage(s, plan, make_engine, args.media_root, out_dir, max_tokens=args.max_tokens, resume=args.resume) for s in stages}
+    rows = {s: run_stage(s, plan, make_engine, args.media_root, out_dir, max_tokens=args.max_tokens, resume=args.resume,
+                         video_frames=args.video_frames, frame_dir_fps=args.frame_dir_fps) for s in stages}
     summary = summarize(rows, plan)
     summary["config"] = {"model": args.model, "stages": stages, "max_tokens": args.max_tokens, "pages": args.pages, "tp": args.tp}
     write_json_atomic(out_dir / "summary.json", summary)
