@@ -13,7 +13,8 @@ import os
 from math import isfinite
 from typing import Any, Mapping
 
-BENCHMARK_SCHEMA_VERSION = 2  # 2: per-benchmark contracts
+BENCHMARK_SCHEMA_VERSION = 3  # 2: per-benchmark contracts; 3: system records carry execution, correctness and KV evidence
+SUPPORTED_SCHEMA_VERSIONS = (1, 2, 3)
 REQUIRED_TOP_LEVEL = ("schema_version", "benchmark", "engine", "model", "hardware", "data", "config", "results")
 
 
@@ -47,7 +48,7 @@ def validate_benchmark_record(record: Mapping[str, Any]) -> Mapping[str, Any]:
     missing = [k for k in REQUIRED_TOP_LEVEL if k not in record]
     if missing:
         raise SchemaError(f"benchmark record is missing {missing}")
-    if record["schema_version"] not in (1, BENCHMARK_SCHEMA_VERSION):
+    if record["schema_version"] not in SUPPORTED_SCHEMA_VERSIONS:
         raise SchemaError(f"unsupported schema_version {record['schema_version']!r}")
     for key in ("benchmark", "engine", "model", "data"):
         if not isinstance(record[key], str) or not record[key]:
@@ -157,12 +158,133 @@ def _online_working_set(record: Mapping[str, Any]) -> None:
         raise SchemaError("more media resident than the workload has groups")
 
 
+STAT_KEYS = ("count", "median", "p90", "p99", "min", "max")
+
+
+def _check_stats(stats: Any, path: str, *, count: int | None = None) -> None:
+    """count / median / p90 / p99 / min / max of one measured quantity, in order."""
+    _check_fields(stats, {"count": "posint", "median": "nonneg", "p90": "nonneg", "p99": "nonneg", "min": "nonneg", "max": "nonneg"}, path)
+    if count is not None and stats["count"] != count:
+        raise SchemaError(f"{path}.count is {stats['count']}, the run had {count} rounds")
+    ladder = [stats[k] for k in ("min", "median", "p90", "p99", "max")]
+    if any(hi < lo * (1 - 1e-9) for lo, hi in zip(ladder, ladder[1:])):
+        raise SchemaError(f"{path}: min <= median <= p90 <= p99 <= max does not hold")
+
+
+def _int_keyed_counts(obj: Any, path: str) -> dict[int, int]:
+    if not isinstance(obj, Mapping):
+        raise SchemaError(f"{path} must be an object")
+    out = {}
+    for k, v in obj.items():
+        if not (isinstance(k, str) and k.isdigit() and int(k) > 0):
+            raise SchemaError(f"{path} has the key {k!r}; keys are positive batch sizes")
+        _check_kind(v, "count", f"{path}.{k}")
+        out[int(k)] = v
+    return out
+
+
+def _execution_evidence(ex: Any) -> None:
+    """Which path each decode step took.  Graph mode: a step of batch size n replays the smallest captured bucket
+    that holds n, steps beyond the largest bucket run eagerly; eager mode: no replay at all (reference
+    ``prism_infer/analysis/benchmark_schema.py:684-927``)."""
+    _check_fields(ex, {"backend": "str", "graph_batch_sizes": "list", "decode_batch_sizes": "obj", "graph_replays": "obj",
+                       "eager_decode_steps": "count", "decode_steps": "count"}, "execution")
+    if ex["backend"] not in ("eager", "cuda_graph"):
+        raise SchemaError(f"execution.backend {ex['backend']!r} is neither 'eager' nor 'cuda_graph'")
+    buckets = list(ex["graph_batch_sizes"])
+    if any(isinstance(b, bool) or not isinstance(b, int) or b <= 0 for b in buckets) or buckets != sorted(set(buckets)):
+        raise SchemaError("execution.graph_batch_sizes must be ascending positive integers without repeats")
+    sizes = _int_keyed_counts(ex["decode_batch_sizes"], "execution.decode_batch_sizes")
+    replays = _int_keyed_counts(ex["graph_replays"], "execution.graph_replays")
+    if sum(sizes.values()) != ex["decode_steps"]:
+        raise SchemaError("execution.decode_steps is not the sum of execution.decode_batch_sizes")
+    if ex["backend"] == "eager":
+        if buckets or any(replays.values()):
+            raise SchemaError("an eager run captured or replayed graphs")
+        if ex["eager_decode_steps"] != ex["decode_steps"]:
+            raise SchemaError("an eager run has decode steps that did not run eagerly")
+        return
+    if not buckets:
+        raise SchemaError("a cuda_graph run captured no graph")
+    if set(replays) - set(buckets):
+        raise SchemaError("execution.graph_replays names a batch size that was not captured")
+    want = {b: 0 for b in buckets}
+    eager = 0
+    for n, c in sizes.items():
+        if n > buckets[-1]:
+            eager += c
+        else:
+            want[next(b for b in buckets if b >= n)] += c
+    if eager != ex["eager_decode_steps"] or any(replays.get(b, 0) != c for b, c in want.items()):
+        raise SchemaError(f"execution: the decode batch sizes imply replays {want} and {eager} eager steps, "
+                          f"the record has {dict(sorted(replays.items()))} and {ex['eager_decode_steps']}")
+
+
+def _correctness_evidence(c: Any, *, batch: int) -> None:
+    from .identity import canonical_json_sha256
+
+    _check_fields(c, {"requests": "posint", "output_tokens": "posint", "output_token_ids": "list", "output_token_ids_sha256": "str",
+                      "identical_across_repeats": "bool"}, "correctness")
+    ids = c["output_token_ids"]
+    if c["requests"] != batch or len(ids) != batch:
+        raise SchemaError("correctness: one token-id list per request of the batch is required")
+    for i, row in enumerate(ids):
+        if not isinstance(row, (list, tuple)) or len(row) != c["output_tokens"] or \
+                any(isinstance(t, bool) or not isinstance(t, int) or t < 0 for t in row):
+            raise SchemaError(f"correctness.output_token_ids[{i}] must hold {c['output_tokens']} non-negative token ids")
+    if canonical_json_sha256([list(r) for r in ids]) != c["output_token_ids_sha256"]:
+        raise SchemaError("correctness.output_token_ids_sha256 does not match the token ids")
+    if not c["identical_across_repeats"]:
+        raise SchemaError("greedy decoding of the same inputs gave different tokens in different rounds")
+
+
+def _kv_accounting(kv: Any, *, batch: int) -> None:
+    _check_fields(kv, {"mode": "str", "page_tokens": "posint", "pages": "count", "bytes_per_page": "posint", "prompt_tokens": "list",
+                       "dropped_prompt_tokens": "list", "dense_prompt_bytes": "posint", "active_prompt_bytes": "posint"}, "kv_cache")
+    prompt, dropped = kv["prompt_tokens"], kv["dropped_prompt_tokens"]
+    if len(prompt) != batch or len(dropped) != batch:
+        raise SchemaError("kv_cache: one prompt length and one dropped-token count per request")
+    for i, (n, d) in enumerate(zip(prompt, dropped)):
+        _check_kind(n, "posint", f"kv_cache.prompt_tokens[{i}]")
+        _check_kind(d, "count", f"kv_cache.dropped_prompt_tokens[{i}]")
+        if d >= n:
+            raise SchemaError(f"kv_cache: request {i} dropped {d} of {n} prompt tokens")
+    page, per = kv["page_tokens"], kv["bytes_per_page"]
+    if kv["dense_prompt_bytes"] != sum(-(-n // page) for n in prompt) * per:
+        raise SchemaError("kv_cache.dense_prompt_bytes does not follow from the prompt lengths, the page size and the bytes per page")
+    if kv["active_prompt_bytes"] != sum(-(-(n - d) // page) for n, d in zip(prompt, dropped)) * per:
+        raise SchemaError("kv_cache.active_prompt_bytes does not follow from the resident prompt tokens")
+    compacting = kv["mode"].startswith("visual_compact")
+    if any(dropped) and not compacting:
+        raise SchemaError(f"kv_cache: mode {kv['mode']!r} does not compact, yet prompt tokens were dropped")
+
+
 def _system_mode_matrix(record: Mapping[str, Any]) -> None:
-    _check_fields(record["config"], {"mode": "str", "workload": "str", "tp": "posint"}, "config")
+    _check_fields(record["config"], {"mode": "str", "workload": "str", "tp": "posint", "repeats": "posint?", "output_tokens": "posint?"}, "config")
     res = record["results"]
     _check_fields(res, {"ttft_ms": "pos", "tpot_ms": "nonneg", "e2e_ms": "pos", "output_tokens_per_s": "pos", "batch": "posint"}, "results")
     if res["e2e_ms"] < res["ttft_ms"] * (1 - 1e-9):
         raise SchemaError("results.e2e_ms is below results.ttft_ms")
+    if record["schema_version"] < 3:  # earlier records carry the four headline numbers only
+        return
+    _check_fields(record["config"], {"repeats": "posint", "output_tokens": "posint"}, "config")
+    stats = res.get("stats")
+    _check_fields(stats, {k: "obj" for k in ("ttft_ms", "tpot_ms", "e2e_ms", "output_tokens_per_s")}, "results.stats")
+    for name in ("ttft_ms", "tpot_ms", "e2e_ms", "output_tokens_per_s"):
+        _check_stats(stats[name], f"results.stats.{name}", count=record["config"]["repeats"])
+        if not _close(res[name], stats[name]["median"], rel=1e-9):
+            raise SchemaError(f"results.{name} is not the median of its rounds")
+    for part in ("execution", "correctness", "kv_cache"):
+        if part not in record:
+            raise SchemaError(f"benchmark record is missing {part!r}")
+    _execution_evidence(record["execution"])
+    graph_mode = record["config"].get("enforce_eager") is False
+    if "enforce_eager" in record["config"] and graph_mode != (record["execution"]["backend"] == "cuda_graph"):
+        raise SchemaError("execution.backend contradicts config.enforce_eager")
+    _correctness_evidence(record["correctness"], batch=res["batch"])
+    if record["correctness"]["output_tokens"] != record["config"]["output_tokens"]:
+        raise SchemaError("correctness.output_tokens and config.output_tokens disagree")
+    _kv_accounting(record["kv_cache"], batch=res["batch"])
 
 
 CONTRACTS = {

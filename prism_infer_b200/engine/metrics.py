@@ -27,6 +27,7 @@ class RequestMetrics:
     cached_tokens: int = 0
     output_tokens: int = 0
     finish_reason: str | None = None
+    dropped_prompt_tokens: int = 0   # visual tokens whose K / V rows a compacting mode removed from the cache
     inter_token_ms: list[float] = field(default_factory=list)
 
     def record(self) -> dict[str, object]:
@@ -37,7 +38,7 @@ class RequestMetrics:
             "output_tokens": self.output_tokens, "queue_ms": ms(self.submitted_ns, self.scheduled_ns),
             "ttft_ms": ms(self.submitted_ns, self.first_token_ns), "tpot_ms": tpot,
             "inter_token_ms": list(self.inter_token_ms), "latency_ms": ms(self.submitted_ns, self.finished_ns),
-            "finish_reason": self.finish_reason,
+            "finish_reason": self.finish_reason, "dropped_prompt_tokens": self.dropped_prompt_tokens,
         }
 
 
@@ -84,6 +85,7 @@ class EngineMetrics:
                 m.inter_token_ms.append((now - m.last_token_ns) / 1e6 / max(1, n))
             m.last_token_ns = now
             m.output_tokens += n
+            m.dropped_prompt_tokens = max(m.dropped_prompt_tokens, int(seq.dropped_tokens))  # the layout is gone once the request finishes
 
     def on_request_finished(self, seq: Sequence) -> None:
         with self._lock:

@@ -183,6 +183,7 @@ class ModelRunner:
         self.graphs: dict[int, _DecodeGraph] = {}
         self.greedy_graphs: dict[int, _DecodeGraph] = {}
         self.run_ahead_counters = {"taken": 0, "discarded": 0}
+        self.decode_counters: dict[str, dict[int, int]] = {"graph_batch_sizes": {}, "eager_batch_sizes": {}}
         self.buckets = decode_buckets(min(config.max_num_seqs, 512))
         self.sample_seed = config.seed
         self.steps_run = 0
@@ -442,6 +443,10 @@ class ModelRunner:
     def execute(self, inp: StepInputs) -> list[int]:
         """Run one step; returns the sampled token of every sampling row."""
         self.steps_run += 1
+        if inp.kind != "prefill":  # which path each decode step took (benchmark records carry this as evidence)
+            graph = bool(self.graphs) and inp.num_seqs <= self.buckets[-1]
+            table = self.decode_counters["graph_batch_sizes" if graph else "eager_batch_sizes"]
+            table[inp.num_seqs] = table.get(inp.num_seqs, 0) + 1
         if self.graphs and inp.kind != "prefill" and inp.num_seqs <= self.buckets[-1]:
             return self._run_decode_graph(inp)
         if getattr(self, "_ahead", None) is not None:  # a launch that ran ahead is not taken over across other kinds of steps
@@ -667,7 +672,8 @@ class ModelRunner:
                 "launches_per_decode_graph": {str(b): getattr(g, "launches", 0) for b, g in self.graphs.items()},
                 "staging_bytes": {str(b): g.nbytes for b, g in self.graphs.items()},
                 "weight_bytes": self.model.weight_bytes(), "kv_sizing": getattr(self, "kv_sizing", None),
-                "decode_run_ahead": dict(self.run_ahead_counters)}
+                "decode_run_ahead": dict(self.run_ahead_counters),
+                "decode_steps": {k: {str(n): c for n, c in sorted(v.items())} for k, v in self.decode_counters.items()}}
 
     def barrier(self) -> None:
         if self.on_cuda:

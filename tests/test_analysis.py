@@ -179,10 +179,75 @@ def test_each_benchmark_has_its_own_record_contract():
 
     system = _record("system_mode_matrix", {"mode": "graph", "workload": "single_image_448", "tp": 1},
                      {"ttft_ms": 16.0, "tpot_ms": 3.9, "e2e_ms": 500.0, "output_tokens_per_s": 250.0, "batch": 1})
+    system["schema_version"] = 2  # the four headline numbers only
     bs.validate_benchmark_record(system)
     system["results"]["e2e_ms"] = 1.0
     with pytest.raises(bs.SchemaError, match="below"):
         bs.validate_benchmark_record(system)
+
+
+def _stats(values):
+    v = sorted(values)
+    return {"count": len(v), "median": v[len(v) // 2], "p90": v[-1], "p99": v[-1], "min": v[0], "max": v[-1]}
+
+
+def _system_record():
+    from prism_infer_b200.analysis.identity import canonical_json_sha256
+
+    ids = [[5, 6, 7, 8], [9, 9, 1, 2], [3, 3, 3, 3]]
+    stats = {"ttft_ms": _stats([16.0, 15.0, 17.0]), "tpot_ms": _stats([3.9, 3.8, 4.0]), "e2e_ms": _stats([500.0, 499.0, 501.0]),
+             "output_tokens_per_s": _stats([24.0, 23.0, 25.0])}
+    rec = _record("system_mode_matrix",
+                  {"mode": "graph_visual_compact_scaled_fp8", "workload": "single_image_448", "tp": 1, "repeats": 3, "output_tokens": 4, "enforce_eager": False},
+                  {"ttft_ms": 16.0, "tpot_ms": 3.9, "e2e_ms": 500.0, "output_tokens_per_s": 24.0, "batch": 3, "stats": stats})
+    # nine decode steps: three rounds of (all three decode, two left, one left); size 3 replays bucket 4, 2 bucket 2, 1 bucket 1
+    rec["execution"] = {"backend": "cuda_graph", "graph_batch_sizes": [1, 2, 4], "decode_batch_sizes": {"3": 3, "2": 3, "1": 3},
+                        "graph_replays": {"1": 3, "2": 3, "4": 3}, "eager_decode_steps": 0, "decode_steps": 9, "run_ahead": {"taken": 2, "discarded": 1}}
+    rec["correctness"] = {"requests": 3, "output_tokens": 4, "output_token_ids": ids, "output_token_ids_sha256": canonical_json_sha256(ids),
+                          "identical_across_repeats": True}
+    rec["kv_cache"] = {"mode": "visual_compact_scaled_fp8", "kv_mode": 2, "page_tokens": 256, "pages": 64, "bytes_per_page": 1000,
+                       "prompt_tokens": [300, 300, 520], "dropped_prompt_tokens": [60, 0, 10], "dense_prompt_bytes": 7000, "active_prompt_bytes": 5000}
+    return rec
+
+
+def test_system_record_carries_execution_correctness_and_kv_evidence():
+    import copy
+
+    good = _system_record()
+    bs.validate_benchmark_record(good)
+    for mutate, needle in (
+        (lambda r: r["execution"]["graph_replays"].update({"4": 2}), "imply replays"),
+        (lambda r: r["execution"].update(eager_decode_steps=1), "imply replays"),
+        (lambda r: r["execution"]["decode_batch_sizes"].update({"8": 1}), "decode_steps is not the sum"),
+        (lambda r: r["execution"]["graph_replays"].update({"3": 0}), "was not captured"),
+        (lambda r: r["execution"].update(graph_batch_sizes=[4, 2, 1]), "ascending"),
+        (lambda r: r["execution"].update(backend="eager"), "an eager run captured"),
+        (lambda r: r["config"].update(enforce_eager=True), "contradicts"),
+        (lambda r: r["correctness"]["output_token_ids"][0].pop(), "must hold 4"),
+        (lambda r: r["correctness"]["output_token_ids"][1].__setitem__(0, 10), "sha256 does not match"),
+        (lambda r: r["correctness"].update(identical_across_repeats=False), "different tokens"),
+        (lambda r: r["correctness"].update(output_tokens=5), "must hold 5"),
+        (lambda r: r["kv_cache"].update(dense_prompt_bytes=6000), "dense_prompt_bytes does not follow"),
+        (lambda r: r["kv_cache"].update(active_prompt_bytes=7000), "active_prompt_bytes does not follow"),
+        (lambda r: r["kv_cache"].update(mode="scaled_fp8_kv"), "does not compact"),
+        (lambda r: r["kv_cache"]["dropped_prompt_tokens"].__setitem__(1, 300), "dropped 300 of 300"),
+        (lambda r: r["results"]["stats"]["ttft_ms"].update(count=2), "3 rounds"),
+        (lambda r: r["results"]["stats"]["tpot_ms"].update(p90=1.0), "does not hold"),
+        (lambda r: r["results"].update(ttft_ms=15.0), "not the median"),
+        (lambda r: r.pop("kv_cache"), "missing 'kv_cache'"),
+    ):
+        bad = copy.deepcopy(good)
+        mutate(bad)
+        with pytest.raises(bs.SchemaError, match=needle):
+            bs.validate_benchmark_record(bad)
+    # an eager run: every decode step eager, nothing captured; a batch beyond the largest bucket runs eagerly in graph mode
+    eager = copy.deepcopy(good)
+    eager["config"]["enforce_eager"] = True
+    eager["execution"].update(backend="eager", graph_batch_sizes=[], graph_replays={}, eager_decode_steps=9)
+    bs.validate_benchmark_record(eager)
+    over = copy.deepcopy(good)
+    over["execution"].update(graph_batch_sizes=[1, 2], decode_batch_sizes={"3": 3, "2": 3, "1": 3}, graph_replays={"1": 3, "2": 3}, eager_decode_steps=3)
+    bs.validate_benchmark_record(over)
 
 
 def test_mvbench_prompt_and_answer_extraction():

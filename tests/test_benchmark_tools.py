@@ -201,3 +201,39 @@ def test_working_set_quality_runner_stages_resume_and_pairing(tmp_path):
     assert summary["samples"] == 5 and summary["groups"] == 2
     assert summary["stages"]["dense_prefix"]["repeat_prefix_hits"] == 3 == summary["stages"]["dense_prefix"]["repeat_questions"]
     assert summary["paired_deleted_subset"]["cohort"] == summary["stages"]["compact_prefix"]["samples_with_deletions"] > 0
+
+
+def test_system_benchmark_cell_produces_a_record_that_satisfies_its_contract():
+    """``bench_system.run_cell`` on the tiny model (CPU, eager): three rounds of two image requests, one dense and one
+    compacting mode; the record carries the round statistics, eager-path evidence, repeatable token ids and the KV
+    accounting of the prompts (dropped visual tokens only in the compacting mode)."""
+    import numpy as np
+    import torch
+
+    from prism_infer_b200 import LLM
+    from prism_infer_b200.analysis import benchmark_schema as bs
+    from prism_infer_b200.models.architecture import Qwen3VLArch
+    from prism_infer_b200.models.weights import random_weights
+
+    b = _load("bench_system")
+    arch = Qwen3VLArch.tiny()
+    weights = random_weights(arch, dtype=torch.float32, seed=0)
+    wl = {"name": "t", "kind": "image", "images": 1, "image_size": 224, "frames": 0, "question_tokens": 6, "output_tokens": 4}
+    for mode, dropped_expected in (("eager_scaled_fp8_kv", False), ("eager_visual_compact", True)):
+        opts = dict(enforce_eager=True, compression_mode="scaled_fp8_kv") if not dropped_expected else \
+            dict(enforce_eager=True, compression_mode="visual_compact", visual_pruning_keep_ratio=0.5, visual_pruning_min_keep_tokens=2)
+        llm = LLM("random:tiny", weights=weights, device="cpu", max_model_len=256, kvcache_block_size=16, num_kvcache_blocks=64,
+                  max_num_seqs=2, max_num_batched_tokens=256, max_chunk_size=256, cpu_kv_cache_ratio=0.0, enable_prefix_caching=False, **opts)
+        cell = b.run_cell(llm, wl, 2, np.random.default_rng(0), repeats=3)
+        llm.exit()
+        rec = {"schema_version": bs.BENCHMARK_SCHEMA_VERSION, "benchmark": "system_mode_matrix", "engine": "prism_infer_b200", "model": "random:tiny",
+               "data": "synthetic", "hardware": {"gpus": 1},
+               "config": {"mode": mode, "workload": "t", "tp": 1, "repeats": 3, "output_tokens": 4, **opts},
+               "results": cell["results"], "execution": cell["execution"], "correctness": cell["correctness"], "kv_cache": cell["kv_cache"]}
+        bs.validate_benchmark_record(rec)
+        ex = cell["execution"]
+        assert ex["backend"] == "eager" and ex["decode_steps"] == ex["eager_decode_steps"] == 3 * 3 and ex["decode_batch_sizes"] == {"2": 9}
+        assert cell["correctness"]["identical_across_repeats"] and len(cell["correctness"]["output_token_ids"]) == 2
+        assert cell["results"]["stats"]["e2e_ms"]["count"] == 3
+        assert any(cell["kv_cache"]["dropped_prompt_tokens"]) == dropped_expected
+        assert (cell["kv_cache"]["active_prompt_bytes"] < cell["kv_cache"]["dense_prompt_bytes"]) == dropped_expected
