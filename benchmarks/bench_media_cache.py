@@ -71,8 +71,7 @@ def main() -> None:
     ap.add_argument("--device", default=None)
     ap.add_argument("--out", default="")
     args = ap.parse_args()
-    with open(args.manifest) as fh:
-        case = harness.find_workload_case(json.load(fh), args.case)
+    case = harness.find_workload_case(harness.load_manifest(args.manifest), args.case)
     llm = LLM(args.model, device=args.device, max_model_len=8192, kvcache_block_size=256, num_kvcache_blocks=args.pages, max_num_seqs=max(8, args.batch),
               max_num_batched_tokens=16384, max_chunk_size=8192, cpu_kv_cache_ratio=0.0, enable_prefix_caching=True,
               enable_visual_embedding_cache=True, compression_mode=args.mode)

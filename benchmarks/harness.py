@@ -163,15 +163,43 @@ def make_image(spec: Mapping[str, Any]) -> np.ndarray:
     return np.broadcast_to(np.asarray(spec.get("color", (128, 128, 128)), dtype=np.uint8), (h, w, 3)).copy()
 
 
-def materialize_requests(case: Mapping[str, Any]) -> list[dict[str, Any]]:
+def load_file_image(spec: Mapping[str, Any], base: str | Path) -> np.ndarray:
+    """An ``image_file`` spec: the file below ``base`` whose bytes hash to ``sha256`` and whose size is as recorded."""
+    import hashlib
+    import io
+
+    from PIL import Image
+
+    data = (Path(base) / spec["path"]).read_bytes()
+    if hashlib.sha256(data).hexdigest() != spec["sha256"]:
+        raise ValueError(f"{spec['path']}: content differs from the manifest's sha256")
+    with Image.open(io.BytesIO(data)) as im:
+        arr = np.asarray(im.convert("RGB"))
+    if arr.shape[:2] != (int(spec["height"]), int(spec["width"])):
+        raise ValueError(f"{spec['path']}: {arr.shape[1]}x{arr.shape[0]} pixels, the manifest records {spec['width']}x{spec['height']}")
+    return arr
+
+
+def load_manifest(path: str | Path) -> dict[str, Any]:
+    """Read and validate a workload manifest (``analysis/workload_manifest.py``)."""
+    from prism_infer_b200.analysis.workload_manifest import load_workload_manifest
+
+    return load_workload_manifest(path)
+
+
+def materialize_requests(case: Mapping[str, Any], base: str | Path | None = None) -> list[dict[str, Any]]:
     """Case requests -> payloads for ``LLM.generate_mixed`` (``type`` in text / image / images /
-    interleaved_images / video)."""
+    interleaved_images / video; an ``image_file`` request becomes an ``image`` payload read below ``base``)."""
     out = []
     for r in case["requests"]:
         kind = r["type"]
-        p: dict[str, Any] = {"type": kind, "prompt": r["prompt"]}
+        p: dict[str, Any] = {"type": "image" if kind == "image_file" else kind, "prompt": r["prompt"]}
         if kind == "image":
             p["image"] = make_image(r["image"])
+        elif kind == "image_file":
+            if base is None:
+                raise ValueError("an image_file request needs the manifest's directory")
+            p["image"] = load_file_image(r["image"], base)
         elif kind in ("images", "interleaved_images"):
             p["images"] = [make_image(s) for s in r["images"]]
         elif kind == "video":
@@ -187,7 +215,7 @@ def describe_case_inputs(case: Mapping[str, Any]) -> dict[str, Any]:
     shapes, images, videos, frames = [], 0, 0, 0
     for r in case["requests"]:
         specs: Sequence[Mapping[str, Any]] = ()
-        if r["type"] == "image":
+        if r["type"] in ("image", "image_file"):
             specs, images = [r["image"]], images + 1
         elif r["type"] in ("images", "interleaved_images"):
             specs, images = r["images"], images + len(r["images"])

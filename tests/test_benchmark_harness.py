@@ -157,3 +157,80 @@ def test_media_cache_benchmark_on_tiny_model():
     assert repeated["reuse"]["repeated_media_requests"] == 4
     assert repeated["visual_embedding_cache"]["misses"] <= 1                                   # at most the first request encodes
     assert repeated["process_gpu_memory"]["error"] is not None                                 # the fake NVML has no methods: recorded, not raised
+
+
+def test_workload_manifest_contract_and_file_images(tmp_path):
+    """The shipped manifest is valid; every kind of defect is named; an image_file request is read with its hash
+    and size checked; a caption task's references are scored against a prediction."""
+    import copy
+    import hashlib
+    import io
+
+    import numpy as np
+    import pytest
+    from PIL import Image
+
+    from prism_infer_b200.analysis import workload_manifest as wm
+    from prism_infer_b200.analysis.reference_quality import score_reference_text
+
+    h = _load("harness")
+    shipped = h.load_manifest(os.path.join(ROOT, "benchmarks", "workloads", "system_cases.json"))
+    assert {c["id"] for c in shipped["cases"]} >= {"text_short", "single_image_448", "mixed_text_image_video"}
+
+    buf = io.BytesIO()
+    Image.fromarray(np.random.default_rng(0).integers(0, 256, (48, 64, 3), dtype=np.uint8)).save(buf, format="PNG")
+    (tmp_path / "media").mkdir()
+    (tmp_path / "media" / "cat.png").write_bytes(buf.getvalue())
+    digest = hashlib.sha256(buf.getvalue()).hexdigest()
+    manifest = {
+        "schema_version": 1, "name": "captioning",
+        "reference_sources": {"coco": {"dataset": "COCO", "split": "val2017", "task": "caption", "source_url": "https://example.org/coco",
+                                       "annotation_file": "captions_val2017.json", "content_sha256": "ab" * 32}},
+        "cases": [{"id": "one_caption", "requests": [
+            {"type": "image_file", "prompt": "Describe the image.",
+             "image": {"path": "media/cat.png", "source_url": "https://example.org/cat.png", "sha256": digest, "width": 64, "height": 48},
+             "evaluation": {"task": "caption", "reference_source": "coco", "image_id": 7,
+                            "references": [{"annotation_id": 1, "text": "A cat sits on a mat."}, {"annotation_id": 2, "text": "a small cat resting"}]}},
+            {"type": "interleaved_images", "prompt": "<image> and <image>", "images": [{"width": 32, "height": 32, "seed": 1},
+                                                                                    {"width": 32, "height": 32, "color": [1, 2, 3]}]},
+            {"type": "video", "prompt": "what moves", "frames": [{"width": 32, "height": 32, "seed": 2}, {"width": 32, "height": 32, "seed": 3}]},
+        ]}],
+    }
+    path = tmp_path / "m.json"
+    path.write_text(json.dumps(manifest))
+    loaded = h.load_manifest(path)
+    case = h.find_workload_case(loaded, "one_caption")
+    payloads = h.materialize_requests(case, base=tmp_path)
+    assert payloads[0]["type"] == "image" and payloads[0]["image"].shape == (48, 64, 3)
+    assert h.describe_case_inputs(case)["images"] == 3 and h.describe_case_inputs(case)["video_frames"] == 2
+    refs = [r["text"] for r in case["requests"][0]["evaluation"]["references"]]
+    assert score_reference_text("a cat sits on a mat", refs)["token_f1"] == 1.0
+    with pytest.raises(ValueError, match="needs the manifest's directory"):
+        h.materialize_requests(case)
+    (tmp_path / "media" / "cat.png").write_bytes(buf.getvalue() + b"x")
+    with pytest.raises(ValueError, match="sha256"):
+        h.materialize_requests(case, base=tmp_path)
+
+    def broken(mutate, needle):
+        bad = copy.deepcopy(manifest)
+        mutate(bad)
+        with pytest.raises(wm.ManifestError, match=needle):
+            wm.validate_workload_manifest(bad)
+
+    req = lambda m, i: m["cases"][0]["requests"][i]  # noqa: E731
+    broken(lambda m: m.update(schema_version=2), "schema_version")
+    broken(lambda m: m["cases"].append(copy.deepcopy(m["cases"][0])), "appears twice")
+    broken(lambda m: m["cases"][0].update(requests=[]), "requests")
+    broken(lambda m: req(m, 0).update(type="audio"), "not one of")
+    broken(lambda m: req(m, 0)["image"].update(sha256="XYZ"), "sha256")
+    broken(lambda m: req(m, 0)["image"].update(path="../cat.png"), "below the manifest")
+    broken(lambda m: req(m, 0)["evaluation"].update(reference_source="flickr"), "unknown source")
+    broken(lambda m: req(m, 0)["evaluation"].update(task="free_text_qa"), "is a 'caption' source")
+    broken(lambda m: req(m, 0)["evaluation"]["references"].append({"annotation_id": 1, "text": "again"}), "twice")
+    broken(lambda m: req(m, 0)["evaluation"]["references"][0].update(text="?!"), "no word left")
+    broken(lambda m: req(m, 1).update(prompt="<image> only"), "markers for 2 images")
+    broken(lambda m: req(m, 1)["images"][0].update(color=[0, 0, 0]), "exactly one of")
+    broken(lambda m: req(m, 1)["images"][1].update(color=[0, 0, 256]), "0..255")
+    broken(lambda m: req(m, 2)["frames"][1].update(width=16), "same size")
+    broken(lambda m: req(m, 2).update(frames=[]), "frames")
+    broken(lambda m: m["reference_sources"]["coco"].pop("split"), "split is missing")
