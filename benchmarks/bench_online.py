@@ -64,9 +64,11 @@ def main() -> None:
     ap.add_argument("--plan", default="", help="plan document from build_working_set_plan.py (measured prefix pages); "
                                                "overrides the group, request, rate, seed and page arguments")
     ap.add_argument("--out", default="")
+    ap.add_argument("--media-root", default="", help="root of the materialised media tree, for a plan built from real records")
     args = ap.parse_args()
 
     plan_sha256 = None
+    load_image = None
     if args.plan:
         from build_working_set_plan import load_plan_document
 
@@ -76,6 +78,12 @@ def main() -> None:
         args.pages, args.rate, args.alpha = plan.page_budget, plan.rate, plan.alpha
         args.groups, args.questions = doc["groups"], doc["questions"]
         args.requests = len(plan.measured)
+        if "media_paths" in doc:  # real media: read (and re-hash) the files the plan names
+            if not args.media_root:
+                ap.error("this plan was built from materialised records: pass --media-root")
+            from build_working_set_plan import file_image_loader
+
+            load_image = file_image_loader(args.media_root, doc["media_paths"])
     else:
         groups = wsp.synthetic_groups(args.groups, args.questions, seed=args.seed, min_images=args.min_images,
                                       max_images=args.max_images, tokens_per_image=(args.image_size // 32) ** 2 + 2)
@@ -89,7 +97,8 @@ def main() -> None:
         return
     session = OnlineServingSession(llm)
     sp = SamplingParams(temperature=0.0, max_tokens=args.max_tokens, ignore_eos=True)
-    images = {g.group_id: [image_for(d, args.image_size) for d in g.media_digests] for g in plan.groups}
+    load_image = load_image or (lambda d: image_for(d, args.image_size))
+    images = {g.group_id: [load_image(d) for d in g.media_digests] for g in plan.groups}
 
     def payload(r: wsp.PlannedRequest) -> dict:
         g = plan.groups[r.group_index]

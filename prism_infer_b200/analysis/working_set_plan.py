@@ -19,7 +19,7 @@ import hashlib
 import random
 from bisect import bisect_left
 from dataclasses import dataclass, field
-from typing import Sequence
+from typing import Any, Mapping, Sequence
 
 DEFAULT_SEED = 20260801
 GROUP_SEED_MASK = 0x47524F5550
@@ -147,3 +147,54 @@ def synthetic_groups(num_groups: int = 42, num_questions: int = 85, *, seed: int
         prefix_tokens = n_img * (tokens_per_image + 6)
         groups.append(MediaGroup(group_id_of(digests), digests, qs, -(-prefix_tokens // page)))
     return groups
+
+
+CHOICE_HINT = "Answer with the option's letter from the given choices directly."
+
+
+def question_text(record: Mapping[str, Any]) -> str:
+    """The text after the media of a materialised quality record: the question (its image markers rewritten to
+    ``Image k`` so the media stay in front), the lettered options of a multiple-choice record and the answer hint."""
+    q = record.get("question")
+    if not isinstance(q, str) or not q:
+        raise ValueError(f"record {record.get('sample_id')!r} has no question")
+    parts = q.split(IMAGE_MARKER)
+    n = len(record["media"])
+    if len(parts) - 1 not in (0, n):
+        raise ValueError(f"record {record.get('sample_id')!r}: {len(parts) - 1} image markers for {n} media")
+    text = parts[0] + "".join(f"Image {k}{seg}" for k, seg in enumerate(parts[1:], 1))
+    options = record.get("options")
+    if isinstance(options, list) and options:
+        text += "\n" + "\n".join(f"({chr(65 + i)}) {o}" for i, o in enumerate(options)) + "\n" + CHOICE_HINT
+    return text
+
+
+def groups_from_records(records: Sequence[Mapping[str, Any]]) -> tuple[list[MediaGroup], dict[str, str]]:
+    """Media groups of materialised image records (``analysis/quality_materialization.py``): records with exactly the
+    same ordered media form a group, groups with fewer than two questions are left out, questions keep their source
+    order.  Also returns where each media file lives (digest -> path relative to the materialisation root).
+    Reference: ``prism_infer/analysis/working_set_plan.py:56-197``."""
+    by_media: dict[tuple[str, ...], list[str]] = {}
+    paths: dict[str, str] = {}
+    seen_ids: set[str] = set()
+    for r in records:
+        sid = str(r.get("sample_id"))
+        if sid in seen_ids:
+            raise ValueError(f"duplicate sample id {sid!r}")
+        seen_ids.add(sid)
+        media = r.get("media")
+        if not isinstance(media, list) or not media:
+            raise ValueError(f"record {sid!r} has no media")
+        digests = []
+        for m in media:
+            d, rel = m.get("sha256"), m.get("materialized_path")
+            if not (isinstance(d, str) and len(d) == 64 and isinstance(rel, str) and rel):
+                raise ValueError(f"record {sid!r} has a media entry without digest or path")
+            if paths.setdefault(d, rel) != rel:
+                raise ValueError(f"media {d[:12]} is recorded under two paths")
+            digests.append(d)
+        by_media.setdefault(tuple(digests), []).append(question_text(r))
+    groups = [MediaGroup(group_id_of(d), d, tuple(qs)) for d, qs in by_media.items() if len(qs) >= 2]
+    groups.sort(key=lambda g: g.group_id)
+    used = {d for g in groups for d in g.media_digests}
+    return groups, {d: p for d, p in sorted(paths.items()) if d in used}

@@ -237,3 +237,71 @@ def test_system_benchmark_cell_produces_a_record_that_satisfies_its_contract():
         assert cell["results"]["stats"]["e2e_ms"]["count"] == 3
         assert any(cell["kv_cache"]["dropped_prompt_tokens"]) == dropped_expected
         assert (cell["kv_cache"]["active_prompt_bytes"] < cell["kv_cache"]["dense_prompt_bytes"]) == dropped_expected
+
+
+def test_working_set_plan_from_materialised_records(tmp_path):
+    """Real media groups: records over the same ordered files form a group, the page measurement reads the files
+    (re-hashed), the plan document names them and the loader refuses a damaged file."""
+    import io
+
+    import numpy as np
+    import pytest
+    import torch
+    from PIL import Image
+
+    from prism_infer_b200 import LLM
+    from prism_infer_b200.analysis import working_set_plan as wsp
+    from prism_infer_b200.analysis.identity import canonical_json_sha256
+    from prism_infer_b200.analysis.quality_materialization import materialize_image
+    from prism_infer_b200.models.architecture import Qwen3VLArch
+    from prism_infer_b200.models.weights import random_weights
+
+    b = _load("build_working_set_plan")
+    root = tmp_path / "media"
+    rng = np.random.default_rng(3)
+
+    def png(size):
+        buf = io.BytesIO()
+        Image.fromarray(rng.integers(0, 256, (size, size, 3), dtype=np.uint8)).save(buf, format="PNG")
+        return materialize_image(buf.getvalue(), root=root, dataset_id="synthetic")
+
+    a, c, d = png(64), png(64), png(96)
+    records = [
+        {"sample_id": "s1", "question": "which is brighter", "options": ["left", "right"], "answer": "A", "media": [a, c]},
+        {"sample_id": "s2", "question": "compare <image> with <image>", "options": ["same", "other"], "answer": "B", "media": [a, c]},
+        {"sample_id": "s3", "question": "read the sign", "answers": ["stop"], "media": [d]},
+        {"sample_id": "s4", "question": "what colour", "answers": ["red"], "media": [d]},
+        {"sample_id": "s5", "question": "order matters", "answers": ["x"], "media": [c, a]},
+    ]
+    groups, paths = wsp.groups_from_records(records)
+    assert len(groups) == 2 and sorted(g.num_images for g in groups) == [1, 2] and set(paths) == {a["sha256"], c["sha256"], d["sha256"]}
+    two = next(g for g in groups if g.num_images == 2)
+    assert two.questions[1].startswith("compare Image 1 with Image 2\n(A) same\n(B) other\n") and two.questions[1].endswith(wsp.CHOICE_HINT)
+    assert two.group_id == wsp.group_id_of([a["sha256"], c["sha256"]])
+    with pytest.raises(ValueError, match="duplicate sample id"):
+        wsp.groups_from_records(records + [records[0]])
+
+    contract = b.measurement_contract(model="random:tiny", page_tokens=16, image_size=0, seed=1, groups=groups,
+                                      records_sha256=canonical_json_sha256(records))
+    assert contract["media"] == "materialized_records"
+    arch = Qwen3VLArch.tiny()
+    weights = random_weights(arch, dtype=torch.float32, seed=0)
+
+    def make_engine():
+        return LLM("random:tiny", weights=weights, device="cpu", max_model_len=512, kvcache_block_size=16, num_kvcache_blocks=128,
+                   enforce_eager=True, max_num_batched_tokens=512, max_chunk_size=512, enable_prefix_caching=True, compression_mode="scaled_fp8_kv")
+
+    loader = b.file_image_loader(root, paths)
+    art = b.measure_all(groups, tmp_path / "plan.json.pages.json", contract, make_engine, loader, resume=False, log=lambda _m: None)
+    assert all(art["groups"][g.group_id]["dense_prefix_pages"] > 0 for g in groups)
+    measured = [wsp.MediaGroup(g.group_id, g.media_digests, g.questions, art["groups"][g.group_id]["dense_prefix_pages"]) for g in groups]
+    plan = wsp.build_plan(measured, num_requests=6, rate=50.0, seed=3, page_budget=4)
+    doc = b.plan_document(plan, contract, "all", paths)
+    assert set(doc["media_paths"]) == set(paths)
+    (tmp_path / "plan.json").write_text(json.dumps(doc))
+    loaded, doc2 = b.load_plan_document(tmp_path / "plan.json")
+    assert doc2["media_paths"] == doc["media_paths"] and loaded.groups == plan.groups
+    victim = root / paths[d["sha256"]]
+    victim.write_bytes(victim.read_bytes() + b"0")
+    with pytest.raises(OSError, match="mismatch"):
+        loader(d["sha256"])
