@@ -112,6 +112,62 @@ def test_profile_session_records_regions_and_is_noop_outside():
     with profile_region("after"):
         pass
     assert len(session.regions) == 3
+    assert all(r["step_id"] is None and r["phase"] == "preprocess" for r in rec["regions"])
+    assert rec["summary"]["a.b"]["calls"] == 2 and rec["summary"]["a.b"]["cuda_ms"] is None
+    assert set(rec["summary"]["a.b"]["cpu_ms"]) == set(pp.STAT_KEYS) and set(rec["summary_by_phase"]) == {"preprocess"}
+
+
+def test_profile_of_engine_steps_links_regions_to_steps_and_phases():
+    """An engine run inside a session: every ``engine.step`` region opens a step, the regions below it carry its id
+    and phase, the summaries split by phase, and a doctored aggregate is refused."""
+    import copy
+
+    import torch
+
+    from prism_infer_b200 import LLM, SamplingParams
+    from prism_infer_b200.models.architecture import Qwen3VLArch
+    from prism_infer_b200.models.weights import random_weights
+
+    arch = Qwen3VLArch.tiny()
+    llm = LLM("random:tiny", weights=random_weights(arch, dtype=torch.float32, seed=0), device="cpu", max_model_len=128,
+              kvcache_block_size=16, num_kvcache_blocks=16, enforce_eager=True)
+    with pp.performance_profile({"run": "engine"}, cuda_timing=False, nvtx=False) as session:
+        with profile_region("submit", cuda=False):
+            llm.add_request([5, 6, 7, 8], SamplingParams(temperature=0.0, max_tokens=3, ignore_eos=True))
+        while not llm.is_finished():
+            llm.step_result()
+    llm.exit()
+    rec = pp.validate_profile_record(session.finalize())
+    assert [s["phase"] for s in rec["steps"]] == ["prefill", "decode", "decode"] and [s["step_id"] for s in rec["steps"]] == [0, 1, 2]
+    assert all(s["status"] == "ok" and s["batch_size"] == 1 for s in rec["steps"])
+    by_name = {}
+    for r in rec["regions"]:
+        by_name.setdefault(r["name"], []).append(r)
+    assert [r["step_id"] for r in by_name["engine.step"]] == [0, 1, 2]
+    assert by_name["submit"][0]["phase"] == "preprocess" and by_name["submit"][0]["step_id"] is None
+    assert {r["phase"] for r in by_name["engine.scheduler.schedule"]} == {"prefill", "decode"}
+    assert set(rec["summary_by_phase"]) == {"preprocess", "prefill", "decode"}
+    assert rec["summary_by_phase"]["decode"]["engine.step"]["calls"] == 2 and rec["summary"]["engine.step"]["calls"] == 3
+    stats = rec["summary"]["engine.step"]["cpu_ms"]
+    assert stats["min"] <= stats["median"] <= stats["p90"] <= stats["p99"] <= stats["max"]
+    for mutate, needle in (
+        (lambda r: r["summary"]["engine.step"].update(calls=4), "summary does not follow"),
+        (lambda r: r["regions"][2].update(phase="decode" if r["regions"][2]["phase"] != "decode" else "prefill"), "its step says"),
+        (lambda r: r["regions"][1].update(step_id=9), "unknown step"),
+        (lambda r: r["steps"][1].update(step_id=0), "distinct"),
+        (lambda r: r["regions"][0].update(cpu_ms=-1.0), "non-negative"),
+        (lambda r: r["totals"]["engine.step"].update(count=1), "totals do not follow"),
+    ):
+        bad = copy.deepcopy(rec)
+        mutate(bad)
+        with pytest.raises(ValueError, match=needle):
+            pp.validate_profile_record(bad)
+    # a step that raises is recorded as an error step
+    with pp.performance_profile(cuda_timing=False, nvtx=False) as session:
+        with pytest.raises(RuntimeError):
+            with profile_region("engine.step", cuda=False):
+                raise RuntimeError("boom")
+    assert session.finalize()["steps"] == [{"step_id": 0, "status": "error"}]
 
 
 def test_runtime_capabilities_fail_closed():
