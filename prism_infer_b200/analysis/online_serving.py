@@ -52,6 +52,21 @@ def summarize_online_run(run: Mapping[str, object]) -> dict[str, object]:
     cancelled = [r for r in records if r.get("finish_reason") == "cancelled"]
     if len(completed) + len(rejected) + len(cancelled) != len(records):
         raise ValueError("every online request must have a terminal finish_reason")
+
+    def metric(name: str, *, optional: bool = False) -> list[float]:
+        values = []
+        for r in completed:
+            v = r.get(name)
+            if v is None:
+                if optional or name not in r:  # a one-token request has no inter-token time; older records lack the field
+                    continue
+                raise ValueError(f"a completed request has no {name}")
+            x = float(v)
+            if not isfinite(x) or x < 0:
+                raise ValueError(f"invalid request metric {name}={v!r}")
+            values.append(x)
+        return values
+
     out_tokens = sum(len(r.get("token_ids", ())) if "token_ids" in r else int(r.get("output_tokens", 0)) for r in completed)
     return {
         "schema_version": ONLINE_SUMMARY_SCHEMA_VERSION,
@@ -59,8 +74,11 @@ def summarize_online_run(run: Mapping[str, object]) -> dict[str, object]:
         "duration_s": duration,
         "output_tokens": out_tokens,
         "output_tokens_per_s": out_tokens / duration,
-        "ttft_ms": summarize_distribution([r["ttft_ms"] for r in completed if r.get("ttft_ms") is not None]),
-        "e2e_ms": summarize_distribution([r["latency_ms"] for r in completed if r.get("latency_ms") is not None]),
+        "requests_per_s": len(completed) / duration,
+        "queue_ms": summarize_distribution(metric("queue_ms", optional=True)),
+        "ttft_ms": summarize_distribution(metric("ttft_ms", optional=True)),
+        "tpot_ms": summarize_distribution(metric("tpot_ms", optional=True)),
+        "e2e_ms": summarize_distribution(metric("latency_ms", optional=True)),
         "prompt_tokens": sum(int(r.get("prompt_tokens", 0)) for r in completed),
         "cached_prompt_tokens": sum(int(r.get("cached_tokens", 0)) for r in completed),
         "recomputed_prompt_tokens": recomputed_prompt_tokens(completed),
