@@ -60,7 +60,8 @@ class Attention(nn.Module):
                 out = ops.varlen_attention(q, k, v, meta.cu_seqlens_q, meta.max_q_len, causal=True)
             else:
                 out = ops.paged_prefill_attention(q, cache, self.layer, meta.cu_seqlens_q, meta.kv_lens, meta.block_tables,
-                                                  meta.max_q_len)
+                                                  meta.max_q_len, cu_seqlens_kv=meta.cu_seqlens_kv, total_kv=meta.total_kv,
+                                                  max_kv_len=meta.max_kv_len)
         else:
             if cache is None:
                 raise RuntimeError("decode needs a bound KV cache")

@@ -279,3 +279,90 @@ def test_layers_run_the_cuda_kernels(cuda_device):
     assert (logits.max(-1).values - picked).max() < 2e-2  # the arg-max up to bf16 rounding of near-ties
     assert torch.equal(layers.Sampler()(logits.cuda(), None, sampling_mode="greedy").cpu(), logits.argmax(-1))
     ops.native.check_status()
+
+
+def test_decoder_composed_of_the_layer_modules_matches_the_oracle():
+    """The module building blocks are not on the engine's hot path, so nothing else notices if they drift from it.
+    A two-layer text decoder put together from them (weights loaded through their loaders from checkpoint names)
+    must give the oracle's hidden states: a prefill chunk, a second chunk over the paged cache, then a decode step."""
+    from prism_infer_b200 import ops
+    from prism_infer_b200.layers import (Attention, MergedColumnParallelLinear, QKVParallelLinear, RMSNorm, RowParallelLinear, SiluAndMul,
+                                         VocabParallelEmbedding, get_rope)
+    from prism_infer_b200.models.architecture import Qwen3VLArch
+    from prism_infer_b200.models.qwen3_vl import AttnMeta
+    from prism_infer_b200.models.reference_model import ReferenceQwen3VL
+    from prism_infer_b200.models.weights import random_weights
+
+    arch = Qwen3VLArch.tiny()
+    t = arch.text
+    w = random_weights(arch, dtype=torch.float32, seed=0)
+    oracle = ReferenceQwen3VL(arch, w)
+    lm = "model.language_model"
+
+    class Layer(torch.nn.Module):
+        def __init__(self, i):
+            super().__init__()
+            p = f"{lm}.layers.{i}"
+            self.input_norm, self.post_norm = RMSNorm(t.hidden_size, t.rms_norm_eps), RMSNorm(t.hidden_size, t.rms_norm_eps)
+            self.q_norm, self.k_norm = RMSNorm(t.head_dim, t.rms_norm_eps), RMSNorm(t.head_dim, t.rms_norm_eps)
+            self.qkv = QKVParallelLinear(t.hidden_size, t.head_dim, t.num_heads, t.num_kv_heads)
+            self.o = RowParallelLinear(t.num_heads * t.head_dim, t.hidden_size)
+            self.gate_up = MergedColumnParallelLinear(t.hidden_size, [t.intermediate_size, t.intermediate_size])
+            self.down = RowParallelLinear(t.intermediate_size, t.hidden_size)
+            self.act, self.attn = SiluAndMul(), Attention(t.num_heads, t.head_dim, num_kv_heads=t.num_kv_heads, layer=i)
+            self.rope = get_rope(t.head_dim, t.head_dim, 512, t.rope_theta)
+            for name, mod in (("input_layernorm", self.input_norm), ("post_attention_layernorm", self.post_norm),
+                              ("self_attn.q_norm", self.q_norm), ("self_attn.k_norm", self.k_norm)):
+                mod.weight.data.copy_(w[f"{p}.{name}.weight"])
+            for shard in "qkv":
+                self.qkv.weight_loader(self.qkv.weight, w[f"{p}.self_attn.{shard}_proj.weight"], shard)
+            self.o.weight_loader(self.o.weight, w[f"{p}.self_attn.o_proj.weight"])
+            self.gate_up.weight_loader(self.gate_up.weight, w[f"{p}.mlp.gate_proj.weight"], 0)
+            self.gate_up.weight_loader(self.gate_up.weight, w[f"{p}.mlp.up_proj.weight"], 1)
+            self.down.weight_loader(self.down.weight, w[f"{p}.mlp.down_proj.weight"])
+
+        def forward(self, x, positions, meta):
+            n = x.shape[0]
+            q, k, v = self.qkv(self.input_norm(x)).split([t.num_heads * t.head_dim, t.num_kv_heads * t.head_dim, t.num_kv_heads * t.head_dim], dim=-1)
+            q = self.q_norm(q.reshape(n, t.num_heads, t.head_dim))
+            k = self.k_norm(k.reshape(n, t.num_kv_heads, t.head_dim))
+            q, k = self.rope(positions, q, k)
+            x = x + self.o(self.attn(q.reshape(n, -1), k.reshape(n, -1), v, meta))
+            return x + self.down(self.act(self.gate_up(self.post_norm(x))))
+
+    embed = VocabParallelEmbedding(t.vocab_size, t.hidden_size)
+    embed.weight_loader(embed.weight, w[f"{lm}.embed_tokens.weight"])
+    final = RMSNorm(t.hidden_size, t.rms_norm_eps)
+    final.weight.data.copy_(w[f"{lm}.norm.weight"])
+    layers = [Layer(i) for i in range(t.num_layers)]
+    page = 16
+    cache = ops.KVCache(t.num_layers, 4, t.num_kv_heads, page, t.head_dim, ops.KV_BF16, "cpu", dtype=torch.float32)
+    for layer in layers:
+        layer.attn.bind_cache(cache)
+
+    ids = torch.randint(0, t.vocab_size, (27,), generator=torch.Generator().manual_seed(3))
+    want = oracle.text_forward(ids, torch.arange(27).expand(3, -1))
+    bt = torch.tensor([[2, 0, 3, 1]], dtype=torch.int32)
+
+    def run(lo, hi, meta):
+        x = embed(ids[lo:hi])
+        pos = torch.arange(lo, hi)
+        for layer in layers:
+            x = layer(x, pos, meta)
+        return final(x)
+
+    def slots(lo, hi):
+        j = torch.arange(lo, hi)
+        return bt[0, (j // page).long()].long() * page + j % page
+
+    def prefill_meta(lo, hi):
+        return AttnMeta(is_prefill=True, block_tables=bt, slots=slots(lo, hi), cu_seqlens_q=torch.tensor([0, hi - lo], dtype=torch.int32),
+                        kv_lens=torch.tensor([hi], dtype=torch.int32), max_q_len=hi - lo, no_history=lo == 0)
+
+    with torch.no_grad():
+        first = run(0, 20, prefill_meta(0, 20))                      # fresh K / V rows
+        second = run(20, 26, prefill_meta(20, 26))                   # six tokens over twenty cached ones
+        last = run(26, 27, AttnMeta(is_prefill=False, block_tables=bt, slots=slots(26, 27), context_lens=torch.tensor([27], dtype=torch.int32)))
+    got = torch.cat((first, second, last))
+    assert got.shape == want.shape
+    assert float((got - want).abs().max()) < 2e-4, float((got - want).abs().max())
