@@ -195,6 +195,12 @@ class ExecutionConfig:
     cooperative_prefill: bool = False
     cooperative_prefill_layer_quantum: int = 4
     cooperative_prefill_vision_block_quantum: int = 4
+    # adaptive cooperative prefill (0 = off): with sequences decoding, fewer than `coalesce_min_seqs` waiting requests are
+    # held back for up to this many milliseconds (less when a deadline reserve ends earlier) so that one prefill serves
+    # several; a prefill of at least that many requests runs in one piece; a smaller one runs in layer quanta only when it
+    # carries a heavy visual input or the decode batch has reached a quarter of max_num_seqs
+    cooperative_prefill_coalesce_ms: float = 0.0
+    cooperative_prefill_coalesce_min_seqs: int = 3
     programmatic_dependent_launch: bool = True
     decode_multi_step: int = 1
     decode_run_ahead: bool = True             # launch the next greedy decode graph before the host has read this one's tokens
@@ -212,6 +218,10 @@ class ExecutionConfig:
             _bool(getattr(self, n), n)
         _int(self.cooperative_prefill_layer_quantum, "cooperative_prefill_layer_quantum", 1)
         _int(self.cooperative_prefill_vision_block_quantum, "cooperative_prefill_vision_block_quantum", 1)
+        _int(self.cooperative_prefill_coalesce_min_seqs, "cooperative_prefill_coalesce_min_seqs", 2)
+        if isinstance(self.cooperative_prefill_coalesce_ms, bool) or not isinstance(self.cooperative_prefill_coalesce_ms, (int, float)) \
+                or not 0 <= self.cooperative_prefill_coalesce_ms <= 10_000:
+            raise ValueError("cooperative_prefill_coalesce_ms must be a number of milliseconds in [0, 10000]")
         _int(self.decode_multi_step, "decode_multi_step", 1)
         _int(self.device_status_check_interval, "device_status_check_interval", 0)
 
@@ -295,6 +305,8 @@ _FLAT = {
         "enable_cooperative_prefill": "cooperative_prefill",
         "cooperative_prefill_layer_quantum": "cooperative_prefill_layer_quantum",
         "cooperative_prefill_vision_block_quantum": "cooperative_prefill_vision_block_quantum",
+        "cooperative_prefill_coalesce_ms": "cooperative_prefill_coalesce_ms",
+        "cooperative_prefill_coalesce_min_seqs": "cooperative_prefill_coalesce_min_seqs",
         "enable_programmatic_dependent_launch": "programmatic_dependent_launch",
         "decode_multi_step": "decode_multi_step",
         "enable_decode_run_ahead": "decode_run_ahead",

@@ -124,7 +124,10 @@ class LLMEngine:
         self._deferred: list[StepResult] = []  # results produced outside step_result (a pending prefill drained by a cancel)
         self._decode_after_interrupt = False
         self.cooperative_counters = {"vision_quanta": 0, "layer_quantum_prefills": 0, "layer_quanta": 0, "decode_steps_between_quanta": 0,
-                                     "slo_prefill_interruptions": 0, "slo_pending_deadline_finishes": 0, "slo_deadline_atomic_prefills": 0}
+                                     "slo_prefill_interruptions": 0, "slo_pending_deadline_finishes": 0, "slo_deadline_atomic_prefills": 0,
+                                     "slo_light_atomic_prefills": 0, "coalesce_deferred_decode_steps": 0, "coalesce_deadline_releases": 0,
+                                     "coalesced_atomic_prefills": 0, "underfilled_atomic_prefills": 0}
+        self._fine_grain_latched = False
         self._steps_since_status = 0
         atexit.register(self.exit)
 
@@ -276,6 +279,14 @@ class LLMEngine:
                 return self._deferred.pop(0)
             if self._pending_prefill is not None:
                 return self._continue_pending_prefill()
+            if self._should_coalesce_prefill():
+                with profile_region("engine.scheduler.schedule", cuda=False):
+                    held = self.scheduler.schedule_decode(count=True)
+                if held is not None:  # the waiting requests stay queued; the running ones take their step
+                    self.cooperative_counters["coalesce_deferred_decode_steps"] += 1
+                    return self._run_plan(held)
+            policy = self.scheduler.policy
+            heavy_gap = getattr(policy, "decode_batches_since_heavy", None)
             with profile_region("engine.scheduler.schedule", cuda=False):
                 plan = self.scheduler.schedule()
             if plan.is_idle and plan.kv_transfers.empty:
@@ -287,15 +298,17 @@ class LLMEngine:
                 # its sequence (or grows its table), so the re-planned prefill carries none of
                 # them again and every transfer it does carry belongs to a new admission
                 self._cooperative_pending = self.executor.hydrate_vision(plan) > 0
-                self.cooperative_counters["vision_quanta"] += 1
                 if self._cooperative_pending:
+                    self.cooperative_counters["vision_quanta"] += 1
+                    if heavy_gap is not None:
+                        # the quantum is not the heavy prefill itself: the decode batches counted so far still stand,
+                        # or the language prefill would wait a whole spacing interval behind its own vision tower
+                        policy.decode_batches_since_heavy = heavy_gap
                     self.scheduler.consecutive_prefill_batches = self.scheduler.policy.max_consecutive_prefill
                     return StepResult(Phase.IDLE)
             self._cooperative_pending = False
-            if cooperative and not self.executor.attention_strategy and self._slo_due(plan.seqs):
-                # a request of the plan has used up its time-to-first-token slack: no yielding to decode steps
-                self.cooperative_counters["slo_deadline_atomic_prefills"] += 1
-                cooperative = False
+            if cooperative and not self.executor.attention_strategy:
+                cooperative = self._cooperative_is_useful(plan)
             if cooperative and not self.executor.attention_strategy:
                 # layer quanta: the prefill's embedding now, its decoder layers a few at a time with a decode step
                 # of the running sequences after every quantum (reference engine/llm_engine.py:1040-1103)
@@ -331,10 +344,9 @@ class LLMEngine:
         """One decode step of the running sequences while a prefill is pending; the scheduler's decode plan only
         touches decoding sequences (victims of a preemption included), never the ones whose prefill is under way."""
         with profile_region("engine.scheduler.schedule", cuda=False):
-            plan = self.scheduler.schedule_decode()
+            plan = self.scheduler.schedule_decode(count=True)
         if plan is None:
             return StepResult(Phase.IDLE)
-        self.scheduler.counters["decode_batches"] += 1
         self.cooperative_counters["decode_steps_between_quanta"] += 1
         return self._run_plan(plan)
 
@@ -356,6 +368,54 @@ class LLMEngine:
     def _slo_due(self, seqs) -> bool:
         now = self.scheduler.clock_ns()
         return any(r is not None and now >= r for r in map(self._release_ns, seqs))
+
+    def _cooperative_is_useful(self, plan) -> bool:
+        """Whether a prefill that meets running decodes yields to them in layer quanta, or runs in one piece
+        (reference engine/llm_engine.py:913-966)."""
+        c = self.cooperative_counters
+        policy = self.scheduler.policy
+        if hasattr(policy, "cost_tier") and any(s.deadline_ns is not None for s in plan.seqs) \
+                and all(policy.cost_tier(s) < 2 for s in plan.seqs):
+            c["slo_light_atomic_prefills"] += 1  # cheap prompts with a deadline: quanta would only delay their first token
+            return False
+        if self._slo_due(plan.seqs):
+            # a request of the plan has used up its time-to-first-token slack: no yielding to decode steps
+            c["slo_deadline_atomic_prefills"] += 1
+            return False
+        if self.config.cooperative_prefill_coalesce_ms <= 0:
+            return True
+        if plan.batch_size >= self.config.cooperative_prefill_coalesce_min_seqs:
+            c["coalesced_atomic_prefills"] += 1  # one pass over the weights serves many requests: worth stalling decode once
+            return False
+        if self.scheduler.num_decoding >= max(1, (self.config.max_num_seqs + 3) // 4):
+            self._fine_grain_latched = True      # stays on: the engine has been under load
+        heavy = plan.num_vision_patches >= self.config.heavy_prefill_vision_patch_threshold
+        if heavy or self._fine_grain_latched:
+            return True
+        c["underfilled_atomic_prefills"] += 1
+        return False
+
+    def _should_coalesce_prefill(self) -> bool:
+        """Hold a few waiting requests back while sequences decode, so that one prefill can serve more of them: until
+        the oldest has waited ``cooperative_prefill_coalesce_ms``, or a waiting request reaches its release time,
+        or enough of them have gathered (reference engine/llm_engine.py:986-1017)."""
+        cfg = self.config
+        if not cfg.cooperative_prefill or cfg.cooperative_prefill_coalesce_ms <= 0 or self.scheduler.num_decoding == 0:
+            return False
+        waiting = list(self.scheduler.waiting)
+        if not waiting or len(waiting) >= cfg.cooperative_prefill_coalesce_min_seqs:
+            return False
+        if any(s.state is RequestState.PREFILLING for s in self.scheduler.running):
+            return False  # a chunked prefill under way is not held up
+        arrivals = [s.arrival_ns for s in waiting if s.arrival_ns is not None]
+        if not arrivals:
+            return False
+        fixed = min(arrivals) + int(cfg.cooperative_prefill_coalesce_ms * 1e6)
+        release = min([fixed] + [r for r in map(self._release_ns, waiting) if r is not None])
+        wait = self.scheduler.clock_ns() < release
+        if not wait and release < fixed:
+            self.cooperative_counters["coalesce_deadline_releases"] += 1
+        return wait
 
     def _slo_interrupt_tier(self) -> int | None:
         """The cost tier an interrupting prefill may admit up to, when a waiting request that is cheaper than

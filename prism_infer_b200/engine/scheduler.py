@@ -141,8 +141,15 @@ class Scheduler:
             self.policy.on_prefill_batch(plan.seqs)
         return plan
 
-    def schedule_decode(self) -> BatchPlan | None:
-        return self._decode_plan()
+    def schedule_decode(self, *, count: bool = False) -> BatchPlan | None:
+        """A decode plan of the running sequences, whatever waits.  With ``count`` the plan is booked the way
+        ``schedule`` books its own decode batches (prefill / decode alternation, heavy-prefill spacing, counters)."""
+        plan = self._decode_plan()
+        if plan is not None and count and plan.phase is Phase.DECODE:
+            self.consecutive_prefill_batches = 0
+            self.counters["decode_batches"] += 1
+            self.policy.on_decode_batch()
+        return plan
 
     def _prefill_plan(self, prefilling: list[Sequence], *, max_cost_tier: int | None = None) -> BatchPlan | None:
         budget = self.max_num_batched_tokens

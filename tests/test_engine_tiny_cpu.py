@@ -187,9 +187,10 @@ def test_cancelling_a_request_whose_prefill_is_pending_drains_the_prefill_first(
     llm.exit()
 
 
-def _slo_engine(weights, now):
+def _slo_engine(weights, now, **kw):
+    # 196 patches (one 224 x 224 image) count as a heavy visual input here: cost tier 2
     llm = _llm(weights, enable_cooperative_prefill=True, cooperative_prefill_layer_quantum=1, scheduler_policy="slo_aware",
-               num_kvcache_blocks=96)
+               num_kvcache_blocks=96, heavy_prefill_vision_patch_threshold=100, **kw)
     llm.scheduler.clock_ns = lambda: now[0]
     return llm
 
@@ -245,6 +246,10 @@ def test_a_due_cheaper_request_interrupts_a_pending_prefill(tiny):
     llm.exit()
 
 
+def _heavy_image_request(arch, seed=8):
+    return prepare_image_inputs(PatchProcessor(arch), load_tokenizer("random:tiny", arch), [31, 32, 33], [_image(seed)])
+
+
 def test_a_pending_prefill_whose_own_release_time_passes_finishes_in_one_piece(tiny):
     arch, weights, oracle = tiny
     now = [5_000_000_000]
@@ -253,43 +258,137 @@ def test_a_pending_prefill_whose_own_release_time_passes_finishes_in_one_piece(t
     a_id = llm.add_request(first, SamplingParams(temperature=0.0, max_tokens=10, ignore_eos=True))
     while llm.scheduler.num_decoding == 0:
         llm.step_result()
-    late = list(range(40, 71))
-    b_id = llm.add_request(late, SamplingParams(temperature=0.0, max_tokens=4, ignore_eos=True))
-    llm._sequences[b_id].deadline_ns = now[0] + 1_000_000_000
+    late = _heavy_image_request(arch)
+    b_id = llm.add_prepared_image_request(late, SamplingParams(temperature=0.0, max_tokens=4, ignore_eos=True))
+    assert llm.scheduler.policy.cost_tier(llm._sequences[b_id]) == 2
+    llm._sequences[b_id].deadline_ns = now[0] + 2_000_000_000
     done = {}
-    for _ in range(4):
+    for _ in range(6):  # vision quantum, then the language prefill is begun
         for o in llm.step_result().outputs:
             if o.finished:
                 done[o.request_id] = list(o.token_ids)
         if llm._pending_prefill is not None:
             break
-    assert llm._pending_prefill is not None and llm.cooperative_counters["slo_deadline_atomic_prefills"] == 0
-    now[0] += 900_000_000  # 100 ms before the deadline: inside the 120 ms reserve
-    res = llm.step_result()
     c = llm.cooperative_counters
+    assert llm._pending_prefill is not None and c["slo_deadline_atomic_prefills"] == 0 and c["slo_light_atomic_prefills"] == 0
+    now[0] += 1_400_000_000  # 600 ms before the deadline: inside the 700 ms reserve of a heavy request
+    res = llm.step_result()
     assert res.phase.value == "prefill" and llm._pending_prefill is None and c["slo_pending_deadline_finishes"] == 1
     assert c["layer_quanta"] == 0  # no layer had run as a quantum: all of them ran in the finishing step
     _drain(llm, done)
-    assert done[a_id] == oracle.generate_greedy(first, 10) and done[b_id] == oracle.generate_greedy(late, 4)
+    assert done[a_id] == oracle.generate_greedy(first, 10)
+    assert done[b_id] == oracle.generate_greedy(late.input_ids, 4, pixel_values=late.pixel_values, image_grid_thw=late.image_grid_thw)
     llm.exit()
 
 
-def test_a_prefill_that_is_already_due_does_not_yield_to_decode_steps(tiny):
+def test_a_prefill_that_is_already_due_or_cheap_does_not_yield_to_decode_steps(tiny):
+    """Under the SLO-aware policy a heavy request past its release time runs in one piece, and so does a prompt of a
+    cheap tier that carries a deadline at all (quanta would only delay its first token)."""
     arch, weights, oracle = tiny
     now = [5_000_000_000]
     llm = _slo_engine(weights, now)
     first = [3, 4, 5, 6, 7]
-    a_id = llm.add_request(first, SamplingParams(temperature=0.0, max_tokens=8, ignore_eos=True))
+    a_id = llm.add_request(first, SamplingParams(temperature=0.0, max_tokens=12, ignore_eos=True))
     while llm.scheduler.num_decoding == 0:
         llm.step_result()
-    late = list(range(40, 71))
-    b_id = llm.add_request(late, SamplingParams(temperature=0.0, max_tokens=4, ignore_eos=True))
+    heavy = _heavy_image_request(arch)
+    b_id = llm.add_prepared_image_request(heavy, SamplingParams(temperature=0.0, max_tokens=3, ignore_eos=True))
     llm._sequences[b_id].deadline_ns = now[0] + 50_000_000
     done = {}
-    _drain(llm, done)
+    while llm.request_state(b_id) is not None and llm.request_state(b_id).value in ("waiting", "prefilling"):
+        for o in llm.step_result().outputs:
+            if o.finished:
+                done[o.request_id] = list(o.token_ids)
     c = llm.cooperative_counters
     assert c["slo_deadline_atomic_prefills"] == 1 and c["layer_quantum_prefills"] == 0
-    assert done[a_id] == oracle.generate_greedy(first, 8) and done[b_id] == oracle.generate_greedy(late, 4)
+    light = list(range(40, 71))
+    l_id = llm.add_request(light, SamplingParams(temperature=0.0, max_tokens=3, ignore_eos=True))
+    llm._sequences[l_id].deadline_ns = now[0] + 10_000_000_000  # far away: only the tier decides
+    _drain(llm, done)
+    assert c["slo_light_atomic_prefills"] == 1 and c["layer_quantum_prefills"] == 0
+    assert done[a_id] == oracle.generate_greedy(first, 12) and done[l_id] == oracle.generate_greedy(light, 3)
+    assert done[b_id] == oracle.generate_greedy(heavy.input_ids, 3, pixel_values=heavy.pixel_values, image_grid_thw=heavy.image_grid_thw)
+    llm.exit()
+
+
+def test_waiting_requests_are_coalesced_into_one_prefill_while_sequences_decode(tiny):
+    """Adaptive cooperative prefill: one waiting request is held back (decode steps go on) until a third arrives or
+    the oldest has waited long enough; three run as one atomic prefill; a lone request past the wait runs atomically
+    while the engine is lightly loaded and in layer quanta once the decode batch has reached a quarter of the limit."""
+    arch, weights, oracle = tiny
+    now = [1_000_000_000]
+    llm = _llm(weights, enable_cooperative_prefill=True, cooperative_prefill_layer_quantum=1, cooperative_prefill_coalesce_ms=250.0,
+               max_num_seqs=8, num_kvcache_blocks=96)
+    llm.scheduler.clock_ns = lambda: now[0]
+    sp = SamplingParams(temperature=0.0, max_tokens=30, ignore_eos=True)
+
+    def add(prompt):
+        rid = llm.add_request(prompt, sp)
+        llm._sequences[rid].arrival_ns = now[0]
+        return rid
+
+    prompts = {}
+    first = [3, 4, 5, 6, 7]
+    prompts[add(first)] = first
+    while llm.scheduler.num_decoding == 0:
+        llm.step_result()
+    c = llm.cooperative_counters
+    for k in range(2):
+        p = list(range(40 + 10 * k, 60 + 10 * k))
+        prompts[add(p)] = p
+    for _ in range(3):
+        assert llm.step_result().phase.value == "decode"
+    assert c["coalesce_deferred_decode_steps"] == 3 and len(llm.scheduler.waiting) == 2
+    p = list(range(90, 120))
+    prompts[add(p)] = p                      # the third waiting request: no more holding back
+    res = llm.step_result()
+    assert res.phase.value == "prefill" and res.num_tokens == 20 + 20 + 30 and c["coalesced_atomic_prefills"] == 1
+    assert llm._pending_prefill is None and llm.scheduler.num_decoding == 4
+    # a lone request: held for 250 ms, then (four sequences decode = a quarter of eight: the engine counts as loaded) in quanta
+    p = list(range(200, 240))
+    lone = add(p)
+    prompts[lone] = p
+    assert llm.step_result().phase.value == "decode" and c["coalesce_deferred_decode_steps"] == 4
+    now[0] += 251_000_000
+    llm.step_result()
+    assert c["layer_quantum_prefills"] == 1 and c["underfilled_atomic_prefills"] == 0 and llm._pending_prefill is not None
+    done = {}
+    _drain(llm, done)
+    for rid, prompt in prompts.items():
+        assert done[rid] == oracle.generate_greedy(prompt, 30), rid
+    llm.exit()
+
+
+def test_a_lone_prefill_on_a_lightly_loaded_engine_runs_atomically_and_a_deadline_ends_the_wait(tiny):
+    arch, weights, oracle = tiny
+    now = [1_000_000_000]
+    llm = _llm(weights, enable_cooperative_prefill=True, cooperative_prefill_layer_quantum=1, cooperative_prefill_coalesce_ms=250.0,
+               max_num_seqs=8, num_kvcache_blocks=96, scheduler_policy="slo_aware")
+    llm.scheduler.clock_ns = lambda: now[0]
+    first = [3, 4, 5, 6, 7]
+    a_id = llm.add_request(first, SamplingParams(temperature=0.0, max_tokens=12, ignore_eos=True))
+    while llm.scheduler.num_decoding == 0:
+        llm.step_result()
+    c = llm.cooperative_counters
+    late = list(range(40, 71))
+    b_id = llm.add_request(late, SamplingParams(temperature=0.0, max_tokens=3, ignore_eos=True))
+    llm._sequences[b_id].arrival_ns = now[0]
+    assert llm.step_result().phase.value == "decode" and c["coalesce_deferred_decode_steps"] == 1
+    now[0] += 251_000_000
+    assert llm.step_result().phase.value == "prefill"   # one decoder of eight: not loaded, so no quanta
+    assert c["underfilled_atomic_prefills"] == 1 and c["layer_quantum_prefills"] == 0 and c["coalesce_deadline_releases"] == 0
+    # a waiting request whose release time (deadline - 120 ms reserve) comes before the 250 ms are over
+    third = list(range(80, 100))
+    c_id = llm.add_request(third, SamplingParams(temperature=0.0, max_tokens=3, ignore_eos=True))
+    llm._sequences[c_id].arrival_ns = now[0]
+    llm._sequences[c_id].deadline_ns = now[0] + 170_000_000
+    assert llm.step_result().phase.value == "decode"
+    now[0] += 60_000_000
+    assert llm.step_result().phase.value == "prefill" and c["coalesce_deadline_releases"] == 1
+    done = {}
+    _drain(llm, done)
+    assert done[a_id] == oracle.generate_greedy(first, 12) and done[b_id] == oracle.generate_greedy(late, 3)
+    assert done[c_id] == oracle.generate_greedy(third, 3)
     llm.exit()
 
 
