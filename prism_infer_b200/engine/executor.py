@@ -76,6 +76,36 @@ class ModelExecutor:
             self._have_visual.add(job.seq_id)
         return len(inputs.vision_jobs)
 
+    def begin_hydrate(self, plan: BatchPlan) -> dict | None:
+        """``hydrate_vision`` in block quanta: page transfers and input preparation now, the vision tower of each
+        pending job a few blocks at a time through ``advance_hydrate``.  None when the plan has no tower work."""
+        if not plan.kv_transfers.empty:
+            self.runners.call("apply_kv_transfers", plan.kv_transfers)
+        inputs = self.preparer.prepare(plan, self._have_visual)
+        if not inputs.vision_jobs:
+            return None
+        return {"jobs": list(inputs.vision_jobs), "next": 0, "encode": None, "quanta": 0}
+
+    def advance_hydrate(self, handle: dict, max_blocks: int) -> bool:
+        """One quantum: up to ``max_blocks`` vision blocks of the job under way (the next job is begun when one ends).
+        True when every job of the plan has its visual embeddings."""
+        while handle["next"] < len(handle["jobs"]):
+            job = handle["jobs"][handle["next"]]
+            if handle["encode"] is None:
+                handle["encode"] = self.runners.call("begin_encode", job)
+                if handle["encode"] is None:  # served from the visual-embedding cache
+                    self._have_visual.add(job.seq_id)
+                    handle["next"] += 1
+                    continue
+            handle["quanta"] += 1
+            if not self.runners.call("advance_encode", handle["encode"], max_blocks):
+                return False
+            self._have_visual.add(job.seq_id)
+            handle["encode"] = None
+            handle["next"] += 1
+            return handle["next"] == len(handle["jobs"])
+        return True
+
     # ---- cooperative prefill: one prefill plan run a few decoder layers at a time (reference
     # ``engine/executor.py:35-95``: begin / advance / finish) ----------------------------------------
     def begin_prefill(self, plan: BatchPlan):

@@ -123,7 +123,8 @@ class LLMEngine:
         self._pending_prefill = None          # executor handle of a prefill whose layers run in quanta
         self._deferred: list[StepResult] = []  # results produced outside step_result (a pending prefill drained by a cancel)
         self._decode_after_interrupt = False
-        self.cooperative_counters = {"vision_quanta": 0, "layer_quantum_prefills": 0, "layer_quanta": 0, "decode_steps_between_quanta": 0,
+        self._pending_vision: dict | None = None
+        self.cooperative_counters = {"vision_quanta": 0, "vision_block_quanta": 0, "layer_quantum_prefills": 0, "layer_quanta": 0, "decode_steps_between_quanta": 0,
                                      "slo_prefill_interruptions": 0, "slo_pending_deadline_finishes": 0, "slo_deadline_atomic_prefills": 0,
                                      "slo_light_atomic_prefills": 0, "coalesce_deferred_decode_steps": 0, "coalesce_deadline_releases": 0,
                                      "coalesced_atomic_prefills": 0, "underfilled_atomic_prefills": 0}
@@ -277,6 +278,8 @@ class LLMEngine:
         with profile_region("engine.step", cuda=False):
             if self._deferred:
                 return self._deferred.pop(0)
+            if self._pending_vision is not None:
+                return self._continue_pending_vision()
             if self._pending_prefill is not None:
                 return self._continue_pending_prefill()
             if self._should_coalesce_prefill():
@@ -297,7 +300,15 @@ class LLMEngine:
                 # ran with the quantum; the scheduler lists a transfer only in the plan that admits
                 # its sequence (or grows its table), so the re-planned prefill carries none of
                 # them again and every transfer it does carry belongs to a new admission
-                self._cooperative_pending = self.executor.hydrate_vision(plan) > 0
+                if self.config.cooperative_prefill_vision_block_quantum < self.arch.vision.depth:
+                    # the tower a few blocks at a time, a decode step of the running sequences after every quantum
+                    self._pending_vision = self.executor.begin_hydrate(plan)
+                    if self._pending_vision is not None:
+                        self._pending_vision["heavy_gap"] = heavy_gap
+                        return self._continue_pending_vision()
+                    self._cooperative_pending = False
+                else:
+                    self._cooperative_pending = self.executor.hydrate_vision(plan) > 0
                 if self._cooperative_pending:
                     self.cooperative_counters["vision_quanta"] += 1
                     if heavy_gap is not None:
@@ -349,6 +360,27 @@ class LLMEngine:
             return StepResult(Phase.IDLE)
         self.cooperative_counters["decode_steps_between_quanta"] += 1
         return self._run_plan(plan)
+
+    def _continue_pending_vision(self, *, drain: bool = False) -> StepResult:
+        """One quantum of the pending vision-tower work, then (next call) a decode step; when the tower is done the
+        language prefill is planned again by the following step."""
+        handle = self._pending_vision
+        if handle.pop("decode_next", False) and not drain and self.scheduler.num_decoding > 0:
+            return self._decode_between_quanta()
+        blocks = self.arch.vision.depth if (drain or self.scheduler.num_decoding == 0) else self.config.cooperative_prefill_vision_block_quantum
+        done = self.executor.advance_hydrate(handle, blocks)
+        self.cooperative_counters["vision_block_quanta"] += 1
+        if not done:
+            handle["decode_next"] = True
+            return StepResult(Phase.IDLE)
+        self._pending_vision = None
+        self.cooperative_counters["vision_quanta"] += 1
+        self._cooperative_pending = True
+        policy = self.scheduler.policy
+        if handle.get("heavy_gap") is not None:
+            policy.decode_batches_since_heavy = max(handle["heavy_gap"], getattr(policy, "decode_batches_since_heavy", 0))
+        self.scheduler.consecutive_prefill_batches = policy.max_consecutive_prefill
+        return StepResult(Phase.IDLE)
 
     def _finish_pending_prefill(self) -> StepResult:
         handle, self._pending_prefill = self._pending_prefill, None
@@ -480,6 +512,11 @@ class LLMEngine:
             raise RuntimeError(f"device status reports failures (rank, unit) -> (code, detail, block, count): {bad}")
 
     def cancel_request(self, request_id: int) -> bool:
+        vision = self._pending_vision
+        if vision is not None and any(job.seq_id == request_id for job in vision["jobs"]):
+            # the runner holds a half-run tower pass for this plan: let it finish, then drop the result with the request
+            while self._pending_vision is not None:
+                self._continue_pending_vision(drain=True)
         pending = self._pending_prefill
         if pending is not None and any(seq.seq_id == request_id for seq in pending["plan"].seqs):
             # its pages must stay allocated until the layers that still write them have run: finish the prefill

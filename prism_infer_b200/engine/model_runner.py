@@ -417,6 +417,38 @@ class ModelRunner:
         """Vision tower for one sequence, kept until its prefill consumes it."""
         self._visual[job.seq_id] = self._encode(job)
 
+    # ---- vision tower in block quanta (cooperative prefill on one rank; eager launches, no tower graph) ----
+    def begin_encode(self, job) -> int | None:
+        """Start the vision tower for one sequence; its blocks follow through ``advance_encode``.  Returns a handle,
+        or None when the visual-embedding cache already holds the result (it is attached at once)."""
+        if self.comm.size != 1:
+            raise ValueError("the vision tower runs in block quanta on one rank only")
+        key = job.cache_key if self.config.enable_visual_embedding_cache else None
+        if key is not None and key in self._visual_cache:
+            self._visual[job.seq_id] = self._encode(job)
+            return None
+        with profile_region("model.vision.encoder", metadata={"quantum": "begin"}):
+            state = self.model.begin_vision(job.pixel_values, job.grid_thw)
+        handle = self.__dict__.setdefault("_encode_handles", 0) + 1
+        self._encode_handles = handle
+        self.__dict__.setdefault("_pending_encodes", {})[handle] = (job, key, state)
+        return handle
+
+    def advance_encode(self, handle: int, max_blocks: int) -> bool:
+        """Up to ``max_blocks`` more vision blocks; when the last has run the mergers follow and the result is attached
+        to the sequence (and cached).  True when done."""
+        job, key, state = self._pending_encodes[handle]
+        with profile_region("model.vision.encoder", metadata={"quantum": max_blocks}):
+            if not self.model.advance_vision(state, max_blocks):
+                return False
+            main, deep = self.model.finish_vision(state)
+        del self._pending_encodes[handle]
+        self._visual[job.seq_id] = (main, deep)
+        if key is not None:
+            self.visual_cache_counters["misses"] += 1
+            self._cache_visual(key, (main, deep))
+        return True
+
     def hydrate_visual_embedding(self, job) -> None:
         """Run the vision tower ahead of scheduling.  The result stays attached to the sequence
         until its prefill has consumed it (reference ``engine/model_runner.py:522-596``) - the

@@ -59,6 +59,20 @@ class AttnMeta:
 
 
 @dataclass
+class VisionTowerState:
+    """A vision-tower pass between blocks (``Qwen3VLModel.begin_vision / advance_vision / finish_vision``)."""
+
+    x: torch.Tensor                  # [patches, vision hidden] after ``next_block`` blocks
+    coords: torch.Tensor
+    cu: torch.Tensor
+    max_len: int
+    comm: object = None              # tensor-parallel ranks: the communicator whose all-gather the mergers feed
+    token_base: int = 0
+    next_block: int = 0
+    deep: list = field(default_factory=list)
+
+
+@dataclass
 class LayerWeights:
     input_norm: torch.Tensor
     qkv: torch.Tensor
@@ -428,29 +442,55 @@ class Qwen3VLModel:
         return out
 
     def _vision_tower(self, pixel_values: torch.Tensor, grid, comm, token_base: int):
-        v = self.arch.vision
+        st = self._vision_begin(pixel_values, grid, comm, token_base)
+        self.advance_vision(st, len(self.vision_blocks))
+        return self.finish_vision(st)
+
+    def _vision_begin(self, pixel_values: torch.Tensor, grid, comm, token_base: int) -> "VisionTowerState":
         dev = self.device
         x = ops.linear(pixel_values.to(device=dev, dtype=self.dtype, non_blocking=True), self.patch_w, bias=self.patch_b)
         idx, wt, coords, cu, max_len = self._vision_geometry(grid)
         ops.pos_embed_add(x, self.pos_embed, idx, wt)
+        return VisionTowerState(x=x, coords=coords, cu=cu, max_len=max_len, comm=comm, token_base=token_base)
+
+    def begin_vision(self, pixel_values: torch.Tensor, grid_thw: Sequence[Sequence[int]]) -> "VisionTowerState":
+        """Patch embedding and position embedding of a vision-tower pass whose blocks ``advance_vision`` runs a few at a
+        time (one rank; cooperative prefill lets decode steps of running sequences go in between; reference
+        ``engine/model_runner.py:1346-1650`` vision-block quanta).  ``finish_vision`` gives what ``encode_vision`` returns."""
+        if self.tp > 1:
+            raise ValueError("the resumable vision tower runs on one rank")
+        return self._vision_begin(pixel_values, [tuple(int(v) for v in g) for g in grid_thw], None, 0)
+
+    def advance_vision(self, st: "VisionTowerState", max_blocks: int) -> bool:
+        """Up to ``max_blocks`` more blocks (DeepStack taps are merged as their block completes); True when all have run."""
+        v = self.arch.vision
+        x = st.x
         N, vh, heads, hd = x.shape[0], v.hidden_size, v.num_heads, v.head_dim
-        deep: list[torch.Tensor] = []
-        for i, b in enumerate(self.vision_blocks):
+        end = min(len(self.vision_blocks), st.next_block + max(0, int(max_blocks)))
+        for i in range(st.next_block, end):
+            b = self.vision_blocks[i]
             h = ops.layernorm(x, b.norm1_w, b.norm1_b, v.layer_norm_eps)
             qkv = ops.linear(h, b.qkv_w, bias=b.qkv_b)
-            ops.vit_rope(qkv, coords, self.vit_inv_freq, heads, hd)
+            ops.vit_rope(qkv, st.coords, self.vit_inv_freq, heads, hd)
             q = qkv[:, :vh].view(N, heads, hd)
             k = qkv[:, vh:2 * vh].view(N, heads, hd)
             val = qkv[:, 2 * vh:].view(N, heads, hd)
-            a = ops.varlen_attention(q, k, val, cu, max_len, causal=False)
+            a = ops.varlen_attention(q, k, val, st.cu, st.max_len, causal=False)
             x = ops.linear(a.view(N, vh), b.proj_w, bias=b.proj_b, residual=x, out=x if x.is_cuda else None)
             h = ops.layernorm(x, b.norm2_w, b.norm2_b, v.layer_norm_eps)
             h = ops.linear(h, b.fc1_w, bias=b.fc1_b, act="gelu_tanh")
             x = ops.linear(h, b.fc2_w, bias=b.fc2_b, residual=x, out=x if x.is_cuda else None)
             if i in v.deepstack_visual_indexes:
                 k_idx = v.deepstack_visual_indexes.index(i)
-                deep.append(self._merge(x, self.mergers[f"deepstack.{k_idx}"], comm, 1 + k_idx, token_base))
-        return self._merge(x, self.mergers["main"], comm, 0, token_base), deep
+                st.deep.append(self._merge(x, self.mergers[f"deepstack.{k_idx}"], st.comm, 1 + k_idx, st.token_base))
+        st.x, st.next_block = x, end
+        return end == len(self.vision_blocks)
+
+    def finish_vision(self, st: "VisionTowerState"):
+        """Remaining blocks, then the main merger: merged visual tokens and the DeepStack features."""
+        if st.next_block < len(self.vision_blocks):
+            self.advance_vision(st, len(self.vision_blocks))
+        return self._merge(st.x, self.mergers["main"], st.comm, 0, st.token_base), st.deep
 
     def _merge(self, x: torch.Tensor, m: MergerWeights, comm=None, output: int = 0, token_base: int = 0):
         v = self.arch.vision

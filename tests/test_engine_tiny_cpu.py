@@ -392,6 +392,65 @@ def test_a_lone_prefill_on_a_lightly_loaded_engine_runs_atomically_and_a_deadlin
     llm.exit()
 
 
+def test_cooperative_prefill_runs_the_vision_tower_in_block_quanta(tiny):
+    """With a sequence decoding, the vision tower of a new image request runs one block per quantum with a decode step
+    after every quantum, then the language prefill in layer quanta; tokens equal the oracle's.  A request cancelled
+    while its tower is half run leaves nothing behind."""
+    arch, weights, oracle = tiny
+    tok = load_tokenizer("random:tiny", arch)
+    llm = _llm(weights, enable_cooperative_prefill=True, cooperative_prefill_layer_quantum=1, cooperative_prefill_vision_block_quantum=1)
+    free0 = llm.scheduler.block_manager.gpu.num_free
+    first = [3, 4, 5, 6, 7]
+    a_id = llm.add_request(first, SamplingParams(temperature=0.0, max_tokens=24, ignore_eos=True))
+    while llm.scheduler.num_decoding == 0:
+        llm.step_result()
+    img = prepare_image_inputs(PatchProcessor(arch), tok, [41, 42], [_image(9)])
+    b_id = llm.add_prepared_image_request(img, SamplingParams(temperature=0.0, max_tokens=4, ignore_eos=True))
+    phases, done = [], {}
+    while llm.request_state(b_id) is not None and llm.request_state(b_id).value in ("waiting", "prefilling"):
+        res = llm.step_result()
+        phases.append(res.phase.value)
+        for o in res.outputs:
+            if o.finished:
+                done[o.request_id] = list(o.token_ids)
+    c = llm.cooperative_counters
+    assert c["vision_block_quanta"] == arch.vision.depth == 2 and c["vision_quanta"] == 1 and c["layer_quantum_prefills"] == 1
+    # quantum (idle), decode, quantum (idle), then the prefill is begun with a decode step, layer quanta follow
+    assert phases[:4] == ["idle", "decode", "idle", "decode"] or phases[:5] == ["decode", "idle", "decode", "idle", "decode"], phases
+    # a second image request is cancelled after its first block quantum
+    img2 = prepare_image_inputs(PatchProcessor(arch), tok, [43, 44], [_image(10)])
+    c_id = llm.add_prepared_image_request(img2, SamplingParams(temperature=0.0, max_tokens=4, ignore_eos=True))
+    for _ in range(6):
+        llm.step_result()
+        if llm._pending_vision is not None:
+            break
+    assert llm._pending_vision is not None
+    assert llm.cancel_request(c_id) and llm._pending_vision is None
+    _drain(llm, done)
+    assert c_id not in done
+    assert done[a_id] == oracle.generate_greedy(first, 24)
+    assert done[b_id] == oracle.generate_greedy(img.input_ids, 4, pixel_values=img.pixel_values, image_grid_thw=img.image_grid_thw)
+    kept = llm.multimodal_prefix_cache_metadata()["resident_pages"]  # the first image's prefix stays cached
+    assert kept > 0 and llm.scheduler.block_manager.gpu.num_free == free0 - kept
+    assert not llm.runners.runner._pending_encodes and c_id not in llm.runners.runner._visual
+    llm.exit()
+
+
+def test_resumable_vision_tower_equals_the_one_piece_tower(tiny):
+    arch, weights, _ = tiny
+    llm = _llm(weights)
+    model = llm.runners.runner.model
+    inp = prepare_image_inputs(PatchProcessor(arch), load_tokenizer("random:tiny", arch), [1, 2], [_image(11), _image(12, 64)])
+    want_main, want_deep = model.encode_vision(inp.pixel_values, inp.image_grid_thw)
+    st = model.begin_vision(inp.pixel_values, inp.image_grid_thw)
+    assert not model.advance_vision(st, 1) and st.next_block == 1
+    assert len(st.deep) == sum(i < 1 for i in arch.vision.deepstack_visual_indexes)  # taps are merged as their block completes
+    assert model.advance_vision(st, 5) and st.next_block == 2
+    main, deep = model.finish_vision(st)
+    assert torch.equal(main, want_main) and len(deep) == len(want_deep) and all(torch.equal(a, b) for a, b in zip(deep, want_deep))
+    llm.exit()
+
+
 def test_visual_compaction_frees_pages_and_hits(tiny):
     arch, weights, _ = tiny
     img = _image(4)
