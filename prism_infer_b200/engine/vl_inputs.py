@@ -90,6 +90,19 @@ def smart_resize(h: int, w: int, factor: int, min_pixels: int, max_pixels: int) 
     return hb, wb
 
 
+def resize_bicubic(arr: np.ndarray, height: int, width: int) -> np.ndarray:
+    """``uint8 [H, W, 3]`` -> ``uint8 [height, width, 3]`` with the antialiased bicubic filter of Pillow, which is what
+    the Hugging Face image processor applies (within one grey level of it on random images; an interpolation without
+    antialiasing differs by tens of levels when an image is shrunk).  Without Pillow: torch's antialiased bicubic."""
+    try:
+        from PIL import Image
+    except ImportError:
+        t = torch.from_numpy(arr).permute(2, 0, 1).unsqueeze(0).float()
+        t = F.interpolate(t, size=(height, width), mode="bicubic", align_corners=False, antialias=True).clamp(0, 255)
+        return t.squeeze(0).permute(1, 2, 0).round().to(torch.uint8).numpy()
+    return np.asarray(Image.fromarray(arr).resize((width, height), resample=Image.BICUBIC))
+
+
 class PatchProcessor:
     def __init__(self, arch, *, min_pixels: int | None = None, max_pixels: int | None = None,
                  video_max_pixels: int | None = None) -> None:
@@ -120,9 +133,7 @@ class PatchProcessor:
         h, w = arr.shape[:2]
         nh, nw = smart_resize(h, w, self.factor, self.min_pixels, self.max_pixels)
         if (nh, nw) != (h, w):
-            t = torch.from_numpy(arr).permute(2, 0, 1).unsqueeze(0).float()
-            t = F.interpolate(t, size=(nh, nw), mode="bicubic", align_corners=False).clamp(0, 255)
-            arr = t.squeeze(0).permute(1, 2, 0).round().to(torch.uint8).numpy()
+            arr = resize_bicubic(arr, nh, nw)
         tp = self.arch.vision.temporal_patch_size
         return self._frames_to_patches(np.repeat(arr[None], tp, axis=0))
 
@@ -135,9 +146,7 @@ class PatchProcessor:
         nh, nw = smart_resize(h, w, self.factor, self.min_pixels, self.video_max_pixels)
         stack = np.stack(arrs)
         if (nh, nw) != (h, w):
-            t = torch.from_numpy(stack).permute(0, 3, 1, 2).float()
-            t = F.interpolate(t, size=(nh, nw), mode="bicubic", align_corners=False).clamp(0, 255)
-            stack = t.permute(0, 2, 3, 1).round().to(torch.uint8).numpy()
+            stack = np.stack([resize_bicubic(f, nh, nw) for f in stack])
         return self._frames_to_patches(stack)
 
     def tokens_for(self, grid: tuple[int, int, int]) -> int:

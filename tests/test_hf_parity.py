@@ -1,0 +1,151 @@
+"""Parity with the Hugging Face implementation of Qwen3-VL (``transformers.models.qwen3_vl``) on a tiny random-weight
+model, CPU, fp32: checkpoint tensor names and shapes, 3-axis rope indices, the vision tower with its DeepStack taps,
+last-token logits for image and video prompts, and greedy tokens of the engine.  The plain-PyTorch oracle of this
+package is what every kernel and engine test compares against; these tests tie the oracle to the upstream model code."""
+
+import numpy as np
+import pytest
+import torch
+
+from prism_infer_b200 import LLM, SamplingParams
+from prism_infer_b200.engine.vl_inputs import PatchProcessor, prepare_image_inputs, prepare_video_inputs
+from prism_infer_b200.models.architecture import Qwen3VLArch
+from prism_infer_b200.models.position import rope_index
+from prism_infer_b200.models.reference_model import ReferenceQwen3VL
+from prism_infer_b200.models.weights import random_weights
+from prism_infer_b200.utils.tokenizer import load_tokenizer
+
+hf_qwen3_vl = pytest.importorskip("transformers.models.qwen3_vl")
+
+
+@pytest.fixture(scope="module")
+def pair():
+    arch = Qwen3VLArch.tiny()
+    cfg = hf_qwen3_vl.Qwen3VLConfig(**arch.to_hf_config())
+    torch.manual_seed(0)
+    hf = hf_qwen3_vl.Qwen3VLForConditionalGeneration(cfg).eval().float()
+    g = torch.Generator().manual_seed(1)
+    weights = {}
+    for k, v in hf.state_dict().items():  # nothing left at its initial value: norm weights and biases are random too
+        base = 1.0 if ("norm" in k and k.endswith("weight")) else 0.0
+        weights[k] = torch.randn(v.shape, generator=g) * (0.05 if v.ndim > 1 else 0.2) + base
+    hf.load_state_dict(weights)
+    return arch, hf, weights, ReferenceQwen3VL(arch, weights)
+
+
+def _types(arch, ids):
+    mm = torch.zeros_like(ids, dtype=torch.int32)
+    mm[ids == arch.image_token_id] = 1
+    mm[ids == arch.video_token_id] = 2
+    return mm
+
+
+def _image(seed, h=224, w=224):
+    return np.random.default_rng(seed).integers(0, 256, (h, w, 3), dtype=np.uint8)
+
+
+def _hf_logits(arch, hf, inputs, extra_ids=()):
+    ids = torch.tensor([list(inputs.input_ids) + list(extra_ids)])
+    kw = {}
+    if hasattr(inputs, "image_grid_thw"):
+        kw.update(pixel_values=inputs.pixel_values.float(), image_grid_thw=torch.tensor(inputs.image_grid_thw))
+    else:
+        kw.update(pixel_values_videos=inputs.pixel_values.float(), video_grid_thw=torch.tensor(inputs.video_grid_thw))
+    with torch.no_grad():
+        out = hf(input_ids=ids, attention_mask=torch.ones_like(ids), mm_token_type_ids=_types(arch, ids), **kw)
+    return out.logits[0, -1]
+
+
+def test_checkpoint_tensor_names_and_shapes_are_the_upstream_ones(pair):
+    arch, hf, _, _ = pair
+    ours = random_weights(arch, dtype=torch.float32, seed=0)
+    theirs = hf.state_dict()
+    assert set(ours) == set(theirs)
+    assert all(tuple(ours[k].shape) == tuple(theirs[k].shape) for k in ours)
+
+
+@pytest.mark.parametrize("kind", ["images", "video", "text"])
+def test_rope_index_equals_upstream(pair, kind):
+    arch, hf, _, _ = pair
+    tok, proc = load_tokenizer("random:tiny", arch), PatchProcessor(arch)
+    kw = dict(image_grid_thw=None, video_grid_thw=None)
+    if kind == "images":
+        inp = prepare_image_inputs(proc, tok, [5, 6, 7], [_image(0), _image(1, 64, 96)])
+        ids, kw["image_grid_thw"] = inp.input_ids, inp.image_grid_thw
+    elif kind == "video":
+        inp = prepare_video_inputs(proc, tok, [5, 6, 7], [_image(s, 64, 64) for s in range(6)])
+        ids, kw["video_grid_thw"] = inp.input_ids, inp.video_grid_thw
+    else:
+        ids = list(range(10, 30))
+    pos, delta = rope_index(ids, image_token_id=arch.image_token_id, video_token_id=arch.video_token_id,
+                            spatial_merge_size=arch.vision.spatial_merge_size, **kw)
+    t = torch.tensor([ids])
+    hf_kw = {k: torch.tensor(v) for k, v in kw.items() if v is not None}
+    hpos, hdelta = hf.model.get_rope_index(t, _types(arch, t), attention_mask=torch.ones_like(t), **hf_kw)
+    assert torch.equal(pos[:, 0, :].long(), hpos[:, 0, :].long()) and int(delta) == int(hdelta)
+
+
+def test_vision_tower_and_deepstack_taps_equal_upstream(pair):
+    arch, hf, _, oracle = pair
+    inp = prepare_image_inputs(PatchProcessor(arch), load_tokenizer("random:tiny", arch), [1], [_image(2), _image(3, 96, 64)])
+    with torch.no_grad():
+        out = hf.model.visual(inp.pixel_values.float(), grid_thw=torch.tensor(inp.image_grid_thw))
+    main, deep = oracle.vision(inp.pixel_values.float(), inp.image_grid_thw)
+    assert float((main - out.pooler_output).abs().max()) < 1e-4
+    assert len(deep) == len(out.deepstack_features) == len(arch.vision.deepstack_visual_indexes)
+    for a, b in zip(deep, out.deepstack_features):
+        assert float((a - b).abs().max()) < 1e-4
+
+
+@pytest.mark.parametrize("kind", ["images", "video"])
+def test_last_token_logits_equal_upstream(pair, kind):
+    arch, hf, _, oracle = pair
+    tok, proc = load_tokenizer("random:tiny", arch), PatchProcessor(arch)
+    if kind == "images":
+        inp = prepare_image_inputs(proc, tok, [5, 6, 7, 8, 9], [_image(4), _image(5, 64, 96)])
+        kw = dict(pixel_values=inp.pixel_values, image_grid_thw=inp.image_grid_thw)
+    else:
+        inp = prepare_video_inputs(proc, tok, [5, 6, 7, 8, 9], [_image(s, 64, 64) for s in range(4)])
+        kw = dict(pixel_values=inp.pixel_values, video_grid_thw=inp.video_grid_thw)
+    _, logits = oracle.generate_greedy(inp.input_ids, 1, return_logits=True, **kw)
+    want = _hf_logits(arch, hf, inp)
+    assert float((logits[0] - want).abs().max()) < 1e-4 * max(1.0, float(want.abs().max()))
+
+
+def test_engine_greedy_tokens_equal_upstream_greedy_tokens(pair):
+    """The engine on CPU (paged KV, the 56-token prompt prefilled in two chunks) against token-by-token arg-max of the upstream model."""
+    arch, hf, weights, _ = pair
+    inp = prepare_image_inputs(PatchProcessor(arch), load_tokenizer("random:tiny", arch), [5, 6, 7, 8, 9], [_image(6)])
+    want, extra = [], []
+    for _ in range(6):
+        nxt = int(torch.argmax(_hf_logits(arch, hf, inp, extra)))
+        want.append(nxt)
+        extra.append(nxt)
+    llm = LLM("random:tiny", weights=weights, device="cpu", max_model_len=256, kvcache_block_size=16, num_kvcache_blocks=32,
+              enforce_eager=True, max_num_batched_tokens=256, max_chunk_size=52)
+    got = llm.generate_prepared_image_inputs(inp, SamplingParams(temperature=0.0, max_tokens=6, ignore_eos=True))["token_ids"]
+    llm.exit()
+    assert got == want
+
+
+def test_patch_processor_equals_the_upstream_image_processor():
+    """Same grid, same patch layout (temporal pair, merge-block order, channel / time / row / column inside a patch), same
+    normalisation; pixels within two grey levels where the image had to be resized (the upstream resize runs in torchvision)."""
+    transformers = pytest.importorskip("transformers")
+    from PIL import Image
+
+    from prism_infer_b200.engine.vl_inputs import IMAGE_MEAN, IMAGE_STD
+
+    arch = Qwen3VLArch.tiny()
+    ours = PatchProcessor(arch)
+    v = arch.vision
+    theirs = transformers.Qwen2VLImageProcessor(patch_size=v.patch_size, temporal_patch_size=v.temporal_patch_size, merge_size=v.spatial_merge_size,
+                                                image_mean=list(IMAGE_MEAN), image_std=list(IMAGE_STD),
+                                                size={"shortest_edge": ours.min_pixels, "longest_edge": ours.max_pixels})
+    for shape, exact in (((224, 224), True), ((64, 96), True), ((100, 130), False), ((37, 500), False), ((1000, 700), False)):
+        arr = _image(sum(shape), *shape)
+        mine, grid = ours.process_image(arr)
+        out = theirs(images=[Image.fromarray(arr)], return_tensors="pt")
+        assert list(grid) == out["image_grid_thw"][0].tolist()
+        diff = float((mine - out["pixel_values"]).abs().max())
+        assert diff < (1e-6 if exact else 2.1 / 127.5), (shape, diff)
