@@ -34,7 +34,6 @@ import torch.distributed as dist
 sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 
 from prism_infer_b200 import ops  # noqa: E402
-from prism_infer_b200.parallel import symm  # noqa: E402
 from prism_infer_b200.parallel.comm import FusedComm, NcclComm  # noqa: E402
 
 NVLINK_GBS = 770.0

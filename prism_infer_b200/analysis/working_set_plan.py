@@ -18,7 +18,7 @@ from __future__ import annotations
 import hashlib
 import random
 from bisect import bisect_left
-from dataclasses import dataclass, field
+from dataclasses import dataclass
 from typing import Any, Mapping, Sequence
 
 DEFAULT_SEED = 20260801

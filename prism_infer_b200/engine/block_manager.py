@@ -20,7 +20,7 @@ from __future__ import annotations
 
 import hashlib
 import struct
-from dataclasses import dataclass, field
+from dataclasses import dataclass
 from typing import Sequence as Seq
 
 from .block_pool import CpuBlockPool, GpuBlockPool, OutOfBlocks

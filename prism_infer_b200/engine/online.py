@@ -29,7 +29,6 @@ import numpy as np
 import torch
 
 from ..sampling_params import SamplingParams
-from .contracts import Phase
 from .vl_inputs import ImageInputs, VideoInputs, image_block, to_uint8_hwc, video_blocks
 
 PAYLOAD_TYPES = ("text", "image", "images", "interleaved_images", "video")
