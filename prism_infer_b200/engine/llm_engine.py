@@ -12,6 +12,7 @@ from __future__ import annotations
 
 import atexit
 import hashlib
+import os
 import time
 from typing import Any, Sequence as Seq
 
@@ -30,7 +31,7 @@ from .progress import GenerationProgress
 from .request import RequestIdAllocator, RequestState
 from .scheduler import Scheduler
 from .sequence import Sequence
-from .vl_inputs import (ImageInputs, PatchProcessor, VideoInputs, prepare_image_inputs,
+from .vl_inputs import (ImageInputs, PatchProcessor, VideoInputs, checkpoint_pixel_budgets, prepare_image_inputs,
                         prepare_interleaved_image_inputs, prepare_video_inputs)
 
 
@@ -85,8 +86,12 @@ class LLMEngine:
         if runner_group is None:
             self._validate_environment(device)
         self.tokenizer = load_tokenizer(cfg.model, self.arch)
-        self.processor = PatchProcessor(self.arch, min_pixels=cfg.image_min_pixels, max_pixels=cfg.image_max_pixels,
-                                        video_max_pixels=cfg.video_max_pixels)
+        # options given by the caller win; otherwise the budgets the checkpoint's own processor files record
+        recorded = checkpoint_pixel_budgets(cfg.model) if os.path.isdir(str(cfg.model)) else {}
+        self.processor = PatchProcessor(self.arch, min_pixels=cfg.image_min_pixels or recorded.get("min_pixels"),
+                                        max_pixels=cfg.image_max_pixels or recorded.get("max_pixels"),
+                                        video_max_pixels=cfg.video_max_pixels or recorded.get("video_max_pixels"),
+                                        video_min_pixels=recorded.get("video_min_pixels"))
         from .chat_prompt import ChatPrompt, HFProcessorAdapter
 
         mode = cfg.chat_template

@@ -90,6 +90,27 @@ def smart_resize(h: int, w: int, factor: int, min_pixels: int, max_pixels: int) 
     return hb, wb
 
 
+def smart_resize_video(num_frames: int, h: int, w: int, temporal_factor: int, factor: int, min_pixels: int, max_pixels: int) -> tuple[int, int]:
+    """Frame size of a clip under a budget on its whole volume (frames x height x width, frames rounded up to the
+    temporal patch), the rule of the Hugging Face Qwen3-VL video processor: sides rounded to ``factor``, shrunk when the
+    volume exceeds ``max_pixels``, enlarged when it is below ``min_pixels``."""
+    if h < factor or w < factor:
+        raise ValueError(f"height {h} or width {w} is smaller than the resize factor {factor}")
+    if max(h, w) / min(h, w) > 200:
+        raise ValueError(f"aspect ratio {max(h, w) / min(h, w):.1f} exceeds 200")
+    hb, wb = round(h / factor) * factor, round(w / factor) * factor
+    tb = math.ceil(num_frames / temporal_factor) * temporal_factor
+    if tb * hb * wb > max_pixels:
+        beta = math.sqrt(num_frames * h * w / max_pixels)
+        hb = max(factor, math.floor(h / beta / factor) * factor)
+        wb = max(factor, math.floor(w / beta / factor) * factor)
+    elif tb * hb * wb < min_pixels:
+        beta = math.sqrt(min_pixels / (num_frames * h * w))
+        hb = math.ceil(h * beta / factor) * factor
+        wb = math.ceil(w * beta / factor) * factor
+    return hb, wb
+
+
 def resize_bicubic(arr: np.ndarray, height: int, width: int) -> np.ndarray:
     """``uint8 [H, W, 3]`` -> ``uint8 [height, width, 3]`` with the antialiased bicubic filter of Pillow, which is what
     the Hugging Face image processor applies (within one grey level of it on random images; an interpolation without
@@ -103,15 +124,54 @@ def resize_bicubic(arr: np.ndarray, height: int, width: int) -> np.ndarray:
     return np.asarray(Image.fromarray(arr).resize((width, height), resample=Image.BICUBIC))
 
 
+def checkpoint_pixel_budgets(model_dir: str) -> dict[str, int]:
+    """Pixel budgets a checkpoint directory records for its processor: ``min_pixels`` / ``max_pixels`` from
+    ``preprocessor_config.json`` (``size.shortest_edge`` / ``size.longest_edge``, or the older ``min_pixels`` /
+    ``max_pixels`` keys) and ``video_min_pixels`` / ``video_max_pixels`` (budgets on frames x height x width) from
+    ``video_preprocessor_config.json``.  Missing files or keys are
+    simply absent from the result; an image smaller than the checkpoint's minimum is then enlarged exactly as the
+    checkpoint's own processor would."""
+    import json
+    import os
+
+    def read(name: str) -> dict:
+        path = os.path.join(model_dir, name)
+        if not os.path.isfile(path):
+            return {}
+        with open(path, encoding="utf-8") as fh:
+            value = json.load(fh)
+        return value if isinstance(value, dict) else {}
+
+    def budget(cfg: dict, size_key: str, flat_key: str):
+        size = cfg.get("size")
+        v = size.get(size_key) if isinstance(size, dict) else None
+        v = cfg.get(flat_key) if v is None else v
+        return int(v) if isinstance(v, (int, float)) and not isinstance(v, bool) and v > 0 else None
+
+    out: dict[str, int] = {}
+    image, video = read("preprocessor_config.json"), read("video_preprocessor_config.json")
+    for key, cfg, size_key, flat in (("min_pixels", image, "shortest_edge", "min_pixels"), ("max_pixels", image, "longest_edge", "max_pixels"),
+                                     ("video_min_pixels", video, "shortest_edge", "min_pixels"),
+                                     ("video_max_pixels", video, "longest_edge", "max_pixels")):
+        v = budget(cfg, size_key, flat)
+        if v is not None:
+            out[key] = v
+    return out
+
+
 class PatchProcessor:
+    """Images: per-image pixel budget (``min_pixels`` .. ``max_pixels``).  Clips: budget on the volume frames x height x
+    width (``video_min_pixels`` .. ``video_max_pixels``), as the checkpoint's video processor counts it."""
+
     def __init__(self, arch, *, min_pixels: int | None = None, max_pixels: int | None = None,
-                 video_max_pixels: int | None = None) -> None:
+                 video_max_pixels: int | None = None, video_min_pixels: int | None = None) -> None:
         self.arch = arch
         v = arch.vision
         self.factor = v.patch_size * v.spatial_merge_size
         self.min_pixels = min_pixels or 4 * self.factor * self.factor
         self.max_pixels = max_pixels or 16384 * self.factor * self.factor
-        self.video_max_pixels = video_max_pixels or self.max_pixels
+        self.video_max_pixels = video_max_pixels or 24 * self.max_pixels // 16   # 25.2 M: the 8B checkpoint's recorded volume budget
+        self.video_min_pixels = video_min_pixels or self.factor * self.factor * 4
 
     def _frames_to_patches(self, frames: np.ndarray) -> tuple[torch.Tensor, tuple[int, int, int]]:
         """``uint8 [F, H, W, 3]`` (F a multiple of the temporal patch) -> patches, grid."""
@@ -143,7 +203,7 @@ class PatchProcessor:
         while len(arrs) % tp:
             arrs.append(arrs[-1])
         h, w = arrs[0].shape[:2]
-        nh, nw = smart_resize(h, w, self.factor, self.min_pixels, self.video_max_pixels)
+        nh, nw = smart_resize_video(len(arrs), h, w, tp, self.factor, self.video_min_pixels, self.video_max_pixels)
         stack = np.stack(arrs)
         if (nh, nw) != (h, w):
             stack = np.stack([resize_bicubic(f, nh, nw) for f in stack])

@@ -133,3 +133,48 @@ def test_prompts_equal_the_reference_builders(synthetic_checkpoint):
     assert chat.image_prompt("t5 t6", 2) == build_image_prompt(proc, "t5 t6", [img, img])
     assert chat.interleaved_image_prompt("t1 <image> t2 <image>", 2) == build_interleaved_image_prompt(proc, "t1 <image> t2 <image>", [img, img])
     assert chat.video_prompt("t9") == build_video_prompt(proc, "t9", [img, img])
+
+
+def test_native_input_preparation_equals_the_checkpoint_processor(synthetic_checkpoint):
+    """``HFProcessorAdapter`` (the checkpoint's own Hugging Face processor) and the built-in preparation give the same
+    token ids, grids and (within the resize tolerance) patches for images, and the same ids and grid for a clip with
+    time stamps."""
+    from transformers import AutoTokenizer
+
+    from prism_infer_b200.engine.chat_prompt import HFProcessorAdapter, has_processor_files
+
+    path, arch = synthetic_checkpoint
+    tok = AutoTokenizer.from_pretrained(path)
+    if not os.path.exists(os.path.join(path, "chat_template.jinja")):
+        with open(os.path.join(path, "chat_template.jinja"), "w") as fh:
+            fh.write(tok.chat_template)
+    assert has_processor_files(path)
+    adapter = HFProcessorAdapter(path)
+    chat = ChatPrompt(tok)
+    from prism_infer_b200.engine.vl_inputs import checkpoint_pixel_budgets
+
+    budgets = checkpoint_pixel_budgets(path)
+    assert budgets == {"min_pixels": 65536, "max_pixels": 16777216, "video_min_pixels": 4096, "video_max_pixels": 25165824}
+    native = PatchProcessor(arch, **budgets)  # what the engine does for a checkpoint directory
+    images = [_img(0, 64), np.random.default_rng(5).integers(0, 256, (100, 130, 3), dtype=np.uint8)]  # both below the minimum: enlarged
+    mine = prepare_image_inputs(native, tok, "t5 t6 t7", images, chat=chat)
+    theirs = adapter.image_inputs(adapter.chat.image_prompt("t5 t6 t7", 2), images)
+    assert mine.input_ids == theirs.input_ids and [tuple(g) for g in mine.image_grid_thw] == [tuple(g) for g in theirs.image_grid_thw]
+    assert mine.pixel_values.shape == theirs.pixel_values.shape
+    assert float((mine.pixel_values - theirs.pixel_values).abs().max()) < 2.1 / 127.5
+    frames = [_img(s, 64) for s in range(4)]
+    timing = VideoTiming((0, 12, 24, 36), 24.0)
+    mine_v = prepare_video_inputs(native, tok, "t5 t6", frames, chat=chat, timing=timing)
+    theirs_v = adapter.video_inputs(adapter.chat.video_prompt("t5 t6"), frames, timing)
+    assert [tuple(g) for g in mine_v.video_grid_thw] == [tuple(g) for g in theirs_v.video_grid_thw]
+    assert float((mine_v.pixel_values - theirs_v.pixel_values).abs().max()) < 1e-5
+    # the token ids of the clip cannot be compared on this synthetic checkpoint: its whitespace-split word-level vocabulary
+    # needs blanks between the special tokens of the template, and the upstream processor looks for the unbroken run
+    # "<|vision_start|><|video_pad|><|vision_end|>" when it inserts the per-group time stamps
+    # a clip whose volume exceeds the budget is shrunk the way the upstream video processor shrinks it
+    from transformers.models.qwen3_vl.video_processing_qwen3_vl import smart_resize as upstream_resize
+
+    from prism_infer_b200.engine.vl_inputs import smart_resize_video
+
+    for n, h, w, lo, hi in ((16, 448, 448, 4096, 25165824), (64, 720, 1280, 4096, 25165824), (3, 40, 64, 65536, 10 ** 7), (7, 333, 517, 4096, 2 * 10 ** 5)):
+        assert smart_resize_video(n, h, w, 2, 32, lo, hi) == upstream_resize(n, h, w, 2, 32, lo, hi)

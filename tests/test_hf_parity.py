@@ -149,3 +149,22 @@ def test_patch_processor_equals_the_upstream_image_processor():
         assert list(grid) == out["image_grid_thw"][0].tolist()
         diff = float((mine - out["pixel_values"]).abs().max())
         assert diff < (1e-6 if exact else 2.1 / 127.5), (shape, diff)
+
+
+def test_a_checkpoint_saved_by_the_upstream_model_loads_and_generates_the_same_tokens(pair, tmp_path):
+    """``save_pretrained`` of the upstream model (config.json + safetensors) -> ``LLM(directory)``: the configuration
+    parser and the safetensors routing see exactly what a real checkpoint directory holds."""
+    arch, hf, _, _ = pair
+    hf.save_pretrained(tmp_path / "ckpt", safe_serialization=True)
+    assert Qwen3VLArch.from_pretrained(str(tmp_path / "ckpt")) == arch
+    inp = prepare_image_inputs(PatchProcessor(arch), load_tokenizer("random:tiny", arch), [9, 8, 7], [_image(7, 64, 96)])
+    want, extra = [], []
+    for _ in range(5):
+        nxt = int(torch.argmax(_hf_logits(arch, hf, inp, extra)))
+        want.append(nxt)
+        extra.append(nxt)
+    llm = LLM(str(tmp_path / "ckpt"), device="cpu", max_model_len=256, kvcache_block_size=16, num_kvcache_blocks=32,
+              enforce_eager=True, max_num_batched_tokens=256, max_chunk_size=256)
+    got = llm.generate_prepared_image_inputs(inp, SamplingParams(temperature=0.0, max_tokens=5, ignore_eos=True))["token_ids"]
+    llm.exit()
+    assert got == want
