@@ -612,3 +612,50 @@ def test_options_document_lists_every_flat_option():
     root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
     with open(os.path.join(root, "docs", "OPTIONS.md")) as fh:
         assert fh.read() == describe_options.markdown(), "run: python -m prism_infer_b200.utils.describe_options > docs/OPTIONS.md"
+
+
+def test_environment_check_reports_checkpoint_and_plan_problems(tmp_path, capsys):
+    """The environment tool passes on a sound checkpoint directory, names every defect of a broken one, refuses a
+    tensor-parallel size the model cannot be split into, and its exit status follows the errors (warnings do not)."""
+    import json
+
+    from prism_infer_b200.models.architecture import Qwen3VLArch
+    from prism_infer_b200.utils import check_environment as ce
+
+    arch = Qwen3VLArch.tiny()
+    good = tmp_path / "good"
+    good.mkdir()
+    (good / "config.json").write_text(json.dumps(arch.to_hf_config()))
+    (good / "model.safetensors").write_bytes(b"\0" * 2048)
+    rc = ce.main(["--allow-cpu", "--model", str(good), "--json"])
+    rep = json.loads(capsys.readouterr().out)
+    assert rc == 0 and rep["status"] == "pass" and rep["model"]["weight_files"] == 1 and rep["model"]["text"]["kv_heads"] == 2
+    assert len(rep["model"]["config_sha256"]) == 64 and rep["kernel_library"]["path"].endswith("libprism_b200.so")
+    assert any("tokenizer_config.json" in w for w in rep["warnings"])  # recommended, not required
+    assert rep["planned_run"] == {"execution_backend": "cuda_graph", "compression_mode": "scaled_fp8_kv", "tensor_parallel_size": 1,
+                                  "require_cuda": False}
+    # two KV heads cannot be split over four ranks
+    rc = ce.main(["--allow-cpu", "--model", str(good), "--tensor-parallel-size", "4", "--json"])
+    rep = json.loads(capsys.readouterr().out)
+    assert rc == 1 and any("configuration rejected" in e for e in rep["errors"])
+    bad = tmp_path / "bad"
+    bad.mkdir()
+    (bad / "config.json").write_text(json.dumps({"model_type": "llama", "architectures": ["LlamaForCausalLM"]}))
+    rc = ce.main(["--allow-cpu", "--model", str(bad), "--json"])
+    rep = json.loads(capsys.readouterr().out)
+    assert rc == 1 and any("no *.safetensors" in e for e in rep["errors"]) and any("does not describe a Qwen3-VL" in e for e in rep["errors"])
+    assert ce.main(["--allow-cpu", "--model", str(tmp_path / "nowhere"), "--json"]) == 1
+    capsys.readouterr()
+    assert ce.main(["--allow-cpu", "--model", "random:nope", "--json"]) == 1
+    capsys.readouterr()
+    # without --allow-cpu a machine without a CUDA device fails; --min-free-gib needs a device to look at
+    import torch
+
+    if not torch.cuda.is_available():
+        assert ce.main(["--model", "random:tiny", "--json"]) == 1
+        rep = json.loads(capsys.readouterr().out)
+        assert any("no CUDA device" in e for e in rep["errors"])
+        assert ce.main(["--allow-cpu", "--min-free-gib", "1", "--json"]) == 1
+        capsys.readouterr()
+    assert ce.main(["--allow-cpu", "--model", "random:tiny"]) == 0
+    assert "result: PASS" in capsys.readouterr().out
