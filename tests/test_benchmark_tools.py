@@ -305,3 +305,48 @@ def test_working_set_plan_from_materialised_records(tmp_path):
     victim.write_bytes(victim.read_bytes() + b"0")
     with pytest.raises(OSError, match="mismatch"):
         loader(d["sha256"])
+
+
+def test_online_benchmark_workload_options_and_profile(tmp_path):
+    """``bench_online`` pieces on the tiny model: engine options from flags and key=value pairs, the three arrival
+    processes, and a run with the SLO-aware policy, cooperative prefill, warm-up requests, deadlines and a profile file."""
+    import argparse
+
+    import torch
+
+    from prism_infer_b200 import LLM
+    from prism_infer_b200.analysis import online_serving
+    from prism_infer_b200.analysis import working_set_plan as wsp
+    from prism_infer_b200.analysis.performance_profile import validate_profile_record
+    from prism_infer_b200.models.architecture import Qwen3VLArch
+    from prism_infer_b200.models.weights import random_weights
+
+    b = _load("bench_online")
+    ns = argparse.Namespace(variant="dense_prefix", engine_option=["max_num_seqs=4", "scheduler_policy=fcfs", "note=free text"],
+                            **{flag.lstrip("-").replace("-", "_"): None for flag in b.ENGINE_FLAGS})
+    ns.scheduler_policy, ns.enable_cooperative_prefill, ns.cooperative_prefill_coalesce_ms = "slo_aware", True, 0.0
+    opts = b.engine_options(ns)
+    assert opts["scheduler_policy"] == "fcfs" and opts["max_num_seqs"] == 4 and opts["note"] == "free text"  # key=value pairs win
+    assert opts["enable_cooperative_prefill"] is True and opts["enable_prefix_caching"] is True and "cooperative_prefill_coalesce_ms" in opts
+    groups = wsp.synthetic_groups(3, 7, seed=5, min_images=1, max_images=2, tokens_per_image=6, page=16)
+    plan = wsp.build_plan(groups, num_requests=6, rate=200.0, seed=5, page_budget=64)
+    assert b.arrival_offsets(plan, "burst", 200.0) == [0.0] * 6
+    assert b.arrival_offsets(plan, "uniform", 200.0) == [i / 200.0 for i in range(6)]
+    assert b.arrival_offsets(plan, "poisson", 200.0) == [r.arrival_offset_s for r in plan.measured]
+
+    arch = Qwen3VLArch.tiny()
+    llm = LLM("random:tiny", weights=random_weights(arch, dtype=torch.float32, seed=0), device="cpu", max_model_len=512, kvcache_block_size=16,
+              num_kvcache_blocks=128, enforce_eager=True, max_num_batched_tokens=512, max_chunk_size=512, enable_prefix_caching=True,
+              compression_mode="scaled_fp8_kv", scheduler_policy="slo_aware", enable_cooperative_prefill=True,
+              cooperative_prefill_layer_quantum=1, max_num_seqs=4)
+    prof = tmp_path / "profile.json"
+    out = b.run_workload(llm, plan, lambda d: b.image_for(d, 64), max_tokens=3, arrival_process="uniform", rate=200.0, ttft_slo_ms=5000.0,
+                         warmup_requests=2, profile_output=str(prof))
+    summary = out["summary"]
+    assert summary["requests"] == {"total": 6, "completed": 6, "rejected": 0, "cancelled": 0} and summary["output_tokens"] == 18
+    assert summary["ttft_ms"]["count"] == 6 and summary["queue_ms"]["count"] in (0, 6)
+    assert llm.multimodal_prefix_cache_metadata()["hits"] >= 6  # every measured request reuses its group's prefix
+    validate_profile_record(json.loads(prof.read_text()))
+    assert online_serving.summarize_online_run({"duration_s": out["result"].duration_s,
+                                                "requests": [r.to_record() for r in out["result"].requests]})["requests_per_s"] > 0
+    llm.exit()
