@@ -350,3 +350,26 @@ def test_online_benchmark_workload_options_and_profile(tmp_path):
     assert online_serving.summarize_online_run({"duration_s": out["result"].duration_s,
                                                 "requests": [r.to_record() for r in out["result"].requests]})["requests_per_s"] > 0
     llm.exit()
+
+
+def test_paged_decode_benchmark_sweeps_and_gates(tmp_path):
+    """The paged-decode micro-benchmark on CPU: a sweep over cache formats, page size, context lengths and batch sizes
+    writes one row per case with its difference to the plain-PyTorch statement; gates that cannot be met fail the run;
+    an existing output is not overwritten silently."""
+    import pytest
+
+    b = _load("bench_paged_decode")
+    out = tmp_path / "pd.json"
+    common = ["--device", "cpu", "--batch-sizes", "1,3", "--context-lens", "37,64", "--page-sizes", "16", "--cache-dtypes", "scaled_fp8,fp8,bf16",
+              "--num-heads", "4", "--num-kv-heads", "2", "--head-dim", "64", "--repeat", "1", "--warmup", "0"]
+    assert b.main(common + ["--output", str(out)]) == 0
+    rec = json.loads(out.read_text())
+    assert rec["passed"] and len(rec["rows"]) == 3 * 2 * 2 and {r["cache_dtype"] for r in rec["rows"]} == {"scaled_fp8", "fp8", "bf16"}
+    row = next(r for r in rec["rows"] if r["cache_dtype"] == "scaled_fp8" and r["batch"] == 3 and r["context_len"] == 37)
+    assert row["kv_bytes"] == 2 * 3 * 37 * 2 * 64 * 1 + 2 * 3 * 37 * 2 * 4 and row["max_abs_diff"] <= 2e-2
+    with pytest.raises(SystemExit):
+        b.main(common + ["--output", str(out)])                       # exists
+    assert b.main(common + ["--output", str(out), "--overwrite", "--max-abs-diff", "-1"]) == 1
+    assert json.loads(out.read_text())["passed"] is False
+    with pytest.raises(SystemExit):
+        b.main(["--device", "cpu", "--cache-dtypes", "int4"])
