@@ -373,3 +373,27 @@ def test_paged_decode_benchmark_sweeps_and_gates(tmp_path):
     assert json.loads(out.read_text())["passed"] is False
     with pytest.raises(SystemExit):
         b.main(["--device", "cpu", "--cache-dtypes", "int4"])
+
+
+def test_kv_capacity_accounting_and_measured_mode(tmp_path, capsys):
+    """Accounting gives the documented ratio; the measured mode on the tiny model shows the scaled-FP8 engine holding about
+    twice the sequences of the bf16 engine at the same byte budget."""
+    b = _load("bench_kv_capacity")
+    acc = b.accounting("random:qwen3-vl-8b", 4_282_122_240, 1)
+    assert acc["off"]["pages"] == 113 and acc["scaled_fp8_kv"]["pages"] == 220 and acc["scaled_over_bf16_bytes"] == 0.515625
+    manifest = {"schema_version": 1, "name": "t", "cases": [{"id": "img", "requests": [
+        {"type": "image", "prompt": "7 8 9", "image": {"width": 224, "height": 224, "seed": 1}}]}]}
+    path = tmp_path / "m.json"
+    path.write_text(json.dumps(manifest))
+    tiny_acc = b.accounting("random:tiny", 10 * 1024 * 1024, 1, page_tokens=16, modes=("off", "scaled_fp8_kv"))
+    rc = b.main(["--measure", "--model", "random:tiny", "--device", "cpu", "--budget-bytes", str(24 * tiny_acc["off"]["bytes_per_page"]),
+                 "--page-tokens", "16", "--manifest", str(path), "--case", "img", "--requests", "6", "--max-tokens", "3", "--max-model-len", "256",
+                 "--modes", "off", "scaled_fp8_kv", "--output", str(tmp_path / "cap.json")])
+    capsys.readouterr()
+    assert rc == 0
+    rec = json.loads((tmp_path / "cap.json").read_text())
+    dense, scaled = rec["measured"]
+    assert dense["pages"] == 24 and scaled["pages"] == int(24 / 0.53125) == 45  # 64-wide heads: one fp32 scale per 64 payload bytes
+    assert dense["completed"] == scaled["completed"] == 6 and dense["prompt_pages_per_request"] == scaled["prompt_pages_per_request"] == 4
+    assert dense["sequences_that_fit_by_pages"] == 6 and scaled["sequences_that_fit_by_pages"] == 11
+    assert scaled["preempted"] == 0 and scaled["peak_resident_sequences"] == 6
