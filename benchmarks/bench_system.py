@@ -5,7 +5,11 @@ eager against CUDA-graph decode, BF16 against FP8 / scaled-FP8 KV, dense against
 visual context).
 
     python benchmarks/bench_system.py [--modes eager graph ...] [--workloads single_image_448 ...]
-                                      [--tensor-parallel-size N] [--batch 1] [--out records.json]
+                                      [--tensor-parallel-size N] [--batch-sizes 1 8] [--output-lengths 32 128]
+                                      [--visual-pruning-keep-ratios 0.4 0.6] [--profile-output prof.json] [--out records.json]
+
+Batch sizes and output lengths are swept inside one engine per mode; keep ratios (compacting and pruning modes only) get
+an engine each.  ``--profile-output`` writes the performance profile of the last timed cell.
 """
 
 from __future__ import annotations
@@ -158,52 +162,81 @@ def run_cell(llm, wl: dict, batch: int, rng, *, repeats: int = 1) -> dict:
     }
 
 
-def main() -> None:
-    ap = argparse.ArgumentParser()
+def main(argv=None) -> None:
+    ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     ap.add_argument("--modes", nargs="*", default=["eager", "graph", "graph_scaled_fp8_kv", "graph_visual_compact_scaled_fp8"])
     ap.add_argument("--workloads", nargs="*", default=["single_image_448", "eight_image_448"])
     ap.add_argument("--tensor-parallel-size", type=int, default=1)
     ap.add_argument("--batch", type=int, default=1)
+    ap.add_argument("--batch-sizes", type=int, nargs="*", default=None, help="sweep; overrides --batch")
+    ap.add_argument("--output-lengths", type=int, nargs="*", default=None, help="sweep of output tokens; default: the workload's own")
+    ap.add_argument("--visual-pruning-keep-ratios", type=float, nargs="*", default=None, help="sweep for modes that drop visual tokens")
+    ap.add_argument("--profile-output", default="")
+    ap.add_argument("--quiet", action="store_true")
     ap.add_argument("--repeats", type=int, default=3, help="timed rounds per (mode, workload)")
     ap.add_argument("--device", default=None)
     ap.add_argument("--page-tokens", type=int, default=256)
     ap.add_argument("--model", default="random:qwen3-vl-8b")
     ap.add_argument("--max-model-len", type=int, default=8192)
     ap.add_argument("--out", default="")
-    args = ap.parse_args()
+    args = ap.parse_args(argv)
     records = []
     provenance = harness.provenance()
+    batches = args.batch_sizes or [args.batch]
+    profile = None
     for mode in args.modes:
         if mode not in MODES:
             raise SystemExit(f"unknown mode {mode!r}; known: {sorted(MODES)}")
-        opts = dict(MODES[mode])
-        llm = LLM(args.model, device=args.device, tensor_parallel_size=args.tensor_parallel_size, max_model_len=args.max_model_len,
-                  kvcache_block_size=args.page_tokens,
-                  num_kvcache_blocks=max(64, args.batch * 24), max_num_seqs=max(args.batch, 1), max_num_batched_tokens=16384,
-                  max_chunk_size=8192, cpu_kv_cache_ratio=0.0, enable_prefix_caching=False, **opts)
-        if not llm.is_driver:
-            llm.serve_forever()
-            continue
-        rng = np.random.default_rng(0)
-        for name in args.workloads:
-            wl = load_workload(name)
-            cell = run_cell(llm, wl, args.batch, rng, repeats=args.repeats)
-            res = cell["results"]
-            rec = {"schema_version": benchmark_schema.BENCHMARK_SCHEMA_VERSION, "benchmark": "system_mode_matrix", "engine": "prism_infer_b200",
-                   "model": args.model, "data": "synthetic", "hardware": {"gpus": args.tensor_parallel_size},
-                   "config": {"mode": mode, "workload": name, **{k: v for k, v in opts.items()}, "tp": args.tensor_parallel_size,
-                              "repeats": args.repeats, "output_tokens": wl["output_tokens"]},
-                   "results": res, "execution": cell["execution"], "correctness": cell["correctness"], "kv_cache": cell["kv_cache"],
-                   "provenance": provenance}
-            benchmark_schema.validate_benchmark_record(rec)
-            records.append(rec)
-            print(json.dumps({"mode": mode, "workload": name, **{k: (round(v, 3) if isinstance(v, float) else v) for k, v in res.items() if k != "stats"},
-                              "graph_replays": cell["execution"]["graph_replays"], "eager_decode_steps": cell["execution"]["eager_decode_steps"]}),
-                  flush=True)
-        llm.exit()
+        ratios = args.visual_pruning_keep_ratios if (args.visual_pruning_keep_ratios and "visual_pruning_keep_ratio" in MODES[mode]) else [None]
+        for ratio in ratios:
+            opts = dict(MODES[mode])
+            if ratio is not None:
+                opts["visual_pruning_keep_ratio"] = ratio
+            llm = LLM(args.model, device=args.device, tensor_parallel_size=args.tensor_parallel_size, max_model_len=args.max_model_len,
+                      kvcache_block_size=args.page_tokens,
+                      num_kvcache_blocks=max(64, max(batches) * 24), max_num_seqs=max(max(batches), 1), max_num_batched_tokens=16384,
+                      max_chunk_size=8192, cpu_kv_cache_ratio=0.0, enable_prefix_caching=False, **opts)
+            if not llm.is_driver:
+                llm.serve_forever()
+                continue
+            rng = np.random.default_rng(0)
+            for name in args.workloads:
+                for n_out in (args.output_lengths or [None]):
+                    wl = load_workload(name)
+                    if n_out is not None:
+                        wl["output_tokens"] = n_out
+                    for batch in batches:
+                        if args.profile_output:
+                            from prism_infer_b200.analysis.performance_profile import performance_profile
+
+                            with performance_profile({"mode": mode, "workload": name, "batch": batch}, nvtx=False) as session:
+                                cell = run_cell(llm, wl, batch, rng, repeats=args.repeats)
+                            profile = session.finalize()
+                        else:
+                            cell = run_cell(llm, wl, batch, rng, repeats=args.repeats)
+                        res = cell["results"]
+                        rec = {"schema_version": benchmark_schema.BENCHMARK_SCHEMA_VERSION, "benchmark": "system_mode_matrix",
+                               "engine": "prism_infer_b200", "model": args.model, "data": "synthetic", "hardware": {"gpus": args.tensor_parallel_size},
+                               "config": {"mode": mode, "workload": name, **{k: v for k, v in opts.items()}, "tp": args.tensor_parallel_size,
+                                          "repeats": args.repeats, "output_tokens": wl["output_tokens"]},
+                               "results": res, "execution": cell["execution"], "correctness": cell["correctness"], "kv_cache": cell["kv_cache"],
+                               "provenance": provenance}
+                        benchmark_schema.validate_benchmark_record(rec)
+                        records.append(rec)
+                        if not args.quiet:
+                            print(json.dumps({"mode": mode, "workload": name, "keep_ratio": ratio, "output_tokens": wl["output_tokens"],
+                                              **{k: (round(v, 3) if isinstance(v, float) else v) for k, v in res.items() if k != "stats"},
+                                              "graph_replays": cell["execution"]["graph_replays"],
+                                              "eager_decode_steps": cell["execution"]["eager_decode_steps"]}), flush=True)
+            llm.exit()
     if args.out:
         with open(args.out, "w") as fh:
             json.dump(records, fh, indent=1)
+    if args.profile_output and profile is not None:
+        from prism_infer_b200.analysis.performance_profile import validate_profile_record
+
+        with open(args.profile_output, "w") as fh:
+            json.dump(validate_profile_record(profile), fh, indent=1)
 
 
 if __name__ == "__main__":

@@ -397,3 +397,26 @@ def test_kv_capacity_accounting_and_measured_mode(tmp_path, capsys):
     assert dense["completed"] == scaled["completed"] == 6 and dense["prompt_pages_per_request"] == scaled["prompt_pages_per_request"] == 4
     assert dense["sequences_that_fit_by_pages"] == 6 and scaled["sequences_that_fit_by_pages"] == 11
     assert scaled["preempted"] == 0 and scaled["peak_resident_sequences"] == 6
+
+
+def test_system_benchmark_main_sweeps_on_the_tiny_model(tmp_path, capsys):
+    """``bench_system.main`` end to end on CPU: two eager modes (one of them dropping visual tokens at two keep ratios),
+    two batch sizes and two output lengths on the text workload give one valid record per cell, and the profile of the
+    last cell is written."""
+    from prism_infer_b200.analysis import benchmark_schema as bs
+    from prism_infer_b200.analysis.performance_profile import validate_profile_record
+
+    b = _load("bench_system")
+    out, prof = tmp_path / "records.json", tmp_path / "profile.json"
+    b.main(["--model", "random:tiny", "--device", "cpu", "--modes", "eager", "eager_visual_prune", "--workloads", "text_256", "--batch-sizes", "1", "2",
+            "--output-lengths", "2", "3", "--visual-pruning-keep-ratios", "0.5", "0.75", "--repeats", "2", "--page-tokens", "16",
+            "--max-model-len", "512", "--out", str(out), "--profile-output", str(prof), "--quiet"])
+    assert capsys.readouterr().out == ""
+    records = json.loads(out.read_text())
+    assert len(records) == (1 + 2) * 2 * 2  # the pruning mode once per keep ratio
+    for rec in records:
+        bs.validate_benchmark_record(rec)
+    assert {(r["config"]["mode"], r["config"].get("visual_pruning_keep_ratio")) for r in records} == \
+        {("eager", None), ("eager_visual_prune", 0.5), ("eager_visual_prune", 0.75)}
+    assert {r["results"]["batch"] for r in records} == {1, 2} and {r["config"]["output_tokens"] for r in records} == {2, 3}
+    validate_profile_record(json.loads(prof.read_text()))
