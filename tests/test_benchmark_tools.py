@@ -420,3 +420,42 @@ def test_system_benchmark_main_sweeps_on_the_tiny_model(tmp_path, capsys):
         {("eager", None), ("eager_visual_prune", 0.5), ("eager_visual_prune", 0.75)}
     assert {r["results"]["batch"] for r in records} == {1, 2} and {r["config"]["output_tokens"] for r in records} == {2, 3}
     validate_profile_record(json.loads(prof.read_text()))
+
+
+def test_external_engine_arm_builds_requests_and_times_a_fake_engine(capsys):
+    """The vLLM arm's adapter with a fake engine: media-first token-id prompts with one placeholder per image, fresh
+    inputs for every timed call, TPOT from the difference of two runs, a refusal when the engine ignores ``ignore_eos``;
+    and, on a box without a CUDA device, the ``unavailable`` line instead of a crash."""
+    import numpy as np
+    import pytest
+    import torch
+
+    from prism_infer_b200.models.architecture import Qwen3VLArch
+
+    b = _load("bench_external_vllm")
+    arch = Qwen3VLArch.qwen3_vl_8b()
+    reqs = b.make_requests(arch, np.random.default_rng(0), batch=2, images=3, size=32, question_tokens=5)
+    ids = reqs[0]["prompt_token_ids"]
+    assert ids[:9] == [arch.vision_start_token_id, arch.image_token_id, arch.vision_end_token_id] * 3 and len(ids) == 9 + 5
+    assert len(reqs[0]["multi_modal_data"]["image"]) == 3 and reqs[0]["multi_modal_data"]["image"][0].size == (32, 32)
+    assert "multi_modal_data" not in b.make_requests(arch, np.random.default_rng(0), batch=1, images=0, size=32, question_tokens=4)[0]
+    now, calls, made = [0.0], [], []
+
+    def make():
+        made.append(len(made))
+        return [{"prompt_token_ids": [made[-1]]}]
+
+    def generate(prompts, max_tokens):  # 10 ms prefill + 2 ms per token after the first
+        calls.append((prompts[0]["prompt_token_ids"][0], max_tokens))
+        now[0] += 0.010 + 0.002 * (max_tokens - 1)
+        return [[7] * max_tokens for _ in prompts]
+
+    res = b.measure(generate, make, output_tokens=20, warmup=1, repeats=3, clock=lambda: now[0])
+    assert abs(res["ttft_ms"] - 10.0) < 1e-6 and abs(res["tpot_ms"] - 2.0) < 1e-6 and abs(res["e2e_ms"] - 50.0) < 1e-6
+    assert [c[1] for c in calls] == [2, 1, 21, 1, 21, 1, 21] and len({c[0] for c in calls}) == 7  # never the same inputs twice
+    with pytest.raises(RuntimeError, match="ignore_eos"):
+        b.measure(lambda p, n: [[1] * min(n, 5) for _ in p], make, output_tokens=20, warmup=0, repeats=1)
+    if not torch.cuda.is_available():
+        assert b.main([]) == 0
+        line = json.loads(capsys.readouterr().out)
+        assert line == {"engine": "vllm", "unavailable": "no CUDA device"}
