@@ -24,7 +24,7 @@ def percentile(values: Sequence[float], q: float) -> float:
     lo = int(pos)
     hi = min(lo + 1, len(xs) - 1)
     w = pos - lo
-    return xs[lo] * (1.0 - w) + xs[hi] * w
+    return min(xs[hi], xs[lo] + (xs[hi] - xs[lo]) * w)  # exact between equal neighbours, never above the upper one
 
 
 def summarize_distribution(values: Sequence[float]) -> dict[str, float | int]:
