@@ -15,7 +15,7 @@ from prism_infer_b200.engine.kv_layout import KVLayout  # noqa: E402
 from prism_infer_b200.engine.visual_pruning import target_keep_count, uniform_keep  # noqa: E402
 from prism_infer_b200.engine.vl_inputs import smart_resize, smart_resize_video  # noqa: E402
 
-FAST = settings(max_examples=300, deadline=None)
+FAST = settings(max_examples=300, deadline=None, derandomize=True, database=None)  # the same examples on every run
 
 
 @FAST
