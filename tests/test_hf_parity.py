@@ -155,7 +155,8 @@ def test_a_checkpoint_saved_by_the_upstream_model_loads_and_generates_the_same_t
     """``save_pretrained`` of the upstream model (config.json + safetensors) -> ``LLM(directory)``: the configuration
     parser and the safetensors routing see exactly what a real checkpoint directory holds."""
     arch, hf, _, _ = pair
-    hf.save_pretrained(tmp_path / "ckpt", safe_serialization=True)
+    hf.save_pretrained(tmp_path / "ckpt", safe_serialization=True, max_shard_size="400KB")  # several shards and an index file
+    assert len(list((tmp_path / "ckpt").glob("*.safetensors"))) > 3 and (tmp_path / "ckpt" / "model.safetensors.index.json").is_file()
     assert Qwen3VLArch.from_pretrained(str(tmp_path / "ckpt")) == arch
     inp = prepare_image_inputs(PatchProcessor(arch), load_tokenizer("random:tiny", arch), [9, 8, 7], [_image(7, 64, 96)])
     want, extra = [], []
