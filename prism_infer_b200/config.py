@@ -202,7 +202,6 @@ class ExecutionConfig:
     cooperative_prefill_coalesce_ms: float = 0.0
     cooperative_prefill_coalesce_min_seqs: int = 3
     programmatic_dependent_launch: bool = True
-    decode_multi_step: int = 1
     decode_run_ahead: bool = True             # launch the next greedy decode graph before the host has read this one's tokens
     device_status_check_interval: int = 256   # engine steps between reads of the kernels' status words (0 = never)
 
@@ -222,7 +221,6 @@ class ExecutionConfig:
         if isinstance(self.cooperative_prefill_coalesce_ms, bool) or not isinstance(self.cooperative_prefill_coalesce_ms, (int, float)) \
                 or not 0 <= self.cooperative_prefill_coalesce_ms <= 10_000:
             raise ValueError("cooperative_prefill_coalesce_ms must be a number of milliseconds in [0, 10000]")
-        _int(self.decode_multi_step, "decode_multi_step", 1)
         _int(self.device_status_check_interval, "device_status_check_interval", 0)
 
     @property
@@ -308,7 +306,6 @@ _FLAT = {
         "cooperative_prefill_coalesce_ms": "cooperative_prefill_coalesce_ms",
         "cooperative_prefill_coalesce_min_seqs": "cooperative_prefill_coalesce_min_seqs",
         "enable_programmatic_dependent_launch": "programmatic_dependent_launch",
-        "decode_multi_step": "decode_multi_step",
         "enable_decode_run_ahead": "decode_run_ahead",
         "device_status_check_interval": "device_status_check_interval",
     },

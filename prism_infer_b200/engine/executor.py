@@ -9,6 +9,7 @@ action goes through ``runner.call`` so tensor-parallel ranks stay in lock step.
 
 from __future__ import annotations
 
+import collections
 import time
 
 from .block_manager import BlockManager
@@ -52,6 +53,17 @@ class ModelExecutor:
         self.pruning_scored = PruningConfig(config.visual_pruning_keep_ratio, config.visual_pruning_min_keep_tokens,
                                             config.visual_pruning_video_min_keep_tokens, "attention")
         self.attention_counters = {"scored": 0, "uniform_fallback": 0}
+        # what was (or, in shadow mode, would have been) kept of every prompt's visual tokens; bounded for a long-running server
+        self.shadow = bool(getattr(config, "enable_visual_pruning_shadow", False)) and not self.compact
+        self.pruning_decisions: collections.deque[dict] = collections.deque(maxlen=4096)
+
+    def _record_decision(self, seq, decision, *, applied: bool) -> None:
+        """One ledger entry per prompt (reference ``engine/compression.py:335-470`` builds the same record per batch)."""
+        self.pruning_decisions.append({
+            "seq_id": seq.seq_id, "applied": applied, "strategy": decision.strategy, "total_visual_tokens": decision.total_visual_tokens,
+            "kept": len(decision.kept), "dropped": len(decision.dropped), "keep_ratio_actual": decision.keep_ratio_actual,
+            "spans": [{"modality": sp.modality, "start": sp.start, "end": sp.end} for sp in decision.spans],
+            "prefix_len": int(seq.multimodal_prefix_boundary)})
 
     def mark_visual_ready(self, seq_id: int) -> None:
         """The runner already holds this sequence's vision result (hydrated at submission)."""
@@ -210,6 +222,7 @@ class ModelExecutor:
                         owners.append(seq)
                         seq.pruning_record = {"kept": len(decision.kept), "dropped": len(decision.dropped),
                                               "total": decision.total_visual_tokens, "strategy": "attention"}
+                        self._record_decision(seq, decision, applied=True)
                 continue
             if not seq.is_multimodal or boundary <= 0 or sl.end != boundary or sl.end >= len(seq):
                 continue
@@ -230,6 +243,16 @@ class ModelExecutor:
                         owners.append(seq)
                         seq.pruning_record = {"kept": len(decision.kept), "dropped": len(decision.dropped),
                                               "total": decision.total_visual_tokens}
+                        self._record_decision(seq, decision, applied=True)
+        if self.shadow:
+            # shadow mode: the selection a compacting mode would make, recorded when the prompt's prefix is complete;
+            # the cache is left as it is (reference ``enable_visual_pruning_shadow``)
+            for seq, sl in zip(plan.seqs, plan.slices):
+                boundary = seq.multimodal_prefix_boundary
+                if seq.is_multimodal and 0 < boundary and sl.start < boundary <= sl.end and seq.num_cached_tokens < boundary:
+                    decision = compute_pruning_decision(seq.token_ids, seq.image_token_id, seq.video_token_id, self.pruning, end=boundary)
+                    if decision is not None:
+                        self._record_decision(seq, decision, applied=False)
         if plans:
             self.runners.call("compact_kv", plans)
             for seq, cp in zip(owners, plans):

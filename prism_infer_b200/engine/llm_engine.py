@@ -553,6 +553,14 @@ class LLMEngine:
     def visual_embedding_cache_metadata(self) -> dict[str, object]:
         return self.runners.call("visual_embedding_cache_metadata")
 
+    def visual_pruning_decisions(self, *, clear: bool = False) -> list[dict[str, object]]:
+        """What was kept of every recent prompt's visual tokens: applied selections of the compacting modes, and with
+        ``enable_visual_pruning_shadow`` the selections a compacting mode would have made (``applied`` false)."""
+        out = [dict(r) for r in self.executor.pruning_decisions]
+        if clear:
+            self.executor.pruning_decisions.clear()
+        return out
+
     def graph_metadata(self) -> dict[str, object]:
         return self.runners.call("graph_metadata")
 

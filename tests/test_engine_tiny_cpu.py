@@ -451,6 +451,35 @@ def test_resumable_vision_tower_equals_the_one_piece_tower(tiny):
     llm.exit()
 
 
+def test_pruning_decisions_are_recorded_and_shadow_mode_leaves_the_cache_alone(tiny):
+    """A compacting mode records what it kept of every prompt's visual tokens; with ``enable_visual_pruning_shadow`` a
+    dense mode records the selection it would have made, drops nothing and generates the dense tokens."""
+    arch, weights, oracle = tiny
+    tok, proc = load_tokenizer("random:tiny", arch), PatchProcessor(arch)
+    inp = prepare_image_inputs(proc, tok, [11, 12, 13], [_image(4)])
+    sp = SamplingParams(temperature=0.0, max_tokens=4, ignore_eos=True)
+    kw = dict(visual_pruning_keep_ratio=0.5, visual_pruning_min_keep_tokens=8)
+    active = _llm(weights, compression_mode="visual_compact_scaled_fp8", **kw)
+    active.generate_prepared_image_inputs(inp, sp)
+    rec = active.visual_pruning_decisions()
+    assert len(rec) == 1 and rec[0]["applied"] and rec[0]["total_visual_tokens"] == 49 and rec[0]["kept"] == 25 and rec[0]["dropped"] == 24
+    assert rec[0]["spans"] == [{"modality": "image", "start": 1, "end": 50}] and abs(rec[0]["keep_ratio_actual"] - 25 / 49) < 1e-9
+    active.exit()
+    shadow = _llm(weights, compression_mode="off", enable_visual_pruning_shadow=True, **kw)
+    out = shadow.generate_prepared_image_inputs(inp, sp)
+    assert out["token_ids"] == oracle.generate_greedy(inp.input_ids, 4, pixel_values=inp.pixel_values, image_grid_thw=inp.image_grid_thw)
+    rec2 = shadow.visual_pruning_decisions(clear=True)
+    assert len(rec2) == 1 and not rec2[0]["applied"] and {k: rec2[0][k] for k in ("kept", "dropped", "spans")} == {k: rec[0][k] for k in ("kept", "dropped", "spans")}
+    assert shadow.metrics_snapshot()["engine"]["requests"][-1]["dropped_prompt_tokens"] == 0 and shadow.visual_pruning_decisions() == []
+    shadow.generate([[5, 6, 7]], sp)                       # text only: nothing to record
+    assert shadow.visual_pruning_decisions() == []
+    shadow.exit()
+    plain = _llm(weights, compression_mode="off")
+    plain.generate_prepared_image_inputs(inp, sp)
+    assert plain.visual_pruning_decisions() == []          # neither compacting nor shadowing
+    plain.exit()
+
+
 def test_visual_compaction_frees_pages_and_hits(tiny):
     arch, weights, _ = tiny
     img = _image(4)
