@@ -612,6 +612,17 @@ def test_options_document_lists_every_flat_option():
     root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
     with open(os.path.join(root, "docs", "OPTIONS.md")) as fh:
         assert fh.read() == describe_options.markdown(), "run: python -m prism_infer_b200.utils.describe_options > docs/OPTIONS.md"
+    # options marked "no effect" exist, and nothing outside the configuration module reads their fields
+    import re
+    import subprocess
+
+    field_of = {r[0]: r[2] for r in rows}
+    assert set(describe_options.COMPATIBILITY_ONLY) <= set(field_of)
+    for public in describe_options.COMPATIBILITY_ONLY:
+        hits = subprocess.run(["grep", "-rlE", "--include=*.py", rf"\.{field_of[public]}\b", os.path.join(root, "prism_infer_b200")],
+                              capture_output=True, text=True).stdout.split()  # attribute reads: config.<field>
+        readers = [h for h in hits if not re.search(r"prism_infer_b200/(config|utils/describe_options)\.py$", h)]
+        assert not readers, (public, readers)
 
 
 def test_environment_check_reports_checkpoint_and_plan_problems(tmp_path, capsys):
