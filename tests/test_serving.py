@@ -249,3 +249,66 @@ def test_cli_engine_config(tmp_path):
     with pytest.raises(ValueError):
         load_engine_options(str(p))
     assert load_engine_options(None) == {}
+
+
+def test_http_server_with_the_real_engine_on_cpu():
+    """The whole stack without a fake: tiny random-weight engine on CPU behind the runtime and the HTTP app.  A text
+    request as JSON, an image request as an SSE stream and three concurrent text requests; the tokens are the ones the
+    engine gives when it is driven directly, and an image request equals the oracle."""
+    import base64
+    import io
+
+    import numpy as np
+    import torch
+    from PIL import Image
+
+    from prism_infer_b200 import LLM, SamplingParams
+    from prism_infer_b200.models.architecture import Qwen3VLArch
+    from prism_infer_b200.models.reference_model import ReferenceQwen3VL
+    from prism_infer_b200.models.weights import random_weights
+
+    arch = Qwen3VLArch.tiny()
+    weights = random_weights(arch, dtype=torch.float32, seed=0)
+
+    def make():
+        return LLM("random:tiny", weights=weights, device="cpu", max_model_len=256, kvcache_block_size=16, num_kvcache_blocks=64,
+                   enforce_eager=True, max_num_batched_tokens=256, max_chunk_size=256, max_num_seqs=4)
+
+    direct = make()
+    sp = SamplingParams(temperature=0.0, max_tokens=5, ignore_eos=True)
+    want_text = {p: direct.generate([p], sp)[0]["token_ids"] for p in ("7 8 9", "10 11", "12 13 14 15")}
+    arr = np.random.default_rng(3).integers(0, 256, (64, 64, 3), dtype=np.uint8)
+    want_image = direct.generate_images("21 22", [Image.fromarray(arr)], sp)["token_ids"]
+    inputs = direct.prepare_images("21 22", [Image.fromarray(arr)])
+    assert want_image == ReferenceQwen3VL(arch, weights).generate_greedy(inputs.input_ids, 5, pixel_values=inputs.pixel_values,
+                                                                        image_grid_thw=inputs.image_grid_thw)
+    direct.exit()
+    buf = io.BytesIO()
+    Image.fromarray(arr).save(buf, format="PNG")
+    url = "data:image/png;base64," + base64.b64encode(buf.getvalue()).decode()
+
+    rt = ServingRuntime(make, ingress_capacity=8)
+    rt.start()
+    app = create_app(rt, manage_runtime=False)
+
+    async def scenario():
+        transport = httpx.ASGITransport(app=app)
+        async with httpx.AsyncClient(transport=transport, base_url="http://t", timeout=60.0) as client:
+            body = {"sampling": {"max_tokens": 5, "ignore_eos": True}}
+            r = await client.post("/v1/generate", json={"prompt": "7 8 9", **body})
+            assert r.status_code == 200 and r.json()["token_ids"] == want_text["7 8 9"] and r.json()["finish_reason"] == "length"
+            async with client.stream("POST", "/v1/generate", json={"prompt": "21 22", "modality": "image", "media": url, "stream": True,
+                                                                  **body}) as resp:
+                frames = [f for f in (await resp.aread()).decode().split("\n\n") if f]
+            kinds = [f.split("\n")[0] for f in frames]
+            assert kinds[0] == "event: accepted" and kinds[-1] == "event: done" and kinds.count("event: token") == 5
+            assert json.loads(frames[-1].split("data: ", 1)[1])["token_ids"] == want_image
+            answers = await asyncio.gather(*[client.post("/v1/generate", json={"prompt": p, **body}) for p in want_text])
+            for p, a in zip(want_text, answers):
+                assert a.status_code == 200 and a.json()["token_ids"] == want_text[p], p
+
+    try:
+        asyncio.run(scenario())
+        assert rt.is_healthy
+    finally:
+        rt.stop()
