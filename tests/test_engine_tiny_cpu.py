@@ -838,3 +838,74 @@ def test_attention_strategy_compacts_by_last_query_scores(tiny, monkeypatch):
     llm.generate_prepared_image_inputs(inp, sp)
     assert llm.executor.attention_counters == {"scored": 0, "uniform_fallback": 1}
     llm.exit()
+
+
+@pytest.mark.parametrize("seed,tight", [(3, False), (10, False), (17, False), (5, True), (21, True), (28, True)])
+def test_randomised_traffic_with_every_prefill_policy_switched_on(tiny, seed, tight):
+    """Cooperative prefill in layer and vision-block quanta, the adaptive (coalescing) policy, the SLO-aware scheduler with
+    random deadlines, a small page pool (preemption by swap), random arrivals and random cancellations, all at once: every
+    request that was not cancelled gets the oracle's tokens, nothing is left pending and no page leaks.  The tight variant
+    has a third of the pages, no coalescing and more heavy images, which brings preemption by swap and SLO interrupts into
+    play (seeds chosen so that the six runs together take every branch; another 120 seeds were run once and passed)."""
+    import random
+
+    arch, weights, oracle = tiny
+    rnd = random.Random(seed)
+    tok, proc = load_tokenizer("random:tiny", arch), PatchProcessor(arch)
+    now = [1_000_000_000]
+    llm = _llm(weights, enable_cooperative_prefill=True, cooperative_prefill_layer_quantum=1, cooperative_prefill_vision_block_quantum=1,
+               cooperative_prefill_coalesce_ms=0.0 if tight else 30.0, scheduler_policy="slo_aware", heavy_prefill_vision_patch_threshold=100,
+               min_decode_batches_between_heavy_prefills=2, num_kvcache_blocks=13 if tight else 40, cpu_kv_cache_ratio=1.0, max_num_seqs=6,
+               max_num_batched_tokens=128, max_chunk_size=64, enable_prefix_caching=True)
+    llm.scheduler.clock_ns = lambda: now[0]
+    total_pages = llm.scheduler.block_manager.gpu.num_free
+    images = [_image(20 + i, 64) for i in range(2)] + [_image(30)]  # two small ones and a heavy one (196 patches)
+    plans = []
+    for i in range(12):
+        n_out = rnd.randint(2, 9)
+        if rnd.random() < (0.6 if tight else 0.4):
+            img = images[2] if tight and rnd.random() < 0.7 else rnd.choice(images)
+            inp = prepare_image_inputs(proc, tok, [rnd.randrange(10, 900) for _ in range(rnd.randint(2, 6))], [img])
+            plans.append(("image", inp, n_out))
+        else:
+            plans.append(("text", [rnd.randrange(10, 900) for _ in range(rnd.randint(3, 90))], n_out))
+    arrivals = sorted(rnd.randint(0, 40) for _ in plans)
+    submitted, done, cancelled = {}, {}, set()
+    step = 0
+    while len(submitted) < len(plans) or not llm.is_finished():
+        while len(submitted) < len(plans) and arrivals[len(submitted)] <= step:
+            kind, payload, n_out = plans[len(submitted)]
+            sp = SamplingParams(temperature=0.0, max_tokens=n_out, ignore_eos=True)
+            rid = llm.add_prepared_image_request(payload, sp) if kind == "image" else llm.add_request(payload, sp)
+            seq = llm._sequences[rid]
+            seq.arrival_ns = now[0]
+            if rnd.random() < 0.5:
+                seq.deadline_ns = now[0] + rnd.choice([50, 200, 900]) * 1_000_000
+            submitted[rid] = (kind, payload, n_out)
+        if submitted and rnd.random() < 0.06:
+            victim = rnd.choice(list(submitted))
+            if victim not in done and victim not in cancelled and llm.cancel_request(victim):
+                cancelled.add(victim)
+        for o in llm.step_result().outputs:
+            if o.finished:
+                done[o.request_id] = list(o.token_ids)
+        now[0] += 7_000_000  # seven milliseconds per engine step
+        step += 1
+        assert step < 3000, "the engine stopped making progress"
+    assert llm._pending_prefill is None and llm._pending_vision is None and not llm._deferred
+    assert set(done) | cancelled >= set(submitted) and len(submitted) == len(plans)
+    for rid, (kind, payload, n_out) in submitted.items():
+        if rid in cancelled and rid not in done:
+            continue
+        # the oracle recomputes the whole sequence per token and takes every placeholder id for a visual row, so it can
+        # only follow a generation up to (and including) a placeholder id that the random model happened to emit
+        got = done[rid]
+        stop = next((i + 1 for i, t in enumerate(got) if t in (arch.image_token_id, arch.video_token_id)), len(got))
+        assert len(got) == n_out
+        want = oracle.generate_greedy(payload.input_ids, stop, pixel_values=payload.pixel_values, image_grid_thw=payload.image_grid_thw) \
+            if kind == "image" else oracle.generate_greedy(payload, stop)
+        assert got[:stop] == want, (rid, kind, n_out)
+    kept = llm.multimodal_prefix_cache_metadata()["resident_pages"]
+    assert llm.scheduler.block_manager.gpu.num_free == total_pages - kept
+    assert not llm.runners.runner.__dict__.get("_pending_encodes") and not llm.runners.runner.__dict__.get("_pending_prefills")
+    llm.exit()
