@@ -31,7 +31,7 @@ from .progress import GenerationProgress
 from .request import RequestIdAllocator, RequestState
 from .scheduler import Scheduler
 from .sequence import Sequence
-from .vl_inputs import (ImageInputs, PatchProcessor, VideoInputs, checkpoint_pixel_budgets, prepare_image_inputs,
+from .vl_inputs import (ImageInputs, PatchProcessor, VideoInputs, checkpoint_pixel_budgets, load_video_file, prepare_image_inputs,
                         prepare_interleaved_image_inputs, prepare_video_inputs)
 
 
@@ -249,8 +249,13 @@ class LLMEngine:
             return prepare_interleaved_image_inputs(self.processor, self.tokenizer, prompt, images, image_marker, chat=self.chat)
         return prepare_image_inputs(self.processor, self.tokenizer, prompt, images, chat=self.chat)
 
-    def prepare_video(self, prompt: str | Seq[int], frames: Seq[Any], *, timing=None) -> VideoInputs:
-        """Prompt + sampled frames (+ ``chat_prompt.VideoTiming``) -> ``VideoInputs``; see ``prepare_images``."""
+    def prepare_video(self, prompt: str | Seq[int], frames: Seq[Any] | str, *, timing=None) -> VideoInputs:
+        """Prompt + sampled frames (+ ``chat_prompt.VideoTiming``) -> ``VideoInputs``; see ``prepare_images``.
+        ``frames`` may also be the path of a video file: its frames are sampled at two per second of source time
+        (4 to 768 of them, evenly spaced) and their source times go into the prompt's time stamps."""
+        if isinstance(frames, (str, os.PathLike)):
+            frames, file_timing = load_video_file(os.fspath(frames))
+            timing = timing or file_timing
         frames = list(frames)
         if self.hf_processor is not None and isinstance(prompt, str):
             return self.hf_processor.video_inputs(self.hf_processor.chat.video_prompt(prompt), frames, timing)

@@ -213,6 +213,62 @@ class PatchProcessor:
         return grid[0] * grid[1] * grid[2] // self.arch.vision.merge_unit
 
 
+VIDEO_SAMPLE_FPS, VIDEO_MIN_FRAMES, VIDEO_MAX_FRAMES = 2.0, 4, 768
+
+
+def video_sample_indices(total_frames: int, source_fps: float | None, *, fps: float = VIDEO_SAMPLE_FPS, min_frames: int = VIDEO_MIN_FRAMES,
+                         max_frames: int = VIDEO_MAX_FRAMES, num_frames: int | None = None) -> list[int]:
+    """Which frames of a clip are read: ``fps`` frames per second of source time, at least ``min_frames`` and at most
+    ``max_frames`` (and never more than the clip has), evenly spaced from the first to the last frame - the rule of the
+    Hugging Face Qwen3-VL video processor.  A clip without a known frame rate counts as 24 frames per second."""
+    if total_frames <= 0:
+        raise ValueError("the clip has no frames")
+    if num_frames is None:
+        n = int(total_frames / float(source_fps or 24.0) * fps)
+        num_frames = min(max(n, min_frames), max_frames, total_frames)
+    if num_frames <= 0:
+        raise ValueError("num_frames must be positive")
+    return [int(i) for i in np.linspace(0, total_frames - 1, num_frames).round().astype(int)]
+
+
+def load_video_file(path: str, *, fps: float = VIDEO_SAMPLE_FPS, min_frames: int = VIDEO_MIN_FRAMES, max_frames: int = VIDEO_MAX_FRAMES,
+                    num_frames: int | None = None):
+    """Decode the sampled frames of a video file with OpenCV -> ``(list of uint8 [H, W, 3] RGB frames, VideoTiming)``.
+    Frames are read in one sequential pass (seeking is unreliable for many containers); the timing carries the source
+    indices and frame rate, from which the prompt's time stamps follow."""
+    try:
+        import cv2  # type: ignore
+    except ImportError as exc:
+        raise RuntimeError("reading a video file needs the optional dependency cv2 (opencv-python-headless); "
+                           "pass a list of frames instead") from exc
+    from .chat_prompt import VideoTiming
+
+    cap = cv2.VideoCapture(str(path))
+    if not cap.isOpened():
+        raise OSError(f"cannot open video: {path}")
+    try:
+        total, source_fps = int(cap.get(cv2.CAP_PROP_FRAME_COUNT)), float(cap.get(cv2.CAP_PROP_FPS)) or None
+        if total <= 0:
+            raise ValueError(f"video reports no frames: {path}")
+        wanted = video_sample_indices(total, source_fps, fps=fps, min_frames=min_frames, max_frames=max_frames, num_frames=num_frames)
+        need, frames, i = {}, [], 0
+        for w in wanted:
+            need[w] = need.get(w, 0) + 1
+        last = max(wanted)
+        while i <= last:
+            ok, bgr = cap.read()
+            if not ok:
+                break
+            for _ in range(need.get(i, 0)):
+                frames.append(np.ascontiguousarray(bgr[:, :, ::-1]))
+            i += 1
+        if len(frames) != len(wanted):
+            raise OSError(f"{path}: the container reports {total} frames but decoding stopped at frame {i}")
+    finally:
+        cap.release()
+    return frames, VideoTiming(tuple(wanted), float(source_fps or 24.0))
+
+
 def image_block(arch, n_tokens: int) -> list[int]:
     return [arch.vision_start_token_id] + [arch.image_token_id] * n_tokens + [arch.vision_end_token_id]
 

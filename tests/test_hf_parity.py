@@ -169,3 +169,35 @@ def test_a_checkpoint_saved_by_the_upstream_model_loads_and_generates_the_same_t
     got = llm.generate_prepared_image_inputs(inp, SamplingParams(temperature=0.0, max_tokens=5, ignore_eos=True))["token_ids"]
     llm.exit()
     assert got == want
+
+
+def test_video_file_sampling_rule_equals_upstream_and_a_file_request_runs(pair, tmp_path):
+    """Frame indices as the upstream video processor picks them for a range of clip lengths and frame rates; a video
+    file goes through ``LLM.generate_video`` with the time stamps of its sampled frames and gives the oracle's tokens."""
+    cv2 = pytest.importorskip("cv2")
+    from transformers.models.qwen3_vl.video_processing_qwen3_vl import Qwen3VLVideoProcessor
+    from transformers.video_utils import VideoMetadata
+
+    from prism_infer_b200.engine.vl_inputs import load_video_file, video_sample_indices
+
+    upstream = Qwen3VLVideoProcessor()
+    for total, fps in ((40, 10.0), (7, 30.0), (3000, 25.0), (100000, 24.0), (5, None), (900, 29.97)):
+        meta = VideoMetadata(total_num_frames=total, fps=fps)
+        assert video_sample_indices(total, fps) == [int(i) for i in upstream.sample_frames(meta)], (total, fps)
+    arch, _, weights, oracle = pair
+    clip = tmp_path / "clip.avi"
+    w = cv2.VideoWriter(str(clip), cv2.VideoWriter_fourcc(*"MJPG"), 10.0, (64, 64))
+    rng = np.random.default_rng(0)
+    for _ in range(40):
+        w.write(rng.integers(0, 256, (64, 64, 3), dtype=np.uint8))
+    w.release()
+    frames, timing = load_video_file(str(clip))
+    assert len(frames) == 8 and timing.fps == 10.0 and list(timing.frame_indices) == [int(i) for i in np.linspace(0, 39, 8).round()]
+    llm = LLM("random:tiny", weights=weights, device="cpu", max_model_len=512, kvcache_block_size=16, num_kvcache_blocks=64,
+              enforce_eager=True, max_num_batched_tokens=512, max_chunk_size=512)
+    sp = SamplingParams(temperature=0.0, max_tokens=4, ignore_eos=True)
+    from_file = llm.generate_video([5, 6, 7], str(clip), sp)
+    inputs = llm.prepare_video([5, 6, 7], frames, timing=timing)
+    assert from_file["token_ids"] == llm.generate_prepared_video_inputs(inputs, sp)["token_ids"]
+    assert from_file["token_ids"] == oracle.generate_greedy(inputs.input_ids, 4, pixel_values=inputs.pixel_values, video_grid_thw=inputs.video_grid_thw)
+    llm.exit()
