@@ -12,6 +12,7 @@ merged 2x2 window.  Chat-template prompts and the optional Hugging Face processo
 from __future__ import annotations
 
 import math
+import os
 from dataclasses import dataclass
 from typing import Any, Sequence
 
@@ -60,7 +61,12 @@ def _validate(ids: Sequence[int], pixels: torch.Tensor, grid: Sequence[Sequence[
 
 
 def to_uint8_hwc(image: Any) -> np.ndarray:
-    """PIL image, numpy array or torch tensor -> ``uint8 [H, W, 3]``."""
+    """PIL image, numpy array, torch tensor or the path of an image file -> ``uint8 [H, W, 3]``."""
+    if isinstance(image, (str, os.PathLike)):
+        from PIL import Image
+
+        with Image.open(os.fspath(image)) as im:
+            return np.asarray(im.convert("RGB"))
     if isinstance(image, torch.Tensor):
         arr = image.detach().cpu().numpy()
     elif isinstance(image, np.ndarray):

@@ -909,3 +909,17 @@ def test_randomised_traffic_with_every_prefill_policy_switched_on(tiny, seed, ti
     assert llm.scheduler.block_manager.gpu.num_free == total_pages - kept
     assert not llm.runners.runner.__dict__.get("_pending_encodes") and not llm.runners.runner.__dict__.get("_pending_prefills")
     llm.exit()
+
+
+def test_image_requests_accept_file_paths(tiny, tmp_path):
+    from PIL import Image
+
+    arch, weights, _ = tiny
+    arr = _image(13, 64)
+    path = tmp_path / "picture.png"
+    Image.fromarray(arr).save(path)
+    llm = _llm(weights)
+    sp = SamplingParams(temperature=0.0, max_tokens=3, ignore_eos=True)
+    assert llm.generate_images([5, 6], [str(path)], sp)["token_ids"] == llm.generate_images([5, 6], [arr], sp)["token_ids"]
+    assert llm.generate_images([5, 6], [path], sp)["token_ids"] == llm.generate_images([5, 6], [Image.fromarray(arr)], sp)["token_ids"]
+    llm.exit()
