@@ -174,6 +174,10 @@ ATTN_TC_ENABLED = True
 # prefill over the paged cache (chunked prefill, prefix hits) at head dimension 128: gather the visible keys from
 # their pages once per layer, then the same tcgen05 kernel (False: the mma.sync kernel that reads the pages itself)
 PAGED_PREFILL_TC_ENABLED = True
+# the gathered rows cost 4 x KV heads x head dimension bytes per visible key (K and V in bf16): above this total the
+# page-reading kernel runs instead (a prefill step over very many long histories), so the scratch stays inside the
+# memory the KV sizing leaves free
+PAGED_PREFILL_TC_MAX_SCRATCH_BYTES = 2 << 30
 # prefill GEMMs of at least this many tokens run the persistent form, tokens on the TMEM lanes
 PERSISTENT_ROWMAJOR = True
 PERSISTENT_MIN_TOKENS = 512
@@ -659,6 +663,7 @@ def paged_prefill_attention(
     assert q.stride(2) == 1 and q.stride(1) == D
     assert cu_seqlens_q.dtype == torch.int32 and kv_lens.dtype == torch.int32 and block_tables.dtype == torch.int32
     if (ATTN_TC_ENABLED and PAGED_PREFILL_TC_ENABLED and D == 128 and cu_seqlens_kv is not None and total_kv > 0
+            and 4 * int(total_kv) * cache.num_kv_heads * D <= PAGED_PREFILL_TC_MAX_SCRATCH_BYTES
             and q.stride(0) % 8 == 0 and (q.data_ptr() | out.data_ptr()) % 16 == 0):
         assert cu_seqlens_kv.dtype == torch.int32 and cu_seqlens_kv.shape == cu_seqlens_q.shape and max_kv_len <= total_kv
         k_rows, v_rows = _gathered_kv_rows(q.device, total_kv, cache.num_kv_heads * D)
