@@ -18,9 +18,22 @@ from prism_infer_b200.utils.tokenizer import load_tokenizer
 hf_qwen3_vl = pytest.importorskip("transformers.models.qwen3_vl")
 
 
-@pytest.fixture(scope="module")
-def pair():
-    arch = Qwen3VLArch.tiny()
+def _production_shaped_arch() -> Qwen3VLArch:
+    """Small, but with the 8B model's structural numbers: 128-wide text heads with rotary sections 24 / 20 / 20, 72-wide
+    vision heads, three DeepStack taps, a 48 x 48 learned position grid, grouped-query attention 4 : 1."""
+    from prism_infer_b200.models.architecture import TextArch, VisionArch
+
+    return Qwen3VLArch(
+        text=TextArch(vocab_size=2048, hidden_size=512, num_layers=3, num_heads=4, num_kv_heads=1, head_dim=128, intermediate_size=768,
+                      mrope_section=(24, 20, 20), max_position_embeddings=4096),
+        vision=VisionArch(hidden_size=144, depth=4, num_heads=2, intermediate_size=288, num_position_embeddings=2304, out_hidden_size=512,
+                          deepstack_visual_indexes=(0, 1, 3)),
+        image_token_id=2001, video_token_id=2002, vision_start_token_id=2003, vision_end_token_id=2004, eos_token_id=2005)
+
+
+@pytest.fixture(scope="module", params=["tiny", "production_shaped"])
+def pair(request):
+    arch = Qwen3VLArch.tiny() if request.param == "tiny" else _production_shaped_arch()
     cfg = hf_qwen3_vl.Qwen3VLConfig(**arch.to_hf_config())
     torch.manual_seed(0)
     hf = hf_qwen3_vl.Qwen3VLForConditionalGeneration(cfg).eval().float()
@@ -121,7 +134,7 @@ def test_engine_greedy_tokens_equal_upstream_greedy_tokens(pair):
         nxt = int(torch.argmax(_hf_logits(arch, hf, inp, extra)))
         want.append(nxt)
         extra.append(nxt)
-    llm = LLM("random:tiny", weights=weights, device="cpu", max_model_len=256, kvcache_block_size=16, num_kvcache_blocks=32,
+    llm = LLM("random:tiny", arch=arch, weights=weights, device="cpu", max_model_len=256, kvcache_block_size=16, num_kvcache_blocks=32,
               enforce_eager=True, max_num_batched_tokens=256, max_chunk_size=52)
     got = llm.generate_prepared_image_inputs(inp, SamplingParams(temperature=0.0, max_tokens=6, ignore_eos=True))["token_ids"]
     llm.exit()
@@ -193,7 +206,7 @@ def test_video_file_sampling_rule_equals_upstream_and_a_file_request_runs(pair, 
     w.release()
     frames, timing = load_video_file(str(clip))
     assert len(frames) == 8 and timing.fps == 10.0 and list(timing.frame_indices) == [int(i) for i in np.linspace(0, 39, 8).round()]
-    llm = LLM("random:tiny", weights=weights, device="cpu", max_model_len=512, kvcache_block_size=16, num_kvcache_blocks=64,
+    llm = LLM("random:tiny", arch=arch, weights=weights, device="cpu", max_model_len=512, kvcache_block_size=16, num_kvcache_blocks=64,
               enforce_eager=True, max_num_batched_tokens=512, max_chunk_size=512)
     sp = SamplingParams(temperature=0.0, max_tokens=4, ignore_eos=True)
     from_file = llm.generate_video([5, 6, 7], str(clip), sp)
