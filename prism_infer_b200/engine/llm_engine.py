@@ -91,7 +91,8 @@ class LLMEngine:
         self.processor = PatchProcessor(self.arch, min_pixels=cfg.image_min_pixels or recorded.get("min_pixels"),
                                         max_pixels=cfg.image_max_pixels or recorded.get("max_pixels"),
                                         video_max_pixels=cfg.video_max_pixels or recorded.get("video_max_pixels"),
-                                        video_min_pixels=recorded.get("video_min_pixels"))
+                                        video_min_pixels=recorded.get("video_min_pixels"), video_fps=recorded.get("video_fps"),
+                                        video_min_frames=recorded.get("video_min_frames"), video_max_frames=recorded.get("video_max_frames"))
         from .chat_prompt import ChatPrompt, HFProcessorAdapter
 
         mode = cfg.chat_template
@@ -254,7 +255,8 @@ class LLMEngine:
         ``frames`` may also be the path of a video file: its frames are sampled at two per second of source time
         (4 to 768 of them, evenly spaced) and their source times go into the prompt's time stamps."""
         if isinstance(frames, (str, os.PathLike)):
-            frames, file_timing = load_video_file(os.fspath(frames))
+            p = self.processor
+            frames, file_timing = load_video_file(os.fspath(frames), fps=p.video_fps, min_frames=p.video_min_frames, max_frames=p.video_max_frames)
             timing = timing or file_timing
         frames = list(frames)
         if self.hf_processor is not None and isinstance(prompt, str):

@@ -96,6 +96,9 @@ def smart_resize(h: int, w: int, factor: int, min_pixels: int, max_pixels: int) 
     return hb, wb
 
 
+VIDEO_SAMPLE_FPS, VIDEO_MIN_FRAMES, VIDEO_MAX_FRAMES = 2.0, 4, 768
+
+
 def smart_resize_video(num_frames: int, h: int, w: int, temporal_factor: int, factor: int, min_pixels: int, max_pixels: int) -> tuple[int, int]:
     """Frame size of a clip under a budget on its whole volume (frames x height x width, frames rounded up to the
     temporal patch), the rule of the Hugging Face Qwen3-VL video processor: sides rounded to ``factor``, shrunk when the
@@ -162,6 +165,10 @@ def checkpoint_pixel_budgets(model_dir: str) -> dict[str, int]:
         v = budget(cfg, size_key, flat)
         if v is not None:
             out[key] = v
+    for key in ("fps", "min_frames", "max_frames"):  # how the checkpoint's video processor samples a file
+        v = video.get(key)
+        if isinstance(v, (int, float)) and not isinstance(v, bool) and v > 0:
+            out[f"video_{key}"] = v if key == "fps" else int(v)
     return out
 
 
@@ -170,7 +177,8 @@ class PatchProcessor:
     width (``video_min_pixels`` .. ``video_max_pixels``), as the checkpoint's video processor counts it."""
 
     def __init__(self, arch, *, min_pixels: int | None = None, max_pixels: int | None = None,
-                 video_max_pixels: int | None = None, video_min_pixels: int | None = None) -> None:
+                 video_max_pixels: int | None = None, video_min_pixels: int | None = None, video_fps: float | None = None,
+                 video_min_frames: int | None = None, video_max_frames: int | None = None) -> None:
         self.arch = arch
         v = arch.vision
         self.factor = v.patch_size * v.spatial_merge_size
@@ -178,6 +186,10 @@ class PatchProcessor:
         self.max_pixels = max_pixels or 16384 * self.factor * self.factor
         self.video_max_pixels = video_max_pixels or 24 * self.max_pixels // 16   # 25.2 M: the 8B checkpoint's recorded volume budget
         self.video_min_pixels = video_min_pixels or self.factor * self.factor * 4
+        # sampling of a video file (frames per second of source time and the bounds on their number)
+        self.video_fps = float(video_fps or VIDEO_SAMPLE_FPS)
+        self.video_min_frames = int(video_min_frames or VIDEO_MIN_FRAMES)
+        self.video_max_frames = int(video_max_frames or VIDEO_MAX_FRAMES)
 
     def _frames_to_patches(self, frames: np.ndarray) -> tuple[torch.Tensor, tuple[int, int, int]]:
         """``uint8 [F, H, W, 3]`` (F a multiple of the temporal patch) -> patches, grid."""
@@ -217,9 +229,6 @@ class PatchProcessor:
 
     def tokens_for(self, grid: tuple[int, int, int]) -> int:
         return grid[0] * grid[1] * grid[2] // self.arch.vision.merge_unit
-
-
-VIDEO_SAMPLE_FPS, VIDEO_MIN_FRAMES, VIDEO_MAX_FRAMES = 2.0, 4, 768
 
 
 def video_sample_indices(total_frames: int, source_fps: float | None, *, fps: float = VIDEO_SAMPLE_FPS, min_frames: int = VIDEO_MIN_FRAMES,

@@ -154,7 +154,9 @@ def test_native_input_preparation_equals_the_checkpoint_processor(synthetic_chec
     from prism_infer_b200.engine.vl_inputs import checkpoint_pixel_budgets
 
     budgets = checkpoint_pixel_budgets(path)
-    assert budgets == {"min_pixels": 65536, "max_pixels": 16777216, "video_min_pixels": 4096, "video_max_pixels": 25165824}
+    assert {k: budgets[k] for k in ("min_pixels", "max_pixels", "video_min_pixels", "video_max_pixels")} == \
+        {"min_pixels": 65536, "max_pixels": 16777216, "video_min_pixels": 4096, "video_max_pixels": 25165824}
+    assert set(budgets) <= {"min_pixels", "max_pixels", "video_min_pixels", "video_max_pixels", "video_fps", "video_min_frames", "video_max_frames"}
     native = PatchProcessor(arch, **budgets)  # what the engine does for a checkpoint directory
     images = [_img(0, 64), np.random.default_rng(5).integers(0, 256, (100, 130, 3), dtype=np.uint8)]  # both below the minimum: enlarged
     mine = prepare_image_inputs(native, tok, "t5 t6 t7", images, chat=chat)

@@ -670,3 +670,22 @@ def test_environment_check_reports_checkpoint_and_plan_problems(tmp_path, capsys
         capsys.readouterr()
     assert ce.main(["--allow-cpu", "--model", "random:tiny"]) == 0
     assert "result: PASS" in capsys.readouterr().out
+
+
+def test_checkpoint_processor_files_set_pixel_budgets_and_video_sampling(tmp_path):
+    import json
+
+    from prism_infer_b200.engine.vl_inputs import PatchProcessor, checkpoint_pixel_budgets
+    from prism_infer_b200.models.architecture import Qwen3VLArch
+
+    assert checkpoint_pixel_budgets(str(tmp_path)) == {}
+    (tmp_path / "preprocessor_config.json").write_text(json.dumps({"min_pixels": 3136, "max_pixels": 1003520}))        # the older flat keys
+    (tmp_path / "video_preprocessor_config.json").write_text(json.dumps({"size": {"shortest_edge": 4096, "longest_edge": 25165824},
+                                                                         "fps": 2, "min_frames": 4, "max_frames": 768, "do_sample_frames": True}))
+    got = checkpoint_pixel_budgets(str(tmp_path))
+    assert got == {"min_pixels": 3136, "max_pixels": 1003520, "video_min_pixels": 4096, "video_max_pixels": 25165824, "video_fps": 2,
+                   "video_min_frames": 4, "video_max_frames": 768}
+    p = PatchProcessor(Qwen3VLArch.tiny(), **got)
+    assert (p.min_pixels, p.max_pixels, p.video_fps, p.video_min_frames, p.video_max_frames) == (3136, 1003520, 2.0, 4, 768)
+    (tmp_path / "preprocessor_config.json").write_text(json.dumps({"size": {"shortest_edge": 65536, "longest_edge": "many"}}))
+    assert "max_pixels" not in checkpoint_pixel_budgets(str(tmp_path))  # a value that is not a number is ignored, not guessed
