@@ -33,11 +33,12 @@ from pathlib import Path
 from typing import Any, Callable, Mapping, Sequence
 
 sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
 
 from prism_infer_b200.analysis import quality_metrics as qm  # noqa: E402
 from prism_infer_b200.analysis import working_set_quality as wsq  # noqa: E402
 from prism_infer_b200.analysis.identity import canonical_json_sha256  # noqa: E402
-from prism_infer_b200.analysis.quality_materialization import (safe_materialized_path, verify_materialized_records,  # noqa: E402
+from prism_infer_b200.analysis.quality_materialization import (safe_materialized_path, sha256_file, verify_materialized_records,  # noqa: E402
                                                                write_json_atomic, write_jsonl_atomic)
 
 STAGES: dict[str, dict[str, Any]] = {
@@ -208,7 +209,7 @@ def summarize(stage_rows: Mapping[str, Sequence[Mapping[str, Any]]], plan: Seque
     return out
 
 
-def main() -> None:
+def main(argv=None) -> None:
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     ap.add_argument("--records", required=True)
     ap.add_argument("--media-root", required=True)
@@ -223,13 +224,13 @@ def main() -> None:
     ap.add_argument("--resume", action="store_true")
     ap.add_argument("--video-frames", type=int, default=16, help="frames sampled from a video record")
     ap.add_argument("--frame-dir-fps", type=float, default=3.0, help="frame rate at which frame directories were exported")
-    args = ap.parse_args()
+    args = ap.parse_args(argv)
     stages = [s for s in args.stages.split(",") if s]
     for s in stages:
         if s not in STAGES:
             ap.error(f"unknown stage {s!r}; known: {sorted(STAGES)}")
     records = evaluable(load_records(args.records))
-    verify_media(records, args.media_root)
+    media_check = verify_media(records, args.media_root)
     sampling_identity = {"video_frames": args.video_frames, "frame_dir_fps": args.frame_dir_fps} if any(map(is_video_record, records)) else None
     plan = wsq.select_multi_question_groups(records, max_groups=args.max_groups, sampling_identity=sampling_identity)
     if not plan:
@@ -247,7 +248,14 @@ def main() -> None:
     rows = {s: run_stage(s, plan, make_engine, args.media_root, out_dir, max_tokens=args.max_tokens, resume=args.resume,
                          video_frames=args.video_frames, frame_dir_fps=args.frame_dir_fps) for s in stages}
     summary = summarize(rows, plan)
-    summary["config"] = {"model": args.model, "stages": stages, "max_tokens": args.max_tokens, "pages": args.pages, "tp": args.tp}
+    summary["config"] = {"model": args.model, "stages": stages, "max_tokens": args.max_tokens, "pages": args.pages, "tp": args.tp,
+                         "video_frames": args.video_frames, "frame_dir_fps": args.frame_dir_fps, "stage_options": {s: STAGES[s] for s in stages}}
+    # what went in: the record file by content, the media that were re-hashed, the source tree and the GPU
+    import harness
+
+    summary["inputs"] = {"records_file_sha256": sha256_file(args.records), "evaluated_records_sha256": canonical_json_sha256(list(records)),
+                         "media_verified": media_check}
+    summary["provenance"] = harness.provenance()
     write_json_atomic(out_dir / "summary.json", summary)
     print(json.dumps({k: summary[k] for k in ("samples", "groups", "stages") if k in summary} | {"paired": summary.get("paired_deleted_subset")}))
 

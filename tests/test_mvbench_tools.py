@@ -279,6 +279,15 @@ def test_quality_runner_on_mvbench_frame_directories(tmp_path):
         by_group.setdefault(r["media_group_id"], set()).add((tuple(r["sampled_indices"]), r["sampled_rgb_identity_sha256"]))
     assert all(len(v) == 1 for v in by_group.values())
     assert all(len(r["sampled_indices"]) == 4 and r["parse_method"] in ("leading_label_period", "embedded_label", "unparseable") for r in rows)
+    # the command-line entry end to end: both stages, summary with the identity of what went in
+    final = tmp_path / "run_main"
+    runner.main(["--records", str(out / "mvbench_test.records.jsonl"), "--media-root", str(out), "--out", str(final), "--model", "random:tiny",
+                 "--device", "cpu", "--pages", "16", "--max-tokens", "2", "--video-frames", "4"])
+    summary = json.loads((final / "summary.json").read_text())
+    assert summary["samples"] == 5 and summary["groups"] == 2 and set(summary["stages"]) == {"dense_prefix", "compact_prefix"}
+    assert summary["inputs"]["media_verified"]["unique_media_files"] == 16 and len(summary["inputs"]["records_file_sha256"]) == 64
+    assert summary["provenance"]["source"] and summary["config"]["video_frames"] == 4
+    assert summary["stages"]["dense_prefix"]["repeat_prefix_hits"] == summary["stages"]["dense_prefix"]["repeat_questions"] == 3
 
 
 def test_video_file_record_is_sampled_inside_its_time_window(tmp_path):
