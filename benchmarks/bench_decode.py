@@ -27,20 +27,26 @@ from prism_infer_b200.analysis import benchmark_schema  # noqa: E402
 from prism_infer_b200.engine.vl_inputs import PatchProcessor, prepare_image_inputs, prepare_video_inputs  # noqa: E402
 
 
-def build_inputs(llm, workload: str, rng):
+def token_ids(llm, rng, n: int) -> list[int]:
+    """Random ids below the special tokens of the model's vocabulary."""
+    return rng.integers(0, min(150000, llm.arch.text.vocab_size - 64), n).tolist()
+
+
+def build_inputs(llm, workload: str, rng, size: int = 448):
     proc = PatchProcessor(llm.arch)
-    q = rng.integers(0, 150000, 32).tolist()
+    q = token_ids(llm, rng, 32)
+    picture = lambda: rng.integers(0, 256, (size, size, 3), dtype=np.uint8)  # noqa: E731
     if workload == "images8":
-        return prepare_image_inputs(proc, llm.tokenizer, q, [rng.integers(0, 256, (448, 448, 3), dtype=np.uint8) for _ in range(8)])
+        return prepare_image_inputs(proc, llm.tokenizer, q, [picture() for _ in range(8)])
     if workload == "image1":
-        return prepare_image_inputs(proc, llm.tokenizer, q, [rng.integers(0, 256, (448, 448, 3), dtype=np.uint8)])
+        return prepare_image_inputs(proc, llm.tokenizer, q, [picture()])
     if workload == "video16":
-        return prepare_video_inputs(proc, llm.tokenizer, q, [rng.integers(0, 256, (448, 448, 3), dtype=np.uint8) for _ in range(16)])
+        return prepare_video_inputs(proc, llm.tokenizer, q, [picture() for _ in range(16)])
     return None
 
 
-def main() -> None:
-    ap = argparse.ArgumentParser()
+def main(argv=None) -> None:
+    ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     ap.add_argument("--workload", default="image1", choices=["images8", "image1", "video16", "text"])
     ap.add_argument("--batches", default="1,8,32,128")
     ap.add_argument("--output-tokens", type=int, default=128)
@@ -48,9 +54,12 @@ def main() -> None:
     ap.add_argument("--tp", type=int, default=1)
     ap.add_argument("--chunk", type=int, default=2048)
     ap.add_argument("--out", default="")
-    args = ap.parse_args()
+    ap.add_argument("--device", default=None)
+    ap.add_argument("--image-size", type=int, default=448)
+    ap.add_argument("--text-tokens", type=int, default=256, help="prompt length of the text workload")
+    args = ap.parse_args(argv)
     batches = [int(b) for b in args.batches.split(",")]
-    llm = LLM(args.model, tensor_parallel_size=args.tp, max_model_len=4096, kvcache_block_size=256,
+    llm = LLM(args.model, device=args.device, tensor_parallel_size=args.tp, max_model_len=4096, kvcache_block_size=256,
               num_kvcache_blocks=max(64, max(batches) * 10), compression_mode="scaled_fp8_kv", max_num_seqs=max(batches),
               max_num_batched_tokens=16384, max_chunk_size=args.chunk, cpu_kv_cache_ratio=0.0, enable_prefix_caching=False)
     if not llm.is_driver:
@@ -64,9 +73,9 @@ def main() -> None:
             ids = []
             t_submit = time.perf_counter()
             for _ in range(b):
-                inp = build_inputs(llm, args.workload, rng)
+                inp = build_inputs(llm, args.workload, rng, args.image_size)
                 if inp is None:
-                    ids.append(llm.add_request(rng.integers(0, 150000, 256).tolist(), sp))
+                    ids.append(llm.add_request(token_ids(llm, rng, args.text_tokens), sp))
                 elif args.workload == "video16":
                     ids.append(llm.add_prepared_video_request(inp, sp))
                 else:

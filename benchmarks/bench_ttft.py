@@ -28,7 +28,7 @@ from prism_infer_b200.analysis.performance_profile import performance_profile  #
 from prism_infer_b200.engine.vl_inputs import PatchProcessor, prepare_image_inputs  # noqa: E402
 
 
-def main() -> None:
+def main(argv=None) -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--images", type=int, default=8)
     ap.add_argument("--repeats", type=int, default=5)
@@ -41,7 +41,9 @@ def main() -> None:
     ap.add_argument("--vision-graph", action="store_true", help="replay the vision tower from a CUDA graph per grid shape")
     ap.add_argument("--cuda-profiler-range", action="store_true",
                     help="bracket the last timed request with cudaProfilerStart/Stop (for ncu --profile-from-start off)")
-    args = ap.parse_args()
+    ap.add_argument("--device", default=None)
+    ap.add_argument("--image-size", type=int, default=448)
+    args = ap.parse_args(argv)
     import torch
 
     sync = torch.cuda.synchronize if torch.cuda.is_available() else (lambda: None)
@@ -51,7 +53,7 @@ def main() -> None:
     kernels = ["tc", "mma"] if args.paged_prefill_kernel == "both" else [args.paged_prefill_kernel]
     long_text = args.text_tokens > 0
     max_len = max(4096, args.text_tokens + 256)
-    llm = LLM(args.model, tensor_parallel_size=args.tp, max_model_len=max_len, kvcache_block_size=256,
+    llm = LLM(args.model, device=args.device, tensor_parallel_size=args.tp, max_model_len=max_len, kvcache_block_size=256,
               num_kvcache_blocks=max(64, 2 * (max_len // 256) + 2), compression_mode="scaled_fp8_kv", max_num_seqs=4,
               max_num_batched_tokens=min(16384, args.chunk) if long_text else 16384, max_chunk_size=args.chunk,
               cpu_kv_cache_ratio=0.0, enable_prefix_caching=False, enable_vision_tensor_cudagraph=args.vision_graph)
@@ -62,12 +64,14 @@ def main() -> None:
     proc = PatchProcessor(llm.arch)
     sp = SamplingParams(temperature=0.0, max_tokens=1, ignore_eos=True)
 
+    vocab = min(150000, llm.arch.text.vocab_size - 64)  # below the special tokens of the model's vocabulary
+
     def make():
         t0 = time.perf_counter()
         if long_text:
-            return rng.integers(0, 150000, args.text_tokens).tolist(), (time.perf_counter() - t0) * 1e3
-        inp = prepare_image_inputs(proc, llm.tokenizer, rng.integers(0, 150000, 32).tolist(),
-                                   [rng.integers(0, 256, (448, 448, 3), dtype=np.uint8) for _ in range(args.images)])
+            return rng.integers(0, vocab, args.text_tokens).tolist(), (time.perf_counter() - t0) * 1e3
+        inp = prepare_image_inputs(proc, llm.tokenizer, rng.integers(0, vocab, 32).tolist(),
+                                   [rng.integers(0, 256, (args.image_size, args.image_size, 3), dtype=np.uint8) for _ in range(args.images)])
         return inp, (time.perf_counter() - t0) * 1e3
 
     def one(inp) -> float:

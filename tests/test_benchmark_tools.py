@@ -459,3 +459,26 @@ def test_external_engine_arm_builds_requests_and_times_a_fake_engine(capsys):
         assert b.main([]) == 0
         line = json.loads(capsys.readouterr().out)
         assert line == {"engine": "vllm", "unavailable": "no CUDA device"}
+
+
+def test_decode_matrix_and_ttft_benchmarks_run_end_to_end_on_cpu(tmp_path, capsys):
+    """The two latency benchmarks through their command-line entries on the tiny model: the decode matrix writes a record
+    that satisfies its contract; the TTFT breakdown prints the engine's profile regions per request for images and for a
+    chunked long text prompt."""
+    from prism_infer_b200.analysis import benchmark_schema as bs
+
+    d = _load("bench_decode")
+    out = tmp_path / "decode.json"
+    d.main(["--model", "random:tiny", "--device", "cpu", "--workload", "image1", "--image-size", "64", "--batches", "1,2", "--output-tokens", "12",
+            "--out", str(out)])
+    rec = json.loads(out.read_text())
+    bs.validate_benchmark_record(rec)
+    assert [r["batch"] for r in rec["results"]["rows"]] == [1, 2] and "steady_step_ms_median" in rec["results"]["rows"][1]
+    capsys.readouterr()
+    t = _load("bench_ttft")
+    t.main(["--model", "random:tiny", "--device", "cpu", "--images", "2", "--image-size", "64", "--repeats", "2"])
+    line = json.loads(capsys.readouterr().out.strip().splitlines()[-1])
+    assert line["workload"] == "images2" and len(line["ttft_ms"]) == 2 and line["regions"]["engine.step"]["count_per_request"] >= 1
+    t.main(["--model", "random:tiny", "--device", "cpu", "--text-tokens", "300", "--chunk", "128", "--repeats", "2", "--paged-prefill-kernel", "both"])
+    lines = [json.loads(x) for x in capsys.readouterr().out.strip().splitlines()]
+    assert [x["workload"] for x in lines] == ["text300_chunk128_tc", "text300_chunk128_mma"] and all(x["prompt_tokens"] == 300 for x in lines)
