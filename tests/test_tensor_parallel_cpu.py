@@ -65,3 +65,39 @@ def test_tp2_cpu_attention_strategy_scores_are_reduced_over_ranks():
     finally:
         two.exit()
     assert got == want
+
+
+@pytest.mark.timeout(300)
+def test_tp2_cpu_loads_an_upstream_checkpoint_directory_and_matches_upstream_tokens(tmp_path):
+    """What a deployment does: a checkpoint directory written by the upstream ``save_pretrained`` (several safetensors
+    shards with an index), two ranks that each read their own slices of it, and the tokens of the upstream model."""
+    hf = pytest.importorskip("transformers.models.qwen3_vl")
+    arch = Qwen3VLArch.tiny()
+    torch.manual_seed(0)
+    model = hf.Qwen3VLForConditionalGeneration(hf.Qwen3VLConfig(**arch.to_hf_config())).eval().float()
+    g = torch.Generator().manual_seed(3)
+    model.load_state_dict({k: torch.randn(v.shape, generator=g) * (0.05 if v.ndim > 1 else 0.2) + (1.0 if ("norm" in k and k.endswith("weight")) else 0.0)
+                           for k, v in model.state_dict().items()})
+    model.save_pretrained(tmp_path / "ckpt", safe_serialization=True, max_shard_size="400KB")
+    img = np.random.default_rng(1).integers(0, 256, (64, 96, 3), dtype=np.uint8)
+    inp = prepare_image_inputs(PatchProcessor(arch), load_tokenizer("random:tiny", arch), [9, 8, 7], [img])
+
+    def upstream_next(extra):
+        ids = torch.tensor([list(inp.input_ids) + extra])
+        mm = torch.zeros_like(ids, dtype=torch.int32)
+        mm[ids == arch.image_token_id] = 1
+        with torch.no_grad():
+            out = model(input_ids=ids, attention_mask=torch.ones_like(ids), mm_token_type_ids=mm, pixel_values=inp.pixel_values.float(),
+                        image_grid_thw=torch.tensor(inp.image_grid_thw))
+        return int(torch.argmax(out.logits[0, -1]))
+
+    want = []
+    for _ in range(5):
+        want.append(upstream_next(want))
+    llm = LLM(str(tmp_path / "ckpt"), tensor_parallel_size=2, device="cpu", max_model_len=256, kvcache_block_size=16, num_kvcache_blocks=32,
+              enforce_eager=True, max_num_batched_tokens=256, max_chunk_size=256, tensor_parallel_timeout_seconds=120)
+    try:
+        got = llm.generate_prepared_image_inputs(inp, SamplingParams(temperature=0.0, max_tokens=5, ignore_eos=True))["token_ids"]
+    finally:
+        llm.exit()
+    assert got == want
