@@ -214,3 +214,33 @@ def test_video_file_sampling_rule_equals_upstream_and_a_file_request_runs(pair, 
     assert from_file["token_ids"] == llm.generate_prepared_video_inputs(inputs, sp)["token_ids"]
     assert from_file["token_ids"] == oracle.generate_greedy(inputs.input_ids, 4, pixel_values=inputs.pixel_values, video_grid_thw=inputs.video_grid_thw)
     llm.exit()
+
+
+def test_tied_embedding_checkpoint_loads_without_an_lm_head_tensor(tmp_path):
+    """Smaller Qwen3-VL checkpoints tie the LM head to the embedding: the saved file has no ``lm_head.weight``."""
+    import dataclasses
+
+    from safetensors import safe_open
+
+    arch = Qwen3VLArch.tiny()
+    arch = dataclasses.replace(arch, text=dataclasses.replace(arch.text, tie_word_embeddings=True))
+    torch.manual_seed(0)
+    hf = hf_qwen3_vl.Qwen3VLForConditionalGeneration(hf_qwen3_vl.Qwen3VLConfig(**arch.to_hf_config())).eval().float()
+    g = torch.Generator().manual_seed(5)
+    with torch.no_grad():
+        for name, p in hf.named_parameters():
+            p.copy_(torch.randn(p.shape, generator=g) * (0.05 if p.ndim > 1 else 0.2) + (1.0 if ("norm" in name and name.endswith("weight")) else 0.0))
+    assert hf.lm_head.weight.data_ptr() == hf.model.language_model.embed_tokens.weight.data_ptr()
+    hf.save_pretrained(tmp_path / "ckpt", safe_serialization=True)
+    with safe_open(str(tmp_path / "ckpt" / "model.safetensors"), "pt") as fh:
+        assert "lm_head.weight" not in list(fh.keys())
+    assert Qwen3VLArch.from_pretrained(str(tmp_path / "ckpt")).text.tie_word_embeddings
+    ids, want = [5, 6, 7, 8, 9, 10], []
+    for _ in range(5):
+        t = torch.tensor([ids + want])
+        with torch.no_grad():
+            want.append(int(hf(input_ids=t, attention_mask=torch.ones_like(t)).logits[0, -1].argmax()))
+    llm = LLM(str(tmp_path / "ckpt"), device="cpu", max_model_len=128, kvcache_block_size=16, num_kvcache_blocks=16, enforce_eager=True)
+    got = llm.generate([ids], SamplingParams(temperature=0.0, max_tokens=5, ignore_eos=True))[0]["token_ids"]
+    llm.exit()
+    assert got == want and len(set(want)) > 1
