@@ -312,3 +312,50 @@ def test_http_server_with_the_real_engine_on_cpu():
         assert rt.is_healthy
     finally:
         rt.stop()
+
+
+def test_prism_serve_process_answers_over_tcp(tmp_path):
+    """The console entry as a user starts it: a child process (``python -m prism_infer_b200.serving.cli``) with an engine
+    configuration file, the tiny model on CPU, a real socket; health, one generation, then a clean shutdown on SIGTERM."""
+    import os
+    import signal
+    import socket
+    import subprocess
+    import sys
+    import time
+    import urllib.request
+
+    cfg = tmp_path / "engine.json"
+    cfg.write_text(json.dumps({"device": "cpu", "max_model_len": 128, "kvcache_block_size": 16, "num_kvcache_blocks": 16, "enforce_eager": True}))
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    proc = subprocess.Popen([sys.executable, "-m", "prism_infer_b200.serving.cli", "--model", "random:tiny", "--engine-config", str(cfg),
+                             "--host", "127.0.0.1", "--port", str(port), "--log-level", "warning"], cwd=root,
+                            stdout=subprocess.PIPE, stderr=subprocess.STDOUT)
+    try:
+        deadline = time.time() + 90
+        while True:
+            try:
+                with urllib.request.urlopen(f"http://127.0.0.1:{port}/health", timeout=2) as r:
+                    if r.status == 200:
+                        break
+            except OSError:
+                pass
+            assert proc.poll() is None, proc.stdout.read().decode()[-2000:]
+            assert time.time() < deadline, "the server did not come up"
+            time.sleep(0.3)
+        body = json.dumps({"prompt": "7 8 9", "sampling": {"max_tokens": 4, "ignore_eos": True}}).encode()
+        req = urllib.request.Request(f"http://127.0.0.1:{port}/v1/generate", data=body, headers={"Content-Type": "application/json"})
+        with urllib.request.urlopen(req, timeout=60) as r:
+            out = json.loads(r.read())
+        assert out["event"] == "done" and len(out["token_ids"]) == 4 and out["finish_reason"] == "length"
+    finally:
+        proc.send_signal(signal.SIGTERM)  # this exact child; uvicorn turns the signal into a lifespan shutdown
+        try:
+            proc.wait(timeout=30)
+        except subprocess.TimeoutExpired:
+            proc.kill()
+            proc.wait(timeout=10)
+    assert proc.returncode in (0, -signal.SIGTERM), proc.returncode
