@@ -141,7 +141,8 @@ def create_app(runtime: ServingRuntime, *, manage_runtime: bool = True) -> FastA
     @app.get("/health")
     async def health() -> JSONResponse:
         if runtime.is_healthy:
-            return JSONResponse({"status": "ok"})
+            restarts = list(getattr(runtime, "restarts", ()))
+            return JSONResponse({"status": "ok", **({"restarts": restarts} if restarts else {})})
         detail = str(runtime.failure) if runtime.failure is not None else "engine is not running"
         return JSONResponse({"status": "unavailable", "error": detail}, status_code=503)
 

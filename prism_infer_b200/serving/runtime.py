@@ -81,12 +81,21 @@ class _Live:
     handle: RequestHandle
     engine_id: int | None = None
     token_ids: list[int] = field(default_factory=list)
+    replayed: int = 0  # after an engine restart: how many of the tokens already delivered the new engine has produced again
 
 
 class ServingRuntime:
+    """``max_restarts`` (default 0: a failure of the engine ends the runtime, as in the reference): after a failure in a step
+    the engine is closed, a new one is built by the factory and every open greedy request is submitted again; the tokens
+    it had already delivered are produced a second time, checked against what was delivered and not sent twice.  Requests
+    that sample (temperature > 0) cannot be reproduced and end with an error.  A fault that leaves the device unusable
+    also fails the rebuild, which ends the runtime."""
+
     def __init__(self, engine_factory: Callable[[], ServingEngine], *, ingress_capacity: int = 64,
-                 idle_sleep_s: float = 0.001) -> None:
+                 idle_sleep_s: float = 0.001, max_restarts: int = 0) -> None:
         self._factory = engine_factory
+        self.max_restarts = int(max_restarts)
+        self.restarts: list[str] = []  # one line per restart: the failure that caused it
         self._ingress: "queue.Queue[_Live]" = queue.Queue(maxsize=ingress_capacity)
         self._cancel: "queue.Queue[str]" = queue.Queue()
         self._live: dict[str, _Live] = {}
@@ -151,7 +160,7 @@ class ServingRuntime:
         with self._ids_lock:
             self._ids.discard(live.request.request_id)
 
-    def _admit(self, live: _Live) -> None:
+    def _admit(self, live: _Live, *, replay: bool = False) -> None:
         eng, req = self.engine, live.request
         assert eng is not None
         try:
@@ -172,7 +181,8 @@ class ServingRuntime:
         live.engine_id = eid
         self._live[req.request_id] = live
         self._by_engine[eid] = live
-        live.handle.publish(ServingEvent(req.request_id, EventKind.ACCEPTED, engine_request_id=eid))
+        if not replay:
+            live.handle.publish(ServingEvent(req.request_id, EventKind.ACCEPTED, engine_request_id=eid))
         state = eng.request_state(eid)
         if state is not None and getattr(state, "value", "") == "rejected":
             self._finish(live, ServingEvent(req.request_id, EventKind.DONE, engine_request_id=eid, text="",
@@ -203,6 +213,44 @@ class ServingRuntime:
                 return
             self._admit(live)
 
+    def _restart(self, cause: BaseException) -> None:
+        """Close the failed engine, build a new one and submit the open requests again (see the class docstring)."""
+        self.restarts.append(f"{type(cause).__name__}: {cause}")
+        try:
+            self.engine.exit()  # type: ignore[union-attr]
+        except Exception:
+            pass
+        self.engine = self._factory()
+        open_requests = list(self._live.values())
+        self._live.clear()
+        self._by_engine.clear()
+        for live in open_requests:
+            live.engine_id, live.replayed = None, 0  # ids of the old engine mean nothing to the new one
+            if live.request.sampling_params.temperature > 0:
+                self._finish(live, ServingEvent(live.request.request_id, EventKind.ERROR,
+                                                error="the engine was restarted and a sampled request cannot be reproduced"))
+                continue
+            self._admit(live, replay=True)
+
+    def _deliver(self, live: _Live, out) -> None:
+        if out.new_token is not None:
+            if live.replayed < len(live.token_ids):
+                # a token the client already has: it must come out the same, and is not sent again
+                if live.token_ids[live.replayed] != out.new_token:
+                    self.engine.cancel_request(out.request_id)  # type: ignore[union-attr]
+                    self._finish(live, ServingEvent(live.request.request_id, EventKind.ERROR,
+                                                    error="the restarted engine did not reproduce the tokens already delivered"))
+                    return
+                live.replayed += 1
+            else:
+                live.token_ids.append(out.new_token)
+                live.replayed = len(live.token_ids)
+                live.handle.publish(ServingEvent(
+                    live.request.request_id, EventKind.TOKEN, engine_request_id=out.request_id,
+                    token_id=out.new_token, token_text=self.engine.tokenizer.decode([out.new_token])))  # type: ignore[union-attr]
+        if out.finished:
+            self._finish(live, self._done(live, out.finish_reason or "finished"))
+
     def _run(self) -> None:
         try:
             self.engine = self._factory()
@@ -213,24 +261,23 @@ class ServingRuntime:
         self._ready.set()
         try:
             while not self._stop.is_set():
-                self._apply_cancellations()
-                self._drain_ingress()
-                if self.engine.is_finished():
-                    time.sleep(self._idle_sleep_s)
+                try:
+                    self._apply_cancellations()
+                    self._drain_ingress()
+                    if self.engine.is_finished():
+                        time.sleep(self._idle_sleep_s)
+                        continue
+                    result = self.engine.step_result()
+                except Exception as exc:  # a failed step: rebuild and replay while restarts are left
+                    if len(self.restarts) >= self.max_restarts or self._stop.is_set():
+                        raise
+                    self._restart(exc)
                     continue
-                result = self.engine.step_result()
                 self.steps += 1
                 for out in result.outputs:
                     live = self._by_engine.get(out.request_id)
-                    if live is None:
-                        continue
-                    if out.new_token is not None:
-                        live.token_ids.append(out.new_token)
-                        live.handle.publish(ServingEvent(
-                            live.request.request_id, EventKind.TOKEN, engine_request_id=out.request_id,
-                            token_id=out.new_token, token_text=self.engine.tokenizer.decode([out.new_token])))
-                    if out.finished:
-                        self._finish(live, self._done(live, out.finish_reason or "finished"))
+                    if live is not None:
+                        self._deliver(live, out)
         except BaseException as exc:  # noqa: BLE001 - reported to every open request
             self.failure = exc
             for live in list(self._live.values()):

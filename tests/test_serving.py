@@ -174,6 +174,67 @@ def test_engine_failure_reaches_every_request_and_health():
     rt.stop()
 
 
+def test_restart_replays_greedy_requests_without_repeating_tokens():
+    """With ``max_restarts`` a failed step costs the clients nothing they can see: the engine is rebuilt, open greedy
+    requests run again from their prompts, tokens already delivered are checked and not sent twice, and a request that
+    samples ends with an error.  A second failure beyond the allowance ends the runtime as without the option."""
+    built = []
+
+    def factory():
+        built.append(FakeEngine(fail_after=3 if not built else None))
+        return built[-1]
+
+    rt = ServingRuntime(factory, max_restarts=1)
+    rt.start()
+    greedy = [rt.submit(_req(f"g{i}", max_tokens=8)) for i in range(2)]
+    sampled = rt.submit(GenerationRequest("s", "hello", Modality.TEXT, None, SamplingParams(temperature=0.8, max_tokens=8)))
+    for h in greedy:
+        events = _drain(h)
+        assert [e.kind for e in events].count(EventKind.ACCEPTED) == 1
+        assert [e.token_id for e in events if e.kind is EventKind.TOKEN] == list(range(101, 109))
+        assert events[-1].kind is EventKind.DONE and events[-1].token_ids == tuple(range(101, 109))
+    events = _drain(sampled)
+    assert events[-1].kind is EventKind.ERROR and "sampled" in events[-1].error
+    assert rt.is_healthy and len(built) == 2 and built[0].exited and len(rt.restarts) == 1 and "boom" in rt.restarts[0]
+    # a request after the restart is served by the new engine
+    assert _drain(rt.submit(_req("after", max_tokens=2)))[-1].token_ids == (101, 102)
+    rt.stop()
+
+    # the new engine answers differently: the request ends with an error instead of a stream that changes its mind
+    class Shifted(FakeEngine):
+        def step_result(self):
+            res = super().step_result()
+            return StepResult(res.phase, tuple(RequestOutput(o.request_id, o.new_token + 1000, o.finished, o.finish_reason)
+                                               for o in res.outputs), res.num_tokens)
+
+    built2 = []
+
+    def factory2():
+        built2.append(FakeEngine(fail_after=2) if not built2 else Shifted())
+        return built2[-1]
+
+    rt2 = ServingRuntime(factory2, max_restarts=1)
+    rt2.start()
+    events = _drain(rt2.submit(_req("x", max_tokens=8)))
+    assert events[-1].kind is EventKind.ERROR and "did not reproduce" in events[-1].error and built2[1].cancelled
+    rt2.stop()
+
+    # the allowance is spent: the next failure is final
+    built3 = []
+
+    def factory3():
+        built3.append(FakeEngine(fail_after=2))
+        return built3[-1]
+
+    rt3 = ServingRuntime(factory3, max_restarts=1)
+    rt3.start()
+    events = _drain(rt3.submit(_req("y", max_tokens=50)))
+    assert events[-1].kind is EventKind.ERROR and "boom" in events[-1].error
+    time.sleep(0.05)
+    assert not rt3.is_healthy and len(built3) == 2
+    rt3.stop()
+
+
 def test_shutdown_finishes_open_requests():
     eng = FakeEngine(step_delay=0.01)
     rt = ServingRuntime(lambda: eng)
@@ -310,6 +371,65 @@ def test_http_server_with_the_real_engine_on_cpu():
     try:
         asyncio.run(scenario())
         assert rt.is_healthy
+    finally:
+        rt.stop()
+
+
+def test_restart_with_the_real_engine_reproduces_the_stream():
+    """The tiny engine on CPU fails once in the middle of decoding two requests (one with an image); after the rebuild
+    both streams continue and equal the ones of an undisturbed engine, and /health names the restart."""
+    import numpy as np
+    import torch
+    from PIL import Image
+
+    from prism_infer_b200 import LLM, SamplingParams
+    from prism_infer_b200.models.architecture import Qwen3VLArch
+    from prism_infer_b200.models.weights import random_weights
+
+    arch = Qwen3VLArch.tiny()
+    weights = random_weights(arch, dtype=torch.float32, seed=0)
+    image = Image.fromarray(np.random.default_rng(5).integers(0, 256, (64, 64, 3), dtype=np.uint8))
+    built = []
+
+    def make():
+        eng = LLM("random:tiny", weights=weights, device="cpu", max_model_len=256, kvcache_block_size=16, num_kvcache_blocks=64,
+                  enforce_eager=True, max_num_batched_tokens=256, max_chunk_size=256, max_num_seqs=4)
+        if not built:  # the first engine breaks on its fifth step
+            inner, calls = eng.step_result, [0]
+
+            def step_result():
+                calls[0] += 1
+                if calls[0] == 5:
+                    raise RuntimeError("injected step failure")
+                return inner()
+
+            eng.step_result = step_result
+        built.append(eng)
+        return eng
+
+    sp = SamplingParams(temperature=0.0, max_tokens=8, ignore_eos=True)
+    direct = LLM("random:tiny", weights=weights, device="cpu", max_model_len=256, kvcache_block_size=16, num_kvcache_blocks=64,
+                 enforce_eager=True, max_num_batched_tokens=256, max_chunk_size=256, max_num_seqs=4)
+    want_text = direct.generate(["7 8 9"], sp)[0]["token_ids"]
+    want_image = direct.generate_images("21 22", [image], sp)["token_ids"]
+    direct.exit()
+
+    rt = ServingRuntime(make, max_restarts=1)
+    rt.start()
+    try:
+        h_text = rt.submit(GenerationRequest("t", "7 8 9", Modality.TEXT, None, sp))
+        h_image = rt.submit(GenerationRequest("i", "21 22", Modality.IMAGE, image, sp))
+        ev_text, ev_image = _drain(h_text, 60.0), _drain(h_image, 60.0)
+        assert [e.token_id for e in ev_text if e.kind is EventKind.TOKEN] == want_text
+        assert [e.token_id for e in ev_image if e.kind is EventKind.TOKEN] == want_image
+        assert ev_text[-1].token_ids == tuple(want_text) and ev_image[-1].token_ids == tuple(want_image)
+        assert len(built) == 2 and rt.restarts == ["RuntimeError: injected step failure"] and rt.is_healthy
+
+        async def health():
+            async with httpx.AsyncClient(transport=httpx.ASGITransport(app=create_app(rt, manage_runtime=False)), base_url="http://t") as c:
+                return (await c.get("/health")).json()
+
+        assert asyncio.run(health()) == {"status": "ok", "restarts": ["RuntimeError: injected step failure"]}
     finally:
         rt.stop()
 
