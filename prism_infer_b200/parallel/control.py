@@ -32,7 +32,7 @@ import pickle
 import time
 import traceback
 from multiprocessing import shared_memory
-from typing import Any
+from typing import Any, Callable
 
 import numpy as np
 
@@ -72,6 +72,16 @@ class TPTimeout(TPControlError):
         super().__init__(f"tensor-parallel command {method!r} (request {request_id}) timed out after "
                          f"{deadline_s:.1f}s; pending ranks: {pending}")
         self.pending = pending
+
+
+class TPWorkerExited(TPControlError):
+    """A worker process ended while its acknowledgement was awaited (seen through the process handle, without
+    waiting for the deadline)."""
+
+    def __init__(self, method: str, request_id: int, exited: dict[int, int | None]) -> None:
+        super().__init__(f"tensor-parallel command {method!r} (request {request_id}): worker process ended before it "
+                         f"acknowledged; rank -> exit code: {exited}")
+        self.exited = exited
 
 
 class TPWorkerError(TPControlError):
@@ -172,9 +182,15 @@ def read_payload(seg: ControlSegment, total: int) -> Any:
 class ControlDriver:
     """Driver side: broadcast a command, run the local copy, collect acknowledgements."""
 
-    def __init__(self, segment: ControlSegment, *, timeout_s: float = 120.0, worker_ranks: list[int] | None = None) -> None:
+    def __init__(self, segment: ControlSegment, *, timeout_s: float = 120.0, worker_ranks: list[int] | None = None,
+                 exit_codes: Callable[[], list[int | None]] | None = None, liveness_period_s: float = 0.05) -> None:
+        """``exit_codes()`` (optional; the group that spawned the workers reads their process handles) gives per worker
+        ``None`` while its process runs and its exit code afterwards; it is asked every ``liveness_period_s`` while
+        acknowledgements are pending, so a worker that died is reported at once instead of at the deadline."""
         self.seg = segment
         self.timeout_s = timeout_s
+        self.exit_codes = exit_codes
+        self.liveness_period_s = liveness_period_s
         self.request_id = 0
         self.worker_ranks = worker_ranks or list(range(1, segment.n_workers + 1))
 
@@ -198,6 +214,7 @@ class ControlDriver:
         done = [False] * n
         results: list[Any] = [None] * n
         spins = 0
+        next_liveness = time.monotonic() + self.liveness_period_s
         while not all(done):
             for w in range(n):
                 if done[w]:
@@ -218,7 +235,15 @@ class ControlDriver:
             spins += 1
             if spins > 2000:
                 time.sleep(0.0002)
-            if time.monotonic() > deadline:
+            now = time.monotonic()
+            if self.exit_codes is not None and now >= next_liveness:
+                next_liveness = now + self.liveness_period_s
+                codes = self.exit_codes()
+                # a worker that acknowledged and then ended (the answer to EXIT) is read on the next pass, not reported
+                gone = [w for w in range(n) if not done[w] and codes[w] is not None and int(self.seg.words[8 + 8 * w]) != request_id]
+                if gone:
+                    raise TPWorkerExited(method, request_id, {self.worker_ranks[w]: codes[w] for w in gone})
+            if now > deadline:
                 pending = [self.worker_ranks[w] for w in range(n) if not done[w]]
                 raise TPTimeout(method, request_id, pending, deadline_s)
         return results

@@ -158,7 +158,8 @@ class TensorParallelGroup:
                 self._terminate_workers()
                 raise
         if self.rank == 0:
-            self.driver = ControlDriver(self.seg, timeout_s=float(timeout))
+            self.driver = ControlDriver(self.seg, timeout_s=float(timeout),
+                                        exit_codes=(lambda: [p.exitcode for p in self.procs]) if self.procs else None)
         else:
             self.worker = ControlWorker(self.seg, self.rank - 1, self.rank)
         try:

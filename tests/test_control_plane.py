@@ -9,7 +9,7 @@ import time
 import pytest
 
 from prism_infer_b200.parallel.control import (ControlDriver, ControlSegment, ControlWorker, TPControlError, TPMethod,
-                                               TPTimeout, TPWorkerError)
+                                               TPTimeout, TPWorkerError, TPWorkerExited)
 
 
 class EchoRunner:
@@ -112,6 +112,32 @@ def test_dead_worker_is_detected_by_the_deadline():
             driver.collect("execute", rid, timeout_s=0.5)
         procs[0].join(timeout=10)
         assert procs[0].exitcode == 17
+    finally:
+        _stop(seg, procs, driver)
+
+
+@pytest.mark.timeout(120)
+def test_dead_worker_is_reported_at_once_through_its_process_handle():
+    """With the workers' exit codes at hand the driver does not wait for the deadline: the rank that ended is named with
+    its exit code while the healthy rank's answer is still accepted, and a worker that acknowledges EXIT and then ends
+    is not mistaken for a dead one."""
+    seg, procs = _start(2, ["echo", "die_on_second"])
+    driver = ControlDriver(seg, timeout_s=60.0, exit_codes=lambda: [p.exitcode for p in procs], liveness_period_s=0.02)
+    try:
+        rid = driver.post("execute", ("a",))
+        assert driver.collect("execute", rid) == [None, (2, "a", 1)]  # a serving worker keeps execute's value to itself
+        rid = driver.post("execute", ("b",))
+        t0 = time.monotonic()
+        with pytest.raises(TPWorkerExited) as info:
+            driver.collect("execute", rid)
+        assert time.monotonic() - t0 < 20.0 and info.value.exited == {2: 17} and isinstance(info.value, TPControlError)
+    finally:
+        _stop(seg, procs, driver)
+    seg, procs = _start(1, ["echo"])
+    driver = ControlDriver(seg, timeout_s=60.0, exit_codes=lambda: [p.exitcode for p in procs], liveness_period_s=0.0)
+    try:
+        rid = driver.post(TPMethod.EXIT, ())
+        assert driver.collect("exit", rid) == [None]
     finally:
         _stop(seg, procs, driver)
 

@@ -101,3 +101,45 @@ def test_tp2_cpu_loads_an_upstream_checkpoint_directory_and_matches_upstream_tok
     finally:
         llm.exit()
     assert got == want
+
+
+@pytest.mark.timeout(300)
+def test_tp2_cpu_worker_killed_in_mid_stream_is_replaced_and_the_stream_continues():
+    """Recovery from a lost rank, end to end on two CPU ranks: the serving runtime streams a greedy request from a
+    two-rank engine, the worker process is killed between tokens (a host-side fault), the driver names the dead rank
+    with its exit code without waiting for the command deadline, the runtime builds a new two-rank engine and the
+    client's stream continues; all tokens equal the oracle's and none arrives twice."""
+    import os
+    import signal
+
+    from prism_infer_b200.serving import EventKind, GenerationRequest, Modality, ServingRuntime
+
+    arch = Qwen3VLArch.tiny()
+    weights = random_weights(arch, dtype=torch.float32, seed=0)
+    built = []
+
+    def make():
+        built.append(LLM("random:tiny", weights=weights, tensor_parallel_size=2, max_model_len=256, kvcache_block_size=16,
+                         num_kvcache_blocks=64, enforce_eager=True, max_chunk_size=64, tensor_parallel_timeout_seconds=60))
+        return built[-1]
+
+    rt = ServingRuntime(make, max_restarts=1)
+    rt.start()
+    try:
+        sp = SamplingParams(temperature=0.0, max_tokens=24, ignore_eos=True)
+        handle = rt.submit(GenerationRequest("r", "5 6 7 8 9", Modality.TEXT, None, sp))
+        tokens, final = [], None
+        while final is None:
+            ev = handle.next_event_blocking(120.0)
+            if ev.kind is EventKind.TOKEN:
+                tokens.append(ev.token_id)
+                if len(tokens) == 3:
+                    os.kill(built[0].runners.procs[0].pid, signal.SIGKILL)
+            elif ev.kind in (EventKind.DONE, EventKind.ERROR):
+                final = ev
+        assert final.kind is EventKind.DONE, final.error
+        assert tokens == list(final.token_ids) == ReferenceQwen3VL(arch, weights).generate_greedy([5, 6, 7, 8, 9], 24)
+        assert len(built) == 2 and len(rt.restarts) == 1 and rt.is_healthy
+        assert "TPWorkerExited" in rt.restarts[0] and "{1: -9}" in rt.restarts[0]
+    finally:
+        rt.stop()
