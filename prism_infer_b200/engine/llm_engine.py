@@ -550,6 +550,34 @@ class LLMEngine:
     def reset_metrics(self) -> None:
         self.metrics.reset()
 
+    def serving_stats(self) -> dict[str, float]:
+        """Flat ``name -> number`` view of the host-side counters, for a metrics endpoint: scheduler queues and counters,
+        KV pages, the multimodal prefix cache, the cooperative-prefill counters and latency summaries of the finished
+        newest 2048 finished requests.  No command goes to the worker ranks and no device work is issued, so the
+        owner thread can call it between steps at any cadence."""
+        from ..analysis.online_serving import percentile
+
+        out: dict[str, float] = {}
+        for k, v in self.scheduler.metrics_snapshot().items():
+            out[f"scheduler_{k}"] = float(v)
+        pool = self.scheduler.block_manager.gpu
+        out["kv_pages_total"] = float(pool.num_blocks)
+        out["kv_pages_used"] = float(pool.num_blocks - pool.num_free)
+        out["kv_bytes_per_page"] = float(self.config.kv_bytes_per_page())
+        for k, v in self.scheduler.block_manager.prefix_cache_metadata().items():
+            if isinstance(v, (int, float)) and not isinstance(v, bool) and k not in ("free_pages", "total_pages"):
+                out[f"prefix_cache_{k}"] = float(v)
+        for k, v in self.cooperative_counters.items():
+            if isinstance(v, (int, float)) and not isinstance(v, bool):
+                out[f"cooperative_{k}"] = float(v)
+        done = self.metrics.recent_finished(2048)
+        out["latency_window_requests"] = float(len(done))
+        for key in ("ttft_ms", "tpot_ms", "queue_ms", "latency_ms"):
+            xs = sorted(float(r[key]) for r in done if r.get(key) is not None)
+            if xs:
+                out[f"{key}_p50"], out[f"{key}_p99"] = percentile(xs, 0.5), percentile(xs, 0.99)
+        return out
+
     def multimodal_prefix_cache_metadata(self) -> dict[str, object]:
         meta = self.scheduler.block_manager.prefix_cache_metadata()
         per_page = self.config.kv_bytes_per_page()

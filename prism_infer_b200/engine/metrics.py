@@ -105,6 +105,18 @@ class EngineMetrics:
         with self._lock:
             return {"requests": [m.record() for m in self.requests.values()], "batches": list(self.batches)}
 
+    def recent_finished(self, limit: int = 2048) -> list[dict[str, object]]:
+        """Records of the newest ``limit`` finished requests, newest first (a cheap view for periodic summaries: the full
+        snapshot of a long-running server copies every record)."""
+        out: list[dict[str, object]] = []
+        with self._lock:
+            for m in reversed(self.requests.values()):
+                if m.finished_ns is not None:
+                    out.append(m.record())
+                    if len(out) >= limit:
+                        break
+        return out
+
 
 class NullMetrics:
     def on_request_submitted(self, seq): ...
@@ -114,3 +126,4 @@ class NullMetrics:
     def on_batch_completed(self, plan, duration_ms, compactions=0): ...
     def reset(self): ...
     def snapshot(self): return {"requests": [], "batches": []}
+    def recent_finished(self, limit=2048): return []

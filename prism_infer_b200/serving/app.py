@@ -1,4 +1,5 @@
-"""FastAPI application: ``GET /health`` and ``POST /v1/generate`` (JSON or SSE).
+"""FastAPI application: ``GET /health``, ``POST /v1/generate`` (JSON or SSE) and, beyond the reference, ``GET /metrics``
+(Prometheus text) and ``GET /v1/stats`` (the same numbers as JSON).
 
 Same wire contract as the reference (``prism_infer/serving/app.py:36-267``): strict
 pydantic bodies (unknown fields rejected), media as ``data:image/...;base64`` URLs or path
@@ -125,6 +126,18 @@ async def _disconnected(request: Request) -> None:
             return
 
 
+def prometheus_text(stats: dict[str, float]) -> str:
+    """``name -> number`` as Prometheus text format 0.0.4.  Names are sanitised to ``[a-zA-Z0-9_]``; values that only
+    grow are still typed ``gauge``, since an engine restart sets them back."""
+    lines = []
+    for name in sorted(stats):
+        value = float(stats[name])
+        metric = "prism_" + "".join(ch if ch.isalnum() or ch == "_" else "_" for ch in name)
+        shown = "NaN" if value != value else ("+Inf" if value == float("inf") else "-Inf" if value == float("-inf") else repr(value))
+        lines += [f"# TYPE {metric} gauge", f"{metric} {shown}"]
+    return "\n".join(lines) + "\n"
+
+
 def create_app(runtime: ServingRuntime, *, manage_runtime: bool = True) -> FastAPI:
     @asynccontextmanager
     async def lifespan(_: FastAPI) -> AsyncIterator[None]:
@@ -145,6 +158,17 @@ def create_app(runtime: ServingRuntime, *, manage_runtime: bool = True) -> FastA
             return JSONResponse({"status": "ok", **({"restarts": restarts} if restarts else {})})
         detail = str(runtime.failure) if runtime.failure is not None else "engine is not running"
         return JSONResponse({"status": "unavailable", "error": detail}, status_code=503)
+
+    @app.get("/metrics")
+    async def metrics():
+        """Prometheus text exposition of ``runtime.stats()``: one gauge per name, prefixed ``prism_``."""
+        from starlette.responses import PlainTextResponse
+
+        return PlainTextResponse(prometheus_text(runtime.stats()), media_type="text/plain; version=0.0.4; charset=utf-8")
+
+    @app.get("/v1/stats")
+    async def stats() -> JSONResponse:
+        return JSONResponse(runtime.stats())
 
     @app.post("/v1/generate")
     async def generate(body: GenerateBody, request: Request):

@@ -92,7 +92,7 @@ class ServingRuntime:
     also fails the rebuild, which ends the runtime."""
 
     def __init__(self, engine_factory: Callable[[], ServingEngine], *, ingress_capacity: int = 64,
-                 idle_sleep_s: float = 0.001, max_restarts: int = 0) -> None:
+                 idle_sleep_s: float = 0.001, max_restarts: int = 0, stats_period_s: float = 1.0) -> None:
         self._factory = engine_factory
         self.max_restarts = int(max_restarts)
         self.restarts: list[str] = []  # one line per restart: the failure that caused it
@@ -109,6 +109,10 @@ class ServingRuntime:
         self.engine: ServingEngine | None = None
         self.failure: BaseException | None = None
         self.steps = 0
+        self.counters = {"accepted": 0, "finished": 0, "errors": 0, "cancelled": 0, "tokens": 0}
+        self._stats_period_s = float(stats_period_s)
+        self._stats_due = 0.0
+        self._stats: dict[str, float] = {}
 
     # ------------------------------------------------------------------ lifecycle
     @property
@@ -129,6 +133,28 @@ class ServingRuntime:
         self._stop.set()
         if self._thread is not None:
             self._thread.join(timeout_s)
+
+    def stats(self) -> dict[str, float]:
+        """Flat ``name -> number``: the runtime's own counters plus the engine's ``serving_stats()`` as the owner thread
+        last published them (every ``stats_period_s`` between steps; the HTTP side never reads the engine itself)."""
+        return {**self._stats, "healthy": float(self.is_healthy), "ingress_depth": float(self._ingress.qsize()),
+                "restarts": float(len(self.restarts))}
+
+    def _publish_stats(self, force: bool = False) -> None:
+        now = time.monotonic()
+        if not force and now < self._stats_due:
+            return
+        self._stats_due = now + self._stats_period_s
+        stats = {f"runtime_{k}": float(v) for k, v in self.counters.items()}
+        stats["runtime_steps"] = float(self.steps)
+        stats["runtime_open_requests"] = float(len(self._live))
+        probe = getattr(self.engine, "serving_stats", None)
+        if probe is not None:
+            try:
+                stats.update({f"engine_{k}": float(v) for k, v in probe().items()})
+            except Exception:  # a summary must never take the engine thread down
+                stats["runtime_stats_failures"] = self._stats.get("runtime_stats_failures", 0.0) + 1.0
+        self._stats = stats  # one reference assignment: readers see the old or the new dictionary, never a mix
 
     # --------------------------------------------------------------------- ingress
     def submit(self, request: GenerationRequest, loop: asyncio.AbstractEventLoop | None = None) -> RequestHandle:
@@ -152,6 +178,8 @@ class ServingRuntime:
 
     # ---------------------------------------------------------------- engine thread
     def _finish(self, live: _Live, event: ServingEvent) -> None:
+        self.counters["errors" if event.kind is EventKind.ERROR else
+                      "cancelled" if event.finish_reason == "cancelled" else "finished"] += 1
         live.handle.publish(event)
         live.handle.closed = True
         self._live.pop(live.request.request_id, None)
@@ -182,6 +210,7 @@ class ServingRuntime:
         self._live[req.request_id] = live
         self._by_engine[eid] = live
         if not replay:
+            self.counters["accepted"] += 1
             live.handle.publish(ServingEvent(req.request_id, EventKind.ACCEPTED, engine_request_id=eid))
         state = eng.request_state(eid)
         if state is not None and getattr(state, "value", "") == "rejected":
@@ -245,6 +274,7 @@ class ServingRuntime:
             else:
                 live.token_ids.append(out.new_token)
                 live.replayed = len(live.token_ids)
+                self.counters["tokens"] += 1
                 live.handle.publish(ServingEvent(
                     live.request.request_id, EventKind.TOKEN, engine_request_id=out.request_id,
                     token_id=out.new_token, token_text=self.engine.tokenizer.decode([out.new_token])))  # type: ignore[union-attr]
@@ -264,6 +294,7 @@ class ServingRuntime:
                 try:
                     self._apply_cancellations()
                     self._drain_ingress()
+                    self._publish_stats()
                     if self.engine.is_finished():
                         time.sleep(self._idle_sleep_s)
                         continue

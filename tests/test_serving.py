@@ -434,6 +434,63 @@ def test_restart_with_the_real_engine_reproduces_the_stream():
         rt.stop()
 
 
+def test_metrics_endpoint_reports_runtime_and_engine_numbers():
+    """``/metrics`` (Prometheus text) and ``/v1/stats`` (JSON) of the tiny engine on CPU after a few requests: the
+    runtime's own counters, scheduler counters, KV pages, prefix-cache counters and latency percentiles, published by
+    the owner thread; every line of the text parses as ``name value`` with a TYPE line before it."""
+    import numpy as np
+    import torch
+    from PIL import Image
+
+    from prism_infer_b200 import LLM, SamplingParams
+    from prism_infer_b200.models.architecture import Qwen3VLArch
+    from prism_infer_b200.models.weights import random_weights
+    from prism_infer_b200.serving.app import prometheus_text
+
+    assert prometheus_text({"a-b": 1.0, "c": float("nan")}) == "# TYPE prism_a_b gauge\nprism_a_b 1.0\n# TYPE prism_c gauge\nprism_c NaN\n"
+    weights = random_weights(Qwen3VLArch.tiny(), dtype=torch.float32, seed=0)
+    rt = ServingRuntime(lambda: LLM("random:tiny", weights=weights, device="cpu", max_model_len=256, kvcache_block_size=16,
+                                    num_kvcache_blocks=64, enforce_eager=True, max_num_batched_tokens=256, max_chunk_size=256,
+                                    max_num_seqs=4), stats_period_s=0.0)
+    rt.start()
+    try:
+        sp = SamplingParams(temperature=0.0, max_tokens=4, ignore_eos=True)
+        image = Image.fromarray(np.random.default_rng(1).integers(0, 256, (64, 64, 3), dtype=np.uint8))
+        for i in range(2):  # the second image request hits the multimodal prefix cache
+            assert _drain(rt.submit(GenerationRequest(f"i{i}", f"{30 + i} 31", Modality.IMAGE, image, sp)), 60.0)[-1].kind is EventKind.DONE
+        assert _drain(rt.submit(GenerationRequest("t", "7 8 9", Modality.TEXT, None, sp)), 60.0)[-1].kind is EventKind.DONE
+        h = rt.submit(GenerationRequest("c", "7 8 9", Modality.TEXT, None, SamplingParams(temperature=0.0, max_tokens=200, ignore_eos=True)))
+        assert h.next_event_blocking(30.0).kind is EventKind.ACCEPTED
+        rt.cancel("c")
+        assert _drain(h, 60.0)[-1].finish_reason == "cancelled"
+        time.sleep(0.05)  # one more pass of the owner thread publishes the final numbers
+
+        async def scrape():
+            async with httpx.AsyncClient(transport=httpx.ASGITransport(app=create_app(rt, manage_runtime=False)), base_url="http://t") as c:
+                return (await c.get("/metrics")), (await c.get("/v1/stats"))
+
+        text, js = asyncio.run(scrape())
+        assert text.status_code == 200 and text.headers["content-type"].startswith("text/plain")
+        lines = text.text.strip().split("\n")
+        parsed = {}
+        for type_line, value_line in zip(lines[0::2], lines[1::2]):
+            name, value = value_line.split(" ")
+            assert type_line == f"# TYPE {name} gauge" and name.startswith("prism_")
+            parsed[name[len("prism_"):]] = float(value)
+        stats = js.json()
+        assert parsed.keys() == stats.keys()
+        assert stats["healthy"] == 1.0 and stats["restarts"] == 0.0 and stats["runtime_open_requests"] == 0.0
+        assert stats["runtime_accepted"] == 4.0 and stats["runtime_finished"] == 3.0 and stats["runtime_cancelled"] == 1.0
+        assert stats["runtime_tokens"] >= 12.0 and stats["runtime_steps"] >= 6.0
+        assert stats["engine_scheduler_admitted"] == 4.0 and stats["engine_scheduler_finished"] == 3.0 and stats["engine_scheduler_cancelled"] == 1.0
+        assert stats["engine_kv_pages_total"] == 64.0 and 0.0 < stats["engine_kv_pages_used"] < 64.0  # the cached image prefix stays resident
+        assert stats["engine_prefix_cache_hits"] == 1.0 and stats["engine_prefix_cache_entries"] >= 1.0
+        assert stats["engine_latency_window_requests"] == 4.0
+        assert 0.0 < stats["engine_ttft_ms_p50"] <= stats["engine_ttft_ms_p99"] and stats["engine_tpot_ms_p50"] > 0.0
+    finally:
+        rt.stop()
+
+
 def test_prism_serve_process_answers_over_tcp(tmp_path):
     """The console entry as a user starts it: a child process (``python -m prism_infer_b200.serving.cli``) with an engine
     configuration file, the tiny model on CPU, a real socket; health, one generation, then a clean shutdown on SIGTERM."""
