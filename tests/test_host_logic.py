@@ -689,3 +689,30 @@ def test_checkpoint_processor_files_set_pixel_budgets_and_video_sampling(tmp_pat
     assert (p.min_pixels, p.max_pixels, p.video_fps, p.video_min_frames, p.video_max_frames) == (3136, 1003520, 2.0, 4, 768)
     (tmp_path / "preprocessor_config.json").write_text(json.dumps({"size": {"shortest_edge": 65536, "longest_edge": "many"}}))
     assert "max_pixels" not in checkpoint_pixel_budgets(str(tmp_path))  # a value that is not a number is ignored, not guessed
+
+
+def test_shipped_configurations_and_a_configuration_written_for_the_reference_load():
+    """Every file under ``configs/`` is a valid ``--engine-config``; and the option set of the reference's two-GPU graph
+    configuration (``configs/tp2_graph.json`` there: its compile-and-graph backend and the switches of its fused
+    kernels) loads unchanged, selects the graph backend here and changes nothing else."""
+    import glob
+    import os
+
+    from prism_infer_b200.config import PrismConfig
+    from prism_infer_b200.serving.cli import load_engine_options
+
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    files = sorted(glob.glob(os.path.join(root, "configs", "*.json")))
+    assert {os.path.basename(f) for f in files} >= {"tp2_graph.json", "tp8_graph.json"}
+    for f in files:
+        cfg = PrismConfig.from_flat_options("random:tiny", load_engine_options(f))
+        assert cfg.execution.uses_graphs, f
+    theirs = {"execution_backend": "compile_graph", "decode_compile_region": "attention", "decode_compile_mode": "default",
+              "tensor_parallel_size": 2, "max_model_len": 1280, "max_num_batched_tokens": 2048, "max_num_seqs": 8,
+              "gpu_memory_utilization": 0.9, "num_kvcache_blocks": 64, "enable_prefix_caching": True, "logits_precision": "model",
+              "mlp_projection_mode": "packed", "paged_decode_block_n": 256, "enable_fused_qk_rmsnorm": True,
+              "enable_fused_qk_mrope": True, "enable_fused_add_rmsnorm": True, "enable_packed_kv_projection": True}
+    cfg = PrismConfig.from_flat_options("random:tiny", theirs)
+    ours = PrismConfig.from_flat_options("random:tiny", load_engine_options(os.path.join(root, "configs", "tp2_graph.json")))
+    assert cfg.execution.uses_graphs and cfg.scheduler == ours.scheduler and cfg.cache == ours.cache
+    assert cfg.model.tensor_parallel_size == ours.model.tensor_parallel_size == 2
