@@ -15,7 +15,7 @@ from prism_infer_b200.engine.contracts import Phase, RequestOutput, StepResult
 from prism_infer_b200.engine.request import RequestState
 from prism_infer_b200.sampling_params import SamplingParams
 from prism_infer_b200.serving import (DuplicateRequest, EventKind, GenerationRequest, IngressFull, Modality,
-                                      ServingRuntime)
+                                      RuntimeUnavailable, ServingRuntime)
 from prism_infer_b200.serving.app import create_app
 from prism_infer_b200.serving.cli import load_engine_options
 
@@ -373,6 +373,28 @@ def test_http_server_with_the_real_engine_on_cpu():
         assert rt.is_healthy
     finally:
         rt.stop()
+
+
+def test_a_rebuild_that_fails_ends_the_runtime():
+    """The device no longer answers, say: the factory raises on the rebuild.  Open requests get the error and the
+    runtime turns unhealthy, as without restarts."""
+    built = []
+
+    def factory():
+        if built:
+            raise RuntimeError("no device")
+        built.append(FakeEngine(fail_after=2))
+        return built[-1]
+
+    rt = ServingRuntime(factory, max_restarts=3)
+    rt.start()
+    events = _drain(rt.submit(_req("z", max_tokens=50)))
+    assert events[-1].kind is EventKind.ERROR and "no device" in events[-1].error
+    time.sleep(0.05)
+    assert not rt.is_healthy and "no device" in str(rt.failure) and len(rt.restarts) == 1 and built[0].exited
+    with pytest.raises(RuntimeUnavailable):
+        rt.submit(_req("late"))
+    rt.stop()
 
 
 def test_restart_with_the_real_engine_reproduces_the_stream():
