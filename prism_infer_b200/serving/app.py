@@ -1,5 +1,6 @@
 """FastAPI application: ``GET /health``, ``POST /v1/generate`` (JSON or SSE) and, beyond the reference, ``GET /metrics``
-(Prometheus text) and ``GET /v1/stats`` (the same numbers as JSON).
+(Prometheus text), ``GET /v1/stats`` (the same numbers as JSON) and the OpenAI-style ``POST /v1/chat/completions`` /
+``GET /v1/models`` of ``openai_api.py``.
 
 Same wire contract as the reference (``prism_infer/serving/app.py:36-267``): strict
 pydantic bodies (unknown fields rejected), media as ``data:image/...;base64`` URLs or path
@@ -138,7 +139,7 @@ def prometheus_text(stats: dict[str, float]) -> str:
     return "\n".join(lines) + "\n"
 
 
-def create_app(runtime: ServingRuntime, *, manage_runtime: bool = True) -> FastAPI:
+def create_app(runtime: ServingRuntime, *, manage_runtime: bool = True, model_name: str = "prism") -> FastAPI:
     @asynccontextmanager
     async def lifespan(_: FastAPI) -> AsyncIterator[None]:
         if manage_runtime:
@@ -169,6 +170,10 @@ def create_app(runtime: ServingRuntime, *, manage_runtime: bool = True) -> FastA
     @app.get("/v1/stats")
     async def stats() -> JSONResponse:
         return JSONResponse(runtime.stats())
+
+    from .openai_api import build_router
+
+    app.include_router(build_router(runtime, model_name, decode_media, _load))  # /v1/chat/completions, /v1/models
 
     @app.post("/v1/generate")
     async def generate(body: GenerateBody, request: Request):

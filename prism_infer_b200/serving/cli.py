@@ -11,6 +11,7 @@ from __future__ import annotations
 
 import argparse
 import json
+import os
 from pathlib import Path
 
 PROTECTED = {"model", "metrics_sink", "clock_ns", "request_id_allocator", "runner_group", "weights"}
@@ -55,7 +56,7 @@ def main(argv: list[str] | None = None) -> int:
 
     runtime = ServingRuntime(lambda: LLM(args.model, **options), ingress_capacity=args.ingress_capacity,
                              max_restarts=args.max_restarts)
-    uvicorn.run(create_app(runtime), host=args.host, port=args.port, log_level=args.log_level, workers=1)
+    uvicorn.run(create_app(runtime, model_name=os.path.basename(os.path.normpath(args.model)) or args.model), host=args.host, port=args.port, log_level=args.log_level, workers=1)
     return 0
 
 

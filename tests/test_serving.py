@@ -302,6 +302,62 @@ def test_http_app_json_sse_and_status_codes():
     asyncio.run(down())
 
 
+def test_openai_style_chat_completions():
+    """``/v1/chat/completions`` and ``/v1/models`` over the fake engine: a plain answer, a streamed one ending with
+    ``[DONE]``, a user turn with text and image parts (one image -> single-image request, two -> multi-image), a system
+    message put before the user's text, fields a client adds being ignored, and 400 for conversations of several turns
+    and for unknown part types."""
+    eng = FakeEngine()
+    seen = []
+    inner = eng._add
+
+    def spy(prompt, sp, media=None, raise_on_reject=True):
+        seen.append((prompt, sp.max_tokens, sp.temperature))
+        return inner(prompt, sp, media, raise_on_reject)
+
+    eng._add = spy
+    rt = ServingRuntime(lambda: eng, ingress_capacity=8)
+    rt.start()
+    app = create_app(rt, manage_runtime=False, model_name="tiny-vl")
+    url = _png_data_url()
+
+    async def scenario():
+        async with httpx.AsyncClient(transport=httpx.ASGITransport(app=app), base_url="http://t") as c:
+            assert (await c.get("/v1/models")).json()["data"][0]["id"] == "tiny-vl"
+            r = await c.post("/v1/chat/completions", json={"model": "m", "messages": [{"role": "user", "content": "hi"}], "max_tokens": 3,
+                                                          "top_p": 0.9, "user": "someone"})
+            body = r.json()
+            assert r.status_code == 200 and body["object"] == "chat.completion" and body["model"] == "m" and body["id"].startswith("chatcmpl-")
+            assert body["choices"] == [{"index": 0, "message": {"role": "assistant", "content": "t101 t102 t103"}, "finish_reason": "length"}]
+            assert body["usage"] == {"completion_tokens": 3} and seen[-1] == ("hi", 3, 0.0)
+            async with c.stream("POST", "/v1/chat/completions", json={"messages": [{"role": "system", "content": "Be brief."},
+                                {"role": "user", "content": "hi"}], "max_completion_tokens": 2, "stream": True}) as resp:
+                frames = [f[len("data: "):] for f in (await resp.aread()).decode().split("\n\n") if f]
+            assert frames[-1] == "[DONE]" and seen[-1] == ("Be brief.\n\nhi", 2, 0.0)
+            chunks = [json.loads(f) for f in frames[:-1]]
+            assert all(ch["object"] == "chat.completion.chunk" and ch["model"] == "tiny-vl" for ch in chunks)
+            assert [ch["choices"][0]["delta"] for ch in chunks] == [{"role": "assistant", "content": ""}, {"content": "t101"}, {"content": "t102"}, {}]
+            assert [ch["choices"][0]["finish_reason"] for ch in chunks] == [None, None, None, "length"]
+            one = {"role": "user", "content": [{"type": "text", "text": "what is this?"}, {"type": "image_url", "image_url": {"url": url}}]}
+            assert (await c.post("/v1/chat/completions", json={"messages": [one], "max_tokens": 1})).status_code == 200
+            assert eng.media_seen[-1][0] == "image" and seen[-1][0] == "what is this?"
+            two = {"role": "user", "content": [{"type": "image_url", "image_url": {"url": url}}, {"type": "image_url", "image_url": url},
+                                               {"type": "text", "text": "compare"}]}
+            assert (await c.post("/v1/chat/completions", json={"messages": [two], "max_tokens": 1})).status_code == 200
+            assert eng.media_seen[-1] == ("images", 2)
+            turns = [{"role": "user", "content": "a"}, {"role": "assistant", "content": "b"}, {"role": "user", "content": "c"}]
+            r = await c.post("/v1/chat/completions", json={"messages": turns})
+            assert r.status_code == 400 and "several turns" in r.json()["detail"]
+            bad = {"role": "user", "content": [{"type": "input_audio", "input_audio": {}}]}
+            assert (await c.post("/v1/chat/completions", json={"messages": [bad]})).status_code == 400
+            assert (await c.post("/v1/chat/completions", json={"messages": []})).status_code == 422
+
+    try:
+        asyncio.run(scenario())
+    finally:
+        rt.stop()
+
+
 def test_cli_engine_config(tmp_path):
     p = tmp_path / "cfg.json"
     p.write_text(json.dumps({"tensor_parallel_size": 2, "max_model_len": 512}))
