@@ -606,6 +606,19 @@ def test_prism_serve_process_answers_over_tcp(tmp_path):
         with urllib.request.urlopen(req, timeout=60) as r:
             out = json.loads(r.read())
         assert out["event"] == "done" and len(out["token_ids"]) == 4 and out["finish_reason"] == "length"
+        # the same server through its other doors: the chat protocol, the model list, the metrics
+        body = json.dumps({"messages": [{"role": "user", "content": "7 8 9"}], "max_tokens": 4}).encode()
+        req = urllib.request.Request(f"http://127.0.0.1:{port}/v1/chat/completions", data=body, headers={"Content-Type": "application/json"})
+        with urllib.request.urlopen(req, timeout=60) as r:
+            chat = json.loads(r.read())
+        assert chat["object"] == "chat.completion" and chat["choices"][0]["message"]["role"] == "assistant"
+        assert 1 <= chat["usage"]["completion_tokens"] <= 4 and chat["choices"][0]["finish_reason"] in ("stop", "length")
+        with urllib.request.urlopen(f"http://127.0.0.1:{port}/v1/models", timeout=10) as r:
+            assert json.loads(r.read())["data"][0]["id"] == "random:tiny"
+        time.sleep(1.2)  # the owner thread publishes its numbers once a second
+        with urllib.request.urlopen(f"http://127.0.0.1:{port}/metrics", timeout=10) as r:
+            text = r.read().decode()
+        assert "prism_runtime_accepted 2.0" in text and "prism_healthy 1.0" in text and "prism_engine_kv_pages_total 16.0" in text
     finally:
         proc.send_signal(signal.SIGTERM)  # this exact child; uvicorn turns the signal into a lifespan shutdown
         try:
