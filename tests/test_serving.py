@@ -431,6 +431,39 @@ def test_http_server_with_the_real_engine_on_cpu():
         rt.stop()
 
 
+@pytest.mark.parametrize("seed", range(6))
+def test_repeated_restarts_at_random_steps_never_repeat_or_lose_a_token(seed):
+    """Several engines in a row fail at random steps while requests of random lengths arrive at random times; every
+    stream is exactly 101, 102, ... up to its length, once, whatever was in flight at each failure."""
+    import random
+
+    rnd = random.Random(seed)
+    fail_steps = [rnd.randint(1, 12) for _ in range(4)]
+    built = []
+
+    def factory():
+        built.append(FakeEngine(fail_after=fail_steps[len(built)] if len(built) < len(fail_steps) else None, step_delay=0.001))
+        return built[-1]
+
+    rt = ServingRuntime(factory, max_restarts=len(fail_steps))
+    rt.start()
+    try:
+        lengths = [rnd.randint(1, 30) for _ in range(8)]
+        handles = []
+        for i, n in enumerate(lengths):
+            handles.append(rt.submit(_req(f"r{i}", max_tokens=n)))
+            time.sleep(rnd.choice([0.0, 0.002, 0.01]))
+        for n, h in zip(lengths, handles):
+            events = _drain(h, 30.0)
+            assert [e.kind for e in events].count(EventKind.ACCEPTED) == 1
+            assert [e.token_id for e in events if e.kind is EventKind.TOKEN] == list(range(101, 101 + n))
+            assert events[-1].kind is EventKind.DONE and events[-1].token_ids == tuple(range(101, 101 + n))
+        assert rt.is_healthy and len(rt.restarts) == len(built) - 1 <= len(fail_steps)
+        assert rt.counters["accepted"] == 8 and rt.counters["finished"] == 8 and rt.counters["tokens"] == sum(lengths)
+    finally:
+        rt.stop()
+
+
 def test_a_rebuild_that_fails_ends_the_runtime():
     """The device no longer answers, say: the factory raises on the rebuild.  Open requests get the error and the
     runtime turns unhealthy, as without restarts."""
