@@ -539,6 +539,12 @@ class LLMEngine:
         self._sequences.pop(request_id, None)
         return ok
 
+    def prompt_token_count(self, request_id: int) -> int | None:
+        """Length of an open request's prompt as the model sees it (media placeholders expanded); ``None`` once the
+        request is gone."""
+        seq = self._sequences.get(request_id) or self.scheduler.find(request_id)
+        return int(seq.num_prompt_tokens) if seq is not None else None
+
     def request_state(self, request_id: int) -> RequestState | None:
         seq = self._sequences.get(request_id) or self.scheduler.find(request_id)
         return seq.state if seq is not None else None

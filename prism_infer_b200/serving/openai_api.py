@@ -160,7 +160,9 @@ def build_router(runtime: ServingRuntime, model_name: str, decode_media, load_me
             raise HTTPException(status_code=400, detail=event.error)
         choice = {"index": 0, "message": {"role": "assistant", "content": event.text or ""},
                   "finish_reason": FINISH.get(event.finish_reason or "", event.finish_reason)}
-        return JSONResponse(_envelope(rid, model, created, "chat.completion", choice,
-                                      usage={"completion_tokens": len(event.token_ids)}))
+        usage = {"completion_tokens": len(event.token_ids)}
+        if event.prompt_tokens is not None:
+            usage.update(prompt_tokens=event.prompt_tokens, total_tokens=event.prompt_tokens + len(event.token_ids))
+        return JSONResponse(_envelope(rid, model, created, "chat.completion", choice, usage=usage))
 
     return router

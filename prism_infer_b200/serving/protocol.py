@@ -65,10 +65,11 @@ class ServingEvent:
     text: str | None = None
     finish_reason: str | None = None
     error: str | None = None
+    prompt_tokens: int | None = None  # DONE only, when the engine can tell: the prompt's length after expansion of the media
 
     def to_dict(self) -> dict[str, object]:
         out: dict[str, object] = {"request_id": self.request_id, "event": self.kind.value}
-        for name in ("engine_request_id", "token_id", "token_text", "text", "finish_reason", "error"):
+        for name in ("engine_request_id", "token_id", "token_text", "text", "finish_reason", "error", "prompt_tokens"):
             value = getattr(self, name)
             if value is not None:
                 out[name] = value

@@ -81,6 +81,7 @@ class _Live:
     handle: RequestHandle
     engine_id: int | None = None
     token_ids: list[int] = field(default_factory=list)
+    prompt_tokens: int | None = None
     replayed: int = 0  # after an engine restart: how many of the tokens already delivered the new engine has produced again
 
 
@@ -207,6 +208,8 @@ class ServingRuntime:
             self._finish(live, ServingEvent(req.request_id, EventKind.ERROR, error=f"{type(exc).__name__}: {exc}"))
             return
         live.engine_id = eid
+        count = getattr(eng, "prompt_token_count", None)
+        live.prompt_tokens = count(eid) if count is not None else None
         self._live[req.request_id] = live
         self._by_engine[eid] = live
         if not replay:
@@ -232,7 +235,7 @@ class ServingRuntime:
     def _done(self, live: _Live, reason: str) -> ServingEvent:
         text = self.engine.tokenizer.decode(live.token_ids) if live.token_ids else ""  # type: ignore[union-attr]
         return ServingEvent(live.request.request_id, EventKind.DONE, engine_request_id=live.engine_id,
-                            token_ids=tuple(live.token_ids), text=text, finish_reason=reason)
+                            token_ids=tuple(live.token_ids), text=text, finish_reason=reason, prompt_tokens=live.prompt_tokens)
 
     def _drain_ingress(self) -> None:
         while True:

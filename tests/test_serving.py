@@ -646,6 +646,8 @@ def test_prism_serve_process_answers_over_tcp(tmp_path):
             chat = json.loads(r.read())
         assert chat["object"] == "chat.completion" and chat["choices"][0]["message"]["role"] == "assistant"
         assert 1 <= chat["usage"]["completion_tokens"] <= 4 and chat["choices"][0]["finish_reason"] in ("stop", "length")
+        assert chat["usage"]["prompt_tokens"] == out["prompt_tokens"] >= 3  # the same prompt through both doors
+        assert chat["usage"]["total_tokens"] == chat["usage"]["prompt_tokens"] + chat["usage"]["completion_tokens"]
         with urllib.request.urlopen(f"http://127.0.0.1:{port}/v1/models", timeout=10) as r:
             assert json.loads(r.read())["data"][0]["id"] == "random:tiny"
         time.sleep(1.2)  # the owner thread publishes its numbers once a second
