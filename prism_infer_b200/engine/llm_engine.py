@@ -539,6 +539,19 @@ class LLMEngine:
         self._sequences.pop(request_id, None)
         return ok
 
+    def set_first_token_deadline(self, request_id: int, ttft_slo_ms: float) -> bool:
+        """Give an open request a time-to-first-token target, counted from its arrival.  The SLO-aware scheduler policy
+        orders the waiting queue by these deadlines and the cooperative prefill yields to them; under the other policies
+        the value is recorded and changes nothing.  Call it right after the request was added, before the next step.
+        False when the request is unknown."""
+        if not (float(ttft_slo_ms) > 0.0) or float(ttft_slo_ms) == float("inf"):
+            raise ValueError("ttft_slo_ms must be a finite positive number")
+        seq = self._sequences.get(request_id) or self.scheduler.find(request_id)
+        if seq is None:
+            return False
+        seq.deadline_ns = int(seq.arrival_ns or time.perf_counter_ns()) + int(float(ttft_slo_ms) * 1e6)
+        return True
+
     def prompt_token_count(self, request_id: int) -> int | None:
         """Length of an open request's prompt as the model sees it (media placeholders expanded); ``None`` once the
         request is gone."""

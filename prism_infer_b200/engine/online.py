@@ -256,6 +256,8 @@ class OnlineServingSession:
         if kind == "text":
             seq_kwargs = dict(raise_on_reject=False)
             rid = eng.add_request(req.payload["prompt"], req.sampling_params, **seq_kwargs)
+            if req.ttft_slo_ms is not None:
+                eng.set_first_token_deadline(rid, req.ttft_slo_ms)  # counted from the engine's own arrival stamp
         else:
             inputs, key = prepared
             seq = eng._multimodal_sequence(inputs, req.sampling_params, media_key=key)

@@ -44,6 +44,7 @@ class GenerateBody(BaseModel):
     media: str | list[str] | None = None
     sampling: SamplingBody = Field(default_factory=SamplingBody)
     stream: bool = False
+    ttft_slo_ms: Annotated[float, Field(gt=0.0, allow_inf_nan=False)] | None = None  # beyond the reference: see GenerationRequest
 
     @model_validator(mode="after")
     def _check_media(self) -> "GenerateBody":
@@ -86,7 +87,7 @@ def to_generation_request(body: GenerateBody) -> GenerationRequest:
     return GenerationRequest(
         request_id=body.request_id or uuid.uuid4().hex, prompt=body.prompt, modality=Modality(body.modality), media=media,
         sampling_params=SamplingParams(temperature=body.sampling.temperature, max_tokens=body.sampling.max_tokens,
-                                       ignore_eos=body.sampling.ignore_eos))
+                                       ignore_eos=body.sampling.ignore_eos), ttft_slo_ms=body.ttft_slo_ms)
 
 
 def _load(obj):

@@ -31,6 +31,7 @@ class GenerationRequest:
     modality: Modality
     media: Any | tuple[Any, ...] | None
     sampling_params: SamplingParams
+    ttft_slo_ms: float | None = None  # time-to-first-token target from arrival; used by the SLO-aware scheduler policy
 
     def __post_init__(self) -> None:
         for broken, error in _REQUEST_RULES:
@@ -51,6 +52,8 @@ _REQUEST_RULES = (
     (lambda r: r.modality is Modality.TEXT and r.media is not None, (ValueError, "text requests must not include media")),
     (lambda r: r.modality is not Modality.TEXT and r.media is None, (ValueError, "{modality} requests require media")),
     (lambda r: isinstance(r.media, tuple) and len(r.media) == 0, (ValueError, "media tuples must not be empty")),
+    (lambda r: r.ttft_slo_ms is not None and not (0.0 < float(r.ttft_slo_ms) < float("inf")),
+     (ValueError, "ttft_slo_ms must be a finite positive number")),
 )
 
 

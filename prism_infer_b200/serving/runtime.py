@@ -208,6 +208,8 @@ class ServingRuntime:
             self._finish(live, ServingEvent(req.request_id, EventKind.ERROR, error=f"{type(exc).__name__}: {exc}"))
             return
         live.engine_id = eid
+        if req.ttft_slo_ms is not None and hasattr(eng, "set_first_token_deadline"):
+            eng.set_first_token_deadline(eid, req.ttft_slo_ms)
         count = getattr(eng, "prompt_token_count", None)
         live.prompt_tokens = count(eid) if count is not None else None
         self._live[req.request_id] = live

@@ -358,6 +358,58 @@ def test_openai_style_chat_completions():
         rt.stop()
 
 
+def test_first_token_target_reaches_the_engine():
+    """``ttft_slo_ms`` of ``/v1/generate`` becomes the request's deadline in the engine (arrival + target), which the
+    SLO-aware scheduler policy orders by; nonsense values are refused by the schema and by the request type."""
+    import torch
+
+    from prism_infer_b200 import LLM
+    from prism_infer_b200.models.architecture import Qwen3VLArch
+    from prism_infer_b200.models.weights import random_weights
+
+    weights = random_weights(Qwen3VLArch.tiny(), dtype=torch.float32, seed=0)
+    seen = {}
+
+    def make():
+        eng = LLM("random:tiny", weights=weights, device="cpu", max_model_len=128, kvcache_block_size=16, num_kvcache_blocks=32,
+                  enforce_eager=True, scheduler_policy="slo_aware")
+        inner = eng.set_first_token_deadline
+
+        def spy(rid, ms):
+            ok = inner(rid, ms)
+            if ok:
+                seq = eng._sequences[rid]
+                seen[rid] = (ms, seq.deadline_ns - seq.arrival_ns)
+            return ok
+
+        eng.set_first_token_deadline = spy
+        return eng
+
+    rt = ServingRuntime(make)
+    rt.start()
+    app = create_app(rt, manage_runtime=False)
+
+    async def scenario():
+        async with httpx.AsyncClient(transport=httpx.ASGITransport(app=app), base_url="http://t", timeout=60.0) as c:
+            body = {"prompt": "7 8 9", "sampling": {"max_tokens": 2, "ignore_eos": True}}
+            r = await c.post("/v1/generate", json={**body, "ttft_slo_ms": 250})
+            assert r.status_code == 200 and len(r.json()["token_ids"]) == 2
+            assert (await c.post("/v1/generate", json=body)).status_code == 200  # no target: the engine is not asked
+            for bad in (0, -5, "soon"):
+                assert (await c.post("/v1/generate", json={**body, "ttft_slo_ms": bad})).status_code == 422
+
+    try:
+        asyncio.run(scenario())
+        assert list(seen.values()) == [(250.0, 250_000_000)]
+        assert rt.engine.set_first_token_deadline(10_000, 5.0) is False
+        with pytest.raises(ValueError):
+            GenerationRequest("x", "hi", Modality.TEXT, None, SamplingParams(), ttft_slo_ms=float("inf"))
+        with pytest.raises(ValueError):
+            rt.engine.set_first_token_deadline(0, float("nan"))
+    finally:
+        rt.stop()
+
+
 def test_cli_engine_config(tmp_path):
     p = tmp_path / "cfg.json"
     p.write_text(json.dumps({"tensor_parallel_size": 2, "max_model_len": 512}))
