@@ -176,13 +176,22 @@ def create_app(runtime: ServingRuntime, *, manage_runtime: bool = True, model_na
 
     app.include_router(build_router(runtime, model_name, decode_media, _load))  # /v1/chat/completions, /v1/models
 
+    @app.delete("/v1/requests/{request_id}")
+    async def cancel(request_id: str) -> JSONResponse:
+        """Cancel an open request by the id it was submitted with (beyond the reference, where only a disconnect
+        cancels).  The request's own answer or stream ends with ``finish_reason: "cancelled"``."""
+        if not runtime.is_open(request_id):
+            raise HTTPException(status_code=404, detail=f"no open request {request_id!r}")
+        runtime.cancel(request_id)
+        return JSONResponse({"request_id": request_id, "status": "cancelling"}, status_code=202)
+
     @app.post("/v1/generate")
     async def generate(body: GenerateBody, request: Request):
         try:
             gen = to_generation_request(body)
             handle = runtime.submit(gen, asyncio.get_running_loop())
         except IngressFull as exc:
-            raise HTTPException(status_code=429, detail=str(exc)) from exc
+            raise HTTPException(status_code=429, detail=str(exc), headers={"Retry-After": "1"}) from exc
         except RuntimeUnavailable as exc:
             raise HTTPException(status_code=503, detail=str(exc)) from exc
         except DuplicateRequest as exc:

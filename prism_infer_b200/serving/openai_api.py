@@ -102,7 +102,7 @@ def build_router(runtime: ServingRuntime, model_name: str, decode_media, load_me
             gen = to_generation_request(body, decode_media, load_media)
             handle = runtime.submit(gen, asyncio.get_running_loop())
         except IngressFull as exc:
-            raise HTTPException(status_code=429, detail=str(exc)) from exc
+            raise HTTPException(status_code=429, detail=str(exc), headers={"Retry-After": "1"}) from exc
         except RuntimeUnavailable as exc:
             raise HTTPException(status_code=503, detail=str(exc)) from exc
         except DuplicateRequest as exc:

@@ -99,6 +99,7 @@ class ServingRuntime:
         self.restarts: list[str] = []  # one line per restart: the failure that caused it
         self._ingress: "queue.Queue[_Live]" = queue.Queue(maxsize=ingress_capacity)
         self._cancel: "queue.Queue[str]" = queue.Queue()
+        self._cancel_early: set[str] = set()  # owner thread only
         self._live: dict[str, _Live] = {}
         self._by_engine: dict[int, _Live] = {}
         self._ids: set[str] = set()
@@ -177,6 +178,11 @@ class ServingRuntime:
     def cancel(self, request_id: str) -> None:
         self._cancel.put(request_id)
 
+    def is_open(self, request_id: str) -> bool:
+        """Submitted and not finished yet (queued for admission or running)."""
+        with self._ids_lock:
+            return request_id in self._ids
+
     # ---------------------------------------------------------------- engine thread
     def _finish(self, live: _Live, event: ServingEvent) -> None:
         self.counters["errors" if event.kind is EventKind.ERROR else
@@ -192,6 +198,10 @@ class ServingRuntime:
     def _admit(self, live: _Live, *, replay: bool = False) -> None:
         eng, req = self.engine, live.request
         assert eng is not None
+        if req.request_id in self._cancel_early:  # cancelled while it waited for admission: never reaches the engine
+            self._cancel_early.discard(req.request_id)
+            self._finish(live, ServingEvent(req.request_id, EventKind.DONE, text="", finish_reason="cancelled"))
+            return
         try:
             if req.modality is Modality.TEXT:
                 eid = eng.add_request(req.prompt, req.sampling_params, raise_on_reject=False)
@@ -230,6 +240,8 @@ class ServingRuntime:
                 return
             live = self._live.get(rid)
             if live is None or live.engine_id is None:
+                if self.is_open(rid):
+                    self._cancel_early.add(rid)  # still in the ingress queue: cancelled when it is taken out
                 continue
             self.engine.cancel_request(live.engine_id)  # type: ignore[union-attr]
             self._finish(live, self._done(live, "cancelled"))

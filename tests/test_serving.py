@@ -410,6 +410,54 @@ def test_first_token_target_reaches_the_engine():
         rt.stop()
 
 
+def test_cancel_endpoint_and_cancellation_before_admission():
+    """``DELETE /v1/requests/{id}`` ends an open request with ``cancelled`` (404 for an unknown id), and a cancellation
+    that overtakes its request in the ingress queue still takes effect when the request is taken out."""
+    eng = FakeEngine(step_delay=0.005)
+    rt = ServingRuntime(lambda: eng, ingress_capacity=8)
+    rt.start()
+    app = create_app(rt, manage_runtime=False)
+
+    async def scenario():
+        async with httpx.AsyncClient(transport=httpx.ASGITransport(app=app), base_url="http://t", timeout=30.0) as c:
+            assert (await c.delete("/v1/requests/nobody")).status_code == 404
+            pending = asyncio.ensure_future(c.post("/v1/generate", json={"request_id": "long", "prompt": "hi", "sampling": {"max_tokens": 100000}}))
+            while not rt.is_open("long"):
+                await asyncio.sleep(0.01)
+            r = await c.delete("/v1/requests/long")
+            assert r.status_code == 202 and r.json() == {"request_id": "long", "status": "cancelling"}
+            answer = await pending
+            assert answer.status_code == 200 and answer.json()["finish_reason"] == "cancelled"
+            assert not rt.is_open("long") and (await c.delete("/v1/requests/long")).status_code == 404
+
+    try:
+        asyncio.run(scenario())
+    finally:
+        rt.stop()
+
+    # the cancellation is consumed before the request is admitted: the owner thread remembers it
+    gate = threading.Event()
+
+    class Gated(FakeEngine):
+        def is_finished(self):
+            gate.wait(5.0)
+            return super().is_finished()
+
+    eng2 = Gated()
+    rt2 = ServingRuntime(lambda: eng2, ingress_capacity=8)
+    rt2.start()
+    try:
+        time.sleep(0.05)             # the owner thread now waits inside is_finished, past its cancellation check
+        h = rt2.submit(_req("early", max_tokens=50))
+        rt2.cancel("early")
+        gate.set()
+        events = _drain(h)
+        assert events[-1].finish_reason == "cancelled" and events[-1].token_ids == () and eng2.next_id == 0  # never reached the engine
+    finally:
+        gate.set()
+        rt2.stop()
+
+
 def test_cli_engine_config(tmp_path):
     p = tmp_path / "cfg.json"
     p.write_text(json.dumps({"tensor_parallel_size": 2, "max_model_len": 512}))
