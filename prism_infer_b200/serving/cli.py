@@ -1,7 +1,7 @@
 """``prism-serve`` console entry (reference ``prism_infer/serving/cli.py:43-93``).
 
     prism-serve --model <dir | random:tiny> [--engine-config file.json] [--host H] [--port P]
-                [--ingress-capacity N] [--max-restarts 0] [--log-level info]
+                [--ingress-capacity N] [--max-restarts 0] [--restart-window 0] [--log-level info]
 
 ``--engine-config`` is a JSON object of ``LLM`` keyword options; a single uvicorn worker is
 used because one process owns the GPUs.
@@ -41,6 +41,8 @@ def build_parser() -> argparse.ArgumentParser:
     ap.add_argument("--ingress-capacity", type=int, default=64)
     ap.add_argument("--max-restarts", type=int, default=0,
                     help="after a failed engine step rebuild the engine and run the open greedy requests again, this many times (0: a failure is final)")
+    ap.add_argument("--restart-window", type=float, default=0.0,
+                    help="seconds; only restarts within this window count against --max-restarts (0: all of them do)")
     ap.add_argument("--log-level", default="info")
     return ap
 
@@ -55,7 +57,7 @@ def main(argv: list[str] | None = None) -> int:
     from .runtime import ServingRuntime
 
     runtime = ServingRuntime(lambda: LLM(args.model, **options), ingress_capacity=args.ingress_capacity,
-                             max_restarts=args.max_restarts)
+                             max_restarts=args.max_restarts, restart_window_s=args.restart_window)
     uvicorn.run(create_app(runtime, model_name=os.path.basename(os.path.normpath(args.model)) or args.model), host=args.host, port=args.port, log_level=args.log_level, workers=1)
     return 0
 

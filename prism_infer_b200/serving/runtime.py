@@ -93,9 +93,14 @@ class ServingRuntime:
     also fails the rebuild, which ends the runtime."""
 
     def __init__(self, engine_factory: Callable[[], ServingEngine], *, ingress_capacity: int = 64,
-                 idle_sleep_s: float = 0.001, max_restarts: int = 0, stats_period_s: float = 1.0) -> None:
+                 idle_sleep_s: float = 0.001, max_restarts: int = 0, restart_window_s: float = 0.0,
+                 stats_period_s: float = 1.0) -> None:
         self._factory = engine_factory
         self.max_restarts = int(max_restarts)
+        # 0: the allowance is for the runtime's whole life; otherwise only restarts of the last ``restart_window_s``
+        # seconds count, so a server that runs for weeks survives rare faults but still gives up on a fault that repeats
+        self.restart_window_s = float(restart_window_s)
+        self._restart_times: list[float] = []
         self.restarts: list[str] = []  # one line per restart: the failure that caused it
         self._ingress: "queue.Queue[_Live]" = queue.Queue(maxsize=ingress_capacity)
         self._cancel: "queue.Queue[str]" = queue.Queue()
@@ -187,13 +192,14 @@ class ServingRuntime:
     def _finish(self, live: _Live, event: ServingEvent) -> None:
         self.counters["errors" if event.kind is EventKind.ERROR else
                       "cancelled" if event.finish_reason == "cancelled" else "finished"] += 1
-        live.handle.publish(event)
-        live.handle.closed = True
+        # the books are closed before the final event goes out: a client that sees it may reuse the id at once
         self._live.pop(live.request.request_id, None)
         if live.engine_id is not None:
             self._by_engine.pop(live.engine_id, None)
         with self._ids_lock:
             self._ids.discard(live.request.request_id)
+        live.handle.publish(event)
+        live.handle.closed = True
 
     def _admit(self, live: _Live, *, replay: bool = False) -> None:
         eng, req = self.engine, live.request
@@ -317,8 +323,11 @@ class ServingRuntime:
                         continue
                     result = self.engine.step_result()
                 except Exception as exc:  # a failed step: rebuild and replay while restarts are left
-                    if len(self.restarts) >= self.max_restarts or self._stop.is_set():
+                    now = time.monotonic()
+                    recent = [t for t in self._restart_times if self.restart_window_s <= 0 or now - t < self.restart_window_s]
+                    if len(recent) >= self.max_restarts or self._stop.is_set():
                         raise
+                    self._restart_times = recent + [now]
                     self._restart(exc)
                     continue
                 self.steps += 1

@@ -564,6 +564,30 @@ def test_repeated_restarts_at_random_steps_never_repeat_or_lose_a_token(seed):
         rt.stop()
 
 
+def test_restart_allowance_counts_only_the_recent_window():
+    """``max_restarts=1`` with a window: failures far apart are each survived, two inside one window are not."""
+    plan = [2, 6, 6, 0]  # steps each engine in turn survives
+    built = []
+
+    def factory():
+        built.append(FakeEngine(fail_after=plan[len(built)]))
+        return built[-1]
+
+    rt = ServingRuntime(factory, max_restarts=1, restart_window_s=0.2)
+    rt.start()
+    want = (101, 102, 103, 104)
+    assert _drain(rt.submit(_req("a", max_tokens=4)))[-1].token_ids == want  # engine 1 fails at its step 3, engine 2 runs it again
+    time.sleep(0.3)                                                           # the first restart leaves the window
+    assert _drain(rt.submit(_req("b", max_tokens=4)))[-1].token_ids == want  # engine 2 fails at its step 7, engine 3 runs it again
+    assert rt.is_healthy and len(built) == 3 and len(rt.restarts) == 2
+    time.sleep(0.3)
+    events = _drain(rt.submit(_req("c", max_tokens=50)))  # engine 3 fails at its step 7, engine 4 at once: two in one window
+    assert events[-1].kind is EventKind.ERROR and "boom" in events[-1].error
+    time.sleep(0.05)
+    assert not rt.is_healthy and len(built) == 4 and len(rt.restarts) == 3
+    rt.stop()
+
+
 def test_a_rebuild_that_fails_ends_the_runtime():
     """The device no longer answers, say: the factory raises on the rebuild.  Open requests get the error and the
     runtime turns unhealthy, as without restarts."""
